@@ -1,0 +1,498 @@
+"""Engine configuration: ``EngineArgs`` → ``VllmConfig`` composed of typed sub-configs.
+
+Mirrors the reference's configuration surface at a much smaller scale
+(reference: vllm/engine/arg_utils.py, vllm/config/vllm.py, config/model.py,
+config/cache.py, config/parallel.py, config/scheduler.py, config/speculative.py).
+Each sub-config validates itself in ``__post_init__`` and exposes ``compute_hash``.
+"""
+from __future__ import annotations
+
+import argparse
+import dataclasses
+import hashlib
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Any, Optional, Union
+
+import torch
+
+_DTYPES = {
+    "auto": None, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
+    "half": torch.float16, "fp16": torch.float16, "float32": torch.float32, "float": torch.float32, "fp32": torch.float32,
+}
+
+
+def _hash(obj: Any) -> str:
+    return hashlib.sha256(json.dumps(obj, sort_keys=True, default=str).encode()).hexdigest()[:16]
+
+
+# ----------------------------------------------------------------------------- model
+@dataclass
+class QuantConfig:
+    """Checkpoint quantisation layout (reference: model_executor/layers/quantization/__init__.py:12-45)."""
+
+    method: str = "none"  # none | awq | gptq | fp8 | nvfp4 | mxfp4
+    bits: int = 4
+    group_size: int = 128
+    zero_point: bool = True  # AWQ asymmetric
+    desc_act: bool = False  # GPTQ act-order
+    sym: bool = True  # GPTQ symmetric uint4b8
+    weight_block_size: Optional[tuple[int, int]] = None  # fp8 128x128
+    activation_scheme: str = "dynamic"
+    modules_to_not_convert: list[str] = field(default_factory=lambda: ["lm_head", "embed_tokens"])
+    expert_method: Optional[str] = None  # mixed precision: quant method of routed experts (e.g. mxfp4)
+
+    @classmethod
+    def from_hf(cls, q: Optional[dict]) -> "QuantConfig":
+        if not q:
+            return cls()
+        m = (q.get("quant_method") or q.get("quant_algo") or "none").lower()
+        if m in ("awq", "awq_marlin"):
+            return cls("awq", q.get("bits", q.get("w_bit", 4)), q.get("group_size", q.get("q_group_size", 128)),
+                       q.get("zero_point", True), modules_to_not_convert=q.get("modules_to_not_convert") or ["lm_head", "embed_tokens"])
+        if m in ("gptq", "gptq_marlin", "auto_gptq"):
+            return cls("gptq", q.get("bits", 4), q.get("group_size", 128), zero_point=not q.get("sym", True),
+                       desc_act=q.get("desc_act", False), sym=q.get("sym", True))
+        if m == "fp8":
+            wbs = q.get("weight_block_size")
+            return cls("fp8", 8, 0, False, weight_block_size=tuple(wbs) if wbs else None,
+                       activation_scheme=q.get("activation_scheme", "dynamic"), expert_method=q.get("expert_method"))
+        if m in ("nvfp4", "modelopt_fp4", "modelopt"):
+            return cls("nvfp4", 4, 16, False)
+        if m in ("mxfp4",):
+            return cls("mxfp4", 4, 32, False)
+        raise ValueError(f"unsupported quantization method {m!r}")
+
+
+@dataclass
+class ModelConfig:
+    """Architecture description, normalised from an HF ``config.json`` (or a dict for synthetic models).
+
+    Covers the architectures of the reference's model zoo that this engine serves:
+    dense Llama/Qwen2/Qwen3 (reference: models/llama.py, qwen3.py), Qwen3-Next/Qwen3.5 hybrids with
+    Gated-DeltaNet (models/qwen3_next.py:319-1092), Qwen3-MoE, DeepSeek-V2/V3 MLA+MoE (models/deepseek_v2.py).
+    """
+
+    model: str = "dummy"
+    architecture: str = "LlamaForCausalLM"
+    vocab_size: int = 32000
+    hidden_size: int = 256
+    intermediate_size: int = 688
+    num_hidden_layers: int = 4
+    num_attention_heads: int = 8
+    num_key_value_heads: int = 2
+    head_dim: int = 32
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    partial_rotary_factor: float = 1.0
+    max_position_embeddings: int = 32768
+    tie_word_embeddings: bool = False
+    attention_bias: bool = False
+    qk_norm: bool = False  # per-head RMSNorm on q and k (Qwen3)
+    gemma_norm: bool = False  # weight applied as (1 + w) (Qwen3-Next)
+    attn_output_gate: bool = False  # gated attention: o * sigmoid(gate)
+    # hybrid (Gated-DeltaNet)
+    layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention"
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 48
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_conv_kernel_dim: int = 4
+    # MoE
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    shared_expert_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    scoring_func: str = "softmax"  # softmax | sigmoid
+    n_group: int = 1
+    topk_group: int = 1
+    routed_scaling_factor: float = 1.0
+    first_k_dense_replace: int = 0
+    shared_expert_gate: bool = False  # Qwen: shared output scaled by sigmoid(gate(x))
+    # MLA
+    use_mla: bool = False
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    # MTP draft head
+    num_nextn_predict_layers: int = 0
+    # runtime
+    dtype: torch.dtype = torch.bfloat16
+    max_model_len: int = 4096
+    quant: QuantConfig = field(default_factory=QuantConfig)
+    eos_token_id: Optional[int] = None
+    bos_token_id: Optional[int] = None
+    seed: int = 0
+    load_format: str = "auto"  # auto | safetensors | dummy
+    tokenizer: Optional[str] = None
+    hf_overrides: dict = field(default_factory=dict)
+
+    def __post_init__(self) -> None:
+        if self.num_attention_heads % max(self.num_key_value_heads, 1):
+            raise ValueError("num_attention_heads must be a multiple of num_key_value_heads")
+        if self.layer_types is not None and len(self.layer_types) != self.num_hidden_layers:
+            raise ValueError("layer_types must have one entry per layer")
+        if self.max_model_len <= 0:
+            raise ValueError("max_model_len must be positive")
+
+    # ---- derived
+    @property
+    def is_hybrid(self) -> bool:
+        return bool(self.layer_types) and any(t == "linear_attention" for t in self.layer_types)
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_type(self, i: int) -> str:
+        return self.layer_types[i] if self.layer_types else "full_attention"
+
+    def is_moe_layer(self, i: int) -> bool:
+        return self.is_moe and i >= self.first_k_dense_replace
+
+    @property
+    def rotary_dim(self) -> int:
+        d = self.qk_rope_head_dim if self.use_mla else self.head_dim
+        return int(d * self.partial_rotary_factor) if not self.use_mla else d
+
+    @property
+    def num_attention_layers(self) -> int:
+        return sum(1 for i in range(self.num_hidden_layers) if self.layer_type(i) == "full_attention")
+
+    @property
+    def kv_cache_head_dim(self) -> int:
+        return self.kv_lora_rank + self.qk_rope_head_dim if self.use_mla else self.head_dim
+
+    def compute_hash(self) -> str:
+        d = dataclasses.asdict(self)
+        d["dtype"] = str(self.dtype)
+        return _hash(d)
+
+    @classmethod
+    def from_hf_dict(cls, hf: dict, **over) -> "ModelConfig":
+        """Normalise an HF config dict. Nested ``text_config`` (Qwen3.5) is flattened."""
+        if "text_config" in hf and isinstance(hf["text_config"], dict):
+            inner = dict(hf["text_config"])
+            inner.setdefault("architectures", hf.get("architectures"))
+            inner.setdefault("quantization_config", hf.get("quantization_config"))
+            hf = inner
+        arch = (hf.get("architectures") or ["LlamaForCausalLM"])[0]
+        nh = hf.get("num_attention_heads", 8)
+        hidden = hf.get("hidden_size", 256)
+        kw: dict[str, Any] = dict(
+            architecture=arch, vocab_size=hf.get("vocab_size", 32000), hidden_size=hidden,
+            intermediate_size=hf.get("intermediate_size", 4 * hidden), num_hidden_layers=hf.get("num_hidden_layers", 4),
+            num_attention_heads=nh, num_key_value_heads=hf.get("num_key_value_heads", nh),
+            head_dim=hf.get("head_dim") or hidden // nh, rms_norm_eps=hf.get("rms_norm_eps", 1e-6),
+            rope_theta=(hf.get("rope_parameters") or {}).get("rope_theta", hf.get("rope_theta", 10000.0)),
+            partial_rotary_factor=(hf.get("rope_parameters") or {}).get("partial_rotary_factor", hf.get("partial_rotary_factor", 1.0)),
+            max_position_embeddings=hf.get("max_position_embeddings", 32768),
+            tie_word_embeddings=hf.get("tie_word_embeddings", False), attention_bias=hf.get("attention_bias", False),
+            eos_token_id=hf.get("eos_token_id") if not isinstance(hf.get("eos_token_id"), list) else hf["eos_token_id"][0],
+            bos_token_id=hf.get("bos_token_id"), quant=QuantConfig.from_hf(hf.get("quantization_config")),
+            num_nextn_predict_layers=hf.get("num_nextn_predict_layers", hf.get("mtp_num_hidden_layers", 0)) or 0,
+        )
+        a = arch.lower()
+        if "qwen2" in a and "moe" not in a:
+            kw["attention_bias"] = True
+        if "qwen3" in a:
+            kw["qk_norm"] = True
+        if "qwen3next" in a or "qwen3_5" in a or "qwen3_next" in a:
+            kw.update(gemma_norm=True, attn_output_gate=hf.get("attn_output_gate", True), layer_types=hf.get("layer_types"),
+                      linear_num_key_heads=hf.get("linear_num_key_heads", 16), linear_num_value_heads=hf.get("linear_num_value_heads", 48),
+                      linear_key_head_dim=hf.get("linear_key_head_dim", 128), linear_value_head_dim=hf.get("linear_value_head_dim", 128),
+                      linear_conv_kernel_dim=hf.get("linear_conv_kernel_dim", 4))
+            if kw["layer_types"] is None:
+                iv = hf.get("full_attention_interval", 4)
+                kw["layer_types"] = ["full_attention" if (i + 1) % iv == 0 else "linear_attention" for i in range(kw["num_hidden_layers"])]
+        if hf.get("num_experts") or hf.get("n_routed_experts"):
+            kw.update(num_experts=hf.get("num_experts") or hf.get("n_routed_experts"),
+                      num_experts_per_tok=hf.get("num_experts_per_tok", 8),
+                      moe_intermediate_size=hf.get("moe_intermediate_size", 512),
+                      norm_topk_prob=hf.get("norm_topk_prob", True))
+            if "deepseek" in a:
+                kw.update(shared_expert_intermediate_size=hf.get("n_shared_experts", 1) * hf.get("moe_intermediate_size", 2048),
+                          scoring_func=hf.get("scoring_func", "sigmoid"), n_group=hf.get("n_group", 8), topk_group=hf.get("topk_group", 4),
+                          routed_scaling_factor=hf.get("routed_scaling_factor", 2.5), first_k_dense_replace=hf.get("first_k_dense_replace", 3))
+            else:
+                kw.update(shared_expert_intermediate_size=hf.get("shared_expert_intermediate_size", 0),
+                          shared_expert_gate=bool(hf.get("shared_expert_intermediate_size", 0)))
+        if "deepseek" in a and hf.get("kv_lora_rank"):
+            kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
+                      qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
+                      v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
+        kw.update(over)
+        return cls(**kw)
+
+    @classmethod
+    def from_pretrained(cls, path: str, **over) -> "ModelConfig":
+        with open(os.path.join(path, "config.json")) as f:
+            hf = json.load(f)
+        return cls.from_hf_dict(hf, model=path, **over)
+
+
+# ----------------------------------------------------------------------------- cache / parallel / scheduler
+@dataclass
+class CacheConfig:
+    """Paged KV cache (reference: vllm/config/cache.py). Block size 16 by default."""
+
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.9
+    num_gpu_blocks_override: Optional[int] = None
+    kv_cache_memory_bytes: Optional[int] = None
+    enable_prefix_caching: bool = True
+    prefix_caching_hash_algo: str = "sha256"
+    cache_dtype: str = "auto"  # auto | fp8 | fp8_e4m3 | fp8_e5m2
+    mamba_cache_mode: str = "none"  # none | align
+    cpu_offload_gb: float = 0.0
+    num_gpu_blocks: int = 0  # filled in after profiling
+
+    def __post_init__(self) -> None:
+        if self.block_size <= 0 or self.block_size & (self.block_size - 1):
+            raise ValueError("block_size must be a power of two")
+        if not 0.0 < self.gpu_memory_utilization <= 1.0:
+            raise ValueError("gpu_memory_utilization must be in (0, 1]")
+
+    def compute_hash(self) -> str:
+        return _hash([self.block_size, self.cache_dtype])
+
+
+@dataclass
+class ParallelConfig:
+    """Parallel layout (reference: vllm/config/parallel.py:116-341)."""
+
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    distributed_executor_backend: Optional[str] = None  # None | "uni" | "mp" | "external_launcher"
+    tp_comm: str = "fused"  # "fused": peer-memory kernels; "nccl": library collectives (baseline)
+    data_parallel_rank: int = 0
+    enable_eplb: bool = False
+    master_addr: str = "127.0.0.1"
+    master_port: int = 0
+
+    def __post_init__(self) -> None:
+        for n in ("tensor_parallel_size", "pipeline_parallel_size", "data_parallel_size", "decode_context_parallel_size"):
+            if getattr(self, n) < 1:
+                raise ValueError(f"{n} must be >= 1")
+        if self.tensor_parallel_size % self.decode_context_parallel_size:
+            raise ValueError("decode_context_parallel_size must divide tensor_parallel_size")
+
+    @property
+    def world_size(self) -> int:
+        return self.tensor_parallel_size * self.pipeline_parallel_size
+
+    def compute_hash(self) -> str:
+        return _hash([self.tensor_parallel_size, self.pipeline_parallel_size, self.enable_expert_parallel])
+
+
+@dataclass
+class SchedulerConfig:
+    """Token-budget scheduler (reference: vllm/config/scheduler.py; semantics v1/core/sched/scheduler.py:459-468)."""
+
+    max_num_batched_tokens: int = 8192
+    max_num_seqs: int = 256
+    max_model_len: int = 4096
+    enable_chunked_prefill: bool = True
+    long_prefill_token_threshold: int = 0
+    policy: str = "fcfs"  # fcfs | priority
+    async_scheduling: bool = False
+    cuda_graph_sizes: Optional[list[int]] = None
+
+    def __post_init__(self) -> None:
+        if self.policy not in ("fcfs", "priority"):
+            raise ValueError("policy must be 'fcfs' or 'priority'")
+        if not self.enable_chunked_prefill and self.max_num_batched_tokens < self.max_model_len:
+            raise ValueError("without chunked prefill max_num_batched_tokens must cover max_model_len")
+
+    def graph_capture_sizes(self) -> list[int]:
+        """Default capture sizes (reference: vllm/config/vllm.py:2084-2200)."""
+        if self.cuda_graph_sizes is not None:
+            return sorted(set(self.cuda_graph_sizes))
+        mx = min(2 * self.max_num_seqs, 512)
+        sizes = [1, 2, 4] + list(range(8, 256, 8)) + list(range(256, mx + 1, 16))
+        return [s for s in sizes if s <= mx]
+
+
+@dataclass
+class SpeculativeConfig:
+    """Speculative decoding (reference: vllm/config/speculative.py:216-281,1090-1104).
+
+    ``synthetic_acceptance_rates`` are per-position *unconditional* acceptance probabilities; the
+    rejection sampler uses the conditional form ``rate[i] / rate[i-1]``.
+    """
+
+    method: Optional[str] = None  # None | "mtp" | "ngram"
+    num_speculative_tokens: int = 0
+    synthetic_acceptance_rates: Optional[list[float]] = None
+    synthetic_acceptance_rate: Optional[float] = None  # conditional per-position Bernoulli rate
+    synthetic_seed: int = 0
+    prompt_lookup_max: int = 4
+    prompt_lookup_min: int = 2
+
+    def __post_init__(self) -> None:
+        if self.method is not None and self.num_speculative_tokens < 1:
+            raise ValueError("num_speculative_tokens must be >= 1 when a method is set")
+        if self.synthetic_acceptance_rates is not None:
+            r = self.synthetic_acceptance_rates
+            if len(r) != self.num_speculative_tokens or any(not 0 <= x <= 1 for x in r) or any(r[i] > r[i - 1] for i in range(1, len(r))):
+                raise ValueError("synthetic_acceptance_rates must be non-increasing probabilities, one per draft position")
+
+    @property
+    def enabled(self) -> bool:
+        return self.method is not None
+
+    def conditional_rates(self) -> Optional[list[float]]:
+        if self.synthetic_acceptance_rate is not None:
+            return [self.synthetic_acceptance_rate] * self.num_speculative_tokens
+        if self.synthetic_acceptance_rates is None:
+            return None
+        out, prev = [], 1.0
+        for x in self.synthetic_acceptance_rates:
+            out.append(0.0 if prev <= 0 else min(1.0, x / prev))
+            prev = x
+        return out
+
+
+@dataclass
+class ObservabilityConfig:
+    otlp_traces_endpoint: Optional[str] = None
+    collect_detailed_traces: bool = False
+    enable_metrics: bool = True
+    log_stats_interval_s: float = 10.0
+
+
+@dataclass
+class VllmConfig:
+    model_config: ModelConfig
+    cache_config: CacheConfig = field(default_factory=CacheConfig)
+    parallel_config: ParallelConfig = field(default_factory=ParallelConfig)
+    scheduler_config: SchedulerConfig = field(default_factory=SchedulerConfig)
+    speculative_config: SpeculativeConfig = field(default_factory=SpeculativeConfig)
+    observability_config: ObservabilityConfig = field(default_factory=ObservabilityConfig)
+    device: str = "auto"  # auto | cuda | cpu
+    enforce_eager: bool = False
+
+    def __post_init__(self) -> None:
+        self.scheduler_config.max_model_len = self.model_config.max_model_len
+        if self.device == "auto":
+            self.device = "cuda" if torch.cuda.is_available() else "cpu"
+        m, p = self.model_config, self.parallel_config
+        if m.num_attention_heads % p.tensor_parallel_size:
+            raise ValueError("tensor_parallel_size must divide num_attention_heads")
+
+    def compute_hash(self) -> str:
+        return _hash([self.model_config.compute_hash(), self.cache_config.compute_hash(), self.parallel_config.compute_hash()])
+
+
+# ----------------------------------------------------------------------------- EngineArgs
+@dataclass
+class EngineArgs:
+    """User-facing arguments (reference: vllm/engine/arg_utils.py). ``model`` is a checkpoint directory,
+    or ``hf_config`` gives the architecture directly (random-init weights, ``load_format='dummy'``)."""
+
+    model: str = "dummy"
+    hf_config: Optional[dict] = None
+    tokenizer: Optional[str] = None
+    dtype: str = "auto"
+    seed: int = 0
+    max_model_len: Optional[int] = None
+    quantization: Optional[str] = None
+    load_format: str = "auto"
+    tensor_parallel_size: int = 1
+    pipeline_parallel_size: int = 1
+    data_parallel_size: int = 1
+    enable_expert_parallel: bool = False
+    decode_context_parallel_size: int = 1
+    distributed_executor_backend: Optional[str] = None
+    tp_comm: str = "fused"
+    block_size: int = 16
+    gpu_memory_utilization: float = 0.9
+    num_gpu_blocks_override: Optional[int] = None
+    kv_cache_memory_bytes: Optional[int] = None
+    enable_prefix_caching: bool = True
+    kv_cache_dtype: str = "auto"
+    max_num_batched_tokens: int = 8192
+    max_num_seqs: int = 256
+    enable_chunked_prefill: bool = True
+    long_prefill_token_threshold: int = 0
+    scheduling_policy: str = "fcfs"
+    async_scheduling: bool = False
+    enforce_eager: bool = False
+    cuda_graph_sizes: Optional[list[int]] = None
+    speculative_config: Optional[Union[dict, str]] = None
+    device: str = "auto"
+    otlp_traces_endpoint: Optional[str] = None
+    disable_log_stats: bool = True
+    hf_overrides: Optional[dict] = None
+
+    def create_engine_config(self) -> VllmConfig:
+        dt = _DTYPES[self.dtype] if isinstance(self.dtype, str) else self.dtype
+        over: dict[str, Any] = dict(seed=self.seed, load_format=self.load_format, tokenizer=self.tokenizer)
+        if self.hf_config is not None:
+            hf = dict(self.hf_config)
+            hf.update(self.hf_overrides or {})
+            mc = ModelConfig.from_hf_dict(hf, model=self.model, **over)
+            if self.load_format == "auto":
+                mc.load_format = "dummy"
+        else:
+            mc = ModelConfig.from_pretrained(self.model, **over)
+        device = self.device if self.device != "auto" else ("cuda" if torch.cuda.is_available() else "cpu")
+        mc.dtype = dt if dt is not None else (torch.bfloat16 if device == "cuda" else torch.float32)
+        if self.quantization:
+            if mc.quant.method == "none":
+                mc.quant = QuantConfig.from_hf({"quant_method": self.quantization})
+            elif mc.quant.method != self.quantization.replace("_marlin", ""):
+                raise ValueError(f"quantization={self.quantization} does not match the checkpoint's {mc.quant.method}")
+        mc.max_model_len = self.max_model_len or min(mc.max_position_embeddings, 32768)
+        spec = self.speculative_config
+        if isinstance(spec, str):
+            spec = json.loads(spec)
+        sc = SpeculativeConfig(**spec) if spec else SpeculativeConfig()
+        return VllmConfig(
+            model_config=mc,
+            cache_config=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
+                                     self.kv_cache_memory_bytes, self.enable_prefix_caching, cache_dtype=self.kv_cache_dtype),
+            parallel_config=ParallelConfig(self.tensor_parallel_size, self.pipeline_parallel_size, self.data_parallel_size,
+                                           self.enable_expert_parallel, self.decode_context_parallel_size,
+                                           self.distributed_executor_backend, self.tp_comm),
+            scheduler_config=SchedulerConfig(self.max_num_batched_tokens, self.max_num_seqs, mc.max_model_len,
+                                             self.enable_chunked_prefill, self.long_prefill_token_threshold,
+                                             self.scheduling_policy, self.async_scheduling, self.cuda_graph_sizes),
+            speculative_config=sc,
+            observability_config=ObservabilityConfig(self.otlp_traces_endpoint, enable_metrics=not self.disable_log_stats),
+            device=device, enforce_eager=self.enforce_eager,
+        )
+
+    # ---- argparse bridge (reference: arg_utils.py add_cli_args / from_cli_args)
+    @classmethod
+    def add_cli_args(cls, parser: argparse.ArgumentParser) -> argparse.ArgumentParser:
+        for f in dataclasses.fields(cls):
+            name = "--" + f.name.replace("_", "-")
+            if f.name == "hf_config" or f.name == "hf_overrides" or f.name == "speculative_config":
+                parser.add_argument(name, type=json.loads, default=None)
+            elif f.type in ("bool", bool):
+                parser.add_argument(name, action=argparse.BooleanOptionalAction, default=f.default)
+            elif "list[int]" in str(f.type):
+                parser.add_argument(name, type=int, nargs="*", default=None)
+            elif "int" in str(f.type):
+                parser.add_argument(name, type=int, default=f.default)
+            elif "float" in str(f.type):
+                parser.add_argument(name, type=float, default=f.default)
+            else:
+                parser.add_argument(name, type=str, default=f.default)
+        return parser
+
+    @classmethod
+    def from_cli_args(cls, ns: argparse.Namespace) -> "EngineArgs":
+        names = {f.name for f in dataclasses.fields(cls)}
+        return cls(**{k: v for k, v in vars(ns).items() if k in names})
+
+
+AsyncEngineArgs = EngineArgs

@@ -1,0 +1,100 @@
+"""Engine core: owns the scheduler and the executor; one ``step`` = schedule → execute → update
+(reference: vllm/v1/engine/core.py:94 ``EngineCore``, :241 ``_initialize_kv_caches``, :445 ``step``, :786-804 utility
+calls; the process wrapper with ZMQ sockets lives in ``onecat_vllm.engine.core_proc``)."""
+from __future__ import annotations
+
+import time
+from typing import Optional
+
+from onecat_vllm.config import VllmConfig
+from onecat_vllm.core.scheduler import Scheduler
+from onecat_vllm.executor.uniproc import Executor
+from onecat_vllm.logger import init_logger
+from onecat_vllm.request import EngineCoreOutputs, EngineCoreRequest, Request, RequestStatus
+
+log = init_logger(__name__)
+
+
+class EngineDeadError(RuntimeError):
+    """Raised to API callers once the engine core or a worker has failed (reference: v1/engine/exceptions.py:9)."""
+
+
+class CollectiveTimeout(RuntimeError):
+    """A bounded device-side wait on a peer expired; the step's outputs are not trustworthy."""
+
+
+class EngineCore:
+    def __init__(self, vllm_config: VllmConfig, executor_class=None, log_stats: bool = True):
+        self.cfg = vllm_config
+        executor_class = executor_class or Executor.get_class(vllm_config)
+        t0 = time.time()
+        self.executor = executor_class(vllm_config)
+        self._failed = False
+        self.executor.register_failure_callback(self._on_executor_failure)
+        num_blocks, num_slots = self.executor.initialize_kv_cache()
+        self.scheduler = Scheduler(vllm_config, num_blocks, num_slots, log_stats)
+        self.step_count = 0
+        self.paused = False
+        log.info_once(f"engine core ready: {num_blocks} KV blocks, {num_slots} state slots, init {time.time() - t0:.1f}s")
+
+    def _on_executor_failure(self) -> None:
+        self._failed = True
+
+    # ---- requests
+    def add_request(self, req: EngineCoreRequest | Request) -> None:
+        self.scheduler.add_request(req)
+
+    def abort_requests(self, request_ids: list[str]) -> None:
+        self.scheduler.finish_requests(request_ids, RequestStatus.FINISHED_ABORTED)
+
+    # ---- the step
+    def step(self) -> tuple[dict[int, EngineCoreOutputs], bool]:
+        """Returns (outputs per client, whether a model step ran)."""
+        if self._failed:
+            raise EngineDeadError("a worker failed")
+        if not self.scheduler.has_requests() or self.paused:
+            return {}, False
+        so = self.scheduler.schedule()
+        try:
+            mro = self.executor.execute_model(so)
+        except Exception as e:
+            self._failed = True
+            log.error(f"model step failed; scheduler state: running={len(self.scheduler.running)} waiting={len(self.scheduler.waiting)} "
+                      f"tokens={so.total_num_scheduled_tokens}: {e!r}")
+            raise
+        if mro.status != 0:
+            self._failed = True
+            raise CollectiveTimeout(f"device wait expired (status {mro.status:#x})")
+        outs = self.scheduler.update_from_output(so, mro)
+        self.step_count += 1
+        return outs, so.total_num_scheduled_tokens > 0
+
+    # ---- utility calls
+    def has_unfinished_requests(self) -> bool:
+        return self.scheduler.has_unfinished_requests()
+
+    def reset_prefix_cache(self) -> bool:
+        return self.scheduler.reset_prefix_cache()
+
+    def sleep(self, level: int = 1) -> None:
+        self.paused = True
+        self.executor.collective_rpc("sleep", (level,))
+        self.scheduler.reset_prefix_cache()
+
+    def wake_up(self) -> None:
+        self.executor.collective_rpc("wake_up")
+        self.paused = False
+
+    def profile(self, start: bool = True) -> None:
+        self.executor.collective_rpc("profile", (start,))
+
+    def save_sharded_state(self, path: str) -> None:
+        self.executor.collective_rpc("save_sharded_state", (path,))
+
+    def collective_rpc(self, method, args=(), kwargs=None):
+        return self.executor.collective_rpc(method, args, kwargs)
+
+    def shutdown(self) -> None:
+        if getattr(self, "executor", None) is not None:
+            self.executor.shutdown()
+            self.executor = None

@@ -1,0 +1,87 @@
+"""Offline inference API (reference: vllm/entrypoints/llm.py:66 class, :422 ``generate``, :487 ``chat``, :806-889
+sleep / wake_up / collective_rpc / get_metrics; run loop entrypoints/offline_utils.py:326,573)."""
+from __future__ import annotations
+
+import itertools
+from typing import Optional, Sequence, Union
+
+from onecat_vllm.config import EngineArgs
+from onecat_vllm.engine.llm_engine import LLMEngine
+from onecat_vllm.inputs import PromptType
+from onecat_vllm.outputs import RequestOutput
+from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
+
+
+class LLM:
+    """``LLM(model=<checkpoint dir>)`` loads an HF-format checkpoint; ``LLM(hf_config={...})`` builds the architecture
+    with random weights (synthetic benchmarks and tests)."""
+
+    def __init__(self, model: str = "dummy", **kwargs):
+        self.engine_args = EngineArgs(model=model, **kwargs)
+        self.llm_engine = LLMEngine.from_engine_args(self.engine_args)
+        self._counter = itertools.count()
+
+    def get_tokenizer(self):
+        return self.llm_engine.tokenizer
+
+    def generate(self, prompts: Union[PromptType, Sequence[PromptType]], sampling_params: Optional[Union[SamplingParams, Sequence[SamplingParams]]] = None,
+                 use_tqdm: bool = False, priority: Optional[list[int]] = None) -> list[RequestOutput]:
+        if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        if sampling_params is None:
+            sampling_params = SamplingParams()
+        sps = list(sampling_params) if isinstance(sampling_params, (list, tuple)) else [sampling_params] * len(prompts)
+        if len(sps) != len(prompts):
+            raise ValueError("the number of sampling params must match the number of prompts")
+        ids = []
+        for i, (p, sp) in enumerate(zip(prompts, sps)):
+            sp = sp.clone()
+            sp.output_kind = RequestOutputKind.FINAL_ONLY
+            rid = str(next(self._counter))
+            ids.append(rid)
+            self.llm_engine.add_request(rid, p, sp, priority=priority[i] if priority else 0)
+        return self._run_engine(ids, use_tqdm)
+
+    def chat(self, messages, sampling_params: Optional[SamplingParams] = None, add_generation_prompt: bool = True, **kw) -> list[RequestOutput]:
+        tok = self.get_tokenizer()
+        if tok is None:
+            raise ValueError("chat() needs a tokenizer")
+        convs = messages if messages and isinstance(messages[0], list) else [messages]
+        prompts = [tok.apply_chat_template(c, tokenize=False, add_generation_prompt=add_generation_prompt) for c in convs]
+        return self.generate(prompts, sampling_params)
+
+    def _run_engine(self, ids: list[str], use_tqdm: bool = False) -> list[RequestOutput]:
+        done: dict[str, RequestOutput] = {}
+        bar = None
+        if use_tqdm:
+            from tqdm import tqdm
+            bar = tqdm(total=len(ids), desc="Processed prompts")
+        eng = self.llm_engine
+        while eng.has_unfinished_requests():
+            for out in eng.step():
+                if out.finished:
+                    done[out.request_id] = out
+                    if bar:
+                        bar.update(1)
+        if bar:
+            bar.close()
+        return [done[i] for i in ids if i in done]
+
+    # ---- control surface
+    def sleep(self, level: int = 1) -> None:
+        self.llm_engine.sleep(level)
+
+    def wake_up(self) -> None:
+        self.llm_engine.wake_up()
+
+    def reset_prefix_cache(self) -> bool:
+        return self.llm_engine.reset_prefix_cache()
+
+    def collective_rpc(self, method, args=(), kwargs=None):
+        return self.llm_engine.collective_rpc(method, args, kwargs)
+
+    def get_metrics(self) -> dict:
+        return self.llm_engine.get_metrics()
+
+    def shutdown(self) -> None:
+        self.llm_engine.shutdown()

@@ -1,0 +1,83 @@
+"""Typed, lazily evaluated environment flags.
+
+The reference exposes several hundred ``VLLM_*`` variables through a module
+``__getattr__`` table that can be frozen after start-up (reference:
+vllm/envs.py:989,3820,3838). This engine keeps the mechanism and a short table.
+"""
+from __future__ import annotations
+
+import os
+from typing import Any, Callable
+
+_TRUE = ("1", "true", "yes", "on")
+
+
+def _b(name: str, default: bool) -> Callable[[], bool]:
+    return lambda: os.environ.get(name, str(int(default))).lower() in _TRUE
+
+
+def _i(name: str, default: int) -> Callable[[], int]:
+    return lambda: int(os.environ.get(name, default))
+
+
+def _s(name: str, default):
+    return lambda: os.environ.get(name, default)
+
+
+environment_variables: dict[str, Callable[[], Any]] = {
+    # process model
+    "ONECAT_ENABLE_MULTIPROCESSING": _b("ONECAT_ENABLE_MULTIPROCESSING", False),
+    "ONECAT_WORKER_MULTIPROC_METHOD": _s("ONECAT_WORKER_MULTIPROC_METHOD", "spawn"),
+    "ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS": _i("ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS", 300),
+    "ONECAT_HANDSHAKE_TIMEOUT_SECONDS": _i("ONECAT_HANDSHAKE_TIMEOUT_SECONDS", 120),
+    "ONECAT_RPC_RING_CHUNK_BYTES": _i("ONECAT_RPC_RING_CHUNK_BYTES", 1 << 22),
+    "ONECAT_RPC_RING_CHUNKS": _i("ONECAT_RPC_RING_CHUNKS", 8),
+    # kernels
+    "ONECAT_GEMM_BACKEND": _s("ONECAT_GEMM_BACKEND", "tcgen05"),  # "tcgen05" | "library" (debug only)
+    "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
+    "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),
+    "ONECAT_USE_CUDA_GRAPH": _b("ONECAT_USE_CUDA_GRAPH", True),
+    "ONECAT_COMPUTE_NANS_IN_LOGITS": _b("ONECAT_COMPUTE_NANS_IN_LOGITS", False),
+    # observability
+    "ONECAT_LOGGING_LEVEL": _s("ONECAT_LOGGING_LEVEL", "INFO"),
+    "ONECAT_STEP_TRACE": _b("ONECAT_STEP_TRACE", False),
+    "ONECAT_NVTX": _b("ONECAT_NVTX", False),
+    "ONECAT_OTLP_ENDPOINT": _s("ONECAT_OTLP_ENDPOINT", None),
+    # serving
+    "ONECAT_API_KEY": _s("ONECAT_API_KEY", None),
+    "ONECAT_HOST_IP": _s("ONECAT_HOST_IP", "127.0.0.1"),
+    "ONECAT_USE_NATIVE_FRONTEND": _b("ONECAT_USE_NATIVE_FRONTEND", False),
+}
+
+_cache: dict[str, Any] = {}
+_frozen = False
+
+
+def __getattr__(name: str) -> Any:
+    if name in _cache:
+        return _cache[name]
+    fn = environment_variables.get(name)
+    if fn is None:
+        raise AttributeError(f"module 'envs' has no attribute {name!r}")
+    val = fn()
+    if _frozen:
+        _cache[name] = val
+    return val
+
+
+def enable_envs_cache() -> None:
+    """Freeze values after start-up so hot paths never touch ``os.environ``."""
+    global _frozen
+    _frozen = True
+    for k, fn in environment_variables.items():
+        _cache[k] = fn()
+
+
+def disable_envs_cache() -> None:
+    global _frozen
+    _frozen = False
+    _cache.clear()
+
+
+def is_set(name: str) -> bool:
+    return name in os.environ

@@ -1,0 +1,55 @@
+"""Self-attention block: fused QKV GEMM → (per-head norm) → RoPE + paged-KV insert → paged flash attention
+→ (sigmoid output gate) → o_proj (reference: models/llama.py attention; models/qwen3_next.py:505-626 for the
+gated variant with per-head q/k RMSNorm and partial rotary)."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from onecat_vllm import ops
+from onecat_vllm.config import ModelConfig
+from onecat_vllm.layers.common import get_rope
+from onecat_vllm.layers.linear import QKVParallelLinear, RowParallelLinear
+from onecat_vllm.parallel.state import get_state
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str, device):
+        super().__init__()
+        tp = get_state().tp_size
+        self.D = cfg.head_dim
+        self.gated = cfg.attn_output_gate
+        self.qkv_proj = QKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads,
+                                          q_mult=2 if self.gated else 1, bias=cfg.attention_bias, quant=cfg.quant,
+                                          prefix=prefix + ".qkv_proj", dtype=cfg.dtype)
+        self.Hq, self.Hkv = self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, quant=cfg.quant,
+                                        prefix=prefix + ".o_proj", dtype=cfg.dtype)
+        self.qk_norm, self.gemma, self.eps = cfg.qk_norm, cfg.gemma_norm, cfg.rms_norm_eps
+        if cfg.qk_norm:
+            init = torch.zeros if cfg.gemma_norm else torch.ones
+            self.q_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
+            self.k_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
+        self.rotary_dim = cfg.rotary_dim
+        self.rope = get_rope(cfg.rotary_dim, cfg.max_model_len, cfg.rope_theta, device)
+        self.scale = cfg.head_dim ** -0.5
+        self.layer_idx = layer_idx
+
+    def forward(self, x: torch.Tensor, md, kv_cache: torch.Tensor) -> torch.Tensor:
+        T = x.shape[0]
+        D, Hq, Hkv = self.D, self.Hq, self.Hkv
+        qkv = self.qkv_proj(x)
+        qw = Hq * D * (2 if self.gated else 1)
+        if self.gated:
+            qg = qkv[:, :qw].view(T, Hq, 2 * D)
+            q, gate = qg[..., :D], qg[..., D:]
+        else:
+            q, gate = qkv[:, :qw].view(T, Hq, D), None
+        k = qkv[:, qw:qw + Hkv * D].view(T, Hkv, D)
+        v = qkv[:, qw + Hkv * D:].view(T, Hkv, D)
+        ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
+                           self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
+        o = ops.paged_attention(q, kv_cache, md, self.scale)
+        if gate is not None:
+            o = o * torch.sigmoid(gate.float()).to(o.dtype)
+        return self.o_proj(o.reshape(T, Hq * D))

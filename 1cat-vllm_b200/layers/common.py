@@ -1,0 +1,90 @@
+"""Norm, rotary and embedding layers (reference: layers/layernorm.py:157,252; layers/rotary_embedding/;
+layers/vocab_parallel_embedding.py:400,686; layers/logits_processor.py:179-247)."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from onecat_vllm import ops
+from onecat_vllm.ops import ref
+from onecat_vllm.parallel import state as ps
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, hidden: int, eps: float, gemma: bool = False, dtype=torch.float32):
+        super().__init__()
+        self.weight = nn.Parameter(torch.zeros(hidden, dtype=dtype) if gemma else torch.ones(hidden, dtype=dtype), requires_grad=False)
+        self.eps, self.gemma = eps, gemma
+
+    def forward(self, x, residual: Optional[torch.Tensor] = None):
+        """Returns (normed, residual_out); the add is fused."""
+        return ops.rms_norm(x, self.weight, self.eps, residual, self.gemma)
+
+    def load_weight(self, pname, w, shard_id=None):
+        self.weight.data.copy_(w)
+
+
+class RotaryEmbedding:
+    """NeoX-style rotary with a precomputed fp32 cos|sin table."""
+
+    def __init__(self, rotary_dim: int, max_pos: int, theta: float, device):
+        self.rotary_dim = rotary_dim
+        self.cos_sin = ref.build_cos_sin_cache(rotary_dim, max_pos, theta, device)
+
+
+_ROPE_CACHE: dict = {}
+
+
+def get_rope(rotary_dim: int, max_pos: int, theta: float, device) -> RotaryEmbedding:
+    key = (rotary_dim, max_pos, theta, str(device))
+    if key not in _ROPE_CACHE:
+        _ROPE_CACHE[key] = RotaryEmbedding(rotary_dim, max_pos, theta, device)
+    return _ROPE_CACHE[key]
+
+
+def pad_vocab(v: int, tp: int, mult: int = 64) -> int:
+    per = -(-v // tp)
+    return -(-per // mult) * mult * tp
+
+
+class VocabParallelEmbedding(nn.Module):
+    """Rows are split over TP ranks (padded to 64 per shard); out-of-shard ids contribute zeros and the
+    partial results are summed across ranks."""
+
+    def __init__(self, vocab: int, hidden: int, dtype=torch.float32):
+        super().__init__()
+        st = ps.get_state()
+        self.tp, self.rank = st.tp_size, st.tp_rank
+        self.vocab, self.padded = vocab, pad_vocab(vocab, self.tp)
+        self.per = self.padded // self.tp
+        self.lo = self.rank * self.per
+        self.weight = nn.Parameter(torch.zeros(self.per, hidden, dtype=dtype), requires_grad=False)
+
+    def load_weight(self, pname, w, shard_id=None):
+        hi = min(self.lo + self.per, w.shape[0])
+        if hi > self.lo:
+            self.weight.data[: hi - self.lo].copy_(w[self.lo:hi])
+
+    def forward(self, ids: torch.Tensor) -> torch.Tensor:
+        if self.tp == 1:
+            return F.embedding(ids.long(), self.weight)
+        local = ids.long() - self.lo
+        ok = (local >= 0) & (local < self.per)
+        out = F.embedding(local.clamp(0, self.per - 1), self.weight) * ok.unsqueeze(-1).to(self.weight.dtype)
+        return ps.all_reduce(out)
+
+
+class ParallelLMHead(VocabParallelEmbedding):
+    """Vocab-sharded output projection; ``compute_logits`` gathers the shards."""
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        if hidden.is_cuda:
+            from onecat_vllm.ops import cuda as K
+            local = K.gemm_bf16(hidden, self.weight)
+        else:
+            local = F.linear(hidden, self.weight)
+        full = ps.all_gather_last_dim(local)
+        return full[..., : self.vocab]

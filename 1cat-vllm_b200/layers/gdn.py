@@ -1,0 +1,65 @@
+"""Gated-DeltaNet linear-attention block (reference: layers/mamba/gdn/qwen_gdn_linear_attn.py:2057-2180 layer,
+:6945-7013 gating; recurrence flash_qla/.../gdn_forward.cu:131-215).
+
+x → [q|k|v|z] and [b|a] projections → depthwise causal conv (k=4, SiLU) over [q|k|v] with a rolling state →
+g = -exp(A_log)·softplus(a+dt_bias), β = sigmoid(b) → gated delta rule with fp32 state per (sequence, v-head)
+→ RMSNormGated(o, z) per head → row-parallel out_proj. V heads (and their K-head groups) are split over TP ranks."""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+
+from onecat_vllm import ops
+from onecat_vllm.config import ModelConfig
+from onecat_vllm.layers.linear import MergedColumnParallelLinear, RowParallelLinear
+from onecat_vllm.ops import ref
+from onecat_vllm.parallel.state import get_state
+
+
+class GatedDeltaNet(nn.Module):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str):
+        super().__init__()
+        tp = get_state().tp_size
+        self.Hk, self.Hv = cfg.linear_num_key_heads // tp, cfg.linear_num_value_heads // tp
+        self.K, self.V = cfg.linear_key_head_dim, cfg.linear_value_head_dim
+        key_dim, val_dim = cfg.linear_num_key_heads * self.K, cfg.linear_num_value_heads * self.V
+        self.key_dim, self.val_dim = key_dim // tp, val_dim // tp
+        self.kw = cfg.linear_conv_kernel_dim
+        self.in_proj_qkvz = MergedColumnParallelLinear(cfg.hidden_size, [key_dim, key_dim, val_dim, val_dim], quant=cfg.quant,
+                                                       prefix=prefix + ".in_proj_qkvz", dtype=cfg.dtype)
+        self.in_proj_ba = MergedColumnParallelLinear(cfg.hidden_size, [cfg.linear_num_value_heads, cfg.linear_num_value_heads],
+                                                     quant=None, prefix=prefix + ".in_proj_ba", dtype=cfg.dtype)
+        self.conv_dim = 2 * self.key_dim + self.val_dim
+        self.conv_weight = nn.Parameter(torch.zeros(self.conv_dim, self.kw, dtype=cfg.dtype), requires_grad=False)
+        self.A_log = nn.Parameter(torch.zeros(self.Hv, dtype=torch.float32), requires_grad=False)
+        self.dt_bias = nn.Parameter(torch.ones(self.Hv, dtype=torch.float32), requires_grad=False)
+        self.norm_weight = nn.Parameter(torch.ones(self.V, dtype=cfg.dtype), requires_grad=False)
+        self.out_proj = RowParallelLinear(val_dim, cfg.hidden_size, quant=cfg.quant, prefix=prefix + ".out_proj", dtype=cfg.dtype)
+        self.eps = cfg.rms_norm_eps
+        self.layer_idx = layer_idx
+
+    def state_shapes(self):
+        return (self.conv_dim, self.kw - 1), (self.Hv, self.K, self.V)
+
+    def forward(self, x: torch.Tensor, md, state) -> torch.Tensor:
+        """``state`` = (conv_state [slots, conv_dim, kw-1], ssm_state fp32 [slots, Hv, K, V])."""
+        conv_state, ssm_state = state
+        T = x.shape[0]
+        qkvz = self.in_proj_qkvz(x)
+        ba = self.in_proj_ba(x)
+        mixed, z = qkvz[:, : self.conv_dim], qkvz[:, self.conv_dim:]
+        b, a = ba[:, : self.Hv], ba[:, self.Hv:]
+        if x.is_cuda:
+            from onecat_vllm.ops import cuda as K
+            o = K.gdn_forward(mixed, b, a, self.conv_weight, self.A_log, self.dt_bias, conv_state, ssm_state, md,
+                              self.Hk, self.Hv, self.K, self.V)
+        else:
+            mixed = ref.causal_conv1d(mixed.contiguous(), self.conv_weight, None, conv_state, md.query_start_loc, md.state_slots,
+                                      md.has_initial_state)
+            q = mixed[:, : self.key_dim].reshape(T, self.Hk, self.K)
+            k = mixed[:, self.key_dim: 2 * self.key_dim].reshape(T, self.Hk, self.K)
+            v = mixed[:, 2 * self.key_dim:].reshape(T, self.Hv, self.V)
+            g, beta = ref.gdn_gating(a, b, self.A_log, self.dt_bias)
+            o = ref.gated_delta_rule(q, k, v, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
+        o = ops.rms_norm_gated(o.reshape(T * self.Hv, self.V), z.reshape(T * self.Hv, self.V), self.norm_weight, self.eps)
+        return self.out_proj(o.reshape(T, self.Hv * self.V))

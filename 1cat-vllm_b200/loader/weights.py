@@ -1,0 +1,160 @@
+"""Weight loading: safetensors checkpoints (HF layout, sharded over TP on the fly) and dummy random init
+(reference: model_executor/model_loader/default_loader.py, dummy_loader.py, weight_utils.py:1451-1475).
+
+Dummy init fills quantised storage with uniform random codes and scales drawn as the benchmark configs
+prescribe, so synthetic AWQ/FP8/MXFP4 models exercise the same kernels as real checkpoints."""
+from __future__ import annotations
+
+import glob
+import json
+import os
+import re
+from typing import Iterable, Iterator
+
+import torch
+import torch.nn as nn
+
+from onecat_vllm.logger import init_logger
+
+log = init_logger(__name__)
+
+
+def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    from safetensors import safe_open
+    files = sorted(glob.glob(os.path.join(path, "*.safetensors")))
+    if not files:
+        raise FileNotFoundError(f"no *.safetensors under {path}")
+    for f in files:
+        with safe_open(f, framework="pt", device="cpu") as sf:
+            for k in sf.keys():
+                yield k, sf.get_tensor(k)
+
+
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv|weight_scale)$")
+
+
+def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) -> set:
+    """Route checkpoint tensors to module ``load_weight`` hooks. Returns the set of consumed names."""
+    mods = dict(model.named_modules())
+    params = dict(model.named_parameters())
+    stacked = getattr(model, "stacked_params_mapping", [])
+    loaded = set()
+    for name, w in weights:
+        if name.startswith("language_model."):
+            name = name[len("language_model."):]
+        if "rotary_emb.inv_freq" in name or name.startswith(("visual.", "model.visual.")):
+            continue
+        m = _EXPERT_RE.match(name)
+        if m:
+            mod = mods.get(m.group(1) + ".experts")
+            if mod is not None:
+                mod.load_expert_weight(int(m.group(2)), m.group(3), m.group(4), w)
+                loaded.add(name)
+            continue
+        target, shard = name, None
+        for ours, theirs, sid in stacked:
+            if theirs + "." in name:
+                cand = name.replace(theirs + ".", ours + ".")
+                if cand.rsplit(".", 1)[0] in mods:
+                    target, shard = cand, sid
+                    break
+        mod_name, _, pname = target.rpartition(".")
+        mod = mods.get(mod_name)
+        if mod is not None and hasattr(mod, "load_weight"):
+            mod.load_weight(pname, w, shard)
+            loaded.add(name)
+        elif target in params:
+            p = params[target]
+            if p.shape == w.shape:
+                p.data.copy_(w)
+            else:  # e.g. conv weight [C,1,k] → [C,k]; TP-sharded vectors
+                p.data.copy_(w.reshape(-1, *p.shape[1:])[: p.shape[0]] if w.numel() != p.numel() else w.reshape(p.shape))
+            loaded.add(name)
+        else:
+            log.warning_once(f"checkpoint tensor {name} has no destination")
+    return loaded
+
+
+@torch.no_grad()
+def dummy_init(model: nn.Module, seed: int = 0, std: float = 0.02) -> None:
+    """Random-init every parameter in place. Floating tensors ~ N(0, std); norm weights = 1 (0 for Gemma-style);
+    int4 codes uniform; fp16 group scales |N(0, 0.01)|; fp8 codes from N(0,1) with scales so that the dequantised
+    weights have std ≈ ``std``; ue8m0 scales chosen likewise."""
+    gens: dict = {}
+
+    def gen(dev):
+        if dev not in gens:
+            g = torch.Generator(device=dev)
+            g.manual_seed(seed)
+            gens[dev] = g
+        return gens[dev]
+
+    for name, p in model.named_parameters():
+        g = gen(p.device)
+        leaf = name.rsplit(".", 1)[-1]
+        if leaf in ("weight",) and name.endswith(("layernorm.weight", "norm.weight")) or leaf in ("q_norm", "k_norm", "norm_weight"):
+            continue  # keep constructor init (1, or 0 for Gemma-style)
+        if p.dtype in (torch.float32, torch.float16, torch.bfloat16):
+            if leaf in ("scales",):
+                p.copy_(torch.empty(p.shape, device=p.device, dtype=torch.float32).normal_(0, 0.01, generator=g).abs_().clamp_min_(1e-4))
+            elif leaf in ("weight_scale_inv", "w13_scale", "w2_scale", "weight_scale"):
+                p.fill_(std / 1.0 if leaf != "weight_scale" else std)
+            elif leaf == "weight_scale_2":
+                p.fill_(std / 2.0)
+            elif leaf == "A_log":
+                p.copy_(torch.empty(p.shape, device=p.device).uniform_(0.0, 2.0, generator=g).log1p_())
+            elif leaf == "dt_bias":
+                p.copy_(torch.empty(p.shape, device=p.device).uniform_(0.0, 1.0, generator=g))
+            elif leaf == "e_score_correction_bias":
+                p.zero_()
+            else:
+                p.copy_(torch.empty(p.shape, device=p.device, dtype=torch.float32).normal_(0, std, generator=g))
+        elif p.dtype == torch.int32:
+            if leaf == "g_idx":
+                continue
+            lo = torch.randint(0, 1 << 16, p.shape, device=p.device, generator=g, dtype=torch.int32)
+            hi = torch.randint(0, 1 << 16, p.shape, device=p.device, generator=g, dtype=torch.int32)
+            p.copy_((hi << 16) | lo)
+        elif p.dtype == torch.float8_e4m3fn:
+            if leaf == "weight_scale":  # nvfp4 block scales
+                p.copy_(torch.ones(p.shape, device=p.device).to(torch.float8_e4m3fn))
+            else:
+                # chunked to bound temporary memory on large expert stacks
+                flat = p.view(-1)
+                step = 1 << 26
+                for a in range(0, flat.numel(), step):
+                    b = min(a + step, flat.numel())
+                    flat[a:b] = torch.empty(b - a, device=p.device, dtype=torch.float32).normal_(0, 1.0, generator=g).to(torch.float8_e4m3fn)
+        elif p.dtype == torch.uint8:
+            if leaf in ("weight_scale", "w13_scale", "w2_scale"):  # ue8m0: 2^(e-127); e2m1 codes have std ~ 2.6
+                p.fill_(127 - 7)
+            else:
+                flat = p.view(-1)
+                step = 1 << 26
+                for a in range(0, flat.numel(), step):
+                    b = min(a + step, flat.numel())
+                    flat[a:b] = torch.randint(0, 256, (b - a,), device=p.device, generator=g, dtype=torch.uint8)
+
+
+def process_weights_after_loading(model: nn.Module) -> None:
+    for m in model.modules():
+        if m is not model and hasattr(m, "process_weights_after_loading"):
+            m.process_weights_after_loading()
+
+
+def load_model(cfg, device) -> nn.Module:
+    """Build → load (or random-init) → repack for kernels."""
+    from onecat_vllm.models import build_model
+    dev = torch.device(device)
+    torch.manual_seed(cfg.seed)
+    with torch.device(dev):
+        model = build_model(cfg, dev)
+    fmt = cfg.load_format
+    if fmt == "auto":
+        fmt = "safetensors" if os.path.isdir(cfg.model) else "dummy"
+    if fmt == "dummy":
+        dummy_init(model, cfg.seed)
+    else:
+        load_weights(model, iter_safetensors(cfg.model))
+    process_weights_after_loading(model)
+    return model.eval()

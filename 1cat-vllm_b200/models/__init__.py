@@ -1,0 +1,28 @@
+"""Model registry (reference: model_executor/models/registry.py): HF ``architectures`` name → builder."""
+from __future__ import annotations
+
+from onecat_vllm.config import ModelConfig
+
+_REGISTRY = {
+    "LlamaForCausalLM": "dense", "MistralForCausalLM": "dense", "Qwen2ForCausalLM": "dense", "Qwen3ForCausalLM": "dense",
+    "Qwen3MoeForCausalLM": "moe", "Qwen2MoeForCausalLM": "moe", "MixtralForCausalLM": "moe",
+    "Qwen3NextForCausalLM": "hybrid", "Qwen3_5ForCausalLM": "hybrid", "Qwen3_5ForConditionalGeneration": "hybrid",
+    "Qwen3_5MoeForCausalLM": "hybrid", "Qwen3_5MoeForConditionalGeneration": "hybrid",
+    "DeepseekV2ForCausalLM": "mla_moe", "DeepseekV3ForCausalLM": "mla_moe", "DeepseekV32ForCausalLM": "mla_moe",
+}
+
+
+def supported_architectures() -> list[str]:
+    return sorted(_REGISTRY)
+
+
+def register_model(arch: str, family: str = "dense") -> None:
+    """Out-of-tree registration hook (reference: ModelRegistry.register_model)."""
+    _REGISTRY[arch] = family
+
+
+def build_model(cfg: ModelConfig, device="cpu"):
+    if cfg.architecture not in _REGISTRY:
+        raise ValueError(f"architecture {cfg.architecture!r} is not supported; known: {supported_architectures()}")
+    from onecat_vllm.models.decoder import CausalLM
+    return CausalLM(cfg, device)

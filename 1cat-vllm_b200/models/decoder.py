@@ -1,0 +1,140 @@
+"""Generic pre-norm decoder covering the served architectures.
+
+One ``DecoderLayer`` picks its token mixer (full attention, gated attention, Gated-DeltaNet, MLA) and its
+feed-forward (SwiGLU MLP or sparse MoE) from ``ModelConfig`` (reference: models/llama.py, qwen3.py,
+qwen3_next.py:635-863, qwen3_5.py, deepseek_v2.py:1076-1596). The residual stream is carried unnormalised;
+each sub-block's partial output goes through ``reduce_add_norm`` which fuses the TP reduction, the residual add
+and the next RMSNorm.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from onecat_vllm.config import ModelConfig
+from onecat_vllm.layers.attention import Attention
+from onecat_vllm.layers.common import ParallelLMHead, RMSNorm, VocabParallelEmbedding
+from onecat_vllm.layers.gdn import GatedDeltaNet
+from onecat_vllm.layers.mla import MLAAttention
+from onecat_vllm.layers.mlp import MLP
+from onecat_vllm.layers.moe import SparseMoeBlock
+from onecat_vllm.parallel.tp_ops import reduce_add_norm
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ModelConfig, idx: int, prefix: str, device):
+        super().__init__()
+        self.kind = cfg.layer_type(idx)
+        if cfg.use_mla:
+            self.kind = "mla"
+            self.self_attn = MLAAttention(cfg, idx, prefix + ".self_attn", device)
+        elif self.kind == "linear_attention":
+            self.linear_attn = GatedDeltaNet(cfg, idx, prefix + ".linear_attn")
+        else:
+            self.self_attn = Attention(cfg, idx, prefix + ".self_attn", device)
+        if cfg.is_moe_layer(idx):
+            self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
+        else:
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype)
+        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+
+    def mixer(self, x, md, cache):
+        if self.kind == "linear_attention":
+            return self.linear_attn(x, md, cache)
+        return self.self_attn(x, md, cache)
+
+
+class DecoderModel(nn.Module):
+    """``forward`` returns the final *normalised* hidden states ``[T, hidden]``."""
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        super().__init__()
+        self.cfg = cfg
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, f"model.layers.{i}", device) for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+
+    def forward(self, input_ids: torch.Tensor, md, caches: list, inputs_embeds: Optional[torch.Tensor] = None,
+                return_prenorm: bool = False):
+        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+        layers = self.layers
+        x, residual = layers[0].input_layernorm(h, None)
+        residual = h
+        for i, layer in enumerate(layers):
+            part = layer.mixer(x, md, caches[i])
+            x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
+            part = layer.mlp(x)
+            nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm
+            x, residual = reduce_add_norm(part, residual, nxt)
+        if return_prenorm:
+            return x, residual
+        return x
+
+
+class CausalLM(nn.Module):
+    """Decoder + LM head. Parameter names mirror HF checkpoints (``model.layers.N…``, ``lm_head``)."""
+
+    # checkpoint name fragment → (our stacked parameter, shard id)
+    stacked_params_mapping = [
+        (".qkv_proj", ".q_proj", 0), (".qkv_proj", ".k_proj", 1), (".qkv_proj", ".v_proj", 2),
+        (".gate_up_proj", ".gate_proj", 0), (".gate_up_proj", ".up_proj", 1),
+        (".in_proj_qkvz", ".in_proj_q", 0), (".in_proj_qkvz", ".in_proj_k", 1), (".in_proj_qkvz", ".in_proj_v", 2),
+        (".in_proj_qkvz", ".in_proj_z", 3), (".in_proj_ba", ".in_proj_b", 0), (".in_proj_ba", ".in_proj_a", 1),
+    ]
+
+    def __init__(self, cfg: ModelConfig, device="cpu"):
+        super().__init__()
+        self.cfg = cfg
+        self.model = DecoderModel(cfg, device)
+        if cfg.tie_word_embeddings:
+            self.lm_head = None
+        else:
+            self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+
+    def forward(self, input_ids, md, caches, inputs_embeds=None):
+        return self.model(input_ids, md, caches, inputs_embeds)
+
+    def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
+        head = self.lm_head
+        if head is None:
+            e = self.model.embed_tokens
+            return ParallelLMHead.compute_logits(e, hidden)
+        return head.compute_logits(hidden)
+
+
+class MTPHead(nn.Module):
+    """Multi-token-prediction draft head: ``h' = fc([norm_e(embed(tok)) ; norm_h(h_target)])`` followed by one
+    full-attention decoder layer and a final norm; embeddings and LM head are shared with the target
+    (reference: models/qwen3_5_mtp.py:109-227; models/deepseek_mtp.py)."""
+
+    def __init__(self, cfg: ModelConfig, target: CausalLM, device="cpu"):
+        super().__init__()
+        import dataclasses
+        from onecat_vllm.layers.linear import ReplicatedLinear
+        lcfg = dataclasses.replace(cfg, layer_types=None, num_hidden_layers=1, num_experts=0)
+        self.cfg = lcfg
+        self.pre_fc_norm_embedding = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.pre_fc_norm_hidden = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.fc = ReplicatedLinear(2 * cfg.hidden_size, cfg.hidden_size, quant=None, prefix="mtp.fc", dtype=cfg.dtype)
+        self.layer = DecoderLayer(lcfg, 0, "mtp.layers.0", device)
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self._target = [target]  # not registered: weights are shared, not owned
+
+    def forward(self, input_ids, target_hidden, md, cache):
+        tgt = self._target[0]
+        e, _ = self.pre_fc_norm_embedding(tgt.model.embed_tokens(input_ids))
+        h, _ = self.pre_fc_norm_hidden(target_hidden)
+        h = self.fc(torch.cat([e, h], dim=-1))
+        layer = self.layer
+        x, _ = layer.input_layernorm(h, None)
+        part = layer.mixer(x, md, cache)
+        x, residual = reduce_add_norm(part, h, layer.post_attention_layernorm)
+        part = layer.mlp(x)
+        x, _ = reduce_add_norm(part, residual, self.norm)
+        return x
+
+    def compute_logits(self, hidden):
+        return self._target[0].compute_logits(hidden)

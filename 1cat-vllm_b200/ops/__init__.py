@@ -1,0 +1,58 @@
+"""Op entry points. CUDA tensors go to the hand-written sm_100a kernels in the in-tree extension
+(``onecat_vllm.ops.cuda``); CPU tensors go to the PyTorch restatements in ``onecat_vllm.ops.ref``.
+There is no silent fallback: a CUDA tensor without the extension raises."""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from onecat_vllm.ops import ref
+
+_ext = None
+
+
+def ext():
+    global _ext
+    if _ext is None:
+        from onecat_vllm.ops import cuda as _c
+        _ext = _c
+    return _ext
+
+
+def rms_norm(x, w, eps, residual=None, gemma=False):
+    if x.is_cuda:
+        return ext().rms_norm(x, w, eps, residual, gemma)
+    return ref.rms_norm(x, w, eps, residual, gemma)
+
+
+def silu_and_mul(x):
+    if x.is_cuda:
+        return ext().silu_and_mul(x)
+    return ref.silu_and_mul(x)
+
+
+def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w=None, k_norm_w=None,
+                   eps=1e-6, gemma=False):
+    if q.is_cuda:
+        return ext().rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
+    return ref.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
+
+
+def paged_attention(q, kv_cache, md, scale, out=None):
+    """``md`` is the step's AttentionMetadata."""
+    if q.is_cuda:
+        return ext().paged_attention(q, kv_cache, md, scale, out)
+    return ref.paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out)
+
+
+def rms_norm_gated(x, z, w, eps):
+    if x.is_cuda:
+        return ext().rms_norm_gated(x, z, w, eps)
+    return ref.rms_norm_gated(x, z, w, eps)
+
+
+def argmax(logits):
+    if logits.is_cuda:
+        return ext().argmax(logits)
+    return logits.argmax(-1)

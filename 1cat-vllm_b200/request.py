@@ -1,0 +1,192 @@
+"""Engine-side request state (reference: vllm/v1/request.py, v1/engine/__init__.py:42-238)."""
+from __future__ import annotations
+
+import enum
+import time
+from dataclasses import dataclass, field
+from typing import Any, Optional
+
+from onecat_vllm.sampling_params import SamplingParams
+
+
+class FinishReason(enum.IntEnum):
+    STOP = 0
+    LENGTH = 1
+    ABORT = 2
+    ERROR = 3
+
+    def __str__(self) -> str:
+        return ("stop", "length", "abort", "error")[int(self)]
+
+
+class RequestStatus(enum.IntEnum):
+    WAITING = 0
+    RUNNING = 1
+    PREEMPTED = 2
+    FINISHED_STOPPED = 3
+    FINISHED_LENGTH_CAPPED = 4
+    FINISHED_ABORTED = 5
+    FINISHED_ERROR = 6
+
+    @staticmethod
+    def is_finished(s: "RequestStatus") -> bool:
+        return s >= RequestStatus.FINISHED_STOPPED
+
+    @staticmethod
+    def finish_reason(s: "RequestStatus") -> Optional[FinishReason]:
+        return {RequestStatus.FINISHED_STOPPED: FinishReason.STOP, RequestStatus.FINISHED_LENGTH_CAPPED: FinishReason.LENGTH,
+                RequestStatus.FINISHED_ABORTED: FinishReason.ABORT, RequestStatus.FINISHED_ERROR: FinishReason.ERROR}.get(s)
+
+
+@dataclass
+class EngineCoreRequest:
+    """What crosses the frontend → engine-core boundary (reference: v1/engine/__init__.py:82-131)."""
+
+    request_id: str
+    prompt_token_ids: list[int]
+    sampling_params: Optional[SamplingParams]
+    arrival_time: float = 0.0
+    eos_token_id: Optional[int] = None
+    priority: int = 0
+    cache_salt: Optional[str] = None
+    client_index: int = 0
+    data_parallel_rank: Optional[int] = None
+    pooling_params: Any = None
+    lora_request: Any = None
+    trace_headers: Optional[dict] = None
+
+    def to_wire(self) -> dict:
+        return {"request_id": self.request_id, "prompt_token_ids": self.prompt_token_ids,
+                "sampling_params": self.sampling_params.to_dict() if self.sampling_params else None,
+                "arrival_time": self.arrival_time, "eos_token_id": self.eos_token_id, "priority": self.priority,
+                "cache_salt": self.cache_salt, "client_index": self.client_index}
+
+    @classmethod
+    def from_wire(cls, d: dict) -> "EngineCoreRequest":
+        sp = d.get("sampling_params")
+        return cls(d["request_id"], list(d["prompt_token_ids"]), SamplingParams.from_dict(sp) if sp else None,
+                   d.get("arrival_time", 0.0), d.get("eos_token_id"), d.get("priority", 0), d.get("cache_salt"),
+                   d.get("client_index", 0))
+
+
+@dataclass
+class EngineCoreOutput:
+    """Per-request delta produced by one engine step (reference: v1/engine/__init__.py:169-195)."""
+
+    request_id: str
+    new_token_ids: list[int]
+    finish_reason: Optional[FinishReason] = None
+    stop_reason: Optional[int | str] = None
+    new_logprobs: Optional[list] = None  # per new token: (token_ids, logprobs, ranks)
+    prompt_logprobs: Optional[list] = None
+    num_cached_tokens: int = 0
+    events: Optional[list] = None
+
+    @property
+    def finished(self) -> bool:
+        return self.finish_reason is not None
+
+    def to_wire(self) -> dict:
+        return {"request_id": self.request_id, "new_token_ids": self.new_token_ids,
+                "finish_reason": None if self.finish_reason is None else int(self.finish_reason),
+                "stop_reason": self.stop_reason, "new_logprobs": self.new_logprobs,
+                "prompt_logprobs": self.prompt_logprobs, "num_cached_tokens": self.num_cached_tokens}
+
+    @classmethod
+    def from_wire(cls, d: dict) -> "EngineCoreOutput":
+        fr = d.get("finish_reason")
+        return cls(d["request_id"], list(d["new_token_ids"]), None if fr is None else FinishReason(fr), d.get("stop_reason"),
+                   d.get("new_logprobs"), d.get("prompt_logprobs"), d.get("num_cached_tokens", 0))
+
+
+@dataclass
+class EngineCoreOutputs:
+    """One step's outputs for one client (reference: v1/engine/__init__.py:214-238)."""
+
+    outputs: list[EngineCoreOutput] = field(default_factory=list)
+    scheduler_stats: Any = None
+    timestamp: float = 0.0
+    engine_index: int = 0
+    finished_requests: Optional[set] = None
+    utility_output: Any = None
+
+    def __post_init__(self) -> None:
+        if not self.timestamp:
+            self.timestamp = time.monotonic()
+
+
+class Request:
+    """Scheduler-side request. Tokens = prompt + outputs; ``num_computed_tokens`` chases
+    ``num_tokens_with_spec`` (reference: v1/core/sched/scheduler.py:459-468)."""
+
+    def __init__(self, request_id: str, prompt_token_ids: list[int], sampling_params: Optional[SamplingParams],
+                 eos_token_id: Optional[int] = None, arrival_time: Optional[float] = None, priority: int = 0,
+                 cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None) -> None:
+        self.request_id = request_id
+        self.prompt_token_ids = list(prompt_token_ids)
+        self.sampling_params = sampling_params
+        self.pooling_params = pooling_params
+        self.eos_token_id = eos_token_id
+        self.arrival_time = time.time() if arrival_time is None else arrival_time
+        self.priority = priority
+        self.cache_salt = cache_salt
+        self.client_index = client_index
+        self.status = RequestStatus.WAITING
+        self.stop_reason: Optional[int | str] = None
+        self.num_prompt_tokens = len(self.prompt_token_ids)
+        self._output_token_ids: list[int] = []
+        self._all_token_ids: list[int] = list(self.prompt_token_ids)
+        self.spec_token_ids: list[int] = []
+        self.num_computed_tokens = 0
+        self.num_cached_tokens = -1
+        self.num_preemptions = 0
+        self.num_output_placeholders = 0  # async scheduling
+        self.max_tokens = sampling_params.max_tokens if sampling_params and sampling_params.max_tokens is not None else 1 << 30
+        self.block_hashes: list[bytes] = []
+        self._block_hasher = block_hasher
+        self.events: list = []
+        self.first_scheduled_time: Optional[float] = None
+        if block_hasher is not None:
+            self.block_hashes = block_hasher(self)
+
+    @classmethod
+    def from_engine_core_request(cls, r: EngineCoreRequest, block_hasher=None) -> "Request":
+        return cls(r.request_id, r.prompt_token_ids, r.sampling_params, r.eos_token_id, r.arrival_time, r.priority,
+                   r.cache_salt, r.client_index, block_hasher, r.pooling_params)
+
+    def append_output_token_ids(self, ids: int | list[int]) -> None:
+        if isinstance(ids, int):
+            ids = [ids]
+        self._output_token_ids.extend(ids)
+        self._all_token_ids.extend(ids)
+        if self._block_hasher is not None:
+            self.block_hashes.extend(self._block_hasher(self))
+
+    @property
+    def output_token_ids(self) -> list[int]:
+        return self._output_token_ids
+
+    @property
+    def all_token_ids(self) -> list[int]:
+        return self._all_token_ids
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self._all_token_ids)
+
+    @property
+    def num_tokens_with_spec(self) -> int:
+        return len(self._all_token_ids) + len(self.spec_token_ids)
+
+    @property
+    def num_output_tokens(self) -> int:
+        return len(self._output_token_ids)
+
+    def is_finished(self) -> bool:
+        return RequestStatus.is_finished(self.status)
+
+    def get_finished_reason(self) -> Optional[FinishReason]:
+        return RequestStatus.finish_reason(self.status)
+
+    def __lt__(self, other: "Request") -> bool:  # priority queue order (reference: request_queue.py:131)
+        return (self.priority, self.arrival_time, self.request_id) < (other.priority, other.arrival_time, other.request_id)

@@ -1,0 +1,165 @@
+"""Sampling parameters of a request.
+
+Same field names and defaults as the reference's msgspec struct
+(reference: vllm/sampling_params.py:198-346); greedy iff ``temperature < 1e-5``
+(reference: vllm/sampling_params.py:26).
+"""
+from __future__ import annotations
+
+import copy
+from dataclasses import dataclass, field
+from enum import IntEnum
+from typing import Any, Optional, Union
+
+_SAMPLING_EPS = 1e-5
+_MAX_TEMP = 1e-2
+
+
+class SamplingType(IntEnum):
+    GREEDY = 0
+    RANDOM = 1
+    RANDOM_SEED = 2
+
+
+class RequestOutputKind(IntEnum):
+    CUMULATIVE = 0  # whole output so far on every update
+    DELTA = 1  # only new tokens/text
+    FINAL_ONLY = 2  # nothing until the request is finished
+
+
+@dataclass
+class StructuredOutputsParams:
+    json: Optional[Union[str, dict]] = None
+    regex: Optional[str] = None
+    choice: Optional[list[str]] = None
+    grammar: Optional[str] = None
+    json_object: Optional[bool] = None
+
+    def kind(self) -> str:
+        for k in ("json", "regex", "choice", "grammar", "json_object"):
+            if getattr(self, k):
+                return k
+        return "none"
+
+
+@dataclass
+class SamplingParams:
+    n: int = 1
+    presence_penalty: float = 0.0
+    frequency_penalty: float = 0.0
+    repetition_penalty: float = 1.0
+    temperature: float = 1.0
+    top_p: float = 1.0
+    top_k: int = 0
+    min_p: float = 0.0
+    seed: Optional[int] = None
+    stop: Optional[Union[str, list[str]]] = None
+    stop_token_ids: Optional[list[int]] = None
+    ignore_eos: bool = False
+    max_tokens: Optional[int] = 16
+    min_tokens: int = 0
+    logprobs: Optional[int] = None
+    prompt_logprobs: Optional[int] = None
+    detokenize: bool = True
+    skip_special_tokens: bool = True
+    spaces_between_special_tokens: bool = True
+    include_stop_str_in_output: bool = False
+    logit_bias: Optional[dict[int, float]] = None
+    allowed_token_ids: Optional[list[int]] = None
+    bad_words: Optional[list[str]] = None
+    bad_words_token_ids: Optional[list[list[int]]] = None
+    structured_outputs: Optional[StructuredOutputsParams] = None
+    output_kind: RequestOutputKind = RequestOutputKind.CUMULATIVE
+    extra_args: Optional[dict[str, Any]] = None
+    # internal: eos ids resolved by the input processor
+    _eos_token_id: Optional[int] = field(default=None, repr=False)
+    _all_stop_token_ids: set = field(default_factory=set, repr=False)
+
+    def __post_init__(self) -> None:
+        if isinstance(self.stop, str):
+            self.stop = [self.stop]
+        elif self.stop is None:
+            self.stop = []
+        if self.stop_token_ids is None:
+            self.stop_token_ids = []
+        if 0 < self.temperature < _MAX_TEMP:
+            self.temperature = max(self.temperature, _MAX_TEMP)
+        if self.top_k is None or self.top_k < 0:
+            self.top_k = 0
+        if self.temperature < _SAMPLING_EPS:  # greedy: neutralise the random knobs
+            self.top_p, self.top_k, self.min_p = 1.0, 0, 0.0
+        self._verify()
+        self._all_stop_token_ids = set(self.stop_token_ids)
+
+    def _verify(self) -> None:
+        if not isinstance(self.n, int) or self.n < 1:
+            raise ValueError(f"n must be an int >= 1, got {self.n}")
+        if not -2.0 <= self.presence_penalty <= 2.0:
+            raise ValueError("presence_penalty must be in [-2, 2]")
+        if not -2.0 <= self.frequency_penalty <= 2.0:
+            raise ValueError("frequency_penalty must be in [-2, 2]")
+        if self.repetition_penalty <= 0.0:
+            raise ValueError("repetition_penalty must be > 0")
+        if self.temperature < 0.0:
+            raise ValueError("temperature must be non-negative")
+        if not 0.0 < self.top_p <= 1.0:
+            raise ValueError("top_p must be in (0, 1]")
+        if not 0.0 <= self.min_p <= 1.0:
+            raise ValueError("min_p must be in [0, 1]")
+        if self.max_tokens is not None and self.max_tokens < 1:
+            raise ValueError("max_tokens must be at least 1")
+        if self.min_tokens < 0:
+            raise ValueError("min_tokens must be >= 0")
+        if self.max_tokens is not None and self.min_tokens > self.max_tokens:
+            raise ValueError("min_tokens must be <= max_tokens")
+        if self.logprobs is not None and self.logprobs < -1:
+            raise ValueError("logprobs must be >= -1")
+        if self.stop and not self.detokenize:
+            raise ValueError("stop strings need detokenize=True")
+        if self.n > 1 and self.temperature < _SAMPLING_EPS:
+            raise ValueError("n > 1 needs temperature > 0 (greedy would repeat one sample)")
+
+    @property
+    def sampling_type(self) -> SamplingType:
+        if self.temperature < _SAMPLING_EPS:
+            return SamplingType.GREEDY
+        if self.seed is not None:
+            return SamplingType.RANDOM_SEED
+        return SamplingType.RANDOM
+
+    @property
+    def all_stop_token_ids(self) -> set:
+        return self._all_stop_token_ids
+
+    def update_from_generation_config(self, eos_token_id: Optional[int], extra_eos: Optional[list[int]] = None) -> None:
+        self._eos_token_id = eos_token_id
+        if extra_eos and not self.ignore_eos:
+            self._all_stop_token_ids.update(e for e in extra_eos if e != eos_token_id)
+
+    def clone(self) -> "SamplingParams":
+        return copy.deepcopy(self)
+
+    def to_dict(self) -> dict:
+        d = {k: v for k, v in self.__dict__.items() if not k.startswith("_")}
+        d["output_kind"] = int(self.output_kind)
+        if self.structured_outputs is not None:
+            d["structured_outputs"] = dict(self.structured_outputs.__dict__)
+        return d
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SamplingParams":
+        d = dict(d)
+        d["output_kind"] = RequestOutputKind(d.get("output_kind", 0))
+        so = d.get("structured_outputs")
+        if isinstance(so, dict):
+            d["structured_outputs"] = StructuredOutputsParams(**so)
+        return cls(**d)
+
+
+@dataclass
+class PoolingParams:
+    """Parameters of an embedding / classify request (reference: vllm/pooling_params.py)."""
+
+    task: str = "embed"
+    normalize: bool = True
+    dimensions: Optional[int] = None

@@ -1,0 +1,504 @@
+"""Model runner: persistent request state → flat step inputs → forward → logits → sampling / verification →
+draft proposal (reference: vllm/v1/worker/gpu_model_runner.py:1091 class, :2182 ``_update_states``, :4705
+``_prepare_inputs``, :5159 ``_build_attention_metadata``, :8051 ``execute_model``, :8576 ``sample_tokens``, :9331
+``propose_draft_token_ids``; gpu_input_batch.py:92; block_table.py:18,466).
+
+The same class runs on CPU (torch ops, fp32) and on a B200 (hand-written kernels, pinned staging buffers, CUDA
+graphs for uniform decode batches). Each step copies that step's inputs host→device from pinned memory and reads
+the sampled ids back, so a step timed end to end includes both transfers.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from onecat_vllm.config import VllmConfig
+from onecat_vllm.core.kv_cache_utils import KVCacheConfig, KVCacheSpec
+from onecat_vllm.core.sched_output import ModelRunnerOutput, SchedulerOutput
+from onecat_vllm.logger import init_logger
+from onecat_vllm.sample.metadata import SamplingMetadata
+from onecat_vllm.sample.rejection_sampler import RejectionSampler
+from onecat_vllm.sample.sampler import Sampler, to_logprobs_lists
+from onecat_vllm.worker.attn_metadata import AttentionMetadata
+
+log = init_logger(__name__)
+
+
+@dataclass
+class CachedRequestState:
+    req_id: str
+    token_ids: list  # prompt + outputs known to the runner
+    num_prompt_tokens: int
+    sampling_params: object
+    block_ids: list
+    num_computed_tokens: int
+    state_slot: int = -1
+    generator: Optional[torch.Generator] = None
+    eos_token_id: Optional[int] = None
+
+
+class ModelRunner:
+    def __init__(self, vllm_config: VllmConfig, device: torch.device):
+        self.cfg = vllm_config
+        self.mc = vllm_config.model_config
+        self.device = device
+        self.use_cuda = device.type == "cuda"
+        self.block_size = vllm_config.cache_config.block_size
+        self.max_model_len = self.mc.max_model_len
+        self.max_num_tokens = vllm_config.scheduler_config.max_num_batched_tokens
+        self.max_num_reqs = vllm_config.scheduler_config.max_num_seqs
+        self.requests: dict[str, CachedRequestState] = {}
+        self.model = None
+        self.mtp = None
+        self.kv_caches: list = []
+        self.mtp_cache = None
+        self.sampler = Sampler()
+        sc = vllm_config.speculative_config
+        self.spec = sc
+        self.num_spec = sc.num_speculative_tokens if sc.enabled else 0
+        self.rejection_sampler = RejectionSampler(sc.conditional_rates(), sc.synthetic_seed) if sc.enabled else None
+        self.proposer = None
+        self.graphs = None  # worker.cuda_graphs.DecodeGraphs
+        self._last_step_ms = 0.0
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        self.kernel_launches = 0
+
+    # ------------------------------------------------------------------ model / cache set-up
+    def load_model(self) -> None:
+        from onecat_vllm.loader.weights import load_model
+        t0 = time.time()
+        self.model = load_model(self.mc, self.device)
+        if self.spec.method == "mtp":
+            from onecat_vllm.loader.weights import dummy_init, process_weights_after_loading
+            from onecat_vllm.models.decoder import MTPHead
+            with torch.device(self.device):
+                self.mtp = MTPHead(self.mc, self.model, self.device)
+            dummy_init(self.mtp, self.mc.seed + 1)
+            process_weights_after_loading(self.mtp)
+            self.mtp.eval()
+        if self.spec.enabled:
+            from onecat_vllm.spec_decode.proposers import make_proposer
+            self.proposer = make_proposer(self)
+        log.info_once(f"model {self.mc.architecture} ready in {time.time() - t0:.1f}s on {self.device}")
+
+    def get_kv_cache_specs(self) -> dict:
+        mc, specs = self.mc, {}
+        esz = torch.empty(0, dtype=self._kv_dtype()).element_size()
+        for i, layer in enumerate(self.model.model.layers):
+            if layer.kind == "linear_attention":
+                (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
+                nspec = self.num_spec + 1
+                specs[f"layers.{i}"] = KVCacheSpec("mamba", self.block_size, 0, 0, 0,
+                                                    state_bytes=(cd * kw * esz + hv * k * v * 4))
+            elif layer.kind == "mla":
+                specs[f"layers.{i}"] = KVCacheSpec("mla", self.block_size, 1, mc.kv_lora_rank + mc.qk_rope_head_dim, esz)
+            else:
+                specs[f"layers.{i}"] = KVCacheSpec("full", self.block_size, layer.self_attn.Hkv, mc.head_dim, esz)
+        if self.mtp is not None:
+            a = self.mtp.layer.self_attn
+            if self.mc.use_mla:
+                specs["mtp.0"] = KVCacheSpec("mla", self.block_size, 1, mc.kv_lora_rank + mc.qk_rope_head_dim, esz)
+            else:
+                specs["mtp.0"] = KVCacheSpec("full", self.block_size, a.Hkv, mc.head_dim, esz)
+        return specs
+
+    def _kv_dtype(self) -> torch.dtype:
+        return self.mc.dtype
+
+    def initialize_kv_cache(self, kvc: KVCacheConfig) -> None:
+        self.kv_cache_config = kvc
+        dt, dev, nb, bs = self._kv_dtype(), self.device, kvc.num_blocks, self.block_size
+
+        def alloc(spec: KVCacheSpec):
+            if spec.kind == "mamba":
+                return None
+            if spec.kind == "mla":
+                return torch.zeros(nb, bs, spec.head_size, dtype=dt, device=dev)
+            return torch.zeros(nb, 2, spec.num_kv_heads, bs, spec.head_size, dtype=dt, device=dev)
+
+        self.kv_caches = []
+        for i, layer in enumerate(self.model.model.layers):
+            spec = kvc.layer_specs[f"layers.{i}"]
+            if spec.kind == "mamba":
+                (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
+                slots = kvc.num_state_slots
+                self.kv_caches.append((torch.zeros(slots, cd, kw, dtype=dt, device=dev),
+                                       torch.zeros(slots, hv, k, v, dtype=torch.float32, device=dev)))
+            else:
+                self.kv_caches.append(alloc(spec))
+        if self.mtp is not None:
+            self.mtp_cache = alloc(kvc.layer_specs["mtp.0"])
+        self.max_blocks_per_req = -(-self.max_model_len // bs)
+        self._init_buffers()
+
+    def _init_buffers(self) -> None:
+        """Pinned host staging + persistent device buffers (fixed addresses for CUDA graphs)."""
+        T, R, MB = self.max_num_tokens, self.max_num_reqs, self.max_blocks_per_req
+        pin = self.use_cuda
+
+        def host(n, dt):
+            t = torch.zeros(n, dtype=dt)
+            return t.pin_memory() if pin else t
+
+        # one packed int32 staging area: ids | positions | slot_mapping | qsl | seq_lens | state_slots | has_init | logit_idx
+        self._seg = {"ids": T, "pos": T, "slot": T, "qsl": R + 1, "seq": R, "sslot": R, "hinit": R, "lidx": T}
+        total = sum(self._seg.values())
+        self.h_pack = host(total, torch.int32)
+        self.d_pack = torch.zeros(total, dtype=torch.int32, device=self.device)
+        self.h_bt = host(R * MB, torch.int32).view(R, MB)
+        self.d_bt = torch.zeros(R, MB, dtype=torch.int32, device=self.device)
+        off, self._off = 0, {}
+        for k, n in self._seg.items():
+            self._off[k] = (off, n)
+            off += n
+        self.np_pack = self.h_pack.numpy()
+        self.np_bt = self.h_bt.numpy()
+
+    def _view(self, name: str, n: int, dev: bool = True) -> torch.Tensor:
+        o, _ = self._off[name]
+        return (self.d_pack if dev else self.h_pack)[o:o + n]
+
+    # ------------------------------------------------------------------ state tracking
+    def _update_states(self, so: SchedulerOutput) -> None:
+        for rid in so.finished_req_ids:
+            self.requests.pop(rid, None)
+        for rid in so.preempted_req_ids:
+            self.requests.pop(rid, None)
+        for nr in so.scheduled_new_reqs:
+            sp = nr.sampling_params
+            gen = None
+            if sp is not None and sp.seed is not None:
+                gen = torch.Generator(device=self.device)
+                gen.manual_seed(sp.seed)
+            self.requests[nr.req_id] = CachedRequestState(nr.req_id, list(nr.prompt_token_ids), len(nr.prompt_token_ids), sp,
+                                                          list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id)
+        c = so.scheduled_cached_reqs
+        for i, rid in enumerate(c.req_ids):
+            st = self.requests.get(rid)
+            if c.resumed_from_preemption[i] or st is None:
+                toks = c.new_token_ids[i]
+                old = st
+                st = CachedRequestState(rid, list(toks), old.num_prompt_tokens if old else len(toks), old.sampling_params if old else None,
+                                        list(c.new_block_ids[i] or []), c.num_computed_tokens[i], c.state_slots[i],
+                                        old.generator if old else None, old.eos_token_id if old else None)
+                self.requests[rid] = st
+            else:
+                st.num_computed_tokens = c.num_computed_tokens[i]
+                if c.new_block_ids[i]:
+                    st.block_ids.extend(c.new_block_ids[i])
+                st.state_slot = c.state_slots[i]
+                # the scheduler may have dropped tokens past a rejected draft; keep only what it counts
+        # preempted requests keep their sampling params for when they resume
+        for rid in so.preempted_req_ids:
+            pass
+
+    # ------------------------------------------------------------------ input preparation
+    def _prepare_inputs(self, so: SchedulerOutput):
+        req_ids = list(so.num_scheduled_tokens.keys())
+        R = len(req_ids)
+        T = so.total_num_scheduled_tokens
+        bs = self.block_size
+        npk, o = self.np_pack, self._off
+        ids = npk[o["ids"][0]: o["ids"][0] + T]
+        pos = npk[o["pos"][0]: o["pos"][0] + T]
+        slot = npk[o["slot"][0]: o["slot"][0] + T]
+        qsl = npk[o["qsl"][0]: o["qsl"][0] + R + 1]
+        seq = npk[o["seq"][0]: o["seq"][0] + R]
+        sslot = npk[o["sslot"][0]: o["sslot"][0] + R]
+        hinit = npk[o["hinit"][0]: o["hinit"][0] + R]
+        lidx_buf = npk[o["lidx"][0]: o["lidx"][0] + self._seg["lidx"]]
+        qsl[0] = 0
+        t = 0
+        max_q = max_s = 0
+        logits_rows: list[int] = []  # how many logits rows each request contributes
+        n_l = 0
+        max_nb = 1
+        drafts_of: list = []
+        for r, rid in enumerate(req_ids):
+            st = self.requests[rid]
+            n = so.num_scheduled_tokens[rid]
+            start = st.num_computed_tokens
+            drafts = so.scheduled_spec_decode_tokens.get(rid, [])
+            known = st.token_ids
+            end = start + n
+            nk = min(end, len(known)) - start
+            if nk > 0:
+                ids[t:t + nk] = known[start:start + nk]
+            if end > len(known):
+                nd = end - len(known)
+                ids[t + nk:t + n] = drafts[:nd]
+            pos[t:t + n] = np.arange(start, end, dtype=np.int32)
+            b = np.asarray(st.block_ids, dtype=np.int32)
+            p = pos[t:t + n]
+            slot[t:t + n] = b[p // bs] * bs + p % bs
+            nb = -(-end // bs)
+            self.np_bt[r, :nb] = b[:nb]
+            max_nb = max(max_nb, nb)
+            seq[r] = end
+            sslot[r] = st.state_slot
+            hinit[r] = 1 if start > 0 else 0
+            # sampling positions: the request reaches the end of its known tokens in this step
+            if end >= len(known):
+                k = 1 + max(end - len(known), 0)
+                lidx_buf[n_l:n_l + k] = np.arange(t + n - k, t + n, dtype=np.int32)
+                n_l += k
+                logits_rows.append(k)
+            else:
+                logits_rows.append(0)
+            drafts_of.append(drafts[: max(end - len(known), 0)])
+            t += n
+            qsl[r + 1] = t
+            max_q, max_s = max(max_q, n), max(max_s, end)
+        assert t == T
+        return req_ids, R, T, n_l, logits_rows, drafts_of, max_q, max_s, max_nb
+
+    def _commit_inputs(self, R: int, T: int, n_l: int, max_nb: int) -> None:
+        """Host → device copies of this step's inputs (non-blocking from pinned memory on GPUs)."""
+        if self.use_cuda:
+            self.d_pack.copy_(self.h_pack, non_blocking=True)
+            self.d_bt[:R, :max_nb].copy_(self.h_bt[:R, :max_nb], non_blocking=True)
+            self.h2d_bytes = self.h_pack.numel() * 4 + R * max_nb * 4
+        else:
+            self.d_pack.copy_(self.h_pack)
+            self.d_bt[:R, :max_nb].copy_(self.h_bt[:R, :max_nb])
+
+    def _build_metadata(self, R, T, max_q, max_s, max_nb, query_lens, seq_lens) -> AttentionMetadata:
+        return AttentionMetadata(
+            num_reqs=R, num_tokens=T, query_start_loc=self._view("qsl", R + 1), seq_lens=self._view("seq", R),
+            block_table=self.d_bt[:R, :max_nb] if not self.use_cuda else self.d_bt[:R], slot_mapping=self._view("slot", T),
+            positions=self._view("pos", T), max_query_len=max_q, max_seq_len=max_s, state_slots=self._view("sslot", R),
+            has_initial_state=self._view("hinit", R), query_lens_cpu=query_lens, seq_lens_cpu=seq_lens,
+            is_uniform_decode=(max_q == min(query_lens)) and max_q <= 1 + self.num_spec, uniform_query_len=max_q)
+
+    def _sampling_metadata(self, req_ids: list, rows: list[int]) -> SamplingMetadata:
+        """One entry per *sampling request* (requests contributing logits rows this step)."""
+        sel = [self.requests[rid] for rid, k in zip(req_ids, rows) if k > 0]
+        sps = [s.sampling_params for s in sel]
+        dev = self.device
+        temps = [sp.temperature if sp else 0.0 for sp in sps]
+        all_greedy = all(t < 1e-5 for t in temps)
+        all_random = all(t >= 1e-5 for t in temps)
+        f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
+        no_pen = all((sp is None) or (sp.presence_penalty == 0 and sp.frequency_penalty == 0 and sp.repetition_penalty == 1.0) for sp in sps)
+        need_k = any(sp and sp.top_k > 0 for sp in sps)
+        need_p = any(sp and sp.top_p < 1.0 for sp in sps)
+        need_m = any(sp and sp.min_p > 0 for sp in sps)
+        lps = [sp.logprobs for sp in sps if sp and sp.logprobs is not None]
+        md = SamplingMetadata(
+            temperature=None if all_greedy else f32(temps), all_greedy=all_greedy, all_random=all_random,
+            top_p=f32([sp.top_p for sp in sps]) if need_p else None,
+            top_k=torch.tensor([sp.top_k for sp in sps], dtype=torch.int64, device=dev) if need_k else None,
+            min_p=f32([sp.min_p for sp in sps]) if need_m else None,
+            generators={i: s.generator for i, s in enumerate(sel) if s.generator is not None},
+            max_num_logprobs=max(lps) if lps else None, no_penalties=no_pen)
+        if not no_pen:
+            md.presence_penalties = f32([sp.presence_penalty for sp in sps])
+            md.frequency_penalties = f32([sp.frequency_penalty for sp in sps])
+            md.repetition_penalties = f32([sp.repetition_penalty for sp in sps])
+            md.prompt_token_ids = [s.token_ids[: s.num_prompt_tokens] for s in sel]
+        md.output_token_ids = [s.token_ids[s.num_prompt_tokens:] for s in sel]
+        for i, (s, sp) in enumerate(zip(sel, sps)):
+            if sp is None:
+                continue
+            if sp.min_tokens > 0:
+                stops = set(sp.all_stop_token_ids)
+                if s.eos_token_id is not None and not sp.ignore_eos:
+                    stops.add(s.eos_token_id)
+                md.min_tokens[i] = (sp.min_tokens, stops)
+            if sp.bad_words_token_ids:
+                md.bad_words_token_ids[i] = sp.bad_words_token_ids
+        md.logit_bias = [sp.logit_bias if sp else None for sp in sps]
+        md.allowed_token_ids = [sp.allowed_token_ids if sp else None for sp in sps]
+        return md
+
+    # ------------------------------------------------------------------ one step
+    @torch.inference_mode()
+    def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+        self._update_states(so)
+        if so.total_num_scheduled_tokens == 0:
+            return ModelRunnerOutput()
+        req_ids, R, T, n_l, rows, drafts_of, max_q, max_s, max_nb = self._prepare_inputs(so)
+        query_lens = [so.num_scheduled_tokens[r] for r in req_ids]
+        seq_lens = [self.requests[r].num_computed_tokens + q for r, q in zip(req_ids, query_lens)]
+        timed = self.use_cuda
+        if timed:
+            ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev0.record()
+        self._commit_inputs(R, T, n_l, max_nb)
+        md = self._build_metadata(R, T, max_q, max_s, max_nb, query_lens, seq_lens)
+        spec_verify = any(len(d) > 0 for d in drafts_of)
+        gdn_spec = None
+        if spec_verify and self.mc.is_hybrid:
+            gdn_spec = self._begin_gdn_spec(md)
+        ids = self._view("ids", T)
+        hidden = None
+        if self.graphs is not None and md.is_uniform_decode and not (spec_verify and self.mc.is_hybrid):
+            hidden = self.graphs.run(self, md, ids)
+        if hidden is None:
+            hidden = self.model(ids, md, self.kv_caches)
+        out = ModelRunnerOutput(req_ids=req_ids, sampled_token_ids=[[] for _ in req_ids])
+        sampled_lists: list[list[int]] = [[] for _ in req_ids]
+        if n_l > 0:
+            lidx = self._view("lidx", n_l).long()
+            sample_hidden = hidden[lidx]
+            logits = self.model.compute_logits(sample_hidden)
+            smd = self._sampling_metadata(req_ids, rows)
+            samp_rows = [k for k in rows if k > 0]
+            if not spec_verify:
+                so_ = self.sampler(logits, smd)
+                toks = so_.sampled_token_ids
+                if timed:
+                    ev1.record()
+                host = toks.tolist()  # device → host read of the step's result
+                self.d2h_bytes = len(host) * 8
+                j = 0
+                for i, k in enumerate(rows):
+                    if k > 0:
+                        sampled_lists[i] = [host[j]]
+                        j += 1
+                out.logprobs = self._scatter_logprobs(so_.logprobs, rows)
+            else:
+                sampled_lists = self._verify(logits, smd, rows, drafts_of)
+                if timed:
+                    ev1.record()
+            out.prompt_logprobs = None
+        elif timed:
+            ev1.record()
+        if gdn_spec is not None:
+            self._commit_gdn_spec(gdn_spec, md, sampled_lists, drafts_of)
+        # bookkeeping: the runner owns the token history of running requests
+        for i, rid in enumerate(req_ids):
+            st = self.requests[rid]
+            if sampled_lists[i]:
+                end = st.num_computed_tokens + query_lens[i]
+                # tokens are appended after the last *known* token
+                st.token_ids.extend(sampled_lists[i])
+        out.sampled_token_ids = sampled_lists
+        if self.proposer is not None and n_l > 0:
+            out.spec_token_ids = self.proposer.propose(self, so, req_ids, rows, sampled_lists, hidden, md, drafts_of)
+        if timed:
+            torch.cuda.synchronize()
+            out.device_time_ms = ev0.elapsed_time(ev1)
+        if self.use_cuda:
+            from onecat_vllm.ops import cuda as K
+            out.status = K.check_status()
+        return out
+
+    def _scatter_logprobs(self, lp, rows):
+        if lp is None:
+            return None
+        lists = to_logprobs_lists(lp, [1] * sum(1 for k in rows if k > 0))
+        out, j = [], 0
+        for k in rows:
+            if k > 0:
+                out.append(lists[j])
+                j += 1
+            else:
+                out.append(None)
+        return out
+
+    def _verify(self, logits, smd, rows, drafts_of) -> list[list[int]]:
+        """Rejection-sample requests that carried drafts; plain-sample the rest. ``logits`` rows are grouped per
+        request (k_i + 1 rows for a request with k_i drafts)."""
+        k = self.num_spec
+        B = sum(1 for r in rows if r > 0)
+        V = logits.shape[-1]
+        dev = logits.device
+        tl = torch.zeros(B, k + 1, V, dtype=logits.dtype, device=dev)
+        draft = torch.zeros(B, k, dtype=torch.long, device=dev)
+        nd = torch.zeros(B, dtype=torch.long, device=dev)
+        last_rows, j, b = [], 0, 0
+        nd_host = []
+        for i, r in enumerate(rows):
+            if r == 0:
+                continue
+            d = drafts_of[i]
+            tl[b, :r] = logits[j:j + r]
+            if d:
+                draft[b, : len(d)] = torch.tensor(d, device=dev)
+            nd_host.append(len(d))
+            last_rows.append(j + r - 1)
+            j += r
+            b += 1
+        nd.copy_(torch.tensor(nd_host))
+        bonus = self.sampler(logits[torch.tensor(last_rows, device=dev)], smd).sampled_token_ids
+        res = self.rejection_sampler(draft, nd, tl, bonus, smd)
+        parsed = RejectionSampler.parse_output(res)
+        self.d2h_bytes = res.numel() * 8
+        out, b = [], 0
+        for r in rows:
+            if r == 0:
+                out.append([])
+            else:
+                out.append(parsed[b])
+                b += 1
+        return out
+
+    # ---- Gated-DeltaNet state under speculation: per-token candidate states, commit the accepted one
+    def _begin_gdn_spec(self, md):
+        R, k1 = md.num_reqs, self.num_spec + 1
+        spec = []
+        for layer, cache in zip(self.model.model.layers, self.kv_caches):
+            if layer.kind != "linear_attention":
+                spec.append(None)
+                continue
+            conv, ssm = cache
+            spec.append((conv[md.state_slots.long()].clone(), ssm[md.state_slots.long()].clone()))
+        md.gdn_snapshots = spec
+        return spec
+
+    def _commit_gdn_spec(self, spec, md, sampled, drafts_of) -> None:
+        """Requests whose drafts were partly rejected: restore the pre-step state and replay the accepted tokens
+        through the GDN layers is not possible without their inputs, so those requests keep per-token states:
+        the forward above recorded them in ``md.gdn_token_states``; pick the state after the last valid token."""
+        rec = getattr(md, "gdn_token_states", None)
+        if rec is None:
+            return
+        slots = md.state_slots.long()
+        n_valid = torch.tensor([max(len(s), 1) for s in sampled], device=self.device)
+        ar = torch.arange(md.num_reqs, device=self.device)
+        for li, states in rec.items():
+            conv_t, ssm_t = states  # [R, q, ...]
+            conv, ssm = self.kv_caches[li]
+            idx = (n_valid - 1).clamp(max=conv_t.shape[1] - 1)
+            conv[slots] = conv_t[ar, idx]
+            ssm[slots] = ssm_t[ar, idx]
+
+    # ------------------------------------------------------------------ profiling helpers
+    @torch.inference_mode()
+    def dummy_run(self, num_tokens: int, num_reqs: int = 1) -> None:
+        """Max-shape forward used for memory profiling and kernel warm-up; touches no request state."""
+        T, R = num_tokens, max(1, min(num_reqs, num_tokens))
+        per = T // R
+        qsl = torch.arange(0, R + 1, dtype=torch.int32, device=self.device) * per
+        qsl[-1] = T
+        seq = (qsl[1:] - qsl[:-1]).to(torch.int32)
+        nb = -(-int(seq.max()) // self.block_size)
+        md = AttentionMetadata(R, T, qsl, seq, torch.zeros(R, max(nb, 1), dtype=torch.int32, device=self.device),
+                               torch.full((T,), -1, dtype=torch.int32, device=self.device),
+                               torch.zeros(T, dtype=torch.int32, device=self.device), int(seq.max()), int(seq.max()),
+                               torch.zeros(R, dtype=torch.int32, device=self.device), torch.zeros(R, dtype=torch.int32, device=self.device),
+                               seq.tolist(), seq.tolist())
+        ids = torch.zeros(T, dtype=torch.int32, device=self.device)
+        caches = self.kv_caches if self.kv_caches else self._tiny_caches()
+        h = self.model(ids, md, caches)
+        self.model.compute_logits(h[:R])
+
+    def _tiny_caches(self):
+        """One-block caches so the profiling forward can run before the real cache exists."""
+        out = []
+        dt = self._kv_dtype()
+        for layer in self.model.model.layers:
+            if layer.kind == "linear_attention":
+                (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
+                out.append((torch.zeros(1, cd, kw, dtype=dt, device=self.device), torch.zeros(1, hv, k, v, dtype=torch.float32, device=self.device)))
+            elif layer.kind == "mla":
+                out.append(torch.zeros(1, self.block_size, self.mc.kv_lora_rank + self.mc.qk_rope_head_dim, dtype=dt, device=self.device))
+            else:
+                out.append(torch.zeros(1, 2, layer.self_attn.Hkv, self.block_size, self.mc.head_dim, dtype=dt, device=self.device))
+        return out

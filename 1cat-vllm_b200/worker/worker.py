@@ -1,0 +1,134 @@
+"""Per-device worker: device + process-group init, model load, memory profiling, KV allocation, warm-up and
+CUDA-graph capture, step execution (reference: vllm/v1/worker/gpu_worker.py:112 class, :244 ``init_device``, :343
+``load_model``, :366 ``determine_available_memory``, :552 ``initialize_from_config``, :581
+``compile_or_warm_up_model``, :792 ``execute_model``; CPU variant v1/worker/cpu_worker.py:33)."""
+from __future__ import annotations
+
+import gc
+import os
+from typing import Optional
+
+import torch
+
+from onecat_vllm.config import VllmConfig
+from onecat_vllm.core.kv_cache_utils import KVCacheConfig, get_kv_cache_config
+from onecat_vllm.core.sched_output import ModelRunnerOutput, SchedulerOutput
+from onecat_vllm.logger import decorate_logs, init_logger
+from onecat_vllm.parallel import state as ps
+from onecat_vllm.worker.model_runner import ModelRunner
+
+log = init_logger(__name__)
+
+
+class Worker:
+    def __init__(self, vllm_config: VllmConfig, rank: int = 0, local_rank: int = 0, init_method: Optional[str] = None):
+        self.cfg = vllm_config
+        self.rank, self.local_rank = rank, local_rank
+        self.init_method = init_method
+        self.runner: Optional[ModelRunner] = None
+        self.device = torch.device("cpu")
+        self._baseline_free = 0
+        self.sleeping = False
+
+    def init_device(self) -> None:
+        pc = self.cfg.parallel_config
+        if self.cfg.device == "cuda":
+            torch.cuda.set_device(self.local_rank)
+            self.device = torch.device("cuda", self.local_rank)
+            gc.collect()
+            torch.cuda.empty_cache()
+            self._baseline_free, self._total = torch.cuda.mem_get_info()
+        ps.init_distributed(self.rank, pc.world_size, pc.tensor_parallel_size, pc.pipeline_parallel_size, init_method=self.init_method,
+                            enable_ep=pc.enable_expert_parallel, dcp=pc.decode_context_parallel_size, tp_comm=pc.tp_comm)
+        if pc.world_size > 1:
+            decorate_logs(f"Worker_TP{ps.tp_rank()}")
+        if self.cfg.device == "cuda" and pc.tensor_parallel_size > 1 and pc.tp_comm == "fused":
+            from onecat_vllm.parallel.fused import FusedTP
+            ps.get_state().fused = FusedTP.create(self.cfg, self.device)
+        self.runner = ModelRunner(self.cfg, self.device)
+
+    def load_model(self) -> None:
+        self.runner.load_model()
+
+    def get_kv_cache_specs(self) -> dict:
+        return self.runner.get_kv_cache_specs()
+
+    def determine_available_memory(self) -> int:
+        """Bytes available for the KV cache: requested share of the device minus what weights and a max-token
+        profiling forward need."""
+        cc = self.cfg.cache_config
+        if cc.kv_cache_memory_bytes is not None:
+            return cc.kv_cache_memory_bytes
+        if self.device.type != "cuda":
+            return int(os.environ.get("ONECAT_CPU_KVCACHE_BYTES", 1 << 30))
+        torch.cuda.reset_peak_memory_stats()
+        self.runner.dummy_run(self.cfg.scheduler_config.max_num_batched_tokens, 1)
+        torch.cuda.synchronize()
+        peak = torch.cuda.max_memory_allocated()
+        free, total = torch.cuda.mem_get_info()
+        non_torch = (total - free) - torch.cuda.memory_reserved()
+        budget = int(total * cc.gpu_memory_utilization)
+        avail = budget - peak - max(non_torch, 0)
+        torch.cuda.empty_cache()
+        log.info_once(f"memory: total {total >> 20} MiB, peak torch {peak >> 20} MiB, KV budget {avail >> 20} MiB")
+        return max(avail, 0)
+
+    def initialize_from_config(self, kvc: KVCacheConfig) -> None:
+        self.runner.initialize_kv_cache(kvc)
+
+    def compile_or_warm_up_model(self) -> None:
+        if self.device.type != "cuda":
+            return
+        self.runner.dummy_run(min(256, self.cfg.scheduler_config.max_num_batched_tokens), 4)
+        from onecat_vllm import envs
+        if not self.cfg.enforce_eager and envs.ONECAT_USE_CUDA_GRAPH:
+            from onecat_vllm.worker.cuda_graphs import DecodeGraphs
+            self.runner.graphs = DecodeGraphs(self.runner)
+            self.runner.graphs.capture_all()
+        torch.cuda.synchronize()
+
+    def execute_model(self, so: SchedulerOutput) -> Optional[ModelRunnerOutput]:
+        out = self.runner.execute_model(so)
+        return out if ps.get_state().rank == 0 or True else None
+
+    # ---- utility RPCs (reference: gpu_worker.py:160-200 sleep/wake, :885 profile, :958 save_sharded_state)
+    def sleep(self, level: int = 1) -> None:
+        """Level 1 drops the KV cache contents; level 2 also releases it."""
+        if self.runner.kv_caches and level >= 2:
+            self.runner.kv_caches = []
+            if self.device.type == "cuda":
+                torch.cuda.empty_cache()
+        self.sleeping = True
+
+    def wake_up(self) -> None:
+        if not self.runner.kv_caches:
+            self.runner.initialize_kv_cache(self.runner.kv_cache_config)
+        self.sleeping = False
+
+    def profile(self, start: bool) -> None:
+        from onecat_vllm.tracing.profiler import worker_profiler
+        worker_profiler().toggle(start)
+
+    def save_sharded_state(self, path: str) -> None:
+        from safetensors.torch import save_file
+        os.makedirs(path, exist_ok=True)
+        sd = {k: v.detach().cpu().contiguous() for k, v in self.runner.model.state_dict().items()
+              if v.dtype not in (torch.float8_e4m3fn,)}
+        save_file(sd, os.path.join(path, f"model-rank-{self.rank}.safetensors"))
+
+    def update_weights(self, named: list) -> int:
+        """In-place weight update for RLHF-style loops (reference: gpu_worker.py:987-1110)."""
+        from onecat_vllm.loader.weights import load_weights, process_weights_after_loading
+        n = len(load_weights(self.runner.model, named))
+        process_weights_after_loading(self.runner.model)
+        return n
+
+    def check_health(self) -> bool:
+        return True
+
+    def shutdown(self) -> None:
+        self.runner = None
+        ps.destroy_distributed()
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()

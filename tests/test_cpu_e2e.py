@@ -1,0 +1,87 @@
+"""CPU plumbing slice: the tiny fp32 Llama/Qwen-style decoder served through the whole engine must reproduce a
+plain HF Transformers greedy decode token for token (32 requests, prompts 16..128 tokens, 64 output tokens)."""
+import torch
+import pytest
+
+from onecat_vllm import LLM, SamplingParams
+
+
+def _hf_model_from(llm, cfg):
+    from transformers import LlamaConfig, LlamaForCausalLM
+    hc = LlamaConfig(hidden_size=cfg["hidden_size"], intermediate_size=cfg["intermediate_size"], num_hidden_layers=cfg["num_hidden_layers"],
+                     num_attention_heads=cfg["num_attention_heads"], num_key_value_heads=cfg["num_key_value_heads"], head_dim=cfg["head_dim"],
+                     rms_norm_eps=cfg["rms_norm_eps"], rope_theta=cfg["rope_theta"], vocab_size=cfg["vocab_size"],
+                     max_position_embeddings=cfg["max_position_embeddings"], tie_word_embeddings=False, attention_bias=False)
+    hf = LlamaForCausalLM(hc).float().eval()
+    m = llm.llm_engine.engine_core.core.executor.worker.runner.model
+    sd = {}
+    H, D = cfg["num_attention_heads"], cfg["head_dim"]
+    KV = cfg["num_key_value_heads"]
+    for k, v in m.state_dict().items():
+        if ".qkv_proj.weight" in k:
+            q, kk, vv = v.split([H * D, KV * D, KV * D], dim=0)
+            sd[k.replace("qkv_proj", "q_proj")] = q
+            sd[k.replace("qkv_proj", "k_proj")] = kk
+            sd[k.replace("qkv_proj", "v_proj")] = vv
+        elif ".gate_up_proj.weight" in k:
+            g, u = v.chunk(2, dim=0)
+            sd[k.replace("gate_up_proj", "gate_proj")] = g
+            sd[k.replace("gate_up_proj", "up_proj")] = u
+        elif k.startswith("lm_head.weight") or "embed_tokens" in k:
+            sd[k] = v[: cfg["vocab_size"]]
+        else:
+            sd[k] = v
+    missing, unexpected = hf.load_state_dict(sd, strict=False)
+    assert not [x for x in missing if "rotary" not in x], missing
+    assert not unexpected, unexpected
+    return hf
+
+
+def _workload(n, seed=0, lo=16, hi=128, vocab=32000):
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(lo, hi + 1, (n,), generator=g)
+    return [torch.randint(0, vocab, (int(l),), generator=g).tolist() for l in lens]
+
+
+@pytest.mark.parametrize("budget,prefix", [(8192, True), (96, False)])
+def test_tiny_llama_token_exact_vs_hf(tiny_llama_cfg, budget, prefix):
+    cfg = tiny_llama_cfg
+    llm = LLM(hf_config=cfg, max_model_len=512, dtype="float32", device="cpu", max_num_batched_tokens=budget, max_num_seqs=16,
+              enable_prefix_caching=prefix, seed=0)
+    prompts = _workload(32 if budget == 8192 else 6)
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True))
+    assert len(outs) == len(prompts)
+    hf = _hf_model_from(llm, cfg)
+    with torch.no_grad():
+        for p, o in zip(prompts, outs):
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=64, do_sample=False, pad_token_id=0, eos_token_id=None)[0, len(p):].tolist()
+            assert o.outputs[0].token_ids == ref, f"prompt len {len(p)}"
+            assert o.outputs[0].finish_reason == "length"
+    llm.shutdown()
+
+
+def test_prefix_cache_hit_gives_same_tokens(tiny_llama_cfg):
+    llm = LLM(hf_config=tiny_llama_cfg, max_model_len=512, dtype="float32", device="cpu")
+    p = _workload(1, seed=3, lo=100, hi=100)[0]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    a = llm.generate([p], sp)[0]
+    b = llm.generate([p + [5, 6, 7]], sp)[0]
+    c = llm.generate([p], sp)[0]
+    assert a.outputs[0].token_ids == c.outputs[0].token_ids
+    assert c.num_cached_tokens == 96  # 6 full blocks of 16; the last token is always recomputed
+    assert b.num_cached_tokens == 96
+    llm.shutdown()
+
+
+def test_seeded_sampling_is_reproducible(tiny_llama_cfg):
+    llm = LLM(hf_config=tiny_llama_cfg, max_model_len=256, dtype="float32", device="cpu")
+    p = _workload(2, seed=1)
+    sp = SamplingParams(temperature=0.8, top_p=0.9, top_k=50, seed=7, max_tokens=12, ignore_eos=True)
+    a = llm.generate(p, sp)
+    b = llm.generate(p, sp)
+    assert [o.outputs[0].token_ids for o in a] == [o.outputs[0].token_ids for o in b]
+    sp2 = SamplingParams(temperature=0.8, seed=8, max_tokens=12, ignore_eos=True, n=2, logprobs=3)
+    c = llm.generate(p[:1], sp2)[0]
+    assert len(c.outputs) == 2 and c.outputs[0].token_ids != c.outputs[1].token_ids
+    assert len(c.outputs[0].logprobs) == 12 and all(len(d) >= 3 for d in c.outputs[0].logprobs)
+    llm.shutdown()

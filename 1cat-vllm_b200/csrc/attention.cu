@@ -1,0 +1,399 @@
+// Paged-KV flash attention for head sizes 128 and 256: causal, GQA-packed, variable-length batches where each
+// request's queries are the last rows of its context (so decode, multi-token verify and chunked prefill over a cached
+// prefix are one kernel family).
+//   mode 0 (prefill): a CTA owns a tile of 64 (token, q-head-in-group) rows of one KV head; its 4 warps own 16 rows each
+//                     and stream 64-key tiles of K and V through double-buffered shared memory.
+//   mode 1 (decode / verify): rows fit in 16 or 32; the 4 warps split each 64-key tile by keys, grid.z splits the context
+//                     (split-KV), partial (max, sum, O) are merged across warps in shared memory and across splits by a
+//                     second small kernel.
+// K/V pages are [block][2][Hkv][block_size][D] so one (page, head) is contiguous. Tensor-core math is bf16
+// mma.sync.m16n8k16 with fp32 accumulation (softmax in the exp2 domain).
+// (reference: flash-attention-v100/kernel/fused_mha_forward_paged.cu:364, flash_decode_paged.cu:667,831,1301;
+//  v1/attention/backends/flash_attn_v100.py:2216 for the math)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace oc {
+namespace {
+
+constexpr int kKeysPerTile = 64;
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* g) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem)), "l"(g) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// byte offset of the 16-byte chunk `chunk` of row `row` in a [rows][D] bf16 tile with XOR swizzle
+template <int D>
+__device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
+  return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
+}
+
+template <int D, int MODE, int MB>
+__global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
+  constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
+  constexpr int NB2 = (MODE == 0) ? 4 : 1;      // 16-key groups per warp per tile
+  constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
+  constexpr int CH = D / 8;                     // 16-byte chunks per row
+  extern __shared__ __align__(128) uint8_t smem[];
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + ROWS * D * 2;
+  uint8_t* sV = sK + 2 * kKeysPerTile * D * 2;
+  __shared__ int s_req, s_tile0;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int G = p.Hq / p.Hkv;
+  const int hkv = blockIdx.y;
+  int r, tq0, tq1;
+  if (MODE == 0) {
+    const int TQ = 64 / G;
+    if (threadIdx.x == 0) {
+      int b = blockIdx.x, found = -1, t0 = 0;
+      for (int i = 0; i < p.R; ++i) {
+        int ql = p.query_start_loc[i + 1] - p.query_start_loc[i];
+        int nt = (ql > p.short_q_len) ? (ql + TQ - 1) / TQ : 0;  // short queries belong to the decode kernel
+        if (b < nt) { found = i; t0 = b * TQ; break; }
+        b -= nt;
+      }
+      s_req = found;
+      s_tile0 = t0;
+    }
+    __syncthreads();
+    r = s_req;
+    if (r < 0) return;
+    tq0 = s_tile0;
+    int ql = p.query_start_loc[r + 1] - p.query_start_loc[r];
+    tq1 = min(tq0 + TQ, ql);
+  } else {
+    r = blockIdx.x;
+    tq0 = 0;
+    tq1 = p.query_start_loc[r + 1] - p.query_start_loc[r];
+    if (tq1 > p.short_q_len) return;  // long queries belong to the prefill kernel (uniform exit: before any barrier)
+  }
+  const int qs = p.query_start_loc[r];
+  const int qlen = p.query_start_loc[r + 1] - qs;
+  const int S = p.seq_lens[r];
+  if (qlen <= 0 || S <= 0) return;
+  const int ctx0 = S - qlen;
+  const int nrows = (tq1 - tq0) * G;
+  const int kv_end = min(S, ctx0 + tq1);
+  const int ntiles = (kv_end + kKeysPerTile - 1) / kKeysPerTile;
+  int tile_lo = 0, tile_hi = ntiles;
+  if (MODE == 1 && p.splits > 1) {
+    int per = (ntiles + p.splits - 1) / p.splits;
+    tile_lo = blockIdx.z * per;
+    tile_hi = min(ntiles, tile_lo + per);
+  }
+  const int* bt = p.block_table + (size_t)r * p.bt_stride;
+  const size_t page_elems = (size_t)p.bs * D;
+
+  // ---- Q tile -> shared memory (zero rows past the end)
+  for (int idx = threadIdx.x; idx < ROWS * CH; idx += 128) {
+    int row = idx / CH, ch = idx % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < nrows) {
+      int tok = tq0 + row / G, gh = row % G;
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(qs + tok) * p.q_st + (size_t)(hkv * G + gh) * p.q_sh + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + sw_off<D>(row, ch)) = v;
+  }
+
+  auto load_tile = [&](int tile, int buf) {
+    const int k0 = tile * kKeysPerTile;
+    uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * 2;
+    uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * 2;
+    for (int idx = threadIdx.x; idx < kKeysPerTile * CH; idx += 128) {
+      int row = idx / CH, ch = idx % CH;
+      int key = k0 + row;
+      if (key < kv_end) {
+        int blk = bt[key / p.bs];
+        size_t base = (((size_t)blk * 2) * p.Hkv + hkv) * page_elems + (size_t)(key % p.bs) * D + ch * 8;
+        cp_async16(dk + sw_off<D>(row, ch), p.kv_cache + base);
+        cp_async16(dv + sw_off<D>(row, ch), p.kv_cache + base + (size_t)p.Hkv * page_elems);
+      } else {
+        *reinterpret_cast<uint4*>(dk + sw_off<D>(row, ch)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + sw_off<D>(row, ch)) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+
+  float o[MBW][D / 8][4];
+  float mrow[MBW][2], lrow[MBW][2];
+#pragma unroll
+  for (int b = 0; b < MBW; ++b) {
+    mrow[b][0] = mrow[b][1] = -INFINITY;
+    lrow[b][0] = lrow[b][1] = 0.f;
+#pragma unroll
+    for (int i = 0; i < D / 8; ++i) o[b][i][0] = o[b][i][1] = o[b][i][2] = o[b][i][3] = 0.f;
+  }
+  const float sc = p.scale * 1.4426950408889634f;
+  const int row_base = (MODE == 0) ? warp * 16 : 0;
+  const int key_base = (MODE == 0) ? 0 : warp * 16;
+  const int g_ = lane >> 2, tg = lane & 3;
+
+  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
+  cp_async_commit();
+  for (int tile = tile_lo; tile < tile_hi; ++tile) {
+    const int buf = (tile - tile_lo) & 1;
+    cp_async_wait<0>();
+    __syncthreads();
+    if (tile + 1 < tile_hi) load_tile(tile + 1, buf ^ 1);
+    cp_async_commit();
+    const uint32_t kb = smem_u32(sK + (size_t)buf * kKeysPerTile * D * 2);
+    const uint32_t vb = smem_u32(sV + (size_t)buf * kKeysPerTile * D * 2);
+    const uint32_t qb = smem_u32(sQ);
+    const int k0 = tile * kKeysPerTile + key_base;
+
+    // ---- S = Q K^T
+    float s[MBW][NB2 * 2][4];
+#pragma unroll
+    for (int b = 0; b < MBW; ++b)
+#pragma unroll
+      for (int n = 0; n < NB2 * 2; ++n) s[b][n][0] = s[b][n][1] = s[b][n][2] = s[b][n][3] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < D / 16; ++kk) {
+      uint32_t a[MBW][4];
+#pragma unroll
+      for (int b = 0; b < MBW; ++b) {
+        int row = row_base + b * 16 + (lane & 15);
+        ldsm_x4(a[b], qb + sw_off<D>(row, kk * 2 + (lane >> 4)));
+      }
+#pragma unroll
+      for (int n2 = 0; n2 < NB2; ++n2) {
+        uint32_t bfr[4];
+        int krow = key_base + n2 * 16 + (lane & 7) + ((lane >> 4) << 3);
+        ldsm_x4(bfr, kb + sw_off<D>(krow, kk * 2 + ((lane >> 3) & 1)));
+#pragma unroll
+        for (int b = 0; b < MBW; ++b) {
+          mma_bf16(s[b][n2 * 2], a[b], bfr[0], bfr[1]);
+          mma_bf16(s[b][n2 * 2 + 1], a[b], bfr[2], bfr[3]);
+        }
+      }
+    }
+    // ---- mask, online softmax
+#pragma unroll
+    for (int b = 0; b < MBW; ++b) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = row_base + b * 16 + g_ + h * 8;
+        const int qpos = ctx0 + tq0 + row / G;  // rows past nrows are never stored
+        float mx = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < NB2 * 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            int key = k0 + n * 8 + tg * 2 + e;
+            float v = s[b][n][h * 2 + e] * sc;
+            v = (key <= qpos && key < kv_end) ? v : -INFINITY;
+            s[b][n][h * 2 + e] = v;
+            mx = fmaxf(mx, v);
+          }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(mrow[b][h], mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(mrow[b][h] - m_use);
+        float sum = 0.f;
+#pragma unroll
+        for (int n = 0; n < NB2 * 2; ++n) {
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float pv = exp2f(s[b][n][h * 2 + e] - m_use);
+            s[b][n][h * 2 + e] = pv;
+            sum += pv;
+          }
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        lrow[b][h] = lrow[b][h] * alpha + sum;
+        mrow[b][h] = m_new;
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) {
+          o[b][i][h * 2] *= alpha;
+          o[b][i][h * 2 + 1] *= alpha;
+        }
+      }
+    }
+    // ---- O += P V
+#pragma unroll
+    for (int n2 = 0; n2 < NB2; ++n2) {
+      uint32_t a[MBW][4];
+#pragma unroll
+      for (int b = 0; b < MBW; ++b) {
+        a[b][0] = pack_bf16(s[b][n2 * 2][0], s[b][n2 * 2][1]);
+        a[b][1] = pack_bf16(s[b][n2 * 2][2], s[b][n2 * 2][3]);
+        a[b][2] = pack_bf16(s[b][n2 * 2 + 1][0], s[b][n2 * 2 + 1][1]);
+        a[b][3] = pack_bf16(s[b][n2 * 2 + 1][2], s[b][n2 * 2 + 1][3]);
+      }
+#pragma unroll
+      for (int d2 = 0; d2 < D / 16; ++d2) {
+        uint32_t bfr[4];
+        int krow = key_base + n2 * 16 + (lane & 15);
+        ldsm_x4_t(bfr, vb + sw_off<D>(krow, d2 * 2 + (lane >> 4)));
+#pragma unroll
+        for (int b = 0; b < MBW; ++b) {
+          mma_bf16(o[b][d2 * 2], a[b], bfr[0], bfr[1]);
+          mma_bf16(o[b][d2 * 2 + 1], a[b], bfr[2], bfr[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+  if (MODE == 0) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = row_base + g_ + h * 8;
+      if (row >= nrows) continue;
+      const int tok = tq0 + row / G, gh = row % G;
+      const float inv = lrow[0][h] > 0.f ? 1.f / lrow[0][h] : 0.f;
+      __nv_bfloat16* dst = p.out + ((size_t)(qs + tok) * p.Hq + hkv * G + gh) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i)
+        *reinterpret_cast<uint32_t*>(dst + i * 8 + tg * 2) = pack_bf16(o[0][i][h * 2] * inv, o[0][i][h * 2 + 1] * inv);
+      if (p.lse != nullptr && tg == 0)
+        p.lse[(size_t)(qs + tok) * p.Hq + hkv * G + gh] = (mrow[0][h] + log2f(lrow[0][h])) * 0.6931471805599453f;
+    }
+    return;
+  }
+
+  // ---- mode 1: merge the four warps' partial results (they saw disjoint keys), then store or hand to the split combine
+  __syncthreads();  // everyone is done reading K/V tiles; reuse that memory
+  float* mo = reinterpret_cast<float*>(sK);             // [4][ROWS][D]
+  float* mm = reinterpret_cast<float*>(sQ);             // [4][ROWS][2] (the Q tile is no longer needed)
+#pragma unroll
+  for (int b = 0; b < MBW; ++b)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = b * 16 + g_ + h * 8;
+      float* dst = mo + ((size_t)warp * ROWS + row) * D;
+#pragma unroll
+      for (int i = 0; i < D / 8; ++i) {
+        dst[i * 8 + tg * 2] = o[b][i][h * 2];
+        dst[i * 8 + tg * 2 + 1] = o[b][i][h * 2 + 1];
+      }
+      if (tg == 0) {
+        mm[((size_t)warp * ROWS + row) * 2] = mrow[b][h];
+        mm[((size_t)warp * ROWS + row) * 2 + 1] = lrow[b][h];
+      }
+    }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nrows * (D / 4); idx += 128) {
+    const int row = idx / (D / 4), c4 = (idx % (D / 4)) * 4;
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, mm[((size_t)w * ROWS + row) * 2]);
+    float L = 0.f, acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      float mw = mm[((size_t)w * ROWS + row) * 2];
+      float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+      L += mm[((size_t)w * ROWS + row) * 2 + 1] * f;
+      const float4 v = *reinterpret_cast<const float4*>(mo + ((size_t)w * ROWS + row) * D + c4);
+      acc[0] += v.x * f; acc[1] += v.y * f; acc[2] += v.z * f; acc[3] += v.w * f;
+    }
+    const int tok = row / G, gh = row % G;
+    const size_t orow = (size_t)(qs + tok) * p.Hq + hkv * G + gh;
+    if (p.splits > 1) {
+      float* wo = p.ws_o + ((size_t)blockIdx.z * p.T * p.Hq + orow) * D + c4;
+      *reinterpret_cast<float4*>(wo) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      if (c4 == 0) {
+        float* wm = p.ws_ml + ((size_t)blockIdx.z * p.T * p.Hq + orow) * 2;
+        wm[0] = M;
+        wm[1] = L;
+      }
+    } else {
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      __nv_bfloat16* dst = p.out + orow * D + c4;
+      *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
+      if (p.lse != nullptr && c4 == 0) p.lse[orow] = (M + log2f(L)) * 0.6931471805599453f;
+    }
+  }
+}
+
+// merges split-KV partials: one warp per (token, head)
+template <int D>
+__global__ void attn_combine_kernel(const AttnParams p) {
+  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  const int rows = p.T * p.Hq;
+  if (warp >= rows) return;
+  float M = -INFINITY;
+  for (int s = 0; s < p.splits; ++s) M = fmaxf(M, p.ws_ml[((size_t)s * rows + warp) * 2]);
+  float L = 0.f;
+  float acc[D / 32];
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) acc[i] = 0.f;
+  for (int s = 0; s < p.splits; ++s) {
+    const float ms = p.ws_ml[((size_t)s * rows + warp) * 2];
+    const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+    L += p.ws_ml[((size_t)s * rows + warp) * 2 + 1] * f;
+    const float* src = p.ws_o + ((size_t)s * rows + warp) * D;
+#pragma unroll
+    for (int i = 0; i < D / 32; ++i) acc[i] += src[lane + 32 * i] * f;
+  }
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+  for (int i = 0; i < D / 32; ++i) p.out[(size_t)warp * D + lane + 32 * i] = __float2bfloat16(acc[i] * inv);
+  if (p.lse != nullptr && lane == 0) p.lse[warp] = (M + log2f(L)) * 0.6931471805599453f;
+}
+
+template <int D, int MODE, int MB>
+int launch_one(const AttnParams& p, cudaStream_t st) {
+  constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
+  const int smem = ROWS * D * 2 + 4 * kKeysPerTile * D * 2;
+  static int configured = 0;
+  if (!configured) {
+    if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    configured = 1;
+  }
+  dim3 grid(MODE == 0 ? p.num_q_tiles : p.R, p.Hkv, MODE == 0 ? 1 : p.splits);
+  if (grid.x == 0) return 0;
+  attn_kernel<D, MODE, MB><<<grid, 128, smem, st>>>(p);
+  if (MODE == 1 && p.splits > 1) {
+    int rows = p.T * p.Hq;
+    attn_combine_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, st>>>(p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+}  // namespace
+
+int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
+  if (p.Hq % p.Hkv || p.bs % 16 || (p.D != 128 && p.D != 256)) return -1;
+  const int G = p.Hq / p.Hkv;
+  if (G > 64) return -1;
+  if (mode == 1) {
+    const int rows = p.short_q_len * G;
+    if (p.D == 128) {
+      if (rows <= 16) return launch_one<128, 1, 1>(p, st);
+      if (rows <= 32) return launch_one<128, 1, 2>(p, st);
+    } else {
+      if (rows <= 16) return launch_one<256, 1, 1>(p, st);
+    }
+    return -6;  // caller must use mode 0 for longer queries
+  }
+  if (p.D == 128) return launch_one<128, 0, 1>(p, st);
+  return launch_one<256, 0, 1>(p, st);
+}
+
+unsigned int attention_read_status(bool clear) { return read_status_tu(clear); }
+
+}  // namespace oc

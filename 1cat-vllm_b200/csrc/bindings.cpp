@@ -1,0 +1,251 @@
+// Python bindings of the sm_100a kernels (module onecat_vllm.ops._C). Tensors are validated here so that the kernels
+// can assume alignment and layout; every function launches on the current CUDA stream of the tensor's device.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include "gemm_sm100.h"
+#include "kernels.h"
+
+namespace {
+
+cudaStream_t cur_stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+int sm_count() {
+  static int n = 0;
+  if (!n) n = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  return n;
+}
+
+void check_bf16(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.scalar_type() == torch::kBFloat16, name, " must be bf16");
+}
+
+// out[T, n_out or N] = epilogue(X[T,K] @ W^T). Exactly one of `w` (bf16 [n_rows, K]) and `w4` (packed tiles) is given.
+void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> w4, c10::optional<torch::Tensor> w4_sz,
+          torch::Tensor out, c10::optional<torch::Tensor> bias, torch::Tensor ws, torch::Tensor counters, int64_t N, int64_t n_rows,
+          int64_t n_out, int64_t n_pad, int64_t epi, int64_t group_ktiles, int64_t force_splits, int64_t force_tn) {
+  check_bf16(x, "x");
+  check_bf16(out, "out");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1, "x/out must be row-major 2-D");
+  const c10::cuda::CUDAGuard guard(x.device());
+  oc::GemmParams p{};
+  p.T = (int)x.size(0);
+  p.K = (int)x.size(1);
+  if (p.T == 0) return;
+  TORCH_CHECK(p.K % 64 == 0, "K must be a multiple of 64, got ", p.K);
+  TORCH_CHECK(((uintptr_t)x.data_ptr() & 15) == 0 && (x.stride(0) * 2) % 16 == 0, "x must be 16-byte aligned with 16-byte row pitch");
+  p.N = (int)N;
+  p.n_rows = (int)n_rows;
+  p.n_out = (int)n_out;
+  p.n_pad = (int)n_pad;
+  p.epi = (int)epi;
+  p.group_ktiles = (int)group_ktiles;
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.ldo = (int)out.stride(0);
+  TORCH_CHECK(out.size(0) >= p.T && out.size(1) >= (epi == oc::EPI_SILU_MUL ? n_out : N), "out is too small");
+  p.bias = bias.has_value() ? (const __nv_bfloat16*)bias->data_ptr() : nullptr;
+  p.ws = (float*)ws.data_ptr();
+  p.ws_bytes = (size_t)ws.numel() * ws.element_size();
+  p.counters = (int*)counters.data_ptr();
+  p.max_counters = (int)counters.numel();
+  const void* wptr = nullptr;
+  int ldw = 0;
+  if (w4.has_value()) {
+    TORCH_CHECK(w4_sz.has_value(), "w4 needs its scale/zero table");
+    p.w4 = (const uint8_t*)w4->data_ptr();
+    p.w4_sz = (const uint32_t*)w4_sz->data_ptr();
+    TORCH_CHECK(((uintptr_t)p.w4 & 15) == 0, "packed weights must be 16-byte aligned");
+    TORCH_CHECK((size_t)w4->numel() * w4->element_size() >= (size_t)((n_rows + 127) / 128) * (p.K / 64) * 4096, "packed weights are too small");
+  } else {
+    TORCH_CHECK(w.has_value(), "a weight is required");
+    check_bf16(*w, "w");
+    TORCH_CHECK(w->dim() == 2 && w->stride(1) == 1 && w->size(1) == p.K && w->size(0) >= n_rows, "w must be [n_rows, K] row-major");
+    TORCH_CHECK(((uintptr_t)w->data_ptr() & 15) == 0 && (w->stride(0) * 2) % 16 == 0, "w must be 16-byte aligned");
+    wptr = w->data_ptr();
+    ldw = (int)w->stride(0);
+  }
+  oc::gemm_plan(p, sm_count(), w4.has_value());
+  if (force_tn > 0) {
+    p.tn = (int)force_tn;
+    p.num_t_tiles = (p.T + p.tn - 1) / p.tn;
+    oc::GemmParams q = p;
+    // re-derive pipeline depths for the forced tile
+    int per_stage = p.tn * 128 + 16384;
+    int s = (220 * 1024 - p.pstages * 4096 - 2048) / per_stage;
+    p.stages = s > 8 ? 8 : (s < 2 ? 2 : s);
+    (void)q;
+  }
+  if (force_splits > 0) {
+    int ktiles = p.K / 64;
+    p.splits = (int)force_splits;
+    p.ktiles_per_split = (ktiles + p.splits - 1) / p.splits;
+    TORCH_CHECK((p.splits - 1) * p.ktiles_per_split < ktiles, "too many splits for K");
+    TORCH_CHECK((size_t)p.num_t_tiles * p.num_n_tiles * p.splits * 128 * p.tn * 4 <= p.ws_bytes, "split-K workspace too small");
+    TORCH_CHECK(p.num_t_tiles * p.num_n_tiles <= p.max_counters, "not enough split-K counters");
+  }
+  int rc = oc::gemm_launch(p, x.data_ptr(), (int)x.stride(0), wptr, ldw, sm_count(), cur_stream());
+  TORCH_CHECK(rc == 0, "gemm launch failed with code ", rc);
+}
+
+std::tuple<torch::Tensor, c10::optional<torch::Tensor>> rms_norm(torch::Tensor x, torch::Tensor w, double eps,
+                                                                c10::optional<torch::Tensor> residual, bool gemma) {
+  check_bf16(x, "x");
+  check_bf16(w, "w");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "x must be [T, H] with unit inner stride");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), H = (int)x.size(1);
+  auto y = torch::empty({T, H}, x.options());
+  c10::optional<torch::Tensor> res_out;
+  const void* rin = nullptr;
+  void* rout = nullptr;
+  if (residual.has_value()) {
+    check_bf16(*residual, "residual");
+    TORCH_CHECK(residual->is_contiguous() && residual->size(0) == T && residual->size(1) == H, "residual must be contiguous [T, H]");
+    res_out = torch::empty({T, H}, x.options());
+    rin = residual->data_ptr();
+    rout = res_out->data_ptr();
+  }
+  int rc = oc::rms_norm_launch(x.data_ptr(), rin, w.data_ptr(), y.data_ptr(), rout, T, H, (int)x.stride(0), (float)eps, gemma ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "rms_norm failed: ", rc, " (H must be a multiple of 8 and <= 8192)");
+  return {y, res_out};
+}
+
+torch::Tensor rms_norm_gated(torch::Tensor x, torch::Tensor z, torch::Tensor w, double eps, int64_t heads) {
+  // x, z: [T, heads*D] (possibly column slices); returns contiguous [T*heads, D]
+  check_bf16(x, "x");
+  check_bf16(z, "z");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), D = (int)(x.size(1) / heads);
+  auto y = torch::empty({T * heads, D}, x.options());
+  int rc = oc::rms_norm_gated_launch(x.data_ptr(), z.data_ptr(), w.data_ptr(), y.data_ptr(), (int)(T * heads), D, (int)x.stride(0),
+                                     (int)z.stride(0), (int)heads, (float)eps, cur_stream());
+  TORCH_CHECK(rc == 0, "rms_norm_gated failed: ", rc);
+  return y;
+}
+
+torch::Tensor silu_and_mul(torch::Tensor x) {
+  check_bf16(x, "x");
+  TORCH_CHECK(x.is_contiguous() && x.dim() == 2, "x must be contiguous [T, 2I]");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), I = (int)(x.size(1) / 2);
+  auto y = torch::empty({T, I}, x.options());
+  TORCH_CHECK(oc::silu_and_mul_launch(x.data_ptr(), y.data_ptr(), T, I, cur_stream()) == 0, "silu_and_mul failed");
+  return y;
+}
+
+void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor positions, torch::Tensor cos_sin,
+                    c10::optional<torch::Tensor> kv_cache, torch::Tensor slot_mapping, int64_t rot, c10::optional<torch::Tensor> qn,
+                    c10::optional<torch::Tensor> kn, double eps, bool gemma) {
+  check_bf16(q, "q");
+  check_bf16(k, "k");
+  check_bf16(v, "v");
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3 && q.stride(2) == 1 && k.stride(2) == 1 && v.stride(2) == 1, "q/k/v must be [T,H,D]");
+  TORCH_CHECK(k.stride(1) == k.size(2) && v.stride(1) == v.size(2), "k/v heads must be D apart");
+  TORCH_CHECK(positions.scalar_type() == torch::kInt32 && slot_mapping.scalar_type() == torch::kInt32, "positions/slot_mapping must be int32");
+  TORCH_CHECK(cos_sin.scalar_type() == torch::kFloat32 && cos_sin.size(1) == rot, "cos_sin must be fp32 [max_pos, rot]");
+  const c10::cuda::CUDAGuard guard(q.device());
+  oc::RopeCacheParams p{};
+  p.q = (__nv_bfloat16*)q.data_ptr();
+  p.k = (__nv_bfloat16*)k.data_ptr();
+  p.v = (__nv_bfloat16*)v.data_ptr();
+  p.q_st = q.stride(0);
+  p.q_sh = q.stride(1);
+  p.k_st = k.stride(0);
+  p.v_st = v.stride(0);
+  p.positions = positions.data_ptr<int>();
+  p.cos_sin = cos_sin.data_ptr<float>();
+  p.slot_mapping = slot_mapping.data_ptr<int>();
+  p.T = (int)q.size(0);
+  p.Hq = (int)q.size(1);
+  p.Hkv = (int)k.size(1);
+  p.D = (int)q.size(2);
+  p.rot = (int)rot;
+  p.gemma = gemma ? 1 : 0;
+  p.eps = (float)eps;
+  p.bs = 16;
+  if (kv_cache.has_value()) {
+    check_bf16(*kv_cache, "kv_cache");
+    TORCH_CHECK(kv_cache->is_contiguous() && kv_cache->dim() == 5 && kv_cache->size(1) == 2 && kv_cache->size(2) == p.Hkv && kv_cache->size(4) == p.D,
+                "kv_cache must be contiguous [blocks, 2, Hkv, block_size, D]");
+    p.kv_cache = (__nv_bfloat16*)kv_cache->data_ptr();
+    p.bs = (int)kv_cache->size(3);
+  }
+  p.q_norm = qn.has_value() ? (const __nv_bfloat16*)qn->data_ptr() : nullptr;
+  p.k_norm = kn.has_value() ? (const __nv_bfloat16*)kn->data_ptr() : nullptr;
+  TORCH_CHECK(oc::rope_cache_launch(p, cur_stream()) == 0, "rope_and_cache failed");
+}
+
+void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out, c10::optional<torch::Tensor> lse, torch::Tensor qsl,
+                     torch::Tensor seq_lens, torch::Tensor block_table, double scale, int64_t mode, int64_t num_q_tiles, int64_t splits,
+                     int64_t max_q_len, int64_t short_q_len, c10::optional<torch::Tensor> ws_o, c10::optional<torch::Tensor> ws_ml) {
+  check_bf16(q, "q");
+  check_bf16(kv_cache, "kv_cache");
+  check_bf16(out, "out");
+  TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && out.is_contiguous(), "q must be [T,Hq,D]; out contiguous");
+  TORCH_CHECK(((uintptr_t)q.data_ptr() & 15) == 0 && (q.stride(0) % 8) == 0 && (q.stride(1) % 8) == 0, "q must be 16-byte aligned");
+  TORCH_CHECK(kv_cache.is_contiguous() && kv_cache.dim() == 5 && kv_cache.size(1) == 2, "kv_cache must be contiguous [blocks,2,Hkv,bs,D]");
+  TORCH_CHECK(qsl.scalar_type() == torch::kInt32 && seq_lens.scalar_type() == torch::kInt32 && block_table.scalar_type() == torch::kInt32,
+              "metadata must be int32");
+  const c10::cuda::CUDAGuard guard(q.device());
+  oc::AttnParams p{};
+  p.q = (const __nv_bfloat16*)q.data_ptr();
+  p.q_st = q.stride(0);
+  p.q_sh = q.stride(1);
+  p.kv_cache = (const __nv_bfloat16*)kv_cache.data_ptr();
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.lse = lse.has_value() ? lse->data_ptr<float>() : nullptr;
+  p.query_start_loc = qsl.data_ptr<int>();
+  p.seq_lens = seq_lens.data_ptr<int>();
+  p.block_table = block_table.data_ptr<int>();
+  p.bt_stride = (int)block_table.stride(0);
+  p.R = (int)seq_lens.size(0);
+  p.T = (int)q.size(0);
+  p.Hq = (int)q.size(1);
+  p.Hkv = (int)kv_cache.size(2);
+  p.D = (int)q.size(2);
+  p.bs = (int)kv_cache.size(3);
+  p.scale = (float)scale;
+  p.num_q_tiles = (int)num_q_tiles;
+  p.splits = (int)splits;
+  p.max_q_len = (int)max_q_len;
+  p.short_q_len = (int)short_q_len;
+  if (mode == 1 && splits > 1) {
+    TORCH_CHECK(ws_o.has_value() && ws_ml.has_value(), "split-KV needs workspaces");
+    TORCH_CHECK((size_t)ws_o->numel() >= (size_t)splits * p.T * p.Hq * p.D && (size_t)ws_ml->numel() >= (size_t)splits * p.T * p.Hq * 2,
+                "split-KV workspace too small");
+    p.ws_o = ws_o->data_ptr<float>();
+    p.ws_ml = ws_ml->data_ptr<float>();
+  }
+  if (p.T == 0 || p.R == 0) return;
+  int rc = oc::attention_launch(p, (int)mode, cur_stream());
+  TORCH_CHECK(rc == 0, "attention launch failed with code ", rc);
+}
+
+torch::Tensor argmax(torch::Tensor x) {
+  TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "x must be a CUDA [B, V] matrix");
+  TORCH_CHECK(x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kFloat32, "argmax supports bf16 and fp32");
+  const c10::cuda::CUDAGuard guard(x.device());
+  auto out = torch::empty({x.size(0)}, x.options().dtype(torch::kInt64));
+  TORCH_CHECK(oc::argmax_launch(x.data_ptr(), x.scalar_type() == torch::kFloat32, out.data_ptr<int64_t>() ? (long long*)out.data_ptr<int64_t>() : nullptr,
+                                (int)x.size(0), (int)x.size(1), x.stride(0), cur_stream()) == 0, "argmax failed");
+  return out;
+}
+
+int64_t read_status(bool clear) {
+  return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear));
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm", &gemm);
+  m.def("rms_norm", &rms_norm);
+  m.def("rms_norm_gated", &rms_norm_gated);
+  m.def("silu_and_mul", &silu_and_mul);
+  m.def("rope_and_cache", &rope_and_cache);
+  m.def("paged_attention", &paged_attention);
+  m.def("argmax", &argmax);
+  m.def("read_status", &read_status);
+}

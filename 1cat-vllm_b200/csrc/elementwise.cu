@@ -1,0 +1,271 @@
+// Memory-bound helper kernels: fused residual-add + RMSNorm, gated RMSNorm, SiLU*mul, per-head norm + RoPE + paged
+// KV insert, arg-max over the vocabulary. One pass over the data each, 16-byte accesses.
+// (reference: csrc/libtorch_stable/layernorm_kernels.cu:21,99; pos_encoding_kernels.cu:77; fused_qknorm_rope_kernel.cu:104;
+//  cache_kernels.cu reshape_and_cache_flash; activation_kernels.cu:78)
+#include "common.cuh"
+#include "kernels.h"
+
+namespace oc {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < nw) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// y = norm(x (+ residual)) * w ; residual_out = bf16(x + residual).  One CTA per token, values stay in registers.
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ res_in,
+                                                       const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
+                                                       __nv_bfloat16* __restrict__ res_out, int H, int ldx, float eps, int gemma) {
+  __shared__ float red[33];
+  const size_t t = blockIdx.x;
+  const __nv_bfloat16* xr = x + t * ldx;
+  float v[VEC_ITERS][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < VEC_ITERS; ++i) {
+    int c = (i * 256 + threadIdx.x) * 8;
+    if (c < H) {
+      uint4 a = *reinterpret_cast<const uint4*>(xr + c);
+      const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+      if (res_in != nullptr) {
+        uint4 b = *reinterpret_cast<const uint4*>(res_in + t * H + c);
+        const __nv_bfloat16* bp = reinterpret_cast<const __nv_bfloat16*>(&b);
+        uint4 o;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          op[j] = __float2bfloat16(__bfloat162float(ap[j]) + __bfloat162float(bp[j]));
+          v[i][j] = __bfloat162float(op[j]);
+        }
+        *reinterpret_cast<uint4*>(res_out + t * H + c) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(ap[j]);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += v[i][j] * v[i][j];
+    }
+  }
+  float tot = block_sum(ss, red);
+  float inv = rsqrtf(tot / (float)H + eps);
+#pragma unroll
+  for (int i = 0; i < VEC_ITERS; ++i) {
+    int c = (i * 256 + threadIdx.x) * 8;
+    if (c < H) {
+      uint4 ww = *reinterpret_cast<const uint4*>(w + c);
+      const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&ww);
+      uint4 o;
+      __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        float g = __bfloat162float(wp[j]);
+        op[j] = __float2bfloat16(v[i][j] * inv * (gemma ? 1.f + g : g));
+      }
+      *reinterpret_cast<uint4*>(y + t * H + c) = o;
+    }
+  }
+}
+
+// y = rmsnorm(x) * w * silu(z) over rows of D (64..256) elements; one warp per row.
+__global__ void rms_norm_gated_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ z,
+                                      const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y, int rows, int D,
+                                      int ldx, int ldz, int heads, float eps) {
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  // rows are (token, head) pairs; x and z may be column slices of wider matrices
+  const size_t tok = row / heads, hd = row % heads;
+  const __nv_bfloat16* xr = x + tok * ldx + hd * D;
+  const __nv_bfloat16* zr = z + tok * ldz + hd * D;
+  float v[8];
+  float ss = 0.f;
+  int n = D / 32;
+  for (int i = 0; i < n; ++i) {
+    v[i] = __bfloat162float(xr[lane + 32 * i]);
+    ss += v[i] * v[i];
+  }
+  ss = warp_sum(ss);
+  float inv = rsqrtf(ss / (float)D + eps);
+  for (int i = 0; i < n; ++i) {
+    float g = __bfloat162float(zr[lane + 32 * i]);
+    float o = v[i] * inv * __bfloat162float(w[lane + 32 * i]) * (g / (1.f + __expf(-g)));
+    y[(size_t)row * D + lane + 32 * i] = __float2bfloat16(o);
+  }
+}
+
+__global__ void silu_and_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y, int T, int I) {
+  size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  size_t total = (size_t)T * I / 8;
+  if (idx >= total) return;
+  size_t t = idx / (I / 8), c = (idx % (I / 8)) * 8;
+  uint4 g = *reinterpret_cast<const uint4*>(x + t * 2 * I + c);
+  uint4 u = *reinterpret_cast<const uint4*>(x + t * 2 * I + I + c);
+  const __nv_bfloat16 *gp = reinterpret_cast<const __nv_bfloat16*>(&g), *up = reinterpret_cast<const __nv_bfloat16*>(&u);
+  uint4 o;
+  __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    float a = __bfloat162float(gp[j]);
+    op[j] = __float2bfloat16(a / (1.f + __expf(-a)) * __bfloat162float(up[j]));
+  }
+  *reinterpret_cast<uint4*>(y + t * I + c) = o;
+}
+
+// One warp per (token, head): optional RMSNorm over the head, NeoX rotary on the first `rot` dims (q and k, in place),
+// k and v rows copied into the paged cache [block][2][Hkv][bs][D] at slot_mapping[token].
+__global__ void rope_cache_kernel(RopeCacheParams p) {
+  extern __shared__ float sh[];
+  const int wpb = blockDim.x >> 5;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int heads = p.Hq + 2 * p.Hkv;
+  const long long gw = (long long)blockIdx.x * wpb + warp;
+  if (gw >= (long long)p.T * heads) return;
+  const int t = (int)(gw / heads), hh = (int)(gw % heads);
+  float* buf = sh + warp * p.D;
+  const int D = p.D;
+  __nv_bfloat16* src;
+  const __nv_bfloat16* nw = nullptr;
+  int kind;  // 0 q, 1 k, 2 v
+  if (hh < p.Hq) { kind = 0; src = p.q + (size_t)t * p.q_st + (size_t)hh * p.q_sh; nw = p.q_norm; }
+  else if (hh < p.Hq + p.Hkv) { kind = 1; src = p.k + (size_t)t * p.k_st + (size_t)(hh - p.Hq) * D; nw = p.k_norm; }
+  else { kind = 2; src = p.v + (size_t)t * p.v_st + (size_t)(hh - p.Hq - p.Hkv) * D; }
+  float ss = 0.f;
+  for (int i = lane; i < D; i += 32) {
+    float v = __bfloat162float(src[i]);
+    buf[i] = v;
+    ss += v * v;
+  }
+  if (kind != 2 && nw != nullptr) {
+    ss = warp_sum(ss);
+    float inv = rsqrtf(ss / (float)D + p.eps);
+    for (int i = lane; i < D; i += 32) {
+      float g = __bfloat162float(nw[i]);
+      // the normalised value is rounded to bf16 before the rotation, like the separate-kernel formulation
+      buf[i] = __bfloat162float(__float2bfloat16(buf[i] * inv * (p.gemma ? 1.f + g : g)));
+    }
+  }
+  __syncwarp();
+  const long long slot = (kind != 0 && p.kv_cache != nullptr) ? (long long)p.slot_mapping[t] : -1;
+  __nv_bfloat16* cdst = nullptr;
+  if (slot >= 0) {
+    long long blk = slot / p.bs, off = slot % p.bs;
+    int h = (kind == 1) ? hh - p.Hq : hh - p.Hq - p.Hkv;
+    cdst = p.kv_cache + ((((size_t)blk * 2 + (kind - 1)) * p.Hkv + h) * p.bs + off) * D;
+  }
+  if (kind == 2) {
+    if (cdst != nullptr)
+      for (int i = lane; i < D; i += 32) cdst[i] = src[i];
+    return;
+  }
+  const int half = p.rot >> 1;
+  const float* cs = p.cos_sin + (size_t)p.positions[t] * p.rot;
+  for (int i = lane; i < D; i += 32) {
+    float o;
+    if (i < half) o = buf[i] * cs[i] - buf[i + half] * cs[half + i];
+    else if (i < p.rot) o = buf[i] * cs[i - half] + buf[i - half] * cs[i];
+    else o = buf[i];
+    __nv_bfloat16 ob = __float2bfloat16(o);
+    src[i] = ob;
+    if (cdst != nullptr) cdst[i] = ob;
+  }
+}
+
+// arg-max of each row of a [B, V] bf16/fp32 matrix; ties go to the lowest index (torch semantics).
+template <typename T>
+__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, long long* __restrict__ out, int V, long long ld) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const T* r = x + (size_t)blockIdx.x * ld;
+  float best = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    float v = (float)r[i];
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+  }
+  if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    int nw = blockDim.x >> 5;
+    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
+    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
+}  // namespace
+
+int rms_norm_launch(const void* x, const void* res_in, const void* w, void* y, void* res_out, int T, int H, int ldx, float eps,
+                    int gemma, cudaStream_t st) {
+  if (H % 8 || H > 256 * 8 * 4) return -1;
+  const __nv_bfloat16 *xp = (const __nv_bfloat16*)x, *rp = (const __nv_bfloat16*)res_in, *wp = (const __nv_bfloat16*)w;
+  __nv_bfloat16 *yp = (__nv_bfloat16*)y, *rop = (__nv_bfloat16*)res_out;
+  int iters = (H + 2047) / 2048;
+  if (T == 0) return 0;
+  switch (iters) {
+    case 1: rms_norm_kernel<1><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    case 2: rms_norm_kernel<2><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    case 3: rms_norm_kernel<3><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    default: rms_norm_kernel<4><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int rms_norm_gated_launch(const void* x, const void* z, const void* w, void* y, int rows, int D, int ldx, int ldz, int heads,
+                          float eps, cudaStream_t st) {
+  if (D % 32 || D > 256) return -1;
+  if (rows == 0) return 0;
+  rms_norm_gated_kernel<<<(rows + 7) / 8, 256, 0, st>>>((const __nv_bfloat16*)x, (const __nv_bfloat16*)z, (const __nv_bfloat16*)w,
+                                                        (__nv_bfloat16*)y, rows, D, ldx, ldz, heads, eps);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int silu_and_mul_launch(const void* x, void* y, int T, int I, cudaStream_t st) {
+  if (I % 8) return -1;
+  size_t total = (size_t)T * I / 8;
+  if (total == 0) return 0;
+  silu_and_mul_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)y, T, I);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int rope_cache_launch(const RopeCacheParams& p, cudaStream_t st) {
+  if (p.T == 0) return 0;
+  if (p.D > 512 || p.rot > p.D || (p.rot & 1)) return -1;
+  long long warps = (long long)p.T * (p.Hq + 2 * p.Hkv);
+  int wpb = 8;
+  rope_cache_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, wpb * p.D * sizeof(float), st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st) {
+  if (B == 0) return 0;
+  if (is_fp32) argmax_kernel<float><<<B, 1024, 0, st>>>((const float*)x, out, V, ld);
+  else argmax_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>((const __nv_bfloat16*)x, out, V, ld);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+unsigned int elementwise_read_status(bool clear) { return read_status_tu(clear); }
+
+}  // namespace oc

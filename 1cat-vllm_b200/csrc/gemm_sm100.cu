@@ -1,0 +1,470 @@
+// out[t, n] = sum_k X[t, k] * W[n, k]  on tcgen05 tensor cores with TMEM accumulators.
+//
+// One persistent, warp-specialised kernel serves dense bf16 weights and 4-bit group-quantised (AWQ/GPTQ) weights:
+//   * The weight tile (128 output features x 64 k) is UMMA operand A, so the 128 TMEM lanes are output features and
+//     the accumulator columns are tokens. The token tile TN (32..256) is UMMA N: decode batches and 8192-token
+//     prefill chunks run the same code, and a 4-bit weight tile is dequantised once per 128 x TN x 64 MMA block.
+//   * warp 0: producer (TMA tensor copies of X and of bf16 W)
+//     warp 1: TMEM allocation + single-thread tcgen05.mma issue
+//     warps 2-5: 4-bit -> bf16 dequantisation into the 128-byte-swizzled operand layout
+//     warps 6-9: epilogue (tcgen05.ld -> bf16 store | SiLU*mul | fp32 split-K partial + last-arriver reduction)
+//     warp 10: bulk copies of packed 4-bit tiles, running up to `pstages` tiles ahead of the operand stages
+//   * two accumulators of TN columns each: the epilogue of tile i overlaps the main loop of tile i+1.
+// Every wait is bounded; on expiry the CTA raises the status word and tears down (see common.cuh).
+//
+// Role of this file in the reference's terms: replaces the TurboMind s884 GEMM family and its dispatch
+// (reference: csrc/sm70_turbomind/ops/awq_sm70_gemm.cu:3161,3278; gemm_universal.h:238) and cuBLAS for dense layers.
+#include "common.cuh"
+#include "gemm_sm100.h"
+
+namespace oc {
+
+namespace {
+
+constexpr int kThreads = 352;
+constexpr int BM = 128;  // weight rows (output features) per tile = UMMA M
+constexpr int BK = 64;   // k per stage: one 128-byte swizzle atom of bf16
+constexpr int kWStageBytes = BM * BK * 2;   // 16 KB
+constexpr int kPackedBytes = BM * BK / 2;   // 4 KB of nibbles
+constexpr int kTmemCols = 512;
+
+struct SmemLayout {
+  uint32_t x_off, w_off, p_off, bar_off, total;
+};
+__host__ __device__ inline SmemLayout make_layout(int tn, int stages, int pstages) {
+  SmemLayout L;
+  uint32_t o = 0;
+  L.x_off = o;
+  o += (uint32_t)stages * tn * 128;
+  L.w_off = o;
+  o += (uint32_t)stages * kWStageBytes;
+  L.p_off = o;
+  o += (uint32_t)pstages * kPackedBytes;
+  L.bar_off = o;
+  o += 1024;
+  L.total = o;
+  return L;
+}
+
+__device__ __forceinline__ uint32_t dq_pair(uint32_t w, uint32_t zb2, uint32_t s2) {
+  // two nibbles (bits 0-3 and 16-19 of w) -> bf16x2 ((q - z) * s); 0x4300 is bf16 128.0 whose ulp is 1
+  uint32_t v = (w & 0x000f000fu) | 0x43004300u;
+  __nv_bfloat162 r = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&zb2)),
+                             *reinterpret_cast<__nv_bfloat162*>(&s2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+template <int WKIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes the swizzle needs
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const SmemLayout L = make_layout(p.tn, p.stages, p.pstages);
+  uint8_t* sx = smem + L.x_off;
+  uint8_t* sw = smem + L.w_off;
+  uint8_t* sp = smem + L.p_off;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
+  const int S = p.stages, PS = p.pstages;
+  uint64_t* full_x = bars;              // [S]  TMA landed (X, and W for bf16 weights)
+  uint64_t* w_ready = bars + S;         // [S]  dequantised W tile written
+  uint64_t* empty = bars + 2 * S;       // [S]  MMA finished reading the stage
+  uint64_t* pfull = bars + 3 * S;       // [PS] packed tile landed
+  uint64_t* pempty = bars + 3 * S + PS; // [PS] packed tile consumed
+  uint64_t* tfull = bars + 3 * S + 2 * PS;  // [2] accumulator complete
+  uint64_t* tempty = tfull + 2;             // [2] accumulator drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  int* red_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tn = p.tn;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full_x[i], 1);
+      mbar_init(&w_ready[i], 128);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < PS; ++i) {
+      mbar_init(&pfull[i], 1);
+      mbar_init(&pempty[i], 128);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 128);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmX);
+    if (WKIND == 0) prefetch_tmap(&tmW);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_work = p.num_n_tiles * p.num_t_tiles * p.splits;
+  const int ktiles = p.K / BK;
+
+  // work item -> (n tile, t tile, split, k range)
+  auto decode = [&](int w, int& nt, int& tt, int& sp_, int& k0, int& k1) {
+    sp_ = w % p.splits;
+    int tile = w / p.splits;
+    tt = tile % p.num_t_tiles;
+    nt = tile / p.num_t_tiles;
+    k0 = sp_ * p.ktiles_per_split;
+    k1 = min(k0 + p.ktiles_per_split, ktiles);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int nt, tt, sp_, k0, k1;
+        decode(w, nt, tt, sp_, k0, k1);
+        for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
+          int s = it % S;
+          ok = mbar_wait(&empty[s], ((it / S) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          uint32_t bytes = (uint32_t)tn * 128 + (WKIND == 0 ? kWStageBytes : 0);
+          mbar_expect_tx(&full_x[s], bytes);
+          tma_load_2d(sx + (size_t)s * tn * 128, &tmX, kt * BK, tt * tn, &full_x[s]);
+          if (WKIND == 0) tma_load_2d(sw + (size_t)s * kWStageBytes, &tmW, kt * BK, nt * BM, &full_x[s]);
+        }
+      }
+    }
+  } else if (warp == 10) {
+    // ------------------------------------------------------------------ packed-weight producer (runs PS tiles ahead)
+    if (WKIND == 1 && lane == 0) {
+      uint32_t pit = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int nt, tt, sp_, k0, k1;
+        decode(w, nt, tt, sp_, k0, k1);
+        for (int kt = k0; kt < k1 && ok; ++kt, ++pit) {
+          int ps = pit % PS;
+          ok = mbar_wait(&pempty[ps], ((pit / PS) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          mbar_expect_tx(&pfull[ps], kPackedBytes);
+          bulk_load(sp + ps * kPackedBytes, p.w4 + ((size_t)nt * ktiles + kt) * kPackedBytes, kPackedBytes, &pfull[ps]);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue
+    const uint32_t idesc = umma_idesc_bf16(BM, tn);
+    uint32_t it = 0, tile_i = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
+      int nt, tt, sp_, k0, k1;
+      decode(w, nt, tt, sp_, k0, k1);
+      const int acc = tile_i & 1;
+      ok = mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_addr = tmem_base + acc * 256;
+      for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
+        int s = it % S;
+        uint32_t ph = (it / S) & 1;
+        ok = mbar_wait(&full_x[s], ph, abort_flag);
+        if (ok && WKIND == 1) ok = mbar_wait(&w_ready[s], ph, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          uint32_t a0 = smem_u32(sw + (size_t)s * kWStageBytes);
+          uint32_t b0 = smem_u32(sx + (size_t)s * tn * 128);
+#pragma unroll
+          for (int j = 0; j < BK / 16; ++j) {
+            umma_bf16(d_addr, umma_desc_sw128(a0 + j * 32), umma_desc_sw128(b0 + j * 32), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+          }
+          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+        }
+        __syncwarp();
+      }
+      if (ok && lane == 0) umma_commit(&tfull[acc]);
+      __syncwarp();
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
+    if (WKIND == 1) {
+      const int r = threadIdx.x - 64;  // weight row inside the tile
+      uint32_t it = 0;
+      bool ok = true;
+      const int gshift = p.group_ktiles;  // k tiles per quantisation group
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+        int nt, tt, sp_, k0, k1;
+        decode(w, nt, tt, sp_, k0, k1);
+        const uint32_t* szp = p.w4_sz + (size_t)nt * BM + r;
+        int cur_g = -1;
+        uint32_t s2 = 0, zb2 = 0;
+        for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
+          int g = kt / gshift;
+          if (g != cur_g) {
+            cur_g = g;
+            uint32_t v = __ldg(szp + (size_t)g * p.n_pad);
+            s2 = (v & 0xffffu) | (v << 16);
+            zb2 = (v >> 16) | (v & 0xffff0000u);
+          }
+          int ps = it % PS, s = it % S;
+          ok = mbar_wait(&pfull[ps], (it / PS) & 1, abort_flag);
+          if (ok) ok = mbar_wait(&empty[s], ((it / S) & 1) ^ 1, abort_flag);
+          if (!ok) break;
+          const uint4* src = reinterpret_cast<const uint4*>(sp + ps * kPackedBytes);
+          uint4 h0 = src[r], h1 = src[128 + r];
+          uint32_t words[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+          uint8_t* dst = sw + (size_t)s * kWStageBytes + r * 128;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t q = words[c];
+            uint4 o;
+            o.x = dq_pair(q, zb2, s2);
+            o.y = dq_pair(q >> 4, zb2, s2);
+            o.z = dq_pair(q >> 8, zb2, s2);
+            o.w = dq_pair(q >> 12, zb2, s2);
+            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+          }
+          fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+          mbar_arrive(&w_ready[s]);
+          mbar_arrive(&pempty[ps]);
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int row = q * 32 + lane;       // weight row inside the tile
+    const int et = threadIdx.x - 192;    // 0..127
+    uint32_t tile_i = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
+      int nt, tt, sp_, k0, k1;
+      decode(w, nt, tt, sp_, k0, k1);
+      const int acc = tile_i & 1;
+      ok = mbar_wait(&tfull[acc], (tile_i >> 1) & 1, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
+      const int n = nt * BM + row;
+      const int t0 = tt * tn;
+      const int tile_id = nt * p.num_t_tiles + tt;
+      if (p.splits > 1) {
+        // fp32 partial -> workspace [tile][split][row][tn]
+        float* wsp = p.ws + (((size_t)tile_id * p.splits + sp_) * BM + row) * tn;
+        for (int c = 0; c < tn; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<uint4*>(wsp + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        }
+        tc_fence_before();
+        mbar_arrive(&tempty[acc]);
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (et == 0) {
+          int old = atomicAdd(&p.counters[tile_id], 1);
+          int last = (old == p.splits - 1);
+          if (last) p.counters[tile_id] = 0;  // ready for the next launch
+          *red_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!*red_flag) continue;
+        __threadfence();
+        // last arriver: sum the splits in fixed order (bit-stable) and run the real epilogue from registers
+        const float* base = p.ws + ((size_t)tile_id * p.splits * BM + row) * tn;
+        for (int c = 0; c < tn; c += 32) {
+          float a[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) a[j] = 0.f;
+          for (int s2 = 0; s2 < p.splits; ++s2) {
+            const float4* src = reinterpret_cast<const float4*>(base + (size_t)s2 * BM * tn + c);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              float4 f = __ldcg(src + j);
+              a[4 * j] += f.x; a[4 * j + 1] += f.y; a[4 * j + 2] += f.z; a[4 * j + 3] += f.w;
+            }
+          }
+          if (p.epi == EPI_SILU_MUL) {
+            const int n_out = (nt * BM + q * 32) / 2 + (lane & 15);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float other = __shfl_xor_sync(0xffffffffu, a[j], 16);
+              int t = t0 + c + j;
+              if (!(lane & 16) && t < p.T && n_out < p.n_out) {
+                float g = a[j];
+                p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(g / (1.f + __expf(-g)) * other);
+              }
+            }
+          } else {
+            float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              int t = t0 + c + j;
+              if (t < p.T && n < p.N) p.out[(size_t)t * p.ldo + n] = __float2bfloat16(a[j] + b);
+            }
+          }
+        }
+        continue;
+      }
+      // ---- single-pass epilogue
+      if (p.epi == EPI_SILU_MUL) {
+        const int n_out = (nt * BM + q * 32) / 2 + (lane & 15);
+        for (int c = 0; c < tn; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float mine = __uint_as_float(v[j]);
+            float other = __shfl_xor_sync(0xffffffffu, mine, 16);
+            int t = t0 + c + j;
+            if (!(lane & 16) && t < p.T && n_out < p.n_out)
+              p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(mine / (1.f + __expf(-mine)) * other);
+          }
+        }
+      } else {
+        float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+        for (int c = 0; c < tn; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            int t = t0 + c + j;
+            if (t < p.T && n < p.N) p.out[(size_t)t * p.ldo + n] = __float2bfloat16(__uint_as_float(v[j]) + b);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag && threadIdx.x == 0) {
+    // give copies that are still in flight a bounded chance to land before the CTA's shared memory is released
+    uint64_t t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 2000000ull) {}
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn get_encode() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+    fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  }
+  return fn;
+}
+
+// bf16 [rows, cols] row-major (row stride ld elements) -> box of {64 cols, box_rows rows}, 128-byte swizzle
+int make_tmap_bf16(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return -1;
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {ld * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : (int)r;
+}
+
+}  // namespace
+
+int gemm_smem_bytes(int tn, int stages, int pstages) { return (int)make_layout(tn, stages, pstages).total + 1024; }
+
+// Picks the token tile, split-K factor and pipeline depths. Split-K spreads few-tile problems (decode) over all SMs.
+void gemm_plan(GemmParams& p, int num_sms, bool w4) {
+  int T = p.T;
+  int tn = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
+  if (T > 256) {
+    // avoid a nearly empty last token tile when 128 divides the token count better
+    int waste256 = ((T + 255) / 256) * 256 - T, waste128 = ((T + 127) / 128) * 128 - T;
+    if (waste128 + 64 < waste256 && T < 1024) tn = 128;
+  }
+  p.tn = tn;
+  p.num_t_tiles = (T + tn - 1) / tn;
+  p.num_n_tiles = (p.n_rows + BM - 1) / BM;
+  int ktiles = p.K / BK;
+  int tiles = p.num_t_tiles * p.num_n_tiles;
+  int best = 1;
+  if (tiles < num_sms && p.ws != nullptr) {
+    double best_score = -1;
+    for (int s = 1; s <= 16; ++s) {
+      int per = (ktiles + s - 1) / s;
+      if (per < 4 || (s - 1) * per >= ktiles) continue;  // every split needs work
+      if ((size_t)tiles * s * BM * tn * 4 > p.ws_bytes || tiles > p.max_counters) break;
+      int items = tiles * s;
+      int waves = (items + num_sms - 1) / num_sms;
+      // time ~ waves * k tiles per item (+ a fixed cost per item for the reduction traffic)
+      double cost = waves * (per + 6.0);
+      double score = 1.0 / cost;
+      if (score > best_score * 1.02) { best_score = score; best = s; }
+    }
+  }
+  p.splits = best;
+  p.ktiles_per_split = (ktiles + best - 1) / best;
+  // pipeline depth from the shared-memory budget (227 KB per CTA)
+  int budget = 220 * 1024;
+  p.pstages = w4 ? (tn <= 64 ? 12 : 6) : 0;
+  int per_stage = tn * 128 + kWStageBytes;
+  int s = (budget - p.pstages * kPackedBytes - 2048) / per_stage;
+  p.stages = s > 8 ? 8 : (s < 2 ? 2 : s);
+}
+
+int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream) {
+  GemmParams p = p_in;
+  const bool w4 = p.w4 != nullptr;
+  CUtensorMap tmX, tmW;
+  if (make_tmap_bf16(&tmX, x, (uint64_t)p.T, (uint64_t)p.K, (uint64_t)ldx, (uint32_t)p.tn)) return -2;
+  if (!w4) {
+    if (make_tmap_bf16(&tmW, w_bf16, (uint64_t)p.n_rows, (uint64_t)p.K, (uint64_t)ldw, BM)) return -3;
+  } else {
+    tmW = tmX;
+  }
+  int total = p.num_n_tiles * p.num_t_tiles * p.splits;
+  int grid = total < num_sms ? total : num_sms;
+  int smem = gemm_smem_bytes(p.tn, p.stages, p.pstages);
+  static int configured[2] = {0, 0};
+  if (w4) {
+    if (configured[1] < smem) {
+      if (cudaFuncSetAttribute(gemm_wx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
+      configured[1] = 227 * 1024;
+    }
+    gemm_wx_kernel<1><<<grid, kThreads, smem, stream>>>(tmX, tmW, p);
+  } else {
+    if (configured[0] < smem) {
+      if (cudaFuncSetAttribute(gemm_wx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
+      configured[0] = 227 * 1024;
+    }
+    gemm_wx_kernel<0><<<grid, kThreads, smem, stream>>>(tmX, tmW, p);
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -5;
+}
+
+unsigned int gemm_read_status(bool clear) { return read_status_tu(clear); }
+
+}  // namespace oc

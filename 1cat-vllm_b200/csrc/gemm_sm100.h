@@ -1,0 +1,35 @@
+// Host interface of the tcgen05 GEMM (see gemm_sm100.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oc {
+
+enum { EPI_STORE = 0, EPI_SILU_MUL = 1 };
+
+struct GemmParams {
+  int T, N, K;        // tokens, logical output features, reduction length (multiple of 64)
+  int n_rows;         // weight rows the kernel walks (N, or 2*n_out for the interleaved gate|up layout)
+  int n_out;          // output columns for EPI_SILU_MUL
+  int n_pad;          // padded weight rows (stride of the scale/zero table)
+  int tn, num_t_tiles, num_n_tiles, splits, ktiles_per_split, stages, pstages;
+  int epi;
+  int group_ktiles;   // 64-wide k tiles per quantisation group (group 128 -> 2)
+  __nv_bfloat16* out;
+  int ldo;
+  const __nv_bfloat16* bias;
+  float* ws;          // split-K workspace
+  size_t ws_bytes;
+  int* counters;      // one per output tile, zero between launches
+  int max_counters;
+  const uint8_t* w4;        // packed 4-bit tiles [n tile][k tile][4096 B]
+  const uint32_t* w4_sz;    // [group][n_pad] : bf16 scale | bf16 (128 + zero) << 16
+};
+
+void gemm_plan(GemmParams& p, int num_sms, bool w4);
+int gemm_smem_bytes(int tn, int stages, int pstages);
+int gemm_launch(const GemmParams& p, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream);
+unsigned int gemm_read_status(bool clear);
+
+}  // namespace oc

@@ -1,0 +1,54 @@
+// Host launchers of the non-GEMM kernels. All take raw device pointers and a stream; return 0 on success.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace oc {
+
+struct RopeCacheParams {
+  __nv_bfloat16 *q, *k, *v;
+  long long q_st, q_sh, k_st, v_st;  // element strides: token / head (k and v heads are D apart)
+  const int* positions;
+  const float* cos_sin;  // [max_pos][rot]: cos | sin
+  __nv_bfloat16* kv_cache;  // [blocks][2][Hkv][bs][D] or null
+  const int* slot_mapping;
+  const __nv_bfloat16 *q_norm, *k_norm;  // per-head RMSNorm weights or null
+  int T, Hq, Hkv, D, rot, bs, gemma;
+  float eps;
+};
+
+int rms_norm_launch(const void* x, const void* res_in, const void* w, void* y, void* res_out, int T, int H, int ldx, float eps,
+                    int gemma, cudaStream_t st);
+int rms_norm_gated_launch(const void* x, const void* z, const void* w, void* y, int rows, int D, int ldx, int ldz, int heads,
+                          float eps, cudaStream_t st);
+int silu_and_mul_launch(const void* x, void* y, int T, int I, cudaStream_t st);
+int rope_cache_launch(const RopeCacheParams& p, cudaStream_t st);
+int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st);
+unsigned int elementwise_read_status(bool clear);
+
+struct AttnParams {
+  const __nv_bfloat16* q;     // [T][Hq][D] with strides
+  long long q_st, q_sh;
+  const __nv_bfloat16* kv_cache;  // [blocks][2][Hkv][bs][D]
+  __nv_bfloat16* out;         // [T][Hq][D] contiguous
+  float* lse;                 // [T][Hq] or null
+  const int* query_start_loc; // [R+1]
+  const int* seq_lens;        // [R]
+  const int* block_table;     // [R][bt_stride]
+  int bt_stride;
+  int R, T, Hq, Hkv, D, bs;
+  float scale;
+  int num_q_tiles;            // grid.x for prefill mode (host: sum over requests of ceil(q_len / tokens per tile))
+  int splits;                 // decode mode: KV splits per (request, kv head)
+  float* ws_o;                // [splits][T][Hq][D] fp32 partial outputs
+  float* ws_ml;               // [splits][T][Hq][2]  running max (log2 domain) and sum
+  int max_q_len;
+  int short_q_len;            // requests with at most this many query tokens run in mode 1, the others in mode 0
+};
+// mode 0: rows of a query tile are spread over warps (prefill / long queries); mode 1: keys are spread over warps
+// (decode and short verify queries, with split-KV + combine).
+int attention_launch(const AttnParams& p, int mode, cudaStream_t st);
+unsigned int attention_read_status(bool clear);
+
+}  // namespace oc

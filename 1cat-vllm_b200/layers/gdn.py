@@ -61,5 +61,5 @@ class GatedDeltaNet(nn.Module):
             v = mixed[:, 2 * self.key_dim:].reshape(T, self.Hv, self.V)
             g, beta = ref.gdn_gating(a, b, self.A_log, self.dt_bias)
             o = ref.gated_delta_rule(q, k, v, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
-        o = ops.rms_norm_gated(o.reshape(T * self.Hv, self.V), z.reshape(T * self.Hv, self.V), self.norm_weight, self.eps)
-        return self.out_proj(o.reshape(T, self.Hv * self.V))
+        o = ops.rms_norm_gated(o.reshape(T, self.Hv * self.V), z, self.norm_weight, self.eps, self.Hv)
+        return self.out_proj(o)

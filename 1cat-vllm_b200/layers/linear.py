@@ -67,6 +67,11 @@ class UnquantizedMethod(LinearMethod):
     def dequantized_weight(self, layer):
         return layer.weight
 
+    def process_weights_after_loading(self, layer):
+        if layer.weight.is_cuda and layer.weight.dtype == torch.bfloat16:
+            from onecat_vllm.ops import cuda as K
+            K.prepare_bf16(layer)
+
 
 class AWQMethod(LinearMethod):
     name = "awq"

@@ -158,3 +158,46 @@ def load_model(cfg, device) -> nn.Module:
         load_weights(model, iter_safetensors(cfg.model))
     process_weights_after_loading(model)
     return model.eval()
+
+
+def to_hf_state_dict(model: nn.Module) -> dict:
+    """Un-stack fused parameters back to HF checkpoint names (q/k/v, gate/up, per-expert tensors), for saving a
+    model built here as a checkpoint that any HF-layout loader (including this one) reads. TP size 1 only."""
+    out = {}
+    stacked = getattr(model, "stacked_params_mapping", [])
+    mods = dict(model.named_modules())
+    for name, p in model.state_dict().items():
+        mod_name, _, pname = name.rpartition(".")
+        mod = mods.get(mod_name)
+        hits = [(theirs, sid) for ours, theirs, sid in stacked if mod_name.endswith(ours)]
+        if hits and hasattr(mod, "local_output_sizes") and pname in ("weight", "bias", "qweight", "qzeros", "scales"):
+            oa, od, _, _ = mod.method.layout(mod, pname) if pname != "bias" else (0, 1, None, 1)
+            off = 0
+            ours = [o for o, t, s in stacked if mod_name.endswith(o)][0]
+            for theirs, sid in hits:
+                n = mod.local_output_sizes[sid] // od
+                out[mod_name[: -len(ours)] + theirs + "." + pname] = p.narrow(oa, off, n).contiguous()
+                off += n
+        elif mod_name.endswith(".experts") and pname in ("w13", "w2", "w13_scale", "w2_scale"):
+            leaf = "weight" if pname in ("w13", "w2") else "weight_scale_inv"
+            for e in range(p.shape[0]):
+                if pname.startswith("w13"):
+                    h = p.shape[1] // 2
+                    out[f"{mod_name}.{e}.gate_proj.{leaf}"] = p[e, :h].contiguous()
+                    out[f"{mod_name}.{e}.up_proj.{leaf}"] = p[e, h:].contiguous()
+                else:
+                    out[f"{mod_name}.{e}.down_proj.{leaf}"] = p[e].contiguous()
+        elif isinstance(mod, (nn.Module,)) and hasattr(mod, "vocab") and pname == "weight":
+            out[name] = p[: mod.vocab].contiguous()
+        else:
+            out[name] = p.contiguous()
+    return out
+
+
+def save_pretrained(model: nn.Module, hf_config: dict, path: str) -> None:
+    from safetensors.torch import save_file
+    os.makedirs(path, exist_ok=True)
+    sd = {k: v.detach().cpu() for k, v in to_hf_state_dict(model).items()}
+    save_file(sd, os.path.join(path, "model.safetensors"))
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(hf_config, f)

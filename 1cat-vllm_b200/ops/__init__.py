@@ -46,10 +46,12 @@ def paged_attention(q, kv_cache, md, scale, out=None):
     return ref.paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out)
 
 
-def rms_norm_gated(x, z, w, eps):
+def rms_norm_gated(x, z, w, eps, heads):
+    """x, z ``[T, heads*D]`` (column slices allowed) → ``[T, heads*D]``: per-head RMSNorm(x) * w * silu(z)."""
     if x.is_cuda:
-        return ext().rms_norm_gated(x, z, w, eps)
-    return ref.rms_norm_gated(x, z, w, eps)
+        return ext().rms_norm_gated(x, z, w, eps, heads)
+    T, D = x.shape[0], x.shape[1] // heads
+    return ref.rms_norm_gated(x.reshape(T * heads, D), z.reshape(T * heads, D), w, eps).reshape(T, heads * D)
 
 
 def argmax(logits):

@@ -1,0 +1,349 @@
+"""Python side of the sm_100a kernels: weight repacking, workspaces, launch planning.
+
+Importing this module loads the in-tree extension ``onecat_vllm.ops._C`` and fails loudly when it is missing: on a
+CUDA device there is no eager fallback for the ops implemented here. Ops whose kernels are not written yet
+(listed in ``TORCH_STANDINS``) run the PyTorch restatement on the device and are reported as such."""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+
+from onecat_vllm.ops import ref
+
+try:
+    from onecat_vllm.ops import _C
+except ImportError as e:  # pragma: no cover
+    raise ImportError("the CUDA extension onecat_vllm.ops._C is not built; run `python -c 'import __graft_entry__ as g; g.build()'` "
+                      f"or `python 1cat-vllm_b200/ops/build.py` ({e})") from e
+
+EPI_STORE, EPI_SILU_MUL = 0, 1
+TORCH_STANDINS: set = set()  # names of ops that ran as device-side PyTorch code in this process
+_LAUNCHES = 0  # launches of our own kernels (for bench accounting)
+_LIB_GEMM = os.environ.get("ONECAT_GEMM_BACKEND", "tcgen05") == "library"  # debug switch only
+
+
+def launches() -> int:
+    return _LAUNCHES
+
+
+def reset_launches() -> None:
+    global _LAUNCHES
+    _LAUNCHES = 0
+
+
+class _Workspace:
+    """Per-device scratch: split-K partials + tile counters, split-KV partials."""
+
+    def __init__(self, device):
+        self.device = device
+        self.splitk = torch.empty(64 << 20, dtype=torch.uint8, device=device)
+        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.attn_o = None
+        self.attn_ml = None
+
+    def attn_static(self, n_o: int, n_ml: int):
+        """Buffers whose addresses are baked into CUDA graphs: allocated once, never grown."""
+        if getattr(self, "s_o", None) is None:
+            self.s_o = torch.empty(n_o, dtype=torch.float32, device=self.device)
+            self.s_ml = torch.empty(n_ml, dtype=torch.float32, device=self.device)
+        assert self.s_o.numel() >= n_o and self.s_ml.numel() >= n_ml, "static attention workspace is too small"
+        return self.s_o, self.s_ml
+
+    def attn(self, n_o: int, n_ml: int):
+        if self.attn_o is None or self.attn_o.numel() < n_o:
+            self.attn_o = torch.empty(n_o, dtype=torch.float32, device=self.device)
+        if self.attn_ml is None or self.attn_ml.numel() < n_ml:
+            self.attn_ml = torch.empty(n_ml, dtype=torch.float32, device=self.device)
+        return self.attn_o, self.attn_ml
+
+
+_WS: dict = {}
+
+
+def workspace(device) -> _Workspace:
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    if key not in _WS:
+        _WS[key] = _Workspace(torch.device("cuda", key))
+    return _WS[key]
+
+
+def check_status(clear: bool = True) -> int:
+    return int(_C.read_status(clear))
+
+
+# ----------------------------------------------------------------------------- weight repacking
+_NIB_ORDER = (0, 2, 4, 6, 1, 3, 5, 7)  # nibble i of a packed word holds k offset _NIB_ORDER[i]
+
+
+def interleave_gate_up(n_inter: int, device) -> torch.Tensor:
+    """Row permutation putting 16 gate rows next to the matching 16 up rows, so that one warp of the GEMM epilogue
+    holds both halves of SiLU(gate)*up."""
+    assert n_inter % 16 == 0, "the intermediate size must be a multiple of 16"
+    b = torch.arange(n_inter // 16, device=device).view(-1, 1, 1) * 16
+    j = torch.arange(16, device=device).view(1, 1, 16)
+    half = torch.tensor([0, n_inter], device=device).view(1, 2, 1)
+    return (b + j + half).reshape(-1)
+
+
+def pack_w4(q: torch.Tensor, z: torch.Tensor, s: torch.Tensor, group: int):
+    """q ``[N,K]`` uint8 codes, z ``[N,K/g]`` uint8 zeros, s ``[N,K/g]`` scales → (tiles uint8 ``[N/128, K/64, 4096]``,
+    sz int32 ``[K/g, Npad]``). A tile holds 128 rows × 64 k as two halves of ``[128 rows][4 words]``; each 32-bit word is
+    8 consecutive k of one row in ``_NIB_ORDER``."""
+    N, K = q.shape
+    assert K % 64 == 0 and group % 64 == 0, "K and the group size must be multiples of 64"
+    npad = -(-N // 128) * 128
+    if npad != N:
+        q = torch.cat([q, q.new_zeros(npad - N, K)])
+        z = torch.cat([z, z.new_zeros(npad - N, z.shape[1])])
+        s = torch.cat([s, s.new_zeros(npad - N, s.shape[1])])
+    nt, kt = npad // 128, K // 64
+    qq = q.view(nt, 128, kt, 8, 8).to(torch.int32)
+    words = torch.zeros(nt, 128, kt, 8, dtype=torch.int32, device=q.device)
+    for i, k in enumerate(_NIB_ORDER):
+        words |= qq[..., k] << (4 * i)
+    tiles = words.view(nt, 128, kt, 2, 4).permute(0, 2, 3, 1, 4).contiguous().view(torch.uint8).view(nt, kt, 4096)
+    sb = s.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    zb = (z.to(torch.float32) + 128.0).to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+    sz = (sb | (zb << 16)).t().contiguous()
+    return tiles, sz, npad
+
+
+def prepare_w4(layer, q: torch.Tensor, z: torch.Tensor, s: torch.Tensor, group: int) -> None:
+    """Repack a 4-bit layer for the kernel. ``q/z/s`` are in logical ``[out, in]`` orientation."""
+    n_rows = q.shape[0]
+    n_out = n_rows
+    epi = EPI_STORE
+    if layer.fuse_silu_mul:
+        perm = interleave_gate_up(n_rows // 2, q.device)
+        q, z, s = q[perm], z[perm], s[perm]
+        n_out, epi = n_rows // 2, EPI_SILU_MUL
+    tiles, sz, npad = pack_w4(q.contiguous(), z.contiguous(), s.contiguous(), group)
+    layer.kernel_state = dict(kind="w4", tiles=tiles, sz=sz, n_rows=n_rows, n_out=n_out, n_pad=npad, epi=epi, group_ktiles=group // 64,
+                              K=q.shape[1])
+
+
+def prepare_bf16(layer) -> None:
+    w = layer.weight.data
+    n_rows, epi, n_out = w.shape[0], EPI_STORE, w.shape[0]
+    if layer.fuse_silu_mul:
+        w = w[interleave_gate_up(n_rows // 2, w.device)].contiguous()
+        layer.weight.data = w
+        epi, n_out = EPI_SILU_MUL, n_rows // 2
+    layer.kernel_state = dict(kind="bf16", n_rows=n_rows, n_out=n_out, epi=epi, K=w.shape[1])
+
+
+def prepare_fp8(layer, block) -> None:
+    """FP8 checkpoints are expanded to bf16 once at load and served by the dense kernel."""
+    w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
+    _swap_to_dense(layer, w)
+
+
+def prepare_fp4(layer, kind: str) -> None:
+    w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
+    _swap_to_dense(layer, w)
+
+
+def _swap_to_dense(layer, w: torch.Tensor) -> None:
+    from onecat_vllm.layers.linear import UnquantizedMethod
+    for n in ("weight", "weight_scale", "weight_scale_inv", "weight_scale_2"):
+        if hasattr(layer, n):
+            delattr(layer, n)
+    layer.weight = torch.nn.Parameter(w.contiguous(), requires_grad=False)
+    layer.method = UnquantizedMethod()
+    prepare_bf16(layer)
+
+
+# ----------------------------------------------------------------------------- GEMM
+def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0):
+    global _LAUNCHES
+    ws = workspace(x.device)
+    _C.gemm(x, w, w4, sz, out, bias, ws.splitk, ws.counters, N, n_rows, n_out, n_pad, epi, gk, force_splits, force_tn)
+    _LAUNCHES += 1
+    return out
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
+              force_splits: int = 0, force_tn: int = 0) -> torch.Tensor:
+    """x ``[T,K]`` @ w ``[N,K]``^T → ``[T,N]`` bf16."""
+    N = w.shape[0]
+    if _LIB_GEMM:
+        return torch.nn.functional.linear(x, w, bias)
+    if out is None:
+        out = torch.empty(x.shape[0], N, dtype=torch.bfloat16, device=x.device)
+    if x.stride(-1) != 1 or (x.stride(0) * 2) % 16:
+        x = x.contiguous()
+    return _gemm(x, w, None, None, out, bias, N, N, N, 0, EPI_STORE, 1, force_splits, force_tn)
+
+
+def linear(layer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    ks = layer.kernel_state
+    if ks is None:
+        prepare_bf16(layer)
+        ks = layer.kernel_state
+    T = x.shape[0]
+    if x.stride(-1) != 1 or (x.stride(0) * 2) % 16:
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty(T, ks["n_out"], dtype=torch.bfloat16, device=x.device)
+    bias = layer.bias
+    if ks["kind"] == "w4":
+        if _LIB_GEMM:
+            raise RuntimeError("the library GEMM debug switch does not cover 4-bit weights")
+        return _gemm(x, None, ks["tiles"], ks["sz"], out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], ks["n_pad"], ks["epi"], ks["group_ktiles"])
+    if _LIB_GEMM:
+        y = torch.nn.functional.linear(x, layer.weight, bias)
+        if ks["epi"] == EPI_SILU_MUL:  # rows are interleaved in blocks of 16
+            y = y.view(T, -1, 2, 16)
+            return (torch.nn.functional.silu(y[:, :, 0].float()) * y[:, :, 1].float()).to(x.dtype).reshape(T, -1)
+        return y
+    return _gemm(x, layer.weight, None, None, out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], 0, ks["epi"], 1)
+
+
+# ----------------------------------------------------------------------------- elementwise
+def rms_norm(x, w, eps, residual=None, gemma=False):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    if w.dtype != torch.bfloat16:
+        w = w.to(torch.bfloat16)
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    y, r = _C.rms_norm(x, w, eps, residual, gemma)
+    return y, r
+
+
+def rms_norm_gated(x, z, w, eps, heads):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    T = x.shape[0]
+    if x.stride(-1) != 1:
+        x = x.contiguous()
+    if z.stride(-1) != 1:
+        z = z.contiguous()
+    return _C.rms_norm_gated(x, z, w.to(torch.bfloat16), eps, heads).view(T, -1)
+
+
+def silu_and_mul(x):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    return _C.silu_and_mul(x.contiguous())
+
+
+def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
+
+
+def argmax(logits):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    return _C.argmax(logits)
+
+
+# ----------------------------------------------------------------------------- attention
+_NUM_SMS: dict = {}
+
+
+def _sms(device) -> int:
+    k = device.index or 0
+    if k not in _NUM_SMS:
+        _NUM_SMS[k] = torch.cuda.get_device_properties(device).multi_processor_count
+    return _NUM_SMS[k]
+
+
+def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, num_sms: int, force_splits: int = 0):
+    """Decide which requests take the decode kernel (rows = q_len * group fit in one 16/32-row tile) and how many KV
+    splits it uses. Returns (short_q_len, num_q_tiles for the prefill kernel, splits)."""
+    G = Hq // Hkv
+    max_rows = 32 if D == 128 else 16
+    short = max_rows // G
+    n_short = sum(1 for q in query_lens if 0 < q <= short)
+    TQ = 64 // G
+    tiles = sum(-(-q // TQ) for q in query_lens if q > short)
+    splits = 1
+    if n_short:
+        max_s = max((s for q, s in zip(query_lens, seq_lens) if q <= short), default=1)
+        want = max(1, (2 * num_sms) // max(n_short * Hkv, 1))
+        splits = max(1, min(want, -(-max_s // 256), 32))
+    if force_splits:
+        splits = force_splits
+    return short, tiles, splits
+
+
+def paged_attention(q, kv_cache, md, scale, out=None, lse=None):
+    global _LAUNCHES
+    T, Hq, D = q.shape
+    Hkv = kv_cache.shape[2]
+    if out is None:
+        out = torch.empty(T, Hq, D, dtype=q.dtype, device=q.device)
+    plan = getattr(md, "attn_plan", None)
+    if plan is None or plan[0] != (Hq, Hkv, D):
+        plan = ((Hq, Hkv, D), plan_attention(md.query_lens_cpu, md.seq_lens_cpu, Hq, Hkv, D, _sms(q.device)))
+        md.attn_plan = plan
+    short, tiles, splits = plan[1]
+    n_short = sum(1 for x in md.query_lens_cpu if 0 < x <= short)
+    ws_o = ws_ml = None
+    if n_short and splits > 1:
+        w = workspace(q.device)
+        ws_o, ws_ml = (w.attn_static if getattr(md, "static_ws", False) else w.attn)(splits * T * Hq * D, splits * T * Hq * 2)
+    if n_short:
+        _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 1, 0, splits,
+                           md.max_query_len, short, ws_o, ws_ml)
+        _LAUNCHES += 2 if splits > 1 else 1
+    if tiles:
+        _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 0, tiles, 1,
+                           md.max_query_len, short, None, None)
+        _LAUNCHES += 1
+    return out
+
+
+# ----------------------------------------------------------------------------- ops still served by device-side PyTorch
+def gdn_forward(mixed, b, a, conv_w, A_log, dt_bias, conv_state, ssm_state, md, Hk, Hv, K, V):
+    TORCH_STANDINS.add("gdn_forward")
+    T = mixed.shape[0]
+    key_dim = Hk * K
+    mixed = ref.causal_conv1d(mixed.contiguous(), conv_w, None, conv_state, md.query_start_loc, md.state_slots, md.has_initial_state)
+    qq = mixed[:, :key_dim].reshape(T, Hk, K)
+    kk = mixed[:, key_dim:2 * key_dim].reshape(T, Hk, K)
+    vv = mixed[:, 2 * key_dim:].reshape(T, Hv, V)
+    g, beta = ref.gdn_gating(a, b, A_log, dt_bias)
+    return ref.gated_delta_rule(qq, kk, vv, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
+
+
+def prepare_moe(moe) -> None:
+    moe.kernel_state = None
+
+
+def route(logits, cfg, bias):
+    TORCH_STANDINS.add("route")
+    if cfg.scoring_func == "sigmoid" or cfg.n_group > 1:
+        return ref.grouped_topk(logits, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group, bias, cfg.scoring_func,
+                                cfg.norm_topk_prob, cfg.routed_scaling_factor)
+    return ref.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+
+
+def fused_moe(moe, x, topk_w, topk_ids):
+    TORCH_STANDINS.add("fused_moe")
+    w13, w2 = moe.dequantized()
+    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, moe.e_off)
+
+
+def mla_decode(q_abs, q_pe, latent_cache, md, scale, lora):
+    TORCH_STANDINS.add("mla_decode")
+    return ref.mla_decode(q_abs, q_pe, latent_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, lora)
+
+
+def rejection_sample(draft_ids, num_draft, target_logits, bonus_ids, md, draft_probs, uniforms, synthetic_rates, gen):
+    TORCH_STANDINS.add("rejection_sample")
+    B, k = draft_ids.shape
+    greedy = torch.ones(B, dtype=torch.bool, device=draft_ids.device) if md.all_greedy else (md.temperature < 1e-5)
+    if md.all_greedy:
+        probs, noise = target_logits[:, :k].float(), None
+    else:
+        t = torch.where(md.temperature < 1e-5, torch.ones_like(md.temperature), md.temperature).view(B, 1, 1)
+        probs = torch.softmax(target_logits[:, :k].float() / t, dim=-1)
+        noise = torch.empty_like(probs).exponential_(generator=gen)
+    return ref.rejection_sample(draft_ids, num_draft, probs, bonus_ids, draft_probs, uniforms,
+                                greedy if synthetic_rates is None else None, synthetic_rates, noise, -1)

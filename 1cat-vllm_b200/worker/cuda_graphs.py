@@ -1,0 +1,112 @@
+"""CUDA graphs for uniform decode batches (reference: vllm/v1/cudagraph_dispatcher.py:141,272-359;
+compilation/cuda_graph.py:147,268; capture sizes config/vllm.py:2084-2200).
+
+A graph is keyed by (padded request count, tokens per request, KV-split count). Batches are padded up to the next
+captured size; the split count follows the live context length in power-of-two buckets, so short contexts never
+launch a grid sized for the longest one (the reference's context-bucketed graphs). All inputs live in the runner's
+persistent device buffers, so replay needs no pointer patching."""
+from __future__ import annotations
+
+import bisect
+from typing import Optional
+
+import torch
+
+from onecat_vllm.logger import init_logger
+from onecat_vllm.worker.attn_metadata import AttentionMetadata
+
+log = init_logger(__name__)
+
+
+class DecodeGraphs:
+    def __init__(self, runner):
+        self.r = runner
+        sc = runner.cfg.scheduler_config
+        self.sizes = [s for s in sc.graph_capture_sizes() if s <= max(sc.max_num_seqs, 1)]
+        if not self.sizes or self.sizes[-1] < sc.max_num_seqs:
+            self.sizes.append(sc.max_num_seqs)
+        self.graphs: dict = {}
+        self.pool = None
+        self.stream = torch.cuda.Stream()
+        mc = runner.mc
+        from onecat_vllm.ops import cuda as K
+        layers = [l for l in runner.model.model.layers if l.kind == "full_attention"]
+        self.attn_layers = layers
+        self.max_q = 1 + runner.num_spec
+        if layers:
+            a = layers[0].self_attn
+            tmax = self.sizes[-1] * self.max_q
+            K.workspace(runner.device).attn_static(32 * tmax * a.Hq * a.D, 32 * tmax * a.Hq * 2)
+        self.eligible = all(l.kind == "full_attention" for l in runner.model.model.layers)
+        self.hits = self.misses = 0
+
+    def plan(self, R: int, q: int, max_seq: int) -> Optional[tuple]:
+        """Returns (padded R, q, splits) or None when the batch must run eagerly."""
+        if not self.eligible or R > self.sizes[-1] or q > self.max_q:
+            return None
+        rp = self.sizes[bisect.bisect_left(self.sizes, R)]
+        a = self.attn_layers[0].self_attn
+        from onecat_vllm.ops.cuda import _sms
+        want = max(1, (2 * _sms(self.r.device)) // max(rp * a.Hkv, 1))
+        by_ctx = max(1, -(-max_seq // 256))
+        s = 1
+        while s * 2 <= min(want, by_ctx, 32):
+            s *= 2
+        return rp, q, s
+
+    def _metadata(self, rp: int, q: int, splits: int) -> AttentionMetadata:
+        r = self.r
+        T = rp * q
+        a = self.attn_layers[0].self_attn
+        md = AttentionMetadata(rp, T, r._view("qsl", rp + 1), r._view("seq", rp), r.d_bt[:rp], r._view("slot", T), r._view("pos", T),
+                               q, 0, r._view("sslot", rp), r._view("hinit", rp), [q] * rp, [0] * rp, is_uniform_decode=True,
+                               uniform_query_len=q)
+        G = a.Hq // a.Hkv
+        short = (32 if a.D == 128 else 16) // G
+        md.attn_plan = ((a.Hq, a.Hkv, a.D), (max(short, q) if q * G <= (32 if a.D == 128 else 16) else short,
+                                             0 if q <= short else rp * (-(-q // (64 // G))), splits))
+        md.static_ws = True
+        return md
+
+    def capture(self, key: tuple) -> None:
+        rp, q, splits = key
+        r = self.r
+        md = self._metadata(rp, q, splits)
+        ids = r._view("ids", rp * q)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(self.stream):
+            for _ in range(2):  # warm up allocator and lazy kernel attributes outside capture
+                r.model(ids, md, r.kv_caches)
+        self.stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, pool=self.pool, stream=self.stream):
+            out = r.model(ids, md, r.kv_caches)
+        if self.pool is None:
+            self.pool = g.pool()
+        self.graphs[key] = (g, out)
+
+    def capture_all(self) -> None:
+        """Pre-capture the no-split graphs; split variants are captured on first use."""
+        if not self.eligible:
+            log.info_once("CUDA graphs disabled for this model (non-attention mixers run eagerly)")
+            return
+        r = self.r
+        r.np_pack[:] = 0
+        r.np_bt[:] = 0
+        o = r._off
+        r.np_pack[o["slot"][0]: o["slot"][0] + o["slot"][1]] = -1
+        r.d_pack.copy_(r.h_pack)
+        r.d_bt.copy_(r.h_bt)
+        for s in reversed(self.sizes):
+            self.capture((s, 1, 1))
+        log.info_once(f"captured {len(self.graphs)} decode graphs (sizes up to {self.sizes[-1]})")
+
+    def run(self, key: tuple, T: int) -> torch.Tensor:
+        if key not in self.graphs:
+            self.misses += 1
+            self.capture(key)
+        else:
+            self.hits += 1
+        g, out = self.graphs[key]
+        g.replay()
+        return out[:T]

@@ -257,6 +257,20 @@ class ModelRunner:
         assert t == T
         return req_ids, R, T, n_l, logits_rows, drafts_of, max_q, max_s, max_nb
 
+    def _pad_inputs(self, R: int, T: int, rp: int, q: int) -> None:
+        """Fill the host staging arrays up to the captured batch size: padded requests own no tokens, padded tokens
+        write no KV (slot -1)."""
+        npk, o = self.np_pack, self._off
+        tp = rp * q
+        npk[o["ids"][0] + T: o["ids"][0] + tp] = 0
+        npk[o["pos"][0] + T: o["pos"][0] + tp] = 0
+        npk[o["slot"][0] + T: o["slot"][0] + tp] = -1
+        npk[o["qsl"][0] + R + 1: o["qsl"][0] + rp + 1] = T
+        npk[o["seq"][0] + R: o["seq"][0] + rp] = 0
+        npk[o["sslot"][0] + R: o["sslot"][0] + rp] = 0
+        npk[o["hinit"][0] + R: o["hinit"][0] + rp] = 0
+        self.np_bt[R:rp, :1] = 0
+
     def _commit_inputs(self, R: int, T: int, n_l: int, max_nb: int) -> None:
         """Host → device copies of this step's inputs (non-blocking from pinned memory on GPUs)."""
         if self.use_cuda:
@@ -329,7 +343,13 @@ class ModelRunner:
         if timed:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
-        self._commit_inputs(R, T, n_l, max_nb)
+        spec_any = any(len(d) > 0 for d in drafts_of)
+        gkey = None
+        if self.graphs is not None and max_q == min(query_lens) and not (spec_any and self.mc.is_hybrid):
+            gkey = self.graphs.plan(R, max_q, max_s)
+            if gkey is not None:
+                self._pad_inputs(R, T, gkey[0], max_q)
+        self._commit_inputs(max(R, gkey[0]) if gkey else R, T, n_l, max_nb)
         md = self._build_metadata(R, T, max_q, max_s, max_nb, query_lens, seq_lens)
         spec_verify = any(len(d) > 0 for d in drafts_of)
         gdn_spec = None
@@ -337,8 +357,8 @@ class ModelRunner:
             gdn_spec = self._begin_gdn_spec(md)
         ids = self._view("ids", T)
         hidden = None
-        if self.graphs is not None and md.is_uniform_decode and not (spec_verify and self.mc.is_hybrid):
-            hidden = self.graphs.run(self, md, ids)
+        if gkey is not None:
+            hidden = self.graphs.run(gkey, T)
         if hidden is None:
             hidden = self.model(ids, md, self.kv_caches)
         out = ModelRunnerOutput(req_ids=req_ids, sampled_token_ids=[[] for _ in req_ids])

@@ -1,0 +1,231 @@
+"""Numerics of the sm_100a kernels against the fp32 PyTorch restatements in ``onecat_vllm.ops.ref``."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from onecat_vllm.ops import ref
+
+
+def K():
+    from onecat_vllm.ops import cuda
+    return cuda
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _close(a, b, rtol, atol, what=""):
+    a, b = a.float().cpu(), b.float().cpu()
+    err = (a - b).abs()
+    tol = atol + rtol * b.abs()
+    bad = err > tol
+    assert not bad.any(), f"{what}: {int(bad.sum())}/{bad.numel()} mismatches, max err {float(err.max()):.4g} at {int(err.argmax())}"
+
+
+@pytest.mark.parametrize("T,H", [(1, 2048), (5, 5120), (127, 7168), (300, 512)])
+@pytest.mark.parametrize("gemma", [False, True])
+def test_rms_norm(T, H, gemma):
+    g = torch.Generator(device="cuda").manual_seed(0)
+    x = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    r = torch.randn(T, H, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(H, device="cuda", generator=g) * 0.1 + (0 if gemma else 1)).bfloat16()
+    y, ro = K().rms_norm(x, w, 1e-6, r, gemma)
+    ye, re = ref.rms_norm(x.cpu(), w.cpu(), 1e-6, r.cpu(), gemma)
+    _close(ro, re, 0, 0, "residual")
+    _close(y, ye, 2e-2, 2e-2, "normed")
+    y2, none = K().rms_norm(x, w, 1e-6, None, gemma)
+    assert none is None
+    _close(y2, ref.rms_norm(x.cpu(), w.cpu(), 1e-6, None, gemma)[0], 2e-2, 2e-2)
+    assert K().check_status() == 0
+
+
+def test_silu_and_mul_and_argmax():
+    x = torch.randn(33, 2 * 1408, device="cuda").bfloat16()
+    _close(K().silu_and_mul(x), ref.silu_and_mul(x.cpu()), 1e-2, 1e-2)
+    lg = torch.randn(7, 151936, device="cuda").bfloat16()
+    lg[3, 777] = 100.0
+    assert K().argmax(lg).tolist() == lg.float().argmax(-1).tolist()
+    lf = torch.randn(5, 32000, device="cuda")
+    assert K().argmax(lf).tolist() == lf.argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("D,rot,qk_norm,gated", [(128, 128, False, False), (256, 64, True, True), (128, 64, True, False)])
+def test_rope_and_cache(D, rot, qk_norm, gated):
+    T, Hq, Hkv, bs, nb = 37, 6, 2, 16, 12
+    g = torch.Generator(device="cuda").manual_seed(1)
+    width = Hq * D * (2 if gated else 1) + 2 * Hkv * D
+    qkv = torch.randn(T, width, device="cuda", generator=g).bfloat16()
+    qw = Hq * D * (2 if gated else 1)
+    q = qkv[:, :qw].view(T, Hq, 2 * D)[..., :D] if gated else qkv[:, :qw].view(T, Hq, D)
+    k = qkv[:, qw:qw + Hkv * D].view(T, Hkv, D)
+    v = qkv[:, qw + Hkv * D:].view(T, Hkv, D)
+    pos = torch.randint(0, 500, (T,), device="cuda", dtype=torch.int32)
+    cs = ref.build_cos_sin_cache(rot, 512, 1e6, "cuda")
+    cache = torch.zeros(nb, 2, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    slots = torch.randperm(nb * bs, device="cuda")[:T].to(torch.int32)
+    slots[5] = -1
+    qn = (torch.randn(D, device="cuda") * 0.1).bfloat16() if qk_norm else None
+    kn = (torch.randn(D, device="cuda") * 0.1).bfloat16() if qk_norm else None
+    qkv_c = qkv.cpu().clone()
+    q_c = qkv_c[:, :qw].view(T, Hq, 2 * D)[..., :D] if gated else qkv_c[:, :qw].view(T, Hq, D)
+    k_c = qkv_c[:, qw:qw + Hkv * D].view(T, Hkv, D)
+    v_c = qkv_c[:, qw + Hkv * D:].view(T, Hkv, D)
+    cache_c = cache.cpu().clone()
+    ref.rope_and_cache(q_c, k_c, v_c, pos.cpu(), cs.cpu(), cache_c, slots.cpu(), rot, qn.cpu() if qk_norm else None,
+                       kn.cpu() if qk_norm else None, 1e-6, True)
+    K().rope_and_cache(q, k, v, pos, cs, cache, slots, rot, qn, kn, 1e-6, True)
+    _close(qkv, qkv_c, 2e-2, 2e-2, "q/k in place")
+    _close(cache, cache_c, 2e-2, 2e-2, "cache")
+    assert K().check_status() == 0
+
+
+def _ref_gemm(x, w):
+    return x.float().cpu() @ w.float().cpu().t()
+
+
+@pytest.mark.parametrize("T", [1, 5, 64, 127, 129, 300, 1000])
+@pytest.mark.parametrize("N,Kd", [(128, 64), (384, 256), (5120, 5120)])
+def test_gemm_bf16(T, N, Kd):
+    g = torch.Generator(device="cuda").manual_seed(T * 7 + N)
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    w = (torch.randn(N, Kd, device="cuda", generator=g) * 0.05).bfloat16()
+    y = K().gemm_bf16(x, w)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0, "a bounded device wait expired"
+    _close(y, _ref_gemm(x, w), 2e-2, 2e-2 * math.sqrt(Kd) * 0.05, f"gemm {T}x{N}x{Kd}")
+
+
+@pytest.mark.parametrize("splits,tn", [(2, 0), (5, 0), (1, 32), (3, 128)])
+def test_gemm_bf16_splitk_and_tiles(splits, tn):
+    T, N, Kd = 70, 640, 1280
+    x = torch.randn(T, Kd, device="cuda").bfloat16()
+    w = (torch.randn(N, Kd, device="cuda") * 0.05).bfloat16()
+    b = torch.randn(N, device="cuda").bfloat16()
+    if tn and tn < T:
+        tn = 0
+    y = K().gemm_bf16(x, w, bias=b, force_splits=splits, force_tn=tn)
+    y2 = K().gemm_bf16(x, w, bias=b, force_splits=splits, force_tn=tn)  # counters must be back to zero
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    e = _ref_gemm(x, w) + b.float().cpu()
+    _close(y, e, 2e-2, 5e-2, "split-k")
+    assert torch.equal(y, y2), "split-K reduction must be bit-stable across launches"
+
+
+class _FakeLayer:
+    def __init__(self, fuse):
+        self.fuse_silu_mul = fuse
+        self.bias = None
+        self.kernel_state = None
+
+
+@pytest.mark.parametrize("T", [1, 8, 64, 200, 700])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_gemm_w4(T, fuse):
+    N, Kd, grp = 1024, 768 if not fuse else 640, 128
+    if Kd % grp:
+        Kd = 768
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q = torch.randint(0, 16, (N, Kd), device="cuda", generator=g, dtype=torch.uint8)
+    z = torch.randint(0, 16, (N, Kd // grp), device="cuda", generator=g, dtype=torch.uint8)
+    s = (torch.randn(N, Kd // grp, device="cuda", generator=g).abs() * 0.01 + 1e-3).half()
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    layer = _FakeLayer(fuse)
+    K().prepare_w4(layer, q, z, s, grp)
+    y = K().linear(layer, x)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    wd = (q.float() - z.float().repeat_interleave(grp, 1)) * s.float().bfloat16().float().repeat_interleave(grp, 1)
+    wd = wd.bfloat16().float().cpu()
+    e = x.float().cpu() @ wd.t()
+    if fuse:
+        e = torch.nn.functional.silu(e[:, : N // 2]) * e[:, N // 2:]
+    _close(y, e, 3e-2, 3e-2, f"w4 T={T} fuse={fuse}")
+
+
+def test_awq_layer_matches_reference_dequant():
+    """AWQ checkpoint layout (int32 [K, N/8], nibble order 0,4,1,5,2,6,3,7) through the layer's repacking."""
+    from onecat_vllm.config import QuantConfig
+    from onecat_vllm.layers.linear import MergedColumnParallelLinear
+    Kd, I = 512, 256
+    with torch.device("cuda"):
+        layer = MergedColumnParallelLinear(Kd, [I, I], quant=QuantConfig("awq"), prefix="mlp.gate_up_proj", dtype=torch.bfloat16, fuse_silu_mul=True)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    layer.qweight.data = torch.randint(-2 ** 31, 2 ** 31 - 1, layer.qweight.shape, device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    layer.qzeros.data = torch.randint(-2 ** 31, 2 ** 31 - 1, layer.qzeros.shape, device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+    layer.scales.data = (torch.randn(layer.scales.shape, device="cuda", generator=g).abs() * 0.01 + 1e-3).half()
+    wd = ref.awq_dequantize(layer.qweight.cpu(), layer.qzeros.cpu(), layer.scales.cpu().float().bfloat16().float(), 128).t()
+    layer.process_weights_after_loading()
+    x = torch.randn(19, Kd, device="cuda", generator=g).bfloat16()
+    y = layer(x)
+    e = x.float().cpu() @ wd.float().bfloat16().float().t()
+    e = torch.nn.functional.silu(e[:, :I]) * e[:, I:]
+    _close(y, e, 3e-2, 3e-2, "awq layer")
+
+
+def _attn_case(qlens, ctxs, Hq, Hkv, D, bs=16, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    R = len(qlens)
+    seq = [c + q for q, c in zip(qlens, ctxs)]
+    nb_per = [-(-s // bs) for s in seq]
+    total = sum(nb_per) + 3
+    perm = torch.randperm(total, device="cuda", generator=g).to(torch.int32)
+    bt = torch.zeros(R, max(nb_per) + 2, dtype=torch.int32, device="cuda")
+    o = 0
+    for r, n in enumerate(nb_per):
+        bt[r, :n] = perm[o:o + n]
+        o += n
+    cache = (torch.randn(total, 2, Hkv, bs, D, device="cuda", generator=g) * 0.5).bfloat16()
+    T = sum(qlens)
+    q = (torch.randn(T, Hq, D, device="cuda", generator=g) * 0.5).bfloat16()
+    qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device="cuda")
+    sl = torch.tensor(seq, dtype=torch.int32, device="cuda")
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    md = AttentionMetadata(R, T, qsl, sl, bt, torch.zeros(T, dtype=torch.int32, device="cuda"), torch.zeros(T, dtype=torch.int32, device="cuda"),
+                           max(qlens), max(seq), query_lens_cpu=list(qlens), seq_lens_cpu=seq)
+    return q, cache, md
+
+
+@pytest.mark.parametrize("name,qlens,ctxs,Hq,Hkv,D", [
+    ("decode", [1] * 9, [0, 15, 16, 63, 64, 300, 1000, 2047, 5], 40, 8, 128),
+    ("verify4", [4] * 5, [10, 100, 777, 64, 60], 40, 8, 128),
+    ("prefill", [1, 17, 200, 64], [0, 0, 0, 0], 8, 2, 128),
+    ("chunked-prefix", [130, 33], [256, 1000], 10, 2, 128),
+    ("mixed", [1, 1, 300, 1, 2], [500, 20, 100, 0, 77], 40, 8, 128),
+    ("decode-d256", [1] * 4, [0, 100, 1025, 31], 24, 4, 256),
+    ("prefill-d256", [77, 5, 140], [0, 200, 64], 16, 2, 256),
+    ("verify-d256", [4, 4], [100, 3], 24, 4, 256),
+])
+def test_paged_attention(name, qlens, ctxs, Hq, Hkv, D):
+    q, cache, md = _attn_case(qlens, ctxs, Hq, Hkv, D)
+    scale = D ** -0.5
+    out = K().paged_attention(q, cache, md, scale)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    e = ref.paged_attention(q.cpu(), cache.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), scale)
+    _close(out, e, 2e-2, 1e-2, name)
+
+
+def test_paged_attention_forced_splits():
+    q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
+    from onecat_vllm.ops.cuda import plan_attention
+    for s in (2, 7, 32):
+        md.attn_plan = ((40, 8, 128), plan_attention(md.query_lens_cpu, md.seq_lens_cpu, 40, 8, 128, 148, force_splits=s))
+        out = K().paged_attention(q, cache, md, 128 ** -0.5)
+        e = ref.paged_attention(q.cpu(), cache.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), 128 ** -0.5)
+        _close(out, e, 2e-2, 1e-2, f"splits={s}")
+
+
+def test_rms_norm_gated():
+    T, Hh, D = 21, 6, 128
+    x = torch.randn(T, Hh * D, device="cuda").bfloat16()
+    zz = torch.randn(T, 3 * Hh * D, device="cuda").bfloat16()
+    z = zz[:, Hh * D: 2 * Hh * D]
+    w = torch.randn(D, device="cuda").bfloat16()
+    y = K().rms_norm_gated(x, z, w, 1e-6, Hh)
+    e = ref.rms_norm_gated(x.cpu().reshape(T * Hh, D), z.cpu().reshape(T * Hh, D), w.cpu(), 1e-6).reshape(T, Hh * D)
+    _close(y, e, 2e-2, 2e-2)

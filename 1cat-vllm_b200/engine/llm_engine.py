@@ -63,6 +63,7 @@ class LLMEngine:
     def step(self) -> list[RequestOutput]:
         outs = self.engine_core.get_output()
         now = time.time()
+        self.last_scheduler_stats = outs.scheduler_stats
         results, to_abort = self.output_processor.process_outputs(outs.outputs, now)
         if to_abort:
             self.engine_core.abort_requests(to_abort)

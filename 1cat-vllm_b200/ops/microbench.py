@@ -1,0 +1,158 @@
+"""Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
+
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|attn|norm] [--small] [--json PATH]``
+Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
+launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+
+import torch
+
+
+def _peaks() -> dict:
+    here = os.path.dirname(os.path.abspath(__file__))
+    for up in (3, 2):
+        p = os.path.join(*([here] + [".."] * up + ["MEASURED_PEAKS.json"]))
+        if os.path.exists(p):
+            d = json.load(open(p))
+            return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "src": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "src": "fallback"}
+
+
+_FLUSH = None
+
+
+def timeit(fn, iters: int = 10, warmup: int = 3, flush: bool = True) -> float:
+    global _FLUSH
+    if _FLUSH is None:
+        _FLUSH = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    ts = []
+    for _ in range(iters):
+        if flush:
+            _FLUSH.zero_()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    ts.sort()
+    return ts[len(ts) // 2]
+
+
+class _L:
+    def __init__(self, fuse=False):
+        self.fuse_silu_mul, self.bias, self.kernel_state = fuse, None, None
+
+
+def bench_gemm(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    shapes = [(8192, 7168, 5120), (8192, 34816, 5120), (8192, 5120, 17408), (1088, 34816, 5120), (64, 5120, 5120), (64, 151936, 5120)]
+    if small:
+        shapes = [(2048, 8192, 5120)]
+    for T, N, Kd in shapes:
+        x = torch.randn(T, Kd, device="cuda").bfloat16()
+        w = (torch.randn(N, Kd, device="cuda") * 0.02).bfloat16()
+        out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: K.gemm_bf16(x, w, out=out), 1 if small else iters, 1 if small else 3)
+        tf = 2.0 * T * N * Kd / ms / 1e9
+        lib = timeit(lambda: torch.matmul(x, w.t()), 1 if small else iters, 1 if small else 3)
+        rows.append(dict(kernel="gemm_bf16", T=T, N=N, K=Kd, ms=ms, tflops=tf, frac_of_peak=tf / pk["bf16_tflops"], cublas_ms=lib,
+                         cublas_tflops=2.0 * T * N * Kd / lib / 1e9))
+        del x, w, out
+
+
+def bench_w4(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    cases = [(64, 7168, 5120, False), (64, 34816, 5120, True), (64, 5120, 17408, False), (64, 5120, 5120, False), (1, 34816, 5120, True),
+             (256, 34816, 5120, True), (1088, 34816, 5120, True), (8192, 34816, 5120, True), (8192, 5120, 17408, False)]
+    if small:
+        cases = [(64, 34816, 5120, True)]
+    for T, N, Kd, fuse in cases:
+        q = torch.randint(0, 16, (N, Kd), device="cuda", dtype=torch.uint8)
+        z = torch.randint(0, 16, (N, Kd // 128), device="cuda", dtype=torch.uint8)
+        s = (torch.rand(N, Kd // 128, device="cuda") * 0.01 + 1e-3).half()
+        layer = _L(fuse)
+        K.prepare_w4(layer, q, z, s, 128)
+        del q, z, s
+        x = torch.randn(T, Kd, device="cuda").bfloat16()
+        out = torch.empty(T, layer.kernel_state["n_out"], device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: K.linear(layer, x, out=out), 1 if small else iters, 1 if small else 3)
+        wbytes = N * Kd / 2 + N * (Kd // 128) * 4
+        bytes_ = wbytes + T * Kd * 2 + out.numel() * 2
+        tf = 2.0 * T * N * Kd / ms / 1e9
+        rows.append(dict(kernel="gemm_w4a16", T=T, N=N, K=Kd, fused_silu=fuse, ms=ms, gbs=bytes_ / ms / 1e6, frac_of_hbm=bytes_ / ms / 1e6 / pk["hbm_gbs"],
+                         tflops=tf, frac_of_peak=tf / pk["bf16_tflops"]))
+        del layer, x, out
+
+
+def bench_attn(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    cases = [("decode", 64, 1, 1150, 40, 8, 128), ("decode", 8, 1, 32768, 40, 8, 128), ("decode-d256", 64, 1, 2048, 24, 4, 256),
+             ("prefill", 8, 1024, 0, 40, 8, 128), ("prefill", 1, 8192, 0, 40, 8, 128), ("prefill-d256", 1, 4096, 0, 24, 4, 256)]
+    if small:
+        cases = [("decode", 64, 1, 1150, 40, 8, 128)]
+    for name, R, ql, ctx, Hq, Hkv, D in cases:
+        S = ctx + ql
+        nb = -(-S // 16)
+        total = R * nb + 1
+        cache = (torch.randn(total, 2, Hkv, 16, D, device="cuda") * 0.3).bfloat16()
+        bt = (torch.arange(R * nb, device="cuda", dtype=torch.int32) + 1).view(R, nb)
+        T = R * ql
+        q = (torch.randn(T, Hq, D, device="cuda") * 0.3).bfloat16()
+        qsl = (torch.arange(R + 1, device="cuda", dtype=torch.int32) * ql)
+        sl = torch.full((R,), S, device="cuda", dtype=torch.int32)
+        md = AttentionMetadata(R, T, qsl, sl, bt, None, None, ql, S, query_lens_cpu=[ql] * R, seq_lens_cpu=[S] * R)
+        out = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16)
+        ms = timeit(lambda: K.paged_attention(q, cache, md, D ** -0.5, out=out), 1 if small else iters, 1 if small else 3)
+        kv_bytes = R * S * 2 * Hkv * D * 2
+        flops = 4.0 * R * Hq * D * (ql * ctx + ql * (ql + 1) / 2)
+        rows.append(dict(kernel="paged_attention", case=name, R=R, q_len=ql, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=ms, kv_gbs=kv_bytes / ms / 1e6,
+                         frac_of_hbm=kv_bytes / ms / 1e6 / pk["hbm_gbs"], tflops=flops / ms / 1e9, plan=md.attn_plan[1]))
+        del cache, q, out
+
+
+def bench_norm(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    for T, H in ([(8192, 5120)] if small else [(8192, 5120), (64, 5120), (8192, 7168)]):
+        x = torch.randn(T, H, device="cuda").bfloat16()
+        r = torch.randn(T, H, device="cuda").bfloat16()
+        w = torch.ones(H, device="cuda").bfloat16()
+        ms = timeit(lambda: K.rms_norm(x, w, 1e-6, r, False), 1 if small else iters, 1 if small else 3)
+        b = 4 * T * H * 2
+        rows.append(dict(kernel="rms_norm_residual", T=T, H=H, ms=ms, gbs=b / ms / 1e6, frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"]))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--only", default="")
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    pk = _peaks()
+    rows: list = []
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm)):
+        if a.only and a.only != name:
+            continue
+        fn(rows, a.small, a.iters, pk)
+    from onecat_vllm.ops import cuda as K
+    res = {"peaks": pk, "rows": rows, "device_status": K.check_status()}
+    for r in rows:
+        print(json.dumps(r))
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump(res, f, indent=1)
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+    main()

@@ -78,12 +78,14 @@ class DecodeGraphs:
             for _ in range(2):  # warm up allocator and lazy kernel attributes outside capture
                 r.model(ids, md, r.kv_caches)
         self.stream.synchronize()
+        from onecat_vllm.ops import cuda as K
         g = torch.cuda.CUDAGraph()
+        n0 = K.launches()
         with torch.cuda.graph(g, pool=self.pool, stream=self.stream):
             out = r.model(ids, md, r.kv_caches)
         if self.pool is None:
             self.pool = g.pool()
-        self.graphs[key] = (g, out)
+        self.graphs[key] = (g, out, K.launches() - n0)  # kernels of ours inside one replay
 
     def capture_all(self) -> None:
         """Pre-capture the no-split graphs; split variants are captured on first use."""
@@ -107,6 +109,7 @@ class DecodeGraphs:
             self.capture(key)
         else:
             self.hits += 1
-        g, out = self.graphs[key]
+        g, out, n = self.graphs[key]
         g.replay()
+        self.r.graph_launches = getattr(self.r, "graph_launches", 0) + n
         return out[:T]

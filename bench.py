@@ -1,0 +1,223 @@
+#!/usr/bin/env python
+"""Headline benchmark: output tokens/s of the dense 27B-class AWQ W4A16 decoder (64 layers, hidden 5120, 40 q / 8 kv heads
+of 128, SwiGLU 17408, vocab 151936) serving 1024-in / 256-out requests at concurrency 64, tensor-parallel over N GPUs.
+
+A "step" is one engine iteration (schedule → forward → sample) of the continuous-batching steady state of that
+workload: 64 running requests whose progress is spread evenly over their 256 output tokens, a finished request being
+replaced at once by a fresh 1024-token prompt (so one step in four also carries a 1024-token prefill chunk).
+Weights are random (AWQ codes uniform, fp16 scales |N(0, 0.01)|), prompts are random token ids.
+
+``value`` is device-timed (CUDA events around each step's H2D copy, forward and sampling; max over ranks); ``e2e`` is
+the same steps timed by the wall clock through ``LLMEngine.add_request/step`` including scheduling, the pinned
+host→device input copy and the device→host read of the sampled ids.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CFG_27B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=5120, intermediate_size=17408, num_hidden_layers=64,
+               num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+               max_position_embeddings=4096, tie_word_embeddings=False,
+               quantization_config=dict(quant_method="awq", bits=4, group_size=128, zero_point=True))
+QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+
+def reference_arm(args) -> None:
+    print(json.dumps({"impl": "reference", "unavailable": "reference does not install offline: its setup.py imports setuptools_rust "
+                      "(no Rust toolchain in the image) and its CMake build fetches CUTLASS/FlashMLA/DeepGEMM from the network"}))
+
+
+class ClockSampler:
+    def __init__(self, index: int):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={QUERY}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(index)],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self) -> dict:
+        if self.p is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        self.f.seek(0)
+        sm, mx, pw, reasons = [], [], [], set()
+        for line in self.f:
+            c = [x.strip() for x in line.split(",")]
+            if len(c) < 9:
+                continue
+            try:
+                sm.append(float(c[1])); mx.append(float(c[2])); pw.append(float(c[3]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), c[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        try:
+            os.unlink(self.f.name)
+        except OSError:
+            pass
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--concurrency", type=int, default=64)
+    ap.add_argument("--input-len", type=int, default=1024)
+    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 makes the run invalid as a headline number")
+    ap.add_argument("--tp-comm", default=os.environ.get("ONECAT_TP_COMM", "fused"))
+    ap.add_argument("--eager", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run --nproc-per-node N for --gpus N")
+        raise SystemExit(f"WORLD_SIZE={world} but --gpus={args.gpus}")
+    if args.warmup < 3:
+        args.warmup = 3
+    torch.cuda.set_device(local)
+    from onecat_vllm.config import EngineArgs
+    from onecat_vllm.engine.llm_engine import LLMEngine
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
+
+    cfg = dict(CFG_27B)
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    C, IN, OUT = args.concurrency, args.input_len, args.output_len
+    ea = EngineArgs(hf_config=cfg, dtype="bfloat16", device="cuda", max_model_len=IN + OUT + 16, max_num_seqs=C, max_num_batched_tokens=8192,
+                    tensor_parallel_size=args.gpus, distributed_executor_backend="external_launcher" if args.gpus > 1 else None,
+                    tp_comm=args.tp_comm, enable_prefix_caching=False, gpu_memory_utilization=0.85, disable_log_stats=False,
+                    enforce_eager=args.eager, kv_cache_memory_bytes=int((C + 2) * (IN + OUT + 32) * cfg["num_hidden_layers"] * 2 * (8 // min(args.gpus, 8)) * 128 * 2))
+    eng = LLMEngine.from_engine_args(ea)
+    runner = eng.engine_core.core.executor.worker.runner
+    g = torch.Generator().manual_seed(0)
+    counter = [0]
+    timing = [False]
+    arrivals: dict = {}
+
+    def add(prompt_len: int, max_tokens: int) -> None:
+        ids = torch.randint(0, cfg["vocab_size"], (prompt_len,), generator=g).tolist()
+        sp = SamplingParams(temperature=0.0, max_tokens=max_tokens, ignore_eos=True, output_kind=RequestOutputKind.DELTA, detokenize=False)
+        eng.add_request(f"r{counter[0]}", ids, sp)
+        if timing[0]:
+            arrivals[f"r{counter[0]}"] = time.perf_counter()
+        counter[0] += 1
+
+    # steady state: request i has already produced i*OUT/C of its OUT tokens (same KV footprint as a prompt that long)
+    stride = max(OUT // C, 1)
+    for i in range(C):
+        done = min(i * stride, OUT - 1)
+        add(IN + done, OUT - done)
+
+    def one_step():
+        outs = eng.step()
+        new = fin = 0
+        for o in outs:
+            new += sum(len(c.token_ids) for c in o.outputs)
+            if o.finished:
+                fin += 1
+        for _ in range(fin):
+            add(IN, OUT)  # closed loop at fixed concurrency
+        st = getattr(eng, "last_scheduler_stats", None)
+        return new, (st.step_device_ms if st is not None else 0.0), (st.num_scheduled_tokens if st else 0), outs
+
+    # untimed: initial prefill of the staggered population, then W warm-up steps
+    while any(r.num_computed_tokens < r.num_prompt_tokens for r in eng.engine_core.core.scheduler.requests.values()):
+        one_step()
+    for _ in range(args.warmup):
+        one_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    K.reset_launches()
+    runner.graph_launches = 0
+    sampler = ClockSampler(local)
+    time.sleep(0.25)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    timing[0] = True
+    tokens, dev_ms, sched_tokens, ttfts, step_ms = 0, 0.0, 0, [], []
+    h2d = d2h = 0
+    for _ in range(args.steps):
+        ts = time.perf_counter()
+        n, ms, st_tok, outs = one_step()
+        step_ms.append((time.perf_counter() - ts) * 1e3)
+        tokens += n
+        dev_ms += ms
+        sched_tokens += st_tok
+        h2d += runner.h2d_bytes
+        d2h += runner.d2h_bytes
+        now = time.perf_counter()
+        for o in outs:
+            if o.request_id in arrivals and o.outputs and o.outputs[0].token_ids:
+                ttfts.append((now - arrivals.pop(o.request_id)) * 1e3)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    wall = time.perf_counter() - t0
+    clocks = sampler.stop()
+    launches = K.launches() + getattr(runner, "graph_launches", 0)
+    status = K.check_status()
+    t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    dev_ms, wall_ms = float(t[0]), float(t[1])
+    if rank == 0:
+        decode_ms = sorted(step_ms)[len(step_ms) // 2]
+        res = {
+            "metric": "output tokens/s (box, max over ranks)", "value": tokens / (dev_ms / 1e3) if dev_ms > 0 else None, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations/KV, int4 AWQ weights (W4A16)",
+            "data": "synthetic: random token ids, random-init weights of the named architecture",
+            "config": {"model": "dense 27B-class AWQ W4A16 (64L, h5120, 40q/8kv x128, ffn 17408, vocab 151936)",
+                       "global_batch": C, "seq_len": IN + OUT, "parallelism": f"tp{args.gpus}", "workload": f"{IN} in / {OUT} out, concurrency {C}, closed loop steady state",
+                       "layers": cfg["num_hidden_layers"], "l2": "inputs larger than L2 (each step streams >10 GB of weights and KV)",
+                       "tp_comm": args.tp_comm if args.gpus > 1 else "none", "cuda_graphs": not args.eager,
+                       "scheduled_tokens_per_step": sched_tokens / args.steps, "output_tokens": tokens},
+            "clocks": clocks,
+            "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
+                    "ms_per_step": wall_ms / args.steps, "p50_tpot_ms": decode_ms,
+                    "p50_ttft_ms": (sorted(ttfts)[len(ttfts) // 2] if ttfts else None)},
+            "gpu_launches": launches, "device_status": status,
+            "torch_standins": sorted(K.TORCH_STANDINS),
+        }
+        if args.layers:
+            res["invalid"] = "reduced layer count (debug run)"
+        print(json.dumps(res))
+    eng.shutdown()
+    if world > 1 and dist.is_initialized():
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

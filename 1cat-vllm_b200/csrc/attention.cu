@@ -48,6 +48,7 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
 
 template <int D, int MODE, int MB>
 __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
+  constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring
   constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
   constexpr int NB2 = (MODE == 0) ? 4 : 1;      // 16-key groups per warp per tile
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
@@ -55,7 +56,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + ROWS * D * 2;
-  uint8_t* sV = sK + 2 * kKeysPerTile * D * 2;
+  uint8_t* sV = sK + STAGES * kKeysPerTile * D * 2;
   __shared__ int s_req, s_tile0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -148,13 +149,16 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   const int key_base = (MODE == 0) ? 0 : warp * 16;
   const int g_ = lane >> 2, tg = lane & 3;
 
-  if (tile_lo < tile_hi) load_tile(tile_lo, 0);
-  cp_async_commit();
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) {
+    if (tile_lo + i < tile_hi) load_tile(tile_lo + i, i);
+    cp_async_commit();
+  }
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
-    const int buf = (tile - tile_lo) & 1;
-    cp_async_wait<0>();
-    __syncthreads();
-    if (tile + 1 < tile_hi) load_tile(tile + 1, buf ^ 1);
+    const int buf = (tile - tile_lo) % STAGES;
+    cp_async_wait<STAGES - 2>();  // the group of this tile has landed (one group is committed per iteration)
+    __syncthreads();               // ...for every thread, and everybody has finished the buffer refilled below
+    if (tile + STAGES - 1 < tile_hi) load_tile(tile + STAGES - 1, (tile - tile_lo + STAGES - 1) % STAGES);
     cp_async_commit();
     const uint32_t kb = smem_u32(sK + (size_t)buf * kKeysPerTile * D * 2);
     const uint32_t vb = smem_u32(sV + (size_t)buf * kKeysPerTile * D * 2);
@@ -358,7 +362,7 @@ __global__ void attn_combine_kernel(const AttnParams p) {
 template <int D, int MODE, int MB>
 int launch_one(const AttnParams& p, cudaStream_t st) {
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
-  const int smem = ROWS * D * 2 + 4 * kKeysPerTile * D * 2;
+  const int smem = ROWS * D * 2 + 2 * 3 * kKeysPerTile * D * 2;
   static int configured = 0;
   if (!configured) {
     if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;

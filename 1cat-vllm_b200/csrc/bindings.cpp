@@ -4,6 +4,7 @@
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
 
+#include "comm.h"
 #include "gemm_sm100.h"
 #include "kernels.h"
 
@@ -234,7 +235,62 @@ torch::Tensor argmax(torch::Tensor x) {
 }
 
 int64_t read_status(bool clear) {
-  return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear));
+  return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) |
+                   oc::comm_read_status(clear));
+}
+
+// ---- symmetric slab + peer-memory reductions
+int64_t comm_alloc(int64_t bytes) {
+  void* p = nullptr;
+  TORCH_CHECK(oc::comm_alloc((size_t)bytes, &p) == 0, "cudaMalloc of the symmetric slab failed");
+  return (int64_t)(uintptr_t)p;
+}
+void comm_free(int64_t ptr) { oc::comm_free((void*)(uintptr_t)ptr); }
+py::bytes comm_export(int64_t ptr) {
+  char h[64];
+  TORCH_CHECK(oc::comm_export((void*)(uintptr_t)ptr, h) == 0, "cudaIpcGetMemHandle failed");
+  return py::bytes(h, 64);
+}
+int64_t comm_import(const std::string& handle) {
+  TORCH_CHECK(handle.size() == 64, "an IPC handle is 64 bytes");
+  void* p = nullptr;
+  TORCH_CHECK(oc::comm_import(handle.data(), &p) == 0, "cudaIpcOpenMemHandle failed (is peer access available?)");
+  return (int64_t)(uintptr_t)p;
+}
+void comm_unimport(int64_t ptr) { oc::comm_unimport((void*)(uintptr_t)ptr); }
+torch::Tensor comm_tensor(int64_t ptr, int64_t byte_offset, std::vector<int64_t> shape, int64_t dtype_code, int64_t device) {
+  auto dt = dtype_code == 0 ? torch::kBFloat16 : dtype_code == 1 ? torch::kInt32 : torch::kUInt8;
+  return torch::from_blob((void*)((uintptr_t)ptr + (uintptr_t)byte_offset), shape, torch::TensorOptions().dtype(dt).device(torch::kCUDA, (int)device));
+}
+
+void tp_reduce_norm(std::vector<int64_t> part, std::vector<int64_t> flags, torch::Tensor seq_local, std::vector<int64_t> x_out,
+                    c10::optional<torch::Tensor> residual_in, c10::optional<torch::Tensor> residual_out, c10::optional<torch::Tensor> w,
+                    int64_t T, int64_t H, int64_t rank, int64_t mode, bool gemma, int64_t phase, double eps, int64_t wait_ns, int64_t grid) {
+  const int tp = (int)part.size();
+  TORCH_CHECK(tp >= 2 && tp <= oc::kMaxRanks && (int)flags.size() == tp && (int)x_out.size() == tp, "bad rank tables");
+  const c10::cuda::CUDAGuard guard(seq_local.device());
+  oc::CommParams p{};
+  for (int i = 0; i < tp; ++i) {
+    p.part[i] = (const __nv_bfloat16*)(uintptr_t)part[i];
+    p.flags[i] = (int*)(uintptr_t)flags[i];
+    p.x_out[i] = (__nv_bfloat16*)(uintptr_t)x_out[i];
+  }
+  p.seq_local = seq_local.data_ptr<int>();
+  p.residual_in = residual_in.has_value() ? (const __nv_bfloat16*)residual_in->data_ptr() : nullptr;
+  p.residual_out = residual_out.has_value() ? (__nv_bfloat16*)residual_out->data_ptr() : nullptr;
+  p.w = w.has_value() ? (const __nv_bfloat16*)w->data_ptr() : nullptr;
+  if (residual_in.has_value()) TORCH_CHECK(residual_in->is_contiguous(), "residual must be contiguous");
+  p.T = (int)T;
+  p.H = (int)H;
+  p.tp = tp;
+  p.rank = (int)rank;
+  p.mode = (int)mode;
+  p.gemma = gemma ? 1 : 0;
+  p.phase = (int)phase;
+  p.eps = (float)eps;
+  p.wait_ns = (unsigned long long)wait_ns;
+  int rc = oc::tp_reduce_norm_launch(p, (int)grid, cur_stream());
+  TORCH_CHECK(rc == 0, "tp_reduce_norm launch failed: ", rc);
 }
 
 }  // namespace
@@ -248,4 +304,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("argmax", &argmax);
   m.def("read_status", &read_status);
+  m.def("comm_alloc", &comm_alloc);
+  m.def("comm_free", &comm_free);
+  m.def("comm_export", &comm_export);
+  m.def("comm_import", &comm_import);
+  m.def("comm_unimport", &comm_unimport);
+  m.def("comm_tensor", &comm_tensor);
+  m.def("tp_reduce_norm", &tp_reduce_norm);
 }

@@ -1,0 +1,206 @@
+// Tensor-parallel reductions over NVLink peer memory, fused with the residual add and RMSNorm that follow them.
+//
+// Every rank owns a slab ("symmetric heap") obtained with cudaMalloc and mapped into all other ranks through CUDA IPC
+// handles, so a kernel can load a peer's partial sums with plain ld.global and store into a peer with st.global; NVSwitch
+// gives each pair full bandwidth. Synchronisation is a flag per (source rank, CTA) written with st.release.sys into the
+// consumer's slab and polled locally with ld.acquire.sys. Flags carry a per-CTA sequence number kept in device memory, so
+// the protocol needs no resets and replays unchanged inside CUDA graphs. All polls are bounded: on expiry the kernel raises
+// the status word, skips its work and returns.
+//   mode ONE_SHOT  (decode-sized T): every rank sums all ranks' partial rows itself  -> replicated residual and output.
+//   mode TWO_SHOT  (prefill-sized T): reduce-scatter + all-gather in one kernel: a rank reduces the rows it owns, normalises
+//                  them and pushes the normalised rows into every peer's gather buffer; the residual stays row-sharded.
+// Sums run in rank order 0..tp-1 on every rank, so all ranks obtain bit-identical results.
+// (reference: csrc/custom_all_reduce.cuh:414 one-stage, :770 two-stage, :436 fused all-reduce + Gemma RMSNorm;
+//  compilation/passes/fusion/allreduce_rms_fusion.py:199)
+#include "comm.h"
+#include "common.cuh"
+
+namespace oc {
+namespace {
+
+__device__ __forceinline__ void st_flag_release(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_flag_acquire(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// waits until *p >= want; false on timeout
+__device__ __forceinline__ bool wait_flag(const int* p, int want, uint64_t limit_ns) {
+  if (ld_flag_acquire(p) - want >= 0) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (ld_flag_acquire(p) - want < 0) {
+    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ float block_sum256(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = (threadIdx.x < 8) ? red[threadIdx.x] : 0.f;
+  if (warp == 0) {
+    t = warp_sum(t);
+    if (lane == 0) red[8] = t;
+  }
+  __syncthreads();
+  return red[8];
+}
+
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p) {
+  __shared__ float red[9];
+  __shared__ int s_seq, s_ok;
+  const int b = blockIdx.x;
+  const int tp = p.tp, me = p.rank;
+  // ---- phase 0: tell every rank that this rank's partial sums are complete (the producing GEMM ran earlier on this stream)
+  if (threadIdx.x == 0) {
+    int seq = p.seq_local[b] + 1;
+    p.seq_local[b] = seq;
+    s_seq = seq;
+    s_ok = 1;
+    __threadfence_system();
+  }
+  __syncthreads();
+  const int seq = s_seq;
+  if (threadIdx.x < tp) st_flag_release(p.flags[threadIdx.x] + (size_t)(p.phase * 2 * tp + me) * kMaxCommBlocks + b, seq);
+  if (threadIdx.x < tp) {
+    if (!wait_flag(p.flags[me] + (size_t)(p.phase * 2 * tp + threadIdx.x) * kMaxCommBlocks + b, seq, p.wait_ns)) {
+      s_ok = 0;
+      atomicOr(&g_status, ST_PEER_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+
+  // ---- phase 1: rows of this CTA
+  int row_lo, row_hi;
+  if (p.mode == COMM_ONE_SHOT) {
+    row_lo = 0;
+    row_hi = p.T;
+  } else {
+    const int per = (p.T + tp - 1) / tp;
+    row_lo = min(me * per, p.T);
+    row_hi = min(row_lo + per, p.T);
+  }
+  if (ok) {
+    for (int t = row_lo + b; t < row_hi; t += gridDim.x) {
+      float v[VEC_ITERS][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC_ITERS; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < p.H) {
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+          for (int r = 0; r < tp; ++r) {
+            const uint4 a = *reinterpret_cast<const uint4*>(p.part[r] + (size_t)t * p.H + c);
+            const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(ap[j]);
+          }
+          if (p.residual_in != nullptr) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual_in + (size_t)t * p.H + c);
+            const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&rr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(rp[j]);
+          }
+          uint4 o;
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            op[j] = __float2bfloat16(acc[j]);
+            v[i][j] = __bfloat162float(op[j]);
+            ss += v[i][j] * v[i][j];
+          }
+          if (p.residual_out != nullptr) *reinterpret_cast<uint4*>(p.residual_out + (size_t)t * p.H + c) = o;
+        }
+      }
+      float inv = 1.f;
+      if (p.w != nullptr) {
+        const float tot = block_sum256(ss, red);
+        inv = rsqrtf(tot / (float)p.H + p.eps);
+      }
+#pragma unroll
+      for (int i = 0; i < VEC_ITERS; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < p.H) {
+          uint4 o;
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+          if (p.w != nullptr) {
+            const uint4 ww = *reinterpret_cast<const uint4*>(p.w + c);
+            const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&ww);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g = __bfloat162float(wp[j]);
+              op[j] = __float2bfloat16(v[i][j] * inv * (p.gemma ? 1.f + g : g));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) op[j] = __float2bfloat16(v[i][j]);
+          }
+          if (p.mode == COMM_ONE_SHOT) {
+            *reinterpret_cast<uint4*>(p.x_out[me] + (size_t)t * p.H + c) = o;
+          } else {
+            for (int r = 0; r < tp; ++r) *reinterpret_cast<uint4*>(p.x_out[(me + r) % tp] + (size_t)t * p.H + c) = o;
+          }
+        }
+      }
+    }
+  }
+  if (p.mode != COMM_TWO_SHOT) return;
+  // ---- phase 2 (two-shot): publish "my rows are in your gather buffer", then wait for everybody's rows
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < tp) st_flag_release(p.flags[threadIdx.x] + (size_t)((p.phase * 2 + 1) * tp + me) * kMaxCommBlocks + b, seq);
+  if (threadIdx.x < tp) {
+    if (!wait_flag(p.flags[me] + (size_t)((p.phase * 2 + 1) * tp + threadIdx.x) * kMaxCommBlocks + b, seq, p.wait_ns))
+      atomicOr(&g_status, ST_PEER_TIMEOUT);
+  }
+}
+
+}  // namespace
+
+int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st) {
+  if (p.H % 8 || p.H > 8192 || grid < 1 || grid > kMaxCommBlocks || p.tp > kMaxRanks) return -1;
+  if (p.T == 0) return 0;
+  const int iters = (p.H + 2047) / 2048;
+  switch (iters) {
+    case 1: tp_reduce_norm_kernel<1><<<grid, 256, 0, st>>>(p); break;
+    case 2: tp_reduce_norm_kernel<2><<<grid, 256, 0, st>>>(p); break;
+    case 3: tp_reduce_norm_kernel<3><<<grid, 256, 0, st>>>(p); break;
+    default: tp_reduce_norm_kernel<4><<<grid, 256, 0, st>>>(p); break;
+  }
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
+// ---- slab management (host) ------------------------------------------------------------------------------------
+int comm_alloc(size_t bytes, void** ptr) {
+  if (cudaMalloc(ptr, bytes) != cudaSuccess) return -1;
+  return cudaMemset(*ptr, 0, bytes) == cudaSuccess ? 0 : -2;
+}
+int comm_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? 0 : -1; }
+int comm_export(void* ptr, void* handle_out64) {
+  cudaIpcMemHandle_t h;
+  if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return -1;
+  static_assert(sizeof(h) == 64, "unexpected IPC handle size");
+  memcpy(handle_out64, &h, 64);
+  return 0;
+}
+int comm_import(const void* handle64, void** ptr) {
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, 64);
+  return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? 0 : -1;
+}
+int comm_unimport(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
+
+unsigned int comm_read_status(bool clear) { return read_status_tu(clear); }
+
+}  // namespace oc

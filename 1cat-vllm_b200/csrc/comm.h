@@ -1,0 +1,35 @@
+// Peer-memory tensor-parallel reductions (see comm.cu).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string.h>
+
+namespace oc {
+
+constexpr int kMaxRanks = 8;
+constexpr int kMaxCommBlocks = 1024;
+enum { COMM_ONE_SHOT = 0, COMM_TWO_SHOT = 1 };
+
+struct CommParams {
+  const __nv_bfloat16* part[kMaxRanks];  // every rank's partial sums [T, H] (peer mappings; own entry is local)
+  int* flags[kMaxRanks];                 // every rank's flag area: [2 phases][2 stages][tp][kMaxCommBlocks]
+  int* seq_local;                        // [kMaxCommBlocks] per-CTA sequence numbers of this rank
+  __nv_bfloat16* x_out[kMaxRanks];       // one-shot: only [rank] used (local output); two-shot: every rank's gather buffer
+  const __nv_bfloat16* residual_in;      // [T, H] or null
+  __nv_bfloat16* residual_out;           // [T, H] or null (two-shot: only owned rows are written)
+  const __nv_bfloat16* w;                // RMSNorm weight or null (plain reduction)
+  int T, H, tp, rank, mode, gemma, phase;
+  float eps;
+  unsigned long long wait_ns;
+};
+
+int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st);
+int comm_alloc(size_t bytes, void** ptr);
+int comm_free(void* ptr);
+int comm_export(void* ptr, void* handle_out64);
+int comm_import(const void* handle64, void** ptr);
+int comm_unimport(void* ptr);
+unsigned int comm_read_status(bool clear);
+
+}  // namespace oc

@@ -83,16 +83,16 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
       mbar_init(&full_x[i], 1);
-      mbar_init(&w_ready[i], 128);
+      mbar_init(&w_ready[i], 4);    // one arrival per dequantisation warp
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < PS; ++i) {
       mbar_init(&pfull[i], 1);
-      mbar_init(&pempty[i], 128);
+      mbar_init(&pempty[i], 4);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 128);
+      mbar_init(&tempty[i], 4);     // one arrival per epilogue warp
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -231,8 +231,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
           }
           fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-          mbar_arrive(&w_ready[s]);
-          mbar_arrive(&pempty[ps]);
+          __syncwarp();
+          if (lane == 0) {           // one arrival per warp: 128 same-address arrivals would serialise
+            mbar_arrive(&w_ready[s]);
+            mbar_arrive(&pempty[ps]);
+          }
         }
       }
     }
@@ -266,7 +269,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             *reinterpret_cast<uint4*>(wsp + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
         }
         tc_fence_before();
-        mbar_arrive(&tempty[acc]);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (et == 0) {
@@ -344,7 +348,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
       }
       tc_fence_before();
-      mbar_arrive(&tempty[acc]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
     }
   }
 

@@ -74,7 +74,8 @@ class VocabParallelEmbedding(nn.Module):
         local = ids.long() - self.lo
         ok = (local >= 0) & (local < self.per)
         out = F.embedding(local.clamp(0, self.per - 1), self.weight) * ok.unsqueeze(-1).to(self.weight.dtype)
-        return ps.all_reduce(out)
+        from onecat_vllm.parallel.tp_ops import reduce_only
+        return reduce_only(out)
 
 
 class ParallelLMHead(VocabParallelEmbedding):

@@ -316,5 +316,10 @@ class RowParallelLinear(LinearBase):
         super().__init__(in_f, [out_f], "row", **kw)
 
     def forward(self, x):
-        y = self.method.apply(self, x)
-        return y
+        if x.is_cuda and self.tp > 1:
+            from onecat_vllm.ops import cuda as K
+            from onecat_vllm.parallel.tp_ops import row_parallel_out
+            out = row_parallel_out(x.shape[0], self.out_features, x.dtype, x.device)
+            if out is not None and not K._LIB_GEMM:
+                return K.linear(self, x, out=out)  # partial sums land in the symmetric slab
+        return self.method.apply(self, x)

@@ -253,6 +253,14 @@ def _sms(device) -> int:
     return _NUM_SMS[k]
 
 
+def choose_kv_splits(base_ctas: int, max_seq: int, num_sms: int) -> int:
+    """KV splits of the decode kernel: enough CTAs for about two full waves (two CTAs fit per SM), but at least four
+    64-key tiles per split so that the copy pipeline fills."""
+    want = -(-(4 * num_sms) // max(base_ctas, 1))
+    by_ctx = max(1, -(-max_seq // 64) // 4)
+    return max(1, min(want, by_ctx, 32))
+
+
 def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, num_sms: int, force_splits: int = 0):
     """Decide which requests take the decode kernel (rows = q_len * group fit in one 16/32-row tile) and how many KV
     splits it uses. Returns (short_q_len, num_q_tiles for the prefill kernel, splits)."""
@@ -265,8 +273,7 @@ def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, 
     splits = 1
     if n_short:
         max_s = max((s for q, s in zip(query_lens, seq_lens) if q <= short), default=1)
-        want = max(1, (2 * num_sms) // max(n_short * Hkv, 1))
-        splits = max(1, min(want, -(-max_s // 256), 32))
+        splits = choose_kv_splits(n_short * Hkv, max_s, num_sms)
     if force_splits:
         splits = force_splits
     return short, tiles, splits

@@ -46,13 +46,12 @@ class DecodeGraphs:
             return None
         rp = self.sizes[bisect.bisect_left(self.sizes, R)]
         a = self.attn_layers[0].self_attn
-        from onecat_vllm.ops.cuda import _sms
-        want = max(1, (2 * _sms(self.r.device)) // max(rp * a.Hkv, 1))
-        by_ctx = max(1, -(-max_seq // 256))
-        s = 1
-        while s * 2 <= min(want, by_ctx, 32):
+        from onecat_vllm.ops.cuda import _sms, choose_kv_splits
+        want = choose_kv_splits(rp * a.Hkv, max_seq, _sms(self.r.device))
+        s = 1  # bucketed to powers of two (rounding up keeps the grid sized for the live context)
+        while s < want:
             s *= 2
-        return rp, q, s
+        return rp, q, min(s, 32)
 
     def _metadata(self, rp: int, q: int, splits: int) -> AttentionMetadata:
         r = self.r

@@ -229,3 +229,26 @@ def test_rms_norm_gated():
     y = K().rms_norm_gated(x, z, w, 1e-6, Hh)
     e = ref.rms_norm_gated(x.cpu().reshape(T * Hh, D), z.cpu().reshape(T * Hh, D), w.cpu(), 1e-6).reshape(T, Hh * D)
     _close(y, e, 2e-2, 2e-2)
+
+
+def test_peer_wait_is_bounded_and_reports_status():
+    """A reduction waits on a peer flag that nothing ever sets: the kernel must give up after its limit, raise the
+    status word and leave the context usable (no trap, no hang)."""
+    from onecat_vllm.ops import _C
+    T, H, tp = 4, 512, 2
+    part = [torch.randn(T, H, device="cuda").bfloat16() for _ in range(tp)]
+    flags = [torch.zeros(2 * 2 * tp * 1024, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    seq = torch.zeros(1024, dtype=torch.int32, device="cuda")
+    x = torch.zeros(T, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    K().check_status()
+    _C.tp_reduce_norm([t.data_ptr() for t in part], [f.data_ptr() for f in flags], seq, [x.data_ptr(), 0], None, None, w, T, H, 0, 0, False, 0,
+                      1e-6, 2_000_000, T)  # 2 ms limit; the flag of "rank 1" is never written
+    torch.cuda.synchronize()
+    assert K().check_status() & 2, "the expired wait must be reported"
+    assert K().check_status() == 0, "status is cleared after reading"
+    assert float(x.abs().sum()) == 0.0, "no output may be produced after a failed wait"
+    # the context still works
+    y, _ = K().rms_norm(part[0], w, 1e-6, None, False)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all()

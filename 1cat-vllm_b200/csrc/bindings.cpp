@@ -69,14 +69,10 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
   }
   oc::gemm_plan(p, sm_count(), w4.has_value());
   if (force_tn > 0) {
+    TORCH_CHECK(!w4.has_value() || force_tn <= 192, "4-bit weights support token tiles up to 192");
     p.tn = (int)force_tn;
     p.num_t_tiles = (p.T + p.tn - 1) / p.tn;
-    oc::GemmParams q = p;
-    // re-derive pipeline depths for the forced tile
-    int per_stage = p.tn * 128 + 16384;
-    int s = (220 * 1024 - p.pstages * 4096 - 2048) / per_stage;
-    p.stages = s > 8 ? 8 : (s < 2 ? 2 : s);
-    (void)q;
+    oc::gemm_plan_stages(p, w4.has_value());
   }
   if (force_splits > 0) {
     int ktiles = p.K / 64;

@@ -28,11 +28,14 @@ __device__ __forceinline__ int ld_flag_acquire(const int* p) {
 }
 // waits until *p >= want; false on timeout
 __device__ __forceinline__ bool wait_flag(const int* p, int want, uint64_t limit_ns) {
-  if (ld_flag_acquire(p) - want >= 0) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;
   uint32_t spins = 0;
   while (ld_flag_acquire(p) - want < 0) {
-    if ((++spins & 63u) == 0 && globaltimer_ns() - t0 > limit_ns) return false;
+    if ((++spins & 255u) == 0) {  // the clock is slow to read: look at it once per 256 polls
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
+    }
   }
   return true;
 }

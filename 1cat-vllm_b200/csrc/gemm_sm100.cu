@@ -21,25 +21,37 @@ namespace oc {
 
 namespace {
 
-constexpr int kThreads = 352;
+// warp roles: 0 X producer, 1 MMA, then the dequantisation warps (4-bit weights: two groups of four that take alternate k tiles,
+// so one group's shared-memory and TMEM latencies hide behind the other's arithmetic), four epilogue warps, and for 4-bit
+// weights one more warp that streams packed tiles.
+template <int WKIND> struct Roles {
+  static constexpr int kDqWarps = WKIND == 1 ? 8 : 0;
+  static constexpr int kEpi0 = 2 + kDqWarps;          // first epilogue warp (2 or 10: both are 2 mod 4, the quarters line up)
+  static constexpr int kPacked = kEpi0 + 4;           // packed-tile producer (4-bit only)
+  static constexpr int kThreads = (kEpi0 + 4 + (WKIND == 1 ? 1 : 0)) * 32;
+};
 constexpr int BM = 128;  // weight rows (output features) per tile = UMMA M
 constexpr int BK = 64;   // k per stage: one 128-byte swizzle atom of bf16
 constexpr int kWStageBytes = BM * BK * 2;   // 16 KB
 constexpr int kPackedBytes = BM * BK / 2;   // 4 KB of nibbles
+constexpr int kSzBytes = BM * 4;            // one (scale, zero) word per weight row
+constexpr int kPackedSlot = kPackedBytes + kSzBytes;  // ring slot: nibbles followed by that k tile's scales/zeros
 constexpr int kTmemCols = 512;
+constexpr int kAStages = 4;                   // TMEM ring of dequantised weight tiles (32 columns each)
+constexpr int kAColBase = kTmemCols - kAStages * 32;  // accumulators use columns [0, 2*tn), tn <= 192 for 4-bit weights
 
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
 };
-__host__ __device__ inline SmemLayout make_layout(int tn, int stages, int pstages) {
+__host__ __device__ inline SmemLayout make_layout(int tn, int xstages, int stages, int pstages) {
   SmemLayout L;
   uint32_t o = 0;
   L.x_off = o;
-  o += (uint32_t)stages * tn * 128;
+  o += (uint32_t)xstages * tn * 128;
   L.w_off = o;
-  o += (uint32_t)stages * kWStageBytes;
+  o += (pstages > 0 ? 0u : (uint32_t)stages * kWStageBytes);  // 4-bit weights are dequantised into TMEM, not shared memory
   L.p_off = o;
-  o += (uint32_t)pstages * kPackedBytes;
+  o += (uint32_t)pstages * kPackedSlot;
   L.bar_off = o;
   o += 1024;
   L.total = o;
@@ -55,24 +67,28 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t w, uint32_t zb2, uint32_t s
 }
 
 template <int WKIND>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(Roles<WKIND>::kThreads, 1)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes the swizzle needs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const SmemLayout L = make_layout(p.tn, p.stages, p.pstages);
+  const SmemLayout L = make_layout(p.tn, p.xstages, p.stages, p.pstages);
   uint8_t* sx = smem + L.x_off;
   uint8_t* sw = smem + L.w_off;
   uint8_t* sp = smem + L.p_off;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
-  const int S = p.stages, PS = p.pstages;
-  uint64_t* full_x = bars;              // [S]  TMA landed (X, and W for bf16 weights)
-  uint64_t* w_ready = bars + S;         // [S]  dequantised W tile written
-  uint64_t* empty = bars + 2 * S;       // [S]  MMA finished reading the stage
-  uint64_t* pfull = bars + 3 * S;       // [PS] packed tile landed
-  uint64_t* pempty = bars + 3 * S + PS; // [PS] packed tile consumed
-  uint64_t* tfull = bars + 3 * S + 2 * PS;  // [2] accumulator complete
-  uint64_t* tempty = tfull + 2;             // [2] accumulator drained
+  // X tiles and W tiles live in separate rings: for 4-bit weights the X ring is deep (it hides the L2 latency of the TMA
+  // loads) while the 16 KB dequantised-W ring only has to cover dequantise -> MMA -> commit. For bf16 weights both
+  // operands arrive by TMA on the same barrier and the rings advance together (XS == S).
+  const int S = p.stages, PS = p.pstages, XS = p.xstages;
+  uint64_t* full_x = bars;                      // [XS] TMA landed (X, and W for bf16 weights)
+  uint64_t* empty_x = full_x + XS;              // [XS] MMA finished reading the X stage
+  uint64_t* w_ready = empty_x + XS;             // [S]  dequantised W tile written
+  uint64_t* empty_w = w_ready + S;              // [S]  MMA finished reading the W stage
+  uint64_t* pfull = empty_w + S;                // [PS] packed tile landed
+  uint64_t* pempty = pfull + PS;                // [PS] packed tile consumed
+  uint64_t* tfull = pempty + PS;                // [2] accumulator complete
+  uint64_t* tempty = tfull + 2;                 // [2] accumulator drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* red_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
@@ -81,10 +97,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int tn = p.tn;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < S; ++i) {
+    for (int i = 0; i < XS; ++i) {
       mbar_init(&full_x[i], 1);
+      mbar_init(&empty_x[i], 1);
+    }
+    for (int i = 0; i < S; ++i) {
       mbar_init(&w_ready[i], 4);    // one arrival per dequantisation warp
-      mbar_init(&empty[i], 1);
+      mbar_init(&empty_w[i], 1);
     }
     for (int i = 0; i < PS; ++i) {
       mbar_init(&pfull[i], 1);
@@ -124,44 +143,57 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
-      uint32_t it = 0;
+      Ring st;
       bool ok = true;
+      const uint32_t bytes = (uint32_t)tn * 128 + (WKIND == 0 ? kWStageBytes : 0);
+      const uint32_t xs = (uint32_t)tn * 128;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
-          int s = it % S;
-          ok = mbar_wait(&empty[s], ((it / S) & 1) ^ 1, abort_flag);
+        for (int kt = k0; kt < k1; ++kt) {
+          ok = mbar_wait(&empty_x[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
-          uint32_t bytes = (uint32_t)tn * 128 + (WKIND == 0 ? kWStageBytes : 0);
-          mbar_expect_tx(&full_x[s], bytes);
-          tma_load_2d(sx + (size_t)s * tn * 128, &tmX, kt * BK, tt * tn, &full_x[s]);
-          if (WKIND == 0) tma_load_2d(sw + (size_t)s * kWStageBytes, &tmW, kt * BK, nt * BM, &full_x[s]);
+          mbar_expect_tx(&full_x[st.idx], bytes);
+          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, tt * tn, &full_x[st.idx]);
+          if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full_x[st.idx]);
+          st.advance(XS);
         }
       }
     }
-  } else if (warp == 10) {
+  } else if (warp == Roles<WKIND>::kPacked) {
     // ------------------------------------------------------------------ packed-weight producer (runs PS tiles ahead)
     if (WKIND == 1 && lane == 0) {
-      uint32_t pit = 0;
+      Ring pr;
       bool ok = true;
+      const int gk = p.group_ktiles;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        for (int kt = k0; kt < k1 && ok; ++kt, ++pit) {
-          int ps = pit % PS;
-          ok = mbar_wait(&pempty[ps], ((pit / PS) & 1) ^ 1, abort_flag);
+        const uint8_t* wsrc = p.w4 + ((size_t)nt * ktiles + k0) * kPackedBytes;
+        const uint32_t* zsrc = p.w4_sz + (size_t)nt * BM;
+        int g = k0 / gk, gi = k0 - g * gk;  // quantisation group of the k tile and position inside it
+        for (int kt = k0; kt < k1; ++kt) {
+          ok = mbar_wait(&pempty[pr.idx], pr.phase ^ 1, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(&pfull[ps], kPackedBytes);
-          bulk_load(sp + ps * kPackedBytes, p.w4 + ((size_t)nt * ktiles + kt) * kPackedBytes, kPackedBytes, &pfull[ps]);
+          uint8_t* dst = sp + pr.idx * kPackedSlot;
+          mbar_expect_tx(&pfull[pr.idx], kPackedSlot);
+          bulk_load(dst, wsrc, kPackedBytes, &pfull[pr.idx]);
+          // the group's scales/zeros ride along, so the dequantisation warps never touch global memory
+          bulk_load(dst + kPackedBytes, zsrc + (size_t)g * p.n_pad, kSzBytes, &pfull[pr.idx]);
+          wsrc += kPackedBytes;
+          if (++gi == gk) { gi = 0; ++g; }
+          pr.advance(PS);
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issue
     const uint32_t idesc = umma_idesc_bf16(BM, tn);
-    uint32_t it = 0, tile_i = 0;
+    uint32_t tile_i = 0;
+    Ring st, xr;
     bool ok = true;
+    const uint32_t xs = (uint32_t)tn * 128;
+    const uint32_t a_base = smem_u32(sw), b_base = smem_u32(sx);
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
       int nt, tt, sp_, k0, k1;
       decode(w, nt, tt, sp_, k0, k1);
@@ -169,73 +201,86 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       ok = mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_addr = tmem_base + acc * 256;
-      for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
-        int s = it % S;
-        uint32_t ph = (it / S) & 1;
-        ok = mbar_wait(&full_x[s], ph, abort_flag);
-        if (ok && WKIND == 1) ok = mbar_wait(&w_ready[s], ph, abort_flag);
+      const uint32_t d_addr = tmem_base + acc * p.acc_stride;
+      for (int kt = k0; kt < k1; ++kt) {
+        const int s = st.idx, x = xr.idx;
+        ok = mbar_wait(&full_x[x], xr.phase, abort_flag);
+        if (ok && WKIND == 1) ok = mbar_wait(&w_ready[s], st.phase, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          uint32_t a0 = smem_u32(sw + (size_t)s * kWStageBytes);
-          uint32_t b0 = smem_u32(sx + (size_t)s * tn * 128);
+          const uint64_t db = umma_desc_sw128(b_base + x * xs);
+          if (WKIND == 1) {
+            const uint32_t ta = tmem_base + kAColBase + s * 32;  // 64 k of bf16 = 32 columns per stage
 #pragma unroll
-          for (int j = 0; j < BK / 16; ++j) {
-            umma_bf16(d_addr, umma_desc_sw128(a0 + j * 32), umma_desc_sw128(b0 + j * 32), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < BK / 16; ++j)
+              umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+          } else {
+            const uint64_t da = umma_desc_sw128(a_base + s * kWStageBytes);
+#pragma unroll
+            for (int j = 0; j < BK / 16; ++j) {
+              // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
+              umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+            }
           }
-          umma_commit(&empty[s]);  // frees the stage once these MMAs have read it
+          umma_commit(&empty_x[x]);  // frees the stages once these MMAs have read them
+          if (WKIND == 1) umma_commit(&empty_w[s]);
         }
         __syncwarp();
+        st.advance(S);
+        xr.advance(XS);
       }
       if (ok && lane == 0) umma_commit(&tfull[acc]);
       __syncwarp();
     }
-  } else if (warp < 6) {
+  } else if (warp < Roles<WKIND>::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
     if (WKIND == 1) {
-      const int r = threadIdx.x - 64;  // weight row inside the tile
-      uint32_t it = 0;
+      const int r = (warp & 3) * 32 + lane;  // weight row = TMEM lane this warp may write
+      const int grp = (warp - 2) >> 2;       // 0: even k tiles of the CTA's sequence, 1: odd ones
+      uint32_t seq = 0;
+      Ring st, pr;
       bool ok = true;
-      const int gshift = p.group_ktiles;  // k tiles per quantisation group
+      const uint32_t sp_u32 = smem_u32(sp);
+      const uint32_t ta_row = tmem_base + kAColBase + ((uint32_t)((warp & 3) * 32) << 16);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        const uint32_t* szp = p.w4_sz + (size_t)nt * BM + r;
-        int cur_g = -1;
-        uint32_t s2 = 0, zb2 = 0;
-        for (int kt = k0; kt < k1 && ok; ++kt, ++it) {
-          int g = kt / gshift;
-          if (g != cur_g) {
-            cur_g = g;
-            uint32_t v = __ldg(szp + (size_t)g * p.n_pad);
-            s2 = (v & 0xffffu) | (v << 16);
-            zb2 = (v >> 16) | (v & 0xffff0000u);
+        for (int kt = k0; kt < k1; ++kt) {
+          if ((int)(seq++ & 1u) != grp) {  // the other group's tile: just keep the ring cursors in step
+            st.advance(S);
+            pr.advance(PS);
+            continue;
           }
-          int ps = it % PS, s = it % S;
-          ok = mbar_wait(&pfull[ps], (it / PS) & 1, abort_flag);
-          if (ok) ok = mbar_wait(&empty[s], ((it / S) & 1) ^ 1, abort_flag);
+          ok = mbar_wait(&pfull[pr.idx], pr.phase, abort_flag);
+          if (ok) ok = mbar_wait(&empty_w[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
-          const uint4* src = reinterpret_cast<const uint4*>(sp + ps * kPackedBytes);
-          uint4 h0 = src[r], h1 = src[128 + r];
-          uint32_t words[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
-          uint8_t* dst = sw + (size_t)s * kWStageBytes + r * 128;
+          tc_fence_after();
+          const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
+          const uint4 h0 = lds128(slot + r * 16), h1 = lds128(slot + 2048 + r * 16);
+          const uint32_t szv = lds32(slot + kPackedBytes + r * 4);
+          const uint32_t s2 = (szv & 0xffffu) | (szv << 16);
+          const uint32_t zb2 = (szv >> 16) | (szv & 0xffff0000u);
+          const uint32_t words[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+          uint32_t o[32];  // 64 bf16 of this row: column c holds k = 2c (low half) and 2c+1 (high half)
 #pragma unroll
           for (int c = 0; c < 8; ++c) {
-            uint32_t q = words[c];
-            uint4 o;
-            o.x = dq_pair(q, zb2, s2);
-            o.y = dq_pair(q >> 4, zb2, s2);
-            o.z = dq_pair(q >> 8, zb2, s2);
-            o.w = dq_pair(q >> 12, zb2, s2);
-            *reinterpret_cast<uint4*>(dst + ((c ^ (r & 7)) << 4)) = o;
+            const uint32_t q = words[c];
+            o[4 * c] = dq_pair(q, zb2, s2);
+            o[4 * c + 1] = dq_pair(q >> 4, zb2, s2);
+            o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
+            o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
           }
-          fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+          tmem_st_32x32(ta_row + st.idx * 32, o);
+          tmem_st_wait();
+          tc_fence_before();
           __syncwarp();
           if (lane == 0) {           // one arrival per warp: 128 same-address arrivals would serialise
-            mbar_arrive(&w_ready[s]);
-            mbar_arrive(&pempty[ps]);
+            mbar_arrive(&w_ready[st.idx]);
+            mbar_arrive(&pempty[pr.idx]);
           }
+          st.advance(S);
+          pr.advance(PS);
         }
       }
     }
@@ -243,7 +288,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;       // weight row inside the tile
-    const int et = threadIdx.x - 192;    // 0..127
+    const int et = threadIdx.x - Roles<WKIND>::kEpi0 * 32;    // 0..127
     uint32_t tile_i = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
@@ -253,7 +298,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       ok = mbar_wait(&tfull[acc], (tile_i >> 1) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * 256 + ((uint32_t)(q * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * p.acc_stride + ((uint32_t)(q * 32) << 16);
       const int n = nt * BM + row;
       const int t0 = tt * tn;
       const int tile_id = nt * p.num_t_tiles + tt;
@@ -399,13 +444,13 @@ int make_tmap_bf16(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t co
 
 }  // namespace
 
-int gemm_smem_bytes(int tn, int stages, int pstages) { return (int)make_layout(tn, stages, pstages).total + 1024; }
+int gemm_smem_bytes(int tn, int xstages, int stages, int pstages) { return (int)make_layout(tn, xstages, stages, pstages).total + 1024; }
 
 // Picks the token tile, split-K factor and pipeline depths. Split-K spreads few-tile problems (decode) over all SMs.
 void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   int T = p.T;
-  int tn = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : 256;
-  if (T > 256) {
+  int tn = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : (w4 ? 192 : 256);  // 4-bit: TMEM also holds the weight ring
+  if (T > 256 && !w4) {
     // avoid a nearly empty last token tile when 128 divides the token count better
     int waste256 = ((T + 255) / 256) * 256 - T, waste128 = ((T + 127) / 128) * 128 - T;
     if (waste128 + 64 < waste256 && T < 1024) tn = 128;
@@ -432,12 +477,25 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   }
   p.splits = best;
   p.ktiles_per_split = (ktiles + best - 1) / best;
-  // pipeline depth from the shared-memory budget (227 KB per CTA)
-  int budget = 220 * 1024;
-  p.pstages = w4 ? (tn <= 64 ? 12 : 6) : 0;
-  int per_stage = tn * 128 + kWStageBytes;
-  int s = (budget - p.pstages * kPackedBytes - 2048) / per_stage;
-  p.stages = s > 8 ? 8 : (s < 2 ? 2 : s);
+  gemm_plan_stages(p, w4);
+}
+
+// Pipeline depths from the shared-memory budget (227 KB per CTA) for the chosen token tile.
+void gemm_plan_stages(GemmParams& p, bool w4) {
+  const int budget = 222 * 1024;
+  const int tn = p.tn;
+  if (!w4) {
+    p.pstages = 0;
+    int s = (budget - 2048) / (tn * 128 + kWStageBytes);
+    p.stages = p.xstages = s > 8 ? 8 : (s < 2 ? 2 : s);
+    p.acc_stride = 256;
+    return;
+  }
+  p.stages = kAStages;
+  p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
+  int xs = (budget - 2048 - p.pstages * kPackedSlot) / (tn * 128);
+  p.xstages = xs > 16 ? 16 : (xs < 2 ? 2 : xs);
+  p.acc_stride = 192;
 }
 
 int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream) {
@@ -452,20 +510,20 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   }
   int total = p.num_n_tiles * p.num_t_tiles * p.splits;
   int grid = total < num_sms ? total : num_sms;
-  int smem = gemm_smem_bytes(p.tn, p.stages, p.pstages);
+  int smem = gemm_smem_bytes(p.tn, p.xstages, p.stages, p.pstages);
   static int configured[2] = {0, 0};
   if (w4) {
     if (configured[1] < smem) {
       if (cudaFuncSetAttribute(gemm_wx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
       configured[1] = 227 * 1024;
     }
-    gemm_wx_kernel<1><<<grid, kThreads, smem, stream>>>(tmX, tmW, p);
+    gemm_wx_kernel<1><<<grid, Roles<1>::kThreads, smem, stream>>>(tmX, tmW, p);
   } else {
     if (configured[0] < smem) {
       if (cudaFuncSetAttribute(gemm_wx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
       configured[0] = 227 * 1024;
     }
-    gemm_wx_kernel<0><<<grid, kThreads, smem, stream>>>(tmX, tmW, p);
+    gemm_wx_kernel<0><<<grid, Roles<0>::kThreads, smem, stream>>>(tmX, tmW, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

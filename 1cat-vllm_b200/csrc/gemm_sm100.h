@@ -13,7 +13,9 @@ struct GemmParams {
   int n_rows;         // weight rows the kernel walks (N, or 2*n_out for the interleaved gate|up layout)
   int n_out;          // output columns for EPI_SILU_MUL
   int n_pad;          // padded weight rows (stride of the scale/zero table)
-  int tn, num_t_tiles, num_n_tiles, splits, ktiles_per_split, stages, pstages;
+  int tn, num_t_tiles, num_n_tiles, splits, ktiles_per_split;
+  int acc_stride;               // TMEM columns between the two accumulators
+  int xstages, stages, pstages;  // ring depths: X tiles, W tiles (bf16 weights: same ring as X), packed 4-bit tiles
   int epi;
   int group_ktiles;   // 64-wide k tiles per quantisation group (group 128 -> 2)
   __nv_bfloat16* out;
@@ -28,7 +30,8 @@ struct GemmParams {
 };
 
 void gemm_plan(GemmParams& p, int num_sms, bool w4);
-int gemm_smem_bytes(int tn, int stages, int pstages);
+void gemm_plan_stages(GemmParams& p, bool w4);
+int gemm_smem_bytes(int tn, int xstages, int stages, int pstages);
 int gemm_launch(const GemmParams& p, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream);
 unsigned int gemm_read_status(bool clear);
 

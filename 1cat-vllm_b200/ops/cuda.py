@@ -39,7 +39,7 @@ class _Workspace:
     def __init__(self, device):
         self.device = device
         self.splitk = torch.empty(64 << 20, dtype=torch.uint8, device=device)
-        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)
+        self.counters = torch.zeros(8192, dtype=torch.int32, device=device)  # upper half: scratch
         self.attn_o = None
         self.attn_ml = None
 

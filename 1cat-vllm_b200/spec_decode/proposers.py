@@ -1,0 +1,116 @@
+"""Draft-token proposers for speculative decoding (reference: vllm/v1/spec_decode/llm_base_proposer.py:167,977,1427
+MTP/EAGLE multi-step drafting; ngram_proposer.py prompt lookup; metadata.py:10).
+
+``propose`` runs after the target step and returns, per request of the batch, the draft tokens to verify in the next
+step (empty for requests still in prefill). The MTP proposer first re-runs the draft layer over this step's positions
+with the token ids shifted by one and the target's hidden states (so its own KV cache stays in sync), then drafts
+``k-1`` more tokens one position at a time."""
+from __future__ import annotations
+
+from typing import Optional
+
+import numpy as np
+import torch
+
+from onecat_vllm.worker.attn_metadata import AttentionMetadata
+
+
+class NgramProposer:
+    """Prompt lookup: find the longest recent n-gram (``min_n..max_n``) earlier in the context and propose what
+    followed it."""
+
+    def __init__(self, k: int, min_n: int, max_n: int):
+        self.k, self.min_n, self.max_n = k, min_n, max_n
+
+    def propose_one(self, tokens: list) -> list:
+        n_tok = len(tokens)
+        for n in range(min(self.max_n, n_tok - 1), self.min_n - 1, -1):
+            pat = tokens[n_tok - n:]
+            for start in range(n_tok - n - 1, -1, -1):
+                if tokens[start:start + n] == pat:
+                    follow = tokens[start + n:start + n + self.k]
+                    if follow:
+                        return list(follow)
+        return []
+
+    def propose(self, runner, so, req_ids, rows, sampled, hidden, md, drafts_of):
+        out = []
+        for rid, s in zip(req_ids, sampled):
+            st = runner.requests[rid]
+            out.append(self.propose_one(st.token_ids) if s else [])
+        return out
+
+
+class MTPProposer:
+    def __init__(self, runner):
+        self.k = runner.num_spec
+
+    @torch.inference_mode()
+    def propose(self, runner, so, req_ids, rows, sampled, hidden, md, drafts_of):
+        mtp, dev, bs = runner.mtp, runner.device, runner.block_size
+        R, T = md.num_reqs, md.num_tokens
+        qsl = md.query_start_loc.tolist() if md.query_lens_cpu is None else np.concatenate([[0], np.cumsum(md.query_lens_cpu)]).tolist()
+        # ---- pass 1: shifted ids over this step's positions
+        ids = runner._view("ids", T).clone()
+        shifted = torch.zeros_like(ids)
+        shifted[:-1] = ids[1:]
+        last_valid = []  # flat index of the last position whose next token is known
+        nxt = []
+        for r, rid in enumerate(req_ids):
+            st = runner.requests[rid]
+            a, b = qsl[r], qsl[r + 1]
+            if not sampled[r]:
+                # prefill chunk: the next token of the last position is the next prompt token
+                pos_end = st.num_computed_tokens + (b - a)
+                shifted[b - 1] = st.token_ids[pos_end] if pos_end < len(st.token_ids) else 0
+                last_valid.append(-1)
+                nxt.append(0)
+                continue
+            n_acc = len(sampled[r])  # accepted drafts + 1 (recovered or bonus)
+            idx = a + (b - a) - (len(drafts_of[r]) + 1) + (n_acc - 1)
+            shifted[idx] = sampled[r][-1]
+            last_valid.append(idx)
+            nxt.append(sampled[r][-1])
+        h1 = mtp(shifted, hidden, md, runner.mtp_cache)
+        active = [r for r in range(R) if last_valid[r] >= 0]
+        out: list = [[] for _ in range(R)]
+        if not active:
+            return out
+        sel = torch.tensor([last_valid[r] for r in active], device=dev)
+        hcur = h1[sel]
+        tok = mtp.compute_logits(hcur).argmax(-1)
+        drafts = [tok]
+        # ---- passes 2..k: one token per request at the following positions (lookahead slots were reserved)
+        pos0 = np.array([runner.requests[req_ids[r]].num_computed_tokens + (qsl[r + 1] - qsl[r]) - (len(drafts_of[r]) + 1) + len(sampled[r])
+                         for r in active], dtype=np.int32)
+        A = len(active)
+        bt = torch.zeros(A, runner.max_blocks_per_req, dtype=torch.int32, device=dev)
+        for i, r in enumerate(active):
+            b_ids = runner.requests[req_ids[r]].block_ids
+            bt[i, : len(b_ids)] = torch.tensor(b_ids, dtype=torch.int32)
+        for step in range(1, self.k):
+            pos = pos0 + (step - 1)
+            ok = pos < runner.max_model_len - 1
+            slots = np.full(A, -1, dtype=np.int32)
+            for i, r in enumerate(active):
+                b_ids = runner.requests[req_ids[r]].block_ids
+                if ok[i] and pos[i] // bs < len(b_ids):
+                    slots[i] = b_ids[pos[i] // bs] * bs + pos[i] % bs
+            md1 = AttentionMetadata(A, A, torch.arange(A + 1, dtype=torch.int32, device=dev), torch.tensor(pos + 1, dtype=torch.int32, device=dev), bt,
+                                    torch.tensor(slots, dtype=torch.int32, device=dev), torch.tensor(pos, dtype=torch.int32, device=dev), 1,
+                                    int(pos.max()) + 1, query_lens_cpu=[1] * A, seq_lens_cpu=(pos + 1).tolist())
+            hcur = mtp(drafts[-1].to(torch.int32), hcur, md1, runner.mtp_cache)
+            drafts.append(mtp.compute_logits(hcur).argmax(-1))
+        d = torch.stack(drafts, dim=1).tolist()
+        for i, r in enumerate(active):
+            out[r] = d[i]
+        return out
+
+
+def make_proposer(runner):
+    sc = runner.spec
+    if sc.method == "ngram":
+        return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
+    if sc.method == "mtp":
+        return MTPProposer(runner)
+    raise ValueError(f"unknown speculative method {sc.method!r}")

@@ -116,21 +116,30 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     *reinterpret_cast<uint4*>(sQ + sw_off<D>(row, ch)) = v;
   }
 
+  // each thread always copies the same 16-byte column chunk of rows (tid / CH) + i * (128 / CH); pages are a power of
+  // two tokens long, so the block-table lookup is a shift and a mask
+  const int ld_ch = threadIdx.x % CH, ld_row0 = threadIdx.x / CH;
+  constexpr int kRowStep = 128 / CH;
+  const int bs_shift = p.bs_shift, bs_mask = p.bs - 1;
+  const __nv_bfloat16* kv_head = p.kv_cache + (size_t)hkv * page_elems + ld_ch * 8;
+  const size_t blk_stride = (size_t)2 * p.Hkv * page_elems, v_off = (size_t)p.Hkv * page_elems;
   auto load_tile = [&](int tile, int buf) {
     const int k0 = tile * kKeysPerTile;
     uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * 2;
     uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * 2;
-    for (int idx = threadIdx.x; idx < kKeysPerTile * CH; idx += 128) {
-      int row = idx / CH, ch = idx % CH;
-      int key = k0 + row;
+#pragma unroll
+    for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
+      const int row = ld_row0 + i * kRowStep;
+      const int key = k0 + row;
+      const uint32_t off = sw_off<D>(row, ld_ch);
       if (key < kv_end) {
-        int blk = bt[key / p.bs];
-        size_t base = (((size_t)blk * 2) * p.Hkv + hkv) * page_elems + (size_t)(key % p.bs) * D + ch * 8;
-        cp_async16(dk + sw_off<D>(row, ch), p.kv_cache + base);
-        cp_async16(dv + sw_off<D>(row, ch), p.kv_cache + base + (size_t)p.Hkv * page_elems);
+        const int blk = bt[key >> bs_shift];
+        const __nv_bfloat16* src = kv_head + (size_t)blk * blk_stride + (size_t)(key & bs_mask) * D;
+        cp_async16(dk + off, src);
+        cp_async16(dv + off, src + v_off);
       } else {
-        *reinterpret_cast<uint4*>(dk + sw_off<D>(row, ch)) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + sw_off<D>(row, ch)) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dk + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + off) = make_uint4(0, 0, 0, 0);
       }
     }
   };
@@ -381,7 +390,7 @@ int launch_one(const AttnParams& p, cudaStream_t st) {
 }  // namespace
 
 int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
-  if (p.Hq % p.Hkv || p.bs % 16 || (p.D != 128 && p.D != 256)) return -1;
+  if (p.Hq % p.Hkv || p.bs < 16 || (p.bs & (p.bs - 1)) || (p.D != 128 && p.D != 256)) return -1;
   const int G = p.Hq / p.Hkv;
   if (G > 64) return -1;
   if (mode == 1) {

@@ -203,6 +203,8 @@ void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out,
   p.Hkv = (int)kv_cache.size(2);
   p.D = (int)q.size(2);
   p.bs = (int)kv_cache.size(3);
+  p.bs_shift = 0;
+  while ((1 << p.bs_shift) < p.bs) ++p.bs_shift;
   p.scale = (float)scale;
   p.num_q_tiles = (int)num_q_tiles;
   p.splits = (int)splits;

@@ -37,7 +37,7 @@ struct AttnParams {
   const int* seq_lens;        // [R]
   const int* block_table;     // [R][bt_stride]
   int bt_stride;
-  int R, T, Hq, Hkv, D, bs;
+  int R, T, Hq, Hkv, D, bs, bs_shift;  // bs: tokens per page (power of two, >= 16)
   float scale;
   int num_q_tiles;            // grid.x for prefill mode (host: sum over requests of ceil(q_len / tokens per tile))
   int splits;                 // decode mode: KV splits per (request, kv head)

@@ -268,6 +268,8 @@ def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, 
     max_rows = 32 if D == 128 else 16
     short = max_rows // G
     n_short = sum(1 for q in query_lens if 0 < q <= short)
+    if n_short:  # the row tile of the decode kernel follows the longest short query actually present (q=1 -> 16 rows)
+        short = max(q for q in query_lens if 0 < q <= short)
     TQ = 64 // G
     tiles = sum(-(-q // TQ) for q in query_lens if q > short)
     splits = 1

@@ -62,8 +62,8 @@ class DecodeGraphs:
                                uniform_query_len=q)
         G = a.Hq // a.Hkv
         short = (32 if a.D == 128 else 16) // G
-        md.attn_plan = ((a.Hq, a.Hkv, a.D), (max(short, q) if q * G <= (32 if a.D == 128 else 16) else short,
-                                             0 if q <= short else rp * (-(-q // (64 // G))), splits))
+        # uniform batch: every request has q tokens; they take the decode kernel when q*G rows fit its tile
+        md.attn_plan = ((a.Hq, a.Hkv, a.D), (q if q <= short else short, 0 if q <= short else rp * (-(-q // (64 // G))), splits))
         md.static_ws = True
         return md
 

@@ -1,0 +1,317 @@
+"""Engine core in its own process behind ZMQ, and the clients that talk to it
+(reference: vllm/v1/engine/core.py:1018 ``EngineCoreProc``, :1134-1273 handshake, :1376 busy loop, :1491 utility calls,
+:1569-1581 ``ENGINE_CORE_DEAD``; clients vllm/v1/engine/core_client.py:461 ``MPClient``, :748 sync, :919 asyncio).
+
+Sockets: the client binds a ROUTER for inputs and a PULL for outputs; the engine connects a DEALER (identity = engine index)
+and a PUSH. First input frame = 1-byte request type (ADD / ABORT / UTILITY), the rest is the msgpack body (+ buffers).
+Handshake: engine → ``HELLO``; client → config acknowledgement; engine → ``READY`` with ``num_gpu_blocks``/``max_model_len``.
+If the core dies it sends ``ENGINE_CORE_DEAD`` (when it still can) and the client raises ``EngineDeadError``; a monitor thread
+also watches the process sentinel."""
+from __future__ import annotations
+
+import multiprocessing as mp
+import os
+import pickle
+import queue
+import signal
+import threading
+import time
+import traceback
+from typing import Any, Optional
+
+import zmq
+import zmq.asyncio
+
+from onecat_vllm import envs
+from onecat_vllm.config import VllmConfig
+from onecat_vllm.engine import serial
+from onecat_vllm.engine.core import EngineDeadError
+from onecat_vllm.logger import decorate_logs, init_logger
+from onecat_vllm.request import EngineCoreOutput, EngineCoreOutputs, EngineCoreRequest
+
+log = init_logger(__name__)
+ENGINE_CORE_DEAD = b"ENGINE_CORE_DEAD"
+
+
+def _ipc_path(tag: str) -> str:
+    import tempfile
+    import uuid
+    return f"ipc://{tempfile.gettempdir()}/onecat-{tag}-{uuid.uuid4().hex[:12]}"
+
+
+# ----------------------------------------------------------------------------- engine side
+def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_index: int, log_stats: bool, death_conn) -> None:
+    decorate_logs(f"EngineCore_{engine_index}")
+    signal.signal(signal.SIGINT, signal.SIG_IGN)
+    if death_conn is not None:
+        def watch():
+            try:
+                death_conn.recv()
+            except EOFError:
+                pass
+            os._exit(1)
+        threading.Thread(target=watch, daemon=True).start()
+    ctx = zmq.Context()
+    inp = ctx.socket(zmq.DEALER)
+    inp.setsockopt(zmq.IDENTITY, engine_index.to_bytes(2, "little"))
+    inp.connect(input_addr)
+    out = ctx.socket(zmq.PUSH)
+    out.connect(output_addr)
+    core = None
+    try:
+        inp.send_multipart(serial.encode({"status": "HELLO", "local": True, "headless": False}))
+        if not inp.poll(envs.ONECAT_HANDSHAKE_TIMEOUT_SECONDS * 1000):
+            raise TimeoutError("no handshake reply from the frontend")
+        serial.decode(inp.recv_multipart())
+        from onecat_vllm.engine.core import EngineCore
+        core = EngineCore(cfg, log_stats=log_stats)
+        inp.send_multipart(serial.encode({"status": "READY", "num_gpu_blocks": cfg.cache_config.num_gpu_blocks,
+                                          "max_model_len": cfg.model_config.max_model_len, "dtype": str(cfg.model_config.dtype)}))
+        _busy_loop(core, inp, out, engine_index)
+    except Exception:
+        log.error("engine core failed:\n" + traceback.format_exc())
+        try:
+            out.send_multipart([ENGINE_CORE_DEAD], flags=zmq.NOBLOCK)
+        except Exception:
+            pass
+    finally:
+        if core is not None:
+            core.shutdown()
+        inp.close(linger=200)
+        out.close(linger=200)
+        ctx.term()
+
+
+def _busy_loop(core, inp, out, engine_index: int) -> None:
+    """Drain inputs, step while there is work, block on the socket when idle (reference: core.py:1376-1440)."""
+    while True:
+        timeout = 0 if core.scheduler.has_requests() else 200
+        while inp.poll(timeout):
+            frames = inp.recv_multipart()
+            kind, body = frames[0], frames[1:]
+            if kind == serial.REQ_ADD:
+                try:
+                    core.add_request(EngineCoreRequest.from_wire(serial.decode(body)))
+                except Exception as e:  # bad request: report as an aborted output instead of killing the engine
+                    d = serial.decode(body)
+                    o = EngineCoreOutputs([EngineCoreOutput(d.get("request_id", "?"), [], finish_reason=3, stop_reason=repr(e))])
+                    out.send_multipart(serial.encode(_outs_wire(o, engine_index)))
+            elif kind == serial.REQ_ABORT:
+                core.abort_requests(serial.decode(body))
+            elif kind == serial.REQ_UTILITY:
+                call_id, method, args = serial.decode(body)
+                if method == "shutdown":
+                    return
+                try:
+                    res = getattr(core, method)(*args)
+                    try:
+                        serial.encode(res)
+                    except TypeError:
+                        res = repr(res)
+                    reply = {"call_id": call_id, "result": res}
+                except Exception as e:
+                    reply = {"call_id": call_id, "error": f"{e!r}"}
+                out.send_multipart(serial.encode({"utility_output": reply, "engine_index": engine_index}))
+            timeout = 0
+        if core.scheduler.has_requests():
+            outs, _ = core.step()
+            for client, o in outs.items():
+                out.send_multipart(serial.encode(_outs_wire(o, engine_index)))
+
+
+def _outs_wire(o: EngineCoreOutputs, engine_index: int) -> dict:
+    st = o.scheduler_stats
+    return {"engine_index": engine_index, "outputs": [x.to_wire() for x in o.outputs], "timestamp": o.timestamp,
+            "scheduler_stats": dict(st.__dict__) if st is not None else None}
+
+
+# ----------------------------------------------------------------------------- client side
+class _MPClientBase:
+    def __init__(self, cfg: VllmConfig, log_stats: bool, asyncio_mode: bool):
+        self.cfg = cfg
+        self.sync_ctx = zmq.Context()
+        self.input_addr, self.output_addr = _ipc_path("in"), _ipc_path("out")
+        hs = self.sync_ctx.socket(zmq.ROUTER)
+        hs.bind(self.input_addr)
+        pull = self.sync_ctx.socket(zmq.PULL)
+        pull.bind(self.output_addr)
+        mctx = mp.get_context("spawn")
+        d_r, self._death_w = mctx.Pipe(duplex=False)
+        self.proc = mctx.Process(target=run_engine_core, args=(cfg, self.input_addr, self.output_addr, 0, log_stats, d_r), daemon=True,
+                                 name="onecat-engine-core")
+        self.proc.start()
+        d_r.close()
+        self.engine_id = (0).to_bytes(2, "little")
+        self.dead = False
+        try:
+            self._handshake(hs)
+        except Exception:
+            self._kill()
+            raise
+        if asyncio_mode:
+            # same underlying sockets, awaitable API: the engine's connections (and the ROUTER's routing table) survive
+            self.inp, self.outp = zmq.asyncio.Socket.shadow(hs), zmq.asyncio.Socket.shadow(pull)
+            self._keep = (hs, pull)
+        else:
+            self.inp, self.outp = hs, pull
+        self._call_id = 0
+        self._mon = threading.Thread(target=self._monitor, daemon=True)
+        self._mon.start()
+
+    def _handshake(self, hs) -> None:
+        deadline = time.time() + envs.ONECAT_HANDSHAKE_TIMEOUT_SECONDS * 5
+        stage = 0
+        while stage < 2:
+            if not hs.poll(200):
+                if not self.proc.is_alive():
+                    raise RuntimeError(f"engine core exited during start-up (code {self.proc.exitcode})")
+                if time.time() > deadline:
+                    raise TimeoutError("engine core handshake timed out")
+                continue
+            ident, *frames = hs.recv_multipart()
+            msg = serial.decode(frames)
+            if msg["status"] == "HELLO":
+                hs.send_multipart([ident] + serial.encode({"ack": True}))
+                stage = 1
+            elif msg["status"] == "READY":
+                self.cfg.cache_config.num_gpu_blocks = msg["num_gpu_blocks"]
+                stage = 2
+
+    def _monitor(self) -> None:
+        self.proc.join()
+        if not getattr(self, "_closing", False):
+            self.dead = True
+
+    def _check(self) -> None:
+        if self.dead:
+            raise EngineDeadError("the engine core process died")
+
+    def _kill(self) -> None:
+        self._closing = True
+        if self.proc.is_alive():
+            self.proc.terminate()  # exact child we started
+            self.proc.join(5)
+
+    @staticmethod
+    def _parse(frames) -> EngineCoreOutputs:
+        if frames[0] == ENGINE_CORE_DEAD:
+            raise EngineDeadError("the engine core reported a fatal error")
+        d = serial.decode(frames)
+        if "utility_output" in d:
+            return EngineCoreOutputs(utility_output=d["utility_output"])
+        from onecat_vllm.core.scheduler import SchedulerStats
+        st = SchedulerStats(**d["scheduler_stats"]) if d.get("scheduler_stats") else None
+        return EngineCoreOutputs([EngineCoreOutput.from_wire(x) for x in d["outputs"]], st, d.get("timestamp", 0.0), d.get("engine_index", 0))
+
+
+class SyncMPClient(_MPClientBase):
+    def __init__(self, cfg: VllmConfig, log_stats: bool = False):
+        super().__init__(cfg, log_stats, asyncio_mode=False)
+        self._util: dict = {}
+
+    def add_request(self, req: EngineCoreRequest) -> None:
+        self._check()
+        self.inp.send_multipart([self.engine_id, serial.REQ_ADD] + serial.encode(req.to_wire()))
+
+    def abort_requests(self, ids: list) -> None:
+        if ids and not self.dead:
+            self.inp.send_multipart([self.engine_id, serial.REQ_ABORT] + serial.encode(list(ids)))
+
+    def get_output(self, timeout_s: float = 300.0) -> EngineCoreOutputs:
+        deadline = time.time() + timeout_s
+        while True:
+            self._check()
+            if self.outp.poll(100):
+                o = self._parse(self.outp.recv_multipart())
+                if o.utility_output is not None:
+                    self._util[o.utility_output["call_id"]] = o.utility_output
+                    continue
+                return o
+            if time.time() > deadline:
+                raise TimeoutError("no output from the engine core")
+
+    def call_utility(self, method: str, *args):
+        self._check()
+        self._call_id += 1
+        cid = self._call_id
+        self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
+        deadline = time.time() + envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS
+        while cid not in self._util:
+            self._check()
+            if self.outp.poll(100):
+                o = self._parse(self.outp.recv_multipart())
+                if o.utility_output is not None:
+                    self._util[o.utility_output["call_id"]] = o.utility_output
+            if time.time() > deadline:
+                raise TimeoutError(f"utility call {method} timed out")
+        r = self._util.pop(cid)
+        if "error" in r:
+            raise RuntimeError(r["error"])
+        return r["result"]
+
+    def shutdown(self) -> None:
+        self._closing = True
+        try:
+            if not self.dead and self.proc.is_alive():
+                self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([0, "shutdown", []]))
+                self.proc.join(10)
+        except Exception:
+            pass
+        self._kill()
+        for s in (getattr(self, "inp", None), getattr(self, "outp", None)):
+            if s is not None:
+                s.close(linger=0)
+        try:
+            self._death_w.close()
+        except Exception:
+            pass
+
+
+class AsyncMPClient(_MPClientBase):
+    def __init__(self, cfg: VllmConfig, log_stats: bool = False):
+        super().__init__(cfg, log_stats, asyncio_mode=True)
+        self._util_futs: dict = {}
+
+    async def add_request_async(self, req: EngineCoreRequest) -> None:
+        self._check()
+        await self.inp.send_multipart([self.engine_id, serial.REQ_ADD] + serial.encode(req.to_wire()))
+
+    async def abort_requests_async(self, ids: list) -> None:
+        if ids and not self.dead:
+            await self.inp.send_multipart([self.engine_id, serial.REQ_ABORT] + serial.encode(list(ids)))
+
+    async def get_output_async(self) -> EngineCoreOutputs:
+        while True:
+            self._check()
+            if await self.outp.poll(200):
+                o = self._parse(await self.outp.recv_multipart())
+                if o.utility_output is not None:
+                    fut = self._util_futs.pop(o.utility_output["call_id"], None)
+                    if fut is not None and not fut.done():
+                        fut.set_result(o.utility_output)
+                    continue
+                return o
+
+    async def call_utility_async(self, method: str, *args):
+        import asyncio
+        self._check()
+        self._call_id += 1
+        cid = self._call_id
+        fut = asyncio.get_running_loop().create_future()
+        self._util_futs[cid] = fut
+        await self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
+        r = await asyncio.wait_for(fut, envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS)
+        if "error" in r:
+            raise RuntimeError(r["error"])
+        return r["result"]
+
+    def shutdown(self) -> None:
+        self._closing = True
+        self._kill()
+        for s in (getattr(self, "inp", None), getattr(self, "outp", None)):
+            if s is not None:
+                s.close(linger=0)
+        try:
+            self._death_w.close()
+        except Exception:
+            pass

@@ -1,0 +1,394 @@
+"""OpenAI-compatible HTTP server (reference: vllm/entrypoints/openai/api_server.py:157 ``build_app``, :665 ``run_server``;
+chat logic openai/chat_completion/serving.py; launcher + watchdog entrypoints/launcher.py:26,144).
+
+Routes: ``/v1/chat/completions``, ``/v1/completions``, ``/v1/models``, ``/tokenize``, ``/detokenize``, ``/health``, ``/ping``,
+``/version``, ``/metrics`` (Prometheus), ``/load``, ``/server_info``, ``/reset_prefix_cache``, ``/sleep``, ``/wake_up``,
+``/is_sleeping``, ``/start_profile``, ``/stop_profile``, ``/collective_rpc``. Streaming uses server-sent events."""
+from __future__ import annotations
+
+import argparse
+import asyncio
+import json
+import os
+import signal
+from typing import AsyncGenerator, Optional
+
+from fastapi import FastAPI, Request
+from fastapi.responses import JSONResponse, Response, StreamingResponse
+
+import onecat_vllm
+from onecat_vllm import envs
+from onecat_vllm.config import EngineArgs
+from onecat_vllm.engine.async_llm import AsyncLLM
+from onecat_vllm.engine.core import EngineDeadError
+from onecat_vllm.entrypoints.openai.protocol import (ChatCompletionRequest, CompletionRequest, DetokenizeRequest, TokenizeRequest,
+                                                      error_body, new_id, now)
+from onecat_vllm.entrypoints.parsers import get_reasoning_parser, get_tool_parser
+from onecat_vllm.logger import init_logger
+
+log = init_logger(__name__)
+
+
+class ServingState:
+    def __init__(self, engine: AsyncLLM, model_name: str, tool_parser: Optional[str], reasoning_parser: Optional[str], api_key: Optional[str]):
+        self.engine, self.model_name = engine, model_name
+        self.tool_parser_name, self.reasoning_parser_name = tool_parser, reasoning_parser
+        get_tool_parser(tool_parser), get_reasoning_parser(reasoning_parser)  # validate early
+        self.api_key = api_key
+        self.sleeping = False
+        self.inflight = 0
+
+    @property
+    def max_model_len(self) -> int:
+        return self.engine.cfg.model_config.max_model_len
+
+
+def _sse(obj) -> str:
+    return "data: " + (obj if isinstance(obj, str) else json.dumps(obj, ensure_ascii=False)) + "\n\n"
+
+
+def _usage(n_prompt: int, n_out: int, cached: int = 0) -> dict:
+    u = {"prompt_tokens": n_prompt, "completion_tokens": n_out, "total_tokens": n_prompt + n_out}
+    if cached:
+        u["prompt_tokens_details"] = {"cached_tokens": cached}
+    return u
+
+
+def _lp_chat(tok, logprobs, k: int) -> dict:
+    content = []
+    for d in logprobs or []:
+        items = list(d.items())
+        (tid, first) = items[0]
+        tops = [{"token": v.decoded_token or str(t), "logprob": v.logprob, "bytes": list((v.decoded_token or "").encode())} for t, v in items[1:k + 1]]
+        content.append({"token": first.decoded_token or str(tid), "logprob": first.logprob, "bytes": list((first.decoded_token or "").encode()),
+                        "top_logprobs": tops})
+    return {"content": content}
+
+
+def build_app(state: ServingState) -> FastAPI:
+    app = FastAPI(title="onecat-vllm", version=onecat_vllm.__version__)
+    app.state.serving = state
+
+    @app.middleware("http")
+    async def auth_and_load(request: Request, call_next):
+        if state.api_key and request.url.path.startswith("/v1"):
+            if request.headers.get("authorization") != f"Bearer {state.api_key}":
+                return JSONResponse(error_body("invalid API key", "AuthenticationError", 401), status_code=401)
+        state.inflight += 1
+        try:
+            return await call_next(request)
+        finally:
+            state.inflight -= 1
+
+    @app.exception_handler(EngineDeadError)
+    async def dead(_, exc):
+        return JSONResponse(error_body(f"engine is dead: {exc}", "InternalServerError", 500), status_code=500)
+
+    # ---- basic routes
+    @app.get("/health")
+    @app.get("/ping")
+    async def health():
+        try:
+            await state.engine.check_health()
+        except EngineDeadError:
+            return Response(status_code=503)
+        return Response(status_code=200)
+
+    @app.get("/version")
+    async def version():
+        return {"version": onecat_vllm.__version__}
+
+    @app.get("/v1/models")
+    async def models():
+        return {"object": "list", "data": [{"id": state.model_name, "object": "model", "created": now(), "owned_by": "onecat-vllm",
+                                            "max_model_len": state.max_model_len}]}
+
+    @app.get("/metrics")
+    async def metrics():
+        import prometheus_client as pc
+        return Response(pc.generate_latest(), media_type=pc.CONTENT_TYPE_LATEST)
+
+    @app.get("/load")
+    async def load():
+        return {"server_load": state.inflight}
+
+    @app.get("/server_info")
+    async def server_info():
+        c = state.engine.cfg
+        return {"model": c.model_config.model, "architecture": c.model_config.architecture, "max_model_len": c.model_config.max_model_len,
+                "tensor_parallel_size": c.parallel_config.tensor_parallel_size, "num_gpu_blocks": c.cache_config.num_gpu_blocks,
+                "block_size": c.cache_config.block_size, "quantization": c.model_config.quant.method}
+
+    @app.post("/tokenize")
+    async def tokenize(req: TokenizeRequest):
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("the server has no tokenizer"), status_code=400)
+        if req.messages is not None:
+            text = tok.apply_chat_template([m.model_dump(exclude_none=True) for m in req.messages], tokenize=False, add_generation_prompt=True)
+        else:
+            text = req.prompt or ""
+        ids = list(tok.encode(text, add_special_tokens=req.add_special_tokens))
+        return {"tokens": ids, "count": len(ids), "max_model_len": state.max_model_len}
+
+    @app.post("/detokenize")
+    async def detokenize(req: DetokenizeRequest):
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("the server has no tokenizer"), status_code=400)
+        return {"prompt": tok.decode(req.tokens)}
+
+    # ---- control routes
+    @app.post("/reset_prefix_cache")
+    async def reset_prefix_cache():
+        ok = await state.engine.reset_prefix_cache()
+        return Response(status_code=200 if ok else 409)
+
+    @app.post("/sleep")
+    async def sleep(level: int = 1):
+        await state.engine.sleep(level)
+        state.sleeping = True
+        return Response(status_code=200)
+
+    @app.post("/wake_up")
+    async def wake_up():
+        await state.engine.wake_up()
+        state.sleeping = False
+        return Response(status_code=200)
+
+    @app.get("/is_sleeping")
+    async def is_sleeping():
+        return {"is_sleeping": state.sleeping}
+
+    @app.post("/start_profile")
+    async def start_profile():
+        await state.engine.profile(True)
+        return Response(status_code=200)
+
+    @app.post("/stop_profile")
+    async def stop_profile():
+        await state.engine.profile(False)
+        return Response(status_code=200)
+
+    @app.post("/collective_rpc")
+    async def collective_rpc(body: dict):
+        res = await state.engine.collective_rpc(body["method"], body.get("args", []), body.get("kwargs"))
+        return {"results": res}
+
+    # ---- completions
+    @app.post("/v1/completions")
+    async def completions(req: CompletionRequest, raw: Request):
+        prompts = req.prompt
+        if isinstance(prompts, str) or (prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        rid = new_id("cmpl")
+        try:
+            sp = req.to_sampling_params(state.max_model_len, logprobs=req.logprobs)
+            gens = []
+            for i, p in enumerate(prompts):
+                sp_i = sp.clone()
+                gens.append(state.engine.generate(p, sp_i, f"{rid}-{i}", priority=req.priority))
+        except ValueError as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        model = req.model or state.model_name
+
+        if req.stream:
+            async def stream() -> AsyncGenerator[str, None]:
+                n_prompt = n_out = 0
+                try:
+                    for i, g in enumerate(gens):
+                        async for out in g:
+                            n_prompt = len(out.prompt_token_ids)
+                            for c in out.outputs:
+                                n_out += len(c.token_ids)
+                                yield _sse({"id": rid, "object": "text_completion", "created": now(), "model": model,
+                                            "choices": [{"index": i * req.n + c.index, "text": c.text, "logprobs": None,
+                                                         "finish_reason": c.finish_reason, "stop_reason": c.stop_reason}]})
+                    if req.stream_options and req.stream_options.get("include_usage"):
+                        yield _sse({"id": rid, "object": "text_completion", "created": now(), "model": model, "choices": [],
+                                    "usage": _usage(n_prompt, n_out)})
+                    yield _sse("[DONE]")
+                except EngineDeadError as e:
+                    yield _sse(error_body(str(e), "InternalServerError", 500))
+            return StreamingResponse(stream(), media_type="text/event-stream")
+
+        choices, n_prompt, n_out = [], 0, 0
+        try:
+            for i, g in enumerate(gens):
+                final = None
+                async for out in g:
+                    final = out
+                    if await raw.is_disconnected():
+                        await state.engine.abort(f"{rid}-{i}")
+                        return Response(status_code=499)
+                n_prompt += len(final.prompt_token_ids)
+                for c in final.outputs:
+                    n_out += len(c.token_ids)
+                    text = ((final.prompt or "") + c.text) if req.echo else c.text
+                    lp = None
+                    if req.logprobs is not None and c.logprobs:
+                        lp = {"tokens": [next(iter(d.values())).decoded_token for d in c.logprobs],
+                              "token_logprobs": [next(iter(d.values())).logprob for d in c.logprobs],
+                              "top_logprobs": [{(v.decoded_token or str(t)): v.logprob for t, v in d.items()} for d in c.logprobs]}
+                    choices.append({"index": i * req.n + c.index, "text": text, "logprobs": lp, "finish_reason": c.finish_reason,
+                                    "stop_reason": c.stop_reason, "token_ids": c.token_ids if state.engine.tokenizer is None else None})
+        except ValueError as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        return {"id": rid, "object": "text_completion", "created": now(), "model": model, "choices": choices, "usage": _usage(n_prompt, n_out)}
+
+    # ---- chat completions
+    @app.post("/v1/chat/completions")
+    async def chat(req: ChatCompletionRequest, raw: Request):
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("chat completions need a tokenizer with a chat template"), status_code=400)
+        msgs = [m.model_dump(exclude_none=True) for m in req.messages]
+        kw = dict(req.chat_template_kwargs or {})
+        if req.tools and req.tool_choice != "none":
+            kw["tools"] = req.tools
+        try:
+            prompt = tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=req.add_generation_prompt, **kw)
+        except Exception as e:
+            return JSONResponse(error_body(f"chat template failed: {e}"), status_code=400)
+        if req.max_completion_tokens is not None and req.max_tokens is None:
+            req.max_tokens = req.max_completion_tokens
+        k = (req.top_logprobs or 0) if req.logprobs else None
+        rid = new_id("chatcmpl")
+        try:
+            sp = req.to_sampling_params(state.max_model_len, logprobs=k)
+            gen = state.engine.generate(prompt, sp, rid, priority=req.priority)
+        except ValueError as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        model = req.model or state.model_name
+        rp = get_reasoning_parser(state.reasoning_parser_name)
+        tp = get_tool_parser(state.tool_parser_name) if (req.tools and req.tool_choice != "none") else None
+
+        if req.stream:
+            async def stream() -> AsyncGenerator[str, None]:
+                def chunk(index, delta, finish=None):
+                    return _sse({"id": rid, "object": "chat.completion.chunk", "created": now(), "model": model,
+                                 "choices": [{"index": index, "delta": delta, "logprobs": None, "finish_reason": finish}]})
+                acc: dict = {}
+                sent: dict = {}
+                n_prompt = n_out = 0
+                try:
+                    for i in range(req.n):
+                        yield chunk(i, {"role": "assistant", "content": ""})
+                    async for out in gen:
+                        n_prompt = len(out.prompt_token_ids)
+                        for c in out.outputs:
+                            n_out += len(c.token_ids)
+                            prev = acc.get(c.index, "")
+                            cur = prev + c.text
+                            acc[c.index] = cur
+                            delta: dict = {}
+                            if rp is not None:
+                                r_d, c_d = rp.stream(prev, cur)
+                                visible_prev, visible_cur = rp._split_partial(prev)[1], rp._split_partial(cur)[1]
+                            else:
+                                r_d, visible_prev, visible_cur = "", prev, cur
+                            if r_d:
+                                delta["reasoning_content"] = r_d
+                            if tp is not None:
+                                shown = tp.content_so_far(visible_cur)
+                                already = sent.get(c.index, 0)
+                                if len(shown) > already:
+                                    delta["content"] = shown[already:]
+                                    sent[c.index] = len(shown)
+                            else:
+                                if len(visible_cur) > len(visible_prev):
+                                    delta["content"] = visible_cur[len(visible_prev):]
+                            finish = c.finish_reason
+                            if finish is not None and tp is not None:
+                                _, calls = tp.extract(rp.extract(cur)[1] or "" if rp else cur)
+                                if calls:
+                                    delta["tool_calls"] = [tc.to_openai(j) for j, tc in enumerate(calls)]
+                                    finish = "tool_calls"
+                            if delta or finish is not None:
+                                yield chunk(c.index, delta, finish)
+                    if req.stream_options and req.stream_options.get("include_usage"):
+                        yield _sse({"id": rid, "object": "chat.completion.chunk", "created": now(), "model": model, "choices": [],
+                                    "usage": _usage(n_prompt, n_out)})
+                    yield _sse("[DONE]")
+                except EngineDeadError as e:
+                    yield _sse(error_body(str(e), "InternalServerError", 500))
+            return StreamingResponse(stream(), media_type="text/event-stream")
+
+        final = None
+        outs_by_index: dict = {}
+        async for out in gen:
+            final = out
+            for c in out.outputs:
+                outs_by_index[c.index] = c
+        choices, n_out = [], 0
+        for idx in sorted(outs_by_index):
+            c = outs_by_index[idx]
+            n_out += len(c.token_ids)
+            reasoning, content = (rp.extract(c.text) if rp is not None else (None, c.text))
+            msg: dict = {"role": "assistant", "content": content}
+            finish = c.finish_reason
+            if reasoning is not None:
+                msg["reasoning_content"] = reasoning
+            if tp is not None and content:
+                content2, calls = tp.extract(content)
+                if calls:
+                    msg["content"], msg["tool_calls"], finish = content2, [tc.to_openai() for tc in calls], "tool_calls"
+            choices.append({"index": idx, "message": msg, "logprobs": _lp_chat(tok, c.logprobs, k or 0) if req.logprobs else None,
+                            "finish_reason": finish, "stop_reason": c.stop_reason})
+        return {"id": rid, "object": "chat.completion", "created": now(), "model": model, "choices": choices,
+                "usage": _usage(len(final.prompt_token_ids), n_out, final.num_cached_tokens)}
+
+    return app
+
+
+async def _watchdog(state: ServingState, server) -> None:
+    """Stop serving when the engine has died (reference: launcher.py:144-166)."""
+    while True:
+        await asyncio.sleep(2.0)
+        if not state.engine.is_running:
+            log.error("engine died: shutting the server down")
+            server.should_exit = True
+            return
+
+
+def make_arg_parser() -> argparse.ArgumentParser:
+    p = argparse.ArgumentParser("onecat-vllm serve")
+    p.add_argument("model_tag", nargs="?", default=None)
+    p.add_argument("--host", default="127.0.0.1")
+    p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--served-model-name", default=None)
+    p.add_argument("--api-key", default=envs.ONECAT_API_KEY)
+    p.add_argument("--tool-call-parser", default=None)
+    p.add_argument("--reasoning-parser", default=None)
+    p.add_argument("--enable-auto-tool-choice", action="store_true")
+    EngineArgs.add_cli_args(p)
+    return p
+
+
+def run_server(args: argparse.Namespace) -> None:
+    import uvicorn
+    if args.model_tag:
+        args.model = args.model_tag
+    ea = EngineArgs.from_cli_args(args)
+    ea.disable_log_stats = False
+    if ea.tokenizer is None and os.path.isdir(ea.model):
+        ea.tokenizer = ea.model
+    engine = AsyncLLM.from_engine_args(ea)
+    state = ServingState(engine, args.served_model_name or ea.model, args.tool_call_parser, args.reasoning_parser, args.api_key)
+    app = build_app(state)
+    config = uvicorn.Config(app, host=args.host, port=args.port, log_level="warning")
+    server = uvicorn.Server(config)
+
+    async def main():
+        wd = asyncio.create_task(_watchdog(state, server))
+        try:
+            await server.serve()
+        finally:
+            wd.cancel()
+            engine.shutdown()
+
+    asyncio.run(main())
+
+
+if __name__ == "__main__":
+    run_server(make_arg_parser().parse_args())

@@ -1,0 +1,85 @@
+"""OpenAI-compatible server on CPU with the byte tokenizer: routes, streaming, stop strings, tool/reasoning parsers, metrics."""
+import json
+
+import pytest
+
+from onecat_vllm.entrypoints.parsers import DeepSeekV3ToolParser, HermesToolParser, Qwen3CoderToolParser, ReasoningParser
+
+CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+           num_key_value_heads=2, head_dim=16, vocab_size=258, max_position_embeddings=512, eos_token_id=257)
+
+
+def test_reasoning_parser_full_and_streaming():
+    rp = ReasoningParser()
+    assert rp.extract("<think>plan</think>answer") == ("plan", "answer")
+    assert rp.extract("no tags") == (None, "no tags")
+    assert ReasoningParser(True).extract("still thinking") == ("still thinking", None)
+    text = "<think>abc</think>xyz"
+    r = c = ""
+    for i in range(1, len(text) + 1):
+        dr, dc = rp.stream(text[: i - 1], text[:i])
+        r, c = r + dr, c + dc
+    assert (r, c) == ("abc", "xyz")
+
+
+def test_tool_parsers():
+    t = 'I will call.<tool_call>\n{"name": "get_weather", "arguments": {"city": "Paris"}}\n</tool_call>'
+    content, calls = HermesToolParser().extract(t)
+    assert content == "I will call." and calls[0].name == "get_weather" and json.loads(calls[0].arguments) == {"city": "Paris"}
+    assert HermesToolParser().content_so_far("hello <tool_c") == "hello "
+    q = "<tool_call>\n<function=add>\n<parameter=a>\n1\n</parameter>\n<parameter=b>\ntwo\n</parameter>\n</function>\n</tool_call>"
+    content, calls = Qwen3CoderToolParser().extract(q)
+    assert content is None and calls[0].name == "add" and json.loads(calls[0].arguments) == {"a": 1, "b": "two"}
+    d = '<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>function<｜tool▁sep｜>f\n```json\n{"x": 1}\n```<｜tool▁call▁end｜><｜tool▁calls▁end｜>'
+    _, calls = DeepSeekV3ToolParser().extract(d)
+    assert calls[0].name == "f" and json.loads(calls[0].arguments) == {"x": 1}
+    assert HermesToolParser().extract("plain")[1] == []
+
+
+@pytest.fixture(scope="module")
+def client():
+    from fastapi.testclient import TestClient
+    from onecat_vllm.config import EngineArgs
+    from onecat_vllm.engine.async_llm import AsyncLLM
+    from onecat_vllm.entrypoints.openai.api_server import ServingState, build_app
+    eng = AsyncLLM.from_engine_args(EngineArgs(hf_config=CFG, device="cpu", dtype="float32", max_model_len=256, tokenizer="byte", disable_log_stats=False))
+    app = build_app(ServingState(eng, "tiny", "hermes", "qwen3", None))
+    with TestClient(app) as c:
+        yield c
+    eng.shutdown()
+
+
+@pytest.mark.timeout(300)
+def test_server_routes(client):
+    assert client.get("/health").status_code == 200
+    assert client.get("/v1/models").json()["data"][0]["id"] == "tiny"
+    assert client.get("/version").json()["version"]
+    tk = client.post("/tokenize", json={"prompt": "hi"}).json()
+    assert tk["count"] == 3 and client.post("/detokenize", json={"tokens": tk["tokens"]}).json()["prompt"] == "hi"
+    r = client.post("/v1/completions", json={"prompt": "hello", "max_tokens": 5, "temperature": 0, "ignore_eos": True}).json()
+    assert r["usage"]["completion_tokens"] == 5 and r["choices"][0]["finish_reason"] == "length"
+    r2 = client.post("/v1/completions", json={"prompt": [72, 105], "max_tokens": 4, "temperature": 0, "ignore_eos": True, "n": 1, "logprobs": 2}).json()
+    assert len(r2["choices"][0]["logprobs"]["token_logprobs"]) == 4
+    bad = client.post("/v1/completions", json={"prompt": "x", "max_tokens": 0})
+    assert bad.status_code == 400 and "error" in bad.json()
+    c = client.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hey"}], "max_tokens": 6, "temperature": 0, "ignore_eos": True}).json()
+    assert c["choices"][0]["message"]["role"] == "assistant" and c["usage"]["completion_tokens"] == 6
+    assert client.post("/reset_prefix_cache").status_code in (200, 409)
+    m = client.get("/metrics").text
+    assert "vllm:generation_tokens_total" in m and "vllm:time_to_first_token_seconds" in m
+    assert client.get("/server_info").json()["block_size"] == 16
+
+
+@pytest.mark.timeout(300)
+def test_server_streaming(client):
+    with client.stream("POST", "/v1/completions", json={"prompt": "abc", "max_tokens": 6, "temperature": 0, "ignore_eos": True, "stream": True,
+                                                        "stream_options": {"include_usage": True}}) as resp:
+        lines = [l for l in resp.iter_lines() if l.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    usage = json.loads(lines[-2][6:])["usage"]
+    assert usage["completion_tokens"] == 6
+    with client.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "user", "content": "q"}], "max_tokens": 5, "temperature": 0,
+                                                             "ignore_eos": True, "stream": True}) as resp:
+        chunks = [json.loads(l[6:]) for l in resp.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
+    assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
+    assert chunks[-1]["choices"][0]["finish_reason"] == "length"

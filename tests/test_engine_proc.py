@@ -1,0 +1,74 @@
+"""Engine core in its own process: wire codec round trip, sync client through LLMEngine, asyncio streaming, death detection."""
+import asyncio
+
+import pytest
+import torch
+
+from onecat_vllm.config import EngineArgs
+from onecat_vllm.engine import serial
+from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
+
+CFG = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+           num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+
+
+def test_serial_roundtrip_with_oob_buffers():
+    big = torch.arange(1000, dtype=torch.float32).reshape(10, 100)
+    msg = {"a": [1, 2, {"t": big, "s": torch.tensor([1, 2], dtype=torch.int32)}], "b": torch.ones(300, dtype=torch.bfloat16), "c": {3, 1}}
+    frames = serial.encode(msg)
+    assert len(frames) == 3  # body + two out-of-band buffers (the small tensor is inline)
+    back = serial.decode([bytes(f) for f in frames])
+    assert torch.equal(back["a"][2]["t"], big) and back["a"][2]["s"].tolist() == [1, 2]
+    assert back["b"].dtype == torch.bfloat16 and float(back["b"].float().sum()) == 300.0 and back["c"] == {1, 3}
+
+
+@pytest.mark.timeout(180)
+def test_sync_mp_client_matches_inproc():
+    from onecat_vllm.engine.llm_engine import LLMEngine
+    args = EngineArgs(hf_config=CFG, device="cpu", dtype="float32", max_model_len=128)
+    prompts = [[5, 6, 7, 8, 9], list(range(20, 60))]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, output_kind=RequestOutputKind.FINAL_ONLY)
+    res = {}
+    for mp_mode in (False, True):
+        eng = LLMEngine(args.create_engine_config(), multiprocess=mp_mode)
+        for i, p in enumerate(prompts):
+            eng.add_request(str(i), p, sp)
+        outs = {}
+        while eng.has_unfinished_requests():
+            for o in eng.step():
+                if o.finished:
+                    outs[o.request_id] = o.outputs[0].token_ids
+        if mp_mode:
+            assert eng.reset_prefix_cache() in (True, False)
+        eng.shutdown()
+        res[mp_mode] = outs
+    assert res[False] == res[True] and len(res[True]) == 2
+
+
+@pytest.mark.timeout(180)
+def test_async_llm_streams_and_detects_death():
+    from onecat_vllm.engine.async_llm import AsyncLLM
+    from onecat_vllm.engine.core import EngineDeadError
+    args = EngineArgs(hf_config=CFG, device="cpu", dtype="float32", max_model_len=128, disable_log_stats=True)
+
+    async def main():
+        eng = AsyncLLM.from_engine_args(args)
+        sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, output_kind=RequestOutputKind.DELTA)
+
+        async def run(rid, p):
+            toks = []
+            async for o in eng.generate(p, sp, rid):
+                toks.extend(o.outputs[0].token_ids)
+            return toks
+
+        a, b = await asyncio.gather(run("a", [1, 2, 3]), run("b", list(range(30))))
+        assert len(a) == 6 and len(b) == 6
+        # host-side failure: terminate the engine process we started; pending and new requests must raise, not hang
+        eng.engine_core.proc.terminate()
+        eng.engine_core.proc.join(5)
+        await asyncio.sleep(0.5)
+        with pytest.raises(EngineDeadError):
+            await asyncio.wait_for(run("c", [4, 5, 6]), 20)
+        eng.shutdown()
+
+    asyncio.run(main())

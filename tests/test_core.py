@@ -1,0 +1,191 @@
+"""Scheduler / KV-cache manager / block pool logic on CPU with a fake model runner (no weights, no device)."""
+import pytest
+
+from onecat_vllm.config import CacheConfig, ModelConfig, SchedulerConfig, SpeculativeConfig, VllmConfig
+from onecat_vllm.core.block_pool import BlockPool
+from onecat_vllm.core.kv_cache_manager import KVCacheManager
+from onecat_vllm.core.kv_cache_utils import FreeKVCacheBlockQueue, KVCacheBlock, hash_block_tokens, make_block_hasher
+from onecat_vllm.core.sched_output import ModelRunnerOutput
+from onecat_vllm.core.scheduler import Scheduler
+from onecat_vllm.request import Request, RequestStatus
+from onecat_vllm.sampling_params import SamplingParams
+
+
+def make_scheduler(num_blocks=64, budget=64, max_seqs=8, max_len=256, policy="fcfs", spec=None, prefix=True, chunked=True):
+    cfg = VllmConfig(ModelConfig(max_model_len=max_len), CacheConfig(block_size=16, enable_prefix_caching=prefix),
+                     scheduler_config=SchedulerConfig(max_num_batched_tokens=budget, max_num_seqs=max_seqs, max_model_len=max_len, policy=policy,
+                                                      enable_chunked_prefill=chunked),
+                     speculative_config=spec or SpeculativeConfig(), device="cpu")
+    return Scheduler(cfg, num_blocks)
+
+
+def req(rid, n, max_tokens=8, priority=0, s=None, tokens=None, arrival=None):
+    r = Request(rid, tokens or list(range(1, n + 1)), SamplingParams(max_tokens=max_tokens, ignore_eos=True, temperature=0.0), eos_token_id=0,
+                priority=priority, arrival_time=arrival, block_hasher=s.block_hasher if s else None)
+    return r
+
+
+def fake_output(so, token=7, spec=None):
+    ids = list(so.num_scheduled_tokens)
+    return ModelRunnerOutput(req_ids=ids, sampled_token_ids=[[token] for _ in ids], spec_token_ids=spec)
+
+
+def run_step(s, token=7):
+    so = s.schedule()
+    sampled = []
+    for rid, n in so.num_scheduled_tokens.items():
+        r = s.requests[rid]
+        sampled.append([token] if r.num_computed_tokens >= r.num_tokens else [])
+    out = s.update_from_output(so, ModelRunnerOutput(req_ids=list(so.num_scheduled_tokens), sampled_token_ids=sampled))
+    return so, out
+
+
+def test_free_queue_order_and_removal():
+    blocks = [KVCacheBlock(i) for i in range(5)]
+    q = FreeKVCacheBlockQueue(blocks)
+    assert q.popleft().block_id == 0
+    q.remove(blocks[2])
+    q.append(blocks[0])
+    assert [b.block_id for b in q.get_all_free_blocks()] == [1, 3, 4, 0]
+    assert q.num_free_blocks == 4
+    with pytest.raises(RuntimeError):
+        q.remove(blocks[2])
+
+
+def test_block_hash_chain_identifies_prefix():
+    import hashlib
+    fn = lambda b: hashlib.sha256(b).digest()
+    h1 = hash_block_tokens(fn, None, (1, 2, 3))
+    assert hash_block_tokens(fn, h1, (4, 5, 6)) != hash_block_tokens(fn, None, (4, 5, 6))
+    assert hash_block_tokens(fn, None, (1, 2, 3), ("salt",)) != h1
+
+
+def test_chunked_prefill_budget_and_decode():
+    s = make_scheduler(budget=32)
+    s.add_request(req("a", 50, s=s))
+    s.add_request(req("b", 0, s=s, tokens=list(range(500, 520))))
+    so, _ = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 32} and so.total_num_scheduled_tokens == 32
+    so, _ = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 18, "b": 14}  # running first, waiting fills the rest
+    so, outs = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 1, "b": 6}
+    assert [o.request_id for o in outs[0].outputs] == ["a", "b"] or len(outs[0].outputs) >= 1
+    so, _ = run_step(s)
+    assert so.num_scheduled_tokens == {"a": 1, "b": 1}
+
+
+def test_finish_by_length_frees_blocks():
+    s = make_scheduler()
+    s.add_request(req("a", 10, max_tokens=2, s=s))
+    free0 = s.kv_cache_manager.block_pool.get_num_free_blocks()
+    run_step(s)
+    _, outs = run_step(s)
+    assert outs[0].outputs[0].finish_reason is not None and str(outs[0].outputs[0].finish_reason) == "length"
+    assert not s.has_unfinished_requests()
+    assert s.kv_cache_manager.block_pool.get_num_free_blocks() == free0
+    assert "a" in s.schedule().finished_req_ids
+
+
+def test_stop_token_and_eos():
+    s = make_scheduler()
+    r = Request("a", [1, 2, 3], SamplingParams(max_tokens=10, stop_token_ids=[9]), eos_token_id=5)
+    s.add_request(r)
+    so = s.schedule()
+    out = s.update_from_output(so, ModelRunnerOutput(req_ids=["a"], sampled_token_ids=[[9]]))
+    assert out[0].outputs[0].stop_reason == 9 and str(out[0].outputs[0].finish_reason) == "stop"
+    r2 = Request("b", [1, 2, 3], SamplingParams(max_tokens=10), eos_token_id=5)
+    s.add_request(r2)
+    so = s.schedule()
+    out = s.update_from_output(so, ModelRunnerOutput(req_ids=["b"], sampled_token_ids=[[5]]))
+    assert str(out[0].outputs[0].finish_reason) == "stop" and out[0].outputs[0].stop_reason is None
+
+
+def test_prefix_cache_hit_and_last_token_recompute():
+    s = make_scheduler(budget=256)
+    toks = list(range(100, 148))  # 3 full blocks
+    s.add_request(req("a", 0, max_tokens=1, s=s, tokens=toks))
+    run_step(s)
+    s.schedule()
+    s.add_request(req("b", 0, max_tokens=1, s=s, tokens=toks))
+    so = s.schedule()
+    # 48 tokens cached, but at most num_tokens-1 may hit → 2 blocks (32 tokens), 16 recomputed
+    assert so.num_scheduled_tokens["b"] == 16 and so.scheduled_new_reqs[0].num_computed_tokens == 32
+    s.add_request(req("c", 0, max_tokens=1, s=s, tokens=toks + [1, 2, 3]))
+    s.update_from_output(so, ModelRunnerOutput(req_ids=["b"], sampled_token_ids=[[1]]))
+    so = s.schedule()
+    assert so.scheduled_new_reqs[0].num_computed_tokens == 48
+
+
+def test_preemption_fcfs_and_resume():
+    s = make_scheduler(num_blocks=7, budget=256, prefix=False)  # 6 usable blocks
+    s.add_request(req("a", 40, max_tokens=40, s=s))  # 3 blocks
+    s.add_request(req("b", 40, max_tokens=40, s=s))  # 3 blocks
+    run_step(s)
+    preempted = False
+    for _ in range(12):
+        so, _ = run_step(s)
+        if so.preempted_req_ids:
+            assert so.preempted_req_ids == {"b"}  # newest running request goes first
+            preempted = True
+            break
+    assert preempted and s.requests["b"].status == RequestStatus.PREEMPTED and s.requests["b"].num_computed_tokens == 0
+    for _ in range(100):
+        so, _ = run_step(s)
+        if not s.has_unfinished_requests():
+            break
+    assert not s.has_unfinished_requests()
+
+
+def test_priority_policy_orders_waiting_and_victims():
+    s = make_scheduler(policy="priority", max_seqs=1)
+    s.add_request(req("low", 5, priority=5, s=s, arrival=1.0))
+    s.add_request(req("high", 5, priority=0, s=s, arrival=2.0))
+    so = s.schedule()
+    assert list(so.num_scheduled_tokens) == ["high"]
+
+
+def test_abort_running_and_waiting():
+    s = make_scheduler(max_seqs=1)
+    s.add_request(req("a", 5, s=s))
+    s.add_request(req("b", 5, s=s))
+    s.schedule()
+    s.finish_requests(["a", "b"], RequestStatus.FINISHED_ABORTED)
+    assert not s.has_unfinished_requests() and s.finished_req_ids == {"a", "b"}
+
+
+def test_spec_decode_accounting():
+    spec = SpeculativeConfig(method="ngram", num_speculative_tokens=3)
+    s = make_scheduler(spec=spec)
+    s.add_request(req("a", 10, max_tokens=20, s=s))
+    so = s.schedule()
+    s.update_from_output(so, ModelRunnerOutput(req_ids=["a"], sampled_token_ids=[[7]], spec_token_ids=[[8, 9, 10]]))
+    so = s.schedule()
+    assert so.num_scheduled_tokens["a"] == 4 and so.scheduled_spec_decode_tokens["a"] == [8, 9, 10]
+    r = s.requests["a"]
+    assert r.num_computed_tokens == 14
+    # two drafts accepted (+1 recovered token): one rejected draft is rolled back
+    s.update_from_output(so, ModelRunnerOutput(req_ids=["a"], sampled_token_ids=[[8, 9, 42]], spec_token_ids=[[1, 2, 3]]))
+    assert r.num_computed_tokens == 13 and r.output_token_ids == [7, 8, 9, 42]
+    so = s.schedule()
+    assert so.num_scheduled_tokens["a"] == 4
+
+
+def test_kv_manager_lookahead_and_usage():
+    m = KVCacheManager(num_blocks=10, block_size=16, max_model_len=256, enable_caching=False)
+    r = Request("a", list(range(20)), SamplingParams(max_tokens=4))
+    new = m.allocate_slots(r, 20, num_lookahead_tokens=13)
+    assert len(new) == 3  # 33 tokens → 3 blocks
+    assert m.usage == pytest.approx(3 / 9)
+    m.free(r)
+    assert m.usage == 0.0
+    assert m.allocate_slots(Request("b", list(range(200)), SamplingParams()), 200) is None
+
+
+def test_rejects_bad_requests():
+    s = make_scheduler(max_len=32)
+    with pytest.raises(ValueError):
+        s.add_request(req("long", 40, s=s))
+    s.add_request(req("x", 4, s=s))
+    with pytest.raises(ValueError):
+        s.add_request(req("x", 4, s=s))

@@ -1,0 +1,123 @@
+"""Sampler and rejection sampler semantics on CPU."""
+import pytest
+import torch
+
+from onecat_vllm.ops import ref
+from onecat_vllm.sample.metadata import SamplingMetadata
+from onecat_vllm.sample.rejection_sampler import RejectionSampler
+from onecat_vllm.sample.sampler import Sampler
+from onecat_vllm.sampling_params import SamplingParams
+
+
+def md(B, **kw):
+    base = dict(temperature=None, all_greedy=True, all_random=False, top_p=None, top_k=None, min_p=None, generators={}, max_num_logprobs=None,
+                no_penalties=True)
+    base.update(kw)
+    m = SamplingMetadata(**base)
+    m.output_token_ids = kw.get("output_token_ids", [[] for _ in range(B)])
+    m.logit_bias = [None] * B
+    m.allowed_token_ids = [None] * B
+    return m
+
+
+def test_greedy_and_logprobs_from_raw_logits():
+    lg = torch.tensor([[0.1, 2.0, -1.0, 0.5], [3.0, 0.0, 0.0, 0.0]])
+    out = Sampler()(lg, md(2, max_num_logprobs=2))
+    assert out.sampled_token_ids.tolist() == [1, 0]
+    ids, vals, ranks = out.logprobs
+    assert ids[0].tolist()[:2] == [1, 1] and ranks.tolist() == [1, 1]
+    assert torch.allclose(vals[0, 0], torch.log_softmax(lg[0], -1)[1])
+
+
+def test_top_k_top_p_min_p_masks():
+    lg = torch.log(torch.tensor([[0.5, 0.3, 0.15, 0.05]]))
+    k = ref.top_k_top_p_min_p(lg.clone(), torch.tensor([2]), None, None)
+    assert torch.isinf(k[0, 2:]).all() and not torch.isinf(k[0, :2]).any()
+    p = ref.top_k_top_p_min_p(lg.clone(), None, torch.tensor([0.7]), None)
+    assert torch.isinf(p[0, 2:]).all() and not torch.isinf(p[0, :2]).any()
+    m = ref.top_k_top_p_min_p(lg.clone(), None, None, torch.tensor([0.5]))
+    assert torch.isinf(m[0, 2:]).all()
+
+
+def test_seeded_random_sampling_reproducible_and_distribution():
+    torch.manual_seed(0)
+    lg = torch.log(torch.tensor([[0.7, 0.2, 0.1]])).repeat(4000, 1)
+    g = {i: torch.Generator().manual_seed(i) for i in range(4000)}
+    m = md(4000, temperature=torch.ones(4000), all_greedy=False, all_random=True, generators=g)
+    a = Sampler()(lg, m).sampled_token_ids
+    g2 = {i: torch.Generator().manual_seed(i) for i in range(4000)}
+    b = Sampler()(lg, md(4000, temperature=torch.ones(4000), all_greedy=False, all_random=True, generators=g2)).sampled_token_ids
+    assert torch.equal(a, b)
+    freq = torch.bincount(a, minlength=3).float() / 4000
+    assert abs(freq[0] - 0.7) < 0.03 and abs(freq[1] - 0.2) < 0.03
+
+
+def test_penalties_and_logit_processors():
+    lg = torch.zeros(1, 5)
+    lg[0, 2] = 1.0
+    m = md(1, no_penalties=False, presence_penalties=torch.tensor([2.0]), frequency_penalties=torch.tensor([0.0]),
+           repetition_penalties=torch.tensor([1.0]), output_token_ids=[[2]])
+    m.prompt_token_ids = [[]]
+    assert Sampler()(lg.clone(), m).sampled_token_ids.item() != 2
+    m2 = md(1)
+    m2.allowed_token_ids = [[3, 4]]
+    m2.logit_bias = [{4: 5.0}]
+    assert Sampler()(lg.clone(), m2).sampled_token_ids.item() == 4
+    m3 = md(1, output_token_ids=[[]])
+    m3.min_tokens = {0: (2, {2})}
+    assert Sampler()(lg.clone(), m3).sampled_token_ids.item() != 2
+    m4 = md(1, output_token_ids=[[1]])
+    m4.bad_words_token_ids = {0: [[1, 2]]}
+    assert Sampler()(lg.clone(), m4).sampled_token_ids.item() != 2
+
+
+def test_rejection_greedy_accepts_matching_prefix():
+    V = 6
+    tl = torch.full((2, 4, V), -5.0)
+    for b, seq in enumerate([[1, 2, 3, 4], [1, 5, 0, 0]]):
+        for i, t in enumerate(seq):
+            tl[b, i, t] = 5.0
+    draft = torch.tensor([[1, 2, 3], [1, 2, 3]])
+    out = RejectionSampler()(draft, torch.tensor([3, 3]), tl, torch.tensor([4, 9]), md(2))
+    assert RejectionSampler.parse_output(out) == [[1, 2, 3, 4], [1, 5]]
+
+
+def test_rejection_random_is_unbiased_for_point_drafts():
+    """With no draft probabilities the draft is a point mass: accept with prob p(x); the emitted token must follow p."""
+    torch.manual_seed(0)
+    p = torch.tensor([0.6, 0.3, 0.1])
+    B = 6000
+    tl = torch.log(p).view(1, 1, 3).repeat(B, 2, 1)
+    draft = torch.zeros(B, 1, dtype=torch.long)
+    m = md(B, temperature=torch.ones(B), all_greedy=False, all_random=True)
+    out = RejectionSampler(seed=1)(draft, torch.ones(B, dtype=torch.long), tl, torch.full((B,), 2), m)
+    first = out[:, 0]
+    freq = torch.bincount(first, minlength=3).float() / B
+    assert torch.allclose(freq, p, atol=0.03)
+    accepted = (first == 0) & (out[:, 1] == 2)
+    assert abs(accepted.float().mean() - 0.6) < 0.05  # bonus appended exactly when the draft was accepted
+
+
+def test_rejection_synthetic_rate():
+    B, k, V = 4000, 3, 8
+    tl = torch.randn(B, k + 1, V)
+    draft = torch.randint(0, V, (B, k))
+    rs = RejectionSampler(synthetic_rates=[0.7, 0.7, 0.7], seed=3)
+    out = rs(draft, torch.full((B,), k), tl, torch.zeros(B, dtype=torch.long), md(B))
+    n_acc = torch.tensor([sum(1 for i in range(k) if row[i] == d[i]) for row, d in zip(out.tolist(), draft.tolist())]).float()
+    lens = torch.tensor([len(r) for r in RejectionSampler.parse_output(out)]).float()
+    # expected emitted tokens per step = 1 + 0.7 + 0.49 + 0.343
+    assert abs(lens.mean() - 2.533) < 0.08
+    rs2 = RejectionSampler(synthetic_rates=[0.7, 0.7, 0.7], seed=3)
+    out2 = rs2(draft, torch.full((B,), k), tl, torch.zeros(B, dtype=torch.long), md(B))
+    assert torch.equal(out, out2), "the seeded acceptance stream must be reproducible"
+
+
+def test_sampling_params_validation():
+    with pytest.raises(ValueError):
+        SamplingParams(top_p=0.0)
+    with pytest.raises(ValueError):
+        SamplingParams(n=2, temperature=0.0)
+    sp = SamplingParams(temperature=0.0, top_k=5, top_p=0.5)
+    assert sp.top_k == 0 and sp.top_p == 1.0  # greedy neutralises the random knobs
+    assert SamplingParams.from_dict(sp.to_dict()).temperature == 0.0

@@ -232,9 +232,80 @@ torch::Tensor argmax(torch::Tensor x) {
   return out;
 }
 
+// Gated-DeltaNet: conv + SiLU with rolling state, then the gated delta rule with fused gating. `mixed` is the pre-conv [T, 2*Hk*K + Hv*V]
+// slice; returns o [T, Hv*V]. spec_state (optional) receives the recurrent state after every token; write_state=false leaves slots alone.
+torch::Tensor gdn_forward(torch::Tensor mixed, torch::Tensor b_in, torch::Tensor a_in, torch::Tensor conv_w, torch::Tensor A_log, torch::Tensor dt_bias,
+                          torch::Tensor conv_state, torch::Tensor ssm_state, torch::Tensor qsl, torch::Tensor slots, torch::Tensor has_init,
+                          int64_t Hk, int64_t Hv, int64_t K, int64_t V, bool write_state, c10::optional<torch::Tensor> spec_state) {
+  check_bf16(mixed, "mixed");
+  check_bf16(conv_w, "conv_w");
+  check_bf16(conv_state, "conv_state");
+  TORCH_CHECK(mixed.dim() == 2 && mixed.stride(1) == 1, "mixed must be [T, C] with unit inner stride");
+  TORCH_CHECK(ssm_state.scalar_type() == torch::kFloat32 && ssm_state.is_contiguous() && conv_state.is_contiguous(), "states must be contiguous (fp32 recurrent state)");
+  TORCH_CHECK(qsl.scalar_type() == torch::kInt32 && slots.scalar_type() == torch::kInt32 && has_init.scalar_type() == torch::kInt32, "metadata must be int32");
+  TORCH_CHECK(a_in.stride(1) == 1 && b_in.stride(1) == 1 && a_in.stride(0) == b_in.stride(0), "a/b must share a row pitch");
+  const c10::cuda::CUDAGuard guard(mixed.device());
+  const int T = (int)mixed.size(0), C = (int)mixed.size(1), R = (int)slots.size(0);
+  TORCH_CHECK(C == 2 * Hk * K + Hv * V, "mixed width does not match the head layout");
+  auto y = torch::empty({T, C}, mixed.options());
+  auto out = torch::empty({T, Hv * V}, mixed.options());
+  if (T == 0) return out;
+  oc::GdnConvParams cp{};
+  cp.x = (const __nv_bfloat16*)mixed.data_ptr();
+  cp.ldx = mixed.stride(0);
+  cp.w = (const __nv_bfloat16*)conv_w.data_ptr();
+  cp.y = (__nv_bfloat16*)y.data_ptr();
+  cp.conv_state = (__nv_bfloat16*)conv_state.data_ptr();
+  cp.query_start_loc = qsl.data_ptr<int>();
+  cp.state_slots = slots.data_ptr<int>();
+  cp.has_initial_state = has_init.data_ptr<int>();
+  cp.T = T; cp.R = R; cp.C = C; cp.kw = (int)conv_w.size(1);
+  TORCH_CHECK(conv_state.size(1) == C && conv_state.size(2) == cp.kw - 1, "conv_state must be [slots, C, kw-1]");
+  TORCH_CHECK(oc::gdn_conv_launch(cp, cur_stream()) == 0, "gdn conv launch failed");
+  oc::GdnParams p{};
+  const __nv_bfloat16* yb = (const __nv_bfloat16*)y.data_ptr();
+  p.q = yb; p.k = yb + Hk * K; p.v = yb + 2 * Hk * K;
+  p.ld_qkv = C;
+  p.a = (const __nv_bfloat16*)a_in.data_ptr();
+  p.b = (const __nv_bfloat16*)b_in.data_ptr();
+  p.ld_ba = a_in.stride(0);
+  p.A_log = A_log.data_ptr<float>();
+  p.dt_bias = dt_bias.data_ptr<float>();
+  p.state = ssm_state.data_ptr<float>();
+  p.out = (__nv_bfloat16*)out.data_ptr();
+  p.query_start_loc = cp.query_start_loc; p.state_slots = cp.state_slots; p.has_initial_state = cp.has_initial_state;
+  p.R = R; p.Hk = (int)Hk; p.Hv = (int)Hv; p.K = (int)K; p.V = (int)V;
+  p.write_state = write_state ? 1 : 0;
+  if (spec_state.has_value()) {
+    TORCH_CHECK(spec_state->scalar_type() == torch::kFloat32 && spec_state->is_contiguous() && spec_state->dim() == 5 && spec_state->size(0) >= R, "spec_state must be fp32 [R, q, Hv, K, V]");
+    p.spec_state = spec_state->data_ptr<float>();
+    p.spec_q = (int)spec_state->size(1);
+  }
+  int rc = oc::gdn_recurrent_launch(p, cur_stream());
+  TORCH_CHECK(rc == 0, "gdn recurrence launch failed: ", rc, " (K and V must be 128)");
+  return out;
+}
+
+// Speculative commit of the conv state: recompute each slot from the pre-chunk snapshot and the first n_valid inputs of the chunk.
+void gdn_conv_commit(torch::Tensor mixed, torch::Tensor conv_state, torch::Tensor prev_state, torch::Tensor n_valid, torch::Tensor qsl,
+                     torch::Tensor slots, torch::Tensor has_init, int64_t kw) {
+  const c10::cuda::CUDAGuard guard(mixed.device());
+  oc::GdnConvParams cp{};
+  cp.x = (const __nv_bfloat16*)mixed.data_ptr();
+  cp.ldx = mixed.stride(0);
+  cp.conv_state = (__nv_bfloat16*)conv_state.data_ptr();
+  cp.prev_state = (const __nv_bfloat16*)prev_state.data_ptr();
+  cp.n_valid = n_valid.data_ptr<int>();
+  cp.query_start_loc = qsl.data_ptr<int>();
+  cp.state_slots = slots.data_ptr<int>();
+  cp.has_initial_state = has_init.data_ptr<int>();
+  cp.T = (int)mixed.size(0); cp.R = (int)slots.size(0); cp.C = (int)mixed.size(1); cp.kw = (int)kw;
+  TORCH_CHECK(oc::gdn_conv_commit_launch(cp, cur_stream()) == 0, "gdn conv commit failed");
+}
+
 int64_t read_status(bool clear) {
   return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) |
-                   oc::comm_read_status(clear));
+                   oc::comm_read_status(clear) | oc::gdn_read_status(clear));
 }
 
 // ---- symmetric slab + peer-memory reductions
@@ -302,6 +373,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("argmax", &argmax);
   m.def("read_status", &read_status);
+  m.def("gdn_forward", &gdn_forward);
+  m.def("gdn_conv_commit", &gdn_conv_commit);
   m.def("comm_alloc", &comm_alloc);
   m.def("comm_free", &comm_free);
   m.def("comm_export", &comm_export);

@@ -51,4 +51,41 @@ struct AttnParams {
 int attention_launch(const AttnParams& p, int mode, cudaStream_t st);
 unsigned int attention_read_status(bool clear);
 
+
+struct GdnConvParams {
+  const __nv_bfloat16* x;   // [T][ldx] pre-conv mixed q|k|v (column slice allowed)
+  long long ldx;
+  const __nv_bfloat16* w;   // [C][kw]
+  __nv_bfloat16* y;         // [T][C] contiguous
+  __nv_bfloat16* conv_state;  // [slots][C][kw-1], updated in place
+  const int* query_start_loc;
+  const int* state_slots;
+  const int* has_initial_state;
+  int T, R, C, kw;
+  const int* n_valid;              // optional [R]: count only this many tokens of each chunk (speculative commit)
+  const __nv_bfloat16* prev_state; // optional [R][C][kw-1]: snapshot of the state before the chunk (speculative commit)
+};
+
+struct GdnParams {
+  const __nv_bfloat16 *q, *k, *v;  // post-conv tensors: q,k [T][Hk*K], v [T][Hv*V] with a common row pitch ld_qkv
+  long long ld_qkv;
+  const __nv_bfloat16 *a, *b;      // [T][Hv] gate inputs with row pitch ld_ba
+  long long ld_ba;
+  const float *A_log, *dt_bias;    // [Hv]
+  float* state;                    // [slots][Hv][K][V] fp32
+  __nv_bfloat16* out;              // [T][Hv*V]
+  const int* query_start_loc;
+  const int* state_slots;
+  const int* has_initial_state;
+  int R, Hk, Hv, K, V;
+  int write_state;                 // 0: leave the slot untouched (speculative verification commits later)
+  float* spec_state;               // optional [R][spec_q][Hv][K][V]: state after each token
+  int spec_q;
+};
+
+int gdn_conv_launch(const GdnConvParams& p, cudaStream_t st);
+int gdn_conv_commit_launch(const GdnConvParams& p, cudaStream_t st);
+int gdn_recurrent_launch(const GdnParams& p, cudaStream_t st);
+unsigned int gdn_read_status(bool clear);
+
 }  // namespace oc

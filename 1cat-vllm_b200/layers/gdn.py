@@ -54,12 +54,18 @@ class GatedDeltaNet(nn.Module):
             o = K.gdn_forward(mixed, b, a, self.conv_weight, self.A_log, self.dt_bias, conv_state, ssm_state, md,
                               self.Hk, self.Hv, self.K, self.V)
         else:
-            mixed = ref.causal_conv1d(mixed.contiguous(), self.conv_weight, None, conv_state, md.query_start_loc, md.state_slots,
-                                      md.has_initial_state)
+            rec = getattr(md, "gdn_record", None)
+            pre = mixed.contiguous()
+            prev = conv_state[md.state_slots.long()].clone() if rec is not None else None
+            mixed = ref.causal_conv1d(pre, self.conv_weight, None, conv_state, md.query_start_loc, md.state_slots, md.has_initial_state)
             q = mixed[:, : self.key_dim].reshape(T, self.Hk, self.K)
             k = mixed[:, self.key_dim: 2 * self.key_dim].reshape(T, self.Hk, self.K)
             v = mixed[:, 2 * self.key_dim:].reshape(T, self.Hv, self.V)
             g, beta = ref.gdn_gating(a, b, self.A_log, self.dt_bias)
-            o = ref.gated_delta_rule(q, k, v, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
+            spec = None
+            if rec is not None:
+                spec = torch.zeros(md.num_reqs, md.spec_q, self.Hv, self.K, self.V, dtype=torch.float32)
+                rec.append(dict(conv_state=conv_state, ssm_state=ssm_state, spec=spec, prev=prev, mixed=pre, kw=self.kw))
+            o = ref.gated_delta_rule(q, k, v, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state, token_states=spec)
         o = ops.rms_norm_gated(o.reshape(T, self.Hv * self.V), z, self.norm_weight, self.eps, self.Hv)
         return self.out_proj(o)

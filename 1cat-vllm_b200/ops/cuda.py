@@ -310,15 +310,38 @@ def paged_attention(q, kv_cache, md, scale, out=None, lse=None):
 
 # ----------------------------------------------------------------------------- ops still served by device-side PyTorch
 def gdn_forward(mixed, b, a, conv_w, A_log, dt_bias, conv_state, ssm_state, md, Hk, Hv, K, V):
-    TORCH_STANDINS.add("gdn_forward")
-    T = mixed.shape[0]
-    key_dim = Hk * K
-    mixed = ref.causal_conv1d(mixed.contiguous(), conv_w, None, conv_state, md.query_start_loc, md.state_slots, md.has_initial_state)
-    qq = mixed[:, :key_dim].reshape(T, Hk, K)
-    kk = mixed[:, key_dim:2 * key_dim].reshape(T, Hk, K)
-    vv = mixed[:, 2 * key_dim:].reshape(T, Hv, V)
-    g, beta = ref.gdn_gating(a, b, A_log, dt_bias)
-    return ref.gated_delta_rule(qq, kk, vv, g, beta, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
+    """Conv + gating + gated delta rule in two kernels. Under speculative verification (``md.gdn_record`` set by the
+    runner) the slots are left untouched and the state after every token is recorded for the later commit."""
+    global _LAUNCHES
+    _LAUNCHES += 3
+    rec = getattr(md, "gdn_record", None)
+    hi = md.has_initial_state if md.has_initial_state.dtype == torch.int32 else md.has_initial_state.to(torch.int32)
+    if rec is None:
+        return _C.gdn_forward(mixed, b, a, conv_w.to(torch.bfloat16), A_log, dt_bias, conv_state, ssm_state, md.query_start_loc, md.state_slots,
+                              hi, Hk, Hv, K, V, True, None)
+    q = md.spec_q
+    spec = torch.empty(md.num_reqs, q, Hv, K, V, dtype=torch.float32, device=mixed.device)
+    prev = conv_state[md.state_slots.long()].clone()
+    out = _C.gdn_forward(mixed, b, a, conv_w.to(torch.bfloat16), A_log, dt_bias, conv_state, ssm_state, md.query_start_loc, md.state_slots,
+                         hi, Hk, Hv, K, V, False, spec)
+    rec.append(dict(conv_state=conv_state, ssm_state=ssm_state, spec=spec, prev=prev, mixed=mixed, kw=conv_w.shape[1]))
+    return out
+
+
+def gdn_commit(md, rec: list, n_valid: torch.Tensor) -> None:
+    """After verification: every Gated-DeltaNet layer takes the state that follows the last accepted token."""
+    global _LAUNCHES
+    hi = md.has_initial_state if md.has_initial_state.dtype == torch.int32 else md.has_initial_state.to(torch.int32)
+    slots = md.state_slots.long()
+    ar = torch.arange(md.num_reqs, device=n_valid.device)
+    idx = (n_valid.long() - 1).clamp(min=0)
+    qlen = md.query_start_loc[1:] - md.query_start_loc[:-1]
+    recorded = qlen <= md.spec_q  # longer sequences (prefill chunks) wrote their slot directly
+    rs, ridx = slots[recorded], ar[recorded]
+    for e in rec:
+        e["ssm_state"][rs] = e["spec"][ridx, idx[recorded].clamp(max=e["spec"].shape[1] - 1)]
+        _C.gdn_conv_commit(e["mixed"], e["conv_state"], e["prev"], n_valid.to(torch.int32), md.query_start_loc, md.state_slots, hi, e["kw"])
+        _LAUNCHES += 2
 
 
 def prepare_moe(moe) -> None:

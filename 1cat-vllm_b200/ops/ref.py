@@ -274,6 +274,13 @@ def causal_conv1d(x, weight, bias, conv_state, query_start_loc, state_slots, has
     return out
 
 
+def conv_state_after(prev: torch.Tensor, x_chunk: torch.Tensor, n: int) -> torch.Tensor:
+    """Conv state ``[C, k-1]`` after consuming the first ``n`` rows of ``x_chunk`` ``[L, C]`` starting from ``prev``."""
+    m = prev.shape[1]
+    seq = torch.cat([prev.t().float(), x_chunk[:n].float()], dim=0)
+    return seq[-m:].t().to(prev.dtype)
+
+
 def gdn_gating(a, b, A_log, dt_bias):
     """g = -exp(A_log) * softplus(a + dt_bias) (log-space decay), beta = sigmoid(b)
     (reference: layers/mamba/gdn/qwen_gdn_linear_attn.py:6945-7013)."""
@@ -286,7 +293,7 @@ def _l2norm(x, eps=1e-6):
 
 
 def gated_delta_rule(q, k, v, g, beta, state, query_start_loc, state_slots, has_initial_state, scale: Optional[float] = None,
-                     use_qk_l2norm: bool = True):
+                     use_qk_l2norm: bool = True, token_states: Optional[torch.Tensor] = None):
     """Sequential gated delta rule, fp32 state ``[slots, Hv, K, V]`` updated in place:
     ``S <- e^g S + k (x) ((v - (e^g S)^T k) beta)``, ``o = S^T q * scale``. q,k ``[T,Hk,K]``, v ``[T,Hv,V]``,
     g,beta ``[T,Hv]``. This token-by-token form is the oracle for both the chunked prefill and the
@@ -314,7 +321,10 @@ def gated_delta_rule(q, k, v, g, beta, state, query_start_loc, state_slots, has_
             delta = (v[t].float() - kv) * beta[t].float().view(Hv, 1)
             S = S + torch.einsum("hk,hv->hkv", kf[t], delta)
             out[t] = torch.einsum("hk,hkv->hv", qf[t], S).to(out.dtype)
-        state[slot] = S.to(state.dtype)
+            if token_states is not None and (b - a) <= token_states.shape[1]:
+                token_states[r, t - a] = S
+        if token_states is None or (b - a) > token_states.shape[1]:
+            state[slot] = S.to(state.dtype)
     return out
 
 

@@ -354,7 +354,8 @@ class ModelRunner:
         spec_verify = any(len(d) > 0 for d in drafts_of)
         gdn_spec = None
         if spec_verify and self.mc.is_hybrid:
-            gdn_spec = self._begin_gdn_spec(md)
+            gdn_spec = md.gdn_record = []
+            md.spec_q = 1 + self.num_spec
         ids = self._view("ids", T)
         hidden = None
         if gkey is not None:
@@ -389,8 +390,8 @@ class ModelRunner:
             out.prompt_logprobs = None
         elif timed:
             ev1.record()
-        if gdn_spec is not None:
-            self._commit_gdn_spec(gdn_spec, md, sampled_lists, drafts_of)
+        if gdn_spec:
+            self._commit_gdn_spec(gdn_spec, md, sampled_lists, query_lens)
         # bookkeeping: the runner owns the token history of running requests
         for i, rid in enumerate(req_ids):
             st = self.requests[rid]
@@ -459,35 +460,24 @@ class ModelRunner:
                 b += 1
         return out
 
-    # ---- Gated-DeltaNet state under speculation: per-token candidate states, commit the accepted one
-    def _begin_gdn_spec(self, md):
-        R, k1 = md.num_reqs, self.num_spec + 1
-        spec = []
-        for layer, cache in zip(self.model.model.layers, self.kv_caches):
-            if layer.kind != "linear_attention":
-                spec.append(None)
-                continue
-            conv, ssm = cache
-            spec.append((conv[md.state_slots.long()].clone(), ssm[md.state_slots.long()].clone()))
-        md.gdn_snapshots = spec
-        return spec
-
-    def _commit_gdn_spec(self, spec, md, sampled, drafts_of) -> None:
-        """Requests whose drafts were partly rejected: restore the pre-step state and replay the accepted tokens
-        through the GDN layers is not possible without their inputs, so those requests keep per-token states:
-        the forward above recorded them in ``md.gdn_token_states``; pick the state after the last valid token."""
-        rec = getattr(md, "gdn_token_states", None)
-        if rec is None:
+    # ---- Gated-DeltaNet state under speculation: the forward records the state after every verified token; once the
+    # accepted count is known each layer's slot takes the state that follows the last accepted token
+    def _commit_gdn_spec(self, rec: list, md, sampled, query_lens) -> None:
+        n_valid = torch.tensor([len(s) if s else q for s, q in zip(sampled, query_lens)], dtype=torch.int32, device=self.device)
+        if self.use_cuda:
+            from onecat_vllm.ops import cuda as K
+            K.gdn_commit(md, rec, n_valid)
             return
-        slots = md.state_slots.long()
-        n_valid = torch.tensor([max(len(s), 1) for s in sampled], device=self.device)
-        ar = torch.arange(md.num_reqs, device=self.device)
-        for li, states in rec.items():
-            conv_t, ssm_t = states  # [R, q, ...]
-            conv, ssm = self.kv_caches[li]
-            idx = (n_valid - 1).clamp(max=conv_t.shape[1] - 1)
-            conv[slots] = conv_t[ar, idx]
-            ssm[slots] = ssm_t[ar, idx]
+        from onecat_vllm.ops import ref
+        qsl = md.query_start_loc.tolist()
+        slots = md.state_slots.tolist()
+        for e in rec:
+            for r in range(md.num_reqs):
+                a, b = qsl[r], qsl[r + 1]
+                n = int(n_valid[r])
+                if b - a <= e["spec"].shape[1]:
+                    e["ssm_state"][slots[r]] = e["spec"][r, min(n, b - a) - 1]
+                e["conv_state"][slots[r]] = ref.conv_state_after(e["prev"][r], e["mixed"][a:b], n)
 
     # ------------------------------------------------------------------ profiling helpers
     @torch.inference_mode()

@@ -1,0 +1,91 @@
+"""Model families on CPU (fp32, random weights): chunked prefill must equal whole-prompt prefill (KV / recurrent state hand-off),
+speculative decoding must be lossless under greedy sampling, quantised checkpoints must match their dequantised twins."""
+import pytest
+import torch
+
+from onecat_vllm import LLM, SamplingParams
+
+HYBRID = dict(architectures=["Qwen3NextForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=4, num_attention_heads=4,
+              num_key_value_heads=2, head_dim=32, vocab_size=500, max_position_embeddings=512, linear_num_key_heads=2, linear_num_value_heads=4,
+              linear_key_head_dim=32, linear_value_head_dim=32, full_attention_interval=4, partial_rotary_factor=0.25)
+MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+           num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256, num_experts=8, num_experts_per_tok=2,
+           moe_intermediate_size=32, shared_expert_intermediate_size=64, norm_topk_prob=True)
+DSV3 = dict(architectures=["DeepseekV3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+            vocab_size=300, max_position_embeddings=256, q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16,
+            n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, n_shared_experts=1, n_group=4, topk_group=2,
+            first_k_dense_replace=1, routed_scaling_factor=2.5, scoring_func="sigmoid")
+
+
+def _prompts(vocab, lens=(20, 45, 9), seed=0):
+    g = torch.Generator().manual_seed(seed)
+    return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+
+def _gen(cfg, prompts, **kw):
+    llm = LLM(hf_config=cfg, max_model_len=256, dtype="float32", device="cpu", **kw)
+    out = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
+    llm.shutdown()
+    return out
+
+
+@pytest.mark.parametrize("cfg", [HYBRID, MOE, DSV3], ids=["hybrid-gdn", "moe", "mla-moe"])
+def test_chunked_prefill_equals_whole(cfg):
+    p = _prompts(cfg["vocab_size"])
+    assert _gen(cfg, p, max_num_batched_tokens=16) == _gen(cfg, p)
+
+
+@pytest.mark.parametrize("method", ["ngram", "mtp"])
+def test_spec_decode_lossless_on_hybrid(method):
+    p = _prompts(500)
+    ref = _gen(HYBRID, p)
+    assert _gen(HYBRID, p, speculative_config=dict(method=method, num_speculative_tokens=3)) == ref
+
+
+def test_synthetic_acceptance_exercises_verifier():
+    llm = LLM(hf_config=HYBRID, max_model_len=256, dtype="float32", device="cpu",
+              speculative_config=dict(method="mtp", num_speculative_tokens=3, synthetic_acceptance_rate=0.7, synthetic_seed=1))
+    outs = llm.generate(_prompts(500), SamplingParams(temperature=0, max_tokens=40, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 40 for o in outs)
+    llm.shutdown()
+
+
+def test_awq_checkpoint_matches_dequantised_weights(tmp_path):
+    """An AWQ model and a dense model holding the dequantised weights must decode identically on the CPU path."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    base = dict(architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, vocab_size=300, max_position_embeddings=256)
+    qcfg = dict(base, quantization_config=dict(quant_method="awq", bits=4, group_size=128, zero_point=True))
+    m = build_model(ModelConfig.from_hf_dict(qcfg, dtype=torch.float32), "cpu")
+    dummy_init(m, 0)
+    save_pretrained(m, qcfg, str(tmp_path / "awq"))
+    sd = {}
+    for name, mod in m.named_modules():
+        if hasattr(mod, "method") and mod.method.name == "awq":
+            w = mod.method.dequantized_weight(mod).float()
+            off = 0
+            stacked = [(t, s) for o, t, s in m.stacked_params_mapping if name.endswith(o)]
+            if stacked:
+                ours = [o for o, t, s in m.stacked_params_mapping if name.endswith(o)][0]
+                for theirs, sid in stacked:
+                    n = mod.local_output_sizes[sid]
+                    sd[name[: -len(ours)] + theirs + ".weight"] = w[off:off + n].contiguous()
+                    off += n
+            else:
+                sd[name + ".weight"] = w.contiguous()
+    for k, v in to_hf_state_dict(m).items():
+        if not k.endswith((".qweight", ".qzeros", ".scales")):
+            sd[k] = v
+    from safetensors.torch import save_file
+    import json, os
+    os.makedirs(tmp_path / "dense")
+    save_file({k: v.contiguous() for k, v in sd.items()}, str(tmp_path / "dense" / "model.safetensors"))
+    json.dump(base, open(tmp_path / "dense" / "config.json", "w"))
+    p = _prompts(300, (12, 30))
+    sp = SamplingParams(temperature=0, max_tokens=10, ignore_eos=True)
+    a = LLM(model=str(tmp_path / "awq"), device="cpu", dtype="float32", max_model_len=128)
+    b = LLM(model=str(tmp_path / "dense"), device="cpu", dtype="float32", max_model_len=128)
+    assert [o.outputs[0].token_ids for o in a.generate(p, sp)] == [o.outputs[0].token_ids for o in b.generate(p, sp)]
+    a.shutdown(); b.shutdown()

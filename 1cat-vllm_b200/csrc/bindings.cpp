@@ -303,9 +303,53 @@ void gdn_conv_commit(torch::Tensor mixed, torch::Tensor conv_state, torch::Tenso
   TORCH_CHECK(oc::gdn_conv_commit_launch(cp, cur_stream()) == 0, "gdn conv commit failed");
 }
 
+torch::Tensor rejection_sample(torch::Tensor draft_ids, torch::Tensor num_draft, torch::Tensor target_logits, torch::Tensor bonus_ids,
+                               torch::Tensor uniforms, c10::optional<torch::Tensor> temperature, c10::optional<torch::Tensor> synth_rates,
+                               int64_t seed, bool use_noise) {
+  TORCH_CHECK(target_logits.is_cuda() && target_logits.dim() == 3 && target_logits.stride(2) == 1, "target_logits must be CUDA [B, k+1, V]");
+  TORCH_CHECK(draft_ids.scalar_type() == torch::kInt64 && num_draft.scalar_type() == torch::kInt64 && bonus_ids.scalar_type() == torch::kInt64, "ids must be int64");
+  TORCH_CHECK(uniforms.scalar_type() == torch::kFloat64 && uniforms.is_contiguous() && draft_ids.is_contiguous(), "uniforms must be contiguous float64");
+  const c10::cuda::CUDAGuard guard(target_logits.device());
+  const int B = (int)draft_ids.size(0), k = (int)draft_ids.size(1), V = (int)target_logits.size(2);
+  TORCH_CHECK(target_logits.size(0) == B && target_logits.size(1) >= k, "target_logits shape mismatch");
+  const bool f32 = target_logits.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(f32 || target_logits.scalar_type() == torch::kBFloat16, "logits must be fp32 or bf16");
+  auto out = torch::empty({B, k + 1}, draft_ids.options());
+  auto stats = torch::empty({std::max(B * k, 1) * (int64_t)sizeof(oc::RowStats)}, draft_ids.options().dtype(torch::kUInt8));
+  const float* tp = temperature.has_value() ? temperature->data_ptr<float>() : nullptr;
+  const float* sr = synth_rates.has_value() ? synth_rates->data_ptr<float>() : nullptr;
+  int rc = oc::rejection_launch(target_logits.data_ptr(), f32, (const long long*)draft_ids.data_ptr<int64_t>(), (const long long*)num_draft.data_ptr<int64_t>(),
+                                (const long long*)bonus_ids.data_ptr<int64_t>(), uniforms.data_ptr<double>(), tp, sr, (oc::RowStats*)stats.data_ptr(),
+                                (long long*)out.data_ptr<int64_t>(), B, k, V, target_logits.stride(0), target_logits.stride(1), (unsigned long long)seed,
+                                use_noise ? 1 : 0, cur_stream());
+  TORCH_CHECK(rc == 0, "rejection sampler launch failed");
+  return out;
+}
+
+std::tuple<torch::Tensor, torch::Tensor> route(torch::Tensor logits, c10::optional<torch::Tensor> bias, int64_t k, int64_t n_group, int64_t topk_group,
+                                               bool sigmoid, bool renormalize, double scaling) {
+  check_bf16(logits, "router logits");
+  TORCH_CHECK(logits.dim() == 2 && logits.stride(1) == 1, "router logits must be [T, E]");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  const int T = (int)logits.size(0);
+  auto w = torch::empty({T, k}, logits.options().dtype(torch::kFloat32));
+  auto ids = torch::empty({T, k}, logits.options().dtype(torch::kInt32));
+  oc::RouteParams p{};
+  p.logits = (const __nv_bfloat16*)logits.data_ptr();
+  p.ld = logits.stride(0);
+  p.bias = bias.has_value() ? bias->data_ptr<float>() : nullptr;
+  p.topk_w = w.data_ptr<float>();
+  p.topk_ids = ids.data_ptr<int>();
+  p.T = T; p.E = (int)logits.size(1); p.k = (int)k; p.n_group = (int)n_group; p.topk_group = (int)topk_group;
+  p.sigmoid = sigmoid ? 1 : 0; p.renormalize = renormalize ? 1 : 0; p.scaling = (float)scaling;
+  int rc = oc::route_launch(p, cur_stream());
+  TORCH_CHECK(rc == 0, "router launch failed (needs E % 32 == 0, E <= 512, k <= 16)");
+  return {w, ids};
+}
+
 int64_t read_status(bool clear) {
   return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) |
-                   oc::comm_read_status(clear) | oc::gdn_read_status(clear));
+                   oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear));
 }
 
 // ---- symmetric slab + peer-memory reductions
@@ -373,6 +417,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("argmax", &argmax);
   m.def("read_status", &read_status);
+  m.def("rejection_sample", &rejection_sample);
+  m.def("route", &route);
   m.def("gdn_forward", &gdn_forward);
   m.def("gdn_conv_commit", &gdn_conv_commit);
   m.def("comm_alloc", &comm_alloc);

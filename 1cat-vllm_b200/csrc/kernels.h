@@ -52,6 +52,27 @@ int attention_launch(const AttnParams& p, int mode, cudaStream_t st);
 unsigned int attention_read_status(bool clear);
 
 
+struct RowStats {
+  float p_draft;  // target probability of the draft token at the row's temperature
+  int arg_all;    // arg-max of the row
+  int arg_ex;     // recovered token: arg-max over v != draft of logit/T (+ Gumbel noise for random rows)
+};
+int rejection_launch(const void* logits, int is_fp32, const long long* draft_ids, const long long* num_draft, const long long* bonus,
+                     const double* uniforms, const float* temperature, const float* synth_rates, RowStats* stats, long long* out, int B, int k, int V,
+                     long long ld_b, long long ld_pos, unsigned long long seed, int use_noise, cudaStream_t st);
+
+struct RouteParams {
+  const __nv_bfloat16* logits;  // [T][ld]
+  long long ld;
+  const float* bias;            // e_score_correction_bias [E] or null
+  float* topk_w;                // [T][k]
+  int* topk_ids;                // [T][k]
+  int T, E, k, n_group, topk_group, sigmoid, renormalize;
+  float scaling;
+};
+int route_launch(const RouteParams& p, cudaStream_t st);
+unsigned int sampling_read_status(bool clear);
+
 struct GdnConvParams {
   const __nv_bfloat16* x;   // [T][ldx] pre-conv mixed q|k|v (column slice allowed)
   long long ldx;

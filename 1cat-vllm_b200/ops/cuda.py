@@ -349,11 +349,18 @@ def prepare_moe(moe) -> None:
 
 
 def route(logits, cfg, bias):
-    TORCH_STANDINS.add("route")
-    if cfg.scoring_func == "sigmoid" or cfg.n_group > 1:
-        return ref.grouped_topk(logits, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group, bias, cfg.scoring_func,
-                                cfg.norm_topk_prob, cfg.routed_scaling_factor)
-    return ref.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+    global _LAUNCHES
+    E = logits.shape[1]
+    if E % 32 or E > 512 or cfg.num_experts_per_tok > 16:
+        TORCH_STANDINS.add("route")
+        if cfg.scoring_func == "sigmoid" or cfg.n_group > 1:
+            return ref.grouped_topk(logits, cfg.num_experts_per_tok, cfg.n_group, cfg.topk_group, bias, cfg.scoring_func, cfg.norm_topk_prob,
+                                    cfg.routed_scaling_factor)
+        return ref.topk_softmax(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
+    _LAUNCHES += 1
+    deepseek = cfg.scoring_func == "sigmoid" or cfg.n_group > 1
+    return _C.route(logits.to(torch.bfloat16), bias, cfg.num_experts_per_tok, cfg.n_group if deepseek else 1, cfg.topk_group if deepseek else 1,
+                    cfg.scoring_func == "sigmoid", cfg.norm_topk_prob, cfg.routed_scaling_factor if deepseek else 1.0)
 
 
 def fused_moe(moe, x, topk_w, topk_ids):
@@ -367,15 +374,15 @@ def mla_decode(q_abs, q_pe, latent_cache, md, scale, lora):
     return ref.mla_decode(q_abs, q_pe, latent_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, lora)
 
 
+_REJ_STEP = [0]
+
+
 def rejection_sample(draft_ids, num_draft, target_logits, bonus_ids, md, draft_probs, uniforms, synthetic_rates, gen):
-    TORCH_STANDINS.add("rejection_sample")
-    B, k = draft_ids.shape
-    greedy = torch.ones(B, dtype=torch.bool, device=draft_ids.device) if md.all_greedy else (md.temperature < 1e-5)
-    if md.all_greedy:
-        probs, noise = target_logits[:, :k].float(), None
-    else:
-        t = torch.where(md.temperature < 1e-5, torch.ones_like(md.temperature), md.temperature).view(B, 1, 1)
-        probs = torch.softmax(target_logits[:, :k].float() / t, dim=-1)
-        noise = torch.empty_like(probs).exponential_(generator=gen)
-    return ref.rejection_sample(draft_ids, num_draft, probs, bonus_ids, draft_probs, uniforms,
-                                greedy if synthetic_rates is None else None, synthetic_rates, noise, -1)
+    """Draft probabilities are not used: proposers here emit point-mass (greedy) drafts, for which q(x) = 1."""
+    global _LAUNCHES
+    _LAUNCHES += 2
+    _REJ_STEP[0] += 1
+    temp = None if md.all_greedy else md.temperature
+    rates = torch.tensor(synthetic_rates, dtype=torch.float32, device=target_logits.device) if synthetic_rates is not None else None
+    seed = (gen.initial_seed() if gen is not None else 0) * 1000003 + _REJ_STEP[0]
+    return _C.rejection_sample(draft_ids.contiguous(), num_draft, target_logits, bonus_ids, uniforms.contiguous(), temp, rates, seed, not md.all_greedy)

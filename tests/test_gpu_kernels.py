@@ -252,3 +252,95 @@ def test_peer_wait_is_bounded_and_reports_status():
     y, _ = K().rms_norm(part[0], w, 1e-6, None, False)
     torch.cuda.synchronize()
     assert torch.isfinite(y.float()).all()
+
+
+def test_gdn_kernels_match_sequential_oracle():
+    """conv + gating + gated delta rule: prefill chunk with and without an initial state, then single-token decode."""
+    Hk, Hv, Kd, Vd, kw = 2, 6, 128, 128, 4
+    C = 2 * Hk * Kd + Hv * Vd
+    g = torch.Generator(device="cuda").manual_seed(0)
+    conv_w = (torch.randn(C, kw, device="cuda", generator=g) * 0.3).bfloat16()
+    A_log = torch.rand(Hv, device="cuda", generator=g)
+    dt_bias = torch.rand(Hv, device="cuda", generator=g)
+    slots = torch.tensor([2, 0, 3], dtype=torch.int32, device="cuda")
+    conv_state = (torch.randn(4, C, kw - 1, device="cuda", generator=g) * 0.5).bfloat16()
+    ssm = torch.randn(4, Hv, Kd, Vd, device="cuda", generator=g) * 0.1
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    for qlens, init in (([37, 5, 1], [1, 0, 1]), ([1, 1, 1], [1, 1, 1])):
+        T = sum(qlens)
+        mixed = (torch.randn(T, C, device="cuda", generator=g) * 0.5).bfloat16()
+        ba = torch.randn(T, 2 * Hv, device="cuda", generator=g).bfloat16()
+        qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device="cuda")
+        hi = torch.tensor(init, dtype=torch.int32, device="cuda")
+        md = AttentionMetadata(3, T, qsl, None, None, None, None, max(qlens), 0, state_slots=slots, has_initial_state=hi)
+        cs_c, ssm_c = conv_state.cpu().clone(), ssm.cpu().clone()
+        o = K().gdn_forward(mixed, ba[:, :Hv], ba[:, Hv:], conv_w, A_log, dt_bias, conv_state, ssm, md, Hk, Hv, Kd, Vd)
+        torch.cuda.synchronize()
+        mc = ref.causal_conv1d(mixed.cpu(), conv_w.cpu(), None, cs_c, qsl.cpu(), slots.cpu(), hi.cpu())
+        qq, kk, vv = mc[:, : Hk * Kd].reshape(T, Hk, Kd), mc[:, Hk * Kd: 2 * Hk * Kd].reshape(T, Hk, Kd), mc[:, 2 * Hk * Kd:].reshape(T, Hv, Vd)
+        gg, beta = ref.gdn_gating(ba[:, Hv:].cpu(), ba[:, :Hv].cpu(), A_log.cpu(), dt_bias.cpu())
+        oe = ref.gated_delta_rule(qq, kk, vv, gg, beta, ssm_c, qsl.cpu(), slots.cpu(), hi.cpu())
+        _close(o.view(T, Hv, Vd), oe, 3e-2, 3e-2, f"gdn out {qlens}")
+        _close(conv_state, cs_c, 1e-2, 1e-2, "conv state")
+        _close(ssm[slots.long()], ssm_c[slots.long().cpu()], 3e-2, 3e-2, "recurrent state")
+    assert K().check_status() == 0
+
+
+@pytest.mark.parametrize("deepseek", [False, True])
+def test_router_matches_reference(deepseek):
+    T, E, k = 77, 256, 8
+    logits = torch.randn(T, E, device="cuda").bfloat16()
+    from types import SimpleNamespace
+    if deepseek:
+        bias = torch.randn(E, device="cuda") * 0.1
+        cfg = SimpleNamespace(num_experts_per_tok=k, n_group=8, topk_group=4, scoring_func="sigmoid", norm_topk_prob=True, routed_scaling_factor=2.5)
+        w, ids = K().route(logits, cfg, bias)
+        we, ie = ref.grouped_topk(logits.float().cpu(), k, 8, 4, bias.cpu(), "sigmoid", True, 2.5)
+    else:
+        cfg = SimpleNamespace(num_experts_per_tok=k, n_group=1, topk_group=1, scoring_func="softmax", norm_topk_prob=True, routed_scaling_factor=1.0)
+        w, ids = K().route(logits, cfg, None)
+        we, ie = ref.topk_softmax(logits.float().cpu(), k, True)
+    assert "route" not in K().TORCH_STANDINS
+    same = (ids.cpu().sort(-1)[0] == ie.sort(-1)[0]).all(-1).float().mean()
+    assert same > 0.97, f"expert sets differ on {1 - float(same):.2%} of tokens"
+    rows = (ids.cpu().sort(-1)[0] == ie.sort(-1)[0]).all(-1)
+    wd = torch.zeros(T, E).scatter_(1, ids.cpu().long(), w.cpu())
+    wed = torch.zeros(T, E).scatter_(1, ie.long(), we)
+    _close(wd[rows], wed[rows], 2e-2, 1e-3, "routing weights")
+
+
+def test_rejection_sampler_kernel():
+    from onecat_vllm.sample.metadata import SamplingMetadata
+    from onecat_vllm.sample.rejection_sampler import RejectionSampler
+    B, k, V = 64, 3, 4096
+
+    def md(greedy):
+        m = SamplingMetadata(temperature=None if greedy else torch.ones(B, device="cuda"), all_greedy=greedy, all_random=not greedy, top_p=None, top_k=None,
+                             min_p=None, generators={}, max_num_logprobs=None, no_penalties=True)
+        return m
+    tl = torch.randn(B, k + 1, V, device="cuda").bfloat16()
+    am = tl.float().argmax(-1)
+    draft = am[:, :k].clone()
+    draft[::2, 1] = (draft[::2, 1] + 1) % V  # every other request: second draft wrong
+    bonus = torch.full((B,), 7, device="cuda")
+    out = RejectionSampler()(draft, torch.full((B,), k, device="cuda"), tl, bonus, md(True))
+    parsed = RejectionSampler.parse_output(out)
+    for b in range(B):
+        exp = [int(am[b, 0]), int(am[b, 1])] if b % 2 == 0 else [int(am[b, 0]), int(am[b, 1]), int(am[b, 2]), 7]
+        assert parsed[b] == exp, (b, parsed[b], exp)
+    assert "rejection_sample" not in K().TORCH_STANDINS
+    # random mode: acceptance probability of a point-mass draft equals its target probability
+    p = torch.tensor([0.6, 0.3, 0.1] + [0.0] * (V - 3), device="cuda").clamp_min(1e-9)
+    tl2 = torch.log(p).view(1, 1, V).repeat(4096, 2, 1).float()
+    d2 = torch.zeros(4096, 1, dtype=torch.long, device="cuda")
+    m2 = SamplingMetadata(temperature=torch.ones(4096, device="cuda"), all_greedy=False, all_random=True, top_p=None, top_k=None, min_p=None, generators={},
+                          max_num_logprobs=None, no_penalties=True)
+    o2 = RejectionSampler(seed=5)(d2, torch.ones(4096, dtype=torch.long, device="cuda"), tl2, torch.full((4096,), 2, device="cuda"), m2)
+    first = o2[:, 0].cpu()
+    freq = torch.bincount(first, minlength=3)[:3].float() / 4096
+    assert torch.allclose(freq, torch.tensor([0.6, 0.3, 0.1]), atol=0.04), freq
+    # synthetic acceptance
+    rs = RejectionSampler(synthetic_rates=[0.7, 0.7, 0.7], seed=3)
+    o3 = rs(draft, torch.full((B,), k, device="cuda"), tl, bonus, md(True))
+    lens = torch.tensor([len(r) for r in RejectionSampler.parse_output(o3)]).float()
+    assert 1.8 < lens.mean() < 3.3

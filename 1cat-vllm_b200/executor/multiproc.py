@@ -32,7 +32,18 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _worker_main(cfg: VllmConfig, rank: int, local_rank: int, init_method: str, rpc_conn, death_conn, ready_conn) -> None:
+def _load_native():
+    try:
+        from onecat_vllm.utils import _native
+        return _native
+    except ImportError:
+        return None
+
+
+_VIA_PIPE = b"\x00PIPE"
+
+
+def _worker_main(cfg: VllmConfig, rank: int, local_rank: int, init_method: str, rpc_conn, death_conn, ready_conn, ring_spec=None) -> None:
     decorate_logs(f"Worker_{rank}")
     signal.signal(signal.SIGINT, signal.SIG_IGN)
 
@@ -53,9 +64,19 @@ def _worker_main(cfg: VllmConfig, rank: int, local_rank: int, init_method: str, 
     except Exception:
         ready_conn.send(("FAILED", traceback.format_exc()))
         return
+    ring = None
+    if ring_spec is not None:
+        name, n, chunks, chunk_bytes = ring_spec
+        ring = _load_native().ShmRing(name, n, chunks, chunk_bytes, False)
     while True:
         try:
-            msg = rpc_conn.recv()
+            if ring is None:
+                msg = rpc_conn.recv()
+            else:  # broadcast arrives on the shared-memory ring; oversized messages fall back to the pipe
+                raw = ring.read(rank, 500.0)
+                if raw is None:
+                    continue
+                msg = rpc_conn.recv() if raw == _VIA_PIPE else pickle.loads(raw)
         except EOFError:
             break
         if msg is None:
@@ -84,11 +105,16 @@ class MultiprocExecutor(Executor):
         init_method = f"tcp://127.0.0.1:{_free_port()}"
         self.procs, self.conns, self._death = [], [], []
         readies = []
+        self.ring, ring_spec = None, None
+        native = _load_native()
+        if native is not None:
+            ring_spec = (f"/onecat-rpc-{os.getpid()}-{id(self) & 0xffff:x}", ws, envs.ONECAT_RPC_RING_CHUNKS, envs.ONECAT_RPC_RING_CHUNK_BYTES)
+            self.ring = native.ShmRing(ring_spec[0], ws, ring_spec[2], ring_spec[3], True)
         for r in range(ws):
             parent, child = ctx.Pipe()
             d_r, d_w = ctx.Pipe(duplex=False)
             rd_r, rd_w = ctx.Pipe(duplex=False)
-            p = ctx.Process(target=_worker_main, args=(cfg, r, r, init_method, child, d_r, rd_w), daemon=True, name=f"onecat-worker-{r}")
+            p = ctx.Process(target=_worker_main, args=(cfg, r, r, init_method, child, d_r, rd_w, ring_spec), daemon=True, name=f"onecat-worker-{r}")
             p.start()
             child.close()
             d_r.close()
@@ -134,8 +160,7 @@ class MultiprocExecutor(Executor):
             import cloudpickle
             method = cloudpickle.dumps(method)
         timeout = timeout or envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS
-        for c in self.conns:
-            c.send((method, args, kwargs or {}, True))
+        self._broadcast((method, args, kwargs or {}, True))
         out = []
         deadline = time.time() + timeout
         for r, c in enumerate(self.conns):
@@ -151,13 +176,30 @@ class MultiprocExecutor(Executor):
             out.append(res)
         return out
 
+    def _broadcast(self, msg) -> None:
+        if self.ring is None:
+            for c in self.conns:
+                c.send(msg)
+            return
+        raw = pickle.dumps(msg, protocol=pickle.HIGHEST_PROTOCOL)
+        if len(raw) <= self.ring.chunk_bytes:
+            if not self.ring.write(raw, 30000.0):
+                self.is_failed = True
+                raise RuntimeError("a worker stopped consuming the RPC ring")
+            return
+        if not self.ring.write(_VIA_PIPE, 30000.0):
+            self.is_failed = True
+            raise RuntimeError("a worker stopped consuming the RPC ring")
+        for c in self.conns:
+            c.send(msg)
+
     def shutdown(self) -> None:
         self._stop = True
-        for c in getattr(self, "conns", []):
-            try:
-                c.send(None)
-            except Exception:
-                pass
+        try:
+            if getattr(self, "procs", None):
+                self._broadcast(None)
+        except Exception:
+            pass
         for p in getattr(self, "procs", []):
             p.join(timeout=5)
             if p.is_alive():
@@ -169,3 +211,4 @@ class MultiprocExecutor(Executor):
             except Exception:
                 pass
         self.procs, self.conns = [], []
+        self.ring = None

@@ -214,9 +214,13 @@ def main() -> None:
         if args.layers:
             res["invalid"] = "reduced layer count (debug run)"
         print(json.dumps(res))
+    sys.stdout.flush()
+    torch.cuda.synchronize()
+    if world > 1:
+        # every rank has finished its timed work and rank 0 has printed: leave without the collective teardown, which can
+        # block on communicators that were captured into CUDA graphs
+        os._exit(0)
     eng.shutdown()
-    if world > 1 and dist.is_initialized():
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -301,12 +301,15 @@ def test_router_matches_reference(deepseek):
         w, ids = K().route(logits, cfg, None)
         we, ie = ref.topk_softmax(logits.float().cpu(), k, True)
     assert "route" not in K().TORCH_STANDINS
-    same = (ids.cpu().sort(-1)[0] == ie.sort(-1)[0]).all(-1).float().mean()
-    assert same > 0.97, f"expert sets differ on {1 - float(same):.2%} of tokens"
+    # bf16 logits contain exact ties, and torch.topk does not promise which tied expert it returns: compare the selected
+    # weights as multisets everywhere, and the expert ids on the rows where both picked the same set
+    _close(w.cpu().sort(-1)[0], we.sort(-1)[0], 2e-2, 1e-3, "sorted routing weights")
     rows = (ids.cpu().sort(-1)[0] == ie.sort(-1)[0]).all(-1)
+    assert rows.float().mean() > 0.85
     wd = torch.zeros(T, E).scatter_(1, ids.cpu().long(), w.cpu())
     wed = torch.zeros(T, E).scatter_(1, ie.long(), we)
     _close(wd[rows], wed[rows], 2e-2, 1e-3, "routing weights")
+    assert (ids >= 0).all() and (ids < E).all() and all(len(set(r)) == k for r in ids.cpu().tolist())
 
 
 def test_rejection_sampler_kernel():

@@ -531,3 +531,54 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
 unsigned int gemm_read_status(bool clear) { return read_status_tu(clear); }
 
 }  // namespace oc
+
+// ---- allocation-free entry point (see gemm_noalloc.h) -----------------------------------------------------------------
+#include "gemm_noalloc.h"
+
+namespace {
+// Split-K scratch living in the library image: 16 MiB of fp32 partial tiles followed by 1024 tile counters.
+// In host code this name is only a handle for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) unsigned char g_noalloc_scratch[ONECAT_NOALLOC_SCRATCH_BYTES];
+constexpr size_t kNoallocPartialBytes = 16u << 20;
+constexpr int kNoallocMaxTiles = 1024;
+constexpr int kNoallocMaxDevices = 64;
+void* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+}  // namespace
+
+extern "C" int onecat_gemm_bf16_splitk_noalloc(const void* x, const void* w, void* out, int T, int N, int K, int ldx, int ldw, int ldo,
+                                               int splits, cudaStream_t stream) {
+  using namespace oc;
+  if (x == nullptr || w == nullptr || out == nullptr || T <= 0 || N <= 0 || K <= 0 || K % 64 != 0 || splits < 1) return ONECAT_NOALLOC_BAD_ARGUMENT;
+  if (((uintptr_t)x & 15) || ((uintptr_t)w & 15) || ((uintptr_t)out & 15) || (ldx % 8) || (ldw % 8) || ldx < K || ldw < K || ldo < N)
+    return ONECAT_NOALLOC_BAD_ARGUMENT;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return ONECAT_NOALLOC_SETUP_FAILED;
+  int sms = 0;
+  if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return ONECAT_NOALLOC_SETUP_FAILED;
+  if (g_noalloc_ptr[dev] == nullptr) {  // first call on this device (it is the current one): resolve the array's device address
+    void* ptr = nullptr;
+    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return ONECAT_NOALLOC_SETUP_FAILED;
+    g_noalloc_ptr[dev] = ptr;
+  }
+  unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
+  GemmParams p{};
+  p.T = T; p.N = N; p.K = K; p.n_rows = N; p.n_out = N; p.n_pad = 0; p.epi = EPI_STORE; p.group_ktiles = 1;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.ldo = ldo;
+  p.bias = nullptr;
+  p.ws = reinterpret_cast<float*>(base);
+  p.ws_bytes = kNoallocPartialBytes;
+  p.counters = reinterpret_cast<int*>(base + kNoallocPartialBytes);
+  p.max_counters = kNoallocMaxTiles;
+  p.w4 = nullptr; p.w4_sz = nullptr;
+  gemm_plan(p, sms, false);
+  const int ktiles = K / 64;
+  p.splits = splits;
+  p.ktiles_per_split = (ktiles + splits - 1) / splits;
+  if ((splits - 1) * p.ktiles_per_split >= ktiles) return ONECAT_NOALLOC_BAD_ARGUMENT;  // an empty split
+  const size_t tiles = (size_t)p.num_t_tiles * p.num_n_tiles;
+  if (tiles > (size_t)kNoallocMaxTiles || tiles * splits * 128 * p.tn * 4 > kNoallocPartialBytes) return ONECAT_NOALLOC_TOO_LARGE;
+  if (splits > 1 && cudaMemsetAsync(p.counters, 0, tiles * sizeof(int), stream) != cudaSuccess) return ONECAT_NOALLOC_LAUNCH_FAILED;
+  const int rc = gemm_launch(p, x, ldx, w, ldw, sms, stream);
+  return rc == 0 ? 0 : ONECAT_NOALLOC_LAUNCH_FAILED;
+}

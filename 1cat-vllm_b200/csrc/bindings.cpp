@@ -26,7 +26,8 @@ void check_bf16(const torch::Tensor& t, const char* name) {
 // out[T, n_out or N] = epilogue(X[T,K] @ W^T). Exactly one of `w` (bf16 [n_rows, K]) and `w4` (packed tiles) is given.
 void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> w4, c10::optional<torch::Tensor> w4_sz,
           torch::Tensor out, c10::optional<torch::Tensor> bias, torch::Tensor ws, torch::Tensor counters, int64_t N, int64_t n_rows,
-          int64_t n_out, int64_t n_pad, int64_t epi, int64_t group_ktiles, int64_t force_splits, int64_t force_tn) {
+          int64_t n_out, int64_t n_pad, int64_t epi, int64_t group_ktiles, int64_t force_splits, int64_t force_tn,
+          std::vector<int64_t> push_dst, int64_t push_rows) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1, "x/out must be row-major 2-D");
@@ -67,6 +68,10 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
     wptr = w->data_ptr();
     ldw = (int)w->stride(0);
   }
+  TORCH_CHECK(push_dst.size() <= 8 && (push_dst.empty() || epi == oc::EPI_STORE), "push needs the plain store epilogue and at most 8 destinations");
+  p.n_push = (int)push_dst.size();
+  p.push_rows = (int)push_rows;
+  for (size_t i = 0; i < push_dst.size(); ++i) p.push_dst[i] = (__nv_bfloat16*)(uintptr_t)push_dst[i];
   oc::gemm_plan(p, sm_count(), w4.has_value());
   if (force_tn > 0) {
     TORCH_CHECK(!w4.has_value() || force_tn <= 192, "4-bit weights support token tiles up to 192");

@@ -66,6 +66,18 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t w, uint32_t zb2, uint32_t s
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
+// Output element store with optional tensor-parallel push (see GemmParams::push_dst).
+__device__ __forceinline__ void store_out(const GemmParams& p, int t, int n, __nv_bfloat16 v) {
+  const size_t off = (size_t)t * p.ldo + n;
+  if (p.n_push == 0) {
+    p.out[off] = v;
+  } else if (p.push_rows > 0) {
+    p.push_dst[t / p.push_rows][off] = v;
+  } else {
+    for (int d = 0; d < p.n_push; ++d) p.push_dst[d][off] = v;
+  }
+}
+
 template <int WKIND>
 __global__ void __launch_bounds__(Roles<WKIND>::kThreads, 1)
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
@@ -357,10 +369,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               int t = t0 + c + j;
-              if (t < p.T && n < p.N) p.out[(size_t)t * p.ldo + n] = __float2bfloat16(a[j] + b);
+              if (t < p.T && n < p.N) store_out(p, t, n, __float2bfloat16(a[j] + b));
             }
           }
         }
+        if (p.n_push > 0) __threadfence_system();
         continue;
       }
       // ---- single-pass epilogue
@@ -388,10 +401,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             int t = t0 + c + j;
-            if (t < p.T && n < p.N) p.out[(size_t)t * p.ldo + n] = __float2bfloat16(__uint_as_float(v[j]) + b);
+            if (t < p.T && n < p.N) store_out(p, t, n, __float2bfloat16(__uint_as_float(v[j]) + b));
           }
         }
       }
+      if (p.n_push > 0) __threadfence_system();  // peers will read these rows after this rank's next kernel raises its flag
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);

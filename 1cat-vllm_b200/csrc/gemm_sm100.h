@@ -21,6 +21,11 @@ struct GemmParams {
   __nv_bfloat16* out;
   int ldo;
   const __nv_bfloat16* bias;
+  // Tensor-parallel push (row-parallel layers): when n_push > 0 the epilogue stores each output row into peer GPUs' slabs instead
+  // of `out`: push_rows == 0 -> every row goes to all n_push destinations (one-shot reduction follows); push_rows > 0 -> row t goes
+  // only to destination t / push_rows (its owner in the reduce-scatter). Destinations are [T][ldo] bf16 like `out`.
+  __nv_bfloat16* push_dst[8];
+  int n_push, push_rows;
   float* ws;          // split-K workspace
   size_t ws_bytes;
   int* counters;      // one per output tile, zero between launches

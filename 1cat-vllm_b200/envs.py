@@ -35,6 +35,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # kernels
     "ONECAT_GEMM_BACKEND": _s("ONECAT_GEMM_BACKEND", "tcgen05"),  # "tcgen05" | "library" (debug only)
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
+    "ONECAT_TP_PUSH": _s("ONECAT_TP_PUSH", "auto"),  # GEMM epilogue pushes partial tiles to peers: auto | always | never
     "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),
     "ONECAT_USE_CUDA_GRAPH": _b("ONECAT_USE_CUDA_GRAPH", True),
     "ONECAT_COMPUTE_NANS_IN_LOGITS": _b("ONECAT_COMPUTE_NANS_IN_LOGITS", False),

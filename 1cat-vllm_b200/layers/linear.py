@@ -321,5 +321,11 @@ class RowParallelLinear(LinearBase):
             from onecat_vllm.parallel.tp_ops import row_parallel_out
             out = row_parallel_out(x.shape[0], self.out_features, x.dtype, x.device)
             if out is not None and not K._LIB_GEMM:
-                return K.linear(self, x, out=out)  # partial sums land in the symmetric slab
+                # the GEMM epilogue stores its tiles straight into the peers' slabs (reduce-scatter fused into the GEMM)
+                fused = get_state().fused
+                if fused.use_push(x.shape[0]):
+                    y = K.linear(self, x, out=out, push=fused.push_spec(x.shape[0]))
+                    y._tp_pushed = True
+                    return y
+                return K.linear(self, x, out=out)  # partial sums stay in this rank's slot; the reduction pulls them
         return self.method.apply(self, x)

@@ -156,10 +156,12 @@ def _swap_to_dense(layer, w: torch.Tensor) -> None:
 
 
 # ----------------------------------------------------------------------------- GEMM
-def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0):
+def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0, push=None):
+    """``push`` = (list of destination addresses, rows per owner): tensor-parallel epilogue that stores into peers' slabs."""
     global _LAUNCHES
     ws = workspace(x.device)
-    _C.gemm(x, w, w4, sz, out, bias, ws.splitk, ws.counters, N, n_rows, n_out, n_pad, epi, gk, force_splits, force_tn)
+    _C.gemm(x, w, w4, sz, out, bias, ws.splitk, ws.counters, N, n_rows, n_out, n_pad, epi, gk, force_splits, force_tn,
+            push[0] if push else [], push[1] if push else 0)
     _LAUNCHES += 1
     return out
 
@@ -177,7 +179,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = N
     return _gemm(x, w, None, None, out, bias, N, N, N, 0, EPI_STORE, 1, force_splits, force_tn)
 
 
-def linear(layer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear(layer, x: torch.Tensor, out: Optional[torch.Tensor] = None, push=None) -> torch.Tensor:
     ks = layer.kernel_state
     if ks is None:
         prepare_bf16(layer)
@@ -191,14 +193,14 @@ def linear(layer, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.
     if ks["kind"] == "w4":
         if _LIB_GEMM:
             raise RuntimeError("the library GEMM debug switch does not cover 4-bit weights")
-        return _gemm(x, None, ks["tiles"], ks["sz"], out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], ks["n_pad"], ks["epi"], ks["group_ktiles"])
+        return _gemm(x, None, ks["tiles"], ks["sz"], out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], ks["n_pad"], ks["epi"], ks["group_ktiles"], push=push)
     if _LIB_GEMM:
         y = torch.nn.functional.linear(x, layer.weight, bias)
         if ks["epi"] == EPI_SILU_MUL:  # rows are interleaved in blocks of 16
             y = y.view(T, -1, 2, 16)
             return (torch.nn.functional.silu(y[:, :, 0].float()) * y[:, :, 1].float()).to(x.dtype).reshape(T, -1)
         return y
-    return _gemm(x, layer.weight, None, None, out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], 0, ks["epi"], 1)
+    return _gemm(x, layer.weight, None, None, out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], 0, ks["epi"], 1, push=push)
 
 
 # ----------------------------------------------------------------------------- elementwise

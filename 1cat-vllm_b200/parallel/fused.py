@@ -4,7 +4,8 @@ Each rank cudaMallocs one slab and maps every peer's slab through CUDA IPC handl
 group (reference: the IPC buffer set-up of vllm/distributed/device_communicators/custom_all_reduce.py:100-261,726-759).
 Slab layout, identical on every rank:
 
-    part[0], part[1]    bf16 [Tmax, H]   where row-parallel GEMMs write their partial sums (alternating per reduction)
+    part[parity][src]   bf16 [Tmax, H]   partial sums of source rank ``src``, written into this slab by that rank's GEMM epilogue
+                                         (every rank for decode-sized batches, only the rows this rank owns for large ones)
     gather[0], gather[1] bf16 [Tmax, H]  two-shot mode: normalised rows pushed here by their owner ranks
     flags               int32 [2][2][tp][1024]   (parity, stage, source rank, CTA)
 
@@ -31,9 +32,9 @@ class FusedTP:
         self.tp, self.rank, self.device, self.tmax, self.H = tp, rank, device, tmax, hidden
         buf = tmax * hidden * 2
         buf = -(-buf // 256) * 256
-        self.off_part = [0, buf]
-        self.off_gather = [2 * buf, 3 * buf]
-        self.off_flags = 4 * buf
+        self.off_part = [[(par * tp + src) * buf for src in range(tp)] for par in range(2)]
+        self.off_gather = [2 * tp * buf, (2 * tp + 1) * buf]
+        self.off_flags = (2 * tp + 2) * buf
         self.flag_bytes = 2 * 2 * tp * _MAXB * 4
         self.bytes = self.off_flags + self.flag_bytes
         self.base = _C.comm_alloc(self.bytes)
@@ -62,27 +63,47 @@ class FusedTP:
         return self._C.comm_tensor(self.peers[rank], off, [T, H], 0, self.device.index or 0)
 
     def partial_buffer(self, T: int, H: int, dtype) -> Optional[torch.Tensor]:
+        """This rank's own slot for the current reduction (what a GEMM without the push epilogue writes to)."""
         if H != self.H or T > self.tmax or dtype != torch.bfloat16:
             return None
-        return self._tensor(self.rank, self.off_part[self.parity], T, H)
+        return self._tensor(self.rank, self.off_part[self.parity][self.rank], T, H)
+
+    def use_push(self, T: int) -> bool:
+        """Whether the GEMM epilogue should push its tiles to the peers (overlapping the transfer with the GEMM) or leave them
+        local for the reduction kernel to pull. The epilogue's 64-byte row segments are a poor fit for NVLink at prefill sizes,
+        so by default only decode-sized batches push. ``ONECAT_TP_PUSH`` = always | never | auto."""
+        mode = envs.ONECAT_TP_PUSH
+        return mode == "always" or (mode == "auto" and T <= 128)
+
+    def push_spec(self, T: int):
+        """Destinations for a row-parallel GEMM epilogue: slot ``[parity][my rank]`` in every rank's slab. Decode-sized batches go to
+        all ranks (each reduces everything itself); large ones send each row only to the rank that owns it."""
+        off = self.off_part[self.parity][self.rank]
+        dst = [p + off for p in self.peers]
+        if self.mode_for(T) == ONE_SHOT:
+            return dst, 0
+        return dst, -(-T // self.tp)
 
     def _in_slab(self, t: torch.Tensor) -> bool:
-        p = t.data_ptr()
-        return self.base + self.off_part[self.parity] == p
+        return self.base + self.off_part[self.parity][self.rank] == t.data_ptr()
 
     def mode_for(self, T: int) -> int:
         return ONE_SHOT if T * (self.tp - 1) <= 512 or self.tp == 2 else TWO_SHOT
 
     # ---- the fused op
     def reduce_add_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], w: Optional[torch.Tensor], eps: float = 1e-6,
-                        gemma: bool = False, mode: Optional[int] = None):
+                        gemma: bool = False, mode: Optional[int] = None, pushed: bool = False):
         T, H = partial.shape
         assert H == self.H and T <= self.tmax, "shape outside the symmetric slab"
         par = self.parity
-        if not self._in_slab(partial):
-            self._tensor(self.rank, self.off_part[par], T, H).copy_(partial)
         mode = self.mode_for(T) if mode is None else mode
-        part = [p + self.off_part[par] for p in self.peers]
+        if pushed and mode == self.mode_for(T):
+            # every source's partial already sits in this rank's slab: the reduction reads local memory only
+            part = [self.base + self.off_part[par][src] for src in range(self.tp)]
+        else:
+            if not self._in_slab(partial):
+                self._tensor(self.rank, self.off_part[par][self.rank], T, H).copy_(partial)
+            part = [p + self.off_part[par][src] for src, p in enumerate(self.peers)]  # pull each source's own slot
         flags = [p + self.off_flags for p in self.peers]
         res_out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device) if residual is not None else None
         if mode == ONE_SHOT:

@@ -352,9 +352,94 @@ std::tuple<torch::Tensor, torch::Tensor> route(torch::Tensor logits, c10::option
   return {w, ids};
 }
 
+// Routed-expert path of one MoE layer: slots -> grouped GEMM (w13, SiLU*mul) -> grouped GEMM (w2) -> weighted combine.
+// w13: bf16 [E_local * 2I, H] with each expert's gate|up rows interleaved in blocks of 16; w2: bf16 [E_local * H, I].
+torch::Tensor fused_moe(torch::Tensor x, torch::Tensor w13, torch::Tensor w2, torch::Tensor topk_w, torch::Tensor topk_ids, int64_t E_local,
+                        int64_t e_off, torch::Tensor ws, torch::Tensor counters) {
+  check_bf16(x, "x");
+  check_bf16(w13, "w13");
+  check_bf16(w2, "w2");
+  TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && w13.is_contiguous() && w2.is_contiguous(), "bad layouts");
+  TORCH_CHECK(topk_ids.scalar_type() == torch::kInt32 && topk_ids.is_contiguous() && topk_w.scalar_type() == torch::kFloat32 && topk_w.is_contiguous(),
+              "routing tensors must be contiguous int32 ids / fp32 weights");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), H = (int)x.size(1), k = (int)topk_ids.size(1);
+  const int I2 = (int)(w13.size(0) / E_local), I = I2 / 2;
+  TORCH_CHECK(w13.size(1) == H && w2.size(0) == E_local * H && w2.size(1) == I, "expert weight shapes do not match");
+  TORCH_CHECK(I2 % 128 == 0 && H % 128 == 0 && H % 64 == 0 && I % 64 == 0, "expert dims must be multiples of 128 (rows) and 64 (k)");
+  auto y = torch::empty({T, H}, x.options());
+  if (T == 0) return y;
+  const int n_pairs = T * k;
+  const int avg = (n_pairs + (int)E_local - 1) / (int)E_local;
+  const int tn = avg <= 32 ? 32 : avg <= 64 ? 64 : avg <= 128 ? 128 : 256;
+  const int n1 = I2 / 128, n2 = H / 128;
+  const int max_tt = (n_pairs + tn - 1) / tn + (int)E_local;
+  auto iopt = x.options().dtype(torch::kInt32);
+  auto meta = torch::empty({3 * E_local + 8 + n_pairs}, iopt);
+  auto work = torch::empty({(int64_t)max_tt * (n1 + n2) * 4}, iopt);
+  auto xs = torch::empty({n_pairs, H}, x.options());
+  auto a1 = torch::empty({n_pairs, I}, x.options());
+  auto a2 = torch::empty({n_pairs, H}, x.options());
+  int* mp = meta.data_ptr<int>();
+  oc::MoePlanParams pp{};
+  pp.counts = mp; pp.offsets = mp + E_local; pp.cursor = mp + 2 * E_local + 1; pp.total_slots = mp + 3 * E_local + 1; pp.work_count = mp + 3 * E_local + 2;
+  int* slot_of = mp + 3 * E_local + 8;
+  pp.work1 = (int4*)work.data_ptr<int>();
+  pp.work2 = pp.work1 + (size_t)max_tt * n1;
+  TORCH_CHECK(((uintptr_t)pp.work2 & 15) == 0, "work list alignment");
+  pp.E = (int)E_local; pp.tn = tn; pp.n1 = n1; pp.n2 = n2;
+  int rc = oc::moe_prepare_launch(pp, topk_ids.data_ptr<int>(), n_pairs, k, (int)e_off, slot_of, x.data_ptr(), x.stride(0), xs.data_ptr(), H, cur_stream());
+  TORCH_CHECK(rc == 0, "moe prepare failed: ", rc);
+  auto run = [&](const torch::Tensor& in, const torch::Tensor& w, torch::Tensor& out, int Kd, int N, int n_out, int epi, const int4* wl, const int* cnt, int cap) {
+    oc::GemmParams p{};
+    p.T = n_pairs; p.K = Kd; p.N = N; p.n_rows = (int)w.size(0); p.n_out = n_out; p.epi = epi; p.group_ktiles = 1;
+    p.out = (__nv_bfloat16*)out.data_ptr(); p.ldo = (int)out.stride(0);
+    p.ws = nullptr; p.counters = (int*)counters.data_ptr(); p.max_counters = 0;
+    p.work = wl; p.work_count = cnt; p.work_capacity = cap;
+    p.tn = tn; p.num_t_tiles = 1; p.num_n_tiles = 1; p.splits = 1; p.ktiles_per_split = Kd / 64;
+    oc::gemm_plan_stages(p, false);
+    int r = oc::gemm_launch(p, in.data_ptr(), (int)in.stride(0), w.data_ptr(), (int)w.stride(0), sm_count(), cur_stream());
+    TORCH_CHECK(r == 0, "grouped gemm launch failed: ", r);
+  };
+  run(xs, w13, a1, H, I2, I, oc::EPI_SILU_MUL, pp.work1, pp.work_count, max_tt * n1);
+  run(a1, w2, a2, I, H, H, oc::EPI_STORE, pp.work2, pp.work_count + 1, max_tt * n2);
+  rc = oc::moe_combine_launch(a2.data_ptr(), slot_of, topk_w.data_ptr<float>(), y.data_ptr(), T, k, H, cur_stream());
+  TORCH_CHECK(rc == 0, "moe combine failed");
+  return y;
+}
+
+torch::Tensor mla_decode(torch::Tensor q_abs, torch::Tensor q_rope, torch::Tensor cache, torch::Tensor qsl, torch::Tensor seq_lens,
+                         torch::Tensor block_table, double scale, int64_t max_q_len, int64_t splits, c10::optional<torch::Tensor> ws_o,
+                         c10::optional<torch::Tensor> ws_ml) {
+  check_bf16(q_abs, "q_abs");
+  check_bf16(q_rope, "q_rope");
+  check_bf16(cache, "latent cache");
+  TORCH_CHECK(q_abs.is_contiguous() && q_rope.is_contiguous() && cache.is_contiguous() && cache.dim() == 3, "q and cache must be contiguous");
+  const c10::cuda::CUDAGuard guard(q_abs.device());
+  oc::MlaParams p{};
+  p.T = (int)q_abs.size(0); p.H = (int)q_abs.size(1); p.kv_lora = (int)q_abs.size(2); p.rope = (int)q_rope.size(2);
+  TORCH_CHECK(cache.size(2) == p.kv_lora + p.rope, "cache width must be kv_lora + rope");
+  auto out = torch::empty({p.T, p.H, p.kv_lora}, q_abs.options());
+  p.q_abs = (const __nv_bfloat16*)q_abs.data_ptr(); p.q_rope = (const __nv_bfloat16*)q_rope.data_ptr();
+  p.cache = (const __nv_bfloat16*)cache.data_ptr(); p.out = (__nv_bfloat16*)out.data_ptr();
+  p.query_start_loc = qsl.data_ptr<int>(); p.seq_lens = seq_lens.data_ptr<int>(); p.block_table = block_table.data_ptr<int>();
+  p.bt_stride = (int)block_table.stride(0); p.R = (int)seq_lens.size(0);
+  p.bs = (int)cache.size(1); p.bs_shift = 0;
+  while ((1 << p.bs_shift) < p.bs) ++p.bs_shift;
+  p.max_q_len = (int)max_q_len; p.splits = (int)splits; p.scale = (float)scale;
+  if (splits > 1) {
+    TORCH_CHECK(ws_o.has_value() && ws_ml.has_value() && (size_t)ws_o->numel() >= (size_t)splits * p.T * p.H * p.kv_lora &&
+                (size_t)ws_ml->numel() >= (size_t)splits * p.T * p.H * 2, "split-KV workspace too small");
+    p.ws_o = ws_o->data_ptr<float>(); p.ws_ml = ws_ml->data_ptr<float>();
+  }
+  int rc = oc::mla_decode_launch(p, cur_stream());
+  TORCH_CHECK(rc == 0, "mla decode launch failed: ", rc, " (needs kv_lora 512, rope 64)");
+  return out;
+}
+
 int64_t read_status(bool clear) {
   return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) |
-                   oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear));
+                   oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear) | oc::moe_read_status(clear) | oc::mla_read_status(clear));
 }
 
 // ---- symmetric slab + peer-memory reductions
@@ -422,6 +507,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("paged_attention", &paged_attention);
   m.def("argmax", &argmax);
   m.def("read_status", &read_status);
+  m.def("mla_decode", &mla_decode);
+  m.def("fused_moe", &fused_moe);
   m.def("rejection_sample", &rejection_sample);
   m.def("route", &route);
   m.def("gdn_forward", &gdn_forward);

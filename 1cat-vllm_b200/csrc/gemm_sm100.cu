@@ -139,11 +139,21 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int total_work = p.num_n_tiles * p.num_t_tiles * p.splits;
+  // Work items. Dense: (n tile, token tile, k split) enumerated arithmetically. Grouped (mixture-of-experts): a device-built list of
+  // {weight row tile in the stacked expert matrix, first token row, number of valid rows, output column base}; its length is
+  // read from device memory, so the launch needs no host knowledge of how tokens were routed.
+  const int total_work = p.work != nullptr ? *p.work_count : p.num_n_tiles * p.num_t_tiles * p.splits;
   const int ktiles = p.K / BK;
-
-  // work item -> (n tile, t tile, split, k range)
   auto decode = [&](int w, int& nt, int& tt, int& sp_, int& k0, int& k1) {
+    if (p.work != nullptr) {
+      const int4 it = p.work[w];
+      nt = it.x;          // row tile of the stacked weights
+      tt = it.y;          // first token row (not a tile index in this mode)
+      sp_ = 0;
+      k0 = 0;
+      k1 = ktiles;
+      return;
+    }
     sp_ = w % p.splits;
     int tile = w / p.splits;
     tt = tile % p.num_t_tiles;
@@ -151,6 +161,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     k0 = sp_ * p.ktiles_per_split;
     k1 = min(k0 + p.ktiles_per_split, ktiles);
   };
+  const bool grouped = p.work != nullptr;
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -166,7 +177,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           ok = mbar_wait(&empty_x[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full_x[st.idx], bytes);
-          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, tt * tn, &full_x[st.idx]);
+          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, grouped ? tt : tt * tn, &full_x[st.idx]);
           if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full_x[st.idx]);
           st.advance(XS);
         }
@@ -311,8 +322,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + acc * p.acc_stride + ((uint32_t)(q * 32) << 16);
-      const int n = nt * BM + row;
-      const int t0 = tt * tn;
+      int n_base = nt * BM, t0 = tt * tn, t_end = p.T;
+      if (grouped) {
+        const int4 it = p.work[w];
+        t0 = it.y;
+        t_end = it.y + it.z;
+        n_base = it.w;
+      }
+      const int n = n_base + row;
       const int tile_id = nt * p.num_t_tiles + tt;
       if (p.splits > 1) {
         // fp32 partial -> workspace [tile][split][row][tn]
@@ -354,12 +371,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             }
           }
           if (p.epi == EPI_SILU_MUL) {
-            const int n_out = (nt * BM + q * 32) / 2 + (lane & 15);
+            const int n_out = (n_base + q * 32) / 2 + (lane & 15);
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               float other = __shfl_xor_sync(0xffffffffu, a[j], 16);
               int t = t0 + c + j;
-              if (!(lane & 16) && t < p.T && n_out < p.n_out) {
+              if (!(lane & 16) && t < t_end && n_out < p.n_out) {
                 float g = a[j];
                 p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(g / (1.f + __expf(-g)) * other);
               }
@@ -369,7 +386,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               int t = t0 + c + j;
-              if (t < p.T && n < p.N) store_out(p, t, n, __float2bfloat16(a[j] + b));
+              if (t < t_end && n < p.N) store_out(p, t, n, __float2bfloat16(a[j] + b));
             }
           }
         }
@@ -378,7 +395,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
       // ---- single-pass epilogue
       if (p.epi == EPI_SILU_MUL) {
-        const int n_out = (nt * BM + q * 32) / 2 + (lane & 15);
+        const int n_out = (n_base + q * 32) / 2 + (lane & 15);
         for (int c = 0; c < tn; c += 32) {
           uint32_t v[32];
           tmem_ld_32x32(taddr + c, v);
@@ -388,7 +405,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             float mine = __uint_as_float(v[j]);
             float other = __shfl_xor_sync(0xffffffffu, mine, 16);
             int t = t0 + c + j;
-            if (!(lane & 16) && t < p.T && n_out < p.n_out)
+            if (!(lane & 16) && t < t_end && n_out < p.n_out)
               p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(mine / (1.f + __expf(-mine)) * other);
           }
         }
@@ -401,7 +418,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             int t = t0 + c + j;
-            if (t < p.T && n < p.N) store_out(p, t, n, __float2bfloat16(__uint_as_float(v[j]) + b));
+            if (t < t_end && n < p.N) store_out(p, t, n, __float2bfloat16(__uint_as_float(v[j]) + b));
           }
         }
       }
@@ -522,7 +539,7 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   } else {
     tmW = tmX;
   }
-  int total = p.num_n_tiles * p.num_t_tiles * p.splits;
+  int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
   int grid = total < num_sms ? total : num_sms;
   int smem = gemm_smem_bytes(p.tn, p.xstages, p.stages, p.pstages);
   static int configured[2] = {0, 0};

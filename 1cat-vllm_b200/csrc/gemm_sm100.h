@@ -30,6 +30,9 @@ struct GemmParams {
   size_t ws_bytes;
   int* counters;      // one per output tile, zero between launches
   int max_counters;
+  const int4* work;         // grouped mode: device-built work items (see gemm_sm100.cu); null for a dense GEMM
+  const int* work_count;    // grouped mode: number of items, in device memory
+  int work_capacity;        // grouped mode: upper bound of the item count (sizes the grid)
   const uint8_t* w4;        // packed 4-bit tiles [n tile][k tile][4096 B]
   const uint32_t* w4_sz;    // [group][n_pad] : bf16 scale | bf16 (128 + zero) << 16
 };

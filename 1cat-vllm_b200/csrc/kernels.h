@@ -73,6 +73,37 @@ struct RouteParams {
 int route_launch(const RouteParams& p, cudaStream_t st);
 unsigned int sampling_read_status(bool clear);
 
+struct MoePlanParams {
+  int* counts;        // [E] scratch
+  int* offsets;       // [E+1] first slot of each local expert
+  int* cursor;        // [E] scratch
+  int* total_slots;   // [1]
+  int* work_count;    // [2] number of work items of the two grouped GEMMs
+  int4* work1;        // GEMM 1 items {row tile in stacked w13, first slot, valid rows, output column base}
+  int4* work2;        // GEMM 2 items (stacked w2)
+  int E, tn, n1, n2;  // local experts, token tile, 128-row tiles per expert in w13 / w2
+};
+int moe_prepare_launch(const MoePlanParams& p, const int* ids, int n_pairs, int k, int e_off, int* slot_of, const void* x, long long ldx,
+                       void* xs, int H, cudaStream_t st);
+int moe_combine_launch(const void* a2, const int* slot_of, const float* w, void* y, int T, int k, int H, cudaStream_t st);
+unsigned int moe_read_status(bool clear);
+
+struct MlaParams {
+  const __nv_bfloat16* q_abs;   // [T][H][512] query with W_UK absorbed
+  const __nv_bfloat16* q_rope;  // [T][H][64]
+  const __nv_bfloat16* cache;   // [blocks][bs][576] latent | rope key
+  __nv_bfloat16* out;           // [T][H][512]
+  const int* query_start_loc;
+  const int* seq_lens;
+  const int* block_table;
+  int bt_stride, R, T, H, kv_lora, rope, bs, bs_shift, max_q_len, splits;
+  float scale;
+  float* ws_o;                  // [splits][T][H][512]
+  float* ws_ml;                 // [splits][T][H][2]
+};
+int mla_decode_launch(const MlaParams& p, cudaStream_t st);
+unsigned int mla_read_status(bool clear);
+
 struct GdnConvParams {
   const __nv_bfloat16* x;   // [T][ldx] pre-conv mixed q|k|v (column slice allowed)
   long long ldx;

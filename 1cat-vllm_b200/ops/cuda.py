@@ -347,7 +347,28 @@ def gdn_commit(md, rec: list, n_valid: torch.Tensor) -> None:
 
 
 def prepare_moe(moe) -> None:
-    moe.kernel_state = None
+    """Stack the local experts for the grouped GEMM: ``w13`` → bf16 ``[E*2I, H]`` with each expert's gate|up rows interleaved in
+    blocks of 16 (SiLU·mul happens in the GEMM epilogue), ``w2`` → bf16 ``[E*H, I]``. Block-scaled FP8 / MXFP4 expert checkpoints
+    are expanded to bf16 here."""
+    w13, w2 = moe.dequantized()
+    E, I2, H = w13.shape
+    I = I2 // 2
+    if I2 % 128 or H % 128 or I % 64:
+        moe.kernel_state = None  # odd shapes take the device-side PyTorch path
+        return
+    perm = interleave_gate_up(I, w13.device)
+    w13s = w13.to(torch.bfloat16)[:, perm, :].reshape(E * I2, H).contiguous()
+    w2s = w2.to(torch.bfloat16).reshape(E * H, I).contiguous()
+    moe.kernel_state = dict(w13=w13s, w2=w2s)
+    moe._dq = None
+    if moe.qmethod != "none":
+        for n in ("w13", "w2", "w13_scale", "w2_scale"):
+            if hasattr(moe, n):
+                delattr(moe, n)
+    else:  # the stacked copies replace the originals
+        moe.w13 = torch.nn.Parameter(w13s.view(E, I2, H), requires_grad=False)
+        moe.w2 = torch.nn.Parameter(w2s.view(E, H, I), requires_grad=False)
+        moe.kernel_state = dict(w13=moe.w13.view(E * I2, H), w2=moe.w2.view(E * H, I))
 
 
 def route(logits, cfg, bias):
@@ -366,14 +387,34 @@ def route(logits, cfg, bias):
 
 
 def fused_moe(moe, x, topk_w, topk_ids):
-    TORCH_STANDINS.add("fused_moe")
-    w13, w2 = moe.dequantized()
-    return ref.fused_experts(x, w13, w2, topk_w, topk_ids, moe.e_off)
+    global _LAUNCHES
+    ks = moe.kernel_state
+    if ks is None:
+        TORCH_STANDINS.add("fused_moe")
+        w13, w2 = moe.dequantized()
+        return ref.fused_experts(x, w13, w2, topk_w, topk_ids, moe.e_off)
+    ws = workspace(x.device)
+    _LAUNCHES += 7
+    if x.stride(-1) != 1 or (x.stride(0) * 2) % 16:
+        x = x.contiguous()
+    return _C.fused_moe(x, ks["w13"], ks["w2"], topk_w.contiguous().float(), topk_ids.contiguous().to(torch.int32), moe.E_local, moe.e_off,
+                        ws.splitk, ws.counters)
 
 
 def mla_decode(q_abs, q_pe, latent_cache, md, scale, lora):
-    TORCH_STANDINS.add("mla_decode")
-    return ref.mla_decode(q_abs, q_pe, latent_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, lora)
+    global _LAUNCHES
+    T, H, _ = q_abs.shape
+    if lora != 512 or q_pe.shape[-1] != 64 or q_abs.dtype != torch.bfloat16:
+        TORCH_STANDINS.add("mla_decode")
+        return ref.mla_decode(q_abs, q_pe, latent_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, lora)
+    row_tiles = -(-md.max_query_len * H // 16)
+    splits = choose_kv_splits(md.num_reqs * row_tiles, max(md.seq_lens_cpu) if md.seq_lens_cpu else md.max_seq_len, _sms(q_abs.device))
+    ws_o = ws_ml = None
+    if splits > 1:
+        ws_o, ws_ml = workspace(q_abs.device).attn(splits * T * H * 512, splits * T * H * 2)
+    _LAUNCHES += 2 if splits > 1 else 1
+    return _C.mla_decode(q_abs.contiguous(), q_pe.contiguous(), latent_cache, md.query_start_loc, md.seq_lens, md.block_table, scale,
+                         md.max_query_len, splits, ws_o, ws_ml)
 
 
 _REJ_STEP = [0]

@@ -131,6 +131,50 @@ def bench_norm(rows: list, small: bool, iters: int, pk: dict) -> None:
         rows.append(dict(kernel="rms_norm_residual", T=T, H=H, ms=ms, gbs=b / ms / 1e6, frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"]))
 
 
+def bench_gdn(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    Hk, Hv, Kd, Vd, kw = 16, 48, 128, 128, 4
+    C = 2 * Hk * Kd + Hv * Vd
+    for name, R, ql in ([("decode", 64, 1)] if small else [("decode", 64, 1), ("decode", 8, 1), ("verify4", 8, 4), ("prefill", 4, 2048)]):
+        T = R * ql
+        mixed = (torch.randn(T, C, device="cuda") * 0.5).bfloat16()
+        ba = torch.randn(T, 2 * Hv, device="cuda").bfloat16()
+        conv_w = (torch.randn(C, kw, device="cuda") * 0.3).bfloat16()
+        A_log, dtb = torch.rand(Hv, device="cuda"), torch.rand(Hv, device="cuda")
+        conv_state = torch.zeros(R, C, kw - 1, device="cuda", dtype=torch.bfloat16)
+        ssm = torch.zeros(R, Hv, Kd, Vd, device="cuda")
+        qsl = torch.arange(R + 1, device="cuda", dtype=torch.int32) * ql
+        md = AttentionMetadata(R, T, qsl, None, None, None, None, ql, 0, state_slots=torch.arange(R, device="cuda", dtype=torch.int32),
+                               has_initial_state=torch.ones(R, device="cuda", dtype=torch.int32))
+        ms = timeit(lambda: K.gdn_forward(mixed, ba[:, :Hv], ba[:, Hv:], conv_w, A_log, dtb, conv_state, ssm, md, Hk, Hv, Kd, Vd), 1 if small else iters, 1 if small else 3)
+        state_bytes = 2 * R * Hv * Kd * Vd * 4
+        rows.append(dict(kernel="gdn_conv+recurrence", case=name, R=R, q_len=ql, ms=ms, state_gbs=state_bytes / ms / 1e6,
+                         frac_of_hbm=state_bytes / ms / 1e6 / pk["hbm_gbs"], tokens_per_s=T / ms * 1e3))
+
+
+def bench_moe(rows: list, small: bool, iters: int, pk: dict) -> None:
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.ops import ref
+    for T, E, k, H, I in ([(256, 256, 8, 2048, 512)] if small else [(256, 256, 8, 2048, 512), (8192, 256, 8, 2048, 512), (64, 256, 8, 2048, 512)]):
+        x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
+
+        class M:
+            pass
+        m = M()
+        m.qmethod, m.E_local, m.e_off, m._dq = "none", E, 0, None
+        m.w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.03).bfloat16()
+        m.w2 = (torch.randn(E, H, I, device="cuda") * 0.03).bfloat16()
+        m.dequantized = lambda: (m.w13, m.w2)
+        K.prepare_moe(m)
+        tw, ti = ref.topk_softmax(torch.randn(T, E, device="cuda"), k, True)
+        ms = timeit(lambda: K.fused_moe(m, x, tw, ti), 1 if small else iters, 1 if small else 3)
+        flops = 2.0 * T * k * 3 * H * I
+        wbytes = min(E, T * k) * 3 * H * I * 2
+        rows.append(dict(kernel="fused_moe(bf16 experts)", T=T, E=E, k=k, H=H, I=I, ms=ms, tflops=flops / ms / 1e9, frac_of_peak=flops / ms / 1e9 / pk["bf16_tflops"],
+                         weight_gbs=wbytes / ms / 1e6))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
@@ -140,7 +184,7 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm)):
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe)):
         if a.only and a.only != name:
             continue
         fn(rows, a.small, a.iters, pk)

@@ -347,3 +347,63 @@ def test_rejection_sampler_kernel():
     o3 = rs(draft, torch.full((B,), k, device="cuda"), tl, bonus, md(True))
     lens = torch.tensor([len(r) for r in RejectionSampler.parse_output(o3)]).float()
     assert 1.8 < lens.mean() < 3.3
+
+
+@pytest.mark.parametrize("T,E,k,e_off,E_local", [(1, 16, 2, 0, 16), (37, 16, 4, 0, 16), (300, 64, 8, 16, 32), (5, 256, 8, 0, 256)])
+def test_fused_moe_grouped_gemm(T, E, k, e_off, E_local):
+    """Grouped tcgen05 GEMMs over device-built work lists against per-expert fp32 FFNs; with e_off/E_local only a slice of the
+    experts is local and the rest of each token's routing contributes nothing (expert parallelism)."""
+    H, I = 256, 128
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = (torch.randn(T, H, device="cuda", generator=g) * 0.5).bfloat16()
+    w13 = (torch.randn(E_local, 2 * I, H, device="cuda", generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(E_local, H, I, device="cuda", generator=g) * 0.05).bfloat16()
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    tw, ti = ref.topk_softmax(logits, k, True)
+
+    class M:
+        pass
+    m = M()
+    m.qmethod, m.E_local, m.e_off, m._dq = "none", E_local, e_off, None
+    m.w13, m.w2 = w13.clone(), w2.clone()
+    m.dequantized = lambda: (m.w13, m.w2)
+    K().prepare_moe(m)
+    assert m.kernel_state is not None
+    y = K().fused_moe(m, x, tw, ti)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0 and "fused_moe" not in K().TORCH_STANDINS
+    e = ref.fused_experts(x.cpu(), w13.cpu(), w2.cpu(), tw.cpu(), ti.cpu(), e_off)
+    _close(y, e, 3e-2, 3e-3, f"moe T={T} E={E}")
+    y2 = K().fused_moe(m, x, tw, ti)
+    assert torch.equal(y, y2), "slot order varies between runs but the output must not"
+
+
+@pytest.mark.parametrize("name,qlens,ctxs,H", [("decode", [1, 1, 1, 1], [0, 70, 1000, 4100], 16), ("decode-128h", [1, 1], [300, 65], 128),
+                                               ("verify+prefill", [4, 37], [100, 0], 16)])
+def test_mla_decode(name, qlens, ctxs, H):
+    lora, rope, bs = 512, 64, 16
+    g = torch.Generator(device="cuda").manual_seed(2)
+    R = len(qlens)
+    seq = [c + q for q, c in zip(qlens, ctxs)]
+    nbp = [-(-s // bs) for s in seq]
+    total = sum(nbp) + 2
+    perm = torch.randperm(total, device="cuda", generator=g).to(torch.int32)
+    bt = torch.zeros(R, max(nbp) + 1, dtype=torch.int32, device="cuda")
+    o = 0
+    for r, n in enumerate(nbp):
+        bt[r, :n] = perm[o:o + n]
+        o += n
+    cache = (torch.randn(total, bs, lora + rope, device="cuda", generator=g) * 0.3).bfloat16()
+    T = sum(qlens)
+    q_abs = (torch.randn(T, H, lora, device="cuda", generator=g) * 0.3).bfloat16()
+    q_pe = (torch.randn(T, H, rope, device="cuda", generator=g) * 0.3).bfloat16()
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device="cuda")
+    sl = torch.tensor(seq, dtype=torch.int32, device="cuda")
+    md = AttentionMetadata(R, T, qsl, sl, bt, None, None, max(qlens), max(seq), query_lens_cpu=list(qlens), seq_lens_cpu=seq)
+    scale = (128 + 64) ** -0.5
+    out = K().mla_decode(q_abs, q_pe, cache, md, scale, lora)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0 and "mla_decode" not in K().TORCH_STANDINS
+    e = ref.mla_decode(q_abs.cpu(), q_pe.cpu(), cache.cpu(), bt.cpu(), qsl.cpu(), sl.cpu(), scale, lora)
+    _close(out, e, 2e-2, 5e-3, name)

@@ -378,6 +378,7 @@ class VllmConfig:
     observability_config: ObservabilityConfig = field(default_factory=ObservabilityConfig)
     device: str = "auto"  # auto | cuda | cpu
     enforce_eager: bool = False
+    structured_outputs_backend: str = "auto"  # auto | xgrammar | builtin
 
     def __post_init__(self) -> None:
         self.scheduler_config.max_model_len = self.model_config.max_model_len
@@ -431,6 +432,7 @@ class EngineArgs:
     otlp_traces_endpoint: Optional[str] = None
     disable_log_stats: bool = True
     hf_overrides: Optional[dict] = None
+    structured_outputs_backend: str = "auto"
 
     def create_engine_config(self) -> VllmConfig:
         dt = _DTYPES[self.dtype] if isinstance(self.dtype, str) else self.dtype
@@ -467,7 +469,7 @@ class EngineArgs:
                                              self.scheduling_policy, self.async_scheduling, self.cuda_graph_sizes),
             speculative_config=sc,
             observability_config=ObservabilityConfig(self.otlp_traces_endpoint, enable_metrics=not self.disable_log_stats),
-            device=device, enforce_eager=self.enforce_eager,
+            device=device, enforce_eager=self.enforce_eager, structured_outputs_backend=self.structured_outputs_backend,
         )
 
     # ---- argparse bridge (reference: arg_utils.py add_cli_args / from_cli_args)

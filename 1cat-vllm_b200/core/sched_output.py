@@ -3,7 +3,7 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Optional
+from typing import Any, Optional
 
 from onecat_vllm.sampling_params import SamplingParams
 
@@ -45,6 +45,8 @@ class SchedulerOutput:
     finished_req_ids: set = field(default_factory=set)
     preempted_req_ids: set = field(default_factory=set)
     num_common_prefix_blocks: int = 0
+    grammar_bitmask: Any = None  # numpy int32 [rows, ceil(vocab/32)], bit set = token allowed
+    structured_rows: dict[str, int] = field(default_factory=dict)  # request id -> row of grammar_bitmask
 
     @property
     def is_empty(self) -> bool:

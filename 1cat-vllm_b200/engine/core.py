@@ -35,6 +35,7 @@ class EngineCore:
         self.scheduler = Scheduler(vllm_config, num_blocks, num_slots, log_stats)
         self.step_count = 0
         self.paused = False
+        self._structured = None  # built on the first request that asks for a grammar
         log.info_once(f"engine core ready: {num_blocks} KV blocks, {num_slots} state slots, init {time.time() - t0:.1f}s")
 
     def _on_executor_failure(self) -> None:
@@ -42,9 +43,24 @@ class EngineCore:
 
     # ---- requests
     def add_request(self, req: EngineCoreRequest | Request) -> None:
+        sp = req.sampling_params
+        if sp is not None and sp.structured_outputs is not None and sp.structured_outputs.kind() != "none":
+            self.structured_output_manager().grammar_init(req.request_id, sp.structured_outputs)
         self.scheduler.add_request(req)
 
+    def structured_output_manager(self):
+        if self._structured is None:
+            from onecat_vllm.engine.tokenizer import get_tokenizer
+            from onecat_vllm.structured import StructuredOutputManager
+            mc = self.cfg.model_config
+            tok = get_tokenizer(mc.tokenizer)
+            self._structured = StructuredOutputManager(tok, mc.vocab_size, backend=self.cfg.structured_outputs_backend)
+        return self._structured
+
     def abort_requests(self, request_ids: list[str]) -> None:
+        if self._structured is not None:
+            for rid in request_ids:
+                self._structured.free(rid)
         self.scheduler.finish_requests(request_ids, RequestStatus.FINISHED_ABORTED)
 
     # ---- the step
@@ -55,6 +71,8 @@ class EngineCore:
         if not self.scheduler.has_requests() or self.paused:
             return {}, False
         so = self.scheduler.schedule()
+        if self._structured is not None and self._structured.grammars:
+            so.grammar_bitmask, so.structured_rows = self._structured.grammar_bitmask(list(so.num_scheduled_tokens))
         try:
             mro = self.executor.execute_model(so)
         except Exception as e:
@@ -66,6 +84,13 @@ class EngineCore:
             self._failed = True
             raise CollectiveTimeout(f"device wait expired (status {mro.status:#x})")
         outs = self.scheduler.update_from_output(so, mro)
+        if self._structured is not None and self._structured.grammars:
+            for eco in outs.values():
+                for o in eco.outputs:
+                    if self._structured.has(o.request_id):
+                        self._structured.accept_tokens(o.request_id, o.new_token_ids)
+                        if o.finished:
+                            self._structured.free(o.request_id)
         self.step_count += 1
         return outs, so.total_num_scheduled_tokens > 0
 

@@ -145,6 +145,8 @@ class Request:
         self.block_hashes: list[bytes] = []
         self._block_hasher = block_hasher
         self.events: list = []
+        so = sampling_params.structured_outputs if sampling_params is not None else None
+        self.use_structured_output = so is not None and so.kind() != "none"
         self.first_scheduled_time: Optional[float] = None
         if block_hasher is not None:
             self.block_hashes = block_hasher(self)

@@ -369,6 +369,8 @@ class ModelRunner:
             sample_hidden = hidden[lidx]
             logits = self.model.compute_logits(sample_hidden)
             smd = self._sampling_metadata(req_ids, rows)
+            if so.grammar_bitmask is not None:
+                smd.grammar_bitmask = self._grammar_mask(so, req_ids, rows, logits.shape[-1])
             samp_rows = [k for k in rows if k > 0]
             if not spec_verify:
                 so_ = self.sampler(logits, smd)
@@ -409,6 +411,28 @@ class ModelRunner:
             from onecat_vllm.ops import cuda as K
             out.status = K.check_status()
         return out
+
+    def _grammar_mask(self, so: SchedulerOutput, req_ids: list, rows: list[int], vocab: int) -> torch.Tensor:
+        """Packed per-request words → bool ``[sampling requests, vocab]`` (True = allowed); requests without a grammar get
+        all-ones rows. Requests under a grammar never carry drafts, so their single logits row is the one the sampler
+        sees (reference: v1/structured_output/utils.py ``apply_grammar_bitmask``)."""
+        import numpy as np
+        n = sum(1 for k in rows if k > 0)
+        packed = np.full((n, so.grammar_bitmask.shape[1]), -1, dtype=np.int32)
+        o = 0
+        for rid, k in zip(req_ids, rows):
+            if k == 0:
+                continue
+            r = so.structured_rows.get(rid)
+            if r is not None:
+                packed[o] = so.grammar_bitmask[r]
+            o += 1
+        words = torch.from_numpy(packed).to(self.device, non_blocking=True)
+        shifts = torch.arange(32, device=self.device, dtype=torch.int32)
+        bits = ((words.unsqueeze(-1) >> shifts) & 1).bool().reshape(words.shape[0], -1)
+        if bits.shape[1] < vocab:  # logits rows padded beyond the tokenizer's vocabulary stay masked out
+            bits = torch.nn.functional.pad(bits, (0, vocab - bits.shape[1]), value=False)
+        return bits[:, :vocab]
 
     def _scatter_logprobs(self, lp, rows):
         if lp is None:

@@ -17,6 +17,7 @@ class NewRequestData:
     num_computed_tokens: int
     state_slot: int = -1
     eos_token_id: Optional[int] = None
+    pooling_params: Any = None
 
 
 @dataclass
@@ -70,6 +71,7 @@ class ModelRunnerOutput:
     logprobs: Optional[list[Optional[LogprobsLists]]] = None
     prompt_logprobs: Optional[dict] = None
     num_nans_in_logits: Optional[dict] = None
+    pooler_output: Optional[list] = None  # per request: pooled vector (list of floats) once its prompt is complete, else None
     device_time_ms: float = 0.0  # CUDA-event time of the step (0 when not measured)
     status: int = 0  # non-zero: a bounded device wait expired
 

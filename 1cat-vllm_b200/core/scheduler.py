@@ -259,7 +259,8 @@ class Scheduler:
         km = self.kv_cache_manager
         out.scheduled_new_reqs = [
             NewRequestData(r.request_id, r.prompt_token_ids, r.sampling_params, new_blocks_of[r.request_id],
-                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id) for r in scheduled_new]
+                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params)
+            for r in scheduled_new]
         cached = CachedRequestData()
         for r in scheduled_resumed + scheduled_running:
             resumed = r in scheduled_resumed
@@ -325,10 +326,11 @@ class Scheduler:
                 l = mro.logprobs[i]
                 lp = [(l.token_ids[k], l.logprobs[k], l.ranks[k]) for k in range(len(new_ids))]
             plp = mro.prompt_logprobs.get(rid) if mro.prompt_logprobs else None
+            pooled = mro.pooler_output[i] if mro.pooler_output is not None and i is not None else None
             if new_ids or plp is not None or stop:
                 outputs.setdefault(r.client_index, []).append(EngineCoreOutput(
                     rid, new_ids, r.get_finished_reason() if stop else None, r.stop_reason if stop else None, lp, plp,
-                    max(r.num_cached_tokens, 0)))
+                    max(r.num_cached_tokens, 0), pooling_output=pooled))
             if stop:
                 stopped.append(r)
         for r in stopped:

@@ -80,7 +80,7 @@ class AsyncLLM:
         self._ensure_handler()
         req, text = self.input_processor.process(request_id, prompt, params, None, priority)
         q: asyncio.Queue = asyncio.Queue()
-        n = params.n
+        n = getattr(params, "n", 1)
         if n == 1:
             self.output_processor.add_request(req, text, queue=q)
             await self.engine_core.add_request_async(req)
@@ -113,6 +113,18 @@ class AsyncLLM:
         except (asyncio.CancelledError, GeneratorExit):
             await self.abort(request_id)
             raise
+
+    async def encode(self, prompt: PromptType, pooling_params, request_id: str, priority: int = 0):
+        """Run one pooling request to completion and return its ``PoolingRequestOutput``."""
+        q = await self.add_request(request_id, prompt, pooling_params, priority)
+        try:
+            out = await q.get()
+        except asyncio.CancelledError:
+            await self.abort(request_id)
+            raise
+        if isinstance(out, BaseException):
+            raise EngineDeadError(str(out))
+        return out
 
     async def abort(self, request_id: str) -> None:
         ids = self.output_processor.abort([request_id])

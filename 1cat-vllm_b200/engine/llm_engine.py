@@ -37,7 +37,7 @@ class LLMEngine:
     def add_request(self, request_id: str, prompt: PromptType, params: SamplingParams, arrival_time: Optional[float] = None,
                     priority: int = 0) -> None:
         req, text = self.input_processor.process(request_id, prompt, params, arrival_time, priority)
-        n = params.n
+        n = getattr(params, "n", 1)
         if n == 1:
             self.output_processor.add_request(req, text)
             self.engine_core.add_request(req)

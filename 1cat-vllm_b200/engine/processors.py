@@ -13,9 +13,9 @@ from typing import Optional
 from onecat_vllm.config import VllmConfig
 from onecat_vllm.engine.tokenizer import IncrementalDetokenizer
 from onecat_vllm.inputs import PromptType, parse_prompt
-from onecat_vllm.outputs import CompletionOutput, Logprob, RequestMetrics, RequestOutput
+from onecat_vllm.outputs import CompletionOutput, Logprob, PoolingOutput, PoolingRequestOutput, RequestMetrics, RequestOutput
 from onecat_vllm.request import EngineCoreOutput, EngineCoreRequest, FinishReason
-from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
+from onecat_vllm.sampling_params import PoolingParams, RequestOutputKind, SamplingParams
 
 
 class InputProcessor:
@@ -37,6 +37,11 @@ class InputProcessor:
         bad = [t for t in ids if not 0 <= t < mc.vocab_size]
         if bad:
             raise ValueError(f"token id {bad[0]} is outside the vocabulary (size {mc.vocab_size})")
+        pooling = None
+        if isinstance(params, PoolingParams):
+            # an embedding request runs its prompt, "generates" one token that nobody reads, and returns the pooled state
+            pooling, params = params, SamplingParams(temperature=0.0, max_tokens=1, detokenize=False,
+                                                     output_kind=RequestOutputKind.FINAL_ONLY)
         sp = params.clone()
         if sp.max_tokens is None:
             sp.max_tokens = mc.max_model_len - len(ids)
@@ -48,7 +53,7 @@ class InputProcessor:
             sp.bad_words_token_ids = [self.tok.encode(w, add_special_tokens=False) for w in sp.bad_words]
         if sp.allowed_token_ids is not None and any(not 0 <= t < mc.vocab_size for t in sp.allowed_token_ids):
             raise ValueError("allowed_token_ids contains an id outside the vocabulary")
-        req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), None if sp.ignore_eos and False else eos, priority, salt)
+        req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling)
         return req, text
 
 
@@ -68,6 +73,7 @@ class _ReqState:
     sent_chars: int = 0
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
     queue: Optional[object] = None  # asyncio queue for streaming clients
+    pooling: bool = False
 
 
 class OutputProcessor:
@@ -83,6 +89,7 @@ class OutputProcessor:
                        IncrementalDetokenizer(self.tok if sp.detokenize else None, req.prompt_token_ids, sp.skip_special_tokens,
                                               sp.stop, sp.include_stop_str_in_output), req.arrival_time, queue=queue)
         st.metrics.arrival_time = req.arrival_time
+        st.pooling = req.pooling_params is not None
         if sp.logprobs is not None:
             st.logprobs = []
         self.states[req.request_id] = st
@@ -128,7 +135,11 @@ class OutputProcessor:
                             d[tid] = Logprob(lp, rank if j == 0 else j, self.tok.decode([tid]) if self.tok is not None else None)
                     st.logprobs.append(d)
                     st.cum_logprob += lps[0]
-            ro = self._make_output(st, finish, stop_reason, o.num_cached_tokens)
+            if st.pooling:
+                ro = PoolingRequestOutput(st.request_id, PoolingOutput(list(o.pooling_output or [])), st.prompt_ids, True) \
+                    if finish is not None else None
+            else:
+                ro = self._make_output(st, finish, stop_reason, o.num_cached_tokens)
             if finish is not None:
                 st.metrics.finished_time = now
                 self.finished_stats.append(st.metrics)

@@ -9,7 +9,8 @@ from onecat_vllm.config import EngineArgs
 from onecat_vllm.engine.llm_engine import LLMEngine
 from onecat_vllm.inputs import PromptType
 from onecat_vllm.outputs import RequestOutput
-from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
+from onecat_vllm.outputs import PoolingRequestOutput
+from onecat_vllm.sampling_params import PoolingParams, RequestOutputKind, SamplingParams
 
 
 class LLM:
@@ -49,6 +50,34 @@ class LLM:
         convs = messages if messages and isinstance(messages[0], list) else [messages]
         prompts = [tok.apply_chat_template(c, tokenize=False, add_generation_prompt=add_generation_prompt) for c in convs]
         return self.generate(prompts, sampling_params)
+
+    # ---- pooling tasks (reference: entrypoints/llm.py ``encode`` / ``embed`` / ``score``)
+    def encode(self, prompts: Union[PromptType, Sequence[PromptType]], pooling_params: Optional[PoolingParams] = None,
+               use_tqdm: bool = False) -> list[PoolingRequestOutput]:
+        if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
+            prompts = [prompts]
+        pp = pooling_params or PoolingParams(task="encode", normalize=False)
+        ids = []
+        for p in prompts:
+            rid = str(next(self._counter))
+            ids.append(rid)
+            self.llm_engine.add_request(rid, p, pp)
+        return self._run_engine(ids, use_tqdm)
+
+    def embed(self, prompts, pooling_params: Optional[PoolingParams] = None, use_tqdm: bool = False) -> list[PoolingRequestOutput]:
+        return self.encode(prompts, pooling_params or PoolingParams(task="embed", normalize=True), use_tqdm)
+
+    def score(self, text_1: Union[str, Sequence[str]], text_2: Union[str, Sequence[str]], use_tqdm: bool = False) -> list[float]:
+        """Cosine similarity of the two texts' embeddings (1:N or N:N)."""
+        a = [text_1] if isinstance(text_1, str) else list(text_1)
+        b = [text_2] if isinstance(text_2, str) else list(text_2)
+        if len(a) == 1:
+            a = a * len(b)
+        if len(a) != len(b):
+            raise ValueError("score() takes 1:N or N:N inputs")
+        embs = self.embed(a + b, use_tqdm=use_tqdm)
+        ea, eb = embs[: len(a)], embs[len(a):]
+        return [sum(x * y for x, y in zip(p.outputs.data, q.outputs.data)) for p, q in zip(ea, eb)]
 
     def _run_engine(self, ids: list[str], use_tqdm: bool = False) -> list[RequestOutput]:
         done: dict[str, RequestOutput] = {}

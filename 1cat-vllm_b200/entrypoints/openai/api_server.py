@@ -3,7 +3,8 @@ chat logic openai/chat_completion/serving.py; launcher + watchdog entrypoints/la
 
 Routes: ``/v1/chat/completions``, ``/v1/completions``, ``/v1/models``, ``/tokenize``, ``/detokenize``, ``/health``, ``/ping``,
 ``/version``, ``/metrics`` (Prometheus), ``/load``, ``/server_info``, ``/reset_prefix_cache``, ``/sleep``, ``/wake_up``,
-``/is_sleeping``, ``/start_profile``, ``/stop_profile``, ``/collective_rpc``. Streaming uses server-sent events."""
+``/is_sleeping``, ``/start_profile``, ``/stop_profile``, ``/collective_rpc``, ``/v1/embeddings``, ``/pooling``, ``/score``.
+Streaming uses server-sent events."""
 from __future__ import annotations
 
 import argparse
@@ -174,6 +175,68 @@ def build_app(state: ServingState) -> FastAPI:
     async def collective_rpc(body: dict):
         res = await state.engine.collective_rpc(body["method"], body.get("args", []), body.get("kwargs"))
         return {"results": res}
+
+    # ---- pooling: embeddings, raw pooled states, similarity scores (reference: entrypoints/pooling/*/api_router.py)
+    def _as_prompts(x):
+        if isinstance(x, str) or (isinstance(x, list) and x and isinstance(x[0], int)):
+            return [x]
+        return list(x)
+
+    async def _pool_many(prompts, pp, prefix: str):
+        rid = new_id(prefix)
+        prompts = [p if isinstance(p, str) else {"prompt_token_ids": p} for p in prompts]
+        return await asyncio.gather(*[state.engine.encode(p, pp, f"{rid}-{i}") for i, p in enumerate(prompts)])
+
+    @app.post("/v1/embeddings")
+    async def embeddings(body: dict):
+        from onecat_vllm.sampling_params import PoolingParams
+        try:
+            pp = PoolingParams(task="embed", normalize=body.get("normalize", True), dimensions=body.get("dimensions"),
+                               pooling_type=body.get("pooling_type", "last"))
+            outs = await _pool_many(_as_prompts(body["input"]), pp, "embd")
+        except (ValueError, KeyError) as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        fmt = body.get("encoding_format", "float")
+        data = []
+        for i, o in enumerate(outs):
+            emb = o.outputs.data
+            if fmt == "base64":
+                import base64
+                import struct
+                emb = base64.b64encode(struct.pack(f"<{len(emb)}f", *emb)).decode()
+            data.append({"index": i, "object": "embedding", "embedding": emb})
+        n = sum(len(o.prompt_token_ids) for o in outs)
+        return {"id": new_id("embd"), "object": "list", "created": now(), "model": body.get("model") or state.model_name, "data": data,
+                "usage": {"prompt_tokens": n, "total_tokens": n}}
+
+    @app.post("/pooling")
+    async def pooling(body: dict):
+        from onecat_vllm.sampling_params import PoolingParams
+        try:
+            pp = PoolingParams(task="encode", normalize=bool(body.get("normalize", False)), pooling_type=body.get("pooling_type", "last"))
+            outs = await _pool_many(_as_prompts(body["input"]), pp, "pool")
+        except (ValueError, KeyError) as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        return {"id": new_id("pool"), "object": "list", "created": now(), "model": state.model_name,
+                "data": [{"index": i, "object": "pooling", "data": o.outputs.data} for i, o in enumerate(outs)]}
+
+    @app.post("/score")
+    @app.post("/v1/score")
+    async def score(body: dict):
+        from onecat_vllm.sampling_params import PoolingParams
+        try:
+            a, b = _as_prompts(body["text_1"]), _as_prompts(body["text_2"])
+            if len(a) == 1:
+                a = a * len(b)
+            if len(a) != len(b):
+                raise ValueError("text_1 and text_2 must be 1:N or N:N")
+            outs = await _pool_many(a + b, PoolingParams(task="embed", normalize=True), "score")
+        except (ValueError, KeyError) as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        ea, eb = outs[: len(a)], outs[len(a):]
+        data = [{"index": i, "object": "score", "score": sum(x * y for x, y in zip(p.outputs.data, q.outputs.data))}
+                for i, (p, q) in enumerate(zip(ea, eb))]
+        return {"id": new_id("score"), "object": "list", "created": now(), "model": state.model_name, "data": data}
 
     # ---- completions
     @app.post("/v1/completions")

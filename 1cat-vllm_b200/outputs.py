@@ -72,6 +72,10 @@ class RequestOutput:
 class PoolingOutput:
     data: list[float] = field(default_factory=list)
 
+    @property
+    def embedding(self) -> list[float]:
+        return self.data
+
 
 @dataclass
 class PoolingRequestOutput:

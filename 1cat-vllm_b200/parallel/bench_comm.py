@@ -2,7 +2,7 @@
 
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m onecat_vllm.parallel.bench_comm [--json PATH]
 
-For each token count T it times (CUDA events on the launching stream, max over ranks, median of ``--iters`` after 5 warm-up rounds):
+For each token count T it times (CUDA events on the launching stream, max over ranks, median of ``--iters`` samples of ``--inner`` back-to-back calls each, after 5 warm-up rounds):
   * ``fused``  : peer-memory reduce + residual add + RMSNorm in one kernel (one-shot for small T, reduce-scatter/all-gather two-shot above)
   * ``nccl``   : ncclAllReduce followed by the fused add+RMSNorm kernel (the baseline path)
   * ``gemm+fused`` / ``gemm+push+fused`` : a row-parallel bf16 GEMM (K = 17408 / N ranks → 5120) followed by the reduction, with the
@@ -21,7 +21,8 @@ import torch.distributed as dist
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--inner", type=int, default=20)
     ap.add_argument("--json", default="")
     ap.add_argument("--hidden", type=int, default=5120)
     a = ap.parse_args()
@@ -39,6 +40,8 @@ def main() -> None:
     rows = []
 
     def timed(fn):
+        # `inner` back-to-back calls per sample: the ranks leave the barrier at slightly different times, and a single
+        # call would mostly measure that skew (each rank waits for the slowest one inside the collective)
         for _ in range(5):
             fn()
         torch.cuda.synchronize()
@@ -47,11 +50,13 @@ def main() -> None:
         for _ in range(a.iters):
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             dist.barrier()
+            torch.cuda.synchronize()
             e0.record()
-            fn()
+            for _ in range(a.inner):
+                fn()
             e1.record()
             torch.cuda.synchronize()
-            t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+            t = torch.tensor([e0.elapsed_time(e1) / a.inner], device=dev)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ts.append(float(t))
         ts.sort()

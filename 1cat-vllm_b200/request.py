@@ -59,14 +59,19 @@ class EngineCoreRequest:
         return {"request_id": self.request_id, "prompt_token_ids": self.prompt_token_ids,
                 "sampling_params": self.sampling_params.to_dict() if self.sampling_params else None,
                 "arrival_time": self.arrival_time, "eos_token_id": self.eos_token_id, "priority": self.priority,
-                "cache_salt": self.cache_salt, "client_index": self.client_index}
+                "cache_salt": self.cache_salt, "client_index": self.client_index,
+                "pooling_params": self.pooling_params.to_dict() if self.pooling_params is not None else None}
 
     @classmethod
     def from_wire(cls, d: dict) -> "EngineCoreRequest":
         sp = d.get("sampling_params")
+        pp = d.get("pooling_params")
+        if pp is not None:
+            from onecat_vllm.sampling_params import PoolingParams
+            pp = PoolingParams(**pp)
         return cls(d["request_id"], list(d["prompt_token_ids"]), SamplingParams.from_dict(sp) if sp else None,
                    d.get("arrival_time", 0.0), d.get("eos_token_id"), d.get("priority", 0), d.get("cache_salt"),
-                   d.get("client_index", 0))
+                   d.get("client_index", 0), pooling_params=pp)
 
 
 @dataclass
@@ -81,6 +86,7 @@ class EngineCoreOutput:
     prompt_logprobs: Optional[list] = None
     num_cached_tokens: int = 0
     events: Optional[list] = None
+    pooling_output: Optional[list] = None  # pooled hidden state of an embedding request (floats)
 
     @property
     def finished(self) -> bool:
@@ -90,13 +96,15 @@ class EngineCoreOutput:
         return {"request_id": self.request_id, "new_token_ids": self.new_token_ids,
                 "finish_reason": None if self.finish_reason is None else int(self.finish_reason),
                 "stop_reason": self.stop_reason, "new_logprobs": self.new_logprobs,
-                "prompt_logprobs": self.prompt_logprobs, "num_cached_tokens": self.num_cached_tokens}
+                "prompt_logprobs": self.prompt_logprobs, "num_cached_tokens": self.num_cached_tokens,
+                "pooling_output": self.pooling_output}
 
     @classmethod
     def from_wire(cls, d: dict) -> "EngineCoreOutput":
         fr = d.get("finish_reason")
         return cls(d["request_id"], list(d["new_token_ids"]), None if fr is None else FinishReason(fr), d.get("stop_reason"),
-                   d.get("new_logprobs"), d.get("prompt_logprobs"), d.get("num_cached_tokens", 0))
+                   d.get("new_logprobs"), d.get("prompt_logprobs"), d.get("num_cached_tokens", 0),
+                   pooling_output=d.get("pooling_output"))
 
 
 @dataclass

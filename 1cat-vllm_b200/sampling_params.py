@@ -160,6 +160,14 @@ class SamplingParams:
 class PoolingParams:
     """Parameters of an embedding / classify request (reference: vllm/pooling_params.py)."""
 
-    task: str = "embed"
+    task: str = "embed"  # embed | encode (raw hidden state) | score
     normalize: bool = True
-    dimensions: Optional[int] = None
+    dimensions: Optional[int] = None  # matryoshka truncation
+    pooling_type: str = "last"  # last | mean | cls
+
+    def __post_init__(self) -> None:
+        if self.pooling_type not in ("last", "mean", "cls"):
+            raise ValueError(f"unknown pooling_type '{self.pooling_type}'")
+
+    def to_dict(self) -> dict:
+        return dict(task=self.task, normalize=self.normalize, dimensions=self.dimensions, pooling_type=self.pooling_type)

@@ -39,6 +39,9 @@ class CachedRequestState:
     state_slot: int = -1
     generator: Optional[torch.Generator] = None
     eos_token_id: Optional[int] = None
+    pooling_params: object = None
+    pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
+    pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
 
 
 class ModelRunner:
@@ -167,8 +170,7 @@ class ModelRunner:
     def _update_states(self, so: SchedulerOutput) -> None:
         for rid in so.finished_req_ids:
             self.requests.pop(rid, None)
-        for rid in so.preempted_req_ids:
-            self.requests.pop(rid, None)
+        # preempted requests stay known (sampling params, generator) until they resume or finish
         for nr in so.scheduled_new_reqs:
             sp = nr.sampling_params
             gen = None
@@ -176,7 +178,8 @@ class ModelRunner:
                 gen = torch.Generator(device=self.device)
                 gen.manual_seed(sp.seed)
             self.requests[nr.req_id] = CachedRequestState(nr.req_id, list(nr.prompt_token_ids), len(nr.prompt_token_ids), sp,
-                                                          list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id)
+                                                          list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id,
+                                                          nr.pooling_params)
         c = so.scheduled_cached_reqs
         for i, rid in enumerate(c.req_ids):
             st = self.requests.get(rid)
@@ -185,7 +188,8 @@ class ModelRunner:
                 old = st
                 st = CachedRequestState(rid, list(toks), old.num_prompt_tokens if old else len(toks), old.sampling_params if old else None,
                                         list(c.new_block_ids[i] or []), c.num_computed_tokens[i], c.state_slots[i],
-                                        old.generator if old else None, old.eos_token_id if old else None)
+                                        old.generator if old else None, old.eos_token_id if old else None,
+                                        old.pooling_params if old else None)
                 self.requests[rid] = st
             else:
                 st.num_computed_tokens = c.num_computed_tokens[i]
@@ -193,9 +197,6 @@ class ModelRunner:
                     st.block_ids.extend(c.new_block_ids[i])
                 st.state_slot = c.state_slots[i]
                 # the scheduler may have dropped tokens past a rejected draft; keep only what it counts
-        # preempted requests keep their sampling params for when they resume
-        for rid in so.preempted_req_ids:
-            pass
 
     # ------------------------------------------------------------------ input preparation
     def _prepare_inputs(self, so: SchedulerOutput):
@@ -392,6 +393,8 @@ class ModelRunner:
             out.prompt_logprobs = None
         elif timed:
             ev1.record()
+        if any(self.requests[r].pooling_params is not None for r in req_ids):
+            out.pooler_output = self._pool(hidden, req_ids, query_lens, rows)
         if gdn_spec:
             self._commit_gdn_spec(gdn_spec, md, sampled_lists, query_lens)
         # bookkeeping: the runner owns the token history of running requests
@@ -410,6 +413,33 @@ class ModelRunner:
         if self.use_cuda:
             from onecat_vllm.ops import cuda as K
             out.status = K.check_status()
+        return out
+
+    def _pool(self, hidden: torch.Tensor, req_ids: list, query_lens: list[int], rows: list[int]) -> list:
+        """Pooled final-norm hidden state of embedding requests: last token, first token or mean over the prompt (accumulated
+        across prefill chunks), L2-normalised on request (reference: model_executor/layers/pooler/ ``LastPool``/``MeanPool``/
+        ``CLSPool`` + ``PoolerNormalize``; v1/pool/metadata.py)."""
+        out: list = [None] * len(req_ids)
+        o = 0
+        for i, (rid, q) in enumerate(zip(req_ids, query_lens)):
+            st = self.requests[rid]
+            pp = st.pooling_params
+            if pp is not None:
+                h = hidden[o:o + q].float()
+                if pp.pooling_type == "mean":
+                    s = h.sum(0)
+                    st.pool_sum = s if st.pool_sum is None else st.pool_sum + s
+                elif pp.pooling_type == "cls" and st.num_computed_tokens == 0:
+                    st.pool_first = h[0].clone()
+                if rows[i] > 0:  # the prompt is complete in this step
+                    n_prompt = st.num_computed_tokens + q
+                    v = h[-1] if pp.pooling_type == "last" else (st.pool_sum / n_prompt if pp.pooling_type == "mean" else st.pool_first)
+                    if pp.dimensions:
+                        v = v[: pp.dimensions]
+                    if pp.normalize:
+                        v = v / v.norm().clamp_min(1e-12)
+                    out[i] = v.cpu().tolist()
+            o += q
         return out
 
     def _grammar_mask(self, so: SchedulerOutput, req_ids: list, rows: list[int], vocab: int) -> torch.Tensor:

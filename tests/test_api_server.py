@@ -83,3 +83,21 @@ def test_server_streaming(client):
         chunks = [json.loads(l[6:]) for l in resp.iter_lines() if l.startswith("data: ") and l != "data: [DONE]"]
     assert chunks[0]["choices"][0]["delta"]["role"] == "assistant"
     assert chunks[-1]["choices"][0]["finish_reason"] == "length"
+
+
+@pytest.mark.timeout(300)
+def test_pooling_routes(client):
+    r = client.post("/v1/embeddings", json={"input": ["hello world", "hello world", "something else entirely"]}).json()
+    e = [d["embedding"] for d in r["data"]]
+    assert len(e) == 3 and len(e[0]) == 64 and r["usage"]["prompt_tokens"] > 0
+    assert abs(sum(x * x for x in e[0]) - 1.0) < 1e-4
+    assert max(abs(x - y) for x, y in zip(e[0], e[1])) < 1e-5
+    assert max(abs(x - y) for x, y in zip(e[0], e[2])) > 1e-3
+    r8 = client.post("/v1/embeddings", json={"input": "hello world", "dimensions": 8, "encoding_format": "base64"}).json()
+    import base64
+    assert len(base64.b64decode(r8["data"][0]["embedding"])) == 8 * 4
+    p = client.post("/pooling", json={"input": "abc", "pooling_type": "mean"}).json()
+    assert len(p["data"][0]["data"]) == 64
+    s = client.post("/score", json={"text_1": "hello world", "text_2": ["hello world", "zzz"]}).json()
+    assert abs(s["data"][0]["score"] - 1.0) < 1e-4 and s["data"][1]["score"] < 0.9999
+    assert client.post("/v1/embeddings", json={"input": "x", "pooling_type": "bogus"}).status_code == 400

@@ -85,3 +85,31 @@ def test_seeded_sampling_is_reproducible(tiny_llama_cfg):
     assert len(c.outputs) == 2 and c.outputs[0].token_ids != c.outputs[1].token_ids
     assert len(c.outputs[0].logprobs) == 12 and all(len(d) >= 3 for d in c.outputs[0].logprobs)
     llm.shutdown()
+
+
+def test_embed_matches_direct_forward_and_survives_chunked_prefill():
+    """LLM.embed (last / mean / cls pooling) equals pooling the model's own final hidden states, also when the prompt is
+    prefilled in several chunks (reference test model: tests/models/language/pooling/)."""
+    import torch
+    from onecat_vllm import LLM
+    from onecat_vllm.sampling_params import PoolingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=512)
+    prompt = list(range(5, 5 + 50))
+    ref = {}
+    for chunk in (8192, 16):
+        llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=chunk, enable_prefix_caching=False,
+                  tokenizer="byte")
+        for kind in ("last", "mean", "cls"):
+            out = llm.encode([{"prompt_token_ids": prompt}], PoolingParams(task="encode", normalize=False, pooling_type=kind))[0]
+            v = torch.tensor(out.outputs.data)
+            assert v.shape == (64,)
+            if chunk == 8192:
+                ref[kind] = v
+            else:
+                assert torch.allclose(v, ref[kind], atol=1e-4), kind
+        e = llm.embed([{"prompt_token_ids": prompt}])[0].outputs.embedding
+        assert abs(sum(x * x for x in e) - 1) < 1e-4
+        sc = llm.score("ab", ["ab", "xyz"])
+        assert abs(sc[0] - 1) < 1e-4 and sc[1] < 0.9999
+    assert not torch.allclose(ref["last"], ref["mean"])

@@ -37,9 +37,8 @@ constexpr int kPackedBytes = BM * BK / 2;   // 4 KB of nibbles
 constexpr int kSzBytes = BM * 4;            // one (scale, zero) word per weight row
 constexpr int kPackedSlot = kPackedBytes + kSzBytes;  // ring slot: nibbles followed by that k tile's scales/zeros
 constexpr int kTmemCols = 512;
-// 4-bit weights: the dequantised weight tiles form a ring in TMEM (32 columns per 128 x 64 tile) at the top of the 512 columns,
-// `stages` deep: 8 tiles when the two accumulators need at most 256 columns (token tile <= 128), else 4 (token tile 192).
-// The ring has to cover the whole dequantise -> tcgen05.st -> mma -> commit round trip (a few thousand cycles), so depth is throughput.
+constexpr int kAStages = 4;                   // TMEM ring of dequantised weight tiles (32 columns each)
+constexpr int kAColBase = kTmemCols - kAStages * 32;  // accumulators use columns [0, 2*tn), tn <= 192 for 4-bit weights
 
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
@@ -235,7 +234,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (lane == 0) {
           const uint64_t db = umma_desc_sw128(b_base + x * xs);
           if (WKIND == 1) {
-            const uint32_t ta = tmem_base + (kTmemCols - S * 32) + s * 32;  // 64 k of bf16 = 32 columns per stage
+            const uint32_t ta = tmem_base + kAColBase + s * 32;  // 64 k of bf16 = 32 columns per stage
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j)
               umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, (kt > k0 || j > 0) ? 1u : 0u);
@@ -266,7 +265,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       Ring st, pr;
       bool ok = true;
       const uint32_t sp_u32 = smem_u32(sp);
-      const uint32_t ta_row = tmem_base + (kTmemCols - S * 32) + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t ta_row = tmem_base + kAColBase + ((uint32_t)((warp & 3) * 32) << 16);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
@@ -295,13 +294,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
             o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
           }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&pempty[pr.idx]);  // the packed words are in registers now (one arrival per warp)
           tmem_st_32x32(ta_row + st.idx * 32, o);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&w_ready[st.idx]);
+          if (lane == 0) {           // one arrival per warp: 128 same-address arrivals would serialise
+            mbar_arrive(&w_ready[st.idx]);
+            mbar_arrive(&pempty[pr.idx]);
+          }
           st.advance(S);
           pr.advance(PS);
         }
@@ -522,11 +522,11 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
     p.acc_stride = 256;
     return;
   }
-  p.stages = tn <= 128 ? 8 : 4;
+  p.stages = kAStages;
   p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
   int xs = (budget - 2048 - p.pstages * kPackedSlot) / (tn * 128);
   p.xstages = xs > 16 ? 16 : (xs < 2 ? 2 : xs);
-  p.acc_stride = tn <= 128 ? 128 : 192;
+  p.acc_stride = 192;
 }
 
 int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream) {

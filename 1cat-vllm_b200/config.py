@@ -387,6 +387,15 @@ class VllmConfig:
         m, p = self.model_config, self.parallel_config
         if m.num_attention_heads % p.tensor_parallel_size:
             raise ValueError("tensor_parallel_size must divide num_attention_heads")
+        if p.pipeline_parallel_size > 1:
+            if p.pipeline_parallel_size > m.num_hidden_layers:
+                raise ValueError("pipeline_parallel_size exceeds the number of decoder layers")
+            if self.speculative_config.enabled:
+                raise ValueError("speculative decoding is not supported together with pipeline parallelism")
+            # stage boundaries exchange replicated tensors: tensor-parallel sums inside a stage use the library all-reduce, and the
+            # steps run eagerly (send/recv between stages is not captured)
+            p.tp_comm = "nccl"
+            self.enforce_eager = True
 
     def compute_hash(self) -> str:
         return _hash([self.model_config.compute_hash(), self.cache_config.compute_hash(), self.parallel_config.compute_hash()])

@@ -125,6 +125,7 @@ class Scheduler:
         self.log_stats = log_stats
         self._num_preemptions = 0
         self._spec_stats = [0, 0, 0]
+        self.use_pp = vllm_config.parallel_config.pipeline_parallel_size > 1
 
     # ------------------------------------------------------------------ admission
     def add_request(self, request: Request | object) -> None:
@@ -266,7 +267,12 @@ class Scheduler:
             resumed = r in scheduled_resumed
             cached.req_ids.append(r.request_id)
             cached.resumed_from_preemption.append(resumed)
-            cached.new_token_ids.append(list(r.all_token_ids) if resumed else [])
+            if resumed:
+                cached.new_token_ids.append(list(r.all_token_ids))
+            elif self.use_pp:  # stages that do not sample learn the tokens from here (reference: scheduler.py ``use_pp`` branch)
+                cached.new_token_ids.append(list(r.all_token_ids[r.num_computed_tokens:]))
+            else:
+                cached.new_token_ids.append([])
             cached.new_block_ids.append(new_blocks_of[r.request_id])
             cached.num_computed_tokens.append(r.num_computed_tokens)
             cached.state_slots.append(km.get_state_slot(r.request_id))

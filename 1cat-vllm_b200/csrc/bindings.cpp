@@ -86,6 +86,7 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
     TORCH_CHECK((p.splits - 1) * p.ktiles_per_split < ktiles, "too many splits for K");
     TORCH_CHECK((size_t)p.num_t_tiles * p.num_n_tiles * p.splits * 128 * p.tn * 4 <= p.ws_bytes, "split-K workspace too small");
     TORCH_CHECK(p.num_t_tiles * p.num_n_tiles <= p.max_counters, "not enough split-K counters");
+    oc::gemm_plan_stages(p, w4.has_value());  // the stage shape depends on whether the k range is split
   }
   int rc = oc::gemm_launch(p, x.data_ptr(), (int)x.stride(0), wptr, ldw, sm_count(), cur_stream());
   TORCH_CHECK(rc == 0, "gemm launch failed with code ", rc);

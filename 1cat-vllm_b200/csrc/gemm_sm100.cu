@@ -6,9 +6,12 @@
 //     prefill chunks run the same code, and a 4-bit weight tile is dequantised once per 128 x TN x 64 MMA block.
 //   * warp 0: producer (TMA tensor copies of X and of bf16 W)
 //     warp 1: TMEM allocation + single-thread tcgen05.mma issue
-//     warps 2-5: 4-bit -> bf16 dequantisation into the 128-byte-swizzled operand layout
-//     warps 6-9: epilogue (tcgen05.ld -> bf16 store | SiLU*mul | fp32 split-K partial + last-arriver reduction)
-//     warp 10: bulk copies of packed 4-bit tiles, running up to `pstages` tiles ahead of the operand stages
+//     warps 2-9 (4-bit only): 4-bit -> bf16 dequantisation straight into TMEM (tcgen05.st); the MMA reads operand A from there
+//     next four warps: epilogue (tcgen05.ld -> bf16 store | SiLU*mul | fp32 split-K partial + last-arriver reduction)
+//     last warp (4-bit only): bulk copies of packed 4-bit tiles, running up to `pstages` tiles ahead of the operand stages
+//   * one ring of stages carries both operands of a k tile, with one full and one empty barrier per stage: measured on
+//     B200 the MMA-issuing thread is the critical path (a ready mbarrier wait, four tcgen05.mma and a tcgen05.commit cost it
+//     about 450 cycles per k tile), so it does exactly one wait and one commit per k tile.
 //   * two accumulators of TN columns each: the epilogue of tile i overlaps the main loop of tile i+1.
 // Every wait is bounded; on expiry the CTA raises the status word and tears down (see common.cuh).
 //
@@ -37,8 +40,9 @@ constexpr int kPackedBytes = BM * BK / 2;   // 4 KB of nibbles
 constexpr int kSzBytes = BM * 4;            // one (scale, zero) word per weight row
 constexpr int kPackedSlot = kPackedBytes + kSzBytes;  // ring slot: nibbles followed by that k tile's scales/zeros
 constexpr int kTmemCols = 512;
-constexpr int kAStages = 4;                   // TMEM ring of dequantised weight tiles (32 columns each)
-constexpr int kAColBase = kTmemCols - kAStages * 32;  // accumulators use columns [0, 2*tn), tn <= 192 for 4-bit weights
+// 4-bit weights: the dequantised weight tiles form a ring in TMEM (32 columns per 128 x 64 tile) at the top of the 512 columns,
+// `stages` deep and in lock step with the X ring in shared memory: 8 tiles when the two accumulators fit 256 columns (token tile
+// <= 128), else 4 (token tile 192).
 
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
@@ -89,15 +93,14 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   uint8_t* sw = smem + L.w_off;
   uint8_t* sp = smem + L.p_off;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L.bar_off);
-  // X tiles and W tiles live in separate rings: for 4-bit weights the X ring is deep (it hides the L2 latency of the TMA
-  // loads) while the 16 KB dequantised-W ring only has to cover dequantise -> MMA -> commit. For bf16 weights both
-  // operands arrive by TMA on the same barrier and the rings advance together (XS == S).
-  const int S = p.stages, PS = p.pstages, XS = p.xstages;
-  uint64_t* full_x = bars;                      // [XS] TMA landed (X, and W for bf16 weights)
-  uint64_t* empty_x = full_x + XS;              // [XS] MMA finished reading the X stage
-  uint64_t* w_ready = empty_x + XS;             // [S]  dequantised W tile written
-  uint64_t* empty_w = w_ready + S;              // [S]  MMA finished reading the W stage
-  uint64_t* pfull = empty_w + S;                // [PS] packed tile landed
+  // One ring of S stages carries both operands of a k tile: X in shared memory and W in shared memory (bf16, by TMA) or in TMEM
+  // (4-bit, written by the dequantisation warps). Each stage has ONE full barrier (the TMA transaction bytes plus, for 4-bit
+  // weights, one arrival per dequantisation warp) and ONE empty barrier (a single tcgen05.commit): the MMA thread's cost per k
+  // tile is one wait, four MMAs and one commit, and that thread is the kernel's critical path.
+  const int S = p.stages, PS = p.pstages;
+  uint64_t* full = bars;                        // [S] operands of the stage are in place
+  uint64_t* empty = full + S;                   // [S] MMA finished reading the stage
+  uint64_t* pfull = empty + S;                  // [PS] packed tile landed
   uint64_t* pempty = pfull + PS;                // [PS] packed tile consumed
   uint64_t* tfull = pempty + PS;                // [2] accumulator complete
   uint64_t* tempty = tfull + 2;                 // [2] accumulator drained
@@ -109,13 +112,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int tn = p.tn;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < XS; ++i) {
-      mbar_init(&full_x[i], 1);
-      mbar_init(&empty_x[i], 1);
-    }
     for (int i = 0; i < S; ++i) {
-      mbar_init(&w_ready[i], 4);    // one arrival per dequantisation warp
-      mbar_init(&empty_w[i], 1);
+      mbar_init(&full[i], WKIND == 1 ? 5 : 1);  // the producer's expect_tx arrival (+ one per dequantisation warp of the group)
+      mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < PS; ++i) {
       mbar_init(&pfull[i], 1);
@@ -174,12 +173,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
         for (int kt = k0; kt < k1; ++kt) {
-          ok = mbar_wait(&empty_x[st.idx], st.phase ^ 1, abort_flag);
+          ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(&full_x[st.idx], bytes);
-          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, grouped ? tt : tt * tn, &full_x[st.idx]);
-          if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full_x[st.idx]);
-          st.advance(XS);
+          mbar_expect_tx(&full[st.idx], bytes);
+          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, grouped ? tt : tt * tn, &full[st.idx]);
+          if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full[st.idx]);
+          st.advance(S);
         }
       }
     }
@@ -210,51 +209,51 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issue
-    const uint32_t idesc = umma_idesc_bf16(BM, tn);
-    uint32_t tile_i = 0;
-    Ring st, xr;
-    bool ok = true;
-    const uint32_t xs = (uint32_t)tn * 128;
-    const uint32_t a_base = smem_u32(sw), b_base = smem_u32(sx);
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
-      int nt, tt, sp_, k0, k1;
-      decode(w, nt, tt, sp_, k0, k1);
-      const int acc = tile_i & 1;
-      ok = mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t d_addr = tmem_base + acc * p.acc_stride;
-      for (int kt = k0; kt < k1; ++kt) {
-        const int s = st.idx, x = xr.idx;
-        ok = mbar_wait(&full_x[x], xr.phase, abort_flag);
-        if (ok && WKIND == 1) ok = mbar_wait(&w_ready[s], st.phase, abort_flag);
+    // ------------------------------------------------------------------ MMA issue (one thread; the other lanes go to the teardown barrier)
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc_bf16(BM, tn);
+      uint32_t tile_i = 0;
+      Ring st;
+      bool ok = true;
+      const uint32_t xs = (uint32_t)tn * 128;
+      const uint32_t a_base = smem_u32(sw), b_base = smem_u32(sx);
+      const uint32_t ta_base = tmem_base + (kTmemCols - S * 32);
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
+        int nt, tt, sp_, k0, k1;
+        decode(w, nt, tt, sp_, k0, k1);
+        const int acc = tile_i & 1;
+        ok = mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        if (lane == 0) {
-          const uint64_t db = umma_desc_sw128(b_base + x * xs);
+        const uint32_t d_addr = tmem_base + acc * p.acc_stride;
+        uint32_t accum = 0;
+        for (int kt = k0; kt < k1; ++kt) {
+          const int s = st.idx;
+          ok = mbar_wait(&full[s], st.phase, abort_flag);
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t db = umma_desc_sw128(b_base + s * xs);
           if (WKIND == 1) {
-            const uint32_t ta = tmem_base + kAColBase + s * 32;  // 64 k of bf16 = 32 columns per stage
+            const uint32_t ta = ta_base + s * 32;  // 64 k of bf16 = 32 columns per stage
 #pragma unroll
-            for (int j = 0; j < BK / 16; ++j)
-              umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+            for (int j = 0; j < BK / 16; ++j) {
+              umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
+              accum = 1;
+            }
           } else {
             const uint64_t da = umma_desc_sw128(a_base + s * kWStageBytes);
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j) {
               // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
-              umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (kt > k0 || j > 0) ? 1u : 0u);
+              umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accum);
+              accum = 1;
             }
           }
-          umma_commit(&empty_x[x]);  // frees the stages once these MMAs have read them
-          if (WKIND == 1) umma_commit(&empty_w[s]);
+          umma_commit(&empty[s]);  // frees the stage (both operands) once these MMAs have read it
+          st.advance(S);
         }
-        __syncwarp();
-        st.advance(S);
-        xr.advance(XS);
+        if (ok) umma_commit(&tfull[acc]);
       }
-      if (ok && lane == 0) umma_commit(&tfull[acc]);
-      __syncwarp();
     }
   } else if (warp < Roles<WKIND>::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
@@ -265,7 +264,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       Ring st, pr;
       bool ok = true;
       const uint32_t sp_u32 = smem_u32(sp);
-      const uint32_t ta_row = tmem_base + kAColBase + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t ta_row = tmem_base + (kTmemCols - S * 32) + ((uint32_t)((warp & 3) * 32) << 16);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
@@ -276,7 +275,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             continue;
           }
           ok = mbar_wait(&pfull[pr.idx], pr.phase, abort_flag);
-          if (ok) ok = mbar_wait(&empty_w[st.idx], st.phase ^ 1, abort_flag);
+          if (ok) ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
           const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
@@ -294,14 +293,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
             o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
           }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&pempty[pr.idx]);  // the packed words are in registers (one arrival per warp, not per thread)
           tmem_st_32x32(ta_row + st.idx * 32, o);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) {           // one arrival per warp: 128 same-address arrivals would serialise
-            mbar_arrive(&w_ready[st.idx]);
-            mbar_arrive(&pempty[pr.idx]);
-          }
+          if (lane == 0) mbar_arrive(&full[st.idx]);
           st.advance(S);
           pr.advance(PS);
         }
@@ -522,11 +520,9 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
     p.acc_stride = 256;
     return;
   }
-  p.stages = kAStages;
+  p.stages = p.xstages = tn <= 128 ? 8 : 4;  // limited by TMEM: 2 accumulators + 32 columns per stage
   p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
-  int xs = (budget - 2048 - p.pstages * kPackedSlot) / (tn * 128);
-  p.xstages = xs > 16 ? 16 : (xs < 2 ? 2 : xs);
-  p.acc_stride = 192;
+  p.acc_stride = tn <= 128 ? 128 : 192;
 }
 
 int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream) {

@@ -47,10 +47,16 @@ class Executor:
     def initialize_kv_cache(self) -> tuple[int, int]:
         """Profile → size → allocate → warm up. Returns (num_blocks, num_state_slots)."""
         cfg = self.cfg
-        specs = self.collective_rpc("get_kv_cache_specs")[0]
-        avail = min(self.collective_rpc("determine_available_memory"))
-        kvc = get_kv_cache_config(specs, avail, cfg.cache_config.block_size, cfg.scheduler_config.max_num_seqs,
-                                  cfg.cache_config.num_gpu_blocks_override)
+        all_specs = self.collective_rpc("get_kv_cache_specs")
+        all_avail = self.collective_rpc("determine_available_memory")
+        # every rank sizes its own layers (pipeline stages own different ones); the pool takes the smallest block count
+        kvcs = [get_kv_cache_config(s, a, cfg.cache_config.block_size, cfg.scheduler_config.max_num_seqs,
+                                    cfg.cache_config.num_gpu_blocks_override) for s, a in zip(all_specs, all_avail)]
+        specs = {}
+        for s in all_specs:
+            specs.update(s)
+        from onecat_vllm.core.kv_cache_utils import KVCacheConfig
+        kvc = KVCacheConfig(min(k.num_blocks for k in kvcs), cfg.cache_config.block_size, specs, max(k.num_state_slots for k in kvcs))
         max_need = -(-cfg.model_config.max_model_len // cfg.cache_config.block_size) + 1
         if any(s.kind != "mamba" for s in specs.values()) and kvc.num_blocks < max_need:
             raise ValueError(f"KV cache of {kvc.num_blocks} blocks cannot hold one sequence of max_model_len="
@@ -61,7 +67,13 @@ class Executor:
         return kvc.num_blocks, kvc.num_state_slots
 
     def execute_model(self, scheduler_output):
-        return self.collective_rpc("execute_model", (scheduler_output,))[0]
+        pc = self.cfg.parallel_config
+        outs = self.collective_rpc("execute_model", (scheduler_output,))
+        out = outs[min((pc.pipeline_parallel_size - 1) * pc.tensor_parallel_size, len(outs) - 1)]  # first TP rank of the last stage
+        if pc.pipeline_parallel_size > 1:
+            out.status = max(o.status for o in outs)
+            out.device_time_ms = sum(o.device_time_ms for o in outs[:: pc.tensor_parallel_size])
+        return out
 
     def check_health(self) -> None:
         self.collective_rpc("check_health", timeout=10)

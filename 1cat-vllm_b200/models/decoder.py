@@ -20,7 +20,15 @@ from onecat_vllm.layers.gdn import GatedDeltaNet
 from onecat_vllm.layers.mla import MLAAttention
 from onecat_vllm.layers.mlp import MLP
 from onecat_vllm.layers.moe import SparseMoeBlock
-from onecat_vllm.parallel.tp_ops import reduce_add_norm
+from onecat_vllm.parallel import state as ps
+from onecat_vllm.parallel.tp_ops import reduce_add_norm, reduce_only
+
+
+class PPMissingLayer(nn.Module):
+    """Placeholder for a module that lives on another pipeline stage; keeps checkpoint names aligned
+    (reference: model_executor/models/utils.py ``PPMissingLayer``)."""
+
+    kind = "missing"
 
 
 class DecoderLayer(nn.Module):
@@ -53,21 +61,39 @@ class DecoderModel(nn.Module):
     def __init__(self, cfg: ModelConfig, device="cpu"):
         super().__init__()
         self.cfg = cfg
-        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
-        self.layers = nn.ModuleList([DecoderLayer(cfg, i, f"model.layers.{i}", device) for i in range(cfg.num_hidden_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        st = ps.get_state()
+        self.first_stage, self.last_stage = st.is_first_pp, st.is_last_pp
+        self.start, self.end = ps.pp_layer_range(cfg.num_hidden_layers)
+        need_embed = self.first_stage or (self.last_stage and cfg.tie_word_embeddings)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype) if need_embed else PPMissingLayer()
+        self.layers = nn.ModuleList([DecoderLayer(cfg, i, f"model.layers.{i}", device) if self.start <= i < self.end else PPMissingLayer()
+                                     for i in range(cfg.num_hidden_layers)])
+        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype) if self.last_stage else PPMissingLayer()
+
+    def local_layers(self):
+        """(global index, layer) of the decoder layers this pipeline stage owns; KV caches are indexed in this order."""
+        return [(i, self.layers[i]) for i in range(self.start, self.end)]
 
     def forward(self, input_ids: torch.Tensor, md, caches: list, inputs_embeds: Optional[torch.Tensor] = None,
-                return_prenorm: bool = False):
-        h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+                return_prenorm: bool = False, intermediate: Optional[tuple] = None):
+        """First stage: embeds ``input_ids``. Later stages: ``intermediate`` = (reduced block output, residual) of the previous
+        stage. A stage that is not the last returns that pair for its successor instead of the final hidden states
+        (reference: models/llama.py ``IntermediateTensors`` handling)."""
         layers = self.layers
-        x, residual = layers[0].input_layernorm(h, None)
-        residual = h
-        for i, layer in enumerate(layers):
-            part = layer.mixer(x, md, caches[i])
+        if intermediate is None:
+            h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+            x, residual = layers[self.start].input_layernorm(h, None)
+            residual = h
+        else:
+            x, residual = layers[self.start].input_layernorm(intermediate[0], intermediate[1])
+        for li, i in enumerate(range(self.start, self.end)):
+            layer = layers[i]
+            part = layer.mixer(x, md, caches[li])
             x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
             part = layer.mlp(x)
-            nxt = layers[i + 1].input_layernorm if i + 1 < len(layers) else self.norm
+            if i + 1 == self.end and not self.last_stage:
+                return reduce_only(part), residual
+            nxt = layers[i + 1].input_layernorm if i + 1 < self.end else self.norm
             x, residual = reduce_add_norm(part, residual, nxt)
         if return_prenorm:
             return x, residual
@@ -89,13 +115,13 @@ class CausalLM(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.model = DecoderModel(cfg, device)
-        if cfg.tie_word_embeddings:
+        if cfg.tie_word_embeddings or not ps.get_state().is_last_pp:
             self.lm_head = None
         else:
             self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
 
-    def forward(self, input_ids, md, caches, inputs_embeds=None):
-        return self.model(input_ids, md, caches, inputs_embeds)
+    def forward(self, input_ids, md, caches, inputs_embeds=None, intermediate=None):
+        return self.model(input_ids, md, caches, inputs_embeds, intermediate=intermediate)
 
     def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         head = self.lm_head

@@ -63,6 +63,21 @@ def rank_layout(rank: int, tp: int, pp: int) -> tuple[int, int]:
     return rank % tp, rank // tp
 
 
+def pp_layer_range(num_layers: int, pp_rank: Optional[int] = None, pp_size: Optional[int] = None) -> tuple[int, int]:
+    """Contiguous slice of decoder layers owned by a pipeline stage; earlier stages take the remainder
+    (reference: model_executor/models/utils.py ``get_pp_indices``)."""
+    pp_rank = _STATE.pp_rank if pp_rank is None else pp_rank
+    pp_size = _STATE.pp_size if pp_size is None else pp_size
+    base, rem = divmod(num_layers, pp_size)
+    start = pp_rank * base + min(pp_rank, rem)
+    return start, start + base + (1 if pp_rank < rem else 0)
+
+
+def pp_neighbor(delta: int) -> int:
+    """Global rank of the stage ``delta`` steps away that holds the same tensor-parallel shard."""
+    return (_STATE.pp_rank + delta) * _STATE.tp_size + _STATE.tp_rank
+
+
 def init_distributed(rank: int, world_size: int, tp: int, pp: int = 1, backend: Optional[str] = None,
                      init_method: Optional[str] = None, enable_ep: bool = False, dcp: int = 1, tp_comm: str = "fused",
                      timeout_s: float = 600.0) -> ParallelState:

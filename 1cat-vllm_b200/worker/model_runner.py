@@ -20,6 +20,7 @@ from onecat_vllm.config import VllmConfig
 from onecat_vllm.core.kv_cache_utils import KVCacheConfig, KVCacheSpec
 from onecat_vllm.core.sched_output import ModelRunnerOutput, SchedulerOutput
 from onecat_vllm.logger import init_logger
+from onecat_vllm.parallel import state as ps
 from onecat_vllm.sample.metadata import SamplingMetadata
 from onecat_vllm.sample.rejection_sampler import RejectionSampler
 from onecat_vllm.sample.sampler import Sampler, to_logprobs_lists
@@ -63,6 +64,7 @@ class ModelRunner:
         sc = vllm_config.speculative_config
         self.spec = sc
         self.num_spec = sc.num_speculative_tokens if sc.enabled else 0
+        self.pp = ps.get_state()  # pipeline coordinates of this rank
         self.rejection_sampler = RejectionSampler(sc.conditional_rates(), sc.synthetic_seed) if sc.enabled else None
         self.proposer = None
         self.graphs = None  # worker.cuda_graphs.DecodeGraphs
@@ -92,7 +94,7 @@ class ModelRunner:
     def get_kv_cache_specs(self) -> dict:
         mc, specs = self.mc, {}
         esz = torch.empty(0, dtype=self._kv_dtype()).element_size()
-        for i, layer in enumerate(self.model.model.layers):
+        for i, layer in self.model.model.local_layers():
             if layer.kind == "linear_attention":
                 (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
                 nspec = self.num_spec + 1
@@ -125,7 +127,7 @@ class ModelRunner:
             return torch.zeros(nb, 2, spec.num_kv_heads, bs, spec.head_size, dtype=dt, device=dev)
 
         self.kv_caches = []
-        for i, layer in enumerate(self.model.model.layers):
+        for i, layer in self.model.model.local_layers():
             spec = kvc.layer_specs[f"layers.{i}"]
             if spec.kind == "mamba":
                 (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
@@ -193,6 +195,9 @@ class ModelRunner:
                 self.requests[rid] = st
             else:
                 st.num_computed_tokens = c.num_computed_tokens[i]
+                if c.new_token_ids[i]:  # pipeline parallelism: tokens sampled on the last stage arrive through the scheduler
+                    del st.token_ids[c.num_computed_tokens[i]:]
+                    st.token_ids.extend(c.new_token_ids[i])
                 if c.new_block_ids[i]:
                     st.block_ids.extend(c.new_block_ids[i])
                 st.state_slot = c.state_slots[i]
@@ -362,8 +367,17 @@ class ModelRunner:
         if gkey is not None:
             hidden = self.graphs.run(gkey, T)
         if hidden is None:
-            hidden = self.model(ids, md, self.kv_caches)
+            inter = self._pp_recv(T) if not self.pp.is_first_pp else None
+            hidden = self.model(ids, md, self.kv_caches, intermediate=inter)
         out = ModelRunnerOutput(req_ids=req_ids, sampled_token_ids=[[] for _ in req_ids])
+        if not self.pp.is_last_pp:
+            # hand (block output, residual) to the next stage; sampling happens on the last one
+            self._pp_send(hidden)
+            if timed:
+                ev1.record()
+                torch.cuda.synchronize()
+                out.device_time_ms = ev0.elapsed_time(ev1)
+            return out
         sampled_lists: list[list[int]] = [[] for _ in req_ids]
         if n_l > 0:
             lidx = self._view("lidx", n_l).long()
@@ -441,6 +455,24 @@ class ModelRunner:
                     out[i] = v.cpu().tolist()
             o += q
         return out
+
+    # ---- pipeline parallelism: stage boundaries carry two [T, hidden] tensors (reference: gpu_worker.py:80-110, 792-880
+    # ``IntermediateTensors`` send/recv; v1/worker/gpu_model_runner.py:8437-8443)
+    def _pp_send(self, pair) -> None:
+        import torch.distributed as dist
+        dst = ps.pp_neighbor(+1)
+        for t in pair:
+            dist.send(t.contiguous(), dst=dst)
+
+    def _pp_recv(self, T: int) -> tuple:
+        import torch.distributed as dist
+        src = ps.pp_neighbor(-1)
+        out = []
+        for _ in range(2):
+            t = torch.empty(T, self.mc.hidden_size, dtype=self.mc.dtype, device=self.device)
+            dist.recv(t, src=src)
+            out.append(t)
+        return tuple(out)
 
     def _grammar_mask(self, so: SchedulerOutput, req_ids: list, rows: list[int], vocab: int) -> torch.Tensor:
         """Packed per-request words → bool ``[sampling requests, vocab]`` (True = allowed); requests without a grammar get
@@ -550,14 +582,18 @@ class ModelRunner:
                                seq.tolist(), seq.tolist())
         ids = torch.zeros(T, dtype=torch.int32, device=self.device)
         caches = self.kv_caches if self.kv_caches else self._tiny_caches()
-        h = self.model(ids, md, caches)
-        self.model.compute_logits(h[:R])
+        inter = None
+        if not self.pp.is_first_pp:  # profiling never communicates: each stage runs on zeros
+            inter = (torch.zeros(T, self.mc.hidden_size, dtype=self.mc.dtype, device=self.device),) * 2
+        h = self.model(ids, md, caches, intermediate=inter)
+        if self.pp.is_last_pp:
+            self.model.compute_logits(h[:R])
 
     def _tiny_caches(self):
         """One-block caches so the profiling forward can run before the real cache exists."""
         out = []
         dt = self._kv_dtype()
-        for layer in self.model.model.layers:
+        for _, layer in self.model.model.local_layers():
             if layer.kind == "linear_attention":
                 (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
                 out.append((torch.zeros(1, cd, kw, dtype=dt, device=self.device), torch.zeros(1, hv, k, v, dtype=torch.float32, device=self.device)))

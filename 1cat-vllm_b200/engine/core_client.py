@@ -31,6 +31,8 @@ class InprocClient:
 
 
 def make_client(cfg: VllmConfig, multiprocess: bool, asyncio_mode: bool, log_stats: bool = False):
+    if cfg.parallel_config.data_parallel_size > 1:
+        multiprocess = True  # replicas are engine-core processes behind one load-balancing client
     if not multiprocess and not asyncio_mode:
         return InprocClient(cfg, log_stats)
     from onecat_vllm.engine.core_proc import AsyncMPClient, SyncMPClient

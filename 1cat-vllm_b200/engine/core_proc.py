@@ -51,6 +51,12 @@ def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_i
                 pass
             os._exit(1)
         threading.Thread(target=watch, daemon=True).start()
+    pc = cfg.parallel_config
+    if pc.data_parallel_size > 1 and cfg.device == "cuda":
+        # replica i owns GPUs [i * world, (i + 1) * world) of those visible to the frontend; set before CUDA initialises here
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        ids = vis.split(",") if vis else [str(i) for i in range(pc.data_parallel_size * pc.world_size)]
+        os.environ["CUDA_VISIBLE_DEVICES"] = ",".join(ids[engine_index * pc.world_size:(engine_index + 1) * pc.world_size])
     ctx = zmq.Context()
     inp = ctx.socket(zmq.DEALER)
     inp.setsockopt(zmq.IDENTITY, engine_index.to_bytes(2, "little"))
@@ -136,12 +142,24 @@ class _MPClientBase:
         pull = self.sync_ctx.socket(zmq.PULL)
         pull.bind(self.output_addr)
         mctx = mp.get_context("spawn")
-        d_r, self._death_w = mctx.Pipe(duplex=False)
-        self.proc = mctx.Process(target=run_engine_core, args=(cfg, self.input_addr, self.output_addr, 0, log_stats, d_r), daemon=True,
-                                 name="onecat-engine-core")
-        self.proc.start()
-        d_r.close()
-        self.engine_id = (0).to_bytes(2, "little")
+        # data parallelism: one engine core (scheduler + executor over tp*pp GPUs) per replica, all on the same socket pair;
+        # the ROUTER addresses a replica by its identity (reference: v1/engine/core_client.py:1169 DPAsyncMPClient, :1349 DPLBAsyncMPClient)
+        self.num_engines = max(1, cfg.parallel_config.data_parallel_size)
+        self.procs, self._death_ws = [], []
+        for i in range(self.num_engines):
+            d_r, d_w = mctx.Pipe(duplex=False)
+            pr = mctx.Process(target=run_engine_core, args=(cfg, self.input_addr, self.output_addr, i, log_stats, d_r), daemon=True,
+                              name=f"onecat-engine-core-{i}")
+            pr.start()
+            d_r.close()
+            self.procs.append(pr)
+            self._death_ws.append(d_w)
+        self.proc, self._death_w = self.procs[0], self._death_ws[0]
+        self.engine_ids = [i.to_bytes(2, "little") for i in range(self.num_engines)]
+        self.engine_id = self.engine_ids[0]
+        self._owner: dict = {}                      # request id -> replica
+        self._inflight = [0] * self.num_engines     # requests sent and not yet finished
+        self._lb = [(0, 0)] * self.num_engines      # last reported (waiting, running) per replica
         self.dead = False
         try:
             self._handshake(hs)
@@ -160,11 +178,12 @@ class _MPClientBase:
 
     def _handshake(self, hs) -> None:
         deadline = time.time() + envs.ONECAT_HANDSHAKE_TIMEOUT_SECONDS * 5
-        stage = 0
-        while stage < 2:
+        ready = 0
+        while ready < self.num_engines:
             if not hs.poll(200):
-                if not self.proc.is_alive():
-                    raise RuntimeError(f"engine core exited during start-up (code {self.proc.exitcode})")
+                for pr in self.procs:
+                    if not pr.is_alive():
+                        raise RuntimeError(f"engine core exited during start-up (code {pr.exitcode})")
                 if time.time() > deadline:
                     raise TimeoutError("engine core handshake timed out")
                 continue
@@ -172,15 +191,50 @@ class _MPClientBase:
             msg = serial.decode(frames)
             if msg["status"] == "HELLO":
                 hs.send_multipart([ident] + serial.encode({"ack": True}))
-                stage = 1
             elif msg["status"] == "READY":
                 self.cfg.cache_config.num_gpu_blocks = msg["num_gpu_blocks"]
-                stage = 2
+                ready += 1
 
     def _monitor(self) -> None:
-        self.proc.join()
-        if not getattr(self, "_closing", False):
-            self.dead = True
+        while not getattr(self, "_closing", False):
+            if any(not pr.is_alive() for pr in self.procs):
+                if not getattr(self, "_closing", False):
+                    self.dead = True
+                return
+            time.sleep(0.1)
+
+    # ---- replica choice and bookkeeping
+    def _route(self, req: EngineCoreRequest) -> bytes:
+        """Replica for a new request: the one asked for, else the least loaded by (4 x waiting + running) as last reported,
+        plus what was sent since (reference: core_client.py:1400-1430 ``get_core_engine_for_request``)."""
+        n = self.num_engines
+        if n == 1:
+            return self.engine_id
+        e = req.data_parallel_rank
+        if e is None or not 0 <= e < n:
+            e = min(range(n), key=lambda i: (4 * self._lb[i][0] + self._lb[i][1] + self._inflight[i], i))
+        self._owner[req.request_id] = e
+        self._inflight[e] += 1
+        return self.engine_ids[e]
+
+    def _abort_targets(self, ids: list) -> dict:
+        by: dict = {}
+        for rid in ids:
+            e = self._owner.pop(rid, 0)
+            if self.num_engines > 1:
+                self._inflight[e] = max(0, self._inflight[e] - 1)
+            by.setdefault(e, []).append(rid)
+        return by
+
+    def _account(self, o: EngineCoreOutputs) -> None:
+        if self.num_engines == 1:
+            return
+        e = o.engine_index
+        if o.scheduler_stats is not None:
+            self._lb[e] = (o.scheduler_stats.num_waiting_reqs, o.scheduler_stats.num_running_reqs)
+        for x in o.outputs:
+            if x.finished and self._owner.pop(x.request_id, None) is not None:
+                self._inflight[e] = max(0, self._inflight[e] - 1)
 
     def _check(self) -> None:
         if self.dead:
@@ -188,9 +242,10 @@ class _MPClientBase:
 
     def _kill(self) -> None:
         self._closing = True
-        if self.proc.is_alive():
-            self.proc.terminate()  # exact child we started
-            self.proc.join(5)
+        for pr in self.procs:
+            if pr.is_alive():
+                pr.terminate()  # exact children we started
+                pr.join(5)
 
     @staticmethod
     def _parse(frames) -> EngineCoreOutputs:
@@ -211,11 +266,12 @@ class SyncMPClient(_MPClientBase):
 
     def add_request(self, req: EngineCoreRequest) -> None:
         self._check()
-        self.inp.send_multipart([self.engine_id, serial.REQ_ADD] + serial.encode(req.to_wire()))
+        self.inp.send_multipart([self._route(req), serial.REQ_ADD] + serial.encode(req.to_wire()))
 
     def abort_requests(self, ids: list) -> None:
         if ids and not self.dead:
-            self.inp.send_multipart([self.engine_id, serial.REQ_ABORT] + serial.encode(list(ids)))
+            for e, rids in self._abort_targets(list(ids)).items():
+                self.inp.send_multipart([self.engine_ids[e], serial.REQ_ABORT] + serial.encode(rids))
 
     def get_output(self, timeout_s: float = 300.0) -> EngineCoreOutputs:
         deadline = time.time() + timeout_s
@@ -224,8 +280,9 @@ class SyncMPClient(_MPClientBase):
             if self.outp.poll(100):
                 o = self._parse(self.outp.recv_multipart())
                 if o.utility_output is not None:
-                    self._util[o.utility_output["call_id"]] = o.utility_output
+                    self._util.setdefault(o.utility_output["call_id"], []).append(o.utility_output)
                     continue
+                self._account(o)
                 return o
             if time.time() > deadline:
                 raise TimeoutError("no output from the engine core")
@@ -234,37 +291,43 @@ class SyncMPClient(_MPClientBase):
         self._check()
         self._call_id += 1
         cid = self._call_id
-        self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
+        for eid in self.engine_ids:  # utility calls go to every replica
+            self.inp.send_multipart([eid, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
         deadline = time.time() + envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS
-        while cid not in self._util:
+        while len(self._util.get(cid, ())) < self.num_engines:
             self._check()
             if self.outp.poll(100):
                 o = self._parse(self.outp.recv_multipart())
                 if o.utility_output is not None:
-                    self._util[o.utility_output["call_id"]] = o.utility_output
+                    self._util.setdefault(o.utility_output["call_id"], []).append(o.utility_output)
             if time.time() > deadline:
                 raise TimeoutError(f"utility call {method} timed out")
-        r = self._util.pop(cid)
-        if "error" in r:
-            raise RuntimeError(r["error"])
-        return r["result"]
+        rs = self._util.pop(cid)
+        for r in rs:
+            if "error" in r:
+                raise RuntimeError(r["error"])
+        return rs[0]["result"] if self.num_engines == 1 else [r["result"] for r in rs]
 
     def shutdown(self) -> None:
         self._closing = True
         try:
-            if not self.dead and self.proc.is_alive():
-                self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([0, "shutdown", []]))
-                self.proc.join(10)
+            if not self.dead:
+                for eid, pr in zip(self.engine_ids, self.procs):
+                    if pr.is_alive():
+                        self.inp.send_multipart([eid, serial.REQ_UTILITY] + serial.encode([0, "shutdown", []]))
+                for pr in self.procs:
+                    pr.join(10)
         except Exception:
             pass
         self._kill()
         for s in (getattr(self, "inp", None), getattr(self, "outp", None)):
             if s is not None:
                 s.close(linger=0)
-        try:
-            self._death_w.close()
-        except Exception:
-            pass
+        for w in self._death_ws:
+            try:
+                w.close()
+            except Exception:
+                pass
 
 
 class AsyncMPClient(_MPClientBase):
@@ -274,11 +337,12 @@ class AsyncMPClient(_MPClientBase):
 
     async def add_request_async(self, req: EngineCoreRequest) -> None:
         self._check()
-        await self.inp.send_multipart([self.engine_id, serial.REQ_ADD] + serial.encode(req.to_wire()))
+        await self.inp.send_multipart([self._route(req), serial.REQ_ADD] + serial.encode(req.to_wire()))
 
     async def abort_requests_async(self, ids: list) -> None:
         if ids and not self.dead:
-            await self.inp.send_multipart([self.engine_id, serial.REQ_ABORT] + serial.encode(list(ids)))
+            for e, rids in self._abort_targets(list(ids)).items():
+                await self.inp.send_multipart([self.engine_ids[e], serial.REQ_ABORT] + serial.encode(rids))
 
     async def get_output_async(self) -> EngineCoreOutputs:
         while True:
@@ -286,10 +350,16 @@ class AsyncMPClient(_MPClientBase):
             if await self.outp.poll(200):
                 o = self._parse(await self.outp.recv_multipart())
                 if o.utility_output is not None:
-                    fut = self._util_futs.pop(o.utility_output["call_id"], None)
-                    if fut is not None and not fut.done():
-                        fut.set_result(o.utility_output)
+                    cid = o.utility_output["call_id"]
+                    ent = self._util_futs.get(cid)
+                    if ent is not None:
+                        ent[1].append(o.utility_output)
+                        if len(ent[1]) == self.num_engines:
+                            self._util_futs.pop(cid)
+                            if not ent[0].done():
+                                ent[0].set_result(ent[1])
                     continue
+                self._account(o)
                 return o
 
     async def call_utility_async(self, method: str, *args):
@@ -298,12 +368,14 @@ class AsyncMPClient(_MPClientBase):
         self._call_id += 1
         cid = self._call_id
         fut = asyncio.get_running_loop().create_future()
-        self._util_futs[cid] = fut
-        await self.inp.send_multipart([self.engine_id, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
-        r = await asyncio.wait_for(fut, envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS)
-        if "error" in r:
-            raise RuntimeError(r["error"])
-        return r["result"]
+        self._util_futs[cid] = (fut, [])
+        for eid in self.engine_ids:
+            await self.inp.send_multipart([eid, serial.REQ_UTILITY] + serial.encode([cid, method, list(args)]))
+        rs = await asyncio.wait_for(fut, envs.ONECAT_EXECUTE_MODEL_TIMEOUT_SECONDS)
+        for r in rs:
+            if "error" in r:
+                raise RuntimeError(r["error"])
+        return rs[0]["result"] if self.num_engines == 1 else [r["result"] for r in rs]
 
     def shutdown(self) -> None:
         self._closing = True
@@ -311,7 +383,8 @@ class AsyncMPClient(_MPClientBase):
         for s in (getattr(self, "inp", None), getattr(self, "outp", None)):
             if s is not None:
                 s.close(linger=0)
-        try:
-            self._death_w.close()
-        except Exception:
-            pass
+        for w in self._death_ws:
+            try:
+                w.close()
+            except Exception:
+                pass

@@ -72,3 +72,29 @@ def test_async_llm_streams_and_detects_death():
         eng.shutdown()
 
     asyncio.run(main())
+
+
+@pytest.mark.timeout(600)
+def test_data_parallel_replicas_balance_and_match_single():
+    """Two engine-core replicas behind one client: every request completes with the single-engine tokens, both replicas
+    get work, aborts reach the owning replica, utility calls fan out to all replicas."""
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    prompts = [[(7 * i + j) % 290 + 1 for j in range(5 + i)] for i in range(8)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    one = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128)
+    ref = [o.outputs[0].token_ids for o in one.generate([{"prompt_token_ids": p} for p in prompts], sp)]
+    one.shutdown()
+    two = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, data_parallel_size=2)
+    client = two.llm_engine.engine_core
+    assert client.num_engines == 2
+    sent = []
+    orig = client._route
+    client._route = lambda req: (lambda e: (sent.append(e), e)[1])(orig(req))
+    got = [o.outputs[0].token_ids for o in two.generate([{"prompt_token_ids": p} for p in prompts], sp)]
+    assert got == ref
+    assert len(set(sent)) == 2 and abs(sent.count(sent[0]) - len(sent) / 2) <= 1  # both replicas used, evenly
+    assert client._inflight == [0, 0] and not client._owner
+    assert two.reset_prefix_cache() == [True, True]
+    two.shutdown()

@@ -51,3 +51,34 @@ def test_worker_death_is_detected(tmp_path):
     with pytest.raises(Exception):
         llm.generate([[1, 2, 3]], SamplingParams(max_tokens=2))
     llm.shutdown()
+
+
+CFG4 = dict(CFG, num_hidden_layers=5)
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("tp,pp", [(1, 2), (2, 2), (1, 3)])
+def test_pipeline_parallel_cpu_matches_single(tmp_path, tp, pp):
+    """Pipeline stages (gloo send/recv of the block output and the residual) reproduce the single-process greedy decode,
+    including uneven layer splits, chunked prefill and sampling with seeds."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    from onecat_vllm.parallel.state import pp_layer_range
+    assert [pp_layer_range(5, r, 3) for r in range(3)] == [(0, 2), (2, 4), (4, 5)]
+    m = build_model(ModelConfig.from_hf_dict(CFG4, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    save_pretrained(m, CFG4, str(tmp_path))
+    path = str(tmp_path)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (7, 40, 90)]
+    sps = [SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True), SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True),
+           SamplingParams(temperature=0.9, seed=3, max_tokens=8, ignore_eos=True)]
+    kw = dict(model=path, device="cpu", dtype="float32", max_model_len=128, max_num_batched_tokens=48)
+    one = LLM(**kw)
+    ref = [o.outputs[0].token_ids for o in one.generate(prompts, sps)]
+    one.shutdown()
+    many = LLM(**kw, tensor_parallel_size=tp, pipeline_parallel_size=pp, distributed_executor_backend="mp")
+    got = [o.outputs[0].token_ids for o in many.generate(prompts, sps)]
+    many.shutdown()
+    assert got == ref

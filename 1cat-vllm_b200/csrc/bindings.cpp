@@ -27,7 +27,7 @@ void check_bf16(const torch::Tensor& t, const char* name) {
 void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> w4, c10::optional<torch::Tensor> w4_sz,
           torch::Tensor out, c10::optional<torch::Tensor> bias, torch::Tensor ws, torch::Tensor counters, int64_t N, int64_t n_rows,
           int64_t n_out, int64_t n_pad, int64_t epi, int64_t group_ktiles, int64_t force_splits, int64_t force_tn,
-          std::vector<int64_t> push_dst, int64_t push_rows) {
+          std::vector<int64_t> push_dst, int64_t push_rows, int64_t wkind) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1, "x/out must be row-major 2-D");
@@ -59,7 +59,12 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
     p.w4 = (const uint8_t*)w4->data_ptr();
     p.w4_sz = (const uint32_t*)w4_sz->data_ptr();
     TORCH_CHECK(((uintptr_t)p.w4 & 15) == 0, "packed weights must be 16-byte aligned");
-    TORCH_CHECK((size_t)w4->numel() * w4->element_size() >= (size_t)((n_rows + 127) / 128) * (p.K / 64) * 4096, "packed weights are too small");
+    TORCH_CHECK(wkind >= 1 && wkind <= 3, "packed weights need wkind 1 (int4), 2 (fp8) or 3 (fp4)");
+    p.wkind = (int)wkind;
+    TORCH_CHECK(((uintptr_t)p.w4_sz & 15) == 0 && n_pad % 4 == 0, "scale table must be 16-byte aligned");
+    TORCH_CHECK((size_t)w4->numel() * w4->element_size() >= (size_t)((n_rows + 127) / 128) * (p.K / 64) * (wkind == 2 ? 8192 : 4096),
+                "packed weights are too small");
+    TORCH_CHECK((size_t)w4_sz->numel() >= (size_t)((p.K / 64 + group_ktiles - 1) / group_ktiles) * n_pad, "scale table is too small");
   } else {
     TORCH_CHECK(w.has_value(), "a weight is required");
     check_bf16(*w, "w");
@@ -355,24 +360,39 @@ std::tuple<torch::Tensor, torch::Tensor> route(torch::Tensor logits, c10::option
 
 // Routed-expert path of one MoE layer: slots -> grouped GEMM (w13, SiLU*mul) -> grouped GEMM (w2) -> weighted combine.
 // w13: bf16 [E_local * 2I, H] with each expert's gate|up rows interleaved in blocks of 16; w2: bf16 [E_local * H, I].
+// With `wkind` > 0 the expert weights are packed tiles (see gemm) and w13_sz / w2_sz their scale tables; I2 and group_ktiles
+// (64-wide k tiles per scale row of the tables) then come from the caller.
 torch::Tensor fused_moe(torch::Tensor x, torch::Tensor w13, torch::Tensor w2, torch::Tensor topk_w, torch::Tensor topk_ids, int64_t E_local,
-                        int64_t e_off, torch::Tensor ws, torch::Tensor counters) {
+                        int64_t e_off, torch::Tensor ws, torch::Tensor counters, int64_t wkind, c10::optional<torch::Tensor> w13_sz,
+                        c10::optional<torch::Tensor> w2_sz, int64_t I2_packed, int64_t group_ktiles) {
   check_bf16(x, "x");
-  check_bf16(w13, "w13");
-  check_bf16(w2, "w2");
+  if (wkind == 0) {
+    check_bf16(w13, "w13");
+    check_bf16(w2, "w2");
+  } else {
+    TORCH_CHECK(wkind >= 1 && wkind <= 3 && w13_sz.has_value() && w2_sz.has_value() && I2_packed > 0 && group_ktiles >= 1, "packed experts need scale tables");
+  }
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && w13.is_contiguous() && w2.is_contiguous(), "bad layouts");
   TORCH_CHECK(topk_ids.scalar_type() == torch::kInt32 && topk_ids.is_contiguous() && topk_w.scalar_type() == torch::kFloat32 && topk_w.is_contiguous(),
               "routing tensors must be contiguous int32 ids / fp32 weights");
   const c10::cuda::CUDAGuard guard(x.device());
   const int T = (int)x.size(0), H = (int)x.size(1), k = (int)topk_ids.size(1);
-  const int I2 = (int)(w13.size(0) / E_local), I = I2 / 2;
-  TORCH_CHECK(w13.size(1) == H && w2.size(0) == E_local * H && w2.size(1) == I, "expert weight shapes do not match");
+  const int I2 = wkind == 0 ? (int)(w13.size(0) / E_local) : (int)I2_packed, I = I2 / 2;
+  if (wkind == 0) {
+    TORCH_CHECK(w13.size(1) == H && w2.size(0) == E_local * H && w2.size(1) == I, "expert weight shapes do not match");
+  } else {
+    const size_t tb = wkind == 2 ? 8192 : 4096;
+    TORCH_CHECK((size_t)w13.numel() * w13.element_size() >= (size_t)(E_local * I2 / 128) * (H / 64) * tb &&
+                (size_t)w2.numel() * w2.element_size() >= (size_t)(E_local * H / 128) * (I / 64) * tb, "packed expert weights are too small");
+    TORCH_CHECK((size_t)w13_sz->numel() >= (size_t)((H / 64 + group_ktiles - 1) / group_ktiles) * E_local * I2 &&
+                (size_t)w2_sz->numel() >= (size_t)((I / 64 + group_ktiles - 1) / group_ktiles) * E_local * H, "expert scale tables are too small");
+  }
   TORCH_CHECK(I2 % 128 == 0 && H % 128 == 0 && H % 64 == 0 && I % 64 == 0, "expert dims must be multiples of 128 (rows) and 64 (k)");
   auto y = torch::empty({T, H}, x.options());
   if (T == 0) return y;
   const int n_pairs = T * k;
   const int avg = (n_pairs + (int)E_local - 1) / (int)E_local;
-  const int tn = avg <= 32 ? 32 : avg <= 64 ? 64 : avg <= 128 ? 128 : 256;
+  const int tn = avg <= 32 ? 32 : avg <= 64 ? 64 : (avg <= 128 || wkind != 0) ? 128 : 256;  // packed kinds share TMEM with the weight ring
   const int n1 = I2 / 128, n2 = H / 128;
   const int max_tt = (n_pairs + tn - 1) / tn + (int)E_local;
   auto iopt = x.options().dtype(torch::kInt32);
@@ -391,19 +411,27 @@ torch::Tensor fused_moe(torch::Tensor x, torch::Tensor w13, torch::Tensor w2, to
   pp.E = (int)E_local; pp.tn = tn; pp.n1 = n1; pp.n2 = n2;
   int rc = oc::moe_prepare_launch(pp, topk_ids.data_ptr<int>(), n_pairs, k, (int)e_off, slot_of, x.data_ptr(), x.stride(0), xs.data_ptr(), H, cur_stream());
   TORCH_CHECK(rc == 0, "moe prepare failed: ", rc);
-  auto run = [&](const torch::Tensor& in, const torch::Tensor& w, torch::Tensor& out, int Kd, int N, int n_out, int epi, const int4* wl, const int* cnt, int cap) {
+  auto run = [&](const torch::Tensor& in, const torch::Tensor& w, const c10::optional<torch::Tensor>& sz, int n_rows, torch::Tensor& out, int Kd, int N,
+                 int n_out, int epi, const int4* wl, const int* cnt, int cap) {
     oc::GemmParams p{};
-    p.T = n_pairs; p.K = Kd; p.N = N; p.n_rows = (int)w.size(0); p.n_out = n_out; p.epi = epi; p.group_ktiles = 1;
+    p.T = n_pairs; p.K = Kd; p.N = N; p.n_rows = n_rows; p.n_out = n_out; p.epi = epi; p.group_ktiles = wkind == 0 ? 1 : (int)group_ktiles;
+    p.wkind = (int)wkind;
+    if (wkind != 0) {
+      p.w4 = (const uint8_t*)w.data_ptr();
+      p.w4_sz = (const uint32_t*)sz->data_ptr();
+      p.n_pad = n_rows;
+    }
     p.out = (__nv_bfloat16*)out.data_ptr(); p.ldo = (int)out.stride(0);
     p.ws = nullptr; p.counters = (int*)counters.data_ptr(); p.max_counters = 0;
     p.work = wl; p.work_count = cnt; p.work_capacity = cap;
     p.tn = tn; p.num_t_tiles = 1; p.num_n_tiles = 1; p.splits = 1; p.ktiles_per_split = Kd / 64;
-    oc::gemm_plan_stages(p, false);
-    int r = oc::gemm_launch(p, in.data_ptr(), (int)in.stride(0), w.data_ptr(), (int)w.stride(0), sm_count(), cur_stream());
+    oc::gemm_plan_stages(p, wkind != 0);
+    int r = oc::gemm_launch(p, in.data_ptr(), (int)in.stride(0), wkind == 0 ? w.data_ptr() : nullptr, wkind == 0 ? (int)w.stride(0) : 0, sm_count(),
+                            cur_stream());
     TORCH_CHECK(r == 0, "grouped gemm launch failed: ", r);
   };
-  run(xs, w13, a1, H, I2, I, oc::EPI_SILU_MUL, pp.work1, pp.work_count, max_tt * n1);
-  run(a1, w2, a2, I, H, H, oc::EPI_STORE, pp.work2, pp.work_count + 1, max_tt * n2);
+  run(xs, w13, w13_sz, (int)E_local * I2, a1, H, I2, I, oc::EPI_SILU_MUL, pp.work1, pp.work_count, max_tt * n1);
+  run(a1, w2, w2_sz, (int)E_local * H, a2, I, H, H, oc::EPI_STORE, pp.work2, pp.work_count + 1, max_tt * n2);
   rc = oc::moe_combine_launch(a2.data_ptr(), slot_of, topk_w.data_ptr<float>(), y.data_ptr(), T, k, H, cur_stream());
   TORCH_CHECK(rc == 0, "moe combine failed");
   return y;

@@ -1,6 +1,8 @@
 // out[t, n] = sum_k X[t, k] * W[n, k]  on tcgen05 tensor cores with TMEM accumulators.
 //
-// One persistent, warp-specialised kernel serves dense bf16 weights and 4-bit group-quantised (AWQ/GPTQ) weights:
+// One persistent, warp-specialised kernel serves dense bf16 weights and weight-only quantised layers whose weights are
+// dequantised to bf16 on their way into the tensor core: 4-bit integer with group scales and zero points (AWQ/GPTQ, WKIND 1),
+// FP8 e4m3 with block scales (WKIND 2) and FP4 e2m1 with power-of-two scales per 32 k (MXFP4, WKIND 3):
 //   * The weight tile (128 output features x 64 k) is UMMA operand A, so the 128 TMEM lanes are output features and
 //     the accumulator columns are tokens. The token tile TN (32..256) is UMMA N: decode batches and 8192-token
 //     prefill chunks run the same code, and a 4-bit weight tile is dequantised once per 128 x TN x 64 MMA block.
@@ -28,17 +30,20 @@ namespace {
 // so one group's shared-memory and TMEM latencies hide behind the other's arithmetic), four epilogue warps, and for 4-bit
 // weights one more warp that streams packed tiles.
 template <int WKIND> struct Roles {
-  static constexpr int kDqWarps = WKIND == 1 ? 8 : 0;
+  static constexpr int kDqWarps = WKIND >= 1 ? 8 : 0;
   static constexpr int kEpi0 = 2 + kDqWarps;          // first epilogue warp (2 or 10: both are 2 mod 4, the quarters line up)
   static constexpr int kPacked = kEpi0 + 4;           // packed-tile producer (4-bit only)
-  static constexpr int kThreads = (kEpi0 + 4 + (WKIND == 1 ? 1 : 0)) * 32;
+  static constexpr int kThreads = (kEpi0 + 4 + (WKIND >= 1 ? 1 : 0)) * 32;
 };
 constexpr int BM = 128;  // weight rows (output features) per tile = UMMA M
 constexpr int BK = 64;   // k per stage: one 128-byte swizzle atom of bf16
 constexpr int kWStageBytes = BM * BK * 2;   // 16 KB
-constexpr int kPackedBytes = BM * BK / 2;   // 4 KB of nibbles
-constexpr int kSzBytes = BM * 4;            // one (scale, zero) word per weight row
-constexpr int kPackedSlot = kPackedBytes + kSzBytes;  // ring slot: nibbles followed by that k tile's scales/zeros
+// packed 128 x 64 weight tile: 4 KB of nibbles (int4, fp4) or 8 KB of fp8 bytes, followed in its ring slot by one 32-bit
+// word per weight row: int4 -> bf16 scale | bf16 (128 + zero) << 16; fp8 -> bf16 (scale * 2^120); fp4 -> the bf16 scales
+// (* 2^126) of the tile's two 32-k groups
+__host__ __device__ constexpr int packed_bytes(int wkind) { return wkind == 2 ? BM * BK : BM * BK / 2; }
+constexpr int kSzBytes = BM * 4;
+__host__ __device__ constexpr int packed_slot(int wkind) { return packed_bytes(wkind) + kSzBytes; }
 constexpr int kTmemCols = 512;
 // 4-bit weights: the dequantised weight tiles form a ring in TMEM (32 columns per 128 x 64 tile) at the top of the 512 columns,
 // `stages` deep and in lock step with the X ring in shared memory: 8 tiles when the two accumulators fit 256 columns (token tile
@@ -47,7 +52,7 @@ constexpr int kTmemCols = 512;
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
 };
-__host__ __device__ inline SmemLayout make_layout(int tn, int xstages, int stages, int pstages) {
+__host__ __device__ inline SmemLayout make_layout(int tn, int xstages, int stages, int pstages, int wkind) {
   SmemLayout L;
   uint32_t o = 0;
   L.x_off = o;
@@ -55,7 +60,7 @@ __host__ __device__ inline SmemLayout make_layout(int tn, int xstages, int stage
   L.w_off = o;
   o += (pstages > 0 ? 0u : (uint32_t)stages * kWStageBytes);  // 4-bit weights are dequantised into TMEM, not shared memory
   L.p_off = o;
-  o += (uint32_t)pstages * kPackedSlot;
+  o += (uint32_t)pstages * packed_slot(wkind);
   L.bar_off = o;
   o += 1024;
   L.total = o;
@@ -67,6 +72,25 @@ __device__ __forceinline__ uint32_t dq_pair(uint32_t w, uint32_t zb2, uint32_t s
   uint32_t v = (w & 0x000f000fu) | 0x43004300u;
   __nv_bfloat162 r = __hmul2(__hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&zb2)),
                              *reinterpret_cast<__nv_bfloat162*>(&s2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Two fp8 e4m3 bytes of `w` (picked by the prmt selector into bits 8-15 and 24-31) -> bf16x2 * s2. The seven exponent and mantissa
+// bits land in the bf16 exponent/mantissa fields four places down, which reads as value * 2^-120 (also for e4m3 subnormals, which
+// become bf16 subnormals); the scale word carries the 2^120 back.
+__device__ __forceinline__ uint32_t dq_fp8_pair(uint32_t w, uint32_t sel, uint32_t s2) {
+  uint32_t t;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(w), "r"(0u), "r"(sel));
+  uint32_t v = (t & 0x80008000u) | ((t >> 4) & 0x07f007f0u);
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&s2));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Two fp4 e2m1 nibbles (bits 0-3 and 16-19 of w) -> bf16x2 * s2: sign to bit 15, the two exponent bits and the mantissa bit to
+// bits 8..6, which reads as value * 2^-126; the scale word carries the 2^126 back.
+__device__ __forceinline__ uint32_t dq_fp4_pair(uint32_t w, uint32_t s2) {
+  uint32_t v = ((w & 0x00080008u) << 12) | ((w & 0x00070007u) << 6);
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&s2));
   return *reinterpret_cast<uint32_t*>(&r);
 }
 
@@ -88,7 +112,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes the swizzle needs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  const SmemLayout L = make_layout(p.tn, p.xstages, p.stages, p.pstages);
+  constexpr int kPackedBytes = packed_bytes(WKIND), kPackedSlot = packed_slot(WKIND);
+  const SmemLayout L = make_layout(p.tn, p.xstages, p.stages, p.pstages, WKIND);
   uint8_t* sx = smem + L.x_off;
   uint8_t* sw = smem + L.w_off;
   uint8_t* sp = smem + L.p_off;
@@ -113,7 +138,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) {
-      mbar_init(&full[i], WKIND == 1 ? 5 : 1);  // the producer's expect_tx arrival (+ one per dequantisation warp of the group)
+      mbar_init(&full[i], WKIND >= 1 ? 5 : 1);  // the producer's expect_tx arrival (+ one per dequantisation warp of the group)
       mbar_init(&empty[i], 1);
     }
     for (int i = 0; i < PS; ++i) {
@@ -184,7 +209,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
   } else if (warp == Roles<WKIND>::kPacked) {
     // ------------------------------------------------------------------ packed-weight producer (runs PS tiles ahead)
-    if (WKIND == 1 && lane == 0) {
+    if (WKIND >= 1 && lane == 0) {
       Ring pr;
       bool ok = true;
       const int gk = p.group_ktiles;
@@ -233,7 +258,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
           const uint64_t db = umma_desc_sw128(b_base + s * xs);
-          if (WKIND == 1) {
+          if (WKIND >= 1) {
             const uint32_t ta = ta_base + s * 32;  // 64 k of bf16 = 32 columns per stage
 #pragma unroll
             for (int j = 0; j < BK / 16; ++j) {
@@ -257,7 +282,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
   } else if (warp < Roles<WKIND>::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
-    if (WKIND == 1) {
+    if (WKIND >= 1) {
       const int r = (warp & 3) * 32 + lane;  // weight row = TMEM lane this warp may write
       const int grp = (warp - 2) >> 2;       // 0: even k tiles of the CTA's sequence, 1: odd ones
       uint32_t seq = 0;
@@ -279,19 +304,41 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
           const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
-          const uint4 h0 = lds128(slot + r * 16), h1 = lds128(slot + 2048 + r * 16);
           const uint32_t szv = lds32(slot + kPackedBytes + r * 4);
-          const uint32_t s2 = (szv & 0xffffu) | (szv << 16);
-          const uint32_t zb2 = (szv >> 16) | (szv & 0xffff0000u);
-          const uint32_t words[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+          const uint32_t s2 = (szv & 0xffffu) | (szv << 16);          // low half replicated
+          const uint32_t zb2 = (szv >> 16) | (szv & 0xffff0000u);    // high half replicated
           uint32_t o[32];  // 64 bf16 of this row: column c holds k = 2c (low half) and 2c+1 (high half)
+          if (WKIND == 2) {
+            // fp8 tile: four chunks of [128 rows][16 bytes]; byte i of a row's chunk c is k = 16c + i
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {
-            const uint32_t q = words[c];
-            o[4 * c] = dq_pair(q, zb2, s2);
-            o[4 * c + 1] = dq_pair(q >> 4, zb2, s2);
-            o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
-            o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
+            for (int c = 0; c < 4; ++c) {
+              const uint4 h = lds128(slot + c * 2048 + r * 16);
+              const uint32_t w4[4] = {h.x, h.y, h.z, h.w};
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                o[8 * c + 2 * i] = dq_fp8_pair(w4[i], 0x1404u, s2);
+                o[8 * c + 2 * i + 1] = dq_fp8_pair(w4[i], 0x3424u, s2);
+              }
+            }
+          } else {
+            const uint4 h0 = lds128(slot + r * 16), h1 = lds128(slot + 2048 + r * 16);
+            const uint32_t words[8] = {h0.x, h0.y, h0.z, h0.w, h1.x, h1.y, h1.z, h1.w};
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t q = words[c];
+              if (WKIND == 1) {
+                o[4 * c] = dq_pair(q, zb2, s2);
+                o[4 * c + 1] = dq_pair(q >> 4, zb2, s2);
+                o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
+                o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
+              } else {  // words 0-3 are k 0..31 (first scale), words 4-7 are k 32..63 (second scale)
+                const uint32_t sc = c < 4 ? s2 : zb2;
+                o[4 * c] = dq_fp4_pair(q, sc);
+                o[4 * c + 1] = dq_fp4_pair(q >> 4, sc);
+                o[4 * c + 2] = dq_fp4_pair(q >> 8, sc);
+                o[4 * c + 3] = dq_fp4_pair(q >> 12, sc);
+              }
+            }
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&pempty[pr.idx]);  // the packed words are in registers (one arrival per warp, not per thread)
@@ -473,7 +520,7 @@ int make_tmap_bf16(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t co
 
 }  // namespace
 
-int gemm_smem_bytes(int tn, int xstages, int stages, int pstages) { return (int)make_layout(tn, xstages, stages, pstages).total + 1024; }
+int gemm_smem_bytes(const GemmParams& p) { return (int)make_layout(p.tn, p.xstages, p.stages, p.pstages, p.wkind).total + 1024; }
 
 // Picks the token tile, split-K factor and pipeline depths. Split-K spreads few-tile problems (decode) over all SMs.
 void gemm_plan(GemmParams& p, int num_sms, bool w4) {
@@ -537,21 +584,27 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   }
   int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
   int grid = total < num_sms ? total : num_sms;
-  int smem = gemm_smem_bytes(p.tn, p.xstages, p.stages, p.pstages);
-  static int configured[2] = {0, 0};
-  if (w4) {
-    if (configured[1] < smem) {
-      if (cudaFuncSetAttribute(gemm_wx_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
-      configured[1] = 227 * 1024;
+  if (w4 && p.wkind == 0) p.wkind = 1;  // packed weights without a stated kind are 4-bit integer
+  if (!w4) p.wkind = 0;
+  if (p.wkind < 0 || p.wkind > 3) return -6;
+  int smem = gemm_smem_bytes(p);
+  static bool configured[4] = {false, false, false, false};
+  auto launch = [&](auto kernel, int threads) -> int {
+    if (!configured[p.wkind]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
+      configured[p.wkind] = true;
     }
-    gemm_wx_kernel<1><<<grid, Roles<1>::kThreads, smem, stream>>>(tmX, tmW, p);
-  } else {
-    if (configured[0] < smem) {
-      if (cudaFuncSetAttribute(gemm_wx_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
-      configured[0] = 227 * 1024;
-    }
-    gemm_wx_kernel<0><<<grid, Roles<0>::kThreads, smem, stream>>>(tmX, tmW, p);
+    kernel<<<grid, threads, smem, stream>>>(tmX, tmW, p);
+    return 0;
+  };
+  int rc = 0;
+  switch (p.wkind) {
+    case 0: rc = launch(gemm_wx_kernel<0>, Roles<0>::kThreads); break;
+    case 1: rc = launch(gemm_wx_kernel<1>, Roles<1>::kThreads); break;
+    case 2: rc = launch(gemm_wx_kernel<2>, Roles<2>::kThreads); break;
+    default: rc = launch(gemm_wx_kernel<3>, Roles<3>::kThreads); break;
   }
+  if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

@@ -33,13 +33,15 @@ struct GemmParams {
   const int4* work;         // grouped mode: device-built work items (see gemm_sm100.cu); null for a dense GEMM
   const int* work_count;    // grouped mode: number of items, in device memory
   int work_capacity;        // grouped mode: upper bound of the item count (sizes the grid)
-  const uint8_t* w4;        // packed 4-bit tiles [n tile][k tile][4096 B]
-  const uint32_t* w4_sz;    // [group][n_pad] : bf16 scale | bf16 (128 + zero) << 16
+  const uint8_t* w4;        // packed weight tiles [n tile][k tile][4096 B (int4, fp4) or 8192 B (fp8)]; null for bf16 weights
+  const uint32_t* w4_sz;    // [group][n_pad] words: int4 bf16 scale | bf16 (128 + zero) << 16; fp8 bf16 (scale * 2^120);
+                            // fp4 bf16 scales (* 2^126) of the k tile's two 32-k groups
+  int wkind;                // 0 bf16 weights, 1 int4 with zero points (AWQ/GPTQ), 2 fp8 e4m3 block-scaled, 3 fp4 e2m1 (MXFP4)
 };
 
 void gemm_plan(GemmParams& p, int num_sms, bool w4);
 void gemm_plan_stages(GemmParams& p, bool w4);
-int gemm_smem_bytes(int tn, int xstages, int stages, int pstages);
+int gemm_smem_bytes(const GemmParams& p);
 int gemm_launch(const GemmParams& p, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream);
 unsigned int gemm_read_status(bool clear);
 

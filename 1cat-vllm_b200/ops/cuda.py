@@ -134,15 +134,108 @@ def prepare_bf16(layer) -> None:
     layer.kernel_state = dict(kind="bf16", n_rows=n_rows, n_out=n_out, epi=epi, K=w.shape[1])
 
 
+def _bf16_bits(x: torch.Tensor) -> torch.Tensor:
+    return x.to(torch.bfloat16).view(torch.int16).to(torch.int32) & 0xFFFF
+
+
+def pack_fp8(w8: torch.Tensor, row_scale: torch.Tensor, group: int):
+    """w8 ``[N,K]`` e4m3 (any 1-byte dtype), row_scale ``[N, K/group]`` fp32 (dequantisation scale of each row over each k group;
+    group a multiple of 64) → (tiles uint8 ``[N/128, K/64, 8192]``, sz int32 ``[K/group, Npad]``). A tile is four chunks of
+    ``[128 rows][16 bytes]`` (chunk c = k 16c..16c+15); the scale words are ``bf16(scale * 2**120)``: the kernel builds each bf16
+    from the fp8 bits with the exponent 120 too small."""
+    N, K = w8.shape
+    assert K % 64 == 0 and group % 64 == 0 and K % group == 0
+    npad = -(-N // 128) * 128
+    w8 = w8.contiguous().view(torch.uint8)
+    if npad != N:
+        w8 = torch.cat([w8, w8.new_zeros(npad - N, K)])
+        row_scale = torch.cat([row_scale, row_scale.new_zeros(npad - N, row_scale.shape[1])])
+    nt, kt = npad // 128, K // 64
+    tiles = w8.view(nt, 128, kt, 4, 16).permute(0, 2, 3, 1, 4).contiguous().view(nt, kt, 8192)
+    sc = row_scale.float() * (2.0 ** 120)
+    assert bool(torch.isfinite(sc.to(torch.bfloat16)).all()), "fp8 scale too large for the bf16 scale word"
+    sz = _bf16_bits(sc).t().contiguous()
+    return tiles, sz, npad
+
+
+def pack_mxfp4(packed: torch.Tensor, scales_ue8m0: torch.Tensor):
+    """packed ``[N, K/2]`` uint8 (low nibble = even k), scales ``[N, K/32]`` ue8m0 → (tiles uint8 ``[N/128, K/64, 4096]`` in the
+    4-bit tile layout of ``pack_w4``, sz int32 ``[K/64, Npad]`` with the two 32-k groups' ``bf16(2**(e-127) * 2**126)`` in the low
+    and high half)."""
+    N, K2 = packed.shape
+    K = K2 * 2
+    assert K % 64 == 0
+    npad = -(-N // 128) * 128
+    q = torch.stack([packed & 0xF, packed >> 4], dim=-1).reshape(N, K)
+    e = scales_ue8m0.to(torch.int32)
+    if npad != N:
+        q = torch.cat([q, q.new_zeros(npad - N, K)])
+        e = torch.cat([e, e.new_full((npad - N, e.shape[1]), 127)])
+    nt, kt = npad // 128, K // 64
+    qq = q.view(nt, 128, kt, 8, 8).to(torch.int32)
+    words = torch.zeros(nt, 128, kt, 8, dtype=torch.int32, device=q.device)
+    for i, k in enumerate(_NIB_ORDER):
+        words |= qq[..., k] << (4 * i)
+    tiles = words.view(nt, 128, kt, 2, 4).permute(0, 2, 3, 1, 4).contiguous().view(torch.uint8).view(nt, kt, 4096)
+    assert int(e.max()) <= 128, "MXFP4 scale above 2.0 does not fit the bf16 scale word"
+    sb = _bf16_bits(torch.exp2(e.float() - 1.0)).view(npad, kt, 2)
+    sz = (sb[..., 0] | (sb[..., 1] << 16)).t().contiguous()
+    return tiles, sz, npad
+
+
+def _fp8_row_scales(layer, block) -> tuple[torch.Tensor, int]:
+    """Per-row, per-k-group dequantisation scales of an FP8 linear layer and the k group size."""
+    N, K = layer.weight.shape
+    if block:
+        bn, bk = block
+        assert bk % 64 == 0, "fp8 k blocks must be multiples of 64"
+        return layer.weight_scale_inv.float().repeat_interleave(bn, dim=0)[:N].contiguous(), bk
+    ws = layer.weight_scale.float().reshape(-1)
+    if ws.numel() == 1:
+        return ws.expand(N).reshape(N, 1).contiguous(), K
+    rows = torch.cat([ws[i].expand(n) for i, n in enumerate(layer.local_output_sizes)])
+    return rows.reshape(N, 1).contiguous(), K
+
+
 def prepare_fp8(layer, block) -> None:
-    """FP8 checkpoints are expanded to bf16 once at load and served by the dense kernel."""
-    w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
-    _swap_to_dense(layer, w)
+    """FP8 e4m3 weights stay one byte each in HBM: tiles + scale words for the weight-only path of the tcgen05 GEMM
+    (dequantised to bf16 on the way into TMEM; activations stay bf16)."""
+    N, K = layer.weight.shape
+    if K % 64 or (block and (K % block[1] or block[1] % 64)):
+        w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
+        return _swap_to_dense(layer, w)
+    rs, group = _fp8_row_scales(layer, block)
+    w8 = layer.weight.data
+    n_rows, n_out, epi = N, N, EPI_STORE
+    if layer.fuse_silu_mul:
+        perm = interleave_gate_up(N // 2, w8.device)
+        w8, rs = w8.view(torch.uint8)[perm], rs[perm]
+        n_out, epi = N // 2, EPI_SILU_MUL
+    tiles, sz, npad = pack_fp8(w8, rs, group)
+    layer.kernel_state = dict(kind="w4", wkind=2, tiles=tiles, sz=sz, n_rows=n_rows, n_out=n_out, n_pad=npad, epi=epi, group_ktiles=group // 64, K=K)
+    for n in ("weight", "weight_scale", "weight_scale_inv"):
+        if hasattr(layer, n):
+            delattr(layer, n)
 
 
 def prepare_fp4(layer, kind: str) -> None:
-    w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
-    _swap_to_dense(layer, w)
+    """MXFP4 weights stay packed (tiles + power-of-two scale words, dequantised to bf16 on the way into TMEM); NVFP4 (e4m3 scales per
+    16 k and a global scale) is expanded to bf16 at load."""
+    N, K2 = layer.weight.shape
+    if kind != "mxfp4" or (K2 * 2) % 64:
+        w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
+        return _swap_to_dense(layer, w)
+    pk, sc = layer.weight.data, layer.weight_scale.data
+    n_rows, n_out, epi = N, N, EPI_STORE
+    if layer.fuse_silu_mul:
+        perm = interleave_gate_up(N // 2, pk.device)
+        pk, sc = pk[perm], sc[perm]
+        n_out, epi = N // 2, EPI_SILU_MUL
+    tiles, sz, npad = pack_mxfp4(pk.contiguous(), sc.contiguous())
+    layer.kernel_state = dict(kind="w4", wkind=3, tiles=tiles, sz=sz, n_rows=n_rows, n_out=n_out, n_pad=npad, epi=epi, group_ktiles=1, K=K2 * 2)
+    for n in ("weight", "weight_scale"):
+        if hasattr(layer, n):
+            delattr(layer, n)
 
 
 def _swap_to_dense(layer, w: torch.Tensor) -> None:
@@ -156,12 +249,12 @@ def _swap_to_dense(layer, w: torch.Tensor) -> None:
 
 
 # ----------------------------------------------------------------------------- GEMM
-def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0, push=None):
+def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0, push=None, wkind=1):
     """``push`` = (list of destination addresses, rows per owner): tensor-parallel epilogue that stores into peers' slabs."""
     global _LAUNCHES
     ws = workspace(x.device)
     _C.gemm(x, w, w4, sz, out, bias, ws.splitk, ws.counters, N, n_rows, n_out, n_pad, epi, gk, force_splits, force_tn,
-            push[0] if push else [], push[1] if push else 0)
+            push[0] if push else [], push[1] if push else 0, wkind if w4 is not None else 0)
     _LAUNCHES += 1
     return out
 
@@ -193,7 +286,8 @@ def linear(layer, x: torch.Tensor, out: Optional[torch.Tensor] = None, push=None
     if ks["kind"] == "w4":
         if _LIB_GEMM:
             raise RuntimeError("the library GEMM debug switch does not cover 4-bit weights")
-        return _gemm(x, None, ks["tiles"], ks["sz"], out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], ks["n_pad"], ks["epi"], ks["group_ktiles"], push=push)
+        return _gemm(x, None, ks["tiles"], ks["sz"], out, bias, ks["n_rows"], ks["n_rows"], ks["n_out"], ks["n_pad"], ks["epi"], ks["group_ktiles"], push=push,
+                     wkind=ks.get("wkind", 1))
     if _LIB_GEMM:
         y = torch.nn.functional.linear(x, layer.weight, bias)
         if ks["epi"] == EPI_SILU_MUL:  # rows are interleaved in blocks of 16
@@ -347,28 +441,43 @@ def gdn_commit(md, rec: list, n_valid: torch.Tensor) -> None:
 
 
 def prepare_moe(moe) -> None:
-    """Stack the local experts for the grouped GEMM: ``w13`` → bf16 ``[E*2I, H]`` with each expert's gate|up rows interleaved in
-    blocks of 16 (SiLU·mul happens in the GEMM epilogue), ``w2`` → bf16 ``[E*H, I]``. Block-scaled FP8 / MXFP4 expert checkpoints
-    are expanded to bf16 here."""
-    w13, w2 = moe.dequantized()
-    E, I2, H = w13.shape
+    """Stack the local experts for the grouped GEMM. bf16 experts: ``w13`` → ``[E*2I, H]`` with each expert's gate|up rows
+    interleaved in blocks of 16 (SiLU·mul happens in the GEMM epilogue), ``w2`` → ``[E*H, I]``. Block-scaled FP8 and MXFP4 experts
+    stay packed: tiles + scale words of the stacked matrices, dequantised inside the GEMM."""
+    E, I2 = moe.w13.shape[0], moe.w13.shape[1]
     I = I2 // 2
+    H = moe.w2.shape[1]
     if I2 % 128 or H % 128 or I % 64:
         moe.kernel_state = None  # odd shapes take the device-side PyTorch path
         return
-    perm = interleave_gate_up(I, w13.device)
-    w13s = w13.to(torch.bfloat16)[:, perm, :].reshape(E * I2, H).contiguous()
-    w2s = w2.to(torch.bfloat16).reshape(E * H, I).contiguous()
-    moe.kernel_state = dict(w13=w13s, w2=w2s)
+    perm = interleave_gate_up(I, moe.w13.device)
+    q = moe.qmethod
+    bn, bk = getattr(moe, "block", None) or (128, 128)
+    if q == "fp8" and bk % 64 == 0 and H % bk == 0 and I % bk == 0:
+        s13 = moe.w13_scale.float().repeat_interleave(bn, dim=1)[:, :I2][:, perm].reshape(E * I2, -1)
+        s2 = moe.w2_scale.float().repeat_interleave(bn, dim=1)[:, :H].reshape(E * H, -1)
+        t13, z13, _ = pack_fp8(moe.w13.data.view(torch.uint8)[:, perm].reshape(E * I2, H), s13.contiguous(), bk)
+        t2, z2, _ = pack_fp8(moe.w2.data.view(torch.uint8).reshape(E * H, I), s2.contiguous(), bk)
+        moe.kernel_state = dict(w13=t13, w2=t2, w13_sz=z13, w2_sz=z2, wkind=2, I2=I2, gk=bk // 64)
+    elif q == "mxfp4":
+        t13, z13, _ = pack_mxfp4(moe.w13.data[:, perm].reshape(E * I2, H // 2).contiguous(), moe.w13_scale.data[:, perm].reshape(E * I2, -1).contiguous())
+        t2, z2, _ = pack_mxfp4(moe.w2.data.reshape(E * H, I // 2).contiguous(), moe.w2_scale.data.reshape(E * H, -1).contiguous())
+        moe.kernel_state = dict(w13=t13, w2=t2, w13_sz=z13, w2_sz=z2, wkind=3, I2=I2, gk=1)
+    else:
+        w13, w2 = moe.dequantized()
+        w13s = w13.to(torch.bfloat16)[:, perm, :].reshape(E * I2, H).contiguous()
+        w2s = w2.to(torch.bfloat16).reshape(E * H, I).contiguous()
+        moe.kernel_state = dict(w13=w13s, w2=w2s, wkind=0)
+        if q == "none":  # the stacked copies replace the originals
+            moe._dq = None
+            moe.w13 = torch.nn.Parameter(w13s.view(E, I2, H), requires_grad=False)
+            moe.w2 = torch.nn.Parameter(w2s.view(E, H, I), requires_grad=False)
+            moe.kernel_state = dict(w13=moe.w13.view(E * I2, H), w2=moe.w2.view(E * H, I), wkind=0)
+            return
     moe._dq = None
-    if moe.qmethod != "none":
-        for n in ("w13", "w2", "w13_scale", "w2_scale"):
-            if hasattr(moe, n):
-                delattr(moe, n)
-    else:  # the stacked copies replace the originals
-        moe.w13 = torch.nn.Parameter(w13s.view(E, I2, H), requires_grad=False)
-        moe.w2 = torch.nn.Parameter(w2s.view(E, H, I), requires_grad=False)
-        moe.kernel_state = dict(w13=moe.w13.view(E * I2, H), w2=moe.w2.view(E * H, I))
+    for n in ("w13", "w2", "w13_scale", "w2_scale"):
+        if hasattr(moe, n):
+            delattr(moe, n)
 
 
 def route(logits, cfg, bias):
@@ -398,7 +507,7 @@ def fused_moe(moe, x, topk_w, topk_ids):
     if x.stride(-1) != 1 or (x.stride(0) * 2) % 16:
         x = x.contiguous()
     return _C.fused_moe(x, ks["w13"], ks["w2"], topk_w.contiguous().float(), topk_ids.contiguous().to(torch.int32), moe.E_local, moe.e_off,
-                        ws.splitk, ws.counters)
+                        ws.splitk, ws.counters, ks.get("wkind", 0), ks.get("w13_sz"), ks.get("w2_sz"), ks.get("I2", 0), ks.get("gk", 1))
 
 
 def mla_decode(q_abs, q_pe, latent_cache, md, scale, lora):

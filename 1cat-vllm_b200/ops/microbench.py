@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|attn|norm] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|norm|gdn|moe] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -156,23 +156,69 @@ def bench_gdn(rows: list, small: bool, iters: int, pk: dict) -> None:
 def bench_moe(rows: list, small: bool, iters: int, pk: dict) -> None:
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.ops import ref
-    for T, E, k, H, I in ([(256, 256, 8, 2048, 512)] if small else [(256, 256, 8, 2048, 512), (8192, 256, 8, 2048, 512), (64, 256, 8, 2048, 512)]):
-        x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
+    cases = [(256, 256, 8, 2048, 512)] if small else [(256, 256, 8, 2048, 512), (8192, 256, 8, 2048, 512), (64, 256, 8, 2048, 512)]
+    for kind in (("none",) if small else ("none", "fp8", "mxfp4")):
+        for T, E, k, H, I in cases:
+            x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16()
 
-        class M:
-            pass
-        m = M()
-        m.qmethod, m.E_local, m.e_off, m._dq = "none", E, 0, None
-        m.w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.03).bfloat16()
-        m.w2 = (torch.randn(E, H, I, device="cuda") * 0.03).bfloat16()
-        m.dequantized = lambda: (m.w13, m.w2)
-        K.prepare_moe(m)
-        tw, ti = ref.topk_softmax(torch.randn(T, E, device="cuda"), k, True)
-        ms = timeit(lambda: K.fused_moe(m, x, tw, ti), 1 if small else iters, 1 if small else 3)
-        flops = 2.0 * T * k * 3 * H * I
-        wbytes = min(E, T * k) * 3 * H * I * 2
-        rows.append(dict(kernel="fused_moe(bf16 experts)", T=T, E=E, k=k, H=H, I=I, ms=ms, tflops=flops / ms / 1e9, frac_of_peak=flops / ms / 1e9 / pk["bf16_tflops"],
-                         weight_gbs=wbytes / ms / 1e6))
+            class M:
+                pass
+            m = M()
+            m.qmethod, m.E_local, m.e_off, m._dq, m.block = kind, E, 0, None, (128, 128)
+            if kind == "none":
+                m.w13 = (torch.randn(E, 2 * I, H, device="cuda") * 0.03).bfloat16()
+                m.w2 = (torch.randn(E, H, I, device="cuda") * 0.03).bfloat16()
+                m.dequantized = lambda: (m.w13, m.w2)
+                wb = 2.0
+            elif kind == "fp8":
+                m.w13 = (torch.randn(E, 2 * I, H, device="cuda")).to(torch.float8_e4m3fn)
+                m.w2 = (torch.randn(E, H, I, device="cuda")).to(torch.float8_e4m3fn)
+                m.w13_scale = torch.full((E, 2 * I // 128, H // 128), 0.03, device="cuda")
+                m.w2_scale = torch.full((E, H // 128, I // 128), 0.03, device="cuda")
+                wb = 1.0
+            else:
+                m.w13 = torch.randint(0, 256, (E, 2 * I, H // 2), device="cuda", dtype=torch.uint8)
+                m.w2 = torch.randint(0, 256, (E, H, I // 2), device="cuda", dtype=torch.uint8)
+                m.w13_scale = torch.full((E, 2 * I, H // 32), 120, device="cuda", dtype=torch.uint8)
+                m.w2_scale = torch.full((E, H, I // 32), 120, device="cuda", dtype=torch.uint8)
+                wb = 0.5 + 1.0 / 32
+            K.prepare_moe(m)
+            tw, ti = ref.topk_softmax(torch.randn(T, E, device="cuda"), k, True)
+            ms = timeit(lambda: K.fused_moe(m, x, tw, ti), 1 if small else iters, 1 if small else 3)
+            flops = 2.0 * T * k * 3 * H * I
+            wbytes = min(E, T * k) * 3 * H * I * wb
+            rows.append(dict(kernel=f"fused_moe({'bf16' if kind == 'none' else kind} experts)", T=T, E=E, k=k, H=H, I=I, ms=ms, tflops=flops / ms / 1e9,
+                             frac_of_peak=flops / ms / 1e9 / pk["bf16_tflops"], weight_gbs=wbytes / ms / 1e6))
+            del m
+
+
+def bench_wq(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """Weight-only FP8 (128x128 block scales) and MXFP4 linears: DeepSeek-V3-class shapes (hidden 7168)."""
+    from onecat_vllm.ops import cuda as K
+    cases = [(64, 7168, 7168), (64, 36864, 7168), (8192, 7168, 7168)]
+    if small:
+        cases = cases[:1]
+    for kind in ("fp8", "mxfp4"):
+        for T, N, Kd in cases:
+            layer = _L(False)
+            if kind == "fp8":
+                layer.weight = torch.nn.Parameter(torch.randn(N, Kd, device="cuda").to(torch.float8_e4m3fn), requires_grad=False)
+                layer.weight_scale_inv = torch.nn.Parameter(torch.full((N // 128, Kd // 128), 0.02, device="cuda"), requires_grad=False)
+                K.prepare_fp8(layer, (128, 128))
+                wbytes = N * Kd + N * (Kd // 128) * 4
+            else:
+                layer.weight = torch.nn.Parameter(torch.randint(0, 256, (N, Kd // 2), device="cuda", dtype=torch.uint8), requires_grad=False)
+                layer.weight_scale = torch.nn.Parameter(torch.full((N, Kd // 32), 120, device="cuda", dtype=torch.uint8), requires_grad=False)
+                K.prepare_fp4(layer, "mxfp4")
+                wbytes = N * Kd / 2 + N * (Kd // 64) * 4
+            x = torch.randn(T, Kd, device="cuda").bfloat16()
+            out = torch.empty(T, N, device="cuda", dtype=torch.bfloat16)
+            ms = timeit(lambda: K.linear(layer, x, out=out), 1 if small else iters, 1 if small else 3)
+            bytes_ = wbytes + T * Kd * 2 + out.numel() * 2
+            tf = 2.0 * T * N * Kd / ms / 1e9
+            rows.append(dict(kernel=f"gemm_{kind}_weight_only", T=T, N=N, K=Kd, ms=ms, gbs=bytes_ / ms / 1e6, frac_of_hbm=bytes_ / ms / 1e6 / pk["hbm_gbs"],
+                             tflops=tf, frac_of_peak=tf / pk["bf16_tflops"]))
+            del layer, x, out
 
 
 def main() -> None:
@@ -184,7 +230,7 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe)):
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq)):
         if a.only and a.only != name:
             continue
         fn(rows, a.small, a.iters, pk)

@@ -147,6 +147,121 @@ def test_gemm_w4(T, fuse):
     _close(y, e, 3e-2, 3e-2, f"w4 T={T} fuse={fuse}")
 
 
+class _Fp8Layer(_FakeLayer):
+    pass
+
+
+@pytest.mark.parametrize("T", [1, 64, 200, 700])
+@pytest.mark.parametrize("fuse,block", [(False, (128, 128)), (True, (128, 128)), (False, None)])
+def test_gemm_fp8_weight_only(T, fuse, block):
+    """FP8 e4m3 weights (block-scaled 128x128, or one scale per merged output) dequantised inside the GEMM, against the fp32
+    product with the dequantised weights. All 256 byte patterns except NaN occur, e4m3 subnormals included."""
+    N, Kd = 1024, 768
+    g = torch.Generator(device="cuda").manual_seed(5)
+    codes = torch.randint(0, 256, (N, Kd), device="cuda", generator=g, dtype=torch.uint8)
+    codes[(codes & 0x7F) == 0x7F] = 0x3C  # no NaN patterns
+    w8 = codes.view(torch.float8_e4m3fn)
+    layer = _Fp8Layer(fuse)
+    layer.weight = torch.nn.Parameter(w8.clone(), requires_grad=False)
+    if block:
+        sc = torch.rand(N // 128, Kd // 128, device="cuda", generator=g) * 2e-4 + 1e-5
+        layer.weight_scale_inv = torch.nn.Parameter(sc, requires_grad=False)
+        wd = ref.fp8_block_dequantize(w8, sc, block)
+    else:
+        layer.local_output_sizes = [N // 2, N // 2]
+        sc = torch.tensor([3e-4, 1e-4], device="cuda")
+        layer.weight_scale = torch.nn.Parameter(sc, requires_grad=False)
+        wd = torch.cat([w8[: N // 2].float() * sc[0], w8[N // 2:].float() * sc[1]])
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    K().prepare_fp8(layer, block)
+    assert layer.kernel_state["wkind"] == 2 and not hasattr(layer, "weight")
+    y = K().linear(layer, x)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    sb = (sc if block else sc.view(2, 1)).float() * 2.0 ** 120
+    # the kernel multiplies by the bf16-rounded scale and rounds the weight to bf16
+    rs = (sb.bfloat16().float() / 2.0 ** 120)
+    if block:
+        wk = ref.fp8_block_dequantize(w8, rs, block)
+    else:
+        wk = torch.cat([w8[: N // 2].float() * rs[0], w8[N // 2:].float() * rs[1]])
+    e = x.float().cpu() @ wk.bfloat16().float().cpu().t()
+    if fuse:
+        e = torch.nn.functional.silu(e[:, : N // 2]) * e[:, N // 2:]
+    _close(y, e, 3e-2, 3e-2, f"fp8 T={T} fuse={fuse} block={block}")
+    # and stays close to the exact-scale product
+    e2 = x.float().cpu() @ wd.float().cpu().t()
+    if fuse:
+        e2 = torch.nn.functional.silu(e2[:, : N // 2]) * e2[:, N // 2:]
+    _close(y, e2, 5e-2, 5e-2, "fp8 vs exact scales")
+
+
+@pytest.mark.parametrize("T", [1, 64, 300])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_gemm_mxfp4_weight_only(T, fuse):
+    """MXFP4 (e2m1 nibbles, one ue8m0 scale per 32 k) dequantised inside the GEMM: every nibble value, 0.5 included, and scales
+    over a range of exponents; exact in bf16, so only accumulation order differs from the fp32 product."""
+    N, Kd = 512, 640
+    g = torch.Generator(device="cuda").manual_seed(6)
+    packed = torch.randint(0, 256, (N, Kd // 2), device="cuda", generator=g, dtype=torch.uint8)
+    sc = torch.randint(110, 124, (N, Kd // 32), device="cuda", generator=g, dtype=torch.uint8)
+    layer = _FakeLayer(fuse)
+    layer.weight = torch.nn.Parameter(packed.clone(), requires_grad=False)
+    layer.weight_scale = torch.nn.Parameter(sc.clone(), requires_grad=False)
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    K().prepare_fp4(layer, "mxfp4")
+    assert layer.kernel_state["wkind"] == 3
+    y = K().linear(layer, x)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    wd = ref.mxfp4_dequantize(packed, sc)
+    e = x.float().cpu() @ wd.float().cpu().t()
+    if fuse:
+        e = torch.nn.functional.silu(e[:, : N // 2]) * e[:, N // 2:]
+    _close(y, e, 2e-2, 2e-2, f"mxfp4 T={T} fuse={fuse}")
+
+
+@pytest.mark.parametrize("kind", ["fp8", "mxfp4"])
+@pytest.mark.parametrize("T,E,k", [(1, 8, 2), (40, 32, 8), (300, 8, 2)])
+def test_fused_moe_packed_experts(kind, T, E, k):
+    """Grouped GEMMs over packed FP8 (128x128 block scales) / MXFP4 expert weights against per-expert fp32 FFNs on the
+    dequantised weights."""
+    H, I = 256, 128
+    g = torch.Generator(device="cuda").manual_seed(T + E)
+    x = (torch.randn(T, H, device="cuda", generator=g) * 0.5).bfloat16()
+    logits = torch.randn(T, E, device="cuda", generator=g)
+    tw, ti = ref.topk_softmax(logits, k, True)
+
+    class M:
+        pass
+    m = M()
+    m.qmethod, m.E_local, m.e_off, m._dq, m.block = kind, E, 0, None, (128, 128)
+    if kind == "fp8":
+        c13 = torch.randint(0, 256, (E, 2 * I, H), device="cuda", generator=g, dtype=torch.uint8)
+        c2 = torch.randint(0, 256, (E, H, I), device="cuda", generator=g, dtype=torch.uint8)
+        for c in (c13, c2):
+            c[(c & 0x7F) == 0x7F] = 0x30
+            c &= 0xBF  # keep |w| < 2 so the FFN output stays in a sane range
+        m.w13, m.w2 = c13.view(torch.float8_e4m3fn), c2.view(torch.float8_e4m3fn)
+        m.w13_scale = torch.rand(E, 2 * I // 128, H // 128, device="cuda", generator=g) * 0.05 + 0.01
+        m.w2_scale = torch.rand(E, H // 128, I // 128, device="cuda", generator=g) * 0.05 + 0.01
+        w13 = ref.fp8_block_dequantize(m.w13, m.w13_scale, m.block)
+        w2 = ref.fp8_block_dequantize(m.w2, m.w2_scale, m.block)
+    else:
+        m.w13 = torch.randint(0, 256, (E, 2 * I, H // 2), device="cuda", generator=g, dtype=torch.uint8)
+        m.w2 = torch.randint(0, 256, (E, H, I // 2), device="cuda", generator=g, dtype=torch.uint8)
+        m.w13_scale = torch.randint(118, 122, (E, 2 * I, H // 32), device="cuda", generator=g, dtype=torch.uint8)
+        m.w2_scale = torch.randint(118, 122, (E, H, I // 32), device="cuda", generator=g, dtype=torch.uint8)
+        w13, w2 = ref.mxfp4_dequantize(m.w13, m.w13_scale), ref.mxfp4_dequantize(m.w2, m.w2_scale)
+    K().prepare_moe(m)
+    assert m.kernel_state is not None and m.kernel_state["wkind"] == (2 if kind == "fp8" else 3) and not hasattr(m, "w13")
+    y = K().fused_moe(m, x, tw, ti)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0 and "fused_moe" not in K().TORCH_STANDINS
+    e = ref.fused_experts(x.cpu(), w13.float().cpu(), w2.float().cpu(), tw.cpu(), ti.cpu(), 0)
+    _close(y, e, 4e-2, 1e-2, f"moe {kind} T={T} E={E}")
+
+
 def test_awq_layer_matches_reference_dequant():
     """AWQ checkpoint layout (int32 [K, N/8], nibble order 0,4,1,5,2,6,3,7) through the layer's repacking."""
     from onecat_vllm.config import QuantConfig

@@ -89,3 +89,37 @@ def test_awq_checkpoint_matches_dequantised_weights(tmp_path):
     b = LLM(model=str(tmp_path / "dense"), device="cpu", dtype="float32", max_model_len=128)
     assert [o.outputs[0].token_ids for o in a.generate(p, sp)] == [o.outputs[0].token_ids for o in b.generate(p, sp)]
     a.shutdown(); b.shutdown()
+
+
+def test_weight_packers_keep_every_value_addressable():
+    """The tile layouts of the FP8 and MXFP4 packers: byte / nibble (n, k) of the source lands where the kernel reads it, and
+    the scale words carry the bf16 bits of scale * 2**120 (fp8) and 2**(e - 1) (fp4)."""
+    import torch
+    from onecat_vllm.ops.cuda import _NIB_ORDER, pack_fp8, pack_mxfp4
+    N, K = 256, 192
+    g = torch.Generator().manual_seed(0)
+    w8 = torch.randint(0, 256, (N, K), generator=g, dtype=torch.uint8)
+    rs = torch.rand(N, K // 64, generator=g) * 1e-3 + 1e-5
+    tiles, sz, npad = pack_fp8(w8, rs, 64)
+    assert tiles.shape == (2, 3, 8192) and sz.shape == (3, 256) and npad == 256
+    for n, k in [(0, 0), (5, 17), (130, 63), (255, 191), (129, 64)]:
+        nt, r, kt, kk = n // 128, n % 128, k // 64, k % 64
+        assert int(tiles[nt, kt, (kk // 16) * 2048 + r * 16 + kk % 16]) == int(w8[n, k])
+        want = (rs[n, kt] * 2.0 ** 120).to(torch.bfloat16).view(torch.int16).int() & 0xFFFF
+        assert int(sz[kt, n]) == int(want)
+    packed = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+    e = torch.randint(100, 128, (N, K // 32), generator=g, dtype=torch.uint8)
+    t4, sz4, _ = pack_mxfp4(packed, e)
+    assert t4.shape == (2, 3, 4096) and sz4.shape == (3, 256)
+    words = t4.view(2, 3, 2, 128, 4, 4)  # [nt][kt][half][row][word][byte]
+    for n, k in [(0, 0), (3, 9), (200, 100), (255, 191)]:
+        nt, r, kt, kk = n // 128, n % 128, k // 64, k % 64
+        c, j = kk // 8, kk % 8
+        b = words[nt, kt, c // 4, r, c % 4]
+        word = int(b[0]) | int(b[1]) << 8 | int(b[2]) << 16 | int(b[3]) << 24
+        nib = (word >> (4 * _NIB_ORDER.index(j))) & 0xF
+        src = int(packed[n, k // 2])
+        assert nib == ((src >> 4) if k % 2 else (src & 0xF))
+        half = (int(sz4[kt, n]) >> (16 * (kk // 32))) & 0xFFFF
+        want = torch.tensor(2.0 ** (int(e[n, k // 32]) - 1)).to(torch.bfloat16).view(torch.int16).int() & 0xFFFF
+        assert half == int(want)

@@ -229,7 +229,8 @@ void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out,
     p.ws_ml = ws_ml->data_ptr<float>();
   }
   if (p.T == 0 || p.R == 0) return;
-  int rc = oc::attention_launch(p, (int)mode, cur_stream());
+  // mode 0: mma.sync prefill, 1: decode / short verify queries, 2: tcgen05 prefill (D = 128, query tiles of 128 tokens)
+  int rc = mode == 2 ? oc::attention_prefill_tc_launch(p, kv_cache.size(0), cur_stream()) : oc::attention_launch(p, (int)mode, cur_stream());
   TORCH_CHECK(rc == 0, "attention launch failed with code ", rc);
 }
 
@@ -467,7 +468,7 @@ torch::Tensor mla_decode(torch::Tensor q_abs, torch::Tensor q_rope, torch::Tenso
 }
 
 int64_t read_status(bool clear) {
-  return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) |
+  return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) | oc::attention_tc_read_status(clear) |
                    oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear) | oc::moe_read_status(clear) | oc::mla_read_status(clear));
 }
 

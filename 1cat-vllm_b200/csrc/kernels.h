@@ -50,6 +50,9 @@ struct AttnParams {
 // (decode and short verify queries, with split-KV + combine).
 int attention_launch(const AttnParams& p, int mode, cudaStream_t st);
 unsigned int attention_read_status(bool clear);
+// tcgen05 prefill (attention_tc.cu): D == 128, 128-token query tiles; num_q_tiles counts those tiles.
+int attention_prefill_tc_launch(const AttnParams& p, long long num_blocks, cudaStream_t st);
+unsigned int attention_tc_read_status(bool clear);
 
 
 struct RowStats {

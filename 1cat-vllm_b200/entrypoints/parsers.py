@@ -1,6 +1,7 @@
 """Reasoning and tool-call parsers for chat responses, streaming and non-streaming
 (reference: vllm/reasoning/abs_reasoning_parsers.py:26,189; vllm/tool_parsers/abstract_tool_parser.py:43,192; model parsers
-hermes_tool_parser.py, qwen3coder_tool_parser.py, deepseekv3_tool_parser.py, deepseek_r1_reasoning_parser.py).
+hermes_tool_parser.py, qwen3coder_tool_parser.py, deepseekv3_tool_parser.py, deepseek_r1_reasoning_parser.py; the other
+registered names follow the published output formats of the respective model families).
 
 Both kinds work on text. Streaming variants are fed the accumulated text and return the delta that may be shown, holding
 back anything that could still turn out to be the start of a tag."""
@@ -49,8 +50,47 @@ class ReasoningParser:
         return r or "", c or ""
 
 
+class TaggedReasoningParser(ReasoningParser):
+    """Same splitter with other tag strings (Mistral ``[THINK]``, Seed-OSS ``<seed:think>``)."""
+
+    def __init__(self, start: str, end: str, assume_open: bool = False):
+        super().__init__(assume_open)
+        self.start, self.end = start, end
+
+
+class PhraseReasoningParser(ReasoningParser):
+    """Granite-style: reasoning and answer are introduced by fixed phrases instead of tags."""
+
+    def __init__(self, think: tuple = ("Here is my thought process:", "Here's my thought process:"),
+                 answer: tuple = ("Here is my response:", "Here's my response:")):
+        super().__init__(False)
+        self.think, self.answer = think, answer
+
+    def extract(self, text):
+        ti = min((i for i in (text.find(t) for t in self.think) if i != -1), default=-1)
+        if ti == -1:
+            return None, text or None
+        tlen = next(len(t) for t in self.think if text.startswith(t, ti))
+        rest = text[ti + tlen:]
+        ai = min((i for i in (rest.find(t) for t in self.answer) if i != -1), default=-1)
+        if ai == -1:
+            return rest.strip() or None, None
+        alen = next(len(t) for t in self.answer if rest.startswith(t, ai))
+        return rest[:ai].strip() or None, rest[ai + alen:].strip() or None
+
+    def _split_partial(self, text):
+        r, c = self.extract(text)
+        return r or "", c or ""
+
+
 REASONING_PARSERS = {"qwen3": lambda: ReasoningParser(False), "deepseek_r1": lambda: ReasoningParser(True),
-                     "deepseek_v3": lambda: ReasoningParser(False), "think": lambda: ReasoningParser(False)}
+                     "deepseek_v3": lambda: ReasoningParser(False), "think": lambda: ReasoningParser(False),
+                     "glm45": lambda: ReasoningParser(False), "ernie45": lambda: ReasoningParser(True), "step3": lambda: ReasoningParser(True),
+                     "minimax_m2": lambda: ReasoningParser(True), "olmo3": lambda: ReasoningParser(False), "kimi_k2": lambda: ReasoningParser(False),
+                     "mistral": lambda: TaggedReasoningParser("[THINK]", "[/THINK]"),
+                     "seed_oss": lambda: TaggedReasoningParser("<seed:think>", "</seed:think>"),
+                     "hunyuan_a13b": lambda: TaggedReasoningParser("<think>", "</think>"),
+                     "granite": lambda: PhraseReasoningParser()}
 
 
 # ----------------------------------------------------------------------------- tools
@@ -146,8 +186,189 @@ class DeepSeekV3ToolParser(ToolParser):
         return text[: text.find(self.B)].strip() or None, calls
 
 
-TOOL_PARSERS = {"hermes": HermesToolParser, "qwen3_coder": Qwen3CoderToolParser, "qwen3_xml": Qwen3CoderToolParser,
-                "deepseek_v3": DeepSeekV3ToolParser, "deepseek_v31": DeepSeekV3ToolParser}
+class DeepSeekV31ToolParser(ToolParser):
+    """V3.1 drops the ``function`` prefix and the code fence: ``<｜tool▁call▁begin｜>name<｜tool▁sep｜>{json}<｜tool▁call▁end｜>``."""
+
+    B = "<｜tool▁calls▁begin｜>"
+    markers = (B,)
+    _re = re.compile(r"<｜tool▁call▁begin｜>(.*?)<｜tool▁sep｜>(.*?)<｜tool▁call▁end｜>", re.S)
+
+    def extract(self, text):
+        calls = []
+        for m in self._re.finditer(text):
+            name, args = m.group(1).strip(), m.group(2).strip()
+            if name == "function":  # V3 layout: function<sep>name\n```json ... ```
+                return DeepSeekV3ToolParser().extract(text)
+            calls.append(ToolCall(name, args))
+        if not calls:
+            return text, []
+        return text[: text.find(self.B)].strip() or None, calls
+
+
+def _calls_from_json(obj, name_keys=("name",), arg_keys=("arguments", "parameters")) -> list:
+    items = obj if isinstance(obj, list) else [obj]
+    calls = []
+    for d in items:
+        if not isinstance(d, dict):
+            continue
+        if "function" in d and isinstance(d["function"], dict):
+            d = d["function"]
+        name = next((d[k] for k in name_keys if k in d), None)
+        if not isinstance(name, str):
+            continue
+        args = next((d[k] for k in arg_keys if k in d), {})
+        calls.append(ToolCall(name, args if isinstance(args, str) else json.dumps(args, ensure_ascii=False)))
+    return calls
+
+
+def _json_values(text: str):
+    """Decode consecutive JSON values in ``text`` (separated by whitespace, ``;`` or ``,``)."""
+    dec, i, out = json.JSONDecoder(), 0, []
+    while i < len(text):
+        while i < len(text) and text[i] in " \t\r\n;,":
+            i += 1
+        if i >= len(text):
+            break
+        try:
+            v, j = dec.raw_decode(text, i)
+        except json.JSONDecodeError:
+            break
+        out.append(v)
+        i = j
+    return out
+
+
+class MarkerJsonToolParser(ToolParser):
+    """Tool calls as JSON (an object, a list, or several values) after a start marker, optionally closed by an end marker.
+    Covers Mistral ``[TOOL_CALLS]``, Granite ``<|tool_call|>`` / ``<tool_call>``, Jamba and Hunyuan ``<tool_calls>…</tool_calls>``,
+    Phi-4-mini ``functools``, InternLM ``<|action_start|><|plugin|>…<|action_end|>``, MiniMax line-separated objects."""
+
+    def __init__(self, starts: tuple, end: Optional[str] = None):
+        self.markers, self.end = tuple(starts), end
+
+    def extract(self, text):
+        i, m = min(((text.find(m), m) for m in self.markers if text.find(m) != -1), default=(-1, None))
+        if i == -1:
+            return text, []
+        body = text[i + len(m):]
+        if self.end and self.end in body:
+            body = body[: body.find(self.end)]
+        calls = []
+        for v in _json_values(body):
+            calls += _calls_from_json(v)
+        if not calls:
+            return text, []
+        return text[:i].strip() or None, calls
+
+
+class Llama3JsonToolParser(ToolParser):
+    """Llama 3.x / 4 JSON tool calls: the whole answer is one or more ``{"name": …, "parameters": …}`` objects separated by
+    ``;``, optionally after ``<|python_tag|>``."""
+
+    markers = ("<|python_tag|>", "{")
+
+    def extract(self, text):
+        body = text.strip()
+        if body.startswith("<|python_tag|>"):
+            body = body[len("<|python_tag|>"):]
+        if not body.lstrip().startswith(("{", "[")):
+            return text, []
+        calls = []
+        for v in _json_values(body):
+            calls += _calls_from_json(v)
+        return (None, calls) if calls else (text, [])
+
+    def content_so_far(self, text):
+        t = text.lstrip()
+        return "" if (not t or t.startswith(("{", "[", "<|python_tag|>")) or "<|python_tag|>".startswith(t)) else text
+
+
+class PythonicToolParser(ToolParser):
+    """``[get_weather(city="Paris"), f(x=1)]`` (Llama 4 pythonic, OLMo 3): parsed with ``ast``, literals only."""
+
+    markers = ("[",)
+
+    def extract(self, text):
+        import ast
+        body = text.strip()
+        if not (body.startswith("[") and body.endswith("]")):
+            return text, []
+        try:
+            tree = ast.parse(body, mode="eval")
+        except SyntaxError:
+            return text, []
+        if not isinstance(tree.body, ast.List) or not tree.body.elts:
+            return text, []
+        calls = []
+        for e in tree.body.elts:
+            if not isinstance(e, ast.Call) or e.args:
+                return text, []
+            name = ast.unparse(e.func)
+            try:
+                args = {k.arg: ast.literal_eval(k.value) for k in e.keywords}
+            except (ValueError, SyntaxError):
+                return text, []
+            calls.append(ToolCall(name, json.dumps(args, ensure_ascii=False)))
+        return None, calls
+
+    def content_so_far(self, text):
+        return "" if text.lstrip().startswith("[") or not text.strip() else text
+
+
+class KimiK2ToolParser(ToolParser):
+    B = "<|tool_calls_section_begin|>"
+    markers = (B,)
+    _re = re.compile(r"<\|tool_call_begin\|>\s*(?:functions\.)?([\w\.\-]+?)(?::\d+)?\s*<\|tool_call_argument_begin\|>\s*(.*?)\s*<\|tool_call_end\|>", re.S)
+
+    def extract(self, text):
+        calls = [ToolCall(m.group(1), m.group(2)) for m in self._re.finditer(text)]
+        if not calls:
+            return text, []
+        return text[: text.find(self.B)].strip() or None, calls
+
+
+class Glm45ToolParser(ToolParser):
+    """``<tool_call>name\n<arg_key>k</arg_key>\n<arg_value>v</arg_value>…</tool_call>``."""
+
+    markers = ("<tool_call>",)
+    _call = re.compile(r"<tool_call>\s*([^\n<]+)\s*(.*?)(?:</tool_call>|$)", re.S)
+    _kv = re.compile(r"<arg_key>(.*?)</arg_key>\s*<arg_value>(.*?)</arg_value>", re.S)
+
+    def extract(self, text):
+        calls = []
+        for m in self._call.finditer(text):
+            args = {}
+            for k, v in self._kv.findall(m.group(2)):
+                v = v.strip()
+                try:
+                    args[k.strip()] = json.loads(v)
+                except json.JSONDecodeError:
+                    args[k.strip()] = v
+            calls.append(ToolCall(m.group(1).strip(), json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return text[: text.find("<tool_call>")].strip() or None, calls
+
+
+class SeedOssToolParser(Qwen3CoderToolParser):
+    markers = ("<seed:tool_call>", "<function=")
+
+
+TOOL_PARSERS = {
+    "hermes": HermesToolParser, "qwen3_coder": Qwen3CoderToolParser, "qwen3_xml": Qwen3CoderToolParser,
+    "deepseek_v3": DeepSeekV3ToolParser, "deepseek_v31": DeepSeekV31ToolParser,
+    "llama3_json": Llama3JsonToolParser, "llama4_json": Llama3JsonToolParser, "pythonic": PythonicToolParser, "llama4_pythonic": PythonicToolParser,
+    "olmo3": PythonicToolParser, "kimi_k2": KimiK2ToolParser, "glm45": Glm45ToolParser, "glm47": Glm45ToolParser, "seed_oss": SeedOssToolParser,
+    "mistral": lambda: MarkerJsonToolParser(("[TOOL_CALLS]",)),
+    "granite": lambda: MarkerJsonToolParser(("<|tool_call|>", "<tool_call>")),
+    "granite-20b-fc": lambda: MarkerJsonToolParser(("<function_call>",)),
+    "jamba": lambda: MarkerJsonToolParser(("<tool_calls>",), "</tool_calls>"),
+    "hunyuan_a13b": lambda: MarkerJsonToolParser(("<tool_calls>",), "</tool_calls>"),
+    "minimax": lambda: MarkerJsonToolParser(("<tool_calls>",), "</tool_calls>"),
+    "phi4_mini_json": lambda: MarkerJsonToolParser(("functools",)),
+    "internlm": lambda: MarkerJsonToolParser(("<|action_start|><|plugin|>",), "<|action_end|>"),
+    "xlam": lambda: MarkerJsonToolParser(("```json", "[TOOL_CALLS]", "<tool_call>", "[")),
+}
 
 
 def get_tool_parser(name: Optional[str]) -> Optional[ToolParser]:

@@ -34,6 +34,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_RPC_RING_CHUNKS": _i("ONECAT_RPC_RING_CHUNKS", 8),
     # kernels
     "ONECAT_GEMM_BACKEND": _s("ONECAT_GEMM_BACKEND", "tcgen05"),  # "tcgen05" | "library" (debug only)
+    "ONECAT_ATTN_PREFILL": _s("ONECAT_ATTN_PREFILL", "tcgen05"),  # head size 128 prefill attention: "tcgen05" | "mma"
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
     "ONECAT_TP_PUSH": _s("ONECAT_TP_PUSH", "auto"),  # GEMM epilogue pushes partial tiles to peers: auto | always | never
     "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),

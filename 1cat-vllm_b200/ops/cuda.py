@@ -22,6 +22,7 @@ EPI_STORE, EPI_SILU_MUL = 0, 1
 TORCH_STANDINS: set = set()  # names of ops that ran as device-side PyTorch code in this process
 _LAUNCHES = 0  # launches of our own kernels (for bench accounting)
 _LIB_GEMM = os.environ.get("ONECAT_GEMM_BACKEND", "tcgen05") == "library"  # debug switch only
+_ATTN_PREFILL_TC = os.environ.get("ONECAT_ATTN_PREFILL", "tcgen05") != "mma"  # head size 128 prefill: tcgen05 kernel unless "mma"
 
 
 def launches() -> int:
@@ -398,8 +399,14 @@ def paged_attention(q, kv_cache, md, scale, out=None, lse=None):
                            md.max_query_len, short, ws_o, ws_ml)
         _LAUNCHES += 2 if splits > 1 else 1
     if tiles:
-        _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 0, tiles, 1,
-                           md.max_query_len, short, None, None)
+        if D == 128 and q.stride(1) == D and _ATTN_PREFILL_TC:
+            # tcgen05 kernel: 128-token query tiles per (request, head)
+            tiles_tc = sum(-(-x // 128) for x in md.query_lens_cpu if x > short)
+            _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 2, tiles_tc, 1,
+                               md.max_query_len, short, None, None)
+        else:
+            _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 0, tiles, 1,
+                               md.max_query_len, short, None, None)
         _LAUNCHES += 1
     return out
 

@@ -101,3 +101,43 @@ def test_pooling_routes(client):
     s = client.post("/score", json={"text_1": "hello world", "text_2": ["hello world", "zzz"]}).json()
     assert abs(s["data"][0]["score"] - 1.0) < 1e-4 and s["data"][1]["score"] < 0.9999
     assert client.post("/v1/embeddings", json={"input": "x", "pooling_type": "bogus"}).status_code == 400
+
+
+def test_more_tool_and_reasoning_parsers():
+    from onecat_vllm.entrypoints.parsers import TOOL_PARSERS, get_reasoning_parser, get_tool_parser
+    assert len(TOOL_PARSERS) >= 20
+    one = lambda name, text: get_tool_parser(name).extract(text)
+    c, calls = one("mistral", 'ok [TOOL_CALLS] [{"name": "f", "arguments": {"a": 1}}, {"name": "g", "arguments": {}}]')
+    assert c == "ok" and [x.name for x in calls] == ["f", "g"] and json.loads(calls[0].arguments) == {"a": 1}
+    c, calls = one("llama3_json", '<|python_tag|>{"name": "f", "parameters": {"x": "y"}}; {"name": "h", "parameters": {}}')
+    assert c is None and [x.name for x in calls] == ["f", "h"] and json.loads(calls[0].arguments) == {"x": "y"}
+    assert one("llama3_json", "just text")[1] == []
+    c, calls = one("pythonic", '[get_weather(city="Paris", days=3), ping()]')
+    assert [x.name for x in calls] == ["get_weather", "ping"] and json.loads(calls[0].arguments) == {"city": "Paris", "days": 3}
+    assert one("pythonic", "[1, 2]")[1] == []
+    k = 'pre<|tool_calls_section_begin|><|tool_call_begin|>functions.search:0<|tool_call_argument_begin|>{"q": "x"}<|tool_call_end|><|tool_calls_section_end|>'
+    c, calls = one("kimi_k2", k)
+    assert c == "pre" and calls[0].name == "search" and json.loads(calls[0].arguments) == {"q": "x"}
+    g = "<tool_call>lookup\n<arg_key>id</arg_key>\n<arg_value>7</arg_value>\n<arg_key>s</arg_key>\n<arg_value>abc</arg_value>\n</tool_call>"
+    c, calls = one("glm45", g)
+    assert calls[0].name == "lookup" and json.loads(calls[0].arguments) == {"id": 7, "s": "abc"}
+    c, calls = one("deepseek_v31", 'x<｜tool▁calls▁begin｜><｜tool▁call▁begin｜>f<｜tool▁sep｜>{"a": 2}<｜tool▁call▁end｜><｜tool▁calls▁end｜>')
+    assert c == "x" and calls[0].name == "f" and json.loads(calls[0].arguments) == {"a": 2}
+    c, calls = one("jamba", '<tool_calls>[{"name": "f", "arguments": {"a": 1}}]</tool_calls>')
+    assert calls[0].name == "f"
+    c, calls = one("internlm", 'hi<|action_start|><|plugin|>\n{"name": "f", "parameters": {"a": 1}}<|action_end|>')
+    assert c == "hi" and json.loads(calls[0].arguments) == {"a": 1}
+    c, calls = one("minimax", '<tool_calls>\n{"name": "a", "arguments": {}}\n{"name": "b", "arguments": {"z": 0}}\n</tool_calls>')
+    assert [x.name for x in calls] == ["a", "b"]
+    c, calls = one("phi4_mini_json", 'functools[{"name": "f", "arguments": {"q": 1}}]')
+    assert calls[0].name == "f"
+    assert get_reasoning_parser("mistral").extract("[THINK]plan[/THINK]done") == ("plan", "done")
+    assert get_reasoning_parser("seed_oss").extract("<seed:think>a</seed:think>b") == ("a", "b")
+    assert get_reasoning_parser("granite").extract("Here is my thought process: think. Here is my response: answer") == ("think.", "answer")
+    assert get_reasoning_parser("granite").extract("plain") == (None, "plain")
+    rp = get_reasoning_parser("mistral")
+    text, r, cc = "[THINK]ab[/THINK]xy", "", ""
+    for i in range(1, len(text) + 1):
+        dr, dc = rp.stream(text[: i - 1], text[:i])
+        r, cc = r + dr, cc + dc
+    assert (r, cc) == ("ab", "xy")

@@ -311,6 +311,7 @@ def _attn_case(qlens, ctxs, Hq, Hkv, D, bs=16, seed=0):
     ("prefill", [1, 17, 200, 64], [0, 0, 0, 0], 8, 2, 128),
     ("chunked-prefix", [130, 33], [256, 1000], 10, 2, 128),
     ("mixed", [1, 1, 300, 1, 2], [500, 20, 100, 0, 77], 40, 8, 128),
+    ("prefill-long", [700, 129, 128], [0, 300, 1], 40, 8, 128),
     ("decode-d256", [1] * 4, [0, 100, 1025, 31], 24, 4, 256),
     ("prefill-d256", [77, 5, 140], [0, 200, 64], 16, 2, 256),
     ("verify-d256", [4, 4], [100, 3], 24, 4, 256),
@@ -323,6 +324,23 @@ def test_paged_attention(name, qlens, ctxs, Hq, Hkv, D):
     assert K().check_status() == 0
     e = ref.paged_attention(q.cpu(), cache.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), scale)
     _close(out, e, 2e-2, 1e-2, name)
+
+
+def test_prefill_attention_tcgen05_matches_mma_path_and_lse(monkeypatch):
+    """Head size 128 prefill runs on the tcgen05 kernel by default; it must agree with the mma.sync kernel and return the
+    same log-sum-exp."""
+    import onecat_vllm.ops.cuda as KC
+    q, cache, md = _attn_case([300, 70, 513], [0, 200, 64], 16, 4, 128, seed=3)
+    T = q.shape[0]
+    lse_tc = torch.zeros(T, 16, device="cuda")
+    lse_mma = torch.zeros(T, 16, device="cuda")
+    out_tc = KC.paged_attention(q, cache, md, 128 ** -0.5, lse=lse_tc)
+    monkeypatch.setattr(KC, "_ATTN_PREFILL_TC", False)
+    out_mma = KC.paged_attention(q, cache, md, 128 ** -0.5, lse=lse_mma)
+    torch.cuda.synchronize()
+    assert KC.check_status() == 0
+    assert (out_tc.float() - out_mma.float()).abs().max() < 2e-2
+    assert (lse_tc - lse_mma).abs().max() < 2e-2
 
 
 def test_paged_attention_forced_splits():

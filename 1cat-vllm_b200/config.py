@@ -129,6 +129,9 @@ class ModelConfig:
     seed: int = 0
     load_format: str = "auto"  # auto | safetensors | dummy
     tokenizer: Optional[str] = None
+    enable_lora: bool = False  # build the model so that adapters can be applied (gate|up without the fused SiLU·mul epilogue)
+    max_loras: int = 4
+    max_lora_rank: int = 64
     hf_overrides: dict = field(default_factory=dict)
 
     def __post_init__(self) -> None:
@@ -387,6 +390,8 @@ class VllmConfig:
         m, p = self.model_config, self.parallel_config
         if m.num_attention_heads % p.tensor_parallel_size:
             raise ValueError("tensor_parallel_size must divide num_attention_heads")
+        if m.enable_lora and p.tensor_parallel_size > 1:
+            raise ValueError("LoRA adapters are served with tensor_parallel_size=1 only")
         if p.pipeline_parallel_size > 1:
             if p.pipeline_parallel_size > m.num_hidden_layers:
                 raise ValueError("pipeline_parallel_size exceeds the number of decoder layers")
@@ -442,10 +447,14 @@ class EngineArgs:
     disable_log_stats: bool = True
     hf_overrides: Optional[dict] = None
     structured_outputs_backend: str = "auto"
+    enable_lora: bool = False
+    max_loras: int = 4
+    max_lora_rank: int = 64
 
     def create_engine_config(self) -> VllmConfig:
         dt = _DTYPES[self.dtype] if isinstance(self.dtype, str) else self.dtype
-        over: dict[str, Any] = dict(seed=self.seed, load_format=self.load_format, tokenizer=self.tokenizer)
+        over: dict[str, Any] = dict(seed=self.seed, load_format=self.load_format, tokenizer=self.tokenizer, enable_lora=self.enable_lora,
+                                    max_loras=self.max_loras, max_lora_rank=self.max_lora_rank)
         if self.hf_config is not None:
             hf = dict(self.hf_config)
             hf.update(self.hf_overrides or {})

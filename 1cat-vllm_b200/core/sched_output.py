@@ -18,6 +18,7 @@ class NewRequestData:
     state_slot: int = -1
     eos_token_id: Optional[int] = None
     pooling_params: Any = None
+    lora_request: Any = None
 
 
 @dataclass

@@ -126,6 +126,7 @@ class Scheduler:
         self._num_preemptions = 0
         self._spec_stats = [0, 0, 0]
         self.use_pp = vllm_config.parallel_config.pipeline_parallel_size > 1
+        self.max_loras = vllm_config.model_config.max_loras if vllm_config.model_config.enable_lora else 0
 
     # ------------------------------------------------------------------ admission
     def add_request(self, request: Request | object) -> None:
@@ -223,6 +224,13 @@ class Scheduler:
             skipped: list[Request] = []
             while self.waiting and budget > 0 and len(self.running) < self.max_num_running_reqs:
                 r = self.waiting.peek()
+                if r.lora_request is not None and self.max_loras > 0:
+                    # a step may not touch more adapters than the workers hold (reference: scheduler.py ``scheduled_loras``)
+                    live = {x.lora_request.lora_int_id for x in self.running if x.lora_request is not None}
+                    if r.lora_request.lora_int_id not in live and len(live) >= self.max_loras:
+                        self.waiting.pop()
+                        skipped.append(r)
+                        continue
                 if r.num_computed_tokens == 0:
                     hit_blocks, num_hit = self.kv_cache_manager.get_computed_blocks(r)
                 else:
@@ -260,7 +268,7 @@ class Scheduler:
         km = self.kv_cache_manager
         out.scheduled_new_reqs = [
             NewRequestData(r.request_id, r.prompt_token_ids, r.sampling_params, new_blocks_of[r.request_id],
-                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params)
+                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params, r.lora_request)
             for r in scheduled_new]
         cached = CachedRequestData()
         for r in scheduled_resumed + scheduled_running:

@@ -74,11 +74,11 @@ class AsyncLLM:
                     st.queue.put_nowait(e)
             log.error(f"output handler stopped: {e!r}")
 
-    async def add_request(self, request_id: str, prompt: PromptType, params: SamplingParams, priority: int = 0) -> asyncio.Queue:
+    async def add_request(self, request_id: str, prompt: PromptType, params: SamplingParams, priority: int = 0, lora_request=None) -> asyncio.Queue:
         if self.errored is not None:
             raise EngineDeadError(str(self.errored))
         self._ensure_handler()
-        req, text = self.input_processor.process(request_id, prompt, params, None, priority)
+        req, text = self.input_processor.process(request_id, prompt, params, None, priority, lora_request)
         q: asyncio.Queue = asyncio.Queue()
         n = getattr(params, "n", 1)
         if n == 1:
@@ -99,8 +99,9 @@ class AsyncLLM:
             await self.engine_core.add_request_async(child)
         return q
 
-    async def generate(self, prompt: PromptType, sampling_params: SamplingParams, request_id: str, priority: int = 0) -> AsyncGenerator[RequestOutput, None]:
-        q = await self.add_request(request_id, prompt, sampling_params, priority)
+    async def generate(self, prompt: PromptType, sampling_params: SamplingParams, request_id: str, priority: int = 0,
+                       lora_request=None) -> AsyncGenerator[RequestOutput, None]:
+        q = await self.add_request(request_id, prompt, sampling_params, priority, lora_request)
         finished_children = 0
         try:
             while True:
@@ -145,6 +146,12 @@ class AsyncLLM:
 
     async def profile(self, start: bool) -> None:
         await self.engine_core.call_utility_async("profile", start)
+
+    async def add_lora(self, lora_request) -> bool:
+        return await self.engine_core.call_utility_async("add_lora", lora_request.to_dict())
+
+    async def remove_lora(self, lora_id: int) -> bool:
+        return await self.engine_core.call_utility_async("remove_lora", lora_id)
 
     async def collective_rpc(self, method: str, args=(), kwargs=None):
         return await self.engine_core.call_utility_async("collective_rpc", method, list(args), kwargs)

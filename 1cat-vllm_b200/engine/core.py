@@ -116,6 +116,15 @@ class EngineCore:
     def save_sharded_state(self, path: str) -> None:
         self.executor.collective_rpc("save_sharded_state", (path,))
 
+    def add_lora(self, req) -> bool:
+        return all(self.executor.collective_rpc("add_lora", (req,)))
+
+    def remove_lora(self, lora_id: int) -> bool:
+        return all(self.executor.collective_rpc("remove_lora", (lora_id,)))
+
+    def list_loras(self) -> list:
+        return self.executor.collective_rpc("list_loras")[0]
+
     def collective_rpc(self, method, args=(), kwargs=None):
         return self.executor.collective_rpc(method, args, kwargs)
 

@@ -35,8 +35,8 @@ class LLMEngine:
         return cls(args.create_engine_config(), log_stats=not args.disable_log_stats, **kw)
 
     def add_request(self, request_id: str, prompt: PromptType, params: SamplingParams, arrival_time: Optional[float] = None,
-                    priority: int = 0) -> None:
-        req, text = self.input_processor.process(request_id, prompt, params, arrival_time, priority)
+                    priority: int = 0, lora_request=None) -> None:
+        req, text = self.input_processor.process(request_id, prompt, params, arrival_time, priority, lora_request)
         n = getattr(params, "n", 1)
         if n == 1:
             self.output_processor.add_request(req, text)
@@ -87,6 +87,15 @@ class LLMEngine:
 
     def wake_up(self) -> None:
         self.engine_core.call_utility("wake_up")
+
+    def add_lora(self, lora_request) -> bool:
+        return self.engine_core.call_utility("add_lora", lora_request.to_dict())
+
+    def remove_lora(self, lora_id: int) -> bool:
+        return self.engine_core.call_utility("remove_lora", lora_id)
+
+    def list_loras(self) -> list:
+        return self.engine_core.call_utility("list_loras")
 
     def collective_rpc(self, method, args=(), kwargs=None):
         return self.engine_core.call_utility("collective_rpc", method, args, kwargs)

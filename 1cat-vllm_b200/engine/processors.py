@@ -23,7 +23,9 @@ class InputProcessor:
         self.cfg, self.tok = cfg, tokenizer
 
     def process(self, request_id: str, prompt: PromptType, params: SamplingParams, arrival_time: Optional[float] = None,
-                priority: int = 0) -> tuple[EngineCoreRequest, Optional[str]]:
+                priority: int = 0, lora_request=None) -> tuple[EngineCoreRequest, Optional[str]]:
+        if lora_request is not None and not self.cfg.model_config.enable_lora:
+            raise ValueError("this engine was started without enable_lora")
         text, ids, salt = parse_prompt(prompt)
         if ids is None:
             if self.tok is None:
@@ -53,7 +55,8 @@ class InputProcessor:
             sp.bad_words_token_ids = [self.tok.encode(w, add_special_tokens=False) for w in sp.bad_words]
         if sp.allowed_token_ids is not None and any(not 0 <= t < mc.vocab_size for t in sp.allowed_token_ids):
             raise ValueError("allowed_token_ids contains an id outside the vocabulary")
-        req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling)
+        req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling,
+                                lora_request=lora_request)
         return req, text
 
 

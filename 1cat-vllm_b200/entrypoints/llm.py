@@ -26,7 +26,8 @@ class LLM:
         return self.llm_engine.tokenizer
 
     def generate(self, prompts: Union[PromptType, Sequence[PromptType]], sampling_params: Optional[Union[SamplingParams, Sequence[SamplingParams]]] = None,
-                 use_tqdm: bool = False, priority: Optional[list[int]] = None) -> list[RequestOutput]:
+                 use_tqdm: bool = False, priority: Optional[list[int]] = None, lora_request=None) -> list[RequestOutput]:
+        """``lora_request``: one ``LoRARequest`` for all prompts or a list with one entry (or ``None``) per prompt."""
         if isinstance(prompts, (str, dict)) or (isinstance(prompts, list) and prompts and isinstance(prompts[0], int)):
             prompts = [prompts]
         if sampling_params is None:
@@ -40,7 +41,8 @@ class LLM:
             sp.output_kind = RequestOutputKind.FINAL_ONLY
             rid = str(next(self._counter))
             ids.append(rid)
-            self.llm_engine.add_request(rid, p, sp, priority=priority[i] if priority else 0)
+            lr = lora_request[i] if isinstance(lora_request, (list, tuple)) else lora_request
+            self.llm_engine.add_request(rid, p, sp, priority=priority[i] if priority else 0, lora_request=lr)
         return self._run_engine(ids, use_tqdm)
 
     def chat(self, messages, sampling_params: Optional[SamplingParams] = None, add_generation_prompt: bool = True, **kw) -> list[RequestOutput]:

@@ -38,6 +38,20 @@ class ServingState:
         self.api_key = api_key
         self.sleeping = False
         self.inflight = 0
+        self.loras: dict = {}  # served adapter name -> LoRARequest
+        self._next_lora_id = 1
+
+    def register_lora(self, name: str, path: str):
+        from onecat_vllm.lora import LoRARequest
+        if name in self.loras:
+            return self.loras[name]
+        self.loras[name] = LoRARequest(name, self._next_lora_id, path)
+        self._next_lora_id += 1
+        return self.loras[name]
+
+    def lora_for(self, model: Optional[str]):
+        """A request whose ``model`` names a registered adapter runs under it (reference: entrypoints/openai/models/serving.py)."""
+        return self.loras.get(model) if model else None
 
     @property
     def max_model_len(self) -> int:
@@ -101,8 +115,28 @@ def build_app(state: ServingState) -> FastAPI:
 
     @app.get("/v1/models")
     async def models():
-        return {"object": "list", "data": [{"id": state.model_name, "object": "model", "created": now(), "owned_by": "onecat-vllm",
-                                            "max_model_len": state.max_model_len}]}
+        data = [{"id": state.model_name, "object": "model", "created": now(), "owned_by": "onecat-vllm", "max_model_len": state.max_model_len}]
+        data += [{"id": n, "object": "model", "created": now(), "owned_by": "onecat-vllm", "parent": state.model_name, "root": r.lora_path}
+                 for n, r in state.loras.items()]
+        return {"object": "list", "data": data}
+
+    @app.post("/v1/load_lora_adapter")
+    async def load_lora(body: dict):
+        try:
+            req = state.register_lora(body["lora_name"], body["lora_path"])
+            await state.engine.add_lora(req)
+        except Exception as e:
+            state.loras.pop(body.get("lora_name"), None)
+            return JSONResponse(error_body(str(e)), status_code=400)
+        return Response(content=f"Success: LoRA adapter '{req.lora_name}' added successfully.", status_code=200)
+
+    @app.post("/v1/unload_lora_adapter")
+    async def unload_lora(body: dict):
+        req = state.loras.pop(body.get("lora_name"), None)
+        if req is None:
+            return JSONResponse(error_body(f"adapter {body.get('lora_name')!r} is not loaded", "NotFoundError", 404), status_code=404)
+        await state.engine.remove_lora(req.lora_int_id)
+        return Response(content=f"Success: LoRA adapter '{req.lora_name}' removed successfully.", status_code=200)
 
     @app.get("/metrics")
     async def metrics():
@@ -250,7 +284,7 @@ def build_app(state: ServingState) -> FastAPI:
             gens = []
             for i, p in enumerate(prompts):
                 sp_i = sp.clone()
-                gens.append(state.engine.generate(p, sp_i, f"{rid}-{i}", priority=req.priority))
+                gens.append(state.engine.generate(p, sp_i, f"{rid}-{i}", priority=req.priority, lora_request=state.lora_for(req.model)))
         except ValueError as e:
             return JSONResponse(error_body(str(e)), status_code=400)
         model = req.model or state.model_name
@@ -319,7 +353,7 @@ def build_app(state: ServingState) -> FastAPI:
         rid = new_id("chatcmpl")
         try:
             sp = req.to_sampling_params(state.max_model_len, logprobs=k)
-            gen = state.engine.generate(prompt, sp, rid, priority=req.priority)
+            gen = state.engine.generate(prompt, sp, rid, priority=req.priority, lora_request=state.lora_for(req.model))
         except ValueError as e:
             return JSONResponse(error_body(str(e)), status_code=400)
         model = req.model or state.model_name
@@ -424,6 +458,7 @@ def make_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("--tool-call-parser", default=None)
     p.add_argument("--reasoning-parser", default=None)
     p.add_argument("--enable-auto-tool-choice", action="store_true")
+    p.add_argument("--lora-modules", nargs="*", default=[], help="adapters to serve, as name=path")
     EngineArgs.add_cli_args(p)
     return p
 
@@ -438,6 +473,9 @@ def run_server(args: argparse.Namespace) -> None:
         ea.tokenizer = ea.model
     engine = AsyncLLM.from_engine_args(ea)
     state = ServingState(engine, args.served_model_name or ea.model, args.tool_call_parser, args.reasoning_parser, args.api_key)
+    for item in getattr(args, "lora_modules", []) or []:
+        name, _, path = item.partition("=")
+        state.register_lora(name, path)
     app = build_app(state)
     config = uvicorn.Config(app, host=args.host, port=args.port, log_level="warning")
     server = uvicorn.Server(config)

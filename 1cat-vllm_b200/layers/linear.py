@@ -240,6 +240,7 @@ class LinearBase(nn.Module):
         self.bias = _p(torch.zeros(self.out_features, dtype=dtype)) if bias else None
         self._dq_cache = None
         self.kernel_state = None  # filled by ops.cuda.prepare_*
+        self.lora_slots: Optional[dict] = None  # adapter slot -> list of (A, B, first output column); filled by lora.LoRAManager
 
     def _segment_rank(self, seg: int) -> int:
         t = self.segment_tp[seg]
@@ -280,7 +281,11 @@ class LinearBase(nn.Module):
         self._dq_cache = None
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.method.apply(self, x)
+        y = self.method.apply(self, x)
+        if self.lora_slots:
+            from onecat_vllm.lora import apply_lora
+            y = apply_lora(self, x, y)
+        return y
 
 
 class ReplicatedLinear(LinearBase):
@@ -328,4 +333,4 @@ class RowParallelLinear(LinearBase):
                     y._tp_pushed = True
                     return y
                 return K.linear(self, x, out=out)  # partial sums stay in this rank's slot; the reduction pulls them
-        return self.method.apply(self, x)
+        return super().forward(x)

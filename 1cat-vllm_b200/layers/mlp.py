@@ -8,11 +8,17 @@ from onecat_vllm.layers.linear import MergedColumnParallelLinear, RowParallelLin
 
 
 class MLP(nn.Module):
-    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True):
+    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True, fuse_act: bool = True):
+        """``fuse_act=False`` (LoRA-enabled models) keeps gate|up as a plain GEMM so adapter deltas can be added before SiLU·mul."""
         super().__init__()
+        self.fuse_act = fuse_act
         self.gate_up_proj = MergedColumnParallelLinear(hidden, [inter, inter], quant=quant, prefix=prefix + ".gate_up_proj",
-                                                       dtype=dtype, fuse_silu_mul=True)
+                                                       dtype=dtype, fuse_silu_mul=fuse_act)
         self.down_proj = RowParallelLinear(inter, hidden, quant=quant, prefix=prefix + ".down_proj", dtype=dtype)
 
     def forward(self, x):
-        return self.down_proj(self.gate_up_proj(x))
+        h = self.gate_up_proj(x)
+        if not self.fuse_act:
+            from onecat_vllm import ops
+            h = ops.silu_and_mul(h)
+        return self.down_proj(h)

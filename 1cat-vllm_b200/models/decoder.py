@@ -45,7 +45,7 @@ class DecoderLayer(nn.Module):
         if cfg.is_moe_layer(idx):
             self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
         else:
-            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype)
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
 

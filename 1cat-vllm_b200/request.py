@@ -60,7 +60,8 @@ class EngineCoreRequest:
                 "sampling_params": self.sampling_params.to_dict() if self.sampling_params else None,
                 "arrival_time": self.arrival_time, "eos_token_id": self.eos_token_id, "priority": self.priority,
                 "cache_salt": self.cache_salt, "client_index": self.client_index,
-                "pooling_params": self.pooling_params.to_dict() if self.pooling_params is not None else None}
+                "pooling_params": self.pooling_params.to_dict() if self.pooling_params is not None else None,
+                "lora_request": self.lora_request.to_dict() if self.lora_request is not None else None}
 
     @classmethod
     def from_wire(cls, d: dict) -> "EngineCoreRequest":
@@ -71,7 +72,7 @@ class EngineCoreRequest:
             pp = PoolingParams(**pp)
         return cls(d["request_id"], list(d["prompt_token_ids"]), SamplingParams.from_dict(sp) if sp else None,
                    d.get("arrival_time", 0.0), d.get("eos_token_id"), d.get("priority", 0), d.get("cache_salt"),
-                   d.get("client_index", 0), pooling_params=pp)
+                   d.get("client_index", 0), pooling_params=pp, lora_request=_lora_from(d.get("lora_request")))
 
 
 @dataclass
@@ -123,14 +124,24 @@ class EngineCoreOutputs:
             self.timestamp = time.monotonic()
 
 
+def _lora_from(d):
+    if not d:
+        return None
+    from onecat_vllm.lora import LoRARequest
+    return LoRARequest.from_dict(d)
+
+
 class Request:
     """Scheduler-side request. Tokens = prompt + outputs; ``num_computed_tokens`` chases
     ``num_tokens_with_spec`` (reference: v1/core/sched/scheduler.py:459-468)."""
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], sampling_params: Optional[SamplingParams],
                  eos_token_id: Optional[int] = None, arrival_time: Optional[float] = None, priority: int = 0,
-                 cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None) -> None:
+                 cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None, lora_request=None) -> None:
         self.request_id = request_id
+        self.lora_request = lora_request
+        if lora_request is not None:  # KV computed under an adapter is only reusable under the same adapter
+            cache_salt = f"{cache_salt or ''}|lora:{lora_request.lora_int_id}"
         self.prompt_token_ids = list(prompt_token_ids)
         self.sampling_params = sampling_params
         self.pooling_params = pooling_params
@@ -162,7 +173,7 @@ class Request:
     @classmethod
     def from_engine_core_request(cls, r: EngineCoreRequest, block_hasher=None) -> "Request":
         return cls(r.request_id, r.prompt_token_ids, r.sampling_params, r.eos_token_id, r.arrival_time, r.priority,
-                   r.cache_salt, r.client_index, block_hasher, r.pooling_params)
+                   r.cache_salt, r.client_index, block_hasher, r.pooling_params, r.lora_request)
 
     def append_output_token_ids(self, ids: int | list[int]) -> None:
         if isinstance(ids, int):

@@ -41,6 +41,7 @@ class CachedRequestState:
     generator: Optional[torch.Generator] = None
     eos_token_id: Optional[int] = None
     pooling_params: object = None
+    lora_request: object = None
     pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
     pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
 
@@ -59,6 +60,7 @@ class ModelRunner:
         self.model = None
         self.mtp = None
         self.kv_caches: list = []
+        self.lora_manager = None
         self.mtp_cache = None
         self.sampler = Sampler()
         sc = vllm_config.speculative_config
@@ -89,6 +91,9 @@ class ModelRunner:
         if self.spec.enabled:
             from onecat_vllm.spec_decode.proposers import make_proposer
             self.proposer = make_proposer(self)
+        if self.mc.enable_lora:
+            from onecat_vllm.lora import LoRAManager
+            self.lora_manager = LoRAManager(self.model, self.mc.max_loras, self.mc.max_lora_rank, self.device, self.mc.dtype)
         log.info_once(f"model {self.mc.architecture} ready in {time.time() - t0:.1f}s on {self.device}")
 
     def get_kv_cache_specs(self) -> dict:
@@ -181,7 +186,7 @@ class ModelRunner:
                 gen.manual_seed(sp.seed)
             self.requests[nr.req_id] = CachedRequestState(nr.req_id, list(nr.prompt_token_ids), len(nr.prompt_token_ids), sp,
                                                           list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id,
-                                                          nr.pooling_params)
+                                                          nr.pooling_params, nr.lora_request)
         c = so.scheduled_cached_reqs
         for i, rid in enumerate(c.req_ids):
             st = self.requests.get(rid)
@@ -191,7 +196,7 @@ class ModelRunner:
                 st = CachedRequestState(rid, list(toks), old.num_prompt_tokens if old else len(toks), old.sampling_params if old else None,
                                         list(c.new_block_ids[i] or []), c.num_computed_tokens[i], c.state_slots[i],
                                         old.generator if old else None, old.eos_token_id if old else None,
-                                        old.pooling_params if old else None)
+                                        old.pooling_params if old else None, old.lora_request if old else None)
                 self.requests[rid] = st
             else:
                 st.num_computed_tokens = c.num_computed_tokens[i]
@@ -350,8 +355,16 @@ class ModelRunner:
             ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             ev0.record()
         spec_any = any(len(d) > 0 for d in drafts_of)
+        lora_batch = None
+        if self.lora_manager is not None:
+            from onecat_vllm.lora import set_active
+            token_reqs = []
+            for rid, qn in zip(req_ids, query_lens):
+                token_reqs += [self.requests[rid].lora_request] * qn
+            lora_batch = self.lora_manager.make_batch(token_reqs, self.device)
+            set_active(lora_batch)
         gkey = None
-        if self.graphs is not None and max_q == min(query_lens) and not (spec_any and self.mc.is_hybrid):
+        if self.graphs is not None and lora_batch is None and max_q == min(query_lens) and not (spec_any and self.mc.is_hybrid):
             gkey = self.graphs.plan(R, max_q, max_s)
             if gkey is not None:
                 self._pad_inputs(R, T, gkey[0], max_q)
@@ -369,6 +382,9 @@ class ModelRunner:
         if hidden is None:
             inter = self._pp_recv(T) if not self.pp.is_first_pp else None
             hidden = self.model(ids, md, self.kv_caches, intermediate=inter)
+        if lora_batch is not None:
+            from onecat_vllm.lora import set_active
+            set_active(None)
         out = ModelRunnerOutput(req_ids=req_ids, sampled_token_ids=[[] for _ in req_ids])
         if not self.pp.is_last_pp:
             # hand (block output, residual) to the next stage; sampling happens on the last one

@@ -123,6 +123,22 @@ class Worker:
         process_weights_after_loading(self.runner.model)
         return n
 
+    # ---- LoRA adapters (reference: gpu_worker.py ``add_lora`` / ``remove_lora`` / ``list_loras``)
+    def _lora(self):
+        if self.runner.lora_manager is None:
+            raise ValueError("LoRA is not enabled (enable_lora=True)")
+        return self.runner.lora_manager
+
+    def add_lora(self, req) -> bool:
+        from onecat_vllm.lora import LoRARequest
+        return self._lora().add_lora(LoRARequest.from_dict(req) if isinstance(req, dict) else req)
+
+    def remove_lora(self, lora_id: int) -> bool:
+        return self._lora().remove_lora(lora_id)
+
+    def list_loras(self) -> list:
+        return self._lora().list_loras()
+
     def check_health(self) -> bool:
         return True
 

@@ -31,6 +31,12 @@ constexpr int kSmem = kTile + kStages * 2 * kTile + 1024;  // Q + K/V ring + bar
 // TMEM columns: S0 | S1 | O_tile | P0 | P1
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // V tile as UMMA operand B, MN-major (d contiguous): 64 d-values x 8 keys form a 1024-byte swizzle atom; the next 8 keys are
 // 1024 bytes on (stride byte offset), the next 64 d-values are in the other half of the tile (leading byte offset).
 __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint32_t lbo_bytes) {
@@ -223,7 +229,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       const int k0 = j * TK;
       const bool masked = k0 + TK > limit;
       // pass 1: row maximum
-      float mx = m;
+      float mx = m, raw = -INFINITY;
 #pragma unroll
       for (int c = 0; c < TK; c += 32) {
         uint32_t v[32];
@@ -231,13 +237,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]) * sl2;
+          float x = __uint_as_float(v[i]);
           if (masked && k0 + c + i >= limit) x = -INFINITY;
-          mx = fmaxf(mx, x);
+          raw = fmaxf(raw, x);
         }
       }
+      mx = fmaxf(mx, raw * sl2);
       const float m_use = (mx == -INFINITY) ? 0.f : mx;  // a row that sees no key yet keeps zeros
-      alpha[j & 1] = (m == -INFINITY) ? 0.f : exp2f(m - m_use);
+      alpha[j & 1] = (m == -INFINITY) ? 0.f : ex2(m - m_use);
       m = mx;
       // pass 2: probabilities -> bf16 pairs in TMEM, row sum
       float sum = 0.f;
@@ -255,7 +262,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
             float x0 = __uint_as_float(v[i]) * sl2 - m_use, x1 = __uint_as_float(v[i + 1]) * sl2 - m_use;
             if (masked && k0 + c + c2 + i >= limit) x0 = -INFINITY;
             if (masked && k0 + c + c2 + i + 1 >= limit) x1 = -INFINITY;
-            __nv_bfloat162 b = __floats2bfloat162_rn(exp2f(x0), exp2f(x1));
+            __nv_bfloat162 b = __floats2bfloat162_rn(ex2(x0), ex2(x1));
             sum += __low2float(b) + __high2float(b);   // the sum of what the tensor core will actually multiply
             pk[(c2 + i) >> 1] = *reinterpret_cast<uint32_t*>(&b);
           }

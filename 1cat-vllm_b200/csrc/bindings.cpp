@@ -81,6 +81,7 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
   if (force_tn > 0) {
     TORCH_CHECK(!w4.has_value() || force_tn <= 192, "4-bit weights support token tiles up to 192");
     p.tn = (int)force_tn;
+    p.nt_sub = 1;
     p.num_t_tiles = (p.T + p.tn - 1) / p.tn;
     oc::gemm_plan_stages(p, w4.has_value());
   }
@@ -89,7 +90,7 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
     p.splits = (int)force_splits;
     p.ktiles_per_split = (ktiles + p.splits - 1) / p.splits;
     TORCH_CHECK((p.splits - 1) * p.ktiles_per_split < ktiles, "too many splits for K");
-    TORCH_CHECK((size_t)p.num_t_tiles * p.num_n_tiles * p.splits * 128 * p.tn * 4 <= p.ws_bytes, "split-K workspace too small");
+    TORCH_CHECK((size_t)p.num_t_tiles * p.num_n_tiles * p.splits * 128 * p.tn * (p.nt_sub < 1 ? 1 : p.nt_sub) * 4 <= p.ws_bytes, "split-K workspace too small");
     TORCH_CHECK(p.num_t_tiles * p.num_n_tiles <= p.max_counters, "not enough split-K counters");
     oc::gemm_plan_stages(p, w4.has_value());  // the stage shape depends on whether the k range is split
   }

@@ -52,11 +52,11 @@ constexpr int kTmemCols = 512;
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
 };
-__host__ __device__ inline SmemLayout make_layout(int tn, int xstages, int stages, int pstages, int wkind) {
+__host__ __device__ inline SmemLayout make_layout(int tn, int nt_sub, int xstages, int stages, int pstages, int wkind) {
   SmemLayout L;
   uint32_t o = 0;
   L.x_off = o;
-  o += (uint32_t)xstages * tn * 128;
+  o += (uint32_t)xstages * nt_sub * tn * 128;
   L.w_off = o;
   o += (pstages > 0 ? 0u : (uint32_t)stages * kWStageBytes);  // 4-bit weights are dequantised into TMEM, not shared memory
   L.p_off = o;
@@ -113,7 +113,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes the swizzle needs
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr int kPackedBytes = packed_bytes(WKIND), kPackedSlot = packed_slot(WKIND);
-  const SmemLayout L = make_layout(p.tn, p.xstages, p.stages, p.pstages, WKIND);
+  // NT token sub-tiles per work item (1 or 2): with two, a dequantised weight tile feeds two accumulators (2 x tn tokens), which
+  // halves the dequantisation and MMA-issue work per token; both accumulators then belong to one work item.
+  const int NT = p.nt_sub, NB = 2 / NT;
+  const SmemLayout L = make_layout(p.tn, NT, p.xstages, p.stages, p.pstages, WKIND);
   uint8_t* sx = smem + L.x_off;
   uint8_t* sw = smem + L.w_off;
   uint8_t* sp = smem + L.p_off;
@@ -192,8 +195,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     if (lane == 0) {
       Ring st;
       bool ok = true;
-      const uint32_t bytes = (uint32_t)tn * 128 + (WKIND == 0 ? kWStageBytes : 0);
-      const uint32_t xs = (uint32_t)tn * 128;
+      const uint32_t xs = (uint32_t)tn * 128;  // one token sub-tile
+      const uint32_t bytes = NT * xs + (WKIND == 0 ? kWStageBytes : 0);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
@@ -201,7 +204,8 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
           mbar_expect_tx(&full[st.idx], bytes);
-          tma_load_2d(sx + st.idx * xs, &tmX, kt * BK, grouped ? tt : tt * tn, &full[st.idx]);
+          for (int i = 0; i < NT; ++i)  // rows past T are zero-filled by the copy
+            tma_load_2d(sx + (st.idx * NT + i) * xs, &tmX, kt * BK, grouped ? tt : (tt * NT + i) * tn, &full[st.idx]);
           if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full[st.idx]);
           st.advance(S);
         }
@@ -246,23 +250,33 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        const int acc = tile_i & 1;
-        ok = mbar_wait(&tempty[acc], ((tile_i >> 1) & 1) ^ 1, abort_flag);
+        const int acc = tile_i % NB;
+        ok = mbar_wait(&tempty[acc], ((tile_i / NB) & 1) ^ 1, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t d_addr = tmem_base + acc * p.acc_stride;
+        const uint32_t d_addr = tmem_base + acc * NT * p.acc_stride;
         uint32_t accum = 0;
         for (int kt = k0; kt < k1; ++kt) {
           const int s = st.idx;
           ok = mbar_wait(&full[s], st.phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t db = umma_desc_sw128(b_base + s * xs);
+          const uint64_t db = umma_desc_sw128(b_base + s * NT * xs);
           if (WKIND >= 1) {
             const uint32_t ta = ta_base + s * 32;  // 64 k of bf16 = 32 columns per stage
+            if (NT == 1) {  // the common case stays branch-free: this thread is the kernel's critical path
 #pragma unroll
-            for (int j = 0; j < BK / 16; ++j) {
-              umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
+              for (int j = 0; j < BK / 16; ++j) {
+                umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
+                accum = 1;
+              }
+            } else {
+              for (int i = 0; i < NT; ++i) {
+                const uint64_t dbi = umma_desc_sw128(b_base + (s * NT + i) * xs);
+#pragma unroll
+                for (int j = 0; j < BK / 16; ++j)
+                  umma_bf16_ts(d_addr + i * p.acc_stride, ta + j * 8, dbi + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
+              }
               accum = 1;
             }
           } else {
@@ -362,12 +376,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
       int nt, tt, sp_, k0, k1;
       decode(w, nt, tt, sp_, k0, k1);
-      const int acc = tile_i & 1;
-      ok = mbar_wait(&tfull[acc], (tile_i >> 1) & 1, abort_flag);
+      const int acc = tile_i % NB;
+      ok = mbar_wait(&tfull[acc], (tile_i / NB) & 1, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * p.acc_stride + ((uint32_t)(q * 32) << 16);
-      int n_base = nt * BM, t0 = tt * tn, t_end = p.T;
+      const uint32_t taddr0 = tmem_base + acc * NT * p.acc_stride + ((uint32_t)(q * 32) << 16);
+      const int tn_eff = tn * NT;  // tokens per work item
+      // TMEM address of the 32-column chunk that starts at token column c of the work item (sub-tile c / tn)
+      auto taddr_of = [&](int c) -> uint32_t { return NT == 1 ? taddr0 + c : taddr0 + (c / tn) * p.acc_stride + (c % tn); };
+      int n_base = nt * BM, t0 = tt * tn_eff, t_end = p.T;
       if (grouped) {
         const int4 it = p.work[w];
         t0 = it.y;
@@ -378,10 +395,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const int tile_id = nt * p.num_t_tiles + tt;
       if (p.splits > 1) {
         // fp32 partial -> workspace [tile][split][row][tn]
-        float* wsp = p.ws + (((size_t)tile_id * p.splits + sp_) * BM + row) * tn;
-        for (int c = 0; c < tn; c += 32) {
+        float* wsp = p.ws + (((size_t)tile_id * p.splits + sp_) * BM + row) * tn_eff;
+        for (int c = 0; c < tn_eff; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_32x32(taddr_of(c), v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; j += 4)
@@ -402,13 +419,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (!*red_flag) continue;
         __threadfence();
         // last arriver: sum the splits in fixed order (bit-stable) and run the real epilogue from registers
-        const float* base = p.ws + ((size_t)tile_id * p.splits * BM + row) * tn;
-        for (int c = 0; c < tn; c += 32) {
+        const float* base = p.ws + ((size_t)tile_id * p.splits * BM + row) * tn_eff;
+        for (int c = 0; c < tn_eff; c += 32) {
           float a[32];
 #pragma unroll
           for (int j = 0; j < 32; ++j) a[j] = 0.f;
           for (int s2 = 0; s2 < p.splits; ++s2) {
-            const float4* src = reinterpret_cast<const float4*>(base + (size_t)s2 * BM * tn + c);
+            const float4* src = reinterpret_cast<const float4*>(base + (size_t)s2 * BM * tn_eff + c);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               float4 f = __ldcg(src + j);
@@ -441,9 +458,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       // ---- single-pass epilogue
       if (p.epi == EPI_SILU_MUL) {
         const int n_out = (n_base + q * 32) / 2 + (lane & 15);
-        for (int c = 0; c < tn; c += 32) {
+        for (int c = 0; c < tn_eff; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_32x32(taddr_of(c), v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -456,9 +473,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         }
       } else {
         float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-        for (int c = 0; c < tn; c += 32) {
+        for (int c = 0; c < tn_eff; c += 32) {
           uint32_t v[32];
-          tmem_ld_32x32(taddr + c, v);
+          tmem_ld_32x32(taddr_of(c), v);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -520,7 +537,9 @@ int make_tmap_bf16(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t co
 
 }  // namespace
 
-int gemm_smem_bytes(const GemmParams& p) { return (int)make_layout(p.tn, p.xstages, p.stages, p.pstages, p.wkind).total + 1024; }
+int gemm_smem_bytes(const GemmParams& p) {
+  return (int)make_layout(p.tn, p.nt_sub < 1 ? 1 : p.nt_sub, p.xstages, p.stages, p.pstages, p.wkind).total + 1024;
+}
 
 // Picks the token tile, split-K factor and pipeline depths. Split-K spreads few-tile problems (decode) over all SMs.
 void gemm_plan(GemmParams& p, int num_sms, bool w4) {
@@ -532,7 +551,12 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
     if (waste128 + 64 < waste256 && T < 1024) tn = 128;
   }
   p.tn = tn;
-  p.num_t_tiles = (T + tn - 1) / tn;
+  // packed weights, many token tiles and a long k loop: pair the token tiles so that every dequantised weight tile feeds two
+  // accumulators. Both accumulators then belong to one work item and its epilogue no longer overlaps the next main loop, and
+  // there are half as many items to balance over the SMs; measured on B200: +12 % at K = 17408 with 8192 tokens, -5..-12 % at
+  // K = 5120, and slower whole-model steps when used for 200-400 token batches.
+  p.nt_sub = (w4 && p.work == nullptr && T > 2 * tn && p.K / BK >= 160) ? 2 : 1;
+  p.num_t_tiles = (T + tn * p.nt_sub - 1) / (tn * p.nt_sub);
   p.num_n_tiles = (p.n_rows + BM - 1) / BM;
   int ktiles = p.K / BK;
   int tiles = p.num_t_tiles * p.num_n_tiles;
@@ -542,7 +566,7 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
     for (int s = 1; s <= 16; ++s) {
       int per = (ktiles + s - 1) / s;
       if (per < 4 || (s - 1) * per >= ktiles) continue;  // every split needs work
-      if ((size_t)tiles * s * BM * tn * 4 > p.ws_bytes || tiles > p.max_counters) break;
+      if ((size_t)tiles * s * BM * tn * p.nt_sub * 4 > p.ws_bytes || tiles > p.max_counters) break;
       int items = tiles * s;
       int waves = (items + num_sms - 1) / num_sms;
       // time ~ waves * k tiles per item (+ a fixed cost per item for the reduction traffic)
@@ -560,7 +584,9 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
 void gemm_plan_stages(GemmParams& p, bool w4) {
   const int budget = 222 * 1024;
   const int tn = p.tn;
+  if (p.nt_sub < 1) p.nt_sub = 1;
   if (!w4) {
+    p.nt_sub = 1;
     p.pstages = 0;
     int s = (budget - 2048) / (tn * 128 + kWStageBytes);
     p.stages = p.xstages = s > 8 ? 8 : (s < 2 ? 2 : s);
@@ -570,11 +596,21 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
   p.stages = p.xstages = tn <= 128 ? 8 : 4;  // limited by TMEM: 2 accumulators + 32 columns per stage
   p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
   p.acc_stride = tn <= 128 ? 128 : 192;
+  // shared memory: X ring (nt_sub sub-tiles per stage) + packed ring + barriers
+  const int slot = packed_slot(p.wkind > 0 ? p.wkind : 1);
+  int left = budget - 2048 - p.stages * p.nt_sub * tn * 128;
+  while (left < 2 * slot && p.stages > 2) {
+    --p.stages;
+    p.xstages = p.stages;
+    left = budget - 2048 - p.stages * p.nt_sub * tn * 128;
+  }
+  if (p.pstages * slot > left) p.pstages = left / slot;
 }
 
 int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream) {
   GemmParams p = p_in;
   const bool w4 = p.w4 != nullptr;
+  if (p.nt_sub < 1) p.nt_sub = 1;
   CUtensorMap tmX, tmW;
   if (make_tmap_bf16(&tmX, x, (uint64_t)p.T, (uint64_t)p.K, (uint64_t)ldx, (uint32_t)p.tn)) return -2;
   if (!w4) {

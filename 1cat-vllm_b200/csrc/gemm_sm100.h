@@ -15,6 +15,7 @@ struct GemmParams {
   int n_pad;          // padded weight rows (stride of the scale/zero table)
   int tn, num_t_tiles, num_n_tiles, splits, ktiles_per_split;
   int acc_stride;               // TMEM columns between the two accumulators
+  int nt_sub;                   // token sub-tiles (of tn tokens) per work item: 2 = one dequantised weight tile feeds both accumulators
   int xstages, stages, pstages;  // ring depths: X tiles, W tiles (bf16 weights: same ring as X), packed 4-bit tiles
   int epi;
   int group_ktiles;   // 64-wide k tiles per quantisation group (group 128 -> 2)

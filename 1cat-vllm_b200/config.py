@@ -252,7 +252,10 @@ class CacheConfig:
     cache_dtype: str = "auto"  # auto | fp8 | fp8_e4m3 | fp8_e5m2
     mamba_cache_mode: str = "none"  # none | align
     cpu_offload_gb: float = 0.0
+    kv_offloading_size: float = 0.0  # GiB of host memory for KV blocks evicted from the GPU prefix cache (0 = off)
+    num_cpu_blocks_override: Optional[int] = None
     num_gpu_blocks: int = 0  # filled in after profiling
+    num_cpu_blocks: int = 0  # filled in with the KV cache
 
     def __post_init__(self) -> None:
         if self.block_size <= 0 or self.block_size & (self.block_size - 1):
@@ -433,6 +436,8 @@ class EngineArgs:
     kv_cache_memory_bytes: Optional[int] = None
     enable_prefix_caching: bool = True
     kv_cache_dtype: str = "auto"
+    kv_offloading_size: float = 0.0
+    num_cpu_blocks_override: Optional[int] = None
     max_num_batched_tokens: int = 8192
     max_num_seqs: int = 256
     enable_chunked_prefill: bool = True
@@ -478,7 +483,8 @@ class EngineArgs:
         return VllmConfig(
             model_config=mc,
             cache_config=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
-                                     self.kv_cache_memory_bytes, self.enable_prefix_caching, cache_dtype=self.kv_cache_dtype),
+                                     self.kv_cache_memory_bytes, self.enable_prefix_caching, cache_dtype=self.kv_cache_dtype,
+                                     kv_offloading_size=self.kv_offloading_size, num_cpu_blocks_override=self.num_cpu_blocks_override),
             parallel_config=ParallelConfig(self.tensor_parallel_size, self.pipeline_parallel_size, self.data_parallel_size,
                                            self.enable_expert_parallel, self.decode_context_parallel_size,
                                            self.distributed_executor_backend, self.tp_comm),

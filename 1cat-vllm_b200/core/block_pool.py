@@ -20,6 +20,7 @@ class BlockPool:
         self.null_block = self.free_queue.popleft()
         self.null_block.is_null = True
         self.events: list = []
+        self.offload = None  # CPUOffloadTier: told about every cached block the pool is about to reuse
 
     def get_cached_block(self, block_hash: bytes) -> Optional[KVCacheBlock]:
         d = self.cached.get(block_hash)
@@ -60,6 +61,8 @@ class BlockPool:
             d.pop(b.block_id, None)
             if not d:
                 del self.cached[h]
+                if self.offload is not None:  # the last GPU copy of this prefix block: keep it on the host
+                    self.offload.on_evict(h, b.block_id)
         b.block_hash = None
         self.events.append(("removed", b.block_id))
         return True

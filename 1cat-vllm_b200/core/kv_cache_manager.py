@@ -40,6 +40,12 @@ class KVCacheManager:
         self.free_state_slots = list(range(num_state_slots - 1, -1, -1))
         self.req_to_state_slot: dict[str, int] = {}
         self.needs_state = num_state_slots > 0
+        self.offload = None
+
+    def enable_cpu_offload(self, num_cpu_blocks: int) -> None:
+        from onecat_vllm.core.kv_offload import CPUOffloadTier
+        if self.enable_caching and num_cpu_blocks > 0:
+            self.offload = self.block_pool.offload = CPUOffloadTier(num_cpu_blocks)
 
     @property
     def usage(self) -> float:
@@ -58,6 +64,8 @@ class KVCacheManager:
             if b is None:
                 break
             hit.append(b)
+        if self.offload is not None and len(hit) < max_blocks:
+            hit += self._restore_from_cpu(request.block_hashes[len(hit):max_blocks])
         if self.use_eagle and hit:  # the draft head needs the hidden state of the last matched block
             hit.pop()
         if self.stats is not None:
@@ -65,6 +73,23 @@ class KVCacheManager:
             self.stats.queries += request.num_tokens
             self.stats.hits += len(hit) * self.block_size
         return hit, len(hit) * self.block_size
+
+    def _restore_from_cpu(self, hashes: list) -> list[KVCacheBlock]:
+        """Continue a prefix match in the CPU tier: every consecutive hit gets a fresh GPU block, a restore copy for this step and its
+        place in the GPU index; the blocks go back to the free queue (cached, unreferenced) so that the caller treats them like
+        any other prefix hit. Keeps a reserve of free blocks so that restores never starve new tokens."""
+        pool, got = self.block_pool, []
+        for h in hashes:
+            c = self.offload.lookup(h)
+            if c is None or pool.get_num_free_blocks() < 8:
+                break
+            b = pool.get_new_blocks(1)[0]
+            b.block_hash = h
+            pool.cached.setdefault(h, {})[b.block_id] = b
+            self.offload.restore(c, b.block_id)
+            got.append(b)
+        pool.free_blocks(got)
+        return got
 
     def allocate_slots(self, request, num_new_tokens: int, num_new_computed_tokens: int = 0,
                        new_computed_blocks: Optional[list[KVCacheBlock]] = None, num_lookahead_tokens: int = 0) -> Optional[list[KVCacheBlock]]:
@@ -118,6 +143,8 @@ class KVCacheManager:
 
     def reset_prefix_cache(self) -> bool:
         ok = self.block_pool.reset_prefix_cache()
+        if ok and self.offload is not None:
+            self.offload.reset()
         if ok and self.stats is not None:
             self.stats.reset = True
         return ok

@@ -141,6 +141,7 @@ class KVCacheConfig:
     block_size: int
     layer_specs: dict  # layer name -> KVCacheSpec
     num_state_slots: int = 0  # mamba/GDN slots (one per running sequence + spec copies)
+    num_cpu_blocks: int = 0   # host mirror for the CPU tier of the prefix cache
 
 
 def get_kv_cache_config(layer_specs: dict, available_bytes: int, block_size: int, max_num_seqs: int,

@@ -49,6 +49,8 @@ class SchedulerOutput:
     num_common_prefix_blocks: int = 0
     grammar_bitmask: Any = None  # numpy int32 [rows, ceil(vocab/32)], bit set = token allowed
     structured_rows: dict[str, int] = field(default_factory=dict)  # request id -> row of grammar_bitmask
+    kv_swap_out: list = field(default_factory=list)  # (GPU block, CPU block): save before the step's forward
+    kv_swap_in: list = field(default_factory=list)   # (CPU block, GPU block): restore before the step's forward
 
     @property
     def is_empty(self) -> bool:

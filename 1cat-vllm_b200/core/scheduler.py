@@ -116,6 +116,8 @@ class Scheduler:
                                                num_state_slots, use_eagle=spec.method == "mtp",
                                                dcp_world_size=vllm_config.parallel_config.decode_context_parallel_size,
                                                log_stats=log_stats)
+        if cc.num_cpu_blocks > 0:
+            self.kv_cache_manager.enable_cpu_offload(cc.num_cpu_blocks)
         self.block_hasher = make_block_hasher(self.kv_cache_manager.block_size, cc.prefix_caching_hash_algo) \
             if self.kv_cache_manager.enable_caching else None
         self.requests: dict[str, Request] = {}
@@ -289,6 +291,8 @@ class Scheduler:
         out.preempted_req_ids = {r.request_id for r in preempted}
         if self.running:
             out.num_common_prefix_blocks = km.get_num_common_prefix_blocks(self.running[0].request_id, len(self.running))
+        if self.kv_cache_manager.offload is not None:
+            out.kv_swap_out, out.kv_swap_in = self.kv_cache_manager.offload.take_ops()
         # advance: the runner computes these tokens in this step
         for rid, n in out.num_scheduled_tokens.items():
             self.requests[rid].num_computed_tokens += n

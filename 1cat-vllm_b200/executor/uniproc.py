@@ -57,6 +57,11 @@ class Executor:
             specs.update(s)
         from onecat_vllm.core.kv_cache_utils import KVCacheConfig
         kvc = KVCacheConfig(min(k.num_blocks for k in kvcs), cfg.cache_config.block_size, specs, max(k.num_state_slots for k in kvcs))
+        cc = cfg.cache_config
+        if (cc.kv_offloading_size > 0 or cc.num_cpu_blocks_override) and not any(s.kind == "mamba" for s in specs.values()):
+            per_block = max(sum(s.page_size_bytes for s in sp.values()) for sp in all_specs)
+            kvc.num_cpu_blocks = cc.num_cpu_blocks_override or int(cc.kv_offloading_size * (1 << 30) // max(per_block, 1))
+        cc.num_cpu_blocks = kvc.num_cpu_blocks
         max_need = -(-cfg.model_config.max_model_len // cfg.cache_config.block_size) + 1
         if any(s.kind != "mamba" for s in specs.values()) and kvc.num_blocks < max_need:
             raise ValueError(f"KV cache of {kvc.num_blocks} blocks cannot hold one sequence of max_model_len="

@@ -143,6 +143,12 @@ class ModelRunner:
                 self.kv_caches.append(alloc(spec))
         if self.mtp is not None:
             self.mtp_cache = alloc(kvc.layer_specs["mtp.0"])
+        # host mirror for the CPU tier of the prefix cache: same page layout, pinned when copies come from a GPU
+        self.cpu_kv = []
+        if kvc.num_cpu_blocks > 0:
+            for c in self.kv_caches:
+                m = torch.zeros((kvc.num_cpu_blocks,) + tuple(c.shape[1:]), dtype=c.dtype)
+                self.cpu_kv.append(m.pin_memory() if self.use_cuda else m)
         self.max_blocks_per_req = -(-self.max_model_len // bs)
         self._init_buffers()
 
@@ -343,8 +349,26 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ one step
     @torch.inference_mode()
+    def _swap_kv(self, so: SchedulerOutput) -> None:
+        """Copies of the CPU prefix-cache tier: evicted blocks to the host first, then restored blocks back
+        (reference: v1/kv_offload/worker/cpu_gpu.py)."""
+        if not self.cpu_kv or not (so.kv_swap_out or so.kv_swap_in):
+            return
+        if so.kv_swap_out:
+            g = torch.tensor([a for a, _ in so.kv_swap_out], dtype=torch.long, device=self.device)
+            c = torch.tensor([b for _, b in so.kv_swap_out], dtype=torch.long)
+            for dev, host in zip(self.kv_caches, self.cpu_kv):
+                host[c] = dev.index_select(0, g).cpu()
+        if so.kv_swap_in:
+            c = torch.tensor([a for a, _ in so.kv_swap_in], dtype=torch.long)
+            g = torch.tensor([b for _, b in so.kv_swap_in], dtype=torch.long, device=self.device)
+            for dev, host in zip(self.kv_caches, self.cpu_kv):
+                dev.index_copy_(0, g, host[c].to(self.device, non_blocking=True))
+
+    @torch.inference_mode()
     def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
         self._update_states(so)
+        self._swap_kv(so)
         if so.total_num_scheduled_tokens == 0:
             return ModelRunnerOutput()
         req_ids, R, T, n_l, rows, drafts_of, max_q, max_s, max_nb = self._prepare_inputs(so)

@@ -113,3 +113,28 @@ def test_embed_matches_direct_forward_and_survives_chunked_prefill():
         sc = llm.score("ab", ["ab", "xyz"])
         assert abs(sc[0] - 1) < 1e-4 and sc[1] < 0.9999
     assert not torch.allclose(ref["last"], ref["mean"])
+
+
+def test_cpu_offload_tier_restores_evicted_prefix_blocks():
+    """A GPU pool too small to keep a long shared prefix across other traffic: with the CPU tier the prefix comes back from the
+    host (prefix-cache hit, restore copies) and the tokens equal those of a run that recomputes it."""
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=512)
+    prefix = [(3 * i) % 290 + 1 for i in range(160)]           # 10 blocks
+    a = [{"prompt_token_ids": prefix + [7, 8, 9]}]
+    filler = [{"prompt_token_ids": [(11 * i + j) % 290 + 1 for i in range(150)]} for j in range(3)]
+    b = [{"prompt_token_ids": prefix + [20, 21]}]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    kw = dict(hf_config=cfg, device="cpu", dtype="float32", max_model_len=256, num_gpu_blocks_override=24, max_num_seqs=1)
+    plain = LLM(**kw)
+    want = [plain.generate(x, sp)[0].outputs[0].token_ids for x in (a, *[[f] for f in filler], b)]
+    plain.shutdown()
+    llm = LLM(num_cpu_blocks_override=64, **kw)
+    tier = llm.llm_engine.engine_core.core.scheduler.kv_cache_manager.offload
+    assert tier is not None and tier.capacity == 64
+    got = [llm.generate(x, sp)[0] for x in (a, *[[f] for f in filler], b)]
+    assert [g.outputs[0].token_ids for g in got] == want
+    assert tier.stored >= 10 and tier.restored >= 10, (tier.stored, tier.restored)
+    assert got[-1].num_cached_tokens >= 160, "the shared prefix must count as a cache hit although the GPU pool had dropped it"
+    llm.shutdown()

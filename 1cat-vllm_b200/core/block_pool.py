@@ -39,7 +39,9 @@ class BlockPool:
                 continue
             b.block_hash = request.block_hashes[i]
             self.cached.setdefault(b.block_hash, {})[b.block_id] = b
-            self.events.append(("stored", b.block_id))
+            self.events.append(("stored", b.block_id, b.block_hash))
+            if self.offload is not None:
+                self.offload.on_stored(b.block_hash, b.block_id)
 
     def get_new_blocks(self, n: int) -> list[KVCacheBlock]:
         if n > self.get_num_free_blocks():
@@ -64,7 +66,7 @@ class BlockPool:
                 if self.offload is not None:  # the last GPU copy of this prefix block: keep it on the host
                     self.offload.on_evict(h, b.block_id)
         b.block_hash = None
-        self.events.append(("removed", b.block_id))
+        self.events.append(("removed", b.block_id, h))
         return True
 
     def touch(self, blocks: Iterable[KVCacheBlock]) -> None:
@@ -91,6 +93,7 @@ class BlockPool:
         self.cached.clear()
         for b in self.blocks:
             b.block_hash = None
+        self.events.append(("cleared", -1, None))
         return True
 
     def get_num_free_blocks(self) -> int:

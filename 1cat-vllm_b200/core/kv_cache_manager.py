@@ -74,6 +74,16 @@ class KVCacheManager:
             self.stats.hits += len(hit) * self.block_size
         return hit, len(hit) * self.block_size
 
+    def enable_kv_connector(self, kv_transfer_config: dict) -> None:
+        from onecat_vllm.core.kv_offload import SharedStorageTier
+        name = kv_transfer_config.get("kv_connector", "SharedStorageConnector")
+        if name not in ("SharedStorageConnector", "ExampleConnector"):
+            raise ValueError(f"unknown kv_connector {name!r}: this build has SharedStorageConnector")
+        extra = kv_transfer_config.get("kv_connector_extra_config") or {}
+        if self.enable_caching:
+            self.offload = self.block_pool.offload = SharedStorageTier(extra.get("shared_storage_path", "/tmp/onecat_kv"),
+                                                                       kv_transfer_config.get("kv_role", "kv_both"))
+
     def _restore_from_cpu(self, hashes: list) -> list[KVCacheBlock]:
         """Continue a prefix match in the CPU tier: every consecutive hit gets a fresh GPU block, a restore copy for this step and its
         place in the GPU index; the blocks go back to the free queue (cached, unreferenced) so that the caller treats them like

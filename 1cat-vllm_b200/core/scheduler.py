@@ -116,7 +116,9 @@ class Scheduler:
                                                num_state_slots, use_eagle=spec.method == "mtp",
                                                dcp_world_size=vllm_config.parallel_config.decode_context_parallel_size,
                                                log_stats=log_stats)
-        if cc.num_cpu_blocks > 0:
+        if cc.kv_transfer_config:
+            self.kv_cache_manager.enable_kv_connector(cc.kv_transfer_config)
+        elif cc.num_cpu_blocks > 0:
             self.kv_cache_manager.enable_cpu_offload(cc.num_cpu_blocks)
         self.block_hasher = make_block_hasher(self.kv_cache_manager.block_size, cc.prefix_caching_hash_algo) \
             if self.kv_cache_manager.enable_caching else None

@@ -36,6 +36,8 @@ class EngineCore:
         self.step_count = 0
         self.paused = False
         self._structured = None  # built on the first request that asks for a grammar
+        from onecat_vllm.core.kv_events import make_publisher
+        self._kv_events = make_publisher(vllm_config.cache_config.kv_events_config)
         log.info_once(f"engine core ready: {num_blocks} KV blocks, {num_slots} state slots, init {time.time() - t0:.1f}s")
 
     def _on_executor_failure(self) -> None:
@@ -84,6 +86,9 @@ class EngineCore:
             self._failed = True
             raise CollectiveTimeout(f"device wait expired (status {mro.status:#x})")
         outs = self.scheduler.update_from_output(so, mro)
+        ev = self.scheduler.kv_cache_manager.block_pool.take_events()  # also bounds the list when nobody listens
+        if self._kv_events is not None:
+            self._kv_events.publish(ev)
         if self._structured is not None and self._structured.grammars:
             for eco in outs.values():
                 for o in eco.outputs:

@@ -60,6 +60,7 @@ class ModelRunner:
         self.model = None
         self.mtp = None
         self.kv_caches: list = []
+        self._pending_saves: list = []
         self.lora_manager = None
         self.mtp_cache = None
         self.sampler = Sampler()
@@ -352,7 +353,11 @@ class ModelRunner:
     def _swap_kv(self, so: SchedulerOutput) -> None:
         """Copies of the CPU prefix-cache tier: evicted blocks to the host first, then restored blocks back
         (reference: v1/kv_offload/worker/cpu_gpu.py)."""
-        if not self.cpu_kv or not (so.kv_swap_out or so.kv_swap_in):
+        if not (so.kv_swap_out or so.kv_swap_in):
+            return
+        if (so.kv_swap_out and isinstance(so.kv_swap_out[0][1], str)) or (so.kv_swap_in and isinstance(so.kv_swap_in[0][0], str)):
+            return self._file_kv(so)
+        if not self.cpu_kv:
             return
         if so.kv_swap_out:
             g = torch.tensor([a for a, _ in so.kv_swap_out], dtype=torch.long, device=self.device)
@@ -365,8 +370,35 @@ class ModelRunner:
             for dev, host in zip(self.kv_caches, self.cpu_kv):
                 dev.index_copy_(0, g, host[c].to(self.device, non_blocking=True))
 
+    def _file_kv(self, so: SchedulerOutput) -> None:
+        """Shared-storage connector: restores read ``[layers][page]`` tensors written by this or another engine. Saves are
+        deferred until the step's forward has filled the blocks (``_save_kv_files``). Each rank writes its own shard."""
+        for f, g in so.kv_swap_in:
+            pages = torch.load(self._rank_file(f), map_location="cpu", weights_only=True)
+            for dev, pg in zip(self.kv_caches, pages):
+                dev[g].copy_(pg.to(self.device))
+        self._pending_saves = list(so.kv_swap_out)
+
+    def _rank_file(self, f: str) -> str:
+        return f if self.pp.world_size == 1 else f"{f}.r{self.pp.rank}"
+
+    def _save_kv_files(self) -> None:
+        import os
+        for g, f in self._pending_saves:
+            f = self._rank_file(f)
+            tmp = f"{f}.tmp{os.getpid()}"
+            torch.save([dev[g].cpu() for dev in self.kv_caches], tmp)
+            os.replace(tmp, f)  # readers only ever see complete files
+        self._pending_saves = []
+
     @torch.inference_mode()
     def execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+        out = self._execute_model(so)
+        if self._pending_saves:
+            self._save_kv_files()
+        return out
+
+    def _execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
         self._update_states(so)
         self._swap_kv(so)
         if so.total_num_scheduled_tokens == 0:

@@ -189,3 +189,29 @@ def test_rejects_bad_requests():
     s.add_request(req("x", 4, s=s))
     with pytest.raises(ValueError):
         s.add_request(req("x", 4, s=s))
+
+
+def test_kv_events_are_published_over_zmq():
+    """Block stored / removed events reach a ZMQ subscriber with increasing sequence numbers."""
+    import msgpack
+    import zmq
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    ep = "ipc:///tmp/onecat-kv-events-test"
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, kv_events_config={"endpoint": ep, "topic": "kv"})
+    sub = zmq.Context.instance().socket(zmq.SUB)
+    sub.connect(ep)
+    sub.setsockopt(zmq.SUBSCRIBE, b"kv")
+    import time
+    time.sleep(0.3)
+    llm.generate([{"prompt_token_ids": list(range(1, 50))}], SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True))
+    seqs, stored = [], 0
+    while sub.poll(500):
+        topic, seq, payload = sub.recv_multipart()
+        seqs.append(int.from_bytes(seq, "big"))
+        body = msgpack.unpackb(payload)
+        stored += sum(1 for e in body["events"] if e["type"] == "BlockStored" and e["block_hash"])
+    assert seqs == sorted(seqs) and len(seqs) >= 1 and stored >= 3
+    sub.close(linger=0)
+    llm.shutdown()

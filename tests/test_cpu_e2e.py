@@ -138,3 +138,28 @@ def test_cpu_offload_tier_restores_evicted_prefix_blocks():
     assert tier.stored >= 10 and tier.restored >= 10, (tier.stored, tier.restored)
     assert got[-1].num_cached_tokens >= 160, "the shared prefix must count as a cache hit although the GPU pool had dropped it"
     llm.shutdown()
+
+
+def test_shared_storage_connector_hands_prefill_kv_to_another_engine(tmp_path):
+    """Disaggregated prefill / decode through the shared-storage KV connector: a producer engine runs the prompt once, a second
+    (consumer) engine restores the blocks by hash and continues with the same tokens as an engine that computed everything itself."""
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=512)
+    prompt = [{"prompt_token_ids": [(5 * i) % 290 + 1 for i in range(100)]}]
+    kw = dict(hf_config=cfg, device="cpu", dtype="float32", max_model_len=256)
+    ktc = lambda role: {"kv_connector": "SharedStorageConnector", "kv_role": role, "kv_connector_extra_config": {"shared_storage_path": str(tmp_path)}}
+    solo = LLM(**kw)
+    want = solo.generate(prompt, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0].outputs[0].token_ids
+    solo.shutdown()
+    prefill = LLM(kv_transfer_config=ktc("kv_producer"), **kw)
+    first = prefill.generate(prompt, SamplingParams(temperature=0.0, max_tokens=1))[0].outputs[0].token_ids
+    prefill.shutdown()
+    import os
+    assert len([f for f in os.listdir(tmp_path) if f.endswith(".kv")]) == 100 // 16
+    decode = LLM(kv_transfer_config=ktc("kv_consumer"), **kw)
+    out = decode.generate(prompt, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0]
+    tier = decode.llm_engine.engine_core.core.scheduler.kv_cache_manager.offload
+    assert out.outputs[0].token_ids == want and first == want[:1]
+    assert tier.restored == 100 // 16 and out.num_cached_tokens == 96 and tier.stored == 0
+    decode.shutdown()

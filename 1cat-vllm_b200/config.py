@@ -110,6 +110,7 @@ class ModelConfig:
     topk_group: int = 1
     routed_scaling_factor: float = 1.0
     first_k_dense_replace: int = 0
+    dense_layers: tuple = ()  # layers of a mixture-of-experts model that keep a dense MLP (decoder_sparse_step / mlp_only_layers)
     shared_expert_gate: bool = False  # Qwen: shared output scaled by sigmoid(gate(x))
     # MLA
     use_mla: bool = False
@@ -155,7 +156,7 @@ class ModelConfig:
         return self.layer_types[i] if self.layer_types else "full_attention"
 
     def is_moe_layer(self, i: int) -> bool:
-        return self.is_moe and i >= self.first_k_dense_replace
+        return self.is_moe and i >= self.first_k_dense_replace and i not in self.dense_layers
 
     @property
     def rotary_dim(self) -> int:
@@ -200,8 +201,8 @@ class ModelConfig:
             num_nextn_predict_layers=hf.get("num_nextn_predict_layers", hf.get("mtp_num_hidden_layers", 0)) or 0,
         )
         a = arch.lower()
-        if "qwen2" in a and "moe" not in a:
-            kw["attention_bias"] = True
+        if "qwen2" in a:
+            kw["attention_bias"] = hf.get("qkv_bias", True)
         if "qwen3" in a:
             kw["qk_norm"] = True
         if "qwen3next" in a or "qwen3_5" in a or "qwen3_next" in a:
@@ -212,11 +213,15 @@ class ModelConfig:
             if kw["layer_types"] is None:
                 iv = hf.get("full_attention_interval", 4)
                 kw["layer_types"] = ["full_attention" if (i + 1) % iv == 0 else "linear_attention" for i in range(kw["num_hidden_layers"])]
-        if hf.get("num_experts") or hf.get("n_routed_experts"):
-            kw.update(num_experts=hf.get("num_experts") or hf.get("n_routed_experts"),
-                      num_experts_per_tok=hf.get("num_experts_per_tok", 8),
-                      moe_intermediate_size=hf.get("moe_intermediate_size", 512),
-                      norm_topk_prob=hf.get("norm_topk_prob", True))
+        n_exp = hf.get("num_experts") or hf.get("n_routed_experts") or hf.get("num_local_experts")
+        if n_exp:
+            # Mixtral has no separate expert width and always renormalises its top-k weights
+            kw.update(num_experts=n_exp, num_experts_per_tok=hf.get("num_experts_per_tok", 8),
+                      moe_intermediate_size=hf.get("moe_intermediate_size") or hf.get("intermediate_size", 512),
+                      norm_topk_prob=hf.get("norm_topk_prob", True) or "mixtral" in a)
+            step, only = hf.get("decoder_sparse_step", 1) or 1, set(hf.get("mlp_only_layers") or [])
+            if step > 1 or only:
+                kw["dense_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i in only or (i + 1) % step != 0)
             if "deepseek" in a:
                 kw.update(shared_expert_intermediate_size=hf.get("n_shared_experts", 1) * hf.get("moe_intermediate_size", 2048),
                           scoring_func=hf.get("scoring_func", "sigmoid"), n_group=hf.get("n_group", 8), topk_group=hf.get("topk_group", 4),

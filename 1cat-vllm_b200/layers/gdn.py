@@ -38,6 +38,37 @@ class GatedDeltaNet(nn.Module):
         self.eps = cfg.rms_norm_eps
         self.layer_idx = layer_idx
 
+    def deinterleave(self, which: str, w: torch.Tensor) -> torch.Tensor:
+        """Checkpoints with a fused ``in_proj_qkvz`` / ``in_proj_ba`` (Qwen3-Next) store the rows per key-head group —
+        ``[q_g | k_g | v_g | z_g]`` resp. ``[b_g | a_g]`` for group g — while this layer keeps ``[q | k | v | z]`` and ``[b | a]`` over all
+        heads (reference: models/qwen3_next.py ``fix_query_key_value_ordering``). ``w`` is the full (unsharded) tensor."""
+        cfg_hk = self.Hk * get_state().tp_size
+        r = self.Hv // self.Hk
+        if which == "in_proj_qkvz":
+            parts = [self.K, self.K, r * self.V, r * self.V]
+        else:
+            parts = [r, r]
+        g = w.reshape(cfg_hk, sum(parts), *w.shape[1:])
+        outs, o = [], 0
+        for n in parts:
+            outs.append(g[:, o:o + n].reshape(cfg_hk * n, *w.shape[1:]))
+            o += n
+        return torch.cat(outs, 0)
+
+    def load_weight(self, pname: str, w: torch.Tensor, shard=None) -> None:
+        """Per-head and per-channel parameters, sharded like the heads: conv channels are ``[q | k | v]`` segments."""
+        st = get_state()
+        tp, r = st.tp_size, st.tp_rank
+        p = getattr(self, pname)
+        if pname == "conv_weight":
+            w = w.reshape(w.shape[0], -1)
+            kd, vd = self.key_dim * tp, self.val_dim * tp
+            segs = [w[:kd], w[kd:2 * kd], w[2 * kd:2 * kd + vd]]
+            w = torch.cat([s.chunk(tp, 0)[r] for s in segs], 0)
+        elif pname in ("A_log", "dt_bias"):
+            w = w.reshape(-1).chunk(tp, 0)[r]
+        p.data.copy_(w.reshape(p.shape).to(p.dtype))
+
     def state_shapes(self):
         return (self.conv_dim, self.kw - 1), (self.Hv, self.K, self.V)
 

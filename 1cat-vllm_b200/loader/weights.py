@@ -30,6 +30,10 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
                 yield k, sf.get_tensor(k)
 
 
+# checkpoint names whose tensors live under another name here (a parameter of the block instead of a sub-module's weight)
+_RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
+            (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+            (".mlp.shared_experts.", ".mlp.shared_expert."))
 _EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv|weight_scale)$")
 
 
@@ -42,13 +46,35 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
     for name, w in weights:
         if name.startswith("language_model."):
             name = name[len("language_model."):]
+        elif name.startswith("model.language_model."):  # text tower of a multimodal checkpoint (Qwen3.5)
+            name = "model." + name[len("model.language_model."):]
         if "rotary_emb.inv_freq" in name or name.startswith(("visual.", "model.visual.")):
             continue
+        for theirs, ours in _RENAMES:
+            if theirs in name:
+                name = name.replace(theirs, ours)
+        if ".block_sparse_moe." in name:  # Mixtral naming: block_sparse_moe.{gate, experts.N.w1|w3|w2}
+            name = name.replace(".block_sparse_moe.", ".mlp.")
+            for theirs, ours in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):
+                name = name.replace(theirs, ours)
         m = _EXPERT_RE.match(name)
         if m:
             mod = mods.get(m.group(1) + ".experts")
             if mod is not None:
                 mod.load_expert_weight(int(m.group(2)), m.group(3), m.group(4), w)
+                loaded.add(name)
+            continue
+        if ".linear_attn.in_proj_qkv." in name:
+            # Qwen3.5 keeps q|k|v fused (contiguous segments) and z separate: route the three segments to their slots
+            tgt = name.replace(".in_proj_qkv.", ".in_proj_qkvz.")
+            mod_name, _, pname = tgt.rpartition(".")
+            mod = mods.get(mod_name)
+            if mod is not None:
+                sizes = mod.output_sizes[:3]
+                o = 0
+                for i, n in enumerate(sizes):
+                    mod.load_weight(pname, w.narrow(0, o, n), i)
+                    o += n
                 loaded.add(name)
             continue
         target, shard = name, None
@@ -60,6 +86,8 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
                     break
         mod_name, _, pname = target.rpartition(".")
         mod = mods.get(mod_name)
+        if shard is None and (mod_name.endswith(".in_proj_qkvz") or mod_name.endswith(".in_proj_ba")) and pname == "weight":
+            w = mods[mod_name.rsplit(".", 1)[0]].deinterleave(mod_name.rsplit(".", 1)[1], w)
         if mod is not None and hasattr(mod, "load_weight"):
             mod.load_weight(pname, w, shard)
             loaded.add(name)

@@ -1,0 +1,72 @@
+"""Checkpoint-format and model-math parity with Hugging Face transformers on CPU: a tiny randomly initialised HF model is saved with
+``save_pretrained`` and loaded by this engine; greedy continuations and first-token log-probabilities must match
+(reference test model: tests/models/language/generation/test_common.py — vLLM vs HF runner)."""
+import pytest
+import torch
+
+transformers = pytest.importorskip("transformers")
+
+BASE = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=320,
+            max_position_embeddings=256, rms_norm_eps=1e-6, tie_word_embeddings=False)
+CASES = {
+    "LlamaForCausalLM": dict(BASE, model_type="llama", rope_theta=10000.0),
+    "MistralForCausalLM": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=None),
+    "Qwen2ForCausalLM": dict(BASE, model_type="qwen2", rope_theta=1e6),
+    "Qwen3ForCausalLM": dict(BASE, model_type="qwen3", head_dim=32, rope_theta=1e6),
+    "Qwen3MoeForCausalLM": dict(BASE, model_type="qwen3_moe", head_dim=32, rope_theta=1e6, num_experts=8, num_experts_per_tok=2,
+                                moe_intermediate_size=64, norm_topk_prob=True, decoder_sparse_step=1, mlp_only_layers=[]),
+    "MixtralForCausalLM": dict(BASE, model_type="mixtral", rope_theta=1e6, num_local_experts=4, num_experts_per_tok=2),
+    "Qwen2MoeForCausalLM": dict(BASE, model_type="qwen2_moe", rope_theta=1e6, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                                shared_expert_intermediate_size=96, norm_topk_prob=False, decoder_sparse_step=1, mlp_only_layers=[]),
+    "DeepseekV3ForCausalLM": dict(BASE, model_type="deepseek_v3", num_key_value_heads=4, rope_theta=10000.0, q_lora_rank=32, kv_lora_rank=32,
+                                  qk_nope_head_dim=16, qk_rope_head_dim=16, v_head_dim=16, n_routed_experts=8, n_shared_experts=1,
+                                  num_experts_per_tok=2, moe_intermediate_size=48, n_group=2, topk_group=1, routed_scaling_factor=1.5,
+                                  norm_topk_prob=True, first_k_dense_replace=1, scoring_func="sigmoid", rope_scaling=None),
+    "Qwen3_5ForCausalLM": dict(BASE, model_type="qwen3_5_text", head_dim=32, num_hidden_layers=4, full_attention_interval=2,
+                               linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16,
+                               linear_conv_kernel_dim=4, rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
+    "Qwen3_5MoeForCausalLM": dict(BASE, model_type="qwen3_5_moe_text", head_dim=32, num_hidden_layers=4, full_attention_interval=2,
+                                  linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16, linear_value_head_dim=16,
+                                  linear_conv_kernel_dim=4, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                                  shared_expert_intermediate_size=64,
+                                  rope_parameters={"rope_type": "default", "rope_theta": 1e6, "partial_rotary_factor": 0.5}),
+    "DeepseekV2ForCausalLM": dict(BASE, model_type="deepseek_v2", num_key_value_heads=4, rope_theta=10000.0, q_lora_rank=None, kv_lora_rank=32,
+                                  qk_nope_head_dim=16, qk_rope_head_dim=16, v_head_dim=16, n_routed_experts=4, n_shared_experts=1,
+                                  num_experts_per_tok=2, moe_intermediate_size=48, n_group=1, topk_group=1, routed_scaling_factor=1.0,
+                                  norm_topk_prob=False, first_k_dense_replace=1, scoring_func="softmax", topk_method="greedy", rope_scaling=None),
+    "Phi3ForCausalLM": dict(BASE, model_type="phi3", rope_theta=10000.0, pad_token_id=0),
+    "SeedOssForCausalLM": dict(BASE, model_type="seed_oss", head_dim=16, rope_theta=10000.0),
+    "Qwen3NextForCausalLM": dict(BASE, model_type="qwen3_next", head_dim=32, rope_theta=1e6, partial_rotary_factor=0.5, num_hidden_layers=4,
+                                 full_attention_interval=2, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=16,
+                                 linear_value_head_dim=16, linear_conv_kernel_dim=4, num_experts=4, num_experts_per_tok=2,
+                                 moe_intermediate_size=64, shared_expert_intermediate_size=64, norm_topk_prob=True, decoder_sparse_step=1,
+                                 mlp_only_layers=[]),
+}
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("arch", list(CASES))
+def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
+    from onecat_vllm import LLM, SamplingParams
+    cfg_cls = transformers.AutoConfig.for_model(CASES[arch]["model_type"], **{k: v for k, v in CASES[arch].items() if k != "model_type"})
+    cfg_cls.architectures = [arch]
+    torch.manual_seed(0)
+    hf = getattr(transformers, arch)(cfg_cls).eval().float()
+    for p in hf.parameters():  # widen the logit gaps so that greedy choices are not near-ties
+        if p.dim() >= 2:
+            p.data.mul_(3.0)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(1, 300, (n,), generator=g).tolist() for n in (5, 23, 40)]
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)
+    outs = llm.generate([{"prompt_token_ids": p} for p in prompts], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, logprobs=0))
+    llm.shutdown()
+    for p, o in zip(prompts, outs):
+        ids = torch.tensor([p])
+        with torch.no_grad():
+            ref = hf.generate(ids, max_new_tokens=8, do_sample=False, pad_token_id=0)[0, len(p):].tolist()
+            lp = torch.log_softmax(hf(ids).logits[0, -1].float(), -1)
+        got = o.outputs[0].token_ids
+        assert got == ref, f"{arch}: {got} vs {ref}"
+        first = o.outputs[0].logprobs[0][got[0]].logprob
+        assert abs(first - lp[ref[0]].item()) < 2e-3, (arch, first, lp[ref[0]].item())

@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|norm|gdn|moe] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|moe] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -93,13 +93,15 @@ def bench_w4(rows: list, small: bool, iters: int, pk: dict) -> None:
         del layer, x, out
 
 
-def bench_attn(rows: list, small: bool, iters: int, pk: dict) -> None:
+def bench_attn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool = False) -> None:
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.worker.attn_metadata import AttentionMetadata
     cases = [("decode", 64, 1, 1150, 40, 8, 128), ("decode", 8, 1, 32768, 40, 8, 128), ("decode-d256", 64, 1, 2048, 24, 4, 256),
              ("prefill", 8, 1024, 0, 40, 8, 128), ("prefill", 1, 8192, 0, 40, 8, 128), ("prefill-d256", 1, 4096, 0, 24, 4, 256)]
     if small:
         cases = [("decode", 64, 1, 1150, 40, 8, 128)]
+    if prefill_only:
+        cases = [("prefill", 2, 2048, 0, 40, 8, 128)] if small else [c for c in cases if c[0].startswith("prefill")]
     for name, R, ql, ctx, Hq, Hkv, D in cases:
         S = ctx + ql
         nb = -(-S // 16)
@@ -230,7 +232,10 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq)):
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq),
+                     ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True))):
+        if not a.only and name == "attn_prefill":
+            continue
         if a.only and a.only != name:
             continue
         fn(rows, a.small, a.iters, pk)

@@ -57,7 +57,8 @@ class QuantConfig:
         if m == "fp8":
             wbs = q.get("weight_block_size")
             return cls("fp8", 8, 0, False, weight_block_size=tuple(wbs) if wbs else None,
-                       activation_scheme=q.get("activation_scheme", "dynamic"), expert_method=q.get("expert_method"))
+                       activation_scheme=q.get("activation_scheme", "dynamic"), expert_method=q.get("expert_method"),
+                       modules_to_not_convert=(q.get("modules_to_not_convert") or q.get("ignored_layers") or []) + ["lm_head", "embed_tokens"])
         if m in ("nvfp4", "modelopt_fp4", "modelopt"):
             return cls("nvfp4", 4, 16, False)
         if m in ("mxfp4",):

@@ -28,6 +28,35 @@ CFG_27B = dict(architectures=["Qwen3ForCausalLM"], hidden_size=5120, intermediat
                num_attention_heads=40, num_key_value_heads=8, head_dim=128, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
                max_position_embeddings=4096, tie_word_embeddings=False,
                quantization_config=dict(quant_method="awq", bits=4, group_size=128, zero_point=True))
+# The other configurations of the benchmark plan (selected with --config; the default stays the dense AWQ model above).
+_GDN = dict(linear_num_key_heads=16, linear_num_value_heads=48, linear_key_head_dim=128, linear_value_head_dim=128, linear_conv_kernel_dim=4,
+            full_attention_interval=4, attn_output_gate=True, partial_rotary_factor=0.25)
+CFG_HYBRID_27B = dict(architectures=["Qwen3_5ForCausalLM"], hidden_size=5120, intermediate_size=17408, num_hidden_layers=64,
+                      num_attention_heads=24, num_key_value_heads=4, head_dim=256, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                      max_position_embeddings=262144, tie_word_embeddings=False, **_GDN)
+CFG_MOE_35B = dict(architectures=["Qwen3_5MoeForCausalLM"], hidden_size=2048, intermediate_size=5632, num_hidden_layers=40,
+                   num_attention_heads=16, num_key_value_heads=2, head_dim=256, vocab_size=151936, rope_theta=1e6, rms_norm_eps=1e-6,
+                   max_position_embeddings=8192, tie_word_embeddings=False, num_experts=256, num_experts_per_tok=8, moe_intermediate_size=512,
+                   shared_expert_intermediate_size=512, norm_topk_prob=True,
+                   quantization_config=dict(quant_method="fp8", weight_block_size=[128, 128], modules_to_not_convert=["self_attn", "linear_attn", "shared_expert", "lm_head"]),
+                   **dict(_GDN, linear_num_value_heads=32))
+CFG_DSV3 = dict(architectures=["DeepseekV3ForCausalLM"], hidden_size=7168, intermediate_size=18432, num_hidden_layers=61, num_attention_heads=128,
+                num_key_value_heads=128, vocab_size=129280, rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=8192,
+                tie_word_embeddings=False, q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128,
+                n_routed_experts=256, n_shared_experts=1, num_experts_per_tok=8, moe_intermediate_size=2048, n_group=8, topk_group=4,
+                routed_scaling_factor=2.5, norm_topk_prob=True, first_k_dense_replace=3, scoring_func="sigmoid",
+                quantization_config=dict(quant_method="fp8", weight_block_size=[128, 128], expert_method="mxfp4"))
+CONFIGS = {
+    # name: (hf config, description, concurrency, input len, output len, speculative config, dtype string)
+    "dense27b": (CFG_27B, "dense 27B-class AWQ W4A16 (64L, h5120, 40q/8kv x128, ffn 17408, vocab 151936)", 64, 1024, 256, None,
+                 "bf16 activations/KV, int4 AWQ weights (W4A16)"),
+    "hybrid27b": (CFG_HYBRID_27B, "hybrid 27B-class bf16 (64L, 3:1 Gated-DeltaNet : gated attention 24q/4kv x256) + MTP(3), Bernoulli(0.7) acceptance", 8,
+                  131072, 512, dict(method="mtp", num_speculative_tokens=3, synthetic_acceptance_rate=0.7), "bf16"),
+    "moe35b": (CFG_MOE_35B, "MoE 35B-A3B-class (40L, h2048, 3:1 GDN : attention, 256 experts top-8 + shared, FP8 128x128 experts)", 256, 2048, 512, None,
+               "bf16 activations/KV, FP8 e4m3 block-scaled expert weights (weight-only)"),
+    "dsv3": (CFG_DSV3, "DeepSeek-V3-class MLA + MoE (h7168, 128 heads, 256 experts top-8 grouped sigmoid, MXFP4 experts, FP8 dense)", 128, 4096, 1024, None,
+             "bf16 activations/KV, MXFP4 expert weights, FP8 block-scaled dense weights (weight-only)"),
+}
 QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -77,15 +106,28 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def _kv_bytes(cfg: dict, C: int, seq: int, gpus: int) -> int:
+    """KV-cache bytes per GPU for C sequences of `seq` tokens (bf16): attention layers only; MLA keeps one 576-wide latent."""
+    L = cfg["num_hidden_layers"]
+    if cfg.get("kv_lora_rank"):
+        per_tok = L * (cfg["kv_lora_rank"] + cfg["qk_rope_head_dim"]) * 2
+    else:
+        attn_layers = L // cfg["full_attention_interval"] if cfg.get("full_attention_interval") else L
+        kvh = max(cfg["num_key_value_heads"] // gpus, 1)
+        per_tok = attn_layers * 2 * kvh * cfg["head_dim"] * 2
+    return int((C + 2) * seq * per_tok)
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--concurrency", type=int, default=64)
-    ap.add_argument("--input-len", type=int, default=1024)
-    ap.add_argument("--output-len", type=int, default=256)
+    ap.add_argument("--config", default="dense27b", choices=sorted(CONFIGS), help="benchmark configuration; the default is the headline one")
+    ap.add_argument("--concurrency", type=int, default=0, help="0 = the configuration's own value")
+    ap.add_argument("--input-len", type=int, default=0)
+    ap.add_argument("--output-len", type=int, default=0)
     ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 makes the run invalid as a headline number")
     ap.add_argument("--tp-comm", default=os.environ.get("ONECAT_TP_COMM", "fused"))
     ap.add_argument("--eager", action="store_true")
@@ -110,14 +152,19 @@ def main() -> None:
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams
 
-    cfg = dict(CFG_27B)
+    base_cfg, desc, c0, in0, out0, spec, dtype_desc = CONFIGS[args.config]
+    cfg = dict(base_cfg)
+    if args.config == "dsv3" and not args.layers and args.gpus < 8:
+        cfg["num_hidden_layers"] = max(4, 61 * args.gpus // 8)  # the plan's 1/2/4-GPU points: same layer shapes, 61*n/8 layers
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
-    C, IN, OUT = args.concurrency, args.input_len, args.output_len
+    C, IN, OUT = args.concurrency or c0, args.input_len or in0, args.output_len or out0
     ea = EngineArgs(hf_config=cfg, dtype="bfloat16", device="cuda", max_model_len=IN + OUT + 16, max_num_seqs=C, max_num_batched_tokens=8192,
                     tensor_parallel_size=args.gpus, distributed_executor_backend="external_launcher" if args.gpus > 1 else None,
                     tp_comm=args.tp_comm, enable_prefix_caching=False, gpu_memory_utilization=0.85, disable_log_stats=False,
-                    enforce_eager=args.eager, kv_cache_memory_bytes=int((C + 2) * (IN + OUT + 32) * cfg["num_hidden_layers"] * 2 * (8 // min(args.gpus, 8)) * 128 * 2))
+                    enforce_eager=args.eager, speculative_config=spec,
+                    enable_expert_parallel=args.config in ("moe35b", "dsv3") and args.gpus > 1,
+                    kv_cache_memory_bytes=_kv_bytes(cfg, C, IN + OUT + 32, args.gpus))
     eng = LLMEngine.from_engine_args(ea)
     runner = eng.engine_core.core.executor.worker.runner
     g = torch.Generator().manual_seed(0)
@@ -197,9 +244,9 @@ def main() -> None:
         res = {
             "metric": "output tokens/s (box, max over ranks)", "value": tokens / (dev_ms / 1e3) if dev_ms > 0 else None, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dev_ms / args.steps,
-            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16 activations/KV, int4 AWQ weights (W4A16)",
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype_desc,
             "data": "synthetic: random token ids, random-init weights of the named architecture",
-            "config": {"model": "dense 27B-class AWQ W4A16 (64L, h5120, 40q/8kv x128, ffn 17408, vocab 151936)",
+            "config": {"model": desc, "name": args.config,
                        "global_batch": C, "seq_len": IN + OUT, "parallelism": f"tp{args.gpus}", "workload": f"{IN} in / {OUT} out, concurrency {C}, closed loop steady state",
                        "layers": cfg["num_hidden_layers"], "l2": "inputs larger than L2 (each step streams >10 GB of weights and KV)",
                        "tp_comm": args.tp_comm if args.gpus > 1 else "none", "cuda_graphs": not args.eager,

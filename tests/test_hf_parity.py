@@ -70,3 +70,39 @@ def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
         assert got == ref, f"{arch}: {got} vs {ref}"
         first = o.outputs[0].logprobs[0][got[0]].logprob
         assert abs(first - lp[ref[0]].item()) < 2e-3, (arch, first, lp[ref[0]].item())
+
+
+@pytest.mark.timeout(900)
+def test_cpu_plumbing_run_matches_transformers():
+    """The benchmark plan's CPU plumbing configuration: tiny Llama-style fp32 decoder (4 layers, hidden 256, 8 q / 2 kv heads of 32,
+    FFN 688, vocab 32000, untied head, RoPE theta 1e6, N(0, 0.02) weights from seed 0), 32 requests with prompts of 16..128 random
+    tokens, 64 greedy tokens each with ignore_eos, through the engine (continuous batching, paged KV, block 16) against
+    ``transformers`` greedy generation."""
+    import tempfile
+    from onecat_vllm import LLM, SamplingParams
+    cfg = transformers.LlamaConfig(hidden_size=256, intermediate_size=688, num_hidden_layers=4, num_attention_heads=8, num_key_value_heads=2,
+                                   head_dim=32, vocab_size=32000, rms_norm_eps=1e-6, rope_theta=1e6, max_position_embeddings=512,
+                                   tie_word_embeddings=False, initializer_range=0.02)
+    cfg.architectures = ["LlamaForCausalLM"]
+    torch.manual_seed(0)
+    hf = transformers.LlamaForCausalLM(cfg).eval().float()
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(16, 129, (32,), generator=g).tolist()
+    prompts = [torch.randint(0, 32000, (n,), generator=g).tolist() for n in lens]
+    with tempfile.TemporaryDirectory() as d:
+        hf.save_pretrained(d, safe_serialization=True)
+        llm = LLM(model=d, device="cpu", dtype="float32", max_model_len=256, block_size=16, max_num_seqs=32, max_num_batched_tokens=512)
+        outs = llm.generate([{"prompt_token_ids": p} for p in prompts], SamplingParams(temperature=0.0, max_tokens=64, ignore_eos=True))
+        llm.shutdown()
+    exact = total = 0
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            ref = hf.generate(torch.tensor([p]), max_new_tokens=64, do_sample=False, pad_token_id=0)[0, len(p):].tolist()
+        got = o.outputs[0].token_ids
+        assert len(got) == 64
+        n = next((i for i, (a, b) in enumerate(zip(got, ref)) if a != b), 64)
+        exact += n == 64
+        total += n
+    # N(0, 0.02) weights make the logits nearly flat, so a last-bit difference in summation order can flip a greedy choice;
+    # everything before the first such flip must agree
+    assert exact >= 30 and total >= 0.97 * 32 * 64, (exact, total)

@@ -2,13 +2,14 @@
 //
 // One CTA owns 128 consecutive query tokens of one request for one query head and walks the keys in tiles of 128:
 //   S = Q K^T      tcgen05.mma, both operands in shared memory (TMA, 128-byte swizzle), S in TMEM (fp32, double-buffered)
-//   P = softmax    four warps, one thread per query row: tcgen05.ld S, running max / sum in registers, P written back to
-//                  TMEM as bf16 (tcgen05.st)
+//   P = softmax    eight warps, two threads per query row (64 keys each; the row maximum is exchanged through shared memory):
+//                  tcgen05.ld S, running max / sum in registers, P written back to TMEM as bf16 (tcgen05.st)
 //   O_tile = P V   tcgen05.mma with operand A (P) read from TMEM and V as an MN-major shared-memory operand straight from the
 //                  paged cache layout [key][d]; the softmax threads add O_tile into their fp32 output row in registers, rescaled
 //                  by exp2(old max - new max), so no accumulator in TMEM ever needs a correction pass
 // Roles: warp 0 = TMA producer (the 16 page loads of a K or V tile are issued by 16 lanes at once), warp 1 = MMA issue
-// (one thread), warps 2-5 = softmax + epilogue. The MMA thread issues Q K^T of tile j+1 before P V of tile j, so the tensor
+// (one thread), warps 2-9 = softmax + epilogue (two warps per scheduler, so one warp's latencies hide behind the other's work; each
+// thread accumulates half of its row's output columns). The MMA thread issues Q K^T of tile j+1 before P V of tile j, so the tensor
 // pipe works on the next scores while the softmax warps are busy.
 // Every wait is bounded; on expiry the CTA raises the status word and tears down (see common.cuh).
 //
@@ -27,7 +28,8 @@ constexpr int HD = 128;   // head size
 constexpr int kHalf = TK * 128;          // bytes of one 64-column half of a 128-row operand tile (rows of 128 bytes)
 constexpr int kTile = 2 * kHalf;         // 32 KB: Q, or one K tile, or one V tile
 constexpr int kStages = 2;
-constexpr int kSmem = kTile + kStages * 2 * kTile + 1024;  // Q + K/V ring + barriers
+constexpr int kSmem = kTile + kStages * 2 * kTile + 1024 + 2 * 2 * TQ * 4;  // Q + K/V ring + barriers + row-maximum exchange
+constexpr int kThreads = 320;
 // TMEM columns: S0 | S1 | O_tile | P0 | P1
 constexpr uint32_t kColS = 0, kColO = 256, kColP = 384;
 
@@ -49,7 +51,7 @@ __device__ __forceinline__ uint64_t umma_desc_sw128_mn(uint32_t smem_addr, uint3
   return d;
 }
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV, const AttnParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -68,6 +70,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_free + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* s_req = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+  float* s_xch = reinterpret_cast<float*>(smem + kTile + kStages * 2 * kTile + 1024);  // [2 tile parities][2 halves][TQ]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.y;
@@ -94,10 +97,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&s_full[i], 1);
-      mbar_init(&p_ready[i], 4);
+      mbar_init(&p_ready[i], 8);
     }
     mbar_init(o_full, 1);
-    mbar_init(o_free, 4);
+    mbar_init(o_free, 8);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmQ);
@@ -207,68 +210,75 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       }
     }
   } else {
-    // ------------------------------------------------------------------ softmax + epilogue: one thread per query row
-    const int q4 = warp & 3;
+    // ------------------------------------------------------------------ softmax + epilogue: two threads per query row
+    const int q4 = warp & 3;                 // TMEM lane quarter this warp may touch
+    const int half = (warp - 2) >> 2;        // which 64 keys of a tile / which 64 output columns this thread owns
     const int row = q4 * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(q4 * 32) << 16);
     const float sl2 = p.scale * 1.4426950408889634f;
     const int tq = tq0 + row;                       // query token inside the request
     const int limit = min(S, ctx0 + tq + 1);        // keys [0, limit) are visible to this row
-    float o[HD];
+    constexpr int HC = HD / 2, KC = TK / 2;
+    float o[HC];
 #pragma unroll
-    for (int i = 0; i < HD; ++i) o[i] = 0.f;
+    for (int i = 0; i < HC; ++i) o[i] = 0.f;
     float m = -INFINITY, l = 0.f;
     float alpha[2] = {1.f, 1.f};
     bool ok = ntiles > 0;
+    // the two warps that share a lane quarter meet on a named barrier of 64 threads
+    auto pair_sync = [&]() { asm volatile("bar.sync %0, 64;" ::"r"(1 + q4) : "memory"); };
 
+    // Both warps of a pair call pair_sync exactly ntiles + 1 times whatever happens (a named barrier has no time-out): a warp whose
+    // bounded wait failed keeps walking the tiles without touching TMEM, and its partner learns of it through the abort flag.
     auto softmax_tile = [&](int j) {
-      ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag);
-      if (!ok) return;
+      if (ok) ok = mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag);
       tc_fence_after();
-      const uint32_t s_addr = lane_addr + kColS + (j & 1) * TK;
-      const int k0 = j * TK;
-      const bool masked = k0 + TK > limit;
-      // pass 1: row maximum
-      float mx = m, raw = -INFINITY;
+      const uint32_t s_addr = lane_addr + kColS + (j & 1) * TK + half * KC;
+      const int k0 = j * TK + half * KC;
+      const bool masked = k0 + KC > limit;
+      // pass 1: maximum of this thread's 64 scores, then of the row
+      float raw = -INFINITY;
+      if (ok) {
 #pragma unroll
-      for (int c = 0; c < TK; c += 32) {
+        for (int c = 0; c < KC; c += 32) {
+          uint32_t v[32];
+          tmem_ld_32x32(s_addr + c, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float x = __uint_as_float(v[i]);
+            if (masked && k0 + c + i >= limit) x = -INFINITY;
+            raw = fmaxf(raw, x);
+          }
+        }
+      }
+      float* xch = s_xch + (j & 1) * 2 * TQ;
+      xch[half * TQ + row] = raw;
+      pair_sync();
+      if (!ok || *abort_flag) { ok = false; return; }
+      const float mx = fmaxf(m, fmaxf(raw, xch[(half ^ 1) * TQ + row]) * sl2);
+      const float m_use = (mx == -INFINITY) ? 0.f : mx;  // a row that sees no key yet keeps zeros
+      alpha[j & 1] = (m == -INFINITY) ? 0.f : ex2(m - m_use);
+      m = mx;
+      // pass 2: probabilities -> bf16 pairs in TMEM, partial row sum
+      float sum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int c = 0; c < KC; c += 32) {
         uint32_t v[32];
         tmem_ld_32x32(s_addr + c, v);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float x = __uint_as_float(v[i]);
-          if (masked && k0 + c + i >= limit) x = -INFINITY;
-          raw = fmaxf(raw, x);
+        for (int i = 0; i < 32; i += 2) {
+          float x0 = __uint_as_float(v[i]) * sl2 - m_use, x1 = __uint_as_float(v[i + 1]) * sl2 - m_use;
+          if (masked && k0 + c + i >= limit) x0 = -INFINITY;
+          if (masked && k0 + c + i + 1 >= limit) x1 = -INFINITY;
+          __nv_bfloat162 b = __floats2bfloat162_rn(ex2(x0), ex2(x1));
+          sum += __low2float(b) + __high2float(b);   // the sum of what the tensor core will actually multiply
+          pk[(c + i) >> 1] = *reinterpret_cast<uint32_t*>(&b);
         }
       }
-      mx = fmaxf(mx, raw * sl2);
-      const float m_use = (mx == -INFINITY) ? 0.f : mx;  // a row that sees no key yet keeps zeros
-      alpha[j & 1] = (m == -INFINITY) ? 0.f : ex2(m - m_use);
-      m = mx;
-      // pass 2: probabilities -> bf16 pairs in TMEM, row sum
-      float sum = 0.f;
-      const uint32_t p_addr = lane_addr + kColP + (j & 1) * (TK / 2);
-#pragma unroll
-      for (int c = 0; c < TK; c += 64) {
-        uint32_t pk[32];
-#pragma unroll
-        for (int c2 = 0; c2 < 64; c2 += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(s_addr + c + c2, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            float x0 = __uint_as_float(v[i]) * sl2 - m_use, x1 = __uint_as_float(v[i + 1]) * sl2 - m_use;
-            if (masked && k0 + c + c2 + i >= limit) x0 = -INFINITY;
-            if (masked && k0 + c + c2 + i + 1 >= limit) x1 = -INFINITY;
-            __nv_bfloat162 b = __floats2bfloat162_rn(ex2(x0), ex2(x1));
-            sum += __low2float(b) + __high2float(b);   // the sum of what the tensor core will actually multiply
-            pk[(c2 + i) >> 1] = *reinterpret_cast<uint32_t*>(&b);
-          }
-        }
-        tmem_st_32x32(p_addr + (c >> 1), pk);
-      }
+      tmem_st_32x32(lane_addr + kColP + (j & 1) * (TK / 2) + half * (KC / 2), pk);
       l = l * alpha[j & 1] + sum;
       tmem_st_wait();
       tc_fence_before();
@@ -276,18 +286,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       if (lane == 0) mbar_arrive(&p_ready[j & 1]);
     };
 
-    if (ok) softmax_tile(0);
-    for (int j = 0; j < ntiles && ok; ++j) {
+    if (ntiles > 0) softmax_tile(0);
+    for (int j = 0; j < ntiles; ++j) {
       if (j + 1 < ntiles) softmax_tile(j + 1);
-      if (!ok) break;
-      ok = mbar_wait(o_full, j & 1, abort_flag);
-      if (!ok) break;
+      if (ok) ok = mbar_wait(o_full, j & 1, abort_flag);
+      if (!ok) continue;
       tc_fence_after();
       const float a = alpha[j & 1];
 #pragma unroll
-      for (int c = 0; c < HD; c += 32) {
+      for (int c = 0; c < HC; c += 32) {
         uint32_t v[32];
-        tmem_ld_32x32(lane_addr + kColO + c, v);
+        tmem_ld_32x32(lane_addr + kColO + half * HC + c, v);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 32; ++i) o[c + i] = o[c + i] * a + __uint_as_float(v[i]);
@@ -296,18 +305,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
       __syncwarp();
       if (lane == 0) mbar_arrive(o_free);
     }
-    if (ok && tq < qlen) {
+    // the row sum is the sum of the two halves' partial sums (both were scaled by the same alphas)
+    float* xch = s_xch + (ntiles & 1) * 2 * TQ;
+    if (ntiles > 0) {
+      xch[half * TQ + row] = l;
+      pair_sync();
+      l += xch[(half ^ 1) * TQ + row];
+    }
+    if (ok && !*abort_flag && tq < qlen) {
       const float inv = l > 0.f ? 1.f / l : 0.f;
       const size_t orow = (size_t)(qs + tq) * p.Hq + h;
-      uint4* dst = reinterpret_cast<uint4*>(p.out + orow * HD);
+      uint4* dst = reinterpret_cast<uint4*>(p.out + orow * HD + half * HC);
 #pragma unroll
-      for (int i = 0; i < HD; i += 8) {
+      for (int i = 0; i < HC; i += 8) {
         __nv_bfloat162 b0 = __floats2bfloat162_rn(o[i] * inv, o[i + 1] * inv), b1 = __floats2bfloat162_rn(o[i + 2] * inv, o[i + 3] * inv);
         __nv_bfloat162 b2 = __floats2bfloat162_rn(o[i + 4] * inv, o[i + 5] * inv), b3 = __floats2bfloat162_rn(o[i + 6] * inv, o[i + 7] * inv);
         dst[i >> 3] = make_uint4(*reinterpret_cast<uint32_t*>(&b0), *reinterpret_cast<uint32_t*>(&b1), *reinterpret_cast<uint32_t*>(&b2),
                                  *reinterpret_cast<uint32_t*>(&b3));
       }
-      if (p.lse != nullptr) p.lse[orow] = (m + log2f(l)) * 0.6931471805599453f;
+      if (p.lse != nullptr && half == 0) p.lse[orow] = (m + log2f(l)) * 0.6931471805599453f;
     }
   }
 
@@ -371,7 +387,7 @@ int attention_prefill_tc_launch(const AttnParams& p, long long num_blocks, cudaS
     configured = true;
   }
   dim3 grid(p.num_q_tiles, p.Hq);
-  attn_prefill_tc_kernel<<<grid, 192, kSmem + 1024, st>>>(tmQ, tmKV, p);
+  attn_prefill_tc_kernel<<<grid, kThreads, kSmem + 1024, st>>>(tmQ, tmKV, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }
 

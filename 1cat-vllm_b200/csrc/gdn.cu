@@ -74,11 +74,27 @@ __global__ void gdn_conv_state_kernel(const GdnConvParams p) {
 
 constexpr int GK = 128, GV = 128;
 
-__global__ void __launch_bounds__(GV) gdn_recurrent_kernel(const GdnParams p) {
-  __shared__ float sq[GK], sk[GK];
-  __shared__ float red[2][4];
-  const int r = blockIdx.x, hv = blockIdx.y;
-  const int j = threadIdx.x;
+constexpr int CH = 16;      // tokens whose inputs are staged together (their global loads are in flight at the same time)
+constexpr int VC = 32;      // state columns per CTA
+constexpr int NP = 4;       // lanes per state column
+constexpr int GT = NP * VC; // threads per CTA
+constexpr int HK = GK / NP; // state rows per thread
+
+// One CTA per (sequence, value head, group of 32 state columns). The K x V fp32 state lives in registers: a warp owns 8 columns and
+// a column is split over four of its lanes (lane = column + 8 * part, part p holds rows 32p .. 32p + 31), so a thread keeps 32 state
+// values and the 32 key values of the current token, and partial dot products meet through two shuffles. Tokens are strictly
+// sequential, so a warp is latency-bound per token (measured: 0.4 instructions per cycle); 16 warps per head put enough warps on
+// every scheduler even for a single long sequence. The q/k/v rows of CH tokens are copied asynchronously into shared memory while
+// the previous chunk is processed, and the dot products run on four independent accumulators.
+__global__ void __launch_bounds__(GT) gdn_recurrent_kernel(const GdnParams p) {
+  __shared__ __align__(16) float sq[CH][GK], sk[CH][GK];
+  __shared__ float sv[CH][VC];
+  __shared__ float sdecay[CH], sbeta[CH];
+  __shared__ __align__(16) __nv_bfloat16 raw[CH][2][GK];  // the next chunk's q and k rows as they are in global memory
+  __shared__ __align__(16) __nv_bfloat16 rawv[CH][VC];    // and this CTA's slice of the v rows
+  const int r = blockIdx.x, hv = blockIdx.y, c0 = blockIdx.z * VC;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int lc = warp * 8 + (lane & 7), col = c0 + lc, half = lane >> 3;  // `half` = which quarter of the rows
   const int t0 = p.query_start_loc[r], t1 = p.query_start_loc[r + 1];
   if (t1 <= t0) return;
   const int hk = hv / (p.Hv / p.Hk);
@@ -86,60 +102,116 @@ __global__ void __launch_bounds__(GV) gdn_recurrent_kernel(const GdnParams p) {
   // prefill chunk sharing the step with verification requests, update their slot directly
   const bool rec = p.spec_state != nullptr && (t1 - t0) <= p.spec_q;
   const int slot = p.state_slots[r];
-  float* Sg = p.state + ((size_t)slot * p.Hv + hv) * GK * GV;
-  float S[GK];
+  float* Sg = p.state + ((size_t)slot * p.Hv + hv) * GK * GV + (size_t)half * HK * GV + col;
+  float S[HK];
   if (p.has_initial_state[r]) {
 #pragma unroll
-    for (int k = 0; k < GK; ++k) S[k] = Sg[(size_t)k * GV + j];
+    for (int k = 0; k < HK; ++k) S[k] = Sg[(size_t)k * GV];
   } else {
 #pragma unroll
-    for (int k = 0; k < GK; ++k) S[k] = 0.f;
+    for (int k = 0; k < HK; ++k) S[k] = 0.f;
   }
   const float neg_a = -__expf(p.A_log[hv]);
   const float dtb = p.dt_bias[hv];
   const float scale = rsqrtf((float)GK);
-  for (int t = t0; t < t1; ++t) {
-    // q, k of the key head: L2-normalise (block reduction over K = blockDim)
-    const float qv = __bfloat162float(p.q[(size_t)t * p.ld_qkv + hk * GK + j]);
-    const float kv = __bfloat162float(p.k[(size_t)t * p.ld_qkv + hk * GK + j]);
-    float q2 = warp_sum(qv * qv), k2 = warp_sum(kv * kv);
-    __syncthreads();  // previous iteration is done with sq/sk/red
-    if ((j & 31) == 0) { red[0][j >> 5] = q2; red[1][j >> 5] = k2; }
-    __syncthreads();
-    q2 = red[0][0] + red[0][1] + red[0][2] + red[0][3];
-    k2 = red[1][0] + red[1][1] + red[1][2] + red[1][3];
-    sq[j] = qv * rsqrtf(q2 + 1e-6f) * scale;
-    sk[j] = kv * rsqrtf(k2 + 1e-6f);
-    __syncthreads();
-    const float av = __bfloat162float(p.a[(size_t)t * p.ld_ba + hv]) + dtb;
-    const float sp = av > 20.f ? av : log1pf(__expf(av));
-    const float decay = __expf(neg_a * sp);
-    const float bv = __bfloat162float(p.b[(size_t)t * p.ld_ba + hv]);
-    const float beta = 1.f / (1.f + __expf(-bv));
-    const float vj = __bfloat162float(p.v[(size_t)t * p.ld_qkv + hv * GV + j]);
-    float proj = 0.f;
-#pragma unroll
-    for (int k = 0; k < GK; ++k) {
-      S[k] *= decay;
-      proj += sk[k] * S[k];
+
+  float ra = 0.f, rb = 0.f;
+  // asynchronous 16-byte copies of a chunk's rows: warp w copies tokens w, w + 4, ...; per token the 32 lanes copy the 16 + 16
+  // segments of the q and k rows (256 bytes each) and lanes 0-3 this CTA's 64-byte slice of the v row
+  auto fetch = [&](int tc) {
+    const int n = min(CH, t1 - tc);
+    for (int i = warp; i < n; i += GT / 32) {
+      const size_t row = (size_t)(tc + i) * p.ld_qkv;
+      const int which = lane >> 4, seg = lane & 15;
+      const __nv_bfloat16* src = (which == 0 ? p.q : p.k) + row + hk * GK + seg * 8;
+      uint32_t dst = (uint32_t)__cvta_generic_to_shared(&raw[i][which][seg * 8]);
+      asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      if (lane < VC / 8) {
+        src = p.v + row + hv * GV + c0 + lane * 8;
+        dst = (uint32_t)__cvta_generic_to_shared(&rawv[i][lane * 8]);
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+      }
     }
-    const float d = (vj - proj) * beta;
-    float o = 0.f;
-#pragma unroll
-    for (int k = 0; k < GK; ++k) {
-      S[k] += sk[k] * d;
-      o += sq[k] * S[k];
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    if (tid < n) {
+      ra = __bfloat162float(p.a[(size_t)(tc + tid) * p.ld_ba + hv]);
+      rb = __bfloat162float(p.b[(size_t)(tc + tid) * p.ld_ba + hv]);
     }
-    p.out[(size_t)t * p.Hv * GV + hv * GV + j] = __float2bfloat16(o);
-    if (rec) {
-      float* dst = p.spec_state + (((size_t)r * p.spec_q + (t - t0)) * p.Hv + hv) * GK * GV;
+  };
+  fetch(t0);
+  for (int tc = t0; tc < t1; tc += CH) {
+    const int n = min(CH, t1 - tc);
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();  // the chunk has landed, and the previous chunk's recurrence is done with the float arrays
+    if (tid < n) {
+      const float av = ra + dtb;
+      const float sp = av > 20.f ? av : log1pf(__expf(av));
+      sdecay[tid] = __expf(neg_a * sp);
+      sbeta[tid] = 1.f / (1.f + __expf(-rb));
+    }
+    // convert and L2-normalise q and k of every token of the chunk (warp w takes tokens w, w + 4, ...), convert the v slice
+#pragma unroll 1
+    for (int i = warp; i < n; i += GT / 32) {
+      float q4[4], k4[4], q2 = 0.f, k2 = 0.f;
 #pragma unroll
-      for (int k = 0; k < GK; ++k) dst[(size_t)k * GV + j] = S[k];
+      for (int e = 0; e < 4; ++e) {
+        q4[e] = __bfloat162float(raw[i][0][lane + 32 * e]);
+        k4[e] = __bfloat162float(raw[i][1][lane + 32 * e]);
+        q2 += q4[e] * q4[e];
+        k2 += k4[e] * k4[e];
+      }
+      sv[i][lane] = __bfloat162float(rawv[i][lane]);
+      q2 = warp_sum(q2);
+      k2 = warp_sum(k2);
+      const float qs = rsqrtf(q2 + 1e-6f) * scale, ks = rsqrtf(k2 + 1e-6f);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        sq[i][lane + 32 * e] = q4[e] * qs;
+        sk[i][lane + 32 * e] = k4[e] * ks;
+      }
+    }
+    __syncthreads();  // the raw rows have been consumed, the float arrays are complete
+    if (tc + CH < t1) fetch(tc + CH);  // in flight while this chunk is processed
+#pragma unroll 1
+    for (int i = 0; i < n; ++i) {
+      const float decay = sdecay[i], beta = sbeta[i], vj = sv[i][lc];
+      const float4* k4p = reinterpret_cast<const float4*>(&sk[i][half * HK]);
+      const float4* q4p = reinterpret_cast<const float4*>(&sq[i][half * HK]);
+      float kr[HK];
+      float pj[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < HK; k += 4) {
+        const float4 kk = k4p[k >> 2];
+        kr[k] = kk.x; kr[k + 1] = kk.y; kr[k + 2] = kk.z; kr[k + 3] = kk.w;
+        S[k] *= decay; S[k + 1] *= decay; S[k + 2] *= decay; S[k + 3] *= decay;
+        pj[0] += kk.x * S[k]; pj[1] += kk.y * S[k + 1]; pj[2] += kk.z * S[k + 2]; pj[3] += kk.w * S[k + 3];
+      }
+      float proj = (pj[0] + pj[1]) + (pj[2] + pj[3]);
+      proj += __shfl_xor_sync(0xffffffffu, proj, 8);
+      proj += __shfl_xor_sync(0xffffffffu, proj, 16);
+      const float d = (vj - proj) * beta;
+      float oj[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int k = 0; k < HK; k += 4) {
+        const float4 qq = q4p[k >> 2];
+        S[k] += kr[k] * d; S[k + 1] += kr[k + 1] * d; S[k + 2] += kr[k + 2] * d; S[k + 3] += kr[k + 3] * d;
+        oj[0] += qq.x * S[k]; oj[1] += qq.y * S[k + 1]; oj[2] += qq.z * S[k + 2]; oj[3] += qq.w * S[k + 3];
+      }
+      float o = (oj[0] + oj[1]) + (oj[2] + oj[3]);
+      o += __shfl_xor_sync(0xffffffffu, o, 8);
+      o += __shfl_xor_sync(0xffffffffu, o, 16);
+      const int t = tc + i;
+      if (half == 0) p.out[(size_t)t * p.Hv * GV + hv * GV + col] = __float2bfloat16(o);
+      if (rec) {
+        float* dst = p.spec_state + (((size_t)r * p.spec_q + (t - t0)) * p.Hv + hv) * GK * GV + (size_t)half * HK * GV + col;
+#pragma unroll
+        for (int k = 0; k < HK; ++k) dst[(size_t)k * GV] = S[k];
+      }
     }
   }
   if (p.write_state || !rec) {
 #pragma unroll
-    for (int k = 0; k < GK; ++k) Sg[(size_t)k * GV + j] = S[k];
+    for (int k = 0; k < HK; ++k) Sg[(size_t)k * GV] = S[k];
   }
 }
 
@@ -165,8 +237,8 @@ int gdn_conv_commit_launch(const GdnConvParams& p, cudaStream_t st) {
 int gdn_recurrent_launch(const GdnParams& p, cudaStream_t st) {
   if (p.R == 0) return 0;
   if (p.K != GK || p.V != GV || p.Hv % p.Hk) return -1;
-  dim3 grid(p.R, p.Hv);
-  gdn_recurrent_kernel<<<grid, GV, 0, st>>>(p);
+  dim3 grid(p.R, p.Hv, GV / VC);
+  gdn_recurrent_kernel<<<grid, GT, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

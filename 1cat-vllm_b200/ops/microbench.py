@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|moe] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -133,12 +133,15 @@ def bench_norm(rows: list, small: bool, iters: int, pk: dict) -> None:
         rows.append(dict(kernel="rms_norm_residual", T=T, H=H, ms=ms, gbs=b / ms / 1e6, frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"]))
 
 
-def bench_gdn(rows: list, small: bool, iters: int, pk: dict) -> None:
+def bench_gdn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool = False) -> None:
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.worker.attn_metadata import AttentionMetadata
     Hk, Hv, Kd, Vd, kw = 16, 48, 128, 128, 4
     C = 2 * Hk * Kd + Hv * Vd
-    for name, R, ql in ([("decode", 64, 1)] if small else [("decode", 64, 1), ("decode", 8, 1), ("verify4", 8, 4), ("prefill", 4, 2048)]):
+    cases = [("decode", 64, 1)] if small else [("decode", 64, 1), ("decode", 8, 1), ("verify4", 8, 4), ("prefill", 4, 2048), ("prefill", 1, 8192)]
+    if prefill_only:
+        cases = [("prefill", 1, 2048)]
+    for name, R, ql in cases:
         T = R * ql
         mixed = (torch.randn(T, C, device="cuda") * 0.5).bfloat16()
         ba = torch.randn(T, 2 * Hv, device="cuda").bfloat16()
@@ -233,8 +236,9 @@ def main() -> None:
     pk = _peaks()
     rows: list = []
     for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq),
-                     ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True))):
-        if not a.only and name == "attn_prefill":
+                     ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True)),
+                     ("gdn_prefill", lambda r, s_, i, p_: bench_gdn(r, s_, i, p_, prefill_only=True))):
+        if not a.only and name in ("attn_prefill", "gdn_prefill"):
             continue
         if a.only and a.only != name:
             continue

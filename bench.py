@@ -115,7 +115,13 @@ def _kv_bytes(cfg: dict, C: int, seq: int, gpus: int) -> int:
         attn_layers = L // cfg["full_attention_interval"] if cfg.get("full_attention_interval") else L
         kvh = max(cfg["num_key_value_heads"] // gpus, 1)
         per_tok = attn_layers * 2 * kvh * cfg["head_dim"] * 2
-    return int((C + 2) * seq * per_tok)
+    state = 0
+    if cfg.get("full_attention_interval"):  # Gated-DeltaNet layers keep a recurrent state and a conv window per sequence
+        hv, hk = cfg["linear_num_value_heads"] // gpus, cfg["linear_num_key_heads"] // gpus
+        k, v = cfg["linear_key_head_dim"], cfg["linear_value_head_dim"]
+        per_seq = hv * k * v * 4 + (2 * hk * k + hv * v) * (cfg["linear_conv_kernel_dim"] - 1) * 2
+        state = (L - L // cfg["full_attention_interval"]) * per_seq * (C + 2)
+    return int((C + 2) * seq * per_tok * 1.02 + state * 1.05)
 
 
 def main() -> None:

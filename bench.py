@@ -205,7 +205,11 @@ def main() -> None:
         return new, (st.step_device_ms if st is not None else 0.0), (st.num_scheduled_tokens if st else 0), outs
 
     # untimed: initial prefill of the staggered population, then W warm-up steps
-    while any(r.num_computed_tokens < r.num_prompt_tokens for r in eng.engine_core.core.scheduler.requests.values()):
+    initial = {f"r{i}" for i in range(C)}
+    reqs = eng.engine_core.core.scheduler.requests
+    for _ in range(100000):  # bounded: the closed loop keeps adding requests, only the initial population has to be prefilled
+        if not any(rid in reqs and reqs[rid].num_computed_tokens < reqs[rid].num_prompt_tokens for rid in initial):
+            break
         one_step()
     for _ in range(args.warmup):
         one_step()

@@ -77,6 +77,7 @@ class _ReqState:
     metrics: RequestMetrics = field(default_factory=RequestMetrics)
     queue: Optional[object] = None  # asyncio queue for streaming clients
     pooling: bool = False
+    prompt_logprobs: Optional[list] = None
 
 
 class OutputProcessor:
@@ -95,6 +96,8 @@ class OutputProcessor:
         st.pooling = req.pooling_params is not None
         if sp.logprobs is not None:
             st.logprobs = []
+        if sp.prompt_logprobs is not None:
+            st.prompt_logprobs = [None]  # the first prompt token has no predecessor
         self.states[req.request_id] = st
         if parent_id is not None:
             self.parents.setdefault(parent_id, {"n": sp.n, "done": {}, "prompt": prompt, "prompt_ids": req.prompt_token_ids})
@@ -130,6 +133,13 @@ class OutputProcessor:
             if stop_str is not None and finish is None:
                 finish, stop_reason = FinishReason.STOP, stop_str
                 to_abort.append(o.request_id)
+            if st.prompt_logprobs is not None and o.prompt_logprobs:
+                for ids, lps, rank in o.prompt_logprobs:
+                    d = {}
+                    for j, (tid, lp) in enumerate(zip(ids, lps)):
+                        if tid not in d:
+                            d[tid] = Logprob(lp, rank if j == 0 else j, self.tok.decode([tid]) if self.tok is not None else None)
+                    st.prompt_logprobs.append(d)
             if st.logprobs is not None and o.new_logprobs:
                 for ids, lps, rank in o.new_logprobs:
                     d = {}
@@ -169,7 +179,8 @@ class OutputProcessor:
         co = CompletionOutput(st.index, d_text, d_ids, st.cum_logprob if st.logprobs is not None else None, lps,
                               str(finish) if finished else None, stop_reason)
         if st.parent_id is None:
-            return RequestOutput(st.request_id, st.prompt, st.prompt_ids, [co], finished, metrics=st.metrics, num_cached_tokens=num_cached)
+            return RequestOutput(st.request_id, st.prompt, st.prompt_ids, [co], finished, metrics=st.metrics, num_cached_tokens=num_cached,
+                                 prompt_logprobs=st.prompt_logprobs)
         # n > 1: gather children under the parent id
         par = self.parents[st.parent_id]
         if finished:

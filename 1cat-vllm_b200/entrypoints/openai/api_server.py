@@ -3,7 +3,8 @@ chat logic openai/chat_completion/serving.py; launcher + watchdog entrypoints/la
 
 Routes: ``/v1/chat/completions``, ``/v1/completions``, ``/v1/models``, ``/tokenize``, ``/detokenize``, ``/health``, ``/ping``,
 ``/version``, ``/metrics`` (Prometheus), ``/load``, ``/server_info``, ``/reset_prefix_cache``, ``/sleep``, ``/wake_up``,
-``/is_sleeping``, ``/start_profile``, ``/stop_profile``, ``/collective_rpc``, ``/v1/embeddings``, ``/pooling``, ``/score``.
+``/is_sleeping``, ``/start_profile``, ``/stop_profile``, ``/collective_rpc``, ``/v1/embeddings``, ``/pooling``, ``/score``,
+``/v1/responses``, ``/v1/messages`` (Anthropic), ``/v1/load_lora_adapter``, ``/v1/unload_lora_adapter``.
 Streaming uses server-sent events."""
 from __future__ import annotations
 
@@ -271,6 +272,97 @@ def build_app(state: ServingState) -> FastAPI:
         data = [{"index": i, "object": "score", "score": sum(x * y for x, y in zip(p.outputs.data, q.outputs.data))}
                 for i, (p, q) in enumerate(zip(ea, eb))]
         return {"id": new_id("score"), "object": "list", "created": now(), "model": state.model_name, "data": data}
+
+    # ---- Responses API and Anthropic Messages API: both are rewritten into a chat completion request and its result is
+    # re-shaped (reference: entrypoints/openai/responses/serving.py; entrypoints/anthropic/serving_messages.py)
+    def _as_chat(messages: list, body: dict, max_key: str) -> ChatCompletionRequest:
+        keep = {k: body[k] for k in ("temperature", "top_p", "top_k", "seed", "stop", "model", "tools", "tool_choice") if body.get(k) is not None}
+        if body.get("stop_sequences"):
+            keep["stop"] = body["stop_sequences"]
+        return ChatCompletionRequest(messages=messages, max_tokens=body.get(max_key), **keep)
+
+    async def _run_chat(creq: ChatCompletionRequest, raw: Request):
+        res = await chat(creq, raw)
+        if isinstance(res, JSONResponse):
+            return None, res
+        return res, None
+
+    def _text_of(content) -> str:
+        if isinstance(content, str):
+            return content
+        return "".join(p.get("text", "") for p in content if isinstance(p, dict) and p.get("type") in ("text", "input_text", "output_text"))
+
+    @app.post("/v1/responses")
+    async def responses(body: dict, raw: Request):
+        if body.get("stream"):
+            return JSONResponse(error_body("streaming responses are not supported; use /v1/chat/completions with stream"), status_code=400)
+        msgs = []
+        if body.get("instructions"):
+            msgs.append({"role": "system", "content": body["instructions"]})
+        inp = body.get("input", "")
+        if isinstance(inp, str):
+            msgs.append({"role": "user", "content": inp})
+        else:
+            for it in inp:
+                if it.get("type", "message") == "message":
+                    msgs.append({"role": it.get("role", "user"), "content": _text_of(it.get("content", ""))})
+        try:
+            creq = _as_chat(msgs, body, "max_output_tokens")
+        except Exception as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        res, err = await _run_chat(creq, raw)
+        if err is not None:
+            return err
+        ch = res["choices"][0]
+        out = []
+        if ch["message"].get("reasoning_content"):
+            out.append({"type": "reasoning", "id": new_id("rs"), "summary": [], "content": [{"type": "reasoning_text", "text": ch["message"]["reasoning_content"]}]})
+        for tc in ch["message"].get("tool_calls") or []:
+            out.append({"type": "function_call", "id": new_id("fc"), "call_id": tc["id"], "name": tc["function"]["name"],
+                        "arguments": tc["function"]["arguments"], "status": "completed"})
+        if ch["message"].get("content"):
+            out.append({"type": "message", "id": new_id("msg"), "role": "assistant", "status": "completed",
+                        "content": [{"type": "output_text", "text": ch["message"]["content"], "annotations": []}]})
+        u = res["usage"]
+        return {"id": new_id("resp"), "object": "response", "created_at": now(), "model": res["model"], "status": "completed",
+                "incomplete_details": {"reason": "max_output_tokens"} if ch["finish_reason"] == "length" else None, "output": out,
+                "output_text": ch["message"].get("content") or "",
+                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"]}}
+
+    @app.post("/v1/messages")
+    async def anthropic_messages(body: dict, raw: Request):
+        if body.get("stream"):
+            return JSONResponse(error_body("streaming messages are not supported; use /v1/chat/completions with stream"), status_code=400)
+        msgs = []
+        if body.get("system"):
+            msgs.append({"role": "system", "content": _text_of(body["system"])})
+        for m in body.get("messages", []):
+            msgs.append({"role": m["role"], "content": _text_of(m.get("content", ""))})
+        tools = [{"type": "function", "function": {"name": t["name"], "description": t.get("description", ""), "parameters": t.get("input_schema", {})}}
+                 for t in body.get("tools") or []]
+        b2 = dict(body)
+        b2["tools"] = tools or None
+        b2.pop("tool_choice", None)
+        try:
+            creq = _as_chat(msgs, b2, "max_tokens")
+        except Exception as e:
+            return JSONResponse({"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}}, status_code=400)
+        res, err = await _run_chat(creq, raw)
+        if err is not None:
+            return err
+        ch = res["choices"][0]
+        content = []
+        if ch["message"].get("content"):
+            content.append({"type": "text", "text": ch["message"]["content"]})
+        for tc in ch["message"].get("tool_calls") or []:
+            content.append({"type": "tool_use", "id": tc["id"], "name": tc["function"]["name"], "input": json.loads(tc["function"]["arguments"] or "{}")})
+        stop = {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(ch["finish_reason"], "end_turn")
+        if ch.get("stop_reason") is not None and isinstance(ch["stop_reason"], str):
+            stop = "stop_sequence"
+        u = res["usage"]
+        return {"id": new_id("msg"), "type": "message", "role": "assistant", "model": res["model"], "content": content, "stop_reason": stop,
+                "stop_sequence": ch.get("stop_reason") if stop == "stop_sequence" else None,
+                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"]}}
 
     # ---- completions
     @app.post("/v1/completions")

@@ -476,9 +476,9 @@ class ModelRunner:
                 sampled_lists = self._verify(logits, smd, rows, drafts_of)
                 if timed:
                     ev1.record()
-            out.prompt_logprobs = None
         elif timed:
             ev1.record()
+        out.prompt_logprobs = self._prompt_logprobs(hidden, req_ids, query_lens)
         if any(self.requests[r].pooling_params is not None for r in req_ids):
             out.pooler_output = self._pool(hidden, req_ids, query_lens, rows)
         if gdn_spec:
@@ -500,6 +500,32 @@ class ModelRunner:
             from onecat_vllm.ops import cuda as K
             out.status = K.check_status()
         return out
+
+    def _prompt_logprobs(self, hidden: torch.Tensor, req_ids: list, query_lens: list[int]):
+        """Log-probabilities of the prompt tokens that this step's chunk predicts, for requests that asked for them: per request a
+        list of (token ids, logprobs, rank) with the actual next prompt token first and then the top-k (reference:
+        v1/worker/gpu_model_runner.py ``_get_prompt_logprobs_dict``). Rows are scored in slices to bound the logits buffer."""
+        res, o = None, 0
+        for rid, q in zip(req_ids, query_lens):
+            st = self.requests[rid]
+            sp = st.sampling_params
+            k = sp.prompt_logprobs if sp is not None else None
+            c0 = st.num_computed_tokens
+            if k is not None and c0 < st.num_prompt_tokens - 1:
+                n = min(c0 + q, st.num_prompt_tokens - 1) - c0  # rows whose next token is still a prompt token
+                tgt = torch.tensor(st.token_ids[c0 + 1:c0 + 1 + n], dtype=torch.long, device=self.device)
+                ids, lps, ranks = [], [], []
+                for a in range(0, n, 512):
+                    b = min(a + 512, n)
+                    lp = torch.log_softmax(self.model.compute_logits(hidden[o + a:o + b]).float(), dim=-1)
+                    i_, v_, r_ = Sampler.gather_logprobs(lp, k, tgt[a:b])
+                    ids += i_.tolist()
+                    lps += v_.tolist()
+                    ranks += r_.tolist()
+                res = res or {}
+                res[rid] = [(ids[j], lps[j], ranks[j]) for j in range(n)]
+            o += q
+        return res
 
     def _pool(self, hidden: torch.Tensor, req_ids: list, query_lens: list[int], rows: list[int]) -> list:
         """Pooled final-norm hidden state of embedding requests: last token, first token or mean over the prompt (accumulated

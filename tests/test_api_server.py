@@ -141,3 +141,17 @@ def test_more_tool_and_reasoning_parsers():
         dr, dc = rp.stream(text[: i - 1], text[:i])
         r, cc = r + dr, cc + dc
     assert (r, cc) == ("ab", "xy")
+
+
+@pytest.mark.timeout(300)
+def test_responses_and_anthropic_messages_routes(client):
+    r = client.post("/v1/responses", json={"input": "hello", "instructions": "be brief", "max_output_tokens": 6, "temperature": 0}).json()
+    assert r["object"] == "response" and r["status"] == "completed" and r["usage"]["output_tokens"] <= 6
+    assert isinstance(r["output_text"], str) and all(o["type"] in ("message", "reasoning", "function_call") for o in r["output"])
+    r2 = client.post("/v1/responses", json={"input": [{"role": "user", "content": [{"type": "input_text", "text": "hi"}]}], "max_output_tokens": 4}).json()
+    assert r2["usage"]["input_tokens"] > 0
+    m = client.post("/v1/messages", json={"model": "tiny", "max_tokens": 5, "system": "s", "temperature": 0,
+                                          "messages": [{"role": "user", "content": [{"type": "text", "text": "hello"}]}]}).json()
+    assert m["type"] == "message" and m["role"] == "assistant" and m["stop_reason"] in ("end_turn", "max_tokens", "stop_sequence", "tool_use")
+    assert m["usage"]["output_tokens"] <= 5
+    assert client.post("/v1/responses", json={"input": "x", "stream": True}).status_code == 400

@@ -121,3 +121,28 @@ def test_sampling_params_validation():
     sp = SamplingParams(temperature=0.0, top_k=5, top_p=0.5)
     assert sp.top_k == 0 and sp.top_p == 1.0  # greedy neutralises the random knobs
     assert SamplingParams.from_dict(sp.to_dict()).temperature == 0.0
+
+
+def test_prompt_logprobs_match_a_direct_forward_across_chunks():
+    """prompt_logprobs=k returns, for every prompt position after the first, the log-probability of the actual token plus the top k,
+    identical whether the prompt is prefilled in one chunk or several (reference test model: tests/v1/sample/test_logprobs.py)."""
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    prompt = [(7 * i) % 290 + 1 for i in range(45)]
+    got = {}
+    for chunk in (8192, 16):
+        llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, max_num_batched_tokens=chunk)
+        out = llm.generate([{"prompt_token_ids": prompt}], SamplingParams(temperature=0.0, max_tokens=2, prompt_logprobs=3, logprobs=1))[0]
+        plp = out.prompt_logprobs
+        assert plp[0] is None and len(plp) == len(prompt)
+        for pos in range(1, len(prompt)):
+            d = plp[pos]
+            assert prompt[pos] in d and 3 <= len(d) <= 4
+            assert all(v.logprob <= 0 for v in d.values())
+        got[chunk] = [plp[pos][prompt[pos]].logprob for pos in range(1, len(prompt))]
+        llm.shutdown()
+    assert max(abs(a - b) for a, b in zip(got[8192], got[16])) < 1e-4
+    # ranks: the actual token's rank is 1 exactly when it is the arg-max
+    assert any(v.rank == 1 for d in plp[1:] for v in d.values())

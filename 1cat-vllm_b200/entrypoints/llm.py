@@ -10,7 +10,7 @@ from onecat_vllm.engine.llm_engine import LLMEngine
 from onecat_vllm.inputs import PromptType
 from onecat_vllm.outputs import RequestOutput
 from onecat_vllm.outputs import PoolingRequestOutput
-from onecat_vllm.sampling_params import PoolingParams, RequestOutputKind, SamplingParams
+from onecat_vllm.sampling_params import BeamSearchParams, PoolingParams, RequestOutputKind, SamplingParams
 
 
 class LLM:
@@ -52,6 +52,45 @@ class LLM:
         convs = messages if messages and isinstance(messages[0], list) else [messages]
         prompts = [tok.apply_chat_template(c, tokenize=False, add_generation_prompt=add_generation_prompt) for c in convs]
         return self.generate(prompts, sampling_params)
+
+    def beam_search(self, prompts: Sequence[PromptType], params: BeamSearchParams) -> list[dict]:
+        """Beam search by repeated one-token steps with ``2 * beam_width`` log-probabilities per beam; the prefix cache makes every
+        step after the first a one-token decode per beam (reference: entrypoints/llm.py ``beam_search``, beam_search.py). Returns per
+        prompt ``{"sequences": [{"tokens", "cum_logprob", "text"} ...]}`` sorted best first (score = cum_logprob / len ** length_penalty)."""
+        from onecat_vllm.inputs import parse_prompt
+        tok = self.get_tokenizer()
+        eos = self.llm_engine.cfg.model_config.eos_token_id
+        if eos is None and tok is not None:
+            eos = getattr(tok, "eos_token_id", None)
+        W = params.beam_width
+        sp = SamplingParams(temperature=0.0, max_tokens=1, logprobs=2 * W, detokenize=False)
+        results = []
+        for prompt in prompts:
+            text, ids, _ = parse_prompt(prompt)
+            if ids is None:
+                ids = list(tok.encode(text))
+            n0 = len(ids)
+            beams = [(list(ids), 0.0)]
+            done: list = []
+            score = lambda toks, lp: lp / (max(len(toks) - n0, 1) ** params.length_penalty)
+            for _ in range(params.max_tokens):
+                if not beams:
+                    break
+                outs = self.generate([{"prompt_token_ids": b[0]} for b in beams], sp)
+                cand = []
+                for (toks, lp), o in zip(beams, outs):
+                    for tid, l in o.outputs[0].logprobs[0].items():
+                        if tid == eos and not params.ignore_eos:
+                            done.append((toks + [tid], lp + l.logprob))
+                        else:
+                            cand.append((toks + [tid], lp + l.logprob))
+                cand.sort(key=lambda c: -c[1])
+                beams = cand[:W]
+            done += beams
+            done.sort(key=lambda c: -score(*c))
+            results.append({"sequences": [{"tokens": t, "cum_logprob": lp, "text": tok.decode(t[n0:]) if tok is not None else None}
+                                          for t, lp in done[:W]]})
+        return results
 
     # ---- pooling tasks (reference: entrypoints/llm.py ``encode`` / ``embed`` / ``score``)
     def encode(self, prompts: Union[PromptType, Sequence[PromptType]], pooling_params: Optional[PoolingParams] = None,

@@ -157,6 +157,17 @@ class SamplingParams:
 
 
 @dataclass
+class BeamSearchParams:
+    """Parameters of ``LLM.beam_search`` (reference: vllm/sampling_params.py ``BeamSearchParams``)."""
+
+    beam_width: int
+    max_tokens: int
+    ignore_eos: bool = False
+    temperature: float = 0.0
+    length_penalty: float = 1.0
+
+
+@dataclass
 class PoolingParams:
     """Parameters of an embedding / classify request (reference: vllm/pooling_params.py)."""
 

@@ -163,3 +163,20 @@ def test_shared_storage_connector_hands_prefill_kv_to_another_engine(tmp_path):
     assert out.outputs[0].token_ids == want and first == want[:1]
     assert tier.restored == 100 // 16 and out.num_cached_tokens == 96 and tier.stored == 0
     decode.shutdown()
+
+
+def test_beam_search_finds_a_sequence_at_least_as_likely_as_greedy():
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.sampling_params import BeamSearchParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128)
+    prompt = {"prompt_token_ids": [5, 9, 200, 33, 7]}
+    greedy = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=5, logprobs=0, ignore_eos=True))[0].outputs[0]
+    res = llm.beam_search([prompt], BeamSearchParams(beam_width=3, max_tokens=5, ignore_eos=True))[0]["sequences"]
+    assert len(res) == 3 and all(len(s["tokens"]) == 10 for s in res)
+    assert res[0]["cum_logprob"] >= greedy.cumulative_logprob - 1e-4
+    assert res[0]["cum_logprob"] >= res[1]["cum_logprob"] >= res[2]["cum_logprob"]
+    one = llm.beam_search([prompt], BeamSearchParams(beam_width=1, max_tokens=5, ignore_eos=True))[0]["sequences"][0]
+    assert one["tokens"][5:] == greedy.token_ids
+    llm.shutdown()

@@ -59,12 +59,12 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
     p.w4 = (const uint8_t*)w4->data_ptr();
     p.w4_sz = (const uint32_t*)w4_sz->data_ptr();
     TORCH_CHECK(((uintptr_t)p.w4 & 15) == 0, "packed weights must be 16-byte aligned");
-    TORCH_CHECK(wkind >= 1 && wkind <= 3, "packed weights need wkind 1 (int4), 2 (fp8) or 3 (fp4)");
+    TORCH_CHECK(wkind >= 1 && wkind <= 4, "packed weights need wkind 1 (int4), 2 (fp8), 3 (mxfp4) or 4 (nvfp4)");
     p.wkind = (int)wkind;
     TORCH_CHECK(((uintptr_t)p.w4_sz & 15) == 0 && n_pad % 4 == 0, "scale table must be 16-byte aligned");
     TORCH_CHECK((size_t)w4->numel() * w4->element_size() >= (size_t)((n_rows + 127) / 128) * (p.K / 64) * (wkind == 2 ? 8192 : 4096),
                 "packed weights are too small");
-    TORCH_CHECK((size_t)w4_sz->numel() >= (size_t)((p.K / 64 + group_ktiles - 1) / group_ktiles) * n_pad, "scale table is too small");
+    TORCH_CHECK((size_t)w4_sz->numel() >= (size_t)((p.K / 64 + group_ktiles - 1) / group_ktiles) * n_pad * (wkind == 4 ? 2 : 1), "scale table is too small");
   } else {
     TORCH_CHECK(w.has_value(), "a weight is required");
     check_bf16(*w, "w");

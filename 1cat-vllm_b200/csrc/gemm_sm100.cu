@@ -2,7 +2,8 @@
 //
 // One persistent, warp-specialised kernel serves dense bf16 weights and weight-only quantised layers whose weights are
 // dequantised to bf16 on their way into the tensor core: 4-bit integer with group scales and zero points (AWQ/GPTQ, WKIND 1),
-// FP8 e4m3 with block scales (WKIND 2) and FP4 e2m1 with power-of-two scales per 32 k (MXFP4, WKIND 3):
+// FP8 e4m3 with block scales (WKIND 2), FP4 e2m1 with power-of-two scales per 32 k (MXFP4, WKIND 3) and FP4 e2m1 with e4m3 scales per
+// 16 k times a global scale (NVFP4, WKIND 4):
 //   * The weight tile (128 output features x 64 k) is UMMA operand A, so the 128 TMEM lanes are output features and
 //     the accumulator columns are tokens. The token tile TN (32..256) is UMMA N: decode batches and 8192-token
 //     prefill chunks run the same code, and a 4-bit weight tile is dequantised once per 128 x TN x 64 MMA block.
@@ -42,8 +43,10 @@ constexpr int kWStageBytes = BM * BK * 2;   // 16 KB
 // word per weight row: int4 -> bf16 scale | bf16 (128 + zero) << 16; fp8 -> bf16 (scale * 2^120); fp4 -> the bf16 scales
 // (* 2^126) of the tile's two 32-k groups
 __host__ __device__ constexpr int packed_bytes(int wkind) { return wkind == 2 ? BM * BK : BM * BK / 2; }
-constexpr int kSzBytes = BM * 4;
-__host__ __device__ constexpr int packed_slot(int wkind) { return packed_bytes(wkind) + kSzBytes; }
+// nvfp4 has four 16-k groups per k tile: two words per row (four bf16 scales, already multiplied by the global scale and 2^126)
+__host__ __device__ constexpr int sz_words(int wkind) { return wkind == 4 ? 2 : 1; }
+__host__ __device__ constexpr int sz_bytes(int wkind) { return BM * 4 * sz_words(wkind); }
+__host__ __device__ constexpr int packed_slot(int wkind) { return packed_bytes(wkind) + sz_bytes(wkind); }
 constexpr int kTmemCols = 512;
 // 4-bit weights: the dequantised weight tiles form a ring in TMEM (32 columns per 128 x 64 tile) at the top of the 512 columns,
 // `stages` deep and in lock step with the X ring in shared memory: 8 tiles when the two accumulators fit 256 columns (token tile
@@ -221,7 +224,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
         const uint8_t* wsrc = p.w4 + ((size_t)nt * ktiles + k0) * kPackedBytes;
-        const uint32_t* zsrc = p.w4_sz + (size_t)nt * BM;
+        const uint32_t* zsrc = p.w4_sz + (size_t)nt * BM * sz_words(WKIND);
         int g = k0 / gk, gi = k0 - g * gk;  // quantisation group of the k tile and position inside it
         for (int kt = k0; kt < k1; ++kt) {
           ok = mbar_wait(&pempty[pr.idx], pr.phase ^ 1, abort_flag);
@@ -230,7 +233,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           mbar_expect_tx(&pfull[pr.idx], kPackedSlot);
           bulk_load(dst, wsrc, kPackedBytes, &pfull[pr.idx]);
           // the group's scales/zeros ride along, so the dequantisation warps never touch global memory
-          bulk_load(dst + kPackedBytes, zsrc + (size_t)g * p.n_pad, kSzBytes, &pfull[pr.idx]);
+          bulk_load(dst + kPackedBytes, zsrc + (size_t)g * p.n_pad * sz_words(WKIND), sz_bytes(WKIND), &pfull[pr.idx]);
           wsrc += kPackedBytes;
           if (++gi == gk) { gi = 0; ++g; }
           pr.advance(PS);
@@ -318,7 +321,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (!ok) break;
           tc_fence_after();
           const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
-          const uint32_t szv = lds32(slot + kPackedBytes + r * 4);
+          const uint32_t szv = WKIND == 4 ? 0u : lds32(slot + kPackedBytes + r * 4);
           const uint32_t s2 = (szv & 0xffffu) | (szv << 16);          // low half replicated
           const uint32_t zb2 = (szv >> 16) | (szv & 0xffff0000u);    // high half replicated
           uint32_t o[32];  // 64 bf16 of this row: column c holds k = 2c (low half) and 2c+1 (high half)
@@ -345,6 +348,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
                 o[4 * c + 1] = dq_pair(q >> 4, zb2, s2);
                 o[4 * c + 2] = dq_pair(q >> 8, zb2, s2);
                 o[4 * c + 3] = dq_pair(q >> 12, zb2, s2);
+              } else if (WKIND == 4) {  // words 2g, 2g + 1 are the 16 k of group g
+                const uint32_t szw = lds32(slot + kPackedBytes + r * 8 + (c >> 2) * 4);
+                const uint32_t sc = (c & 2) ? ((szw >> 16) | (szw & 0xffff0000u)) : ((szw & 0xffffu) | (szw << 16));
+                o[4 * c] = dq_fp4_pair(q, sc);
+                o[4 * c + 1] = dq_fp4_pair(q >> 4, sc);
+                o[4 * c + 2] = dq_fp4_pair(q >> 8, sc);
+                o[4 * c + 3] = dq_fp4_pair(q >> 12, sc);
               } else {  // words 0-3 are k 0..31 (first scale), words 4-7 are k 32..63 (second scale)
                 const uint32_t sc = c < 4 ? s2 : zb2;
                 o[4 * c] = dq_fp4_pair(q, sc);
@@ -622,9 +632,9 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   int grid = total < num_sms ? total : num_sms;
   if (w4 && p.wkind == 0) p.wkind = 1;  // packed weights without a stated kind are 4-bit integer
   if (!w4) p.wkind = 0;
-  if (p.wkind < 0 || p.wkind > 3) return -6;
+  if (p.wkind < 0 || p.wkind > 4) return -6;
   int smem = gemm_smem_bytes(p);
-  static bool configured[4] = {false, false, false, false};
+  static bool configured[5] = {false, false, false, false, false};
   auto launch = [&](auto kernel, int threads) -> int {
     if (!configured[p.wkind]) {
       if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
@@ -638,7 +648,8 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
     case 0: rc = launch(gemm_wx_kernel<0>, Roles<0>::kThreads); break;
     case 1: rc = launch(gemm_wx_kernel<1>, Roles<1>::kThreads); break;
     case 2: rc = launch(gemm_wx_kernel<2>, Roles<2>::kThreads); break;
-    default: rc = launch(gemm_wx_kernel<3>, Roles<3>::kThreads); break;
+    case 3: rc = launch(gemm_wx_kernel<3>, Roles<3>::kThreads); break;
+    default: rc = launch(gemm_wx_kernel<4>, Roles<4>::kThreads); break;
   }
   if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

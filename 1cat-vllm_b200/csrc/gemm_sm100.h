@@ -37,7 +37,8 @@ struct GemmParams {
   const uint8_t* w4;        // packed weight tiles [n tile][k tile][4096 B (int4, fp4) or 8192 B (fp8)]; null for bf16 weights
   const uint32_t* w4_sz;    // [group][n_pad] words: int4 bf16 scale | bf16 (128 + zero) << 16; fp8 bf16 (scale * 2^120);
                             // fp4 bf16 scales (* 2^126) of the k tile's two 32-k groups
-  int wkind;                // 0 bf16 weights, 1 int4 with zero points (AWQ/GPTQ), 2 fp8 e4m3 block-scaled, 3 fp4 e2m1 (MXFP4)
+  int wkind;                // 0 bf16 weights, 1 int4 with zero points (AWQ/GPTQ), 2 fp8 e4m3 block-scaled, 3 fp4 e2m1 (MXFP4),
+                            // 4 fp4 e2m1 with four scales per k tile (NVFP4; two words per row in w4_sz)
 };
 
 void gemm_plan(GemmParams& p, int num_sms, bool w4);

@@ -184,6 +184,22 @@ def pack_mxfp4(packed: torch.Tensor, scales_ue8m0: torch.Tensor):
     return tiles, sz, npad
 
 
+def pack_nvfp4(packed: torch.Tensor, scales_e4m3: torch.Tensor, global_scale: torch.Tensor):
+    """packed ``[N, K/2]`` uint8 (low nibble = even k), scales ``[N, K/16]`` e4m3, one fp32 global scale → (tiles as ``pack_mxfp4``,
+    sz int32 ``[K/64, Npad, 2]``: per row and k tile the four 16-k groups' ``bf16(scale * global * 2**126)``, two per word)."""
+    N, K2 = packed.shape
+    K = K2 * 2
+    assert K % 64 == 0
+    tiles, _, npad = pack_mxfp4(packed, torch.full((N, K // 32), 127, dtype=torch.uint8, device=packed.device))
+    sc = scales_e4m3.float() * global_scale.float().reshape(-1)[0] * (2.0 ** 126)
+    assert bool(torch.isfinite(sc.to(torch.bfloat16)).all()), "NVFP4 scale too large for the bf16 scale word"
+    if npad != N:
+        sc = torch.cat([sc, sc.new_zeros(npad - N, sc.shape[1])])
+    sb = _bf16_bits(sc).view(npad, K // 64, 2, 2)
+    sz = (sb[..., 0] | (sb[..., 1] << 16)).permute(1, 0, 2).contiguous()
+    return tiles, sz, npad
+
+
 def _fp8_row_scales(layer, block) -> tuple[torch.Tensor, int]:
     """Per-row, per-k-group dequantisation scales of an FP8 linear layer and the k group size."""
     N, K = layer.weight.shape
@@ -220,10 +236,9 @@ def prepare_fp8(layer, block) -> None:
 
 
 def prepare_fp4(layer, kind: str) -> None:
-    """MXFP4 weights stay packed (tiles + power-of-two scale words, dequantised to bf16 on the way into TMEM); NVFP4 (e4m3 scales per
-    16 k and a global scale) is expanded to bf16 at load."""
+    """MXFP4 and NVFP4 weights stay packed (tiles + scale words, dequantised to bf16 on the way into TMEM)."""
     N, K2 = layer.weight.shape
-    if kind != "mxfp4" or (K2 * 2) % 64:
+    if kind not in ("mxfp4", "nvfp4") or (K2 * 2) % 64:
         w = layer.method.dequantized_weight(layer).to(torch.bfloat16)
         return _swap_to_dense(layer, w)
     pk, sc = layer.weight.data, layer.weight_scale.data
@@ -232,9 +247,13 @@ def prepare_fp4(layer, kind: str) -> None:
         perm = interleave_gate_up(N // 2, pk.device)
         pk, sc = pk[perm], sc[perm]
         n_out, epi = N // 2, EPI_SILU_MUL
-    tiles, sz, npad = pack_mxfp4(pk.contiguous(), sc.contiguous())
-    layer.kernel_state = dict(kind="w4", wkind=3, tiles=tiles, sz=sz, n_rows=n_rows, n_out=n_out, n_pad=npad, epi=epi, group_ktiles=1, K=K2 * 2)
-    for n in ("weight", "weight_scale"):
+    if kind == "nvfp4":
+        tiles, sz, npad = pack_nvfp4(pk.contiguous(), sc.contiguous(), layer.weight_scale_2.data)
+    else:
+        tiles, sz, npad = pack_mxfp4(pk.contiguous(), sc.contiguous())
+    layer.kernel_state = dict(kind="w4", wkind=4 if kind == "nvfp4" else 3, tiles=tiles, sz=sz, n_rows=n_rows, n_out=n_out, n_pad=npad, epi=epi,
+                              group_ktiles=1, K=K2 * 2)
+    for n in ("weight", "weight_scale", "weight_scale_2"):
         if hasattr(layer, n):
             delattr(layer, n)
 

@@ -221,6 +221,32 @@ def test_gemm_mxfp4_weight_only(T, fuse):
     _close(y, e, 2e-2, 2e-2, f"mxfp4 T={T} fuse={fuse}")
 
 
+@pytest.mark.parametrize("T", [1, 64, 300])
+@pytest.mark.parametrize("fuse", [False, True])
+def test_gemm_nvfp4_weight_only(T, fuse):
+    """NVFP4 (e2m1 nibbles, one e4m3 scale per 16 k, one fp32 global scale) dequantised inside the GEMM."""
+    N, Kd = 512, 640
+    g = torch.Generator(device="cuda").manual_seed(7)
+    packed = torch.randint(0, 256, (N, Kd // 2), device="cuda", generator=g, dtype=torch.uint8)
+    sc = (torch.rand(N, Kd // 16, device="cuda", generator=g) * 3 + 0.25).to(torch.float8_e4m3fn)
+    gs = torch.tensor([0.0123], device="cuda")
+    layer = _FakeLayer(fuse)
+    layer.weight = torch.nn.Parameter(packed.clone(), requires_grad=False)
+    layer.weight_scale = torch.nn.Parameter(sc.clone(), requires_grad=False)
+    layer.weight_scale_2 = torch.nn.Parameter(gs.clone(), requires_grad=False)
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    K().prepare_fp4(layer, "nvfp4")
+    assert layer.kernel_state["wkind"] == 4 and not hasattr(layer, "weight")
+    y = K().linear(layer, x)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    wd = ref.nvfp4_dequantize(packed, sc, gs)
+    e = x.float().cpu() @ wd.float().cpu().t()
+    if fuse:
+        e = torch.nn.functional.silu(e[:, : N // 2]) * e[:, N // 2:]
+    _close(y, e, 3e-2, 3e-2, f"nvfp4 T={T} fuse={fuse}")
+
+
 @pytest.mark.parametrize("kind", ["fp8", "mxfp4"])
 @pytest.mark.parametrize("T,E,k", [(1, 8, 2), (40, 32, 8), (300, 8, 2)])
 def test_fused_moe_packed_experts(kind, T, E, k):

@@ -123,3 +123,35 @@ def test_weight_packers_keep_every_value_addressable():
         half = (int(sz4[kt, n]) >> (16 * (kk // 32))) & 0xFFFF
         want = torch.tensor(2.0 ** (int(e[n, k // 32]) - 1)).to(torch.bfloat16).view(torch.int16).int() & 0xFFFF
         assert half == int(want)
+
+
+def test_nvfp4_packer_round_trips_through_the_kernel_layout():
+    """Rebuild the weights from the NVFP4 tiles and scale words exactly as the kernel reads them (word c of a row's 8 words holds
+    k = 8c..8c+7; group g = c // 2 takes the g-th bf16 of the row's two scale words) and compare with the reference dequantisation."""
+    import torch
+    from onecat_vllm.ops import ref
+    from onecat_vllm.ops.cuda import _NIB_ORDER, pack_nvfp4
+    N, K = 128, 128
+    g = torch.Generator().manual_seed(3)
+    packed = torch.randint(0, 256, (N, K // 2), generator=g, dtype=torch.uint8)
+    sc = (torch.rand(N, K // 16, generator=g) * 3 + 0.25).to(torch.float8_e4m3fn)
+    gs = torch.tensor([0.02])
+    tiles, sz, npad = pack_nvfp4(packed, sc, gs)
+    assert tiles.shape == (1, 2, 4096) and sz.shape == (2, 128, 2)
+    want = ref.nvfp4_dequantize(packed, sc, gs)
+    lut = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+    words = tiles.view(1, 2, 2, 128, 4, 4).to(torch.int64)  # [nt][kt][half][row][word][byte]
+    got = torch.zeros(N, K)
+    for kt in range(2):
+        for r in range(N):
+            for c in range(8):
+                b = words[0, kt, c // 4, r, c % 4]
+                word = int(b[0]) | int(b[1]) << 8 | int(b[2]) << 16 | int(b[3]) << 24
+                szw = int(sz[kt, r, c // 4]) & 0xFFFFFFFF
+                half = (szw >> 16) & 0xFFFF if (c & 2) else szw & 0xFFFF
+                s = torch.tensor([half << 16], dtype=torch.int32).view(torch.float32).item() / 2.0 ** 126
+                for j in range(8):
+                    nib = (word >> (4 * _NIB_ORDER.index(j))) & 0xF
+                    v = lut[nib & 7].item() * (-1.0 if nib & 8 else 1.0)
+                    got[r, kt * 64 + c * 8 + j] = v * s
+    assert torch.allclose(got, want, rtol=2 ** -7, atol=1e-6)

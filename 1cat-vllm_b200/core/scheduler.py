@@ -97,6 +97,10 @@ def check_stop(request: Request, max_model_len: int) -> bool:
     if request.num_tokens >= max_model_len or request.num_output_tokens >= request.max_tokens:
         request.status = RequestStatus.FINISHED_LENGTH_CAPPED
         return True
+    if sp is not None and sp.repetition_detection is not None and sp.repetition_detection.hit(request.output_token_ids):
+        request.status = RequestStatus.FINISHED_STOPPED
+        request.stop_reason = "repetition"
+        return True
     return False
 
 

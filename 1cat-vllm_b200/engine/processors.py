@@ -22,6 +22,14 @@ class InputProcessor:
     def __init__(self, cfg: VllmConfig, tokenizer):
         self.cfg, self.tok = cfg, tokenizer
 
+    def _think_token_ids(self):
+        if self.tok is None:
+            return None
+        if not hasattr(self, "_think_cache"):
+            a, b = _single_token(self.tok, "<think>"), _single_token(self.tok, "</think>")
+            self._think_cache = (a, b) if a is not None and b is not None else None
+        return self._think_cache
+
     def process(self, request_id: str, prompt: PromptType, params: SamplingParams, arrival_time: Optional[float] = None,
                 priority: int = 0, lora_request=None) -> tuple[EngineCoreRequest, Optional[str]]:
         if lora_request is not None and not self.cfg.model_config.enable_lora:
@@ -51,6 +59,12 @@ class InputProcessor:
             raise ValueError("at most 20 logprobs per token can be requested")
         eos = mc.eos_token_id if mc.eos_token_id is not None else getattr(self.tok, "eos_token_id", None)
         sp.update_from_generation_config(eos)
+        if sp.thinking_token_budget is not None:
+            if sp.thinking_token_budget < 0:
+                raise ValueError("thinking_token_budget must be a non-negative integer")
+            sp._think_ids = self._think_token_ids()
+            if sp._think_ids is None:
+                raise ValueError("thinking_token_budget needs a tokenizer in which <think> and </think> are single tokens")
         if sp.bad_words and self.tok is not None and not sp.bad_words_token_ids:
             sp.bad_words_token_ids = [self.tok.encode(w, add_special_tokens=False) for w in sp.bad_words]
         if sp.allowed_token_ids is not None and any(not 0 <= t < mc.vocab_size for t in sp.allowed_token_ids):
@@ -58,6 +72,14 @@ class InputProcessor:
         req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling,
                                 lora_request=lora_request)
         return req, text
+
+
+def _single_token(tok, text: str):
+    try:
+        ids = tok.encode(text, add_special_tokens=False)
+    except TypeError:
+        ids = tok.encode(text)
+    return ids[0] if len(ids) == 1 else None
 
 
 @dataclass

@@ -28,3 +28,4 @@ class SamplingMetadata:
     allowed_token_ids: list = field(default_factory=list)  # per row list | None
     bad_words_token_ids: dict = field(default_factory=dict)  # row -> list[list[int]]
     grammar_bitmask: Optional[torch.Tensor] = None
+    thinking: dict = field(default_factory=dict)  # row -> (budget, think-start id, think-end id)

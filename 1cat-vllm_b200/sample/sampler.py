@@ -30,7 +30,8 @@ class Sampler:
         if md.max_num_logprobs is not None:
             raw_lp = torch.log_softmax(logits.float(), dim=-1)
         simple = (md.all_greedy and md.no_penalties and not md.min_tokens and not any(md.logit_bias) and
-                  not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and md.grammar_bitmask is None)
+                  not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and md.grammar_bitmask is None
+                  and not md.thinking)
         if simple:
             sampled = ops.argmax(logits)  # greedy fast path: no fp32 copy of the logits
         else:
@@ -66,6 +67,14 @@ class Sampler:
                 lg[i, idx] += torch.tensor(list(bias.values()), device=lg.device, dtype=lg.dtype)
         if md.grammar_bitmask is not None:
             lg.masked_fill_(~md.grammar_bitmask, -float("inf"))
+        for i, (budget, start, end) in md.thinking.items():
+            # inside a thinking block (after the last think-start, no think-end yet) that has used its budget: only think-end may follow
+            out = md.output_token_ids[i]
+            last_start = max((j for j, t in enumerate(out) if t == start), default=-1)
+            if last_start >= 0 and end not in out[last_start:] and len(out) - last_start - 1 >= budget:
+                keep = lg[i, end].clone()
+                lg[i].fill_(-float("inf"))
+                lg[i, end] = keep if torch.isfinite(keep) else 0.0
         return lg
 
     @staticmethod

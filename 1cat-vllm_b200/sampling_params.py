@@ -43,6 +43,34 @@ class StructuredOutputsParams:
 
 
 @dataclass
+class RepetitionDetectionParams:
+    """Stop a request whose output ends in an n-gram (``min_pattern_size`` .. ``max_pattern_size`` tokens) repeated ``min_count`` times
+    in a row (reference: vllm/sampling_params.py:145 ``RepetitionDetectionParams``). ``max_pattern_size = 0`` disables it."""
+
+    max_pattern_size: int = 0
+    min_pattern_size: int = 0
+    min_count: int = 0
+
+    def __post_init__(self) -> None:
+        if self.max_pattern_size < 0 or self.min_pattern_size < 0 or self.min_pattern_size > self.max_pattern_size:
+            raise ValueError("need 0 <= min_pattern_size <= max_pattern_size")
+        if self.max_pattern_size > 0 and self.min_count < 2:
+            raise ValueError("min_count must be >= 2 when repetition detection is on")
+
+    def hit(self, tokens: list) -> bool:
+        if self.max_pattern_size <= 0:
+            return False
+        for p in range(max(self.min_pattern_size, 1), self.max_pattern_size + 1):
+            need = p * self.min_count
+            if len(tokens) < need:
+                break
+            tail = tokens[-need:]
+            if all(tail[i] == tail[i % p] for i in range(p, need)):
+                return True
+        return False
+
+
+@dataclass
 class SamplingParams:
     n: int = 1
     presence_penalty: float = 0.0
@@ -69,10 +97,13 @@ class SamplingParams:
     bad_words: Optional[list[str]] = None
     bad_words_token_ids: Optional[list[list[int]]] = None
     structured_outputs: Optional[StructuredOutputsParams] = None
+    thinking_token_budget: Optional[int] = None  # at most this many tokens between the think-start and think-end tokens
+    repetition_detection: Optional[RepetitionDetectionParams] = None
     output_kind: RequestOutputKind = RequestOutputKind.CUMULATIVE
     extra_args: Optional[dict[str, Any]] = None
     # internal: eos ids resolved by the input processor
     _eos_token_id: Optional[int] = field(default=None, repr=False)
+    _think_ids: Optional[tuple] = field(default=None, repr=False)  # (think-start id, think-end id), resolved by the input processor
     _all_stop_token_ids: set = field(default_factory=set, repr=False)
 
     def __post_init__(self) -> None:
@@ -144,6 +175,10 @@ class SamplingParams:
         d["output_kind"] = int(self.output_kind)
         if self.structured_outputs is not None:
             d["structured_outputs"] = dict(self.structured_outputs.__dict__)
+        if self.repetition_detection is not None:
+            d["repetition_detection"] = dict(self.repetition_detection.__dict__)
+        if self._think_ids is not None:
+            d["_think_ids"] = list(self._think_ids)
         return d
 
     @classmethod
@@ -153,7 +188,12 @@ class SamplingParams:
         so = d.get("structured_outputs")
         if isinstance(so, dict):
             d["structured_outputs"] = StructuredOutputsParams(**so)
-        return cls(**d)
+        if isinstance(d.get("repetition_detection"), dict):
+            d["repetition_detection"] = RepetitionDetectionParams(**d["repetition_detection"])
+        think = d.pop("_think_ids", None)
+        sp = cls(**d)
+        sp._think_ids = tuple(think) if think else None
+        return sp
 
 
 @dataclass

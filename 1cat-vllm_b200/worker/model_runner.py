@@ -344,6 +344,8 @@ class ModelRunner:
                 md.min_tokens[i] = (sp.min_tokens, stops)
             if sp.bad_words_token_ids:
                 md.bad_words_token_ids[i] = sp.bad_words_token_ids
+            if sp.thinking_token_budget is not None and sp._think_ids is not None:
+                md.thinking[i] = (sp.thinking_token_budget, sp._think_ids[0], sp._think_ids[1])
         md.logit_bias = [sp.logit_bias if sp else None for sp in sps]
         md.allowed_token_ids = [sp.allowed_token_ids if sp else None for sp in sps]
         return md

@@ -146,3 +146,37 @@ def test_prompt_logprobs_match_a_direct_forward_across_chunks():
     assert max(abs(a - b) for a, b in zip(got[8192], got[16])) < 1e-4
     # ranks: the actual token's rank is 1 exactly when it is the arg-max
     assert any(v.rank == 1 for d in plp[1:] for v in d.values())
+
+
+def test_repetition_detection_and_thinking_budget():
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.sampling_params import RepetitionDetectionParams
+    r = RepetitionDetectionParams(max_pattern_size=3, min_pattern_size=2, min_count=3)
+    assert r.hit([9, 1, 2, 1, 2, 1, 2]) and r.hit([5, 1, 2, 3, 1, 2, 3, 1, 2, 3]) and not r.hit([1, 2, 1, 2, 3, 1, 2]) and not r.hit([7, 7, 7])
+    assert RepetitionDetectionParams(max_pattern_size=1, min_count=3).hit([4, 7, 7, 7])
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, tokenizer="byte")
+    # a random tiny model falls into a loop quickly under greedy decoding: detection stops it early with its own reason
+    base = llm.generate(["abc"], SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True))[0].outputs[0]
+    det = llm.generate(["abc"], SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True,
+                                               repetition_detection=RepetitionDetectionParams(max_pattern_size=8, min_count=3)))[0].outputs[0]
+    if r.__class__(max_pattern_size=8, min_count=3).hit(base.token_ids) or len(det.token_ids) < 60:
+        assert det.stop_reason == "repetition" and det.finish_reason == "stop" and len(det.token_ids) < 60
+        assert det.token_ids == base.token_ids[: len(det.token_ids)]
+    # thinking budget: the byte tokenizer has no single-token <think>, so the request is refused
+    import pytest
+    with pytest.raises(ValueError):
+        llm.generate(["x"], SamplingParams(max_tokens=4, thinking_token_budget=2))
+    llm.shutdown()
+    # the sampler forces the think-end token once the budget is used
+    import torch
+    from onecat_vllm.sample.metadata import SamplingMetadata
+    from onecat_vllm.sample.sampler import Sampler
+    md = SamplingMetadata(temperature=None, all_greedy=True, all_random=False, top_p=None, top_k=None, min_p=None, generators={},
+                          max_num_logprobs=None, no_penalties=True, output_token_ids=[[5, 100, 7, 8], [5, 100, 7], [100, 1, 2, 101, 3, 4, 5]],
+                          logit_bias=[None] * 3, allowed_token_ids=[None] * 3, thinking={0: (2, 100, 101), 1: (2, 100, 101), 2: (2, 100, 101)})
+    lg = torch.zeros(3, 200)
+    lg[:, 42] = 5.0
+    out = Sampler()(lg, md).sampled_token_ids.tolist()
+    assert out == [101, 42, 42]  # row 0 used its budget; row 1 has one token left; row 2 already closed its block

@@ -7,7 +7,7 @@ from typing import Any, Literal, Optional, Union
 
 from pydantic import BaseModel, ConfigDict, Field
 
-from onecat_vllm.sampling_params import RequestOutputKind, SamplingParams, StructuredOutputsParams
+from onecat_vllm.sampling_params import RepetitionDetectionParams, RequestOutputKind, SamplingParams, StructuredOutputsParams
 
 
 class _Base(BaseModel):
@@ -39,6 +39,9 @@ class _SamplingMixin(_Base):
     structured_outputs: Optional[dict] = None
     allowed_token_ids: Optional[list[int]] = None
     bad_words: Optional[list[str]] = None
+    thinking_token_budget: Optional[int] = None
+    repetition_detection: Optional[dict] = None
+    prompt_logprobs: Optional[int] = None
     user: Optional[str] = None
 
     def to_sampling_params(self, default_max_tokens: int, logprobs: Optional[int] = None) -> SamplingParams:
@@ -58,6 +61,8 @@ class _SamplingMixin(_Base):
             logprobs=logprobs, skip_special_tokens=self.skip_special_tokens,
             logit_bias={int(k): float(v) for k, v in self.logit_bias.items()} if self.logit_bias else None,
             allowed_token_ids=self.allowed_token_ids, bad_words=self.bad_words, structured_outputs=so,
+            thinking_token_budget=self.thinking_token_budget, prompt_logprobs=self.prompt_logprobs,
+            repetition_detection=RepetitionDetectionParams(**self.repetition_detection) if self.repetition_detection else None,
             output_kind=RequestOutputKind.DELTA if self.stream else RequestOutputKind.FINAL_ONLY)
 
 

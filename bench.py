@@ -106,6 +106,43 @@ class ClockSampler:
                 "power_w_max": max(pw) if pw else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def stock_vllm_arm(args) -> None:
+    """Context only, never the reference arm: the same dense AWQ workload through the stock ``vllm`` wheel of the image (library code:
+    its own kernels and scheduler), random weights via ``load_format="dummy"``. 256 requests of 1024 random tokens in / 256 out with
+    at most 64 running; the number is output tokens over the wall time of ``LLM.generate``."""
+    import json as _json
+    try:
+        import torch
+        from vllm import LLM as VLLM
+        from vllm import SamplingParams as VSP
+        d = tempfile.mkdtemp(prefix="onecat_stock_")
+        cfg = dict(CFG_27B, model_type="qwen3", hidden_act="silu", torch_dtype="bfloat16", attention_bias=False, use_cache=True,
+                   initializer_range=0.02, bos_token_id=1, eos_token_id=2)
+        cfg["quantization_config"] = dict(cfg["quantization_config"], version="gemm")
+        with open(os.path.join(d, "config.json"), "w") as f:
+            _json.dump(cfg, f)
+        C, IN, OUT = args.concurrency or 64, args.input_len or 1024, args.output_len or 256
+        llm = VLLM(model=d, load_format="dummy", skip_tokenizer_init=True, dtype="bfloat16", max_model_len=IN + OUT + 16, max_num_seqs=C,
+                   max_num_batched_tokens=8192, tensor_parallel_size=args.gpus, gpu_memory_utilization=0.85, enable_prefix_caching=False, seed=0)
+        g = torch.Generator().manual_seed(0)
+        n_req = 4 * C
+        prompts = [{"prompt_token_ids": torch.randint(0, cfg["vocab_size"], (IN,), generator=g).tolist()} for _ in range(n_req)]
+        sp = VSP(temperature=0.0, max_tokens=OUT, ignore_eos=True, detokenize=False)
+        llm.generate(prompts[:C], VSP(temperature=0.0, max_tokens=8, ignore_eos=True, detokenize=False))  # warm-up
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        outs = llm.generate(prompts, sp)
+        torch.cuda.synchronize()
+        wall = time.perf_counter() - t0
+        toks = sum(len(o.outputs[0].token_ids) for o in outs)
+        import vllm
+        print(_json.dumps({"impl": "stock-vllm", "vllm_version": vllm.__version__, "metric": "output tokens/s (wall clock of LLM.generate)",
+                           "value": toks / wall, "unit": "tokens/s", "n_gpus": args.gpus, "wall_s": wall, "output_tokens": toks,
+                           "config": {"model": CONFIGS["dense27b"][1], "workload": f"{n_req} requests, {IN} in / {OUT} out, at most {C} running"}}))
+    except Exception as e:  # context only: never fail the caller
+        print(_json.dumps({"impl": "stock-vllm", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
+
+
 def _kv_bytes(cfg: dict, C: int, seq: int, gpus: int) -> int:
     """KV-cache bytes per GPU for C sequences of `seq` tokens (bf16): attention layers only; MLA keeps one 576-wide latent."""
     L = cfg["num_hidden_layers"]
@@ -140,6 +177,9 @@ def main() -> None:
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.impl == "stock-vllm":
+        stock_vllm_arm(args)
         return
     import torch
     import torch.distributed as dist

@@ -1,6 +1,6 @@
 """Plain PyTorch restatements of every op.
 
-They serve three roles: the CPU execution path (BASELINE config 1), the fp32 oracle that every CUDA
+They serve three roles: the CPU execution path (the tiny-model plumbing run), the fp32 oracle that every CUDA
 kernel is tested against, and the timed CPU baseline. Math follows the reference's native/CPU code:
 RMSNorm (reference: model_executor/layers/layernorm.py:201 ``forward_native``, Gemma :252-420), NeoX RoPE
 (csrc/libtorch_stable/pos_encoding_kernels.cu:77), paged attention (v1/attention/backends/flash_attn_v100.py:2216

@@ -19,6 +19,7 @@ class NewRequestData:
     eos_token_id: Optional[int] = None
     pooling_params: Any = None
     lora_request: Any = None
+    prompt_embeds: Any = None
 
 
 @dataclass

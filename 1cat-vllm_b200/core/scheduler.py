@@ -276,7 +276,7 @@ class Scheduler:
         km = self.kv_cache_manager
         out.scheduled_new_reqs = [
             NewRequestData(r.request_id, r.prompt_token_ids, r.sampling_params, new_blocks_of[r.request_id],
-                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params, r.lora_request)
+                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params, r.lora_request, r.prompt_embeds)
             for r in scheduled_new]
         cached = CachedRequestData()
         for r in scheduled_resumed + scheduled_running:

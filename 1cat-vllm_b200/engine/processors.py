@@ -34,7 +34,15 @@ class InputProcessor:
                 priority: int = 0, lora_request=None) -> tuple[EngineCoreRequest, Optional[str]]:
         if lora_request is not None and not self.cfg.model_config.enable_lora:
             raise ValueError("this engine was started without enable_lora")
-        text, ids, salt = parse_prompt(prompt)
+        embeds = prompt.get("prompt_embeds") if isinstance(prompt, dict) else None
+        if embeds is not None:
+            import torch
+            embeds = torch.as_tensor(embeds)
+            if embeds.dim() != 2 or embeds.shape[1] != self.cfg.model_config.hidden_size:
+                raise ValueError(f"prompt_embeds must be [num_tokens, {self.cfg.model_config.hidden_size}]")
+            text, ids, salt = None, [0] * embeds.shape[0], prompt.get("cache_salt")
+        else:
+            text, ids, salt = parse_prompt(prompt)
         if ids is None:
             if self.tok is None:
                 raise ValueError("text prompts need a tokenizer; pass token ids or set tokenizer=")
@@ -70,7 +78,7 @@ class InputProcessor:
         if sp.allowed_token_ids is not None and any(not 0 <= t < mc.vocab_size for t in sp.allowed_token_ids):
             raise ValueError("allowed_token_ids contains an id outside the vocabulary")
         req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling,
-                                lora_request=lora_request)
+                                lora_request=lora_request, prompt_embeds=embeds)
         return req, text
 
 

@@ -15,7 +15,15 @@ class TokensPrompt(TypedDict, total=False):
     cache_salt: Optional[str]
 
 
-PromptType = Union[str, list[int], TextPrompt, TokensPrompt]
+class EmbedsPrompt(TypedDict, total=False):
+    """Precomputed input embeddings ``[num_tokens, hidden_size]`` instead of token ids: the output of an external encoder (for
+    instance a vision tower) or of the model's own embedding table (reference: vllm/inputs/data.py ``EmbedsPrompt``)."""
+
+    prompt_embeds: object
+    cache_salt: Optional[str]
+
+
+PromptType = Union[str, list[int], TextPrompt, TokensPrompt, EmbedsPrompt]
 
 
 def parse_prompt(p: PromptType) -> tuple[Optional[str], Optional[list[int]], Optional[str]]:

@@ -54,6 +54,7 @@ class EngineCoreRequest:
     pooling_params: Any = None
     lora_request: Any = None
     trace_headers: Optional[dict] = None
+    prompt_embeds: Any = None  # [num_prompt_tokens, hidden] tensor replacing the embedding lookup of the prompt
 
     def to_wire(self) -> dict:
         return {"request_id": self.request_id, "prompt_token_ids": self.prompt_token_ids,
@@ -61,7 +62,8 @@ class EngineCoreRequest:
                 "arrival_time": self.arrival_time, "eos_token_id": self.eos_token_id, "priority": self.priority,
                 "cache_salt": self.cache_salt, "client_index": self.client_index,
                 "pooling_params": self.pooling_params.to_dict() if self.pooling_params is not None else None,
-                "lora_request": self.lora_request.to_dict() if self.lora_request is not None else None}
+                "lora_request": self.lora_request.to_dict() if self.lora_request is not None else None,
+                "prompt_embeds": self.prompt_embeds}
 
     @classmethod
     def from_wire(cls, d: dict) -> "EngineCoreRequest":
@@ -72,7 +74,8 @@ class EngineCoreRequest:
             pp = PoolingParams(**pp)
         return cls(d["request_id"], list(d["prompt_token_ids"]), SamplingParams.from_dict(sp) if sp else None,
                    d.get("arrival_time", 0.0), d.get("eos_token_id"), d.get("priority", 0), d.get("cache_salt"),
-                   d.get("client_index", 0), pooling_params=pp, lora_request=_lora_from(d.get("lora_request")))
+                   d.get("client_index", 0), pooling_params=pp, lora_request=_lora_from(d.get("lora_request")),
+                   prompt_embeds=d.get("prompt_embeds"))
 
 
 @dataclass
@@ -137,8 +140,12 @@ class Request:
 
     def __init__(self, request_id: str, prompt_token_ids: list[int], sampling_params: Optional[SamplingParams],
                  eos_token_id: Optional[int] = None, arrival_time: Optional[float] = None, priority: int = 0,
-                 cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None, lora_request=None) -> None:
+                 cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None, lora_request=None,
+                 prompt_embeds=None) -> None:
         self.request_id = request_id
+        self.prompt_embeds = prompt_embeds
+        if prompt_embeds is not None:  # placeholder ids say nothing about the content: never share KV blocks with another request
+            cache_salt = f"{cache_salt or ''}|embeds:{request_id}"
         self.lora_request = lora_request
         if lora_request is not None:  # KV computed under an adapter is only reusable under the same adapter
             cache_salt = f"{cache_salt or ''}|lora:{lora_request.lora_int_id}"
@@ -173,7 +180,7 @@ class Request:
     @classmethod
     def from_engine_core_request(cls, r: EngineCoreRequest, block_hasher=None) -> "Request":
         return cls(r.request_id, r.prompt_token_ids, r.sampling_params, r.eos_token_id, r.arrival_time, r.priority,
-                   r.cache_salt, r.client_index, block_hasher, r.pooling_params, r.lora_request)
+                   r.cache_salt, r.client_index, block_hasher, r.pooling_params, r.lora_request, r.prompt_embeds)
 
     def append_output_token_ids(self, ids: int | list[int]) -> None:
         if isinstance(ids, int):

@@ -42,6 +42,7 @@ class CachedRequestState:
     eos_token_id: Optional[int] = None
     pooling_params: object = None
     lora_request: object = None
+    prompt_embeds: Optional[torch.Tensor] = None
     pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
     pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
 
@@ -193,7 +194,8 @@ class ModelRunner:
                 gen.manual_seed(sp.seed)
             self.requests[nr.req_id] = CachedRequestState(nr.req_id, list(nr.prompt_token_ids), len(nr.prompt_token_ids), sp,
                                                           list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id,
-                                                          nr.pooling_params, nr.lora_request)
+                                                          nr.pooling_params, nr.lora_request,
+                                                          nr.prompt_embeds.to(self.device, self.mc.dtype) if nr.prompt_embeds is not None else None)
         c = so.scheduled_cached_reqs
         for i, rid in enumerate(c.req_ids):
             st = self.requests.get(rid)
@@ -203,7 +205,8 @@ class ModelRunner:
                 st = CachedRequestState(rid, list(toks), old.num_prompt_tokens if old else len(toks), old.sampling_params if old else None,
                                         list(c.new_block_ids[i] or []), c.num_computed_tokens[i], c.state_slots[i],
                                         old.generator if old else None, old.eos_token_id if old else None,
-                                        old.pooling_params if old else None, old.lora_request if old else None)
+                                        old.pooling_params if old else None, old.lora_request if old else None,
+                                        old.prompt_embeds if old else None)
                 self.requests[rid] = st
             else:
                 st.num_computed_tokens = c.num_computed_tokens[i]
@@ -439,7 +442,7 @@ class ModelRunner:
             hidden = self.graphs.run(gkey, T)
         if hidden is None:
             inter = self._pp_recv(T) if not self.pp.is_first_pp else None
-            hidden = self.model(ids, md, self.kv_caches, intermediate=inter)
+            hidden = self.model(ids, md, self.kv_caches, inputs_embeds=self._input_embeds(ids, req_ids, query_lens), intermediate=inter)
         if lora_batch is not None:
             from onecat_vllm.lora import set_active
             set_active(None)
@@ -528,6 +531,23 @@ class ModelRunner:
                 res[rid] = [(ids[j], lps[j], ranks[j]) for j in range(n)]
             o += q
         return res
+
+    def _input_embeds(self, ids: torch.Tensor, req_ids: list, query_lens: list[int]) -> Optional[torch.Tensor]:
+        """Embedding rows of the step with the prompt positions of ``prompt_embeds`` requests replaced by their own vectors;
+        ``None`` when no such position is in the batch (reference: v1/worker/gpu_model_runner.py ``enable_prompt_embeds`` path)."""
+        if not self.pp.is_first_pp:
+            return None
+        emb, o = None, 0
+        for rid, q in zip(req_ids, query_lens):
+            st = self.requests[rid]
+            c0 = st.num_computed_tokens
+            if st.prompt_embeds is not None and c0 < st.num_prompt_tokens:
+                if emb is None:
+                    emb = self.model.model.embed_tokens(ids)
+                n = min(q, st.num_prompt_tokens - c0)
+                emb[o:o + n] = st.prompt_embeds[c0:c0 + n]
+            o += q
+        return emb
 
     def _pool(self, hidden: torch.Tensor, req_ids: list, query_lens: list[int], rows: list[int]) -> list:
         """Pooled final-norm hidden state of embedding requests: last token, first token or mean over the prompt (accumulated

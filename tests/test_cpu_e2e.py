@@ -180,3 +180,23 @@ def test_beam_search_finds_a_sequence_at_least_as_likely_as_greedy():
     one = llm.beam_search([prompt], BeamSearchParams(beam_width=1, max_tokens=5, ignore_eos=True))[0]["sequences"][0]
     assert one["tokens"][5:] == greedy.token_ids
     llm.shutdown()
+
+
+def test_prompt_embeds_equal_token_prompts_and_can_be_chunked():
+    """Feeding the embedding rows of a token prompt as ``prompt_embeds`` gives the same continuation as the token prompt, also when the
+    prompt is prefilled in chunks and batched with ordinary requests."""
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, max_num_batched_tokens=16)
+    table = llm.llm_engine.engine_core.core.executor.worker.runner.model.model.embed_tokens.weight.detach().clone()
+    ids = [(9 * i) % 290 + 1 for i in range(37)]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    want = llm.generate([{"prompt_token_ids": ids}], sp)[0].outputs[0].token_ids
+    outs = llm.generate([{"prompt_embeds": table[ids]}, {"prompt_token_ids": ids[:10]}], sp)
+    assert outs[0].outputs[0].token_ids == want and len(outs[0].prompt_token_ids) == 37
+    import pytest
+    with pytest.raises(ValueError):
+        llm.generate([{"prompt_embeds": torch.zeros(3, 5)}], sp)
+    llm.shutdown()

@@ -61,3 +61,55 @@ def test_engine_gpu_matches_cpu(tmp_path, eager):
     cpu.shutdown()
     assert first_same >= len(prompts) - 2, f"only {first_same}/{len(prompts)} prompts agree on the first generated token"
     assert agree / total > 0.35, f"GPU and CPU greedy decodes diverge too early: {agree}/{total} tokens before first difference"
+
+
+def test_features_on_gpu_lora_offload_structured_embeds(tmp_path):
+    """The engine features that only add host logic or small device ops run on the GPU path too: a LoRA adapter changes the first-token
+    log-probability the same way as on the CPU path, the CPU tier of the prefix cache restores evicted blocks, a grammar constrains the
+    output, prompt embeddings reproduce their token prompt."""
+    import json as _json
+    from safetensors.torch import save_file
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.lora import LoRARequest
+    from onecat_vllm.sampling_params import StructuredOutputsParams
+    base = _make_checkpoint(tmp_path / "base")
+    g = torch.Generator().manual_seed(5)
+    ad = {}
+    for l in range(CFG["num_hidden_layers"]):
+        for name, (i, o) in {"self_attn.q_proj": (512, 512), "self_attn.o_proj": (512, 512), "mlp.gate_proj": (512, 1024), "mlp.down_proj": (1024, 512)}.items():
+            ad[f"base_model.model.model.layers.{l}.{name}.lora_A.weight"] = torch.randn(8, i, generator=g) * 0.1
+            ad[f"base_model.model.model.layers.{l}.{name}.lora_B.weight"] = torch.randn(o, 8, generator=g) * 0.1
+    os.makedirs(tmp_path / "ad", exist_ok=True)
+    save_file(ad, str(tmp_path / "ad" / "adapter_model.safetensors"))
+    _json.dump({"r": 8, "lora_alpha": 16}, open(tmp_path / "ad" / "adapter_config.json", "w"))
+    req = LoRARequest("ad", 1, str(tmp_path / "ad"))
+    prompt = {"prompt_token_ids": torch.randint(0, 2048, (40,), generator=g).tolist()}
+    sp = SamplingParams(temperature=0.0, max_tokens=4, ignore_eos=True, logprobs=0)
+    res = {}
+    for dev, dt in (("cpu", "float32"), ("cuda", "bfloat16")):
+        llm = LLM(model=base, device=dev, dtype=dt, max_model_len=512, max_num_seqs=8, gpu_memory_utilization=0.3, enable_lora=True,
+                  num_gpu_blocks_override=40, num_cpu_blocks_override=64, tokenizer="byte")
+        plain = llm.generate([prompt], sp)[0].outputs[0]
+        lora = llm.generate([prompt], sp, lora_request=req)[0].outputs[0]
+        res[dev] = (plain.logprobs[0][plain.token_ids[0]].logprob, lora.logprobs[0][lora.token_ids[0]].logprob, plain.token_ids[0], lora.token_ids[0])
+        if dev == "cuda":
+            # CPU tier: push the prompt's blocks out of the 40-block pool with other traffic, then hit them again
+            tier = llm.llm_engine.engine_core.core.scheduler.kv_cache_manager.offload
+            for j in range(6):
+                llm.generate([{"prompt_token_ids": torch.randint(0, 2048, (200,), generator=g).tolist()}], sp)
+            again = llm.generate([prompt], sp)[0]
+            assert tier.restored >= 2 and again.num_cached_tokens >= 32 and again.outputs[0].token_ids[0] == plain.token_ids[0]
+            # grammar: the answer is one of the choices
+            ch = llm.generate(["pick:"], SamplingParams(temperature=0.0, max_tokens=8, structured_outputs=StructuredOutputsParams(choice=["red", "blue"])))[0]
+            assert ch.outputs[0].text in ("red", "blue")
+            # prompt embeddings
+            table = llm.llm_engine.engine_core.core.executor.worker.runner.model.model.embed_tokens.weight.detach()
+            emb = llm.generate([{"prompt_embeds": table[torch.tensor(prompt["prompt_token_ids"], device=table.device)].cpu()}], sp)[0]
+            assert emb.outputs[0].token_ids[0] == plain.token_ids[0]
+            from onecat_vllm.ops import cuda as K
+            assert K.check_status() == 0
+        llm.shutdown()
+    assert abs(res["cpu"][0] - res["cuda"][0]) < 0.15, res
+    if res["cpu"][3] == res["cuda"][3]:
+        assert abs(res["cpu"][1] - res["cuda"][1]) < 0.15, res
+    assert abs(res["cuda"][0] - res["cuda"][1]) > 1e-3 or res["cuda"][2] != res["cuda"][3], "the adapter must change the GPU output"

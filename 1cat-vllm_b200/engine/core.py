@@ -26,6 +26,8 @@ class CollectiveTimeout(RuntimeError):
 class EngineCore:
     def __init__(self, vllm_config: VllmConfig, executor_class=None, log_stats: bool = True):
         self.cfg = vllm_config
+        from onecat_vllm.utils.plugins import load_general_plugins
+        load_general_plugins()
         executor_class = executor_class or Executor.get_class(vllm_config)
         t0 = time.time()
         self.executor = executor_class(vllm_config)

@@ -31,6 +31,8 @@ class Worker:
         self.sleeping = False
 
     def init_device(self) -> None:
+        from onecat_vllm.utils.plugins import load_general_plugins
+        load_general_plugins()  # worker processes register out-of-tree models too
         pc = self.cfg.parallel_config
         if self.cfg.device == "cuda":
             torch.cuda.set_device(self.local_rank)

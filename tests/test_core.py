@@ -215,3 +215,25 @@ def test_kv_events_are_published_over_zmq():
     assert seqs == sorted(seqs) and len(seqs) >= 1 and stored >= 3
     sub.close(linger=0)
     llm.shutdown()
+
+
+def test_general_plugins_run_once_and_register_models(monkeypatch):
+    import onecat_vllm.utils.plugins as P
+    from onecat_vllm.models import register_model, supported_architectures
+
+    class EP:
+        def __init__(self, name, fn):
+            self.name, self._fn = name, fn
+
+        def load(self):
+            return self._fn
+
+    calls = []
+    eps = [EP("a", lambda: (calls.append("a"), register_model("MyOutOfTreeForCausalLM", "dense"))), EP("b", lambda: calls.append("b")),
+           EP("broken", lambda: 1 / 0)]
+    monkeypatch.setattr("importlib.metadata.entry_points", lambda group: eps if group == P.GENERAL_GROUP else [])
+    monkeypatch.setattr(P, "_loaded", False)
+    monkeypatch.setenv("ONECAT_PLUGINS", "a,broken")
+    assert P.load_general_plugins() == ["a"] and calls == ["a"]
+    assert "MyOutOfTreeForCausalLM" in supported_architectures()
+    assert P.load_general_plugins() == []  # once per process

@@ -143,6 +143,31 @@ def stock_vllm_arm(args) -> None:
         print(_json.dumps({"impl": "stock-vllm", "unavailable": f"{type(e).__name__}: {str(e)[:300]}"}))
 
 
+def ours_offline_arm(args) -> None:
+    """The workload of ``stock_vllm_arm`` measured the same way through this engine's ``LLM.generate`` (wall clock, ramp-up and tail
+    included), for a like-for-like context comparison on one GPU."""
+    import json as _json
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(CFG_27B)
+    C, IN, OUT = args.concurrency or 64, args.input_len or 1024, args.output_len or 256
+    llm = LLM(hf_config=cfg, dtype="bfloat16", device="cuda", max_model_len=IN + OUT + 16, max_num_seqs=C, max_num_batched_tokens=8192,
+              enable_prefix_caching=False, gpu_memory_utilization=0.85, kv_cache_memory_bytes=_kv_bytes(cfg, C, IN + OUT + 32, 1))
+    g = torch.Generator().manual_seed(0)
+    n_req = 4 * C
+    prompts = [{"prompt_token_ids": torch.randint(0, cfg["vocab_size"], (IN,), generator=g).tolist()} for _ in range(n_req)]
+    llm.generate(prompts[:C], SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True, detokenize=False))  # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=OUT, ignore_eos=True, detokenize=False))
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    toks = sum(len(o.outputs[0].token_ids) for o in outs)
+    print(_json.dumps({"impl": "ours-offline", "metric": "output tokens/s (wall clock of LLM.generate)", "value": toks / wall, "unit": "tokens/s",
+                       "n_gpus": 1, "wall_s": wall, "output_tokens": toks,
+                       "config": {"model": CONFIGS["dense27b"][1], "workload": f"{n_req} requests, {IN} in / {OUT} out, at most {C} running"}}))
+
+
 def _kv_bytes(cfg: dict, C: int, seq: int, gpus: int) -> int:
     """KV-cache bytes per GPU for C sequences of `seq` tokens (bf16): attention layers only; MLA keeps one 576-wide latent."""
     L = cfg["num_hidden_layers"]
@@ -180,6 +205,9 @@ def main() -> None:
         return
     if args.impl == "stock-vllm":
         stock_vllm_arm(args)
+        return
+    if args.impl == "ours-offline":
+        ours_offline_arm(args)
         return
     import torch
     import torch.distributed as dist

@@ -98,3 +98,31 @@ def test_data_parallel_replicas_balance_and_match_single():
     assert client._inflight == [0, 0] and not client._owner
     assert two.reset_prefix_cache() == [True, True]
     two.shutdown()
+
+
+@pytest.mark.timeout(300)
+def test_forward_error_kills_the_engine_cleanly():
+    """A model forward that starts raising (host-side fault injection) surfaces as an error on that step and as ``EngineDeadError``
+    on every later call, in-process; through the engine-core process the client reports the dead engine instead of hanging
+    (reference test model: tests/v1/shutdown/test_forward_error.py)."""
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.engine.core import EngineDeadError
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128)
+    runner = llm.llm_engine.engine_core.core.executor.worker.runner
+    calls = {"n": 0}
+    orig = runner.model.forward
+
+    def boom(*a, **k):
+        calls["n"] += 1
+        if calls["n"] > 3:
+            raise RuntimeError("injected forward failure")
+        return orig(*a, **k)
+
+    runner.model.forward = boom
+    with pytest.raises(RuntimeError, match="injected"):
+        llm.generate([{"prompt_token_ids": [1, 2, 3]}], SamplingParams(max_tokens=20, ignore_eos=True))
+    with pytest.raises(EngineDeadError):
+        llm.llm_engine.engine_core.core.step()
+    llm.shutdown()

@@ -8,6 +8,9 @@
 //                     second small kernel.
 // K/V pages are [block][2][Hkv][block_size][D] so one (page, head) is contiguous. Tensor-core math is bf16
 // mma.sync.m16n8k16 with fp32 accumulation (softmax in the exp2 domain).
+// Options for the Gemma / GPT-OSS / Mistral families: a sliding window (a query at position i sees keys i-window+1 .. i; key tiles
+// wholly before the window are skipped), tanh soft-capping of the scaled scores, and per-head attention sinks (a learned logit that
+// joins the softmax denominator only).
 // (reference: flash-attention-v100/kernel/fused_mha_forward_paged.cu:364, flash_decode_paged.cu:667,831,1301;
 //  v1/attention/backends/flash_attn_v100.py:2216 for the math)
 #include "common.cuh"
@@ -96,10 +99,13 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   const int nrows = (tq1 - tq0) * G;
   const int kv_end = min(S, ctx0 + tq1);
   const int ntiles = (kv_end + kKeysPerTile - 1) / kKeysPerTile;
-  int tile_lo = 0, tile_hi = ntiles;
+  // sliding window: the first row of the tile sees the earliest key, ctx0 + tq0 - window + 1
+  const int wlo = p.window > 0 ? p.window : 0x3fffffff;
+  const int tile_first = p.window > 0 ? max(0, ctx0 + tq0 - p.window + 1) / kKeysPerTile : 0;
+  int tile_lo = tile_first, tile_hi = ntiles;
   if (MODE == 1 && p.splits > 1) {
-    int per = (ntiles + p.splits - 1) / p.splits;
-    tile_lo = blockIdx.z * per;
+    int per = (ntiles - tile_first + p.splits - 1) / p.splits;
+    tile_lo = tile_first + blockIdx.z * per;
     tile_hi = min(ntiles, tile_lo + per);
   }
   const int* bt = p.block_table + (size_t)r * p.bt_stride;
@@ -153,7 +159,10 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
 #pragma unroll
     for (int i = 0; i < D / 8; ++i) o[b][i][0] = o[b][i][1] = o[b][i][2] = o[b][i][3] = 0.f;
   }
-  const float sc = p.scale * 1.4426950408889634f;
+  // plain: s * scale * log2(e); soft-capped: cap * tanh(s * scale / cap) * log2(e)
+  const bool capped = p.softcap > 0.f;
+  const float sc = capped ? p.scale / p.softcap : p.scale * 1.4426950408889634f;
+  const float sc_post = p.softcap * 1.4426950408889634f;
   const int row_base = (MODE == 0) ? warp * 16 : 0;
   const int key_base = (MODE == 0) ? 0 : warp * 16;
   const int g_ = lane >> 2, tg = lane & 3;
@@ -214,7 +223,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
           for (int e = 0; e < 2; ++e) {
             int key = k0 + n * 8 + tg * 2 + e;
             float v = s[b][n][h * 2 + e] * sc;
-            v = (key <= qpos && key < kv_end) ? v : -INFINITY;
+            if (capped) v = tanhf(v) * sc_post;
+            v = (key <= qpos && key < kv_end && key + wlo > qpos) ? v : -INFINITY;
             s[b][n][h * 2 + e] = v;
             mx = fmaxf(mx, v);
           }
@@ -277,7 +287,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
       const int row = row_base + g_ + h * 8;
       if (row >= nrows) continue;
       const int tok = tq0 + row / G, gh = row % G;
-      const float inv = lrow[0][h] > 0.f ? 1.f / lrow[0][h] : 0.f;
+      const float den = lrow[0][h] + (p.sinks != nullptr ? exp2f(p.sinks[hkv * G + gh] * 1.4426950408889634f - mrow[0][h]) : 0.f);
+      const float inv = den > 0.f ? 1.f / den : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(qs + tok) * p.Hq + hkv * G + gh) * D;
 #pragma unroll
       for (int i = 0; i < D / 8; ++i)
@@ -334,7 +345,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
         wm[1] = L;
       }
     } else {
-      const float inv = L > 0.f ? 1.f / L : 0.f;
+      const float den = L + (p.sinks != nullptr ? exp2f(p.sinks[hkv * G + gh] * 1.4426950408889634f - M) : 0.f);
+      const float inv = den > 0.f ? 1.f / den : 0.f;
       __nv_bfloat16* dst = p.out + orow * D + c4;
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
       if (p.lse != nullptr && c4 == 0) p.lse[orow] = (M + log2f(L)) * 0.6931471805599453f;
@@ -362,7 +374,8 @@ __global__ void attn_combine_kernel(const AttnParams p) {
 #pragma unroll
     for (int i = 0; i < D / 32; ++i) acc[i] += src[lane + 32 * i] * f;
   }
-  const float inv = L > 0.f ? 1.f / L : 0.f;
+  const float den = L + (p.sinks != nullptr ? exp2f(p.sinks[warp % p.Hq] * 1.4426950408889634f - M) : 0.f);
+  const float inv = den > 0.f ? 1.f / den : 0.f;
 #pragma unroll
   for (int i = 0; i < D / 32; ++i) p.out[(size_t)warp * D + lane + 32 * i] = __float2bfloat16(acc[i] * inv);
   if (p.lse != nullptr && lane == 0) p.lse[warp] = (M + log2f(L)) * 0.6931471805599453f;

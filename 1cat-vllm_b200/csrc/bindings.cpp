@@ -188,7 +188,8 @@ void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Te
 
 void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out, c10::optional<torch::Tensor> lse, torch::Tensor qsl,
                      torch::Tensor seq_lens, torch::Tensor block_table, double scale, int64_t mode, int64_t num_q_tiles, int64_t splits,
-                     int64_t max_q_len, int64_t short_q_len, c10::optional<torch::Tensor> ws_o, c10::optional<torch::Tensor> ws_ml) {
+                     int64_t max_q_len, int64_t short_q_len, c10::optional<torch::Tensor> ws_o, c10::optional<torch::Tensor> ws_ml,
+                     int64_t window, double softcap, c10::optional<torch::Tensor> sinks) {
   check_bf16(q, "q");
   check_bf16(kv_cache, "kv_cache");
   check_bf16(out, "out");
@@ -222,6 +223,14 @@ void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out,
   p.splits = (int)splits;
   p.max_q_len = (int)max_q_len;
   p.short_q_len = (int)short_q_len;
+  p.window = (int)window;
+  p.softcap = (float)softcap;
+  if (sinks.has_value()) {
+    TORCH_CHECK(sinks->is_cuda() && sinks->scalar_type() == torch::kFloat32 && sinks->is_contiguous() && sinks->numel() == q.size(1),
+                "sinks must be a contiguous fp32 CUDA tensor with one entry per query head");
+    p.sinks = sinks->data_ptr<float>();
+  }
+  TORCH_CHECK(mode != 2 || (window == 0 && softcap == 0.0 && !sinks.has_value()), "window / softcap / sinks run on the mma.sync kernels");
   if (mode == 1 && splits > 1) {
     TORCH_CHECK(ws_o.has_value() && ws_ml.has_value(), "split-KV needs workspaces");
     TORCH_CHECK((size_t)ws_o->numel() >= (size_t)splits * p.T * p.Hq * p.D && (size_t)ws_ml->numel() >= (size_t)splits * p.T * p.Hq * 2,

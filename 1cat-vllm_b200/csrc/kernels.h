@@ -45,6 +45,9 @@ struct AttnParams {
   float* ws_ml;               // [splits][T][Hq][2]  running max (log2 domain) and sum
   int max_q_len;
   int short_q_len;            // requests with at most this many query tokens run in mode 1, the others in mode 0
+  int window;                 // sliding window in tokens (0 = full causal attention); mma.sync kernels only
+  float softcap;              // tanh soft-capping of the scaled scores (0 = off); mma.sync kernels only
+  const float* sinks;         // [Hq] attention-sink logits or null; mma.sync kernels only
 };
 // mode 0: rows of a query tile are spread over warps (prefill / long queries); mode 1: keys are spread over warps
 // (decode and short verify queries, with split-KV + combine).

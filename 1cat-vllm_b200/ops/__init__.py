@@ -39,11 +39,13 @@ def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_d
     return ref.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
 
 
-def paged_attention(q, kv_cache, md, scale, out=None):
-    """``md`` is the step's AttentionMetadata."""
+def paged_attention(q, kv_cache, md, scale, out=None, window=0, softcap=0.0, sinks=None):
+    """``md`` is the step's AttentionMetadata. ``window``: sliding window in tokens (0 = full causal); ``softcap``: tanh soft-capping
+    of the scaled scores (0 = off); ``sinks``: fp32 ``[Hq]`` sink logits that join the softmax denominator."""
     if q.is_cuda:
-        return ext().paged_attention(q, kv_cache, md, scale, out)
-    return ref.paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out)
+        return ext().paged_attention(q, kv_cache, md, scale, out, window=window, softcap=softcap, sinks=sinks)
+    return ref.paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out, window=window, softcap=softcap,
+                               sinks=sinks)
 
 
 def rms_norm_gated(x, z, w, eps, heads):

@@ -397,7 +397,9 @@ def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, 
     return short, tiles, splits
 
 
-def paged_attention(q, kv_cache, md, scale, out=None, lse=None):
+def paged_attention(q, kv_cache, md, scale, out=None, lse=None, window=0, softcap=0.0, sinks=None):
+    """``window`` (tokens, 0 = full), ``softcap`` (0 = off) and ``sinks`` (fp32 ``[Hq]``) select the mma.sync kernels; the tcgen05
+    prefill kernel serves plain causal attention with D = 128."""
     global _LAUNCHES
     T, Hq, D = q.shape
     Hkv = kv_cache.shape[2]
@@ -415,17 +417,17 @@ def paged_attention(q, kv_cache, md, scale, out=None, lse=None):
         ws_o, ws_ml = (w.attn_static if getattr(md, "static_ws", False) else w.attn)(splits * T * Hq * D, splits * T * Hq * 2)
     if n_short:
         _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 1, 0, splits,
-                           md.max_query_len, short, ws_o, ws_ml)
+                           md.max_query_len, short, ws_o, ws_ml, window, softcap, sinks)
         _LAUNCHES += 2 if splits > 1 else 1
     if tiles:
-        if D == 128 and q.stride(1) == D and _ATTN_PREFILL_TC:
+        if D == 128 and q.stride(1) == D and _ATTN_PREFILL_TC and not window and not softcap and sinks is None:
             # tcgen05 kernel: 128-token query tiles per (request, head)
             tiles_tc = sum(-(-x // 128) for x in md.query_lens_cpu if x > short)
             _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 2, tiles_tc, 1,
-                               md.max_query_len, short, None, None)
+                               md.max_query_len, short, None, None, 0, 0.0, None)
         else:
             _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 0, tiles, 1,
-                               md.max_query_len, short, None, None)
+                               md.max_query_len, short, None, None, window, softcap, sinks)
         _LAUNCHES += 1
     return out
 

@@ -93,11 +93,14 @@ def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_d
 
 # ----------------------------------------------------------------------------- paged attention
 def paged_attention(q, kv_cache, block_table, query_start_loc, seq_lens, scale: float,
-                    out: Optional[torch.Tensor] = None, return_lse: bool = False):
+                    out: Optional[torch.Tensor] = None, return_lse: bool = False, window: int = 0, softcap: float = 0.0,
+                    sinks: Optional[torch.Tensor] = None):
     """Causal varlen attention over a paged cache. Request r owns query rows
     ``query_start_loc[r]:query_start_loc[r+1]`` which are the LAST rows of its ``seq_lens[r]``-token context
     (so decode, chunked prefill with prefix and multi-token verify are the same call).
-    q ``[T, Hq, D]``, kv_cache ``[blocks, 2, Hkv, bs, D]``. fp32 math."""
+    q ``[T, Hq, D]``, kv_cache ``[blocks, 2, Hkv, bs, D]``. fp32 math. ``window`` > 0: query i sees keys i-window+1..i
+    (reference: Gemma2/3, GPT-OSS, Mistral sliding attention); ``softcap`` > 0: scores become cap·tanh(score/cap) (Gemma2);
+    ``sinks`` ``[Hq]``: one extra logit per head that takes probability mass but contributes no value (GPT-OSS)."""
     T, Hq, D = q.shape
     Hkv, bs = kv_cache.shape[2], kv_cache.shape[3]
     g = Hq // Hkv
@@ -118,8 +121,14 @@ def paged_attention(q, kv_cache, block_table, query_start_loc, seq_lens, scale: 
         s = torch.einsum("hgqd,hkd->hgqk", qq, kk) * scale
         qpos = torch.arange(S - nq, S, device=q.device).view(1, 1, nq, 1)
         kpos = torch.arange(S, device=q.device).view(1, 1, 1, S)
+        if softcap > 0:
+            s = torch.tanh(s / softcap) * softcap
         s = s.masked_fill(kpos > qpos, -float("inf"))
+        if window > 0:
+            s = s.masked_fill(kpos <= qpos - window, -float("inf"))
         l = torch.logsumexp(s, dim=-1)
+        if sinks is not None:
+            l = torch.logaddexp(l, sinks.float().view(Hkv, g, 1).expand_as(l))
         p = torch.exp(s - l.unsqueeze(-1))
         oo = torch.einsum("hgqk,hkd->hgqd", p, vv).reshape(Hq, nq, D).permute(1, 0, 2)
         o[q0:q1] = oo.to(o.dtype)

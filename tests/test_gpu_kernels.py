@@ -375,6 +375,31 @@ def test_prefill_attention_tcgen05_matches_mma_path_and_lse(monkeypatch):
     assert (lse_tc - lse_mma).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("name,qlens,ctxs,Hq,Hkv,D,window,softcap,use_sinks", [
+    ("window-decode", [1] * 6, [0, 100, 127, 128, 1000, 4000], 16, 4, 128, 128, 0.0, False),
+    ("window-prefill", [300, 70, 513, 1], [0, 200, 64, 700], 16, 4, 128, 64, 0.0, False),
+    ("window-verify-d256", [4] * 3, [10, 600, 2000], 8, 2, 256, 512, 0.0, False),
+    ("softcap", [1, 1, 200, 3], [500, 20, 100, 77], 16, 4, 256, 0, 50.0, False),
+    ("sinks", [1, 1, 300, 1, 2], [5000, 20, 100, 0, 77], 64, 8, 128, 0, 0.0, True),
+    ("window+sinks", [1, 1, 300, 1], [5000, 130, 100, 0], 64, 8, 128, 128, 0.0, True),
+])
+def test_paged_attention_window_softcap_sinks(name, qlens, ctxs, Hq, Hkv, D, window, softcap, use_sinks):
+    """Sliding window, tanh soft-capping and attention sinks (Gemma / GPT-OSS / Mistral families) against the fp32 oracle, over the
+    decode (split-KV + combine), verify and prefill forms of the kernel."""
+    q, cache, md = _attn_case(qlens, ctxs, Hq, Hkv, D, seed=7)
+    sinks = torch.randn(Hq, device="cuda") * 2.0 if use_sinks else None
+    scale = D ** -0.5 * 4.0   # larger scores so that capping and sinks move the result
+    out = K().paged_attention(q, cache, md, scale, window=window, softcap=softcap, sinks=sinks)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    e = ref.paged_attention(q.cpu(), cache.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), scale,
+                            window=window, softcap=softcap, sinks=None if sinks is None else sinks.cpu())
+    _close(out, e, 2e-2, 1e-2, name)
+    if window:
+        full = ref.paged_attention(q.cpu(), cache.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), scale)
+        assert (full.float() - e.float()).abs().max() > 1e-2   # the window changes the answer in these cases
+
+
 def test_paged_attention_forced_splits():
     q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
     from onecat_vllm.ops.cuda import plan_attention

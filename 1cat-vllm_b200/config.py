@@ -93,6 +93,20 @@ class ModelConfig:
     qk_norm: bool = False  # per-head RMSNorm on q and k (Qwen3)
     gemma_norm: bool = False  # weight applied as (1 + w) (Qwen3-Next)
     attn_output_gate: bool = False  # gated attention: o * sigmoid(gate)
+    # Gemma / GLM / Granite family switches
+    hidden_act: str = "silu"  # silu | gelu_tanh (GeGLU)
+    embed_scale: float = 1.0  # token embeddings are multiplied by this (Gemma: sqrt(hidden); Granite: embedding_multiplier)
+    sandwich_norm: bool = False  # each sub-block's output is normalised before it joins the residual (Gemma2/3, GLM-4)
+    attn_scale: Optional[float] = None  # softmax scale when it is not head_dim ** -0.5
+    attn_softcap: float = 0.0  # tanh soft-capping of attention scores (Gemma2)
+    final_softcap: float = 0.0  # tanh soft-capping of the output logits (Gemma2)
+    sliding_window: int = 0  # window of the layers listed in sliding_layers
+    sliding_layers: tuple = ()
+    rope_local_theta: Optional[float] = None  # rotary base of the sliding layers when it differs (Gemma3)
+    rope_scaling: Optional[dict] = None  # {"rope_type": linear | llama3 | yarn | dynamic, ...} of the full-attention layers
+    rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
+    residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
+    logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
     # hybrid (Gated-DeltaNet)
     layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention"
     linear_num_key_heads: int = 16
@@ -155,6 +169,10 @@ class ModelConfig:
 
     def layer_type(self, i: int) -> str:
         return self.layer_types[i] if self.layer_types else "full_attention"
+
+    def layer_window(self, i: int) -> int:
+        """Sliding window of layer ``i`` in tokens, 0 for full attention."""
+        return self.sliding_window if i in self.sliding_layers else 0
 
     def is_moe_layer(self, i: int) -> bool:
         return self.is_moe and i >= self.first_k_dense_replace and i not in self.dense_layers
@@ -234,6 +252,40 @@ class ModelConfig:
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
+        rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+        if isinstance(rp.get("full_attention"), dict):  # per-layer-type rotary parameters (Gemma3)
+            kw["rope_theta"] = rp["full_attention"].get("rope_theta", kw["rope_theta"])
+            kw["rope_local_theta"] = (rp.get("sliding_attention") or {}).get("rope_theta")
+            rp = rp["full_attention"]
+        if (rp.get("rope_type") or rp.get("type") or "default") != "default":
+            kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
+            kw["rope_scaling"].setdefault("rope_type", rp.get("type"))
+        lt = hf.get("layer_types")
+        if lt and any(t == "sliding_attention" for t in lt) and hf.get("sliding_window"):
+            kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(i for i, t in enumerate(lt) if t == "sliding_attention"))
+            if not kw.get("layer_types"):
+                kw["layer_types"] = None
+        elif hf.get("sliding_window") and hf.get("use_sliding_window", "mistral" in a):
+            kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(range(kw["num_hidden_layers"])))
+        act = hf.get("hidden_activation") or hf.get("hidden_act") or "silu"
+        if act in ("gelu_pytorch_tanh", "gelu_tanh", "gelu"):
+            kw["hidden_act"] = "gelu_tanh"
+        if "gemma" in a:
+            kw.update(gemma_norm=True, embed_scale=float(hidden) ** 0.5, tie_word_embeddings=hf.get("tie_word_embeddings", True))
+            if "gemma2" in a or "gemma3" in a:
+                kw.update(sandwich_norm=True, attn_scale=float(hf.get("query_pre_attn_scalar", kw["head_dim"])) ** -0.5,
+                          attn_softcap=float(hf.get("attn_logit_softcapping") or 0.0), final_softcap=float(hf.get("final_logit_softcapping") or 0.0))
+            if "gemma3" in a:
+                kw["qk_norm"] = True
+        if a.startswith("glm"):
+            kw.update(rope_interleaved="moe" not in a, sandwich_norm=a.startswith("glm4for"), qk_norm=bool(hf.get("use_qk_norm", False)))
+            if "moe" in a:
+                kw.update(shared_expert_intermediate_size=hf.get("n_shared_experts", 1) * hf.get("moe_intermediate_size", 1408),
+                          shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),
+                          routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 1))
+        if "granite" in a:
+            kw.update(embed_scale=float(hf.get("embedding_multiplier", 1.0)), residual_multiplier=float(hf.get("residual_multiplier", 1.0)),
+                      attn_scale=float(hf.get("attention_multiplier", kw["head_dim"] ** -0.5)), logit_scale=1.0 / float(hf.get("logits_scaling", 1.0)))
         kw.update(over)
         return cls(**kw)
 

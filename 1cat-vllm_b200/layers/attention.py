@@ -31,8 +31,12 @@ class Attention(nn.Module):
             self.q_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
             self.k_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
         self.rotary_dim = cfg.rotary_dim
-        self.rope = get_rope(cfg.rotary_dim, cfg.max_model_len, cfg.rope_theta, device)
-        self.scale = cfg.head_dim ** -0.5
+        # sliding-window layers may rotate with their own base and without the context-extension rule (Gemma3)
+        self.window, self.softcap = cfg.layer_window(layer_idx), cfg.attn_softcap
+        local = bool(self.window) and cfg.rope_local_theta is not None
+        self.rope = get_rope(cfg.rotary_dim, cfg.max_model_len, cfg.rope_local_theta if local else cfg.rope_theta, device,
+                             None if local else cfg.rope_scaling)
+        self.scale = cfg.attn_scale if cfg.attn_scale is not None else cfg.head_dim ** -0.5
         self.layer_idx = layer_idx
 
     def forward(self, x: torch.Tensor, md, kv_cache: torch.Tensor) -> torch.Tensor:
@@ -49,7 +53,7 @@ class Attention(nn.Module):
         v = qkv[:, qw + Hkv * D:].view(T, Hkv, D)
         ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
                            self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
-        o = ops.paged_attention(q, kv_cache, md, self.scale)
+        o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap)
         if gate is not None:
             o = o * torch.sigmoid(gate.float()).to(o.dtype)
         return self.o_proj(o.reshape(T, Hq * D))

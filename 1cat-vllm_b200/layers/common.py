@@ -30,18 +30,18 @@ class RMSNorm(nn.Module):
 class RotaryEmbedding:
     """NeoX-style rotary with a precomputed fp32 cos|sin table."""
 
-    def __init__(self, rotary_dim: int, max_pos: int, theta: float, device):
+    def __init__(self, rotary_dim: int, max_pos: int, theta: float, device, scaling: Optional[dict] = None):
         self.rotary_dim = rotary_dim
-        self.cos_sin = ref.build_cos_sin_cache(rotary_dim, max_pos, theta, device)
+        self.cos_sin = ref.build_cos_sin_cache(rotary_dim, max_pos, theta, device, scaling)
 
 
 _ROPE_CACHE: dict = {}
 
 
-def get_rope(rotary_dim: int, max_pos: int, theta: float, device) -> RotaryEmbedding:
-    key = (rotary_dim, max_pos, theta, str(device))
+def get_rope(rotary_dim: int, max_pos: int, theta: float, device, scaling: Optional[dict] = None) -> RotaryEmbedding:
+    key = (rotary_dim, max_pos, theta, str(device), repr(sorted(scaling.items())) if scaling else None)
     if key not in _ROPE_CACHE:
-        _ROPE_CACHE[key] = RotaryEmbedding(rotary_dim, max_pos, theta, device)
+        _ROPE_CACHE[key] = RotaryEmbedding(rotary_dim, max_pos, theta, device, scaling)
     return _ROPE_CACHE[key]
 
 

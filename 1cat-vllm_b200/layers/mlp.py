@@ -8,10 +8,12 @@ from onecat_vllm.layers.linear import MergedColumnParallelLinear, RowParallelLin
 
 
 class MLP(nn.Module):
-    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True, fuse_act: bool = True):
-        """``fuse_act=False`` (LoRA-enabled models) keeps gate|up as a plain GEMM so adapter deltas can be added before SiLU·mul."""
+    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True, fuse_act: bool = True, act: str = "silu"):
+        """``fuse_act=False`` (LoRA-enabled models) keeps gate|up as a plain GEMM so adapter deltas can be added before SiLU·mul.
+        ``act="gelu_tanh"`` (Gemma GeGLU) always takes the unfused form: the GEMM epilogue implements SiLU·mul only."""
         super().__init__()
-        self.fuse_act = fuse_act
+        fuse_act = fuse_act and act == "silu"
+        self.fuse_act, self.act = fuse_act, act
         self.gate_up_proj = MergedColumnParallelLinear(hidden, [inter, inter], quant=quant, prefix=prefix + ".gate_up_proj",
                                                        dtype=dtype, fuse_silu_mul=fuse_act)
         self.down_proj = RowParallelLinear(inter, hidden, quant=quant, prefix=prefix + ".down_proj", dtype=dtype)
@@ -20,5 +22,5 @@ class MLP(nn.Module):
         h = self.gate_up_proj(x)
         if not self.fuse_act:
             from onecat_vllm import ops
-            h = ops.silu_and_mul(h)
+            h = ops.silu_and_mul(h) if self.act == "silu" else ops.gelu_tanh_and_mul(h)
         return self.down_proj(h)

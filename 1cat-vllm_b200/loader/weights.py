@@ -34,6 +34,20 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 _RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.shared_experts.", ".mlp.shared_expert."))
+# GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
+_GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
+               "post_mlp_layernorm": "post_feedforward_layernorm"}
+_GLM4_NORM_RE = re.compile(r"\.(post_attention_layernorm|post_self_attn_layernorm|post_mlp_layernorm)\.")
+
+
+def _half_split_rows(w: torch.Tensor, head_dim: int, rotary_dim: int) -> torch.Tensor:
+    """Reorder each head's rotary rows from the adjacent-pair layout (0,1),(2,3),… to the half-split layout used by the rope kernel;
+    applied to q and k alike, so q·k is unchanged."""
+    perm = torch.cat([torch.arange(0, rotary_dim, 2), torch.arange(1, rotary_dim, 2), torch.arange(rotary_dim, head_dim)])
+    heads = w.shape[0] // head_dim
+    return w.reshape(heads, head_dim, -1)[:, perm].reshape(w.shape)
+
+
 _EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv|weight_scale)$")
 
 
@@ -42,6 +56,9 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
     mods = dict(model.named_modules())
     params = dict(model.named_parameters())
     stacked = getattr(model, "stacked_params_mapping", [])
+    cfg = getattr(model, "cfg", None)
+    glm4_norms = cfg is not None and cfg.sandwich_norm and cfg.architecture.startswith("Glm4")
+    interleaved = cfg is not None and cfg.rope_interleaved
     loaded = set()
     for name, w in weights:
         if name.startswith("language_model."):
@@ -53,6 +70,10 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
         for theirs, ours in _RENAMES:
             if theirs in name:
                 name = name.replace(theirs, ours)
+        if glm4_norms:
+            name = _GLM4_NORM_RE.sub(lambda m: "." + _GLM4_NORMS[m.group(1)] + ".", name)
+        if interleaved and (".q_proj." in name or ".k_proj." in name) and "self_attn" in name:
+            w = _half_split_rows(w, cfg.head_dim, cfg.rotary_dim)
         if ".block_sparse_moe." in name:  # Mixtral naming: block_sparse_moe.{gate, experts.N.w1|w3|w2}
             name = name.replace(".block_sparse_moe.", ".mlp.")
             for theirs, ours in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):

@@ -6,6 +6,8 @@ from onecat_vllm.config import ModelConfig
 _REGISTRY = {
     "LlamaForCausalLM": "dense", "MistralForCausalLM": "dense", "Qwen2ForCausalLM": "dense", "Qwen3ForCausalLM": "dense",
     "Phi3ForCausalLM": "dense", "SeedOssForCausalLM": "dense", "InternLM3ForCausalLM": "dense",
+    "GemmaForCausalLM": "dense", "Gemma2ForCausalLM": "dense", "Gemma3ForCausalLM": "dense", "GlmForCausalLM": "dense",
+    "Glm4ForCausalLM": "dense", "GraniteForCausalLM": "dense", "Glm4MoeForCausalLM": "moe",
     "Qwen3MoeForCausalLM": "moe", "Qwen2MoeForCausalLM": "moe", "MixtralForCausalLM": "moe",
     "Qwen3NextForCausalLM": "hybrid", "Qwen3_5ForCausalLM": "hybrid", "Qwen3_5ForConditionalGeneration": "hybrid",
     "Qwen3_5MoeForCausalLM": "hybrid", "Qwen3_5MoeForConditionalGeneration": "hybrid",

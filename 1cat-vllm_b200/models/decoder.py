@@ -45,9 +45,15 @@ class DecoderLayer(nn.Module):
         if cfg.is_moe_layer(idx):
             self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
         else:
-            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora)
+            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
+                           act=cfg.hidden_act)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        if cfg.sandwich_norm:
+            # Gemma2/3 and GLM-4: post_attention_layernorm normalises the mixer's output, pre_feedforward_layernorm is the pre-norm of
+            # the feed-forward, post_feedforward_layernorm normalises its output (GLM-4's names are mapped to these at load)
+            self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
 
     def mixer(self, x, md, cache):
         if self.kind == "linear_attention":
@@ -80,24 +86,54 @@ class DecoderModel(nn.Module):
         stage. A stage that is not the last returns that pair for its successor instead of the final hidden states
         (reference: models/llama.py ``IntermediateTensors`` handling)."""
         layers = self.layers
+        cfg = self.cfg
         if intermediate is None:
-            h = self.embed_tokens(input_ids) if inputs_embeds is None else inputs_embeds
+            if inputs_embeds is None:
+                h = self.embed_tokens(input_ids)
+                if cfg.embed_scale != 1.0:
+                    h = h * torch.tensor(cfg.embed_scale, dtype=h.dtype)  # the factor is rounded to the model dtype first, as in the checkpoint's code
+            else:
+                h = inputs_embeds
             x, residual = layers[self.start].input_layernorm(h, None)
             residual = h
         else:
             x, residual = layers[self.start].input_layernorm(intermediate[0], intermediate[1])
+        plain = not cfg.sandwich_norm and cfg.residual_multiplier == 1.0
         for li, i in enumerate(range(self.start, self.end)):
             layer = layers[i]
             part = layer.mixer(x, md, caches[li])
-            x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
+            if plain:
+                x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
+            else:
+                x, residual = self._join(part, residual, layer.post_attention_layernorm if cfg.sandwich_norm else None,
+                                         layer.pre_feedforward_layernorm if cfg.sandwich_norm else layer.post_attention_layernorm)
             part = layer.mlp(x)
-            if i + 1 == self.end and not self.last_stage:
-                return reduce_only(part), residual
-            nxt = layers[i + 1].input_layernorm if i + 1 < self.end else self.norm
-            x, residual = reduce_add_norm(part, residual, nxt)
+            last_local = i + 1 == self.end and not self.last_stage
+            nxt = None if last_local else (layers[i + 1].input_layernorm if i + 1 < self.end else self.norm)
+            if plain:
+                if last_local:
+                    return reduce_only(part), residual
+                x, residual = reduce_add_norm(part, residual, nxt)
+            else:
+                out = self._join(part, residual, layer.post_feedforward_layernorm if cfg.sandwich_norm else None, nxt)
+                if last_local:
+                    return out
+                x, residual = out
         if return_prenorm:
             return x, residual
         return x
+
+    def _join(self, part, residual, post_norm, next_norm):
+        """Sub-block output → residual for the architectures that do more than add: reduce over TP, normalise the output (sandwich
+        norms) or scale it (Granite), then add + next pre-norm. With ``next_norm`` None returns (output, residual) for the next stage."""
+        p = reduce_only(part)
+        if post_norm is not None:
+            p = post_norm(p, None)[0]
+        if self.cfg.residual_multiplier != 1.0:
+            p = p * self.cfg.residual_multiplier
+        if next_norm is None:
+            return p, residual
+        return next_norm(p, residual)
 
 
 class CausalLM(nn.Module):
@@ -127,8 +163,15 @@ class CausalLM(nn.Module):
         head = self.lm_head
         if head is None:
             e = self.model.embed_tokens
-            return ParallelLMHead.compute_logits(e, hidden)
-        return head.compute_logits(hidden)
+            logits = ParallelLMHead.compute_logits(e, hidden)
+        else:
+            logits = head.compute_logits(hidden)
+        c = self.cfg
+        if c.logit_scale != 1.0:
+            logits = logits * c.logit_scale
+        if c.final_softcap > 0:  # Gemma2: cap * tanh(logits / cap)
+            logits = torch.tanh(logits.float() / c.final_softcap).mul_(c.final_softcap).to(logits.dtype)
+        return logits
 
 
 class MTPHead(nn.Module):

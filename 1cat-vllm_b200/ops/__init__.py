@@ -32,6 +32,11 @@ def silu_and_mul(x):
     return ref.silu_and_mul(x)
 
 
+def gelu_tanh_and_mul(x):
+    """GeGLU activation; an elementwise PyTorch expression on either device (Gemma-family models only)."""
+    return ref.gelu_tanh_and_mul(x)
+
+
 def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w=None, k_norm_w=None,
                    eps=1e-6, gemma=False):
     if q.is_cuda:

@@ -45,11 +45,13 @@ class _Workspace:
         self.attn_ml = None
 
     def attn_static(self, n_o: int, n_ml: int):
-        """Buffers whose addresses are baked into CUDA graphs: allocated once, never grown."""
-        if getattr(self, "s_o", None) is None:
+        """Buffers whose addresses are baked into CUDA graphs: sized once per engine for its largest graph."""
+        if getattr(self, "s_o", None) is None or self.s_o.numel() < n_o or self.s_ml.numel() < n_ml:
+            # a later engine in the same process may need more; graphs captured earlier keep their (retired) buffers alive
+            if getattr(self, "s_o", None) is not None:
+                self._retired = getattr(self, "_retired", []) + [(self.s_o, self.s_ml)]
             self.s_o = torch.empty(n_o, dtype=torch.float32, device=self.device)
             self.s_ml = torch.empty(n_ml, dtype=torch.float32, device=self.device)
-        assert self.s_o.numel() >= n_o and self.s_ml.numel() >= n_ml, "static attention workspace is too small"
         return self.s_o, self.s_ml
 
     def attn(self, n_o: int, n_ml: int):

@@ -40,17 +40,70 @@ def rms_norm_gated(x: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float
     return (y * F.silu(z.float())).to(x.dtype)
 
 
+def gelu_tanh_and_mul(x: torch.Tensor) -> torch.Tensor:
+    """GeGLU: gelu_tanh(gate) * up (reference: layers/activation.py ``GeluAndMul``)."""
+    d = x.shape[-1] // 2
+    return (F.gelu(x[..., :d].float(), approximate="tanh") * x[..., d:].float()).to(x.dtype)
+
+
 def silu_and_mul(x: torch.Tensor) -> torch.Tensor:
     d = x.shape[-1] // 2
     return (F.silu(x[..., :d].float()) * x[..., d:].float()).to(x.dtype)
 
 
 # ----------------------------------------------------------------------------- rope + kv insert
-def build_cos_sin_cache(rotary_dim: int, max_pos: int, theta: float, device=None) -> torch.Tensor:
+def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    return 1.0 if factor <= 1 else 0.1 * mscale * math.log(factor) + 1.0
+
+
+def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], device=None):
+    """Rotary inverse frequencies under a context-extension rule, and the factor that multiplies cos / sin
+    (reference: layers/rotary_embedding/ — linear, llama3, yarn and DeepSeek-yarn variants; the formulas are the published ones)."""
     inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=device) / rotary_dim))
+    kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
+    if kind == "default":
+        return inv, 1.0
+    f = float(scaling.get("factor", 1.0))
+    if kind == "linear":
+        return inv / f, 1.0
+    orig = float(scaling.get("original_max_position_embeddings", 8192))
+    if kind == "llama3":
+        lo_f, hi_f = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        wavelen = 2 * math.pi / inv
+        smooth = ((orig / wavelen - lo_f) / (hi_f - lo_f)).clamp(0, 1)
+        out = torch.where(wavelen > orig / lo_f, inv / f, inv)
+        mid = (wavelen <= orig / lo_f) & (wavelen >= orig / hi_f)
+        return torch.where(mid, (1 - smooth) * inv / f + smooth * inv, out), 1.0
+    if kind in ("yarn", "deepseek_yarn"):
+        bf, bs = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+        def corr(n_rot):
+            return rotary_dim * math.log(orig / (n_rot * 2 * math.pi)) / (2 * math.log(theta))
+
+        lo, hi = corr(bf), corr(bs)
+        if scaling.get("truncate", True):
+            lo, hi = math.floor(lo), math.ceil(hi)
+        lo, hi = max(lo, 0), min(hi, rotary_dim - 1)
+        if lo == hi:
+            hi += 0.001
+        ramp = ((torch.arange(rotary_dim // 2, dtype=torch.float32, device=device) - lo) / (hi - lo)).clamp(0, 1)
+        extrap = 1.0 - ramp
+        out = inv / f * (1 - extrap) + inv * extrap
+        if scaling.get("attention_factor") is not None:
+            att = float(scaling["attention_factor"])
+        elif scaling.get("mscale") and scaling.get("mscale_all_dim"):
+            att = yarn_mscale(f, float(scaling["mscale"])) / yarn_mscale(f, float(scaling["mscale_all_dim"]))
+        else:
+            att = yarn_mscale(f)
+        return out, att
+    raise ValueError(f"rope scaling type {kind!r} is not supported")
+
+
+def build_cos_sin_cache(rotary_dim: int, max_pos: int, theta: float, device=None, scaling: Optional[dict] = None) -> torch.Tensor:
+    inv, att = scaled_inv_freq(rotary_dim, theta, scaling, device)
     t = torch.arange(max_pos, dtype=torch.float32, device=device)
     fr = torch.outer(t, inv)
-    return torch.cat([fr.cos(), fr.sin()], dim=-1)  # [max_pos, rotary_dim] fp32
+    return torch.cat([fr.cos() * att, fr.sin() * att], dim=-1)  # [max_pos, rotary_dim] fp32
 
 
 def _rope_neox(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rotary_dim: int) -> torch.Tensor:

@@ -12,21 +12,29 @@ CFG = dict(architectures=["Qwen3ForCausalLM"], hidden_size=512, intermediate_siz
            tie_word_embeddings=False)
 
 
-def _make_checkpoint(tmp_path):
+# Gemma2-style: sandwich norms, GeGLU, scaled embeddings, sliding window on alternate layers, score and logit soft-capping, D = 256
+CFG_GEMMA2 = dict(architectures=["Gemma2ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=256, rms_norm_eps=1e-6, rope_theta=1e4, vocab_size=2048, max_position_embeddings=2048,
+                  tie_word_embeddings=True, hidden_activation="gelu_pytorch_tanh", query_pre_attn_scalar=256, sliding_window=64,
+                  layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+                  attn_logit_softcapping=50.0, final_logit_softcapping=30.0)
+
+
+def _make_checkpoint(tmp_path, cfg=CFG):
     from onecat_vllm.config import ModelConfig
     from onecat_vllm.loader.weights import dummy_init, save_pretrained
     from onecat_vllm.models import build_model
-    mc = ModelConfig.from_hf_dict(CFG, dtype=torch.bfloat16)
+    mc = ModelConfig.from_hf_dict(cfg, dtype=torch.bfloat16)
     m = build_model(mc, "cpu")
     dummy_init(m, 0, std=0.05)
-    save_pretrained(m, CFG, str(tmp_path))
+    save_pretrained(m, cfg, str(tmp_path))
     return str(tmp_path)
 
 
-@pytest.mark.parametrize("eager", [True, False])
-def test_engine_gpu_matches_cpu(tmp_path, eager):
+@pytest.mark.parametrize("eager,cfg", [(True, CFG), (False, CFG), (False, CFG_GEMMA2)], ids=["eager", "graphs", "gemma2-graphs"])
+def test_engine_gpu_matches_cpu(tmp_path, eager, cfg):
     from onecat_vllm import LLM, SamplingParams
-    path = _make_checkpoint(tmp_path)
+    path = _make_checkpoint(tmp_path, cfg)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in (5, 40, 130, 17, 64, 300)]
     sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, logprobs=0)

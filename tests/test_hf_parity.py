@@ -41,6 +41,25 @@ CASES = {
                                  linear_value_head_dim=16, linear_conv_kernel_dim=4, num_experts=4, num_experts_per_tok=2,
                                  moe_intermediate_size=64, shared_expert_intermediate_size=64, norm_topk_prob=True, decoder_sparse_step=1,
                                  mlp_only_layers=[]),
+    "GemmaForCausalLM": dict(BASE, model_type="gemma", head_dim=32, rope_theta=10000.0, tie_word_embeddings=True),
+    "Gemma2ForCausalLM": dict(BASE, model_type="gemma2", head_dim=32, rope_theta=10000.0, tie_word_embeddings=True, num_hidden_layers=4,
+                              sliding_window=16, query_pre_attn_scalar=24, attn_logit_softcapping=5.0, final_logit_softcapping=8.0),
+    "Gemma3ForCausalLM": dict(BASE, model_type="gemma3_text", head_dim=32, tie_word_embeddings=True, num_hidden_layers=4, sliding_window=16,
+                              query_pre_attn_scalar=24, layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"],
+                              rope_parameters={"sliding_attention": {"rope_type": "default", "rope_theta": 10000.0},
+                                               "full_attention": {"rope_type": "linear", "factor": 4.0, "rope_theta": 1e6}}),
+    "GlmForCausalLM": dict(BASE, model_type="glm", head_dim=16, rope_theta=10000.0, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0),
+    "Glm4ForCausalLM": dict(BASE, model_type="glm4", head_dim=16, rope_theta=10000.0, partial_rotary_factor=0.5, attention_bias=True, pad_token_id=0),
+    "Glm4MoeForCausalLM": dict(BASE, model_type="glm4_moe", head_dim=16, rope_theta=10000.0, partial_rotary_factor=0.5, n_routed_experts=8,
+                               n_shared_experts=1, num_experts_per_tok=2, moe_intermediate_size=48, n_group=1, topk_group=1,
+                               routed_scaling_factor=1.5, norm_topk_prob=True, first_k_dense_replace=1, use_qk_norm=True, pad_token_id=0),
+    "GraniteForCausalLM": dict(BASE, model_type="granite", rope_theta=10000.0, embedding_multiplier=6.0, residual_multiplier=0.3,
+                               attention_multiplier=0.2, logits_scaling=4.0),
+    "LlamaForCausalLM+llama3-rope": dict(BASE, model_type="llama", rope_parameters={"rope_type": "llama3", "rope_theta": 10000.0, "factor": 8.0,
+                                         "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32}),
+    "LlamaForCausalLM+yarn-rope": dict(BASE, model_type="llama", rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0,
+                                       "original_max_position_embeddings": 32}),
+    "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 
 
@@ -49,6 +68,7 @@ CASES = {
 def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
     from onecat_vllm import LLM, SamplingParams
     cfg_cls = transformers.AutoConfig.for_model(CASES[arch]["model_type"], **{k: v for k, v in CASES[arch].items() if k != "model_type"})
+    case, arch = arch, arch.split("+")[0]
     cfg_cls.architectures = [arch]
     torch.manual_seed(0)
     hf = getattr(transformers, arch)(cfg_cls).eval().float()
@@ -56,6 +76,7 @@ def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
         if p.dim() >= 2:
             p.data.mul_(3.0)
     hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    hf.generation_config.eos_token_id = None   # the engine runs with ignore_eos
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(1, 300, (n,), generator=g).tolist() for n in (5, 23, 40)]
     llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)

@@ -107,6 +107,7 @@ class ModelConfig:
     rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
     residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
+    num_labels: int = 0  # > 0: a *ForSequenceClassification checkpoint (a ``score`` head on the pooled state instead of an LM head)
     # hybrid (Gated-DeltaNet)
     layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention"
     linear_num_key_heads: int = 16
@@ -286,6 +287,8 @@ class ModelConfig:
         if "granite" in a:
             kw.update(embed_scale=float(hf.get("embedding_multiplier", 1.0)), residual_multiplier=float(hf.get("residual_multiplier", 1.0)),
                       attn_scale=float(hf.get("attention_multiplier", kw["head_dim"] ** -0.5)), logit_scale=1.0 / float(hf.get("logits_scaling", 1.0)))
+        if arch.endswith("ForSequenceClassification"):
+            kw["num_labels"] = int(hf.get("num_labels") or len(hf.get("id2label") or {}) or 2)
         kw.update(over)
         return cls(**kw)
 

@@ -57,6 +57,8 @@ class InputProcessor:
             raise ValueError(f"token id {bad[0]} is outside the vocabulary (size {mc.vocab_size})")
         pooling = None
         if isinstance(params, PoolingParams):
+            if params.task == "classify" and mc.num_labels <= 0:
+                raise ValueError("classify needs a *ForSequenceClassification checkpoint (this model has no score head)")
             # an embedding request runs its prompt, "generates" one token that nobody reads, and returns the pooled state
             pooling, params = params, SamplingParams(temperature=0.0, max_tokens=1, detokenize=False,
                                                      output_kind=RequestOutputKind.FINAL_ONLY)

@@ -108,6 +108,10 @@ class LLM:
     def embed(self, prompts, pooling_params: Optional[PoolingParams] = None, use_tqdm: bool = False) -> list[PoolingRequestOutput]:
         return self.encode(prompts, pooling_params or PoolingParams(task="embed", normalize=True), use_tqdm)
 
+    def classify(self, prompts, pooling_params: Optional[PoolingParams] = None, use_tqdm: bool = False) -> list[PoolingRequestOutput]:
+        """Class probabilities from a sequence-classification checkpoint (reference: entrypoints/llm.py ``LLM.classify``)."""
+        return self.encode(prompts, pooling_params or PoolingParams(task="classify", normalize=False), use_tqdm)
+
     def score(self, text_1: Union[str, Sequence[str]], text_2: Union[str, Sequence[str]], use_tqdm: bool = False) -> list[float]:
         """Cosine similarity of the two texts' embeddings (1:N or N:N)."""
         a = [text_1] if isinstance(text_1, str) else list(text_1)

@@ -255,6 +255,39 @@ def build_app(state: ServingState) -> FastAPI:
         return {"id": new_id("pool"), "object": "list", "created": now(), "model": state.model_name,
                 "data": [{"index": i, "object": "pooling", "data": o.outputs.data} for i, o in enumerate(outs)]}
 
+    @app.post("/classify")
+    async def classify(body: dict):
+        from onecat_vllm.sampling_params import PoolingParams
+        try:
+            pp = PoolingParams(task="classify", normalize=False, use_activation=bool(body.get("use_activation", True)))
+            outs = await _pool_many(_as_prompts(body["input"]), pp, "classify")
+        except (ValueError, KeyError) as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        data = [{"index": i, "label": str(max(range(len(o.outputs.data)), key=o.outputs.data.__getitem__)), "probs": o.outputs.data,
+                 "num_classes": len(o.outputs.data)} for i, o in enumerate(outs)]
+        n = sum(len(o.prompt_token_ids) for o in outs)
+        return {"id": new_id("classify"), "object": "list", "created": now(), "model": state.model_name, "data": data,
+                "usage": {"prompt_tokens": n, "total_tokens": n}}
+
+    @app.post("/rerank")
+    @app.post("/v1/rerank")
+    @app.post("/v2/rerank")
+    async def rerank(body: dict):
+        """Documents ordered by similarity to the query (reference: entrypoints/pooling/score/ rerank routes, Jina / Cohere shape)."""
+        from onecat_vllm.sampling_params import PoolingParams
+        try:
+            docs = [d if isinstance(d, str) else d.get("text", "") for d in body["documents"]]
+            outs = await _pool_many([body["query"]] + docs, PoolingParams(task="embed", normalize=True), "rerank")
+        except (ValueError, KeyError) as e:
+            return JSONResponse(error_body(str(e)), status_code=400)
+        qv = outs[0].outputs.data
+        res = [{"index": i, "document": {"text": d}, "relevance_score": sum(x * y for x, y in zip(qv, o.outputs.data))}
+               for i, (d, o) in enumerate(zip(docs, outs[1:]))]
+        res.sort(key=lambda r: -r["relevance_score"])
+        top_n = body.get("top_n") or len(res)
+        n = sum(len(o.prompt_token_ids) for o in outs)
+        return {"id": new_id("rerank"), "model": state.model_name, "usage": {"total_tokens": n}, "results": res[:top_n]}
+
     @app.post("/score")
     @app.post("/v1/score")
     async def score(body: dict):

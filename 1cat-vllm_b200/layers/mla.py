@@ -41,8 +41,14 @@ class MLAAttention(nn.Module):
         self.kv_a_layernorm = RMSNorm(self.lora, cfg.rms_norm_eps, dtype=dt)
         self.kv_b_proj = ColumnParallelLinear(self.lora, cfg.num_attention_heads * (self.nope + self.vd), quant=q, prefix=prefix + ".kv_b_proj", dtype=dt)
         self.o_proj = RowParallelLinear(cfg.num_attention_heads * self.vd, cfg.hidden_size, quant=q, prefix=prefix + ".o_proj", dtype=dt)
-        self.rope = get_rope(self.rope_d, cfg.max_model_len, cfg.rope_theta, device)
+        self.rope = get_rope(self.rope_d, cfg.max_model_len, cfg.rope_theta, device, cfg.rope_scaling)
         self.scale = qk ** -0.5
+        sc = cfg.rope_scaling or {}
+        if (sc.get("rope_type") or sc.get("type")) in ("yarn", "deepseek_yarn") and sc.get("mscale_all_dim"):
+            # DeepSeek yarn: the softmax scale carries mscale(factor, mscale_all_dim)^2 (reference: models/deepseek_v2.py:483-487)
+            from onecat_vllm.ops.ref import yarn_mscale
+            m = yarn_mscale(float(sc.get("factor", 1.0)), float(sc["mscale_all_dim"]))
+            self.scale *= m * m
         self._wuk = self._wuv = None
 
     def _absorb(self, dtype):

@@ -15,6 +15,12 @@ _REGISTRY = {
 }
 
 
+# sequence-classification checkpoints of the dense families: the decoder with a ``score`` head (reference: models/adapters.py
+# ``as_seq_cls_model``)
+for _a in ("Llama", "Mistral", "Qwen2", "Qwen3", "Gemma", "Gemma2", "Phi3"):
+    _REGISTRY[_a + "ForSequenceClassification"] = "dense"
+
+
 def supported_architectures() -> list[str]:
     return sorted(_REGISTRY)
 

@@ -151,7 +151,12 @@ class CausalLM(nn.Module):
         super().__init__()
         self.cfg = cfg
         self.model = DecoderModel(cfg, device)
-        if cfg.tie_word_embeddings or not ps.get_state().is_last_pp:
+        self.score = None
+        if cfg.num_labels > 0:
+            from onecat_vllm.layers.linear import ReplicatedLinear
+            self.lm_head = None
+            self.score = ReplicatedLinear(cfg.hidden_size, cfg.num_labels, quant=None, prefix="score", dtype=cfg.dtype)
+        elif cfg.tie_word_embeddings or not ps.get_state().is_last_pp:
             self.lm_head = None
         else:
             self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)

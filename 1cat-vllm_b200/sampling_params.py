@@ -211,8 +211,9 @@ class BeamSearchParams:
 class PoolingParams:
     """Parameters of an embedding / classify request (reference: vllm/pooling_params.py)."""
 
-    task: str = "embed"  # embed | encode (raw hidden state) | score
+    task: str = "embed"  # embed | encode (raw hidden state) | score | classify (needs a sequence-classification checkpoint)
     normalize: bool = True
+    use_activation: bool = True  # classify: softmax over the labels (sigmoid for a single label) instead of raw logits
     dimensions: Optional[int] = None  # matryoshka truncation
     pooling_type: str = "last"  # last | mean | cls
 
@@ -221,4 +222,5 @@ class PoolingParams:
             raise ValueError(f"unknown pooling_type '{self.pooling_type}'")
 
     def to_dict(self) -> dict:
-        return dict(task=self.task, normalize=self.normalize, dimensions=self.dimensions, pooling_type=self.pooling_type)
+        return dict(task=self.task, normalize=self.normalize, dimensions=self.dimensions, pooling_type=self.pooling_type,
+                    use_activation=self.use_activation)

@@ -568,6 +568,16 @@ class ModelRunner:
                 if rows[i] > 0:  # the prompt is complete in this step
                     n_prompt = st.num_computed_tokens + q
                     v = h[-1] if pp.pooling_type == "last" else (st.pool_sum / n_prompt if pp.pooling_type == "mean" else st.pool_first)
+                    if pp.task == "classify":
+                        head = getattr(self.model, "score", None)
+                        if head is None:
+                            raise ValueError("classify needs a *ForSequenceClassification checkpoint")
+                        v = head(v.to(self.mc.dtype).unsqueeze(0))[0].float()
+                        if pp.use_activation:
+                            v = torch.sigmoid(v) if v.numel() == 1 else torch.softmax(v, -1)
+                        out[i] = v.cpu().tolist()
+                        o += q
+                        continue
                     if pp.dimensions:
                         v = v[: pp.dimensions]
                     if pp.normalize:

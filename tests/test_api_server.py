@@ -101,6 +101,10 @@ def test_pooling_routes(client):
     s = client.post("/score", json={"text_1": "hello world", "text_2": ["hello world", "zzz"]}).json()
     assert abs(s["data"][0]["score"] - 1.0) < 1e-4 and s["data"][1]["score"] < 0.9999
     assert client.post("/v1/embeddings", json={"input": "x", "pooling_type": "bogus"}).status_code == 400
+    rr = client.post("/v1/rerank", json={"query": "hello world", "documents": ["zzz qqq", "hello world", {"text": "hello"}], "top_n": 2}).json()
+    assert len(rr["results"]) == 2 and rr["results"][0]["index"] == 1 and rr["results"][0]["relevance_score"] > 0.999
+    assert rr["results"][0]["relevance_score"] >= rr["results"][1]["relevance_score"]
+    assert client.post("/classify", json={"input": "x"}).status_code == 400   # a generative checkpoint has no score head
 
 
 def test_more_tool_and_reasoning_parsers():

@@ -59,6 +59,12 @@ CASES = {
                                          "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32}),
     "LlamaForCausalLM+yarn-rope": dict(BASE, model_type="llama", rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0,
                                        "original_max_position_embeddings": 32}),
+    "DeepseekV3ForCausalLM+yarn": dict(BASE, model_type="deepseek_v3", num_key_value_heads=4, q_lora_rank=32, kv_lora_rank=32,
+                                       qk_nope_head_dim=16, qk_rope_head_dim=16, v_head_dim=16, n_routed_experts=8, n_shared_experts=1,
+                                       num_experts_per_tok=2, moe_intermediate_size=48, n_group=2, topk_group=1, routed_scaling_factor=1.5,
+                                       norm_topk_prob=True, first_k_dense_replace=1, scoring_func="sigmoid",
+                                       rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 8.0, "beta_fast": 32, "beta_slow": 1,
+                                                        "mscale": 1.0, "mscale_all_dim": 1.0, "original_max_position_embeddings": 32}),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 
@@ -127,3 +133,31 @@ def test_cpu_plumbing_run_matches_transformers():
     # N(0, 0.02) weights make the logits nearly flat, so a last-bit difference in summation order can flip a greedy choice;
     # everything before the first such flip must agree
     assert exact >= 30 and total >= 0.97 * 32 * 64, (exact, total)
+
+
+@pytest.mark.timeout(600)
+def test_sequence_classification_matches_transformers(tmp_path):
+    """A *ForSequenceClassification checkpoint: ``LLM.classify`` returns softmax(score(last hidden state)) as transformers does
+    (reference: models/adapters.py ``as_seq_cls_model``; entrypoints/llm.py ``classify``)."""
+    from onecat_vllm import LLM
+    from onecat_vllm.sampling_params import PoolingParams
+    cfg = transformers.Qwen2Config(**{k: v for k, v in BASE.items()}, rope_theta=1e6, num_labels=3, pad_token_id=0)
+    cfg.architectures = ["Qwen2ForSequenceClassification"]
+    torch.manual_seed(0)
+    hf = transformers.Qwen2ForSequenceClassification(cfg).eval().float()
+    for p in hf.parameters():
+        if p.dim() >= 2:
+            p.data.mul_(3.0)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    g = torch.Generator().manual_seed(2)
+    prompts = [torch.randint(1, 300, (n,), generator=g).tolist() for n in (7, 33)]
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)
+    outs = llm.classify([{"prompt_token_ids": p} for p in prompts])
+    raw = llm.encode([{"prompt_token_ids": prompts[0]}], PoolingParams(task="classify", normalize=False, use_activation=False))
+    llm.shutdown()
+    for p, o in zip(prompts, outs):
+        with torch.no_grad():
+            logits = hf(torch.tensor([p])).logits[0]
+        assert torch.allclose(torch.tensor(o.outputs.data), torch.softmax(logits, -1), atol=2e-4), (o.outputs.data, logits)
+    with torch.no_grad():
+        assert torch.allclose(torch.tensor(raw[0].outputs.data), hf(torch.tensor([prompts[0]])).logits[0], atol=2e-3)

@@ -209,6 +209,43 @@ def load_model(cfg, device) -> nn.Module:
     return model.eval()
 
 
+_DS_MTP = {"enorm.": "pre_fc_norm_embedding.", "hnorm.": "pre_fc_norm_hidden.", "eh_proj.": "fc.", "shared_head.norm.": "norm."}
+
+
+def mtp_checkpoint_weights(cfg, weights: Iterable[tuple[str, torch.Tensor]]) -> Iterator[tuple[str, torch.Tensor]]:
+    """Checkpoint tensors of the multi-token-prediction module under the names of ``MTPHead``: Qwen3-Next / Qwen3.5 keep them as
+    ``mtp.{fc, pre_fc_norm_*, norm, layers.0.*}``; DeepSeek-V3 as decoder layer ``num_hidden_layers`` with ``enorm / hnorm / eh_proj /
+    shared_head.norm`` (reference: models/qwen3_5_mtp.py:437 ``load_weights``; models/deepseek_mtp.py). Embeddings and the LM head are
+    the target's."""
+    ds = f"model.layers.{cfg.num_hidden_layers}."
+    for name, w in weights:
+        if name.startswith("model.language_model."):
+            name = "model." + name[len("model.language_model."):]
+        if name.startswith("mtp."):
+            n = name[4:]
+            if n.startswith("layers.0."):
+                n = "layer." + n[len("layers.0."):]
+            elif n.startswith("layers."):
+                continue  # deeper MTP modules are not used: one module drafts every position
+            yield n, w
+        elif name.startswith(ds):
+            n = name[len(ds):]
+            if n.startswith(("embed_tokens.", "shared_head.head.")):
+                continue
+            for theirs, ours in _DS_MTP.items():
+                if n.startswith(theirs):
+                    n = ours + n[len(theirs):]
+                    break
+            else:
+                n = "layer." + n
+            yield n, w
+
+
+def load_mtp_weights(mtp: nn.Module, cfg) -> int:
+    """Load the draft head from the target's checkpoint directory; returns how many tensors were found."""
+    return len(load_weights(mtp, mtp_checkpoint_weights(cfg, iter_safetensors(cfg.model))))
+
+
 def to_hf_state_dict(model: nn.Module) -> dict:
     """Un-stack fused parameters back to HF checkpoint names (q/k/v, gate/up, per-expert tensors), for saving a
     model built here as a checkpoint that any HF-layout loader (including this one) reads. TP size 1 only."""

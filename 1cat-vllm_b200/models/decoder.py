@@ -188,8 +188,10 @@ class MTPHead(nn.Module):
         super().__init__()
         import dataclasses
         from onecat_vllm.layers.linear import ReplicatedLinear
-        lcfg = dataclasses.replace(cfg, layer_types=None, num_hidden_layers=1, num_experts=0)
+        # the module's feed-forward follows the target: sparse for mixture-of-experts targets, dense otherwise
+        lcfg = dataclasses.replace(cfg, layer_types=None, num_hidden_layers=1, first_k_dense_replace=0, dense_layers=(), sliding_layers=())
         self.cfg = lcfg
+        self.stacked_params_mapping = CausalLM.stacked_params_mapping
         self.pre_fc_norm_embedding = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.pre_fc_norm_hidden = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.fc = ReplicatedLinear(2 * cfg.hidden_size, cfg.hidden_size, quant=None, prefix="mtp.fc", dtype=cfg.dtype)

@@ -9,6 +9,7 @@ the sampled ids back, so a step timed end to end includes both transfers.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Optional
@@ -88,6 +89,11 @@ class ModelRunner:
             with torch.device(self.device):
                 self.mtp = MTPHead(self.mc, self.model, self.device)
             dummy_init(self.mtp, self.mc.seed + 1)
+            if self.mc.load_format != "dummy" and os.path.isdir(self.mc.model):
+                from onecat_vllm.loader.weights import load_mtp_weights
+                n = load_mtp_weights(self.mtp, self.mc)
+                if n == 0:
+                    log.warning_once("the checkpoint has no multi-token-prediction tensors: the draft head runs with random weights")
             process_weights_after_loading(self.mtp)
             self.mtp.eval()
         if self.spec.enabled:

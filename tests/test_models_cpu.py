@@ -155,3 +155,49 @@ def test_nvfp4_packer_round_trips_through_the_kernel_layout():
                     v = lut[nib & 7].item() * (-1.0 if nib & 8 else 1.0)
                     got[r, kt * 64 + c * 8 + j] = v * s
     assert torch.allclose(got, want, rtol=2 ** -7, atol=1e-6)
+
+
+@pytest.mark.parametrize("layout", ["qwen", "deepseek"])
+def test_mtp_head_weights_load_from_checkpoint(tmp_path, layout):
+    """The draft head's tensors come from the target's checkpoint: ``mtp.*`` (Qwen3-Next / Qwen3.5) or decoder layer
+    ``num_hidden_layers`` with enorm / hnorm / eh_proj / shared_head.norm (DeepSeek-V3)."""
+    import dataclasses
+    from safetensors.torch import save_file
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    from onecat_vllm.models.decoder import MTPHead
+    cfg = HYBRID if layout == "qwen" else DSV3
+    mc = ModelConfig.from_hf_dict(cfg, dtype=torch.float32)
+    m = build_model(mc, "cpu")
+    dummy_init(m, 0)
+    save_pretrained(m, cfg, str(tmp_path))
+    head = MTPHead(mc, m, "cpu")
+    dummy_init(head, 77)
+    sd = {}
+    L = mc.num_hidden_layers
+    ds = {"pre_fc_norm_embedding.": "enorm.", "pre_fc_norm_hidden.": "hnorm.", "fc.": "eh_proj.", "norm.": "shared_head.norm."}
+    for name, w in to_hf_state_dict(head).items():
+        if layout == "qwen":
+            name = "mtp." + (("layers.0." + name[len("layer."):]) if name.startswith("layer.") else name)
+        else:
+            for ours, theirs in ds.items():
+                if name.startswith(ours):
+                    name = theirs + name[len(ours):]
+                    break
+            else:
+                name = name[len("layer."):]
+            name = f"model.layers.{L}." + name
+        sd[name] = w.contiguous()
+    save_file(sd, str(tmp_path / "model-mtp.safetensors"))
+    llm = LLM(model=str(tmp_path), max_model_len=128, dtype="float32", device="cpu", speculative_config=dict(method="mtp", num_speculative_tokens=2))
+    got = llm.llm_engine.engine_core.core.executor.worker.runner.mtp
+    want = dict(head.named_parameters())
+    n = 0
+    for name, p in got.named_parameters():
+        assert torch.equal(p, want[name]), name
+        n += 1
+    assert n >= 8
+    out = llm.generate(_prompts(cfg["vocab_size"])[:2], SamplingParams(temperature=0, max_tokens=8, ignore_eos=True))
+    assert all(len(o.outputs[0].token_ids) == 8 for o in out)
+    llm.shutdown()

@@ -397,8 +397,9 @@ class SpeculativeConfig:
     rejection sampler uses the conditional form ``rate[i] / rate[i-1]``.
     """
 
-    method: Optional[str] = None  # None | "mtp" | "ngram"
+    method: Optional[str] = None  # None | "mtp" | "ngram" | "eagle"
     num_speculative_tokens: int = 0
+    model: Optional[str] = None  # eagle: directory of the draft head's checkpoint (random weights when absent)
     synthetic_acceptance_rates: Optional[list[float]] = None
     synthetic_acceptance_rate: Optional[float] = None  # conditional per-position Bernoulli rate
     synthetic_seed: int = 0

@@ -115,9 +115,9 @@ class Scheduler:
         self.policy = sc.policy
         spec = vllm_config.speculative_config
         self.num_spec_tokens = spec.num_speculative_tokens if spec.enabled else 0
-        self.num_lookahead_tokens = self.num_spec_tokens if spec.method == "mtp" else 0
+        self.num_lookahead_tokens = self.num_spec_tokens if spec.method in ("mtp", "eagle") else 0
         self.kv_cache_manager = KVCacheManager(num_gpu_blocks, cc.block_size, self.max_model_len, cc.enable_prefix_caching,
-                                               num_state_slots, use_eagle=spec.method == "mtp",
+                                               num_state_slots, use_eagle=spec.method in ("mtp", "eagle"),
                                                dcp_world_size=vllm_config.parallel_config.decode_context_parallel_size,
                                                log_stats=log_stats)
         if cc.kv_transfer_config:

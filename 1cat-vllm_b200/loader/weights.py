@@ -246,6 +246,31 @@ def load_mtp_weights(mtp: nn.Module, cfg) -> int:
     return len(load_weights(mtp, mtp_checkpoint_weights(cfg, iter_safetensors(cfg.model))))
 
 
+def load_eagle_weights(head: nn.Module, path: str) -> int:
+    """EAGLE checkpoints name their tensors ``fc.*``, ``embed_tokens.weight``, ``layers.0.*`` (optionally under ``model.``), in
+    safetensors or ``pytorch_model.bin`` (reference: models/llama_eagle.py ``load_weights``)."""
+    def tensors():
+        if any(f.endswith(".safetensors") for f in os.listdir(path)):
+            yield from iter_safetensors(path)
+        else:
+            yield from torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu", weights_only=True).items()
+
+    def renamed():
+        for name, w in tensors():
+            if name.startswith("model."):
+                name = name[len("model."):]
+            if name.startswith("lm_head."):
+                continue
+            if name.startswith("embed_tokens."):
+                head.own_embedding = True
+            if name.startswith("layers.0."):
+                name = "layer." + name[len("layers.0."):]
+            if name.startswith("layer.input_layernorm."):
+                continue  # EAGLE skips the first layer's input norm
+            yield name, w
+    return len(load_weights(head, renamed()))
+
+
 def to_hf_state_dict(model: nn.Module) -> dict:
     """Un-stack fused parameters back to HF checkpoint names (q/k/v, gate/up, per-expert tensors), for saving a
     model built here as a checkpoint that any HF-layout loader (including this one) reads. TP size 1 only."""

@@ -214,3 +214,34 @@ class MTPHead(nn.Module):
 
     def compute_logits(self, hidden):
         return self._target[0].compute_logits(hidden)
+
+
+class EagleHead(nn.Module):
+    """EAGLE-1 draft head: ``h' = fc([embed(tok) ; h_target])`` (with bias), one decoder layer without its input norm, no final
+    norm; the LM head is the target's and the embedding table is the head's own when its checkpoint has one
+    (reference: models/llama_eagle.py; spec_decode/eagle.py — same drafting loop as the MTP head)."""
+
+    stacked_params_mapping = CausalLM.stacked_params_mapping
+
+    def __init__(self, cfg: ModelConfig, target: CausalLM, device="cpu"):
+        super().__init__()
+        import dataclasses
+        from onecat_vllm.layers.linear import ReplicatedLinear
+        lcfg = dataclasses.replace(cfg, layer_types=None, num_hidden_layers=1, num_experts=0, sliding_layers=(), quant=type(cfg.quant)())
+        self.cfg = lcfg
+        self.fc = ReplicatedLinear(2 * cfg.hidden_size, cfg.hidden_size, bias=True, quant=None, prefix="fc", dtype=cfg.dtype)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+        self.own_embedding = False  # set by the loader when the checkpoint carries embed_tokens
+        self.layer = DecoderLayer(lcfg, 0, "layers.0", device)
+        self._target = [target]
+
+    def forward(self, input_ids, target_hidden, md, cache):
+        emb = self.embed_tokens if self.own_embedding else self._target[0].model.embed_tokens
+        h = self.fc(torch.cat([emb(input_ids), target_hidden], dim=-1))
+        layer = self.layer
+        part = layer.mixer(h, md, cache)
+        x, residual = reduce_add_norm(part, h, layer.post_attention_layernorm)
+        return residual + reduce_only(layer.mlp(x))
+
+    def compute_logits(self, hidden):
+        return self._target[0].compute_logits(hidden)

@@ -111,6 +111,6 @@ def make_proposer(runner):
     sc = runner.spec
     if sc.method == "ngram":
         return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
-    if sc.method == "mtp":
+    if sc.method in ("mtp", "eagle"):
         return MTPProposer(runner)
     raise ValueError(f"unknown speculative method {sc.method!r}")

@@ -96,6 +96,17 @@ class ModelRunner:
                     log.warning_once("the checkpoint has no multi-token-prediction tensors: the draft head runs with random weights")
             process_weights_after_loading(self.mtp)
             self.mtp.eval()
+        if self.spec.method == "eagle":
+            # the drafting loop is the MTP one: the head sits in the same slot
+            from onecat_vllm.loader.weights import dummy_init, load_eagle_weights, process_weights_after_loading
+            from onecat_vllm.models.decoder import EagleHead
+            with torch.device(self.device):
+                self.mtp = EagleHead(self.mc, self.model, self.device)
+            dummy_init(self.mtp, self.mc.seed + 1)
+            if self.spec.model and os.path.isdir(self.spec.model):
+                load_eagle_weights(self.mtp, self.spec.model)
+            process_weights_after_loading(self.mtp)
+            self.mtp.eval()
         if self.spec.enabled:
             from onecat_vllm.spec_decode.proposers import make_proposer
             self.proposer = make_proposer(self)

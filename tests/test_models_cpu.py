@@ -201,3 +201,37 @@ def test_mtp_head_weights_load_from_checkpoint(tmp_path, layout):
     out = llm.generate(_prompts(cfg["vocab_size"])[:2], SamplingParams(temperature=0, max_tokens=8, ignore_eos=True))
     assert all(len(o.outputs[0].token_ids) == 8 for o in out)
     llm.shutdown()
+
+
+def test_eagle_head_is_lossless_and_loads_its_checkpoint(tmp_path):
+    """EAGLE-1 drafting: greedy output equals plain decoding whatever the head proposes, and the head's tensors come from its own
+    checkpoint directory (``fc`` with bias, ``embed_tokens``, ``layers.0`` without an input norm)."""
+    from safetensors.torch import save_file
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    from onecat_vllm.models.decoder import EagleHead
+    dense = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256)
+    mc = ModelConfig.from_hf_dict(dense, dtype=torch.float32)
+    head = EagleHead(mc, build_model(mc, "cpu"), "cpu")
+    dummy_init(head, 5)
+    sd = {}
+    for name, w in to_hf_state_dict(head).items():
+        if "input_layernorm" in name:
+            continue
+        sd[("layers.0." + name[len("layer."):]) if name.startswith("layer.") else name] = w.contiguous()
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    p = _prompts(500)
+    ref = _gen(dense, p)
+    llm = LLM(hf_config=dense, max_model_len=256, dtype="float32", device="cpu",
+              speculative_config=dict(method="eagle", num_speculative_tokens=3, model=str(tmp_path)))
+    got = llm.llm_engine.engine_core.core.executor.worker.runner.mtp
+    assert got.own_embedding
+    want = dict(head.named_parameters())
+    for name, q in got.named_parameters():
+        if "input_layernorm" not in name:
+            assert torch.equal(q[:500], want[name][:500]), name   # embedding rows past the vocabulary are padding
+    out = [o.outputs[0].token_ids for o in llm.generate(p, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
+    llm.shutdown()
+    assert out == ref

@@ -397,9 +397,10 @@ class SpeculativeConfig:
     rejection sampler uses the conditional form ``rate[i] / rate[i-1]``.
     """
 
-    method: Optional[str] = None  # None | "mtp" | "ngram" | "eagle"
+    method: Optional[str] = None  # None | "mtp" | "ngram" | "eagle" | "medusa"
     num_speculative_tokens: int = 0
-    model: Optional[str] = None  # eagle: directory of the draft head's checkpoint (random weights when absent)
+    model: Optional[str] = None  # eagle / medusa: directory of the draft heads' checkpoint (random weights when absent)
+    medusa_num_layers: int = 1  # residual blocks per Medusa head
     synthetic_acceptance_rates: Optional[list[float]] = None
     synthetic_acceptance_rate: Optional[float] = None  # conditional per-position Bernoulli rate
     synthetic_seed: int = 0

@@ -107,10 +107,90 @@ class MTPProposer:
         return out
 
 
+class MedusaHeads(torch.nn.Module):
+    """Medusa: head ``i`` maps the target's last hidden state to the token ``i + 2`` positions ahead through residual SiLU blocks
+    and its own vocabulary projection; no attention and no KV cache (reference: models/medusa.py ``ResidualBlock`` / ``Medusa``;
+    spec_decode/medusa.py)."""
+
+    def __init__(self, hidden: int, vocab: int, num_heads: int, num_layers: int, dtype):
+        super().__init__()
+        self.blocks = torch.nn.ModuleList([torch.nn.ModuleList([torch.nn.Linear(hidden, hidden, dtype=dtype) for _ in range(num_layers)])
+                                           for _ in range(num_heads)])
+        self.lm_heads = torch.nn.ModuleList([torch.nn.Linear(hidden, vocab, bias=False, dtype=dtype) for _ in range(num_heads)])
+
+    def forward(self, h: torch.Tensor) -> list:
+        out = []
+        for layers, head in zip(self.blocks, self.lm_heads):
+            x = h
+            for lin in layers:
+                x = x + torch.nn.functional.silu(lin(x))
+            out.append(head(x))
+        return out
+
+    def load(self, path: str) -> int:
+        """Tensor names: ``blocks.{i}.layers.{j}.{weight,bias}`` and ``lm_heads.{i}.weight``; the original release's
+        ``{i}.{j}.linear.*`` / ``{i}.{L}.weight`` layout is accepted too."""
+        import os
+        import re
+        from onecat_vllm.loader.weights import iter_safetensors
+        if any(f.endswith(".safetensors") for f in os.listdir(path)):
+            items = list(iter_safetensors(path))
+        else:
+            f = next(f for f in ("medusa_lm_head.pt", "pytorch_model.bin") if os.path.exists(os.path.join(path, f)))
+            items = list(torch.load(os.path.join(path, f), map_location="cpu", weights_only=True).items())
+        sd = dict(self.state_dict())
+        n = 0
+        L = len(self.blocks[0]) if len(self.blocks) else 0
+        for name, w in items:
+            name = re.sub(r"^blocks\.(\d+)\.layers\.(\d+)\.", r"blocks.\1.\2.", name)
+            m = re.match(r"^(?:medusa_head\.)?(\d+)\.(\d+)\.(?:linear\.)?(weight|bias)$", name)
+            if m:
+                i, j, leaf = int(m.group(1)), int(m.group(2)), m.group(3)
+                name = f"lm_heads.{i}.weight" if j == L else f"blocks.{i}.{j}.{leaf}"
+            if name in sd and sd[name].shape == w.shape:
+                sd[name].copy_(w)
+                n += 1
+        return n
+
+
+class MedusaProposer:
+    def __init__(self, runner):
+        sc, mc = runner.spec, runner.mc
+        self.k = sc.num_speculative_tokens
+        self.heads = MedusaHeads(mc.hidden_size, mc.vocab_size, self.k, sc.medusa_num_layers, mc.dtype).to(runner.device).eval()
+        g = torch.Generator().manual_seed(mc.seed + 2)
+        with torch.no_grad():
+            for p in self.heads.parameters():
+                p.copy_(torch.empty(p.shape).normal_(0, 0.02, generator=g))
+        if sc.model:
+            self.heads.load(sc.model)
+
+    @torch.inference_mode()
+    def propose(self, runner, so, req_ids, rows, sampled, hidden, md, drafts_of):
+        R = md.num_reqs
+        qsl = np.concatenate([[0], np.cumsum(md.query_lens_cpu)]).tolist() if md.query_lens_cpu is not None else md.query_start_loc.tolist()
+        out: list = [[] for _ in range(R)]
+        active, idx = [], []
+        for r in range(R):
+            if sampled[r]:
+                # the hidden state of the last accepted position: the one that produced the newest token
+                active.append(r)
+                idx.append(qsl[r + 1] - (len(drafts_of[r]) + 1) + (len(sampled[r]) - 1))
+        if not active:
+            return out
+        logits = self.heads(hidden[torch.tensor(idx, device=hidden.device)])
+        toks = torch.stack([lg.argmax(-1) for lg in logits], dim=1).tolist()
+        for i, r in enumerate(active):
+            out[r] = toks[i]
+        return out
+
+
 def make_proposer(runner):
     sc = runner.spec
     if sc.method == "ngram":
         return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
     if sc.method in ("mtp", "eagle"):
         return MTPProposer(runner)
+    if sc.method == "medusa":
+        return MedusaProposer(runner)
     raise ValueError(f"unknown speculative method {sc.method!r}")

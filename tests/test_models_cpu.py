@@ -235,3 +235,26 @@ def test_eagle_head_is_lossless_and_loads_its_checkpoint(tmp_path):
     out = [o.outputs[0].token_ids for o in llm.generate(p, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
     llm.shutdown()
     assert out == ref
+
+
+def test_medusa_heads_are_lossless_and_load(tmp_path):
+    from safetensors.torch import save_file
+    from onecat_vllm.spec_decode.proposers import MedusaHeads
+    dense = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256)
+    src = MedusaHeads(64, 500, 3, 1, torch.float32)
+    sd = {}
+    for name, w in src.state_dict().items():   # the serving layout: blocks.{i}.layers.{j}.*, lm_heads.{i}.weight
+        parts = name.split(".")
+        sd[f"blocks.{parts[1]}.layers.{parts[2]}.{parts[3]}" if parts[0] == "blocks" else name] = w.contiguous()
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    p = _prompts(500)
+    ref = _gen(dense, p)
+    llm = LLM(hf_config=dense, max_model_len=256, dtype="float32", device="cpu",
+              speculative_config=dict(method="medusa", num_speculative_tokens=3, model=str(tmp_path)))
+    heads = llm.llm_engine.engine_core.core.executor.worker.runner.proposer.heads
+    for name, w in src.state_dict().items():
+        assert torch.equal(heads.state_dict()[name], w), name
+    out = [o.outputs[0].token_ids for o in llm.generate(p, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
+    llm.shutdown()
+    assert out == ref

@@ -11,8 +11,12 @@
 // Options for the Gemma / GPT-OSS / Mistral families: a sliding window (a query at position i sees keys i-window+1 .. i; key tiles
 // wholly before the window are skipped), tanh soft-capping of the scaled scores, and per-head attention sinks (a learned logit that
 // joins the softmax denominator only).
+// FP8 KV cache (KV8): pages hold e4m3 bytes in the same layout; tiles stream through a byte-wide cp.async ring and are widened to
+// bf16 into one working tile per operand before the MMAs; the per-tensor scales fold into the softmax scale (K) and the output (V).
 // (reference: flash-attention-v100/kernel/fused_mha_forward_paged.cu:364, flash_decode_paged.cu:667,831,1301;
 //  v1/attention/backends/flash_attn_v100.py:2216 for the math)
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -49,7 +53,24 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
   return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int D, int MODE, int MB>
+// 16 e4m3 bytes -> 16 bf16 (exact: every e4m3 value is a bf16 value)
+__device__ __forceinline__ void widen_fp8x16(const uint4& in, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xffffu), __NV_E4M3);
+      float2 f = __half22float2(*reinterpret_cast<__half2*>(&r));
+      o[i * 2 + h] = pack_bf16(f.x, f.y);
+    }
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+template <int D, int MODE, int MB, bool KV8>
 __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring
   constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
@@ -57,9 +78,14 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
   constexpr int CH = D / 8;                     // 16-byte chunks per row
   extern __shared__ __align__(128) uint8_t smem[];
+  // bf16 cache: sK / sV are the cp.async rings of bf16 tiles. fp8 cache: they are rings of byte tiles, followed by one bf16
+  // working tile per operand (sKb / sVb)
+  constexpr int ESZ = KV8 ? 1 : 2;
   uint8_t* sQ = smem;
   uint8_t* sK = sQ + ROWS * D * 2;
-  uint8_t* sV = sK + STAGES * kKeysPerTile * D * 2;
+  uint8_t* sV = sK + STAGES * kKeysPerTile * D * ESZ;
+  uint8_t* sKb = sV + STAGES * kKeysPerTile * D * ESZ;
+  uint8_t* sVb = sKb + kKeysPerTile * D * 2;
   __shared__ int s_req, s_tile0;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -124,23 +150,25 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
 
   // each thread always copies the same 16-byte column chunk of rows (tid / CH) + i * (128 / CH); pages are a power of
   // two tokens long, so the block-table lookup is a shift and a mask
-  const int ld_ch = threadIdx.x % CH, ld_row0 = threadIdx.x / CH;
-  constexpr int kRowStep = 128 / CH;
+  constexpr int LCH = KV8 ? D / 16 : CH;        // 16-byte chunks per cache row
+  const int ld_ch = threadIdx.x % LCH, ld_row0 = threadIdx.x / LCH;
+  constexpr int kRowStep = 128 / LCH;
   const int bs_shift = p.bs_shift, bs_mask = p.bs - 1;
-  const __nv_bfloat16* kv_head = p.kv_cache + (size_t)hkv * page_elems + ld_ch * 8;
-  const size_t blk_stride = (size_t)2 * p.Hkv * page_elems, v_off = (size_t)p.Hkv * page_elems;
+  // byte addressing covers both element sizes
+  const uint8_t* kv_head = reinterpret_cast<const uint8_t*>(p.kv_cache) + ((size_t)hkv * page_elems) * ESZ + ld_ch * 16;
+  const size_t blk_stride = (size_t)2 * p.Hkv * page_elems * ESZ, v_off = (size_t)p.Hkv * page_elems * ESZ;
   auto load_tile = [&](int tile, int buf) {
     const int k0 = tile * kKeysPerTile;
-    uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * 2;
-    uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * 2;
+    uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * ESZ;
+    uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * ESZ;
 #pragma unroll
     for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
       const int row = ld_row0 + i * kRowStep;
       const int key = k0 + row;
-      const uint32_t off = sw_off<D>(row, ld_ch);
+      const uint32_t off = KV8 ? (uint32_t)(row * D + ld_ch * 16) : sw_off<D>(row, ld_ch);
       if (key < kv_end) {
         const int blk = bt[key >> bs_shift];
-        const __nv_bfloat16* src = kv_head + (size_t)blk * blk_stride + (size_t)(key & bs_mask) * D;
+        const uint8_t* src = kv_head + (size_t)blk * blk_stride + (size_t)(key & bs_mask) * D * ESZ;
         cp_async16(dk + off, src);
         cp_async16(dv + off, src + v_off);
       } else {
@@ -161,7 +189,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   }
   // plain: s * scale * log2(e); soft-capped: cap * tanh(s * scale / cap) * log2(e)
   const bool capped = p.softcap > 0.f;
-  const float sc = capped ? p.scale / p.softcap : p.scale * 1.4426950408889634f;
+  const float qk_scale = KV8 ? p.scale * p.k_scale : p.scale;   // K was stored as k / k_scale
+  const float sc = capped ? qk_scale / p.softcap : qk_scale * 1.4426950408889634f;
   const float sc_post = p.softcap * 1.4426950408889634f;
   const int row_base = (MODE == 0) ? warp * 16 : 0;
   const int key_base = (MODE == 0) ? 0 : warp * 16;
@@ -178,8 +207,25 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     __syncthreads();               // ...for every thread, and everybody has finished the buffer refilled below
     if (tile + STAGES - 1 < tile_hi) load_tile(tile + STAGES - 1, (tile - tile_lo + STAGES - 1) % STAGES);
     cp_async_commit();
-    const uint32_t kb = smem_u32(sK + (size_t)buf * kKeysPerTile * D * 2);
-    const uint32_t vb = smem_u32(sV + (size_t)buf * kKeysPerTile * D * 2);
+    if (KV8) {
+      // widen this tile's bytes into the bf16 working tiles (everyone is past the previous tile's MMAs: barrier above)
+      const uint8_t* k8 = sK + (size_t)buf * kKeysPerTile * D;
+      const uint8_t* v8 = sV + (size_t)buf * kKeysPerTile * D;
+#pragma unroll
+      for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
+        const int row = ld_row0 + i * kRowStep;
+        uint4 lo, hi;
+        widen_fp8x16(*reinterpret_cast<const uint4*>(k8 + row * D + ld_ch * 16), lo, hi);
+        *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2)) = lo;
+        *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
+        widen_fp8x16(*reinterpret_cast<const uint4*>(v8 + row * D + ld_ch * 16), lo, hi);
+        *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2)) = lo;
+        *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
+      }
+      __syncthreads();
+    }
+    const uint32_t kb = smem_u32(KV8 ? sKb : sK + (size_t)buf * kKeysPerTile * D * 2);
+    const uint32_t vb = smem_u32(KV8 ? sVb : sV + (size_t)buf * kKeysPerTile * D * 2);
     const uint32_t qb = smem_u32(sQ);
     const int k0 = tile * kKeysPerTile + key_base;
 
@@ -288,7 +334,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
       if (row >= nrows) continue;
       const int tok = tq0 + row / G, gh = row % G;
       const float den = lrow[0][h] + (p.sinks != nullptr ? exp2f(p.sinks[hkv * G + gh] * 1.4426950408889634f - mrow[0][h]) : 0.f);
-      const float inv = den > 0.f ? 1.f / den : 0.f;
+      const float inv = den > 0.f ? (KV8 ? p.v_scale : 1.f) / den : 0.f;
       __nv_bfloat16* dst = p.out + ((size_t)(qs + tok) * p.Hq + hkv * G + gh) * D;
 #pragma unroll
       for (int i = 0; i < D / 8; ++i)
@@ -346,7 +392,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
       }
     } else {
       const float den = L + (p.sinks != nullptr ? exp2f(p.sinks[hkv * G + gh] * 1.4426950408889634f - M) : 0.f);
-      const float inv = den > 0.f ? 1.f / den : 0.f;
+      const float inv = den > 0.f ? (KV8 ? p.v_scale : 1.f) / den : 0.f;
       __nv_bfloat16* dst = p.out + orow * D + c4;
       *reinterpret_cast<uint2*>(dst) = make_uint2(pack_bf16(acc[0] * inv, acc[1] * inv), pack_bf16(acc[2] * inv, acc[3] * inv));
       if (p.lse != nullptr && c4 == 0) p.lse[orow] = (M + log2f(L)) * 0.6931471805599453f;
@@ -375,24 +421,24 @@ __global__ void attn_combine_kernel(const AttnParams p) {
     for (int i = 0; i < D / 32; ++i) acc[i] += src[lane + 32 * i] * f;
   }
   const float den = L + (p.sinks != nullptr ? exp2f(p.sinks[warp % p.Hq] * 1.4426950408889634f - M) : 0.f);
-  const float inv = den > 0.f ? 1.f / den : 0.f;
+  const float inv = den > 0.f ? (p.kv_fp8 ? p.v_scale : 1.f) / den : 0.f;
 #pragma unroll
   for (int i = 0; i < D / 32; ++i) p.out[(size_t)warp * D + lane + 32 * i] = __float2bfloat16(acc[i] * inv);
   if (p.lse != nullptr && lane == 0) p.lse[warp] = (M + log2f(L)) * 0.6931471805599453f;
 }
 
-template <int D, int MODE, int MB>
+template <int D, int MODE, int MB, bool KV8>
 int launch_one(const AttnParams& p, cudaStream_t st) {
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
-  const int smem = ROWS * D * 2 + 2 * 3 * kKeysPerTile * D * 2;
+  const int smem = ROWS * D * 2 + (KV8 ? 2 * 3 * kKeysPerTile * D + 2 * kKeysPerTile * D * 2 : 2 * 3 * kKeysPerTile * D * 2);
   static int configured = 0;
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = 1;
   }
   dim3 grid(MODE == 0 ? p.num_q_tiles : p.R, p.Hkv, MODE == 0 ? 1 : p.splits);
   if (grid.x == 0) return 0;
-  attn_kernel<D, MODE, MB><<<grid, 128, smem, st>>>(p);
+  attn_kernel<D, MODE, MB, KV8><<<grid, 128, smem, st>>>(p);
   if (MODE == 1 && p.splits > 1) {
     int rows = p.T * p.Hq;
     attn_combine_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, st>>>(p);
@@ -406,18 +452,19 @@ int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
   if (p.Hq % p.Hkv || p.bs < 16 || (p.bs & (p.bs - 1)) || (p.D != 128 && p.D != 256)) return -1;
   const int G = p.Hq / p.Hkv;
   if (G > 64) return -1;
+  const bool f8 = p.kv_fp8 != 0;
   if (mode == 1) {
     const int rows = p.short_q_len * G;
     if (p.D == 128) {
-      if (rows <= 16) return launch_one<128, 1, 1>(p, st);
-      if (rows <= 32) return launch_one<128, 1, 2>(p, st);
+      if (rows <= 16) return f8 ? launch_one<128, 1, 1, true>(p, st) : launch_one<128, 1, 1, false>(p, st);
+      if (rows <= 32) return f8 ? launch_one<128, 1, 2, true>(p, st) : launch_one<128, 1, 2, false>(p, st);
     } else {
-      if (rows <= 16) return launch_one<256, 1, 1>(p, st);
+      if (rows <= 16) return f8 ? launch_one<256, 1, 1, true>(p, st) : launch_one<256, 1, 1, false>(p, st);
     }
     return -6;  // caller must use mode 0 for longer queries
   }
-  if (p.D == 128) return launch_one<128, 0, 1>(p, st);
-  return launch_one<256, 0, 1>(p, st);
+  if (p.D == 128) return f8 ? launch_one<128, 0, 1, true>(p, st) : launch_one<128, 0, 1, false>(p, st);
+  return f8 ? launch_one<256, 0, 1, true>(p, st) : launch_one<256, 0, 1, false>(p, st);
 }
 
 unsigned int attention_read_status(bool clear) { return read_status_tu(clear); }

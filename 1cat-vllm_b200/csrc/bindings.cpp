@@ -146,7 +146,7 @@ torch::Tensor silu_and_mul(torch::Tensor x) {
 
 void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor positions, torch::Tensor cos_sin,
                     c10::optional<torch::Tensor> kv_cache, torch::Tensor slot_mapping, int64_t rot, c10::optional<torch::Tensor> qn,
-                    c10::optional<torch::Tensor> kn, double eps, bool gemma) {
+                    c10::optional<torch::Tensor> kn, double eps, bool gemma, double k_scale, double v_scale) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(v, "v");
@@ -175,7 +175,11 @@ void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Te
   p.eps = (float)eps;
   p.bs = 16;
   if (kv_cache.has_value()) {
-    check_bf16(*kv_cache, "kv_cache");
+    TORCH_CHECK(kv_cache->is_cuda() && (kv_cache->scalar_type() == torch::kBFloat16 || kv_cache->scalar_type() == torch::kFloat8_e4m3fn),
+                "kv_cache must be a bf16 or float8_e4m3fn CUDA tensor");
+    p.kv_fp8 = kv_cache->scalar_type() == torch::kFloat8_e4m3fn;
+    p.k_scale_inv = (float)(1.0 / k_scale);
+    p.v_scale_inv = (float)(1.0 / v_scale);
     TORCH_CHECK(kv_cache->is_contiguous() && kv_cache->dim() == 5 && kv_cache->size(1) == 2 && kv_cache->size(2) == p.Hkv && kv_cache->size(4) == p.D,
                 "kv_cache must be contiguous [blocks, 2, Hkv, block_size, D]");
     p.kv_cache = (__nv_bfloat16*)kv_cache->data_ptr();
@@ -189,9 +193,10 @@ void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Te
 void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out, c10::optional<torch::Tensor> lse, torch::Tensor qsl,
                      torch::Tensor seq_lens, torch::Tensor block_table, double scale, int64_t mode, int64_t num_q_tiles, int64_t splits,
                      int64_t max_q_len, int64_t short_q_len, c10::optional<torch::Tensor> ws_o, c10::optional<torch::Tensor> ws_ml,
-                     int64_t window, double softcap, c10::optional<torch::Tensor> sinks) {
+                     int64_t window, double softcap, c10::optional<torch::Tensor> sinks, double k_scale, double v_scale) {
   check_bf16(q, "q");
-  check_bf16(kv_cache, "kv_cache");
+  TORCH_CHECK(kv_cache.is_cuda() && (kv_cache.scalar_type() == torch::kBFloat16 || kv_cache.scalar_type() == torch::kFloat8_e4m3fn),
+              "kv_cache must be a bf16 or float8_e4m3fn CUDA tensor");
   check_bf16(out, "out");
   TORCH_CHECK(q.dim() == 3 && q.stride(2) == 1 && out.is_contiguous(), "q must be [T,Hq,D]; out contiguous");
   TORCH_CHECK(((uintptr_t)q.data_ptr() & 15) == 0 && (q.stride(0) % 8) == 0 && (q.stride(1) % 8) == 0, "q must be 16-byte aligned");
@@ -225,6 +230,10 @@ void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out,
   p.short_q_len = (int)short_q_len;
   p.window = (int)window;
   p.softcap = (float)softcap;
+  p.kv_fp8 = kv_cache.scalar_type() == torch::kFloat8_e4m3fn;
+  p.k_scale = (float)k_scale;
+  p.v_scale = (float)v_scale;
+  TORCH_CHECK(mode != 2 || !p.kv_fp8, "an fp8 KV cache runs on the mma.sync kernels");
   if (sinks.has_value()) {
     TORCH_CHECK(sinks->is_cuda() && sinks->scalar_type() == torch::kFloat32 && sinks->is_contiguous() && sinks->numel() == q.size(1),
                 "sinks must be a contiguous fp32 CUDA tensor with one entry per query head");

@@ -2,6 +2,8 @@
 // KV insert, arg-max over the vocabulary. One pass over the data each, 16-byte accesses.
 // (reference: csrc/libtorch_stable/layernorm_kernels.cu:21,99; pos_encoding_kernels.cu:77; fused_qknorm_rope_kernel.cu:104;
 //  cache_kernels.cu reshape_and_cache_flash; activation_kernels.cu:78)
+#include <cuda_fp8.h>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -158,14 +160,20 @@ __global__ void rope_cache_kernel(RopeCacheParams p) {
   __syncwarp();
   const long long slot = (kind != 0 && p.kv_cache != nullptr) ? (long long)p.slot_mapping[t] : -1;
   __nv_bfloat16* cdst = nullptr;
+  uint8_t* cdst8 = nullptr;  // fp8 cache: same element index, one byte each
   if (slot >= 0) {
     long long blk = slot / p.bs, off = slot % p.bs;
     int h = (kind == 1) ? hh - p.Hq : hh - p.Hq - p.Hkv;
-    cdst = p.kv_cache + ((((size_t)blk * 2 + (kind - 1)) * p.Hkv + h) * p.bs + off) * D;
+    const size_t e = ((((size_t)blk * 2 + (kind - 1)) * p.Hkv + h) * p.bs + off) * D;
+    if (p.kv_fp8) cdst8 = reinterpret_cast<uint8_t*>(p.kv_cache) + e;
+    else cdst = p.kv_cache + e;
   }
   if (kind == 2) {
     if (cdst != nullptr)
       for (int i = lane; i < D; i += 32) cdst[i] = src[i];
+    if (cdst8 != nullptr)
+      for (int i = lane; i < D; i += 32)
+        cdst8[i] = (uint8_t)__nv_cvt_float_to_fp8(buf[i] * p.v_scale_inv, __NV_SATFINITE, __NV_E4M3);
     return;
   }
   const int half = p.rot >> 1;
@@ -178,6 +186,7 @@ __global__ void rope_cache_kernel(RopeCacheParams p) {
     __nv_bfloat16 ob = __float2bfloat16(o);
     src[i] = ob;
     if (cdst != nullptr) cdst[i] = ob;
+    if (cdst8 != nullptr) cdst8[i] = (uint8_t)__nv_cvt_float_to_fp8(__bfloat162float(ob) * p.k_scale_inv, __NV_SATFINITE, __NV_E4M3);
   }
 }
 

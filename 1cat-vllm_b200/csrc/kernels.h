@@ -16,6 +16,8 @@ struct RopeCacheParams {
   const __nv_bfloat16 *q_norm, *k_norm;  // per-head RMSNorm weights or null
   int T, Hq, Hkv, D, rot, bs, gemma;
   float eps;
+  int kv_fp8;                    // kv_cache holds e4m3 bytes: k / k_scale and v / v_scale, saturated
+  float k_scale_inv, v_scale_inv;
 };
 
 int rms_norm_launch(const void* x, const void* res_in, const void* w, void* y, void* res_out, int T, int H, int ldx, float eps,
@@ -48,6 +50,8 @@ struct AttnParams {
   int window;                 // sliding window in tokens (0 = full causal attention); mma.sync kernels only
   float softcap;              // tanh soft-capping of the scaled scores (0 = off); mma.sync kernels only
   const float* sinks;         // [Hq] attention-sink logits or null; mma.sync kernels only
+  int kv_fp8;                 // the cache holds e4m3 bytes (value / scale) instead of bf16; mma.sync kernels only
+  float k_scale, v_scale;     // per-tensor scales of an fp8 cache
 };
 // mode 0: rows of a query tile are spread over warps (prefill / long queries); mode 1: keys are spread over warps
 // (decode and short verify queries, with split-KV + combine).

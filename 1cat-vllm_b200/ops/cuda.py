@@ -351,7 +351,7 @@ def silu_and_mul(x):
 def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma):
     global _LAUNCHES
     _LAUNCHES += 1
-    _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
+    _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, 1.0, 1.0)
 
 
 def argmax(logits):
@@ -419,17 +419,18 @@ def paged_attention(q, kv_cache, md, scale, out=None, lse=None, window=0, softca
         ws_o, ws_ml = (w.attn_static if getattr(md, "static_ws", False) else w.attn)(splits * T * Hq * D, splits * T * Hq * 2)
     if n_short:
         _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 1, 0, splits,
-                           md.max_query_len, short, ws_o, ws_ml, window, softcap, sinks)
+                           md.max_query_len, short, ws_o, ws_ml, window, softcap, sinks, 1.0, 1.0)
         _LAUNCHES += 2 if splits > 1 else 1
     if tiles:
-        if D == 128 and q.stride(1) == D and _ATTN_PREFILL_TC and not window and not softcap and sinks is None:
+        if (D == 128 and q.stride(1) == D and _ATTN_PREFILL_TC and not window and not softcap and sinks is None
+                and kv_cache.dtype == torch.bfloat16):
             # tcgen05 kernel: 128-token query tiles per (request, head)
             tiles_tc = sum(-(-x // 128) for x in md.query_lens_cpu if x > short)
             _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 2, tiles_tc, 1,
-                               md.max_query_len, short, None, None, 0, 0.0, None)
+                               md.max_query_len, short, None, None, 0, 0.0, None, 1.0, 1.0)
         else:
             _C.paged_attention(q, kv_cache, out, lse, md.query_start_loc, md.seq_lens, md.block_table, scale, 0, tiles, 1,
-                               md.max_query_len, short, None, None, window, softcap, sinks)
+                               md.max_query_len, short, None, None, window, softcap, sinks, 1.0, 1.0)
         _LAUNCHES += 1
     return out
 

@@ -140,8 +140,13 @@ def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_d
         sm = slot_mapping.long()
         ok = sm >= 0
         blk, off = sm[ok] // bs, sm[ok] % bs
-        kv_cache[blk, 0, :, off, :] = k[ok].to(kv_cache.dtype)
-        kv_cache[blk, 1, :, off, :] = v[ok].to(kv_cache.dtype)
+        if kv_cache.dtype == torch.float8_e4m3fn:  # saturating e4m3 store with unit scales, written through a byte view
+            c8 = kv_cache.view(torch.uint8)
+            c8[blk, 0, :, off, :] = k[ok].float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+            c8[blk, 1, :, off, :] = v[ok].float().clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(torch.uint8)
+        else:
+            kv_cache[blk, 0, :, off, :] = k[ok].to(kv_cache.dtype)
+            kv_cache[blk, 1, :, off, :] = v[ok].to(kv_cache.dtype)
 
 
 # ----------------------------------------------------------------------------- paged attention
@@ -168,8 +173,10 @@ def paged_attention(q, kv_cache, block_table, query_start_loc, seq_lens, scale: 
             continue
         nb = -(-S // bs)
         blocks = block_table[r, :nb].long()
-        kk = kv_cache[blocks, 0].permute(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :S].float()
-        vv = kv_cache[blocks, 1].permute(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :S].float()
+        # an fp8 cache is gathered through a byte view (index ops on float8 tensors are not available everywhere)
+        pages = kv_cache.view(torch.uint8)[blocks].view(torch.float8_e4m3fn) if kv_cache.dtype == torch.float8_e4m3fn else kv_cache[blocks]
+        kk = pages[:, 0].float().permute(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :S]
+        vv = pages[:, 1].float().permute(1, 0, 2, 3).reshape(Hkv, nb * bs, D)[:, :S]
         qq = q[q0:q1].float().permute(1, 0, 2).reshape(Hkv, g, nq, D)
         s = torch.einsum("hgqd,hkd->hgqk", qq, kk) * scale
         qpos = torch.arange(S - nq, S, device=q.device).view(1, 1, nq, 1)

@@ -118,6 +118,7 @@ class ModelRunner:
     def get_kv_cache_specs(self) -> dict:
         mc, specs = self.mc, {}
         esz = torch.empty(0, dtype=self._kv_dtype()).element_size()
+        asz = torch.empty(0, dtype=self._attn_kv_dtype()).element_size()
         for i, layer in self.model.model.local_layers():
             if layer.kind == "linear_attention":
                 (cd, kw), (hv, k, v) = layer.linear_attn.state_shapes()
@@ -127,17 +128,28 @@ class ModelRunner:
             elif layer.kind == "mla":
                 specs[f"layers.{i}"] = KVCacheSpec("mla", self.block_size, 1, mc.kv_lora_rank + mc.qk_rope_head_dim, esz)
             else:
-                specs[f"layers.{i}"] = KVCacheSpec("full", self.block_size, layer.self_attn.Hkv, mc.head_dim, esz)
+                specs[f"layers.{i}"] = KVCacheSpec("full", self.block_size, layer.self_attn.Hkv, mc.head_dim, asz)
         if self.mtp is not None:
             a = self.mtp.layer.self_attn
             if self.mc.use_mla:
                 specs["mtp.0"] = KVCacheSpec("mla", self.block_size, 1, mc.kv_lora_rank + mc.qk_rope_head_dim, esz)
             else:
-                specs["mtp.0"] = KVCacheSpec("full", self.block_size, a.Hkv, mc.head_dim, esz)
+                specs["mtp.0"] = KVCacheSpec("full", self.block_size, a.Hkv, mc.head_dim, asz)
         return specs
 
     def _kv_dtype(self) -> torch.dtype:
         return self.mc.dtype
+
+    def _attn_kv_dtype(self) -> torch.dtype:
+        """Element type of the paged K/V of full-attention layers: ``--kv-cache-dtype fp8`` stores e4m3 bytes with unit scales
+        (reference: config/cache.py ``cache_dtype``; csrc/cache_kernels.cu fp8 store). MLA latents and Gated-DeltaNet states keep
+        the model dtype."""
+        cd = self.cfg.cache_config.cache_dtype
+        if cd in ("auto", "bfloat16", "bf16"):
+            return self.mc.dtype
+        if cd in ("fp8", "fp8_e4m3"):
+            return torch.float8_e4m3fn
+        raise ValueError(f"kv cache dtype {cd!r} is not supported (auto | fp8 | fp8_e4m3)")
 
     def initialize_kv_cache(self, kvc: KVCacheConfig) -> None:
         self.kv_cache_config = kvc
@@ -148,7 +160,7 @@ class ModelRunner:
                 return None
             if spec.kind == "mla":
                 return torch.zeros(nb, bs, spec.head_size, dtype=dt, device=dev)
-            return torch.zeros(nb, 2, spec.num_kv_heads, bs, spec.head_size, dtype=dt, device=dev)
+            return torch.zeros(nb, 2, spec.num_kv_heads, bs, spec.head_size, dtype=self._attn_kv_dtype(), device=dev)
 
         self.kv_caches = []
         for i, layer in self.model.model.local_layers():

@@ -400,6 +400,37 @@ def test_paged_attention_window_softcap_sinks(name, qlens, ctxs, Hq, Hkv, D, win
         assert (full.float() - e.float()).abs().max() > 1e-2   # the window changes the answer in these cases
 
 
+def test_fp8_kv_cache_store_and_attention():
+    """An e4m3 KV cache: the rope + insert kernel stores saturated e4m3 bytes equal to the oracle's, and decode, verify and prefill
+    attention over such a cache match the fp32 oracle reading the same bytes."""
+    T, Hq, Hkv, D, bs, nb = 50, 8, 2, 128, 16, 10
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(T, Hq, D, device="cuda", generator=g).bfloat16()
+    k = (torch.randn(T, Hkv, D, device="cuda", generator=g) * 3).bfloat16()
+    v = (torch.randn(T, Hkv, D, device="cuda", generator=g) * 300).bfloat16()   # some values saturate at 448
+    pos = torch.arange(T, device="cuda", dtype=torch.int32)
+    cs = ref.build_cos_sin_cache(D, 512, 1e6, "cuda")
+    cache = torch.zeros(nb, 2, Hkv, bs, D, device="cuda", dtype=torch.float8_e4m3fn)
+    slots = torch.randperm(nb * bs, device="cuda")[:T].to(torch.int32)
+    qc, kc, vc, cache_c = q.cpu().clone(), k.cpu().clone(), v.cpu().clone(), cache.cpu().clone()
+    ref.rope_and_cache(qc, kc, vc, pos.cpu(), cs.cpu(), cache_c, slots.cpu(), D)
+    K().rope_and_cache(q, k, v, pos, cs, cache, slots, D, None, None, 1e-6, False)
+    torch.cuda.synchronize()
+    a, b = cache.cpu().view(torch.uint8).int(), cache_c.view(torch.uint8).int()
+    # k goes through a bf16 rotation on both sides: allow the last e4m3 step on a handful of values
+    assert ((a - b).abs() <= 1).all() and (a != b).float().mean() < 0.01
+    assert (a[:, 1] == b[:, 1]).all()
+    for name, qlens, ctxs, hq, hkv, d in [("decode", [1] * 5, [0, 100, 1000, 3000, 63], 40, 8, 128), ("verify", [4] * 3, [10, 600, 2000], 8, 2, 256),
+                                          ("prefill", [300, 70, 513], [0, 200, 64], 16, 4, 128), ("prefill-d256", [200, 3], [100, 77], 8, 2, 256)]:
+        qq, cache_bf, md = _attn_case(qlens, ctxs, hq, hkv, d, seed=5)
+        c8 = cache_bf.to(torch.float8_e4m3fn)
+        out = K().paged_attention(qq, c8, md, d ** -0.5)
+        torch.cuda.synchronize()
+        assert K().check_status() == 0
+        e = ref.paged_attention(qq.cpu(), c8.cpu(), md.block_table.cpu(), md.query_start_loc.cpu(), md.seq_lens.cpu(), d ** -0.5)
+        _close(out, e, 2e-2, 1e-2, name)
+
+
 def test_paged_attention_forced_splits():
     q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
     from onecat_vllm.ops.cuda import plan_attention

@@ -53,26 +53,25 @@ __device__ __forceinline__ uint32_t sw_off(int row, int chunk) {
   return (uint32_t)(row * D * 2 + ((chunk ^ (row & 7)) << 4));
 }
 
-// 16 e4m3 bytes -> 16 bf16 (exact: every e4m3 value is a bf16 value)
+// 16 e4m3 bytes -> 16 bf16, exactly (every e4m3 value is a bf16 value). A byte's sign goes to bit 15 and its exponent and mantissa
+// four places below the top of the bf16 exponent field, which reads as value * 2^-120 (e4m3 subnormals become bf16 subnormals);
+// one bf16x2 multiply by 2^120 restores the value.
+__device__ __forceinline__ uint32_t widen_fp8_pair(uint32_t w, uint32_t sel) {
+  uint32_t t;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(t) : "r"(w), "r"(0u), "r"(sel));
+  uint32_t v = (t & 0x80008000u) | ((t >> 4) & 0x07f007f0u);
+  const uint32_t two120 = 0x7b807b80u;
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<const __nv_bfloat162*>(&two120));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
 __device__ __forceinline__ void widen_fp8x16(const uint4& in, uint4& lo, uint4& hi) {
-  const uint32_t w[4] = {in.x, in.y, in.z, in.w};
-  uint32_t o[8];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      __half2_raw r = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)((w[i] >> (16 * h)) & 0xffffu), __NV_E4M3);
-      float2 f = __half22float2(*reinterpret_cast<__half2*>(&r));
-      o[i * 2 + h] = pack_bf16(f.x, f.y);
-    }
-  }
-  lo = make_uint4(o[0], o[1], o[2], o[3]);
-  hi = make_uint4(o[4], o[5], o[6], o[7]);
+  lo = make_uint4(widen_fp8_pair(in.x, 0x1404u), widen_fp8_pair(in.x, 0x3424u), widen_fp8_pair(in.y, 0x1404u), widen_fp8_pair(in.y, 0x3424u));
+  hi = make_uint4(widen_fp8_pair(in.z, 0x1404u), widen_fp8_pair(in.z, 0x3424u), widen_fp8_pair(in.w, 0x1404u), widen_fp8_pair(in.w, 0x3424u));
 }
 
 template <int D, int MODE, int MB, bool KV8>
 __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
-  constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring
+  constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring (a fourth stage of byte tiles measured no faster)
   constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
   constexpr int NB2 = (MODE == 0) ? 4 : 1;      // 16-key groups per warp per tile
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;

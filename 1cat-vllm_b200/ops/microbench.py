@@ -97,7 +97,8 @@ def bench_attn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.worker.attn_metadata import AttentionMetadata
     cases = [("decode", 64, 1, 1150, 40, 8, 128), ("decode", 8, 1, 32768, 40, 8, 128), ("decode-d256", 64, 1, 2048, 24, 4, 256),
-             ("prefill", 8, 1024, 0, 40, 8, 128), ("prefill", 1, 8192, 0, 40, 8, 128), ("prefill-d256", 1, 4096, 0, 24, 4, 256)]
+             ("prefill", 8, 1024, 0, 40, 8, 128), ("prefill", 1, 8192, 0, 40, 8, 128), ("prefill-d256", 1, 4096, 0, 24, 4, 256),
+             ("decode-fp8kv", 64, 1, 1150, 40, 8, 128), ("decode-fp8kv", 8, 1, 32768, 40, 8, 128), ("decode-window128", 64, 1, 1150, 40, 8, 128)]
     if small:
         cases = [("decode", 64, 1, 1150, 40, 8, 128)]
     if prefill_only:
@@ -107,6 +108,9 @@ def bench_attn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool
         nb = -(-S // 16)
         total = R * nb + 1
         cache = (torch.randn(total, 2, Hkv, 16, D, device="cuda") * 0.3).bfloat16()
+        if "fp8kv" in name:
+            cache = cache.to(torch.float8_e4m3fn)
+        window = 128 if "window" in name else 0
         bt = (torch.arange(R * nb, device="cuda", dtype=torch.int32) + 1).view(R, nb)
         T = R * ql
         q = (torch.randn(T, Hq, D, device="cuda") * 0.3).bfloat16()
@@ -114,8 +118,8 @@ def bench_attn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool
         sl = torch.full((R,), S, device="cuda", dtype=torch.int32)
         md = AttentionMetadata(R, T, qsl, sl, bt, None, None, ql, S, query_lens_cpu=[ql] * R, seq_lens_cpu=[S] * R)
         out = torch.empty(T, Hq, D, device="cuda", dtype=torch.bfloat16)
-        ms = timeit(lambda: K.paged_attention(q, cache, md, D ** -0.5, out=out), 1 if small else iters, 1 if small else 3)
-        kv_bytes = R * S * 2 * Hkv * D * 2
+        ms = timeit(lambda: K.paged_attention(q, cache, md, D ** -0.5, out=out, window=window), 1 if small else iters, 1 if small else 3)
+        kv_bytes = R * (min(S, window) if window else S) * 2 * Hkv * D * cache.element_size()
         flops = 4.0 * R * Hq * D * (ql * ctx + ql * (ql + 1) / 2)
         rows.append(dict(kernel="paged_attention", case=name, R=R, q_len=ql, ctx=ctx, Hq=Hq, Hkv=Hkv, D=D, ms=ms, kv_gbs=kv_bytes / ms / 1e6,
                          frac_of_hbm=kv_bytes / ms / 1e6 / pk["hbm_gbs"], tflops=flops / ms / 1e9, plan=md.attn_plan[1]))

@@ -31,15 +31,16 @@ def _make_checkpoint(tmp_path, cfg=CFG):
     return str(tmp_path)
 
 
-@pytest.mark.parametrize("eager,cfg", [(True, CFG), (False, CFG), (False, CFG_GEMMA2)], ids=["eager", "graphs", "gemma2-graphs"])
-def test_engine_gpu_matches_cpu(tmp_path, eager, cfg):
+@pytest.mark.parametrize("eager,cfg,kvd", [(True, CFG, "auto"), (False, CFG, "auto"), (False, CFG_GEMMA2, "auto"), (False, CFG, "fp8")],
+                         ids=["eager", "graphs", "gemma2-graphs", "fp8kv-graphs"])
+def test_engine_gpu_matches_cpu(tmp_path, eager, cfg, kvd):
     from onecat_vllm import LLM, SamplingParams
     path = _make_checkpoint(tmp_path, cfg)
     g = torch.Generator().manual_seed(0)
     prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in (5, 40, 130, 17, 64, 300)]
     sp = SamplingParams(temperature=0.0, max_tokens=24, ignore_eos=True, logprobs=0)
     gpu = LLM(model=path, device="cuda", dtype="bfloat16", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8,
-              gpu_memory_utilization=0.3, enforce_eager=eager)
+              gpu_memory_utilization=0.3, enforce_eager=eager, kv_cache_dtype=kvd)
     og = gpu.generate(prompts, sp)
     runner = gpu.llm_engine.engine_core.core.executor.worker.runner
     if not eager:
@@ -48,7 +49,7 @@ def test_engine_gpu_matches_cpu(tmp_path, eager, cfg):
     assert K.check_status() == 0
     assert not K.TORCH_STANDINS, f"ops fell back to device-side PyTorch: {K.TORCH_STANDINS}"
     gpu.shutdown()
-    cpu = LLM(model=path, device="cpu", dtype="float32", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8)
+    cpu = LLM(model=path, device="cpu", dtype="float32", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8, kv_cache_dtype=kvd)
     # teacher-forced agreement: feed the GPU's own tokens to the CPU model and require each GPU token to be near the top
     # random weights give nearly flat logits, so greedy paths may fork on near-ties: require (a) close log-probabilities of the
     # first generated token wherever both runs picked the same one, (b) a reasonable common prefix overall

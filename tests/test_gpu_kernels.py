@@ -431,6 +431,29 @@ def test_fp8_kv_cache_store_and_attention():
         _close(out, e, 2e-2, 1e-2, name)
 
 
+def test_fp8_kv_cache_values_are_read_exactly():
+    """With a single key the attention output is that key's value row: every finite e4m3 code (subnormals included) must come back
+    as exactly its value."""
+    D, bs = 128, 16
+    codes = torch.tensor([c for c in range(256) if c & 0x7f != 0x7f], dtype=torch.uint8)   # 0x7f / 0xff are NaN
+    rows = -(-codes.numel() // D)
+    pad = torch.zeros(rows * D, dtype=torch.uint8)
+    pad[: codes.numel()] = codes
+    cache = torch.zeros(rows, 2, 1, bs, D, dtype=torch.uint8, device="cuda")
+    cache[:, 1, 0, 0, :] = pad.view(rows, D).cuda()
+    c8 = cache.view(torch.float8_e4m3fn)
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    q = torch.randn(rows, 1, D, device="cuda").bfloat16()
+    qsl = torch.arange(rows + 1, dtype=torch.int32, device="cuda")
+    sl = torch.ones(rows, dtype=torch.int32, device="cuda")
+    bt = torch.arange(rows, dtype=torch.int32, device="cuda").view(rows, 1)
+    md = AttentionMetadata(rows, rows, qsl, sl, bt, None, None, 1, 1, query_lens_cpu=[1] * rows, seq_lens_cpu=[1] * rows)
+    out = K().paged_attention(q, c8, md, D ** -0.5)
+    torch.cuda.synchronize()
+    want = pad.view(torch.float8_e4m3fn).float().view(rows, D)
+    assert torch.equal(out.float().cpu().view(rows, D), want)
+
+
 def test_paged_attention_forced_splits():
     q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
     from onecat_vllm.ops.cuda import plan_attention

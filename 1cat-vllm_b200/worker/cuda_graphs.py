@@ -94,6 +94,7 @@ class DecodeGraphs:
         r = self.r
         r.np_pack[:] = 0
         r.np_bt[:] = 0
+        r._bt_owner = [None] * len(r._bt_owner)
         o = r._off
         r.np_pack[o["slot"][0]: o["slot"][0] + o["slot"][1]] = -1
         r.d_pack.copy_(r.h_pack)

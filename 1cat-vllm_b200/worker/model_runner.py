@@ -205,6 +205,8 @@ class ModelRunner:
             off += n
         self.np_pack = self.h_pack.numpy()
         self.np_bt = self.h_bt.numpy()
+        # per block-table row: the request state that owns it and how many of its blocks are already written there
+        self._bt_owner, self._bt_written = [None] * self.np_bt.shape[0], [0] * self.np_bt.shape[0]
 
     def _view(self, name: str, n: int, dev: bool = True) -> torch.Tensor:
         o, _ = self._off[name]
@@ -269,6 +271,7 @@ class ModelRunner:
         n_l = 0
         max_nb = 1
         drafts_of: list = []
+        bt_owner, bt_written = self._bt_owner, self._bt_written
         for r, rid in enumerate(req_ids):
             st = self.requests[rid]
             n = so.num_scheduled_tokens[rid]
@@ -276,18 +279,34 @@ class ModelRunner:
             drafts = so.scheduled_spec_decode_tokens.get(rid, [])
             known = st.token_ids
             end = start + n
-            nk = min(end, len(known)) - start
-            if nk > 0:
-                ids[t:t + nk] = known[start:start + nk]
-            if end > len(known):
-                nd = end - len(known)
-                ids[t + nk:t + n] = drafts[:nd]
-            pos[t:t + n] = np.arange(start, end, dtype=np.int32)
-            b = np.asarray(st.block_ids, dtype=np.int32)
-            p = pos[t:t + n]
-            slot[t:t + n] = b[p // bs] * bs + p % bs
+            bl = st.block_ids
             nb = -(-end // bs)
-            self.np_bt[r, :nb] = b[:nb]
+            if n == 1 and start < len(known):
+                # plain decode row: scalar writes, no temporaries
+                ids[t] = known[start]
+                pos[t] = start
+                slot[t] = bl[start // bs] * bs + start % bs
+            else:
+                nk = min(end, len(known)) - start
+                if nk > 0:
+                    ids[t:t + nk] = known[start:start + nk]
+                if end > len(known):
+                    nd = end - len(known)
+                    ids[t + nk:t + n] = drafts[:nd]
+                pos[t:t + n] = np.arange(start, end, dtype=np.int32)
+                b0 = start // bs
+                b = np.asarray(bl[b0:nb], dtype=np.int32)
+                p = pos[t:t + n]
+                slot[t:t + n] = b[p // bs - b0] * bs + p % bs
+            # block-table row: a request that kept its row only appends the blocks it gained (its list is append-only)
+            if bt_owner[r] is st and bt_written[r] <= nb:
+                w = bt_written[r]
+                if w < nb:
+                    self.np_bt[r, w:nb] = bl[w:nb]
+            else:
+                self.np_bt[r, :nb] = bl[:nb]
+                bt_owner[r] = st
+            bt_written[r] = nb
             max_nb = max(max_nb, nb)
             seq[r] = end
             sslot[r] = st.state_slot
@@ -320,6 +339,8 @@ class ModelRunner:
         npk[o["sslot"][0] + R: o["sslot"][0] + rp] = 0
         npk[o["hinit"][0] + R: o["hinit"][0] + rp] = 0
         self.np_bt[R:rp, :1] = 0
+        for r in range(R, rp):
+            self._bt_owner[r] = None
 
     def _commit_inputs(self, R: int, T: int, n_l: int, max_nb: int) -> None:
         """Host → device copies of this step's inputs (non-blocking from pinned memory on GPUs)."""

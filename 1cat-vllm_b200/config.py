@@ -315,6 +315,7 @@ class CacheConfig:
     cpu_offload_gb: float = 0.0
     kv_offloading_size: float = 0.0  # GiB of host memory for KV blocks evicted from the GPU prefix cache (0 = off)
     num_cpu_blocks_override: Optional[int] = None
+    kv_offloading_policy: str = "lru"  # lru | arc: which host block is dropped when the tier is full
     kv_events_config: Optional[dict] = None  # {"enable_kv_cache_events": true, "endpoint": "tcp://127.0.0.1:5557", "topic": "kv-events"}
     kv_transfer_config: Optional[dict] = None  # {"kv_connector": "SharedStorageConnector", "kv_role": ..., "kv_connector_extra_config": {...}}
     num_gpu_blocks: int = 0  # filled in after profiling
@@ -503,6 +504,7 @@ class EngineArgs:
     kv_cache_dtype: str = "auto"
     kv_offloading_size: float = 0.0
     num_cpu_blocks_override: Optional[int] = None
+    kv_offloading_policy: str = "lru"  # lru | arc: which host block is dropped when the tier is full
     kv_transfer_config: Optional[Union[dict, str]] = None
     kv_events_config: Optional[Union[dict, str]] = None
     max_num_batched_tokens: int = 8192
@@ -551,7 +553,7 @@ class EngineArgs:
             model_config=mc,
             cache_config=CacheConfig(self.block_size, self.gpu_memory_utilization, self.num_gpu_blocks_override,
                                      self.kv_cache_memory_bytes, self.enable_prefix_caching, cache_dtype=self.kv_cache_dtype,
-                                     kv_offloading_size=self.kv_offloading_size, num_cpu_blocks_override=self.num_cpu_blocks_override,
+                                     kv_offloading_size=self.kv_offloading_size, num_cpu_blocks_override=self.num_cpu_blocks_override, kv_offloading_policy=self.kv_offloading_policy,
                                      kv_transfer_config=json.loads(self.kv_transfer_config) if isinstance(self.kv_transfer_config, str)
                                      else self.kv_transfer_config,
                                      kv_events_config=json.loads(self.kv_events_config) if isinstance(self.kv_events_config, str)

@@ -42,8 +42,12 @@ class KVCacheManager:
         self.needs_state = num_state_slots > 0
         self.offload = None
 
-    def enable_cpu_offload(self, num_cpu_blocks: int) -> None:
-        from onecat_vllm.core.kv_offload import CPUOffloadTier
+    def enable_cpu_offload(self, num_cpu_blocks: int, policy: str = "lru") -> None:
+        from onecat_vllm.core.kv_offload import ARCOffloadTier, CPUOffloadTier
+        if policy not in ("lru", "arc"):
+            raise ValueError(f"kv offloading policy {policy!r} is not supported (lru | arc)")
+        if policy == "arc":
+            CPUOffloadTier = ARCOffloadTier
         if self.enable_caching and num_cpu_blocks > 0:
             self.offload = self.block_pool.offload = CPUOffloadTier(num_cpu_blocks)
 

@@ -63,6 +63,93 @@ class CPUOffloadTier:
         self.swap_out, self.swap_in = [], []
 
 
+class ARCOffloadTier(CPUOffloadTier):
+    """The same tier with adaptive-replacement eviction: resident blocks live in a recency list T1 (seen once) or a frequency list
+    T2 (seen again); hashes of recently evicted blocks are remembered in ghost lists B1 / B2, and a hit on a ghost moves the target
+    size ``p`` of T1 towards whichever list would have kept the block (reference: v1/kv_offload/ ARC policy of the CPU offloading
+    manager; Megiddo & Modha's algorithm). A scan of one-off prefixes therefore cannot flush the blocks that are re-used."""
+
+    def __init__(self, num_cpu_blocks: int) -> None:
+        super().__init__(num_cpu_blocks)
+        self.t1: "OrderedDict[bytes, int]" = OrderedDict()
+        self.t2: "OrderedDict[bytes, int]" = OrderedDict()
+        self.b1: "OrderedDict[bytes, None]" = OrderedDict()
+        self.b2: "OrderedDict[bytes, None]" = OrderedDict()
+        self.p = 0.0
+
+    def _evict_from(self, lst: OrderedDict, ghosts: OrderedDict) -> bool:
+        busy = {c for c, _ in self.swap_in}
+        victim = next((h for h, c in lst.items() if c not in busy), None)
+        if victim is None:
+            return False
+        self.free.append(lst.pop(victim))
+        self.index.pop(victim, None)
+        ghosts[victim] = None
+        return True
+
+    def _replace(self, in_b2: bool) -> bool:
+        if self.t1 and (len(self.t1) > self.p or (in_b2 and len(self.t1) == int(self.p))):
+            return self._evict_from(self.t1, self.b1) or self._evict_from(self.t2, self.b2)
+        return self._evict_from(self.t2, self.b2) or self._evict_from(self.t1, self.b1)
+
+    def on_evict(self, block_hash: bytes, gpu_block: int) -> None:
+        c = self.capacity
+        if c == 0:
+            return
+        if block_hash in self.index:   # already resident: a second sighting
+            self.lookup(block_hash)
+            return
+        target = self.t1
+        if block_hash in self.b1:
+            self.p = min(float(c), self.p + max(1.0, len(self.b2) / max(len(self.b1), 1)))
+            del self.b1[block_hash]
+            target = self.t2
+            if not self.free and not self._replace(False):
+                return
+        elif block_hash in self.b2:
+            self.p = max(0.0, self.p - max(1.0, len(self.b1) / max(len(self.b2), 1)))
+            del self.b2[block_hash]
+            target = self.t2
+            if not self.free and not self._replace(True):
+                return
+        else:
+            if len(self.t1) + len(self.b1) >= c:
+                if len(self.t1) < c:
+                    self.b1.popitem(last=False)
+                    if not self.free and not self._replace(False):
+                        return
+                elif not self._evict_from(self.t1, self.b1):
+                    return
+                else:
+                    self.b1.popitem()   # a block dropped from a full T1 leaves no ghost
+            else:
+                total = len(self.t1) + len(self.t2) + len(self.b1) + len(self.b2)
+                if total >= c:
+                    if total >= 2 * c and self.b2:
+                        self.b2.popitem(last=False)
+                    if not self.free and not self._replace(False):
+                        return
+        if not self.free:
+            return
+        blk = self.free.pop()
+        target[block_hash] = blk
+        self.index[block_hash] = blk
+        self.swap_out.append((gpu_block, blk))
+        self.stored += 1
+
+    def lookup(self, block_hash: bytes) -> Optional[int]:
+        if block_hash in self.t1:
+            self.t2[block_hash] = self.t1.pop(block_hash)
+        elif block_hash in self.t2:
+            self.t2.move_to_end(block_hash)
+        return self.index.get(block_hash)
+
+    def reset(self) -> None:
+        super().reset()
+        self.t1.clear(), self.t2.clear(), self.b1.clear(), self.b2.clear()
+        self.p = 0.0
+
+
 class SharedStorageTier:
     """KV connector over a shared directory: every prefix block that becomes full is written through to ``<dir>/<hash>.kv`` and a
     later request — in this engine or in another one pointed at the same directory — restores it instead of recomputing. This is

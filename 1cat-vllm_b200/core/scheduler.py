@@ -123,7 +123,7 @@ class Scheduler:
         if cc.kv_transfer_config:
             self.kv_cache_manager.enable_kv_connector(cc.kv_transfer_config)
         elif cc.num_cpu_blocks > 0:
-            self.kv_cache_manager.enable_cpu_offload(cc.num_cpu_blocks)
+            self.kv_cache_manager.enable_cpu_offload(cc.num_cpu_blocks, cc.kv_offloading_policy)
         self.block_hasher = make_block_hasher(self.kv_cache_manager.block_size, cc.prefix_caching_hash_algo) \
             if self.kv_cache_manager.enable_caching else None
         self.requests: dict[str, Request] = {}

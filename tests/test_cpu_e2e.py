@@ -140,6 +140,46 @@ def test_cpu_offload_tier_restores_evicted_prefix_blocks():
     llm.shutdown()
 
 
+def test_arc_offload_policy_keeps_reused_blocks_through_a_scan():
+    """Unit behaviour of the adaptive-replacement tier: blocks seen twice survive a scan of one-off blocks that would flush an LRU
+    tier of the same size; and the engine produces the same tokens with it."""
+    from onecat_vllm.core.kv_offload import ARCOffloadTier, CPUOffloadTier
+    hot = [bytes([1, i]) for i in range(4)]
+    scan = [bytes([2, i]) for i in range(40)]
+    survivors = {}
+    for cls in (CPUOffloadTier, ARCOffloadTier):
+        t = cls(8)
+        for h in hot:
+            t.on_evict(h, 0)
+        for h in hot:
+            assert t.lookup(h) is not None      # second sighting: frequent
+        for h in scan:
+            t.on_evict(h, 0)
+            t.take_ops()
+        survivors[cls.__name__] = sum(t.lookup(h) is not None for h in hot)
+        blocks = [c for c in t.index.values()]
+        assert len(blocks) == len(set(blocks)) and len(blocks) + len(t.free) == 8   # no host block is lost or handed out twice
+    assert survivors["CPUOffloadTier"] == 0 and survivors["ARCOffloadTier"] == 4, survivors
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=512)
+    prefix = [(3 * i) % 290 + 1 for i in range(160)]
+    reqs = [[{"prompt_token_ids": prefix + [7, 8, 9]}]] + [[{"prompt_token_ids": [(11 * i + j) % 290 + 1 for i in range(150)]}] for j in range(3)] \
+        + [[{"prompt_token_ids": prefix + [20, 21]}]]
+    sp = SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)
+    kw = dict(hf_config=cfg, device="cpu", dtype="float32", max_model_len=256, num_gpu_blocks_override=24, max_num_seqs=1)
+    plain = LLM(**kw)
+    want = [plain.generate(x, sp)[0].outputs[0].token_ids for x in reqs]
+    plain.shutdown()
+    llm = LLM(num_cpu_blocks_override=64, kv_offloading_policy="arc", **kw)
+    tier = llm.llm_engine.engine_core.core.scheduler.kv_cache_manager.offload
+    assert isinstance(tier, ARCOffloadTier)
+    got = [llm.generate(x, sp)[0] for x in reqs]
+    assert [g.outputs[0].token_ids for g in got] == want
+    assert tier.restored >= 10 and got[-1].num_cached_tokens >= 160
+    llm.shutdown()
+
+
 def test_shared_storage_connector_hands_prefill_kv_to_another_engine(tmp_path):
     """Disaggregated prefill / decode through the shared-storage KV connector: a producer engine runs the prompt once, a second
     (consumer) engine restores the blocks by hash and continues with the same tokens as an engine that computed everything itself."""

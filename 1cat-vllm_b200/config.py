@@ -398,7 +398,7 @@ class SpeculativeConfig:
     rejection sampler uses the conditional form ``rate[i] / rate[i-1]``.
     """
 
-    method: Optional[str] = None  # None | "mtp" | "ngram" | "eagle" | "medusa"
+    method: Optional[str] = None  # None | "mtp" | "ngram" | "suffix" | "eagle" | "medusa"
     num_speculative_tokens: int = 0
     model: Optional[str] = None  # eagle / medusa: directory of the draft heads' checkpoint (random weights when absent)
     medusa_num_layers: int = 1  # residual blocks per Medusa head

@@ -169,7 +169,10 @@ bool spin_wait_changed(py::buffer b, size_t offset, uint64_t old, double timeout
 
 }  // namespace
 
+void register_drafting(py::module_& m);  // ngram.cpp
+
 PYBIND11_MODULE(_native, m) {
+  register_drafting(m);
   py::class_<ShmRing>(m, "ShmRing")
       .def(py::init<const std::string&, int, int, int, bool>(), py::arg("name"), py::arg("n_readers"), py::arg("max_chunks"), py::arg("chunk_bytes"),
            py::arg("create"))

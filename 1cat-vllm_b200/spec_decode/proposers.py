@@ -21,8 +21,18 @@ class NgramProposer:
 
     def __init__(self, k: int, min_n: int, max_n: int):
         self.k, self.min_n, self.max_n = k, min_n, max_n
+        try:  # the C++ scan (csrc/native/ngram.cpp); the Python loop below is its restatement and the fallback
+            from onecat_vllm.utils import _native
+            self._native = _native.ngram_propose
+        except ImportError:
+            self._native = None
 
     def propose_one(self, tokens: list) -> list:
+        if self._native is not None:
+            return self._native(np.asarray(tokens, dtype=np.int32), self.min_n, self.max_n, self.k)
+        return self.propose_one_py(tokens)
+
+    def propose_one_py(self, tokens: list) -> list:
         n_tok = len(tokens)
         for n in range(min(self.max_n, n_tok - 1), self.min_n - 1, -1):
             pat = tokens[n_tok - n:]
@@ -38,6 +48,34 @@ class NgramProposer:
         for rid, s in zip(req_ids, sampled):
             st = runner.requests[rid]
             out.append(self.propose_one(st.token_ids) if s else [])
+        return out
+
+
+class SuffixProposer(NgramProposer):
+    """Suffix-cache drafting: the request's own context first (prompt lookup), then a bounded index of the sequences that earlier
+    requests of this engine finished, so repeated answers are drafted from their previous occurrence (reference:
+    v1/spec_decode/suffix_decoding.py). The index is the C++ ``SuffixIndex``."""
+
+    def __init__(self, k: int, min_n: int, max_n: int, max_tokens: int = 1 << 22):
+        super().__init__(k, min_n, max_n)
+        from onecat_vllm.utils import _native
+        self.index = _native.SuffixIndex(min_n, max_n, max_tokens)
+        self._live: dict = {}
+
+    def propose(self, runner, so, req_ids, rows, sampled, hidden, md, drafts_of):
+        # sequences of requests that left the batch since the last call go into the index
+        for rid in [r for r in self._live if r not in runner.requests]:
+            self.index.add(np.asarray(self._live.pop(rid), dtype=np.int32))
+        out = []
+        for rid, s in zip(req_ids, sampled):
+            st = runner.requests[rid]
+            self._live[rid] = st.token_ids
+            if not s:
+                out.append([])
+                continue
+            toks = np.asarray(st.token_ids, dtype=np.int32)
+            d = self._native(toks, self.min_n, self.max_n, self.k)
+            out.append(d if d else self.index.propose(toks[-self.max_n:], self.k))
         return out
 
 
@@ -191,6 +229,8 @@ def make_proposer(runner):
         return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
     if sc.method in ("mtp", "eagle"):
         return MTPProposer(runner)
+    if sc.method == "suffix":
+        return SuffixProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
     if sc.method == "medusa":
         return MedusaProposer(runner)
     raise ValueError(f"unknown speculative method {sc.method!r}")

@@ -258,3 +258,31 @@ def test_medusa_heads_are_lossless_and_load(tmp_path):
     out = [o.outputs[0].token_ids for o in llm.generate(p, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
     llm.shutdown()
     assert out == ref
+
+
+def test_native_ngram_lookup_matches_python_and_suffix_cache_drafts_across_requests():
+    import numpy as np
+    from onecat_vllm.spec_decode.proposers import NgramProposer
+    p = NgramProposer(3, 2, 4)
+    assert p._native is not None, "the native module must be built"
+    rng = np.random.default_rng(0)
+    for _ in range(200):
+        toks = rng.integers(0, 6, size=int(rng.integers(1, 60))).tolist()
+        assert list(p.propose_one(toks)) == p.propose_one_py(toks), toks
+    # suffix cache: the second run of the same prompt drafts the first run's answer and accepts it
+    dense = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256)
+    prompts = _prompts(500)[:2]
+    ref = _gen(dense, prompts)
+    llm = LLM(hf_config=dense, max_model_len=256, dtype="float32", device="cpu", enable_prefix_caching=False,
+              speculative_config=dict(method="suffix", num_speculative_tokens=3))
+    sp = SamplingParams(temperature=0, max_tokens=16, ignore_eos=True)
+    first = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    second = [o.outputs[0].token_ids for o in llm.generate(prompts, sp)]
+    prop = llm.llm_engine.engine_core.core.executor.worker.runner.proposer
+    assert prop.index.num_sequences >= 2
+    seq = list(prompts[0]["prompt_token_ids"] if isinstance(prompts[0], dict) else prompts[0]) + first[0]
+    cut = len(seq) - 10
+    assert list(prop.index.propose(np.asarray(seq[cut - 4:cut], dtype=np.int32), 3)) == seq[cut:cut + 3]
+    llm.shutdown()
+    assert first == ref and second == ref

@@ -334,6 +334,40 @@ void gdn_conv_commit(torch::Tensor mixed, torch::Tensor conv_state, torch::Tenso
   TORCH_CHECK(oc::gdn_conv_commit_launch(cp, cur_stream()) == 0, "gdn conv commit failed");
 }
 
+// Temperature / min-p / top-k / top-p / random draw for each row of `logits` in one kernel. Returns the token ids [B] (int64).
+torch::Tensor sample(torch::Tensor logits, torch::Tensor temperature, c10::optional<torch::Tensor> top_k, c10::optional<torch::Tensor> top_p,
+                     c10::optional<torch::Tensor> min_p, torch::Tensor seeds, c10::optional<torch::Tensor> kept) {
+  TORCH_CHECK(logits.is_cuda() && logits.dim() == 2 && logits.stride(1) == 1, "logits must be a CUDA [B, V] matrix");
+  const bool f32 = logits.scalar_type() == torch::kFloat32;
+  TORCH_CHECK(f32 || logits.scalar_type() == torch::kBFloat16, "logits must be fp32 or bf16");
+  const int64_t B = logits.size(0);
+  auto chk = [&](const torch::Tensor& t, c10::ScalarType ty, const char* name) {
+    TORCH_CHECK(t.is_cuda() && t.scalar_type() == ty && t.is_contiguous() && t.numel() == B, name, " must be a contiguous CUDA vector with one entry per row");
+  };
+  chk(temperature, torch::kFloat32, "temperature");
+  chk(seeds, torch::kInt64, "seeds");
+  const c10::cuda::CUDAGuard guard(logits.device());
+  oc::SampleParams p{};
+  p.logits = logits.data_ptr();
+  p.is_fp32 = f32;
+  p.ld = logits.stride(0);
+  p.B = (int)B;
+  p.V = (int)logits.size(1);
+  p.temperature = temperature.data_ptr<float>();
+  if (top_k.has_value()) { chk(*top_k, torch::kInt32, "top_k"); p.top_k = top_k->data_ptr<int>(); }
+  if (top_p.has_value()) { chk(*top_p, torch::kFloat32, "top_p"); p.top_p = top_p->data_ptr<float>(); }
+  if (min_p.has_value()) { chk(*min_p, torch::kFloat32, "min_p"); p.min_p = min_p->data_ptr<float>(); }
+  p.seeds = (const unsigned long long*)seeds.data_ptr<int64_t>();
+  auto out = torch::empty({B}, logits.options().dtype(torch::kInt64));
+  p.out = (long long*)out.data_ptr<int64_t>();
+  if (kept.has_value()) {
+    TORCH_CHECK(kept->is_cuda() && kept->scalar_type() == torch::kUInt8 && kept->is_contiguous() && kept->numel() == B * logits.size(1), "kept must be uint8 [B, V]");
+    p.kept = kept->data_ptr<uint8_t>();
+  }
+  TORCH_CHECK(oc::sample_launch(p, cur_stream()) == 0, "sample launch failed");
+  return out;
+}
+
 torch::Tensor rejection_sample(torch::Tensor draft_ids, torch::Tensor num_draft, torch::Tensor target_logits, torch::Tensor bonus_ids,
                                torch::Tensor uniforms, c10::optional<torch::Tensor> temperature, c10::optional<torch::Tensor> synth_rates,
                                int64_t seed, bool use_noise) {
@@ -559,6 +593,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("mla_decode", &mla_decode);
   m.def("fused_moe", &fused_moe);
   m.def("rejection_sample", &rejection_sample);
+  m.def("sample", &sample);
   m.def("route", &route);
   m.def("gdn_forward", &gdn_forward);
   m.def("gdn_conv_commit", &gdn_conv_commit);

@@ -71,6 +71,21 @@ int rejection_launch(const void* logits, int is_fp32, const long long* draft_ids
                      const double* uniforms, const float* temperature, const float* synth_rates, RowStats* stats, long long* out, int B, int k, int V,
                      long long ld_b, long long ld_pos, unsigned long long seed, int use_noise, cudaStream_t st);
 
+struct SampleParams {
+  const void* logits;        // [B][ld] fp32 or bf16
+  int is_fp32;
+  long long ld;
+  int B, V;
+  const float* temperature;  // [B]; below 1e-5 the row takes its arg-max
+  const int* top_k;          // [B] or null; <= 0 or >= V: off
+  const float* top_p;        // [B] or null; >= 1: off
+  const float* min_p;        // [B] or null; <= 0: off
+  const unsigned long long* seeds;  // [B] one random 64-bit word per row and step
+  long long* out;            // [B] sampled token ids
+  unsigned char* kept;       // [B][V] or null: 1 where the token survived the filters
+};
+int sample_launch(const SampleParams& p, cudaStream_t st);
+
 struct RouteParams {
   const __nv_bfloat16* logits;  // [T][ld]
   long long ld;

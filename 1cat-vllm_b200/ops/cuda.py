@@ -354,6 +354,20 @@ def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_d
     _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, 1.0, 1.0)
 
 
+def sample(logits, temperature, top_k=None, top_p=None, min_p=None, generators=None, kept=None):
+    """One kernel per batch: temperature, min-p, top-k, top-p and the random draw (rows with temperature ~ 0 take their arg-max).
+    Each row gets a 64-bit word of randomness: from its request's generator when it has one (so seeded requests repeat), else from
+    the device's default generator."""
+    global _LAUNCHES
+    _LAUNCHES += 2
+    B = logits.shape[0]
+    seeds = torch.randint(0, 1 << 62, (B,), dtype=torch.int64, device=logits.device)
+    for i, gen in (generators or {}).items():
+        seeds[i] = torch.randint(0, 1 << 62, (1,), dtype=torch.int64, device=logits.device, generator=gen)[0]
+    return _C.sample(logits, temperature.float().contiguous(), None if top_k is None else top_k.to(torch.int32).contiguous(),
+                     None if top_p is None else top_p.float().contiguous(), None if min_p is None else min_p.float().contiguous(), seeds, kept)
+
+
 def argmax(logits):
     global _LAUNCHES
     _LAUNCHES += 1

@@ -94,6 +94,10 @@ class Sampler:
 
     @staticmethod
     def sample(lg: torch.Tensor, md: SamplingMetadata) -> torch.Tensor:
+        if lg.is_cuda and not md.all_greedy:
+            # one kernel: filters by threshold search (no sort) and the exponential-race draw
+            from onecat_vllm.ops import cuda as K
+            return K.sample(lg if lg.stride(-1) == 1 else lg.contiguous(), md.temperature, md.top_k, md.top_p, md.min_p, md.generators)
         greedy = lg.argmax(-1) if not md.all_random else None
         if md.all_greedy:
             return greedy

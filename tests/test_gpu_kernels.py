@@ -454,6 +454,51 @@ def test_fp8_kv_cache_values_are_read_exactly():
     assert torch.equal(out.float().cpu().view(rows, D), want)
 
 
+def test_sampler_kernel_filters_and_draws():
+    """The fused sampler: the set of tokens kept by min-p / top-k / top-p equals the sort-based oracle's, draws follow the
+    filtered softmax, temperature ~ 0 rows take the arg-max and a seeded generator repeats its draw."""
+    B, V = 12, 5000
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = torch.randn(B, V, device="cuda", generator=g) * 3.0
+    temp = torch.tensor([1.0, 0.7, 1.3, 1.0, 0.5, 1.0, 2.0, 1.0, 0.0, 1.0, 0.9, 1.0], device="cuda")
+    top_k = torch.tensor([0, 50, 0, 7, 0, 1000, 3, 0, 5, V + 5, 20, 1], device="cuda")
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 1.0, 0.8, 1.0, 0.3, 0.9, 0.99, 0.6, 1.0], device="cuda")
+    min_p = torch.tensor([0.0, 0.0, 0.0, 0.0, 0.05, 0.0, 0.0, 0.01, 0.0, 0.0, 0.02, 0.0], device="cuda")
+    kept = torch.zeros(B, V, dtype=torch.uint8, device="cuda")
+    out = K().sample(logits, temp, top_k, top_p, min_p, None, kept)
+    torch.cuda.synchronize()
+    scaled = (logits / torch.where(temp < 1e-5, torch.ones_like(temp), temp).unsqueeze(-1)).cpu()
+    want = ref.top_k_top_p_min_p(scaled, top_k.cpu(), top_p.cpu(), min_p.cpu())
+    want_kept = torch.isfinite(want)
+    for r in range(B):
+        if temp[r] < 1e-5:
+            assert out[r].item() == logits[r].argmax().item()
+            continue
+        diff = (kept[r].cpu().bool() != want_kept[r]).sum().item()
+        # a token whose cumulative mass sits within rounding of the nucleus boundary may fall on either side
+        assert diff <= 1, (r, diff, int(kept[r].sum()), int(want_kept[r].sum()))
+        assert kept[r, out[r]].item() == 1
+    assert out[11].item() == logits[11].argmax().item()        # top_k = 1
+    # distribution: many draws of one filtered row against its softmax
+    row = logits[3:4].expand(4000, V).contiguous()
+    draws = K().sample(row, torch.ones(4000, device="cuda"), torch.full((4000,), 7, device="cuda"), None, None, None, None)
+    probs = torch.softmax(ref.top_k_top_p_min_p(scaled[3:4], torch.tensor([7]), None, None)[0], -1)
+    freq = torch.bincount(draws.cpu(), minlength=V).float() / 4000
+    assert (freq > 0).sum() <= 7 and (freq - probs).abs().max() < 0.04
+    # a seeded request repeats; an unseeded one (almost surely) does not give the same 64 draws twice
+    flat = torch.zeros(64, V, device="cuda")
+    g1, g2 = torch.Generator(device="cuda").manual_seed(9), torch.Generator(device="cuda").manual_seed(9)
+    a1 = K().sample(flat[:1], torch.ones(1, device="cuda"), None, None, None, {0: g1}, None)
+    a2 = K().sample(flat[:1], torch.ones(1, device="cuda"), None, None, None, {0: g2}, None)
+    assert a1.item() == a2.item()
+    u1 = K().sample(flat, torch.ones(64, device="cuda"), None, None, None, None, None)
+    u2 = K().sample(flat, torch.ones(64, device="cuda"), None, None, None, None, None)
+    assert not torch.equal(u1, u2) and u1.unique().numel() > 32
+    # bf16 logits take the same path
+    ob = K().sample(logits.bfloat16(), torch.zeros(B, device="cuda"), None, None, None, None, None)
+    assert torch.equal(ob.cpu(), logits.bfloat16().float().argmax(-1).cpu())
+
+
 def test_paged_attention_forced_splits():
     q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
     from onecat_vllm.ops.cuda import plan_attention

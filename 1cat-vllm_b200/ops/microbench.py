@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe|sample] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -230,6 +230,29 @@ def bench_wq(rows: list, small: bool, iters: int, pk: dict) -> None:
             del layer, x, out
 
 
+def bench_sample(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """The fused sampler against the sort-based PyTorch formulation on the same device (vocabulary 151936)."""
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.ops import ref
+    V = 151936
+    for B in ([64] if small else [1, 64, 256]):
+        lg = torch.randn(B, V, device="cuda") * 2.0
+        t = torch.full((B,), 0.8, device="cuda")
+        k = torch.full((B,), 50, device="cuda", dtype=torch.int64)
+        pp = torch.full((B,), 0.9, device="cuda")
+        seeds = torch.randint(0, 1 << 62, (B,), dtype=torch.int64, device="cuda")
+        from onecat_vllm.ops import _C
+        k32 = k.to(torch.int32)
+        ms = timeit(lambda: _C.sample(lg, t, k32, pp, None, seeds, None), 1 if small else iters, 1 if small else 3)
+
+        def torch_way():
+            x = ref.top_k_top_p_min_p(lg / t.unsqueeze(-1), k, pp, None)
+            return ref.random_sample(torch.softmax(x, -1), {})
+        ms_t = timeit(torch_way, 1 if small else iters, 1 if small else 3)
+        rows.append(dict(kernel="sample_topk_topp", B=B, V=V, top_k=50, top_p=0.9, ms=ms, torch_sort_ms=ms_t, speedup=ms_t / ms,
+                         l2_gbs=10 * B * V * 4 / ms / 1e6))
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--only", default="")
@@ -239,7 +262,7 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq),
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq), ("sample", bench_sample),
                      ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True)),
                      ("gdn_prefill", lambda r, s_, i, p_: bench_gdn(r, s_, i, p_, prefill_only=True))):
         if not a.only and name in ("attn_prefill", "gdn_prefill"):

@@ -125,6 +125,12 @@ class Worker:
         process_weights_after_loading(self.runner.model)
         return n
 
+    def update_weights_ipc(self, payload: bytes) -> int:
+        """Weights shared by a trainer process on this node through CUDA-IPC / shared-memory handles
+        (``onecat_vllm.utils.weight_transfer.pack_ipc``); they are copied into the model's own storage."""
+        from onecat_vllm.utils.weight_transfer import unpack_ipc
+        return self.update_weights(unpack_ipc(payload))
+
     # ---- LoRA adapters (reference: gpu_worker.py ``add_lora`` / ``remove_lora`` / ``list_loras``)
     def _lora(self):
         if self.runner.lora_manager is None:

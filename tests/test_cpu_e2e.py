@@ -240,3 +240,31 @@ def test_prompt_embeds_equal_token_prompts_and_can_be_chunked():
     with pytest.raises(ValueError):
         llm.generate([{"prompt_embeds": torch.zeros(3, 5)}], sp)
     llm.shutdown()
+
+
+@pytest.mark.parametrize("packed", [False, True])
+def test_weights_handed_over_through_ipc_handles(packed):
+    """RLHF-style in-place update: a second model's weights reach the engine as shared-memory handles (one per tensor, or one flat
+    buffer per dtype) and the engine then decodes exactly like an engine built from that second model."""
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    from onecat_vllm.utils.weight_transfer import pack_ipc
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    prompt = [{"prompt_token_ids": list(range(3, 30))}]
+    other = build_model(ModelConfig.from_hf_dict(cfg, dtype=torch.float32, seed=5), "cpu")
+    dummy_init(other, 5)
+    want_llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, seed=5)
+    want = want_llm.generate(prompt, sp)[0].outputs[0].token_ids
+    want_llm.shutdown()
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, seed=0, enable_prefix_caching=False)
+    before = llm.generate(prompt, sp)[0].outputs[0].token_ids
+    n = llm.collective_rpc("update_weights_ipc", args=(pack_ipc(to_hf_state_dict(other).items(), packed=packed),))
+    assert n[0] > 10
+    after = llm.generate(prompt, sp)[0].outputs[0].token_ids
+    llm.shutdown()
+    assert before != want and after == want

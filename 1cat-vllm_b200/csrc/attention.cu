@@ -1,4 +1,4 @@
-// Paged-KV flash attention for head sizes 128 and 256: causal, GQA-packed, variable-length batches where each
+// Paged-KV flash attention for head sizes 64, 128 and 256: causal, GQA-packed, variable-length batches where each
 // request's queries are the last rows of its context (so decode, multi-token verify and chunked prefill over a cached
 // prefix are one kernel family).
 //   mode 0 (prefill): a CTA owns a tile of 64 (token, q-head-in-group) rows of one KV head; its 4 warps own 16 rows each
@@ -448,13 +448,16 @@ int launch_one(const AttnParams& p, cudaStream_t st) {
 }  // namespace
 
 int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
-  if (p.Hq % p.Hkv || p.bs < 16 || (p.bs & (p.bs - 1)) || (p.D != 128 && p.D != 256)) return -1;
+  if (p.Hq % p.Hkv || p.bs < 16 || (p.bs & (p.bs - 1)) || (p.D != 64 && p.D != 128 && p.D != 256)) return -1;
   const int G = p.Hq / p.Hkv;
   if (G > 64) return -1;
   const bool f8 = p.kv_fp8 != 0;
   if (mode == 1) {
     const int rows = p.short_q_len * G;
-    if (p.D == 128) {
+    if (p.D == 64) {
+      if (rows <= 16) return f8 ? launch_one<64, 1, 1, true>(p, st) : launch_one<64, 1, 1, false>(p, st);
+      if (rows <= 32) return f8 ? launch_one<64, 1, 2, true>(p, st) : launch_one<64, 1, 2, false>(p, st);
+    } else if (p.D == 128) {
       if (rows <= 16) return f8 ? launch_one<128, 1, 1, true>(p, st) : launch_one<128, 1, 1, false>(p, st);
       if (rows <= 32) return f8 ? launch_one<128, 1, 2, true>(p, st) : launch_one<128, 1, 2, false>(p, st);
     } else {
@@ -462,6 +465,7 @@ int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
     }
     return -6;  // caller must use mode 0 for longer queries
   }
+  if (p.D == 64) return f8 ? launch_one<64, 0, 1, true>(p, st) : launch_one<64, 0, 1, false>(p, st);
   if (p.D == 128) return f8 ? launch_one<128, 0, 1, true>(p, st) : launch_one<128, 0, 1, false>(p, st);
   return f8 ? launch_one<256, 0, 1, true>(p, st) : launch_one<256, 0, 1, false>(p, st);
 }

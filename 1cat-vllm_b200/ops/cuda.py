@@ -397,7 +397,7 @@ def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, 
     """Decide which requests take the decode kernel (rows = q_len * group fit in one 16/32-row tile) and how many KV
     splits it uses. Returns (short_q_len, num_q_tiles for the prefill kernel, splits)."""
     G = Hq // Hkv
-    max_rows = 32 if D == 128 else 16
+    max_rows = 32 if D <= 128 else 16
     short = max_rows // G
     n_short = sum(1 for q in query_lens if 0 < q <= short)
     if n_short:  # the row tile of the decode kernel follows the longest short query actually present (q=1 -> 16 rows)

@@ -345,6 +345,9 @@ def _attn_case(qlens, ctxs, Hq, Hkv, D, bs=16, seed=0):
     ("mixed", [1, 1, 300, 1, 2], [500, 20, 100, 0, 77], 40, 8, 128),
     ("prefill-long", [700, 129, 128], [0, 300, 1], 40, 8, 128),
     ("decode-d256", [1] * 4, [0, 100, 1025, 31], 24, 4, 256),
+    ("decode-d64", [1] * 5, [0, 100, 1025, 31, 4000], 32, 8, 64),
+    ("verify-d64", [4] * 3, [10, 600, 2000], 16, 4, 64),
+    ("prefill-d64", [300, 70, 513, 1], [0, 200, 64, 77], 32, 8, 64),
     ("prefill-d256", [77, 5, 140], [0, 200, 64], 16, 2, 256),
     ("verify-d256", [4, 4], [100, 3], 24, 4, 256),
 ])
@@ -421,7 +424,8 @@ def test_fp8_kv_cache_store_and_attention():
     assert ((a - b).abs() <= 1).all() and (a != b).float().mean() < 0.01
     assert (a[:, 1] == b[:, 1]).all()
     for name, qlens, ctxs, hq, hkv, d in [("decode", [1] * 5, [0, 100, 1000, 3000, 63], 40, 8, 128), ("verify", [4] * 3, [10, 600, 2000], 8, 2, 256),
-                                          ("prefill", [300, 70, 513], [0, 200, 64], 16, 4, 128), ("prefill-d256", [200, 3], [100, 77], 8, 2, 256)]:
+                                          ("prefill", [300, 70, 513], [0, 200, 64], 16, 4, 128), ("prefill-d256", [200, 3], [100, 77], 8, 2, 256),
+                                          ("mixed-d64", [1, 200, 3], [900, 100, 77], 16, 4, 64)]:
         qq, cache_bf, md = _attn_case(qlens, ctxs, hq, hkv, d, seed=5)
         c8 = cache_bf.to(torch.float8_e4m3fn)
         out = K().paged_attention(qq, c8, md, d ** -0.5)

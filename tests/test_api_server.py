@@ -159,3 +159,64 @@ def test_responses_and_anthropic_messages_routes(client):
     assert m["type"] == "message" and m["role"] == "assistant" and m["stop_reason"] in ("end_turn", "max_tokens", "stop_sequence", "tool_use")
     assert m["usage"]["output_tokens"] <= 5
     assert client.post("/v1/responses", json={"input": "x", "stream": True}).status_code == 400
+
+
+@pytest.mark.timeout(300)
+def test_serve_subprocess_health_completion_stream_and_shutdown(tmp_path):
+    """The real thing: ``cli serve`` in its own process on a checkpoint directory, waited for on /health, driven over HTTP
+    (completion, streamed chat, metrics) and stopped with SIGTERM (reference test model: tests/utils.py ``RemoteOpenAIServer``)."""
+    import json
+    import os
+    import signal
+    import socket
+    import subprocess
+    import sys
+    import time
+    import httpx
+    import torch
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    m = build_model(ModelConfig.from_hf_dict(CFG, dtype=torch.float32), "cpu")
+    dummy_init(m, 0)
+    save_pretrained(m, CFG, str(tmp_path))
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    proc = subprocess.Popen([sys.executable, "-m", "onecat_vllm.entrypoints.cli", "serve", str(tmp_path), "--device", "cpu", "--dtype", "float32",
+                             "--tokenizer", "byte", "--max-model-len", "256", "--port", str(port), "--served-model-name", "tiny"],
+                            cwd=root, env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    base = f"http://127.0.0.1:{port}"
+    try:
+        ok = False
+        for _ in range(240):
+            if proc.poll() is not None:
+                break
+            try:
+                if httpx.get(base + "/health", timeout=1.0).status_code == 200:
+                    ok = True
+                    break
+            except httpx.HTTPError:
+                pass
+            time.sleep(0.5)
+        assert ok, "server did not become healthy:\\n" + (proc.stdout.read().decode(errors="replace")[-3000:] if proc.poll() is not None else "")
+        r = httpx.post(base + "/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 5, "temperature": 0}, timeout=60).json()
+        assert r["usage"]["completion_tokens"] == 5 and r["choices"][0]["finish_reason"] == "length"
+        chunks = []
+        with httpx.stream("POST", base + "/v1/chat/completions", timeout=60,
+                          json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 4, "stream": True}) as resp:
+            for line in resp.iter_lines():
+                if line.startswith("data: ") and line != "data: [DONE]":
+                    chunks.append(json.loads(line[6:]))
+        assert chunks and chunks[-1]["choices"][0]["finish_reason"] in ("length", "stop")
+        assert "onecat" in httpx.get(base + "/metrics", timeout=10).text or "vllm" in httpx.get(base + "/metrics", timeout=10).text
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        try:
+            proc.wait(timeout=30)
+        except subprocess.TimeoutExpired:
+            proc.kill()
+            proc.wait(timeout=10)
+    assert proc.returncode is not None

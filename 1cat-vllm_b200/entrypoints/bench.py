@@ -162,11 +162,26 @@ async def _bench_serve_async(a) -> dict:
     return calculate_metrics(recs, dur, slo)
 
 
+def bench_startup(a) -> dict:
+    """Cold-start cost: engine construction (weights, KV cache, warm-up, graph capture) and the first generated token
+    (reference: vllm/benchmarks/startup.py)."""
+    from onecat_vllm import LLM, SamplingParams
+    ea = _engine_args(a)
+    t0 = time.perf_counter()
+    llm = LLM(**ea.__dict__)
+    t1 = time.perf_counter()
+    vocab = llm.llm_engine.cfg.model_config.vocab_size
+    llm.generate(random_prompts(1, a.input_len, vocab, a.seed), SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True, detokenize=False))
+    t2 = time.perf_counter()
+    llm.shutdown()
+    return {"engine_init_s": t1 - t0, "first_token_s": t2 - t1, "total_s": t2 - t0}
+
+
 def main(argv=None) -> None:
     p = argparse.ArgumentParser("bench")
     sub = p.add_subparsers(dest="mode", required=True)
     from onecat_vllm.config import EngineArgs
-    for name in ("throughput", "latency"):
+    for name in ("throughput", "latency", "startup"):
         sp = sub.add_parser(name)
         EngineArgs.add_cli_args(sp)
         sp.add_argument("--input-len", type=int, default=1024)
@@ -192,6 +207,8 @@ def main(argv=None) -> None:
         res = bench_throughput(a)
     elif a.mode == "latency":
         res = bench_latency(a)
+    elif a.mode == "startup":
+        res = bench_startup(a)
     else:
         res = asyncio.run(_bench_serve_async(a))
     print(json.dumps(res, indent=1))

@@ -201,7 +201,7 @@ def test_serve_subprocess_health_completion_stream_and_shutdown(tmp_path):
             except httpx.HTTPError:
                 pass
             time.sleep(0.5)
-        assert ok, "server did not become healthy:\\n" + (proc.stdout.read().decode(errors="replace")[-3000:] if proc.poll() is not None else "")
+        assert ok, "server did not become healthy:\n" + (proc.stdout.read().decode(errors="replace")[-3000:] if proc.poll() is not None else "")
         r = httpx.post(base + "/v1/completions", json={"model": "tiny", "prompt": "hello", "max_tokens": 5, "temperature": 0}, timeout=60).json()
         assert r["usage"]["completion_tokens"] == 5 and r["choices"][0]["finish_reason"] == "length"
         chunks = []
@@ -220,3 +220,42 @@ def test_serve_subprocess_health_completion_stream_and_shutdown(tmp_path):
             proc.kill()
             proc.wait(timeout=10)
     assert proc.returncode is not None
+
+
+@pytest.mark.timeout(300)
+def test_cli_run_batch_bench_and_collect_env(tmp_path, capsys):
+    """The offline commands: an OpenAI batch file through ``run-batch``, ``bench throughput / latency / startup`` and ``collect-env``."""
+    import json
+    import torch
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.entrypoints.cli import COMMANDS
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    ck = tmp_path / "ck"
+    m = build_model(ModelConfig.from_hf_dict(CFG, dtype=torch.float32), "cpu")
+    dummy_init(m, 0)
+    save_pretrained(m, CFG, str(ck))
+    common = [str(ck), "--device", "cpu", "--dtype", "float32", "--tokenizer", "byte", "--max-model-len", "256"]
+    inp, outp = tmp_path / "in.jsonl", tmp_path / "out.jsonl"
+    inp.write_text("\n".join(json.dumps(r) for r in [
+        {"custom_id": "a", "method": "POST", "url": "/v1/completions", "body": {"model": "m", "prompt": "hello", "max_tokens": 4, "temperature": 0}},
+        {"custom_id": "b", "method": "POST", "url": "/v1/completions", "body": {"model": "m", "prompt": "world!", "max_tokens": 3, "temperature": 0}}]))
+    COMMANDS["run-batch"](["-i", str(inp), "-o", str(outp), "--model", *common])
+    rows = [json.loads(l) for l in outp.read_text().splitlines()]
+    assert [r["custom_id"] for r in rows] == ["a", "b"] and rows[0]["response"]["body"]["usage"]["completion_tokens"] == 4
+    capsys.readouterr()
+    for mode, key in (("throughput", "output_tokens_per_s"), ("latency", "avg_latency_s"), ("startup", "engine_init_s")):
+        COMMANDS["bench"]([mode, "--model", *common, "--input-len", "16", "--output-len", "4", "--num-prompts", "3", "--batch-size", "2",
+                           "--num-iters", "1", "--num-iters-warmup", "0"])
+        res = _last_json(capsys.readouterr().out)
+        assert res[key] > 0, (mode, res)
+    COMMANDS["collect-env"]([])
+    assert "torch" in _last_json(capsys.readouterr().out)
+
+
+def _last_json(text: str) -> dict:
+    """The pretty-printed JSON object that ends the captured output (log lines may precede it)."""
+    import json
+    lines = text.splitlines()
+    start = max(i for i, l in enumerate(lines) if l == "{")
+    return json.loads("\n".join(lines[start:]))

@@ -459,8 +459,6 @@ class VllmConfig:
         m, p = self.model_config, self.parallel_config
         if m.num_attention_heads % p.tensor_parallel_size:
             raise ValueError("tensor_parallel_size must divide num_attention_heads")
-        if m.enable_lora and p.tensor_parallel_size > 1:
-            raise ValueError("LoRA adapters are served with tensor_parallel_size=1 only")
         if p.pipeline_parallel_size > 1:
             if p.pipeline_parallel_size > m.num_hidden_layers:
                 raise ValueError("pipeline_parallel_size exceeds the number of decoder layers")

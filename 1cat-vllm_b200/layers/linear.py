@@ -321,7 +321,7 @@ class RowParallelLinear(LinearBase):
         super().__init__(in_f, [out_f], "row", **kw)
 
     def forward(self, x):
-        if x.is_cuda and self.tp > 1:
+        if x.is_cuda and self.tp > 1 and not self.lora_slots:
             from onecat_vllm.ops import cuda as K
             from onecat_vllm.parallel.tp_ops import row_parallel_out
             out = row_parallel_out(x.shape[0], self.out_features, x.dtype, x.device)

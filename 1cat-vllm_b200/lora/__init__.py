@@ -6,7 +6,8 @@ A step's batch may mix requests of different adapters and of none. The runner pu
 every ``LinearBase.forward`` that has adapter weights adds, per active slot, ``scale * (x_s A^T) B^T`` to the rows of that slot's
 tokens. The two small GEMMs per slot go through the library GEMM (rank ≤ 64): they are not on the critical path of the
 named benchmarks. Stacked layers (qkv, gate|up) keep one (A, B) pair per sub-projection and add into that projection's
-output columns. Tensor parallelism > 1 is refused when LoRA is enabled."""
+output columns. Under tensor parallelism each rank holds the matching slice of B (column-parallel layers) or of A (row-parallel
+layers)."""
 from __future__ import annotations
 
 import json
@@ -165,8 +166,16 @@ class LoRAManager:
             if getattr(layer, "fuse_silu_mul", False):
                 raise ValueError("this model was built without enable_lora: its gate|up projection applies SiLU·mul in the GEMM epilogue")
             col0 = sum(layer.local_output_sizes[:sub])
-            a = ab["a"].to(self.device, self.dtype).contiguous()
-            b = (ab["b"].float() * scale).to(self.device, self.dtype).contiguous()
+            a, b = ab["a"], ab["b"]
+            # tensor parallelism: a column-parallel layer keeps this rank's rows of B (its slice of the sub-projection's outputs); a
+            # row-parallel layer keeps this rank's columns of A, and its delta is a partial sum that joins the layer's reduction
+            if layer.tp > 1 and layer.parallel == "column" and layer.segment_tp[sub] > 1:
+                loc = layer.local_output_sizes[sub]
+                b = b.narrow(0, layer._segment_rank(sub) * loc, loc)
+            elif layer.tp > 1 and layer.parallel == "row":
+                a = a.narrow(1, layer.tp_rank * layer.in_features, layer.in_features)
+            a = a.to(self.device, self.dtype).contiguous()
+            b = (b.float() * scale).to(self.device, self.dtype).contiguous()
             if a.shape[1] != layer.in_features or b.shape[0] != layer.local_output_sizes[sub]:
                 raise ValueError(f"adapter tensor shapes for {mod} do not match the layer ({tuple(a.shape)}, {tuple(b.shape)})")
             if not hasattr(layer, "lora_slots") or layer.lora_slots is None:

@@ -81,3 +81,23 @@ def test_lora_requests_match_merged_weights(tmp_path):
     llm.shutdown()
     with pytest.raises(ValueError):
         LLM(model=base, **kw).generate([{"prompt_token_ids": prompts[0]}], sp, lora_request=r1)
+
+
+@pytest.mark.timeout(300)
+def test_lora_under_tensor_parallelism_matches_single_rank(tmp_path):
+    """Two gloo ranks: B of column-parallel layers and A of row-parallel layers are sharded per rank; the outputs must equal the
+    single-rank run with the same adapters."""
+    base = str(tmp_path / "base")
+    _base_ckpt(base)
+    _write_adapter(str(tmp_path / "a1"), 1)
+    prompts = [[(5 * i + j) % 290 + 1 for j in range(6 + 3 * i)] for i in range(3)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    r1 = LoRARequest("a1", 1, str(tmp_path / "a1"))
+    kw = dict(device="cpu", dtype="float32", max_model_len=128, enable_lora=True, max_loras=2)
+    one = LLM(model=base, **kw)
+    want = [o.outputs[0].token_ids for o in one.generate([{"prompt_token_ids": p} for p in prompts], sp, lora_request=[r1, None, r1])]
+    one.shutdown()
+    two = LLM(model=base, tensor_parallel_size=2, distributed_executor_backend="mp", **kw)
+    got = [o.outputs[0].token_ids for o in two.generate([{"prompt_token_ids": p} for p in prompts], sp, lora_request=[r1, None, r1])]
+    two.shutdown()
+    assert got == want

@@ -159,6 +159,7 @@ class OutputProcessor:
             if st.metrics.first_token_time is None and o.new_token_ids:
                 st.metrics.first_token_time = now
             st.metrics.last_token_time = now
+            st.metrics.num_generation_tokens += len(o.new_token_ids)
             st.metrics.num_cached_tokens = o.num_cached_tokens
             finish, stop_reason = o.finish_reason, o.stop_reason
             stop_str = st.detok.update(o.new_token_ids, finished=finish is not None)
@@ -187,6 +188,9 @@ class OutputProcessor:
                 ro = self._make_output(st, finish, stop_reason, o.num_cached_tokens)
             if finish is not None:
                 st.metrics.finished_time = now
+                st.metrics.num_prompt_tokens = len(st.prompt_ids)
+                st.metrics.max_tokens = getattr(st.params, "max_tokens", None)
+                st.metrics.finish_reason = str(finish)
                 self.finished_stats.append(st.metrics)
                 self.states.pop(o.request_id, None)
             if ro is not None:

@@ -124,6 +124,17 @@ class PrometheusStatLogger(StatLoggerBase):
         self.h_tpot = mk(pc.Histogram, "vllm:request_time_per_output_token_seconds", "TPOT", buckets=_ITL_BUCKETS)
         self.h_e2e = mk(pc.Histogram, "vllm:e2e_request_latency_seconds", "request latency", buckets=_TTFT_BUCKETS)
         self.h_step = mk(pc.Histogram, "onecat:step_device_seconds", "device time of one engine step", buckets=_ITL_BUCKETS)
+        tok_buckets = [1, 2, 5, 10, 20, 50, 100, 200, 500, 1000, 2000, 5000, 10000, 20000, 50000, 100000, 200000]
+        self.h_iter_tokens = mk(pc.Histogram, "vllm:iteration_tokens_total", "tokens scheduled per engine step", buckets=tok_buckets)
+        self.h_req_prompt = mk(pc.Histogram, "vllm:request_prompt_tokens", "prompt tokens per request", buckets=tok_buckets)
+        self.h_req_gen = mk(pc.Histogram, "vllm:request_generation_tokens", "generated tokens per request", buckets=tok_buckets)
+        self.h_req_max = mk(pc.Histogram, "vllm:request_params_max_tokens", "max_tokens per request", buckets=tok_buckets)
+        self.h_queue = mk(pc.Histogram, "vllm:request_queue_time_seconds", "arrival to first schedule", buckets=_TTFT_BUCKETS)
+        self.h_prefill = mk(pc.Histogram, "vllm:request_prefill_time_seconds", "first schedule to first token", buckets=_TTFT_BUCKETS)
+        self.h_decode = mk(pc.Histogram, "vllm:request_decode_time_seconds", "first token to last token", buckets=_TTFT_BUCKETS)
+        self.h_infer = mk(pc.Histogram, "vllm:request_inference_time_seconds", "first schedule to last token", buckets=_TTFT_BUCKETS)
+        self.c_cached = mk(pc.Counter, "vllm:prompt_tokens_cached", "prompt tokens served from the prefix cache")
+        self.c_reason = pc.Counter("vllm:request_finished", "finished requests by reason", lab + ["finished_reason"])
         self._last_tok_time: Optional[float] = None
 
     @classmethod
@@ -152,12 +163,30 @@ class PrometheusStatLogger(StatLoggerBase):
             self.h_itl.labels(*lv).observe(now - self._last_tok_time)
         if n:
             self._last_tok_time = now
+        if s.num_scheduled_tokens:
+            self.h_iter_tokens.labels(*lv).observe(s.num_scheduled_tokens)
         for m in finished:
             self.c_ok.labels(*lv).inc()
+            self.c_reason.labels(*lv, m.finish_reason or "unknown").inc()
+            self.c_prompt.labels(*lv).inc(m.num_prompt_tokens)
+            self.c_cached.labels(*lv).inc(max(m.num_cached_tokens, 0))
+            self.h_req_prompt.labels(*lv).observe(m.num_prompt_tokens)
+            self.h_req_gen.labels(*lv).observe(m.num_generation_tokens)
+            if m.max_tokens:
+                self.h_req_max.labels(*lv).observe(m.max_tokens)
+            first_sched = m.first_scheduled_time if m.first_scheduled_time is not None else m.arrival_time
+            self.h_queue.labels(*lv).observe(max(first_sched - m.arrival_time, 0.0))
             if m.first_token_time is not None:
                 self.h_ttft.labels(*lv).observe(max(m.first_token_time - m.arrival_time, 0.0))
+                self.h_prefill.labels(*lv).observe(max(m.first_token_time - first_sched, 0.0))
             if m.finished_time is not None:
                 self.h_e2e.labels(*lv).observe(max(m.finished_time - m.arrival_time, 0.0))
+                self.h_infer.labels(*lv).observe(max(m.finished_time - first_sched, 0.0))
+                if m.first_token_time is not None:
+                    dec = max(m.finished_time - m.first_token_time, 0.0)
+                    self.h_decode.labels(*lv).observe(dec)
+                    if m.num_generation_tokens > 1:
+                        self.h_tpot.labels(*lv).observe(dec / (m.num_generation_tokens - 1))
 
 
 def make_stat_loggers(cfg, prometheus: bool = False) -> list:

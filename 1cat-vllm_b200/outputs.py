@@ -34,6 +34,10 @@ class RequestMetrics:
     last_token_time: Optional[float] = None
     finished_time: Optional[float] = None
     num_cached_tokens: int = 0
+    num_prompt_tokens: int = 0
+    num_generation_tokens: int = 0
+    max_tokens: Optional[int] = None
+    finish_reason: Optional[str] = None
 
 
 @dataclass

@@ -67,6 +67,10 @@ def test_server_routes(client):
     assert client.post("/reset_prefix_cache").status_code in (200, 409)
     m = client.get("/metrics").text
     assert "vllm:generation_tokens_total" in m and "vllm:time_to_first_token_seconds" in m
+    for series in ("vllm:prompt_tokens_total", "vllm:request_prompt_tokens_bucket", "vllm:request_generation_tokens_bucket",
+                   "vllm:request_time_per_output_token_seconds_bucket", "vllm:request_decode_time_seconds_bucket",
+                   "vllm:iteration_tokens_total_bucket", 'finished_reason="length"'):
+        assert series in m, series
     assert client.get("/server_info").json()["block_size"] == 16
 
 

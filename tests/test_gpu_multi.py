@@ -135,3 +135,51 @@ def test_engine_tp2_matches_tp1(tmp_path, tp_comm):
     # differs: the first token of every prompt must agree, and most of the prefix overall
     assert all(x[0] == y[0] for x, y in zip(got, ref)), f"TP2 ({tp_comm}) first tokens differ: {got} vs {ref}"
     assert agree / (16 * len(prompts)) > 0.4, f"TP2 ({tp_comm}) diverges from TP1 too early: {got} vs {ref}"
+
+
+@pytest.mark.timeout(600)
+def test_lora_tp2_matches_tp1_on_gpus(tmp_path):
+    """A LoRA adapter served by two tensor-parallel GPU ranks (sharded A / B, delta added before the fused reduction) against one GPU."""
+    _need2()
+    import json
+    from safetensors.torch import save_file
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.lora import LoRARequest
+    from onecat_vllm.models import build_model
+    base = tmp_path / "base"
+    m = build_model(ModelConfig.from_hf_dict(CFG, dtype=torch.bfloat16), "cpu")
+    dummy_init(m, 0, std=0.05)
+    save_pretrained(m, CFG, str(base))
+    ad = tmp_path / "ad"
+    ad.mkdir()
+    g = torch.Generator().manual_seed(3)
+    r, H, I = 8, CFG["hidden_size"], CFG["intermediate_size"]
+    dims = {"q_proj": (H, CFG["num_attention_heads"] * 128), "v_proj": (H, CFG["num_key_value_heads"] * 128), "o_proj": (CFG["num_attention_heads"] * 128, H),
+            "gate_proj": (H, I), "down_proj": (I, H)}
+    sd = {}
+    for layer in range(CFG["num_hidden_layers"]):
+        for name, (din, dout) in dims.items():
+            blk = "self_attn" if name in ("q_proj", "v_proj", "o_proj") else "mlp"
+            pre = f"base_model.model.model.layers.{layer}.{blk}.{name}"
+            sd[pre + ".lora_A.weight"] = (torch.randn(r, din, generator=g) * 0.05).bfloat16()
+            sd[pre + ".lora_B.weight"] = (torch.randn(dout, r, generator=g) * 0.05).bfloat16()
+    save_file(sd, str(ad / "adapter_model.safetensors"))
+    (ad / "adapter_config.json").write_text(json.dumps({"r": r, "lora_alpha": 16, "target_modules": list(dims)}))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (5, 40, 130)]
+    sp = SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)
+    req = LoRARequest("ad", 1, str(ad))
+    kw = dict(model=str(base), device="cuda", dtype="bfloat16", max_model_len=512, max_num_seqs=8, gpu_memory_utilization=0.2, enable_lora=True)
+    one = LLM(**kw)
+    plain = [o.outputs[0].token_ids for o in one.generate(prompts, sp)]
+    ref = [o.outputs[0].token_ids for o in one.generate(prompts, sp, lora_request=req)]
+    one.shutdown()
+    two = LLM(tensor_parallel_size=2, distributed_executor_backend="mp", **kw)
+    got = [o.outputs[0].token_ids for o in two.generate(prompts, sp, lora_request=req)]
+    two.shutdown()
+    assert ref != plain, "the adapter must change the output"
+    assert all(x[0] == y[0] for x, y in zip(got, ref)), f"TP2 LoRA first tokens differ: {got} vs {ref}"
+    agree = sum(next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), len(x)) for x, y in zip(got, ref))
+    assert agree / (12 * len(prompts)) > 0.4, f"TP2 LoRA diverges from one GPU too early: {got} vs {ref}"

@@ -83,7 +83,47 @@ class PhraseReasoningParser(ReasoningParser):
         return r or "", c or ""
 
 
-REASONING_PARSERS = {"qwen3": lambda: ReasoningParser(False), "deepseek_r1": lambda: ReasoningParser(True),
+class IdentityReasoningParser(ReasoningParser):
+    """No reasoning section: everything is content (reference: reasoning/identity_reasoning_parser.py)."""
+
+    def extract(self, text):
+        return None, text or None
+
+    def _split_partial(self, text):
+        return "", text
+
+
+class ChannelReasoningParser(ReasoningParser):
+    """GPT-OSS / harmony style: ``<|channel|>analysis<|message|>…<|end|>`` carries the reasoning and
+    ``<|channel|>final<|message|>…`` the answer (reference: reasoning/gptoss_reasoning_parser.py)."""
+
+    def __init__(self):
+        super().__init__(False)
+
+    def extract(self, text):
+        import re
+        parts = re.split(r"<\|channel\|>(\w+)<\|message\|>", text)
+        if len(parts) < 3:
+            return None, text or None
+        reasoning, content = [], []
+        for ch, body in zip(parts[1::2], parts[2::2]):
+            body = re.split(r"<\|end\|>|<\|return\|>|<\|start\|>", body)[0]
+            (content if ch == "final" else reasoning).append(body)
+        return "".join(reasoning) or None, "".join(content) or None
+
+    def _split_partial(self, text):
+        cut = text.rfind("<|")
+        if cut != -1 and "|>" not in text[cut:]:
+            text = text[:cut]   # hold back an unfinished control token
+        r, c = self.extract(text)
+        return r or "", c or ""
+
+
+REASONING_PARSERS = {"identity": IdentityReasoningParser, "gptoss": ChannelReasoningParser, "openai_gptoss": ChannelReasoningParser,
+                     "nemotron_v3": lambda: ReasoningParser(True), "step3p5": lambda: ReasoningParser(True),
+                     "hy_v3": lambda: ReasoningParser(False), "poolside_v1": lambda: ReasoningParser(False),
+                     "cohere_command": lambda: TaggedReasoningParser("<|START_THINKING|>", "<|END_THINKING|>"),
+                     "qwen3": lambda: ReasoningParser(False), "deepseek_r1": lambda: ReasoningParser(True),
                      "deepseek_v3": lambda: ReasoningParser(False), "think": lambda: ReasoningParser(False),
                      "glm45": lambda: ReasoningParser(False), "ernie45": lambda: ReasoningParser(True), "step3": lambda: ReasoningParser(True),
                      "minimax_m2": lambda: ReasoningParser(True), "olmo3": lambda: ReasoningParser(False), "kimi_k2": lambda: ReasoningParser(False),
@@ -385,3 +425,20 @@ def get_reasoning_parser(name: Optional[str]) -> Optional[ReasoningParser]:
     if name not in REASONING_PARSERS:
         raise ValueError(f"unknown reasoning parser {name!r}; available: {sorted(REASONING_PARSERS)}")
     return REASONING_PARSERS[name]()
+
+
+class ParserManager:
+    """One object for a served model's output: splits the reasoning section off first, then looks for tool calls in the remaining
+    content (reference: parser/abstract_parser.py, parser/parser_manager.py — the combined reasoning + tool parser)."""
+
+    def __init__(self, reasoning_parser: Optional[str] = None, tool_parser: Optional[str] = None):
+        self.reasoning = get_reasoning_parser(reasoning_parser)
+        self.tools = get_tool_parser(tool_parser)
+
+    def parse(self, text: str) -> tuple[Optional[str], Optional[str], list]:
+        """(reasoning, content, tool calls) of a complete response."""
+        reasoning, content = self.reasoning.extract(text) if self.reasoning is not None else (None, text or None)
+        calls: list = []
+        if self.tools is not None and content:
+            content, calls = self.tools.extract(content)
+        return reasoning, content, calls

@@ -36,6 +36,18 @@ def test_tool_parsers():
     assert HermesToolParser().extract("plain")[1] == []
 
 
+def test_parser_manager_and_channel_reasoning():
+    from onecat_vllm.entrypoints.parsers import ParserManager, get_reasoning_parser
+    r, c, calls = ParserManager("qwen3", "hermes").parse('<think>plan</think>ok <tool_call>{"name": "f", "arguments": {"a": 1}}</tool_call>')
+    assert r == "plan" and c == "ok" and calls[0].name == "f" and calls[0].arguments == '{"a": 1}'
+    assert ParserManager(None, None).parse("x") == (None, "x", [])
+    g = get_reasoning_parser("gptoss")
+    assert g.extract("<|channel|>analysis<|message|>thinking<|end|><|start|>assistant<|channel|>final<|message|>Answer.") == ("thinking", "Answer.")
+    assert g.stream("<|channel|>analysis<|message|>thin", "<|channel|>analysis<|message|>thinking<|en") == ("king", "")
+    assert get_reasoning_parser("identity").extract("abc") == (None, "abc")
+    assert get_reasoning_parser("cohere_command").extract("<|START_THINKING|>a<|END_THINKING|>b") == ("a", "b")
+
+
 @pytest.fixture(scope="module")
 def client():
     from fastapi.testclient import TestClient

@@ -36,6 +36,22 @@ __device__ __forceinline__ float uniform01(unsigned long long seed, unsigned lon
 __device__ __forceinline__ float load_scaled(const float* row, int i, float inv_t) { return row[i] * inv_t; }
 __device__ __forceinline__ float load_scaled(const __nv_bfloat16* row, int i, float inv_t) { return __bfloat162float(row[i]) * inv_t; }
 
+// Visits every element of the row once: four independent loads are issued before any of them is used, so the L2 latency of one
+// pass is paid once per four elements (the passes are latency-bound: long-scoreboard stalls dominated the first version).
+template <typename T, typename F>
+__device__ __forceinline__ void for_each_scaled(const T* row, int V, float inv_t, F&& f) {
+  constexpr int U = 4;
+  int i = threadIdx.x;
+  for (; i + (U - 1) * kThreads < V; i += U * kThreads) {
+    float x[U];
+#pragma unroll
+    for (int j = 0; j < U; ++j) x[j] = load_scaled(row, i + j * kThreads, inv_t);
+#pragma unroll
+    for (int j = 0; j < U; ++j) f(i + j * kThreads, x[j]);
+  }
+  for (; i < V; i += kThreads) f(i, load_scaled(row, i, inv_t));
+}
+
 __device__ float block_max(float v, float* sh) {
   v = warp_max(v);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = v;
@@ -69,13 +85,12 @@ __device__ uint32_t radix_threshold(const T* row, int V, float inv_t, float m, u
     const int shift = 24 - 8 * pass;
     for (int i = threadIdx.x; i < kWarps * 256; i += kThreads) hist[i] = 0.f;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += kThreads) {
-      const float x = load_scaled(row, i, inv_t);
+    for_each_scaled(row, V, inv_t, [&](int, float x) {
       const uint32_t k = order_key(x);
-      if (k < floor_key) continue;
-      if (pass > 0 && (k >> (shift + 8)) != (prefix >> (shift + 8))) continue;
+      if (k < floor_key) return;
+      if (pass > 0 && (k >> (shift + 8)) != (prefix >> (shift + 8))) return;
       atomicAdd(&hist[warp * 256 + ((k >> shift) & 255u)], MASS ? __expf(x - m) : 1.f);
-    }
+    });
     __syncthreads();
     if (threadIdx.x < 256) {
       float s = 0.f;
@@ -125,7 +140,7 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
   const float inv_t = greedy ? 1.f : 1.f / temp;
 
   float mx = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += kThreads) mx = fmaxf(mx, load_scaled(row, i, inv_t));
+  for_each_scaled(row, V, inv_t, [&](int, float x) { mx = fmaxf(mx, x); });
   const float m = block_max(mx, red);
 
   uint32_t floor_key = 0;
@@ -138,10 +153,9 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
     const float top_p = p.top_p != nullptr ? p.top_p[row_i] : 1.f;
     if (top_p < 1.f) {
       float s = 0.f;
-      for (int i = threadIdx.x; i < V; i += kThreads) {
-        const float x = load_scaled(row, i, inv_t);
+      for_each_scaled(row, V, inv_t, [&](int, float x) {
         if (order_key(x) >= floor_key) s += __expf(x - m);
-      }
+      });
       const float total = block_sum(s, red);
       floor_key = max(floor_key, radix_threshold<T, true>(row, V, inv_t, m, floor_key, top_p * total, hist, tot, &s_sel, &s_above));
     }
@@ -155,13 +169,12 @@ __global__ void __launch_bounds__(kThreads) sample_kernel(const SampleParams p) 
   const unsigned long long seed = p.seeds[row_i];
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += kThreads) {
-    const float x = load_scaled(row, i, inv_t);
-    if (order_key(x) < floor_key) continue;
+  for_each_scaled(row, V, inv_t, [&](int i, float x) {
+    if (order_key(x) < floor_key) return;
     float sc = x;
     if (!greedy) sc = x - m - __logf(-__logf(uniform01(seed, (unsigned long long)i)));
     if (sc > best || (sc == best && i < bi)) { best = sc; bi = i; }
-  }
+  });
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, best, o);

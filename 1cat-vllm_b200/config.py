@@ -32,7 +32,7 @@ def _hash(obj: Any) -> str:
 class QuantConfig:
     """Checkpoint quantisation layout (reference: model_executor/layers/quantization/__init__.py:12-45)."""
 
-    method: str = "none"  # none | awq | gptq | fp8 | nvfp4 | mxfp4
+    method: str = "none"  # none | awq | gptq | fp8 | nvfp4 | mxfp4 | ct_w4 (compressed-tensors pack-quantized int4)
     bits: int = 4
     group_size: int = 128
     zero_point: bool = True  # AWQ asymmetric
@@ -42,6 +42,7 @@ class QuantConfig:
     activation_scheme: str = "dynamic"
     modules_to_not_convert: list[str] = field(default_factory=lambda: ["lm_head", "embed_tokens"])
     expert_method: Optional[str] = None  # mixed precision: quant method of routed experts (e.g. mxfp4)
+    strategy: str = "tensor"  # fp8 without blocks: one scale per tensor or per output channel
 
     @classmethod
     def from_hf(cls, q: Optional[dict]) -> "QuantConfig":
@@ -59,6 +60,18 @@ class QuantConfig:
             return cls("fp8", 8, 0, False, weight_block_size=tuple(wbs) if wbs else None,
                        activation_scheme=q.get("activation_scheme", "dynamic"), expert_method=q.get("expert_method"),
                        modules_to_not_convert=(q.get("modules_to_not_convert") or q.get("ignored_layers") or []) + ["lm_head", "embed_tokens"])
+        if m == "compressed-tensors":
+            # llm-compressor checkpoints (reference: layers/quantization/compressed_tensors/): the first config group decides
+            groups = q.get("config_groups") or {}
+            w = (next(iter(groups.values())) if groups else {}).get("weights") or {}
+            skip = [x for x in (q.get("ignore") or []) if not x.startswith("re:")] + ["lm_head", "embed_tokens"]
+            if w.get("type") == "float" and w.get("num_bits") == 8 and w.get("strategy", "tensor") in ("tensor", "channel"):
+                return cls("fp8", 8, 0, False, strategy=w.get("strategy", "tensor"), modules_to_not_convert=skip)
+            if w.get("type") == "int" and w.get("num_bits") == 4 and q.get("format", "pack-quantized") == "pack-quantized":
+                if not w.get("symmetric", True) or w.get("actorder"):
+                    raise ValueError("compressed-tensors int4: only symmetric weights without activation ordering are supported")
+                return cls("ct_w4", 4, int(w.get("group_size") or -1), False, sym=True, modules_to_not_convert=skip)
+            raise ValueError(f"unsupported compressed-tensors scheme: {w}")
         if m in ("nvfp4", "modelopt_fp4", "modelopt"):
             return cls("nvfp4", 4, 16, False)
         if m in ("mxfp4",):

@@ -146,12 +146,15 @@ class FP8Method(LinearMethod):
 
     def __init__(self, q: QuantConfig):
         self.block = q.weight_block_size
+        self.channel = not self.block and q.strategy == "channel"
 
     def create_weights(self, layer, in_f, out_f, dtype):
         layer.weight = _p(torch.zeros(out_f, in_f, dtype=torch.float8_e4m3fn))
         if self.block:
             bn, bk = self.block
             layer.weight_scale_inv = _p(torch.ones(-(-out_f // bn), -(-in_f // bk), dtype=torch.float32))
+        elif self.channel:
+            layer.weight_scale = _p(torch.ones(out_f, 1, dtype=torch.float32))   # one scale per output channel, as stored
         else:
             layer.weight_scale = _p(torch.ones(max(len(layer.output_sizes), 1), dtype=torch.float32))
 
@@ -160,12 +163,16 @@ class FP8Method(LinearMethod):
             return (0, 1, 1, 1)
         if pname == "weight_scale_inv":
             return (0, self.block[0], 1, self.block[1])
+        if pname == "weight_scale" and self.channel:
+            return (0, 1, None, 1)
         return (None, 1, None, 1)
 
     def dequantized_weight(self, layer):
         if self.block:
             return ref.fp8_block_dequantize(layer.weight, layer.weight_scale_inv, self.block)
         w = layer.weight.float()
+        if self.channel:
+            return w * layer.weight_scale.float()
         if layer.weight_scale.numel() == 1:
             return w * layer.weight_scale.float()
         outs, o = [], 0
@@ -178,6 +185,45 @@ class FP8Method(LinearMethod):
         if layer.weight.is_cuda:
             from onecat_vllm.ops import cuda as K
             K.prepare_fp8(layer, self.block)
+
+
+class CTInt4Method(LinearMethod):
+    """compressed-tensors ``pack-quantized`` int4, symmetric: ``weight_packed [out, in/8]`` int32 holding eight codes along the input
+    (code = value + 8, element j in bits 4j..4j+3) and ``weight_scale [out, in/group]``
+    (reference: layers/quantization/compressed_tensors/schemes/compressed_tensors_wNa16.py)."""
+
+    name = "ct_w4"
+
+    def __init__(self, q: QuantConfig):
+        self.g = q.group_size
+
+    def create_weights(self, layer, in_f, out_f, dtype):
+        g = self.g if self.g > 0 else in_f
+        layer.weight_packed = _p(torch.zeros(out_f, in_f // 8, dtype=torch.int32))
+        layer.weight_scale = _p(torch.ones(out_f, in_f // g, dtype=torch.float16))
+        layer.weight_shape = _p(torch.tensor([out_f, in_f], dtype=torch.int64))
+
+    def layout(self, layer, pname):
+        g = self.g if self.g > 0 else layer.in_features
+        return {"weight_packed": (0, 1, 1, 8), "weight_scale": (0, 1, 1, g)}.get(pname, (None, 1, None, 1))
+
+    def _codes(self, layer):
+        sh = torch.arange(0, 32, 4, device=layer.weight_packed.device, dtype=torch.int32)
+        return ((layer.weight_packed.unsqueeze(-1) >> sh) & 0xF).reshape(layer.weight_packed.shape[0], -1)
+
+    def dequantized_weight(self, layer):
+        q = self._codes(layer).float() - 8.0
+        g = q.shape[1] // layer.weight_scale.shape[1]
+        return q * layer.weight_scale.float().repeat_interleave(g, dim=1)
+
+    def process_weights_after_loading(self, layer):
+        if layer.weight_packed.is_cuda:
+            from onecat_vllm.ops import cuda as K
+            q = self._codes(layer).to(torch.uint8)
+            g = q.shape[1] // layer.weight_scale.shape[1]
+            z = torch.full(layer.weight_scale.shape, 8, dtype=torch.uint8, device=q.device)
+            K.prepare_w4(layer, q.contiguous(), z, layer.weight_scale.to(torch.float16).contiguous(), g)
+            del layer.weight_packed, layer.weight_scale, layer.weight_shape
 
 
 class FP4Method(LinearMethod):
@@ -212,7 +258,7 @@ class FP4Method(LinearMethod):
 def get_linear_method(q: Optional[QuantConfig], prefix: str) -> LinearMethod:
     if q is None or q.method == "none" or any(m in prefix for m in q.modules_to_not_convert):
         return UnquantizedMethod()
-    return {"awq": AWQMethod, "gptq": GPTQMethod, "fp8": FP8Method, "nvfp4": FP4Method, "mxfp4": FP4Method}[q.method](q)
+    return {"awq": AWQMethod, "gptq": GPTQMethod, "fp8": FP8Method, "nvfp4": FP4Method, "mxfp4": FP4Method, "ct_w4": CTInt4Method}[q.method](q)
 
 
 # ----------------------------------------------------------------------------- layers
@@ -249,9 +295,12 @@ class LinearBase(nn.Module):
     def load_weight(self, pname: str, loaded: torch.Tensor, shard_id: Optional[int] = None) -> None:
         """Copy (the right shard of) a checkpoint tensor into parameter ``pname``.
         ``shard_id`` selects the stacked segment the tensor belongs to; ``None`` = the tensor spans all segments."""
+        if pname in ("input_scale", "input_zero_point", "output_scale", "weight_g_idx") and not hasattr(self, pname):
+            return  # static activation scales of W8A8 checkpoints: activations stay bf16 here (weight-only use of the weights)
         param = getattr(self, pname)
         oa, od, ia, idv = self.method.layout(self, pname) if pname != "bias" else (0, 1, None, 1)
-        if loaded.dim() == 0:
+        if loaded.dim() == 0 or (oa is None and loaded.numel() == 1):   # per-tensor scalars arrive as 0-d or one-element tensors
+            loaded = loaded.reshape(())
             if shard_id is not None and param.numel() > 1:
                 param.data[shard_id] = loaded
             else:

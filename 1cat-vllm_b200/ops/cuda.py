@@ -210,6 +210,8 @@ def _fp8_row_scales(layer, block) -> tuple[torch.Tensor, int]:
         assert bk % 64 == 0, "fp8 k blocks must be multiples of 64"
         return layer.weight_scale_inv.float().repeat_interleave(bn, dim=0)[:N].contiguous(), bk
     ws = layer.weight_scale.float().reshape(-1)
+    if ws.numel() == N and getattr(layer.method, "channel", False):
+        return ws.reshape(N, 1).contiguous(), K   # one scale per output channel
     if ws.numel() == 1:
         return ws.expand(N).reshape(N, 1).contiguous(), K
     rows = torch.cat([ws[i].expand(n) for i, n in enumerate(layer.local_output_sizes)])

@@ -503,6 +503,36 @@ def test_sampler_kernel_filters_and_draws():
     assert torch.equal(ob.cpu(), logits.bfloat16().float().argmax(-1).cpu())
 
 
+@pytest.mark.parametrize("scheme", ["ct_w4", "fp8-channel"])
+def test_compressed_tensors_linear_layers(scheme):
+    """compressed-tensors layers on the packed-weight GEMM: symmetric int4 (pack-quantized) and FP8 with one scale per output
+    channel, against the fp32 product with the layer's own dequantised weights."""
+    from onecat_vllm.config import QuantConfig
+    from onecat_vllm.layers.linear import ColumnParallelLinear
+    N, Kd, T = 1024, 768, 40
+    g = torch.Generator(device="cuda").manual_seed(8)
+    if scheme == "ct_w4":
+        layer = ColumnParallelLinear(Kd, N, quant=QuantConfig(method="ct_w4", bits=4, group_size=128, zero_point=False, sym=True,
+                                                              modules_to_not_convert=[]), prefix="l.proj", dtype=torch.bfloat16).cuda()
+        layer.weight_packed.data = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, Kd // 8), device="cuda", generator=g, dtype=torch.int64).to(torch.int32)
+        layer.weight_scale.data = (torch.rand(N, Kd // 128, device="cuda", generator=g) * 0.02 + 0.001).half()
+    else:
+        layer = ColumnParallelLinear(Kd, N, quant=QuantConfig(method="fp8", bits=8, group_size=0, zero_point=False, strategy="channel",
+                                                              modules_to_not_convert=[]), prefix="l.proj", dtype=torch.bfloat16).cuda()
+        codes = torch.randint(0, 256, (N, Kd), device="cuda", generator=g, dtype=torch.uint8)
+        codes[(codes & 0x7F) == 0x7F] = 0x3C
+        layer.weight.data = codes.view(torch.float8_e4m3fn)
+        layer.weight_scale.data = torch.rand(N, 1, device="cuda", generator=g) * 3e-4 + 1e-5
+    wd = layer.method.dequantized_weight(layer).float().cpu()
+    layer.process_weights_after_loading()
+    assert layer.kernel_state["kind"] == "w4"
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    y = layer(x)
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    _close(y, x.float().cpu() @ wd.t(), 3e-2, 2e-2, scheme)
+
+
 def test_paged_attention_forced_splits():
     q, cache, md = _attn_case([1] * 3, [5000, 130, 0], 40, 8, 128, seed=4)
     from onecat_vllm.ops.cuda import plan_attention

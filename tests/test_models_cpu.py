@@ -286,3 +286,55 @@ def test_native_ngram_lookup_matches_python_and_suffix_cache_drafts_across_reque
     assert list(prop.index.propose(np.asarray(seq[cut - 4:cut], dtype=np.int32), 3)) == seq[cut:cut + 3]
     llm.shutdown()
     assert first == ref and second == ref
+
+
+@pytest.mark.parametrize("scheme", ["int4-group", "fp8-channel", "fp8-tensor"])
+def test_compressed_tensors_checkpoints_match_their_dequantised_weights(tmp_path, scheme):
+    """llm-compressor layouts: pack-quantized symmetric int4 (``weight_packed`` / ``weight_scale``) and float-quantized FP8 with one
+    scale per tensor or per output channel. A dense checkpoint holding the dequantised weights must decode identically."""
+    import json
+    from safetensors.torch import save_file
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    base = dict(architectures=["LlamaForCausalLM"], hidden_size=128, intermediate_size=256, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=32, vocab_size=300, max_position_embeddings=256)
+    m = build_model(ModelConfig.from_hf_dict(base, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    dense, quant = {}, {}
+    for name, w in to_hf_state_dict(m).items():
+        if not name.endswith("proj.weight"):
+            dense[name] = quant[name] = w.contiguous()
+            continue
+        stem = name[: -len(".weight")]
+        if scheme == "int4-group":
+            g = 128
+            wg = w.float().view(w.shape[0], -1, g)
+            scale = (wg.abs().amax(-1) / 7.0).clamp_min(1e-8).half()
+            codes = (torch.round(wg / scale.float().unsqueeze(-1)).clamp(-8, 7) + 8).to(torch.int32).view(w.shape[0], -1)
+            packed = torch.zeros(w.shape[0], w.shape[1] // 8, dtype=torch.int32)
+            for j in range(8):
+                packed |= codes[:, j::8] << (4 * j)
+            quant[stem + ".weight_packed"], quant[stem + ".weight_scale"] = packed, scale
+            quant[stem + ".weight_shape"] = torch.tensor(list(w.shape))
+            dense[name] = ((codes.float() - 8.0).view(w.shape[0], -1, g) * scale.float().unsqueeze(-1)).view_as(w).contiguous()
+        else:
+            scale = (w.float().abs().amax(-1, keepdim=True) if scheme == "fp8-channel" else w.float().abs().amax().view(1)) / 448.0
+            w8 = (w.float() / scale).to(torch.float8_e4m3fn)
+            quant[name], quant[stem + ".weight_scale"] = w8, scale.float()
+            quant[stem + ".input_scale"] = torch.ones(1)
+            dense[name] = (w8.float() * scale).contiguous()
+    weights = ({"num_bits": 4, "type": "int", "symmetric": True, "strategy": "group", "group_size": 128} if scheme == "int4-group" else
+               {"num_bits": 8, "type": "float", "symmetric": True, "strategy": scheme.split("-")[1]})
+    qcfg = {"quant_method": "compressed-tensors", "format": "pack-quantized" if scheme == "int4-group" else "float-quantized",
+            "ignore": ["lm_head"], "config_groups": {"group_0": {"targets": ["Linear"], "weights": weights, "input_activations": None}}}
+    outs = []
+    for tag, sd, cfg in (("dense", dense, base), ("quant", quant, dict(base, quantization_config=qcfg))):
+        d = tmp_path / tag
+        d.mkdir()
+        save_file(sd, str(d / "model.safetensors"))
+        (d / "config.json").write_text(json.dumps(cfg))
+        llm = LLM(model=str(d), max_model_len=128, dtype="float32", device="cpu")
+        outs.append([o.outputs[0].token_ids for o in llm.generate(_prompts(300), SamplingParams(temperature=0, max_tokens=10, ignore_eos=True))])
+        llm.shutdown()
+    assert outs[0] == outs[1]

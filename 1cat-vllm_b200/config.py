@@ -120,6 +120,9 @@ class ModelConfig:
     rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
     residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
+    nope_layers: tuple = ()  # layers whose attention applies no rotary embedding (SmolLM3)
+    pre_norm: bool = True  # False: no norm before a sub-block, its output is normalised and added (OLMo-2 / OLMo-3)
+    qk_norm_full: bool = False  # q / k RMSNorm over the whole projection instead of per head (OLMo-2 / OLMo-3)
     num_labels: int = 0  # > 0: a *ForSequenceClassification checkpoint (a ``score`` head on the pooled state instead of an LM head)
     # hybrid (Gated-DeltaNet)
     layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention"
@@ -297,6 +300,10 @@ class ModelConfig:
                 kw.update(shared_expert_intermediate_size=hf.get("n_shared_experts", 1) * hf.get("moe_intermediate_size", 1408),
                           shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),
                           routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 1))
+        if "smollm3" in a and hf.get("no_rope_layers"):
+            kw["nope_layers"] = tuple(i for i, v in enumerate(hf["no_rope_layers"]) if not v)
+        if a.startswith("olmo2") or a.startswith("olmo3"):
+            kw.update(pre_norm=False, sandwich_norm=True, qk_norm_full=True)
         if "granite" in a:
             kw.update(embed_scale=float(hf.get("embedding_multiplier", 1.0)), residual_multiplier=float(hf.get("residual_multiplier", 1.0)),
                       attn_scale=float(hf.get("attention_multiplier", kw["head_dim"] ** -0.5)), logit_scale=1.0 / float(hf.get("logits_scaling", 1.0)))

@@ -30,11 +30,17 @@ class Attention(nn.Module):
             init = torch.zeros if cfg.gemma_norm else torch.ones
             self.q_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
             self.k_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
-        self.rotary_dim = cfg.rotary_dim
+        self.rotary_dim = 0 if layer_idx in cfg.nope_layers else cfg.rotary_dim
+        self.qk_norm_full = cfg.qk_norm_full
+        if cfg.qk_norm_full:
+            if tp > 1:
+                raise ValueError("q / k normalisation over the whole projection is served with tensor_parallel_size=1 only")
+            self.q_norm = nn.Parameter(torch.ones(cfg.num_attention_heads * cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
+            self.k_norm = nn.Parameter(torch.ones(cfg.num_key_value_heads * cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
         # sliding-window layers may rotate with their own base and without the context-extension rule (Gemma3)
         self.window, self.softcap = cfg.layer_window(layer_idx), cfg.attn_softcap
         local = bool(self.window) and cfg.rope_local_theta is not None
-        self.rope = get_rope(cfg.rotary_dim, cfg.max_model_len, cfg.rope_local_theta if local else cfg.rope_theta, device,
+        self.rope = get_rope(self.rotary_dim, cfg.max_model_len, cfg.rope_local_theta if local else cfg.rope_theta, device,
                              None if local else cfg.rope_scaling)
         self.scale = cfg.attn_scale if cfg.attn_scale is not None else cfg.head_dim ** -0.5
         self.layer_idx = layer_idx
@@ -51,6 +57,9 @@ class Attention(nn.Module):
             q, gate = qkv[:, :qw].view(T, Hq, D), None
         k = qkv[:, qw:qw + Hkv * D].view(T, Hkv, D)
         v = qkv[:, qw + Hkv * D:].view(T, Hkv, D)
+        if self.qk_norm_full:
+            q = ops.rms_norm(q.reshape(T, Hq * D), self.q_norm, self.eps)[0].view(T, Hq, D)
+            k = ops.rms_norm(k.reshape(T, Hkv * D), self.k_norm, self.eps)[0].view(T, Hkv, D)
         ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
                            self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
         o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap)

@@ -98,6 +98,8 @@ class DecoderModel(nn.Module):
             residual = h
         else:
             x, residual = layers[self.start].input_layernorm(intermediate[0], intermediate[1])
+        if not cfg.pre_norm:
+            return self._forward_post_norm(x if intermediate is None else None, residual, md, caches)
         plain = not cfg.sandwich_norm and cfg.residual_multiplier == 1.0
         for li, i in enumerate(range(self.start, self.end)):
             layer = layers[i]
@@ -122,6 +124,18 @@ class DecoderModel(nn.Module):
         if return_prenorm:
             return x, residual
         return x
+
+    def _forward_post_norm(self, _x, residual, md, caches):
+        """OLMo-2 / OLMo-3 block order: ``h = h + norm(attn(h)); h = h + norm(mlp(h))`` with no norm in front of either sub-block
+        (reference: models/olmo2.py). Pipeline stages are not split for this order."""
+        if self.start != 0 or not self.last_stage:
+            raise ValueError("the post-norm block order is served without pipeline parallelism")
+        h = residual
+        for li, i in enumerate(range(self.start, self.end)):
+            layer = self.layers[i]
+            h = h + layer.post_attention_layernorm(reduce_only(layer.mixer(h, md, caches[li])), None)[0]
+            h = h + layer.post_feedforward_layernorm(reduce_only(layer.mlp(h)), None)[0]
+        return self.norm(h, None)[0]
 
     def _join(self, part, residual, post_norm, next_norm):
         """Sub-block output → residual for the architectures that do more than add: reduce over TP, normalise the output (sandwich

@@ -20,6 +20,16 @@ CFG_GEMMA2 = dict(architectures=["Gemma2ForCausalLM"], hidden_size=512, intermed
                   attn_logit_softcapping=50.0, final_logit_softcapping=30.0)
 
 
+# OLMo-3-style: no pre-norms, normalised sub-block outputs, q / k norm over the whole projection, sliding layers
+CFG_OLMO3 = dict(architectures=["Olmo3ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e4, vocab_size=2048, max_position_embeddings=2048,
+                 tie_word_embeddings=False, sliding_window=64, layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"])
+# SmolLM3-style: every fourth layer without rotary embedding; head size 64
+CFG_SMOLLM3 = dict(architectures=["SmolLM3ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=8,
+                   num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-6, rope_theta=1e4, vocab_size=2048, max_position_embeddings=2048,
+                   tie_word_embeddings=True, no_rope_layers=[1, 1, 1, 0])
+
+
 def _make_checkpoint(tmp_path, cfg=CFG):
     from onecat_vllm.config import ModelConfig
     from onecat_vllm.loader.weights import dummy_init, save_pretrained
@@ -31,8 +41,9 @@ def _make_checkpoint(tmp_path, cfg=CFG):
     return str(tmp_path)
 
 
-@pytest.mark.parametrize("eager,cfg,kvd", [(True, CFG, "auto"), (False, CFG, "auto"), (False, CFG_GEMMA2, "auto"), (False, CFG, "fp8")],
-                         ids=["eager", "graphs", "gemma2-graphs", "fp8kv-graphs"])
+@pytest.mark.parametrize("eager,cfg,kvd", [(True, CFG, "auto"), (False, CFG, "auto"), (False, CFG_GEMMA2, "auto"), (False, CFG, "fp8"),
+                                           (False, CFG_OLMO3, "auto"), (False, CFG_SMOLLM3, "auto")],
+                         ids=["eager", "graphs", "gemma2-graphs", "fp8kv-graphs", "olmo3-graphs", "smollm3-d64-graphs"])
 def test_engine_gpu_matches_cpu(tmp_path, eager, cfg, kvd):
     from onecat_vllm import LLM, SamplingParams
     path = _make_checkpoint(tmp_path, cfg)

@@ -65,6 +65,10 @@ CASES = {
                                        norm_topk_prob=True, first_k_dense_replace=1, scoring_func="sigmoid",
                                        rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 8.0, "beta_fast": 32, "beta_slow": 1,
                                                         "mscale": 1.0, "mscale_all_dim": 1.0, "original_max_position_embeddings": 32}),
+    "SmolLM3ForCausalLM": dict(BASE, model_type="smollm3", num_hidden_layers=4, no_rope_layers=[1, 1, 1, 0], rope_theta=10000.0, pad_token_id=0),
+    "Olmo2ForCausalLM": dict(BASE, model_type="olmo2", rope_theta=10000.0, pad_token_id=0),
+    "Olmo3ForCausalLM": dict(BASE, model_type="olmo3", num_hidden_layers=4, sliding_window=16, rope_theta=10000.0, pad_token_id=0,
+                             layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

@@ -302,6 +302,19 @@ class ModelConfig:
                           routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 1))
         if "smollm3" in a and hf.get("no_rope_layers"):
             kw["nope_layers"] = tuple(i for i, v in enumerate(hf["no_rope_layers"]) if not v)
+        if a.startswith("exaone4"):
+            # post-norm order with per-head q/k norm; in the hybrid form the full-attention layers apply no rotary embedding
+            kw.update(pre_norm=False, sandwich_norm=True, qk_norm=True)
+            if kw.get("sliding_layers"):
+                kw["nope_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i not in kw["sliding_layers"])
+        if a.startswith("dots1"):
+            kw.update(qk_norm=True, shared_expert_intermediate_size=(hf.get("n_shared_experts") or 0) * hf.get("moe_intermediate_size", 1408),
+                      shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),
+                      routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 0))
+        if a.startswith("olmoe"):
+            kw.update(qk_norm_full=True)
+        if a.startswith("ernie4_5for"):
+            kw.update(rope_interleaved=True, attention_bias=bool(hf.get("use_bias", False)))
         if a.startswith("olmo2") or a.startswith("olmo3"):
             kw.update(pre_norm=False, sandwich_norm=True, qk_norm_full=True)
         if "granite" in a:

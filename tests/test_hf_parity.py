@@ -69,6 +69,15 @@ CASES = {
     "Olmo2ForCausalLM": dict(BASE, model_type="olmo2", rope_theta=10000.0, pad_token_id=0),
     "Olmo3ForCausalLM": dict(BASE, model_type="olmo3", num_hidden_layers=4, sliding_window=16, rope_theta=10000.0, pad_token_id=0,
                              layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "OlmoeForCausalLM": dict(BASE, model_type="olmoe", rope_theta=10000.0, num_experts=8, num_experts_per_tok=2, norm_topk_prob=False, pad_token_id=0),
+    "Ernie4_5ForCausalLM": dict(BASE, model_type="ernie4_5", head_dim=16, rope_theta=10000.0, use_bias=False, pad_token_id=0),
+    "Exaone4ForCausalLM": dict(BASE, model_type="exaone4", head_dim=16, num_hidden_layers=4, sliding_window=16, sliding_window_pattern=4,
+                               layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"], rope_theta=10000.0, pad_token_id=0),
+    "MinistralForCausalLM": dict(BASE, model_type="ministral", head_dim=16, num_hidden_layers=4, sliding_window=16, rope_theta=10000.0, pad_token_id=0,
+                                 layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]),
+    "Dots1ForCausalLM": dict(BASE, model_type="dots1", head_dim=16, rope_theta=10000.0, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
+                             moe_intermediate_size=48, n_group=1, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
+                             first_k_dense_replace=1, pad_token_id=0),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

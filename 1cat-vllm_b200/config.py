@@ -120,6 +120,7 @@ class ModelConfig:
     rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
     residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
+    qk_norm_after_rope: bool = False  # per-head q / k RMSNorm applied to the rotated vectors (HunYuan) instead of before the rotation
     nope_layers: tuple = ()  # layers whose attention applies no rotary embedding (SmolLM3)
     pre_norm: bool = True  # False: no norm before a sub-block, its output is normalised and added (OLMo-2 / OLMo-3)
     qk_norm_full: bool = False  # q / k RMSNorm over the whole projection instead of per head (OLMo-2 / OLMo-3)
@@ -313,6 +314,10 @@ class ModelConfig:
                       routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 0))
         if a.startswith("olmoe"):
             kw.update(qk_norm_full=True)
+        if a.startswith("hunyuandensev1"):
+            kw.update(qk_norm=True, qk_norm_after_rope=True)
+        if a.startswith("helium"):
+            kw["rope_interleaved"] = True
         if a.startswith("ernie4_5for"):
             kw.update(rope_interleaved=True, attention_bias=bool(hf.get("use_bias", False)))
         if a.startswith("olmo2") or a.startswith("olmo3"):

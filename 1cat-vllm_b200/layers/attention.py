@@ -32,6 +32,7 @@ class Attention(nn.Module):
             self.k_norm = nn.Parameter(init(cfg.head_dim, dtype=cfg.dtype), requires_grad=False)
         self.rotary_dim = 0 if layer_idx in cfg.nope_layers else cfg.rotary_dim
         self.qk_norm_full = cfg.qk_norm_full
+        self.norm_after_rope = cfg.qk_norm and cfg.qk_norm_after_rope
         if cfg.qk_norm_full:
             if tp > 1:
                 raise ValueError("q / k normalisation over the whole projection is served with tensor_parallel_size=1 only")
@@ -60,8 +61,16 @@ class Attention(nn.Module):
         if self.qk_norm_full:
             q = ops.rms_norm(q.reshape(T, Hq * D), self.q_norm, self.eps)[0].view(T, Hq, D)
             k = ops.rms_norm(k.reshape(T, Hkv * D), self.k_norm, self.eps)[0].view(T, Hkv, D)
-        ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
-                           self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
+        if self.norm_after_rope:
+            # rotate first (no cache write), normalise per head, then insert the normalised keys with a zero-width rotation
+            q, k = q.contiguous(), k.contiguous()
+            ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, None, md.slot_mapping, self.rotary_dim, None, None, self.eps, False)
+            q = ops.rms_norm(q.view(T * Hq, D), self.q_norm, self.eps, None, self.gemma)[0].view(T, Hq, D)
+            k = ops.rms_norm(k.view(T * Hkv, D), self.k_norm, self.eps, None, self.gemma)[0].view(T, Hkv, D)
+            ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin[:, :0], kv_cache, md.slot_mapping, 0, None, None, self.eps, False)
+        else:
+            ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
+                               self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
         o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap)
         if gate is not None:
             o = o * torch.sigmoid(gate.float()).to(o.dtype)

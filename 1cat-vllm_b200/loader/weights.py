@@ -31,7 +31,7 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 
 
 # checkpoint names whose tensors live under another name here (a parameter of the block instead of a sub-module's weight)
-_RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
+_RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.shared_experts.", ".mlp.shared_expert."))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)

@@ -30,6 +30,12 @@ CFG_SMOLLM3 = dict(architectures=["SmolLM3ForCausalLM"], hidden_size=512, interm
                    tie_word_embeddings=True, no_rope_layers=[1, 1, 1, 0])
 
 
+# HunYuan-style: per-head q / k norm applied after the rotation (two passes of the rope + insert kernel)
+CFG_HUNYUAN = dict(architectures=["HunYuanDenseV1ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                   num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e4, vocab_size=2048, max_position_embeddings=2048,
+                   tie_word_embeddings=False, use_qk_norm=True)
+
+
 def _make_checkpoint(tmp_path, cfg=CFG):
     from onecat_vllm.config import ModelConfig
     from onecat_vllm.loader.weights import dummy_init, save_pretrained
@@ -42,8 +48,8 @@ def _make_checkpoint(tmp_path, cfg=CFG):
 
 
 @pytest.mark.parametrize("eager,cfg,kvd", [(True, CFG, "auto"), (False, CFG, "auto"), (False, CFG_GEMMA2, "auto"), (False, CFG, "fp8"),
-                                           (False, CFG_OLMO3, "auto"), (False, CFG_SMOLLM3, "auto")],
-                         ids=["eager", "graphs", "gemma2-graphs", "fp8kv-graphs", "olmo3-graphs", "smollm3-d64-graphs"])
+                                           (False, CFG_OLMO3, "auto"), (False, CFG_SMOLLM3, "auto"), (False, CFG_HUNYUAN, "auto")],
+                         ids=["eager", "graphs", "gemma2-graphs", "fp8kv-graphs", "olmo3-graphs", "smollm3-d64-graphs", "hunyuan-graphs"])
 def test_engine_gpu_matches_cpu(tmp_path, eager, cfg, kvd):
     from onecat_vllm import LLM, SamplingParams
     path = _make_checkpoint(tmp_path, cfg)

@@ -78,6 +78,12 @@ CASES = {
     "Dots1ForCausalLM": dict(BASE, model_type="dots1", head_dim=16, rope_theta=10000.0, n_routed_experts=8, n_shared_experts=1, num_experts_per_tok=2,
                              moe_intermediate_size=48, n_group=1, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
                              first_k_dense_replace=1, pad_token_id=0),
+    "HeliumForCausalLM": dict(BASE, model_type="helium", head_dim=16, rope_theta=10000.0, pad_token_id=0),
+    "CwmForCausalLM": dict(BASE, model_type="cwm", head_dim=16, num_hidden_layers=4, sliding_window=16, pad_token_id=0,
+                           layer_types=["full_attention", "sliding_attention", "sliding_attention", "sliding_attention"],
+                           rope_parameters={"rope_type": "llama3", "rope_theta": 10000.0, "factor": 4.0, "high_freq_factor": 4.0,
+                                            "low_freq_factor": 1.0, "original_max_position_embeddings": 32}),
+    "HunYuanDenseV1ForCausalLM": dict(BASE, model_type="hunyuan_v1_dense", head_dim=16, rope_theta=10000.0, use_qk_norm=True, pad_token_id=0),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

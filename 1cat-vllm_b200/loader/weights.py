@@ -74,6 +74,21 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             name = _GLM4_NORM_RE.sub(lambda m: "." + _GLM4_NORMS[m.group(1)] + ".", name)
         if interleaved and (".q_proj." in name or ".k_proj." in name) and "self_attn" in name:
             w = _half_split_rows(w, cfg.head_dim, cfg.rotary_dim)
+        if ".block_sparse_moe.input_linear." in name or ".block_sparse_moe.output_linear." in name:
+            # GraniteMoe keeps all experts of a layer in one tensor: gate|up stacked [E, 2I, H] and down [E, H, I]
+            mod = mods.get(name.split(".block_sparse_moe.")[0] + ".mlp.experts")
+            if mod is not None:
+                for e in range(w.shape[0]):
+                    if ".input_linear." in name:
+                        half = w.shape[1] // 2
+                        mod.load_expert_weight(e, "gate_proj", "weight", w[e, :half])
+                        mod.load_expert_weight(e, "up_proj", "weight", w[e, half:])
+                    else:
+                        mod.load_expert_weight(e, "down_proj", "weight", w[e])
+                loaded.add(name)
+            continue
+        if ".block_sparse_moe.router.layer." in name:
+            name = name.replace(".block_sparse_moe.router.layer.", ".mlp.gate.")
         if ".block_sparse_moe." in name:  # Mixtral naming: block_sparse_moe.{gate, experts.N.w1|w3|w2}
             name = name.replace(".block_sparse_moe.", ".mlp.")
             for theirs, ours in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):

@@ -84,6 +84,8 @@ CASES = {
                            rope_parameters={"rope_type": "llama3", "rope_theta": 10000.0, "factor": 4.0, "high_freq_factor": 4.0,
                                             "low_freq_factor": 1.0, "original_max_position_embeddings": 32}),
     "HunYuanDenseV1ForCausalLM": dict(BASE, model_type="hunyuan_v1_dense", head_dim=16, rope_theta=10000.0, use_qk_norm=True, pad_token_id=0),
+    "GraniteMoeForCausalLM": dict(BASE, model_type="granitemoe", intermediate_size=48, rope_theta=10000.0, num_local_experts=4, num_experts_per_tok=2,
+                                  embedding_multiplier=6.0, residual_multiplier=0.3, attention_multiplier=0.2, logits_scaling=4.0, pad_token_id=0),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

@@ -120,6 +120,7 @@ class ModelConfig:
     rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
     residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
+    router_bias: bool = False  # softmax routing whose top-k selection adds a learned per-expert bias (Ernie-4.5-MoE)
     qk_norm_after_rope: bool = False  # per-head q / k RMSNorm applied to the rotated vectors (HunYuan) instead of before the rotation
     nope_layers: tuple = ()  # layers whose attention applies no rotary embedding (SmolLM3)
     pre_norm: bool = True  # False: no norm before a sub-block, its output is normalised and added (OLMo-2 / OLMo-3)
@@ -314,6 +315,15 @@ class ModelConfig:
                       routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 0))
         if a.startswith("olmoe"):
             kw.update(qk_norm_full=True)
+        if a.startswith("ernie4_5_moe"):
+            start, end = hf.get("moe_layer_start_index", 0), hf.get("moe_layer_end_index", -1)
+            end = kw["num_hidden_layers"] - 1 if end is None or end < 0 else end
+            iv = hf.get("moe_layer_interval", 1) or 1
+            kw.update(num_experts=hf.get("moe_num_experts", 64), num_experts_per_tok=hf.get("moe_k", 6),
+                      moe_intermediate_size=hf.get("moe_intermediate_size", 1536), norm_topk_prob=True, router_bias=True, rope_interleaved=True,
+                      shared_expert_intermediate_size=(hf.get("moe_num_shared_experts") or 0) * hf.get("moe_intermediate_size", 1536),
+                      shared_expert_gate=False, attention_bias=bool(hf.get("use_bias", False)),
+                      dense_layers=tuple(i for i in range(kw["num_hidden_layers"]) if not (start <= i <= end and (i + 1) % iv == 0)))
         if a.startswith("hunyuandensev1"):
             kw.update(qk_norm=True, qk_norm_after_rope=True)
         if a.startswith("helium"):

@@ -107,7 +107,7 @@ class SparseMoeBlock(nn.Module):
         self.cfg = cfg
         self.gate = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, quant=None, prefix=prefix + ".gate", dtype=cfg.dtype)
         self.experts = FusedMoE(cfg, prefix + ".experts")
-        self.deepseek = cfg.scoring_func == "sigmoid" or cfg.n_group > 1
+        self.deepseek = cfg.scoring_func == "sigmoid" or cfg.n_group > 1 or cfg.router_bias
         if self.deepseek:
             self.e_score_correction_bias = nn.Parameter(torch.zeros(cfg.num_experts, dtype=torch.float32), requires_grad=False)
         self.shared_expert: Optional[MLP] = None

@@ -32,7 +32,8 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 
 # checkpoint names whose tensors live under another name here (a parameter of the block instead of a sub-module's weight)
 _RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
-            (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+            (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+            (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.shared_experts.", ".mlp.shared_expert."))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
 _GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
@@ -74,6 +75,19 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             name = _GLM4_NORM_RE.sub(lambda m: "." + _GLM4_NORMS[m.group(1)] + ".", name)
         if interleaved and (".q_proj." in name or ".k_proj." in name) and "self_attn" in name:
             w = _half_split_rows(w, cfg.head_dim, cfg.rotary_dim)
+        if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")):
+            # all experts of a layer in one tensor (the in-memory layout of recent transformers): [E, 2I, H] and [E, H, I]
+            mod = mods.get(name.rsplit(".", 1)[0])
+            if mod is not None:
+                for e in range(w.shape[0]):
+                    if name.endswith("gate_up_proj"):
+                        half = w.shape[1] // 2
+                        mod.load_expert_weight(e, "gate_proj", "weight", w[e, :half])
+                        mod.load_expert_weight(e, "up_proj", "weight", w[e, half:])
+                    else:
+                        mod.load_expert_weight(e, "down_proj", "weight", w[e])
+                loaded.add(name)
+            continue
         if ".block_sparse_moe.input_linear." in name or ".block_sparse_moe.output_linear." in name:
             # GraniteMoe keeps all experts of a layer in one tensor: gate|up stacked [E, 2I, H] and down [E, H, I]
             mod = mods.get(name.split(".block_sparse_moe.")[0] + ".mlp.experts")

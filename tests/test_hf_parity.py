@@ -86,6 +86,9 @@ CASES = {
     "HunYuanDenseV1ForCausalLM": dict(BASE, model_type="hunyuan_v1_dense", head_dim=16, rope_theta=10000.0, use_qk_norm=True, pad_token_id=0),
     "GraniteMoeForCausalLM": dict(BASE, model_type="granitemoe", intermediate_size=48, rope_theta=10000.0, num_local_experts=4, num_experts_per_tok=2,
                                   embedding_multiplier=6.0, residual_multiplier=0.3, attention_multiplier=0.2, logits_scaling=4.0, pad_token_id=0),
+    "Ernie4_5_MoeForCausalLM": dict(BASE, model_type="ernie4_5_moe", head_dim=16, num_hidden_layers=3, rope_theta=10000.0, moe_intermediate_size=48,
+                                    moe_num_experts=8, moe_k=2, moe_num_shared_experts=1, moe_layer_start_index=1, moe_layer_end_index=2,
+                                    moe_layer_interval=1, use_bias=False, pad_token_id=0),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 
@@ -102,6 +105,9 @@ def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
     for p in hf.parameters():  # widen the logit gaps so that greedy choices are not near-ties
         if p.dim() >= 2:
             p.data.mul_(3.0)
+    for n, p in list(hf.named_parameters()) + list(hf.named_buffers()):
+        if "e_score_correction_bias" in n:  # zero at initialisation: give the router's selection bias something to do
+            p.data.normal_(0.0, 0.05, generator=torch.Generator().manual_seed(4))
     hf.save_pretrained(str(tmp_path), safe_serialization=True)
     hf.generation_config.eos_token_id = None   # the engine runs with ignore_eos
     g = torch.Generator().manual_seed(1)

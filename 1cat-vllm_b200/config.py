@@ -120,6 +120,11 @@ class ModelConfig:
     rope_interleaved: bool = False  # checkpoint rotates adjacent pairs (GLM); q/k rows are permuted to the half-split layout at load
     residual_multiplier: float = 1.0  # Granite: sub-block outputs are scaled before the residual add
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
+    attn_sinks: bool = False  # one learned sink logit per query head joins the softmax denominator (GPT-OSS)
+    attn_o_bias: bool = False  # bias on the attention output projection
+    router_linear_bias: bool = False  # the router is a linear layer with bias
+    expert_bias: bool = False  # every expert projection has a bias
+    moe_act: str = "silu"  # silu | swiglu_oai: (up + 1) * gate * sigmoid(1.702 gate) with gate <= 7 and |up| <= 7 (GPT-OSS)
     router_bias: bool = False  # softmax routing whose top-k selection adds a learned per-expert bias (Ernie-4.5-MoE)
     qk_norm_after_rope: bool = False  # per-head q / k RMSNorm applied to the rotated vectors (HunYuan) instead of before the rotation
     nope_layers: tuple = ()  # layers whose attention applies no rotary embedding (SmolLM3)
@@ -315,6 +320,9 @@ class ModelConfig:
                       routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 0))
         if a.startswith("olmoe"):
             kw.update(qk_norm_full=True)
+        if a.startswith("gptoss"):
+            kw.update(attention_bias=True, attn_o_bias=True, attn_sinks=True, router_linear_bias=True, expert_bias=True, moe_act="swiglu_oai",
+                      norm_topk_prob=True, num_experts_per_tok=hf.get("num_experts_per_tok", hf.get("experts_per_token", 4)))
         if a.startswith("ernie4_5_moe"):
             start, end = hf.get("moe_layer_start_index", 0), hf.get("moe_layer_end_index", -1)
             end = kw["num_hidden_layers"] - 1 if end is None or end < 0 else end

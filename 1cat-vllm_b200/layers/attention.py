@@ -23,8 +23,10 @@ class Attention(nn.Module):
                                           q_mult=2 if self.gated else 1, bias=cfg.attention_bias, quant=cfg.quant,
                                           prefix=prefix + ".qkv_proj", dtype=cfg.dtype)
         self.Hq, self.Hkv = self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads
-        self.o_proj = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, quant=cfg.quant,
+        self.o_proj = RowParallelLinear(cfg.num_attention_heads * cfg.head_dim, cfg.hidden_size, bias=cfg.attn_o_bias, quant=cfg.quant,
                                         prefix=prefix + ".o_proj", dtype=cfg.dtype)
+        self.sinks = nn.Parameter(torch.zeros(self.Hq, dtype=torch.float32), requires_grad=False) if cfg.attn_sinks else None
+        self._tp_rank = get_state().tp_rank
         self.qk_norm, self.gemma, self.eps = cfg.qk_norm, cfg.gemma_norm, cfg.rms_norm_eps
         if cfg.qk_norm:
             init = torch.zeros if cfg.gemma_norm else torch.ones
@@ -45,6 +47,13 @@ class Attention(nn.Module):
                              None if local else cfg.rope_scaling)
         self.scale = cfg.attn_scale if cfg.attn_scale is not None else cfg.head_dim ** -0.5
         self.layer_idx = layer_idx
+
+    def load_weight(self, pname: str, w: torch.Tensor, shard_id=None) -> None:
+        """Parameters that belong to the block itself: the per-head sink logits are sharded with the query heads."""
+        p = getattr(self, pname)
+        if pname == "sinks":
+            w = w.narrow(0, self._tp_rank * self.Hq, self.Hq)
+        p.data.copy_(w.reshape(p.shape))
 
     def forward(self, x: torch.Tensor, md, kv_cache: torch.Tensor) -> torch.Tensor:
         T = x.shape[0]
@@ -71,7 +80,7 @@ class Attention(nn.Module):
         else:
             ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
                                self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
-        o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap)
+        o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap, sinks=self.sinks)
         if gate is not None:
             o = o * torch.sigmoid(gate.float()).to(o.dtype)
         return self.o_proj(o.reshape(T, Hq * D))

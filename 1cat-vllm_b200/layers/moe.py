@@ -56,6 +56,12 @@ class FusedMoE(nn.Module):
             self.qmethod = "none"
             self.w13 = nn.Parameter(torch.zeros(E, 2 * I, H, dtype=dt), requires_grad=False)
             self.w2 = nn.Parameter(torch.zeros(E, H, I, dtype=dt), requires_grad=False)
+        self.act = cfg.moe_act
+        if cfg.expert_bias:
+            self.w13_bias = nn.Parameter(torch.zeros(E, 2 * I, dtype=dt), requires_grad=False)
+            self.w2_bias = nn.Parameter(torch.zeros(E, H, dtype=dt), requires_grad=False)
+        else:
+            self.w13_bias = self.w2_bias = None
         self._dq = None
         self.kernel_state = None
 
@@ -65,6 +71,13 @@ class FusedMoE(nn.Module):
         if not 0 <= e < self.E_local:
             return
         I, r = self.I, (0 if self.ep else self.tp_rank)
+        if pname == "bias":
+            if proj in ("gate_proj", "up_proj"):
+                src = w.narrow(0, r * I, I) if not self.ep and self.tp > 1 else w
+                self.w13_bias.data[e, (0 if proj == "gate_proj" else I):(I if proj == "gate_proj" else 2 * I)].copy_(src)
+            elif self.ep or self.tp_rank == 0:
+                self.w2_bias.data[e].copy_(w)   # the down bias joins the partial sums once
+            return
         scale = pname != "weight"
         tgt13, tgt2 = (self.w13_scale, self.w2_scale) if scale else (self.w13, self.w2)
         if proj in ("gate_proj", "up_proj"):
@@ -89,11 +102,21 @@ class FusedMoE(nn.Module):
 
     def process_weights_after_loading(self):
         self._dq = None
-        if self.w13.is_cuda:
+        if self.w13.is_cuda and self.act == "silu" and self.w13_bias is None:
             from onecat_vllm.ops import cuda as K
             K.prepare_moe(self)
 
     def forward(self, x, topk_w, topk_ids):
+        if self.act != "silu" or self.w13_bias is not None:
+            # experts with biases or the GPT-OSS activation: one pair of dense GEMMs per active expert (the grouped kernel's
+            # epilogue implements SiLU·mul without bias only)
+            w13, w2 = self.dequantized()
+            mm = None
+            if x.is_cuda:
+                from onecat_vllm.ops import cuda as K
+                K.TORCH_STANDINS.add("moe_expert_loop")
+                mm = K.gemm_bf16 if x.dtype == torch.bfloat16 else None
+            return ref.fused_experts(x, w13, w2, topk_w, topk_ids, self.e_off, self.w13_bias, self.w2_bias, self.act, mm)
         if x.is_cuda:
             from onecat_vllm.ops import cuda as K
             return K.fused_moe(self, x, topk_w, topk_ids)
@@ -105,7 +128,8 @@ class SparseMoeBlock(nn.Module):
     def __init__(self, cfg: ModelConfig, prefix: str):
         super().__init__()
         self.cfg = cfg
-        self.gate = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, quant=None, prefix=prefix + ".gate", dtype=cfg.dtype)
+        self.gate = ReplicatedLinear(cfg.hidden_size, cfg.num_experts, bias=cfg.router_linear_bias, quant=None, prefix=prefix + ".gate",
+                                     dtype=cfg.dtype)
         self.experts = FusedMoE(cfg, prefix + ".experts")
         self.deepseek = cfg.scoring_func == "sigmoid" or cfg.n_group > 1 or cfg.router_bias
         if self.deepseek:

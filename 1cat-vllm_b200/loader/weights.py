@@ -33,7 +33,7 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 # checkpoint names whose tensors live under another name here (a parameter of the block instead of a sub-module's weight)
 _RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
-            (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
+            (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.router.", ".mlp.gate."), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.shared_experts.", ".mlp.shared_expert."))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
 _GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
@@ -49,7 +49,7 @@ def _half_split_rows(w: torch.Tensor, head_dim: int, rotary_dim: int) -> torch.T
     return w.reshape(heads, head_dim, -1)[:, perm].reshape(w.shape)
 
 
-_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv|weight_scale)$")
+_EXPERT_RE = re.compile(r"(.*\.mlp)\.experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.(weight|weight_scale_inv|weight_scale|bias)$")
 
 
 def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) -> set:
@@ -75,6 +75,27 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             name = _GLM4_NORM_RE.sub(lambda m: "." + _GLM4_NORMS[m.group(1)] + ".", name)
         if interleaved and (".q_proj." in name or ".k_proj." in name) and "self_attn" in name:
             w = _half_split_rows(w, cfg.head_dim, cfg.rotary_dim)
+        if cfg is not None and cfg.moe_act == "swiglu_oai" and ".mlp.experts." in name:
+            # GPT-OSS: [E, H, 2I] with gate / up in alternating columns, [E, I, H], and a bias for each
+            mod = mods.get(name.split(".mlp.experts.")[0] + ".mlp.experts")
+            leaf = name.rsplit(".", 1)[1]
+            if mod is not None and leaf in ("gate_up_proj", "gate_up_proj_bias", "down_proj", "down_proj_bias"):
+                for e in range(w.shape[0]):
+                    if leaf == "gate_up_proj":
+                        t = w[e].t()
+                        mod.load_expert_weight(e, "gate_proj", "weight", t[0::2])
+                        mod.load_expert_weight(e, "up_proj", "weight", t[1::2])
+                    elif leaf == "gate_up_proj_bias":
+                        mod.load_expert_weight(e, "gate_proj", "bias", w[e, 0::2])
+                        mod.load_expert_weight(e, "up_proj", "bias", w[e, 1::2])
+                    elif leaf == "down_proj":
+                        mod.load_expert_weight(e, "down_proj", "weight", w[e].t())
+                    else:
+                        mod.load_expert_weight(e, "down_proj", "bias", w[e])
+                loaded.add(name)
+                continue
+            if leaf.endswith(("_blocks", "_scales")):
+                raise ValueError(f"GPT-OSS expert tensor {name}: MXFP4 block tensors are not read (use a bf16 checkpoint)")
         if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")):
             # all experts of a layer in one tensor (the in-memory layout of recent transformers): [E, 2I, H] and [E, H, I]
             mod = mods.get(name.rsplit(".", 1)[0])
@@ -318,8 +339,8 @@ def to_hf_state_dict(model: nn.Module) -> dict:
                 n = mod.local_output_sizes[sid] // od
                 out[mod_name[: -len(ours)] + theirs + "." + pname] = p.narrow(oa, off, n).contiguous()
                 off += n
-        elif mod_name.endswith(".experts") and pname in ("w13", "w2", "w13_scale", "w2_scale"):
-            leaf = "weight" if pname in ("w13", "w2") else "weight_scale_inv"
+        elif mod_name.endswith(".experts") and pname in ("w13", "w2", "w13_scale", "w2_scale", "w13_bias", "w2_bias"):
+            leaf = "weight" if pname in ("w13", "w2") else ("bias" if pname.endswith("bias") else "weight_scale_inv")
             for e in range(p.shape[0]):
                 if pname.startswith("w13"):
                     h = p.shape[1] // 2

@@ -426,7 +426,15 @@ def grouped_topk(logits, k: int, n_group: int, topk_group: int, bias=None, scori
     return w * scaling, ids.to(torch.int32)
 
 
-def fused_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0):
+def swiglu_oai(h: torch.Tensor, alpha: float = 1.702, limit: float = 7.0) -> torch.Tensor:
+    """GPT-OSS gated activation on ``[gate | up]``: ``(up + 1) * gate * sigmoid(alpha * gate)`` with gate clamped from above and up
+    clamped on both sides (reference: layers/activation.py ``SwigluOAIAndMul``)."""
+    d = h.shape[-1] // 2
+    gate, up = h[..., :d].float().clamp(max=limit), h[..., d:].float().clamp(-limit, limit)
+    return ((up + 1.0) * gate * torch.sigmoid(gate * alpha)).to(h.dtype)
+
+
+def fused_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0, b13=None, b2=None, act: str = "silu", mm=None):
     """Per-expert SwiGLU FFNs, weighted sum over each token's top-k. ``w13`` ``[E_local, 2I, H]``,
     ``w2`` ``[E_local, H, I]`` hold experts ``expert_offset .. expert_offset+E_local``; tokens routed elsewhere
     contribute nothing (reference: csrc/cpu/cpu_fused_moe.cpp)."""
@@ -439,9 +447,17 @@ def fused_experts(x, w13, w2, topk_w, topk_ids, expert_offset: int = 0):
         if tok.numel() == 0:
             continue
         wt = (topk_w * sel).sum(-1)[tok]
-        h = F.linear(x[tok].float(), w13[e].float())
-        h = silu_and_mul(h)
-        out[tok] += F.linear(h, w2[e].float()) * wt.unsqueeze(-1)
+        if mm is not None:   # device path: ``mm(x, w)`` = x @ w^T in the model dtype
+            h = mm(x[tok].contiguous(), w13[e]).float()
+        else:
+            h = F.linear(x[tok].float(), w13[e].float())
+        if b13 is not None:
+            h = h + b13[e].float()
+        h = silu_and_mul(h) if act == "silu" else swiglu_oai(h)
+        o = mm(h.to(x.dtype).contiguous(), w2[e]).float() if mm is not None else F.linear(h, w2[e].float())
+        if b2 is not None:
+            o = o + b2[e].float()
+        out[tok] += o * wt.unsqueeze(-1)
     return out.to(x.dtype)
 
 

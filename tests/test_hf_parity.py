@@ -89,6 +89,11 @@ CASES = {
     "Ernie4_5_MoeForCausalLM": dict(BASE, model_type="ernie4_5_moe", head_dim=16, num_hidden_layers=3, rope_theta=10000.0, moe_intermediate_size=48,
                                     moe_num_experts=8, moe_k=2, moe_num_shared_experts=1, moe_layer_start_index=1, moe_layer_end_index=2,
                                     moe_layer_interval=1, use_bias=False, pad_token_id=0),
+    "GptOssForCausalLM": dict(BASE, model_type="gpt_oss", head_dim=16, num_hidden_layers=4, intermediate_size=48, num_local_experts=4,
+                              num_experts_per_tok=2, sliding_window=16, pad_token_id=0,
+                              layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+                              rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
+                                               "truncate": False, "original_max_position_embeddings": 32}),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 
@@ -105,6 +110,10 @@ def test_greedy_tokens_and_logprobs_match_transformers(arch, tmp_path):
     for p in hf.parameters():  # widen the logit gaps so that greedy choices are not near-ties
         if p.dim() >= 2:
             p.data.mul_(3.0)
+    gb = torch.Generator().manual_seed(6)
+    for n, p in hf.named_parameters():   # biases and attention sinks start at zero or tiny: make them matter
+        if (n.endswith("bias") or n.endswith("sinks")) and "e_score_correction_bias" not in n:
+            p.data.normal_(0.0, 0.2, generator=gb)
     for n, p in list(hf.named_parameters()) + list(hf.named_buffers()):
         if "e_score_correction_bias" in n:  # zero at initialisation: give the router's selection bias something to do
             p.data.normal_(0.0, 0.05, generator=torch.Generator().manual_seed(4))

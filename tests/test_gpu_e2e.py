@@ -40,7 +40,7 @@ CFG_HUNYUAN = dict(architectures=["HunYuanDenseV1ForCausalLM"], hidden_size=512,
 # one pair of dense GEMMs per expert), head size 64
 CFG_GPTOSS = dict(architectures=["GptOssForCausalLM"], hidden_size=512, intermediate_size=512, num_hidden_layers=4, num_attention_heads=8,
                   num_key_value_heads=2, head_dim=64, rms_norm_eps=1e-5, vocab_size=2048, max_position_embeddings=2048, tie_word_embeddings=False,
-                  num_local_experts=4, num_experts_per_tok=2, sliding_window=64,
+                  num_local_experts=32, num_experts_per_tok=4, sliding_window=64,
                   layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
                   rope_parameters={"rope_type": "yarn", "rope_theta": 150000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0, "truncate": False,
                                    "original_max_position_embeddings": 512})
@@ -79,6 +79,21 @@ def test_engine_gpu_matches_cpu(tmp_path, eager, cfg, kvd):
     K.TORCH_STANDINS.clear()
     gpu.shutdown()
     cpu = LLM(model=path, device="cpu", dtype="float32", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8, kv_cache_dtype=kvd)
+    if cfg is CFG_GPTOSS:
+        # top-4 of 32 experts with random weights: a near-tie in the router forks the greedy path within a few tokens, so compare
+        # teacher-forced instead: the fp32 model scores the GPU's own tokens, and those scores must match what the GPU reported
+        diffs = []
+        for p, o in zip(prompts, og):
+            toks = o.outputs[0].token_ids
+            assert len(toks) == 24
+            r = cpu.generate([{"prompt_token_ids": p + toks}], SamplingParams(temperature=0.0, max_tokens=1, prompt_logprobs=0))[0]
+            for i, t in enumerate(toks):
+                diffs.append(abs(o.outputs[0].logprobs[i][t].logprob - r.prompt_logprobs[len(p) + i][t].logprob))
+        cpu.shutdown()
+        diffs.sort()
+        # bf16 against fp32 through four routed layers: typical differences are ~0.1 nat, a flipped expert costs up to ~1.5
+        assert diffs[len(diffs) // 2] < 0.2 and sum(diffs) / len(diffs) < 0.3 and diffs[-1] < 3.0, (diffs[len(diffs) // 2], sum(diffs) / len(diffs), diffs[-5:])
+        return
     # teacher-forced agreement: feed the GPU's own tokens to the CPU model and require each GPU token to be near the top
     # random weights give nearly flat logits, so greedy paths may fork on near-ties: require (a) close log-probabilities of the
     # first generated token wherever both runs picked the same one, (b) a reasonable common prefix overall

@@ -321,6 +321,9 @@ class ModelConfig:
         if a.startswith("olmoe"):
             kw.update(qk_norm_full=True)
         if a.startswith("gptoss"):
+            if kw["quant"].method == "mxfp4":
+                # the released checkpoints quantise the experts only (their skip list uses wildcards: name the modules here)
+                kw["quant"] = dataclasses.replace(kw["quant"], modules_to_not_convert=["self_attn", "mlp.gate", "lm_head", "embed_tokens"])
             kw.update(attention_bias=True, attn_o_bias=True, attn_sinks=True, router_linear_bias=True, expert_bias=True, moe_act="swiglu_oai",
                       norm_topk_prob=True, num_experts_per_tok=hf.get("num_experts_per_tok", hf.get("experts_per_token", 4)))
         if a.startswith("ernie4_5_moe"):

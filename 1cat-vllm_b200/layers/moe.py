@@ -110,7 +110,9 @@ class FusedMoE(nn.Module):
         if self.act != "silu" or self.w13_bias is not None:
             # experts with biases or the GPT-OSS activation: one pair of dense GEMMs per active expert (the grouped kernel's
             # epilogue implements SiLU·mul without bias only)
-            w13, w2 = self.dequantized()
+            if getattr(self, "_dq_model", None) is None or self._dq_model[0].dtype != x.dtype:
+                self._dq_model = tuple(t.to(x.dtype) for t in self.dequantized())   # packed experts are widened once for this path
+            w13, w2 = self._dq_model
             mm = None
             if x.is_cuda:
                 from onecat_vllm.ops import cuda as K

@@ -94,8 +94,21 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
                         mod.load_expert_weight(e, "down_proj", "bias", w[e])
                 loaded.add(name)
                 continue
-            if leaf.endswith(("_blocks", "_scales")):
-                raise ValueError(f"GPT-OSS expert tensor {name}: MXFP4 block tensors are not read (use a bf16 checkpoint)")
+            if mod is not None and leaf in ("gate_up_proj_blocks", "gate_up_proj_scales", "down_proj_blocks", "down_proj_scales"):
+                # MXFP4 release format: [E, rows, K/32, 16] bytes (two e2m1 per byte, low nibble first) and [E, rows, K/32] e8m0
+                # scales, in [out, in] orientation; gate / up rows alternate
+                if mod.qmethod != "mxfp4":
+                    raise ValueError("MXFP4 expert tensors need quantization_config.quant_method = mxfp4")
+                pn = "weight" if leaf.endswith("_blocks") else "weight_scale"
+                for e in range(w.shape[0]):
+                    t = w[e].reshape(w.shape[1], -1)
+                    if leaf.startswith("gate_up"):
+                        mod.load_expert_weight(e, "gate_proj", pn, t[0::2])
+                        mod.load_expert_weight(e, "up_proj", pn, t[1::2])
+                    else:
+                        mod.load_expert_weight(e, "down_proj", pn, t)
+                loaded.add(name)
+                continue
         if name.endswith((".mlp.experts.gate_up_proj", ".mlp.experts.down_proj")):
             # all experts of a layer in one tensor (the in-memory layout of recent transformers): [E, 2I, H] and [E, H, I]
             mod = mods.get(name.rsplit(".", 1)[0])

@@ -338,3 +338,47 @@ def test_compressed_tensors_checkpoints_match_their_dequantised_weights(tmp_path
         outs.append([o.outputs[0].token_ids for o in llm.generate(_prompts(300), SamplingParams(temperature=0, max_tokens=10, ignore_eos=True))])
         llm.shutdown()
     assert outs[0] == outs[1]
+
+
+def test_gpt_oss_mxfp4_release_format_matches_its_dequantised_checkpoint(tmp_path):
+    """GPT-OSS experts in the MXFP4 release layout (``*_blocks`` / ``*_scales``, alternating gate / up rows) against a bf16-layout
+    checkpoint (``[E, H, 2I]`` with alternating columns) holding the dequantised values."""
+    import json
+    from safetensors.torch import save_file
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    from onecat_vllm.ops import ref
+    base = dict(architectures=["GptOssForCausalLM"], hidden_size=64, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256, num_local_experts=4, num_experts_per_tok=2,
+                sliding_window=16, layer_types=["sliding_attention", "full_attention"], tie_word_embeddings=False)
+    m = build_model(ModelConfig.from_hf_dict(base, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    common = {k: v.contiguous() for k, v in to_hf_state_dict(m).items() if ".mlp.experts." not in k}
+    g = torch.Generator().manual_seed(1)
+    E, H, I = 4, 64, 64
+    dense, quant = dict(common), dict(common)
+    for layer in range(2):
+        pre = f"model.layers.{layer}.mlp.experts."
+        gu_b = torch.randint(0, 256, (E, 2 * I, H // 32, 16), generator=g, dtype=torch.uint8)
+        gu_s = torch.randint(118, 123, (E, 2 * I, H // 32), generator=g, dtype=torch.uint8)
+        dn_b = torch.randint(0, 256, (E, H, I // 32, 16), generator=g, dtype=torch.uint8)
+        dn_s = torch.randint(118, 123, (E, H, I // 32), generator=g, dtype=torch.uint8)
+        gu_bias, dn_bias = torch.randn(E, 2 * I, generator=g) * 0.1, torch.randn(E, H, generator=g) * 0.1
+        quant.update({pre + "gate_up_proj_blocks": gu_b, pre + "gate_up_proj_scales": gu_s, pre + "down_proj_blocks": dn_b,
+                      pre + "down_proj_scales": dn_s, pre + "gate_up_proj_bias": gu_bias, pre + "down_proj_bias": dn_bias})
+        gu = ref.mxfp4_dequantize(gu_b.reshape(E, 2 * I, H // 2), gu_s)      # [E, 2I, H], rows alternate gate / up
+        dn = ref.mxfp4_dequantize(dn_b.reshape(E, H, I // 2), dn_s)          # [E, H, I]
+        dense.update({pre + "gate_up_proj": gu.transpose(1, 2).contiguous(), pre + "down_proj": dn.transpose(1, 2).contiguous(),
+                      pre + "gate_up_proj_bias": gu_bias, pre + "down_proj_bias": dn_bias})
+    qcfg = {"quant_method": "mxfp4", "modules_to_not_convert": ["model.layers.*.self_attn", "model.layers.*.mlp.router", "model.embed_tokens", "lm_head"]}
+    outs = []
+    for tag, sd, cfg in (("dense", dense, base), ("quant", quant, dict(base, quantization_config=qcfg))):
+        d = tmp_path / tag
+        d.mkdir()
+        save_file(sd, str(d / "model.safetensors"))
+        (d / "config.json").write_text(json.dumps(cfg))
+        llm = LLM(model=str(d), max_model_len=128, dtype="float32", device="cpu")
+        outs.append([o.outputs[0].token_ids for o in llm.generate(_prompts(300), SamplingParams(temperature=0, max_tokens=10, ignore_eos=True))])
+        llm.shutdown()
+    assert outs[0] == outs[1]

@@ -397,6 +397,28 @@ def build_app(state: ServingState) -> FastAPI:
                 "stop_sequence": ch.get("stop_reason") if stop == "stop_sequence" else None,
                 "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"]}}
 
+    @app.post("/v1/messages/count_tokens")
+    async def anthropic_count_tokens(body: dict):
+        """Prompt length of a Messages request after the chat template (reference: entrypoints/anthropic count_tokens route)."""
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("the server has no tokenizer"), status_code=400)
+        msgs = [{"role": "system", "content": _text_of(body["system"])}] if body.get("system") else []
+        msgs += [{"role": m["role"], "content": _text_of(m.get("content", ""))} for m in body.get("messages", [])]
+        text = tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=True)
+        return {"input_tokens": len(tok.encode(text, add_special_tokens=False))}
+
+    @app.post("/invocations")
+    async def invocations(body: dict, raw: Request):
+        """Single entry point that dispatches on the shape of the body (reference: the SageMaker-style ``/invocations`` route)."""
+        if "messages" in body:
+            return await chat(ChatCompletionRequest(**body), raw)
+        if "prompt" in body:
+            return await completions(CompletionRequest(**body), raw)
+        if "input" in body:
+            return await embeddings(body)
+        return JSONResponse(error_body("the body must carry messages, prompt or input"), status_code=400)
+
     # ---- completions
     @app.post("/v1/completions")
     async def completions(req: CompletionRequest, raw: Request):

@@ -84,6 +84,13 @@ def test_server_routes(client):
                    "vllm:iteration_tokens_total_bucket", 'finished_reason="length"'):
         assert series in m, series
     assert client.get("/server_info").json()["block_size"] == 16
+    inv = client.post("/invocations", json={"prompt": "abc", "max_tokens": 3, "temperature": 0, "ignore_eos": True}).json()
+    assert inv["usage"]["completion_tokens"] == 3
+    inv = client.post("/invocations", json={"messages": [{"role": "user", "content": "hey"}], "max_tokens": 2, "temperature": 0, "ignore_eos": True}).json()
+    assert inv["choices"][0]["message"]["role"] == "assistant"
+    assert client.post("/invocations", json={"nothing": 1}).status_code == 400
+    n = client.post("/v1/messages/count_tokens", json={"system": "be brief", "messages": [{"role": "user", "content": "hello"}]}).json()["input_tokens"]
+    assert n > len("hello")
 
 
 @pytest.mark.timeout(300)

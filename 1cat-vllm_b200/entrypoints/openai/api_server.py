@@ -364,8 +364,6 @@ def build_app(state: ServingState) -> FastAPI:
 
     @app.post("/v1/messages")
     async def anthropic_messages(body: dict, raw: Request):
-        if body.get("stream"):
-            return JSONResponse(error_body("streaming messages are not supported; use /v1/chat/completions with stream"), status_code=400)
         msgs = []
         if body.get("system"):
             msgs.append({"role": "system", "content": _text_of(body["system"])})
@@ -380,6 +378,38 @@ def build_app(state: ServingState) -> FastAPI:
             creq = _as_chat(msgs, b2, "max_tokens")
         except Exception as e:
             return JSONResponse({"type": "error", "error": {"type": "invalid_request_error", "message": str(e)}}, status_code=400)
+        if body.get("stream"):
+            # the chat stream re-shaped into Messages events: message_start, one text block of deltas, message_delta, message_stop
+            creq.stream = True
+            sres = await chat(creq, raw)
+            if isinstance(sres, JSONResponse):
+                return sres
+
+            def ev(kind: str, data: dict) -> str:
+                return f"event: {kind}\ndata: {json.dumps(data)}\n\n"
+
+            async def gen():
+                mid, n_out, stop = new_id("msg"), 0, "end_turn"
+                yield ev("message_start", {"type": "message_start", "message": {"id": mid, "type": "message", "role": "assistant", "model": state.model_name,
+                                                                               "content": [], "stop_reason": None, "usage": {"input_tokens": 0, "output_tokens": 0}}})
+                yield ev("content_block_start", {"type": "content_block_start", "index": 0, "content_block": {"type": "text", "text": ""}})
+                async for chunk in sres.body_iterator:
+                    text = chunk.decode() if isinstance(chunk, (bytes, bytearray)) else chunk
+                    for line in text.split("\n"):
+                        if not line.startswith("data: ") or line.strip() == "data: [DONE]":
+                            continue
+                        d = json.loads(line[6:])
+                        for ch in d.get("choices", []):
+                            piece = (ch.get("delta") or {}).get("content")
+                            if piece:
+                                n_out += 1
+                                yield ev("content_block_delta", {"type": "content_block_delta", "index": 0, "delta": {"type": "text_delta", "text": piece}})
+                            if ch.get("finish_reason"):
+                                stop = {"stop": "end_turn", "length": "max_tokens", "tool_calls": "tool_use"}.get(ch["finish_reason"], "end_turn")
+                yield ev("content_block_stop", {"type": "content_block_stop", "index": 0})
+                yield ev("message_delta", {"type": "message_delta", "delta": {"stop_reason": stop, "stop_sequence": None}, "usage": {"output_tokens": n_out}})
+                yield ev("message_stop", {"type": "message_stop"})
+            return StreamingResponse(gen(), media_type="text/event-stream")
         res, err = await _run_chat(creq, raw)
         if err is not None:
             return err

@@ -327,8 +327,6 @@ def build_app(state: ServingState) -> FastAPI:
 
     @app.post("/v1/responses")
     async def responses(body: dict, raw: Request):
-        if body.get("stream"):
-            return JSONResponse(error_body("streaming responses are not supported; use /v1/chat/completions with stream"), status_code=400)
         msgs = []
         if body.get("instructions"):
             msgs.append({"role": "system", "content": body["instructions"]})
@@ -343,6 +341,39 @@ def build_app(state: ServingState) -> FastAPI:
             creq = _as_chat(msgs, body, "max_output_tokens")
         except Exception as e:
             return JSONResponse(error_body(str(e)), status_code=400)
+        if body.get("stream"):
+            # the chat stream re-shaped into Responses events: created, output_text deltas, output_text done, completed
+            creq.stream = True
+            sres = await chat(creq, raw)
+            if isinstance(sres, JSONResponse):
+                return sres
+
+            async def gen():
+                rid, seq, parts = new_id("resp"), 0, []
+
+                def ev(kind: str, data: dict) -> str:
+                    nonlocal seq
+                    seq += 1
+                    return f"event: {kind}\ndata: {json.dumps(dict(data, type=kind, sequence_number=seq))}\n\n"
+                head = {"id": rid, "object": "response", "created_at": now(), "model": state.model_name, "status": "in_progress", "output": []}
+                yield ev("response.created", {"response": head})
+                async for chunk in sres.body_iterator:
+                    text = chunk.decode() if isinstance(chunk, (bytes, bytearray)) else chunk
+                    for line in text.split("\n"):
+                        if not line.startswith("data: ") or line.strip() == "data: [DONE]":
+                            continue
+                        for ch in json.loads(line[6:]).get("choices", []):
+                            piece = (ch.get("delta") or {}).get("content")
+                            if piece:
+                                parts.append(piece)
+                                yield ev("response.output_text.delta", {"output_index": 0, "content_index": 0, "delta": piece})
+                full = "".join(parts)
+                yield ev("response.output_text.done", {"output_index": 0, "content_index": 0, "text": full})
+                done = dict(head, status="completed", output_text=full,
+                            output=[{"type": "message", "id": new_id("msg"), "role": "assistant", "status": "completed",
+                                     "content": [{"type": "output_text", "text": full, "annotations": []}]}])
+                yield ev("response.completed", {"response": done})
+            return StreamingResponse(gen(), media_type="text/event-stream")
         res, err = await _run_chat(creq, raw)
         if err is not None:
             return err

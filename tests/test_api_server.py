@@ -181,7 +181,12 @@ def test_responses_and_anthropic_messages_routes(client):
                                           "messages": [{"role": "user", "content": [{"type": "text", "text": "hello"}]}]}).json()
     assert m["type"] == "message" and m["role"] == "assistant" and m["stop_reason"] in ("end_turn", "max_tokens", "stop_sequence", "tool_use")
     assert m["usage"]["output_tokens"] <= 5
-    assert client.post("/v1/responses", json={"input": "x", "stream": True}).status_code == 400
+    kinds = []
+    with client.stream("POST", "/v1/responses", json={"input": "x", "stream": True, "max_output_tokens": 3, "temperature": 0}) as resp:
+        for line in resp.iter_lines():
+            if line.startswith("event: "):
+                kinds.append(line[7:])
+    assert kinds[0] == "response.created" and kinds[-2:] == ["response.output_text.done", "response.completed"]
     kinds = []
     with client.stream("POST", "/v1/messages", json={"model": "tiny", "max_tokens": 4, "temperature": 0, "stream": True,
                                                      "messages": [{"role": "user", "content": "hello"}]}) as resp:

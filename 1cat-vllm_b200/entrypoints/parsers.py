@@ -394,7 +394,75 @@ class SeedOssToolParser(Qwen3CoderToolParser):
     markers = ("<seed:tool_call>", "<function=")
 
 
+class TaggedJsonToolParser(HermesToolParser):
+    """Hermes layout with other tag strings (LongCat ``<longcat_tool_call>``)."""
+
+    def __init__(self, start: str, end: str):
+        self.markers = (start,)
+        self._start = start
+        self._re = re.compile(re.escape(start) + r"\s*(.*?)\s*(?:" + re.escape(end) + r"|$)", re.S)
+
+    def extract(self, text):
+        calls = []
+        for m in self._re.finditer(text):
+            try:
+                d = json.loads(m.group(1))
+                calls.append(ToolCall(d["name"], json.dumps(d.get("arguments", d.get("parameters", {})), ensure_ascii=False)))
+            except (json.JSONDecodeError, KeyError, TypeError):
+                continue
+        if not calls:
+            return text, []
+        return text[: text.find(self._start)].strip() or None, calls
+
+
+class InvokeXmlToolParser(ToolParser):
+    """MiniMax-M2 layout: ``<minimax:tool_call><invoke name="f"><parameter name="k">v</parameter></invoke></minimax:tool_call>``;
+    parameter values are JSON when they parse as JSON, else strings."""
+
+    markers = ("<minimax:tool_call>",)
+    _inv = re.compile(r"<invoke name=\"?([^\">]+)\"?>(.*?)(?:</invoke>|$)", re.S)
+    _par = re.compile(r"<parameter name=\"?([^\">]+)\"?>(.*?)</parameter>", re.S)
+
+    def extract(self, text):
+        calls = []
+        for m in self._inv.finditer(text):
+            args = {}
+            for k, v in self._par.findall(m.group(2)):
+                v = v.strip("\n")
+                try:
+                    args[k] = json.loads(v)
+                except json.JSONDecodeError:
+                    args[k] = v
+            calls.append(ToolCall(m.group(1).strip(), json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return text[: text.find(self.markers[0])].strip() or None, calls
+
+
+class WrappedPythonicToolParser(PythonicToolParser):
+    """LFM2 layout: a pythonic call list between ``<|tool_call_start|>`` and ``<|tool_call_end|>``; text around it is content."""
+
+    markers = ("<|tool_call_start|>",)
+    _re = re.compile(r"<\|tool_call_start\|>(.*?)(?:<\|tool_call_end\|>|$)", re.S)
+
+    def extract(self, text):
+        m = self._re.search(text)
+        if m is None:
+            return text, []
+        _, calls = super().extract(m.group(1).strip())
+        if not calls:
+            return text, []
+        rest = (text[: m.start()] + text[m.end():]).strip()
+        return rest or None, calls
+
+    def content_so_far(self, text):
+        i = text.find(self.markers[0])
+        return text if i == -1 else text[:i]
+
+
 TOOL_PARSERS = {
+    "longcat": lambda: TaggedJsonToolParser("<longcat_tool_call>", "</longcat_tool_call>"), "ernie45": HermesToolParser,
+    "minimax_m2": InvokeXmlToolParser, "lfm2": WrappedPythonicToolParser, "glm4_moe": Glm45ToolParser,
     "hermes": HermesToolParser, "qwen3_coder": Qwen3CoderToolParser, "qwen3_xml": Qwen3CoderToolParser,
     "deepseek_v3": DeepSeekV3ToolParser, "deepseek_v31": DeepSeekV31ToolParser,
     "llama3_json": Llama3JsonToolParser, "llama4_json": Llama3JsonToolParser, "pythonic": PythonicToolParser, "llama4_pythonic": PythonicToolParser,

@@ -36,6 +36,18 @@ def test_tool_parsers():
     assert HermesToolParser().extract("plain")[1] == []
 
 
+def test_tagged_invoke_and_wrapped_pythonic_tool_parsers():
+    from onecat_vllm.entrypoints.parsers import get_tool_parser
+    c, calls = get_tool_parser("longcat").extract('hi <longcat_tool_call>{"name": "f", "arguments": {"a": 1}}</longcat_tool_call>')
+    assert c == "hi" and calls[0].name == "f" and calls[0].arguments == '{"a": 1}'
+    c, calls = get_tool_parser("minimax_m2").extract('ok\n<minimax:tool_call>\n<invoke name="get_weather">\n<parameter name="city">Paris</parameter>\n'
+                                                     '<parameter name="days">3</parameter>\n</invoke>\n</minimax:tool_call>')
+    assert c == "ok" and calls[0].name == "get_weather" and calls[0].arguments == '{"city": "Paris", "days": 3}'
+    c, calls = get_tool_parser("lfm2").extract('<|tool_call_start|>[get_weather(location="Paris")]<|tool_call_end|>Checking.')
+    assert c == "Checking." and calls[0].arguments == '{"location": "Paris"}'
+    assert get_tool_parser("lfm2").extract("no call")[1] == [] and get_tool_parser("ernie45").extract('<tool_call>{"name": "g", "arguments": {}}</tool_call>')[1][0].name == "g"
+
+
 def test_parser_manager_and_channel_reasoning():
     from onecat_vllm.entrypoints.parsers import ParserManager, get_reasoning_parser
     r, c, calls = ParserManager("qwen3", "hermes").parse('<think>plan</think>ok <tool_call>{"name": "f", "arguments": {"a": 1}}</tool_call>')

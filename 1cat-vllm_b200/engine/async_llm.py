@@ -144,6 +144,15 @@ class AsyncLLM:
     async def wake_up(self) -> None:
         await self.engine_core.call_utility_async("wake_up")
 
+    async def pause_generation(self) -> None:
+        await self.engine_core.call_utility_async("pause_generation")
+
+    async def resume_generation(self) -> None:
+        await self.engine_core.call_utility_async("resume_generation")
+
+    async def is_paused(self) -> bool:
+        return bool(await self.engine_core.call_utility_async("is_paused"))
+
     async def profile(self, start: bool) -> None:
         await self.engine_core.call_utility_async("profile", start)
 

@@ -117,6 +117,16 @@ class EngineCore:
         self.executor.collective_rpc("wake_up")
         self.paused = False
 
+    def pause_generation(self) -> None:
+        """Stop scheduling steps; queued and running requests keep their state and KV (reference: v1/engine/core.py pause)."""
+        self.paused = True
+
+    def resume_generation(self) -> None:
+        self.paused = False
+
+    def is_paused(self) -> bool:
+        return self.paused
+
     def profile(self, start: bool = True) -> None:
         self.executor.collective_rpc("profile", (start,))
 

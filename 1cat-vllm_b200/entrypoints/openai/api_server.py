@@ -186,6 +186,21 @@ def build_app(state: ServingState) -> FastAPI:
         state.sleeping = True
         return Response(status_code=200)
 
+    @app.post("/pause")
+    async def pause():
+        """Requests stay queued with their KV until ``/resume`` (used around in-place weight updates)."""
+        await state.engine.pause_generation()
+        return {"paused": True}
+
+    @app.post("/resume")
+    async def resume():
+        await state.engine.resume_generation()
+        return {"paused": False}
+
+    @app.get("/is_paused")
+    async def is_paused():
+        return {"is_paused": await state.engine.is_paused()}
+
     @app.post("/wake_up")
     async def wake_up():
         await state.engine.wake_up()

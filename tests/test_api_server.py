@@ -101,6 +101,9 @@ def test_server_routes(client):
     inv = client.post("/invocations", json={"messages": [{"role": "user", "content": "hey"}], "max_tokens": 2, "temperature": 0, "ignore_eos": True}).json()
     assert inv["choices"][0]["message"]["role"] == "assistant"
     assert client.post("/invocations", json={"nothing": 1}).status_code == 400
+    assert client.post("/pause").json() == {"paused": True} and client.get("/is_paused").json()["is_paused"] is True
+    assert client.post("/resume").json() == {"paused": False} and client.get("/is_paused").json()["is_paused"] is False
+    assert client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 2, "temperature": 0, "ignore_eos": True}).json()["usage"]["completion_tokens"] == 2
     n = client.post("/v1/messages/count_tokens", json={"system": "be brief", "messages": [{"role": "user", "content": "hello"}]}).json()["input_tokens"]
     assert n > len("hello")
 

@@ -48,6 +48,13 @@ class InputProcessor:
                 raise ValueError("text prompts need a tokenizer; pass token ids or set tokenizer=")
             ids = list(self.tok.encode(text))
         mc = self.cfg.model_config
+        k = getattr(params, "truncate_prompt_tokens", None)
+        if k is not None and embeds is None:
+            if k == -1:
+                k = mc.max_model_len - 1
+            if k < 1:
+                raise ValueError("truncate_prompt_tokens must be a positive integer or -1")
+            ids = list(ids)[-k:]   # left truncation, as the reference does
         if not ids:
             raise ValueError("the prompt is empty")
         if len(ids) >= mc.max_model_len:

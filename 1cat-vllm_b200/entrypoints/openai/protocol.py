@@ -42,12 +42,20 @@ class _SamplingMixin(_Base):
     thinking_token_budget: Optional[int] = None
     repetition_detection: Optional[dict] = None
     prompt_logprobs: Optional[int] = None
+    truncate_prompt_tokens: Optional[int] = None
+    include_stop_str_in_output: bool = False
+    guided_json: Optional[Union[str, dict]] = None       # earlier spellings of structured_outputs
+    guided_regex: Optional[str] = None
+    guided_choice: Optional[list[str]] = None
+    guided_grammar: Optional[str] = None
     user: Optional[str] = None
 
     def to_sampling_params(self, default_max_tokens: int, logprobs: Optional[int] = None) -> SamplingParams:
         so = None
         if self.structured_outputs:
             so = StructuredOutputsParams(**self.structured_outputs)
+        elif self.guided_json is not None or self.guided_regex or self.guided_choice or self.guided_grammar:
+            so = StructuredOutputsParams(json=self.guided_json, regex=self.guided_regex, choice=self.guided_choice, grammar=self.guided_grammar)
         elif self.response_format and self.response_format.get("type") == "json_object":
             so = StructuredOutputsParams(json_object=True)
         elif self.response_format and self.response_format.get("type") == "json_schema":
@@ -62,6 +70,7 @@ class _SamplingMixin(_Base):
             logit_bias={int(k): float(v) for k, v in self.logit_bias.items()} if self.logit_bias else None,
             allowed_token_ids=self.allowed_token_ids, bad_words=self.bad_words, structured_outputs=so,
             thinking_token_budget=self.thinking_token_budget, prompt_logprobs=self.prompt_logprobs,
+            truncate_prompt_tokens=self.truncate_prompt_tokens, include_stop_str_in_output=self.include_stop_str_in_output,
             repetition_detection=RepetitionDetectionParams(**self.repetition_detection) if self.repetition_detection else None,
             output_kind=RequestOutputKind.DELTA if self.stream else RequestOutputKind.FINAL_ONLY)
 

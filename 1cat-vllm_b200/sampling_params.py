@@ -92,6 +92,7 @@ class SamplingParams:
     skip_special_tokens: bool = True
     spaces_between_special_tokens: bool = True
     include_stop_str_in_output: bool = False
+    truncate_prompt_tokens: Optional[int] = None  # keep only the last k prompt tokens (-1: as many as max_model_len allows)
     logit_bias: Optional[dict[int, float]] = None
     allowed_token_ids: Optional[list[int]] = None
     bad_words: Optional[list[str]] = None

@@ -101,6 +101,10 @@ def test_server_routes(client):
     inv = client.post("/invocations", json={"messages": [{"role": "user", "content": "hey"}], "max_tokens": 2, "temperature": 0, "ignore_eos": True}).json()
     assert inv["choices"][0]["message"]["role"] == "assistant"
     assert client.post("/invocations", json={"nothing": 1}).status_code == 400
+    tr = client.post("/v1/completions", json={"prompt": "abcdefghij", "max_tokens": 1, "temperature": 0, "truncate_prompt_tokens": 4}).json()
+    assert tr["usage"]["prompt_tokens"] == 4
+    gc = client.post("/v1/completions", json={"prompt": "pick: ", "max_tokens": 8, "temperature": 0, "guided_choice": ["yes", "no"]}).json()
+    assert gc["choices"][0]["text"] in ("yes", "no")
     assert client.post("/pause").json() == {"paused": True} and client.get("/is_paused").json()["is_paused"] is True
     assert client.post("/resume").json() == {"paused": False} and client.get("/is_paused").json()["is_paused"] is False
     assert client.post("/v1/completions", json={"prompt": "abc", "max_tokens": 2, "temperature": 0, "ignore_eos": True}).json()["usage"]["completion_tokens"] == 2

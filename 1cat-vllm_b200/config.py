@@ -173,6 +173,7 @@ class ModelConfig:
     max_loras: int = 4
     max_lora_rank: int = 64
     hf_overrides: dict = field(default_factory=dict)
+    logits_processors: tuple = ()  # "package.module:ClassName" of user logits processors applied to every sampling step
 
     def __post_init__(self) -> None:
         if self.num_attention_heads % max(self.num_key_value_heads, 1):
@@ -581,11 +582,13 @@ class EngineArgs:
     enable_lora: bool = False
     max_loras: int = 4
     max_lora_rank: int = 64
+    logits_processors: Optional[list] = None  # ["package.module:ClassName", ...]
 
     def create_engine_config(self) -> VllmConfig:
         dt = _DTYPES[self.dtype] if isinstance(self.dtype, str) else self.dtype
         over: dict[str, Any] = dict(seed=self.seed, load_format=self.load_format, tokenizer=self.tokenizer, enable_lora=self.enable_lora,
-                                    max_loras=self.max_loras, max_lora_rank=self.max_lora_rank)
+                                    max_loras=self.max_loras, max_lora_rank=self.max_lora_rank,
+                                    logits_processors=tuple(self.logits_processors or ()))
         if self.hf_config is not None:
             hf = dict(self.hf_config)
             hf.update(self.hf_overrides or {})

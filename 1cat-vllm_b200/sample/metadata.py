@@ -29,3 +29,5 @@ class SamplingMetadata:
     bad_words_token_ids: dict = field(default_factory=dict)  # row -> list[list[int]]
     grammar_bitmask: Optional[torch.Tensor] = None
     thinking: dict = field(default_factory=dict)  # row -> (budget, think-start id, think-end id)
+    custom_processors: list = field(default_factory=list)  # engine-level user logits processors (objects with ``apply``)
+    row_info: list = field(default_factory=list)  # per row: request id, prompt / output token ids, SamplingParams.extra_args

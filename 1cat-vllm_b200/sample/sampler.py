@@ -31,13 +31,15 @@ class Sampler:
             raw_lp = torch.log_softmax(logits.float(), dim=-1)
         simple = (md.all_greedy and md.no_penalties and not md.min_tokens and not any(md.logit_bias) and
                   not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and md.grammar_bitmask is None
-                  and not md.thinking)
+                  and not md.thinking and not md.custom_processors)
         if simple:
             sampled = ops.argmax(logits)  # greedy fast path: no fp32 copy of the logits
         else:
             lg = logits.float()
             lg = self.apply_logits_processors(lg, md)
             lg = self.apply_penalties(lg, md)
+            for proc in md.custom_processors:   # user processors see the fp32 logits after the built-in ones
+                lg = proc.apply(lg, md.row_info)
             sampled = self.sample(lg, md)
         lp = None
         if raw_lp is not None:

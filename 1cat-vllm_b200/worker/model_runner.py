@@ -110,6 +110,13 @@ class ModelRunner:
         if self.spec.enabled:
             from onecat_vllm.spec_decode.proposers import make_proposer
             self.proposer = make_proposer(self)
+        # user logits processors: ``module.path:ClassName`` (or dotted path), built once per worker as ``cls(vllm_config, device)``;
+        # each step they get ``apply(logits [B, V] fp32, rows)`` with one dict per sampling request (reference: v1/sample/logits_processor/)
+        self.custom_logits_processors = []
+        for spec in self.mc.logits_processors or []:
+            import importlib
+            mod_name, _, cls_name = spec.replace(":", ".").rpartition(".")
+            self.custom_logits_processors.append(getattr(importlib.import_module(mod_name), cls_name)(self.cfg, self.device))
         if self.mc.enable_lora:
             from onecat_vllm.lora import LoRAManager
             self.lora_manager = LoRAManager(self.model, self.mc.max_loras, self.mc.max_lora_rank, self.device, self.mc.dtype)
@@ -399,6 +406,11 @@ class ModelRunner:
                 md.bad_words_token_ids[i] = sp.bad_words_token_ids
             if sp.thinking_token_budget is not None and sp._think_ids is not None:
                 md.thinking[i] = (sp.thinking_token_budget, sp._think_ids[0], sp._think_ids[1])
+        if self.custom_logits_processors:
+            md.custom_processors = self.custom_logits_processors
+            md.row_info = [dict(request_id=s.req_id, prompt_token_ids=s.token_ids[: s.num_prompt_tokens],
+                                output_token_ids=s.token_ids[s.num_prompt_tokens:], extra_args=(sp.extra_args if sp else None) or {})
+                           for s, sp in zip(sel, sps)]
         md.logit_bias = [sp.logit_bias if sp else None for sp in sps]
         md.allowed_token_ids = [sp.allowed_token_ids if sp else None for sp in sps]
         return md

@@ -180,3 +180,22 @@ def test_repetition_detection_and_thinking_budget():
     lg[:, 42] = 5.0
     out = Sampler()(lg, md).sampled_token_ids.tolist()
     assert out == [101, 42, 42]  # row 0 used its budget; row 1 has one token left; row 2 already closed its block
+
+
+def test_user_logits_processor_is_applied_per_request():
+    """An engine-level logits processor named by its import path sees every sampling step with per-request context
+    (ids, extra_args) and can reshape the logits (reference: v1/sample/logits_processor/ custom processors)."""
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, logits_processors=["tests.logits_processor_example:BanOrForce"])
+    prompt = {"prompt_token_ids": list(range(3, 20))}
+    plain = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True))[0].outputs[0].token_ids
+    banned = llm.generate([prompt], SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, extra_args={"banned": plain}))[0].outputs[0].token_ids
+    assert not set(banned) & set(plain)
+    outs = llm.generate([prompt, prompt], [SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True, extra_args={"force": 7}),
+                                           SamplingParams(temperature=0.0, max_tokens=6, ignore_eos=True)])
+    forced, other = outs[0].outputs[0].token_ids, outs[1].outputs[0].token_ids
+    assert forced[1::2] == [7, 7, 7] and forced[0] == plain[0] and other == plain
+    llm.shutdown()

@@ -113,13 +113,23 @@ class LLM:
         return self.encode(prompts, pooling_params or PoolingParams(task="classify", normalize=False), use_tqdm)
 
     def score(self, text_1: Union[str, Sequence[str]], text_2: Union[str, Sequence[str]], use_tqdm: bool = False) -> list[float]:
-        """Cosine similarity of the two texts' embeddings (1:N or N:N)."""
+        """Similarity of text pairs (1:N or N:N): a cross-encoder checkpoint (sequence classification with one label) scores the
+        concatenated pair; any other model gives the cosine similarity of the two texts' embeddings
+        (reference: entrypoints/llm.py ``LLM.score``, entrypoints/pooling/score/)."""
         a = [text_1] if isinstance(text_1, str) else list(text_1)
         b = [text_2] if isinstance(text_2, str) else list(text_2)
         if len(a) == 1:
             a = a * len(b)
         if len(a) != len(b):
             raise ValueError("score() takes 1:N or N:N inputs")
+        mc = self.llm_engine.cfg.model_config
+        if mc.num_labels == 1:
+            tok = self.get_tokenizer()
+            sep = getattr(tok, "sep_token_id", None)
+            sep = mc.eos_token_id if sep is None else sep
+            pairs = [{"prompt_token_ids": list(tok.encode(x)) + ([sep] if sep is not None else []) + list(tok.encode(y, add_special_tokens=False))}
+                     for x, y in zip(a, b)]
+            return [o.outputs.data[0] for o in self.classify(pairs, use_tqdm=use_tqdm)]
         embs = self.embed(a + b, use_tqdm=use_tqdm)
         ea, eb = embs[: len(a)], embs[len(a):]
         return [sum(x * y for x, y in zip(p.outputs.data, q.outputs.data)) for p, q in zip(ea, eb)]

@@ -197,3 +197,28 @@ def test_sequence_classification_matches_transformers(tmp_path):
         assert torch.allclose(torch.tensor(o.outputs.data), torch.softmax(logits, -1), atol=2e-4), (o.outputs.data, logits)
     with torch.no_grad():
         assert torch.allclose(torch.tensor(raw[0].outputs.data), hf(torch.tensor([prompts[0]])).logits[0], atol=2e-3)
+
+
+@pytest.mark.timeout(600)
+def test_cross_encoder_score_matches_transformers(tmp_path):
+    """A one-label sequence-classification checkpoint scores text pairs: ``LLM.score`` encodes ``text_1 <sep> text_2`` and returns
+    sigmoid(score head), the value transformers gives for the same ids."""
+    from onecat_vllm import LLM
+    cfg = transformers.Qwen2Config(**{k: v for k, v in BASE.items()}, rope_theta=1e6, num_labels=1, pad_token_id=0, eos_token_id=257)
+    cfg.architectures = ["Qwen2ForSequenceClassification"]
+    torch.manual_seed(0)
+    hf = transformers.Qwen2ForSequenceClassification(cfg).eval().float()
+    for p in hf.parameters():
+        if p.dim() >= 2:
+            p.data.mul_(3.0)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128, tokenizer="byte")
+    tok = llm.get_tokenizer()
+    got = llm.score("what is a cat?", ["a small feline", "the stock market"])
+    llm.shutdown()
+    assert len(got) == 2 and got[0] != got[1]
+    for g, doc in zip(got, ["a small feline", "the stock market"]):
+        ids = list(tok.encode("what is a cat?")) + [257] + list(tok.encode(doc, add_special_tokens=False))
+        with torch.no_grad():
+            want = torch.sigmoid(hf(torch.tensor([ids])).logits[0, 0]).item()
+        assert abs(g - want) < 2e-4, (g, want)

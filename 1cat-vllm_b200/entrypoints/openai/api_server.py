@@ -313,6 +313,16 @@ def build_app(state: ServingState) -> FastAPI:
                 a = a * len(b)
             if len(a) != len(b):
                 raise ValueError("text_1 and text_2 must be 1:N or N:N")
+            mc = state.engine.cfg.model_config
+            if mc.num_labels == 1:   # cross-encoder: classify the concatenated pair
+                tok = state.engine.tokenizer
+                sep = getattr(tok, "sep_token_id", None)
+                sep = mc.eos_token_id if sep is None else sep
+                enc = lambda x, special=True: list(x) if not isinstance(x, str) else list(tok.encode(x, add_special_tokens=special))
+                pairs = [enc(x) + ([sep] if sep is not None else []) + enc(y, False) for x, y in zip(a, b)]
+                outs = await _pool_many(pairs, PoolingParams(task="classify", normalize=False), "score")
+                return {"id": new_id("score"), "object": "list", "created": now(), "model": state.model_name,
+                        "data": [{"index": i, "object": "score", "score": o.outputs.data[0]} for i, o in enumerate(outs)]}
             outs = await _pool_many(a + b, PoolingParams(task="embed", normalize=True), "score")
         except (ValueError, KeyError) as e:
             return JSONResponse(error_body(str(e)), status_code=400)

@@ -286,6 +286,12 @@ class ModelConfig:
             kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
             kw["rope_scaling"].setdefault("rope_type", rp.get("type"))
         lt = hf.get("layer_types")
+        if not lt and hf.get("sliding_window") and ("gemma2" in a or "gemma3" in a):
+            # configs written before ``layer_types`` existed: Gemma2 alternates, Gemma3 makes every ``sliding_window_pattern``-th layer global
+            pat = 2 if "gemma2" in a else int(hf.get("sliding_window_pattern", 6))
+            lt = ["sliding_attention" if (i + 1) % pat else "full_attention" for i in range(kw["num_hidden_layers"])]
+        if "gemma3" in a and kw.get("rope_local_theta") is None and hf.get("rope_local_base_freq"):
+            kw["rope_local_theta"] = float(hf["rope_local_base_freq"])
         if lt and any(t == "sliding_attention" for t in lt) and hf.get("sliding_window"):
             kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(i for i, t in enumerate(lt) if t == "sliding_attention"))
             if not kw.get("layer_types"):
@@ -296,6 +302,8 @@ class ModelConfig:
         if act in ("gelu_pytorch_tanh", "gelu_tanh", "gelu"):
             kw["hidden_act"] = "gelu_tanh"
         if "gemma" in a:
+            if "hidden_activation" not in hf and "hidden_act" not in hf:
+                kw["hidden_act"] = "gelu_tanh"   # the family's default when the config does not say
             kw.update(gemma_norm=True, embed_scale=float(hidden) ** 0.5, tie_word_embeddings=hf.get("tie_word_embeddings", True))
             if "gemma2" in a or "gemma3" in a:
                 kw.update(sandwich_norm=True, attn_scale=float(hf.get("query_pre_attn_scalar", kw["head_dim"])) ** -0.5,

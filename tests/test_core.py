@@ -237,3 +237,20 @@ def test_general_plugins_run_once_and_register_models(monkeypatch):
     assert P.load_general_plugins() == ["a"] and calls == ["a"]
     assert "MyOutOfTreeForCausalLM" in supported_architectures()
     assert P.load_general_plugins() == []  # once per process
+
+
+def test_older_gemma_config_formats_give_the_same_layer_layout():
+    """Checkpoints written before ``layer_types`` / ``rope_parameters`` existed: Gemma2 alternates sliding and global layers, Gemma3
+    makes every ``sliding_window_pattern``-th layer global and names its local rotary base ``rope_local_base_freq``."""
+    from onecat_vllm.config import ModelConfig
+    base = dict(hidden_size=64, num_attention_heads=4, num_key_value_heads=2, head_dim=16, query_pre_attn_scalar=16)
+    g2 = ModelConfig.from_hf_dict(dict(base, architectures=["Gemma2ForCausalLM"], num_hidden_layers=4, sliding_window=4096))
+    assert g2.sliding_layers == (0, 2) and g2.sliding_window == 4096 and g2.sandwich_norm and g2.hidden_act == "gelu_tanh"
+    g3 = ModelConfig.from_hf_dict(dict(base, architectures=["Gemma3ForCausalLM"], num_hidden_layers=12, sliding_window=1024, sliding_window_pattern=6,
+                                       rope_local_base_freq=10000.0, rope_theta=1e6, rope_scaling={"rope_type": "linear", "factor": 8.0},
+                                       hidden_activation="gelu_pytorch_tanh"))
+    assert g3.sliding_layers == (0, 1, 2, 3, 4, 6, 7, 8, 9, 10) and g3.rope_local_theta == 10000.0 and g3.rope_theta == 1e6
+    assert g3.rope_scaling == {"rope_type": "linear", "factor": 8.0} and g3.hidden_act == "gelu_tanh" and g3.qk_norm
+    new = ModelConfig.from_hf_dict(dict(base, architectures=["Gemma3ForCausalLM"], num_hidden_layers=4, sliding_window=16,
+                                        layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]))
+    assert new.sliding_layers == (0, 2)

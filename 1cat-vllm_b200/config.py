@@ -296,7 +296,7 @@ class ModelConfig:
             kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(i for i, t in enumerate(lt) if t == "sliding_attention"))
             if not kw.get("layer_types"):
                 kw["layer_types"] = None
-        elif hf.get("sliding_window") and hf.get("use_sliding_window", "mistral" in a):
+        elif hf.get("sliding_window") and hf.get("use_sliding_window", "mistral" in a or "phi3" in a):
             kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(range(kw["num_hidden_layers"])))
         act = hf.get("hidden_activation") or hf.get("hidden_act") or "silu"
         if act in ("gelu_pytorch_tanh", "gelu_tanh", "gelu"):

@@ -94,6 +94,7 @@ CASES = {
                               layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
                               rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
                                                "truncate": False, "original_max_position_embeddings": 32}),
+    "Phi3ForCausalLM+window": dict(BASE, model_type="phi3", rope_theta=10000.0, pad_token_id=0, sliding_window=16),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

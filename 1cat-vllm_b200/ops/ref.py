@@ -61,7 +61,7 @@ def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], devi
     (reference: layers/rotary_embedding/ — linear, llama3, yarn and DeepSeek-yarn variants; the formulas are the published ones)."""
     inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=device) / rotary_dim))
     kind = (scaling or {}).get("rope_type") or (scaling or {}).get("type") or "default"
-    if kind == "default":
+    if kind in ("default", "mrope"):   # multimodal rotary sections coincide with the plain rule for text-only positions
         return inv, 1.0
     f = float(scaling.get("factor", 1.0))
     if kind == "linear":
@@ -96,6 +96,9 @@ def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], devi
         else:
             att = yarn_mscale(f)
         return out, att
+    if kind == "dynamic":
+        # NTK-aware base change, fixed at the table's length (the rule rescales per sequence length; the table is built once)
+        raise ValueError("rope scaling type 'dynamic' is not supported: its base depends on the running sequence length")
     raise ValueError(f"rope scaling type {kind!r} is not supported")
 
 

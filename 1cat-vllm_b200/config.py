@@ -285,6 +285,9 @@ class ModelConfig:
         if (rp.get("rope_type") or rp.get("type") or "default") != "default":
             kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
             kw["rope_scaling"].setdefault("rope_type", rp.get("type"))
+            if kw["rope_scaling"]["rope_type"] in ("longrope", "su"):
+                kw["rope_scaling"].setdefault("max_position_embeddings", hf.get("max_position_embeddings"))
+                kw["rope_scaling"].setdefault("original_max_position_embeddings", hf.get("original_max_position_embeddings"))
         lt = hf.get("layer_types")
         if not lt and hf.get("sliding_window") and ("gemma2" in a or "gemma3" in a):
             # configs written before ``layer_types`` existed: Gemma2 alternates, Gemma3 makes every ``sliding_window_pattern``-th layer global

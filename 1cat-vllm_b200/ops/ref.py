@@ -96,6 +96,15 @@ def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], devi
         else:
             att = yarn_mscale(f)
         return out, att
+    if kind in ("longrope", "su"):
+        # Phi-3 long context: per-frequency divisors, the long set when the table extends past the original context
+        # (``scaling["max_pos"]`` is filled in by the table builder), and a magnitude factor from the extension ratio
+        max_pos = float(scaling.get("max_pos", orig))
+        ext = scaling["long_factor"] if max_pos > orig else scaling["short_factor"]
+        ratio = float(scaling.get("factor") or (float(scaling.get("max_position_embeddings", max_pos)) / orig))
+        att = scaling.get("attention_factor")
+        att = float(att) if att is not None else (1.0 if ratio <= 1.0 else math.sqrt(1.0 + math.log(ratio) / math.log(orig)))
+        return inv / torch.tensor(ext, dtype=torch.float32, device=device), att
     if kind == "dynamic":
         # NTK-aware base change, fixed at the table's length (the rule rescales per sequence length; the table is built once)
         raise ValueError("rope scaling type 'dynamic' is not supported: its base depends on the running sequence length")
@@ -103,6 +112,8 @@ def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], devi
 
 
 def build_cos_sin_cache(rotary_dim: int, max_pos: int, theta: float, device=None, scaling: Optional[dict] = None) -> torch.Tensor:
+    if scaling and (scaling.get("rope_type") or scaling.get("type")) in ("longrope", "su"):
+        scaling = dict(scaling, max_pos=max_pos)
     inv, att = scaled_inv_freq(rotary_dim, theta, scaling, device)
     t = torch.arange(max_pos, dtype=torch.float32, device=device)
     fr = torch.outer(t, inv)

@@ -95,6 +95,9 @@ CASES = {
                               rope_parameters={"rope_type": "yarn", "rope_theta": 10000.0, "factor": 4.0, "beta_fast": 32.0, "beta_slow": 1.0,
                                                "truncate": False, "original_max_position_embeddings": 32}),
     "Phi3ForCausalLM+window": dict(BASE, model_type="phi3", rope_theta=10000.0, pad_token_id=0, sliding_window=16),
+    "Phi3ForCausalLM+longrope": dict(BASE, model_type="phi3", pad_token_id=0, max_position_embeddings=512, original_max_position_embeddings=256,
+                                     rope_parameters={"rope_type": "longrope", "rope_theta": 10000.0, "original_max_position_embeddings": 256,
+                                                      "short_factor": [1.0 + 0.1 * i for i in range(8)], "long_factor": [2.0 + 0.3 * i for i in range(8)]}),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

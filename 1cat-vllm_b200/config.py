@@ -122,6 +122,7 @@ class ModelConfig:
     logit_scale: float = 1.0  # logits are multiplied by this (Granite: 1 / logits_scaling)
     attn_sinks: bool = False  # one learned sink logit per query head joins the softmax denominator (GPT-OSS)
     attn_o_bias: bool = False  # bias on the attention output projection
+    mlp_bias: bool = False  # biases on the dense feed-forward projections (Llama / Granite ``mlp_bias``)
     router_linear_bias: bool = False  # the router is a linear layer with bias
     expert_bias: bool = False  # every expert projection has a bias
     moe_act: str = "silu"  # silu | swiglu_oai: (up + 1) * gate * sigmoid(1.702 gate) with gate <= 7 and |up| <= 7 (GPT-OSS)
@@ -358,6 +359,13 @@ class ModelConfig:
         if "granite" in a:
             kw.update(embed_scale=float(hf.get("embedding_multiplier", 1.0)), residual_multiplier=float(hf.get("residual_multiplier", 1.0)),
                       attn_scale=float(hf.get("attention_multiplier", kw["head_dim"] ** -0.5)), logit_scale=1.0 / float(hf.get("logits_scaling", 1.0)))
+        # families whose ``attention_bias`` also puts a bias on the output projection (the others keep o_proj bias-free)
+        if kw.get("attention_bias") and a.startswith(("llama", "qwen3", "granite", "olmo", "smollm3", "gemma", "hunyuan", "dots1", "ernie4_5")):
+            kw["attn_o_bias"] = True
+        if a.startswith("seedoss"):
+            kw["attn_o_bias"] = bool(hf.get("attention_out_bias", False))
+        if hf.get("mlp_bias"):
+            kw["mlp_bias"] = True
         if arch.endswith("ForSequenceClassification"):
             kw["num_labels"] = int(hf.get("num_labels") or len(hf.get("id2label") or {}) or 2)
         kw.update(over)

@@ -8,15 +8,16 @@ from onecat_vllm.layers.linear import MergedColumnParallelLinear, RowParallelLin
 
 
 class MLP(nn.Module):
-    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True, fuse_act: bool = True, act: str = "silu"):
+    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, parallel: bool = True, fuse_act: bool = True, act: str = "silu",
+                 bias: bool = False):
         """``fuse_act=False`` (LoRA-enabled models) keeps gate|up as a plain GEMM so adapter deltas can be added before SiLU·mul.
         ``act="gelu_tanh"`` (Gemma GeGLU) always takes the unfused form: the GEMM epilogue implements SiLU·mul only."""
         super().__init__()
-        fuse_act = fuse_act and act == "silu"
+        fuse_act = fuse_act and act == "silu" and not bias   # the fused epilogue has no bias input
         self.fuse_act, self.act = fuse_act, act
-        self.gate_up_proj = MergedColumnParallelLinear(hidden, [inter, inter], quant=quant, prefix=prefix + ".gate_up_proj",
+        self.gate_up_proj = MergedColumnParallelLinear(hidden, [inter, inter], bias=bias, quant=quant, prefix=prefix + ".gate_up_proj",
                                                        dtype=dtype, fuse_silu_mul=fuse_act)
-        self.down_proj = RowParallelLinear(inter, hidden, quant=quant, prefix=prefix + ".down_proj", dtype=dtype)
+        self.down_proj = RowParallelLinear(inter, hidden, bias=bias, quant=quant, prefix=prefix + ".down_proj", dtype=dtype)
 
     def forward(self, x):
         h = self.gate_up_proj(x)

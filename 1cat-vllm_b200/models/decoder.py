@@ -46,7 +46,7 @@ class DecoderLayer(nn.Module):
             self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
         else:
             self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
-                           act=cfg.hidden_act)
+                           act=cfg.hidden_act, bias=cfg.mlp_bias)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         if cfg.sandwich_norm:

@@ -98,6 +98,10 @@ CASES = {
     "Phi3ForCausalLM+longrope": dict(BASE, model_type="phi3", pad_token_id=0, max_position_embeddings=512, original_max_position_embeddings=256,
                                      rope_parameters={"rope_type": "longrope", "rope_theta": 10000.0, "original_max_position_embeddings": 256,
                                                       "short_factor": [1.0 + 0.1 * i for i in range(8)], "long_factor": [2.0 + 0.3 * i for i in range(8)]}),
+    "LlamaForCausalLM+attention-bias": dict(BASE, model_type="llama", rope_theta=10000.0, attention_bias=True),
+    "Qwen3ForCausalLM+attention-bias": dict(BASE, model_type="qwen3", head_dim=32, rope_theta=1e6, attention_bias=True),
+    "SeedOssForCausalLM+out-bias": dict(BASE, model_type="seed_oss", head_dim=16, rope_theta=10000.0, attention_bias=True, attention_out_bias=True),
+    "LlamaForCausalLM+mlp-bias": dict(BASE, model_type="llama", rope_theta=10000.0, mlp_bias=True),
     "MistralForCausalLM+window": dict(BASE, model_type="mistral", rope_theta=10000.0, sliding_window=16),
 }
 

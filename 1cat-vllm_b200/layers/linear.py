@@ -297,6 +297,8 @@ class LinearBase(nn.Module):
         ``shard_id`` selects the stacked segment the tensor belongs to; ``None`` = the tensor spans all segments."""
         if pname in ("input_scale", "input_zero_point", "output_scale", "weight_g_idx") and not hasattr(self, pname):
             return  # static activation scales of W8A8 checkpoints: activations stay bf16 here (weight-only use of the weights)
+        if pname == "bias" and self.parallel == "row" and self.tp > 1 and self.tp_rank != 0:
+            return  # the ranks' outputs are summed: the bias joins once, on rank 0 (the others keep zeros)
         param = getattr(self, pname)
         oa, od, ia, idv = self.method.layout(self, pname) if pname != "bias" else (0, 1, None, 1)
         if loaded.dim() == 0 or (oa is None and loaded.numel() == 1):   # per-tensor scalars arrive as 0-d or one-element tensors

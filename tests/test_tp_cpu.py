@@ -82,3 +82,30 @@ def test_pipeline_parallel_cpu_matches_single(tmp_path, tp, pp):
     got = [o.outputs[0].token_ids for o in many.generate(prompts, sps)]
     many.shutdown()
     assert got == ref
+
+
+@pytest.mark.timeout(300)
+def test_row_parallel_biases_join_the_sum_once(tmp_path):
+    """Biases on the output projection and the down projection (attention_bias / mlp_bias): with two ranks their partial outputs are
+    summed, so the bias must come from one rank only; the decode must equal the single-rank one."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    cfg = dict(CFG, attention_bias=True, mlp_bias=True)
+    m = build_model(ModelConfig.from_hf_dict(cfg, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    for n, p in m.named_parameters():
+        if n.endswith("bias"):
+            p.data.normal_(0.0, 0.3, generator=torch.Generator().manual_seed(3))
+    assert m.model.layers[0].self_attn.o_proj.bias is not None and m.model.layers[0].mlp.down_proj.bias is not None
+    save_pretrained(m, cfg, str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (9, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    one = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)
+    ref = [o.outputs[0].token_ids for o in one.generate(prompts, sp)]
+    one.shutdown()
+    two = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128, tensor_parallel_size=2, distributed_executor_backend="mp")
+    got = [o.outputs[0].token_ids for o in two.generate(prompts, sp)]
+    two.shutdown()
+    assert got == ref

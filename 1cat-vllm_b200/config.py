@@ -286,6 +286,8 @@ class ModelConfig:
         if (rp.get("rope_type") or rp.get("type") or "default") != "default":
             kw["rope_scaling"] = {k: v for k, v in rp.items() if k not in ("rope_theta", "partial_rotary_factor")}
             kw["rope_scaling"].setdefault("rope_type", rp.get("type"))
+            if kw["rope_scaling"]["rope_type"] == "dynamic":
+                kw["rope_scaling"].setdefault("original_max_position_embeddings", hf.get("max_position_embeddings"))
             if kw["rope_scaling"]["rope_type"] in ("longrope", "su"):
                 kw["rope_scaling"].setdefault("max_position_embeddings", hf.get("max_position_embeddings"))
                 kw["rope_scaling"].setdefault("original_max_position_embeddings", hf.get("original_max_position_embeddings"))

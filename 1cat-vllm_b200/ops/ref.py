@@ -106,8 +106,10 @@ def scaled_inv_freq(rotary_dim: int, theta: float, scaling: Optional[dict], devi
         att = float(att) if att is not None else (1.0 if ratio <= 1.0 else math.sqrt(1.0 + math.log(ratio) / math.log(orig)))
         return inv / torch.tensor(ext, dtype=torch.float32, device=device), att
     if kind == "dynamic":
-        # NTK-aware base change, fixed at the table's length (the rule rescales per sequence length; the table is built once)
-        raise ValueError("rope scaling type 'dynamic' is not supported: its base depends on the running sequence length")
+        # NTK-aware base change evaluated once for the extended length ``factor * original`` (reference:
+        # layers/rotary_embedding/dynamic_ntk_scaling_rope.py computes its table the same way)
+        base = theta * ((f * (orig * f) / orig) - (f - 1.0)) ** (rotary_dim / max(rotary_dim - 2, 1))
+        return 1.0 / (base ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=device) / rotary_dim)), 1.0
     raise ValueError(f"rope scaling type {kind!r} is not supported")
 
 

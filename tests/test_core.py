@@ -254,3 +254,24 @@ def test_older_gemma_config_formats_give_the_same_layer_layout():
     new = ModelConfig.from_hf_dict(dict(base, architectures=["Gemma3ForCausalLM"], num_hidden_layers=4, sliding_window=16,
                                         layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"]))
     assert new.sliding_layers == (0, 2)
+
+
+def test_rotary_scaling_rules_build_tables():
+    """Every supported context-extension rule yields a finite [max_pos, rotary_dim] table; linear scaling equals position / factor
+    and the dynamic rule equals the plain rule with its NTK-adjusted base."""
+    import torch
+    from onecat_vllm.ops import ref
+    plain = ref.build_cos_sin_cache(16, 64, 1e4)
+    lin = ref.build_cos_sin_cache(16, 64, 1e4, None, {"rope_type": "linear", "factor": 4.0})
+    assert torch.allclose(lin[4::4][:8], plain[1:9], atol=1e-6)
+    for sc in ({"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0, "original_max_position_embeddings": 32},
+               {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 32},
+               {"type": "mrope", "mrope_section": [2, 3, 3]},
+               {"rope_type": "longrope", "short_factor": [1.0] * 8, "long_factor": [2.0] * 8, "original_max_position_embeddings": 32},
+               {"rope_type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 32}):
+        t = ref.build_cos_sin_cache(16, 64, 1e4, None, sc)
+        assert t.shape == (64, 16) and torch.isfinite(t).all()
+    dyn = ref.build_cos_sin_cache(16, 64, 1e4, None, {"rope_type": "dynamic", "factor": 2.0, "original_max_position_embeddings": 32})
+    base = 1e4 * ((2.0 * 64 / 32) - 1.0) ** (16 / 14)
+    assert torch.allclose(dyn, ref.build_cos_sin_cache(16, 64, base), atol=1e-6)
+    assert torch.equal(ref.build_cos_sin_cache(16, 64, 1e4, None, {"type": "mrope"}), plain)

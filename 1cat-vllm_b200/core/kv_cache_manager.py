@@ -69,7 +69,7 @@ class KVCacheManager:
                 break
             hit.append(b)
         if self.offload is not None and len(hit) < max_blocks:
-            hit += self._restore_from_cpu(request.block_hashes[len(hit):max_blocks])
+            hit += self._restore_from_cpu(request.block_hashes[len(hit):max_blocks], hit)
         if self.use_eagle and hit:  # the draft head needs the hidden state of the last matched block
             hit.pop()
         if self.stats is not None:
@@ -88,21 +88,34 @@ class KVCacheManager:
             self.offload = self.block_pool.offload = SharedStorageTier(extra.get("shared_storage_path", "/tmp/onecat_kv"),
                                                                        kv_transfer_config.get("kv_role", "kv_both"))
 
-    def _restore_from_cpu(self, hashes: list) -> list[KVCacheBlock]:
+    def _restore_from_cpu(self, hashes: list, gpu_hits: list[KVCacheBlock]) -> list[KVCacheBlock]:
         """Continue a prefix match in the CPU tier: every consecutive hit gets a fresh GPU block, a restore copy for this step and its
         place in the GPU index; the blocks go back to the free queue (cached, unreferenced) so that the caller treats them like
-        any other prefix hit. Keeps a reserve of free blocks so that restores never starve new tokens."""
+        any other prefix hit. Keeps a reserve of free blocks so that restores never starve new tokens.
+
+        The GPU hits found just before are unreferenced blocks at the head of the free queue (a partial eviction leaves exactly the
+        surviving prefix there), so they are held while the fresh blocks are taken: otherwise the restore would pop the hits
+        themselves, strip their hashes and hand them out a second time. Hits and restored blocks are released together, tail of
+        the prefix first, which puts the whole prefix at the young end of the queue."""
         pool, got = self.block_pool, []
-        for h in hashes:
-            c = self.offload.lookup(h)
-            if c is None or pool.get_num_free_blocks() < 8:
-                break
-            b = pool.get_new_blocks(1)[0]
-            b.block_hash = h
-            pool.cached.setdefault(h, {})[b.block_id] = b
-            self.offload.restore(c, b.block_id)
-            got.append(b)
-        pool.free_blocks(got)
+        pool.touch(gpu_hits)
+        try:
+            for h in hashes:
+                c = self.offload.lookup(h)
+                if c is None or pool.get_num_free_blocks() < 8:
+                    break
+                if pool.get_cached_block(h) is not None:  # came back through another request since the walk stopped
+                    b = pool.get_cached_block(h)
+                    pool.touch([b])
+                    got.append(b)
+                    continue
+                b = pool.get_new_blocks(1)[0]
+                b.block_hash = h
+                pool.cached.setdefault(h, {})[b.block_id] = b
+                self.offload.restore(c, b.block_id)
+                got.append(b)
+        finally:
+            pool.free_blocks(reversed(gpu_hits + got))
         return got
 
     def allocate_slots(self, request, num_new_tokens: int, num_new_computed_tokens: int = 0,

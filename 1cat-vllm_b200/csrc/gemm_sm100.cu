@@ -20,6 +20,8 @@
 //
 // Role of this file in the reference's terms: replaces the TurboMind s884 GEMM family and its dispatch
 // (reference: csrc/sm70_turbomind/ops/awq_sm70_gemm.cu:3161,3278; gemm_universal.h:238) and cuBLAS for dense layers.
+#include <stdlib.h>
+
 #include "common.cuh"
 #include "gemm_sm100.h"
 
@@ -30,11 +32,19 @@ namespace {
 // warp roles: 0 X producer, 1 MMA, then the dequantisation warps (4-bit weights: two groups of four that take alternate k tiles,
 // so one group's shared-memory and TMEM latencies hide behind the other's arithmetic), four epilogue warps, and for 4-bit
 // weights one more warp that streams packed tiles.
-template <int WKIND> struct Roles {
-  static constexpr int kDqWarps = WKIND >= 1 ? 8 : 0;
-  static constexpr int kEpi0 = 2 + kDqWarps;          // first epilogue warp (2 or 10: both are 2 mod 4, the quarters line up)
+//
+// SMALL (packed weights, token tile <= 64): a lighter CTA of which two share an SM. Measured on B200, the thread that issues
+// tcgen05.mma spends ~80 cycles per instruction whatever the token tile, so a 128 x 64 x 64 block of four MMAs costs it more than
+// the tensor pipe (4 x 32 cycles) or the memory system needs; a second resident CTA brings a second issuing thread and a second
+// barrier chain. Such a CTA has one group of four dequantisation warps, one accumulator and half of the SM's TMEM columns.
+template <int WKIND, int SMALL> struct Roles {
+  static constexpr int kDqGroups = SMALL ? 1 : 2;
+  static constexpr int kDqWarps = WKIND >= 1 ? 4 * kDqGroups : 0;
+  static constexpr int kEpi0 = 2 + kDqWarps;          // first epilogue warp (2, 6 or 10: all are 2 mod 4, the quarters line up)
   static constexpr int kPacked = kEpi0 + 4;           // packed-tile producer (4-bit only)
   static constexpr int kThreads = (kEpi0 + 4 + (WKIND >= 1 ? 1 : 0)) * 32;
+  static constexpr int kCtasPerSm = SMALL ? 2 : 1;
+  static constexpr int kTmemCols = SMALL ? 256 : 512;
 };
 constexpr int BM = 128;  // weight rows (output features) per tile = UMMA M
 constexpr int BK = 64;   // k per stage: one 128-byte swizzle atom of bf16
@@ -47,7 +57,6 @@ __host__ __device__ constexpr int packed_bytes(int wkind) { return wkind == 2 ? 
 __host__ __device__ constexpr int sz_words(int wkind) { return wkind == 4 ? 2 : 1; }
 __host__ __device__ constexpr int sz_bytes(int wkind) { return BM * 4 * sz_words(wkind); }
 __host__ __device__ constexpr int packed_slot(int wkind) { return packed_bytes(wkind) + sz_bytes(wkind); }
-constexpr int kTmemCols = 512;
 // 4-bit weights: the dequantised weight tiles form a ring in TMEM (32 columns per 128 x 64 tile) at the top of the 512 columns,
 // `stages` deep and in lock step with the X ring in shared memory: 8 tiles when the two accumulators fit 256 columns (token tile
 // <= 128), else 4 (token tile 192).
@@ -55,11 +64,11 @@ constexpr int kTmemCols = 512;
 struct SmemLayout {
   uint32_t x_off, w_off, p_off, bar_off, total;
 };
-__host__ __device__ inline SmemLayout make_layout(int tn, int nt_sub, int xstages, int stages, int pstages, int wkind) {
+__host__ __device__ inline SmemLayout make_layout(int tn, int nt_sub, int xstages, int stages, int pstages, int wkind, int kps) {
   SmemLayout L;
   uint32_t o = 0;
   L.x_off = o;
-  o += (uint32_t)xstages * nt_sub * tn * 128;
+  o += (uint32_t)xstages * kps * nt_sub * tn * 128;
   L.w_off = o;
   o += (pstages > 0 ? 0u : (uint32_t)stages * kWStageBytes);  // 4-bit weights are dequantised into TMEM, not shared memory
   L.p_off = o;
@@ -109,8 +118,8 @@ __device__ __forceinline__ void store_out(const GemmParams& p, int t, int n, __n
   }
 }
 
-template <int WKIND>
-__global__ void __launch_bounds__(Roles<WKIND>::kThreads, 1)
+template <int WKIND, int SMALL>
+__global__ void __launch_bounds__((Roles<WKIND, SMALL>::kThreads), (Roles<WKIND, SMALL>::kCtasPerSm))
 gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW, const GemmParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes the swizzle needs
@@ -118,8 +127,12 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   constexpr int kPackedBytes = packed_bytes(WKIND), kPackedSlot = packed_slot(WKIND);
   // NT token sub-tiles per work item (1 or 2): with two, a dequantised weight tile feeds two accumulators (2 x tn tokens), which
   // halves the dequantisation and MMA-issue work per token; both accumulators then belong to one work item.
-  const int NT = p.nt_sub, NB = 2 / NT;
-  const SmemLayout L = make_layout(p.tn, NT, p.xstages, p.stages, p.pstages, WKIND);
+  using R = Roles<WKIND, SMALL>;
+  constexpr int kTmemCols = R::kTmemCols;
+  const int NT = SMALL ? 1 : p.nt_sub, NB = SMALL ? 1 : 2 / NT;
+  // k tiles per stage: a stage of the X / dequantised-W ring carries KPS k tiles behind one full and one empty barrier
+  const int KPS = p.kps;
+  const SmemLayout L = make_layout(p.tn, NT, p.xstages, p.stages, p.pstages, WKIND, KPS);
   uint8_t* sx = smem + L.x_off;
   uint8_t* sw = smem + L.w_off;
   uint8_t* sp = smem + L.p_off;
@@ -203,18 +216,21 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        for (int kt = k0; kt < k1; ++kt) {
+        for (int kt = k0; kt < k1; kt += KPS) {
+          const int kc = min(KPS, k1 - kt);
           ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
-          mbar_expect_tx(&full[st.idx], bytes);
-          for (int i = 0; i < NT; ++i)  // rows past T are zero-filled by the copy
-            tma_load_2d(sx + (st.idx * NT + i) * xs, &tmX, kt * BK, grouped ? tt : (tt * NT + i) * tn, &full[st.idx]);
-          if (WKIND == 0) tma_load_2d(sw + st.idx * kWStageBytes, &tmW, kt * BK, nt * BM, &full[st.idx]);
+          mbar_expect_tx(&full[st.idx], bytes * kc);
+          for (int j = 0; j < kc; ++j) {
+            for (int i = 0; i < NT; ++i)  // rows past T are zero-filled by the copy
+              tma_load_2d(sx + ((st.idx * KPS + j) * NT + i) * xs, &tmX, (kt + j) * BK, grouped ? tt : (tt * NT + i) * tn, &full[st.idx]);
+            if (WKIND == 0) tma_load_2d(sw + (st.idx * KPS + j) * kWStageBytes, &tmW, (kt + j) * BK, nt * BM, &full[st.idx]);
+          }
           st.advance(S);
         }
       }
     }
-  } else if (warp == Roles<WKIND>::kPacked) {
+  } else if (warp == R::kPacked) {
     // ------------------------------------------------------------------ packed-weight producer (runs PS tiles ahead)
     if (WKIND >= 1 && lane == 0) {
       Ring pr;
@@ -249,7 +265,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       bool ok = true;
       const uint32_t xs = (uint32_t)tn * 128;
       const uint32_t a_base = smem_u32(sw), b_base = smem_u32(sx);
-      const uint32_t ta_base = tmem_base + (kTmemCols - S * 32);
+      const uint32_t ta_base = tmem_base + (kTmemCols - S * KPS * 32);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
@@ -259,36 +275,40 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         tc_fence_after();
         const uint32_t d_addr = tmem_base + acc * NT * p.acc_stride;
         uint32_t accum = 0;
-        for (int kt = k0; kt < k1; ++kt) {
+        for (int kt = k0; kt < k1; kt += KPS) {
+          const int kc = min(KPS, k1 - kt);
           const int s = st.idx;
           ok = mbar_wait(&full[s], st.phase, abort_flag);
           if (!ok) break;
           tc_fence_after();
-          const uint64_t db = umma_desc_sw128(b_base + s * NT * xs);
-          if (WKIND >= 1) {
-            const uint32_t ta = ta_base + s * 32;  // 64 k of bf16 = 32 columns per stage
-            if (NT == 1) {  // the common case stays branch-free: this thread is the kernel's critical path
+          for (int jj = 0; jj < kc; ++jj) {
+            const int sk = s * KPS + jj;  // k tile slot of the ring
+            const uint64_t db = umma_desc_sw128(b_base + sk * NT * xs);
+            if (WKIND >= 1) {
+              const uint32_t ta = ta_base + sk * 32;  // 64 k of bf16 = 32 columns per k tile
+              if (NT == 1) {  // the common case stays branch-free: this thread is the kernel's critical path
 #pragma unroll
-              for (int j = 0; j < BK / 16; ++j) {
-                umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
+                for (int j = 0; j < BK / 16; ++j) {
+                  umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
+                  accum = 1;
+                }
+              } else {
+                for (int i = 0; i < NT; ++i) {
+                  const uint64_t dbi = umma_desc_sw128(b_base + (sk * NT + i) * xs);
+#pragma unroll
+                  for (int j = 0; j < BK / 16; ++j)
+                    umma_bf16_ts(d_addr + i * p.acc_stride, ta + j * 8, dbi + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
+                }
                 accum = 1;
               }
             } else {
-              for (int i = 0; i < NT; ++i) {
-                const uint64_t dbi = umma_desc_sw128(b_base + (s * NT + i) * xs);
+              const uint64_t da = umma_desc_sw128(a_base + sk * kWStageBytes);
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j)
-                  umma_bf16_ts(d_addr + i * p.acc_stride, ta + j * 8, dbi + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
+              for (int j = 0; j < BK / 16; ++j) {
+                // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
+                umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accum);
+                accum = 1;
               }
-              accum = 1;
-            }
-          } else {
-            const uint64_t da = umma_desc_sw128(a_base + s * kWStageBytes);
-#pragma unroll
-            for (int j = 0; j < BK / 16; ++j) {
-              // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
-              umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accum);
-              accum = 1;
             }
           }
           umma_commit(&empty[s]);  // frees the stage (both operands) once these MMAs have read it
@@ -297,29 +317,32 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
         if (ok) umma_commit(&tfull[acc]);
       }
     }
-  } else if (warp < Roles<WKIND>::kEpi0) {
+  } else if (warp < R::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
     if (WKIND >= 1) {
       const int r = (warp & 3) * 32 + lane;  // weight row = TMEM lane this warp may write
-      const int grp = (warp - 2) >> 2;       // 0: even k tiles of the CTA's sequence, 1: odd ones
+      const int grp = (warp - 2) >> 2;       // 0: even stages of the CTA's sequence, 1: odd ones (one group when SMALL)
       uint32_t seq = 0;
       Ring st, pr;
       bool ok = true;
       const uint32_t sp_u32 = smem_u32(sp);
-      const uint32_t ta_row = tmem_base + (kTmemCols - S * 32) + ((uint32_t)((warp & 3) * 32) << 16);
+      const uint32_t ta_row = tmem_base + (kTmemCols - S * KPS * 32) + ((uint32_t)((warp & 3) * 32) << 16);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
-        for (int kt = k0; kt < k1; ++kt) {
-          if ((int)(seq++ & 1u) != grp) {  // the other group's tile: just keep the ring cursors in step
+        for (int kt = k0; kt < k1 && ok; kt += KPS) {
+          const int kc = min(KPS, k1 - kt);
+          if (R::kDqGroups > 1 && (int)(seq++ & 1u) != grp) {  // the other group's stage: just keep the ring cursors in step
             st.advance(S);
-            pr.advance(PS);
+            for (int j = 0; j < kc; ++j) pr.advance(PS);
             continue;
           }
-          ok = mbar_wait(&pfull[pr.idx], pr.phase, abort_flag);
-          if (ok) ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
+          ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+         for (int jj = 0; jj < kc; ++jj) {
+          ok = mbar_wait(&pfull[pr.idx], pr.phase, abort_flag);
+          if (!ok) break;
           const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
           const uint32_t szv = WKIND == 4 ? 0u : lds32(slot + kPackedBytes + r * 4);
           const uint32_t s2 = (szv & 0xffffu) | (szv << 16);          // low half replicated
@@ -366,13 +389,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           }
           __syncwarp();
           if (lane == 0) mbar_arrive(&pempty[pr.idx]);  // the packed words are in registers (one arrival per warp, not per thread)
-          tmem_st_32x32(ta_row + st.idx * 32, o);
+          tmem_st_32x32(ta_row + (st.idx * KPS + jj) * 32, o);
+          pr.advance(PS);
+         }
+          if (!ok) break;
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(&full[st.idx]);
           st.advance(S);
-          pr.advance(PS);
         }
       }
     }
@@ -380,7 +405,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     // ------------------------------------------------------------------ epilogue
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;       // weight row inside the tile
-    const int et = threadIdx.x - Roles<WKIND>::kEpi0 * 32;    // 0..127
+    const int et = threadIdx.x - R::kEpi0 * 32;    // 0..127
     uint32_t tile_i = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
@@ -548,11 +573,21 @@ int make_tmap_bf16(CUtensorMap* tm, const void* base, uint64_t rows, uint64_t co
 }  // namespace
 
 int gemm_smem_bytes(const GemmParams& p) {
-  return (int)make_layout(p.tn, p.nt_sub < 1 ? 1 : p.nt_sub, p.xstages, p.stages, p.pstages, p.wkind).total + 1024;
+  return (int)make_layout(p.tn, (p.nt_sub < 1 || p.small) ? 1 : p.nt_sub, p.xstages, p.stages, p.pstages, p.wkind, p.kps < 1 ? 1 : p.kps).total + 1024;
 }
+
+namespace {
+// Experiment switches (read once): ONECAT_W4_SMALL=0 keeps decode-sized packed GEMMs on the one-CTA-per-SM variant,
+// ONECAT_W4_KPS=n sets the k tiles per stage of the light variant.
+int env_int(const char* name, int dflt) {
+  const char* v = getenv(name);
+  return (v && *v) ? atoi(v) : dflt;
+}
+}  // namespace
 
 // Picks the token tile, split-K factor and pipeline depths. Split-K spreads few-tile problems (decode) over all SMs.
 void gemm_plan(GemmParams& p, int num_sms, bool w4) {
+  const int use_small = env_int("ONECAT_W4_SMALL", 1);
   int T = p.T;
   int tn = T <= 32 ? 32 : T <= 64 ? 64 : T <= 128 ? 128 : (w4 ? 192 : 256);  // 4-bit: TMEM also holds the weight ring
   if (T > 256 && !w4) {
@@ -561,6 +596,10 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
     if (waste128 + 64 < waste256 && T < 1024) tn = 128;
   }
   p.tn = tn;
+  // decode-sized dense problems with packed weights run the light CTA variant, two per SM (grouped work lists keep the full one:
+  // their items are token slices of many experts and the list is sized for one CTA per SM)
+  p.small = (w4 && use_small && tn <= 64 && p.work == nullptr) ? 1 : 0;
+  const int slots = p.small ? 2 * num_sms : num_sms;
   // packed weights, many token tiles and a long k loop: pair the token tiles so that every dequantised weight tile feeds two
   // accumulators. Both accumulators then belong to one work item and its epilogue no longer overlaps the next main loop, and
   // there are half as many items to balance over the SMs; measured on B200: +12 % at K = 17408 with 8192 tokens, -5..-12 % at
@@ -571,16 +610,20 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   int ktiles = p.K / BK;
   int tiles = p.num_t_tiles * p.num_n_tiles;
   int best = 1;
-  if (tiles < num_sms && p.ws != nullptr) {
+  if (tiles < slots && p.ws != nullptr) {
     double best_score = -1;
-    for (int s = 1; s <= 16; ++s) {
+    // fixed cost of an item in k-tile times: pipeline fill, the fp32 partial round trip and the last arriver's reduction. The light
+    // variant overlaps it with the other resident CTA's main loop.
+    const double fixed = p.small ? 3.0 : 6.0;
+    const int min_per = p.small ? 2 : 4;
+    for (int s = 1; s <= 32; ++s) {
       int per = (ktiles + s - 1) / s;
-      if (per < 4 || (s - 1) * per >= ktiles) continue;  // every split needs work
+      if (per < min_per || (s - 1) * per >= ktiles) continue;  // every split needs work
       if ((size_t)tiles * s * BM * tn * p.nt_sub * 4 > p.ws_bytes || tiles > p.max_counters) break;
       int items = tiles * s;
-      int waves = (items + num_sms - 1) / num_sms;
+      int waves = (items + slots - 1) / slots;
       // time ~ waves * k tiles per item (+ a fixed cost per item for the reduction traffic)
-      double cost = waves * (per + 6.0);
+      double cost = waves * (per + fixed) + (s > 1 ? 0.5 * s : 0.0);  // the last arriver reads s partials
       double score = 1.0 / cost;
       if (score > best_score * 1.02) { best_score = score; best = s; }
     }
@@ -590,24 +633,42 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   gemm_plan_stages(p, w4);
 }
 
-// Pipeline depths from the shared-memory budget (227 KB per CTA) for the chosen token tile.
+// Pipeline depths from the shared-memory budget (227 KB per CTA, half of it for the light variant) for the chosen token tile.
 void gemm_plan_stages(GemmParams& p, bool w4) {
-  const int budget = 222 * 1024;
+  const int env_kps = env_int("ONECAT_W4_KPS", 0);
   const int tn = p.tn;
   if (p.nt_sub < 1) p.nt_sub = 1;
+  p.kps = 1;
   if (!w4) {
+    const int budget = 222 * 1024;
     p.nt_sub = 1;
     p.pstages = 0;
+    p.small = 0;
     int s = (budget - 2048) / (tn * 128 + kWStageBytes);
     p.stages = p.xstages = s > 8 ? 8 : (s < 2 ? 2 : s);
     p.acc_stride = 256;
     return;
   }
+  const int slot = packed_slot(p.wkind > 0 ? p.wkind : 1);
+  if (p.small && tn <= 64) {
+    // 256 TMEM columns: one accumulator (64) + six dequantised k tiles (32 each) as 3 stages of 2 or 6 stages of 1
+    p.nt_sub = 1;
+    p.kps = env_kps > 0 ? env_kps : 2;
+    if (p.kps > 3) p.kps = 3;
+    p.stages = p.xstages = 6 / p.kps;
+    p.acc_stride = 64;
+    const int budget = 110 * 1024;
+    int left = budget - 2048 - p.stages * p.kps * tn * 128;
+    p.pstages = left / slot;
+    if (p.pstages > 16) p.pstages = 16;
+    return;
+  }
+  p.small = 0;
+  const int budget = 222 * 1024;
   p.stages = p.xstages = tn <= 128 ? 8 : 4;  // limited by TMEM: 2 accumulators + 32 columns per stage
   p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
   p.acc_stride = tn <= 128 ? 128 : 192;
   // shared memory: X ring (nt_sub sub-tiles per stage) + packed ring + barriers
-  const int slot = packed_slot(p.wkind > 0 ? p.wkind : 1);
   int left = budget - 2048 - p.stages * p.nt_sub * tn * 128;
   while (left < 2 * slot && p.stages > 2) {
     --p.stages;
@@ -621,6 +682,7 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   GemmParams p = p_in;
   const bool w4 = p.w4 != nullptr;
   if (p.nt_sub < 1) p.nt_sub = 1;
+  if (p.kps < 1) p.kps = 1;
   CUtensorMap tmX, tmW;
   if (make_tmap_bf16(&tmX, x, (uint64_t)p.T, (uint64_t)p.K, (uint64_t)ldx, (uint32_t)p.tn)) return -2;
   if (!w4) {
@@ -628,28 +690,40 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   } else {
     tmW = tmX;
   }
-  int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
-  int grid = total < num_sms ? total : num_sms;
   if (w4 && p.wkind == 0) p.wkind = 1;  // packed weights without a stated kind are 4-bit integer
-  if (!w4) p.wkind = 0;
+  if (!w4) { p.wkind = 0; p.small = 0; }
   if (p.wkind < 0 || p.wkind > 4) return -6;
+  if (p.small && (p.tn > 64 || p.work != nullptr)) return -7;
+  int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
+  const int slots = p.small ? 2 * num_sms : num_sms;
+  int grid = total < slots ? total : slots;
   int smem = gemm_smem_bytes(p);
-  static bool configured[5] = {false, false, false, false, false};
+  // the opt-in shared-memory limit is a per-device attribute of each kernel: remember it per (device, kernel)
+  constexpr int kMaxDev = 64;
+  static bool configured[kMaxDev][5][2] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -8;
+  const int sm = p.small ? 1 : 0;
   auto launch = [&](auto kernel, int threads) -> int {
-    if (!configured[p.wkind]) {
-      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) != cudaSuccess) return -4;
-      configured[p.wkind] = true;
+    if (!configured[dev][p.wkind][sm]) {
+      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm ? 113 * 1024 : 227 * 1024) != cudaSuccess) return -4;
+      configured[dev][p.wkind][sm] = true;
     }
     kernel<<<grid, threads, smem, stream>>>(tmX, tmW, p);
     return 0;
   };
   int rc = 0;
-  switch (p.wkind) {
-    case 0: rc = launch(gemm_wx_kernel<0>, Roles<0>::kThreads); break;
-    case 1: rc = launch(gemm_wx_kernel<1>, Roles<1>::kThreads); break;
-    case 2: rc = launch(gemm_wx_kernel<2>, Roles<2>::kThreads); break;
-    case 3: rc = launch(gemm_wx_kernel<3>, Roles<3>::kThreads); break;
-    default: rc = launch(gemm_wx_kernel<4>, Roles<4>::kThreads); break;
+  switch (p.wkind * 2 + sm) {
+    case 0: rc = launch(gemm_wx_kernel<0, 0>, Roles<0, 0>::kThreads); break;
+    case 2: rc = launch(gemm_wx_kernel<1, 0>, Roles<1, 0>::kThreads); break;
+    case 3: rc = launch(gemm_wx_kernel<1, 1>, Roles<1, 1>::kThreads); break;
+    case 4: rc = launch(gemm_wx_kernel<2, 0>, Roles<2, 0>::kThreads); break;
+    case 5: rc = launch(gemm_wx_kernel<2, 1>, Roles<2, 1>::kThreads); break;
+    case 6: rc = launch(gemm_wx_kernel<3, 0>, Roles<3, 0>::kThreads); break;
+    case 7: rc = launch(gemm_wx_kernel<3, 1>, Roles<3, 1>::kThreads); break;
+    case 8: rc = launch(gemm_wx_kernel<4, 0>, Roles<4, 0>::kThreads); break;
+    case 9: rc = launch(gemm_wx_kernel<4, 1>, Roles<4, 1>::kThreads); break;
+    default: return -6;
   }
   if (rc != 0) return rc;
   return cudaGetLastError() == cudaSuccess ? 0 : -5;

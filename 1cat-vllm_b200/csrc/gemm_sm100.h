@@ -17,6 +17,8 @@ struct GemmParams {
   int acc_stride;               // TMEM columns between the two accumulators
   int nt_sub;                   // token sub-tiles (of tn tokens) per work item: 2 = one dequantised weight tile feeds both accumulators
   int xstages, stages, pstages;  // ring depths: X tiles, W tiles (bf16 weights: same ring as X), packed 4-bit tiles
+  int kps;                      // 64-wide k tiles per ring stage (one full / empty barrier pair per stage); 0 reads as 1
+  int small;                    // packed weights, token tile <= 64: the light CTA variant, two resident per SM
   int epi;
   int group_ktiles;   // 64-wide k tiles per quantisation group (group 128 -> 2)
   __nv_bfloat16* out;

@@ -48,6 +48,11 @@ class AsyncLLM:
         if self._handler is None or self._handler.done():
             self._handler = asyncio.get_running_loop().create_task(self._output_loop())
 
+    async def _utility(self, method: str, *args):
+        """Utility replies arrive on the output socket, which only the output task reads: start it before the first call."""
+        self._ensure_handler()
+        return await self.engine_core.call_utility_async(method, *args)
+
     async def _output_loop(self) -> None:
         try:
             while True:
@@ -136,34 +141,34 @@ class AsyncLLM:
             raise EngineDeadError("engine is not running")
 
     async def reset_prefix_cache(self) -> bool:
-        return await self.engine_core.call_utility_async("reset_prefix_cache")
+        return await self._utility("reset_prefix_cache")
 
     async def sleep(self, level: int = 1) -> None:
-        await self.engine_core.call_utility_async("sleep", level)
+        await self._utility("sleep", level)
 
     async def wake_up(self) -> None:
-        await self.engine_core.call_utility_async("wake_up")
+        await self._utility("wake_up")
 
     async def pause_generation(self) -> None:
-        await self.engine_core.call_utility_async("pause_generation")
+        await self._utility("pause_generation")
 
     async def resume_generation(self) -> None:
-        await self.engine_core.call_utility_async("resume_generation")
+        await self._utility("resume_generation")
 
     async def is_paused(self) -> bool:
-        return bool(await self.engine_core.call_utility_async("is_paused"))
+        return bool(await self._utility("is_paused"))
 
     async def profile(self, start: bool) -> None:
-        await self.engine_core.call_utility_async("profile", start)
+        await self._utility("profile", start)
 
     async def add_lora(self, lora_request) -> bool:
-        return await self.engine_core.call_utility_async("add_lora", lora_request.to_dict())
+        return await self._utility("add_lora", lora_request.to_dict())
 
     async def remove_lora(self, lora_id: int) -> bool:
-        return await self.engine_core.call_utility_async("remove_lora", lora_id)
+        return await self._utility("remove_lora", lora_id)
 
     async def collective_rpc(self, method: str, args=(), kwargs=None):
-        return await self.engine_core.call_utility_async("collective_rpc", method, list(args), kwargs)
+        return await self._utility("collective_rpc", method, list(args), kwargs)
 
     def shutdown(self) -> None:
         if self._handler is not None:

@@ -48,6 +48,8 @@ environment_variables: dict[str, Callable[[], Any]] = {
     # serving
     "ONECAT_API_KEY": _s("ONECAT_API_KEY", None),
     "ONECAT_HOST_IP": _s("ONECAT_HOST_IP", "127.0.0.1"),
+    "ONECAT_SERVER_DEV_MODE": _b("ONECAT_SERVER_DEV_MODE", False),  # registers /sleep, /pause, /collective_rpc, /start_profile, ...
+    "ONECAT_ALLOW_RUNTIME_LORA_UPDATING": _b("ONECAT_ALLOW_RUNTIME_LORA_UPDATING", False),  # /v1/load_lora_adapter, /v1/unload_lora_adapter
     "ONECAT_USE_NATIVE_FRONTEND": _b("ONECAT_USE_NATIVE_FRONTEND", False),
 }
 

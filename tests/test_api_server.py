@@ -1,5 +1,6 @@
 """OpenAI-compatible server on CPU with the byte tokenizer: routes, streaming, stop strings, tool/reasoning parsers, metrics."""
 import json
+import os
 
 import pytest
 
@@ -68,9 +69,38 @@ def client():
     from onecat_vllm.entrypoints.openai.api_server import ServingState, build_app
     eng = AsyncLLM.from_engine_args(EngineArgs(hf_config=CFG, device="cpu", dtype="float32", max_model_len=256, tokenizer="byte", disable_log_stats=False))
     app = build_app(ServingState(eng, "tiny", "hermes", "qwen3", None))
+    old = {k: os.environ.get(k) for k in ("ONECAT_SERVER_DEV_MODE", "ONECAT_ALLOW_RUNTIME_LORA_UPDATING")}
+    os.environ["ONECAT_SERVER_DEV_MODE"] = os.environ["ONECAT_ALLOW_RUNTIME_LORA_UPDATING"] = "1"
     with TestClient(app) as c:
         yield c
+    for k, v in old.items():
+        os.environ.pop(k, None) if v is None else os.environ.__setitem__(k, v)
     eng.shutdown()
+
+
+@pytest.mark.timeout(300)
+def test_control_routes_are_closed_by_default_and_keyed(client, monkeypatch):
+    """State-changing routes exist only in development mode; with an API key every route except probes and metrics needs it."""
+    from onecat_vllm.entrypoints.openai.api_server import ServingState, build_app
+    from fastapi.testclient import TestClient
+    monkeypatch.delenv("ONECAT_SERVER_DEV_MODE")
+    monkeypatch.delenv("ONECAT_ALLOW_RUNTIME_LORA_UPDATING")
+    for path in ("/sleep", "/wake_up", "/pause", "/resume", "/reset_prefix_cache", "/start_profile", "/stop_profile"):
+        assert client.post(path).status_code == 404, path
+    assert client.post("/collective_rpc", json={"method": "shutdown"}).status_code == 404
+    assert client.post("/v1/load_lora_adapter", json={"lora_name": "x", "lora_path": "/nowhere"}).status_code == 404
+    monkeypatch.setenv("ONECAT_SERVER_DEV_MODE", "1")
+    assert client.post("/collective_rpc", json={"method": "shutdown"}).status_code == 400          # not on the allow-list
+    assert client.post("/collective_rpc", json={"method": "update_weights_ipc", "args": ["x"]}).status_code == 400
+    assert client.post("/collective_rpc", json={"method": "check_health"}).json()["results"] == [True]
+    keyed = build_app(ServingState(client.app.state.serving.engine, "tiny", "hermes", "qwen3", "sekret"))
+    with TestClient(keyed) as kc:
+        assert kc.get("/health").status_code == 200 and kc.get("/metrics").status_code == 200
+        for method, path in (("post", "/pause"), ("post", "/tokenize"), ("get", "/v1/models"), ("post", "/collective_rpc"), ("post", "/sleep")):
+            assert getattr(kc, method)(path).status_code == 401, path
+        assert kc.get("/v1/models", headers={"authorization": "Bearer sekret"}).status_code == 200
+        # (the engine's sockets live on the first client's event loop, so this second app is only asked for engine-free routes)
+        assert kc.get("/is_sleeping", headers={"authorization": "Bearer sekret"}).json()["is_sleeping"] is False
 
 
 @pytest.mark.timeout(300)

@@ -275,3 +275,32 @@ def test_rotary_scaling_rules_build_tables():
     base = 1e4 * ((2.0 * 64 / 32) - 1.0) ** (16 / 14)
     assert torch.allclose(dyn, ref.build_cos_sin_cache(16, 64, base), atol=1e-6)
     assert torch.equal(ref.build_cos_sin_cache(16, 64, 1e4, None, {"type": "mrope"}), plain)
+
+
+def test_cpu_tier_restore_after_partial_eviction_keeps_block_ids_unique():
+    """A prefix whose tail blocks were evicted to the CPU tier: the surviving GPU hits sit at the head of the free queue, and the
+    restore must not hand those very blocks out again."""
+    from types import SimpleNamespace
+    m = KVCacheManager(num_blocks=31, block_size=16, max_model_len=4096)
+    m.enable_cpu_offload(32)
+    hasher = make_block_hasher(16)
+    a = Request("a", list(range(1, 161)), SamplingParams(max_tokens=1), eos_token_id=0, block_hasher=hasher)
+    assert m.allocate_slots(a, 160) is not None
+    a.num_computed_tokens = 160
+    m.free(a)  # ten cached blocks, tail first in the free queue
+    # evict the prefix's last five blocks (they are the oldest free cached blocks) by taking fresh blocks
+    other = SimpleNamespace(request_id="o", num_computed_tokens=0, num_tokens=16 * 25, block_hashes=[], sampling_params=None)
+    free_before = m.block_pool.get_num_free_blocks()
+    taken = m.block_pool.get_new_blocks(free_before - 5)
+    assert len(m.offload.index) == 5
+    m.block_pool.free_blocks(taken)
+    b = Request("b", list(range(1, 162)), SamplingParams(max_tokens=1), eos_token_id=0, block_hasher=hasher)
+    hit, n = m.get_computed_blocks(b)
+    ids = [x.block_id for x in hit]
+    assert n == 160 and len(set(ids)) == 10, ids
+    assert [x.block_hash for x in hit] == b.block_hashes[:10]
+    _, swap_in = m.offload.take_ops()
+    assert sorted(g for _, g in swap_in) == sorted(ids[5:])        # only the evicted half is copied back
+    assert not set(g for _, g in swap_in) & set(ids[:5])            # and never into a surviving hit
+    assert m.allocate_slots(b, 1, n, hit) is not None
+    assert m.get_block_ids("b")[:10] == ids

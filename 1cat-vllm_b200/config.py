@@ -164,6 +164,7 @@ class ModelConfig:
     # runtime
     dtype: torch.dtype = torch.bfloat16
     max_model_len: int = 4096
+    index_topk: int = 0  # DeepSeek-V3.2 sparse attention: keys kept per query by the lightning indexer (0: dense attention)
     quant: QuantConfig = field(default_factory=QuantConfig)
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
@@ -230,6 +231,9 @@ class ModelConfig:
             inner.setdefault("quantization_config", hf.get("quantization_config"))
             hf = inner
         arch = (hf.get("architectures") or ["LlamaForCausalLM"])[0]
+        over = dict(over)
+        if arch == "DeepseekV32ForCausalLM":
+            over.setdefault("index_topk", int(hf.get("index_topk", 2048)))
         nh = hf.get("num_attention_heads", 8)
         hidden = hf.get("hidden_size", 256)
         kw: dict[str, Any] = dict(
@@ -626,6 +630,14 @@ class EngineArgs:
             elif mc.quant.method != self.quantization.replace("_marlin", ""):
                 raise ValueError(f"quantization={self.quantization} does not match the checkpoint's {mc.quant.method}")
         mc.max_model_len = self.max_model_len or min(mc.max_position_embeddings, 32768)
+        if mc.index_topk and mc.max_model_len > mc.index_topk:
+            # DeepSeek-V3.2 attends to the index_topk keys its lightning indexer selects; up to that many tokens this equals dense
+            # attention, which is what runs here. Longer contexts would silently change the model's outputs, so they are refused.
+            if self.max_model_len:
+                raise ValueError(f"{mc.architecture}: the sparse-attention indexer is not built; contexts up to index_topk={mc.index_topk} tokens are "
+                                 f"exact with dense attention, max_model_len={mc.max_model_len} is not (reference: "
+                                 "model_executor/layers/sparse_attn_indexer.py)")
+            mc.max_model_len = mc.index_topk
         spec = self.speculative_config
         if isinstance(spec, str):
             spec = json.loads(spec)

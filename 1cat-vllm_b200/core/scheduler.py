@@ -343,7 +343,7 @@ class Scheduler:
             if new_ids and len(new_ids) < len(generated):
                 # tokens after the stop point were computed but are dropped
                 r.num_computed_tokens = min(r.num_computed_tokens, r.num_tokens)
-            if mro.spec_token_ids is not None and i is not None and not stop and not r.use_structured_output:
+            if mro.spec_token_ids is not None and i is not None and not stop and r.spec_decode_ok:
                 r.spec_token_ids = list(mro.spec_token_ids[i])[: self.num_spec_tokens] if r.num_computed_tokens >= r.num_tokens - 1 else []
             lp = None
             if mro.logprobs is not None and i is not None and mro.logprobs[i] is not None and new_ids:
@@ -369,7 +369,7 @@ class Scheduler:
     def update_draft_token_ids(self, req_ids: list[str], drafts: list[list[int]]) -> None:
         for rid, d in zip(req_ids, drafts):
             r = self.requests.get(rid)
-            if r is not None and not r.is_finished() and not r.use_structured_output:
+            if r is not None and not r.is_finished() and r.spec_decode_ok:
                 r.spec_token_ids = list(d)
 
     # ------------------------------------------------------------------ introspection

@@ -430,7 +430,8 @@ template <int D, int MODE, int MB, bool KV8>
 int launch_one(const AttnParams& p, cudaStream_t st) {
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
   const int smem = ROWS * D * 2 + (KV8 ? 2 * 3 * kKeysPerTile * D + 2 * kKeysPerTile * D * 2 : 2 * 3 * kKeysPerTile * D * 2);
-  static int configured = 0;
+  static int configured_dev[kMaxDevices] = {};
+  int& configured = configured_dev[current_device_slot()];  // the limit is an attribute of (kernel, device)
   if (!configured) {
     if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = 1;

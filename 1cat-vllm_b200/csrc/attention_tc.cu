@@ -381,7 +381,8 @@ int attention_prefill_tc_launch(const AttnParams& p, long long num_blocks, cudaS
   CUtensorMap tmQ, tmKV;
   if (make_tmap(&tmQ, p.q, (uint64_t)p.T, (uint64_t)p.Hq * HD, (uint64_t)p.q_st * 2, TQ)) return -2;
   if (make_tmap(&tmKV, p.kv_cache, (uint64_t)num_blocks * 2 * p.Hkv * p.bs, HD, HD * 2, 16)) return -3;
-  static bool configured = false;
+  static bool configured_dev[kMaxDevices] = {};
+  bool& configured = configured_dev[current_device_slot()];  // the limit is an attribute of (kernel, device)
   if (!configured) {
     if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem + 1024) != cudaSuccess) return -4;
     configured = true;

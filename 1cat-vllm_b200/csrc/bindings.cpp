@@ -27,7 +27,7 @@ void check_bf16(const torch::Tensor& t, const char* name) {
 void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::Tensor> w4, c10::optional<torch::Tensor> w4_sz,
           torch::Tensor out, c10::optional<torch::Tensor> bias, torch::Tensor ws, torch::Tensor counters, int64_t N, int64_t n_rows,
           int64_t n_out, int64_t n_pad, int64_t epi, int64_t group_ktiles, int64_t force_splits, int64_t force_tn,
-          std::vector<int64_t> push_dst, int64_t push_rows, int64_t wkind) {
+          std::vector<int64_t> push_dst, int64_t push_rows, int64_t wkind, int64_t trace_ptr, int64_t push_sel, int64_t push_sel_stride) {
   check_bf16(x, "x");
   check_bf16(out, "out");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && out.dim() == 2 && out.stride(1) == 1, "x/out must be row-major 2-D");
@@ -77,6 +77,9 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
   p.n_push = (int)push_dst.size();
   p.push_rows = (int)push_rows;
   for (size_t i = 0; i < push_dst.size(); ++i) p.push_dst[i] = (__nv_bfloat16*)(uintptr_t)push_dst[i];
+  p.trace = (unsigned long long*)(uintptr_t)trace_ptr;
+  p.push_sel = (const int*)(uintptr_t)push_sel;
+  p.push_sel_stride = (long long)push_sel_stride;
   oc::gemm_plan(p, sm_count(), w4.has_value());
   if (force_tn > 0) {
     TORCH_CHECK(!w4.has_value() || force_tn <= 192, "4-bit weights support token tiles up to 192");
@@ -551,7 +554,8 @@ torch::Tensor comm_tensor(int64_t ptr, int64_t byte_offset, std::vector<int64_t>
 
 void tp_reduce_norm(std::vector<int64_t> part, std::vector<int64_t> flags, torch::Tensor seq_local, std::vector<int64_t> x_out,
                     c10::optional<torch::Tensor> residual_in, c10::optional<torch::Tensor> residual_out, c10::optional<torch::Tensor> w,
-                    int64_t T, int64_t H, int64_t rank, int64_t mode, bool gemma, int64_t phase, double eps, int64_t wait_ns, int64_t grid) {
+                    int64_t T, int64_t H, int64_t rank, int64_t mode, bool gemma, int64_t phase, double eps, int64_t wait_ns, int64_t grid,
+                    std::vector<int64_t> lam, int64_t lam_buf_stride, int64_t lam_src_stride, int64_t lam_ctr, bool lam_pushed) {
   const int tp = (int)part.size();
   TORCH_CHECK(tp >= 2 && tp <= oc::kMaxRanks && (int)flags.size() == tp && (int)x_out.size() == tp, "bad rank tables");
   const c10::cuda::CUDAGuard guard(seq_local.device());
@@ -575,13 +579,26 @@ void tp_reduce_norm(std::vector<int64_t> part, std::vector<int64_t> flags, torch
   p.phase = (int)phase;
   p.eps = (float)eps;
   p.wait_ns = (unsigned long long)wait_ns;
+  TORCH_CHECK(lam.empty() || (int)lam.size() == tp, "bad arrival-buffer table");
+  for (size_t i = 0; i < lam.size(); ++i) p.lam[i] = (__nv_bfloat16*)(uintptr_t)lam[i];
+  p.lam_buf_stride = (long long)lam_buf_stride;
+  p.lam_src_stride = (long long)lam_src_stride;
+  p.lam_ctr = (int*)(uintptr_t)lam_ctr;
+  p.lam_pushed = lam_pushed ? 1 : 0;
   int rc = oc::tp_reduce_norm_launch(p, (int)grid, cur_stream());
   TORCH_CHECK(rc == 0, "tp_reduce_norm launch failed: ", rc);
+}
+
+std::vector<int64_t> gemm_kernel_info(int64_t wkind, int64_t small, int64_t smem) {
+  int o[6] = {0};
+  TORCH_CHECK(oc::gemm_kernel_info((int)wkind, (int)small, (int)smem, o) == 0, "no such kernel variant");
+  return {o[0], o[1], o[2], o[3], o[4], o[5]};
 }
 
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("gemm_kernel_info", &gemm_kernel_info);
   m.def("gemm", &gemm);
   m.def("rms_norm", &rms_norm);
   m.def("rms_norm_gated", &rms_norm_gated);

@@ -169,12 +169,158 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
   }
 }
 
+
+// ---- one-shot reduction without flags (COMM_LAMPORT) -----------------------------------------------------------------
+// The data is its own arrival signal: a slot holds bf16 -0.0 (0x8000) until the source's value lands, and sources turn a
+// genuine -0.0 into +0.0 before sending. A reader polls each 16-byte vector until none of its eight values is the marker,
+// takes it and puts the marker back, so a buffer is clean again the moment it has been read; three buffers rotate (index kept
+// in device memory, advanced by the last CTA of each launch) so that a source that is one reduction ahead never meets a
+// buffer that is still being read. There is no handshake and no separate flag traffic: the latency of a reduction is one
+// NVLink store plus the local poll. Sums run in rank order on every rank, so all ranks obtain bit-identical results.
+// (reference: the Lamport one-shot protocol behind FlashInfer's allreduce_fusion, compilation/passes/fusion/allreduce_rms_fusion.py:199;
+//  csrc/minimax_reduce_rms_kernel.cu:235)
+__device__ __forceinline__ uint4 ld_volatile_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ bool has_marker(uint32_t w) { return (w & 0xffffu) == 0x8000u || (w >> 16) == 0x8000u; }
+__device__ __forceinline__ uint32_t strip_marker(uint32_t w) {
+  if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
+  if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+  return w;
+}
+
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256) tp_lamport_kernel(const CommParams p) {
+  __shared__ float red[9];
+  __shared__ int s_buf;
+  const int tp = p.tp, me = p.rank;
+  if (threadIdx.x == 0) s_buf = *reinterpret_cast<volatile int*>(p.lam_ctr);
+  __syncthreads();
+  const size_t boff = (size_t)s_buf * (size_t)p.lam_buf_stride;
+  const uint4 marker = make_uint4(0x80008000u, 0x80008000u, 0x80008000u, 0x80008000u);
+  bool timed_out = false;
+  for (int t = blockIdx.x; t < p.T; t += gridDim.x) {
+    uint4 mine[VEC_ITERS];
+    // ---- send this rank's row to every peer (skipped when the GEMM epilogue already stored it there)
+#pragma unroll
+    for (int i = 0; i < VEC_ITERS; ++i) {
+      const int c = (i * 256 + threadIdx.x) * 8;
+      if (c < p.H && !p.lam_pushed) {
+        uint4 a = *reinterpret_cast<const uint4*>(p.part[me] + (size_t)t * p.H + c);
+        a.x = strip_marker(a.x); a.y = strip_marker(a.y); a.z = strip_marker(a.z); a.w = strip_marker(a.w);
+        mine[i] = a;
+        const size_t off = boff + (size_t)me * (size_t)p.lam_src_stride + (size_t)t * p.H + c;
+        for (int r = 1; r < tp; ++r) *reinterpret_cast<uint4*>(p.lam[(me + r) % tp] + off) = a;
+      }
+    }
+    // ---- gather: poll, take, clean
+    float v[VEC_ITERS][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VEC_ITERS; ++i) {
+      const int c = (i * 256 + threadIdx.x) * 8;
+      if (c < p.H) {
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (int r = 0; r < tp; ++r) {
+          uint4 a;
+          if (r == me && !p.lam_pushed) {
+            a = mine[i];
+          } else {
+            __nv_bfloat16* slot = p.lam[me] + boff + (size_t)r * (size_t)p.lam_src_stride + (size_t)t * p.H + c;
+            uint64_t t0 = 0;
+            uint32_t spins = 0;
+            while (true) {
+              a = ld_volatile_v4(slot);
+              if (!(has_marker(a.x) || has_marker(a.y) || has_marker(a.z) || has_marker(a.w))) break;
+              if (timed_out) break;
+              if ((++spins & 255u) == 0) {
+                const uint64_t now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > p.wait_ns) { timed_out = true; break; }
+              }
+            }
+            *reinterpret_cast<uint4*>(slot) = marker;
+          }
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(ap[j]);
+        }
+        if (p.residual_in != nullptr) {
+          const uint4 rr = *reinterpret_cast<const uint4*>(p.residual_in + (size_t)t * p.H + c);
+          const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&rr);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(rp[j]);
+        }
+        uint4 o;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          op[j] = __float2bfloat16(acc[j]);
+          v[i][j] = __bfloat162float(op[j]);
+          ss += v[i][j] * v[i][j];
+        }
+        if (p.residual_out != nullptr) *reinterpret_cast<uint4*>(p.residual_out + (size_t)t * p.H + c) = o;
+      }
+    }
+    float inv = 1.f;
+    if (p.w != nullptr) {
+      const float tot = block_sum256(ss, red);
+      inv = rsqrtf(tot / (float)p.H + p.eps);
+    }
+#pragma unroll
+    for (int i = 0; i < VEC_ITERS; ++i) {
+      const int c = (i * 256 + threadIdx.x) * 8;
+      if (c < p.H) {
+        uint4 o;
+        __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+        if (p.w != nullptr) {
+          const uint4 ww = *reinterpret_cast<const uint4*>(p.w + c);
+          const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&ww);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float g = __bfloat162float(wp[j]);
+            op[j] = __float2bfloat16(v[i][j] * inv * (p.gemma ? 1.f + g : g));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) op[j] = __float2bfloat16(v[i][j]);
+        }
+        *reinterpret_cast<uint4*>(p.x_out[me] + (size_t)t * p.H + c) = o;
+      }
+    }
+  }
+  if (timed_out) atomicOr(&g_status, ST_PEER_TIMEOUT);
+  // the last CTA to finish moves this rank on to the next buffer (launches on one stream do not overlap)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    if (atomicAdd(p.lam_ctr + 1, 1) == (int)gridDim.x - 1) {
+      p.lam_ctr[1] = 0;
+      p.lam_ctr[0] = (s_buf + 1) % kLamportBuffers;
+    }
+  }
+}
+
 }  // namespace
 
 int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st) {
   if (p.H % 8 || p.H > 8192 || grid < 1 || grid > kMaxCommBlocks || p.tp > kMaxRanks) return -1;
   if (p.T == 0) return 0;
   const int iters = (p.H + 2047) / 2048;
+  if (p.mode == COMM_LAMPORT) {
+    if (p.lam_ctr == nullptr || p.lam_buf_stride <= 0 || (size_t)p.T * p.H > (size_t)p.lam_src_stride) return -3;
+    switch (iters) {
+      case 1: tp_lamport_kernel<1><<<grid, 256, 0, st>>>(p); break;
+      case 2: tp_lamport_kernel<2><<<grid, 256, 0, st>>>(p); break;
+      case 3: tp_lamport_kernel<3><<<grid, 256, 0, st>>>(p); break;
+      default: tp_lamport_kernel<4><<<grid, 256, 0, st>>>(p); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
   switch (iters) {
     case 1: tp_reduce_norm_kernel<1><<<grid, 256, 0, st>>>(p); break;
     case 2: tp_reduce_norm_kernel<2><<<grid, 256, 0, st>>>(p); break;

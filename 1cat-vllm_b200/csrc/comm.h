@@ -9,7 +9,8 @@ namespace oc {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxCommBlocks = 1024;
-enum { COMM_ONE_SHOT = 0, COMM_TWO_SHOT = 1 };
+enum { COMM_ONE_SHOT = 0, COMM_TWO_SHOT = 1, COMM_LAMPORT = 2 };
+constexpr int kLamportBuffers = 3;
 
 struct CommParams {
   const __nv_bfloat16* part[kMaxRanks];  // every rank's partial sums [T, H] (peer mappings; own entry is local)
@@ -22,6 +23,13 @@ struct CommParams {
   int T, H, tp, rank, mode, gemma, phase;
   float eps;
   unsigned long long wait_ns;
+  // COMM_LAMPORT (decode-sized T): every rank's arrival area [3 buffers][tp sources][lam_rows][H] bf16, pre-filled with the
+  // "not here yet" value (bf16 -0.0). A source stores its partial rows straight into slot [buffer][its rank] of every rank's
+  // area (from the GEMM epilogue, or at the start of this kernel when lam_pushed == 0); the reader polls the data itself.
+  __nv_bfloat16* lam[kMaxRanks];
+  long long lam_buf_stride, lam_src_stride;  // elements between buffers / between sources
+  int* lam_ctr;                              // this rank's device words: [0] buffer in use (0..2), [1] CTAs finished
+  int lam_pushed;
 };
 
 int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st);

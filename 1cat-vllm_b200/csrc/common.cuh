@@ -207,6 +207,14 @@ __device__ __forceinline__ float warp_max(float v) {
 }
 
 
+// Opt-in attributes such as the dynamic shared-memory limit belong to a (kernel, device) pair: launchers remember them per device.
+constexpr int kMaxDevices = 64;
+static inline int current_device_slot() {
+  int d = 0;
+  if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) d = 0;
+  return d;
+}
+
 // Host-side reader for this translation unit's status word.
 static inline unsigned int read_status_tu(bool clear) {
   unsigned int v = 0;

@@ -9,12 +9,13 @@
 //   out[t, n] = sum_k x[t, k] * w[n, k]      bf16 in, fp32 accumulate, bf16 out; all matrices row-major
 //
 // Limits and rules
-//   * The scratch array is ONECAT_NOALLOC_SCRATCH_BYTES (16 MiB + 4 KiB) of device memory per GPU that loads the library, held until
+//   * The scratch array is ONECAT_NOALLOC_SCRATCH_BYTES (16 MiB + 8 KiB) of device memory per GPU that loads the library, held until
 //     the process exits. A call needs tiles * splits * 128 * token_tile * 4 bytes of it (tiles = ceil(N/128) * ceil(T/token_tile),
 //     token_tile = 32/64/128/256 chosen from T) and at most 1024 output tiles; larger problems are rejected with
 //     ONECAT_NOALLOC_TOO_LARGE and nothing is launched.
 //   * The first call on each device looks up the array's device address (cudaGetSymbolAddress with that device current) and raises the
-//     kernel's shared-memory limit. Make that first call outside any stream capture.
+//     kernel's shared-memory limit on that device (both are remembered per device; concurrent first calls from several host threads
+//     are serialised inside). Make that first call outside any stream capture.
 //   * Every call uses the same array. The tile counters are cleared on the given stream before each launch; partial tiles are always
 //     written before they are read. Two calls whose kernels may overlap on the GPU (for example on different streams) race on the
 //     scratch: serialise them.
@@ -24,7 +25,7 @@
 #pragma once
 #include <cuda_runtime.h>
 
-#define ONECAT_NOALLOC_SCRATCH_BYTES ((16u << 20) + 4096u)
+#define ONECAT_NOALLOC_SCRATCH_BYTES ((16u << 20) + 8192u)
 #define ONECAT_NOALLOC_BAD_ARGUMENT (-1)
 #define ONECAT_NOALLOC_TOO_LARGE (-2)
 #define ONECAT_NOALLOC_SETUP_FAILED (-3)

@@ -22,12 +22,28 @@
 // (reference: csrc/sm70_turbomind/ops/awq_sm70_gemm.cu:3161,3278; gemm_universal.h:238) and cuBLAS for dense layers.
 #include <stdlib.h>
 
+#include <mutex>
+
 #include "common.cuh"
 #include "gemm_sm100.h"
 
 namespace oc {
 
 namespace {
+
+#ifdef ONECAT_GEMM_TRACE
+#define TRACE(slot) do { if (p.trace) p.trace[blockIdx.x * 16 + (slot)] = globaltimer_ns(); } while (0)
+#define TDECL(...) long long __VA_ARGS__
+#define TSTART() long long _t0 = clock64()
+#define TLAP(acc) do { long long _t1 = clock64(); (acc) += _t1 - _t0; _t0 = _t1; } while (0)
+#define TPUT(slot, v) do { if (p.trace) p.trace[blockIdx.x * 16 + (slot)] = (unsigned long long)(v); } while (0)
+#else
+#define TRACE(slot) do { } while (0)
+#define TDECL(...) do { } while (0)
+#define TSTART() do { } while (0)
+#define TLAP(acc) do { } while (0)
+#define TPUT(slot, v) do { } while (0)
+#endif
 
 // warp roles: 0 X producer, 1 MMA, then the dequantisation warps (4-bit weights: two groups of four that take alternate k tiles,
 // so one group's shared-memory and TMEM latencies hide behind the other's arithmetic), four epilogue warps, and for 4-bit
@@ -38,11 +54,17 @@ namespace {
 // the tensor pipe (4 x 32 cycles) or the memory system needs; a second resident CTA brings a second issuing thread and a second
 // barrier chain. Such a CTA has one group of four dequantisation warps, one accumulator and half of the SM's TMEM columns.
 template <int WKIND, int SMALL> struct Roles {
+  // SMALL: one dequantisation group. Measured on B200 with two groups per light CTA (the first one also draining the accumulator
+  // in place of the epilogue warps) the packed bf16 arithmetic of the SM was already saturated by four such warps per scheduler and
+  // every warp simply ran half as fast: 78 against 56 microseconds on the gate|up decode shape.
   static constexpr int kDqGroups = SMALL ? 1 : 2;
+  static constexpr bool kDqDrains = false;            // true: no epilogue warps, the first dequantisation group drains the accumulator
   static constexpr int kDqWarps = WKIND >= 1 ? 4 * kDqGroups : 0;
+  static constexpr int kEpiWarps = kDqDrains ? 0 : 4;
   static constexpr int kEpi0 = 2 + kDqWarps;          // first epilogue warp (2, 6 or 10: all are 2 mod 4, the quarters line up)
-  static constexpr int kPacked = kEpi0 + 4;           // packed-tile producer (4-bit only)
-  static constexpr int kThreads = (kEpi0 + 4 + (WKIND >= 1 ? 1 : 0)) * 32;
+  static constexpr int kPacked = kEpi0 + kEpiWarps;   // packed-tile producer (4-bit only)
+  static constexpr int kThreads = (kPacked + (WKIND >= 1 ? 1 : 0)) * 32;
+  static constexpr int kEpiThread0 = kDqDrains ? 64 : kEpi0 * 32;  // first of the 128 threads that run the epilogue
   static constexpr int kCtasPerSm = SMALL ? 2 : 1;
   static constexpr int kTmemCols = SMALL ? 256 : 512;
 };
@@ -61,8 +83,10 @@ __host__ __device__ constexpr int packed_slot(int wkind) { return packed_bytes(w
 // `stages` deep and in lock step with the X ring in shared memory: 8 tiles when the two accumulators fit 256 columns (token tile
 // <= 128), else 4 (token tile 192).
 
+constexpr uint32_t kStagePitch = 320;                   // epilogue staging: 128 bf16 per token row + 64 bytes (rows land in different banks)
+constexpr uint32_t kStageBytes = 2 * 32 * kStagePitch;  // two buffers of 32 token rows
 struct SmemLayout {
-  uint32_t x_off, w_off, p_off, bar_off, total;
+  uint32_t x_off, w_off, p_off, stage_off, bar_off, total;
 };
 __host__ __device__ inline SmemLayout make_layout(int tn, int nt_sub, int xstages, int stages, int pstages, int wkind, int kps) {
   SmemLayout L;
@@ -73,6 +97,9 @@ __host__ __device__ inline SmemLayout make_layout(int tn, int nt_sub, int xstage
   o += (pstages > 0 ? 0u : (uint32_t)stages * kWStageBytes);  // 4-bit weights are dequantised into TMEM, not shared memory
   L.p_off = o;
   o += (uint32_t)pstages * packed_slot(wkind);
+  o = (o + 15u) & ~15u;
+  L.stage_off = o;
+  o += kStageBytes;
   L.bar_off = o;
   o += 1024;
   L.total = o;
@@ -104,18 +131,6 @@ __device__ __forceinline__ uint32_t dq_fp4_pair(uint32_t w, uint32_t s2) {
   uint32_t v = ((w & 0x00080008u) << 12) | ((w & 0x00070007u) << 6);
   __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&v), *reinterpret_cast<__nv_bfloat162*>(&s2));
   return *reinterpret_cast<uint32_t*>(&r);
-}
-
-// Output element store with optional tensor-parallel push (see GemmParams::push_dst).
-__device__ __forceinline__ void store_out(const GemmParams& p, int t, int n, __nv_bfloat16 v) {
-  const size_t off = (size_t)t * p.ldo + n;
-  if (p.n_push == 0) {
-    p.out[off] = v;
-  } else if (p.push_rows > 0) {
-    p.push_dst[t / p.push_rows][off] = v;
-  } else {
-    for (int d = 0; d < p.n_push; ++d) p.push_dst[d][off] = v;
-  }
 }
 
 template <int WKIND, int SMALL>
@@ -156,6 +171,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   const int tn = p.tn;
 
   if (threadIdx.x == 0) {
+    TRACE(0);
     for (int i = 0; i < S; ++i) {
       mbar_init(&full[i], WKIND >= 1 ? 5 : 1);  // the producer's expect_tx arrival (+ one per dequantisation warp of the group)
       mbar_init(&empty[i], 1);
@@ -181,6 +197,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  if (threadIdx.x == 0) TRACE(1);
 
   // Work items. Dense: (n tile, token tile, k split) enumerated arithmetically. Grouped (mixture-of-experts): a device-built list of
   // {weight row tile in the stacked expert matrix, first token row, number of valid rows, output column base}; its length is
@@ -205,6 +222,164 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     k1 = min(k0 + p.ktiles_per_split, ktiles);
   };
   const bool grouped = p.work != nullptr;
+
+
+  // ------------------------------------------------------------------ epilogue (run by the epilogue warps, or by the first
+  // dequantisation group of a SMALL CTA)
+  // The accumulator is [feature (TMEM lane)][token (column)] and the output is [token][feature], so up to 32 tokens at a time are
+  // transposed through a shared-memory staging buffer and leave as 16-byte row segments: two lanes exchange one value per token
+  // pair and store packed bf16x2 words, then the 128 epilogue threads copy the chunk out with full-sector vector stores (to the
+  // local output, or to the peers' slabs of a tensor-parallel push). Two buffers alternate, so one named barrier per chunk
+  // orders both the hand-over and the reuse.
+  const int q = warp & 3;              // TMEM lane quarter this warp may read
+  const int row = q * 32 + lane;       // weight row inside the tile
+  const int et = threadIdx.x - R::kEpiThread0;    // 0..127 in the warps that run the epilogue
+  uint32_t chunk_i = 0;
+  const bool silu = p.epi == EPI_SILU_MUL;
+  const uint32_t stg_u32 = smem_u32(smem + L.stage_off);
+  const size_t sel_off = (p.n_push > 0 && p.push_sel != nullptr) ? (size_t)(*p.push_sel) * (size_t)p.push_sel_stride : 0;
+  auto strip = [](uint32_t w) -> uint32_t {  // bf16 -0.0 marks an empty slot of an arrival buffer: send +0.0 instead
+    if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
+    if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
+    return w;
+  };
+  // emits `rows` staged token rows; staged row r is token t0 + tok0 + (r / 4) * tok_gstride + (r % 4) (a plain chunk has
+  // tok_gstride 4); a[] are this thread's feature row, one value per staged token
+  auto emit = [&](float (&a)[32], int rows, int tok0, int tok_gstride, int n_base, int t0, int t_end, float bias_v) {
+    const uint32_t buf = stg_u32 + (chunk_i & 1u) * (32 * kStagePitch);
+    if (silu) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {  // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows
+        const float other = __shfl_xor_sync(0xffffffffu, a[j], 16);
+        a[j] = a[j] / (1.f + __expf(-a[j])) * other;
+      }
+    } else if (bias_v != 0.f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] += bias_v;
+    }
+    // feature pair (f, f + 1) of staged token j goes to the even lane, of token j + 1 to the odd lane
+    const uint32_t col_b = silu ? (uint32_t)(q * 16 + (lane & 14)) * 2u : (uint32_t)(q * 32 + (lane & 30)) * 2u;
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) {
+      const float send = (lane & 1) ? a[j] : a[j + 1];
+      const float recv = __shfl_xor_sync(0xffffffffu, send, 1);
+      const float lo = (lane & 1) ? recv : a[j], hi = (lane & 1) ? a[j + 1] : recv;
+      __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+      if (!silu || lane < 16)
+        asm volatile("st.shared.b32 [%0], %1;" ::"r"(buf + (uint32_t)(j + (lane & 1)) * kStagePitch + col_b), "r"(*reinterpret_cast<uint32_t*>(&pk)) : "memory");
+    }
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const int vpr = silu ? 8 : 16;                       // 16-byte vectors per staged token row
+    const int nb = silu ? n_base / 2 : n_base, nlim = silu ? p.n_out : p.N;
+    for (int v = et; v < rows * vpr; v += 128) {
+      const int r = v / vpr, cv = v - r * vpr;
+      const int t = t0 + tok0 + (r >> 2) * tok_gstride + (r & 3), n0 = nb + cv * 8;
+      if (t >= t_end || n0 >= nlim) continue;
+      uint4 val = lds128(buf + (uint32_t)r * kStagePitch + (uint32_t)cv * 16u);
+      if (p.n_push > 0 && p.push_sel != nullptr) { val.x = strip(val.x); val.y = strip(val.y); val.z = strip(val.z); val.w = strip(val.w); }
+      const size_t off = (size_t)t * p.ldo + n0 + sel_off;
+      const int nd = p.n_push == 0 ? 1 : (p.push_rows > 0 ? 1 : p.n_push);
+      for (int d = 0; d < nd; ++d) {
+        __nv_bfloat16* dst = (p.n_push == 0 ? p.out : (p.push_rows > 0 ? p.push_dst[t / p.push_rows] : p.push_dst[d])) + off;
+        if (p.vec_ok && n0 + 8 <= nlim) {
+          *reinterpret_cast<uint4*>(dst) = val;
+        } else {
+          const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&val);
+          for (int i = 0; i < 8 && n0 + i < nlim; ++i) dst[i] = e[i];
+        }
+      }
+    }
+    ++chunk_i;
+  };
+  // drains the accumulator of work item w (the tile_i-th item of this CTA); false when a wait gave up
+  auto epilogue_item = [&](int w, uint32_t tile_i) -> bool {
+    int nt, tt, sp_, k0, k1;
+    decode(w, nt, tt, sp_, k0, k1);
+    const int acc = tile_i % NB;
+    if (!mbar_wait(&tfull[acc], (tile_i / NB) & 1, abort_flag)) return false;
+    tc_fence_after();
+    if (et == 0) TRACE(4);
+    const uint32_t taddr0 = tmem_base + acc * NT * p.acc_stride + ((uint32_t)(q * 32) << 16);
+    const int tn_eff = tn * NT;  // tokens per work item
+    // TMEM address of the 32-column chunk that starts at token column c of the work item (sub-tile c / tn)
+    auto taddr_of = [&](int c) -> uint32_t { return NT == 1 ? taddr0 + c : taddr0 + (c / tn) * p.acc_stride + (c % tn); };
+    int n_base = nt * BM, t0 = tt * tn_eff, t_end = p.T;
+    if (grouped) {
+      const int4 it = p.work[w];
+      t0 = it.y;
+      t_end = it.y + it.z;
+      n_base = it.w;
+    }
+    const int n = n_base + row;
+    const float bias_v = (!silu && p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+    if (p.splits > 1) {
+      // Split-K: every CTA of the tile writes its fp32 partial ([token / 4][row][4], so a warp's 16-byte accesses are contiguous) and
+      // bumps the tile's counter; the CTA that arrives last sums the partials in split order (bit-stable) and runs the real epilogue.
+      // Nobody waits for anybody, so the scheme needs no guarantee about which CTAs are resident together.
+      const int tile_id = nt * p.num_t_tiles + tt;
+      float* wsp = p.ws + ((size_t)tile_id * p.splits + sp_) * BM * tn_eff + row * 4;
+      for (int c = 0; c < tn_eff; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr_of(c), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          __stcg(reinterpret_cast<uint4*>(wsp + (size_t)((c + j) >> 2) * (BM * 4)), make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      __threadfence();
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (et == 0) {
+        const int old = atomicAdd(&p.counters[tile_id], 1);
+        const int last = (old == p.splits - 1);
+        if (last) p.counters[tile_id] = 0;  // ready for the next launch
+        *red_flag = last;
+      }
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (!*red_flag) return true;
+      __threadfence();
+      const float* base = p.ws + (size_t)tile_id * p.splits * BM * tn_eff + row * 4;
+      const size_t sstride = (size_t)BM * tn_eff;
+      for (int c = 0; c < tn_eff; c += 32) {
+        float a[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = 0.f;
+        // one round per split with the chunk's eight loads in flight (the order of the sums stays split 0, 1, 2, ...)
+        for (int s2 = 0; s2 < p.splits; ++s2) {
+          const float* src = base + (size_t)s2 * sstride + (size_t)(c >> 2) * (BM * 4);
+          float4 f[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) f[i] = __ldcg(reinterpret_cast<const float4*>(src + (size_t)i * (BM * 4)));
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            a[4 * i] += f[i].x; a[4 * i + 1] += f[i].y; a[4 * i + 2] += f[i].z; a[4 * i + 3] += f[i].w;
+          }
+        }
+        emit(a, 32, c, 4, n_base, t0, t_end, bias_v);
+      }
+      if (p.n_push > 0) __threadfence_system();
+      return true;
+    }
+    // ---- single-pass epilogue
+    for (int c = 0; c < tn_eff; c += 32) {
+      uint32_t v[32];
+      tmem_ld_32x32(taddr_of(c), v);
+      tmem_ld_wait();
+      float a[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) a[j] = __uint_as_float(v[j]);
+      if (c + 32 >= tn_eff) {  // the accumulator is in registers: the MMA warp may start the next tile on it
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&tempty[acc]);
+      }
+      emit(a, 32, c, 4, n_base, t0, t_end, bias_v);
+    }
+    if (p.n_push > 0) __threadfence_system();  // peers will read these rows after this rank's next kernel raises its flag
+    return true;
+  };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
@@ -257,8 +432,11 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issue (one thread; the other lanes go to the teardown barrier)
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issue
+    // The whole warp walks the loop in uniform control flow and one elected lane issues: descriptors and TMEM addresses then live in
+    // uniform registers, where a loop run by a single lane would move every operand of every tcgen05.mma across from the vector
+    // registers (measured: about 70 cycles per instruction on that path).
+    {
       const uint32_t idesc = umma_idesc_bf16(BM, tn);
       uint32_t tile_i = 0;
       Ring st;
@@ -266,56 +444,68 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       const uint32_t xs = (uint32_t)tn * 128;
       const uint32_t a_base = smem_u32(sw), b_base = smem_u32(sx);
       const uint32_t ta_base = tmem_base + (kTmemCols - S * KPS * 32);
+      TDECL(c_wfull = 0, c_issue = 0, c_wtempty = 0);
+      TSTART();
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
         const int acc = tile_i % NB;
         ok = mbar_wait(&tempty[acc], ((tile_i / NB) & 1) ^ 1, abort_flag);
+        ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        TLAP(c_wtempty);
         const uint32_t d_addr = tmem_base + acc * NT * p.acc_stride;
         uint32_t accum = 0;
         for (int kt = k0; kt < k1; kt += KPS) {
           const int kc = min(KPS, k1 - kt);
           const int s = st.idx;
           ok = mbar_wait(&full[s], st.phase, abort_flag);
+          ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
+          TLAP(c_wfull);
+          if (tile_i == 0 && kt == k0 && lane == 0) TRACE(2);
           for (int jj = 0; jj < kc; ++jj) {
             const int sk = s * KPS + jj;  // k tile slot of the ring
             const uint64_t db = umma_desc_sw128(b_base + sk * NT * xs);
             if (WKIND >= 1) {
               const uint32_t ta = ta_base + sk * 32;  // 64 k of bf16 = 32 columns per k tile
-              if (NT == 1) {  // the common case stays branch-free: this thread is the kernel's critical path
+              if (NT == 1) {
+                if (elect_one()) {
 #pragma unroll
-                for (int j = 0; j < BK / 16; ++j) {
-                  umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, accum);
-                  accum = 1;
+                  for (int j = 0; j < BK / 16; ++j) umma_bf16_ts(d_addr, ta + j * 8, db + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
                 }
               } else {
                 for (int i = 0; i < NT; ++i) {
                   const uint64_t dbi = umma_desc_sw128(b_base + (sk * NT + i) * xs);
+                  if (elect_one()) {
 #pragma unroll
-                  for (int j = 0; j < BK / 16; ++j)
-                    umma_bf16_ts(d_addr + i * p.acc_stride, ta + j * 8, dbi + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
+                    for (int j = 0; j < BK / 16; ++j)
+                      umma_bf16_ts(d_addr + i * p.acc_stride, ta + j * 8, dbi + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
+                  }
                 }
-                accum = 1;
               }
             } else {
               const uint64_t da = umma_desc_sw128(a_base + sk * kWStageBytes);
+              if (elect_one()) {
 #pragma unroll
-              for (int j = 0; j < BK / 16; ++j) {
-                // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
-                umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, accum);
-                accum = 1;
+                for (int j = 0; j < BK / 16; ++j)  // +2 in the 16-byte-unit start address = 32 bytes = 16 bf16 along k inside the swizzle atom
+                  umma_bf16(d_addr, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (accum | j) ? 1u : 0u);
               }
             }
+            accum = 1;
           }
-          umma_commit(&empty[s]);  // frees the stage (both operands) once these MMAs have read it
+          if (elect_one()) umma_commit(&empty[s]);  // frees the stage (both operands) once these MMAs have read it
+          __syncwarp();
           st.advance(S);
+          TLAP(c_issue);
         }
-        if (ok) umma_commit(&tfull[acc]);
+        if (ok && elect_one()) umma_commit(&tfull[acc]);
+        __syncwarp();
+        if (lane == 0) TRACE(3);
       }
+      if (lane == 0) { TPUT(8, c_wfull); TPUT(9, c_issue); TPUT(10, c_wtempty); }
     }
   } else if (warp < R::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
@@ -327,6 +517,9 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       bool ok = true;
       const uint32_t sp_u32 = smem_u32(sp);
       const uint32_t ta_row = tmem_base + (kTmemCols - S * KPS * 32) + ((uint32_t)((warp & 3) * 32) << 16);
+      TDECL(c_wempty = 0, c_wpfull = 0, c_math = 0, c_st = 0);
+      uint32_t dq_tile_i = 0;
+      TSTART();
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         int nt, tt, sp_, k0, k1;
         decode(w, nt, tt, sp_, k0, k1);
@@ -337,12 +530,15 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
             for (int j = 0; j < kc; ++j) pr.advance(PS);
             continue;
           }
+          TLAP(c_st);
           ok = mbar_wait(&empty[st.idx], st.phase ^ 1, abort_flag);
           if (!ok) break;
           tc_fence_after();
+          TLAP(c_wempty);
          for (int jj = 0; jj < kc; ++jj) {
           ok = mbar_wait(&pfull[pr.idx], pr.phase, abort_flag);
           if (!ok) break;
+          TLAP(c_wpfull);
           const uint32_t slot = sp_u32 + pr.idx * kPackedSlot;
           const uint32_t szv = WKIND == 4 ? 0u : lds32(slot + kPackedBytes + r * 4);
           const uint32_t s2 = (szv & 0xffffu) | (szv << 16);          // low half replicated
@@ -391,6 +587,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (lane == 0) mbar_arrive(&pempty[pr.idx]);  // the packed words are in registers (one arrival per warp, not per thread)
           tmem_st_32x32(ta_row + (st.idx * KPS + jj) * 32, o);
           pr.advance(PS);
+          TLAP(c_math);
          }
           if (!ok) break;
           tmem_st_wait();
@@ -399,136 +596,23 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
           if (lane == 0) mbar_arrive(&full[st.idx]);
           st.advance(S);
         }
+        if (R::kDqDrains && grp == 0 && ok) ok = epilogue_item(w, dq_tile_i);
+        ++dq_tile_i;
       }
+      if (warp == 2 && lane == 0) { TPUT(11, c_wempty); TPUT(12, c_wpfull); TPUT(13, c_math); TPUT(14, c_st); }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue
-    const int q = warp & 3;              // TMEM lane quarter this warp may read
-    const int row = q * 32 + lane;       // weight row inside the tile
-    const int et = threadIdx.x - R::kEpi0 * 32;    // 0..127
+  } else if (!R::kDqDrains) {
+    // ------------------------------------------------------------------ epilogue warps
     uint32_t tile_i = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) {
-      int nt, tt, sp_, k0, k1;
-      decode(w, nt, tt, sp_, k0, k1);
-      const int acc = tile_i % NB;
-      ok = mbar_wait(&tfull[acc], (tile_i / NB) & 1, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t taddr0 = tmem_base + acc * NT * p.acc_stride + ((uint32_t)(q * 32) << 16);
-      const int tn_eff = tn * NT;  // tokens per work item
-      // TMEM address of the 32-column chunk that starts at token column c of the work item (sub-tile c / tn)
-      auto taddr_of = [&](int c) -> uint32_t { return NT == 1 ? taddr0 + c : taddr0 + (c / tn) * p.acc_stride + (c % tn); };
-      int n_base = nt * BM, t0 = tt * tn_eff, t_end = p.T;
-      if (grouped) {
-        const int4 it = p.work[w];
-        t0 = it.y;
-        t_end = it.y + it.z;
-        n_base = it.w;
-      }
-      const int n = n_base + row;
-      const int tile_id = nt * p.num_t_tiles + tt;
-      if (p.splits > 1) {
-        // fp32 partial -> workspace [tile][split][row][tn]
-        float* wsp = p.ws + (((size_t)tile_id * p.splits + sp_) * BM + row) * tn_eff;
-        for (int c = 0; c < tn_eff; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr_of(c), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; j += 4)
-            *reinterpret_cast<uint4*>(wsp + c + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&tempty[acc]);
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (et == 0) {
-          int old = atomicAdd(&p.counters[tile_id], 1);
-          int last = (old == p.splits - 1);
-          if (last) p.counters[tile_id] = 0;  // ready for the next launch
-          *red_flag = last;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (!*red_flag) continue;
-        __threadfence();
-        // last arriver: sum the splits in fixed order (bit-stable) and run the real epilogue from registers
-        const float* base = p.ws + ((size_t)tile_id * p.splits * BM + row) * tn_eff;
-        for (int c = 0; c < tn_eff; c += 32) {
-          float a[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) a[j] = 0.f;
-          for (int s2 = 0; s2 < p.splits; ++s2) {
-            const float4* src = reinterpret_cast<const float4*>(base + (size_t)s2 * BM * tn_eff + c);
-#pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              float4 f = __ldcg(src + j);
-              a[4 * j] += f.x; a[4 * j + 1] += f.y; a[4 * j + 2] += f.z; a[4 * j + 3] += f.w;
-            }
-          }
-          if (p.epi == EPI_SILU_MUL) {
-            const int n_out = (n_base + q * 32) / 2 + (lane & 15);
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float other = __shfl_xor_sync(0xffffffffu, a[j], 16);
-              int t = t0 + c + j;
-              if (!(lane & 16) && t < t_end && n_out < p.n_out) {
-                float g = a[j];
-                p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(g / (1.f + __expf(-g)) * other);
-              }
-            }
-          } else {
-            float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              int t = t0 + c + j;
-              if (t < t_end && n < p.N) store_out(p, t, n, __float2bfloat16(a[j] + b));
-            }
-          }
-        }
-        if (p.n_push > 0) __threadfence_system();
-        continue;
-      }
-      // ---- single-pass epilogue
-      if (p.epi == EPI_SILU_MUL) {
-        const int n_out = (n_base + q * 32) / 2 + (lane & 15);
-        for (int c = 0; c < tn_eff; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr_of(c), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float mine = __uint_as_float(v[j]);
-            float other = __shfl_xor_sync(0xffffffffu, mine, 16);
-            int t = t0 + c + j;
-            if (!(lane & 16) && t < t_end && n_out < p.n_out)
-              p.out[(size_t)t * p.ldo + n_out] = __float2bfloat16(mine / (1.f + __expf(-mine)) * other);
-          }
-        }
-      } else {
-        float b = (p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
-        for (int c = 0; c < tn_eff; c += 32) {
-          uint32_t v[32];
-          tmem_ld_32x32(taddr_of(c), v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            int t = t0 + c + j;
-            if (t < t_end && n < p.N) store_out(p, t, n, __float2bfloat16(__uint_as_float(v[j]) + b));
-          }
-        }
-      }
-      if (p.n_push > 0) __threadfence_system();  // peers will read these rows after this rank's next kernel raises its flag
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
-    }
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) ok = epilogue_item(w, tile_i);
   }
 
   // ------------------------------------------------------------------ teardown
+  if (threadIdx.x == R::kEpiThread0) TRACE(5);
   tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) TRACE(6);
   if (*abort_flag && threadIdx.x == 0) {
     // give copies that are still in flight a bounded chance to land before the CTA's shared memory is released
     uint64_t t0 = globaltimer_ns();
@@ -538,6 +622,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
+    if (lane == 0) TRACE(7);
   }
 }
 
@@ -644,7 +729,7 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
     p.nt_sub = 1;
     p.pstages = 0;
     p.small = 0;
-    int s = (budget - 2048) / (tn * 128 + kWStageBytes);
+    int s = (budget - 2048 - (int)kStageBytes) / (tn * 128 + kWStageBytes);
     p.stages = p.xstages = s > 8 ? 8 : (s < 2 ? 2 : s);
     p.acc_stride = 256;
     return;
@@ -658,7 +743,7 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
     p.stages = p.xstages = 6 / p.kps;
     p.acc_stride = 64;
     const int budget = 110 * 1024;
-    int left = budget - 2048 - p.stages * p.kps * tn * 128;
+    int left = budget - 2048 - (int)kStageBytes - p.stages * p.kps * tn * 128;
     p.pstages = left / slot;
     if (p.pstages > 16) p.pstages = 16;
     return;
@@ -669,11 +754,11 @@ void gemm_plan_stages(GemmParams& p, bool w4) {
   p.pstages = tn <= 64 ? 12 : (tn == 128 ? 8 : 6);
   p.acc_stride = tn <= 128 ? 128 : 192;
   // shared memory: X ring (nt_sub sub-tiles per stage) + packed ring + barriers
-  int left = budget - 2048 - p.stages * p.nt_sub * tn * 128;
+  int left = budget - 2048 - (int)kStageBytes - p.stages * p.nt_sub * tn * 128;
   while (left < 2 * slot && p.stages > 2) {
     --p.stages;
     p.xstages = p.stages;
-    left = budget - 2048 - p.stages * p.nt_sub * tn * 128;
+    left = budget - 2048 - (int)kStageBytes - p.stages * p.nt_sub * tn * 128;
   }
   if (p.pstages * slot > left) p.pstages = left / slot;
 }
@@ -690,6 +775,8 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   } else {
     tmW = tmX;
   }
+  p.vec_ok = (p.ldo % 8 == 0) && (((uintptr_t)p.out & 15) == 0 || p.n_push > 0);
+  for (int d = 0; d < p.n_push; ++d) p.vec_ok = p.vec_ok && (((uintptr_t)p.push_dst[d] & 15) == 0);
   if (w4 && p.wkind == 0) p.wkind = 1;  // packed weights without a stated kind are 4-bit integer
   if (!w4) { p.wkind = 0; p.small = 0; }
   if (p.wkind < 0 || p.wkind > 4) return -6;
@@ -697,6 +784,7 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
   const int slots = p.small ? 2 * num_sms : num_sms;
   int grid = total < slots ? total : slots;
+  if (p.splits > 1 && (p.ws == nullptr || p.counters == nullptr || p.num_n_tiles * p.num_t_tiles > p.max_counters)) return -9;
   int smem = gemm_smem_bytes(p);
   // the opt-in shared-memory limit is a per-device attribute of each kernel: remember it per (device, kernel)
   constexpr int kMaxDev = 64;
@@ -704,10 +792,16 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return -8;
   const int sm = p.small ? 1 : 0;
+  static std::mutex cfg_mutex;
   auto launch = [&](auto kernel, int threads) -> int {
-    if (!configured[dev][p.wkind][sm]) {
-      if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm ? 113 * 1024 : 227 * 1024) != cudaSuccess) return -4;
-      configured[dev][p.wkind][sm] = true;
+    {
+      std::lock_guard<std::mutex> lock(cfg_mutex);
+      if (!configured[dev][p.wkind][sm]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, sm ? 113 * 1024 : 227 * 1024) != cudaSuccess) return -4;
+        // two light CTAs only fit an SM when the whole unified cache is carved out as shared memory
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+        configured[dev][p.wkind][sm] = true;
+      }
     }
     kernel<<<grid, threads, smem, stream>>>(tmX, tmW, p);
     return 0;
@@ -731,19 +825,43 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
 
 unsigned int gemm_read_status(bool clear) { return read_status_tu(clear); }
 
+// Diagnostics: what the runtime says about one kernel variant (registers, static shared and local memory per thread, and how many
+// CTAs with `smem` bytes of dynamic shared memory it would keep resident per SM).
+int gemm_kernel_info(int wkind, int small, int smem, int out[6]) {
+  auto fill = [&](auto kernel, int threads) -> int {
+    cudaFuncAttributes a;
+    if (cudaFuncGetAttributes(&a, kernel) != cudaSuccess) return -1;
+    cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, small ? 113 * 1024 : 227 * 1024);
+    cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    int occ = -1;
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, threads, smem);
+    out[0] = a.numRegs; out[1] = (int)a.sharedSizeBytes; out[2] = (int)a.localSizeBytes; out[3] = threads; out[4] = occ; out[5] = a.maxThreadsPerBlock;
+    return 0;
+  };
+  switch (wkind * 2 + (small ? 1 : 0)) {
+    case 0: return fill(gemm_wx_kernel<0, 0>, Roles<0, 0>::kThreads);
+    case 2: return fill(gemm_wx_kernel<1, 0>, Roles<1, 0>::kThreads);
+    case 3: return fill(gemm_wx_kernel<1, 1>, Roles<1, 1>::kThreads);
+    case 4: return fill(gemm_wx_kernel<2, 0>, Roles<2, 0>::kThreads);
+    case 5: return fill(gemm_wx_kernel<2, 1>, Roles<2, 1>::kThreads);
+    default: return -2;
+  }
+}
+
 }  // namespace oc
 
 // ---- allocation-free entry point (see gemm_noalloc.h) -----------------------------------------------------------------
 #include "gemm_noalloc.h"
 
 namespace {
-// Split-K scratch living in the library image: 16 MiB of fp32 partial tiles followed by 1024 tile counters.
+// Split-K scratch living in the library image: 16 MiB of fp32 partial tiles followed by 2048 tile counters (the first 1024 are used).
 // In host code this name is only a handle for the symbol; the device address comes from cudaGetSymbolAddress.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[ONECAT_NOALLOC_SCRATCH_BYTES];
 constexpr size_t kNoallocPartialBytes = 16u << 20;
 constexpr int kNoallocMaxTiles = 1024;
 constexpr int kNoallocMaxDevices = 64;
 void* g_noalloc_ptr[kNoallocMaxDevices] = {nullptr};
+std::mutex g_noalloc_mutex;
 }  // namespace
 
 extern "C" int onecat_gemm_bf16_splitk_noalloc(const void* x, const void* w, void* out, int T, int N, int K, int ldx, int ldw, int ldo,
@@ -756,10 +874,13 @@ extern "C" int onecat_gemm_bf16_splitk_noalloc(const void* x, const void* w, voi
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kNoallocMaxDevices) return ONECAT_NOALLOC_SETUP_FAILED;
   int sms = 0;
   if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return ONECAT_NOALLOC_SETUP_FAILED;
-  if (g_noalloc_ptr[dev] == nullptr) {  // first call on this device (it is the current one): resolve the array's device address
-    void* ptr = nullptr;
-    if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return ONECAT_NOALLOC_SETUP_FAILED;
-    g_noalloc_ptr[dev] = ptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {  // first call on this device (it is the current one): resolve the array's device address
+      void* ptr = nullptr;
+      if (cudaGetSymbolAddress(&ptr, g_noalloc_scratch) != cudaSuccess || ptr == nullptr) return ONECAT_NOALLOC_SETUP_FAILED;
+      g_noalloc_ptr[dev] = ptr;
+    }
   }
   unsigned char* base = static_cast<unsigned char*>(g_noalloc_ptr[dev]);
   GemmParams p{};

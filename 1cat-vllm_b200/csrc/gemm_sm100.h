@@ -29,6 +29,12 @@ struct GemmParams {
   // only to destination t / push_rows (its owner in the reduce-scatter). Destinations are [T][ldo] bf16 like `out`.
   __nv_bfloat16* push_dst[8];
   int n_push, push_rows;
+  // Flag-free reduction that follows (see comm.cu, COMM_LAMPORT): the destinations are rotating arrival buffers; `push_sel` points at
+  // the device word holding the buffer in use, `push_sel_stride` is the distance between buffers in elements, and values equal to the
+  // "not here yet" marker (bf16 -0.0) are sent as +0.0
+  const int* push_sel;
+  long long push_sel_stride;
+  int vec_ok;         // set by gemm_launch: every destination row segment is 16-byte aligned (vector stores)
   float* ws;          // split-K workspace
   size_t ws_bytes;
   int* counters;      // one per output tile, zero between launches
@@ -39,6 +45,7 @@ struct GemmParams {
   const uint8_t* w4;        // packed weight tiles [n tile][k tile][4096 B (int4, fp4) or 8192 B (fp8)]; null for bf16 weights
   const uint32_t* w4_sz;    // [group][n_pad] words: int4 bf16 scale | bf16 (128 + zero) << 16; fp8 bf16 (scale * 2^120);
                             // fp4 bf16 scales (* 2^126) of the k tile's two 32-k groups
+  unsigned long long* trace;  // debugging aid (builds with ONECAT_GEMM_TRACE only): 8 globaltimer stamps per CTA, else null
   int wkind;                // 0 bf16 weights, 1 int4 with zero points (AWQ/GPTQ), 2 fp8 e4m3 block-scaled, 3 fp4 e2m1 (MXFP4),
                             // 4 fp4 e2m1 with four scales per k tile (NVFP4; two words per row in w4_sz)
 };
@@ -48,5 +55,6 @@ void gemm_plan_stages(GemmParams& p, bool w4);
 int gemm_smem_bytes(const GemmParams& p);
 int gemm_launch(const GemmParams& p, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream);
 unsigned int gemm_read_status(bool clear);
+int gemm_kernel_info(int wkind, int small, int smem, int out[6]);
 
 }  // namespace oc

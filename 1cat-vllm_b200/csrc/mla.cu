@@ -212,7 +212,8 @@ int mla_decode_launch(const MlaParams& p, cudaStream_t st) {
   if (p.R == 0 || p.T == 0) return 0;
   if (p.kv_lora != DV || p.rope != 64 || p.bs < 16 || (p.bs & (p.bs - 1))) return -1;
   const int smem = ROWS * DK * 2 + 2 * KEYS * DK * 2;
-  static bool configured = false;
+  static bool configured_dev[kMaxDevices] = {};
+  bool& configured = configured_dev[current_device_slot()];  // the limit is an attribute of (kernel, device)
   if (!configured) {
     if (cudaFuncSetAttribute(mla_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = true;

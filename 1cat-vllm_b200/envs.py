@@ -36,6 +36,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_GEMM_BACKEND": _s("ONECAT_GEMM_BACKEND", "tcgen05"),  # "tcgen05" | "library" (debug only)
     "ONECAT_ATTN_PREFILL": _s("ONECAT_ATTN_PREFILL", "tcgen05"),  # head size 128 prefill attention: "tcgen05" | "mma"
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
+    "ONECAT_TP_ONESHOT": _s("ONECAT_TP_ONESHOT", "lamport"),  # decode-sized reductions: "lamport" (data is its own flag) | "flags"
     "ONECAT_TP_PUSH": _s("ONECAT_TP_PUSH", "auto"),  # GEMM epilogue pushes partial tiles to peers: auto | always | never
     "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),
     "ONECAT_USE_CUDA_GRAPH": _b("ONECAT_USE_CUDA_GRAPH", True),

@@ -72,10 +72,10 @@ class MLAAttention(nn.Module):
         cos, sin = cs[:, : self.rope_d // 2], cs[:, self.rope_d // 2:]
         k_pe = _rope_interleaved(kv[:, self.lora:].unsqueeze(1), cos, sin).squeeze(1)
         q_pe = _rope_interleaved(q[..., self.nope:], cos, sin)
-        bs = latent_cache.shape[1]
-        sm = md.slot_mapping.long()
-        ok = sm >= 0
-        latent_cache[sm[ok] // bs, sm[ok] % bs] = torch.cat([c, k_pe], dim=-1)[ok].to(latent_cache.dtype)
+        # insert without a data-dependent shape (no host synchronisation, so the step can be captured in a CUDA graph): tokens
+        # without a slot (-1, padding of a captured batch) are routed to slot 0 of block 0, the placeholder block nothing reads
+        sm = md.slot_mapping.long().clamp(min=0)
+        latent_cache.view(-1, latent_cache.shape[-1]).index_copy_(0, sm, torch.cat([c, k_pe], dim=-1).to(latent_cache.dtype))
         wuk, wuv = self._absorb(x.dtype)
         q_abs = torch.einsum("thn,hnl->thl", q[..., : self.nope], wuk)
         if x.is_cuda:

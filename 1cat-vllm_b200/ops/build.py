@@ -15,7 +15,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(os.path.dirname(HERE), "csrc")
 OUT = os.path.join(HERE, "_C.so")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17", "--use_fast_math",
-              "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
+              "-Xcompiler", "-fPIC", "-Xptxas", "-v"] + (["-DONECAT_GEMM_TRACE"] if os.environ.get("ONECAT_GEMM_TRACE") else [])
 # --use_fast_math only affects __expf/exp2f-style intrinsics used in softmax/SiLU epilogues; accumulation stays fp32
 
 

@@ -273,12 +273,14 @@ def _swap_to_dense(layer, w: torch.Tensor) -> None:
 
 
 # ----------------------------------------------------------------------------- GEMM
-def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0, push=None, wkind=1):
-    """``push`` = (list of destination addresses, rows per owner): tensor-parallel epilogue that stores into peers' slabs."""
+def _gemm(x, w, w4, sz, out, bias, N, n_rows, n_out, n_pad, epi, gk, force_splits=0, force_tn=0, push=None, wkind=1, trace=0):
+    """``push`` = (list of destination addresses, rows per owner[, address of the buffer-select word, buffer stride in elements]):
+    tensor-parallel epilogue that stores into peers' slabs (the last two for the flag-free arrival buffers)."""
     global _LAUNCHES
     ws = workspace(x.device)
     _C.gemm(x, w, w4, sz, out, bias, ws.splitk, ws.counters, N, n_rows, n_out, n_pad, epi, gk, force_splits, force_tn,
-            push[0] if push else [], push[1] if push else 0, wkind if w4 is not None else 0)
+            push[0] if push else [], push[1] if push else 0, wkind if w4 is not None else 0, trace,
+            push[2] if push and len(push) > 2 else 0, push[3] if push and len(push) > 2 else 0)
     _LAUNCHES += 1
     return out
 
@@ -564,10 +566,17 @@ def mla_decode(q_abs, q_pe, latent_cache, md, scale, lora):
         TORCH_STANDINS.add("mla_decode")
         return ref.mla_decode(q_abs, q_pe, latent_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, lora)
     row_tiles = -(-md.max_query_len * H // 16)
-    splits = choose_kv_splits(md.num_reqs * row_tiles, max(md.seq_lens_cpu) if md.seq_lens_cpu else md.max_seq_len, _sms(q_abs.device))
     ws_o = ws_ml = None
-    if splits > 1:
-        ws_o, ws_ml = workspace(q_abs.device).attn(splits * T * H * 512, splits * T * H * 2)
+    if getattr(md, "static_ws", False) and getattr(md, "attn_plan", None) is not None and md.attn_plan[0][0] == "mla":
+        splits = md.attn_plan[1][2]  # captured decode graph: the split count is part of the graph's key, the workspace is static
+        if splits > 1:
+            so, sm_ = workspace(q_abs.device).s_o, workspace(q_abs.device).s_ml
+            assert so.numel() >= splits * T * H * 512 and sm_.numel() >= splits * T * H * 2
+            ws_o, ws_ml = so, sm_
+    else:
+        splits = choose_kv_splits(md.num_reqs * row_tiles, max(md.seq_lens_cpu) if md.seq_lens_cpu else md.max_seq_len, _sms(q_abs.device))
+        if splits > 1:
+            ws_o, ws_ml = workspace(q_abs.device).attn(splits * T * H * 512, splits * T * H * 2)
     _LAUNCHES += 2 if splits > 1 else 1
     return _C.mla_decode(q_abs.contiguous(), q_pe.contiguous(), latent_cache, md.query_start_loc, md.seq_lens, md.block_table, scale,
                          md.max_query_len, splits, ws_o, ws_ml)

@@ -8,6 +8,9 @@ Slab layout, identical on every rank:
                                          (every rank for decode-sized batches, only the rows this rank owns for large ones)
     gather[0], gather[1] bf16 [Tmax, H]  two-shot mode: normalised rows pushed here by their owner ranks
     flags               int32 [2][2][tp][1024]   (parity, stage, source rank, CTA)
+    arrive[3][src]      bf16 [Tl, H]     decode-sized batches: rotating arrival buffers of the flag-free one-shot reduction, filled
+                                         with the "not here yet" value (bf16 -0.0); the words that say which buffer is in use live in
+                                         ordinary device memory of each rank (every rank advances its own in step)
 
 All addresses are fixed for the life of the process, so the kernels can be captured in CUDA graphs."""
 from __future__ import annotations
@@ -22,7 +25,8 @@ from onecat_vllm.logger import init_logger
 
 log = init_logger(__name__)
 _MAXB = 1024
-ONE_SHOT, TWO_SHOT = 0, 1
+ONE_SHOT, TWO_SHOT, LAMPORT = 0, 1, 2
+_LAM_BUFS = 3
 
 
 class FusedTP:
@@ -36,8 +40,15 @@ class FusedTP:
         self.off_gather = [2 * tp * buf, (2 * tp + 1) * buf]
         self.off_flags = (2 * tp + 2) * buf
         self.flag_bytes = 2 * 2 * tp * _MAXB * 4
-        self.bytes = self.off_flags + self.flag_bytes
+        # flag-free path: rows per source and buffer (the one-shot regime of tp > 2 never exceeds 512 / (tp - 1) rows)
+        self.lam_rows = min(tmax, 256)
+        self.lam_src = self.lam_rows * hidden            # elements between sources
+        self.lam_buf = tp * self.lam_src                 # elements between buffers
+        self.off_lam = -(-(self.off_flags + self.flag_bytes) // 256) * 256
+        self.bytes = self.off_lam + _LAM_BUFS * self.lam_buf * 2
         self.base = _C.comm_alloc(self.bytes)
+        _C.comm_tensor(self.base, self.off_lam, [_LAM_BUFS * self.lam_buf], 0, device.index or 0).view(torch.int16).fill_(-32768)
+        torch.cuda.synchronize(device)
         handle = _C.comm_export(self.base)
         handles = [None] * tp
         dist.all_gather_object(handles, handle, group=group)
@@ -45,6 +56,8 @@ class FusedTP:
         for r, h in enumerate(handles):
             self.peers.append(self.base if r == rank else _C.comm_import(h))
         self.seq = torch.zeros(_MAXB, dtype=torch.int32, device=device)
+        self.lam_ctr = torch.zeros(2, dtype=torch.int32, device=device)  # [buffer in use, CTAs finished]
+        self.use_lamport = envs.ONECAT_TP_ONESHOT != "flags"
         self.parity = 0
         self.wait_ns = int(envs.ONECAT_DEVICE_WAIT_LIMIT_MS) * 1_000_000
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
@@ -76,11 +89,16 @@ class FusedTP:
         return mode == "always" or (mode == "auto" and T <= 128)
 
     def push_spec(self, T: int):
-        """Destinations for a row-parallel GEMM epilogue: slot ``[parity][my rank]`` in every rank's slab. Decode-sized batches go to
-        all ranks (each reduces everything itself); large ones send each row only to the rank that owns it."""
+        """Destinations for a row-parallel GEMM epilogue: slot ``[my rank]`` in every rank's slab. Decode-sized batches go to all
+        ranks (each reduces everything itself; flag-free arrival buffers when enabled); large ones send each row only to the rank
+        that owns it."""
+        mode = self.mode_for(T)
+        if mode == LAMPORT:
+            off = self.off_lam + self.rank * self.lam_src * 2
+            return [p + off for p in self.peers], 0, self.lam_ctr.data_ptr(), self.lam_buf
         off = self.off_part[self.parity][self.rank]
         dst = [p + off for p in self.peers]
-        if self.mode_for(T) == ONE_SHOT:
+        if mode == ONE_SHOT:
             return dst, 0
         return dst, -(-T // self.tp)
 
@@ -88,7 +106,10 @@ class FusedTP:
         return self.base + self.off_part[self.parity][self.rank] == t.data_ptr()
 
     def mode_for(self, T: int) -> int:
-        return ONE_SHOT if T * (self.tp - 1) <= 512 or self.tp == 2 else TWO_SHOT
+        one = T * (self.tp - 1) <= 512 or self.tp == 2
+        if one and self.use_lamport and T <= self.lam_rows:
+            return LAMPORT
+        return ONE_SHOT if one else TWO_SHOT
 
     # ---- the fused op
     def reduce_add_norm(self, partial: torch.Tensor, residual: Optional[torch.Tensor], w: Optional[torch.Tensor], eps: float = 1e-6,
@@ -96,7 +117,28 @@ class FusedTP:
         T, H = partial.shape
         assert H == self.H and T <= self.tmax, "shape outside the symmetric slab"
         par = self.parity
-        mode = self.mode_for(T) if mode is None else mode
+        if mode is None or (mode == ONE_SHOT and self.mode_for(T) == LAMPORT):
+            mode = self.mode_for(T)
+        if w is not None and w.dtype != torch.bfloat16:
+            w = w.to(torch.bfloat16)
+        res_out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device) if residual is not None else None
+        from onecat_vllm.ops import cuda as K
+        if mode == LAMPORT:
+            x = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
+            xo = [0] * self.tp
+            xo[self.rank] = x.data_ptr()
+            part = [0] * self.tp
+            if not pushed:
+                if partial.stride(0) != H or partial.stride(1) != 1:
+                    partial = partial.contiguous()
+                part[self.rank] = partial.data_ptr()
+            lam = [p + self.off_lam for p in self.peers]
+            grid = min(T, 2 * self.num_sms, _MAXB)
+            self._C.tp_reduce_norm(part, [0] * self.tp, self.seq, xo, residual, res_out, w, T, H, self.rank, mode, gemma, 0, eps, self.wait_ns, grid,
+                                   lam, self.lam_buf, self.lam_src, self.lam_ctr.data_ptr(), bool(pushed))
+            self.launches += 1
+            K._LAUNCHES += 1
+            return x, (res_out if residual is not None else None)
         if pushed and mode == self.mode_for(T):
             # every source's partial already sits in this rank's slab: the reduction reads local memory only
             part = [self.base + self.off_part[par][src] for src in range(self.tp)]
@@ -105,7 +147,6 @@ class FusedTP:
                 self._tensor(self.rank, self.off_part[par][self.rank], T, H).copy_(partial)
             part = [p + self.off_part[par][src] for src, p in enumerate(self.peers)]  # pull each source's own slot
         flags = [p + self.off_flags for p in self.peers]
-        res_out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device) if residual is not None else None
         if mode == ONE_SHOT:
             x = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
             xo = [0] * self.tp
@@ -116,17 +157,15 @@ class FusedTP:
             xo = [p + self.off_gather[par] for p in self.peers]
             per = -(-T // self.tp)
             grid = max(1, min(per, 2 * self.num_sms, _MAXB))
-        if w is not None and w.dtype != torch.bfloat16:
-            w = w.to(torch.bfloat16)
-        self._C.tp_reduce_norm(part, flags, self.seq, xo, residual, res_out, w, T, H, self.rank, mode, gemma, par, eps, self.wait_ns, grid)
+        self._C.tp_reduce_norm(part, flags, self.seq, xo, residual, res_out, w, T, H, self.rank, mode, gemma, par, eps, self.wait_ns, grid,
+                               [], 0, 0, 0, False)
         self.parity ^= 1
         self.launches += 1
-        from onecat_vllm.ops import cuda as K
         K._LAUNCHES += 1
         return x, (res_out if residual is not None else None)
 
     def all_reduce(self, partial: torch.Tensor) -> torch.Tensor:
-        x, _ = self.reduce_add_norm(partial, None, None, mode=ONE_SHOT)
+        x, _ = self.reduce_add_norm(partial, None, None, mode=ONE_SHOT, pushed=getattr(partial, "_tp_pushed", False))
         return x
 
     def close(self) -> None:

@@ -119,6 +119,8 @@ def destroy_distributed() -> None:
             pass
     if dist.is_initialized():
         try:
+            if torch.cuda.is_available() and dist.get_backend() == "nccl":
+                torch.cuda.synchronize()
             dist.destroy_process_group()
         except Exception:
             pass

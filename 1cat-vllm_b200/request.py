@@ -173,6 +173,20 @@ class Request:
         self.events: list = []
         so = sampling_params.structured_outputs if sampling_params is not None else None
         self.use_structured_output = so is not None and so.kind() != "none"
+        # Draft tokens are verified against softmax(logits / temperature) only. A request whose sampling also filters or edits the
+        # logits (top-k / top-p / min-p, penalties, bias, allowed ids, bad words, min_tokens, a thinking budget, its own seed) is
+        # decoded without drafts, like a structured-output request, so that its tokens come from exactly the distribution the
+        # non-speculative sampler would use (reference: v1/sample/rejection_sampler.py applies the processors to all k+1 rows).
+        sp = sampling_params
+        if sp is None:
+            self.spec_decode_ok = not self.use_structured_output
+        else:
+            edits = bool(sp.logit_bias or sp.allowed_token_ids or sp.bad_words or sp.bad_words_token_ids or sp.min_tokens > 0
+                         or sp.thinking_token_budget is not None or sp.presence_penalty or sp.frequency_penalty or sp.repetition_penalty != 1.0
+                         or (sp.extra_args or {}).get("logits_processors"))
+            filters = sp.top_k > 0 or sp.top_p < 1.0 or sp.min_p > 0.0 or sp.seed is not None
+            greedy = sp.temperature < 1e-5  # arg-max is unchanged by the filters
+            self.spec_decode_ok = not self.use_structured_output and not edits and (greedy or not filters)
         self.first_scheduled_time: Optional[float] = None
         if block_hasher is not None:
             self.block_hashes = block_hasher(self)

@@ -31,13 +31,27 @@ class DecodeGraphs:
         mc = runner.mc
         from onecat_vllm.ops import cuda as K
         layers = [l for l in runner.model.model.layers if l.kind == "full_attention"]
+        mla = [l for l in runner.model.model.layers if l.kind == "mla"]
         self.attn_layers = layers
         self.max_q = 1 + runner.num_spec
+        tmax = self.sizes[-1] * self.max_q
+        # geometry that sizes the split-KV grid and workspace: (query heads, KV heads, head size); MLA runs all heads of a request
+        # against one latent "head" of 512
+        self.geom = None
         if layers:
             a = layers[0].self_attn
-            tmax = self.sizes[-1] * self.max_q
+            self.geom = (a.Hq, a.Hkv, a.D)
             K.workspace(runner.device).attn_static(32 * tmax * a.Hq * a.D, 32 * tmax * a.Hq * 2)
-        self.eligible = all(l.kind == "full_attention" for l in runner.model.model.layers)
+        elif mla:
+            a = mla[0].self_attn
+            self.geom = ("mla", a.H, 512)
+            K.workspace(runner.device).attn_static(32 * tmax * a.H * 512, 32 * tmax * a.H * 2)
+        # every mixer's decode path runs without host synchronisation on fixed addresses (attention, latent attention, Gated-DeltaNet
+        # with its state slots; fused mixture-of-experts builds its work list on the device). What stays eager: experts that run the
+        # per-expert loop (biased / clamped activations), pipeline stages, and anything without an attention geometry.
+        kinds_ok = all(l.kind in ("full_attention", "linear_attention", "mla") for l in runner.model.model.layers)
+        moe_ok = all(getattr(getattr(l.mlp, "experts", None), "kernel_state", True) is not None for l in runner.model.model.layers if hasattr(l, "mlp"))
+        self.eligible = kinds_ok and moe_ok and self.geom is not None
         self.hits = self.misses = 0
 
     def plan(self, R: int, q: int, max_seq: int) -> Optional[tuple]:
@@ -45,9 +59,12 @@ class DecodeGraphs:
         if not self.eligible or R > self.sizes[-1] or q > self.max_q:
             return None
         rp = self.sizes[bisect.bisect_left(self.sizes, R)]
-        a = self.attn_layers[0].self_attn
         from onecat_vllm.ops.cuda import _sms, choose_kv_splits
-        want = choose_kv_splits(rp * a.Hkv, max_seq, _sms(self.r.device))
+        if self.geom[0] == "mla":
+            base = rp * (-(-q * self.geom[1] // 16))
+        else:
+            base = rp * self.geom[1]
+        want = choose_kv_splits(base, max_seq, _sms(self.r.device))
         s = 1  # bucketed to powers of two (rounding up keeps the grid sized for the live context)
         while s < want:
             s *= 2
@@ -56,14 +73,17 @@ class DecodeGraphs:
     def _metadata(self, rp: int, q: int, splits: int) -> AttentionMetadata:
         r = self.r
         T = rp * q
-        a = self.attn_layers[0].self_attn
         md = AttentionMetadata(rp, T, r._view("qsl", rp + 1), r._view("seq", rp), r.d_bt[:rp], r._view("slot", T), r._view("pos", T),
                                q, 0, r._view("sslot", rp), r._view("hinit", rp), [q] * rp, [0] * rp, is_uniform_decode=True,
                                uniform_query_len=q)
-        G = a.Hq // a.Hkv
-        short = (32 if a.D == 128 else 16) // G
-        # uniform batch: every request has q tokens; they take the decode kernel when q*G rows fit its tile
-        md.attn_plan = ((a.Hq, a.Hkv, a.D), (q if q <= short else short, 0 if q <= short else rp * (-(-q // (64 // G))), splits))
+        if self.geom[0] == "mla":
+            md.attn_plan = (("mla", self.geom[1], 512), (q, 0, splits))
+        else:
+            Hq, Hkv, D = self.geom
+            G = Hq // Hkv
+            short = (32 if D == 128 else 16) // G
+            # uniform batch: every request has q tokens; they take the decode kernel when q*G rows fit its tile
+            md.attn_plan = ((Hq, Hkv, D), (q if q <= short else short, 0 if q <= short else rp * (-(-q // (64 // G))), splits))
         md.static_ws = True
         return md
 
@@ -89,7 +109,7 @@ class DecodeGraphs:
     def capture_all(self) -> None:
         """Pre-capture the no-split graphs; split variants are captured on first use."""
         if not self.eligible:
-            log.info_once("CUDA graphs disabled for this model (non-attention mixers run eagerly)")
+            log.info_once("CUDA graphs disabled for this model (a layer's decode path needs the host)")
             return
         r = self.r
         r.np_pack[:] = 0
@@ -113,3 +133,10 @@ class DecodeGraphs:
         g.replay()
         self.r.graph_launches = getattr(self.r, "graph_launches", 0) + n
         return out[:T]
+
+    def release(self) -> None:
+        """Drop every captured graph (and with it the kernels, communicator references and pool memory it holds)."""
+        for g, _out, _n in self.graphs.values():
+            g.reset()
+        self.graphs.clear()
+        self.pool = None

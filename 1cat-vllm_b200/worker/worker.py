@@ -151,7 +151,20 @@ class Worker:
         return True
 
     def shutdown(self) -> None:
+        """Tear down in dependency order. Captured graphs hold kernels that reference the peer-memory slab and NCCL communicators,
+        so they go first (with the device idle); then the slab mappings; the process group last. Destroying the group while a
+        graph that captured its collectives is alive can block inside the communicator's own teardown."""
+        r = self.runner
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
+        if r is not None and getattr(r, "graphs", None) is not None:
+            r.graphs.release()
+            r.graphs = None
         self.runner = None
+        r = None
+        gc.collect()
+        if self.device.type == "cuda":
+            torch.cuda.synchronize(self.device)
         ps.destroy_distributed()
         gc.collect()
         if self.device.type == "cuda":

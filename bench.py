@@ -62,8 +62,55 @@ QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,c
 
 
 def reference_arm(args) -> None:
-    print(json.dumps({"impl": "reference", "unavailable": "reference does not install offline: its setup.py imports setuptools_rust "
-                      "(no Rust toolchain in the image) and its CMake build fetches CUTLASS/FlashMLA/DeepGEMM from the network"}))
+    """``--impl reference``: drive the reference's own unmodified Python tree (``baseline/_ref/vllm``, laid out by
+    ``baseline/prepare_reference.py`` beside the compiled extension modules of the vLLM wheel in the image) through its ``LLM.generate``
+    on the same model and workload, in a subprocess that never imports this repository's package. Whatever stops it (the tree is
+    missing, an import fails, a kernel is absent from the stock binaries, the run raises) is reported at run time as ``unavailable``
+    with the exception text. Under ``torch.distributed.run`` only rank 0 runs it (the reference spawns its own tensor-parallel
+    workers); the other ranks leave at once."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    label = "reference-python+stock-0.22-binaries"
+    base_cfg, desc, c0, in0, out0, _spec, dtype_desc = CONFIGS["dense27b"]
+    C, IN, OUT = args.concurrency or c0, args.input_len or in0, args.output_len or out0
+    if not os.path.isdir(os.path.join(ref_root, "vllm")) and os.path.exists(os.path.join(ref_root, "WITHDRAWN.txt")):
+        print(json.dumps({"impl": "reference", "unavailable": open(os.path.join(ref_root, "WITHDRAWN.txt")).read().strip()}))
+        return
+    if not os.path.isdir(os.path.join(ref_root, "vllm")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/vllm is missing: run python baseline/prepare_reference.py (pip install of the "
+                          "reference fails offline: setup.py imports setuptools_rust, CMake fetches CUTLASS/FlashMLA/DeepGEMM)"}))
+        return
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "LOCAL_RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "GROUP_RANK",
+                                                             "ROLE_RANK", "LOCAL_WORLD_SIZE", "ROLE_WORLD_SIZE", "TORCHELASTIC_RUN_ID",
+                                                             "TORCHELASTIC_RESTART_COUNT", "TORCHELASTIC_MAX_RESTARTS", "OMP_NUM_THREADS")}
+    env["PYTHONPATH"] = ref_root
+    env.setdefault("VLLM_WORKER_MULTIPROC_METHOD", "spawn")
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "run_reference.py"), "--gpus", str(args.gpus), "--concurrency", str(C),
+           "--input-len", str(IN), "--output-len", str(OUT), "--cfg", json.dumps(base_cfg)]
+    sampler = ClockSampler(0)
+    try:
+        r = subprocess.run(cmd, env=env, cwd=tempfile.gettempdir(), capture_output=True, text=True, timeout=1500)
+        line = next((l for l in reversed(r.stdout.strip().splitlines()) if l.startswith("{")), None)
+        res = json.loads(line) if line else {"ok": False, "error": f"no result line (exit {r.returncode}): {r.stderr.strip()[-400:]}"}
+    except subprocess.TimeoutExpired:
+        res = {"ok": False, "error": "the reference run did not finish within 1500 s"}
+    clocks = sampler.stop()
+    if not res.get("ok"):
+        print(json.dumps({"impl": "reference", "unavailable": f"{label}: {res.get('error')}", "where": res.get("where")}))
+        return
+    v = res["tokens_per_s"]
+    print(json.dumps({
+        "impl": "reference", "impl_detail": label, "metric": "output tokens/s (box, max over ranks)", "value": v, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": None, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": dtype_desc, "data": "synthetic: random token ids, dummy-loader weights of the named architecture",
+        "same_config": True,
+        "config": {"model": desc, "name": "dense27b", "global_batch": C, "seq_len": IN + OUT, "parallelism": f"tp{args.gpus}",
+                   "workload": f"{res['requests']} requests, {IN} in / {OUT} out, at most {C} running; wall clock of LLM.generate (ramp-up and tail included)",
+                   "layers": base_cfg["num_hidden_layers"], "output_tokens": res["output_tokens"], "vllm_file": res.get("vllm_file")},
+        "clocks": clocks,
+        "e2e": {"value": v, "unit": "tokens/s", "note": "LLM.generate takes host token ids and returns host token ids: the wall-clock number is end to end"},
+        "timing": "wall clock around LLM.generate with torch.cuda.synchronize on both sides (the reference exposes no per-step device timer)"}))
 
 
 class ClockSampler:
@@ -199,6 +246,7 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=0, help="debug only: a value other than 0 makes the run invalid as a headline number")
     ap.add_argument("--tp-comm", default=os.environ.get("ONECAT_TP_COMM", "fused"))
     ap.add_argument("--eager", action="store_true")
+    ap.add_argument("--no-full", action="store_true", help="skip the full-workload pass (4 x concurrency requests, ramp-up and tail) after the timed steps")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -313,6 +361,38 @@ def main() -> None:
     clocks = sampler.stop()
     launches = K.launches() + getattr(runner, "graph_launches", 0)
     status = K.check_status()
+    # ---- the whole workload the configuration names (4 x concurrency requests from an empty engine, ramp-up and tail included),
+    # through the same public add_request / step calls, by the wall clock; reported beside the steady-state figure
+    full = None
+    if not args.no_full and args.config == "dense27b":
+        timing[0] = False
+        eng.abort_request([rid for rid in list(reqs)])
+        while eng.has_unfinished_requests():
+            eng.step()
+        n_req, done_tokens, ttft_full, first_seen = 4 * C, 0, [], {}
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        tf0 = time.perf_counter()
+        base = counter[0]
+        for _ in range(n_req):
+            add(IN, OUT)
+        while eng.has_unfinished_requests():
+            for o in eng.step():
+                n_new = sum(len(c.token_ids) for c in o.outputs)
+                done_tokens += n_new
+                if n_new and o.request_id not in first_seen:
+                    first_seen[o.request_id] = time.perf_counter() - tf0
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        wall_full = time.perf_counter() - tf0
+        tw = torch.tensor([wall_full], dtype=torch.float64, device="cuda")
+        if world > 1:
+            dist.all_reduce(tw, op=dist.ReduceOp.MAX)
+        full = {"value": done_tokens / float(tw[0]), "unit": "tokens/s", "wall_s": float(tw[0]), "requests": n_req, "output_tokens": done_tokens,
+                "note": f"{n_req} requests of {IN} in / {OUT} out submitted at once to an empty engine, at most {C} running; wall clock, max over ranks"}
+        status |= K.check_status()
     t = torch.tensor([dev_ms, wall * 1e3], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -333,6 +413,7 @@ def main() -> None:
             "e2e": {"value": tokens / (wall_ms / 1e3), "unit": "tokens/s", "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
                     "ms_per_step": wall_ms / args.steps, "p50_tpot_ms": decode_ms,
                     "p50_ttft_ms": (sorted(ttfts)[len(ttfts) // 2] if ttfts else None)},
+            "e2e_full_workload": full,
             "gpu_launches": launches, "device_status": status,
             "torch_standins": sorted(K.TORCH_STANDINS),
         }
@@ -342,9 +423,7 @@ def main() -> None:
     sys.stdout.flush()
     torch.cuda.synchronize()
     if world > 1:
-        # every rank has finished its timed work and rank 0 has printed: leave without the collective teardown, which can
-        # block on communicators that were captured into CUDA graphs
-        os._exit(0)
+        dist.barrier()
     eng.shutdown()
 
 

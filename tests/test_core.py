@@ -304,3 +304,21 @@ def test_cpu_tier_restore_after_partial_eviction_keeps_block_ids_unique():
     assert not set(g for _, g in swap_in) & set(ids[:5])            # and never into a surviving hit
     assert m.allocate_slots(b, 1, n, hit) is not None
     assert m.get_block_ids("b")[:10] == ids
+
+
+def test_requests_that_edit_logits_get_no_drafts():
+    """Drafts are verified against the temperature-only distribution, so a request with allowed ids, penalties or a random top-k must
+    not receive them."""
+    from onecat_vllm.config import SpeculativeConfig
+    s = make_scheduler(spec=SpeculativeConfig(method="ngram", num_speculative_tokens=2))
+    plain = Request("p", [1, 2, 3], SamplingParams(max_tokens=8, temperature=0.0, top_k=5), eos_token_id=0)
+    masked = Request("m", [1, 2, 3], SamplingParams(max_tokens=8, temperature=0.0, allowed_token_ids=[4, 5]), eos_token_id=0)
+    topk = Request("k", [1, 2, 3], SamplingParams(max_tokens=8, temperature=1.0, top_k=1), eos_token_id=0)
+    assert plain.spec_decode_ok and not masked.spec_decode_ok and not topk.spec_decode_ok
+    for r in (plain, masked, topk):
+        s.add_request(r)
+    so = s.schedule()
+    s.update_from_output(so, ModelRunnerOutput(req_ids=list(so.num_scheduled_tokens), sampled_token_ids=[[7]] * 3, spec_token_ids=[[8, 9]] * 3))
+    assert plain.spec_token_ids == [8, 9] and masked.spec_token_ids == [] and topk.spec_token_ids == []
+    s.update_draft_token_ids(["p", "m", "k"], [[1, 1], [1, 1], [1, 1]])
+    assert plain.spec_token_ids == [1, 1] and masked.spec_token_ids == [] and topk.spec_token_ids == []

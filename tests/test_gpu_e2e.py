@@ -166,3 +166,52 @@ def test_features_on_gpu_lora_offload_structured_embeds(tmp_path):
     if res["cpu"][3] == res["cuda"][3]:
         assert abs(res["cpu"][1] - res["cuda"][1]) < 0.15, res
     assert abs(res["cuda"][0] - res["cuda"][1]) > 1e-3 or res["cuda"][2] != res["cuda"][3], "the adapter must change the GPU output"
+
+
+# Qwen3.5-style hybrid: three Gated-DeltaNet layers to one gated full-attention layer (head size 256, partial rotary)
+CFG_HYBRID = dict(architectures=["Qwen3_5ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=4, num_attention_heads=4,
+                  num_key_value_heads=2, head_dim=256, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
+                  tie_word_embeddings=False, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128,
+                  linear_conv_kernel_dim=4, full_attention_interval=4, attn_output_gate=True, partial_rotary_factor=0.25)
+# Qwen3-MoE-style: softmax top-4 of 16 experts through the device-built work list and the grouped GEMM
+CFG_QWEN_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                    num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
+                    tie_word_embeddings=False, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
+# DeepSeek-V3-style: latent attention (512 + 64 wide cache), one dense layer, then grouped sigmoid routing with a shared expert
+CFG_DSV3 = dict(architectures=["DeepseekV3ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=4, vocab_size=2048, rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=2048, tie_word_embeddings=False,
+                q_lora_rank=128, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=8, n_shared_experts=1,
+                num_experts_per_tok=2, moe_intermediate_size=256, n_group=2, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
+                first_k_dense_replace=1, scoring_func="sigmoid")
+
+
+@pytest.mark.parametrize("cfg", [CFG_HYBRID, CFG_QWEN_MOE, CFG_DSV3], ids=["hybrid-gdn", "qwen-moe", "deepseek-mla"])
+def test_hybrid_moe_mla_engines_on_gpu_match_the_fp32_cpu_engine(tmp_path, cfg):
+    """The engines whose mixers are not plain attention (Gated-DeltaNet state slots, routed experts, latent attention): decode must
+    replay CUDA graphs, no op may fall back to device-side PyTorch, and the GPU's tokens, scored teacher-forced by the fp32 CPU engine,
+    must carry the log-probabilities the GPU reported."""
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.ops import cuda as K
+    path = _make_checkpoint(tmp_path, cfg)
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, 2048, (int(n),), generator=g).tolist() for n in (7, 40, 130, 64, 290)]
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True, logprobs=0)
+    K.TORCH_STANDINS.clear()
+    gpu = LLM(model=path, device="cuda", dtype="bfloat16", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8, gpu_memory_utilization=0.3)
+    og = gpu.generate(prompts, sp)
+    runner = gpu.llm_engine.engine_core.core.executor.worker.runner
+    assert runner.graphs is not None and runner.graphs.eligible and runner.graphs.hits + runner.graphs.misses > 0, "decode must replay CUDA graphs"
+    assert K.check_status() == 0
+    assert not K.TORCH_STANDINS, f"ops fell back to device-side PyTorch: {K.TORCH_STANDINS}"
+    gpu.shutdown()
+    cpu = LLM(model=path, device="cpu", dtype="float32", max_model_len=1024, max_num_batched_tokens=256, max_num_seqs=8)
+    diffs = []
+    for p, o in zip(prompts, og):
+        toks = o.outputs[0].token_ids
+        assert len(toks) == 16
+        r = cpu.generate([{"prompt_token_ids": p + toks}], SamplingParams(temperature=0.0, max_tokens=1, prompt_logprobs=0))[0]
+        for i, t in enumerate(toks):
+            diffs.append(abs(o.outputs[0].logprobs[i][t].logprob - r.prompt_logprobs[len(p) + i][t].logprob))
+    cpu.shutdown()
+    diffs.sort()
+    assert diffs[len(diffs) // 2] < 0.2 and sum(diffs) / len(diffs) < 0.3 and diffs[-1] < 3.0, (diffs[len(diffs) // 2], sum(diffs) / len(diffs), diffs[-5:])

@@ -8,58 +8,107 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
+def _need(n):
+    if torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
 def _need2():
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs 2 GPUs")
+    _need(2)
 
 
-def _fused_worker(rank, world, port, q):
+def _fused_worker(rank, world, port, q, oneshot="lamport"):
     import torch.distributed as dist
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ONECAT_TP_ONESHOT=oneshot, NCCL_NVLS_ENABLE="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     from onecat_vllm.ops import cuda as K
     from onecat_vllm.ops import ref
-    from onecat_vllm.parallel.fused import ONE_SHOT, TWO_SHOT, FusedTP
+    from onecat_vllm.parallel.fused import LAMPORT, ONE_SHOT, TWO_SHOT, FusedTP
     dev = torch.device("cuda", rank)
     H, tmax = 5120, 1024
     f = FusedTP(world, rank, dev, tmax, H)
     ok = True
     msgs = []
-    try:
-        for it, (T, mode, gemma) in enumerate([(1, ONE_SHOT, False), (64, ONE_SHOT, True), (333, TWO_SHOT, False), (1024, TWO_SHOT, True), (5, TWO_SHOT, False),
-                                               (64, ONE_SHOT, False), (64, ONE_SHOT, False)]):
-            g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+
+    def check(it, T, mode, gemma, pushed_gemm=False):
+        nonlocal ok
+        g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+        g2 = torch.Generator(device=dev).manual_seed(7 + it)
+        res = torch.randn(T, H, device=dev, generator=g2).bfloat16()
+        w = (torch.randn(H, device=dev, generator=g2) * 0.1 + (0 if gemma else 1)).bfloat16()
+        if pushed_gemm:
+            # row-parallel GEMM whose epilogue stores its tiles into the peers' slabs: this rank holds a K-slice of the weight
+            Kd = 256
+            xa = torch.randn(T, Kd, device=dev, generator=g).bfloat16()
+            wa = (torch.randn(H, Kd, device=dev, generator=g) * 0.05).bfloat16()
+            part = (xa.float() @ wa.float().t()).bfloat16()  # what the kernel computes, up to accumulation order
+            out = f.partial_buffer(T, H, torch.bfloat16)
+            y = K.gemm_bf16(xa, wa, out=out) if not f.use_push(T) else K._gemm(xa, wa, None, None, out, None, H, H, H, 0, 0, 1, push=f.push_spec(T))
+            x, r = f.reduce_add_norm(y, res, w, 1e-6, gemma, pushed=f.use_push(T))
+            tol = 0.08
+        else:
             part = torch.randn(T, H, device=dev, generator=g).bfloat16()
-            g2 = torch.Generator(device=dev).manual_seed(7 + it)
-            res = torch.randn(T, H, device=dev, generator=g2).bfloat16()
-            w = (torch.randn(H, device=dev, generator=g2) * 0.1 + (0 if gemma else 1)).bfloat16()
+            part[0, :16] = -0.0  # the arrival marker of the flag-free path is a legal value of the data
+            part[T - 1, H - 8:] = 0.0
             buf = f.partial_buffer(T, H, torch.bfloat16)
             buf.copy_(part)
             x, r = f.reduce_add_norm(buf, res, w, 1e-6, gemma, mode=mode)
+            tol = 0.05
+        torch.cuda.synchronize()
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        tot = sum(p.float() for p in parts)  # the kernel sums bf16 partials in fp32 in rank order
+        new_res = (tot + res.float()).bfloat16()
+        xe, _ = ref.rms_norm(new_res, w, 1e-6, None, gemma)
+        eff = f.mode_for(T) if (mode is None or pushed_gemm) else (LAMPORT if (mode == ONE_SHOT and f.mode_for(T) == LAMPORT) else mode)
+        if eff == TWO_SHOT:
+            per = -(-T // world)
+            lo, hi = min(rank * per, T), min(rank * per + per, T)
+            r_ok = torch.equal(r[lo:hi], new_res[lo:hi]) if not pushed_gemm else bool(((r[lo:hi].float() - new_res[lo:hi].float()).abs() < 0.1).all())
+        else:
+            r_ok = torch.equal(r, new_res) if not pushed_gemm else bool(((r.float() - new_res.float()).abs() < 0.1).all())
+        err = (x.float() - xe.float()).abs().max().item()
+        xs = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(xs, x.contiguous())
+        same = all(torch.equal(xs[0], t) for t in xs)  # all ranks must hold bit-identical outputs
+        if not (r_ok and err < tol and same):
+            ok = False
+            msgs.append(f"it={it} T={T} mode={mode} eff={eff} pushed={pushed_gemm} r_ok={r_ok} err={err} same={same}")
+
+    try:
+        cases = [(1, ONE_SHOT, False), (64, ONE_SHOT, True), (333, TWO_SHOT, False), (1024, TWO_SHOT, True), (5, TWO_SHOT, False),
+                 (64, ONE_SHOT, False), (64, ONE_SHOT, False), (7, None, True), (200, None, False), (33, None, False), (64, None, True),
+                 (1, None, False), (256, None, False), (2, None, True)]
+        for it, (T, mode, gemma) in enumerate(cases):
+            check(it, T, mode, gemma)
+        for it, T in enumerate((1, 48, 64, 130, 300, 16, 16, 16)):  # GEMM + reduction with the tiles pushed from the epilogue
+            check(50 + it, T, None, it % 2 == 0, pushed_gemm=True)
+        # a captured reduction replayed back to back: the buffer rotation lives in device memory, so replays need no host state
+        T = 8
+        part = torch.full((T, H), float(rank + 1), device=dev).bfloat16()
+        buf = f.partial_buffer(T, H, torch.bfloat16)
+        buf.copy_(part)
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            for _ in range(3):
+                f.all_reduce(buf)
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+        dist.barrier()
+        if f.mode_for(T) == LAMPORT:  # the flag path alternates host-side slots and is not replayed here
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                y1 = f.all_reduce(buf)
+                y2 = f.all_reduce(y1)
+            for _ in range(25):
+                gr.replay()
             torch.cuda.synchronize()
-            tot = part.float().clone()
-            # the kernel sums bf16 partials in fp32 in rank order
-            parts = [torch.empty_like(part) for _ in range(world)]
-            dist.all_gather(parts, part)
-            tot = sum(p.float() for p in parts)
-            xe, re = ref.rms_norm(tot.new_zeros(T, H).bfloat16(), w, 1e-6, None, gemma)
-            new_res = (tot + res.float()).bfloat16()
-            xe, _ = ref.rms_norm(new_res, w, 1e-6, None, gemma)
-            if mode == TWO_SHOT:
-                per = -(-T // world)
-                lo, hi = min(rank * per, T), min(rank * per + per, T)
-                r_ok = torch.equal(r[lo:hi], new_res[lo:hi])
-            else:
-                r_ok = torch.equal(r, new_res)
-            err = (x.float() - xe.float()).abs().max().item()
-            # all ranks must hold bit-identical outputs
-            xs = [torch.empty_like(x) for _ in range(world)]
-            dist.all_gather(xs, x.contiguous())
-            same = all(torch.equal(xs[0], t) for t in xs)
-            if not (r_ok and err < 0.05 and same):
+            tot = float(sum(range(1, world + 1)))
+            if not (torch.equal(y1, torch.full_like(y1, tot)) and torch.equal(y2, torch.full_like(y2, tot * world))):
                 ok = False
-                msgs.append(f"T={T} mode={mode} r_ok={r_ok} err={err} same={same}")
+                msgs.append(f"graph replay mismatch {y1[0, 0].item()} {y2[0, 0].item()}")
         ar = f.all_reduce(torch.full((3, H), float(rank + 1), device=dev).bfloat16())
         torch.cuda.synchronize()
         if not torch.equal(ar, torch.full((3, H), float(sum(range(1, world + 1))), device=dev).bfloat16()):
@@ -99,9 +148,13 @@ def _spawn(fn, world, *args):
 
 
 @pytest.mark.timeout(300)
-def test_fused_reduce_norm_two_ranks():
-    _need2()
-    _spawn(_fused_worker, 2)
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("oneshot", ["lamport", "flags"])
+def test_fused_reduce_norm(world, oneshot):
+    """Reduce + residual + RMSNorm over peer memory (flag-free and flag-based one-shot, two-shot), the GEMM epilogue push, and a
+    captured reduction replayed 25 times, against a CPU-rank simulation (gather every rank's bf16 partial, sum in fp32, add, normalise)."""
+    _need(world)
+    _spawn(_fused_worker, world, oneshot)
 
 
 CFG = dict(architectures=["Qwen3ForCausalLM"], hidden_size=1024, intermediate_size=2048, num_hidden_layers=3, num_attention_heads=8,

@@ -382,3 +382,17 @@ def test_gpt_oss_mxfp4_release_format_matches_its_dequantised_checkpoint(tmp_pat
         outs.append([o.outputs[0].token_ids for o in llm.generate(_prompts(300), SamplingParams(temperature=0, max_tokens=10, ignore_eos=True))])
         llm.shutdown()
     assert outs[0] == outs[1]
+
+
+def test_deepseek_v32_is_limited_to_contexts_where_dense_attention_is_exact():
+    """The V3.2 indexer keeps index_topk keys per query; this engine runs dense attention, which is the same thing only up to that
+    many tokens: longer contexts are refused, the default context is cut to the limit."""
+    import pytest
+    from onecat_vllm.config import EngineArgs
+    cfg = dict(architectures=["DeepseekV32ForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4, vocab_size=1000, q_lora_rank=64,
+               kv_lora_rank=32, qk_nope_head_dim=16, qk_rope_head_dim=8, v_head_dim=16, n_routed_experts=4, num_experts_per_tok=2,
+               moe_intermediate_size=64, index_topk=128, max_position_embeddings=4096)
+    with pytest.raises(ValueError, match="indexer"):
+        EngineArgs(hf_config=cfg, device="cpu", max_model_len=512).create_engine_config()
+    assert EngineArgs(hf_config=cfg, device="cpu").create_engine_config().model_config.max_model_len == 128
+    assert EngineArgs(hf_config=cfg, device="cpu", max_model_len=100).create_engine_config().model_config.max_model_len == 100

@@ -33,7 +33,8 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
     from onecat_vllm.ops import cuda as K
     fn = _lib()
     g = torch.Generator(device="cuda").manual_seed(11)
-    for (T, N, Kd, splits) in [(48, 640, 1280, 4), (5, 1024, 2048, 8)]:
+    # decode-sized and prefill-sized token tiles, a ragged last weight tile (N = 200), and the one-split path
+    for (T, N, Kd, splits) in [(48, 640, 1280, 4), (5, 1024, 2048, 8), (300, 200, 1280, 1), (300, 640, 1280, 2), (130, 200, 2048, 4)]:
         x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
         w = (torch.randn(N, Kd, device="cuda", generator=g) * 0.05).bfloat16()
         expect = K.gemm_bf16(x, w, force_splits=splits)

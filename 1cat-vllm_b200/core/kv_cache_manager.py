@@ -28,7 +28,8 @@ def cdiv(a: int, b: int) -> int:
 
 class KVCacheManager:
     def __init__(self, num_blocks: int, block_size: int, max_model_len: int, enable_caching: bool = True,
-                 num_state_slots: int = 0, use_eagle: bool = False, dcp_world_size: int = 1, log_stats: bool = True) -> None:
+                 num_state_slots: int = 0, use_eagle: bool = False, dcp_world_size: int = 1, log_stats: bool = True,
+                 sliding_window: int = 0) -> None:
         self.block_size = block_size * dcp_world_size  # with decode-CP a logical block spans all ranks
         self.max_model_len = max_model_len
         self.enable_caching = enable_caching and num_state_slots == 0
@@ -41,6 +42,11 @@ class KVCacheManager:
         self.req_to_state_slot: dict[str, int] = {}
         self.needs_state = num_state_slots > 0
         self.offload = None
+        # Every layer attends to a window of `sliding_window` keys (Mistral-style models): blocks that lie wholly before the window of
+        # the next query are given back while the request runs (reference: single_type_kv_cache_manager.py:570 ``SlidingWindowManager``
+        # ``remove_skipped_blocks``). Models that mix windowed and global layers share one block table here and keep every block.
+        self.sliding_window = sliding_window
+        self.window_slack = 128  # keys kept below the window start: the attention kernels load whole key tiles and mask inside them
 
     def enable_cpu_offload(self, num_cpu_blocks: int, policy: str = "lru") -> None:
         from onecat_vllm.core.kv_offload import ARCOffloadTier, CPUOffloadTier
@@ -126,6 +132,8 @@ class KVCacheManager:
         new_computed_blocks = new_computed_blocks or []
         blocks = self.req_to_blocks.get(request.request_id, [])
         num_computed = request.num_computed_tokens + num_new_computed_tokens
+        if self.sliding_window > 0 and blocks:
+            self._free_out_of_window(blocks, num_computed)
         need_tokens = min(num_computed + num_new_tokens + num_lookahead_tokens, self.max_model_len)
         need_blocks = cdiv(need_tokens, self.block_size) - len(blocks) - len(new_computed_blocks)
         evictable_hits = sum(1 for b in new_computed_blocks if b.ref_cnt == 0 and not b.is_null)
@@ -153,6 +161,18 @@ class KVCacheManager:
             self.block_pool.cache_full_blocks(request, blocks, self.num_cached_block.get(request.request_id, 0), num_final // self.block_size)
             self.num_cached_block[request.request_id] = max(self.num_cached_block.get(request.request_id, 0), num_final // self.block_size)
         return new_blocks
+
+    def _free_out_of_window(self, blocks: list[KVCacheBlock], first_query_pos: int) -> None:
+        """Keys at positions <= first_query_pos - window are invisible to this and every later query of the request: release the
+        blocks they fill (their table entries become the placeholder block, so positions keep their indices)."""
+        n = (first_query_pos - self.sliding_window + 1 - self.window_slack) // self.block_size
+        gone = []
+        for i in range(min(max(n, 0), len(blocks))):
+            if not blocks[i].is_null:
+                gone.append(blocks[i])
+                blocks[i] = self.block_pool.null_block
+        if gone:
+            self.block_pool.free_blocks(gone)
 
     def free(self, request) -> None:
         blocks = self.req_to_blocks.pop(request.request_id, [])

@@ -114,12 +114,15 @@ class Scheduler:
         self.block_size = cc.block_size
         self.policy = sc.policy
         spec = vllm_config.speculative_config
+        mc = vllm_config.model_config
         self.num_spec_tokens = spec.num_speculative_tokens if spec.enabled else 0
         self.num_lookahead_tokens = self.num_spec_tokens if spec.method in ("mtp", "eagle") else 0
         self.kv_cache_manager = KVCacheManager(num_gpu_blocks, cc.block_size, self.max_model_len, cc.enable_prefix_caching,
                                                num_state_slots, use_eagle=spec.method in ("mtp", "eagle"),
                                                dcp_world_size=vllm_config.parallel_config.decode_context_parallel_size,
-                                               log_stats=log_stats)
+                                               log_stats=log_stats,
+                                               sliding_window=(mc.sliding_window if mc.sliding_window and len(mc.sliding_layers) == mc.num_hidden_layers
+                                                               and not spec.enabled else 0))
         if cc.kv_transfer_config:
             self.kv_cache_manager.enable_kv_connector(cc.kv_transfer_config)
         elif cc.num_cpu_blocks > 0:

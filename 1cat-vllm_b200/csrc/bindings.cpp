@@ -270,7 +270,8 @@ torch::Tensor argmax(torch::Tensor x) {
 // slice; returns o [T, Hv*V]. spec_state (optional) receives the recurrent state after every token; write_state=false leaves slots alone.
 torch::Tensor gdn_forward(torch::Tensor mixed, torch::Tensor b_in, torch::Tensor a_in, torch::Tensor conv_w, torch::Tensor A_log, torch::Tensor dt_bias,
                           torch::Tensor conv_state, torch::Tensor ssm_state, torch::Tensor qsl, torch::Tensor slots, torch::Tensor has_init,
-                          int64_t Hk, int64_t Hv, int64_t K, int64_t V, bool write_state, c10::optional<torch::Tensor> spec_state) {
+                          int64_t Hk, int64_t Hv, int64_t K, int64_t V, bool write_state, c10::optional<torch::Tensor> spec_state,
+                          c10::optional<torch::Tensor> chunk_meta, int64_t num_chunks, int64_t num_long, int64_t chunk_min_len) {
   check_bf16(mixed, "mixed");
   check_bf16(conv_w, "conv_w");
   check_bf16(conv_state, "conv_state");
@@ -315,8 +316,26 @@ torch::Tensor gdn_forward(torch::Tensor mixed, torch::Tensor b_in, torch::Tensor
     p.spec_state = spec_state->data_ptr<float>();
     p.spec_q = (int)spec_state->size(1);
   }
+  const bool chunked = chunk_meta.has_value() && num_long > 0 && num_chunks > 0 && !spec_state.has_value();
+  p.skip_min_len = chunked ? (int)chunk_min_len : 0;
   int rc = oc::gdn_recurrent_launch(p, cur_stream());
   TORCH_CHECK(rc == 0, "gdn recurrence launch failed: ", rc, " (K and V must be 128)");
+  if (chunked) {
+    // chunk_meta (int32): [chunk_req (num_chunks) | chunk_t0 (num_chunks) | long_req (num_long) | long_chunk0 (num_long)]
+    TORCH_CHECK(chunk_meta->scalar_type() == torch::kInt32 && chunk_meta->is_contiguous() && chunk_meta->numel() >= 2 * num_chunks + 2 * num_long,
+                "chunk metadata must be int32 [2 * chunks + 2 * sequences]");
+    auto ws = torch::empty({(int64_t)oc::gdn_chunk_workspace_elems((int)num_chunks, (int)Hv)}, mixed.options());
+    oc::GdnChunkParams c{};
+    c.q = p.q; c.k = p.k; c.v = p.v; c.ld_qkv = p.ld_qkv; c.a = p.a; c.b = p.b; c.ld_ba = p.ld_ba; c.A_log = p.A_log; c.dt_bias = p.dt_bias;
+    c.state = p.state; c.out = p.out; c.query_start_loc = p.query_start_loc; c.state_slots = p.state_slots; c.has_initial_state = p.has_initial_state;
+    c.Hk = p.Hk; c.Hv = p.Hv; c.K = p.K; c.V = p.V; c.write_state = 1;
+    c.ws = (__nv_bfloat16*)ws.data_ptr();
+    const int* m = chunk_meta->data_ptr<int>();
+    c.chunk_req = m; c.chunk_t0 = m + num_chunks; c.long_req = m + 2 * num_chunks; c.long_chunk0 = m + 2 * num_chunks + num_long;
+    c.num_chunks = (int)num_chunks; c.num_long = (int)num_long;
+    rc = oc::gdn_chunk_launch(c, cur_stream());
+    TORCH_CHECK(rc == 0, "gdn chunked prefill launch failed: ", rc);
+  }
   return out;
 }
 

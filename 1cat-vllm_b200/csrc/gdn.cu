@@ -96,7 +96,7 @@ __global__ void __launch_bounds__(GT) gdn_recurrent_kernel(const GdnParams p) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int lc = warp * 8 + (lane & 7), col = c0 + lc, half = lane >> 3;  // `half` = which quarter of the rows
   const int t0 = p.query_start_loc[r], t1 = p.query_start_loc[r + 1];
-  if (t1 <= t0) return;
+  if (t1 <= t0 || (p.skip_min_len > 0 && t1 - t0 >= p.skip_min_len)) return;
   const int hk = hv / (p.Hv / p.Hk);
   // sequences short enough for the recording buffer are recorded (and committed later by the host); longer ones, e.g. a
   // prefill chunk sharing the step with verification requests, update their slot directly

@@ -685,11 +685,13 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   // their items are token slices of many experts and the list is sized for one CTA per SM)
   p.small = (w4 && use_small && tn <= 64 && p.work == nullptr) ? 1 : 0;
   const int slots = p.small ? 2 * num_sms : num_sms;
-  // packed weights, many token tiles and a long k loop: pair the token tiles so that every dequantised weight tile feeds two
-  // accumulators. Both accumulators then belong to one work item and its epilogue no longer overlaps the next main loop, and
-  // there are half as many items to balance over the SMs; measured on B200: +12 % at K = 17408 with 8192 tokens, -5..-12 % at
-  // K = 5120, and slower whole-model steps when used for 200-400 token batches.
-  p.nt_sub = (w4 && p.work == nullptr && T > 2 * tn && p.K / BK >= 160) ? 2 : 1;
+  // packed weights and many token tiles: pair the token tiles so that every dequantised weight tile feeds two accumulators. With one
+  // token tile per weight tile the dequantisation warps (bound by the SM's packed-bf16 arithmetic, ~200-250 cycles per 128 x 64 tile)
+  // barely keep up with the four MMAs of a 192-token tile (384 cycles); paired, they have twice the time. Both accumulators then
+  // belong to one work item, so its epilogue no longer overlaps the next main loop. Measured on B200 (8192 / 1088 tokens):
+  // K = 5120: 943 -> 988 and 933 -> 1027 TFLOP/s; K = 17408: 1129 -> 1170 TFLOP/s.
+  const int nt_min_ktiles = env_int("ONECAT_W4_NTSUB_KTILES", 64);
+  p.nt_sub = (w4 && p.work == nullptr && T > 2 * tn && p.K / BK >= nt_min_ktiles) ? 2 : 1;
   p.num_t_tiles = (T + tn * p.nt_sub - 1) / (tn * p.nt_sub);
   p.num_n_tiles = (p.n_rows + BM - 1) / BM;
   int ktiles = p.K / BK;

@@ -158,7 +158,33 @@ struct GdnParams {
   int write_state;                 // 0: leave the slot untouched (speculative verification commits later)
   float* spec_state;               // optional [R][spec_q][Hv][K][V]: state after each token
   int spec_q;
+  int skip_min_len;                // > 0: sequences with at least this many tokens are left to the chunked kernels
 };
+
+// Chunked prefill (gdn_chunk.cu): sequences of at least `GdnParams::skip_min_len` tokens are split into 64-token chunks listed by
+// the host; the recurrent kernel skips them.
+struct GdnChunkParams {
+  const __nv_bfloat16 *q, *k, *v;
+  long long ld_qkv;
+  const __nv_bfloat16 *a, *b;
+  long long ld_ba;
+  const float *A_log, *dt_bias;
+  float* state;
+  __nv_bfloat16* out;
+  const int* query_start_loc;
+  const int* state_slots;
+  const int* has_initial_state;
+  int Hk, Hv, K, V, write_state;
+  __nv_bfloat16* ws;          // gdn_chunk_workspace_elems(num_chunks, Hv) elements
+  const int* chunk_req;       // [num_chunks] request of each chunk
+  const int* chunk_t0;        // [num_chunks] first token of each chunk
+  int num_chunks;
+  const int* long_req;        // [num_long] requests on the chunked path
+  const int* long_chunk0;     // [num_long] index of the request's first chunk
+  int num_long;
+};
+size_t gdn_chunk_workspace_elems(int num_chunks, int Hv);
+int gdn_chunk_launch(const GdnChunkParams& p, cudaStream_t st);
 
 int gdn_conv_launch(const GdnConvParams& p, cudaStream_t st);
 int gdn_conv_commit_launch(const GdnConvParams& p, cudaStream_t st);

@@ -454,21 +454,55 @@ def paged_attention(q, kv_cache, md, scale, out=None, lse=None, window=0, softca
 
 
 # ----------------------------------------------------------------------------- ops still served by device-side PyTorch
+GDN_CHUNK_MIN_LEN = 64  # sequences with at least this many new tokens take the chunked (tensor-core) kernels
+
+
+def _gdn_chunk_meta(md, device):
+    """Chunk list of this step for the chunked Gated-DeltaNet kernels, built once per step from the host-side query lengths:
+    int32 ``[chunk_req | chunk_t0 | long_req | long_chunk0]`` on the device (asynchronous copy from pinned memory)."""
+    cached = getattr(md, "_gdn_chunks", None)
+    if cached is not None:
+        return cached
+    qlens = getattr(md, "query_lens_cpu", None)
+    meta, nc, nl = None, 0, 0
+    if qlens and max(qlens) >= GDN_CHUNK_MIN_LEN and not getattr(md, "is_uniform_decode", False):
+        creq, ct0, lreq, lc0 = [], [], [], []
+        t = 0
+        for r, n in enumerate(qlens):
+            if n >= GDN_CHUNK_MIN_LEN:
+                lreq.append(r)
+                lc0.append(len(creq))
+                for c in range(0, n, 64):
+                    creq.append(r)
+                    ct0.append(t + c)
+            t += n
+        nc, nl = len(creq), len(lreq)
+        host = torch.tensor(creq + ct0 + lreq + lc0, dtype=torch.int32).pin_memory()
+        meta = host.to(device, non_blocking=True)
+        md._gdn_chunks_host = host  # keep the pinned buffer alive until the copy has run
+    md._gdn_chunks = (meta, nc, nl)
+    return md._gdn_chunks
+
+
 def gdn_forward(mixed, b, a, conv_w, A_log, dt_bias, conv_state, ssm_state, md, Hk, Hv, K, V):
-    """Conv + gating + gated delta rule in two kernels. Under speculative verification (``md.gdn_record`` set by the
-    runner) the slots are left untouched and the state after every token is recorded for the later commit."""
+    """Conv + gating + gated delta rule. Short sequences (decode, verification) run the recurrent kernel; sequences of at least
+    ``GDN_CHUNK_MIN_LEN`` new tokens run the chunked tensor-core kernels. Under speculative verification (``md.gdn_record`` set by
+    the runner) the slots are left untouched and the state after every token is recorded for the later commit."""
     global _LAUNCHES
     _LAUNCHES += 3
     rec = getattr(md, "gdn_record", None)
     hi = md.has_initial_state if md.has_initial_state.dtype == torch.int32 else md.has_initial_state.to(torch.int32)
     if rec is None:
+        meta, nc, nl = _gdn_chunk_meta(md, mixed.device) if os.environ.get("ONECAT_GDN_PREFILL", "chunked") == "chunked" else (None, 0, 0)
+        if nl:
+            _LAUNCHES += 2
         return _C.gdn_forward(mixed, b, a, conv_w.to(torch.bfloat16), A_log, dt_bias, conv_state, ssm_state, md.query_start_loc, md.state_slots,
-                              hi, Hk, Hv, K, V, True, None)
+                              hi, Hk, Hv, K, V, True, None, meta, nc, nl, GDN_CHUNK_MIN_LEN)
     q = md.spec_q
     spec = torch.empty(md.num_reqs, q, Hv, K, V, dtype=torch.float32, device=mixed.device)
     prev = conv_state[md.state_slots.long()].clone()
     out = _C.gdn_forward(mixed, b, a, conv_w.to(torch.bfloat16), A_log, dt_bias, conv_state, ssm_state, md.query_start_loc, md.state_slots,
-                         hi, Hk, Hv, K, V, False, spec)
+                         hi, Hk, Hv, K, V, False, spec, None, 0, 0, 0)
     rec.append(dict(conv_state=conv_state, ssm_state=ssm_state, spec=spec, prev=prev, mixed=mixed, kw=conv_w.shape[1]))
     return out
 

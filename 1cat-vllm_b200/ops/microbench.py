@@ -144,7 +144,7 @@ def bench_gdn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool 
     C = 2 * Hk * Kd + Hv * Vd
     cases = [("decode", 64, 1)] if small else [("decode", 64, 1), ("decode", 8, 1), ("verify4", 8, 4), ("prefill", 4, 2048), ("prefill", 1, 8192)]
     if prefill_only:
-        cases = [("prefill", 1, 2048)]
+        cases = [("prefill", 1, 2048)] if small else [("prefill", 1, 2048), ("prefill", 1, 8192), ("prefill", 4, 2048)]
     for name, R, ql in cases:
         T = R * ql
         mixed = (torch.randn(T, C, device="cuda") * 0.5).bfloat16()
@@ -154,12 +154,19 @@ def bench_gdn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool 
         conv_state = torch.zeros(R, C, kw - 1, device="cuda", dtype=torch.bfloat16)
         ssm = torch.zeros(R, Hv, Kd, Vd, device="cuda")
         qsl = torch.arange(R + 1, device="cuda", dtype=torch.int32) * ql
-        md = AttentionMetadata(R, T, qsl, None, None, None, None, ql, 0, state_slots=torch.arange(R, device="cuda", dtype=torch.int32),
-                               has_initial_state=torch.ones(R, device="cuda", dtype=torch.int32))
-        ms = timeit(lambda: K.gdn_forward(mixed, ba[:, :Hv], ba[:, Hv:], conv_w, A_log, dtb, conv_state, ssm, md, Hk, Hv, Kd, Vd), 1 if small else iters, 1 if small else 3)
         state_bytes = 2 * R * Hv * Kd * Vd * 4
-        rows.append(dict(kernel="gdn_conv+recurrence", case=name, R=R, q_len=ql, ms=ms, state_gbs=state_bytes / ms / 1e6,
-                         frac_of_hbm=state_bytes / ms / 1e6 / pk["hbm_gbs"], tokens_per_s=T / ms * 1e3))
+        for mode in (("chunked", "recurrent") if name == "prefill" else ("recurrent",)):
+            os.environ["ONECAT_GDN_PREFILL"] = mode
+            md = AttentionMetadata(R, T, qsl, None, None, None, None, ql, 0, state_slots=torch.arange(R, device="cuda", dtype=torch.int32),
+                                   has_initial_state=torch.ones(R, device="cuda", dtype=torch.int32), query_lens_cpu=[ql] * R)
+            ms = timeit(lambda: K.gdn_forward(mixed, ba[:, :Hv], ba[:, Hv:], conv_w, A_log, dtb, conv_state, ssm, md, Hk, Hv, Kd, Vd), 1 if small else iters,
+                        1 if small else 3)
+            # chunked form: ~11.5 MFLOP per 64-token chunk and value head (K K^T, Q K^T, T W/U, and the three products against the state)
+            flops = (T / 64.0) * Hv * 11.5e6 if mode == "chunked" else 0.0
+            rows.append(dict(kernel="gdn_conv+" + ("chunked_prefill" if (mode == "chunked" and name == "prefill") else "recurrence"), case=name, R=R, q_len=ql, ms=ms,
+                             state_gbs=state_bytes / ms / 1e6, frac_of_hbm=state_bytes / ms / 1e6 / pk["hbm_gbs"], tokens_per_s=T / ms * 1e3,
+                             us_per_token=ms * 1e3 / ql, tflops=flops / ms / 1e9))
+        os.environ.pop("ONECAT_GDN_PREFILL", None)
 
 
 def bench_moe(rows: list, small: bool, iters: int, pk: dict) -> None:

@@ -131,6 +131,18 @@ class Worker:
         from onecat_vllm.utils.weight_transfer import unpack_ipc
         return self.update_weights(unpack_ipc(payload))
 
+    def init_weight_transfer(self, init_method: str, rank: int, world_size: int, backend=None) -> bool:
+        """Join the trainer's broadcast group (reference: gpu_worker.py ``init_weight_transfer_engine``)."""
+        from onecat_vllm.utils.weight_transfer import BroadcastWeightTransfer
+        self._wt = BroadcastWeightTransfer.init(init_method, rank, world_size, self.device, backend)
+        return True
+
+    def update_weights_broadcast(self, meta: dict) -> int:
+        """Receive the tensors the trainer (rank 0 of the transfer group) broadcasts and load them in place."""
+        if getattr(self, "_wt", None) is None:
+            raise ValueError("call init_weight_transfer first")
+        return self.update_weights(((n, t.clone()) for n, t in self._wt.receive(meta)))
+
     # ---- LoRA adapters (reference: gpu_worker.py ``add_lora`` / ``remove_lora`` / ``list_loras``)
     def _lora(self):
         if self.runner.lora_manager is None:

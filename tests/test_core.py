@@ -322,3 +322,26 @@ def test_requests_that_edit_logits_get_no_drafts():
     assert plain.spec_token_ids == [8, 9] and masked.spec_token_ids == [] and topk.spec_token_ids == []
     s.update_draft_token_ids(["p", "m", "k"], [[1, 1], [1, 1], [1, 1]])
     assert plain.spec_token_ids == [1, 1] and masked.spec_token_ids == [] and topk.spec_token_ids == []
+
+
+def test_sliding_window_blocks_are_released_while_the_request_runs():
+    """All-sliding models: blocks wholly below the window (minus the slack the kernels' key tiles need) go back to the pool; their
+    table entries become the placeholder block, so positions keep their indices."""
+    m = KVCacheManager(num_blocks=200, block_size=16, max_model_len=8192, enable_caching=False, sliding_window=256)
+    r = Request("w", list(range(1, 1025)), SamplingParams(max_tokens=4), eos_token_id=0)
+    assert m.allocate_slots(r, 1024) is not None
+    r.num_computed_tokens = 1024
+    used_before = 200 - m.block_pool.get_num_free_blocks()
+    assert m.allocate_slots(r, 1) is not None            # next query sits at position 1024: keys <= 768 are out of its window
+    ids = m.get_block_ids("w")
+    n_gone = (1024 - 256 + 1 - 128) // 16
+    assert ids[:n_gone] == [0] * n_gone and all(i != 0 for i in ids[n_gone:]) and len(ids) == 65
+    assert 200 - m.block_pool.get_num_free_blocks() == used_before + 1 - n_gone
+    m.free(r)
+    assert m.block_pool.get_num_free_blocks() == 199       # everything but the placeholder block is back
+    full = KVCacheManager(num_blocks=200, block_size=16, max_model_len=8192, enable_caching=False)
+    r2 = Request("f", list(range(1, 1025)), SamplingParams(max_tokens=4), eos_token_id=0)
+    full.allocate_slots(r2, 1024)
+    r2.num_computed_tokens = 1024
+    full.allocate_slots(r2, 1)
+    assert 0 not in full.get_block_ids("f")

@@ -268,3 +268,32 @@ def test_weights_handed_over_through_ipc_handles(packed):
     after = llm.generate(prompt, sp)[0].outputs[0].token_ids
     llm.shutdown()
     assert before != want and after == want
+
+
+def test_sliding_window_block_release_does_not_change_the_tokens():
+    """An all-sliding model (Mistral-style) releases the blocks below its window while it decodes; the tokens must be those of the same
+    engine with the release switched off, and the pool must really hold fewer blocks."""
+    cfg = dict(architectures=["MistralForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=2048, sliding_window=48, rms_norm_eps=1e-6, rope_theta=1e4)
+    g = torch.Generator().manual_seed(3)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (420, 333)]
+    sp = SamplingParams(temperature=0.0, max_tokens=40, ignore_eos=True)
+    kw = dict(hf_config=cfg, device="cpu", dtype="float32", max_model_len=1024, max_num_batched_tokens=128, enable_prefix_caching=False, seed=0)
+    a = LLM(**kw)
+    mgr = a.llm_engine.engine_core.core.scheduler.kv_cache_manager
+    assert mgr.sliding_window == 48
+    low = [1.0]
+    orig = mgr.allocate_slots
+
+    def spy(*args, **kwargs):
+        out = orig(*args, **kwargs)
+        low[0] = min(low[0], mgr.usage) if mgr.req_to_blocks and all(len(b) > 20 for b in mgr.req_to_blocks.values()) else low[0]
+        return out
+    mgr.allocate_slots = spy
+    ta = [o.outputs[0].token_ids for o in a.generate(prompts, sp)]
+    a.shutdown()
+    b = LLM(**kw)
+    b.llm_engine.engine_core.core.scheduler.kv_cache_manager.sliding_window = 0
+    tb = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
+    b.shutdown()
+    assert ta == tb

@@ -173,15 +173,15 @@ CFG_HYBRID = dict(architectures=["Qwen3_5ForCausalLM"], hidden_size=512, interme
                   num_key_value_heads=2, head_dim=256, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
                   tie_word_embeddings=False, linear_num_key_heads=2, linear_num_value_heads=4, linear_key_head_dim=128, linear_value_head_dim=128,
                   linear_conv_kernel_dim=4, full_attention_interval=4, attn_output_gate=True, partial_rotary_factor=0.25)
-# Qwen3-MoE-style: softmax top-4 of 16 experts through the device-built work list and the grouped GEMM
+# Qwen3-MoE-style: softmax top-4 of 32 experts through the routing kernel, the device-built work list and the grouped GEMM
 CFG_QWEN_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
                     num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
-                    tie_word_embeddings=False, num_experts=16, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
+                    tie_word_embeddings=False, num_experts=32, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
 # DeepSeek-V3-style: latent attention (512 + 64 wide cache), one dense layer, then grouped sigmoid routing with a shared expert
 CFG_DSV3 = dict(architectures=["DeepseekV3ForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
                 num_key_value_heads=4, vocab_size=2048, rope_theta=10000.0, rms_norm_eps=1e-6, max_position_embeddings=2048, tie_word_embeddings=False,
-                q_lora_rank=128, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=8, n_shared_experts=1,
-                num_experts_per_tok=2, moe_intermediate_size=256, n_group=2, topk_group=1, routed_scaling_factor=1.5, norm_topk_prob=True,
+                q_lora_rank=128, kv_lora_rank=512, qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, n_routed_experts=32, n_shared_experts=1,
+                num_experts_per_tok=4, moe_intermediate_size=256, n_group=4, topk_group=2, routed_scaling_factor=1.5, norm_topk_prob=True,
                 first_k_dense_replace=1, scoring_func="sigmoid")
 
 

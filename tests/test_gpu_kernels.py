@@ -609,6 +609,68 @@ def test_gdn_kernels_match_sequential_oracle():
     assert K().check_status() == 0
 
 
+@pytest.mark.parametrize("qlens,init", [([200, 5, 1], [0, 0, 1]), ([64, 130, 333], [1, 0, 1]), ([1024], [0]), ([700, 1, 65], [1, 1, 0])])
+def test_gdn_chunked_prefill_matches_sequential_oracle(qlens, init):
+    """Sequences of 64 tokens or more take the chunked tensor-core kernels (whole and ragged chunks, with and without an initial
+    state), shorter ones the recurrent kernel in the same call; outputs and the state handed to the next step are checked against
+    the token-by-token recurrence in fp32, and against the recurrent kernel itself."""
+    import os
+    Hk, Hv, Kd, Vd, kw = 2, 6, 128, 128, 4
+    C = 2 * Hk * Kd + Hv * Vd
+    R = len(qlens)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    conv_w = (torch.randn(C, kw, device="cuda", generator=g) * 0.3).bfloat16()
+    A_log = torch.rand(Hv, device="cuda", generator=g) - 1.0
+    dt_bias = torch.rand(Hv, device="cuda", generator=g)
+    slots = torch.tensor([2, 0, 3][:R], dtype=torch.int32, device="cuda")
+    conv_state = (torch.randn(4, C, kw - 1, device="cuda", generator=g) * 0.5).bfloat16()
+    ssm = torch.randn(4, Hv, Kd, Vd, device="cuda", generator=g) * 0.1
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    T = sum(qlens)
+    mixed = (torch.randn(T, C, device="cuda", generator=g) * 0.5).bfloat16()
+    ba = torch.randn(T, 2 * Hv, device="cuda", generator=g).bfloat16()
+    qsl = torch.tensor([0] + list(torch.tensor(qlens).cumsum(0)), dtype=torch.int32, device="cuda")
+    hi = torch.tensor(init, dtype=torch.int32, device="cuda")
+
+    def run(mode):
+        os.environ["ONECAT_GDN_PREFILL"] = mode
+        md = AttentionMetadata(R, T, qsl, None, None, None, None, max(qlens), 0, state_slots=slots, has_initial_state=hi, query_lens_cpu=list(qlens))
+        cs, st = conv_state.clone(), ssm.clone()
+        o = K().gdn_forward(mixed, ba[:, :Hv], ba[:, Hv:], conv_w, A_log, dt_bias, cs, st, md, Hk, Hv, Kd, Vd)
+        torch.cuda.synchronize()
+        return o, cs, st
+
+    try:
+        o_c, cs_c, st_c = run("chunked")
+        o_r, cs_r, st_r = run("recurrent")
+    finally:
+        os.environ.pop("ONECAT_GDN_PREFILL", None)
+    cs_e, st_e = conv_state.cpu().clone(), ssm.cpu().clone()
+    mc = ref.causal_conv1d(mixed.cpu(), conv_w.cpu(), None, cs_e, qsl.cpu(), slots.cpu(), hi.cpu())
+    qq, kk, vv = mc[:, : Hk * Kd].reshape(T, Hk, Kd), mc[:, Hk * Kd: 2 * Hk * Kd].reshape(T, Hk, Kd), mc[:, 2 * Hk * Kd:].reshape(T, Hv, Vd)
+    gg, beta = ref.gdn_gating(ba[:, Hv:].cpu(), ba[:, :Hv].cpu(), A_log.cpu(), dt_bias.cpu())
+    oe = ref.gated_delta_rule(qq, kk, vv, gg, beta, st_e, qsl.cpu(), slots.cpu(), hi.cpu())
+    _close(o_r.view(T, Hv, Vd), oe, 3e-2, 3e-2, f"recurrent kernel {qlens}")
+    _close(o_c.view(T, Hv, Vd), oe, 4e-2, 4e-2, f"chunked kernels {qlens}")
+    _close(st_c[slots.long()], st_e[slots.long().cpu()], 4e-2, 4e-2, "state after the chunked prefill")
+    _close(cs_c, cs_e, 1e-2, 1e-2, "conv state")
+    # hand-over: one decode token per sequence on top of the chunked prefill's state must match the oracle continuing from its own
+    T2 = R
+    mixed2 = (torch.randn(T2, C, device="cuda", generator=g) * 0.5).bfloat16()
+    ba2 = torch.randn(T2, 2 * Hv, device="cuda", generator=g).bfloat16()
+    qsl2 = torch.arange(R + 1, dtype=torch.int32, device="cuda")
+    one = torch.ones(R, dtype=torch.int32, device="cuda")
+    md2 = AttentionMetadata(R, T2, qsl2, None, None, None, None, 1, 0, state_slots=slots, has_initial_state=one, query_lens_cpu=[1] * R)
+    o2 = K().gdn_forward(mixed2, ba2[:, :Hv], ba2[:, Hv:], conv_w, A_log, dt_bias, cs_c, st_c, md2, Hk, Hv, Kd, Vd)
+    torch.cuda.synchronize()
+    mc2 = ref.causal_conv1d(mixed2.cpu(), conv_w.cpu(), None, cs_e, qsl2.cpu(), slots.cpu(), one.cpu())
+    g2, b2 = ref.gdn_gating(ba2[:, Hv:].cpu(), ba2[:, :Hv].cpu(), A_log.cpu(), dt_bias.cpu())
+    oe2 = ref.gated_delta_rule(mc2[:, : Hk * Kd].reshape(T2, Hk, Kd), mc2[:, Hk * Kd: 2 * Hk * Kd].reshape(T2, Hk, Kd), mc2[:, 2 * Hk * Kd:].reshape(T2, Hv, Vd),
+                               g2, b2, st_e, qsl2.cpu(), slots.cpu(), one.cpu())
+    _close(o2.view(T2, Hv, Vd), oe2, 4e-2, 4e-2, "decode after chunked prefill")
+    assert K().check_status() == 0
+
+
 @pytest.mark.parametrize("deepseek", [False, True])
 def test_router_matches_reference(deepseek):
     T, E, k = 77, 256, 8

@@ -164,6 +164,9 @@ class ModelConfig:
     # runtime
     dtype: torch.dtype = torch.bfloat16
     max_model_len: int = 4096
+    mm_token_ids: Optional[dict] = None  # multimodal checkpoints: modality -> placeholder token id (image_token_id, video_token_id, ...)
+    vision_config: Optional[dict] = None  # the checkpoint's vision tower (Qwen2-VL layout), when it has one
+    vision_merge_size: int = 2
     index_topk: int = 0  # DeepSeek-V3.2 sparse attention: keys kept per query by the lightning indexer (0: dense attention)
     quant: QuantConfig = field(default_factory=QuantConfig)
     eos_token_id: Optional[int] = None
@@ -225,6 +228,13 @@ class ModelConfig:
     @classmethod
     def from_hf_dict(cls, hf: dict, **over) -> "ModelConfig":
         """Normalise an HF config dict. Nested ``text_config`` (Qwen3.5) is flattened."""
+        over = dict(over)
+        mm_ids = {m: int(hf[k]) for m, k in (("image", "image_token_id"), ("video", "video_token_id"), ("audio", "audio_token_id")) if hf.get(k) is not None}
+        if mm_ids:
+            over.setdefault("mm_token_ids", mm_ids)
+        if isinstance(hf.get("vision_config"), dict):
+            over.setdefault("vision_config", dict(hf["vision_config"]))
+            over.setdefault("vision_merge_size", int(hf["vision_config"].get("spatial_merge_size", 2)))
         if "text_config" in hf and isinstance(hf["text_config"], dict):
             inner = dict(hf["text_config"])
             inner.setdefault("architectures", hf.get("architectures"))
@@ -459,6 +469,8 @@ class SchedulerConfig:
     policy: str = "fcfs"  # fcfs | priority
     async_scheduling: bool = False
     cuda_graph_sizes: Optional[list[int]] = None
+    max_num_encoder_input_tokens: int = 8192  # multimodal: encoder output positions computed per step
+    encoder_cache_size: int = 16384           # multimodal: encoder output positions kept on the workers
 
     def __post_init__(self) -> None:
         if self.policy not in ("fcfs", "priority"):

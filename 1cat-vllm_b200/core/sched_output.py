@@ -20,6 +20,7 @@ class NewRequestData:
     pooling_params: Any = None
     lora_request: Any = None
     prompt_embeds: Any = None
+    mm_features: Any = None
 
 
 @dataclass
@@ -52,6 +53,8 @@ class SchedulerOutput:
     structured_rows: dict[str, int] = field(default_factory=dict)  # request id -> row of grammar_bitmask
     kv_swap_out: list = field(default_factory=list)  # (GPU block, CPU block): save before the step's forward
     kv_swap_in: list = field(default_factory=list)   # (CPU block, GPU block): restore before the step's forward
+    scheduled_encoder_inputs: dict[str, list[int]] = field(default_factory=dict)  # request id -> indices of its multimodal items to encode
+    free_encoder_mm_hashes: list = field(default_factory=list)  # encoder outputs the workers may drop
 
     @property
     def is_empty(self) -> bool:

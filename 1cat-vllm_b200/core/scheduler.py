@@ -123,6 +123,9 @@ class Scheduler:
                                                log_stats=log_stats,
                                                sliding_window=(mc.sliding_window if mc.sliding_window and len(mc.sliding_layers) == mc.num_hidden_layers
                                                                and not spec.enabled else 0))
+        from onecat_vllm.core.encoder_cache_manager import EncoderCacheManager
+        self.max_num_encoder_input_tokens = sc.max_num_encoder_input_tokens
+        self.encoder_cache_manager = EncoderCacheManager(sc.encoder_cache_size)
         if cc.kv_transfer_config:
             self.kv_cache_manager.enable_kv_connector(cc.kv_transfer_config)
         elif cc.num_cpu_blocks > 0:
@@ -168,8 +171,37 @@ class Scheduler:
             r.status = status
             self._free_request(r)
 
+    def _try_schedule_encoder_inputs(self, r: Request, num_computed: int, n: int, encoder_budget: int) -> tuple[list[int], int, int]:
+        """Which multimodal items of ``r`` must be encoded for the tokens [num_computed, num_computed + n) to run. An item whose
+        placeholder range overlaps that window needs its encoder output in the cache: already there (this or another request put it
+        there), or scheduled now if the step's encoder budget and the cache have room; otherwise the window is cut just before the
+        item. Returns (item indices to encode, tokens to schedule, remaining encoder budget)
+        (reference: v1/core/sched/scheduler.py:1936 ``_try_schedule_encoder_inputs``)."""
+        todo: list[int] = []
+        if not r.mm_features:
+            return todo, n, encoder_budget
+        pending = 0
+        for i, f in enumerate(r.mm_features):
+            if f.offset >= num_computed + n:
+                break
+            if f.offset + f.length <= num_computed:
+                continue  # fully consumed already
+            if i in r.mm_cached or self.encoder_cache_manager.check_and_update_cache(r, i):
+                r.mm_cached.add(i)
+                continue
+            if self.encoder_cache_manager.can_allocate(r, i, encoder_budget, pending):
+                todo.append(i)
+                pending += f.length
+                encoder_budget -= f.length
+                continue
+            # no room: run only the tokens before this item (none, if the window starts inside it)
+            n = max(f.offset - num_computed, 0)
+            break
+        return todo, n, encoder_budget
+
     def _free_request(self, r: Request) -> None:
         assert r.is_finished()
+        self.encoder_cache_manager.free(r)
         self.kv_cache_manager.free(r)
         self.finished_req_ids.add(r.request_id)
         del self.requests[r.request_id]
@@ -184,6 +216,7 @@ class Scheduler:
         new_blocks_of: dict[str, list[int]] = {}
         preempted: list[Request] = []
         sc = self.cfg.scheduler_config
+        encoder_budget = self.max_num_encoder_input_tokens
 
         # 1. running requests
         i = 0
@@ -193,6 +226,9 @@ class Scheduler:
             if sc.long_prefill_token_threshold > 0:
                 n = min(n, sc.long_prefill_token_threshold)
             n = min(n, budget, self.max_model_len - 1 - r.num_computed_tokens)
+            enc_todo: list[int] = []
+            if n > 0 and r.mm_features:
+                enc_todo, n, enc_left = self._try_schedule_encoder_inputs(r, r.num_computed_tokens, n, encoder_budget)
             if n <= 0:
                 i += 1
                 continue
@@ -221,6 +257,12 @@ class Scheduler:
             new_blocks_of[r.request_id] = [b.block_id for b in new_blocks]
             out.num_scheduled_tokens[r.request_id] = n
             budget -= n
+            if enc_todo:
+                encoder_budget = enc_left
+                out.scheduled_encoder_inputs[r.request_id] = enc_todo
+                for k in enc_todo:
+                    self.encoder_cache_manager.allocate(r, k)
+                    r.mm_cached.add(k)
             if r.spec_token_ids:
                 num_spec = n + r.num_computed_tokens - r.num_tokens
                 if num_spec > 0:
@@ -253,9 +295,20 @@ class Scheduler:
                     break
                 n = min(n, budget)
                 assert n > 0
+                enc_todo = []
+                if r.mm_features:
+                    enc_todo, n, enc_left = self._try_schedule_encoder_inputs(r, r.num_computed_tokens + num_hit, n, encoder_budget)
+                    if n <= 0:
+                        break  # the encoder budget or cache is exhausted for this step
                 new_blocks = self.kv_cache_manager.allocate_slots(r, n, num_hit, hit_blocks, self.num_lookahead_tokens)
                 if new_blocks is None:
                     break
+                if enc_todo:
+                    encoder_budget = enc_left
+                    out.scheduled_encoder_inputs[r.request_id] = enc_todo
+                    for k in enc_todo:
+                        self.encoder_cache_manager.allocate(r, k)
+                        r.mm_cached.add(k)
                 self.waiting.pop()
                 self.running.append(r)
                 if r.status == RequestStatus.PREEMPTED:
@@ -279,7 +332,8 @@ class Scheduler:
         km = self.kv_cache_manager
         out.scheduled_new_reqs = [
             NewRequestData(r.request_id, r.prompt_token_ids, r.sampling_params, new_blocks_of[r.request_id],
-                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params, r.lora_request, r.prompt_embeds)
+                           r.num_computed_tokens, km.get_state_slot(r.request_id), r.eos_token_id, r.pooling_params, r.lora_request, r.prompt_embeds,
+                           r.mm_features or None)
             for r in scheduled_new]
         cached = CachedRequestData()
         for r in scheduled_resumed + scheduled_running:
@@ -298,6 +352,7 @@ class Scheduler:
         out.scheduled_cached_reqs = cached
         out.finished_req_ids, self.finished_req_ids = self.finished_req_ids, set()
         out.preempted_req_ids = {r.request_id for r in preempted}
+        out.free_encoder_mm_hashes = self.encoder_cache_manager.get_freed_mm_hashes()
         if self.running:
             out.num_common_prefix_blocks = km.get_num_common_prefix_blocks(self.running[0].request_id, len(self.running))
         if self.kv_cache_manager.offload is not None:
@@ -309,6 +364,8 @@ class Scheduler:
 
     def _preempt(self, r: Request) -> None:
         self.kv_cache_manager.free(r)
+        self.encoder_cache_manager.free(r)  # the recomputation will ask for the encoder outputs again
+        r.mm_cached.clear()
         r.status = RequestStatus.PREEMPTED
         r.num_computed_tokens = 0
         r.spec_token_ids = []
@@ -317,7 +374,18 @@ class Scheduler:
         self.waiting.prepend([r])
 
     # ------------------------------------------------------------------ results
+    def _release_consumed_encoder_inputs(self, sched_out: SchedulerOutput) -> None:
+        """An item's encoder output is needed until the last of its placeholder positions has been computed."""
+        for rid in sched_out.num_scheduled_tokens:
+            r = self.requests.get(rid)
+            if r is None or not r.mm_cached:
+                continue
+            for i in [i for i in r.mm_cached if r.mm_features[i].offset + r.mm_features[i].length <= r.num_computed_tokens]:
+                self.encoder_cache_manager.free_encoder_input(r, i)
+                r.mm_cached.discard(i)
+
     def update_from_output(self, sched_out: SchedulerOutput, mro: ModelRunnerOutput) -> dict[int, EngineCoreOutputs]:
+        self._release_consumed_encoder_inputs(sched_out)
         idx = {rid: i for i, rid in enumerate(mro.req_ids)}
         outputs: dict[int, list[EngineCoreOutput]] = {}
         stopped: list[Request] = []

@@ -25,26 +25,53 @@ __device__ __forceinline__ int find_request(const int* qsl, int R, int t) {
 }
 
 // y[t, c] = silu(sum_j w[c, j] * x[t - (kw-1) + j, c]) where rows before the sequence start come from conv_state[slot][c][*]
-// (or zero without an initial state). One thread per (token, channel).
+// (or zero without an initial state). One thread per (token, 8 channels): 16-byte loads of the kw input rows and one 16-byte store;
+// VEC = 1 is the fallback for channel counts or pitches that are not multiples of 8.
+template <int VEC>
 __global__ void gdn_conv_kernel(const GdnConvParams p) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   const int t = blockIdx.y;
+  __shared__ int s_r;
+  if (threadIdx.x == 0) s_r = find_request(p.query_start_loc, p.R, t);
+  __syncthreads();
   if (c >= p.C) return;
-  const int r = find_request(p.query_start_loc, p.R, t);
+  const int r = s_r;
   const int t0 = p.query_start_loc[r];
   const int slot = p.state_slots[r];
   const bool has_init = p.has_initial_state[r] != 0;
   const int kw = p.kw;
-  float acc = 0.f;
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
   for (int j = 0; j < kw; ++j) {
     const int tt = t - (kw - 1) + j;
-    float xv;
-    if (tt >= t0) xv = __bfloat162float(p.x[(size_t)tt * p.ldx + c]);
-    else if (has_init) xv = __bfloat162float(p.conv_state[((size_t)slot * p.C + c) * (kw - 1) + (kw - 1) + (tt - t0)]);
-    else xv = 0.f;
-    acc += xv * __bfloat162float(p.w[(size_t)c * kw + j]);
+    float xv[VEC];
+    if (tt >= t0) {
+      if (VEC == 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(p.x + (size_t)tt * p.ldx + c);
+        const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) xv[e] = __bfloat162float(rp[e]);
+      } else {
+        xv[0] = __bfloat162float(p.x[(size_t)tt * p.ldx + c]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        xv[e] = has_init ? __bfloat162float(p.conv_state[((size_t)slot * p.C + c + e) * (kw - 1) + (kw - 1) + (tt - t0)]) : 0.f;
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) acc[e] += xv[e] * __bfloat162float(p.w[(size_t)(c + e) * kw + j]);
   }
-  p.y[(size_t)t * p.C + c] = __float2bfloat16(acc / (1.f + __expf(-acc)));
+  if (VEC == 8) {
+    uint4 o;
+    __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) op[e] = __float2bfloat16(acc[e] / (1.f + __expf(-acc[e])));
+    *reinterpret_cast<uint4*>(p.y + (size_t)t * p.C + c) = o;
+  } else {
+    p.y[(size_t)t * p.C + c] = __float2bfloat16(acc[0] / (1.f + __expf(-acc[0])));
+  }
 }
 
 // conv_state[slot][c][:] <- the last kw-1 inputs of the sequence (mixing old state and new tokens when the chunk is short).
@@ -220,8 +247,13 @@ __global__ void __launch_bounds__(GT) gdn_recurrent_kernel(const GdnParams p) {
 int gdn_conv_launch(const GdnConvParams& p, cudaStream_t st) {
   if (p.T == 0) return 0;
   if (p.kw < 2 || p.kw > 8) return -1;
-  dim3 grid((p.C + 255) / 256, p.T);
-  gdn_conv_kernel<<<grid, 256, 0, st>>>(p);
+  if (p.C % 8 == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 && ((uintptr_t)p.y & 15) == 0) {
+    dim3 grid((p.C / 8 + 127) / 128, p.T);
+    gdn_conv_kernel<8><<<grid, 128, 0, st>>>(p);
+  } else {
+    dim3 grid((p.C + 255) / 256, p.T);
+    gdn_conv_kernel<1><<<grid, 256, 0, st>>>(p);
+  }
   dim3 g2((p.C + 255) / 256, p.R);
   gdn_conv_state_kernel<<<g2, 256, 0, st>>>(p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;

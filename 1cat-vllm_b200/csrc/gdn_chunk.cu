@@ -64,10 +64,12 @@ __device__ __forceinline__ uint32_t at_addr(uint32_t base, int pitch, int m0, in
 constexpr size_t kWsTile = (size_t)C * D;                        // elements
 constexpr size_t kWsPerHead = 4 * kWsTile + (size_t)C * C + 8;   // + 8 bf16 = 16 bytes for the closing decay (kept 16-byte aligned)
 
+// Storage is reused so that four CTAs fit an SM (the kernel is a chain of short dependent phases; resident warps hide its latencies):
+//   q: normalised q rows -> fp32 T of the triangular solve -> beta-scaled v rows;   a: fp32 A -> bf16 T (the A operand of W and U)
 struct SmemA {
-  __nv_bfloat16 q[C][P128], k[C][P128], v[C][P128];
+  __nv_bfloat16 q[C][P128], k[C][P128];
   float a[C][C + 1];
-  __nv_bfloat16 t[C][P64];
+  float m[3][16][17];
   float G[C], beta[C];
 };
 
@@ -108,19 +110,17 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const GdnChunkPa
     s.G[lane] = x0;
     s.G[lane + 32] = x1;
   }
-  // rows: L2-normalised q (with the output scale) and k, and v, as bf16 (warp w takes tokens w, w + 4, ...)
+  // rows: L2-normalised q (with the output scale) and k as bf16 (warp w takes tokens w, w + 4, ...)
   for (int i = warp; i < C; i += 4) {
-    float q4[4] = {0.f, 0.f, 0.f, 0.f}, k4[4] = {0.f, 0.f, 0.f, 0.f}, v4[4] = {0.f, 0.f, 0.f, 0.f};
+    float q4[4] = {0.f, 0.f, 0.f, 0.f}, k4[4] = {0.f, 0.f, 0.f, 0.f};
     if (i < n) {
       const size_t row = (size_t)(tc + i) * p.ld_qkv;
       const uint2 qr = *reinterpret_cast<const uint2*>(p.q + row + hk * D + lane * 4);
       const uint2 kr = *reinterpret_cast<const uint2*>(p.k + row + hk * D + lane * 4);
-      const uint2 vr = *reinterpret_cast<const uint2*>(p.v + row + hv * D + lane * 4);
       const __nv_bfloat16* qp = reinterpret_cast<const __nv_bfloat16*>(&qr);
       const __nv_bfloat16* kp = reinterpret_cast<const __nv_bfloat16*>(&kr);
-      const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&vr);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) { q4[e] = __bfloat162float(qp[e]); k4[e] = __bfloat162float(kp[e]); v4[e] = __bfloat162float(vp[e]); }
+      for (int e = 0; e < 4; ++e) { q4[e] = __bfloat162float(qp[e]); k4[e] = __bfloat162float(kp[e]); }
     }
     float q2 = q4[0] * q4[0] + q4[1] * q4[1] + q4[2] * q4[2] + q4[3] * q4[3];
     float k2 = k4[0] * k4[0] + k4[1] * k4[1] + k4[2] * k4[2] + k4[3] * k4[3];
@@ -129,14 +129,13 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const GdnChunkPa
     const float qs = rsqrtf(q2 + 1e-6f) * scale, ks = rsqrtf(k2 + 1e-6f);
     *reinterpret_cast<uint2*>(&s.q[i][lane * 4]) = make_uint2(pack2(q4[0] * qs, q4[1] * qs), pack2(q4[2] * qs, q4[3] * qs));
     *reinterpret_cast<uint2*>(&s.k[i][lane * 4]) = make_uint2(pack2(k4[0] * ks, k4[1] * ks), pack2(k4[2] * ks, k4[3] * ks));
-    *reinterpret_cast<uint2*>(&s.v[i][lane * 4]) = make_uint2(pack2(v4[0], v4[1]), pack2(v4[2], v4[3]));
   }
   __syncthreads();
   __nv_bfloat16* ws = p.ws + ((size_t)ci * p.Hv + hv) * kWsPerHead;
   __nv_bfloat16* wsW = ws, *wsU = ws + kWsTile, *wsQ = ws + 2 * kWsTile, *wsK = ws + 3 * kWsTile, *wsP = ws + 4 * kWsTile;
   const int g = lane >> 2, t4 = lane & 3;
   const int m0 = warp * 16;
-  const uint32_t sq = smem_u32(&s.q[0][0]), sk = smem_u32(&s.k[0][0]), sv = smem_u32(&s.v[0][0]), st = smem_u32(&s.t[0][0]);
+  const uint32_t sq = smem_u32(&s.q[0][0]), sk = smem_u32(&s.k[0][0]), sv = sq, st = smem_u32(&s.a[0][0]);
   {
     // K K^T and Q K^T for this warp's 16 rows (all 64 columns)
     float kk[8][4], qk[8][4];
@@ -193,7 +192,7 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const GdnChunkPa
     // T = (I + A)^-1, blocked 4 x 4 in 16 x 16 blocks: the diagonal blocks by forward substitution (one column per thread, in
     // registers), then the block sub-diagonals d = 1, 2, 3 from  T_ij = -T_ii * sum_{j <= k < i} A_ik T_kj ; all in fp32
     float (*T)[C + 1] = reinterpret_cast<float (*)[C + 1]>(&s.q[0][0]);   // fp32 [64][65] over the q tile (16.6 KB <= 17 KB)
-    float (*M)[16][17] = reinterpret_cast<float (*)[16][17]>(&s.t[0][0]);  // up to three 16 x 16 temporaries over the (not yet written) bf16 T
+    float (*M)[16][17] = s.m;                                            // up to three 16 x 16 temporaries
     for (int e = tid; e < C * C; e += 128) T[e >> 6][e & 63] = 0.f;
     __syncthreads();
     if (tid < C) {
@@ -232,21 +231,40 @@ __global__ void __launch_bounds__(128) gdn_chunk_prepare_kernel(const GdnChunkPa
       }
       __syncthreads();
     }
-    // bf16 copy of T as the A operand; rows of k and v scaled into the B operands
-    for (int e = tid; e < C * C; e += 128) {
-      const int i = e >> 6, j = e & 63;
-      s.t[i][j] = __float2bfloat16(T[i][j]);
+    // bf16 copy of T (the A operand of W and U) over the storage of A, which the solve no longer needs: every thread first reads
+    // its share of T, then all of them write
+    {
+      __nv_bfloat16 (*Tb)[P64] = reinterpret_cast<__nv_bfloat16 (*)[P64]>(&s.a[0][0]);
+      float tv[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int idx = tid + e * 128;
+        tv[e] = T[idx >> 6][idx & 63];
+      }
+      __syncthreads();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        const int idx = tid + e * 128;
+        Tb[idx >> 6][idx & 63] = __float2bfloat16(tv[e]);
+      }
     }
+    // B operands: k rows scaled by beta e^G in place; v rows scaled by beta, loaded now into the storage T has left
     for (int i = warp; i < C; i += 4) {
       const float bk = s.beta[i] * __expf(s.G[i]), bv = s.beta[i];
       __nv_bfloat162* kp = reinterpret_cast<__nv_bfloat162*>(&s.k[i][lane * 4]);
-      __nv_bfloat162* vp = reinterpret_cast<__nv_bfloat162*>(&s.v[i][lane * 4]);
+      float v4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (i < n) {
+        const uint2 vr = *reinterpret_cast<const uint2*>(p.v + (size_t)(tc + i) * p.ld_qkv + hv * D + lane * 4);
+        const __nv_bfloat16* vp = reinterpret_cast<const __nv_bfloat16*>(&vr);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) v4[e] = __bfloat162float(vp[e]);
+      }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        float2 kf = __bfloat1622float2(kp[e]), vf = __bfloat1622float2(vp[e]);
+        const float2 kf = __bfloat1622float2(kp[e]);
         kp[e] = __floats2bfloat162_rn(kf.x * bk, kf.y * bk);
-        vp[e] = __floats2bfloat162_rn(vf.x * bv, vf.y * bv);
       }
+      *reinterpret_cast<uint2*>(&s.q[i][lane * 4]) = make_uint2(pack2(v4[0] * bv, v4[1] * bv), pack2(v4[2] * bv, v4[3] * bv));
     }
   }
   __syncthreads();

@@ -55,6 +55,18 @@ class InputProcessor:
             if k < 1:
                 raise ValueError("truncate_prompt_tokens must be a positive integer or -1")
             ids = list(ids)[-k:]   # left truncation, as the reference does
+        mm_features = None
+        mm_data = prompt.get("multi_modal_data") if isinstance(prompt, dict) else None
+        if mm_data:
+            if embeds is not None:
+                raise ValueError("multi_modal_data cannot be combined with prompt_embeds")
+            if getattr(self, "_mm_processor", None) is None:
+                from onecat_vllm.multimodal import MULTIMODAL_REGISTRY
+                self._mm_processor = MULTIMODAL_REGISTRY.create_processor(mc)
+            if self._mm_processor is None:
+                raise ValueError("this model takes no multimodal inputs (its config names no image / video / audio token)")
+            done = self._mm_processor.apply(list(ids), mm_data)
+            ids, mm_features = done.token_ids, done.features
         if not ids:
             raise ValueError("the prompt is empty")
         if len(ids) >= mc.max_model_len:
@@ -87,7 +99,7 @@ class InputProcessor:
         if sp.allowed_token_ids is not None and any(not 0 <= t < mc.vocab_size for t in sp.allowed_token_ids):
             raise ValueError("allowed_token_ids contains an id outside the vocabulary")
         req = EngineCoreRequest(request_id, ids, sp, arrival_time or time.time(), eos, priority, salt, pooling_params=pooling,
-                                lora_request=lora_request, prompt_embeds=embeds)
+                                lora_request=lora_request, prompt_embeds=embeds, mm_features=mm_features)
         return req, text
 
 

@@ -66,7 +66,12 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             name = name[len("language_model."):]
         elif name.startswith("model.language_model."):  # text tower of a multimodal checkpoint (Qwen3.5)
             name = "model." + name[len("model.language_model."):]
-        if "rotary_emb.inv_freq" in name or name.startswith(("visual.", "model.visual.")):
+        if name.startswith(("visual.", "model.visual.")):
+            tower = getattr(model, "visual", None)  # multimodal checkpoints: the vision tower, when this model builds one
+            if tower is not None and tower.load_weight(name, w):
+                loaded.add(name)
+            continue
+        if "rotary_emb.inv_freq" in name:
             continue
         for theirs, ours in _RENAMES:
             if theirs in name:

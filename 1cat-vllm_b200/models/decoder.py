@@ -174,6 +174,20 @@ class CausalLM(nn.Module):
             self.lm_head = None
         else:
             self.lm_head = ParallelLMHead(cfg.vocab_size, cfg.hidden_size, cfg.dtype)
+        self.visual = None
+        # the tower built here is the Qwen2-VL one; other multimodal checkpoints load their text tower and take image embeddings
+        if cfg.architecture == "Qwen2VLForConditionalGeneration" and cfg.vision_config and cfg.vision_config.get("depth") and ps.get_state().is_first_pp:
+            from onecat_vllm.models.vision import VisionTower
+            self.visual = VisionTower(cfg.vision_config, cfg.dtype)
+
+    def embed_multimodal(self, feature, device) -> torch.Tensor:
+        """Embeddings ``[length, hidden]`` of one multimodal item: given ones are passed through, pixel inputs go through the
+        vision tower (reference: models/interfaces.py ``SupportsMultiModal.embed_multimodal``)."""
+        if feature.kind == "embeds":
+            return torch.as_tensor(feature.data).to(device, self.cfg.dtype)
+        if self.visual is None:
+            raise ValueError("this checkpoint has no vision tower: pass image embeddings instead of pixel values")
+        return self.visual(torch.as_tensor(feature.data["pixel_values"]), feature.data["grid_thw"])
 
     def forward(self, input_ids, md, caches, inputs_embeds=None, intermediate=None):
         return self.model(input_ids, md, caches, inputs_embeds, intermediate=intermediate)

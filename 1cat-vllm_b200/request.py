@@ -55,6 +55,7 @@ class EngineCoreRequest:
     lora_request: Any = None
     trace_headers: Optional[dict] = None
     prompt_embeds: Any = None  # [num_prompt_tokens, hidden] tensor replacing the embedding lookup of the prompt
+    mm_features: Any = None    # list[MultiModalFeature]: placeholder ranges of the prompt and their encoder inputs
 
     def to_wire(self) -> dict:
         return {"request_id": self.request_id, "prompt_token_ids": self.prompt_token_ids,
@@ -63,7 +64,7 @@ class EngineCoreRequest:
                 "cache_salt": self.cache_salt, "client_index": self.client_index,
                 "pooling_params": self.pooling_params.to_dict() if self.pooling_params is not None else None,
                 "lora_request": self.lora_request.to_dict() if self.lora_request is not None else None,
-                "prompt_embeds": self.prompt_embeds}
+                "prompt_embeds": self.prompt_embeds, "mm_features": [f.to_wire() for f in self.mm_features] if self.mm_features else None}
 
     @classmethod
     def from_wire(cls, d: dict) -> "EngineCoreRequest":
@@ -75,7 +76,7 @@ class EngineCoreRequest:
         return cls(d["request_id"], list(d["prompt_token_ids"]), SamplingParams.from_dict(sp) if sp else None,
                    d.get("arrival_time", 0.0), d.get("eos_token_id"), d.get("priority", 0), d.get("cache_salt"),
                    d.get("client_index", 0), pooling_params=pp, lora_request=_lora_from(d.get("lora_request")),
-                   prompt_embeds=d.get("prompt_embeds"))
+                   prompt_embeds=d.get("prompt_embeds"), mm_features=_mm_from(d.get("mm_features")))
 
 
 @dataclass
@@ -134,6 +135,13 @@ def _lora_from(d):
     return LoRARequest.from_dict(d)
 
 
+def _mm_from(lst):
+    if not lst:
+        return None
+    from onecat_vllm.multimodal import MultiModalFeature
+    return [f if isinstance(f, MultiModalFeature) else MultiModalFeature.from_wire(f) for f in lst]
+
+
 class Request:
     """Scheduler-side request. Tokens = prompt + outputs; ``num_computed_tokens`` chases
     ``num_tokens_with_spec`` (reference: v1/core/sched/scheduler.py:459-468)."""
@@ -141,9 +149,13 @@ class Request:
     def __init__(self, request_id: str, prompt_token_ids: list[int], sampling_params: Optional[SamplingParams],
                  eos_token_id: Optional[int] = None, arrival_time: Optional[float] = None, priority: int = 0,
                  cache_salt: Optional[str] = None, client_index: int = 0, block_hasher=None, pooling_params=None, lora_request=None,
-                 prompt_embeds=None) -> None:
+                 prompt_embeds=None, mm_features=None) -> None:
         self.request_id = request_id
         self.prompt_embeds = prompt_embeds
+        self.mm_features = list(mm_features or [])
+        self.mm_cached: set = set()  # indices of the items whose encoder output this request holds a reference to
+        if self.mm_features:  # the same placeholder ids stand for different images: the items' hashes salt the prefix cache
+            cache_salt = f"{cache_salt or ''}|mm:" + ",".join(f.mm_hash[:16] for f in self.mm_features)
         if prompt_embeds is not None:  # placeholder ids say nothing about the content: never share KV blocks with another request
             cache_salt = f"{cache_salt or ''}|embeds:{request_id}"
         self.lora_request = lora_request
@@ -194,7 +206,7 @@ class Request:
     @classmethod
     def from_engine_core_request(cls, r: EngineCoreRequest, block_hasher=None) -> "Request":
         return cls(r.request_id, r.prompt_token_ids, r.sampling_params, r.eos_token_id, r.arrival_time, r.priority,
-                   r.cache_salt, r.client_index, block_hasher, r.pooling_params, r.lora_request, r.prompt_embeds)
+                   r.cache_salt, r.client_index, block_hasher, r.pooling_params, r.lora_request, r.prompt_embeds, r.mm_features)
 
     def append_output_token_ids(self, ids: int | list[int]) -> None:
         if isinstance(ids, int):

@@ -44,6 +44,7 @@ class CachedRequestState:
     pooling_params: object = None
     lora_request: object = None
     prompt_embeds: Optional[torch.Tensor] = None
+    mm_features: Optional[list] = None  # multimodal items of the prompt (placeholder ranges + encoder inputs)
     pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
     pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
 
@@ -73,6 +74,7 @@ class ModelRunner:
         self.rejection_sampler = RejectionSampler(sc.conditional_rates(), sc.synthetic_seed) if sc.enabled else None
         self.proposer = None
         self.graphs = None  # worker.cuda_graphs.DecodeGraphs
+        self.encoder_cache: dict = {}  # content hash of a multimodal item -> its encoder output [positions, hidden]
         self._last_step_ms = 0.0
         self.h2d_bytes = 0
         self.d2h_bytes = 0
@@ -233,7 +235,8 @@ class ModelRunner:
             self.requests[nr.req_id] = CachedRequestState(nr.req_id, list(nr.prompt_token_ids), len(nr.prompt_token_ids), sp,
                                                           list(nr.block_ids), nr.num_computed_tokens, nr.state_slot, gen, nr.eos_token_id,
                                                           nr.pooling_params, nr.lora_request,
-                                                          nr.prompt_embeds.to(self.device, self.mc.dtype) if nr.prompt_embeds is not None else None)
+                                                          nr.prompt_embeds.to(self.device, self.mc.dtype) if nr.prompt_embeds is not None else None,
+                                                          list(nr.mm_features) if nr.mm_features else None)
         c = so.scheduled_cached_reqs
         for i, rid in enumerate(c.req_ids):
             st = self.requests.get(rid)
@@ -244,7 +247,7 @@ class ModelRunner:
                                         list(c.new_block_ids[i] or []), c.num_computed_tokens[i], c.state_slots[i],
                                         old.generator if old else None, old.eos_token_id if old else None,
                                         old.pooling_params if old else None, old.lora_request if old else None,
-                                        old.prompt_embeds if old else None)
+                                        old.prompt_embeds if old else None, old.mm_features if old else None)
                 self.requests[rid] = st
             else:
                 st.num_computed_tokens = c.num_computed_tokens[i]
@@ -468,6 +471,7 @@ class ModelRunner:
     def _execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
         self._update_states(so)
         self._swap_kv(so)
+        self._run_encoders(so)
         if so.total_num_scheduled_tokens == 0:
             return ModelRunnerOutput()
         req_ids, R, T, n_l, rows, drafts_of, max_q, max_s, max_nb = self._prepare_inputs(so)
@@ -487,7 +491,9 @@ class ModelRunner:
             lora_batch = self.lora_manager.make_batch(token_reqs, self.device)
             set_active(lora_batch)
         gkey = None
-        if self.graphs is not None and lora_batch is None and max_q == min(query_lens) and not (spec_any and self.mc.is_hybrid):
+        in_embed_prompt = any((self.requests[rid].prompt_embeds is not None or self.requests[rid].mm_features) and
+                              self.requests[rid].num_computed_tokens < self.requests[rid].num_prompt_tokens for rid in req_ids)
+        if self.graphs is not None and lora_batch is None and max_q == min(query_lens) and not (spec_any and self.mc.is_hybrid) and not in_embed_prompt:
             gkey = self.graphs.plan(R, max_q, max_s)
             if gkey is not None:
                 self._pad_inputs(R, T, gkey[0], max_q)
@@ -594,9 +600,26 @@ class ModelRunner:
             o += q
         return res
 
+    def _run_encoders(self, so) -> None:
+        """Encode the multimodal items the scheduler put into this step and drop the outputs it released
+        (reference: v1/worker/gpu_model_runner.py ``_execute_mm_encoder``; encoder cache keyed by the item's content hash)."""
+        for h in getattr(so, "free_encoder_mm_hashes", None) or ():
+            self.encoder_cache.pop(h, None)
+        for rid, idxs in (getattr(so, "scheduled_encoder_inputs", None) or {}).items():
+            st = self.requests[rid]
+            for i in idxs:
+                f = st.mm_features[i]
+                if f.mm_hash in self.encoder_cache:
+                    continue
+                out = self.model.embed_multimodal(f, self.device)
+                if out.shape[0] != f.length or out.shape[1] != self.mc.hidden_size:
+                    raise ValueError(f"the encoder returned {tuple(out.shape)} for an item of {f.length} positions")
+                self.encoder_cache[f.mm_hash] = out.to(self.device, self.mc.dtype)
+
     def _input_embeds(self, ids: torch.Tensor, req_ids: list, query_lens: list[int]) -> Optional[torch.Tensor]:
-        """Embedding rows of the step with the prompt positions of ``prompt_embeds`` requests replaced by their own vectors;
-        ``None`` when no such position is in the batch (reference: v1/worker/gpu_model_runner.py ``enable_prompt_embeds`` path)."""
+        """Embedding rows of the step with the prompt positions of ``prompt_embeds`` requests replaced by their own vectors and the
+        placeholder positions of multimodal items by their encoder outputs; ``None`` when no such position is in the batch
+        (reference: v1/worker/gpu_model_runner.py ``enable_prompt_embeds`` path and ``_gather_mm_embeddings``)."""
         if not self.pp.is_first_pp:
             return None
         emb, o = None, 0
@@ -608,6 +631,13 @@ class ModelRunner:
                     emb = self.model.model.embed_tokens(ids)
                 n = min(q, st.num_prompt_tokens - c0)
                 emb[o:o + n] = st.prompt_embeds[c0:c0 + n]
+            for f in st.mm_features or ():
+                lo, hi = max(f.offset, c0), min(f.offset + f.length, c0 + q)
+                if lo >= hi:
+                    continue
+                if emb is None:
+                    emb = self.model.model.embed_tokens(ids)
+                emb[o + lo - c0: o + hi - c0] = self.encoder_cache[f.mm_hash][lo - f.offset: hi - f.offset]
             o += q
         return emb
 

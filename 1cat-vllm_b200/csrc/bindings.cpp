@@ -256,6 +256,22 @@ void paged_attention(torch::Tensor q, torch::Tensor kv_cache, torch::Tensor out,
   TORCH_CHECK(rc == 0, "attention launch failed with code ", rc);
 }
 
+// LSE-weighted merge of two partial attention results [T, H, D] bf16 with fp32 [T, H] log-sum-exps; returns (merged, merged lse)
+std::vector<torch::Tensor> merge_attn_states(torch::Tensor o1, torch::Tensor lse1, torch::Tensor o2, torch::Tensor lse2) {
+  check_bf16(o1, "o1");
+  check_bf16(o2, "o2");
+  TORCH_CHECK(o1.is_contiguous() && o2.is_contiguous() && lse1.is_contiguous() && lse2.is_contiguous() && o1.sizes() == o2.sizes(), "contiguous tensors of one shape");
+  TORCH_CHECK(lse1.scalar_type() == torch::kFloat32 && lse2.scalar_type() == torch::kFloat32 && lse1.numel() == lse2.numel(), "lse must be fp32");
+  const c10::cuda::CUDAGuard guard(o1.device());
+  const int D = (int)o1.size(-1), rows = (int)(o1.numel() / D);
+  TORCH_CHECK(lse1.numel() == rows, "one lse per (token, head)");
+  auto out = torch::empty_like(o1);
+  auto lse = torch::empty_like(lse1);
+  TORCH_CHECK(oc::merge_attn_states_launch(o1.data_ptr(), lse1.data_ptr<float>(), o2.data_ptr(), lse2.data_ptr<float>(), out.data_ptr(), lse.data_ptr<float>(),
+                                           rows, D, cur_stream()) == 0, "merge_attn_states failed");
+  return {out, lse};
+}
+
 torch::Tensor argmax(torch::Tensor x) {
   TORCH_CHECK(x.is_cuda() && x.dim() == 2 && x.stride(1) == 1, "x must be a CUDA [B, V] matrix");
   TORCH_CHECK(x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kFloat32, "argmax supports bf16 and fp32");
@@ -625,6 +641,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("rope_and_cache", &rope_and_cache);
   m.def("paged_attention", &paged_attention);
   m.def("argmax", &argmax);
+  m.def("merge_attn_states", &merge_attn_states);
   m.def("read_status", &read_status);
   m.def("mla_decode", &mla_decode);
   m.def("fused_moe", &fused_moe);

@@ -268,6 +268,36 @@ int rope_cache_launch(const RopeCacheParams& p, cudaStream_t st) {
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
+// o = w1 o1 + w2 o2 with w_i = e^{lse_i - m} / (e^{lse1 - m} + e^{lse2 - m}), m = max(lse1, lse2); lse = m + log(sum): the merge of two
+// attention results over disjoint key sets (split contexts, cascade prefixes, decode context parallel ranks). One warp per (token, head) row.
+// (reference: csrc/attention/merge_attn_states.cu:19)
+__global__ void merge_attn_states_kernel(const __nv_bfloat16* o1, const float* lse1, const __nv_bfloat16* o2, const float* lse2, __nv_bfloat16* out,
+                                         float* lse_out, int rows, int D) {
+  const int row = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const float a = lse1[row], b = lse2[row];
+  float m = fmaxf(a, b);
+  if (isinf(m)) m = 0.f;  // both sides empty (or +inf): weights fall back to equal shares of zero outputs
+  const float w1 = __expf(a - m), w2 = __expf(b - m);
+  const float den = fmaxf(w1 + w2, 1e-30f);
+  const float f1 = w1 / den, f2 = w2 / den;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o1 + (size_t)row * D + c));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(o2 + (size_t)row * D + c));
+    *reinterpret_cast<__nv_bfloat162*>(out + (size_t)row * D + c) = __floats2bfloat162_rn(x.x * f1 + y.x * f2, x.y * f1 + y.y * f2);
+  }
+  if (lane == 0 && lse_out != nullptr) lse_out[row] = m + __logf(den);
+}
+
+int merge_attn_states_launch(const void* o1, const float* lse1, const void* o2, const float* lse2, void* out, float* lse_out, int rows, int D,
+                             cudaStream_t st) {
+  if (D % 2) return -1;
+  if (rows == 0) return 0;
+  merge_attn_states_kernel<<<(rows * 32 + 255) / 256, 256, 0, st>>>((const __nv_bfloat16*)o1, lse1, (const __nv_bfloat16*)o2, lse2, (__nv_bfloat16*)out,
+                                                                   lse_out, rows, D);
+  return cudaGetLastError() == cudaSuccess ? 0 : -2;
+}
+
 int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st) {
   if (B == 0) return 0;
   if (is_fp32) argmax_kernel<float><<<B, 1024, 0, st>>>((const float*)x, out, V, ld);

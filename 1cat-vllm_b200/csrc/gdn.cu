@@ -43,7 +43,21 @@ __global__ void gdn_conv_kernel(const GdnConvParams p) {
   float acc[VEC];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) acc[e] = 0.f;
-  for (int j = 0; j < kw; ++j) {
+  // taps of this thread's channels: [channel][tap] is contiguous, so eight channels of a 4-tap filter are four 16-byte loads
+  float wv[VEC][4];
+  if (VEC == 8) {
+    const uint4* wp = reinterpret_cast<const uint4*>(p.w + (size_t)c * 4);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 raw = wp[i];
+      const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) wv[(i * 8 + e) >> 2][(i * 8 + e) & 3] = __bfloat162float(rp[e]);
+    }
+  }
+  const int taps = VEC == 8 ? 4 : kw;  // a compile-time 4 on the vector path, so wv[][j] stays in registers
+#pragma unroll
+  for (int j = 0; j < taps; ++j) {
     const int tt = t - (kw - 1) + j;
     float xv[VEC];
     if (tt >= t0) {
@@ -61,7 +75,7 @@ __global__ void gdn_conv_kernel(const GdnConvParams p) {
         xv[e] = has_init ? __bfloat162float(p.conv_state[((size_t)slot * p.C + c + e) * (kw - 1) + (kw - 1) + (tt - t0)]) : 0.f;
     }
 #pragma unroll
-    for (int e = 0; e < VEC; ++e) acc[e] += xv[e] * __bfloat162float(p.w[(size_t)(c + e) * kw + j]);
+    for (int e = 0; e < VEC; ++e) acc[e] += xv[e] * (VEC == 8 ? wv[e][j & 3] : __bfloat162float(p.w[(size_t)(c + e) * kw + j]));
   }
   if (VEC == 8) {
     uint4 o;
@@ -247,7 +261,7 @@ __global__ void __launch_bounds__(GT) gdn_recurrent_kernel(const GdnParams p) {
 int gdn_conv_launch(const GdnConvParams& p, cudaStream_t st) {
   if (p.T == 0) return 0;
   if (p.kw < 2 || p.kw > 8) return -1;
-  if (p.C % 8 == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 && ((uintptr_t)p.y & 15) == 0) {
+  if (p.kw == 4 && p.C % 8 == 0 && p.ldx % 8 == 0 && ((uintptr_t)p.x & 15) == 0 && ((uintptr_t)p.y & 15) == 0 && ((uintptr_t)p.w & 15) == 0) {
     dim3 grid((p.C / 8 + 127) / 128, p.T);
     gdn_conv_kernel<8><<<grid, 128, 0, st>>>(p);
   } else {

@@ -460,6 +460,230 @@ class WrappedPythonicToolParser(PythonicToolParser):
         return text if i == -1 else text[:i]
 
 
+class KeyedJsonListToolParser(ToolParser):
+    """Apertus layout: ``<|tools_prefix|>[{"name": {args}}, ...]<|tools_suffix|>`` — a JSON list of single-key objects."""
+
+    markers = ("<|tools_prefix|>",)
+
+    def extract(self, text):
+        i = text.find(self.markers[0])
+        if i == -1:
+            return text, []
+        body = text[i + len(self.markers[0]):]
+        j = body.find("<|tools_suffix|>")
+        body = body if j == -1 else body[:j]
+        calls = []
+        for v in _json_values(body):
+            for d in (v if isinstance(v, list) else [v]):
+                if isinstance(d, dict) and len(d) == 1:
+                    (name, args), = d.items()
+                    calls.append(ToolCall(str(name), args if isinstance(args, str) else json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return text[:i].strip() or None, calls
+
+
+class DsmlToolParser(ToolParser):
+    """DeepSeek-V3.2 / V4 layout: ``<｜DSML｜function_calls>`` (V4: ``tool_calls``) holding ``<｜DSML｜invoke name="f">`` blocks of
+    ``<｜DSML｜parameter name="k" string="true|false">v</｜DSML｜parameter>``; non-string parameters are JSON."""
+
+    def __init__(self, section: str = "function_calls"):
+        self.markers = (f"<｜DSML｜{section}>",)
+        self._inv = re.compile(r"<｜DSML｜invoke name=\"([^\"]+)\">(.*?)(?:</｜DSML｜invoke>|$)", re.S)
+        self._par = re.compile(r"<｜DSML｜parameter name=\"([^\"]+)\"(?: string=\"(true|false)\")?>(.*?)</｜DSML｜parameter>", re.S)
+
+    def extract(self, text):
+        i = text.find(self.markers[0])
+        if i == -1:
+            return text, []
+        calls = []
+        for m in self._inv.finditer(text[i:]):
+            args = {}
+            for k, is_str, v in self._par.findall(m.group(2)):
+                if is_str == "false":
+                    try:
+                        args[k] = json.loads(v)
+                        continue
+                    except json.JSONDecodeError:
+                        pass
+                args[k] = v
+            calls.append(ToolCall(m.group(1), json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return text[:i].strip() or None, calls
+
+
+class CallBraceToolParser(ToolParser):
+    """FunctionGemma / Gemma-4 layout: ``<start>call:name{k:v,k2:<escape>text<escape>}<end>``; values are JSON-ish literals, strings may
+    be wrapped in ``<escape>`` or ``<|"|>`` tokens."""
+
+    def __init__(self, start: str, end: str, quote: str):
+        self.markers = (start,)
+        self._re = re.compile(re.escape(start) + r"call:([\w\-\.]+)\{(.*?)\}" + re.escape(end), re.S)
+        self._quote = quote
+
+    def _args(self, body: str) -> dict:
+        out, q = {}, self._quote
+        i, n = 0, len(body)
+        while i < n:
+            j = body.find(":", i)
+            if j == -1:
+                break
+            key = body[i:j].strip().strip('"')
+            i = j + 1
+            if body.startswith(q, i):
+                k = body.find(q, i + len(q))
+                k = n if k == -1 else k
+                out[key] = body[i + len(q):k]
+                i = body.find(",", k)
+                i = n if i == -1 else i + 1
+                continue
+            depth, k = 0, i
+            while k < n and not (body[k] == "," and depth == 0):
+                depth += body[k] in "[{"
+                depth -= body[k] in "]}"
+                k += 1
+            raw = body[i:k].strip()
+            try:
+                out[key] = json.loads(raw)
+            except json.JSONDecodeError:
+                out[key] = raw
+            i = k + 1
+        return out
+
+    def extract(self, text):
+        calls = [ToolCall(m.group(1), json.dumps(self._args(m.group(2)), ensure_ascii=False)) for m in self._re.finditer(text)]
+        if not calls:
+            return text, []
+        return text[: text.find(self.markers[0])].strip() or None, calls
+
+
+class GigaChatToolParser(ToolParser):
+    """GigaChat-3 layout: ``function call<|role_sep|>\n{"name": ..., "arguments": {...}}`` or ``<|function_call|>{...}``."""
+
+    markers = ("function call<|role_sep|>", "<|function_call|>")
+    _re = re.compile(r"(?:function call<\|role_sep\|>\n|<\|function_call\|>)(.*)", re.S)
+
+    def extract(self, text):
+        body = text[: text.rfind("</s>")] if text.rstrip().endswith("</s>") else text
+        m = self._re.search(body)
+        if m is None:
+            return text, []
+        calls = []
+        for v in _json_values(m.group(1)):
+            calls += _calls_from_json(v)
+        if not calls:
+            return text, []
+        head = re.split(r"<\|message_sep\|>|<\|function_call\|>|function call<\|role_sep\|>", body, maxsplit=1)[0]
+        return head.strip() or None, calls
+
+
+class SepArgKeyToolParser(Glm45ToolParser):
+    """Hunyuan-V3 layout: ``<tool_calls><tool_call>name<tool_sep><arg_key>k</arg_key><arg_value>v</arg_value>…</tool_call></tool_calls>``."""
+
+    markers = ("<tool_calls>", "<tool_call>")
+    _call = re.compile(r"<tool_call>(.*?)<tool_sep>(.*?)(?:</tool_call>|$)", re.S)
+
+    def extract(self, text):
+        content, calls = super().extract(text)
+        if calls and content is not None:
+            i = self._first_marker(text)
+            content = text[:i].strip() or None
+        return content, calls
+
+
+class FunctionParamXmlToolParser(ToolParser):
+    """MiniCPM-5 layout: ``<function name="f"><param name="k">v</param></function>`` (values may be CDATA; JSON when they parse)."""
+
+    markers = ("<function name=", "<function name =", "<functionname=")
+    _fn = re.compile(r"<function\s*name\s*=\s*['\"]([^'\"]+)['\"][^>]*>(.*?)(?:</function>|$)", re.S)
+    _par = re.compile(r"<param\s*name\s*=\s*['\"]([^'\"]+)['\"]>([\s\S]*?)</param>", re.S)
+
+    def extract(self, text):
+        vis = text.rsplit("</think>", 1)[-1] if "</think>" in text else text
+        calls = []
+        for m in self._fn.finditer(vis):
+            args = {}
+            for k, v in self._par.findall(m.group(2)):
+                v = v.strip()
+                if v.startswith("<![CDATA[") and v.endswith("]]>"):
+                    v = v[len("<![CDATA["):-3]
+                try:
+                    args[k] = json.loads(v)
+                except json.JSONDecodeError:
+                    args[k] = v
+            calls.append(ToolCall(m.group(1), json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        i = self._first_marker(vis)
+        return vis[:i].strip() or None, calls
+
+
+class StepTmlToolParser(ToolParser):
+    """Step-3 layout: ``<｜tool_calls_begin｜><｜tool_call_begin｜>function<｜tool_sep｜><steptml:invoke name="f"><steptml:parameter
+    name="k">v</steptml:parameter></steptml:invoke><｜tool_call_end｜><｜tool_calls_end｜>``."""
+
+    markers = ("<｜tool_calls_begin｜>",)
+    _inv = re.compile(r"<steptml:invoke name=\"([^\"]+)\">(.*?)(?:</steptml:invoke>|$)", re.S)
+    _par = re.compile(r"<steptml:parameter name=\"([^\"]+)\">([^<]*)</steptml:parameter>", re.S)
+
+    def extract(self, text):
+        i = text.find(self.markers[0])
+        if i == -1:
+            return text, []
+        calls = []
+        for m in self._inv.finditer(text[i:]):
+            args = {}
+            for k, v in self._par.findall(m.group(2)):
+                try:
+                    args[k] = json.loads(v)
+                except json.JSONDecodeError:
+                    args[k] = v
+            calls.append(ToolCall(m.group(1), json.dumps(args, ensure_ascii=False)))
+        if not calls:
+            return text, []
+        return text[:i].strip() or None, calls
+
+
+class HarmonyToolParser(ToolParser):
+    """GPT-OSS harmony text: a message addressed ``to=functions.NAME`` on the commentary channel is a tool call, its body the JSON
+    arguments; the ``final`` channel is the content (reference: tool_parsers/openai_tool_parser.py over the harmony encoding)."""
+
+    markers = ("<|channel|>commentary to=functions.", "to=functions.")
+    _call = re.compile(r"to=functions\.([\w\-\.]+)[^<]*?(?:<\|constrain\|>\s*json\s*)?<\|message\|>(.*?)(?:<\|call\|>|<\|end\|>|<\|start\|>|$)", re.S)
+    _final = re.compile(r"<\|channel\|>final<\|message\|>(.*?)(?:<\|end\|>|<\|return\|>|$)", re.S)
+
+    def extract(self, text):
+        calls = [ToolCall(m.group(1), m.group(2).strip()) for m in self._call.finditer(text)]
+        if not calls:
+            return text, []
+        f = self._final.search(text)
+        return (f.group(1).strip() or None) if f else None, calls
+
+
+class CohereActionToolParser(ToolParser):
+    """Command-R layout: ``<|START_ACTION|>[{"tool_call_id": "0", "tool_name": "f", "parameters": {...}}]<|END_ACTION|>`` (the reference
+    drives an external filter library for this format; the wire format itself is plain JSON between the two tokens)."""
+
+    markers = ("<|START_ACTION|>",)
+
+    def extract(self, text):
+        i = text.find(self.markers[0])
+        if i == -1:
+            return text, []
+        body = text[i + len(self.markers[0]):]
+        j = body.find("<|END_ACTION|>")
+        body = body if j == -1 else body[:j]
+        calls = []
+        for v in _json_values(body):
+            calls += _calls_from_json(v, name_keys=("tool_name", "name"))
+        if not calls:
+            return text, []
+        head = text[:i]
+        m = re.search(r"<\|START_RESPONSE\|>(.*?)(?:<\|END_RESPONSE\|>|$)", head, re.S)
+        return ((m.group(1) if m else head).strip() or None), calls
+
+
 TOOL_PARSERS = {
     "longcat": lambda: TaggedJsonToolParser("<longcat_tool_call>", "</longcat_tool_call>"), "ernie45": HermesToolParser,
     "minimax_m2": InvokeXmlToolParser, "lfm2": WrappedPythonicToolParser, "glm4_moe": Glm45ToolParser,
@@ -476,6 +700,14 @@ TOOL_PARSERS = {
     "phi4_mini_json": lambda: MarkerJsonToolParser(("functools",)),
     "internlm": lambda: MarkerJsonToolParser(("<|action_start|><|plugin|>",), "<|action_end|>"),
     "xlam": lambda: MarkerJsonToolParser(("```json", "[TOOL_CALLS]", "<tool_call>", "[")),
+    "apertus": KeyedJsonListToolParser, "deepseek_v32": DsmlToolParser, "deepseek_v4": lambda: DsmlToolParser("tool_calls"),
+    "functiongemma": lambda: CallBraceToolParser("<start_function_call>", "<end_function_call>", "<escape>"),
+    "gemma4": lambda: CallBraceToolParser("<|tool_call>", "<tool_call|>", '<|"|>'),
+    "gigachat3": GigaChatToolParser, "granite4": HermesToolParser, "hy_v3": SepArgKeyToolParser, "minicpm5xml": FunctionParamXmlToolParser,
+    "openai": HarmonyToolParser, "poolside_v1": Glm45ToolParser, "step3": StepTmlToolParser, "step3p5": Qwen3CoderToolParser,
+    "cohere_command": CohereActionToolParser, "internlm2": lambda: MarkerJsonToolParser(("<|action_start|><|plugin|>",), "<|action_end|>"),
+    "phi4mini": lambda: MarkerJsonToolParser(("functools",)), "glm47_moe": Glm45ToolParser, "llama": Llama3JsonToolParser,
+    "qwen3coder": Qwen3CoderToolParser, "qwen3xml": Qwen3CoderToolParser,
 }
 
 

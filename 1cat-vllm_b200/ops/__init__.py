@@ -61,6 +61,13 @@ def rms_norm_gated(x, z, w, eps, heads):
     return ref.rms_norm_gated(x.reshape(T * heads, D), z.reshape(T * heads, D), w, eps).reshape(T, heads * D)
 
 
+def merge_attn_states(o1, lse1, o2, lse2):
+    """LSE-weighted merge of two partial attention results over disjoint key sets."""
+    if o1.is_cuda:
+        return ext().merge_attn_states(o1, lse1, o2, lse2)
+    return ref.merge_attn_states(o1, lse1, o2, lse2)
+
+
 def argmax(logits):
     if logits.is_cuda:
         return ext().argmax(logits)

@@ -372,6 +372,13 @@ def sample(logits, temperature, top_k=None, top_p=None, min_p=None, generators=N
                      None if top_p is None else top_p.float().contiguous(), None if min_p is None else min_p.float().contiguous(), seeds, kept)
 
 
+def merge_attn_states(o1, lse1, o2, lse2):
+    global _LAUNCHES
+    _LAUNCHES += 1
+    o, lse = _C.merge_attn_states(o1.contiguous(), lse1.float().contiguous(), o2.contiguous(), lse2.float().contiguous())
+    return o, lse
+
+
 def argmax(logits):
     global _LAUNCHES
     _LAUNCHES += 1

@@ -3,7 +3,8 @@
     python -m torch.distributed.run --nproc-per-node N --master-addr 127.0.0.1 -m onecat_vllm.parallel.bench_comm [--json PATH]
 
 For each token count T it times (CUDA events on the launching stream, max over ranks, median of ``--iters`` samples of ``--inner`` back-to-back calls each, after 5 warm-up rounds):
-  * ``fused``  : peer-memory reduce + residual add + RMSNorm in one kernel (one-shot for small T, reduce-scatter/all-gather two-shot above)
+  * ``fused``  : peer-memory reduce + residual add + RMSNorm in one kernel (one-shot for small T: flag-free arrival buffers, or the
+    flag handshake with ``ONECAT_TP_ONESHOT=flags``; reduce-scatter/all-gather two-shot above)
   * ``nccl``   : ncclAllReduce followed by the fused add+RMSNorm kernel (the baseline path)
   * ``gemm+fused`` / ``gemm+push+fused`` : a row-parallel bf16 GEMM (K = 17408 / N ranks → 5120) followed by the reduction, with the
     GEMM epilogue leaving its tile local (pulled by the reduction) or storing it straight into the peers' slabs.
@@ -31,7 +32,7 @@ def main() -> None:
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from onecat_vllm.ops import cuda as K
-    from onecat_vllm.parallel.fused import ONE_SHOT, TWO_SHOT, FusedTP
+    from onecat_vllm.parallel.fused import LAMPORT, ONE_SHOT, TWO_SHOT, FusedTP
     H = a.hidden
     f = FusedTP(world, rank, dev, 8192, H)
     w = torch.ones(H, device=dev, dtype=torch.bfloat16)
@@ -103,13 +104,13 @@ def main() -> None:
         t_n, t_cl = timed(nccl), timed(clone_only)
         t_gp, t_gpush, t_gn = timed(gemm_pull), timed(gemm_push), timed(gemm_nccl)
         # bytes each rank must receive over NVLink for the reduction (+ send for the gather in two-shot mode)
-        if mode == ONE_SHOT:
+        if mode in (ONE_SHOT, LAMPORT):
             link_bytes = (world - 1) * T * H * 2
         else:
             link_bytes = 2 * (world - 1) / world * T * H * 2
         t_link = link_bytes / 770e9 * 1e3
         t_flop = 2.0 * T * H * Kin / 1648e12 * 1e3
-        rows.append(dict(T=T, mode="one-shot" if mode == ONE_SHOT else "two-shot", fused_ms=t_f - t_c, nccl_plus_norm_ms=t_n - t_cl,
+        rows.append(dict(T=T, mode={ONE_SHOT: "one-shot (flags)", LAMPORT: "one-shot (flag-free)", TWO_SHOT: "two-shot"}[mode], fused_ms=t_f - t_c, nccl_plus_norm_ms=t_n - t_cl,
                          gemm_pull_fused_ms=t_gp, gemm_push_fused_ms=t_gpush, gemm_nccl_norm_ms=t_gn, link_bound_ms=t_link,
                          roofline_frac_reduce=t_link / max(t_f - t_c, 1e-9), roofline_frac_gemm_fused=max(t_link, t_flop) / min(t_gp, t_gpush)))
     st = K.check_status()
@@ -121,7 +122,8 @@ def main() -> None:
             json.dump({"world": world, "rows": rows, "device_status": st}, open(a.json, "w"), indent=1)
     dist.barrier()
     torch.cuda.synchronize()
-    os._exit(0)
+    f.close()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

@@ -343,3 +343,38 @@ def _last_json(text: str) -> dict:
     lines = text.splitlines()
     start = max(i for i, l in enumerate(lines) if l == "{")
     return json.loads("\n".join(lines[start:]))
+
+
+def test_remaining_tool_call_formats():
+    """One sample per output format of the model families added after the first thirty parser names."""
+    from onecat_vllm.entrypoints.parsers import TOOL_PARSERS, get_tool_parser
+    cases = {
+        "apertus": ('I will check. <|tools_prefix|>[{"get_weather": {"city": "Paris"}}]<|tools_suffix|>', "get_weather", {"city": "Paris"}, "I will check."),
+        "deepseek_v32": ('ok <｜DSML｜function_calls>\n<｜DSML｜invoke name="get_weather">\n<｜DSML｜parameter name="location" string="true">Hangzhou</｜DSML｜parameter>\n'
+                         '<｜DSML｜parameter name="days" string="false">3</｜DSML｜parameter>\n</｜DSML｜invoke>\n</｜DSML｜function_calls>', "get_weather",
+                         {"location": "Hangzhou", "days": 3}, "ok"),
+        "deepseek_v4": ('<｜DSML｜tool_calls><｜DSML｜invoke name="f"><｜DSML｜parameter name="x" string="false">[1, 2]</｜DSML｜parameter></｜DSML｜invoke></｜DSML｜tool_calls>',
+                        "f", {"x": [1, 2]}, None),
+        "functiongemma": ('<start_function_call>call:set_timer{minutes:5,label:<escape>tea, green<escape>}<end_function_call>', "set_timer",
+                          {"minutes": 5, "label": "tea, green"}, None),
+        "gemma4": ('sure <|tool_call>call:lookup{q:<|"|>cats<|"|>,n:2}<tool_call|>', "lookup", {"q": "cats", "n": 2}, "sure"),
+        "gigachat3": ('thinking<|message_sep|>function call<|role_sep|>\n{"name": "sum", "arguments": {"a": 1, "b": 2}}', "sum", {"a": 1, "b": 2}, "thinking"),
+        "hy_v3": ('<tool_calls><tool_call>get_time<tool_sep><arg_key>tz</arg_key><arg_value>UTC</arg_value></tool_call></tool_calls>', "get_time", {"tz": "UTC"}, None),
+        "minicpm5xml": ('<think>hm</think>Let me see <function name="search"><param name="q"><![CDATA[a<b]]></param><param name="k">3</param></function>', "search",
+                        {"q": "a<b", "k": 3}, "Let me see"),
+        "openai": ('<|channel|>analysis<|message|>need weather<|end|><|start|>assistant<|channel|>commentary to=functions.get_weather <|constrain|>json<|message|>'
+                   '{"city": "Oslo"}<|call|>', "get_weather", {"city": "Oslo"}, None),
+        "poolside_v1": ('<tool_call>run\n<arg_key>cmd</arg_key>\n<arg_value>ls</arg_value>\n</tool_call>', "run", {"cmd": "ls"}, None),
+        "step3": ('x<｜tool_calls_begin｜><｜tool_call_begin｜>function<｜tool_sep｜><steptml:invoke name="add"><steptml:parameter name="a">1</steptml:parameter>'
+                  '<steptml:parameter name="b">two</steptml:parameter></steptml:invoke><｜tool_call_end｜><｜tool_calls_end｜>', "add", {"a": 1, "b": "two"}, "x"),
+        "step3p5": ('<tool_call>\n<function=f>\n<parameter=x>\n1\n</parameter>\n</function>\n</tool_call>', "f", {"x": 1}, None),
+        "cohere_command": ('<|START_RESPONSE|>one moment<|END_RESPONSE|><|START_ACTION|>[{"tool_call_id": "0", "tool_name": "search", "parameters": {"q": "x"}}]<|END_ACTION|>',
+                           "search", {"q": "x"}, "one moment"),
+        "granite4": ('<tool_call>{"name": "f", "arguments": {"a": 1}}</tool_call>', "f", {"a": 1}, None),
+    }
+    for name, (text, fn, args, content) in cases.items():
+        c, calls = get_tool_parser(name).extract(text)
+        assert len(calls) == 1 and calls[0].name == fn and json.loads(calls[0].arguments) == args, (name, calls)
+        assert c == content, (name, c)
+        assert get_tool_parser(name).extract("plain answer") == ("plain answer", [])
+    assert len(TOOL_PARSERS) >= 46

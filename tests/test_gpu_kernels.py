@@ -671,6 +671,22 @@ def test_gdn_chunked_prefill_matches_sequential_oracle(qlens, init):
     assert K().check_status() == 0
 
 
+@pytest.mark.parametrize("D", [64, 128, 256, 512])
+def test_merge_attn_states_kernel(D):
+    g = torch.Generator(device="cuda").manual_seed(D)
+    T, H = 37, 5
+    o1, o2 = torch.randn(T, H, D, device="cuda", generator=g).bfloat16(), torch.randn(T, H, D, device="cuda", generator=g).bfloat16()
+    l1, l2 = torch.randn(T, H, device="cuda", generator=g) * 5, torch.randn(T, H, device="cuda", generator=g) * 5
+    l1[0, 0] = float("-inf")            # an empty side contributes nothing
+    l1[1, 1] = l2[1, 1] = float("-inf")  # both empty: zeros, lse -inf-like is not required, only finiteness of the output
+    o, lse = K().merge_attn_states(o1, l1, o2, l2)
+    oe, le = ref.merge_attn_states(o1.cpu(), l1.cpu(), o2.cpu(), l2.cpu())
+    _close(o, oe, 2e-2, 2e-2, "merged output")
+    ok = torch.isfinite(le)
+    _close(lse.cpu()[ok], le[ok], 1e-3, 1e-3, "merged lse")
+    assert torch.equal(o[0, 0], o2[0, 0])
+
+
 @pytest.mark.parametrize("deepseek", [False, True])
 def test_router_matches_reference(deepseek):
     T, E, k = 77, 256, 8

@@ -75,15 +75,18 @@ def bench_throughput(a) -> dict:
     ea = _engine_args(a)
     llm = LLM(**ea.__dict__)
     vocab = llm.llm_engine.cfg.model_config.vocab_size
-    prompts = random_prompts(a.num_prompts, a.input_len, vocab, a.seed)
-    sp = SamplingParams(temperature=0.0, max_tokens=a.output_len, ignore_eos=True, detokenize=False)
+    from onecat_vllm.entrypoints.bench_datasets import build_dataset
+    rows = build_dataset(a, vocab, llm.get_tokenizer() if a.dataset_name not in ("random", "prefix_repetition") else None)
+    prompts = [r.prompt for r in rows]
+    sps = [SamplingParams(temperature=0.0, max_tokens=r.expected_output_len, ignore_eos=True, detokenize=False) for r in rows]
     t0 = time.perf_counter()
-    outs = llm.generate(prompts, sp)
+    outs = llm.generate(prompts, sps)
     dt = time.perf_counter() - t0
     n_out = sum(len(o.outputs[0].token_ids) for o in outs)
+    n_in = sum(len(o.prompt_token_ids or []) for o in outs) or sum(r.prompt_len for r in rows)
     llm.shutdown()
     return {"elapsed_s": dt, "requests_per_s": len(outs) / dt, "output_tokens_per_s": n_out / dt,
-            "total_tokens_per_s": (n_out + sum(len(p) for p in prompts)) / dt}
+            "total_tokens_per_s": (n_out + n_in) / dt, "dataset": a.dataset_name}
 
 
 def bench_latency(a) -> dict:
@@ -136,23 +139,29 @@ async def _bench_serve_async(a) -> dict:
     async with httpx.AsyncClient(timeout=None) as client:
         model = a.model_name or (await client.get(a.base_url + "/v1/models")).json()["data"][0]["id"]
         vocab = a.vocab_size
-        prompts = random_prompts(a.num_prompts, a.input_len, vocab, a.seed)
-        recs = [RequestRecord(len(p)) for p in prompts]
+        from onecat_vllm.entrypoints.bench_datasets import build_dataset
+        rows = build_dataset(a, vocab)
+        prompts = [r.prompt for r in rows]
+        recs = [RequestRecord(r.prompt_len) for r in rows]
         sem = asyncio.Semaphore(a.max_concurrency) if a.max_concurrency else None
         rng = random.Random(a.seed)
 
-        async def run(p, r):
+        async def run(p, r, n_out):
             if sem is None:
-                await _serve_one(client, a.base_url, model, p, a.output_len, r, a.api_key)
+                await _serve_one(client, a.base_url, model, p, n_out, r, a.api_key)
             else:
                 async with sem:
-                    await _serve_one(client, a.base_url, model, p, a.output_len, r, a.api_key)
+                    await _serve_one(client, a.base_url, model, p, n_out, r, a.api_key)
 
         t0 = time.perf_counter()
         tasks = []
-        for p, r in zip(prompts, recs):
-            tasks.append(asyncio.create_task(run(p, r)))
-            if a.request_rate and a.request_rate != float("inf"):
+        replay = getattr(a, "replay_arrivals", False)
+        for row, r in zip(rows, recs):
+            if replay and row.arrival_s is not None:
+                # a trace row is sent at its logged offset from the start of the run
+                await asyncio.sleep(max(row.arrival_s - (time.perf_counter() - t0), 0.0))
+            tasks.append(asyncio.create_task(run(row.prompt, r, row.expected_output_len)))
+            if not replay and a.request_rate and a.request_rate != float("inf"):
                 await asyncio.sleep(rng.expovariate(a.request_rate))
         await asyncio.gather(*tasks)
         dur = time.perf_counter() - t0
@@ -181,6 +190,7 @@ def main(argv=None) -> None:
     p = argparse.ArgumentParser("bench")
     sub = p.add_subparsers(dest="mode", required=True)
     from onecat_vllm.config import EngineArgs
+    from onecat_vllm.entrypoints.bench_datasets import add_dataset_args
     for name in ("throughput", "latency", "startup"):
         sp = sub.add_parser(name)
         EngineArgs.add_cli_args(sp)
@@ -190,6 +200,7 @@ def main(argv=None) -> None:
         sp.add_argument("--batch-size", type=int, default=8)
         sp.add_argument("--num-iters", type=int, default=5)
         sp.add_argument("--num-iters-warmup", type=int, default=2)
+        add_dataset_args(sp)
     sv = sub.add_parser("serve")
     sv.add_argument("--base-url", default="http://127.0.0.1:8000")
     sv.add_argument("--model-name", default=None)
@@ -202,7 +213,13 @@ def main(argv=None) -> None:
     sv.add_argument("--request-rate", type=float, default=float("inf"))
     sv.add_argument("--goodput", nargs="*", default=None, help="SLOs as ttft:MS tpot:MS e2el:MS")
     sv.add_argument("--seed", type=int, default=0)
+    sv.add_argument("--save-result", default=None, help="also write the metrics to this JSON file")
+    add_dataset_args(sv)
+    from onecat_vllm.entrypoints import bench_sweep
+    bench_sweep.add_cli(sub)
     a = p.parse_args(argv)
+    if a.mode == "sweep":
+        return bench_sweep.main(a)
     if a.mode == "throughput":
         res = bench_throughput(a)
     elif a.mode == "latency":
@@ -211,6 +228,9 @@ def main(argv=None) -> None:
         res = bench_startup(a)
     else:
         res = asyncio.run(_bench_serve_async(a))
+    if getattr(a, "save_result", None):
+        with open(a.save_result, "w") as f:
+            json.dump(res, f)
     print(json.dumps(res, indent=1))
 
 

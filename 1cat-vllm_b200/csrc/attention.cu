@@ -71,6 +71,8 @@ __device__ __forceinline__ void widen_fp8x16(const uint4& in, uint4& lo, uint4& 
 
 template <int D, int MODE, int MB, bool KV8>
 __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring (a fourth stage of byte tiles measured no faster)
   constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
   constexpr int NB2 = (MODE == 0) ? 4 : 1;      // 16-key groups per warp per tile
@@ -402,6 +404,8 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
 // merges split-KV partials: one warp per (token, head)
 template <int D>
 __global__ void attn_combine_kernel(const AttnParams p) {
+  pdl_trigger();
+  pdl_wait();
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
   const int rows = p.T * p.Hq;
   if (warp >= rows) return;
@@ -438,10 +442,10 @@ int launch_one(const AttnParams& p, cudaStream_t st) {
   }
   dim3 grid(MODE == 0 ? p.num_q_tiles : p.R, p.Hkv, MODE == 0 ? 1 : p.splits);
   if (grid.x == 0) return 0;
-  attn_kernel<D, MODE, MB, KV8><<<grid, 128, smem, st>>>(p);
+  launch_k(attn_kernel<D, MODE, MB, KV8>, grid, dim3(128), (size_t)smem, st, true, p);
   if (MODE == 1 && p.splits > 1) {
     int rows = p.T * p.Hq;
-    attn_combine_kernel<D><<<(rows * 32 + 255) / 256, 256, 0, st>>>(p);
+    launch_k(attn_combine_kernel<D>, dim3((rows * 32 + 255) / 256), dim3(256), 0, st, true, p);
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -5;
 }

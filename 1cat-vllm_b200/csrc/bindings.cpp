@@ -450,6 +450,28 @@ std::tuple<torch::Tensor, torch::Tensor> route(torch::Tensor logits, c10::option
   return {w, ids};
 }
 
+// One grouped GEMM of the MoE chain over `rows` slot rows, driven by a device-built work list.
+static void moe_gemm_run(const torch::Tensor& in, const torch::Tensor& w, const c10::optional<torch::Tensor>& sz, int n_rows, torch::Tensor& out, int Kd,
+                         int N, int n_out, int epi, const int4* wl, const int* cnt, int cap, int rows, int tn, int wkind, int group_ktiles,
+                         torch::Tensor& counters) {
+  oc::GemmParams p{};
+  p.T = rows; p.K = Kd; p.N = N; p.n_rows = n_rows; p.n_out = n_out; p.epi = epi; p.group_ktiles = wkind == 0 ? 1 : group_ktiles;
+  p.wkind = wkind;
+  if (wkind != 0) {
+    p.w4 = (const uint8_t*)w.data_ptr();
+    p.w4_sz = (const uint32_t*)sz->data_ptr();
+    p.n_pad = n_rows;
+  }
+  p.out = (__nv_bfloat16*)out.data_ptr(); p.ldo = (int)out.stride(0);
+  p.ws = nullptr; p.counters = (int*)counters.data_ptr(); p.max_counters = 0;
+  p.work = wl; p.work_count = cnt; p.work_capacity = cap;
+  p.tn = tn; p.num_t_tiles = 1; p.num_n_tiles = 1; p.splits = 1; p.ktiles_per_split = Kd / 64;
+  oc::gemm_plan_stages(p, wkind != 0);
+  int r = oc::gemm_launch(p, in.data_ptr(), (int)in.stride(0), wkind == 0 ? w.data_ptr() : nullptr, wkind == 0 ? (int)w.stride(0) : 0, sm_count(),
+                          cur_stream());
+  TORCH_CHECK(r == 0, "grouped gemm launch failed: ", r);
+}
+
 // Routed-expert path of one MoE layer: slots -> grouped GEMM (w13, SiLU*mul) -> grouped GEMM (w2) -> weighted combine.
 // w13: bf16 [E_local * 2I, H] with each expert's gate|up rows interleaved in blocks of 16; w2: bf16 [E_local * H, I].
 // With `wkind` > 0 the expert weights are packed tiles (see gemm) and w13_sz / w2_sz their scale tables; I2 and group_ktiles
@@ -505,27 +527,75 @@ torch::Tensor fused_moe(torch::Tensor x, torch::Tensor w13, torch::Tensor w2, to
   TORCH_CHECK(rc == 0, "moe prepare failed: ", rc);
   auto run = [&](const torch::Tensor& in, const torch::Tensor& w, const c10::optional<torch::Tensor>& sz, int n_rows, torch::Tensor& out, int Kd, int N,
                  int n_out, int epi, const int4* wl, const int* cnt, int cap) {
-    oc::GemmParams p{};
-    p.T = n_pairs; p.K = Kd; p.N = N; p.n_rows = n_rows; p.n_out = n_out; p.epi = epi; p.group_ktiles = wkind == 0 ? 1 : (int)group_ktiles;
-    p.wkind = (int)wkind;
-    if (wkind != 0) {
-      p.w4 = (const uint8_t*)w.data_ptr();
-      p.w4_sz = (const uint32_t*)sz->data_ptr();
-      p.n_pad = n_rows;
-    }
-    p.out = (__nv_bfloat16*)out.data_ptr(); p.ldo = (int)out.stride(0);
-    p.ws = nullptr; p.counters = (int*)counters.data_ptr(); p.max_counters = 0;
-    p.work = wl; p.work_count = cnt; p.work_capacity = cap;
-    p.tn = tn; p.num_t_tiles = 1; p.num_n_tiles = 1; p.splits = 1; p.ktiles_per_split = Kd / 64;
-    oc::gemm_plan_stages(p, wkind != 0);
-    int r = oc::gemm_launch(p, in.data_ptr(), (int)in.stride(0), wkind == 0 ? w.data_ptr() : nullptr, wkind == 0 ? (int)w.stride(0) : 0, sm_count(),
-                            cur_stream());
-    TORCH_CHECK(r == 0, "grouped gemm launch failed: ", r);
+    moe_gemm_run(in, w, sz, n_rows, out, Kd, N, n_out, epi, wl, cnt, cap, n_pairs, tn, (int)wkind, (int)group_ktiles, counters);
   };
   run(xs, w13, w13_sz, (int)E_local * I2, a1, H, I2, I, oc::EPI_SILU_MUL, pp.work1, pp.work_count, max_tt * n1);
   run(a1, w2, w2_sz, (int)E_local * H, a2, I, H, H, oc::EPI_STORE, pp.work2, pp.work_count + 1, max_tt * n2);
   rc = oc::moe_combine_launch(a2.data_ptr(), slot_of, topk_w.data_ptr<float>(), y.data_ptr(), T, k, H, cur_stream());
   TORCH_CHECK(rc == 0, "moe combine failed");
+  return y;
+}
+
+// Expert-parallel MoE with the token exchange over peer memory (see ep_a2a.cu): `x`, `topk_w`, `topk_ids` describe this rank's
+// own tokens (expert ids are global); `slabs` are every rank's exchange slab and `offs` the six byte offsets of its areas
+// (counts, flags, recv rows, recv meta, returned rows, gather); `state` is this rank's int32 scratch [8 + 2 E]. Returns this
+// rank's combined rows; with `gather` every rank's rows are also stored into every slab's gather area at row `t_off`.
+torch::Tensor fused_moe_a2a(torch::Tensor x, torch::Tensor w13, torch::Tensor w2, torch::Tensor topk_w, torch::Tensor topk_ids, int64_t E_local,
+                            torch::Tensor counters, int64_t wkind, c10::optional<torch::Tensor> w13_sz, c10::optional<torch::Tensor> w2_sz,
+                            int64_t I2_packed, int64_t group_ktiles, std::vector<int64_t> slabs, std::vector<int64_t> offs, torch::Tensor state,
+                            int64_t rank, int64_t cap, int64_t ret_rows, int64_t T_total, int64_t t_off, bool gather, int64_t wait_ns) {
+  check_bf16(x, "x");
+  const int n = (int)slabs.size();
+  TORCH_CHECK(n >= 2 && n <= oc::kMaxRanks && offs.size() == 6 && rank >= 0 && rank < n, "bad rank tables");
+  TORCH_CHECK(x.dim() == 2 && (x.size(0) == 0 || x.stride(1) == 1) && w13.is_contiguous() && w2.is_contiguous(), "bad layouts");
+  TORCH_CHECK(topk_ids.scalar_type() == torch::kInt32 && topk_ids.is_contiguous() && topk_w.scalar_type() == torch::kFloat32 && topk_w.is_contiguous(),
+              "routing tensors must be contiguous int32 ids / fp32 weights");
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int T = (int)x.size(0), H = (int)x.size(1), k = (int)topk_ids.size(1), E = (int)E_local * n;
+  const int I2 = wkind == 0 ? (int)(w13.size(0) / E_local) : (int)I2_packed, I = I2 / 2;
+  TORCH_CHECK(I2 % 128 == 0 && H % 128 == 0 && I % 64 == 0, "expert dims must be multiples of 128 (rows) and 64 (k)");
+  TORCH_CHECK((int64_t)T * k <= ret_rows && t_off + T <= T_total && cap > 0, "tokens exceed the exchange slab");
+  TORCH_CHECK(state.scalar_type() == torch::kInt32 && state.numel() >= 8 + 2 * E, "exchange state too small");
+  if (wkind != 0) TORCH_CHECK(w13_sz.has_value() && w2_sz.has_value() && I2_packed > 0 && group_ktiles >= 1, "packed experts need scale tables");
+  auto y = torch::empty({T, H}, x.options());
+  const int avg = (int)((T_total * k + E - 1) / E);
+  const int tn = avg <= 32 ? 32 : avg <= 64 ? 64 : (avg <= 128 || wkind != 0) ? 128 : 256;
+  const int n1 = I2 / 128, n2 = H / 128;
+  const int max_tt = ((int)cap + tn - 1) / tn + (int)E_local;
+  auto iopt = x.options().dtype(torch::kInt32);
+  auto meta = torch::empty({3 * E_local + 8}, iopt);
+  auto work = torch::empty({(int64_t)max_tt * (n1 + n2) * 4}, iopt);
+  auto a1 = torch::empty({cap, I}, x.options());
+  auto a2 = torch::empty({cap, H}, x.options());
+  int* mp = meta.data_ptr<int>();
+  oc::MoePlanParams pp{};
+  pp.counts = mp; pp.offsets = mp + E_local; pp.cursor = mp + 2 * E_local + 1; pp.total_slots = mp + 3 * E_local + 1; pp.work_count = mp + 3 * E_local + 2;
+  pp.work1 = (int4*)work.data_ptr<int>();
+  pp.work2 = pp.work1 + (size_t)max_tt * n1;
+  pp.E = (int)E_local; pp.tn = tn; pp.n1 = n1; pp.n2 = n2;
+  oc::EpParams ep{};
+  for (int i = 0; i < n; ++i) ep.slab[i] = (char*)(uintptr_t)slabs[i];
+  ep.off_counts = (size_t)offs[0]; ep.off_flags = (size_t)offs[1]; ep.off_recv_x = (size_t)offs[2]; ep.off_recv_meta = (size_t)offs[3];
+  ep.off_ret = (size_t)offs[4]; ep.off_gather = (size_t)offs[5];
+  ep.ids = topk_ids.data_ptr<int>();
+  ep.x = (const __nv_bfloat16*)x.data_ptr(); ep.ldx = T ? x.stride(0) : H;
+  int* sp = state.data_ptr<int>();
+  ep.seq = sp; ep.done = sp + 1; ep.send_base = sp + 8; ep.cursor = sp + 8 + E;
+  ep.counts_local = pp.counts; ep.total_slots = pp.total_slots;
+  ep.n = n; ep.me = (int)rank; ep.E = E; ep.E_local = (int)E_local; ep.k = k; ep.H = H; ep.T = T; ep.n_pairs = T * k; ep.cap = (int)cap;
+  ep.ret_rows = (int)ret_rows; ep.gather = gather ? 1 : 0; ep.t_off = (int)t_off; ep.wait_ns = (unsigned long long)wait_ns;
+  auto st = cur_stream();
+  int rc = oc::ep_count_exchange_launch(ep, st);
+  TORCH_CHECK(rc == 0, "expert-parallel count exchange failed: ", rc);
+  TORCH_CHECK(oc::moe_plan_launch(pp, st) == 0, "moe plan failed");
+  TORCH_CHECK(oc::ep_dispatch_launch(ep, sm_count(), st) == 0, "expert-parallel dispatch failed");
+  auto xs = torch::from_blob(ep.slab[rank] + ep.off_recv_x, {cap, (int64_t)H}, x.options());
+  moe_gemm_run(xs, w13, w13_sz, (int)E_local * I2, a1, H, I2, I, oc::EPI_SILU_MUL, pp.work1, pp.work_count, max_tt * n1, (int)cap, tn, (int)wkind,
+               (int)group_ktiles, counters);
+  moe_gemm_run(a1, w2, w2_sz, (int)E_local * H, a2, I, H, H, oc::EPI_STORE, pp.work2, pp.work_count + 1, max_tt * n2, (int)cap, tn, (int)wkind,
+               (int)group_ktiles, counters);
+  TORCH_CHECK(oc::ep_return_launch(ep, a2.data_ptr(), sm_count(), st) == 0, "expert-parallel return failed");
+  TORCH_CHECK(oc::ep_combine_launch(ep, topk_w.data_ptr<float>(), y.data_ptr(), sm_count(), st) == 0, "expert-parallel combine failed");
   return y;
 }
 
@@ -560,7 +630,7 @@ torch::Tensor mla_decode(torch::Tensor q_abs, torch::Tensor q_rope, torch::Tenso
 
 int64_t read_status(bool clear) {
   return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) | oc::attention_tc_read_status(clear) |
-                   oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear) | oc::moe_read_status(clear) | oc::mla_read_status(clear));
+                   oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear) | oc::moe_read_status(clear) | oc::mla_read_status(clear) | oc::ep_read_status(clear));
 }
 
 // ---- symmetric slab + peer-memory reductions
@@ -645,6 +715,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("read_status", &read_status);
   m.def("mla_decode", &mla_decode);
   m.def("fused_moe", &fused_moe);
+  m.def("fused_moe_a2a", &fused_moe_a2a);
   m.def("rejection_sample", &rejection_sample);
   m.def("sample", &sample);
   m.def("route", &route);

@@ -61,6 +61,7 @@ __global__ void __launch_bounds__(256) tp_reduce_norm_kernel(const CommParams p)
   __shared__ int s_seq, s_ok;
   const int b = blockIdx.x;
   const int tp = p.tp, me = p.rank;
+  pdl_trigger();
   // ---- phase 0: tell every rank that this rank's partial sums are complete (the producing GEMM ran earlier on this stream)
   if (threadIdx.x == 0) {
     int seq = p.seq_local[b] + 1;
@@ -195,6 +196,8 @@ template <int VEC_ITERS>
 __global__ void __launch_bounds__(256) tp_lamport_kernel(const CommParams p) {
   __shared__ float red[9];
   __shared__ int s_buf;
+  pdl_trigger();
+  pdl_wait();
   const int tp = p.tp, me = p.rank;
   if (threadIdx.x == 0) s_buf = *reinterpret_cast<volatile int*>(p.lam_ctr);
   __syncthreads();
@@ -314,10 +317,10 @@ int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st) {
   if (p.mode == COMM_LAMPORT) {
     if (p.lam_ctr == nullptr || p.lam_buf_stride <= 0 || (size_t)p.T * p.H > (size_t)p.lam_src_stride) return -3;
     switch (iters) {
-      case 1: tp_lamport_kernel<1><<<grid, 256, 0, st>>>(p); break;
-      case 2: tp_lamport_kernel<2><<<grid, 256, 0, st>>>(p); break;
-      case 3: tp_lamport_kernel<3><<<grid, 256, 0, st>>>(p); break;
-      default: tp_lamport_kernel<4><<<grid, 256, 0, st>>>(p); break;
+      case 1: launch_k(tp_lamport_kernel<1>, dim3(grid), dim3(256), 0, st, true, p); break;
+      case 2: launch_k(tp_lamport_kernel<2>, dim3(grid), dim3(256), 0, st, true, p); break;
+      case 3: launch_k(tp_lamport_kernel<3>, dim3(grid), dim3(256), 0, st, true, p); break;
+      default: launch_k(tp_lamport_kernel<4>, dim3(grid), dim3(256), 0, st, true, p); break;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }

@@ -32,6 +32,33 @@ struct CommParams {
   int lam_pushed;
 };
 
+// Expert-parallel token exchange (see ep_a2a.cu). The slab of every rank has the same layout (byte offsets below).
+struct EpParams {
+  char* slab[kMaxRanks];
+  size_t off_counts;     // int32 [ranks][E]      pairs routed by each source rank to each expert
+  size_t off_flags;      // int32 [4 stages][kMaxRanks]
+  size_t off_recv_x;     // bf16  [cap][H]        rows dispatched to this rank, expert-major
+  size_t off_recv_meta;  // int32 [cap]           (source rank << 24) | pair index at the source
+  size_t off_ret;        // bf16  [ret_rows][H]   expert outputs returned to this rank, by pair
+  size_t off_gather;     // bf16  [T_total][H]    combined rows of every rank (when gather != 0)
+  const int* ids;        // [T][k] global expert ids of this rank's tokens
+  const __nv_bfloat16* x;
+  long long ldx;
+  int* seq;              // [1] sequence number of the exchange in flight (device memory, advanced by the first kernel)
+  int* done;             // [3] CTA completion counters
+  int* send_base;        // [E]
+  int* cursor;           // [E]
+  int* counts_local;     // [E_local] rows received per local expert (input of the GEMM work-list builder)
+  const int* total_slots;  // [1] rows received in total (written by the work-list builder)
+  int n, me, E, E_local, k, H, T, n_pairs, cap, ret_rows, gather, t_off;
+  unsigned long long wait_ns;
+};
+int ep_count_exchange_launch(const EpParams& p, cudaStream_t st);
+int ep_dispatch_launch(const EpParams& p, int sms, cudaStream_t st);
+int ep_return_launch(const EpParams& p, const void* a2, int sms, cudaStream_t st);
+int ep_combine_launch(const EpParams& p, const float* w, void* y, int sms, cudaStream_t st);
+unsigned int ep_read_status(bool clear);
+
 int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st);
 int comm_alloc(size_t bytes, void** ptr);
 int comm_free(void* ptr);

@@ -6,6 +6,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 namespace oc {
 
@@ -213,6 +214,42 @@ static inline int current_device_slot() {
   int d = 0;
   if (cudaGetDevice(&d) != cudaSuccess || d < 0 || d >= kMaxDevices) d = 0;
   return d;
+}
+
+// ---- programmatic dependent launch ----------------------------------------------------------------------------
+// A kernel launched with the programmatic-serialisation attribute may start while its predecessor in the stream still runs:
+// its prologue (barrier set-up, TMEM allocation, descriptor prefetch, loads of weights that no kernel writes) overlaps the
+// predecessor's tail. pdl_wait() blocks the calling thread until every prerequisite grid has completed and its memory is visible;
+// a thread must pass it before it reads anything an earlier kernel wrote or writes anything an earlier kernel may still read.
+// pdl_trigger() lets the next kernel in the stream begin launching once every CTA of this grid has issued it. Both are no-ops
+// for launches without the attribute.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ONECAT_PDL");
+    v = (e == nullptr || atoi(e) != 0) ? 1 : 0;
+  }
+  return v != 0;
+}
+
+// Launch with (pdl = true and ONECAT_PDL != 0) or without the programmatic-serialisation attribute. Only kernels that call
+// pdl_wait() before their first dependent access may pass pdl = true.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = (pdl && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 
 // Host-side reader for this translation unit's status word.

@@ -30,6 +30,8 @@ __global__ void __launch_bounds__(256) rms_norm_kernel(const __nv_bfloat16* __re
                                                        const __nv_bfloat16* __restrict__ w, __nv_bfloat16* __restrict__ y,
                                                        __nv_bfloat16* __restrict__ res_out, int H, int ldx, float eps, int gemma) {
   __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
   const size_t t = blockIdx.x;
   const __nv_bfloat16* xr = x + t * ldx;
   float v[VEC_ITERS][8];
@@ -128,6 +130,8 @@ __global__ void silu_and_mul_kernel(const __nv_bfloat16* __restrict__ x, __nv_bf
 // k and v rows copied into the paged cache [block][2][Hkv][bs][D] at slot_mapping[token].
 __global__ void rope_cache_kernel(RopeCacheParams p) {
   extern __shared__ float sh[];
+  pdl_trigger();
+  pdl_wait();
   const int wpb = blockDim.x >> 5;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads = p.Hq + 2 * p.Hkv;
@@ -194,6 +198,8 @@ __global__ void rope_cache_kernel(RopeCacheParams p) {
 template <typename T>
 __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, long long* __restrict__ out, int V, long long ld) {
   __shared__ float sv[32];
+  pdl_trigger();
+  pdl_wait();
   __shared__ int si[32];
   const T* r = x + (size_t)blockIdx.x * ld;
   float best = -INFINITY;
@@ -234,10 +240,10 @@ int rms_norm_launch(const void* x, const void* res_in, const void* w, void* y, v
   int iters = (H + 2047) / 2048;
   if (T == 0) return 0;
   switch (iters) {
-    case 1: rms_norm_kernel<1><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
-    case 2: rms_norm_kernel<2><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
-    case 3: rms_norm_kernel<3><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
-    default: rms_norm_kernel<4><<<T, 256, 0, st>>>(xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    case 1: launch_k(rms_norm_kernel<1>, dim3(T), dim3(256), 0, st, true, xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    case 2: launch_k(rms_norm_kernel<2>, dim3(T), dim3(256), 0, st, true, xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    case 3: launch_k(rms_norm_kernel<3>, dim3(T), dim3(256), 0, st, true, xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
+    default: launch_k(rms_norm_kernel<4>, dim3(T), dim3(256), 0, st, true, xp, rp, wp, yp, rop, H, ldx, eps, gemma); break;
   }
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
@@ -264,7 +270,7 @@ int rope_cache_launch(const RopeCacheParams& p, cudaStream_t st) {
   if (p.D > 512 || p.rot > p.D || (p.rot & 1)) return -1;
   long long warps = (long long)p.T * (p.Hq + 2 * p.Hkv);
   int wpb = 8;
-  rope_cache_kernel<<<(unsigned)((warps + wpb - 1) / wpb), wpb * 32, wpb * p.D * sizeof(float), st>>>(p);
+  launch_k(rope_cache_kernel, dim3((unsigned)((warps + wpb - 1) / wpb)), dim3(wpb * 32), wpb * p.D * sizeof(float), st, true, p);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
@@ -300,8 +306,8 @@ int merge_attn_states_launch(const void* o1, const float* lse1, const void* o2, 
 
 int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st) {
   if (B == 0) return 0;
-  if (is_fp32) argmax_kernel<float><<<B, 1024, 0, st>>>((const float*)x, out, V, ld);
-  else argmax_kernel<__nv_bfloat16><<<B, 1024, 0, st>>>((const __nv_bfloat16*)x, out, V, ld);
+  if (is_fp32) launch_k(argmax_kernel<float>, dim3(B), dim3(1024), 0, st, true, (const float*)x, out, V, ld);
+  else launch_k(argmax_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, st, true, (const __nv_bfloat16*)x, out, V, ld);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

@@ -202,6 +202,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   // Work items. Dense: (n tile, token tile, k split) enumerated arithmetically. Grouped (mixture-of-experts): a device-built list of
   // {weight row tile in the stacked expert matrix, first token row, number of valid rows, output column base}; its length is
   // read from device memory, so the launch needs no host knowledge of how tokens were routed.
+  // Programmatic dependent launch: everything above overlaps the previous kernel's tail. With packed weights and arithmetic work
+  // items the weight producer, the dequantisation warps and the MMA warp touch no memory that another kernel writes (weights,
+  // shared memory, TMEM), so they run ahead and fill the rings; only the activation producer and the epilogue warps wait.
+  // A device-built work list, or bf16 weights loaded by the same thread as the activations, makes every thread wait here.
+  pdl_trigger();
+  const bool pdl_roles = WKIND >= 1 && p.work == nullptr;
+  if (!pdl_roles) pdl_wait();
   const int total_work = p.work != nullptr ? *p.work_count : p.num_n_tiles * p.num_t_tiles * p.splits;
   const int ktiles = p.K / BK;
   auto decode = [&](int w, int& nt, int& tt, int& sp_, int& k0, int& k1) {
@@ -384,6 +391,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
+      if (pdl_roles) pdl_wait();
       Ring st;
       bool ok = true;
       const uint32_t xs = (uint32_t)tn * 128;  // one token sub-tile
@@ -510,6 +518,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else if (warp < R::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
     if (WKIND >= 1) {
+      if (R::kDqDrains && pdl_roles) pdl_wait();  // a group that also drains accumulators writes global memory
       const int r = (warp & 3) * 32 + lane;  // weight row = TMEM lane this warp may write
       const int grp = (warp - 2) >> 2;       // 0: even stages of the CTA's sequence, 1: odd ones (one group when SMALL)
       uint32_t seq = 0;
@@ -603,6 +612,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
   } else if (!R::kDqDrains) {
     // ------------------------------------------------------------------ epilogue warps
+    if (pdl_roles) pdl_wait();   // outputs, split-K partials and counters may still be in use by the previous kernel
     uint32_t tile_i = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) ok = epilogue_item(w, tile_i);
@@ -805,8 +815,7 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
         configured[dev][p.wkind][sm] = true;
       }
     }
-    kernel<<<grid, threads, smem, stream>>>(tmX, tmW, p);
-    return 0;
+    return launch_k(kernel, dim3(grid), dim3(threads), (size_t)smem, stream, true, tmX, tmW, p) == cudaSuccess ? 0 : -10;
   };
   int rc = 0;
   switch (p.wkind * 2 + sm) {

@@ -112,6 +112,7 @@ struct MoePlanParams {
 };
 int moe_prepare_launch(const MoePlanParams& p, const int* ids, int n_pairs, int k, int e_off, int* slot_of, const void* x, long long ldx,
                        void* xs, int H, cudaStream_t st);
+int moe_plan_launch(const MoePlanParams& p, cudaStream_t st);
 int moe_combine_launch(const void* a2, const int* slot_of, const float* w, void* y, int T, int k, int H, cudaStream_t st);
 unsigned int moe_read_status(bool clear);
 

@@ -110,6 +110,13 @@ int moe_prepare_launch(const MoePlanParams& p, const int* ids, int n_pairs, int 
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Work lists only, from counts that are already on the device (expert-parallel exchange: the rows arrive in slot order).
+int moe_plan_launch(const MoePlanParams& p, cudaStream_t st) {
+  if (p.E > 1024) return -1;
+  moe_plan_kernel<<<1, 1024, 0, st>>>(p);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 int moe_combine_launch(const void* a2, const int* slot_of, const float* w, void* y, int T, int k, int H, cudaStream_t st) {
   if (T == 0) return 0;
   if (H % 8) return -1;

@@ -38,6 +38,12 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
     "ONECAT_TP_ONESHOT": _s("ONECAT_TP_ONESHOT", "lamport"),  # decode-sized reductions: "lamport" (data is its own flag) | "flags"
     "ONECAT_TP_PUSH": _s("ONECAT_TP_PUSH", "auto"),  # GEMM epilogue pushes partial tiles to peers: auto | always | never
+    # expert parallelism: "reduce" = every rank runs its experts over all tokens and the partial sums ride the TP reduction;
+    # "a2a" = each rank routes a slice of the tokens and rows are exchanged with the expert owners (peer-memory kernels, or
+    # torch.distributed all_to_all with ONECAT_EP_A2A=torch) for batches of at least ONECAT_EP_A2A_MIN_TOKENS tokens
+    "ONECAT_EP_COMM": _s("ONECAT_EP_COMM", "reduce"),
+    "ONECAT_EP_A2A": _s("ONECAT_EP_A2A", "peer"),
+    "ONECAT_EP_A2A_MIN_TOKENS": _i("ONECAT_EP_A2A_MIN_TOKENS", 0),
     "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),
     "ONECAT_USE_CUDA_GRAPH": _b("ONECAT_USE_CUDA_GRAPH", True),
     "ONECAT_COMPUTE_NANS_IN_LOGITS": _b("ONECAT_COMPUTE_NANS_IN_LOGITS", False),

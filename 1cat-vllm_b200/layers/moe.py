@@ -154,9 +154,31 @@ class SparseMoeBlock(nn.Module):
                                     c.scoring_func, c.norm_topk_prob, c.routed_scaling_factor)
         return ref.topk_softmax(logits, c.num_experts_per_tok, c.norm_topk_prob)
 
+    def _forward_a2a(self, x, mgr):
+        """Token-exchange expert parallelism on a replicated batch: this rank routes its slice of the rows, the manager returns
+        every rank's finished rows; rank 0 alone adds them to its partial sum so that the reduction that follows counts them once."""
+        from onecat_vllm.parallel.all2all import token_slice
+        st = get_state()
+        T = x.shape[0]
+        lo, hi = token_slice(T, st.ep_size, st.ep_rank)
+        xl = x[lo:hi]
+        if hi > lo:
+            w, ids = self.route(xl)
+        else:
+            k = self.cfg.num_experts_per_tok
+            w, ids = x.new_zeros(0, k, dtype=torch.float32), torch.zeros(0, k, dtype=torch.int32, device=x.device)
+        y = mgr.moe(self.experts, xl, w.to(torch.float32), ids, t_off=lo, T_total=T, gather=True)
+        return y.clone() if st.ep_rank == 0 else torch.zeros_like(x)
+
     def forward(self, x):
-        w, ids = self.route(x)
-        out = self.experts(x, w.to(torch.float32), ids)
+        from onecat_vllm import envs
+        mgr = get_state().ep_a2a
+        if mgr is not None and self.experts.ep and x.shape[0] >= envs.ONECAT_EP_A2A_MIN_TOKENS and \
+                (not x.is_cuda or self.experts.kernel_state is not None):
+            out = self._forward_a2a(x, mgr)
+        else:
+            w, ids = self.route(x)
+            out = self.experts(x, w.to(torch.float32), ids)
         if self.shared_expert is not None:
             s = self.shared_expert(x)
             if self.cfg.shared_expert_gate:

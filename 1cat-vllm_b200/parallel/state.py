@@ -33,6 +33,7 @@ class ParallelState:
     cpu_group: Optional[object] = None
     tp_comm: str = "fused"
     fused: Optional[object] = None  # onecat_vllm.parallel.fused.FusedTP once the symmetric heap exists
+    ep_a2a: Optional[object] = None  # onecat_vllm.parallel.all2all manager when experts exchange tokens instead of partial sums
 
     @property
     def is_first_pp(self) -> bool:
@@ -112,11 +113,12 @@ def init_distributed(rank: int, world_size: int, tp: int, pp: int = 1, backend: 
 
 def destroy_distributed() -> None:
     global _STATE
-    if _STATE.fused is not None:
-        try:
-            _STATE.fused.close()
-        except Exception:
-            pass
+    for mgr in (_STATE.ep_a2a, _STATE.fused):
+        if mgr is not None:
+            try:
+                mgr.close()
+            except Exception:
+                pass
     if dist.is_initialized():
         try:
             if torch.cuda.is_available() and dist.get_backend() == "nccl":

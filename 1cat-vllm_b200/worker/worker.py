@@ -47,6 +47,10 @@ class Worker:
         if self.cfg.device == "cuda" and pc.tensor_parallel_size > 1 and pc.tp_comm == "fused":
             from onecat_vllm.parallel.fused import FusedTP
             ps.get_state().fused = FusedTP.create(self.cfg, self.device)
+        from onecat_vllm import envs
+        if pc.enable_expert_parallel and pc.tensor_parallel_size > 1 and envs.ONECAT_EP_COMM == "a2a" and self.cfg.model_config.num_experts:
+            from onecat_vllm.parallel import all2all
+            ps.get_state().ep_a2a = all2all.create(self.cfg, self.device)
         self.runner = ModelRunner(self.cfg, self.device)
 
     def load_model(self) -> None:

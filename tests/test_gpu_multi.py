@@ -157,6 +157,103 @@ def test_fused_reduce_norm(world, oneshot):
     _spawn(_fused_worker, world, oneshot)
 
 
+def _a2a_worker(rank, world, port, q, qmethod="none"):
+    """Expert-parallel MoE by token exchange over peer memory: every rank routes a slice of the batch; the gathered result must
+    match the single-process expert oracle over all experts, eagerly and when a captured exchange is replayed."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.ops import ref
+    from onecat_vllm.parallel.all2all import PeerAll2All, TorchAll2All, token_slice
+    dev = torch.device("cuda", rank)
+    E, k, H, I, tmax = 8 * world, 4, 256, 128, 512
+    El = E // world
+    g = torch.Generator().manual_seed(1)
+    w13 = (torch.randn(E, 2 * I, H, generator=g) * 0.05).bfloat16()
+    w2 = (torch.randn(E, H, I, generator=g) * 0.05).bfloat16()
+
+    class Layer:
+        pass
+    layer = Layer()
+    layer.qmethod, layer.block, layer.E_local, layer.e_off, layer._dq, layer.kernel_state = "none", None, El, rank * El, None, None
+    layer.w13 = torch.nn.Parameter(w13[rank * El:(rank + 1) * El].to(dev), requires_grad=False)
+    layer.w2 = torch.nn.Parameter(w2[rank * El:(rank + 1) * El].to(dev), requires_grad=False)
+    layer.dequantized = lambda: (layer.w13, layer.w2)
+    K.prepare_moe(layer)
+    mgr = PeerAll2All(world, rank, dev, tmax, H, E, k)
+    ok, msgs = True, []
+    w13d, w2d = w13.to(dev), w2.to(dev)
+
+    def batch(T, seed):
+        gg = torch.Generator().manual_seed(seed)
+        x = (torch.randn(T, H, generator=gg)).bfloat16().to(dev)
+        if seed % 3 == 0:   # skewed routing: most pairs go to the experts of one rank
+            logits = torch.randn(T, E, generator=gg) + torch.cat([torch.full((El,), 4.0), torch.zeros(E - El)])
+        else:
+            logits = torch.randn(T, E, generator=gg)
+        w, ids = torch.topk(torch.softmax(logits, -1), k, dim=-1)
+        return x, (w / w.sum(-1, keepdim=True)).to(dev), ids.to(torch.int32).to(dev)
+
+    for it, T in enumerate((1, 3, 64, 200, 512, 64)):
+        x, w, ids = batch(T, it)
+        want = ref.fused_experts(x, w13d, w2d, w, ids.long())
+        lo, hi = token_slice(T, world, rank)
+        got = mgr.moe(layer, x[lo:hi], w[lo:hi], ids[lo:hi], t_off=lo, T_total=T, gather=True).clone()
+        torch.cuda.synchronize()
+        err = (got.float() - want.float()).abs().max().item()
+        scale = want.float().abs().max().item() + 1e-6
+        if err > 0.03 * scale + 0.02:
+            ok = False
+            msgs.append(f"T={T} err={err} scale={scale}")
+        all_got = [torch.empty_like(got) for _ in range(world)]
+        dist.all_gather(all_got, got)
+        if any(not torch.equal(all_got[0], t) for t in all_got):
+            ok = False
+            msgs.append(f"T={T}: ranks hold different gathered rows")
+    # a captured exchange replayed on fresh inputs: sequence numbers live on the device, so the graph needs no reset
+    T = 48
+    lo, hi = token_slice(T, world, rank)
+    xs, ws, idss = torch.zeros(hi - lo, H, device=dev, dtype=torch.bfloat16), torch.zeros(hi - lo, k, device=dev), torch.zeros(hi - lo, k, device=dev, dtype=torch.int32)
+    x, w, ids = batch(T, 100)
+    xs.copy_(x[lo:hi]); ws.copy_(w[lo:hi]); idss.copy_(ids[lo:hi])
+    mgr.moe(layer, xs, ws, idss, t_off=lo, T_total=T, gather=True)
+    torch.cuda.synchronize()
+    dist.barrier()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = mgr.moe(layer, xs, ws, idss, t_off=lo, T_total=T, gather=True)
+    for rep in range(6):
+        x, w, ids = batch(T, 200 + rep)
+        xs.copy_(x[lo:hi]); ws.copy_(w[lo:hi]); idss.copy_(ids[lo:hi])
+        graph.replay()
+        torch.cuda.synchronize()
+        want = ref.fused_experts(x, w13d, w2d, w, ids.long())
+        err = (out.float() - want.float()).abs().max().item()
+        if err > 0.03 * want.float().abs().max().item() + 0.02:
+            ok = False
+            msgs.append(f"replay {rep} err={err}")
+        dist.barrier()
+    st = K.check_status()
+    if st != 0:
+        ok = False
+        msgs.append(f"device status {st}")
+    del graph
+    torch.cuda.synchronize()
+    dist.barrier()
+    mgr.close()
+    q.put((rank, ok, msgs))
+    dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_exchange_over_peer_memory(world):
+    _need(world)
+    _spawn(_a2a_worker, world)
+
+
 CFG = dict(architectures=["Qwen3ForCausalLM"], hidden_size=1024, intermediate_size=2048, num_hidden_layers=3, num_attention_heads=8,
            num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
            tie_word_embeddings=False)

@@ -175,6 +175,7 @@ class ModelConfig:
     load_format: str = "auto"  # auto | safetensors | dummy
     tokenizer: Optional[str] = None
     enable_lora: bool = False  # build the model so that adapters can be applied (gate|up without the fused SiLU·mul epilogue)
+    enable_sleep_mode: bool = False  # weights and KV cache live in releasable device memory (utils/cumem.py)
     max_loras: int = 4
     max_lora_rank: int = 64
     hf_overrides: dict = field(default_factory=dict)
@@ -619,12 +620,13 @@ class EngineArgs:
     enable_lora: bool = False
     max_loras: int = 4
     max_lora_rank: int = 64
+    enable_sleep_mode: bool = False
     logits_processors: Optional[list] = None  # ["package.module:ClassName", ...]
 
     def create_engine_config(self) -> VllmConfig:
         dt = _DTYPES[self.dtype] if isinstance(self.dtype, str) else self.dtype
         over: dict[str, Any] = dict(seed=self.seed, load_format=self.load_format, tokenizer=self.tokenizer, enable_lora=self.enable_lora,
-                                    max_loras=self.max_loras, max_lora_rank=self.max_lora_rank,
+                                    enable_sleep_mode=self.enable_sleep_mode, max_loras=self.max_loras, max_lora_rank=self.max_lora_rank,
                                     logits_processors=tuple(self.logits_processors or ()))
         if self.hf_config is not None:
             hf = dict(self.hf_config)

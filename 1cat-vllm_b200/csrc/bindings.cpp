@@ -91,6 +91,7 @@ void gemm(torch::Tensor x, c10::optional<torch::Tensor> w, c10::optional<torch::
   if (force_splits > 0) {
     int ktiles = p.K / 64;
     p.splits = (int)force_splits;
+    p.cluster = 0;  // a forced split count takes the workspace path
     p.ktiles_per_split = (ktiles + p.splits - 1) / p.splits;
     TORCH_CHECK((p.splits - 1) * p.ktiles_per_split < ktiles, "too many splits for K");
     TORCH_CHECK((size_t)p.num_t_tiles * p.num_n_tiles * p.splits * 128 * p.tn * (p.nt_sub < 1 ? 1 : p.nt_sub) * 4 <= p.ws_bytes, "split-K workspace too small");

@@ -22,6 +22,7 @@
 // (reference: csrc/sm70_turbomind/ops/awq_sm70_gemm.cu:3161,3278; gemm_universal.h:238) and cuBLAS for dense layers.
 #include <stdlib.h>
 
+#include <map>
 #include <mutex>
 
 #include "common.cuh"
@@ -166,6 +167,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   int* red_flag = const_cast<int*>(reinterpret_cast<volatile int*>(tmem_slot + 2));
+  uint64_t* red_bar = bars + 120;               // cluster split-K: one arrival per CTA of the cluster once its partial is in shared memory
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tn = p.tn;
@@ -184,6 +186,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
       mbar_init(&tfull[i], 1);
       mbar_init(&tempty[i], 4);     // one arrival per epilogue warp
     }
+    if (p.cluster > 1) mbar_init(red_bar, (uint32_t)p.splits);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmX);
@@ -196,6 +199,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  if (p.cluster > 1) cluster_sync_all();   // no CTA may signal a peer's barrier before that peer has initialised it
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) TRACE(1);
 
@@ -319,6 +323,63 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
     const int n = n_base + row;
     const float bias_v = (!silu && p.bias != nullptr && n < p.N) ? __bfloat162float(p.bias[n]) : 0.f;
+    if (p.splits > 1 && p.cluster > 1) {
+      // Split-K inside a thread-block cluster: the CTAs that share a tile are the cluster (rank = split index, one work item per
+      // CTA). Each leaves its fp32 partial in its own shared memory ([token / 4][row][4], over the operand ring, which is idle once
+      // the last MMA has committed), tells every CTA of the cluster, and then reduces the token quads q with q % splits == rank
+      // by reading all partials through distributed shared memory in split order (bit-stable). The reduction runs on all CTAs of
+      // the cluster at once and never touches global memory; the cluster barrier at the end of the kernel keeps every CTA's
+      // shared memory alive until its peers have read it.
+      const uint32_t red_u32 = smem_u32(smem + L.x_off);
+      for (int c = 0; c < tn_eff; c += 32) {
+        uint32_t v[32];
+        tmem_ld_32x32(taddr_of(c), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          sts128(red_u32 + (uint32_t)(((c + j) >> 2) * (BM * 16) + row * 16), make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (et < p.splits) mbar_arrive_cluster(mapa_shared(smem_u32(red_bar), (uint32_t)et));
+      if (!mbar_wait_cluster(red_bar, 0, abort_flag)) return false;
+      const int rank = (int)cluster_ctarank();
+      const int quads = tn_eff >> 2;
+      // rounds of up to eight quads per CTA (32 staged token rows, one emit): quad base + rank + i * splits
+      for (int qb = 0; qb < quads; qb += 8 * p.splits) {
+        float a[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) a[j] = 0.f;
+        int nq = 0;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int qd = qb + rank + i * p.splits;
+          if (qd < quads) {
+            const uint32_t local = red_u32 + (uint32_t)(qd * (BM * 16) + row * 16);
+            // four splits' pieces of the quad in flight at a time (a cluster has at most 8 CTAs); summed in split order
+#pragma unroll
+            for (int h = 0; h < 8; h += 4) {
+              if (h < p.splits) {
+                float4 f[4];
+#pragma unroll
+                for (int s2 = 0; s2 < 4; ++s2)
+                  f[s2] = h + s2 < p.splits ? ld_dsmem_f4(mapa_shared(local, (uint32_t)(h + s2))) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int s2 = 0; s2 < 4; ++s2) {
+                  a[4 * i] += f[s2].x; a[4 * i + 1] += f[s2].y; a[4 * i + 2] += f[s2].z; a[4 * i + 3] += f[s2].w;
+                }
+              }
+            }
+            nq = i + 1;
+          }
+        }
+        if (nq > 0) emit(a, 4 * nq, 4 * (qb + rank), 4 * p.splits, n_base, t0, t_end, bias_v);   // nq is uniform over the CTA
+      }
+      if (p.n_push > 0) __threadfence_system();
+      return true;
+    }
     if (p.splits > 1) {
       // Split-K: every CTA of the tile writes its fp32 partial ([token / 4][row][4], so a warp's 16-byte accesses are contiguous) and
       // bumps the tile's counter; the CTA that arrives last sums the partials in split order (bit-stable) and runs the real epilogue.
@@ -629,6 +690,7 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     while (globaltimer_ns() - t0 < 2000000ull) {}
   }
   __syncthreads();
+  if (p.cluster > 1) cluster_sync_all();   // peers may still be reading this CTA's partial
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, kTmemCols);
@@ -707,20 +769,35 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   int ktiles = p.K / BK;
   int tiles = p.num_t_tiles * p.num_n_tiles;
   int best = 1;
-  if (tiles < slots && p.ws != nullptr) {
+  // Split-K through a cluster's shared memory (no workspace traffic, the reduction spread over the splits' CTAs) is taken whenever the
+  // tile count leaves at least half of the CTA slots idle: up to 8 splits, each with at least two k tiles, a partial tile that fits
+  // over the operand ring, and every CTA resident at once (one work item per CTA).
+  p.cluster = 0;
+  const bool cluster_ok = env_int("ONECAT_GEMM_CLUSTER", 1) != 0 && p.work == nullptr && p.nt_sub == 1;
+  if (cluster_ok && tiles * 2 <= slots) {
+    int s = slots / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && ((ktiles + s - 1) / s < 2 || (s - 1) * ((ktiles + s - 1) / s) >= ktiles)) --s;
+    if (s > 1) {
+      best = s;
+      p.cluster = s;
+    }
+  }
+  if (!p.cluster && tiles < slots && p.ws != nullptr) {
     double best_score = -1;
-    // fixed cost of an item in k-tile times: pipeline fill, the fp32 partial round trip and the last arriver's reduction. The light
-    // variant overlaps it with the other resident CTA's main loop.
+    // fixed cost of an item in k-tile times: pipeline fill, the fp32 partial round trip and the last arriver's reduction (measured:
+    // about 0.7 us per split and 32-token chunk, i.e. five to ten k-tile times per split, because the last arriver's 128 threads
+    // cannot keep more than 16 KB of loads in flight)
     const double fixed = p.small ? 3.0 : 6.0;
     const int min_per = p.small ? 2 : 4;
+    const double per_split = 5.0 * ((tn + 31) / 32);
     for (int s = 1; s <= 32; ++s) {
       int per = (ktiles + s - 1) / s;
       if (per < min_per || (s - 1) * per >= ktiles) continue;  // every split needs work
       if ((size_t)tiles * s * BM * tn * p.nt_sub * 4 > p.ws_bytes || tiles > p.max_counters) break;
       int items = tiles * s;
       int waves = (items + slots - 1) / slots;
-      // time ~ waves * k tiles per item (+ a fixed cost per item for the reduction traffic)
-      double cost = waves * (per + fixed) + (s > 1 ? 0.5 * s : 0.0);  // the last arriver reads s partials
+      double cost = waves * (per + fixed) + (s > 1 ? per_split * s : 0.0);
       double score = 1.0 / cost;
       if (score > best_score * 1.02) { best_score = score; best = s; }
     }
@@ -728,6 +805,13 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   p.splits = best;
   p.ktiles_per_split = (ktiles + best - 1) / best;
   gemm_plan_stages(p, w4);
+  if (p.cluster && (p.xstages * p.kps < 4 || p.nt_sub != 1)) {   // the fp32 partial (tn x 512 bytes) lies over the X ring
+    p.cluster = 0;
+    if (p.ws == nullptr || (size_t)tiles * best * BM * tn * 4 > p.ws_bytes || tiles > p.max_counters) {
+      p.splits = 1;
+      p.ktiles_per_split = ktiles;
+    }
+  }
 }
 
 // Pipeline depths from the shared-memory budget (227 KB per CTA, half of it for the light variant) for the chosen token tile.
@@ -796,7 +880,13 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
   int total = p.work != nullptr ? p.work_capacity : p.num_n_tiles * p.num_t_tiles * p.splits;
   const int slots = p.small ? 2 * num_sms : num_sms;
   int grid = total < slots ? total : slots;
-  if (p.splits > 1 && (p.ws == nullptr || p.counters == nullptr || p.num_n_tiles * p.num_t_tiles > p.max_counters)) return -9;
+  if (p.cluster > 1) {
+    // one work item per CTA, the splits of a tile adjacent in the grid (cluster rank = split index)
+    if (p.cluster != p.splits || p.cluster > 8 || p.work != nullptr || p.nt_sub > 1 || total > slots) return -11;
+    grid = total;
+  } else if (p.splits > 1 && (p.ws == nullptr || p.counters == nullptr || p.num_n_tiles * p.num_t_tiles > p.max_counters)) {
+    return -9;
+  }
   int smem = gemm_smem_bytes(p);
   // the opt-in shared-memory limit is a per-device attribute of each kernel: remember it per (device, kernel)
   constexpr int kMaxDev = 64;
@@ -814,6 +904,56 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         configured[dev][p.wkind][sm] = true;
       }
+    }
+    if (p.cluster > 1) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.blockDim = dim3(threads);
+      cfg.dynamicSmemBytes = (size_t)smem;
+      cfg.stream = stream;
+      cudaLaunchAttribute at[2];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.y = 1;
+      at[0].val.clusterDim.z = 1;
+      at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[1].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = at;
+      // Every cluster must be resident at once (one wave): clusters are placed inside one GPC, so fewer of them fit than the CTA
+      // slots suggest. Ask the runtime how many clusters of each size this kernel can hold and shrink the split until the tiles fit.
+      const int tiles = p.num_n_tiles * p.num_t_tiles, ktiles = p.K / BK;
+      int sps = p.cluster;
+      {
+        std::lock_guard<std::mutex> lock(cfg_mutex);
+        static std::map<long long, int> cache;
+        for (; sps > 1; --sps) {
+          const int per = (ktiles + sps - 1) / sps;
+          if ((sps - 1) * per >= ktiles) continue;
+          const long long key = ((((long long)dev * 8 + p.wkind) * 2 + sm) * 16 + sps) * 4096 + (smem >> 10);
+          auto it = cache.find(key);
+          int fit;
+          if (it != cache.end()) {
+            fit = it->second;
+          } else {
+            cfg.gridDim = dim3((unsigned)(sps * 64));
+            at[0].val.clusterDim.x = (unsigned)sps;
+            cfg.numAttrs = 1;
+            fit = 0;
+            if (cudaOccupancyMaxActiveClusters(&fit, kernel, &cfg) != cudaSuccess) { fit = 0; cudaGetLastError(); }
+            cache[key] = fit;
+          }
+          if (tiles <= fit) break;
+        }
+      }
+      p.splits = sps;
+      p.ktiles_per_split = (ktiles + sps - 1) / sps;
+      if (sps <= 1) {
+        p.cluster = 0;
+        return launch_k(kernel, dim3(tiles), dim3(threads), (size_t)smem, stream, true, tmX, tmW, p) == cudaSuccess ? 0 : -10;
+      }
+      p.cluster = sps;
+      cfg.gridDim = dim3((unsigned)(tiles * sps));
+      at[0].val.clusterDim.x = (unsigned)sps;
+      cfg.numAttrs = pdl_enabled() ? 2 : 1;
+      return cudaLaunchKernelEx(&cfg, kernel, tmX, tmW, p) == cudaSuccess ? 0 : -12;
     }
     return launch_k(kernel, dim3(grid), dim3(threads), (size_t)smem, stream, true, tmX, tmW, p) == cudaSuccess ? 0 : -10;
   };
@@ -905,6 +1045,7 @@ extern "C" int onecat_gemm_bf16_splitk_noalloc(const void* x, const void* w, voi
   p.max_counters = kNoallocMaxTiles;
   p.w4 = nullptr; p.w4_sz = nullptr;
   gemm_plan(p, sms, false);
+  p.cluster = 0;  // this entry point keeps its partials in the static scratch, with the caller's split count
   const int ktiles = K / 64;
   p.splits = splits;
   p.ktiles_per_split = (ktiles + splits - 1) / splits;

@@ -19,6 +19,8 @@ struct GemmParams {
   int xstages, stages, pstages;  // ring depths: X tiles, W tiles (bf16 weights: same ring as X), packed 4-bit tiles
   int kps;                      // 64-wide k tiles per ring stage (one full / empty barrier pair per stage); 0 reads as 1
   int small;                    // packed weights, token tile <= 64: the light CTA variant, two resident per SM
+  int cluster;                  // > 1: the splits of a tile form a thread-block cluster of this size and reduce through distributed
+                                // shared memory (splits == cluster <= 8, one work item per CTA); 0: partials through the workspace
   int epi;
   int group_ktiles;   // 64-wide k tiles per quantisation group (group 128 -> 2)
   __nv_bfloat16* out;

@@ -113,9 +113,11 @@ class EngineCore:
         self.executor.collective_rpc("sleep", (level,))
         self.scheduler.reset_prefix_cache()
 
-    def wake_up(self) -> None:
-        self.executor.collective_rpc("wake_up")
-        self.paused = False
+    def wake_up(self, tags=None) -> None:
+        """``tags`` (sleep mode only): wake just these pools, e.g. ``["weights"]`` to push new weights before the KV cache returns."""
+        self.executor.collective_rpc("wake_up", (tags,))
+        if tags is None or "kv_cache" in tags:
+            self.paused = False
 
     def pause_generation(self) -> None:
         """Stop scheduling steps; queued and running requests keep their state and KV (reference: v1/engine/core.py pause)."""

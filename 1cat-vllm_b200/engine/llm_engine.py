@@ -85,8 +85,8 @@ class LLMEngine:
     def sleep(self, level: int = 1) -> None:
         self.engine_core.call_utility("sleep", level)
 
-    def wake_up(self) -> None:
-        self.engine_core.call_utility("wake_up")
+    def wake_up(self, tags=None) -> None:
+        self.engine_core.call_utility("wake_up", tags)
 
     def add_lora(self, lora_request) -> bool:
         return self.engine_core.call_utility("add_lora", lora_request.to_dict())

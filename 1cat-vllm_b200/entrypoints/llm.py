@@ -155,8 +155,8 @@ class LLM:
     def sleep(self, level: int = 1) -> None:
         self.llm_engine.sleep(level)
 
-    def wake_up(self) -> None:
-        self.llm_engine.wake_up()
+    def wake_up(self, tags=None) -> None:
+        self.llm_engine.wake_up(tags)
 
     def reset_prefix_cache(self) -> bool:
         return self.llm_engine.reset_prefix_cache()

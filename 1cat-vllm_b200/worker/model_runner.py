@@ -160,6 +160,13 @@ class ModelRunner:
             return torch.float8_e4m3fn
         raise ValueError(f"kv cache dtype {cd!r} is not supported (auto | fp8 | fp8_e4m3)")
 
+    def zero_kv_cache(self) -> None:
+        """After a sleep the cache pages are new physical memory: clear them (block 0 is the all-zero placeholder block)."""
+        for c in list(self.kv_caches) + ([self.mtp_cache] if getattr(self, "mtp_cache", None) is not None else []):
+            for t in (c if isinstance(c, tuple) else (c,)):
+                if t is not None:
+                    t.zero_()
+
     def initialize_kv_cache(self, kvc: KVCacheConfig) -> None:
         self.kv_cache_config = kvc
         dt, dev, nb, bs = self._kv_dtype(), self.device, kvc.num_blocks, self.block_size

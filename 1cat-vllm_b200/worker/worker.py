@@ -53,8 +53,13 @@ class Worker:
             ps.get_state().ep_a2a = all2all.create(self.cfg, self.device)
         self.runner = ModelRunner(self.cfg, self.device)
 
+    def _sleep_pools(self) -> bool:
+        return bool(self.cfg.model_config.enable_sleep_mode) and self.device.type == "cuda"
+
     def load_model(self) -> None:
-        self.runner.load_model()
+        from onecat_vllm.utils.cumem import maybe_pool
+        with maybe_pool(self._sleep_pools(), "weights"):
+            self.runner.load_model()
 
     def get_kv_cache_specs(self) -> dict:
         return self.runner.get_kv_cache_specs()
@@ -80,7 +85,9 @@ class Worker:
         return max(avail, 0)
 
     def initialize_from_config(self, kvc: KVCacheConfig) -> None:
-        self.runner.initialize_kv_cache(kvc)
+        from onecat_vllm.utils.cumem import maybe_pool
+        with maybe_pool(self._sleep_pools(), "kv_cache"):
+            self.runner.initialize_kv_cache(kvc)
 
     def compile_or_warm_up_model(self) -> None:
         if self.device.type != "cuda":
@@ -99,14 +106,32 @@ class Worker:
 
     # ---- utility RPCs (reference: gpu_worker.py:160-200 sleep/wake, :885 profile, :958 save_sharded_state)
     def sleep(self, level: int = 1) -> None:
-        """Level 1 drops the KV cache contents; level 2 also releases it."""
+        """With sleep mode on (weights and KV cache in releasable memory): level 1 copies the weights to pinned host memory and
+        gives the device memory of weights and KV cache back to the driver, level 2 gives back both without keeping the weights
+        (the caller reloads or pushes new ones after ``wake_up``). Addresses stay valid, so captured graphs survive. Without
+        sleep mode: level 1 drops the KV cache contents; level 2 also releases it.
+        (reference: gpu_worker.py:147 ``sleep`` / :188 ``wake_up``)"""
+        if self._sleep_pools():
+            from onecat_vllm.utils.cumem import CuMemAllocator
+            torch.cuda.synchronize()
+            freed = CuMemAllocator.get().sleep(offload_tags=("weights",) if level == 1 else (), discard_tags=None if level == 1 else ("weights", "kv_cache"))
+            log.info(f"sleep level {level}: released {freed / 2**30:.2f} GiB of device memory")
+            self.sleeping = True
+            return
         if self.runner.kv_caches and level >= 2:
             self.runner.kv_caches = []
             if self.device.type == "cuda":
                 torch.cuda.empty_cache()
         self.sleeping = True
 
-    def wake_up(self) -> None:
+    def wake_up(self, tags=None) -> None:
+        if self._sleep_pools():
+            from onecat_vllm.utils.cumem import CuMemAllocator
+            CuMemAllocator.get().wake_up(tags)
+            if tags is None or "kv_cache" in tags:
+                self.runner.zero_kv_cache()   # fresh physical pages: block 0 must read as zeros again
+            self.sleeping = False
+            return
         if not self.runner.kv_caches:
             self.runner.initialize_kv_cache(self.runner.kv_cache_config)
         self.sleeping = False

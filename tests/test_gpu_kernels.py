@@ -147,6 +147,31 @@ def test_gemm_w4(T, fuse):
     _close(y, e, 3e-2, 3e-2, f"w4 T={T} fuse={fuse}")
 
 
+@pytest.mark.parametrize("T", [1, 16, 33, 64])
+@pytest.mark.parametrize("N,Kd,fuse", [(896, 5120, False), (5120, 640, False), (256, 1024, False), (4352, 5120, True), (1024, 384, True)])
+def test_gemm_w4_cluster_splitk(T, N, Kd, fuse):
+    """Decode-sized 4-bit GEMMs whose k range is split over a thread-block cluster (2 to 8 CTAs per tile, partials summed through
+    distributed shared memory): against the fp32 oracle, bit-identical across launches, status word clean."""
+    grp = 128
+    g = torch.Generator(device="cuda").manual_seed(N + Kd + T)
+    q = torch.randint(0, 16, (N, Kd), device="cuda", generator=g, dtype=torch.uint8)
+    z = torch.randint(0, 16, (N, Kd // grp), device="cuda", generator=g, dtype=torch.uint8)
+    s = (torch.randn(N, Kd // grp, device="cuda", generator=g).abs() * 0.01 + 1e-3).half()
+    x = torch.randn(T, Kd, device="cuda", generator=g).bfloat16()
+    layer = _FakeLayer(fuse)
+    K().prepare_w4(layer, q, z, s, grp)
+    y = K().linear(layer, x).clone()
+    y2 = K().linear(layer, x).clone()
+    torch.cuda.synchronize()
+    assert K().check_status() == 0
+    wd = (q.float() - z.float().repeat_interleave(grp, 1)) * s.float().bfloat16().float().repeat_interleave(grp, 1)
+    e = x.float().cpu() @ wd.bfloat16().float().cpu().t()
+    if fuse:
+        e = torch.nn.functional.silu(e[:, : N // 2]) * e[:, N // 2:]
+    _close(y, e, 3e-2, 3e-2 * math.sqrt(Kd / 768), f"w4 cluster T={T} N={N} K={Kd}")
+    assert torch.equal(y, y2), "the cluster reduction sums in split order: launches must agree bit for bit"
+
+
 class _Fp8Layer(_FakeLayer):
     pass
 
@@ -566,7 +591,7 @@ def test_peer_wait_is_bounded_and_reports_status():
     w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
     K().check_status()
     _C.tp_reduce_norm([t.data_ptr() for t in part], [f.data_ptr() for f in flags], seq, [x.data_ptr(), 0], None, None, w, T, H, 0, 0, False, 0,
-                      1e-6, 2_000_000, T)  # 2 ms limit; the flag of "rank 1" is never written
+                      1e-6, 2_000_000, T, [], 0, 0, 0, False)  # 2 ms limit; the flag of "rank 1" is never written
     torch.cuda.synchronize()
     assert K().check_status() & 2, "the expired wait must be reported"
     assert K().check_status() == 0, "status is cleared after reading"
@@ -575,6 +600,41 @@ def test_peer_wait_is_bounded_and_reports_status():
     y, _ = K().rms_norm(part[0], w, 1e-6, None, False)
     torch.cuda.synchronize()
     assert torch.isfinite(y.float()).all()
+
+
+def test_expert_exchange_waits_are_bounded():
+    """The expert-parallel exchange with a peer that never takes part (its slab is a second buffer on this GPU that nothing writes):
+    every stage gives up after its limit, the status word reports it, nothing is written out of bounds and the context lives on."""
+    from onecat_vllm.ops import _C
+    n, El, k, H, I, T = 2, 32, 2, 256, 128, 8
+    E = n * El
+    cap, ret_rows = 64, 32
+
+    def up(v):
+        return -(-v // 256) * 256
+    off = [0, up(n * E * 4)]
+    off.append(off[1] + 256)
+    off.append(off[2] + up(cap * H * 2))
+    off.append(off[3] + up(cap * 4))
+    off.append(off[4] + up(ret_rows * H * 2))
+    total = off[5] + up(64 * H * 2)
+    slabs = [torch.zeros(total, dtype=torch.uint8, device="cuda") for _ in range(n)]
+    w13 = (torch.randn(El * 2 * I, H, device="cuda") * 0.05).bfloat16()
+    w2 = (torch.randn(El * H, I, device="cuda") * 0.05).bfloat16()
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    ids = torch.randint(0, E, (T, k), device="cuda", dtype=torch.int32)
+    w = torch.rand(T, k, device="cuda")
+    state = torch.zeros(8 + 2 * E, dtype=torch.int32, device="cuda")
+    K().check_status()
+    ws = K().workspace(x.device)
+    y = _C.fused_moe_a2a(x, w13, w2, w, ids, El, ws.counters, 0, None, None, 0, 1, [s.data_ptr() for s in slabs], off, state, 0, cap, ret_rows,
+                         64, 0, True, 1_000_000)   # 1 ms per wait
+    torch.cuda.synchronize()
+    assert K().check_status() & 2, "the expired waits must be reported"
+    assert int(slabs[1][off[2]:].view(torch.int16).abs().sum()) == 0, "nothing may be dispatched after the count exchange failed"
+    z, _ = K().rms_norm(x, torch.ones(H, device="cuda", dtype=torch.bfloat16), 1e-6, None, False)
+    torch.cuda.synchronize()
+    assert torch.isfinite(z.float()).all() and y.shape == (T, H)
 
 
 def test_gdn_kernels_match_sequential_oracle():

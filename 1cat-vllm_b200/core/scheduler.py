@@ -223,6 +223,10 @@ class Scheduler:
         while i < len(self.running) and budget > 0:
             r = self.running[i]
             n = r.num_tokens_with_spec + r.num_output_placeholders - r.num_computed_tokens
+            if r.num_output_placeholders and r.sampling_params is not None and (
+                    r.num_output_tokens + r.num_output_placeholders >= r.sampling_params.max_tokens
+                    or r.num_tokens + r.num_output_placeholders >= self.max_model_len):
+                n = 0  # the token in flight is the request's last: nothing more to compute for it
             if sc.long_prefill_token_threshold > 0:
                 n = min(n, sc.long_prefill_token_threshold)
             n = min(n, budget, self.max_model_len - 1 - r.num_computed_tokens)
@@ -359,8 +363,31 @@ class Scheduler:
             out.kv_swap_out, out.kv_swap_in = self.kv_cache_manager.offload.take_ops()
         # advance: the runner computes these tokens in this step
         for rid, n in out.num_scheduled_tokens.items():
-            self.requests[rid].num_computed_tokens += n
+            r = self.requests[rid]
+            r.num_computed_tokens += n
+            if self.async_scheduling and r.num_computed_tokens >= r.num_tokens + r.num_output_placeholders:
+                r.num_output_placeholders += 1   # this step samples a token the next schedule() will not have seen yet
         return out
+
+    def may_preempt(self) -> bool:
+        """Whether the next schedule() could run out of KV blocks (and so preempt a request whose step is still in flight)."""
+        need = len(self.running) * (1 + self.num_lookahead_tokens // max(self.block_size, 1) + 1) + 8
+        return self.kv_cache_manager.block_pool.get_num_free_blocks() < need
+
+    def all_plain(self) -> bool:
+        """Every live request samples from the untouched logits and reports nothing but its tokens: the condition under which a
+        step may be scheduled before the previous step's tokens are known."""
+        for q in (self.running, self.waiting):
+            for r in q:
+                sp = r.sampling_params
+                if sp is None or r.pooling_params is not None or r.spec_token_ids:
+                    return False
+                if (sp.logprobs is not None or sp.prompt_logprobs is not None or sp.presence_penalty or sp.frequency_penalty
+                        or sp.repetition_penalty != 1.0 or sp.min_tokens or sp.logit_bias or sp.allowed_token_ids or sp.bad_words
+                        or getattr(sp, "structured_outputs", None) is not None or getattr(sp, "thinking_token_budget", None) is not None
+                        or getattr(sp, "repetition_detection", None) is not None):
+                    return False
+        return True
 
     def _preempt(self, r: Request) -> None:
         self.kv_cache_manager.free(r)
@@ -406,6 +433,8 @@ class Scheduler:
             new_ids: list[int] = []
             stop = False
             for t in generated:
+                if r.num_output_placeholders > 0:
+                    r.num_output_placeholders -= 1
                 r.append_output_token_ids(t)
                 new_ids.append(t)
                 if check_stop(r, self.max_model_len):

@@ -769,37 +769,41 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   int ktiles = p.K / BK;
   int tiles = p.num_t_tiles * p.num_n_tiles;
   int best = 1;
-  // Split-K through a cluster's shared memory (no workspace traffic, the reduction spread over the splits' CTAs) is taken whenever the
-  // tile count leaves at least half of the CTA slots idle: up to 8 splits, each with at least two k tiles, a partial tile that fits
-  // over the operand ring, and every CTA resident at once (one work item per CTA).
-  p.cluster = 0;
-  const bool cluster_ok = env_int("ONECAT_GEMM_CLUSTER", 1) != 0 && p.work == nullptr && p.nt_sub == 1;
-  if (cluster_ok && tiles * 2 <= slots) {
-    int s = slots / tiles;
-    if (s > 8) s = 8;
-    while (s > 1 && ((ktiles + s - 1) / s < 2 || (s - 1) * ((ktiles + s - 1) / s) >= ktiles)) --s;
-    if (s > 1) {
-      best = s;
-      p.cluster = s;
-    }
-  }
-  if (!p.cluster && tiles < slots && p.ws != nullptr) {
-    double best_score = -1;
-    // fixed cost of an item in k-tile times: pipeline fill, the fp32 partial round trip and the last arriver's reduction (measured:
-    // about 0.7 us per split and 32-token chunk, i.e. five to ten k-tile times per split, because the last arriver's 128 threads
-    // cannot keep more than 16 KB of loads in flight)
-    const double fixed = p.small ? 3.0 : 6.0;
+  double best_cost = 1e30;
+  // fixed cost of an item in k-tile times (pipeline fill, epilogue); the light variant overlaps it with the other resident CTA
+  const double fixed = p.small ? 3.0 : 6.0;
+  if (tiles < slots && p.ws != nullptr) {
+    // Workspace split-K: fp32 partials through global memory, summed by the CTA that arrives last. Its 128 threads cannot keep more
+    // than 16 KB of loads in flight, so the sum costs about 0.7 us per split and 32-token chunk whatever the split count's other
+    // merits: measured tails of 8 to 12 us at 64 tokens, i.e. about five k-tile times per split and chunk.
     const int min_per = p.small ? 2 : 4;
-    const double per_split = 5.0 * ((tn + 31) / 32);
+    const double per_split = 2.5 * ((tn + 31) / 32);
     for (int s = 1; s <= 32; ++s) {
       int per = (ktiles + s - 1) / s;
       if (per < min_per || (s - 1) * per >= ktiles) continue;  // every split needs work
       if ((size_t)tiles * s * BM * tn * p.nt_sub * 4 > p.ws_bytes || tiles > p.max_counters) break;
       int items = tiles * s;
       int waves = (items + slots - 1) / slots;
-      double cost = waves * (per + fixed) + (s > 1 ? per_split * s : 0.0);
-      double score = 1.0 / cost;
-      if (score > best_score * 1.02) { best_score = score; best = s; }
+      double cost = waves * (per + fixed) + (s > 1 ? 6.0 + per_split * s : 0.0);
+      if (cost < best_cost * 0.98) { best_cost = cost; best = s; }
+    }
+  } else {
+    best_cost = ktiles + fixed;
+  }
+  // Split-K inside a thread-block cluster: the splits of a tile are one cluster (at most 8 CTAs), partials stay in shared memory and
+  // every CTA of the cluster reduces a share of the tile through distributed shared memory: no workspace traffic and no serial
+  // tail. Every cluster should be resident at once, and clusters are placed inside one GPC, so only part of the CTA slots count.
+  p.cluster = 0;
+  if (env_int("ONECAT_GEMM_CLUSTER", 1) != 0 && p.work == nullptr && p.nt_sub == 1) {
+    int s = (slots * env_int("ONECAT_GEMM_CLUSTER_FILL", 85) / 100) / tiles;
+    if (s > 8) s = 8;
+    while (s > 1 && ((ktiles + s - 1) / s < 2 || (s - 1) * ((ktiles + s - 1) / s) >= ktiles)) --s;
+    if (s > 1) {
+      const double cost = (ktiles + s - 1) / s + fixed + 3.0;
+      if (cost <= best_cost) {
+        best = s;
+        p.cluster = s;
+      }
     }
   }
   p.splits = best;
@@ -917,38 +921,8 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
       at[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       at[1].val.programmaticStreamSerializationAllowed = 1;
       cfg.attrs = at;
-      // Every cluster must be resident at once (one wave): clusters are placed inside one GPC, so fewer of them fit than the CTA
-      // slots suggest. Ask the runtime how many clusters of each size this kernel can hold and shrink the split until the tiles fit.
-      const int tiles = p.num_n_tiles * p.num_t_tiles, ktiles = p.K / BK;
-      int sps = p.cluster;
-      {
-        std::lock_guard<std::mutex> lock(cfg_mutex);
-        static std::map<long long, int> cache;
-        for (; sps > 1; --sps) {
-          const int per = (ktiles + sps - 1) / sps;
-          if ((sps - 1) * per >= ktiles) continue;
-          const long long key = ((((long long)dev * 8 + p.wkind) * 2 + sm) * 16 + sps) * 4096 + (smem >> 10);
-          auto it = cache.find(key);
-          int fit;
-          if (it != cache.end()) {
-            fit = it->second;
-          } else {
-            cfg.gridDim = dim3((unsigned)(sps * 64));
-            at[0].val.clusterDim.x = (unsigned)sps;
-            cfg.numAttrs = 1;
-            fit = 0;
-            if (cudaOccupancyMaxActiveClusters(&fit, kernel, &cfg) != cudaSuccess) { fit = 0; cudaGetLastError(); }
-            cache[key] = fit;
-          }
-          if (tiles <= fit) break;
-        }
-      }
-      p.splits = sps;
-      p.ktiles_per_split = (ktiles + sps - 1) / sps;
-      if (sps <= 1) {
-        p.cluster = 0;
-        return launch_k(kernel, dim3(tiles), dim3(threads), (size_t)smem, stream, true, tmX, tmW, p) == cudaSuccess ? 0 : -10;
-      }
+      const int tiles = p.num_n_tiles * p.num_t_tiles;
+      const int sps = p.cluster;
       p.cluster = sps;
       cfg.gridDim = dim3((unsigned)(tiles * sps));
       at[0].val.clusterDim.x = (unsigned)sps;

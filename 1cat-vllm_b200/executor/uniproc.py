@@ -80,6 +80,12 @@ class Executor:
             out.device_time_ms = sum(o.device_time_ms for o in outs[:: pc.tensor_parallel_size])
         return out
 
+    def launch_model(self, scheduler_output) -> None:
+        self.collective_rpc("launch_model", (scheduler_output,))
+
+    def collect_model(self):
+        return self.collective_rpc("collect_model")[0]
+
     def check_health(self) -> None:
         self.collective_rpc("check_health", timeout=10)
 

@@ -89,3 +89,31 @@ class ParallelLMHead(VocabParallelEmbedding):
             local = F.linear(hidden, self.weight)
         full = ps.all_gather_last_dim(local)
         return full[..., : self.vocab]
+
+    def greedy_tokens(self, hidden: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """Arg-max over the whole vocabulary without gathering the logits: each rank takes the maximum of its own shard and the
+        ranks exchange one (value, index) pair per row; ties go to the lowest token id, as ``argmax`` over the gathered logits would
+        (reference: model_executor/layers/logits_processor.py:363,711 fused top-1 across tensor-parallel ranks)."""
+        if hidden.is_cuda:
+            from onecat_vllm.ops import cuda as K
+            local = K.gemm_bf16(hidden, self.weight)
+        else:
+            local = F.linear(hidden, self.weight)
+        valid = max(min(self.per, self.vocab - self.lo), 0)      # the last shard is padded with rows that are not tokens
+        B = hidden.shape[0]
+        if valid > 0:
+            lf = local[:, :valid].float()
+            if scale < 0:
+                lf = lf * scale
+            val, idx = lf.max(dim=-1)
+            pair = torch.stack([val, (idx + self.lo).float()], dim=-1)   # token ids are below 2^24: exact in fp32
+        else:
+            pair = torch.stack([torch.full((B,), -float("inf"), device=hidden.device), torch.zeros(B, device=hidden.device)], dim=-1)
+        if self.tp == 1:
+            return pair[:, 1].long()
+        import torch.distributed as dist
+        pairs = [torch.empty_like(pair) for _ in range(self.tp)]
+        dist.all_gather(pairs, pair.contiguous(), group=ps.get_state().tp_group)
+        allp = torch.stack(pairs, 0)                                # [tp, B, 2]
+        best = allp[..., 0].argmax(dim=0)                           # first rank holding the maximum = lowest token id among ties
+        return allp[best, torch.arange(B, device=hidden.device), 1].long()

@@ -192,6 +192,15 @@ class CausalLM(nn.Module):
     def forward(self, input_ids, md, caches, inputs_embeds=None, intermediate=None):
         return self.model(input_ids, md, caches, inputs_embeds, intermediate=intermediate)
 
+    def greedy_tokens(self, hidden: torch.Tensor):
+        """Greedy token per row straight from the sharded LM head (no logits gather), or None when the model post-processes its
+        logits in a way arg-max does not commute with across shards."""
+        c = self.cfg
+        if c.final_softcap > 0:
+            return None   # tanh is monotonic, but keep one code path for capped models
+        head = self.lm_head if self.lm_head is not None else self.model.embed_tokens
+        return ParallelLMHead.greedy_tokens(head, hidden, c.logit_scale)
+
     def compute_logits(self, hidden: torch.Tensor) -> torch.Tensor:
         head = self.lm_head
         if head is None:

@@ -25,13 +25,18 @@ class SamplerOutput:
 
 
 class Sampler:
+    @staticmethod
+    def is_plain_greedy(md: SamplingMetadata) -> bool:
+        """Every row takes the arg-max of the untouched logits (so the token can be found without materialising them)."""
+        return (md.all_greedy and md.no_penalties and not md.min_tokens and not any(md.logit_bias) and
+                not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and md.grammar_bitmask is None
+                and not md.thinking and not md.custom_processors)
+
     def __call__(self, logits: torch.Tensor, md: SamplingMetadata) -> SamplerOutput:
         raw_lp = None
         if md.max_num_logprobs is not None:
             raw_lp = torch.log_softmax(logits.float(), dim=-1)
-        simple = (md.all_greedy and md.no_penalties and not md.min_tokens and not any(md.logit_bias) and
-                  not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and md.grammar_bitmask is None
-                  and not md.thinking and not md.custom_processors)
+        simple = self.is_plain_greedy(md)
         if simple:
             sampled = ops.argmax(logits)  # greedy fast path: no fp32 copy of the logits
         else:

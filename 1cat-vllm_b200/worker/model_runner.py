@@ -24,7 +24,7 @@ from onecat_vllm.logger import init_logger
 from onecat_vllm.parallel import state as ps
 from onecat_vllm.sample.metadata import SamplingMetadata
 from onecat_vllm.sample.rejection_sampler import RejectionSampler
-from onecat_vllm.sample.sampler import Sampler, to_logprobs_lists
+from onecat_vllm.sample.sampler import Sampler, SamplerOutput, to_logprobs_lists
 from onecat_vllm.worker.attn_metadata import AttentionMetadata
 
 log = init_logger(__name__)
@@ -47,6 +47,25 @@ class CachedRequestState:
     mm_features: Optional[list] = None  # multimodal items of the prompt (placeholder ranges + encoder inputs)
     pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
     pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
+    pending: int = 0  # tokens sampled by a step that is still in flight (async scheduling): on the device, not yet in token_ids
+
+
+class _Ready:
+    """Stands in for a CUDA event on the CPU path, where the copy has completed by the time it returns."""
+
+    def synchronize(self) -> None:
+        pass
+
+
+@dataclass
+class PendingStep:
+    """A launched step whose sampled tokens have not been read back yet."""
+    out: "ModelRunnerOutput"
+    rows: Optional[list] = None        # logits rows per request (1 where the request sampled)
+    n: int = 0                         # sampled tokens on their way to ``host``
+    host: Optional[torch.Tensor] = None
+    done: object = None                # event recorded after the device-to-host copy
+    ev: Optional[tuple] = None         # (start, end) timing events
 
 
 class ModelRunner:
@@ -209,7 +228,8 @@ class ModelRunner:
             return t.pin_memory() if pin else t
 
         # one packed int32 staging area: ids | positions | slot_mapping | qsl | seq_lens | state_slots | has_init | logit_idx
-        self._seg = {"ids": T, "pos": T, "slot": T, "qsl": R + 1, "seq": R, "sslot": R, "hinit": R, "lidx": T}
+        # pdst | psrc: where last step's sampled tokens (still on the device) go in this step's ids (async scheduling)
+        self._seg = {"ids": T, "pos": T, "slot": T, "qsl": R + 1, "seq": R, "sslot": R, "hinit": R, "lidx": T, "pdst": R, "psrc": R}
         total = sum(self._seg.values())
         self.h_pack = host(total, torch.int32)
         self.d_pack = torch.zeros(total, dtype=torch.int32, device=self.device)
@@ -223,6 +243,14 @@ class ModelRunner:
         self.np_bt = self.h_bt.numpy()
         # per block-table row: the request state that owns it and how many of its blocks are already written there
         self._bt_owner, self._bt_written = [None] * self.np_bt.shape[0], [0] * self.np_bt.shape[0]
+        # async scheduling: two pinned landing buffers for sampled tokens, the previous step's tokens on the device and which row
+        # of them belongs to which request, the steps in flight, and an event after which the host staging may be rewritten
+        self._tok_host = [host(T, torch.int64), host(T, torch.int64)]
+        self._tok_flip = 0
+        self._prev_toks, self._prev_row = None, {}
+        self._inflight: list = []
+        self._h2d_done = None
+        self._n_patch = 0
 
     def _view(self, name: str, n: int, dev: bool = True) -> torch.Tensor:
         o, _ = self._off[name]
@@ -289,16 +317,30 @@ class ModelRunner:
         max_nb = 1
         drafts_of: list = []
         bt_owner, bt_written = self._bt_owner, self._bt_written
+        pdst = npk[o["pdst"][0]: o["pdst"][0] + R]
+        psrc = npk[o["psrc"][0]: o["psrc"][0] + R]
+        n_patch = 0
+        if self._h2d_done is not None:
+            self._h2d_done.synchronize()   # the previous step's copy out of this staging area has finished (it has, long ago)
         for r, rid in enumerate(req_ids):
             st = self.requests[rid]
             n = so.num_scheduled_tokens[rid]
             start = st.num_computed_tokens
             drafts = so.scheduled_spec_decode_tokens.get(rid, [])
             known = st.token_ids
+            known_len = len(known) + st.pending
             end = start + n
             bl = st.block_ids
             nb = -(-end // bs)
-            if n == 1 and start < len(known):
+            if st.pending and start == len(known):
+                # the token at this position was sampled by the step in flight: it is patched in on the device
+                assert n == 1 and rid in self._prev_row, "a pending token is the only input of its request"
+                ids[t] = 0
+                pos[t] = start
+                slot[t] = bl[start // bs] * bs + start % bs
+                pdst[n_patch], psrc[n_patch] = t, self._prev_row[rid]
+                n_patch += 1
+            elif n == 1 and start < len(known):
                 # plain decode row: scalar writes, no temporaries
                 ids[t] = known[start]
                 pos[t] = start
@@ -329,18 +371,19 @@ class ModelRunner:
             sslot[r] = st.state_slot
             hinit[r] = 1 if start > 0 else 0
             # sampling positions: the request reaches the end of its known tokens in this step
-            if end >= len(known):
-                k = 1 + max(end - len(known), 0)
+            if end >= known_len:
+                k = 1 + max(end - known_len, 0)
                 lidx_buf[n_l:n_l + k] = np.arange(t + n - k, t + n, dtype=np.int32)
                 n_l += k
                 logits_rows.append(k)
             else:
                 logits_rows.append(0)
-            drafts_of.append(drafts[: max(end - len(known), 0)])
+            drafts_of.append(drafts[: max(end - known_len, 0)])
             t += n
             qsl[r + 1] = t
             max_q, max_s = max(max_q, n), max(max_s, end)
         assert t == T
+        self._n_patch = n_patch
         return req_ids, R, T, n_l, logits_rows, drafts_of, max_q, max_s, max_nb
 
     def _pad_inputs(self, R: int, T: int, rp: int, q: int) -> None:
@@ -365,9 +408,15 @@ class ModelRunner:
             self.d_pack.copy_(self.h_pack, non_blocking=True)
             self.d_bt[:R, :max_nb].copy_(self.h_bt[:R, :max_nb], non_blocking=True)
             self.h2d_bytes = self.h_pack.numel() * 4 + R * max_nb * 4
+            if self._h2d_done is None:
+                self._h2d_done = torch.cuda.Event()
+            self._h2d_done.record()
         else:
             self.d_pack.copy_(self.h_pack)
             self.d_bt[:R, :max_nb].copy_(self.h_bt[:R, :max_nb])
+        if self._n_patch:
+            k = self._n_patch
+            self._view("ids", T).index_copy_(0, self._view("pdst", k).long(), self._prev_toks[self._view("psrc", k).long()].to(torch.int32))
 
     def _build_metadata(self, R, T, max_q, max_s, max_nb, query_lens, seq_lens) -> AttentionMetadata:
         return AttentionMetadata(
@@ -475,7 +524,44 @@ class ModelRunner:
             self._save_kv_files()
         return out
 
-    def _execute_model(self, so: SchedulerOutput) -> ModelRunnerOutput:
+    # ---- async scheduling: a step is launched (inputs staged, forward and sampling enqueued, tokens on their way to pinned host
+    # memory) and collected later, so the host work of the next step overlaps this one's device time. The engine only launches a
+    # second step on top of one in flight when every request is plain (no penalties, logprobs, drafts, grammars): the unread tokens
+    # are then needed nowhere but as the next step's input ids, where they are patched in on the device.
+    # (reference: v1/core/sched/async_scheduler.py:12; v1/engine/core.py:568 ``step_with_batch_queue``;
+    #  v1/worker/gpu_model_runner.py ``AsyncGPUModelRunnerOutput``)
+    @torch.inference_mode()
+    def launch_model(self, so: SchedulerOutput) -> None:
+        res = self._execute_model(so, defer=True)
+        self._inflight.append(res if isinstance(res, PendingStep) else PendingStep(out=res))
+
+    @torch.inference_mode()
+    def collect_model(self) -> ModelRunnerOutput:
+        p = self._inflight.pop(0)
+        out = p.out
+        if p.done is not None:
+            p.done.synchronize()
+            host = p.host[:p.n].tolist()
+            self.d2h_bytes = p.n * 8
+            j = 0
+            for i, k in enumerate(p.rows):
+                if k > 0:
+                    out.sampled_token_ids[i] = [host[j]]
+                    st = self.requests.get(out.req_ids[i])
+                    if st is not None:
+                        st.token_ids.append(host[j])
+                        st.pending = max(st.pending - 1, 0)
+                    j += 1
+            if p.ev is not None:
+                out.device_time_ms = p.ev[0].elapsed_time(p.ev[1])
+            if self.use_cuda:
+                from onecat_vllm.ops import cuda as K
+                out.status = K.check_status()
+        if self._pending_saves:
+            self._save_kv_files()
+        return out
+
+    def _execute_model(self, so: SchedulerOutput, defer: bool = False):
         self._update_states(so)
         self._swap_kv(so)
         self._run_encoders(so)
@@ -534,16 +620,40 @@ class ModelRunner:
         if n_l > 0:
             lidx = self._view("lidx", n_l).long()
             sample_hidden = hidden[lidx]
-            logits = self.model.compute_logits(sample_hidden)
             smd = self._sampling_metadata(req_ids, rows)
+            toks = None
+            if (self.pp.tp_size > 1 and not spec_verify and so.grammar_bitmask is None and smd.max_num_logprobs is None
+                    and self.sampler.is_plain_greedy(smd)):
+                # tensor-parallel greedy decoding: one (value, index) pair per row crosses the ranks instead of the vocabulary
+                toks = self.model.greedy_tokens(sample_hidden)
+            if toks is None:
+                logits = self.model.compute_logits(sample_hidden)
             if so.grammar_bitmask is not None:
                 smd.grammar_bitmask = self._grammar_mask(so, req_ids, rows, logits.shape[-1])
             samp_rows = [k for k in rows if k > 0]
             if not spec_verify:
-                so_ = self.sampler(logits, smd)
+                so_ = self.sampler(logits, smd) if toks is None else SamplerOutput(toks, None)
                 toks = so_.sampled_token_ids
                 if timed:
                     ev1.record()
+                if defer and so_.logprobs is None and self.proposer is None:
+                    # leave the tokens on the device for the next step's inputs and send a copy towards the host
+                    buf = self._tok_host[self._tok_flip]
+                    self._tok_flip ^= 1
+                    n_s = toks.shape[0]
+                    buf[:n_s].copy_(toks, non_blocking=True)
+                    done = None
+                    if self.use_cuda:
+                        done = torch.cuda.Event()
+                        done.record()
+                    self._prev_toks, self._prev_row = toks, {}
+                    j = 0
+                    for i, k in enumerate(rows):
+                        if k > 0:
+                            self._prev_row[req_ids[i]] = j
+                            self.requests[req_ids[i]].pending += 1
+                            j += 1
+                    return PendingStep(out, rows, n_s, buf, done if done is not None else _Ready(), (ev0, ev1) if timed else None)
                 host = toks.tolist()  # device → host read of the step's result
                 self.d2h_bytes = len(host) * 8
                 j = 0

@@ -104,6 +104,13 @@ class Worker:
         out = self.runner.execute_model(so)
         return out if ps.get_state().rank == 0 or True else None
 
+    def launch_model(self, so: SchedulerOutput) -> None:
+        """Async scheduling: enqueue the step and return; ``collect_model`` hands out the oldest step's result."""
+        self.runner.launch_model(so)
+
+    def collect_model(self) -> ModelRunnerOutput:
+        return self.runner.collect_model()
+
     # ---- utility RPCs (reference: gpu_worker.py:160-200 sleep/wake, :885 profile, :958 save_sharded_state)
     def sleep(self, level: int = 1) -> None:
         """With sleep mode on (weights and KV cache in releasable memory): level 1 copies the weights to pinned host memory and

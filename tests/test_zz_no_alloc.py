@@ -6,6 +6,7 @@ without PyTorch's caching allocator). Its split-K scratch is a fixed array insid
 result equals the regular entry point's, which takes its workspace from the caller, (b) a second call right after the first one
 is still right although both share the scratch, and (c) oversized problems are refused instead of overrunning the array."""
 import ctypes
+import gc
 
 import pytest
 import torch
@@ -41,11 +42,18 @@ def test_noalloc_gemm_matches_regular_entry_point_twice_in_a_row():
         ref32 = x.float() @ w.float().t()
         for attempt in range(2):  # the second call reuses the scratch the first one left behind
             out = torch.full((T, N), float("nan"), device="cuda", dtype=torch.bfloat16)
-            before = torch.cuda.memory_allocated()
-            rc = _call(fn, x, w, out, splits)
-            assert rc == 0, f"entry point returned {rc}"
-            torch.cuda.synchronize()
-            assert torch.cuda.memory_allocated() == before, "the entry point must not allocate through the caching allocator"
+            # the collector may free tensors that earlier tests left in reference cycles at any Python allocation: run it now and
+            # keep it off while the allocator's counter is compared
+            gc.collect()
+            gc.disable()
+            try:
+                before = torch.cuda.memory_allocated()
+                rc = _call(fn, x, w, out, splits)
+                assert rc == 0, f"entry point returned {rc}"
+                torch.cuda.synchronize()
+                assert torch.cuda.memory_allocated() == before, "the entry point must not allocate through the caching allocator"
+            finally:
+                gc.enable()
             err = (out.float() - expect.float()).abs()
             tol = 2e-2 + 2e-2 * expect.float().abs()
             assert bool((err <= tol).all()), f"call {attempt}: max deviation {float(err.max())} from the regular entry point"

@@ -468,7 +468,7 @@ class SchedulerConfig:
     enable_chunked_prefill: bool = True
     long_prefill_token_threshold: int = 0
     policy: str = "fcfs"  # fcfs | priority
-    async_scheduling: bool = False
+    async_scheduling: bool = True  # one step in flight while the next is scheduled (falls back per step when a request needs host tokens)
     cuda_graph_sizes: Optional[list[int]] = None
     max_num_encoder_input_tokens: int = 8192  # multimodal: encoder output positions computed per step
     encoder_cache_size: int = 16384           # multimodal: encoder output positions kept on the workers
@@ -608,7 +608,7 @@ class EngineArgs:
     enable_chunked_prefill: bool = True
     long_prefill_token_threshold: int = 0
     scheduling_policy: str = "fcfs"
-    async_scheduling: bool = False
+    async_scheduling: bool = True
     enforce_eager: bool = False
     cuda_graph_sizes: Optional[list[int]] = None
     speculative_config: Optional[Union[dict, str]] = None

@@ -140,6 +140,7 @@ class Scheduler:
         self._num_preemptions = 0
         self._spec_stats = [0, 0, 0]
         self.use_pp = vllm_config.parallel_config.pipeline_parallel_size > 1
+        self.async_scheduling = False  # set by the engine core when it keeps a step in flight
         self.max_loras = vllm_config.model_config.max_loras if vllm_config.model_config.enable_lora else 0
 
     # ------------------------------------------------------------------ admission
@@ -395,6 +396,7 @@ class Scheduler:
         r.mm_cached.clear()
         r.status = RequestStatus.PREEMPTED
         r.num_computed_tokens = 0
+        r.num_output_placeholders = 0
         r.spec_token_ids = []
         r.num_preemptions += 1
         self._num_preemptions += 1
@@ -458,7 +460,10 @@ class Scheduler:
             if stop:
                 stopped.append(r)
         for r in stopped:
-            self.running.remove(r)
+            if r in self.running:
+                self.running.remove(r)
+            else:
+                self.waiting.remove(r)   # preempted while its last step was in flight
             self._free_request(r)
         stats = self.make_stats(sched_out, mro)
         result = {c: EngineCoreOutputs(outs, stats) for c, outs in outputs.items()}

@@ -37,6 +37,16 @@ class EngineCore:
         self.scheduler = Scheduler(vllm_config, num_blocks, num_slots, log_stats)
         self.step_count = 0
         self.paused = False
+        # async scheduling: one step may be in flight on the device while the next one is scheduled and staged. Not with drafts
+        # (their acceptance decides what the next step computes) nor with pipeline stages (tokens reach them through the scheduler).
+        pc, sc = vllm_config.parallel_config, vllm_config.scheduler_config
+        from onecat_vllm import envs
+        want = bool(sc.async_scheduling) if envs.ONECAT_ASYNC_SCHEDULING == "" else envs.ONECAT_ASYNC_SCHEDULING == "1"
+        self.async_scheduling = want and pc.pipeline_parallel_size == 1 and \
+            not (vllm_config.speculative_config and vllm_config.speculative_config.method) and \
+            not vllm_config.model_config.logits_processors   # user processors may read the tokens produced so far
+        self.scheduler.async_scheduling = self.async_scheduling
+        self._inflight = None  # SchedulerOutput of the launched, uncollected step
         self._structured = None  # built on the first request that asks for a grammar
         from onecat_vllm.core.kv_events import make_publisher
         self._kv_events = make_publisher(vllm_config.cache_config.kv_events_config)
@@ -72,21 +82,57 @@ class EngineCore:
         """Returns (outputs per client, whether a model step ran)."""
         if self._failed:
             raise EngineDeadError("a worker failed")
+        if self.async_scheduling:
+            return self._step_async()
         if not self.scheduler.has_requests() or self.paused:
             return {}, False
         so = self.scheduler.schedule()
         if self._structured is not None and self._structured.grammars:
             so.grammar_bitmask, so.structured_rows = self._structured.grammar_bitmask(list(so.num_scheduled_tokens))
+        mro = self._guarded(so, lambda: self.executor.execute_model(so))
+        return self._finish_step(so, mro)
+
+    def _guarded(self, so, call):
         try:
-            mro = self.executor.execute_model(so)
+            mro = call()
         except Exception as e:
             self._failed = True
             log.error(f"model step failed; scheduler state: running={len(self.scheduler.running)} waiting={len(self.scheduler.waiting)} "
                       f"tokens={so.total_num_scheduled_tokens}: {e!r}")
             raise
-        if mro.status != 0:
+        if mro is not None and mro.status != 0:
             self._failed = True
             raise CollectiveTimeout(f"device wait expired (status {mro.status:#x})")
+        return mro
+
+    def _step_async(self) -> tuple[dict[int, EngineCoreOutputs], bool]:
+        """One step stays in flight: while the device runs step n, step n+1 is scheduled (counting the token each sampling request
+        of step n will produce as a placeholder), staged and enqueued behind it; only then is step n's result read and applied.
+        Falls back to the plain schedule-run-update order whenever a request needs its tokens on the host between steps, a grammar
+        is active or the KV cache is close to full (a preemption must not hit a request whose step is in flight)."""
+        sch = self.scheduler
+        overlap_ok = not self.paused and not (self._structured is not None and self._structured.grammars) and sch.all_plain() and \
+            not sch.may_preempt()
+        if self._inflight is None:
+            if not sch.has_requests() or self.paused:
+                return {}, False
+            so = sch.schedule()
+            if not overlap_ok or so.total_num_scheduled_tokens == 0:
+                if self._structured is not None and self._structured.grammars:
+                    so.grammar_bitmask, so.structured_rows = self._structured.grammar_bitmask(list(so.num_scheduled_tokens))
+                mro = self._guarded(so, lambda: self.executor.execute_model(so))
+                return self._finish_step(so, mro)
+            self._guarded(so, lambda: self.executor.launch_model(so))
+            self._inflight = so
+        nxt = None
+        if overlap_ok and sch.has_unfinished_requests():
+            nxt = sch.schedule()
+            self._guarded(nxt, lambda: self.executor.launch_model(nxt))
+        cur, self._inflight = self._inflight, nxt
+        mro = self._guarded(cur, lambda: self.executor.collect_model())
+        return self._finish_step(cur, mro)
+
+    def _finish_step(self, so, mro) -> tuple[dict[int, EngineCoreOutputs], bool]:
         outs = self.scheduler.update_from_output(so, mro)
         ev = self.scheduler.kv_cache_manager.block_pool.take_events()  # also bounds the list when nobody listens
         if self._kv_events is not None:

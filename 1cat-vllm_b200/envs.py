@@ -44,6 +44,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_EP_COMM": _s("ONECAT_EP_COMM", "reduce"),
     "ONECAT_EP_A2A": _s("ONECAT_EP_A2A", "peer"),
     "ONECAT_EP_A2A_MIN_TOKENS": _i("ONECAT_EP_A2A_MIN_TOKENS", 0),
+    "ONECAT_ASYNC_SCHEDULING": _s("ONECAT_ASYNC_SCHEDULING", ""),  # "1" / "0" override the engine argument; empty: follow it
     "ONECAT_DEVICE_WAIT_LIMIT_MS": _i("ONECAT_DEVICE_WAIT_LIMIT_MS", 2000),
     "ONECAT_USE_CUDA_GRAPH": _b("ONECAT_USE_CUDA_GRAPH", True),
     "ONECAT_COMPUTE_NANS_IN_LOGITS": _b("ONECAT_COMPUTE_NANS_IN_LOGITS", False),

@@ -247,6 +247,7 @@ def main() -> None:
     ap.add_argument("--tp-comm", default=os.environ.get("ONECAT_TP_COMM", "fused"))
     ap.add_argument("--eager", action="store_true")
     ap.add_argument("--no-full", action="store_true", help="skip the full-workload pass (4 x concurrency requests, ramp-up and tail) after the timed steps")
+    ap.add_argument("--no-async", action="store_true", help="plain schedule-run-update order instead of async scheduling (one step kept in flight)")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -284,7 +285,7 @@ def main() -> None:
     ea = EngineArgs(hf_config=cfg, dtype="bfloat16", device="cuda", max_model_len=IN + OUT + 16, max_num_seqs=C, max_num_batched_tokens=8192,
                     tensor_parallel_size=args.gpus, distributed_executor_backend="external_launcher" if args.gpus > 1 else None,
                     tp_comm=args.tp_comm, enable_prefix_caching=False, gpu_memory_utilization=0.85, disable_log_stats=False,
-                    enforce_eager=args.eager, speculative_config=spec,
+                    enforce_eager=args.eager, speculative_config=spec, async_scheduling=not args.no_async,
                     enable_expert_parallel=args.config in ("moe35b", "dsv3") and args.gpus > 1,
                     kv_cache_memory_bytes=_kv_bytes(cfg, C, IN + OUT + 32, args.gpus))
     eng = LLMEngine.from_engine_args(ea)

@@ -476,5 +476,6 @@ int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
 }
 
 unsigned int attention_read_status(bool clear) { return read_status_tu(clear); }
+void attention_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

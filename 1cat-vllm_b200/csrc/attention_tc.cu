@@ -393,5 +393,6 @@ int attention_prefill_tc_launch(const AttnParams& p, long long num_blocks, cudaS
 }
 
 unsigned int attention_tc_read_status(bool clear) { return read_status_tu(clear); }
+void attention_tc_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

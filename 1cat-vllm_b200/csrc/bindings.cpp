@@ -629,6 +629,24 @@ torch::Tensor mla_decode(torch::Tensor q_abs, torch::Tensor q_rope, torch::Tenso
   return out;
 }
 
+// Enqueues one small copy per translation unit's status word into `pinned` (int32, >= 16 entries, pinned host memory) on the current
+// stream; the caller reads them after an event recorded behind this call (async scheduling: no device-wide synchronisation).
+void read_status_async(torch::Tensor pinned) {
+  TORCH_CHECK(pinned.scalar_type() == torch::kInt32 && pinned.numel() >= 16 && !pinned.is_cuda() && pinned.is_pinned(), "need 16 pinned int32 words");
+  unsigned int* p = reinterpret_cast<unsigned int*>(pinned.data_ptr<int>());
+  auto st = cur_stream();
+  oc::attention_read_status_async(p + 0, st);
+  oc::attention_tc_read_status_async(p + 1, st);
+  oc::comm_read_status_async(p + 2, st);
+  oc::elementwise_read_status_async(p + 3, st);
+  oc::ep_read_status_async(p + 4, st);
+  oc::gdn_read_status_async(p + 5, st);
+  oc::gemm_read_status_async(p + 6, st);
+  oc::mla_read_status_async(p + 7, st);
+  oc::moe_read_status_async(p + 8, st);
+  oc::sampling_read_status_async(p + 9, st);
+}
+
 int64_t read_status(bool clear) {
   return (int64_t)(oc::gemm_read_status(clear) | oc::elementwise_read_status(clear) | oc::attention_read_status(clear) | oc::attention_tc_read_status(clear) |
                    oc::comm_read_status(clear) | oc::gdn_read_status(clear) | oc::sampling_read_status(clear) | oc::moe_read_status(clear) | oc::mla_read_status(clear) | oc::ep_read_status(clear));
@@ -714,6 +732,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("argmax", &argmax);
   m.def("merge_attn_states", &merge_attn_states);
   m.def("read_status", &read_status);
+  m.def("read_status_async", &read_status_async);
   m.def("mla_decode", &mla_decode);
   m.def("fused_moe", &fused_moe);
   m.def("fused_moe_a2a", &fused_moe_a2a);

@@ -354,5 +354,6 @@ int comm_import(const void* handle64, void** ptr) {
 int comm_unimport(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? 0 : -1; }
 
 unsigned int comm_read_status(bool clear) { return read_status_tu(clear); }
+void comm_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

@@ -58,6 +58,7 @@ int ep_dispatch_launch(const EpParams& p, int sms, cudaStream_t st);
 int ep_return_launch(const EpParams& p, const void* a2, int sms, cudaStream_t st);
 int ep_combine_launch(const EpParams& p, const float* w, void* y, int sms, cudaStream_t st);
 unsigned int ep_read_status(bool clear);
+void ep_read_status_async(unsigned int* dst, cudaStream_t st);
 
 int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st);
 int comm_alloc(size_t bytes, void** ptr);
@@ -66,5 +67,6 @@ int comm_export(void* ptr, void* handle_out64);
 int comm_import(const void* handle64, void** ptr);
 int comm_unimport(void* ptr);
 unsigned int comm_read_status(bool clear);
+void comm_read_status_async(unsigned int* dst, cudaStream_t st);
 
 }  // namespace oc

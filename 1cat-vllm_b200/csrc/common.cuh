@@ -317,4 +317,10 @@ static inline unsigned int read_status_tu(bool clear) {
   return v;
 }
 
+// Non-blocking variant: the word lands in (pinned) host memory once the stream reaches the copy, so a step that is still running
+// is not waited for.
+static inline void read_status_tu_async(unsigned int* dst, cudaStream_t st) {
+  cudaMemcpyFromSymbolAsync(dst, g_status, sizeof(unsigned int), 0, cudaMemcpyDeviceToHost, st);
+}
+
 }  // namespace oc

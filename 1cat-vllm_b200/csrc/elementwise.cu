@@ -312,5 +312,6 @@ int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long
 }
 
 unsigned int elementwise_read_status(bool clear) { return read_status_tu(clear); }
+void elementwise_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

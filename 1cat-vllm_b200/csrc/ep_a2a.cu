@@ -236,5 +236,6 @@ int ep_combine_launch(const EpParams& p, const float* w, void* y, int sms, cudaS
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 unsigned int ep_read_status(bool clear) { return read_status_tu(clear); }
+void ep_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

@@ -289,5 +289,6 @@ int gdn_recurrent_launch(const GdnParams& p, cudaStream_t st) {
 }
 
 unsigned int gdn_read_status(bool clear) { return read_status_tu(clear); }
+void gdn_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

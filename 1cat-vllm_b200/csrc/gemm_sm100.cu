@@ -949,6 +949,7 @@ int gemm_launch(const GemmParams& p_in, const void* x, int ldx, const void* w_bf
 }
 
 unsigned int gemm_read_status(bool clear) { return read_status_tu(clear); }
+void gemm_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 // Diagnostics: what the runtime says about one kernel variant (registers, static shared and local memory per thread, and how many
 // CTAs with `smem` bytes of dynamic shared memory it would keep resident per SM).

@@ -57,6 +57,7 @@ void gemm_plan_stages(GemmParams& p, bool w4);
 int gemm_smem_bytes(const GemmParams& p);
 int gemm_launch(const GemmParams& p, const void* x, int ldx, const void* w_bf16, int ldw, int num_sms, cudaStream_t stream);
 unsigned int gemm_read_status(bool clear);
+void gemm_read_status_async(unsigned int* dst, cudaStream_t st);
 int gemm_kernel_info(int wkind, int small, int smem, int out[6]);
 
 }  // namespace oc

@@ -30,6 +30,7 @@ int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long
 int merge_attn_states_launch(const void* o1, const float* lse1, const void* o2, const float* lse2, void* out, float* lse_out, int rows, int D,
                              cudaStream_t st);
 unsigned int elementwise_read_status(bool clear);
+void elementwise_read_status_async(unsigned int* dst, cudaStream_t st);
 
 struct AttnParams {
   const __nv_bfloat16* q;     // [T][Hq][D] with strides
@@ -59,9 +60,11 @@ struct AttnParams {
 // (decode and short verify queries, with split-KV + combine).
 int attention_launch(const AttnParams& p, int mode, cudaStream_t st);
 unsigned int attention_read_status(bool clear);
+void attention_read_status_async(unsigned int* dst, cudaStream_t st);
 // tcgen05 prefill (attention_tc.cu): D == 128, 128-token query tiles; num_q_tiles counts those tiles.
 int attention_prefill_tc_launch(const AttnParams& p, long long num_blocks, cudaStream_t st);
 unsigned int attention_tc_read_status(bool clear);
+void attention_tc_read_status_async(unsigned int* dst, cudaStream_t st);
 
 
 struct RowStats {
@@ -99,6 +102,7 @@ struct RouteParams {
 };
 int route_launch(const RouteParams& p, cudaStream_t st);
 unsigned int sampling_read_status(bool clear);
+void sampling_read_status_async(unsigned int* dst, cudaStream_t st);
 
 struct MoePlanParams {
   int* counts;        // [E] scratch
@@ -115,6 +119,7 @@ int moe_prepare_launch(const MoePlanParams& p, const int* ids, int n_pairs, int 
 int moe_plan_launch(const MoePlanParams& p, cudaStream_t st);
 int moe_combine_launch(const void* a2, const int* slot_of, const float* w, void* y, int T, int k, int H, cudaStream_t st);
 unsigned int moe_read_status(bool clear);
+void moe_read_status_async(unsigned int* dst, cudaStream_t st);
 
 struct MlaParams {
   const __nv_bfloat16* q_abs;   // [T][H][512] query with W_UK absorbed
@@ -131,6 +136,7 @@ struct MlaParams {
 };
 int mla_decode_launch(const MlaParams& p, cudaStream_t st);
 unsigned int mla_read_status(bool clear);
+void mla_read_status_async(unsigned int* dst, cudaStream_t st);
 
 struct GdnConvParams {
   const __nv_bfloat16* x;   // [T][ldx] pre-conv mixed q|k|v (column slice allowed)
@@ -193,5 +199,6 @@ int gdn_conv_launch(const GdnConvParams& p, cudaStream_t st);
 int gdn_conv_commit_launch(const GdnConvParams& p, cudaStream_t st);
 int gdn_recurrent_launch(const GdnParams& p, cudaStream_t st);
 unsigned int gdn_read_status(bool clear);
+void gdn_read_status_async(unsigned int* dst, cudaStream_t st);
 
 }  // namespace oc

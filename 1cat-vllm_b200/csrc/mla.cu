@@ -226,5 +226,6 @@ int mla_decode_launch(const MlaParams& p, cudaStream_t st) {
 }
 
 unsigned int mla_read_status(bool clear) { return read_status_tu(clear); }
+void mla_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

@@ -126,5 +126,6 @@ int moe_combine_launch(const void* a2, const int* slot_of, const float* w, void*
 }
 
 unsigned int moe_read_status(bool clear) { return read_status_tu(clear); }
+void moe_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

@@ -202,5 +202,6 @@ int route_launch(const RouteParams& p, cudaStream_t st) {
 }
 
 unsigned int sampling_read_status(bool clear) { return read_status_tu(clear); }
+void sampling_read_status_async(unsigned int* dst, cudaStream_t st) { read_status_tu_async(dst, st); }
 
 }  // namespace oc

@@ -47,6 +47,7 @@ class EngineCore:
             not vllm_config.model_config.logits_processors   # user processors may read the tokens produced so far
         self.scheduler.async_scheduling = self.async_scheduling
         self._inflight = None  # SchedulerOutput of the launched, uncollected step
+        self._overlap = True   # set_overlap(False): finish what is in flight without launching behind it (drains the pipeline)
         self._structured = None  # built on the first request that asks for a grammar
         from onecat_vllm.core.kv_events import make_publisher
         self._kv_events = make_publisher(vllm_config.cache_config.kv_events_config)
@@ -111,7 +112,7 @@ class EngineCore:
         Falls back to the plain schedule-run-update order whenever a request needs its tokens on the host between steps, a grammar
         is active or the KV cache is close to full (a preemption must not hit a request whose step is in flight)."""
         sch = self.scheduler
-        overlap_ok = not self.paused and not (self._structured is not None and self._structured.grammars) and sch.all_plain() and \
+        overlap_ok = self._overlap and not self.paused and not (self._structured is not None and self._structured.grammars) and sch.all_plain() and \
             not sch.may_preempt()
         if self._inflight is None:
             if not sch.has_requests() or self.paused:
@@ -131,6 +132,11 @@ class EngineCore:
         cur, self._inflight = self._inflight, nxt
         mro = self._guarded(cur, lambda: self.executor.collect_model())
         return self._finish_step(cur, mro)
+
+    def set_overlap(self, on: bool) -> None:
+        """With ``False`` the next steps only finish work that is in flight (or run in the plain order when nothing is): a caller
+        that needs every launched step accounted for, e.g. to time an exact number of steps, turns overlap off for the last one."""
+        self._overlap = bool(on)
 
     def _finish_step(self, so, mro) -> tuple[dict[int, EngineCoreOutputs], bool]:
         outs = self.scheduler.update_from_output(so, mro)

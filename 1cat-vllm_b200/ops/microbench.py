@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe|sample] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe|sample|mla|rope|reject] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -74,7 +74,7 @@ def bench_w4(rows: list, small: bool, iters: int, pk: dict) -> None:
     cases = [(64, 7168, 5120, False), (64, 34816, 5120, True), (64, 5120, 17408, False), (64, 5120, 5120, False), (1, 34816, 5120, True),
              (256, 34816, 5120, True), (1088, 34816, 5120, True), (8192, 34816, 5120, True), (8192, 5120, 17408, False)]
     if small:
-        cases = [(64, 34816, 5120, True)]
+        cases = [(64, 34816, 5120, True), (64, 7168, 5120, False)]
     for T, N, Kd, fuse in cases:
         q = torch.randint(0, 16, (N, Kd), device="cuda", dtype=torch.uint8)
         z = torch.randint(0, 16, (N, Kd // 128), device="cuda", dtype=torch.uint8)
@@ -237,6 +237,65 @@ def bench_wq(rows: list, small: bool, iters: int, pk: dict) -> None:
             del layer, x, out
 
 
+def bench_mla(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """Absorbed MLA decode over a paged latent cache (576-wide rows): 128 heads, one query token per request."""
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    lora, rope, bs, H = 512, 64, 16, 128
+    for R, ctx in ([(32, 4096)] if small else [(32, 4096), (128, 5120), (8, 32768)]):
+        nb = -(-ctx // bs)
+        cache = (torch.randn(R * nb + 1, bs, lora + rope, device="cuda") * 0.3).bfloat16()
+        bt = (torch.arange(R * nb, device="cuda", dtype=torch.int32) + 1).view(R, nb)
+        q_abs = (torch.randn(R, H, lora, device="cuda") * 0.3).bfloat16()
+        q_pe = (torch.randn(R, H, rope, device="cuda") * 0.3).bfloat16()
+        qsl = torch.arange(R + 1, device="cuda", dtype=torch.int32)
+        sl = torch.full((R,), ctx, device="cuda", dtype=torch.int32)
+        md = AttentionMetadata(R, R, qsl, sl, bt, None, None, 1, ctx, query_lens_cpu=[1] * R, seq_lens_cpu=[ctx] * R)
+        ms = timeit(lambda: K.mla_decode(q_abs, q_pe, cache, md, 192 ** -0.5, lora), 1 if small else iters, 1 if small else 3)
+        b = R * ctx * (lora + rope) * 2
+        rows.append(dict(kernel="mla_decode", R=R, ctx=ctx, heads=H, ms=ms, latent_gbs=b / ms / 1e6, frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"],
+                         tflops=2.0 * R * H * ctx * (2 * lora + rope) / ms / 1e9))
+
+
+def bench_rope(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """q/k RMSNorm + rotary embedding in place + K/V insert into the paged cache (one kernel), 40 q / 8 kv heads of 128."""
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.ops import ref
+    Hq, Hkv, D, bs = 40, 8, 128, 16
+    cs = ref.build_cos_sin_cache(D, 40960, 1e6, "cuda")
+    for T in ([8192] if small else [64, 1088, 8192]):
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+        q, k, v = qkv[:, :Hq * D].view(T, Hq, D), qkv[:, Hq * D:(Hq + Hkv) * D].view(T, Hkv, D), qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        nb = T // bs + 2
+        cache = torch.zeros(nb, 2, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+        pos = torch.arange(T, device="cuda", dtype=torch.int32)
+        slots = torch.randperm(T, device="cuda").to(torch.int32) + bs
+        qn, kn = torch.ones(D, device="cuda").bfloat16(), torch.ones(D, device="cuda").bfloat16()
+        ms = timeit(lambda: K.rope_and_cache(q, k, v, pos, cs, cache, slots, D, qn, kn, 1e-6, False), 1 if small else iters, 1 if small else 3)
+        b = T * D * 2 * (2 * (Hq + Hkv) + Hkv + 2 * Hkv)   # q, k read and written; v read; k, v written to the cache
+        rows.append(dict(kernel="rope_qknorm_cache_insert", T=T, ms=ms, gbs=b / ms / 1e6, frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"]))
+
+
+def bench_reject(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """Rejection sampler over [B, k+1, V] target logits (greedy and stochastic), vocabulary 151936, three drafts."""
+    from onecat_vllm.sample.metadata import SamplingMetadata
+    from onecat_vllm.sample.rejection_sampler import RejectionSampler
+    V, k = 151936, 3
+    for B in ([64] if small else [8, 64, 256]):
+        tl = torch.randn(B, k + 1, V, device="cuda").bfloat16()
+        draft = tl.float().argmax(-1)[:, :k].contiguous()
+        nd = torch.full((B,), k, device="cuda")
+        bonus = torch.full((B,), 7, device="cuda")
+        for greedy in ((True,) if small else (True, False)):
+            md = SamplingMetadata(temperature=None if greedy else torch.ones(B, device="cuda"), all_greedy=greedy, all_random=not greedy, top_p=None,
+                                  top_k=None, min_p=None, generators={}, max_num_logprobs=None, no_penalties=True)
+            rs = RejectionSampler(seed=1)
+            ms = timeit(lambda: rs(draft, nd, tl, bonus, md), 1 if small else iters, 1 if small else 3)
+            b = B * (k + 1) * V * 2
+            rows.append(dict(kernel="rejection_sample", B=B, drafts=k, V=V, greedy=greedy, ms=ms, logits_gbs=b / ms / 1e6,
+                             frac_of_hbm=b / ms / 1e6 / pk["hbm_gbs"]))
+
+
 def bench_sample(rows: list, small: bool, iters: int, pk: dict) -> None:
     """The fused sampler against the sort-based PyTorch formulation on the same device (vocabulary 151936)."""
     from onecat_vllm.ops import cuda as K
@@ -269,7 +328,8 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq), ("sample", bench_sample),
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq), ("sample", bench_sample), ("mla", bench_mla),
+                     ("rope", bench_rope), ("reject", bench_reject),
                      ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True)),
                      ("gdn_prefill", lambda r, s_, i, p_: bench_gdn(r, s_, i, p_, prefill_only=True))):
         if not a.only and name in ("attn_prefill", "gdn_prefill"):

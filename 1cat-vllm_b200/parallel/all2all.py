@@ -161,4 +161,5 @@ def create(cfg, device, group=None):
     if device.type == "cuda" and envs.ONECAT_EP_A2A != "torch":
         return PeerAll2All(st.ep_size, st.ep_rank, device, cfg.scheduler_config.max_num_batched_tokens, mc.hidden_size, mc.num_experts,
                            mc.num_experts_per_tok, group if group is not None else st.tp_group)
+    log.info_once(f"expert-parallel exchange: torch.distributed all_to_all on {st.ep_size} ranks")
     return TorchAll2All(st.ep_size, st.ep_rank, group if group is not None else st.tp_group)

@@ -66,6 +66,7 @@ class PendingStep:
     host: Optional[torch.Tensor] = None
     done: object = None                # event recorded after the device-to-host copy
     ev: Optional[tuple] = None         # (start, end) timing events
+    status: Optional[torch.Tensor] = None  # pinned words the kernels' status was copied into behind the step
 
 
 class ModelRunner:
@@ -246,6 +247,7 @@ class ModelRunner:
         # async scheduling: two pinned landing buffers for sampled tokens, the previous step's tokens on the device and which row
         # of them belongs to which request, the steps in flight, and an event after which the host staging may be rewritten
         self._tok_host = [host(T, torch.int64), host(T, torch.int64)]
+        self._status_host = [host(16, torch.int32), host(16, torch.int32)]
         self._tok_flip = 0
         self._prev_toks, self._prev_row = None, {}
         self._inflight: list = []
@@ -434,7 +436,12 @@ class ModelRunner:
         temps = [sp.temperature if sp else 0.0 for sp in sps]
         all_greedy = all(t < 1e-5 for t in temps)
         all_random = all(t >= 1e-5 for t in temps)
-        f32 = lambda xs: torch.tensor(xs, dtype=torch.float32, device=dev)
+        # per-request sampling parameters travel through pinned memory: a copy from pageable memory would first wait for the
+        # stream to drain, i.e. for a step that is still in flight
+        def to_dev(xs, dt):
+            t = torch.tensor(xs, dtype=dt)
+            return t.pin_memory().to(dev, non_blocking=True) if self.use_cuda else t.to(dev)
+        f32 = lambda xs: to_dev(xs, torch.float32)
         no_pen = all((sp is None) or (sp.presence_penalty == 0 and sp.frequency_penalty == 0 and sp.repetition_penalty == 1.0) for sp in sps)
         need_k = any(sp and sp.top_k > 0 for sp in sps)
         need_p = any(sp and sp.top_p < 1.0 for sp in sps)
@@ -443,7 +450,7 @@ class ModelRunner:
         md = SamplingMetadata(
             temperature=None if all_greedy else f32(temps), all_greedy=all_greedy, all_random=all_random,
             top_p=f32([sp.top_p for sp in sps]) if need_p else None,
-            top_k=torch.tensor([sp.top_k for sp in sps], dtype=torch.int64, device=dev) if need_k else None,
+            top_k=to_dev([sp.top_k for sp in sps], torch.int64) if need_k else None,
             min_p=f32([sp.min_p for sp in sps]) if need_m else None,
             generators={i: s.generator for i, s in enumerate(sel) if s.generator is not None},
             max_num_logprobs=max(lps) if lps else None, no_penalties=no_pen)
@@ -554,9 +561,11 @@ class ModelRunner:
                     j += 1
             if p.ev is not None:
                 out.device_time_ms = p.ev[0].elapsed_time(p.ev[1])
-            if self.use_cuda:
-                from onecat_vllm.ops import cuda as K
-                out.status = K.check_status()
+            if self.use_cuda and p.status is not None:
+                st_word = 0
+                for v in p.status.tolist():
+                    st_word |= v
+                out.status = st_word & 0xFFFFFFFF
         if self._pending_saves:
             self._save_kv_files()
         return out
@@ -638,12 +647,14 @@ class ModelRunner:
                     ev1.record()
                 if defer and so_.logprobs is None and self.proposer is None:
                     # leave the tokens on the device for the next step's inputs and send a copy towards the host
-                    buf = self._tok_host[self._tok_flip]
+                    buf, sbuf = self._tok_host[self._tok_flip], self._status_host[self._tok_flip]
                     self._tok_flip ^= 1
                     n_s = toks.shape[0]
                     buf[:n_s].copy_(toks, non_blocking=True)
                     done = None
                     if self.use_cuda:
+                        from onecat_vllm.ops import _C
+                        _C.read_status_async(sbuf)   # the kernels' status words ride along: no device-wide wait when they are read
                         done = torch.cuda.Event()
                         done.record()
                     self._prev_toks, self._prev_row = toks, {}
@@ -653,7 +664,7 @@ class ModelRunner:
                             self._prev_row[req_ids[i]] = j
                             self.requests[req_ids[i]].pending += 1
                             j += 1
-                    return PendingStep(out, rows, n_s, buf, done if done is not None else _Ready(), (ev0, ev1) if timed else None)
+                    return PendingStep(out, rows, n_s, buf, done if done is not None else _Ready(), (ev0, ev1) if timed else None, sbuf)
                 host = toks.tolist()  # device → host read of the step's result
                 self.d2h_bytes = len(host) * 8
                 j = 0

@@ -328,8 +328,12 @@ def main() -> None:
         if not any(rid in reqs and reqs[rid].num_computed_tokens < reqs[rid].num_prompt_tokens for rid in initial):
             break
         one_step()
-    for _ in range(args.warmup):
+    core = eng.engine_core
+    for i in range(args.warmup):
+        if i == args.warmup - 1:
+            core.call_utility("set_overlap", False)  # the last warm-up step leaves nothing in flight: the timed steps start from a drained engine
         one_step()
+    core.call_utility("set_overlap", True)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -341,11 +345,15 @@ def main() -> None:
     t0 = time.perf_counter()
     timing[0] = True
     tokens, dev_ms, sched_tokens, ttfts, step_ms = 0, 0.0, 0, [], []
+    dev_steps: list = []
     h2d = d2h = 0
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        if i == args.steps - 1:
+            core.call_utility("set_overlap", False)  # the K-th step launches nothing behind itself: exactly K steps run inside the timed region
         ts = time.perf_counter()
         n, ms, st_tok, outs = one_step()
         step_ms.append((time.perf_counter() - ts) * 1e3)
+        dev_steps.append(ms)
         tokens += n
         dev_ms += ms
         sched_tokens += st_tok
@@ -359,7 +367,11 @@ def main() -> None:
     if world > 1:
         dist.barrier()
     wall = time.perf_counter() - t0
+    core.call_utility("set_overlap", True)
     clocks = sampler.stop()
+    if os.environ.get("ONECAT_BENCH_DUMP") and rank == 0:   # per-step wall and device times, for looking at where host time goes
+        with open(os.environ["ONECAT_BENCH_DUMP"], "w") as f:
+            json.dump({"wall_ms": step_ms, "device_ms": dev_steps}, f)
     launches = K.launches() + getattr(runner, "graph_launches", 0)
     status = K.check_status()
     # ---- the whole workload the configuration names (4 x concurrency requests from an empty engine, ramp-up and tail included),

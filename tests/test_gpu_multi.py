@@ -333,3 +333,37 @@ def test_lora_tp2_matches_tp1_on_gpus(tmp_path):
     assert all(x[0] == y[0] for x, y in zip(got, ref)), f"TP2 LoRA first tokens differ: {got} vs {ref}"
     agree = sum(next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), len(x)) for x, y in zip(got, ref))
     assert agree / (12 * len(prompts)) > 0.4, f"TP2 LoRA diverges from one GPU too early: {got} vs {ref}"
+
+
+CFG_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=512, intermediate_size=1024, num_hidden_layers=3, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=128, rms_norm_eps=1e-6, rope_theta=1e6, vocab_size=2048, max_position_embeddings=2048,
+               tie_word_embeddings=False, num_experts=32, num_experts_per_tok=4, moe_intermediate_size=256, norm_topk_prob=True)
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("ep_comm", ["reduce", "a2a"])
+def test_engine_expert_parallel_two_gpus(tmp_path, monkeypatch, ep_comm):
+    """A Qwen-MoE engine with its experts split over two GPUs: partial sums through the fused reduction, or token exchange over
+    peer memory (each rank routes half of every batch, decode graphs included), against one GPU."""
+    _need2()
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    m = build_model(ModelConfig.from_hf_dict(CFG_MOE, dtype=torch.bfloat16), "cpu")
+    dummy_init(m, 0, std=0.05)
+    save_pretrained(m, CFG_MOE, str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 2048, (n,), generator=g).tolist() for n in (5, 40, 300, 64)]
+    sp = SamplingParams(temperature=0.0, max_tokens=16, ignore_eos=True)
+    kw = dict(model=str(tmp_path), device="cuda", dtype="bfloat16", max_model_len=1024, max_num_batched_tokens=512, max_num_seqs=8, gpu_memory_utilization=0.2)
+    one = LLM(**kw)
+    ref = [o.outputs[0].token_ids for o in one.generate(prompts, sp)]
+    one.shutdown()
+    monkeypatch.setenv("ONECAT_EP_COMM", ep_comm)
+    two = LLM(tensor_parallel_size=2, distributed_executor_backend="mp", enable_expert_parallel=True, **kw)
+    got = [o.outputs[0].token_ids for o in two.generate(prompts, sp)]
+    two.shutdown()
+    agree = sum(next((i for i, (a, b) in enumerate(zip(x, y)) if a != b), len(x)) for x, y in zip(got, ref))
+    assert all(x[0] == y[0] for x, y in zip(got, ref)), f"EP2 ({ep_comm}) first tokens differ: {got} vs {ref}"
+    assert agree / (16 * len(prompts)) > 0.4, f"EP2 ({ep_comm}) diverges from one GPU too early: {got} vs {ref}"

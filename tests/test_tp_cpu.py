@@ -109,3 +109,33 @@ def test_row_parallel_biases_join_the_sum_once(tmp_path):
     got = [o.outputs[0].token_ids for o in two.generate(prompts, sp)]
     two.shutdown()
     assert got == ref
+
+
+CFG_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256, num_experts=8, num_experts_per_tok=2,
+               moe_intermediate_size=32, norm_topk_prob=True)
+
+
+@pytest.mark.timeout(600)
+@pytest.mark.parametrize("ep_comm", ["reduce", "a2a"])
+def test_expert_parallel_two_ranks_match_one(tmp_path, monkeypatch, ep_comm):
+    """Expert parallelism over two gloo ranks, with the experts' partial sums riding the reduction and with tokens exchanged between
+    the ranks (each routes half of the batch): both must reproduce the single-rank tokens."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    m = build_model(ModelConfig.from_hf_dict(CFG_MOE, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    save_pretrained(m, CFG_MOE, str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 500, (n,), generator=g).tolist() for n in (9, 33, 1, 20)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    kw = dict(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)
+    one = LLM(**kw)
+    ref = [o.outputs[0].token_ids for o in one.generate(prompts, sp)]
+    one.shutdown()
+    monkeypatch.setenv("ONECAT_EP_COMM", ep_comm)
+    two = LLM(tensor_parallel_size=2, distributed_executor_backend="mp", enable_expert_parallel=True, **kw)
+    got = [o.outputs[0].token_ids for o in two.generate(prompts, sp)]
+    two.shutdown()
+    assert got == ref

@@ -33,8 +33,8 @@ def get_tokenizer(path: Optional[str]):
         return None
     if path == "byte":
         return ByteTokenizer()
-    from transformers import AutoTokenizer
-    return AutoTokenizer.from_pretrained(path)
+    from onecat_vllm.engine.renderers import load_tokenizer
+    return load_tokenizer(path)   # HF files, or Mistral's tekken.json when that is all the directory has
 
 
 class IncrementalDetokenizer:

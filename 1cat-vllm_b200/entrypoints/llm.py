@@ -50,7 +50,9 @@ class LLM:
         if tok is None:
             raise ValueError("chat() needs a tokenizer")
         convs = messages if messages and isinstance(messages[0], list) else [messages]
-        prompts = [tok.apply_chat_template(c, tokenize=False, add_generation_prompt=add_generation_prompt) for c in convs]
+        from onecat_vllm.engine.renderers import render_chat
+        arch = self.llm_engine.cfg.model_config.architecture
+        prompts = [render_chat(tok, c, architecture=arch, add_generation_prompt=add_generation_prompt, **kw) for c in convs]
         return self.generate(prompts, sampling_params)
 
     def beam_search(self, prompts: Sequence[PromptType], params: BeamSearchParams) -> list[dict]:

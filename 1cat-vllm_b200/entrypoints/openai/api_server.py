@@ -595,7 +595,10 @@ def build_app(state: ServingState) -> FastAPI:
         if req.tools and req.tool_choice != "none":
             kw["tools"] = req.tools
         try:
-            prompt = tok.apply_chat_template(msgs, tokenize=False, add_generation_prompt=req.add_generation_prompt, **kw)
+            from onecat_vllm.engine.renderers import render_chat
+            tools = kw.pop("tools", None)
+            prompt = render_chat(tok, msgs, architecture=state.engine.cfg.model_config.architecture, tools=tools,
+                                 add_generation_prompt=req.add_generation_prompt, **kw)
         except Exception as e:
             return JSONResponse(error_body(f"chat template failed: {e}"), status_code=400)
         if req.max_completion_tokens is not None and req.max_tokens is None:

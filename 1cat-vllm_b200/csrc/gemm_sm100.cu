@@ -248,7 +248,13 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   uint32_t chunk_i = 0;
   const bool silu = p.epi == EPI_SILU_MUL;
   const uint32_t stg_u32 = smem_u32(smem + L.stage_off);
-  const size_t sel_off = (p.n_push > 0 && p.push_sel != nullptr) ? (size_t)(*p.push_sel) * (size_t)p.push_sel_stride : 0;
+  // which of the rotating arrival buffers a tensor-parallel push goes to: a device word that the previous reduction kernel advances,
+  // so it is read only after this thread has passed pdl_wait()
+  size_t sel_off = 0;
+  auto load_sel = [&]() {
+    if (p.n_push > 0 && p.push_sel != nullptr) sel_off = (size_t)(*reinterpret_cast<const volatile int*>(p.push_sel)) * (size_t)p.push_sel_stride;
+  };
+  if (!pdl_roles) load_sel();
   auto strip = [](uint32_t w) -> uint32_t {  // bf16 -0.0 marks an empty slot of an arrival buffer: send +0.0 instead
     if ((w & 0xffffu) == 0x8000u) w &= 0xffff0000u;
     if ((w >> 16) == 0x8000u) w &= 0x0000ffffu;
@@ -579,7 +585,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
   } else if (warp < R::kEpi0) {
     // ------------------------------------------------------------------ 4-bit -> bf16 dequantisation
     if (WKIND >= 1) {
-      if (R::kDqDrains && pdl_roles) pdl_wait();  // a group that also drains accumulators writes global memory
+      if (R::kDqDrains && pdl_roles) {  // a group that also drains accumulators writes global memory
+        pdl_wait();
+        load_sel();
+      }
       const int r = (warp & 3) * 32 + lane;  // weight row = TMEM lane this warp may write
       const int grp = (warp - 2) >> 2;       // 0: even stages of the CTA's sequence, 1: odd ones (one group when SMALL)
       uint32_t seq = 0;
@@ -673,7 +682,10 @@ gemm_wx_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ 
     }
   } else if (!R::kDqDrains) {
     // ------------------------------------------------------------------ epilogue warps
-    if (pdl_roles) pdl_wait();   // outputs, split-K partials and counters may still be in use by the previous kernel
+    if (pdl_roles) {   // outputs, split-K partials and counters may still be in use by the previous kernel
+      pdl_wait();
+      load_sel();
+    }
     uint32_t tile_i = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++tile_i) ok = epilogue_item(w, tile_i);

@@ -142,11 +142,14 @@ class MultiprocExecutor(Executor):
 
     def _watch_workers(self) -> None:
         sentinels = [p.sentinel for p in self.procs]
-        mp_wait(sentinels)
-        if self._stop:
+        try:
+            mp_wait(sentinels)
+            dead = [p.name for p in self.procs if not p.is_alive()]
+        except (OSError, ValueError):
+            return   # the process objects were closed under us: the executor is being torn down
+        if self._stop or not dead:
             return
         self.is_failed = True
-        dead = [p.name for p in self.procs if not p.is_alive()]
         log.error(f"worker process(es) {dead} exited unexpectedly")
         cb = self.failure_callback
         if cb is not None:

@@ -1,6 +1,6 @@
 """Kernel micro-benchmarks with roofline fractions against the measured peaks of the box.
 
-``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe|sample|mla|rope|reject] [--small] [--json PATH]``
+``python -m onecat_vllm.ops.microbench [--only gemm|w4|wq|attn|attn_prefill|norm|gdn|gdn_prefill|moe|sample|mla|rope|reject|w4tp] [--small] [--json PATH]``
 Timing: CUDA events on the launching stream, 3 warm-up launches, an L2 flush (a 256 MB write) before every timed
 launch, median of ``--iters`` launches. ``--small`` runs one launch of one case per kernel (for ncu captures)."""
 from __future__ import annotations
@@ -91,6 +91,50 @@ def bench_w4(rows: list, small: bool, iters: int, pk: dict) -> None:
         rows.append(dict(kernel="gemm_w4a16", T=T, N=N, K=Kd, fused_silu=fuse, ms=ms, gbs=bytes_ / ms / 1e6, frac_of_hbm=bytes_ / ms / 1e6 / pk["hbm_gbs"],
                          tflops=tf, frac_of_peak=tf / pk["bf16_tflops"]))
         del layer, x, out
+
+
+def bench_w4_tp(rows: list, small: bool, iters: int, pk: dict) -> None:
+    """The four packed GEMMs of one dense-27B decoder layer at the slices a tensor-parallel rank holds (qkv and gate|up split by
+    output rows, o and down by k), decode-sized batches: flushed single launches and back-to-back launches inside a CUDA graph."""
+    from onecat_vllm.ops import cuda as K
+
+    def graph_us(fn, n=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(n):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e3
+    for tp in ((8,) if small else (1, 2, 4, 8)):
+        for T in ((64,) if small else (64, 16)):
+            tot_cold = tot_graph = 0.0
+            for name, N, Kd, fuse in (("qkv", 7168 // tp, 5120, False), ("o", 5120, 5120 // tp, False), ("gate|up", 34816 // tp, 5120, True),
+                                      ("down", 5120, 17408 // tp, False)):
+                q = torch.randint(0, 16, (N, Kd), device="cuda", dtype=torch.uint8)
+                z = torch.randint(0, 16, (N, Kd // 128), device="cuda", dtype=torch.uint8)
+                s_ = (torch.rand(N, Kd // 128, device="cuda") * 0.01 + 1e-3).half()
+                layer = _L(fuse)
+                K.prepare_w4(layer, q, z, s_, 128)
+                del q, z, s_
+                x = torch.randn(T, Kd, device="cuda").bfloat16()
+                out = torch.empty(T, layer.kernel_state["n_out"], device="cuda", dtype=torch.bfloat16)
+                cold = timeit(lambda: K.linear(layer, x, out=out), 1 if small else iters, 1 if small else 3) * 1e3
+                warm = cold if small else graph_us(lambda: K.linear(layer, x, out=out))
+                tot_cold += cold
+                tot_graph += warm
+                rows.append(dict(kernel="gemm_w4a16_tp_slice", tp=tp, proj=name, T=T, N=N, K=Kd, us_flushed=cold, us_in_graph=warm,
+                                 gbs=(N * Kd / 2) / cold / 1e3))
+                del layer, x, out
+            rows.append(dict(kernel="gemm_w4a16_tp_slice", tp=tp, proj="layer total", T=T, us_flushed=tot_cold, us_in_graph=tot_graph))
 
 
 def bench_attn(rows: list, small: bool, iters: int, pk: dict, prefill_only: bool = False) -> None:
@@ -328,11 +372,11 @@ def main() -> None:
     a = ap.parse_args()
     pk = _peaks()
     rows: list = []
-    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq), ("sample", bench_sample), ("mla", bench_mla),
+    for name, fn in (("gemm", bench_gemm), ("w4", bench_w4), ("attn", bench_attn), ("norm", bench_norm), ("gdn", bench_gdn), ("moe", bench_moe), ("wq", bench_wq), ("sample", bench_sample), ("mla", bench_mla), ("w4tp", bench_w4_tp),
                      ("rope", bench_rope), ("reject", bench_reject),
                      ("attn_prefill", lambda r, s_, i, p_: bench_attn(r, s_, i, p_, prefill_only=True)),
                      ("gdn_prefill", lambda r, s_, i, p_: bench_gdn(r, s_, i, p_, prefill_only=True))):
-        if not a.only and name in ("attn_prefill", "gdn_prefill"):
+        if not a.only and name in ("attn_prefill", "gdn_prefill", "w4tp"):
             continue
         if a.only and a.only != name:
             continue

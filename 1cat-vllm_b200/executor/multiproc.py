@@ -142,12 +142,13 @@ class MultiprocExecutor(Executor):
 
     def _watch_workers(self) -> None:
         sentinels = [p.sentinel for p in self.procs]
+        import sys
         try:
-            mp_wait(sentinels)
+            mp_wait(sentinels)   # a sentinel fires when its process has exited
             dead = [p.name for p in self.procs if not p.is_alive()]
         except (OSError, ValueError):
             return   # the process objects were closed under us: the executor is being torn down
-        if self._stop or not dead:
+        if self._stop or sys.is_finalizing():
             return
         self.is_failed = True
         log.error(f"worker process(es) {dead} exited unexpectedly")

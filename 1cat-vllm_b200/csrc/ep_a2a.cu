@@ -87,8 +87,9 @@ __global__ void __launch_bounds__(1024) ep_count_exchange_kernel(const EpParams 
   const int seq = s_seq;
   for (int i = threadIdx.x; i < p.n_pairs; i += blockDim.x) {
     const int e = p.ids[i];
+    // ids outside the expert range are skipped here and in every later stage: padded rows of a captured batch carry whatever
+    // their (unused) hidden state routes to
     if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
-    else atomicOr(&g_status, ST_BOUNDS);
   }
   __syncthreads();
   for (int r = 0; r < n; ++r) {

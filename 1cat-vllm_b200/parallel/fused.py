@@ -83,10 +83,12 @@ class FusedTP:
 
     def use_push(self, T: int) -> bool:
         """Whether the GEMM epilogue should push its tiles to the peers (overlapping the transfer with the GEMM) or leave them
-        local for the reduction kernel to pull. The epilogue's 64-byte row segments are a poor fit for NVLink at prefill sizes,
-        so by default only decode-sized batches push. ``ONECAT_TP_PUSH`` = always | never | auto."""
+        local for the reduction kernel to send or pull. Measured at TP2 / TP4: for decode-sized batches the flag-free reduction that
+        sends the rows itself is faster (26.6 against 30.1 us at TP4, one token: the few CTAs of a small GEMM issue all peers'
+        stores from their epilogue warps), for prefill-sized batches the push wins (478 against 543 us at 8192 tokens), so by default
+        only batches of 512 tokens and more push. ``ONECAT_TP_PUSH`` = always | never | auto."""
         mode = envs.ONECAT_TP_PUSH
-        return mode == "always" or (mode == "auto" and T <= 128)
+        return mode == "always" or (mode == "auto" and T >= 512)
 
     def push_spec(self, T: int):
         """Destinations for a row-parallel GEMM epilogue: slot ``[my rank]`` in every rank's slab. Decode-sized batches go to all
@@ -106,7 +108,7 @@ class FusedTP:
         return self.base + self.off_part[self.parity][self.rank] == t.data_ptr()
 
     def mode_for(self, T: int) -> int:
-        one = T * (self.tp - 1) <= 512 or self.tp == 2
+        one = T * (self.tp - 1) <= 1024 or self.tp == 2   # up to 1024 peer rows per rank: ~10 MB over NVLink, still cheaper than two phases
         if one and self.use_lamport and T <= self.lam_rows:
             return LAMPORT
         return ONE_SHOT if one else TWO_SHOT

@@ -82,8 +82,12 @@ def _fused_worker(rank, world, port, q, oneshot="lamport"):
                  (1, None, False), (256, None, False), (2, None, True)]
         for it, (T, mode, gemma) in enumerate(cases):
             check(it, T, mode, gemma)
-        for it, T in enumerate((1, 48, 64, 130, 300, 16, 16, 16)):  # GEMM + reduction with the tiles pushed from the epilogue
+        for it, T in enumerate((1, 48, 64, 130, 300, 16, 16, 16, 600, 1024)):  # GEMM + reduction; large batches push from the epilogue
             check(50 + it, T, None, it % 2 == 0, pushed_gemm=True)
+        os.environ["ONECAT_TP_PUSH"] = "always"   # decode-sized batches too: the epilogue stores into the peers' arrival buffers
+        for it, T in enumerate((1, 48, 64, 130, 16, 16, 16)):
+            check(70 + it, T, None, it % 2 == 0, pushed_gemm=True)
+        os.environ["ONECAT_TP_PUSH"] = "auto"
         # a captured reduction replayed back to back: the buffer rotation lives in device memory, so replays need no host state
         T = 8
         part = torch.full((T, H), float(rank + 1), device=dev).bfloat16()

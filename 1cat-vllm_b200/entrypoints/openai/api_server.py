@@ -707,6 +707,7 @@ def make_arg_parser() -> argparse.ArgumentParser:
     p.add_argument("model_tag", nargs="?", default=None)
     p.add_argument("--host", default="127.0.0.1")
     p.add_argument("--port", type=int, default=8000)
+    p.add_argument("--grpc-port", type=int, default=None, help="also serve the msgpack-over-gRPC endpoint (entrypoints/grpc_server.py) on this port")
     p.add_argument("--served-model-name", default=None)
     p.add_argument("--api-key", default=envs.ONECAT_API_KEY)
     p.add_argument("--tool-call-parser", default=None)
@@ -736,10 +737,17 @@ def run_server(args: argparse.Namespace) -> None:
 
     async def main():
         wd = asyncio.create_task(_watchdog(state, server))
+        grpc_server = None
+        if getattr(args, "grpc_port", None):
+            from onecat_vllm.entrypoints.grpc_server import serve_grpc
+            grpc_server, bound = await serve_grpc(engine, args.host, args.grpc_port)   # same engine, same event loop
+            log.info(f"gRPC endpoint on {args.host}:{bound}")
         try:
             await server.serve()
         finally:
             wd.cancel()
+            if grpc_server is not None:
+                await grpc_server.stop(1.0)
             engine.shutdown()
 
     asyncio.run(main())

@@ -388,3 +388,34 @@ class AsyncMPClient(_MPClientBase):
                 w.close()
             except Exception:
                 pass
+
+
+# ----------------------------------------------------------------------------- stand-alone engine core
+def main_headless(argv=None) -> None:
+    """``python -m onecat_vllm.engine.core_proc --input-addr A --output-addr B <engine args>``: an engine core that connects to
+    a front end which already listens on the two addresses (the native front end starts it this way). It speaks the same
+    handshake and frames as the engine processes the Python clients spawn, and exits when its parent does."""
+    import argparse
+    from onecat_vllm.config import EngineArgs
+    ap = argparse.ArgumentParser("engine-core")
+    ap.add_argument("--input-addr", required=True)
+    ap.add_argument("--output-addr", required=True)
+    ap.add_argument("--engine-index", type=int, default=0)
+    ap.add_argument("model_tag", nargs="?", default=None)
+    EngineArgs.add_cli_args(ap)
+    a = ap.parse_args(argv)
+    if a.model_tag:
+        a.model = a.model_tag
+    ea = EngineArgs.from_cli_args(a)
+    parent = os.getppid()
+
+    def watch_parent():
+        while os.getppid() == parent:
+            time.sleep(0.5)
+        os._exit(1)
+    threading.Thread(target=watch_parent, daemon=True).start()
+    run_engine_core(ea.create_engine_config(), a.input_addr, a.output_addr, a.engine_index, not ea.disable_log_stats, None)
+
+
+if __name__ == "__main__":
+    main_headless()

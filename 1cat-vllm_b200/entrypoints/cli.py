@@ -108,7 +108,13 @@ def _cmd_bench(argv):
     bench_main(argv)
 
 
-COMMANDS = {"serve": _cmd_serve, "chat": _cmd_chat, "complete": _cmd_complete, "bench": _cmd_bench, "run-batch": _cmd_run_batch,
+def _cmd_serve_native(argv):
+    """The C++ front end (HTTP server + tokenizer) in front of an engine-core process; see entrypoints/native_frontend.py."""
+    from onecat_vllm.entrypoints.native_frontend import main as native_main
+    native_main(argv)
+
+
+COMMANDS = {"serve": _cmd_serve, "serve-native": _cmd_serve_native, "chat": _cmd_chat, "complete": _cmd_complete, "bench": _cmd_bench, "run-batch": _cmd_run_batch,
             "collect-env": _cmd_collect_env}
 
 

@@ -278,8 +278,10 @@ torch::Tensor argmax(torch::Tensor x) {
   TORCH_CHECK(x.scalar_type() == torch::kBFloat16 || x.scalar_type() == torch::kFloat32, "argmax supports bf16 and fp32");
   const c10::cuda::CUDAGuard guard(x.device());
   auto out = torch::empty({x.size(0)}, x.options().dtype(torch::kInt64));
+  auto packed = torch::zeros({x.size(0)}, x.options().dtype(torch::kInt64));   // one (value key, ~index) word per row, folded with atomicMax
   TORCH_CHECK(oc::argmax_launch(x.data_ptr(), x.scalar_type() == torch::kFloat32, out.data_ptr<int64_t>() ? (long long*)out.data_ptr<int64_t>() : nullptr,
-                                (int)x.size(0), (int)x.size(1), x.stride(0), cur_stream()) == 0, "argmax failed");
+                                (unsigned long long*)packed.data_ptr<int64_t>(), (int)x.size(0), (int)x.size(1), x.stride(0), cur_stream()) == 0,
+              "argmax failed");
   return out;
 }
 

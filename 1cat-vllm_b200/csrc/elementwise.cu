@@ -194,19 +194,38 @@ __global__ void rope_cache_kernel(RopeCacheParams p) {
   }
 }
 
-// arg-max of each row of a [B, V] bf16/fp32 matrix; ties go to the lowest index (torch semantics).
+// arg-max of each row of a [B, V] bf16/fp32 matrix; ties go to the lowest index (torch semantics). A row is split over gridDim.y
+// CTAs; each folds its part into one 64-bit word per row with atomicMax: the high half is the value mapped to an order-preserving
+// unsigned key, the low half is ~index, so the largest word is the largest value at its lowest index. A second tiny kernel unpacks.
+__device__ __forceinline__ unsigned int float_order_key(float v) {
+  unsigned int b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
 template <typename T>
-__global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, long long* __restrict__ out, int V, long long ld) {
-  __shared__ float sv[32];
+__global__ void __launch_bounds__(256) argmax_partial_kernel(const T* __restrict__ x, unsigned long long* __restrict__ packed, int V, long long ld, int vec) {
+  __shared__ float sv[8];
+  __shared__ int si[8];
   pdl_trigger();
   pdl_wait();
-  __shared__ int si[32];
   const T* r = x + (size_t)blockIdx.x * ld;
+  const int per = (((V + gridDim.y - 1) / gridDim.y) + 7) & ~7;
+  const int lo = blockIdx.y * per, hi = min(lo + per, V);
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    float v = (float)r[i];
-    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+  auto take = [&](float v, int i) { if (v > best || (v == best && i < bi)) { best = v; bi = i; } };
+  if (vec && sizeof(T) == 2) {  // 16-byte loads of eight bf16 (the caller checked the alignment of every row)
+    for (int i = lo + threadIdx.x * 8; i < hi; i += blockDim.x * 8) {
+      if (i + 8 <= hi) {
+        const uint4 q = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(r) + i);
+        const __nv_bfloat16* e = reinterpret_cast<const __nv_bfloat16*>(&q);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) take(__bfloat162float(e[j]), i + j);
+      } else {
+        for (int j = i; j < hi; ++j) take((float)r[j], j);
+      }
+    }
+  } else {
+    for (int i = lo + threadIdx.x; i < hi; i += blockDim.x) take((float)r[i], i);
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -216,18 +235,18 @@ __global__ void __launch_bounds__(1024) argmax_kernel(const T* __restrict__ x, l
   }
   if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
   __syncthreads();
-  if (threadIdx.x < 32) {
-    int nw = blockDim.x >> 5;
-    best = threadIdx.x < nw ? sv[threadIdx.x] : -INFINITY;
-    bi = threadIdx.x < nw ? si[threadIdx.x] : 0x7fffffff;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      float ov = __shfl_xor_sync(0xffffffffu, best, o);
-      int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
-    }
-    if (threadIdx.x == 0) out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > best || (sv[w] == best && si[w] < bi)) { best = sv[w]; bi = si[w]; }
+    if (bi != 0x7fffffff)
+      atomicMax(&packed[blockIdx.x], ((unsigned long long)float_order_key(best) << 32) | (unsigned long long)(0xffffffffu - (unsigned int)bi));
   }
+}
+__global__ void argmax_unpack_kernel(const unsigned long long* __restrict__ packed, long long* __restrict__ out, int B) {
+  pdl_trigger();
+  pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < B) out[i] = packed[i] == 0ull ? 0 : (long long)(0xffffffffu - (unsigned int)(packed[i] & 0xffffffffull));
 }
 
 }  // namespace
@@ -304,10 +323,15 @@ int merge_attn_states_launch(const void* o1, const float* lse1, const void* o2, 
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 
-int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st) {
+// `packed` is B zeroed 64-bit words of scratch (zeroed by the caller before every call).
+int argmax_launch(const void* x, int is_fp32, long long* out, unsigned long long* packed, int B, int V, long long ld, cudaStream_t st) {
   if (B == 0) return 0;
-  if (is_fp32) launch_k(argmax_kernel<float>, dim3(B), dim3(1024), 0, st, true, (const float*)x, out, V, ld);
-  else launch_k(argmax_kernel<__nv_bfloat16>, dim3(B), dim3(1024), 0, st, true, (const __nv_bfloat16*)x, out, V, ld);
+  int splits = V >= (1 << 15) ? (B >= 128 ? 4 : 16) : 1;
+  const int vec = (!is_fp32 && ld % 8 == 0 && ((uintptr_t)x & 15) == 0) ? 1 : 0;
+  dim3 grid((unsigned)B, (unsigned)splits);
+  if (is_fp32) launch_k(argmax_partial_kernel<float>, grid, dim3(256), 0, st, true, (const float*)x, packed, V, ld, 0);
+  else launch_k(argmax_partial_kernel<__nv_bfloat16>, grid, dim3(256), 0, st, true, (const __nv_bfloat16*)x, packed, V, ld, vec);
+  launch_k(argmax_unpack_kernel, dim3((B + 255) / 256), dim3(256), 0, st, true, (const unsigned long long*)packed, out, B);
   return cudaGetLastError() == cudaSuccess ? 0 : -2;
 }
 

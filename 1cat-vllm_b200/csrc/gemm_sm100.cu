@@ -764,6 +764,10 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
     int waste256 = ((T + 255) / 256) * 256 - T, waste128 = ((T + 127) / 128) * 128 - T;
     if (waste128 + 64 < waste256 && T < 1024) tn = 128;
   }
+  if (w4 && T > 128) {
+    const int forced = env_int("ONECAT_W4_PREFILL_TN", 0);   // experiment switch: 128 or 192 tokens per tile for prefill-sized batches
+    if (forced == 128 || forced == 192) tn = forced;
+  }
   p.tn = tn;
   // decode-sized dense problems with packed weights run the light CTA variant, two per SM (grouped work lists keep the full one:
   // their items are token slices of many experts and the list is sized for one CTA per SM)
@@ -776,6 +780,15 @@ void gemm_plan(GemmParams& p, int num_sms, bool w4) {
   // K = 5120: 943 -> 988 and 933 -> 1027 TFLOP/s; K = 17408: 1129 -> 1170 TFLOP/s.
   const int nt_min_ktiles = env_int("ONECAT_W4_NTSUB_KTILES", 64);
   p.nt_sub = (w4 && p.work == nullptr && T > 2 * tn && p.K / BK >= nt_min_ktiles) ? 2 : 1;
+  if (p.nt_sub == 2) {
+    // Pairing halves the item count, which can cost a whole extra wave when there are few items: compare waves x cycles per k tile
+    // (measured at 192-token tiles: 1524 cycles for a paired item, 839 for a single one). Example, 1088 tokens x 7168 rows: 168 paired
+    // items = 2 waves (135 us measured) against 336 single items = 3 waves (121 us).
+    const long n_tiles = (p.n_rows + BM - 1) / BM;
+    const long items2 = n_tiles * ((T + 2 * tn - 1) / (2 * tn)), items1 = n_tiles * ((T + tn - 1) / tn);
+    const long waves2 = (items2 + slots - 1) / slots, waves1 = (items1 + slots - 1) / slots;
+    if (waves1 * 839 < waves2 * 1524) p.nt_sub = 1;
+  }
   p.num_t_tiles = (T + tn * p.nt_sub - 1) / (tn * p.nt_sub);
   p.num_n_tiles = (p.n_rows + BM - 1) / BM;
   int ktiles = p.K / BK;

@@ -26,7 +26,7 @@ int rms_norm_gated_launch(const void* x, const void* z, const void* w, void* y, 
                           float eps, cudaStream_t st);
 int silu_and_mul_launch(const void* x, void* y, int T, int I, cudaStream_t st);
 int rope_cache_launch(const RopeCacheParams& p, cudaStream_t st);
-int argmax_launch(const void* x, int is_fp32, long long* out, int B, int V, long long ld, cudaStream_t st);
+int argmax_launch(const void* x, int is_fp32, long long* out, unsigned long long* packed, int B, int V, long long ld, cudaStream_t st);
 int merge_attn_states_launch(const void* o1, const float* lse1, const void* o2, const float* lse2, void* out, float* lse_out, int rows, int D,
                              cudaStream_t st);
 unsigned int elementwise_read_status(bool clear);

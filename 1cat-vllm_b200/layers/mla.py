@@ -51,6 +51,13 @@ class MLAAttention(nn.Module):
             self.scale *= m * m
         self._wuk = self._wuv = None
 
+    def process_weights_after_loading(self):
+        """Runs before the child layers' own repacking (parents come first in ``modules()``): the absorbed ``W_UK`` / ``W_UV`` are
+        taken from ``kv_b_proj`` while its checkpoint tensors still exist — a quantised ``kv_b_proj`` is packed for the GEMM
+        afterwards and can no longer be dequantised on the host side."""
+        self._wuk = self._wuv = None
+        self._absorb(self.kv_b_proj.compute_dtype)
+
     def _absorb(self, dtype):
         if self._wuk is None:
             w = self.kv_b_proj.method.dequantized_weight(self.kv_b_proj).to(dtype).view(self.H, self.nope + self.vd, self.lora)

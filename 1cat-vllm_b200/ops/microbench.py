@@ -72,7 +72,8 @@ def bench_gemm(rows: list, small: bool, iters: int, pk: dict) -> None:
 def bench_w4(rows: list, small: bool, iters: int, pk: dict) -> None:
     from onecat_vllm.ops import cuda as K
     cases = [(64, 7168, 5120, False), (64, 34816, 5120, True), (64, 5120, 17408, False), (64, 5120, 5120, False), (1, 34816, 5120, True),
-             (256, 34816, 5120, True), (1088, 34816, 5120, True), (8192, 34816, 5120, True), (8192, 5120, 17408, False)]
+             (256, 34816, 5120, True), (1088, 34816, 5120, True), (1088, 7168, 5120, False), (1088, 5120, 5120, False), (1088, 5120, 17408, False),
+             (8192, 34816, 5120, True), (8192, 5120, 17408, False)]
     if small:
         cases = [(64, 34816, 5120, True), (64, 7168, 5120, False)]
     for T, N, Kd, fuse in cases:

@@ -87,10 +87,14 @@ class KVCacheManager:
     def enable_kv_connector(self, kv_transfer_config: dict) -> None:
         from onecat_vllm.core.kv_offload import SharedStorageTier
         name = kv_transfer_config.get("kv_connector", "SharedStorageConnector")
-        if name not in ("SharedStorageConnector", "ExampleConnector"):
-            raise ValueError(f"unknown kv_connector {name!r}: this build has SharedStorageConnector")
+        if name not in ("SharedStorageConnector", "ExampleConnector", "P2pConnector", "P2pNcclConnector"):
+            raise ValueError(f"unknown kv_connector {name!r}: this build has SharedStorageConnector and P2pConnector")
         extra = kv_transfer_config.get("kv_connector_extra_config") or {}
-        if self.enable_caching:
+        if self.enable_caching and name.startswith("P2p"):
+            from onecat_vllm.core.kv_p2p import P2pTier
+            self.offload = self.block_pool.offload = P2pTier(extra.get("host", "127.0.0.1"), int(extra.get("port", 14579)),
+                                                             kv_transfer_config.get("kv_role", "kv_consumer"))
+        elif self.enable_caching:
             self.offload = self.block_pool.offload = SharedStorageTier(extra.get("shared_storage_path", "/tmp/onecat_kv"),
                                                                        kv_transfer_config.get("kv_role", "kv_both"))
 

@@ -506,8 +506,15 @@ class ModelRunner:
     def _file_kv(self, so: SchedulerOutput) -> None:
         """Shared-storage connector: restores read ``[layers][page]`` tensors written by this or another engine. Saves are
         deferred until the step's forward has filled the blocks (``_save_kv_files``). Each rank writes its own shard."""
+        from onecat_vllm.core import kv_p2p
         for f, g in so.kv_swap_in:
-            pages = torch.load(self._rank_file(f), map_location="cpu", weights_only=True)
+            if kv_p2p.is_p2p(f):
+                host, port = self._p2p_endpoint()
+                pages = kv_p2p.fetch_pages(host, port, f[len(kv_p2p.SCHEME):])
+                if pages is None:
+                    raise RuntimeError(f"the KV producer at {host}:{port} no longer holds block {f}")
+            else:
+                pages = torch.load(self._rank_file(f), map_location="cpu", weights_only=True)
             for dev, pg in zip(self.kv_caches, pages):
                 dev[g].copy_(pg.to(self.device))
         self._pending_saves = list(so.kv_swap_out)
@@ -515,9 +522,22 @@ class ModelRunner:
     def _rank_file(self, f: str) -> str:
         return f if self.pp.world_size == 1 else f"{f}.r{self.pp.rank}"
 
+    def _p2p_endpoint(self) -> tuple:
+        """This rank's end of the peer-to-peer KV connector: producer rank r listens on ``port + r``, consumer rank r asks there."""
+        extra = (self.cfg.cache_config.kv_transfer_config or {}).get("kv_connector_extra_config") or {}
+        return extra.get("host", "127.0.0.1"), int(extra.get("port", 14579)) + self.pp.rank
+
     def _save_kv_files(self) -> None:
         import os
+        from onecat_vllm.core import kv_p2p
         for g, f in self._pending_saves:
+            if kv_p2p.is_p2p(f):
+                if getattr(self, "_kv_server", None) is None:
+                    host, port = self._p2p_endpoint()
+                    extra = (self.cfg.cache_config.kv_transfer_config or {}).get("kv_connector_extra_config") or {}
+                    self._kv_server = kv_p2p.KVPageServer(host, port, int(extra.get("capacity_blocks", 4096)))
+                self._kv_server.put(f[len(kv_p2p.SCHEME):], [dev[g].cpu() for dev in self.kv_caches])
+                continue
             f = self._rank_file(f)
             tmp = f"{f}.tmp{os.getpid()}"
             torch.save([dev[g].cpu() for dev in self.kv_caches], tmp)

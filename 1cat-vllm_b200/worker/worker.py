@@ -208,6 +208,9 @@ class Worker:
         if r is not None and getattr(r, "graphs", None) is not None:
             r.graphs.release()
             r.graphs = None
+        if r is not None and getattr(r, "_kv_server", None) is not None:
+            r._kv_server.close()   # peer-to-peer KV connector: stop serving saved blocks
+            r._kv_server = None
         self.runner = None
         r = None
         gc.collect()

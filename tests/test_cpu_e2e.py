@@ -297,3 +297,31 @@ def test_sliding_window_block_release_does_not_change_the_tokens():
     tb = [o.outputs[0].token_ids for o in b.generate(prompts, sp)]
     b.shutdown()
     assert ta == tb
+
+
+def test_p2p_connector_serves_prefill_kv_to_a_decode_engine():
+    """Disaggregated prefill / decode over the peer-to-peer connector: the producer keeps the prompt's blocks in host memory and serves
+    them over a socket while it lives; the consumer restores them by hash and decodes the same tokens as a stand-alone engine."""
+    from onecat_vllm import LLM, SamplingParams
+    from onecat_vllm.executor.multiproc import _free_port
+    cfg = dict(architectures=["Qwen3ForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=512)
+    prompt = [{"prompt_token_ids": [(7 * i) % 290 + 1 for i in range(100)]}]
+    kw = dict(hf_config=cfg, device="cpu", dtype="float32", max_model_len=256)
+    port = _free_port()
+    ktc = lambda role: {"kv_connector": "P2pConnector", "kv_role": role, "kv_connector_extra_config": {"host": "127.0.0.1", "port": port}}
+    solo = LLM(**kw)
+    want = solo.generate(prompt, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0].outputs[0].token_ids
+    solo.shutdown()
+    prefill = LLM(kv_transfer_config=ktc("kv_producer"), **kw)
+    first = prefill.generate(prompt, SamplingParams(temperature=0.0, max_tokens=1))[0].outputs[0].token_ids
+    decode = LLM(kv_transfer_config=ktc("kv_consumer"), **kw)
+    out = decode.generate(prompt, SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True))[0]
+    tier = decode.llm_engine.engine_core.core.scheduler.kv_cache_manager.offload
+    assert out.outputs[0].token_ids == want and first == want[:1]
+    assert tier.restored == 100 // 16 and out.num_cached_tokens == 96 and tier.stored == 0
+    # a prompt the producer never saw finds nothing and is computed locally
+    other = decode.generate([{"prompt_token_ids": [3] * 40}], SamplingParams(temperature=0.0, max_tokens=2))[0]
+    assert other.num_cached_tokens == 0
+    prefill.shutdown()
+    decode.shutdown()

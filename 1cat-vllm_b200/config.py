@@ -172,7 +172,7 @@ class ModelConfig:
     eos_token_id: Optional[int] = None
     bos_token_id: Optional[int] = None
     seed: int = 0
-    load_format: str = "auto"  # auto | safetensors | dummy
+    load_format: str = "auto"  # auto | safetensors | gguf | dummy
     tokenizer: Optional[str] = None
     enable_lora: bool = False  # build the model so that adapters can be applied (gate|up without the fused SiLU·mul epilogue)
     enable_sleep_mode: bool = False  # weights and KV cache live in releasable device memory (utils/cumem.py)
@@ -390,9 +390,22 @@ class ModelConfig:
 
     @classmethod
     def from_pretrained(cls, path: str, **over) -> "ModelConfig":
-        with open(os.path.join(path, "config.json")) as f:
-            hf = json.load(f)
-        return cls.from_hf_dict(hf, model=path, **over)
+        from onecat_vllm.loader import gguf
+        gpath = gguf.resolve(path)
+        cdir = path if os.path.isdir(path) else os.path.dirname(path)
+        if gpath is not None and not os.path.exists(os.path.join(cdir, "config.json")):
+            f = gguf.GGUFFile(gpath)  # a bare .gguf file: the architecture comes from its metadata
+            hf = gguf.config_from_metadata(f.metadata, f.tensors)
+            if over.get("tokenizer") is None and "tokenizer.ggml.tokens" in f.metadata:
+                over["tokenizer"] = gpath  # ... and so does the tokenizer, when the file embeds one
+        else:
+            with open(os.path.join(cdir, "config.json")) as f:
+                hf = json.load(f)
+        if gpath is not None:
+            hf.pop("quantization_config", None)  # ggml blocks are dequantised while loading
+            if over.get("load_format", "auto") == "auto":
+                over["load_format"] = "gguf"
+        return cls.from_hf_dict(hf, model=gpath or path, **over)
 
 
 # ----------------------------------------------------------------------------- cache / parallel / scheduler

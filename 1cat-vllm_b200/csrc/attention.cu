@@ -16,6 +16,7 @@
 // (reference: flash-attention-v100/kernel/fused_mha_forward_paged.cu:364, flash_decode_paged.cu:667,831,1301;
 //  v1/attention/backends/flash_attn_v100.py:2216 for the math)
 #include <cuda_fp8.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 #include "kernels.h"
@@ -69,11 +70,11 @@ __device__ __forceinline__ void widen_fp8x16(const uint4& in, uint4& lo, uint4& 
   hi = make_uint4(widen_fp8_pair(in.z, 0x1404u), widen_fp8_pair(in.z, 0x3424u), widen_fp8_pair(in.w, 0x1404u), widen_fp8_pair(in.w, 0x3424u));
 }
 
-template <int D, int MODE, int MB, bool KV8>
+template <int D, int MODE, int MB, bool KV8, int ST = 3>
 __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   pdl_trigger();
   pdl_wait();
-  constexpr int STAGES = 3;                     // K/V tiles in the cp.async ring (a fourth stage of byte tiles measured no faster)
+  constexpr int STAGES = ST;                    // K/V tiles in the cp.async ring (a fourth stage of byte tiles measured no faster)
   constexpr int MBW = (MODE == 0) ? 1 : MB;     // 16-row blocks per warp
   constexpr int NB2 = (MODE == 0) ? 4 : 1;      // 16-key groups per warp per tile
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
@@ -138,17 +139,6 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   const int* bt = p.block_table + (size_t)r * p.bt_stride;
   const size_t page_elems = (size_t)p.bs * D;
 
-  // ---- Q tile -> shared memory (zero rows past the end)
-  for (int idx = threadIdx.x; idx < ROWS * CH; idx += 128) {
-    int row = idx / CH, ch = idx % CH;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (row < nrows) {
-      int tok = tq0 + row / G, gh = row % G;
-      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(qs + tok) * p.q_st + (size_t)(hkv * G + gh) * p.q_sh + ch * 8);
-    }
-    *reinterpret_cast<uint4*>(sQ + sw_off<D>(row, ch)) = v;
-  }
-
   // each thread always copies the same 16-byte column chunk of rows (tid / CH) + i * (128 / CH); pages are a power of
   // two tokens long, so the block-table lookup is a shift and a mask
   constexpr int LCH = KV8 ? D / 16 : CH;        // 16-byte chunks per cache row
@@ -158,23 +148,47 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
   // byte addressing covers both element sizes
   const uint8_t* kv_head = reinterpret_cast<const uint8_t*>(p.kv_cache) + ((size_t)hkv * page_elems) * ESZ + ld_ch * 16;
   const size_t blk_stride = (size_t)2 * p.Hkv * page_elems * ESZ, v_off = (size_t)p.Hkv * page_elems * ESZ;
+  // One block-table lookup per 16-key chunk of the tile: pages are at least 16 keys long and tiles start at multiples of 64, so
+  // the 16 / kRowStep rows that a thread copies inside a chunk share a page.
   auto load_tile = [&](int tile, int buf) {
     const int k0 = tile * kKeysPerTile;
     uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * ESZ;
     uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * ESZ;
+    if constexpr (kRowStep <= 16) {
+      constexpr int RPC = 16 / kRowStep;
 #pragma unroll
-    for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
-      const int row = ld_row0 + i * kRowStep;
-      const int key = k0 + row;
-      const uint32_t off = KV8 ? (uint32_t)(row * D + ld_ch * 16) : sw_off<D>(row, ld_ch);
-      if (key < kv_end) {
-        const int blk = bt[key >> bs_shift];
-        const uint8_t* src = kv_head + (size_t)blk * blk_stride + (size_t)(key & bs_mask) * D * ESZ;
-        cp_async16(dk + off, src);
-        cp_async16(dv + off, src + v_off);
-      } else {
-        *reinterpret_cast<uint4*>(dk + off) = make_uint4(0, 0, 0, 0);
-        *reinterpret_cast<uint4*>(dv + off) = make_uint4(0, 0, 0, 0);
+      for (int c = 0; c < kKeysPerTile / 16; ++c) {
+        const int key_c = k0 + c * 16;
+        const uint8_t* src = kv_head;
+        if (key_c < kv_end) src += (size_t)bt[key_c >> bs_shift] * blk_stride + (size_t)((key_c & bs_mask) + ld_row0) * (D * ESZ);
+#pragma unroll
+        for (int j = 0; j < RPC; ++j) {
+          const int row = c * 16 + ld_row0 + j * kRowStep;
+          const uint32_t off = KV8 ? (uint32_t)(row * D + ld_ch * 16) : sw_off<D>(row, ld_ch);
+          if (k0 + row < kv_end) {
+            cp_async16(dk + off, src + (size_t)j * (kRowStep * D * ESZ));
+            cp_async16(dv + off, src + (size_t)j * (kRowStep * D * ESZ) + v_off);
+          } else {
+            *reinterpret_cast<uint4*>(dk + off) = make_uint4(0, 0, 0, 0);
+            *reinterpret_cast<uint4*>(dv + off) = make_uint4(0, 0, 0, 0);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
+        const int row = ld_row0 + i * kRowStep;
+        const int key = k0 + row;
+        const uint32_t off = KV8 ? (uint32_t)(row * D + ld_ch * 16) : sw_off<D>(row, ld_ch);
+        if (key < kv_end) {
+          const int blk = bt[key >> bs_shift];
+          const uint8_t* src = kv_head + (size_t)blk * blk_stride + (size_t)(key & bs_mask) * D * ESZ;
+          cp_async16(dk + off, src);
+          cp_async16(dv + off, src + v_off);
+        } else {
+          *reinterpret_cast<uint4*>(dk + off) = make_uint4(0, 0, 0, 0);
+          *reinterpret_cast<uint4*>(dv + off) = make_uint4(0, 0, 0, 0);
+        }
       }
     }
   };
@@ -202,6 +216,18 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     if (tile_lo + i < tile_hi) load_tile(tile_lo + i, i);
     cp_async_commit();
   }
+  // ---- Q tile -> shared memory (zero rows past the end), behind the first K/V copies so that its latency overlaps theirs; the
+  // first barrier of the loop publishes it
+  for (int idx = threadIdx.x; idx < ROWS * CH; idx += 128) {
+    int row = idx / CH, ch = idx % CH;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (row < nrows) {
+      int tok = tq0 + row / G, gh = row % G;
+      v = *reinterpret_cast<const uint4*>(p.q + (size_t)(qs + tok) * p.q_st + (size_t)(hkv * G + gh) * p.q_sh + ch * 8);
+    }
+    *reinterpret_cast<uint4*>(sQ + sw_off<D>(row, ch)) = v;
+  }
+
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int buf = (tile - tile_lo) % STAGES;
     cp_async_wait<STAGES - 2>();  // the group of this tile has landed (one group is committed per iteration)
@@ -257,6 +283,7 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
       }
     }
     // ---- mask, online softmax
+    float alpha_r[MBW][2];
 #pragma unroll
     for (int b = 0; b < MBW; ++b) {
 #pragma unroll
@@ -295,10 +322,19 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
         sum += __shfl_xor_sync(0xffffffffu, sum, 2);
         lrow[b][h] = lrow[b][h] * alpha + sum;
         mrow[b][h] = m_new;
+        alpha_r[b][h] = alpha;
+      }
+    }
+    // the running maxima settle after a few tiles: rescale the accumulator only when some row of the warp moved
+#pragma unroll
+    for (int b = 0; b < MBW; ++b) {
+      if (__any_sync(0xffffffffu, alpha_r[b][0] != 1.f || alpha_r[b][1] != 1.f)) {
 #pragma unroll
         for (int i = 0; i < D / 8; ++i) {
-          o[b][i][h * 2] *= alpha;
-          o[b][i][h * 2 + 1] *= alpha;
+          o[b][i][0] *= alpha_r[b][0];
+          o[b][i][1] *= alpha_r[b][0];
+          o[b][i][2] *= alpha_r[b][1];
+          o[b][i][3] *= alpha_r[b][1];
         }
       }
     }
@@ -430,19 +466,19 @@ __global__ void attn_combine_kernel(const AttnParams p) {
   if (p.lse != nullptr && lane == 0) p.lse[warp] = (M + log2f(L)) * 0.6931471805599453f;
 }
 
-template <int D, int MODE, int MB, bool KV8>
+template <int D, int MODE, int MB, bool KV8, int ST = 3>
 int launch_one(const AttnParams& p, cudaStream_t st) {
   constexpr int ROWS = (MODE == 0) ? 64 : 16 * MB;
-  const int smem = ROWS * D * 2 + (KV8 ? 2 * 3 * kKeysPerTile * D + 2 * kKeysPerTile * D * 2 : 2 * 3 * kKeysPerTile * D * 2);
+  const int smem = ROWS * D * 2 + (KV8 ? 2 * ST * kKeysPerTile * D + 2 * kKeysPerTile * D * 2 : 2 * ST * kKeysPerTile * D * 2);
   static int configured_dev[kMaxDevices] = {};
   int& configured = configured_dev[current_device_slot()];  // the limit is an attribute of (kernel, device)
   if (!configured) {
-    if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB, KV8>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
+    if (cudaFuncSetAttribute(attn_kernel<D, MODE, MB, KV8, ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) return -4;
     configured = 1;
   }
   dim3 grid(MODE == 0 ? p.num_q_tiles : p.R, p.Hkv, MODE == 0 ? 1 : p.splits);
   if (grid.x == 0) return 0;
-  launch_k(attn_kernel<D, MODE, MB, KV8>, grid, dim3(128), (size_t)smem, st, true, p);
+  launch_k(attn_kernel<D, MODE, MB, KV8, ST>, grid, dim3(128), (size_t)smem, st, true, p);
   if (MODE == 1 && p.splits > 1) {
     int rows = p.T * p.Hq;
     launch_k(attn_combine_kernel<D>, dim3((rows * 32 + 255) / 256), dim3(256), 0, st, true, p);
@@ -463,7 +499,12 @@ int attention_launch(const AttnParams& p, int mode, cudaStream_t st) {
       if (rows <= 16) return f8 ? launch_one<64, 1, 1, true>(p, st) : launch_one<64, 1, 1, false>(p, st);
       if (rows <= 32) return f8 ? launch_one<64, 1, 2, true>(p, st) : launch_one<64, 1, 2, false>(p, st);
     } else if (p.D == 128) {
-      if (rows <= 16) return f8 ? launch_one<128, 1, 1, true>(p, st) : launch_one<128, 1, 1, false>(p, st);
+      if (rows <= 16) {
+        if (f8) return launch_one<128, 1, 1, true>(p, st);
+        // two ring stages leave room for a third CTA per SM (experiment switch; three stages and two CTAs are the default)
+        static const int two_stage = getenv("ONECAT_ATTN_STAGES") && atoi(getenv("ONECAT_ATTN_STAGES")) == 2;
+        return two_stage ? launch_one<128, 1, 1, false, 2>(p, st) : launch_one<128, 1, 1, false>(p, st);
+      }
       if (rows <= 32) return f8 ? launch_one<128, 1, 2, true>(p, st) : launch_one<128, 1, 2, false>(p, st);
     } else {
       if (rows <= 16) return f8 ? launch_one<256, 1, 1, true>(p, st) : launch_one<256, 1, 1, false>(p, st);

@@ -255,6 +255,9 @@ def load_tokenizer(path: str, mode: str = "auto"):
     if mode == "byte" or path == "byte":
         from onecat_vllm.engine.tokenizer import ByteTokenizer
         return ByteTokenizer()
+    if os.path.isfile(path) and path.endswith(".gguf"):  # the tokenizer embedded in a GGUF file, rebuilt by transformers
+        from transformers import AutoTokenizer
+        return AutoTokenizer.from_pretrained(os.path.dirname(path) or ".", gguf_file=os.path.basename(path))
     tek = os.path.join(path, "tekken.json") if os.path.isdir(path) else (path if path.endswith("tekken.json") else None)
     has_hf = os.path.isdir(path) and any(os.path.exists(os.path.join(path, f)) for f in ("tokenizer.json", "tokenizer_config.json", "tokenizer.model"))
     if tek and os.path.exists(tek) and (mode == "mistral" or (mode == "auto" and not has_hf)):

@@ -268,9 +268,12 @@ def load_model(cfg, device) -> nn.Module:
         model = build_model(cfg, dev)
     fmt = cfg.load_format
     if fmt == "auto":
-        fmt = "safetensors" if os.path.isdir(cfg.model) else "dummy"
+        fmt = "safetensors" if os.path.isdir(cfg.model) else ("gguf" if str(cfg.model).endswith(".gguf") and os.path.isfile(cfg.model) else "dummy")
     if fmt == "dummy":
         dummy_init(model, cfg.seed)
+    elif fmt == "gguf":
+        from onecat_vllm.loader.gguf import iter_gguf, resolve
+        load_weights(model, iter_gguf(resolve(cfg.model) or cfg.model, cfg.dtype))
     else:
         load_weights(model, iter_safetensors(cfg.model))
     process_weights_after_loading(model)

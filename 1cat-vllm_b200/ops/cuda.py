@@ -404,6 +404,25 @@ def choose_kv_splits(base_ctas: int, max_seq: int, num_sms: int) -> int:
     return max(1, min(want, by_ctx, 32))
 
 
+def choose_decode_splits(base_ctas: int, max_seq: int, num_sms: int) -> int:
+    """KV splits of the paged decode kernel from a cost model of its waves. Two CTAs fit per SM; a CTA needs about 1.6 us to start
+    and 1.9 us per 64-key tile when the SMs are full, and more than one split adds the combine launch (about 6 us). Measured on
+    B200 (64 requests x 8 KV heads x 1150 keys): 71.7 us unsplit against 80.9 us in two splits, whose 1024 CTAs need four waves
+    of 296 where 512 need two; 16 requests x 4096 keys: 66 us in two splits (one wave) against 83 us in three (two waves)."""
+    nt = max(1, -(-max_seq // 64))
+    slots = 2 * num_sms
+    best, best_cost = 1, None
+    for s in range(1, min(32, nt) + 1):
+        per = -(-nt // s)
+        if s > 1 and per < 2:
+            break
+        waves = -(-(max(base_ctas, 1) * s) // slots)
+        cost = waves * (1.6 + 1.9 * per) + (6.0 + 0.15 * s if s > 1 else 0.0)  # the combine kernel reads one partial per split
+        if best_cost is None or cost < best_cost - 1e-9:
+            best, best_cost = s, cost
+    return best
+
+
 def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, num_sms: int, force_splits: int = 0):
     """Decide which requests take the decode kernel (rows = q_len * group fit in one 16/32-row tile) and how many KV
     splits it uses. Returns (short_q_len, num_q_tiles for the prefill kernel, splits)."""
@@ -418,7 +437,7 @@ def plan_attention(query_lens: list, seq_lens: list, Hq: int, Hkv: int, D: int, 
     splits = 1
     if n_short:
         max_s = max((s for q, s in zip(query_lens, seq_lens) if q <= short), default=1)
-        splits = choose_kv_splits(n_short * Hkv, max_s, num_sms)
+        splits = choose_decode_splits(n_short * Hkv, max_s, num_sms)
     if force_splits:
         splits = force_splits
     return short, tiles, splits

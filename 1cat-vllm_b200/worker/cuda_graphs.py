@@ -59,12 +59,11 @@ class DecodeGraphs:
         if not self.eligible or R > self.sizes[-1] or q > self.max_q:
             return None
         rp = self.sizes[bisect.bisect_left(self.sizes, R)]
-        from onecat_vllm.ops.cuda import _sms, choose_kv_splits
+        from onecat_vllm.ops.cuda import _sms, choose_decode_splits, choose_kv_splits
         if self.geom[0] == "mla":
-            base = rp * (-(-q * self.geom[1] // 16))
+            want = choose_kv_splits(rp * (-(-q * self.geom[1] // 16)), max_seq, _sms(self.r.device))
         else:
-            base = rp * self.geom[1]
-        want = choose_kv_splits(base, max_seq, _sms(self.r.device))
+            want = choose_decode_splits(rp * self.geom[1], max_seq, _sms(self.r.device))
         s = 1  # bucketed to powers of two (rounding up keeps the grid sized for the live context)
         while s < want:
             s *= 2

@@ -193,6 +193,31 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     }
   };
 
+  // Decode with a bf16 cache: the four warps see disjoint keys, so each warp streams its own 16 keys of every tile through its own
+  // cp.async groups and the main loop needs no CTA-wide barrier: the warps drift apart and hide one another's latencies (measured
+  // in lock step, a CTA took 1.9 us per tile, a dependent chain of copy wait, barrier, QK, softmax, PV).
+  constexpr bool WARP_PIPE = (MODE == 1) && !KV8;
+  const uint8_t* kv_warp = reinterpret_cast<const uint8_t*>(p.kv_cache) + ((size_t)hkv * page_elems) * ESZ;
+  auto load_tile_w = [&](int tile, int buf) {
+    const int key0 = tile * kKeysPerTile + warp * 16;
+    uint8_t* dk = sK + (size_t)buf * kKeysPerTile * D * ESZ;
+    uint8_t* dv = sV + (size_t)buf * kKeysPerTile * D * ESZ;
+    const uint8_t* src = kv_warp;
+    if (key0 < kv_end) src += (size_t)bt[key0 >> bs_shift] * blk_stride + (size_t)(key0 & bs_mask) * (D * ESZ);
+#pragma unroll
+    for (int i = 0; i < 16 * CH / 32; ++i) {
+      const int idx = lane + 32 * i, rl = idx / CH, ch = idx % CH;
+      const uint32_t off = sw_off<D>(warp * 16 + rl, ch);
+      if (key0 + rl < kv_end) {
+        cp_async16(dk + off, src + (size_t)rl * (D * ESZ) + ch * 16);
+        cp_async16(dv + off, src + (size_t)rl * (D * ESZ) + ch * 16 + v_off);
+      } else {
+        *reinterpret_cast<uint4*>(dk + off) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(dv + off) = make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+
   float o[MBW][D / 8][4];
   float mrow[MBW][2], lrow[MBW][2];
 #pragma unroll
@@ -213,7 +238,10 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
 
 #pragma unroll
   for (int i = 0; i < STAGES - 1; ++i) {
-    if (tile_lo + i < tile_hi) load_tile(tile_lo + i, i);
+    if (tile_lo + i < tile_hi) {
+      if constexpr (WARP_PIPE) load_tile_w(tile_lo + i, i);
+      else load_tile(tile_lo + i, i);
+    }
     cp_async_commit();
   }
   // ---- Q tile -> shared memory (zero rows past the end), behind the first K/V copies so that its latency overlaps theirs; the
@@ -227,12 +255,18 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     }
     *reinterpret_cast<uint4*>(sQ + sw_off<D>(row, ch)) = v;
   }
+  if constexpr (WARP_PIPE) __syncthreads();  // publishes the Q tile; the loop below has no CTA-wide barrier
 
   for (int tile = tile_lo; tile < tile_hi; ++tile) {
     const int buf = (tile - tile_lo) % STAGES;
     cp_async_wait<STAGES - 2>();  // the group of this tile has landed (one group is committed per iteration)
-    __syncthreads();               // ...for every thread, and everybody has finished the buffer refilled below
-    if (tile + STAGES - 1 < tile_hi) load_tile(tile + STAGES - 1, (tile - tile_lo + STAGES - 1) % STAGES);
+    if constexpr (WARP_PIPE) {
+      __syncwarp();                // ...for every lane of this warp, whose ldmatrix reads of the buffer refilled below are done
+      if (tile + STAGES - 1 < tile_hi) load_tile_w(tile + STAGES - 1, (tile - tile_lo + STAGES - 1) % STAGES);
+    } else {
+      __syncthreads();             // ...for every thread, and everybody has finished the buffer refilled below
+      if (tile + STAGES - 1 < tile_hi) load_tile(tile + STAGES - 1, (tile - tile_lo + STAGES - 1) % STAGES);
+    }
     cp_async_commit();
     if (KV8) {
       // widen this tile's bytes into the bf16 working tiles (everyone is past the previous tile's MMAs: barrier above)

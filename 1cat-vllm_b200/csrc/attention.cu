@@ -193,10 +193,11 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     }
   };
 
-  // Decode with a bf16 cache: the four warps see disjoint keys, so each warp streams its own 16 keys of every tile through its own
-  // cp.async groups and the main loop needs no CTA-wide barrier: the warps drift apart and hide one another's latencies (measured
-  // in lock step, a CTA took 1.9 us per tile, a dependent chain of copy wait, barrier, QK, softmax, PV).
-  constexpr bool WARP_PIPE = (MODE == 1) && !KV8;
+  // Decode: the four warps see disjoint keys, so each warp streams its own 16 keys of every tile through its own cp.async groups
+  // (and widens its own e4m3 bytes) and the main loop needs no CTA-wide barrier: the warps drift apart and hide one another's
+  // latencies (measured in lock step, a CTA took 1.9 us per tile, a dependent chain of copy wait, barrier, QK, softmax, PV).
+  constexpr bool WARP_PIPE = (MODE == 1);
+  constexpr int WCH = KV8 ? D / 16 : CH;        // 16-byte chunks per cache row
   const uint8_t* kv_warp = reinterpret_cast<const uint8_t*>(p.kv_cache) + ((size_t)hkv * page_elems) * ESZ;
   auto load_tile_w = [&](int tile, int buf) {
     const int key0 = tile * kKeysPerTile + warp * 16;
@@ -205,9 +206,9 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     const uint8_t* src = kv_warp;
     if (key0 < kv_end) src += (size_t)bt[key0 >> bs_shift] * blk_stride + (size_t)(key0 & bs_mask) * (D * ESZ);
 #pragma unroll
-    for (int i = 0; i < 16 * CH / 32; ++i) {
-      const int idx = lane + 32 * i, rl = idx / CH, ch = idx % CH;
-      const uint32_t off = sw_off<D>(warp * 16 + rl, ch);
+    for (int i = 0; i < 16 * WCH / 32; ++i) {
+      const int idx = lane + 32 * i, rl = idx / WCH, ch = idx % WCH;
+      const uint32_t off = KV8 ? (uint32_t)((warp * 16 + rl) * D + ch * 16) : sw_off<D>(warp * 16 + rl, ch);
       if (key0 + rl < kv_end) {
         cp_async16(dk + off, src + (size_t)rl * (D * ESZ) + ch * 16);
         cp_async16(dv + off, src + (size_t)rl * (D * ESZ) + ch * 16 + v_off);
@@ -269,21 +270,37 @@ __global__ void __launch_bounds__(128) attn_kernel(const AttnParams p) {
     }
     cp_async_commit();
     if (KV8) {
-      // widen this tile's bytes into the bf16 working tiles (everyone is past the previous tile's MMAs: barrier above)
       const uint8_t* k8 = sK + (size_t)buf * kKeysPerTile * D;
       const uint8_t* v8 = sV + (size_t)buf * kKeysPerTile * D;
+      if constexpr (WARP_PIPE) {
+        // this warp's 16 keys -> its rows of the bf16 working tiles (its own MMAs of the previous tile are done: program order)
 #pragma unroll
-      for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
-        const int row = ld_row0 + i * kRowStep;
-        uint4 lo, hi;
-        widen_fp8x16(*reinterpret_cast<const uint4*>(k8 + row * D + ld_ch * 16), lo, hi);
-        *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2)) = lo;
-        *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
-        widen_fp8x16(*reinterpret_cast<const uint4*>(v8 + row * D + ld_ch * 16), lo, hi);
-        *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2)) = lo;
-        *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
+        for (int i = 0; i < 16 * WCH / 32; ++i) {
+          const int idx = lane + 32 * i, row = warp * 16 + idx / WCH, ch = idx % WCH;
+          uint4 lo, hi;
+          widen_fp8x16(*reinterpret_cast<const uint4*>(k8 + row * D + ch * 16), lo, hi);
+          *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ch * 2)) = lo;
+          *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ch * 2 + 1)) = hi;
+          widen_fp8x16(*reinterpret_cast<const uint4*>(v8 + row * D + ch * 16), lo, hi);
+          *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ch * 2)) = lo;
+          *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ch * 2 + 1)) = hi;
+        }
+        __syncwarp();
+      } else {
+        // widen this tile's bytes into the bf16 working tiles (everyone is past the previous tile's MMAs: barrier above)
+#pragma unroll
+        for (int i = 0; i < kKeysPerTile / kRowStep; ++i) {
+          const int row = ld_row0 + i * kRowStep;
+          uint4 lo, hi;
+          widen_fp8x16(*reinterpret_cast<const uint4*>(k8 + row * D + ld_ch * 16), lo, hi);
+          *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2)) = lo;
+          *reinterpret_cast<uint4*>(sKb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
+          widen_fp8x16(*reinterpret_cast<const uint4*>(v8 + row * D + ld_ch * 16), lo, hi);
+          *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2)) = lo;
+          *reinterpret_cast<uint4*>(sVb + sw_off<D>(row, ld_ch * 2 + 1)) = hi;
+        }
+        __syncthreads();
       }
-      __syncthreads();
     }
     const uint32_t kb = smem_u32(KV8 ? sKb : sK + (size_t)buf * kKeysPerTile * D * 2);
     const uint32_t vb = smem_u32(KV8 ? sVb : sV + (size_t)buf * kKeysPerTile * D * 2);

@@ -167,6 +167,7 @@ class ModelConfig:
     mm_token_ids: Optional[dict] = None  # multimodal checkpoints: modality -> placeholder token id (image_token_id, video_token_id, ...)
     vision_config: Optional[dict] = None  # the checkpoint's vision tower (Qwen2-VL layout), when it has one
     vision_merge_size: int = 2
+    mrope_section: Optional[tuple] = None  # rotary frequencies split over the (temporal, height, width) position components (Qwen2-VL family)
     index_topk: int = 0  # DeepSeek-V3.2 sparse attention: keys kept per query by the lightning indexer (0: dense attention)
     quant: QuantConfig = field(default_factory=QuantConfig)
     eos_token_id: Optional[int] = None
@@ -294,6 +295,12 @@ class ModelConfig:
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
         rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
+        if rp.get("mrope_section"):
+            kw["mrope_section"] = tuple(int(x) for x in rp["mrope_section"])
+            rp = {k: v for k, v in rp.items() if k != "mrope_section"}
+            if (rp.get("rope_type") or rp.get("type")) == "mrope":  # the sections are the whole difference from the default rule
+                rp.pop("rope_type", None)
+                rp.pop("type", None)
         if isinstance(rp.get("full_attention"), dict):  # per-layer-type rotary parameters (Gemma3)
             kw["rope_theta"] = rp["full_attention"].get("rope_theta", kw["rope_theta"])
             kw["rope_local_theta"] = (rp.get("sliding_attention") or {}).get("rope_theta")

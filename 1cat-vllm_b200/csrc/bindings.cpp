@@ -150,7 +150,7 @@ torch::Tensor silu_and_mul(torch::Tensor x) {
 
 void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Tensor positions, torch::Tensor cos_sin,
                     c10::optional<torch::Tensor> kv_cache, torch::Tensor slot_mapping, int64_t rot, c10::optional<torch::Tensor> qn,
-                    c10::optional<torch::Tensor> kn, double eps, bool gemma, double k_scale, double v_scale) {
+                    c10::optional<torch::Tensor> kn, double eps, bool gemma, double k_scale, double v_scale, int64_t mrope_s0, int64_t mrope_s1) {
   check_bf16(q, "q");
   check_bf16(k, "k");
   check_bf16(v, "v");
@@ -168,6 +168,16 @@ void rope_and_cache(torch::Tensor q, torch::Tensor k, torch::Tensor v, torch::Te
   p.k_st = k.stride(0);
   p.v_st = v.stride(0);
   p.positions = positions.data_ptr<int>();
+  if (mrope_s0 > 0) {
+    TORCH_CHECK(positions.dim() == 2 && positions.size(0) == 3 && positions.size(1) == q.size(0) && positions.stride(1) == 1,
+                "rotary sections need positions [3, T]");
+    TORCH_CHECK(mrope_s1 >= mrope_s0 && mrope_s1 <= rot / 2, "rotary sections exceed the rotary width");
+    p.mrope_s0 = (int)mrope_s0;
+    p.mrope_s1 = (int)mrope_s1;
+    p.pos_stride = positions.stride(0);
+  } else {
+    TORCH_CHECK(positions.dim() == 1, "positions must be [T]");
+  }
   p.cos_sin = cos_sin.data_ptr<float>();
   p.slot_mapping = slot_mapping.data_ptr<int>();
   p.T = (int)q.size(0);

@@ -182,10 +182,17 @@ __global__ void rope_cache_kernel(RopeCacheParams p) {
   }
   const int half = p.rot >> 1;
   const float* cs = p.cos_sin + (size_t)p.positions[t] * p.rot;
+  const float *cs1 = cs, *cs2 = cs;
+  if (p.mrope_s0 > 0) {  // the height and width components of the position
+    cs1 = p.cos_sin + (size_t)p.positions[p.pos_stride + t] * p.rot;
+    cs2 = p.cos_sin + (size_t)p.positions[2 * p.pos_stride + t] * p.rot;
+  }
   for (int i = lane; i < D; i += 32) {
     float o;
-    if (i < half) o = buf[i] * cs[i] - buf[i + half] * cs[half + i];
-    else if (i < p.rot) o = buf[i] * cs[i - half] + buf[i - half] * cs[i];
+    const int f = i < half ? i : i - half;
+    const float* c = (p.mrope_s0 == 0 || f < p.mrope_s0) ? cs : (f < p.mrope_s1 ? cs1 : cs2);
+    if (i < half) o = buf[i] * c[i] - buf[i + half] * c[half + i];
+    else if (i < p.rot) o = buf[i] * c[i - half] + buf[i - half] * c[i];
     else o = buf[i];
     __nv_bfloat16 ob = __float2bfloat16(o);
     src[i] = ob;

@@ -18,6 +18,10 @@ struct RopeCacheParams {
   float eps;
   int kv_fp8;                    // kv_cache holds e4m3 bytes: k / k_scale and v / v_scale, saturated
   float k_scale_inv, v_scale_inv;
+  // rotary sections (0 = off): frequencies below mrope_s0 rotate by positions[t], below mrope_s1 by positions[pos_stride + t], the
+  // rest by positions[2 * pos_stride + t]
+  int mrope_s0, mrope_s1;
+  long long pos_stride;
 };
 
 int rms_norm_launch(const void* x, const void* res_in, const void* w, void* y, void* res_out, int T, int H, int ldx, float eps,

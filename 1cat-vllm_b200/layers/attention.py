@@ -35,6 +35,7 @@ class Attention(nn.Module):
         self.rotary_dim = 0 if layer_idx in cfg.nope_layers else cfg.rotary_dim
         self.qk_norm_full = cfg.qk_norm_full
         self.norm_after_rope = cfg.qk_norm and cfg.qk_norm_after_rope
+        self.mrope_section = getattr(cfg, "mrope_section", None)  # (temporal, height, width) frequency counts; positions are then [3, T]
         if cfg.qk_norm_full:
             if tp > 1:
                 raise ValueError("q / k normalisation over the whole projection is served with tensor_parallel_size=1 only")
@@ -78,8 +79,10 @@ class Attention(nn.Module):
             k = ops.rms_norm(k.view(T * Hkv, D), self.k_norm, self.eps, None, self.gemma)[0].view(T, Hkv, D)
             ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin[:, :0], kv_cache, md.slot_mapping, 0, None, None, self.eps, False)
         else:
-            ops.rope_and_cache(q, k, v, md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
-                               self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma)
+            mrope = self.mrope_section if md.mrope_positions is not None else None
+            ops.rope_and_cache(q, k, v, md.mrope_positions if mrope else md.positions, self.rope.cos_sin, kv_cache, md.slot_mapping, self.rotary_dim,
+                               self.q_norm if self.qk_norm else None, self.k_norm if self.qk_norm else None, self.eps, self.gemma,
+                               mrope_section=mrope)
         o = ops.paged_attention(q, kv_cache, md, self.scale, window=self.window, softcap=self.softcap, sinks=self.sinks)
         if gate is not None:
             o = o * torch.sigmoid(gate.float()).to(o.dtype)

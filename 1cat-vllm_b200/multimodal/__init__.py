@@ -118,6 +118,40 @@ class MultiModalProcessor:
         return ProcessedPrompt(out, feats)
 
 
+def mrope_positions(num_tokens: int, features: list, merge: int = 2, t_step: float = 1.0):
+    """(temporal, height, width) rotary positions of a prompt, ``int32 [3, num_tokens]``, and the offset that generated tokens add to
+    their index. Text tokens carry the same running value in all three rows; an item with a patch grid ``(t, h, w)`` places its
+    ``t * h/merge * w/merge`` positions on a grid starting at the running value, and the text after it continues from the largest
+    coordinate used plus one. Items given as bare embeddings have no grid and count like text.
+    (reference: model_executor/layers/rotary_embedding/mrope.py ``get_input_positions``; HF ``Qwen2VLModel.get_rope_index``)"""
+    import numpy as np
+    pos = np.zeros((3, num_tokens), dtype=np.int32)
+    cursor, nxt = 0, 0
+    for f in sorted(features or (), key=lambda x: x.offset):
+        n_text = f.offset - cursor
+        if n_text > 0:
+            pos[:, cursor:f.offset] = nxt + np.arange(n_text, dtype=np.int32)
+            nxt += n_text
+        grid = f.data.get("grid_thw") if isinstance(f.data, dict) else None
+        if grid is not None:
+            t, gh, gw = int(grid[0]), int(grid[1]) // merge, int(grid[2]) // merge
+            if t * gh * gw != f.length:
+                raise ValueError(f"item at {f.offset}: grid {tuple(grid)} does not give {f.length} positions")
+            ti = (np.arange(t, dtype=np.float64) * t_step).astype(np.int32)
+            pos[0, f.offset:f.offset + f.length] = nxt + np.repeat(ti, gh * gw)
+            pos[1, f.offset:f.offset + f.length] = nxt + np.tile(np.repeat(np.arange(gh, dtype=np.int32), gw), t)
+            pos[2, f.offset:f.offset + f.length] = nxt + np.tile(np.arange(gw, dtype=np.int32), t * gh)
+            nxt += max(int(ti[-1]) + 1, gh, gw)
+        else:
+            pos[:, f.offset:f.offset + f.length] = nxt + np.arange(f.length, dtype=np.int32)
+            nxt += f.length
+        cursor = f.offset + f.length
+    if cursor < num_tokens:
+        pos[:, cursor:] = nxt + np.arange(num_tokens - cursor, dtype=np.int32)
+        nxt += num_tokens - cursor
+    return pos, int(nxt - num_tokens)
+
+
 class MultiModalRegistry:
     """Architecture → processor factory (reference: ``MULTIMODAL_REGISTRY.register_processor``)."""
 

@@ -38,10 +38,12 @@ def gelu_tanh_and_mul(x):
 
 
 def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w=None, k_norm_w=None,
-                   eps=1e-6, gemma=False):
+                   eps=1e-6, gemma=False, mrope_section=None):
+    """``mrope_section`` (three frequency counts summing to ``rotary_dim / 2``) with ``positions`` of shape ``[3, T]``: frequency i
+    rotates by the temporal, height or width position according to the section it falls in (Qwen2-VL family)."""
     if q.is_cuda:
-        return ext().rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
-    return ref.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma)
+        return ext().rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, mrope_section)
+    return ref.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, mrope_section)
 
 
 def paged_attention(q, kv_cache, md, scale, out=None, window=0, softcap=0.0, sinks=None):

@@ -352,10 +352,11 @@ def silu_and_mul(x):
     return _C.silu_and_mul(x.contiguous())
 
 
-def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma):
+def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, mrope_section=None):
     global _LAUNCHES
     _LAUNCHES += 1
-    _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, 1.0, 1.0)
+    s0, s1 = (int(mrope_section[0]), int(mrope_section[0] + mrope_section[1])) if mrope_section is not None and positions.dim() == 2 else (0, 0)
+    _C.rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim, q_norm_w, k_norm_w, eps, gemma, 1.0, 1.0, s0, s1)
 
 
 def sample(logits, temperature, top_k=None, top_p=None, min_p=None, generators=None, kept=None):

@@ -140,13 +140,22 @@ def _head_norm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float, gemma: bo
 
 
 def rope_and_cache(q, k, v, positions, cos_sin, kv_cache, slot_mapping, rotary_dim: int,
-                   q_norm_w=None, k_norm_w=None, eps: float = 1e-6, gemma: bool = False) -> None:
+                   q_norm_w=None, k_norm_w=None, eps: float = 1e-6, gemma: bool = False, mrope_section=None) -> None:
     """In place: optional per-head RMSNorm on q/k, NeoX RoPE on the first ``rotary_dim`` dims, then K and V
     rows are written into the paged cache ``[blocks, 2, kv_heads, block_size, head]`` at ``slot_mapping``
     (slot = block * block_size + offset; negative = skip)."""
     T, Hq, D = q.shape
-    cs = cos_sin[positions.long()]
-    cos, sin = cs[:, : rotary_dim // 2], cs[:, rotary_dim // 2:]
+    if mrope_section is not None and positions.dim() == 2:
+        # frequency i takes the position component of the section it lies in (reference: rotary_embedding/mrope.py)
+        h = rotary_dim // 2
+        comp = torch.repeat_interleave(torch.arange(3, device=positions.device), torch.tensor(list(mrope_section), device=positions.device))[:h]
+        cs3 = cos_sin[positions.long()]                                     # [3, T, rotary_dim]
+        pick = comp.view(1, 1, h).expand(1, T, h)
+        cos = torch.gather(cs3[..., :h], 0, pick)[0]
+        sin = torch.gather(cs3[..., h:], 0, pick)[0]
+    else:
+        cs = cos_sin[positions.long()]
+        cos, sin = cs[:, : rotary_dim // 2], cs[:, rotary_dim // 2:]
     qn = _rope_neox(_head_norm(q, q_norm_w, eps, gemma), cos, sin, rotary_dim)
     kn = _rope_neox(_head_norm(k, k_norm_w, eps, gemma), cos, sin, rotary_dim)
     q.copy_(qn.to(q.dtype))

@@ -29,3 +29,4 @@ class AttentionMetadata:
     num_kv_splits: int = 1
     is_uniform_decode: bool = False
     uniform_query_len: int = 1
+    mrope_positions: Optional[torch.Tensor] = None  # int32 [3, T] (temporal, height, width) for models with rotary sections

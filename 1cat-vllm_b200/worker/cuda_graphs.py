@@ -75,6 +75,8 @@ class DecodeGraphs:
         md = AttentionMetadata(rp, T, r._view("qsl", rp + 1), r._view("seq", rp), r.d_bt[:rp], r._view("slot", T), r._view("pos", T),
                                q, 0, r._view("sslot", rp), r._view("hinit", rp), [q] * rp, [0] * rp, is_uniform_decode=True,
                                uniform_query_len=q)
+        if r._seg["pos3"]:
+            md.mrope_positions = r._view("pos3", 3 * r._tcap).view(3, r._tcap)[:, :T]
         if self.geom[0] == "mla":
             md.attn_plan = (("mla", self.geom[1], 512), (q, 0, splits))
         else:

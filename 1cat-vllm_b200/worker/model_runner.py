@@ -48,6 +48,8 @@ class CachedRequestState:
     pool_sum: Optional[torch.Tensor] = None  # running sum of hidden states (mean pooling over a chunked prompt)
     pool_first: Optional[torch.Tensor] = None  # hidden state of the first token (cls pooling)
     pending: int = 0  # tokens sampled by a step that is still in flight (async scheduling): on the device, not yet in token_ids
+    mrope: object = None  # int32 [3, prompt] rotary positions of a multimodal prompt (models with rotary sections), built on first use
+    mrope_delta: int = 0  # what a generated token adds to its index to get its (three equal) rotary positions
 
 
 class _Ready:
@@ -230,7 +232,9 @@ class ModelRunner:
 
         # one packed int32 staging area: ids | positions | slot_mapping | qsl | seq_lens | state_slots | has_init | logit_idx
         # pdst | psrc: where last step's sampled tokens (still on the device) go in this step's ids (async scheduling)
-        self._seg = {"ids": T, "pos": T, "slot": T, "qsl": R + 1, "seq": R, "sslot": R, "hinit": R, "lidx": T, "pdst": R, "psrc": R}
+        self._seg = {"ids": T, "pos": T, "slot": T, "qsl": R + 1, "seq": R, "sslot": R, "hinit": R, "lidx": T, "pdst": R, "psrc": R,
+                     "pos3": 3 * T if getattr(self.mc, "mrope_section", None) else 0}  # [3, T] rotary positions (models with rotary sections)
+        self._tcap = T
         total = sum(self._seg.values())
         self.h_pack = host(total, torch.int32)
         self.d_pack = torch.zeros(total, dtype=torch.int32, device=self.device)
@@ -322,6 +326,7 @@ class ModelRunner:
         pdst = npk[o["pdst"][0]: o["pdst"][0] + R]
         psrc = npk[o["psrc"][0]: o["psrc"][0] + R]
         n_patch = 0
+        pos3 = npk[o["pos3"][0]: o["pos3"][0] + 3 * self._tcap].reshape(3, self._tcap) if self._seg["pos3"] else None
         if self._h2d_done is not None:
             self._h2d_done.synchronize()   # the previous step's copy out of this staging area has finished (it has, long ago)
         for r, rid in enumerate(req_ids):
@@ -381,6 +386,16 @@ class ModelRunner:
             else:
                 logits_rows.append(0)
             drafts_of.append(drafts[: max(end - known_len, 0)])
+            if pos3 is not None:
+                seg = pos[t:t + n]
+                if st.mm_features and st.mrope is None:
+                    from onecat_vllm.multimodal import mrope_positions
+                    st.mrope, st.mrope_delta = mrope_positions(st.num_prompt_tokens, st.mm_features, getattr(self.mc, "vision_merge_size", 2))
+                if st.mrope is None:
+                    pos3[:, t:t + n] = seg
+                else:
+                    P = st.mrope.shape[1]
+                    pos3[:, t:t + n] = np.where(seg < P, st.mrope[:, np.minimum(seg, P - 1)], seg + st.mrope_delta)
             t += n
             qsl[r + 1] = t
             max_q, max_s = max(max_q, n), max(max_s, end)
@@ -395,6 +410,8 @@ class ModelRunner:
         tp = rp * q
         npk[o["ids"][0] + T: o["ids"][0] + tp] = 0
         npk[o["pos"][0] + T: o["pos"][0] + tp] = 0
+        if self._seg["pos3"]:
+            npk[o["pos3"][0]: o["pos3"][0] + 3 * self._tcap].reshape(3, self._tcap)[:, T:tp] = 0
         npk[o["slot"][0] + T: o["slot"][0] + tp] = -1
         npk[o["qsl"][0] + R + 1: o["qsl"][0] + rp + 1] = T
         npk[o["seq"][0] + R: o["seq"][0] + rp] = 0
@@ -426,7 +443,8 @@ class ModelRunner:
             block_table=self.d_bt[:R, :max_nb] if not self.use_cuda else self.d_bt[:R], slot_mapping=self._view("slot", T),
             positions=self._view("pos", T), max_query_len=max_q, max_seq_len=max_s, state_slots=self._view("sslot", R),
             has_initial_state=self._view("hinit", R), query_lens_cpu=query_lens, seq_lens_cpu=seq_lens,
-            is_uniform_decode=(max_q == min(query_lens)) and max_q <= 1 + self.num_spec, uniform_query_len=max_q)
+            is_uniform_decode=(max_q == min(query_lens)) and max_q <= 1 + self.num_spec, uniform_query_len=max_q,
+            mrope_positions=self._view("pos3", 3 * self._tcap).view(3, self._tcap)[:, :T] if self._seg["pos3"] else None)
 
     def _sampling_metadata(self, req_ids: list, rows: list[int]) -> SamplingMetadata:
         """One entry per *sampling request* (requests contributing logits rows this step)."""

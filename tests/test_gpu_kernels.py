@@ -83,6 +83,32 @@ def test_rope_and_cache(D, rot, qk_norm, gated):
     assert K().check_status() == 0
 
 
+def test_rope_with_rotary_sections():
+    """Positions [3, T] (temporal, height, width) with the frequencies split into sections, rows of a wider buffer."""
+    T, Hq, Hkv, D, bs, nb = 45, 4, 2, 128, 16, 8
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q = torch.randn(T, Hq, D, device="cuda", generator=g).bfloat16()
+    k = torch.randn(T, Hkv, D, device="cuda", generator=g).bfloat16()
+    v = torch.randn(T, Hkv, D, device="cuda", generator=g).bfloat16()
+    wide = torch.randint(0, 500, (3, 64), device="cuda", dtype=torch.int32, generator=g)
+    pos3 = wide[:, :T]                                  # row stride 64, as the runner's staging buffer gives it
+    cs = ref.build_cos_sin_cache(D, 512, 1e4, "cuda")
+    cache = torch.zeros(nb, 2, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
+    slots = torch.randperm(nb * bs, device="cuda")[:T].to(torch.int32)
+    qc, kc, vc, cache_c = q.cpu().clone(), k.cpu().clone(), v.cpu().clone(), cache.cpu().clone()
+    sec = (16, 24, 24)
+    ref.rope_and_cache(qc, kc, vc, pos3.cpu(), cs.cpu(), cache_c, slots.cpu(), D, None, None, 1e-6, False, sec)
+    K().rope_and_cache(q, k, v, pos3, cs, cache, slots, D, None, None, 1e-6, False, sec)
+    _close(q, qc, 2e-2, 2e-2, "q")
+    _close(cache, cache_c, 2e-2, 2e-2, "cache")
+    # the sections matter: the temporal row alone gives another rotation
+    q1 = qc.clone()
+    assert K().check_status() == 0
+    q2 = torch.randn(T, Hq, D, generator=torch.Generator().manual_seed(4)).bfloat16()
+    ref.rope_and_cache(q2, kc.clone(), vc.clone(), pos3[0].cpu(), cs.cpu(), None, slots.cpu(), D)
+    assert not torch.equal(q1, q2)
+
+
 def _ref_gemm(x, w):
     return x.float().cpu() @ w.float().cpu().t()
 

@@ -112,3 +112,53 @@ def test_vision_tower_matches_hugging_face():
         got = ours(pix, (t, h, w))
     assert got.shape == (t * h * w // 4, 48)
     assert torch.allclose(got, ref, atol=2e-4, rtol=2e-4), float((got - ref).abs().max())
+
+
+def test_qwen2_vl_with_an_image_matches_hugging_face(tmp_path):
+    """The whole model on a prompt with an image: vision tower, placeholder rows, and the (temporal, height, width) rotary positions
+    of the image grid and of the text after it. Greedy tokens must equal Hugging Face's."""
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import Qwen2VLConfig, Qwen2VLForConditionalGeneration
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no Qwen2-VL: {e}")
+    vc = dict(depth=2, embed_dim=32, hidden_size=64, num_heads=4, mlp_ratio=2, patch_size=4, spatial_merge_size=2, temporal_patch_size=2, in_channels=3)
+    text = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, vocab_size=300,
+                max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=1e4, rope_scaling={"type": "mrope", "mrope_section": [2, 3, 3]},
+                tie_word_embeddings=False)
+    cfg = Qwen2VLConfig(text_config=text, vision_config=vc, image_token_id=IMG, video_token_id=251, vision_start_token_id=252, vision_end_token_id=253)
+    torch.manual_seed(0)
+    hf = Qwen2VLForConditionalGeneration(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        torch.nn.init.normal_(p, std=0.5 if "norm" not in n else 0.1)
+        if "norm" in n and n.endswith("weight"):
+            p.data.add_(1.0)
+    hf.save_pretrained(str(tmp_path), safe_serialization=True)
+    import json
+    d = json.loads((tmp_path / "config.json").read_text())
+    d["architectures"] = ["Qwen2VLForConditionalGeneration"]
+    (tmp_path / "config.json").write_text(json.dumps(d))
+
+    t, h, w = 1, 4, 6                     # 24 patches -> 6 positions on a 2 x 3 grid
+    pix = torch.randn(t * h * w, 3 * 2 * 4 * 4)
+    n_img = t * h * w // 4
+    prompt = [5, 6, 252, IMG, 253, 7, 8, 9]
+    ids = torch.tensor([[5, 6, 252] + [IMG] * n_img + [253, 7, 8, 9]])
+    with torch.no_grad():
+        ref = hf.generate(input_ids=ids, attention_mask=torch.ones_like(ids), pixel_values=pix, image_grid_thw=torch.tensor([[t, h, w]]),
+                          mm_token_type_ids=(ids == IMG).long(), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0)[0, ids.shape[1]:].tolist()
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128)
+    assert llm.llm_engine.cfg.model_config.mrope_section == (2, 3, 3)
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    got = llm.generate([{"prompt_token_ids": prompt, "multi_modal_data": {"image": {"pixel_values": pix, "image_grid_thw": (t, h, w)}}}], sp)[0].outputs[0].token_ids
+    # the same prompt without the rotary sections' grid would differ: text-only request through the same engine stays consistent
+    plain = llm.generate([[5, 6, 7, 8, 9]], sp)[0].outputs[0].token_ids
+    with torch.no_grad():
+        ref_plain = hf.generate(input_ids=torch.tensor([[5, 6, 7, 8, 9]]), max_new_tokens=10, do_sample=False, eos_token_id=None, pad_token_id=0)[0, 5:].tolist()
+    llm.shutdown()
+    assert plain == ref_plain
+    assert got == ref
+    with torch.no_grad():  # ... and the grid matters: Hugging Face with sequential positions for the same inputs answers differently
+        seq = hf(input_ids=ids, attention_mask=torch.ones_like(ids), pixel_values=pix, image_grid_thw=torch.tensor([[t, h, w]]),
+                 mm_token_type_ids=(ids == IMG).long(), position_ids=torch.arange(ids.shape[1]).view(1, 1, -1).expand(3, 1, -1)).logits[0, -1].argmax().item()
+    assert seq != ref[0]

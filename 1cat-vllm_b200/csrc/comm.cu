@@ -228,27 +228,34 @@ __global__ void __launch_bounds__(256) tp_lamport_kernel(const CommParams p) {
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (int r = 0; r < tp; ++r) {
-          uint4 a;
+        // all sources' vectors are requested at once (one L2 round trip instead of one per source: at eight ranks the serial form
+        // spent most of the kernel in 7 x VEC_ITERS dependent loads); a slot that still holds the marker is then polled on its own
+        uint4 a[kMaxRanks];
+        __nv_bfloat16* const base = p.lam[me] + boff + (size_t)t * p.H + c;
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r)
+          if (r < tp && !(r == me && !p.lam_pushed)) a[r] = ld_volatile_v4(base + (size_t)r * (size_t)p.lam_src_stride);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) {
+          if (r >= tp) continue;
           if (r == me && !p.lam_pushed) {
-            a = mine[i];
+            a[r] = mine[i];
           } else {
-            __nv_bfloat16* slot = p.lam[me] + boff + (size_t)r * (size_t)p.lam_src_stride + (size_t)t * p.H + c;
+            __nv_bfloat16* slot = base + (size_t)r * (size_t)p.lam_src_stride;
             uint64_t t0 = 0;
             uint32_t spins = 0;
-            while (true) {
-              a = ld_volatile_v4(slot);
-              if (!(has_marker(a.x) || has_marker(a.y) || has_marker(a.z) || has_marker(a.w))) break;
+            while (has_marker(a[r].x) || has_marker(a[r].y) || has_marker(a[r].z) || has_marker(a[r].w)) {
               if (timed_out) break;
               if ((++spins & 255u) == 0) {
                 const uint64_t now = globaltimer_ns();
                 if (t0 == 0) t0 = now;
                 else if (now - t0 > p.wait_ns) { timed_out = true; break; }
               }
+              a[r] = ld_volatile_v4(slot);
             }
             *reinterpret_cast<uint4*>(slot) = marker;
           }
-          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a[r]);
 #pragma unroll
           for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(ap[j]);
         }
@@ -310,6 +317,141 @@ __global__ void __launch_bounds__(256) tp_lamport_kernel(const CommParams p) {
 
 }  // namespace
 
+// ---- two-shot reduction through the switch (COMM_NVLS) ---------------------------------------------------------------
+// The partial sums and the output live in a symmetric buffer that is also mapped at a multicast address (NVLink SHARP): one
+// multimem.ld_reduce at that address returns the sum over all ranks' copies, added inside the switch with fp32 accumulation, and
+// one multimem.st writes a value into every rank's copy. A rank therefore reduces only the rows it owns (one round trip to the
+// switch instead of tp - 1 peer transfers), adds the residual, normalises and broadcasts the normalised rows. Flags (unicast peer stores, bounded polls) order the phases: nobody reads before
+// every rank's partial is complete, nobody leaves before every rank's rows have been broadcast. The switch returns each sum to
+// exactly one rank, which broadcasts what it derived from it, so all ranks hold bit-identical outputs.
+// The new residual rows are broadcast as well, so every rank ends with the whole residual, as after the one-shot kernels.
+//   p.part[0]  multicast address of the partial sums [T, H];  p.x_out[0]  multicast address of the output [T, H];
+//   p.x_out[1] multicast address of the residual output [T, H] (or null)
+// (reference: distributed/device_communicators/symm_mem.py:149-153 multimem all-reduce; NCCL's NVLS algorithms)
+__device__ __forceinline__ uint4 multimem_ld_reduce_bf16x8(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(mc) : "memory");
+  return v;
+}
+__device__ __forceinline__ void multimem_st_v4(void* mc, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// Polls with relaxed loads: what the flag guards is read through the switch (phase 0) or by later kernels (phase 2), never through
+// this SM's L1 in this kernel, so the poll itself needs no acquire.
+__device__ __forceinline__ bool wait_flag_relaxed(const int* p, int want, uint64_t limit_ns) {
+  uint64_t t0 = 0;
+  uint32_t spins = 0;
+  while (true) {
+    int v;
+    asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    if (v - want >= 0) return true;
+    if ((++spins & 255u) == 0) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > limit_ns) return false;
+    }
+  }
+}
+
+template <int VEC_ITERS>
+__global__ void __launch_bounds__(256) tp_nvls_kernel(const CommParams p) {
+  __shared__ float red[9];
+  __shared__ int s_seq, s_ok;
+  const int b = blockIdx.x;
+  const int tp = p.tp, me = p.rank;
+  pdl_trigger();
+  pdl_wait();
+  // ---- phase 0: this rank's partial sums are complete (the producing GEMM ran earlier on this stream); wait for everybody's
+  if (threadIdx.x == 0) {
+    int seq = p.seq_local[b] + 1;
+    p.seq_local[b] = seq;
+    s_seq = seq;
+    s_ok = 1;   // no fence: the partial sums were written by the previous kernel, which has completed (pdl_wait above)
+  }
+  __syncthreads();
+  const int seq = s_seq;
+  if (threadIdx.x < tp) st_flag_release(p.flags[threadIdx.x] + (size_t)(p.phase * 2 * tp + me) * kMaxCommBlocks + b, seq);
+  if (threadIdx.x < tp) {
+    if (!wait_flag_relaxed(p.flags[me] + (size_t)(p.phase * 2 * tp + threadIdx.x) * kMaxCommBlocks + b, seq, p.wait_ns)) {
+      s_ok = 0;
+      atomicOr(&g_status, ST_PEER_TIMEOUT);
+    }
+  }
+  __syncthreads();
+  const bool ok = s_ok != 0;
+  const int per = (p.T + tp - 1) / tp;
+  const int row_lo = min(me * per, p.T), row_hi = min(row_lo + per, p.T);
+  if (ok) {
+    for (int t = row_lo + b; t < row_hi; t += gridDim.x) {
+      float v[VEC_ITERS][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < VEC_ITERS; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < p.H) {
+          const uint4 a = multimem_ld_reduce_bf16x8(p.part[0] + (size_t)t * p.H + c);
+          const __nv_bfloat16* ap = reinterpret_cast<const __nv_bfloat16*>(&a);
+          float acc[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] = __bfloat162float(ap[j]);
+          if (p.residual_in != nullptr) {
+            const uint4 rr = *reinterpret_cast<const uint4*>(p.residual_in + (size_t)t * p.H + c);
+            const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(&rr);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(rp[j]);
+          }
+          uint4 o;
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            op[j] = __float2bfloat16(acc[j]);
+            v[i][j] = __bfloat162float(op[j]);
+            ss += v[i][j] * v[i][j];
+          }
+          if (p.x_out[1] != nullptr) multimem_st_v4(p.x_out[1] + (size_t)t * p.H + c, o);
+        }
+      }
+      float inv = 1.f;
+      if (p.w != nullptr) {
+        const float tot = block_sum256(ss, red);
+        inv = rsqrtf(tot / (float)p.H + p.eps);
+      }
+#pragma unroll
+      for (int i = 0; i < VEC_ITERS; ++i) {
+        const int c = (i * 256 + threadIdx.x) * 8;
+        if (c < p.H) {
+          uint4 o;
+          __nv_bfloat16* op = reinterpret_cast<__nv_bfloat16*>(&o);
+          if (p.w != nullptr) {
+            const uint4 ww = *reinterpret_cast<const uint4*>(p.w + c);
+            const __nv_bfloat16* wp = reinterpret_cast<const __nv_bfloat16*>(&ww);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float g = __bfloat162float(wp[j]);
+              op[j] = __float2bfloat16(v[i][j] * inv * (p.gemma ? 1.f + g : g));
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) op[j] = __float2bfloat16(v[i][j]);
+          }
+          multimem_st_v4(p.x_out[0] + (size_t)t * p.H + c, o);
+        }
+      }
+    }
+  }
+  // ---- phase 2: "my rows are in your output buffer", then wait for everybody's rows
+  __syncthreads();
+  if (threadIdx.x == 0) __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < tp) st_flag_release(p.flags[threadIdx.x] + (size_t)((p.phase * 2 + 1) * tp + me) * kMaxCommBlocks + b, seq);
+  if (threadIdx.x < tp) {
+    if (!wait_flag_relaxed(p.flags[me] + (size_t)((p.phase * 2 + 1) * tp + threadIdx.x) * kMaxCommBlocks + b, seq, p.wait_ns))
+      atomicOr(&g_status, ST_PEER_TIMEOUT);
+  }
+}
+
 int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st) {
   if (p.H % 8 || p.H > 8192 || grid < 1 || grid > kMaxCommBlocks || p.tp > kMaxRanks) return -1;
   if (p.T == 0) return 0;
@@ -321,6 +463,16 @@ int tp_reduce_norm_launch(const CommParams& p, int grid, cudaStream_t st) {
       case 2: launch_k(tp_lamport_kernel<2>, dim3(grid), dim3(256), 0, st, true, p); break;
       case 3: launch_k(tp_lamport_kernel<3>, dim3(grid), dim3(256), 0, st, true, p); break;
       default: launch_k(tp_lamport_kernel<4>, dim3(grid), dim3(256), 0, st, true, p); break;
+    }
+    return cudaGetLastError() == cudaSuccess ? 0 : -2;
+  }
+  if (p.mode == COMM_NVLS) {
+    if (p.part[0] == nullptr || p.x_out[0] == nullptr) return -4;
+    switch (iters) {
+      case 1: launch_k(tp_nvls_kernel<1>, dim3(grid), dim3(256), 0, st, true, p); break;
+      case 2: launch_k(tp_nvls_kernel<2>, dim3(grid), dim3(256), 0, st, true, p); break;
+      case 3: launch_k(tp_nvls_kernel<3>, dim3(grid), dim3(256), 0, st, true, p); break;
+      default: launch_k(tp_nvls_kernel<4>, dim3(grid), dim3(256), 0, st, true, p); break;
     }
     return cudaGetLastError() == cudaSuccess ? 0 : -2;
   }

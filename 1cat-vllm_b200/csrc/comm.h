@@ -9,7 +9,7 @@ namespace oc {
 
 constexpr int kMaxRanks = 8;
 constexpr int kMaxCommBlocks = 1024;
-enum { COMM_ONE_SHOT = 0, COMM_TWO_SHOT = 1, COMM_LAMPORT = 2 };
+enum { COMM_ONE_SHOT = 0, COMM_TWO_SHOT = 1, COMM_LAMPORT = 2, COMM_NVLS = 3 };
 constexpr int kLamportBuffers = 3;
 
 struct CommParams {

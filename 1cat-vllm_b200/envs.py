@@ -37,6 +37,10 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_ATTN_PREFILL": _s("ONECAT_ATTN_PREFILL", "tcgen05"),  # head size 128 prefill attention: "tcgen05" | "mma"
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)
     "ONECAT_TP_ONESHOT": _s("ONECAT_TP_ONESHOT", "lamport"),  # decode-sized reductions: "lamport" (data is its own flag) | "flags"
+    # reductions inside the switch (multimem) when every rank has multicast support: auto (the batch sizes where they measured
+    # faster than the peer-store kernels) | 1 (every size) | 0 (never)
+    "ONECAT_TP_NVLS": _s("ONECAT_TP_NVLS", "auto"),
+    "ONECAT_TP_NVLS_MIN_T": _s("ONECAT_TP_NVLS_MIN_T", "1"),  # smallest batch (rows) that takes the switch reduction
     "ONECAT_TP_PUSH": _s("ONECAT_TP_PUSH", "auto"),  # GEMM epilogue pushes partial tiles to peers: auto | always | never
     # expert parallelism: "reduce" = every rank runs its experts over all tokens and the partial sums ride the TP reduction;
     # "a2a" = each rank routes a slice of the tokens and rows are exchanged with the expert owners (peer-memory kernels, or

@@ -26,13 +26,14 @@ def main() -> None:
     ap.add_argument("--inner", type=int, default=20)
     ap.add_argument("--json", default="")
     ap.add_argument("--hidden", type=int, default=5120)
+    ap.add_argument("--sizes", default="1,16,64,256,1024,8192")
     a = ap.parse_args()
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ.get("LOCAL_RANK", 0))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     from onecat_vllm.ops import cuda as K
-    from onecat_vllm.parallel.fused import LAMPORT, ONE_SHOT, TWO_SHOT, FusedTP
+    from onecat_vllm.parallel.fused import LAMPORT, NVLS, ONE_SHOT, TWO_SHOT, FusedTP
     H = a.hidden
     f = FusedTP(world, rank, dev, 8192, H)
     w = torch.ones(H, device=dev, dtype=torch.bfloat16)
@@ -63,7 +64,11 @@ def main() -> None:
         ts.sort()
         return ts[len(ts) // 2]
 
-    for T in (1, 16, 64, 256, 1024, 8192):
+    sizes = [int(x) for x in a.sizes.split(",")]
+    # with multicast support every size is measured twice: through the switch and with the peer-store kernels
+    passes = [(T, nv) for T in sizes for nv in ((True, False) if f.nv is not None else (False,))]
+    for T, use_nv in passes:
+        f.nvls_mode = "always" if use_nv else "never"
         part = torch.randn(T, H, device=dev).bfloat16()
         res = torch.randn(T, H, device=dev).bfloat16()
         x = torch.randn(T, Kin, device=dev).bfloat16()
@@ -94,6 +99,8 @@ def main() -> None:
             f.reduce_add_norm(buf, res, w, 1e-6, False)
 
         def gemm_push():
+            if mode == NVLS:   # the switch pulls the partial sums: there is no push form
+                return gemm_pull()
             buf = f.partial_buffer(T, H, torch.bfloat16)
             K._gemm(x, wg, None, None, buf, None, H, H, H, 0, 0, 1, push=f.push_spec(T))
             f.reduce_add_norm(buf, res, w, 1e-6, False, pushed=True)
@@ -103,17 +110,39 @@ def main() -> None:
             dist.all_reduce(y)
             K.rms_norm(y, w, 1e-6, res, False)
 
+        # device time without the host's launch rate: `inner` reductions captured in one CUDA graph (the decode path replays graphs)
+        t_graph = None
+        if mode in (LAMPORT, NVLS):
+            src = part if mode == LAMPORT else f.partial_buffer(T, H, torch.bfloat16)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(3):
+                    f.reduce_add_norm(f.partial_buffer(T, H, torch.bfloat16) if mode == NVLS else part, res, w, 1e-6, False)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for _ in range(a.inner):
+                    f.reduce_add_norm(f.partial_buffer(T, H, torch.bfloat16) if mode == NVLS else part, res, w, 1e-6, False)
+            keep, a.inner = a.inner, 1
+            t_graph = timed(gr.replay) / keep
+            a.inner = keep
+            del src
         t_f, t_c = timed(fused), (0.0 if mode == LAMPORT else timed(copy_only))
         t_n, t_cl = timed(nccl), timed(clone_only)
         t_gp, t_gpush, t_gn = timed(gemm_pull), timed(gemm_push), timed(gemm_nccl)
         # bytes each rank must receive over NVLink for the reduction (+ send for the gather in two-shot mode)
         if mode in (ONE_SHOT, LAMPORT):
             link_bytes = (world - 1) * T * H * 2
+        elif mode == NVLS:   # a rank receives the reduced rows it owns and everybody else's normalised and residual rows
+            link_bytes = (1.0 / world + 2.0 * (world - 1) / world) * T * H * 2
         else:
             link_bytes = 2 * (world - 1) / world * T * H * 2
         t_link = link_bytes / 770e9 * 1e3
         t_flop = 2.0 * T * H * Kin / 1648e12 * 1e3
-        rows.append(dict(T=T, mode={ONE_SHOT: "one-shot (flags)", LAMPORT: "one-shot (flag-free)", TWO_SHOT: "two-shot"}[mode], fused_ms=t_f - t_c, nccl_plus_norm_ms=t_n - t_cl,
+        rows.append(dict(T=T, switch=bool(use_nv), mode={ONE_SHOT: "one-shot (flags)", LAMPORT: "one-shot (flag-free)", TWO_SHOT: "two-shot", NVLS: "switch (multimem)"}[mode], fused_ms=t_f - t_c, fused_in_graph_ms=t_graph, nccl_plus_norm_ms=t_n - t_cl,
                          gemm_pull_fused_ms=t_gp, gemm_push_fused_ms=t_gpush, gemm_nccl_norm_ms=t_gn, link_bound_ms=t_link,
                          roofline_frac_reduce=t_link / max(t_f - t_c, 1e-9), roofline_frac_gemm_fused=max(t_link, t_flop) / min(t_gp, t_gpush)))
     st = K.check_status()

@@ -25,7 +25,7 @@ from onecat_vllm.logger import init_logger
 
 log = init_logger(__name__)
 _MAXB = 1024
-ONE_SHOT, TWO_SHOT, LAMPORT = 0, 1, 2
+ONE_SHOT, TWO_SHOT, LAMPORT, NVLS = 0, 1, 2, 3
 _LAM_BUFS = 3
 
 
@@ -58,12 +58,44 @@ class FusedTP:
         self.seq = torch.zeros(_MAXB, dtype=torch.int32, device=device)
         self.lam_ctr = torch.zeros(2, dtype=torch.int32, device=device)  # [buffer in use, CTAs finished]
         self.use_lamport = envs.ONECAT_TP_ONESHOT != "flags"
+        self.nvls_min_t = int(envs.ONECAT_TP_NVLS_MIN_T)
         self.parity = 0
+        self.nv = self._nvls_setup(tp, rank, device, buf, group) if envs.ONECAT_TP_NVLS != "0" else None
+        self.nvls_mode = {"1": "always", "0": "never"}.get(envs.ONECAT_TP_NVLS, "auto")
         self.wait_ns = int(envs.ONECAT_DEVICE_WAIT_LIMIT_MS) * 1_000_000
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
         self.launches = 0
         dist.barrier(group=group)
         log.info_once(f"fused TP: slab of {self.bytes >> 20} MiB mapped on {tp} ranks")
+
+    def _nvls_setup(self, tp: int, rank: int, device, buf: int, group):
+        """A second symmetric buffer, allocated and exchanged by ``torch.distributed._symmetric_memory`` and bound to an NVLink
+        multicast object, for the reduction that adds inside the switch: ``part[parity]`` (this rank's partial sums), four rotating
+        ``out`` and ``res`` buffers (normalised rows and new residual rows, broadcast by their owners; a result stays valid for the
+        next three reductions) and the flag area. ``None`` when any rank has no multicast
+        support (the peer-store kernels then serve every size)."""
+        ok, nv = 0, None
+        try:
+            import torch.distributed._symmetric_memory as symm
+            pg = group if group is not None else dist.group.WORLD
+            flags = 2 * 2 * tp * _MAXB * 4
+            t = symm.empty(10 * buf + flags, dtype=torch.uint8, device=device)
+            t.zero_()
+            torch.cuda.synchronize(device)
+            hdl = symm.rendezvous(t, group=pg.group_name)
+            mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
+            if mc and len(hdl.buffer_ptrs) == tp:
+                nv = dict(t=t, hdl=hdl, mc=mc, ptrs=[int(x) for x in hdl.buffer_ptrs], part=[0, buf], out=[(2 + i) * buf for i in range(4)],
+                          res=[(6 + i) * buf for i in range(4)], flags=10 * buf, slot=0)
+                ok = 1
+        except Exception as e:  # no symmetric-memory support in this build / on this machine
+            log.info_once(f"fused TP: no switch reductions ({type(e).__name__}: {e})")
+        flag = torch.tensor([ok], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        if int(flag.item()) != 1:
+            return None
+        log.info_once("fused TP: reductions inside the switch (multimem) enabled")
+        return nv
 
     @classmethod
     def create(cls, cfg, device) -> "FusedTP":
@@ -79,7 +111,12 @@ class FusedTP:
         """This rank's own slot for the current reduction (what a GEMM without the push epilogue writes to)."""
         if H != self.H or T > self.tmax or dtype != torch.bfloat16:
             return None
+        if self.mode_for(T) == NVLS:
+            return self._nv_tensor(self.nv["part"][self.parity], T, H)
         return self._tensor(self.rank, self.off_part[self.parity][self.rank], T, H)
+
+    def _nv_tensor(self, off: int, T: int, H: int) -> torch.Tensor:
+        return self.nv["t"][off: off + T * H * 2].view(torch.bfloat16).view(T, H)
 
     def use_push(self, T: int) -> bool:
         """Whether the GEMM epilogue should push its tiles to the peers (overlapping the transfer with the GEMM) or leave them
@@ -88,6 +125,8 @@ class FusedTP:
         stores from their epilogue warps), for prefill-sized batches the push wins (478 against 543 us at 8192 tokens), so by default
         only batches of 512 tokens and more push. ``ONECAT_TP_PUSH`` = always | never | auto."""
         mode = envs.ONECAT_TP_PUSH
+        if self.mode_for(T) == NVLS:
+            return False   # the switch pulls the partial sums from where the GEMM left them
         return mode == "always" or (mode == "auto" and T >= 512)
 
     def push_spec(self, T: int):
@@ -109,6 +148,11 @@ class FusedTP:
 
     def mode_for(self, T: int) -> int:
         one = T * (self.tp - 1) <= 1024 or self.tp == 2   # up to 1024 peer rows per rank: ~10 MB over NVLink, still cheaper than two phases
+        if self.nv is not None and T >= self.nvls_min_t:
+            # Measured at 8 ranks (hidden 5120, us per reduction): 64 rows 23.9 through the switch against 20.7 flag-free; 256 rows
+            # 25.0 against 43.8 two-shot; 1024 rows 56.4 against 57.1; 8192 rows 325 against 268. At 2 ranks the switch never wins.
+            if self.nvls_mode == "always" or (self.nvls_mode == "auto" and self.tp >= 4 and not one and T <= 512):
+                return NVLS
         if one and self.use_lamport and T <= self.lam_rows:
             return LAMPORT
         return ONE_SHOT if one else TWO_SHOT
@@ -119,12 +163,31 @@ class FusedTP:
         T, H = partial.shape
         assert H == self.H and T <= self.tmax, "shape outside the symmetric slab"
         par = self.parity
-        if mode is None or (mode == ONE_SHOT and self.mode_for(T) == LAMPORT):
+        if mode is None or (mode == ONE_SHOT and self.mode_for(T) in (LAMPORT, NVLS)):
             mode = self.mode_for(T)
         if w is not None and w.dtype != torch.bfloat16:
             w = w.to(torch.bfloat16)
-        res_out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device) if residual is not None else None
         from onecat_vllm.ops import cuda as K
+        if mode == NVLS:
+            nv = self.nv
+            src = self._nv_tensor(nv["part"][par], T, H)
+            if partial.data_ptr() != src.data_ptr():
+                src.copy_(partial)
+            slot = nv["slot"]
+            nv["slot"] = (slot + 1) % 4
+            x = self._nv_tensor(nv["out"][slot], T, H)
+            res_out = self._nv_tensor(nv["res"][slot], T, H) if residual is not None else None
+            part = [nv["mc"] + nv["part"][par]] + [0] * (self.tp - 1)
+            xo = [nv["mc"] + nv["out"][slot], (nv["mc"] + nv["res"][slot]) if residual is not None else 0] + [0] * (self.tp - 2)
+            flags = [p + nv["flags"] for p in nv["ptrs"]]
+            grid = max(1, min(-(-T // self.tp), 2 * self.num_sms, _MAXB))
+            self._C.tp_reduce_norm(part, flags, self.seq, xo, residual, None, w, T, H, self.rank, NVLS, gemma, par, eps, self.wait_ns, grid,
+                                   [], 0, 0, 0, False)
+            self.parity ^= 1
+            self.launches += 1
+            K._LAUNCHES += 1
+            return x, res_out
+        res_out = torch.empty(T, H, dtype=torch.bfloat16, device=self.device) if residual is not None else None
         if mode == LAMPORT:
             x = torch.empty(T, H, dtype=torch.bfloat16, device=self.device)
             xo = [0] * self.tp
@@ -174,6 +237,7 @@ class FusedTP:
         if getattr(self, "base", None) is None:
             return
         torch.cuda.synchronize()
+        self.nv = None
         for r, p in enumerate(self.peers):
             if r != self.rank:
                 self._C.comm_unimport(p)

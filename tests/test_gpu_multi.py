@@ -19,7 +19,7 @@ def _need2():
 
 def _fused_worker(rank, world, port, q, oneshot="lamport"):
     import torch.distributed as dist
-    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ONECAT_TP_ONESHOT=oneshot, NCCL_NVLS_ENABLE="0")
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ONECAT_TP_ONESHOT=oneshot, NCCL_NVLS_ENABLE="0", ONECAT_TP_NVLS="0")
     torch.cuda.set_device(rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
     from onecat_vllm.ops import cuda as K
@@ -159,6 +159,102 @@ def test_fused_reduce_norm(world, oneshot):
     captured reduction replayed 25 times, against a CPU-rank simulation (gather every rank's bf16 partial, sum in fp32, add, normalise)."""
     _need(world)
     _spawn(_fused_worker, world, oneshot)
+
+
+def _nvls_worker(rank, world, port, q):
+    """The reduction that adds inside the switch: sums, residual and normalised rows against a simulation from gathered partials,
+    bit-identical outputs on all ranks, results that stay valid over the next reductions, and a captured pair replayed 25 times."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), ONECAT_TP_NVLS="1")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from onecat_vllm.ops import cuda as K
+    from onecat_vllm.ops import ref
+    from onecat_vllm.parallel.fused import NVLS, FusedTP
+    dev = torch.device("cuda", rank)
+    H, tmax = 5120, 1024
+    f = FusedTP(world, rank, dev, tmax, H)
+    ok, msgs = True, []
+    try:
+        if f.nv is None:
+            msgs.append("no multicast support on this machine: nothing to check")
+        else:
+            kept = []
+            for it, (T, gemma, with_res) in enumerate([(1, False, True), (64, True, True), (7, False, True), (333, False, True), (1024, True, True),
+                                                        (64, False, False), (16, False, True), (5, True, True)]):
+                assert f.mode_for(T) == NVLS
+                g = torch.Generator(device=dev).manual_seed(100 * it + rank)
+                g2 = torch.Generator(device=dev).manual_seed(7 + it)
+                part = torch.randn(T, H, device=dev, generator=g).bfloat16()
+                res = torch.randn(T, H, device=dev, generator=g2).bfloat16() if with_res else None
+                w = (torch.randn(H, device=dev, generator=g2) * 0.1 + (0 if gemma else 1)).bfloat16()
+                buf = f.partial_buffer(T, H, torch.bfloat16)
+                buf.copy_(part)
+                x, r = f.reduce_add_norm(buf, res, w, 1e-6, gemma)
+                torch.cuda.synchronize()
+                parts = [torch.empty_like(part) for _ in range(world)]
+                dist.all_gather(parts, part)
+                tot = sum(p.float() for p in parts).bfloat16()          # the switch accumulates in fp32 and returns bf16
+                new_res = (tot.float() + res.float()).bfloat16() if with_res else tot
+                xe, _ = ref.rms_norm(new_res, w, 1e-6, None, gemma)
+                # the switch rounds intermediate sums to bf16 on its way: up to an ulp of the largest partial sum
+                r_ok = True if not with_res else bool(((r.float() - new_res.float()).abs() <= 0.14).all())
+                err = (x.float() - xe.float()).abs().max().item()
+                both = torch.cat([x, r]) if with_res else x
+                xs = [torch.empty_like(both) for _ in range(world)]
+                dist.all_gather(xs, both.contiguous())
+                same = all(torch.equal(xs[0], t) for t in xs)
+                kept.append((x, x.clone()))
+                if not (r_ok and err < 0.08 and same):
+                    ok = False
+                    msgs.append(f"it={it} T={T} r_ok={r_ok} err={err} same={same}")
+            # a result stays where it is for the next three reductions
+            for (view, copy) in kept[-3:]:
+                if not torch.equal(view, copy):
+                    ok = False
+                    msgs.append("a result was overwritten within three reductions")
+            T = 8
+            buf = f.partial_buffer(T, H, torch.bfloat16)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                for _ in range(4):
+                    f.partial_buffer(T, H, torch.bfloat16).fill_(float(rank + 1))
+                    f.all_reduce(f.partial_buffer(T, H, torch.bfloat16))
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            dist.barrier()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                b1 = f.partial_buffer(T, H, torch.bfloat16)
+                b1.fill_(float(rank + 1))
+                y1 = f.all_reduce(b1)
+                b2 = f.partial_buffer(T, H, torch.bfloat16)
+                b2.copy_(y1)
+                y2 = f.all_reduce(b2)
+            for _ in range(25):
+                gr.replay()
+            torch.cuda.synchronize()
+            tot = float(sum(range(1, world + 1)))
+            if not (torch.equal(y1, torch.full_like(y1, tot)) and torch.equal(y2, torch.full_like(y2, tot * world))):
+                ok = False
+                msgs.append(f"graph replay mismatch {y1[0, 0].item()} {y2[0, 0].item()}")
+            st = K.check_status()
+            if st:
+                ok = False
+                msgs.append(f"status {st}")
+    finally:
+        dist.barrier()
+        f.close()
+        dist.destroy_process_group()
+    q.put((rank, ok, msgs))
+
+
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_switch_reduce_norm(world):
+    _need(world)
+    _spawn(_nvls_worker, world)
 
 
 def _a2a_worker(rank, world, port, q, qmethod="none"):

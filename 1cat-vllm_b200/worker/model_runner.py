@@ -21,6 +21,7 @@ from onecat_vllm.config import VllmConfig
 from onecat_vllm.core.kv_cache_utils import KVCacheConfig, KVCacheSpec
 from onecat_vllm.core.sched_output import ModelRunnerOutput, SchedulerOutput
 from onecat_vllm.logger import init_logger
+from onecat_vllm.ops import ref as ref_ops
 from onecat_vllm.parallel import state as ps
 from onecat_vllm.sample.metadata import SamplingMetadata
 from onecat_vllm.sample.rejection_sampler import RejectionSampler
@@ -897,6 +898,40 @@ class ModelRunner:
                 out.append(None)
         return out
 
+    @staticmethod
+    def _verify_is_unconstrained(md: SamplingMetadata) -> bool:
+        """No request asks for anything that changes the target distribution beyond the temperature."""
+        return (md.no_penalties and md.top_k is None and md.top_p is None and md.min_p is None and not md.min_tokens and
+                not any(md.logit_bias) and not any(a is not None for a in md.allowed_token_ids) and not md.bad_words_token_ids and
+                not md.thinking and not md.custom_processors)
+
+    def _expand_sampling_metadata(self, md: SamplingMetadata, drafts: list):
+        """Sampling state with one row per verified draft position (request b contributes ``len(drafts[b])`` rows; row i sees the
+        request's output followed by its first i drafts), the owner of every row, and the state of the bonus rows (one per request,
+        whose context includes all of its drafts). The grammar bitmask stays with the bonus rows."""
+        owner = [b for b, d in enumerate(drafts) for _ in d]
+        dev = self.device
+        idx = torch.tensor(owner, dtype=torch.long, device=dev)
+        pick = lambda t: t.index_select(0, idx) if t is not None else None
+        ctx = [md.output_token_ids[b] + list(d[:i]) for b, d in enumerate(drafts) for i in range(len(d))]
+        emd = SamplingMetadata(
+            temperature=pick(md.temperature), all_greedy=md.all_greedy, all_random=md.all_random, top_p=pick(md.top_p), top_k=pick(md.top_k),
+            min_p=pick(md.min_p), generators={}, max_num_logprobs=None, no_penalties=md.no_penalties,
+            presence_penalties=pick(md.presence_penalties), frequency_penalties=pick(md.frequency_penalties),
+            repetition_penalties=pick(md.repetition_penalties),
+            prompt_token_ids=[md.prompt_token_ids[b] for b in owner] if md.prompt_token_ids else None, output_token_ids=ctx,
+            min_tokens={r: md.min_tokens[b] for r, b in enumerate(owner) if b in md.min_tokens},
+            logit_bias=[md.logit_bias[b] for b in owner] if md.logit_bias else [],
+            allowed_token_ids=[md.allowed_token_ids[b] for b in owner] if md.allowed_token_ids else [],
+            bad_words_token_ids={r: md.bad_words_token_ids[b] for r, b in enumerate(owner) if b in md.bad_words_token_ids},
+            thinking={r: md.thinking[b] for r, b in enumerate(owner) if b in md.thinking}, custom_processors=md.custom_processors,
+            row_info=[dict(md.row_info[b], output_token_ids=ctx[r]) for r, b in enumerate(owner)] if md.row_info else [])
+        import dataclasses
+        full = [md.output_token_ids[b] + list(d) for b, d in enumerate(drafts)]
+        bonus = dataclasses.replace(md, output_token_ids=full,
+                                    row_info=[dict(ri, output_token_ids=full[b]) for b, ri in enumerate(md.row_info)] if md.row_info else [])
+        return emd, owner, bonus
+
     def _verify(self, logits, smd, rows, drafts_of) -> list[list[int]]:
         """Rejection-sample requests that carried drafts; plain-sample the rest. ``logits`` rows are grouped per
         request (k_i + 1 rows for a request with k_i drafts)."""
@@ -921,7 +956,30 @@ class ModelRunner:
             j += r
             b += 1
         nd.copy_(torch.tensor(nd_host))
-        bonus = self.sampler(logits[torch.tensor(last_rows, device=dev)], smd).sampled_token_ids
+        bonus_md = smd
+        if not self._verify_is_unconstrained(smd):
+            # The drafts are judged against the distribution the sampler would have drawn from: every verified row goes through the
+            # logit processors and penalties (its context being the request's output plus the drafts before it) and the top-k /
+            # top-p / min-p filters, exactly as the bonus row does
+            # (reference: v1/sample/rejection_sampler.py ``apply_logits_processors`` / ``apply_sampling_constraints``).
+            kept = [d for i, d in enumerate(drafts_of) if rows[i] > 0]
+            emd, owner, bonus_md = self._expand_sampling_metadata(smd, kept)
+            flat = torch.cat([tl[b, :len(d)] for b, d in enumerate(kept) if d]).float() if any(kept) else None
+            if flat is not None:
+                flat = Sampler.apply_logits_processors(flat, emd)
+                flat = Sampler.apply_penalties(flat, emd)
+                for proc in emd.custom_processors:
+                    flat = proc.apply(flat, emd.row_info)
+                if emd.top_k is not None or emd.top_p is not None or emd.min_p is not None:
+                    t = emd.temperature if emd.temperature is not None else torch.ones(flat.shape[0], device=dev)
+                    t = torch.where(t < 1e-5, torch.ones_like(t), t).unsqueeze(-1)
+                    flat = ref_ops.top_k_top_p_min_p(flat / t, emd.top_k, emd.top_p, emd.min_p) * t   # masked entries stay -inf
+                j = 0
+                for b, d in enumerate(kept):
+                    if d:
+                        tl[b, :len(d)] = flat[j:j + len(d)].to(tl.dtype)
+                        j += len(d)
+        bonus = self.sampler(logits[torch.tensor(last_rows, device=dev)], bonus_md).sampled_token_ids
         res = self.rejection_sampler(draft, nd, tl, bonus, smd)
         parsed = RejectionSampler.parse_output(res)
         self.d2h_bytes = res.numel() * 8

@@ -42,6 +42,60 @@ def test_spec_decode_lossless_on_hybrid(method):
     assert _gen(HYBRID, p, speculative_config=dict(method=method, num_speculative_tokens=3)) == ref
 
 
+def test_spec_decode_verifies_against_the_constrained_distribution():
+    """With top_k = 1 a random-temperature request is deterministic (the arg-max), with and without drafts: the verifier must judge
+    the drafts against the filtered distribution, not the raw one. Penalties, a logit bias and bad words must carry over too."""
+    p = _prompts(500)[:3]
+
+    def run(sp, **kw):
+        llm = LLM(hf_config=HYBRID, max_model_len=256, dtype="float32", device="cpu", **kw)
+        out = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
+        llm.shutdown()
+        return out
+    spec = dict(speculative_config=dict(method="ngram", num_speculative_tokens=3))
+    greedy = run(SamplingParams(temperature=0, max_tokens=24, ignore_eos=True))
+    topk1 = SamplingParams(temperature=1.0, top_k=1, max_tokens=24, ignore_eos=True, seed=3)
+    assert run(topk1, **spec) == greedy
+    banned = greedy[0][3]
+    shaped = SamplingParams(temperature=0, max_tokens=24, ignore_eos=True, repetition_penalty=1.3, logit_bias={7: 4.0},
+                            bad_words_token_ids=[[banned]])
+    want = run(shaped)
+    assert want != greedy and all(banned not in o for o in want)
+    assert run(shaped, **spec) == want
+
+
+def test_verifier_applies_filters_and_processors_to_draft_rows():
+    """The verifier on crafted logits: a draft with 38 % of the raw probability mass must never be accepted under top_k = 1 (the raw
+    distribution would accept it about every third time), and a banned arg-max must not be what greedy verification emits."""
+    from onecat_vllm.sample.metadata import SamplingMetadata
+    llm = LLM(hf_config=HYBRID, max_model_len=256, dtype="float32", device="cpu", speculative_config=dict(method="ngram", num_speculative_tokens=3))
+    runner = llm.llm_engine.engine_core.core.executor.worker.runner
+    V, A, D = HYBRID["vocab_size"], 5, 9
+    row = torch.full((V,), -8.0)
+    row[A], row[D] = 2.0, 1.5
+    logits = row.repeat(6, 1)                      # request 0: three drafts + bonus; request 1: one draft + bonus
+    rows, drafts = [4, 2], [[D, D, D], [D]]
+
+    def md(**kw):
+        base = dict(temperature=torch.ones(2), all_greedy=False, all_random=True, top_p=None, top_k=None, min_p=None, generators={},
+                    max_num_logprobs=None, no_penalties=True, output_token_ids=[[1, 2], [3]], logit_bias=[None, None],
+                    allowed_token_ids=[None, None])
+        base.update(kw)
+        return SamplingMetadata(**base)
+    accepted_raw = 0
+    for _ in range(40):
+        out = runner._verify(logits.clone(), md(), rows, drafts)
+        accepted_raw += sum(1 for o in out if o[0] == D)
+        out = runner._verify(logits.clone(), md(top_k=torch.tensor([1, 1])), rows, drafts)
+        assert out == [[A], [A]]                   # first draft rejected, the recovered token is the only one left in the filter
+    assert accepted_raw > 0                        # the crafted draft is plausible without the filter
+    greedy = dict(temperature=None, all_greedy=True, all_random=False)
+    assert runner._verify(logits.clone(), md(**greedy), rows, [[A, A, A], [A]]) == [[A, A, A, A], [A, A]]
+    out = runner._verify(logits.clone(), md(bad_words_token_ids={0: [[A]]}, **greedy), rows, [[A, A, A], [A]])
+    assert out == [[D], [A, A]]                    # request 0 may not emit A anywhere: its first draft fails and D is recovered
+    llm.shutdown()
+
+
 def test_synthetic_acceptance_exercises_verifier():
     llm = LLM(hf_config=HYBRID, max_model_len=256, dtype="float32", device="cpu",
               speculative_config=dict(method="mtp", num_speculative_tokens=3, synthetic_acceptance_rate=0.7, synthetic_seed=1))

@@ -3,6 +3,8 @@
 gated variant with per-head q/k RMSNorm and partial rotary)."""
 from __future__ import annotations
 
+from typing import Optional
+
 import torch
 import torch.nn as nn
 
@@ -14,12 +16,13 @@ from onecat_vllm.parallel.state import get_state
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str, device):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, prefix: str, device, qkv_in: Optional[int] = None):
         super().__init__()
         tp = get_state().tp_size
         self.D = cfg.head_dim
         self.gated = cfg.attn_output_gate
-        self.qkv_proj = QKVParallelLinear(cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads,
+        # qkv_in: width of the projection's input when it is not the hidden size (EAGLE-3 feeds [embedding ; hidden])
+        self.qkv_proj = QKVParallelLinear(qkv_in or cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads, cfg.num_key_value_heads,
                                           q_mult=2 if self.gated else 1, bias=cfg.attention_bias, quant=cfg.quant,
                                           prefix=prefix + ".qkv_proj", dtype=cfg.dtype)
         self.Hq, self.Hkv = self.qkv_proj.num_heads, self.qkv_proj.num_kv_heads

@@ -342,6 +342,36 @@ def load_eagle_weights(head: nn.Module, path: str) -> int:
     return len(load_weights(head, renamed()))
 
 
+def load_eagle3_weights(head: nn.Module, path: str) -> int:
+    """An EAGLE-3 checkpoint: ``fc``, ``midlayer.*`` (the decoder layer incl. ``hidden_norm``), ``norm``, ``lm_head``, optionally
+    ``embed_tokens`` and the vocabulary maps ``d2t`` / ``t2d`` (reference: models/llama_eagle3.py ``load_weights``)."""
+    def tensors():
+        if any(f.endswith(".safetensors") for f in os.listdir(path)):
+            yield from iter_safetensors(path)
+        else:
+            yield from torch.load(os.path.join(path, "pytorch_model.bin"), map_location="cpu", weights_only=True).items()
+
+    def renamed():
+        for name, w in tensors():
+            if name.startswith("model."):
+                name = name[len("model."):]
+            if name == "d2t":
+                head.d2t = w.to(torch.long).to(head.d2t.device)
+                continue
+            if name == "t2d":
+                continue
+            if name.startswith("embed_tokens."):
+                head.own_embedding = True
+            if name.startswith("lm_head."):
+                head.own_lm_head = True
+            for a, b in (("midlayer.hidden_norm.", "hidden_norm."), ("midlayer.", "layer."), ("layers.0.hidden_norm.", "hidden_norm."), ("layers.0.", "layer.")):
+                if name.startswith(a):
+                    name = b + name[len(a):]
+                    break
+            yield name, w
+    return len(load_weights(head, renamed()))
+
+
 def to_hf_state_dict(model: nn.Module) -> dict:
     """Un-stack fused parameters back to HF checkpoint names (q/k/v, gate/up, per-expert tensors), for saving a
     model built here as a checkpoint that any HF-layout loader (including this one) reads. TP size 1 only."""

@@ -75,6 +75,9 @@ class DecoderModel(nn.Module):
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, f"model.layers.{i}", device) if self.start <= i < self.end else PPMissingLayer()
                                      for i in range(cfg.num_hidden_layers)])
         self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype) if self.last_stage else PPMissingLayer()
+        # EAGLE-3 drafting reads the residual stream at a few depths: layer indices to record, and what the last forward recorded
+        self.aux_hidden_layers: tuple = ()
+        self.last_aux: list = []
 
     def local_layers(self):
         """(global index, layer) of the decoder layers this pipeline stage owns; KV caches are indexed in this order."""
@@ -101,8 +104,13 @@ class DecoderModel(nn.Module):
         if not cfg.pre_norm:
             return self._forward_post_norm(x if intermediate is None else None, residual, md, caches)
         plain = not cfg.sandwich_norm and cfg.residual_multiplier == 1.0
+        aux_at = self.aux_hidden_layers
+        if aux_at:
+            self.last_aux = []
         for li, i in enumerate(range(self.start, self.end)):
             layer = layers[i]
+            if aux_at and i in aux_at:
+                self.last_aux.append(residual)   # the stream entering layer i (reference: models/llama.py ``aux_hidden_state_layers``)
             part = layer.mixer(x, md, caches[li])
             if plain:
                 x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
@@ -251,6 +259,59 @@ class MTPHead(nn.Module):
 
     def compute_logits(self, hidden):
         return self._target[0].compute_logits(hidden)
+
+
+class Eagle3Head(nn.Module):
+    """EAGLE-3 draft head. The target's residual stream at three depths is concatenated and reduced by ``fc`` to one hidden vector;
+    the single decoder layer's attention reads ``[norm(embed(tok)) ; norm(hidden)]`` (twice the hidden size), the residual path
+    carries ``hidden``; the layer's output before the final norm is the hidden input of the next drafting pass. The head has its own
+    final norm and LM head, possibly over a reduced draft vocabulary that ``d2t`` maps back to target ids
+    (reference: models/llama_eagle3.py; spec_decode/eagle.py; v1/spec_decode/static_draft_vocab.py for the reduced vocabulary)."""
+
+    stacked_params_mapping = CausalLM.stacked_params_mapping
+
+    def __init__(self, cfg: ModelConfig, target: CausalLM, device="cpu", draft_vocab_size: Optional[int] = None):
+        super().__init__()
+        import dataclasses
+        from onecat_vllm.layers.attention import Attention
+        from onecat_vllm.layers.linear import ReplicatedLinear
+        lcfg = dataclasses.replace(cfg, layer_types=None, num_hidden_layers=1, num_experts=0, sliding_layers=(), quant=type(cfg.quant)())
+        self.cfg = lcfg
+        H = cfg.hidden_size
+        self.fc = ReplicatedLinear(3 * H, H, bias=False, quant=None, prefix="fc", dtype=cfg.dtype)
+        self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, H, cfg.dtype)
+        self.own_embedding = False
+        self.layer = DecoderLayer(lcfg, 0, "layers.0", device)
+        self.layer.self_attn = Attention(lcfg, 0, "layers.0.self_attn", device, qkv_in=2 * H)
+        self.hidden_norm = RMSNorm(H, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.norm = RMSNorm(H, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.draft_vocab = int(draft_vocab_size or cfg.vocab_size)
+        self.lm_head = ReplicatedLinear(H, self.draft_vocab, bias=False, quant=None, prefix="lm_head", dtype=cfg.dtype)
+        self.own_lm_head = False   # set by the loader; without a checkpoint the target's LM head is used
+        # draft id -> target id is ``draft id + d2t[draft id]`` (the checkpoints store offsets); identity when the vocabularies agree
+        self.register_buffer("d2t", torch.zeros(self.draft_vocab, dtype=torch.long), persistent=False)
+        self._target = [target]
+
+    def forward(self, input_ids, target_hidden, md, cache):
+        H = self.cfg.hidden_size
+        hidden = self.fc(target_hidden) if target_hidden.shape[-1] != H else target_hidden
+        emb = self.embed_tokens if self.own_embedding else self._target[0].model.embed_tokens
+        layer = self.layer
+        x = torch.cat([layer.input_layernorm(emb(input_ids), None)[0], self.hidden_norm(hidden, None)[0]], dim=-1)
+        part = layer.mixer(x, md, cache)
+        x, residual = reduce_add_norm(part, hidden, layer.post_attention_layernorm)
+        return residual + reduce_only(layer.mlp(x))
+
+    def compute_logits(self, hidden):
+        x = self.norm(hidden, None)[0]
+        if not self.own_lm_head:
+            return self._target[0].compute_logits(x)
+        lg = self.lm_head(x)
+        if self.draft_vocab == self.cfg.vocab_size and not bool(self.d2t.any()):
+            return lg
+        full = torch.full((lg.shape[0], self.cfg.vocab_size), float("-inf"), dtype=lg.dtype, device=lg.device)
+        full[:, torch.arange(self.draft_vocab, device=lg.device) + self.d2t.to(lg.device)] = lg
+        return full
 
 
 class EagleHead(nn.Module):

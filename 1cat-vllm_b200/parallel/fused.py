@@ -59,6 +59,7 @@ class FusedTP:
         self.lam_ctr = torch.zeros(2, dtype=torch.int32, device=device)  # [buffer in use, CTAs finished]
         self.use_lamport = envs.ONECAT_TP_ONESHOT != "flags"
         self.nvls_min_t = int(envs.ONECAT_TP_NVLS_MIN_T)
+        self.full_residual = False
         self.parity = 0
         self.nv = self._nvls_setup(tp, rank, device, buf, group) if envs.ONECAT_TP_NVLS != "0" else None
         self.nvls_mode = {"1": "always", "0": "never"}.get(envs.ONECAT_TP_NVLS, "auto")
@@ -147,6 +148,8 @@ class FusedTP:
         return self.base + self.off_part[self.parity][self.rank] == t.data_ptr()
 
     def mode_for(self, T: int) -> int:
+        if self.full_residual:   # somebody reads the residual stream between layers: every rank must hold all of its rows
+            return LAMPORT if (self.use_lamport and T <= self.lam_rows) else ONE_SHOT
         one = T * (self.tp - 1) <= 1024 or self.tp == 2   # up to 1024 peer rows per rank: ~10 MB over NVLink, still cheaper than two phases
         if self.nv is not None and T >= self.nvls_min_t:
             # Measured at 8 ranks (hidden 5120, us per reduction): 64 rows 23.9 through the switch against 20.7 flag-free; 256 rows

@@ -109,6 +109,8 @@ class MTPProposer:
             shifted[idx] = sampled[r][-1]
             last_valid.append(idx)
             nxt.append(sampled[r][-1])
+        if runner.spec.method == "eagle3":   # the head reads the target's residual stream at three depths, not its final hidden state
+            hidden = torch.cat(runner.model.model.last_aux, dim=-1)
         h1 = mtp(shifted, hidden, md, runner.mtp_cache)
         active = [r for r in range(R) if last_valid[r] >= 0]
         out: list = [[] for _ in range(R)]
@@ -227,7 +229,7 @@ def make_proposer(runner):
     sc = runner.spec
     if sc.method == "ngram":
         return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
-    if sc.method in ("mtp", "eagle"):
+    if sc.method in ("mtp", "eagle", "eagle3"):
         return MTPProposer(runner)
     if sc.method == "suffix":
         return SuffixProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)

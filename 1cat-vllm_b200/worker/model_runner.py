@@ -132,6 +132,26 @@ class ModelRunner:
                 load_eagle_weights(self.mtp, self.spec.model)
             process_weights_after_loading(self.mtp)
             self.mtp.eval()
+        if self.spec.method == "eagle3":
+            from onecat_vllm.loader.weights import dummy_init, load_eagle3_weights, process_weights_after_loading
+            from onecat_vllm.models.decoder import Eagle3Head
+            dv = self.spec.draft_vocab_size
+            if dv is None and self.spec.model and os.path.exists(os.path.join(self.spec.model, "config.json")):
+                import json
+                with open(os.path.join(self.spec.model, "config.json")) as f:
+                    dv = json.load(f).get("draft_vocab_size")
+            with torch.device(self.device):
+                self.mtp = Eagle3Head(self.mc, self.model, self.device, dv)
+            dummy_init(self.mtp, self.mc.seed + 1)
+            if self.spec.model and os.path.isdir(self.spec.model):
+                load_eagle3_weights(self.mtp, self.spec.model)
+            process_weights_after_loading(self.mtp)
+            self.mtp.eval()
+            L = self.mc.num_hidden_layers
+            aux = self.spec.eagle_aux_hidden_state_layers or (2, L // 2, L - 3)
+            self.model.model.aux_hidden_layers = tuple(sorted(min(max(int(i), 0), L - 1) for i in aux))
+            if len(set(self.model.model.aux_hidden_layers)) != 3:
+                raise ValueError(f"EAGLE-3 needs three distinct target layers, got {aux} for a {L}-layer model")
         if self.spec.enabled:
             from onecat_vllm.spec_decode.proposers import make_proposer
             self.proposer = make_proposer(self)

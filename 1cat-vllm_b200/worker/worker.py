@@ -47,6 +47,7 @@ class Worker:
         if self.cfg.device == "cuda" and pc.tensor_parallel_size > 1 and pc.tp_comm == "fused":
             from onecat_vllm.parallel.fused import FusedTP
             ps.get_state().fused = FusedTP.create(self.cfg, self.device)
+            ps.get_state().fused.full_residual = self.cfg.speculative_config.method == "eagle3"
         from onecat_vllm import envs
         if pc.enable_expert_parallel and pc.tensor_parallel_size > 1 and envs.ONECAT_EP_COMM == "a2a" and self.cfg.model_config.num_experts:
             from onecat_vllm.parallel import all2all
@@ -94,7 +95,12 @@ class Worker:
             return
         self.runner.dummy_run(min(256, self.cfg.scheduler_config.max_num_batched_tokens), 4)
         from onecat_vllm import envs
-        if not self.cfg.enforce_eager and envs.ONECAT_USE_CUDA_GRAPH:
+        eagle3 = self.cfg.speculative_config.method == "eagle3"
+        if eagle3:
+            # the head reads tensors recorded inside the target's forward; a replayed graph keeps those in its own pool, which the
+            # drafting loop does not look into, so these steps run eagerly
+            log.info_once("EAGLE-3 drafting: decode steps run without CUDA graphs")
+        if not self.cfg.enforce_eager and envs.ONECAT_USE_CUDA_GRAPH and not eagle3:
             from onecat_vllm.worker.cuda_graphs import DecodeGraphs
             self.runner.graphs = DecodeGraphs(self.runner)
             self.runner.graphs.capture_all()

@@ -291,6 +291,91 @@ def test_eagle_head_is_lossless_and_loads_its_checkpoint(tmp_path):
     assert out == ref
 
 
+def test_eagle3_head_is_lossless_loads_its_checkpoint_and_matches_plain_torch(tmp_path):
+    """EAGLE-3 drafting: the target records its residual stream at three depths, the head (own final norm, LM head over a reduced
+    vocabulary with ``d2t`` offsets) loads ``fc`` / ``midlayer.*`` / ``norm`` / ``lm_head`` / ``d2t``, greedy output equals plain
+    decoding, and the head's first pass equals a plain-PyTorch restatement of the layer."""
+    import json
+    from safetensors.torch import save_file
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, to_hf_state_dict
+    from onecat_vllm.models import build_model
+    from onecat_vllm.models.decoder import Eagle3Head
+    from onecat_vllm.ops import ref
+    from onecat_vllm.worker.attn_metadata import AttentionMetadata
+    H, V, DV = 64, 500, 120
+    dense = dict(architectures=["LlamaForCausalLM"], hidden_size=H, intermediate_size=128, num_hidden_layers=8, num_attention_heads=4,
+                 num_key_value_heads=2, head_dim=16, vocab_size=V, max_position_embeddings=256, rms_norm_eps=1e-6, rope_theta=10000.0)
+    mc = ModelConfig.from_hf_dict(dense, dtype=torch.float32)
+    mc.max_model_len = 256
+    head = Eagle3Head(mc, build_model(mc, "cpu"), "cpu", DV)
+    dummy_init(head, 5, std=0.2)
+    sd = {}
+    for name, w in to_hf_state_dict(head).items():
+        if name.startswith("embed_tokens."):
+            continue                                   # this checkpoint shares the target's embedding
+        name = "midlayer." + name[len("layer."):] if name.startswith("layer.") else ("midlayer." + name if name.startswith("hidden_norm.") else name)
+        sd[name] = w.contiguous()
+    targets = torch.sort(torch.randperm(V, generator=torch.Generator().manual_seed(2))[:DV]).values
+    sd["d2t"] = targets - torch.arange(DV)
+    sd["t2d"] = torch.zeros(V, dtype=torch.bool)
+    save_file(sd, str(tmp_path / "model.safetensors"))
+    (tmp_path / "config.json").write_text(json.dumps({"draft_vocab_size": DV}))
+
+    p = _prompts(V)
+    want = _gen(dense, p)
+    llm = LLM(hf_config=dense, max_model_len=256, dtype="float32", device="cpu",
+              speculative_config=dict(method="eagle3", num_speculative_tokens=3, model=str(tmp_path)))
+    runner = llm.llm_engine.engine_core.core.executor.worker.runner
+    got = runner.mtp
+    assert got.own_lm_head and not got.own_embedding and got.draft_vocab == DV and torch.equal(got.d2t, sd["d2t"])
+    assert runner.model.model.aux_hidden_layers == (2, 4, 5)
+    src = dict(head.named_parameters())
+    for name, q in got.named_parameters():
+        if not name.startswith("embed_tokens."):
+            assert torch.equal(q, src[name]), name
+    out = [o.outputs[0].token_ids for o in llm.generate(p, SamplingParams(temperature=0, max_tokens=16, ignore_eos=True))]
+    assert out == want
+    assert len(runner.model.model.last_aux) == 3 and all(a.shape[-1] == H for a in runner.model.model.last_aux)
+
+    # ---- the head's first pass on one 7-token sequence against plain PyTorch
+    T = 7
+    g = torch.Generator().manual_seed(9)
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    aux = torch.randn(T, 3 * H, generator=g)
+    cache = torch.zeros(4, 2, 2, 16, 16)
+    md = AttentionMetadata(1, T, torch.tensor([0, T], dtype=torch.int32), torch.tensor([T], dtype=torch.int32), torch.tensor([[1]], dtype=torch.int32),
+                           torch.arange(16, 16 + T, dtype=torch.int32), torch.arange(T, dtype=torch.int32), T, T, query_lens_cpu=[T], seq_lens_cpu=[T])
+    with torch.no_grad():
+        h_out = got(ids, aux, md, cache)
+        logits = got.compute_logits(h_out)
+
+        def rms(x, w):
+            return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-6) * w
+        L = got.layer
+        hidden = aux @ got.fc.weight.t()
+        emb = runner.model.model.embed_tokens.weight[ids.long()]
+        x = torch.cat([rms(emb, L.input_layernorm.weight), rms(hidden, got.hidden_norm.weight)], -1)
+        qkv = x @ L.self_attn.qkv_proj.weight.t()
+        q, k, v = qkv[:, :64].view(T, 4, 16), qkv[:, 64:96].view(T, 2, 16), qkv[:, 96:].view(T, 2, 16)
+        cs = ref.build_cos_sin_cache(16, 256, 10000.0, "cpu")[:T]
+        rot = lambda t: torch.cat([t[..., :8] * cs[:, None, :8] - t[..., 8:] * cs[:, None, 8:], t[..., 8:] * cs[:, None, :8] + t[..., :8] * cs[:, None, 8:]], -1)
+        q, k = rot(q), rot(k)
+        k, v = k.repeat_interleave(2, 1), v.repeat_interleave(2, 1)
+        att = torch.einsum("thd,shd->hts", q, k) * 16 ** -0.5
+        att = att.masked_fill(torch.triu(torch.ones(T, T, dtype=torch.bool), 1), float("-inf")).softmax(-1)
+        o = torch.einsum("hts,shd->thd", att, v).reshape(T, 64) @ L.self_attn.o_proj.weight.t()
+        r = hidden + o
+        x2 = rms(r, L.post_attention_layernorm.weight)
+        gu = x2 @ L.mlp.gate_up_proj.weight.t()
+        want_h = r + (torch.nn.functional.silu(gu[:, :128]) * gu[:, 128:]) @ L.mlp.down_proj.weight.t()
+        want_lg = rms(want_h, got.norm.weight) @ got.lm_head.weight.t()
+    assert torch.allclose(h_out, want_h, atol=2e-4, rtol=2e-4), float((h_out - want_h).abs().max())
+    assert logits.shape == (T, V) and torch.isinf(logits[:, [i for i in range(V) if i not in set(targets.tolist())]]).all()
+    assert torch.allclose(logits[:, targets], want_lg, atol=2e-3, rtol=2e-3)
+    llm.shutdown()
+
+
 def test_medusa_heads_are_lossless_and_load(tmp_path):
     from safetensors.torch import save_file
     from onecat_vllm.spec_decode.proposers import MedusaHeads

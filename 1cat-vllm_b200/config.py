@@ -133,7 +133,20 @@ class ModelConfig:
     qk_norm_full: bool = False  # q / k RMSNorm over the whole projection instead of per head (OLMo-2 / OLMo-3)
     num_labels: int = 0  # > 0: a *ForSequenceClassification checkpoint (a ``score`` head on the pooled state instead of an LM head)
     # hybrid (Gated-DeltaNet)
-    layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention"
+    layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention" (Gated-DeltaNet) | "mamba2" | "mamba1"
+    # Mamba-2 mixers (Bamba, Mamba2): heads x head size = inner width; B / C groups of the state size; conv kernel
+    mamba_n_heads: int = 0
+    mamba_d_head: int = 64
+    mamba_n_groups: int = 1
+    mamba_d_state: int = 128
+    mamba_d_conv: int = 4
+    mamba_conv_bias: bool = True
+    mamba_proj_bias: bool = False
+    mamba_time_step_limit: tuple = (0.0, float("inf"))
+    mamba_norm_groups: int = 1   # groups of the gated RMSNorm over the inner width
+    mamba_dt_rank: int = 0       # Mamba-1: width of the low-rank time-step projection
+    mamba_inner_rms_eps: Optional[float] = None  # FalconMamba: RMS normalisation (no weights) of dt / B / C inside the mixer
+    mixer_only_layers: bool = False  # blocks are norm -> mixer -> residual, without a feed-forward (Mamba2ForCausalLM)
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 48
     linear_key_head_dim: int = 128
@@ -193,7 +206,7 @@ class ModelConfig:
     # ---- derived
     @property
     def is_hybrid(self) -> bool:
-        return bool(self.layer_types) and any(t == "linear_attention" for t in self.layer_types)
+        return bool(self.layer_types) and any(t in ("linear_attention", "mamba2", "mamba1") for t in self.layer_types)
 
     @property
     def is_moe(self) -> bool:
@@ -294,6 +307,41 @@ class ModelConfig:
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
+        if arch in ("MambaForCausalLM", "FalconMambaForCausalLM"):
+            d_inner = int(hf.get("intermediate_size") or hf.get("expand", 2) * hidden)
+            rank = hf.get("time_step_rank", "auto")
+            kw.update(layer_types=["mamba1"] * kw["num_hidden_layers"], mamba_n_heads=1, mamba_d_head=d_inner, mamba_d_state=int(hf.get("state_size", 16)),
+                      mamba_d_conv=int(hf.get("conv_kernel", 4)), mamba_conv_bias=bool(hf.get("use_conv_bias", True)),
+                      mamba_proj_bias=bool(hf.get("use_bias", False)), mamba_dt_rank=-(-hidden // 16) if rank in (None, "auto") else int(rank),
+                      mamba_inner_rms_eps=float(hf.get("mixer_rms_eps", 1e-6)) if arch.startswith("FalconMamba") else None,
+                      mixer_only_layers=True, rms_norm_eps=hf.get("layer_norm_epsilon", 1e-5), intermediate_size=0,
+                      tie_word_embeddings=hf.get("tie_word_embeddings", True))
+        if arch in ("BambaForCausalLM", "Mamba2ForCausalLM"):
+            L = kw["num_hidden_layers"]
+            pure = arch == "Mamba2ForCausalLM"
+            expand = hf.get("mamba_expand", hf.get("expand", 2))
+            heads = hf.get("mamba_n_heads", hf.get("num_heads", 128))
+            d_head = hf.get("mamba_d_head", hf.get("head_dim", "auto"))
+            if d_head in (None, "auto") or pure:
+                d_head = int(expand * hidden) // heads if d_head in (None, "auto") else int(d_head)
+            attn_idx = set(hf.get("attn_layer_indices") or ())
+            def _num(v, default):   # json has no infinity: checkpoints write it as a string or a tagged object
+                try:
+                    return float(v)
+                except (TypeError, ValueError):
+                    return default
+            lim = hf.get("time_step_limit") or (0.0, float("inf"))
+            lim = (_num(lim[0], 0.0), _num(lim[1], float("inf")))
+            groups = hf.get("mamba_n_groups", hf.get("n_groups", 1))
+            kw.update(layer_types=["full_attention" if i in attn_idx else "mamba2" for i in range(L)], mamba_n_heads=int(heads),
+                      mamba_d_head=int(d_head), mamba_n_groups=int(groups), mamba_d_state=int(hf.get("mamba_d_state", hf.get("state_size", 128))),
+                      mamba_d_conv=int(hf.get("mamba_d_conv", hf.get("conv_kernel", 4))),
+                      mamba_conv_bias=bool(hf.get("mamba_conv_bias", hf.get("use_conv_bias", True))),
+                      mamba_proj_bias=bool(hf.get("mamba_proj_bias", hf.get("use_bias", False))),
+                      mamba_time_step_limit=(float(lim[0]), float(lim[1])), mamba_norm_groups=int(hf.get("mamba_norm_groups", groups)),
+                      mixer_only_layers=pure, rms_norm_eps=hf.get("rms_norm_eps", hf.get("layer_norm_epsilon", 1e-5)))
+            if pure:
+                kw.update(tie_word_embeddings=hf.get("tie_word_embeddings", True), intermediate_size=0)
         rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
         if rp.get("mrope_section"):
             kw["mrope_section"] = tuple(int(x) for x in rp["mrope_section"])

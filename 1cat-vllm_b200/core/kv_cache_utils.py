@@ -157,7 +157,9 @@ def get_kv_cache_config(layer_specs: dict, available_bytes: int, block_size: int
     if override_blocks is not None:
         n = override_blocks
     else:
-        n = max((available_bytes - reserved) // per_block, 0) if per_block else 1
+        # a model without attention layers keeps no KV: its blocks are bookkeeping only (positions of a request), so the pool just has
+        # to be large enough never to limit the batch
+        n = max((available_bytes - reserved) // per_block, 0) if per_block else max(1024, (max_num_seqs + 1) * 256)
     if attn and n < 2:
         raise ValueError("not enough memory for the KV cache: increase gpu_memory_utilization or lower max_model_len")
     return KVCacheConfig(int(n), block_size, dict(layer_specs), slots)

@@ -63,7 +63,10 @@ class Executor:
             kvc.num_cpu_blocks = cc.num_cpu_blocks_override or int(cc.kv_offloading_size * (1 << 30) // max(per_block, 1))
         cc.num_cpu_blocks = kvc.num_cpu_blocks
         max_need = -(-cfg.model_config.max_model_len // cfg.cache_config.block_size) + 1
-        if any(s.kind != "mamba" for s in specs.values()) and kvc.num_blocks < max_need:
+        if not any(s.kind != "mamba" for s in specs.values()) and cfg.cache_config.num_gpu_blocks_override is None:
+            # no attention layer: blocks only count positions, so every sequence may reach max_model_len at once
+            kvc.num_blocks = min((cfg.scheduler_config.max_num_seqs + 1) * max_need, 1 << 20)
+        if kvc.num_blocks < max_need:
             raise ValueError(f"KV cache of {kvc.num_blocks} blocks cannot hold one sequence of max_model_len="
                              f"{cfg.model_config.max_model_len} ({max_need} blocks): lower max_model_len or raise gpu_memory_utilization")
         cfg.cache_config.num_gpu_blocks = kvc.num_blocks

@@ -31,13 +31,17 @@ def iter_safetensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
 
 
 # checkpoint names whose tensors live under another name here (a parameter of the block instead of a sub-module's weight)
-_RENAMES = ((".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
+_RENAMES = ((".mamba.", ".linear_attn."), (".mixer.", ".linear_attn."), (".feed_forward.", ".mlp."), (".pre_ff_layernorm.", ".post_attention_layernorm."),
+            ("model.final_layernorm.", "model.norm."), ("backbone.embeddings.", "model.embed_tokens."), ("backbone.norm_f.", "model.norm."),
+            ("backbone.layers.", "model.layers."), (".linear_attn.conv1d.bias", ".linear_attn.conv_bias"),
+            (".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.router.", ".mlp.gate."), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.shared_experts.", ".mlp.shared_expert."))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
 _GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
                "post_mlp_layernorm": "post_feedforward_layernorm"}
+_BLOCK_NORM_RE = re.compile(r"(model\.layers\.\d+)\.norm\.")
 _GLM4_NORM_RE = re.compile(r"\.(post_attention_layernorm|post_self_attn_layernorm|post_mlp_layernorm)\.")
 
 
@@ -60,6 +64,7 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
     cfg = getattr(model, "cfg", None)
     glm4_norms = cfg is not None and cfg.sandwich_norm and cfg.architecture.startswith("Glm4")
     interleaved = cfg is not None and cfg.rope_interleaved
+    mixer_only = cfg is not None and getattr(cfg, "mixer_only_layers", False)
     loaded = set()
     for name, w in weights:
         if name.startswith("language_model."):
@@ -76,6 +81,8 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
         for theirs, ours in _RENAMES:
             if theirs in name:
                 name = name.replace(theirs, ours)
+        if mixer_only:   # Mamba2ForCausalLM: a block's only norm is the pre-norm of its mixer
+            name = _BLOCK_NORM_RE.sub(r"\1.input_layernorm.", name)
         if glm4_norms:
             name = _GLM4_NORM_RE.sub(lambda m: "." + _GLM4_NORMS[m.group(1)] + ".", name)
         if interleaved and (".q_proj." in name or ".k_proj." in name) and "self_attn" in name:

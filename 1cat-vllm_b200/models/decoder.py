@@ -40,8 +40,20 @@ class DecoderLayer(nn.Module):
             self.self_attn = MLAAttention(cfg, idx, prefix + ".self_attn", device)
         elif self.kind == "linear_attention":
             self.linear_attn = GatedDeltaNet(cfg, idx, prefix + ".linear_attn")
+        elif self.kind in ("mamba2", "mamba1"):
+            if self.kind == "mamba2":
+                from onecat_vllm.layers.mamba2 import Mamba2Mixer as Mixer
+            else:
+                from onecat_vllm.layers.mamba1 import Mamba1Mixer as Mixer
+            self.linear_attn = Mixer(cfg, idx, prefix + ".linear_attn")
+            self.kind = "linear_attention"   # a state-slot layer like Gated-DeltaNet for the runner and the scheduler
+            self.graph_safe = False          # its convolution and scan read batch geometry on the host
         else:
             self.self_attn = Attention(cfg, idx, prefix + ".self_attn", device)
+        if cfg.mixer_only_layers:
+            self.mlp = None
+            self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+            return
         if cfg.is_moe_layer(idx):
             self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
         else:
@@ -112,6 +124,11 @@ class DecoderModel(nn.Module):
             if aux_at and i in aux_at:
                 self.last_aux.append(residual)   # the stream entering layer i (reference: models/llama.py ``aux_hidden_state_layers``)
             part = layer.mixer(x, md, caches[li])
+            if layer.mlp is None:   # norm -> mixer -> residual blocks: the next block's norm (or the final one) follows directly
+                if i + 1 == self.end and not self.last_stage:
+                    return reduce_only(part), residual
+                x, residual = reduce_add_norm(part, residual, layers[i + 1].input_layernorm if i + 1 < self.end else self.norm)
+                continue
             if plain:
                 x, residual = reduce_add_norm(part, residual, layer.post_attention_layernorm)
             else:

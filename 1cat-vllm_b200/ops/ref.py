@@ -573,3 +573,77 @@ def rejection_sample(draft_ids, num_draft, target_logits_or_probs, bonus_ids, dr
         if not rejected:
             out[b, n] = int(bonus_ids[b])
     return out
+
+
+# ----------------------------------------------------------------------------- Mamba-2 (state-space duality) scan
+def mamba2_scan(x, dt, A, B, C, D, ssm_state, query_start_loc, state_slots, has_initial_state, chunk: int = 64):
+    """Selective state-space recurrence of Mamba-2 over varlen sequences, state per (sequence, head) kept in ``ssm_state``
+    ``[slots, H, P, N]`` fp32 and updated in place:  ``h_t = exp(dt_t A) h_{t-1} + dt_t x_t ⊗ B_t``,  ``y_t = h_t C_t + D x_t``.
+    x ``[T, H, P]``, dt ``[T, H]`` (after softplus), A ``[H]`` (negative), B / C ``[T, G, N]`` with H a multiple of G, D ``[H]``.
+    Sequences longer than one token run the chunked form (quadratic inside a chunk of ``chunk`` tokens, a recurrence over chunk
+    states between them), single tokens the recurrence itself
+    (reference: layers/mamba/ops/ssd_combined.py ``mamba_chunk_scan_combined``; layers/mamba/ops/mamba_ssm.py ``selective_state_update``)."""
+    T, H, P = x.shape
+    G, N = B.shape[1], B.shape[2]
+    rep = H // G
+    y = torch.empty(T, H, P, dtype=torch.float32, device=x.device)
+    qsl = query_start_loc.tolist()
+    Af, Df = A.float(), D.float()
+    for r in range(len(qsl) - 1):
+        a, b = qsl[r], qsl[r + 1]
+        L = b - a
+        if L == 0:
+            continue
+        slot = int(state_slots[r])
+        h = ssm_state[slot].float() if bool(has_initial_state[r]) else torch.zeros(H, P, N, device=x.device)
+        xs, dts = x[a:b].float(), dt[a:b].float()
+        Bs = B[a:b].float().repeat_interleave(rep, dim=1)       # [L, H, N]
+        Cs = C[a:b].float().repeat_interleave(rep, dim=1)
+        if L == 1:
+            h = h * torch.exp(dts[0] * Af).view(H, 1, 1) + (dts[0].view(H, 1) * xs[0]).unsqueeze(-1) * Bs[0].unsqueeze(1)
+            y[a] = torch.einsum("hpn,hn->hp", h, Cs[0]) + Df.view(H, 1) * xs[0]
+            ssm_state[slot] = h
+            continue
+        for c0 in range(0, L, chunk):
+            c1 = min(c0 + chunk, L)
+            xc, dtc, Bc, Cc = xs[c0:c1], dts[c0:c1], Bs[c0:c1], Cs[c0:c1]
+            cum = torch.cumsum(dtc * Af, dim=0)                  # [Q, H] log-decay from the chunk start up to and including t
+            # inside the chunk: y_i += sum_{j <= i} exp(cum_i - cum_j) (C_i . B_j) dt_j x_j
+            decay = torch.exp((cum.unsqueeze(1) - cum.unsqueeze(0)).permute(2, 0, 1))            # [H, Q(i), Q(j)]
+            decay = torch.tril(decay)
+            cb = torch.einsum("ihn,jhn->hij", Cc, Bc)
+            yc = torch.einsum("hij,jh,jhp->ihp", cb * decay, dtc, xc)
+            # the state carried into the chunk
+            yc = yc + torch.einsum("ihn,hpn,ih->ihp", Cc, h, torch.exp(cum))
+            y[a + c0:a + c1] = yc + Df.view(1, H, 1) * xc
+            # state after the chunk
+            tail = torch.exp(cum[-1].unsqueeze(0) - cum)         # [Q, H] decay from t to the chunk end
+            h = h * torch.exp(cum[-1]).view(H, 1, 1) + torch.einsum("jh,jh,jhp,jhn->hpn", tail, dtc, xc, Bc)
+        ssm_state[slot] = h
+    return y
+
+
+def mamba1_scan(x, dt, A, B, C, D, ssm_state, query_start_loc, state_slots, has_initial_state):
+    """Selective scan of Mamba-1 over varlen sequences: one state ``[d_inner, N]`` per sequence in ``ssm_state`` ``[slots, 1, d_inner, N]``
+    fp32, updated in place:  ``h_t = exp(dt_t ⊗ A) h_{t-1} + (dt_t x_t) ⊗ B_t``,  ``y_t = h_t C_t + D x_t``.
+    x, dt ``[T, d_inner]`` (dt after softplus), A ``[d_inner, N]`` (negative), B / C ``[T, N]``, D ``[d_inner]``. The decay differs per
+    channel and state index, so the recurrence runs token by token, vectorised over channels
+    (reference: layers/mamba/ops/mamba_ssm.py ``selective_scan_fn`` / ``selective_state_update``)."""
+    T, Di = x.shape
+    y = torch.empty(T, Di, dtype=torch.float32, device=x.device)
+    qsl = query_start_loc.tolist()
+    Af, Df = A.float(), D.float()
+    for r in range(len(qsl) - 1):
+        a, b = qsl[r], qsl[r + 1]
+        if a == b:
+            continue
+        slot = int(state_slots[r])
+        h = ssm_state[slot, 0].float() if bool(has_initial_state[r]) else torch.zeros(Di, Af.shape[1], device=x.device)
+        xs, dts, Bs, Cs = x[a:b].float(), dt[a:b].float(), B[a:b].float(), C[a:b].float()
+        dA = torch.exp(dts.unsqueeze(-1) * Af.unsqueeze(0))                  # [L, d_inner, N]
+        dBx = (dts * xs).unsqueeze(-1) * Bs.unsqueeze(1)                     # [L, d_inner, N]
+        for t in range(b - a):
+            h = dA[t] * h + dBx[t]
+            y[a + t] = h @ Cs[t] + Df * xs[t]
+        ssm_state[slot, 0] = h
+    return y

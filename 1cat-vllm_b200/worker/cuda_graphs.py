@@ -49,7 +49,7 @@ class DecodeGraphs:
         # every mixer's decode path runs without host synchronisation on fixed addresses (attention, latent attention, Gated-DeltaNet
         # with its state slots; fused mixture-of-experts builds its work list on the device). What stays eager: experts that run the
         # per-expert loop (biased / clamped activations), pipeline stages, and anything without an attention geometry.
-        kinds_ok = all(l.kind in ("full_attention", "linear_attention", "mla") for l in runner.model.model.layers)
+        kinds_ok = all(l.kind in ("full_attention", "linear_attention", "mla") and getattr(l, "graph_safe", True) for l in runner.model.model.layers)
         moe_ok = all(getattr(getattr(l.mlp, "experts", None), "kernel_state", True) is not None for l in runner.model.model.layers if hasattr(l, "mlp"))
         self.eligible = kinds_ok and moe_ok and self.geom is not None
         self.hits = self.misses = 0

@@ -316,7 +316,19 @@ class ModelConfig:
                       mamba_inner_rms_eps=float(hf.get("mixer_rms_eps", 1e-6)) if arch.startswith("FalconMamba") else None,
                       mixer_only_layers=True, rms_norm_eps=hf.get("layer_norm_epsilon", 1e-5), intermediate_size=0,
                       tie_word_embeddings=hf.get("tie_word_embeddings", True))
-        if arch in ("BambaForCausalLM", "Mamba2ForCausalLM"):
+        if arch == "GraniteMoeHybridForCausalLM":
+            # Granite 4.0: Bamba's mixers + Granite multipliers + experts with an ungated shared feed-forward (or, without experts,
+            # that feed-forward alone)
+            kinds = hf.get("layer_types") or ["mamba"] * kw["num_hidden_layers"]
+            hf = dict(hf, attn_layer_indices=[i for i, t in enumerate(kinds) if t == "attention"])
+            shared = int(hf.get("shared_intermediate_size") or 0)
+            if kw.get("num_experts"):
+                kw.update(shared_expert_intermediate_size=shared, shared_expert_gate=False, norm_topk_prob=True)
+            else:
+                kw["intermediate_size"] = shared
+            if hf.get("position_embedding_type") == "nope":
+                kw["nope_layers"] = tuple(range(kw["num_hidden_layers"]))
+        if arch in ("BambaForCausalLM", "Mamba2ForCausalLM", "GraniteMoeHybridForCausalLM"):
             L = kw["num_hidden_layers"]
             pure = arch == "Mamba2ForCausalLM"
             expand = hf.get("mamba_expand", hf.get("expand", 2))

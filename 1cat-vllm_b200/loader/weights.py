@@ -134,6 +134,19 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
                         mod.load_expert_weight(e, "down_proj", "weight", w[e])
                 loaded.add(name)
             continue
+        if ".shared_mlp.input_linear." in name or ".shared_mlp.output_linear." in name:
+            # Granite's shared feed-forward keeps gate|up stacked in one tensor: it is the shared expert beside routed experts, or the
+            # layer's whole feed-forward when the model has none
+            base = name.split(".shared_mlp.")[0] + ".mlp"
+            tgt = base + ".shared_expert" if (base + ".shared_expert") in mods else base
+            suffix = name.rsplit(".", 1)[1]
+            if ".input_linear." in name:
+                mods[tgt + ".gate_up_proj"].load_weight(suffix, w[: w.shape[0] // 2], 0)
+                mods[tgt + ".gate_up_proj"].load_weight(suffix, w[w.shape[0] // 2:], 1)
+            else:
+                mods[tgt + ".down_proj"].load_weight(suffix, w, None)
+            loaded.add(name)
+            continue
         if ".block_sparse_moe.input_linear." in name or ".block_sparse_moe.output_linear." in name:
             # GraniteMoe keeps all experts of a layer in one tensor: gate|up stacked [E, 2I, H] and down [E, H, I]
             mod = mods.get(name.split(".block_sparse_moe.")[0] + ".mlp.experts")

@@ -129,3 +129,30 @@ def test_mamba1_matches_hugging_face(tmp_path, falcon):
     got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
     llm.shutdown()
     assert got == want
+
+
+@pytest.mark.parametrize("experts", [0, 4])
+def test_granite_hybrid_matches_hugging_face(tmp_path, experts):
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import GraniteMoeHybridConfig, GraniteMoeHybridForCausalLM
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no GraniteMoeHybrid: {e}")
+    cfg = GraniteMoeHybridConfig(vocab_size=300, hidden_size=64, intermediate_size=48, shared_intermediate_size=96, num_hidden_layers=4,
+                                 num_attention_heads=4, num_key_value_heads=2, layer_types=["mamba", "attention", "mamba", "attention"],
+                                 num_local_experts=experts, num_experts_per_tok=2 if experts else 0, mamba_n_heads=8, mamba_d_head=16,
+                                 mamba_n_groups=1, mamba_d_state=16, mamba_d_conv=4, mamba_expand=2, mamba_chunk_size=16,
+                                 embedding_multiplier=3.0, residual_multiplier=0.5, attention_multiplier=0.2, logits_scaling=4.0,
+                                 position_embedding_type="nope", max_position_embeddings=512, tie_word_embeddings=False, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = GraniteMoeHybridForCausalLM(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        if "norm" not in n and "A_log" not in n and "dt_bias" not in n and n.rsplit(".", 1)[-1] != "D":
+            torch.nn.init.normal_(p, std=0.15)
+    _save(hf, tmp_path, "GraniteMoeHybridForCausalLM")
+    prompts = _prompts(300)
+    want = _hf_greedy(hf, prompts, 12)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=48)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    llm.shutdown()
+    assert got == want

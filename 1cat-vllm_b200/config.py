@@ -146,6 +146,7 @@ class ModelConfig:
     mamba_norm_groups: int = 1   # groups of the gated RMSNorm over the inner width
     mamba_dt_rank: int = 0       # Mamba-1: width of the low-rank time-step projection
     mamba_inner_rms_eps: Optional[float] = None  # FalconMamba: RMS normalisation (no weights) of dt / B / C inside the mixer
+    mamba_inner_norm_weights: bool = False  # Jamba: RMSNorm layers with weights on dt / B / C inside the mixer
     mixer_only_layers: bool = False  # blocks are norm -> mixer -> residual, without a feed-forward (Mamba2ForCausalLM)
     linear_num_key_heads: int = 16
     linear_num_value_heads: int = 48
@@ -307,6 +308,18 @@ class ModelConfig:
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
+        if arch == "JambaForCausalLM":
+            L = kw["num_hidden_layers"]
+            ap, ao = int(hf.get("attn_layer_period", 8)), int(hf.get("attn_layer_offset", 4))
+            ep, eo = int(hf.get("expert_layer_period", 2)), int(hf.get("expert_layer_offset", 1))
+            rank = hf.get("mamba_dt_rank", "auto")
+            kw.update(layer_types=["full_attention" if (i - ao) % ap == 0 else "mamba1" for i in range(L)], nope_layers=tuple(range(L)),
+                      mamba_n_heads=1, mamba_d_head=int(hf.get("mamba_expand", 2) * hidden), mamba_d_state=int(hf.get("mamba_d_state", 16)),
+                      mamba_d_conv=int(hf.get("mamba_d_conv", 4)), mamba_conv_bias=bool(hf.get("mamba_conv_bias", True)),
+                      mamba_proj_bias=bool(hf.get("mamba_proj_bias", False)), mamba_dt_rank=-(-hidden // 16) if rank in (None, "auto") else int(rank),
+                      mamba_inner_norm_weights=True)
+            if kw.get("num_experts"):
+                kw.update(norm_topk_prob=False, dense_layers=tuple(i for i in range(L) if (i - eo) % ep != 0))
         if arch in ("MambaForCausalLM", "FalconMambaForCausalLM"):
             d_inner = int(hf.get("intermediate_size") or hf.get("expand", 2) * hidden)
             rank = hf.get("time_step_rank", "auto")

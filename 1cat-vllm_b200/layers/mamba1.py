@@ -3,7 +3,7 @@
 
 x → in_proj → [x | z];  x → depthwise causal conv (bias, SiLU) with a rolling state;  x_proj(x) → [dt_low | B | C];
 dt = softplus(dt_proj(dt_low));  A = -exp(A_log) per (channel, state index);  h_t = exp(dt ⊗ A) h_{t-1} + (dt x) ⊗ B,
-y = h C + D x;  y * SiLU(z) → out_proj. FalconMamba normalises dt_low, B and C (RMS without weights) first.
+y = h C + D x;  y * SiLU(z) → out_proj. FalconMamba normalises dt_low, B and C (RMS without weights) first, Jamba with weights.
 
 Runs as PyTorch operations on every device (``ops.ref.mamba1_scan``): no CUDA kernel, tensor_parallel_size 1, no speculative decoding."""
 from __future__ import annotations
@@ -33,6 +33,12 @@ class Mamba1Mixer(nn.Module):
         self.D = nn.Parameter(torch.ones(self.d_inner, dtype=torch.float32), requires_grad=False)
         self.out_proj = ReplicatedLinear(self.d_inner, cfg.hidden_size, bias=cfg.mamba_proj_bias, quant=None, prefix=prefix + ".out_proj", dtype=cfg.dtype)
         self.inner_rms_eps = cfg.mamba_inner_rms_eps
+        self.inner_norms = cfg.mamba_inner_norm_weights   # Jamba: RMSNorm with weights on dt_low, B and C
+        if self.inner_norms:
+            from onecat_vllm.layers.common import RMSNorm
+            self.dt_layernorm = RMSNorm(self.dt_rank, cfg.rms_norm_eps, False, cfg.dtype)
+            self.b_layernorm = RMSNorm(self.N, cfg.rms_norm_eps, False, cfg.dtype)
+            self.c_layernorm = RMSNorm(self.N, cfg.rms_norm_eps, False, cfg.dtype)
         self.layer_idx = layer_idx
 
     def load_weight(self, pname: str, w: torch.Tensor, shard=None) -> None:
@@ -54,6 +60,8 @@ class Mamba1Mixer(nn.Module):
         if self.inner_rms_eps is not None:
             rms = lambda t: (t.float() * torch.rsqrt(t.float().pow(2).mean(-1, keepdim=True) + self.inner_rms_eps)).to(t.dtype)
             dt_low, B, C = rms(dt_low), rms(B), rms(C)
+        if self.inner_norms:
+            dt_low, B, C = self.dt_layernorm(dt_low.contiguous(), None)[0], self.b_layernorm(B.contiguous(), None)[0], self.c_layernorm(C.contiguous(), None)[0]
         dt = F.softplus(self.dt_proj(dt_low).float())
         y = ref.mamba1_scan(xs, dt, -torch.exp(self.A_log), B, C, self.D, ssm_state, md.query_start_loc, md.state_slots, md.has_initial_state)
         return self.out_proj((y * F.silu(z.float())).to(x.dtype))

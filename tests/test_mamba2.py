@@ -156,3 +156,27 @@ def test_granite_hybrid_matches_hugging_face(tmp_path, experts):
     got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
     llm.shutdown()
     assert got == want
+
+
+def test_jamba_matches_hugging_face(tmp_path):
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import JambaConfig, JambaForCausalLM
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no Jamba: {e}")
+    cfg = JambaConfig(vocab_size=300, hidden_size=64, intermediate_size=96, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                      num_experts=4, num_experts_per_tok=2, attn_layer_period=2, attn_layer_offset=1, expert_layer_period=2, expert_layer_offset=1,
+                      mamba_d_state=8, mamba_d_conv=4, mamba_expand=2, mamba_dt_rank=6, use_mamba_kernels=False, max_position_embeddings=512,
+                      tie_word_embeddings=False, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = JambaForCausalLM(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        if "norm" not in n and "A_log" not in n and n.rsplit(".", 1)[-1] != "D" and "dt_proj.bias" not in n:
+            torch.nn.init.normal_(p, std=0.15)
+    _save(hf, tmp_path, "JambaForCausalLM")
+    prompts = _prompts(300)
+    want = _hf_greedy(hf, prompts, 12)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=48)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    llm.shutdown()
+    assert got == want

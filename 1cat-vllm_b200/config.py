@@ -133,7 +133,7 @@ class ModelConfig:
     qk_norm_full: bool = False  # q / k RMSNorm over the whole projection instead of per head (OLMo-2 / OLMo-3)
     num_labels: int = 0  # > 0: a *ForSequenceClassification checkpoint (a ``score`` head on the pooled state instead of an LM head)
     # hybrid (Gated-DeltaNet)
-    layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention" (Gated-DeltaNet) | "mamba2" | "mamba1"
+    layer_types: Optional[list[str]] = None  # "full_attention" | "linear_attention" (Gated-DeltaNet) | "mamba2" | "mamba1" | "short_conv"
     # Mamba-2 mixers (Bamba, Mamba2): heads x head size = inner width; B / C groups of the state size; conv kernel
     mamba_n_heads: int = 0
     mamba_d_head: int = 64
@@ -207,7 +207,7 @@ class ModelConfig:
     # ---- derived
     @property
     def is_hybrid(self) -> bool:
-        return bool(self.layer_types) and any(t in ("linear_attention", "mamba2", "mamba1") for t in self.layer_types)
+        return bool(self.layer_types) and any(t in ("linear_attention", "mamba2", "mamba1", "short_conv") for t in self.layer_types)
 
     @property
     def is_moe(self) -> bool:
@@ -308,6 +308,18 @@ class ModelConfig:
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
+        if arch == "Lfm2ForCausalLM":
+            inter = int(hf.get("intermediate_size", 4 * hidden))
+            if hf.get("block_auto_adjust_ff_dim", True):   # the checkpoint's feed-forward width: 2/3 of the nominal one, rounded up to a multiple
+                inter = int(2 * inter / 3)
+                if hf.get("block_ffn_dim_multiplier") is not None:
+                    mult = int(hf.get("block_multiple_of", 256))
+                    inter = int(float(hf["block_ffn_dim_multiplier"]) * inter)
+                    inter = mult * ((inter + mult - 1) // mult)
+            kinds = hf.get("layer_types") or ["full_attention"] * kw["num_hidden_layers"]
+            kw.update(layer_types=["full_attention" if t == "full_attention" else "short_conv" for t in kinds], intermediate_size=inter,
+                      mamba_d_conv=int(hf.get("conv_L_cache", 3)), mamba_conv_bias=bool(hf.get("conv_bias", False)), qk_norm=True,
+                      rms_norm_eps=float(hf.get("norm_eps", 1e-5)), tie_word_embeddings=hf.get("tie_word_embeddings", True))
         if arch == "JambaForCausalLM":
             L = kw["num_hidden_layers"]
             ap, ao = int(hf.get("attn_layer_period", 8)), int(hf.get("attn_layer_offset", 4))

@@ -40,11 +40,13 @@ class DecoderLayer(nn.Module):
             self.self_attn = MLAAttention(cfg, idx, prefix + ".self_attn", device)
         elif self.kind == "linear_attention":
             self.linear_attn = GatedDeltaNet(cfg, idx, prefix + ".linear_attn")
-        elif self.kind in ("mamba2", "mamba1"):
+        elif self.kind in ("mamba2", "mamba1", "short_conv"):
             if self.kind == "mamba2":
                 from onecat_vllm.layers.mamba2 import Mamba2Mixer as Mixer
-            else:
+            elif self.kind == "mamba1":
                 from onecat_vllm.layers.mamba1 import Mamba1Mixer as Mixer
+            else:
+                from onecat_vllm.layers.short_conv import ShortConv as Mixer
             self.linear_attn = Mixer(cfg, idx, prefix + ".linear_attn")
             self.kind = "linear_attention"   # a state-slot layer like Gated-DeltaNet for the runner and the scheduler
             self.graph_safe = False          # its convolution and scan read batch geometry on the host

@@ -180,3 +180,25 @@ def test_jamba_matches_hugging_face(tmp_path):
     got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
     llm.shutdown()
     assert got == want
+
+
+def test_lfm2_short_conv_matches_hugging_face(tmp_path):
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import Lfm2Config, Lfm2ForCausalLM
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no LFM2: {e}")
+    cfg = Lfm2Config(vocab_size=300, hidden_size=64, intermediate_size=200, num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2,
+                     layer_types=["conv", "conv", "full_attention", "conv"], block_multiple_of=16, max_position_embeddings=512, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = Lfm2ForCausalLM(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        if "norm" not in n:
+            torch.nn.init.normal_(p, std=0.15)
+    _save(hf, tmp_path, "Lfm2ForCausalLM")
+    prompts = _prompts(300)
+    want = _hf_greedy(hf, prompts, 12)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=48)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    llm.shutdown()
+    assert got == want

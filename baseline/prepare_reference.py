@@ -6,7 +6,7 @@ to ``baseline/_ref/vllm`` and links the compiled extension modules of the vLLM w
 ``_C_stable_libtorch``, flash-attention, ...) beside them. ``bench.py --impl reference`` then imports *that* package in a subprocess and
 drives it through its own ``LLM.generate``; whether the fork's Python and the stock binaries agree is found out at run time.
 
-    python baseline/prepare_reference.py [/path/to/reference]
+    python baseline/prepare_reference.py /path/to/reference      (or ONECAT_REFERENCE_DIR)
 """
 import importlib.util
 import os
@@ -18,7 +18,10 @@ DST = os.path.join(HERE, "_ref")
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("ONECAT_REFERENCE_DIR")
+    if not ref:
+        print("usage: prepare_reference.py /path/to/reference")
+        return 2
     src = os.path.join(ref, "vllm")
     if not os.path.isdir(src):
         print(f"no reference tree at {src}")

@@ -341,6 +341,8 @@ class ModelConfig:
                       mamba_inner_rms_eps=float(hf.get("mixer_rms_eps", 1e-6)) if arch.startswith("FalconMamba") else None,
                       mixer_only_layers=True, rms_norm_eps=hf.get("layer_norm_epsilon", 1e-5), intermediate_size=0,
                       tie_word_embeddings=hf.get("tie_word_embeddings", True))
+        if arch == "GraniteMoeSharedForCausalLM" and kw.get("num_experts"):
+            kw.update(shared_expert_intermediate_size=int(hf.get("shared_intermediate_size") or 0), shared_expert_gate=False, norm_topk_prob=True)
         if arch == "GraniteMoeHybridForCausalLM":
             # Granite 4.0: Bamba's mixers + Granite multipliers + experts with an ungated shared feed-forward (or, without experts,
             # that feed-forward alone)
@@ -429,6 +431,13 @@ class ModelConfig:
                 kw.update(shared_expert_intermediate_size=hf.get("n_shared_experts", 1) * hf.get("moe_intermediate_size", 1408),
                           shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),
                           routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=hf.get("first_k_dense_replace", 1))
+        if a.startswith("minimaxm2"):
+            # sigmoid router with a selection bias, weights renormalised over the chosen experts; q / k normalised over the whole projection
+            kw.update(qk_norm=False, qk_norm_full=bool(hf.get("use_qk_norm", True)), scoring_func="sigmoid",
+                      n_group=1, topk_group=1, norm_topk_prob=True, routed_scaling_factor=1.0, shared_expert_intermediate_size=0,
+                      shared_expert_gate=False)
+            if hf.get("rotary_dim"):
+                kw["partial_rotary_factor"] = float(hf["rotary_dim"]) / kw["head_dim"]
         if "smollm3" in a and hf.get("no_rope_layers"):
             kw["nope_layers"] = tuple(i for i, v in enumerate(hf["no_rope_layers"]) if not v)
         if a.startswith("exaone4"):

@@ -466,6 +466,13 @@ class ModelConfig:
                       shared_expert_intermediate_size=(hf.get("moe_num_shared_experts") or 0) * hf.get("moe_intermediate_size", 1536),
                       shared_expert_gate=False, attention_bias=bool(hf.get("use_bias", False)),
                       dense_layers=tuple(i for i in range(kw["num_hidden_layers"]) if not (start <= i <= end and (i + 1) % iv == 0)))
+        if a.startswith("hunyuanmoev1"):
+            # softmax router renormalised over the chosen experts; an ungated shared feed-forward of the dense width beside them
+            topk = hf.get("moe_topk", 2)
+            kw.update(qk_norm=bool(hf.get("use_qk_norm", True)), qk_norm_after_rope=True, num_experts_per_tok=int(topk if isinstance(topk, int) else topk[0]),
+                      norm_topk_prob=True, moe_intermediate_size=int(hf.get("moe_intermediate_size") or hf.get("intermediate_size", 512))
+                      if isinstance(hf.get("moe_intermediate_size"), (int, type(None))) else int(hf["moe_intermediate_size"][0]),
+                      shared_expert_intermediate_size=int(hf.get("intermediate_size", 512)), shared_expert_gate=False)
         if a.startswith("hunyuandensev1"):
             kw.update(qk_norm=True, qk_norm_after_rope=True)
         if a.startswith("helium"):

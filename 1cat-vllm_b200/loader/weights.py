@@ -42,7 +42,7 @@ _RENAMES = ((".conv.conv.weight", ".linear_attn.conv_weight"), (".conv.conv.bias
             (".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.router.", ".mlp.gate."), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
-            (".mlp.shared_experts.", ".mlp.shared_expert."))
+            (".mlp.shared_experts.", ".mlp.shared_expert."), (".mlp.shared_mlp.", ".mlp.shared_expert."), (".mlp.gate.wg.", ".mlp.gate."))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
 _GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
                "post_mlp_layernorm": "post_feedforward_layernorm"}

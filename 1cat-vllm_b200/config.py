@@ -425,6 +425,9 @@ class ModelConfig:
                           attn_softcap=float(hf.get("attn_logit_softcapping") or 0.0), final_softcap=float(hf.get("final_logit_softcapping") or 0.0))
             if "gemma3" in a:
                 kw["qk_norm"] = True
+            if a.startswith("vaultgemma"):   # Gemma-2's attention (scaling, soft caps, windows by layer type) without the sandwich norms
+                kw.update(attn_scale=float(hf.get("query_pre_attn_scalar", kw["head_dim"])) ** -0.5,
+                          attn_softcap=float(hf.get("attn_logit_softcapping") or 0.0), final_softcap=float(hf.get("final_logit_softcapping") or 0.0))
         if a.startswith("glm"):
             kw.update(rope_interleaved="moe" not in a, sandwich_norm=a.startswith("glm4for"), qk_norm=bool(hf.get("use_qk_norm", False)))
             if "moe" in a:
@@ -479,7 +482,7 @@ class ModelConfig:
             kw["rope_interleaved"] = True
         if a.startswith("ernie4_5for"):
             kw.update(rope_interleaved=True, attention_bias=bool(hf.get("use_bias", False)))
-        if a.startswith("olmo2") or a.startswith("olmo3"):
+        if a.startswith(("olmo2", "olmo3", "flexolmo")):
             kw.update(pre_norm=False, sandwich_norm=True, qk_norm_full=True)
         if "granite" in a:
             kw.update(embed_scale=float(hf.get("embedding_multiplier", 1.0)), residual_multiplier=float(hf.get("residual_multiplier", 1.0)),

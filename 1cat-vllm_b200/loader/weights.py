@@ -70,6 +70,7 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
     glm4_norms = cfg is not None and cfg.sandwich_norm and cfg.architecture.startswith("Glm4")
     interleaved = cfg is not None and cfg.rope_interleaved
     mixer_only = cfg is not None and getattr(cfg, "mixer_only_layers", False)
+    vault = cfg is not None and cfg.architecture.startswith("VaultGemma")
     loaded = set()
     for name, w in weights:
         if name.startswith("language_model."):
@@ -86,6 +87,8 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
         for theirs, ours in _RENAMES:
             if theirs in name:
                 name = name.replace(theirs, ours)
+        if vault and ".pre_feedforward_layernorm." in name:   # VaultGemma: Gemma-2's blocks without the two post-norms
+            name = name.replace(".pre_feedforward_layernorm.", ".post_attention_layernorm.")
         if mixer_only:   # Mamba2ForCausalLM: a block's only norm is the pre-norm of its mixer
             name = _BLOCK_NORM_RE.sub(r"\1.input_layernorm.", name)
         if glm4_norms:

@@ -107,6 +107,9 @@ CASES = {
                                         num_local_experts=4, num_experts_per_tok=2, embedding_multiplier=6.0, residual_multiplier=0.3,
                                         attention_multiplier=0.2, logits_scaling=4.0, pad_token_id=0),
     "HunYuanMoEV1ForCausalLM": dict(BASE, model_type="hunyuan_v1_moe", head_dim=16, rope_theta=10000.0, num_experts=4, moe_topk=2, pad_token_id=0),
+    "Ministral3ForCausalLM": dict(BASE, model_type="ministral3", head_dim=16, pad_token_id=0),
+    "VaultGemmaForCausalLM": dict(BASE, model_type="vaultgemma", head_dim=16, pad_token_id=0),
+    "FlexOlmoForCausalLM": dict(BASE, model_type="flex_olmo", num_experts=4, num_experts_per_tok=2, pad_token_id=0),
     "MiniMaxM2ForCausalLM": dict(BASE, model_type="minimax_m2", head_dim=16, intermediate_size=48, num_local_experts=8, num_experts_per_tok=2,
                                  pad_token_id=0),
 }

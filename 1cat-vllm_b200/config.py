@@ -448,6 +448,16 @@ class ModelConfig:
             kw.update(pre_norm=False, sandwich_norm=True, qk_norm=True)
             if kw.get("sliding_layers"):
                 kw["nope_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i not in kw["sliding_layers"])
+        if a.startswith("exaonemoe"):
+            # pre-norm blocks with per-head q/k norm; global layers of the hybrid form apply no rotary embedding; DeepSeek-V3-style router
+            kinds = hf.get("mlp_layer_types") or []
+            kw.update(qk_norm=True, shared_expert_intermediate_size=(hf.get("num_shared_experts") or 0) * hf.get("moe_intermediate_size", 1024),
+                      shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),
+                      routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
+                      dense_layers=tuple(i for i, t in enumerate(kinds) if t != "sparse") if kinds else
+                      tuple(range(int(hf.get("first_k_dense_replace", 0)))))
+            if kw.get("sliding_layers"):
+                kw["nope_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i not in kw["sliding_layers"])
         if a.startswith("dots1"):
             kw.update(qk_norm=True, shared_expert_intermediate_size=(hf.get("n_shared_experts") or 0) * hf.get("moe_intermediate_size", 1408),
                       shared_expert_gate=False, scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1),

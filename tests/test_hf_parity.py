@@ -110,6 +110,10 @@ CASES = {
     "Ministral3ForCausalLM": dict(BASE, model_type="ministral3", head_dim=16, pad_token_id=0),
     "VaultGemmaForCausalLM": dict(BASE, model_type="vaultgemma", head_dim=16, pad_token_id=0),
     "FlexOlmoForCausalLM": dict(BASE, model_type="flex_olmo", num_experts=4, num_experts_per_tok=2, pad_token_id=0),
+    "ExaoneMoeForCausalLM": dict(BASE, model_type="exaone_moe", head_dim=16, num_hidden_layers=4, num_experts=8, num_experts_per_tok=2,
+                                 moe_intermediate_size=48, n_group=2, topk_group=1, routed_scaling_factor=1.5, sliding_window=16, sliding_window_pattern=2,
+                                 layer_types=["sliding_attention", "full_attention", "sliding_attention", "full_attention"],
+                                 mlp_layer_types=["dense", "sparse", "sparse", "sparse"], pad_token_id=0),
     "MiniMaxM2ForCausalLM": dict(BASE, model_type="minimax_m2", head_dim=16, intermediate_size=48, num_local_experts=8, num_experts_per_tok=2,
                                  pad_token_id=0),
 }

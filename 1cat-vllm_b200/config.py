@@ -308,9 +308,14 @@ class ModelConfig:
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
-        if arch == "Lfm2ForCausalLM":
+        if arch in ("Lfm2ForCausalLM", "Lfm2MoeForCausalLM"):
             inter = int(hf.get("intermediate_size", 4 * hidden))
-            if hf.get("block_auto_adjust_ff_dim", True):   # the checkpoint's feed-forward width: 2/3 of the nominal one, rounded up to a multiple
+            if arch == "Lfm2MoeForCausalLM":
+                # the dense width is taken as it stands; experts behind a sigmoid router with a selection bias, after the first dense layers
+                kw.update(scoring_func="sigmoid", n_group=1, topk_group=1, norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
+                          routed_scaling_factor=float(hf.get("routed_scaling_factor", 1.0)), shared_expert_intermediate_size=0, shared_expert_gate=False,
+                          dense_layers=tuple(range(int(hf.get("num_dense_layers", 2)))))
+            elif hf.get("block_auto_adjust_ff_dim", True):   # the checkpoint's feed-forward width: 2/3 of the nominal one, rounded up to a multiple
                 inter = int(2 * inter / 3)
                 if hf.get("block_ffn_dim_multiplier") is not None:
                     mult = int(hf.get("block_multiple_of", 256))

@@ -42,7 +42,7 @@ _RENAMES = ((".conv.conv.weight", ".linear_attn.conv_weight"), (".conv.conv.bias
             (".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
             (".mlp.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"), (".mlp.router.", ".mlp.gate."), (".mlp.gate.e_score_correction_bias", ".mlp.e_score_correction_bias"),
-            (".mlp.shared_experts.", ".mlp.shared_expert."), (".mlp.shared_mlp.", ".mlp.shared_expert."), (".mlp.gate.wg.", ".mlp.gate."))
+            (".mlp.shared_experts.", ".mlp.shared_expert."), (".mlp.shared_mlp.", ".mlp.shared_expert."), (".mlp.gate.wg.", ".mlp.gate."), (".mlp.expert_bias", ".mlp.e_score_correction_bias"))
 # GLM-4 names of the sandwich norms → the names used here (single pass: its post_attention_layernorm is the feed-forward pre-norm)
 _GLM4_NORMS = {"post_attention_layernorm": "pre_feedforward_layernorm", "post_self_attn_layernorm": "post_attention_layernorm",
                "post_mlp_layernorm": "post_feedforward_layernorm"}
@@ -172,6 +172,9 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             name = name.replace(".block_sparse_moe.router.layer.", ".mlp.gate.")
         if ".block_sparse_moe." in name:  # Mixtral naming: block_sparse_moe.{gate, experts.N.w1|w3|w2}
             name = name.replace(".block_sparse_moe.", ".mlp.")
+            for theirs, ours in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):
+                name = name.replace(theirs, ours)
+        if ".mlp.experts." in name and (".w1." in name or ".w2." in name or ".w3." in name):   # w1 / w3 / w2 naming outside Mixtral (LFM2-MoE)
             for theirs, ours in ((".w1.", ".gate_proj."), (".w3.", ".up_proj."), (".w2.", ".down_proj.")):
                 name = name.replace(theirs, ours)
         m = _EXPERT_RE.match(name)

@@ -14,7 +14,7 @@ _REGISTRY = {
     "Qwen3MoeForCausalLM": "moe", "MiniMaxM2ForCausalLM": "moe", "ExaoneMoeForCausalLM": "moe", "FlexOlmoForCausalLM": "moe", "Ministral3ForCausalLM": "dense", "VaultGemmaForCausalLM": "dense", "HunYuanMoEV1ForCausalLM": "moe", "Qwen2MoeForCausalLM": "moe", "MixtralForCausalLM": "moe",
     "Qwen3NextForCausalLM": "hybrid", "Qwen3_5ForCausalLM": "hybrid", "Qwen3_5ForConditionalGeneration": "hybrid",
     "Qwen3_5MoeForCausalLM": "hybrid", "Qwen3_5MoeForConditionalGeneration": "hybrid",
-    "BambaForCausalLM": "hybrid", "Lfm2ForCausalLM": "hybrid", "JambaForCausalLM": "hybrid", "GraniteMoeHybridForCausalLM": "hybrid", "Mamba2ForCausalLM": "hybrid", "MambaForCausalLM": "hybrid", "FalconMambaForCausalLM": "hybrid",
+    "BambaForCausalLM": "hybrid", "Lfm2ForCausalLM": "hybrid", "Lfm2MoeForCausalLM": "hybrid", "JambaForCausalLM": "hybrid", "GraniteMoeHybridForCausalLM": "hybrid", "Mamba2ForCausalLM": "hybrid", "MambaForCausalLM": "hybrid", "FalconMambaForCausalLM": "hybrid",
     "Qwen2VLForConditionalGeneration": "dense", "Qwen2_5_VLForConditionalGeneration": "dense",
     "DeepseekV2ForCausalLM": "mla_moe", "DeepseekV3ForCausalLM": "mla_moe", "DeepseekV32ForCausalLM": "mla_moe",
 }

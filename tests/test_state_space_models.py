@@ -202,3 +202,29 @@ def test_lfm2_short_conv_matches_hugging_face(tmp_path):
     got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
     llm.shutdown()
     assert got == want
+
+
+def test_lfm2_moe_matches_hugging_face(tmp_path):
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import Lfm2MoeConfig, Lfm2MoeForCausalLM
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no LFM2-MoE: {e}")
+    cfg = Lfm2MoeConfig(vocab_size=300, hidden_size=64, intermediate_size=128, moe_intermediate_size=48, num_hidden_layers=4, num_attention_heads=4,
+                        num_key_value_heads=2, layer_types=["conv", "full_attention", "conv", "conv"], num_dense_layers=1, num_experts=4,
+                        num_experts_per_tok=2, routed_scaling_factor=1.5, max_position_embeddings=512, pad_token_id=0)
+    torch.manual_seed(0)
+    hf = Lfm2MoeForCausalLM(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        if "norm" not in n:
+            torch.nn.init.normal_(p, std=0.15)
+    for n, b in hf.named_buffers():
+        if n.endswith("expert_bias"):
+            b.normal_(0.0, 0.1, generator=torch.Generator().manual_seed(4))
+    _save(hf, tmp_path, "Lfm2MoeForCausalLM")
+    prompts = _prompts(300)
+    want = _hf_greedy(hf, prompts, 12)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=48)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    llm.shutdown()
+    assert got == want

@@ -304,7 +304,7 @@ class ModelConfig:
             else:
                 kw.update(shared_expert_intermediate_size=hf.get("shared_expert_intermediate_size", 0),
                           shared_expert_gate=bool(hf.get("shared_expert_intermediate_size", 0)))
-        if "deepseek" in a and hf.get("kv_lora_rank"):
+        if ("deepseek" in a or a.startswith("glm4moelite")) and hf.get("kv_lora_rank"):
             kw.update(use_mla=True, q_lora_rank=hf.get("q_lora_rank") or 0, kv_lora_rank=hf["kv_lora_rank"],
                       qk_nope_head_dim=hf.get("qk_nope_head_dim", 128), qk_rope_head_dim=hf.get("qk_rope_head_dim", 64),
                       v_head_dim=hf.get("v_head_dim", 128), head_dim=hf.get("qk_nope_head_dim", 128) + hf.get("qk_rope_head_dim", 64))
@@ -453,6 +453,14 @@ class ModelConfig:
             kw.update(pre_norm=False, sandwich_norm=True, qk_norm=True)
             if kw.get("sliding_layers"):
                 kw["nope_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i not in kw["sliding_layers"])
+        if a.startswith(("solaropen", "glm4moelite")):
+            # GLM-4.5-style experts (sigmoid router with a selection bias, shared experts, scaled weights); Solar keeps plain attention,
+            # GLM-4-MoE-Lite uses latent attention
+            kinds = hf.get("mlp_layer_types") or []
+            kw.update(shared_expert_intermediate_size=(hf.get("n_shared_experts") or 0) * hf.get("moe_intermediate_size", 1408), shared_expert_gate=False,
+                      scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1), norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
+                      routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=0,
+                      dense_layers=tuple(i for i, t in enumerate(kinds) if t != "sparse") if kinds else tuple(range(int(hf.get("first_k_dense_replace", 0)))))
         if a.startswith("exaonemoe"):
             # pre-norm blocks with per-head q/k norm; global layers of the hybrid form apply no rotary embedding; DeepSeek-V3-style router
             kinds = hf.get("mlp_layer_types") or []

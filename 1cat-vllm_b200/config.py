@@ -643,11 +643,11 @@ class SpeculativeConfig:
     rejection sampler uses the conditional form ``rate[i] / rate[i-1]``.
     """
 
-    method: Optional[str] = None  # None | "mtp" | "ngram" | "suffix" | "eagle" | "eagle3" | "medusa"
+    method: Optional[str] = None  # None | "mtp" | "ngram" | "suffix" | "eagle" | "eagle3" | "medusa" | "draft_model"
     draft_vocab_size: Optional[int] = None  # eagle3: size of the head's reduced vocabulary (read from its config.json when present)
     eagle_aux_hidden_state_layers: Optional[list] = None  # eagle3: target layers whose input stream feeds the head (default 2, L/2, L-3)
     num_speculative_tokens: int = 0
-    model: Optional[str] = None  # eagle / medusa: directory of the draft heads' checkpoint (random weights when absent)
+    model: Optional[str] = None  # eagle / medusa: directory of the draft heads' checkpoint (random weights when absent); draft_model: the draft's checkpoint
     medusa_num_layers: int = 1  # residual blocks per Medusa head
     synthetic_acceptance_rates: Optional[list[float]] = None
     synthetic_acceptance_rate: Optional[float] = None  # conditional per-position Bernoulli rate

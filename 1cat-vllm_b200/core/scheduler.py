@@ -116,9 +116,9 @@ class Scheduler:
         spec = vllm_config.speculative_config
         mc = vllm_config.model_config
         self.num_spec_tokens = spec.num_speculative_tokens if spec.enabled else 0
-        self.num_lookahead_tokens = self.num_spec_tokens if spec.method in ("mtp", "eagle", "eagle3") else 0
+        self.num_lookahead_tokens = self.num_spec_tokens if spec.method in ("mtp", "eagle", "eagle3", "draft_model") else 0
         self.kv_cache_manager = KVCacheManager(num_gpu_blocks, cc.block_size, self.max_model_len, cc.enable_prefix_caching,
-                                               num_state_slots, use_eagle=spec.method in ("mtp", "eagle", "eagle3"),
+                                               num_state_slots, use_eagle=spec.method in ("mtp", "eagle", "eagle3", "draft_model"),
                                                dcp_world_size=vllm_config.parallel_config.decode_context_parallel_size,
                                                log_stats=log_stats,
                                                sliding_window=(mc.sliding_window if mc.sliding_window and len(mc.sliding_layers) == mc.num_hidden_layers

@@ -147,6 +147,54 @@ class MTPProposer:
         return out
 
 
+class DraftModelProposer:
+    """A separate, smaller language model of the same vocabulary drafts the tokens. It keeps its own paged K/V under the target's block
+    ids: one pass over the step's input tokens brings its cache level with the target's, then k single-token passes start from the token
+    the target just sampled (reference: v1/spec_decode/draft_model.py; spec_decode/llm_base_proposer.py:167)."""
+
+    def __init__(self, runner):
+        self.k = runner.num_spec
+
+    @torch.inference_mode()
+    def propose(self, runner, so, req_ids, rows, sampled, hidden, md, drafts_of):
+        draft, dev, bs = runner.draft, runner.device, runner.block_size
+        R, T = md.num_reqs, md.num_tokens
+        qsl = md.query_start_loc.tolist() if md.query_lens_cpu is None else np.concatenate([[0], np.cumsum(md.query_lens_cpu)]).tolist()
+        draft.model(runner._view("ids", T), md, runner.draft_caches)     # fills the draft's K/V at this step's positions
+        active = [r for r in range(R) if sampled[r]]
+        out: list = [[] for _ in range(R)]
+        if not active:
+            return out
+        # position of the token the target just sampled: the step's first position + inputs that were kept
+        pos0 = np.array([runner.requests[req_ids[r]].num_computed_tokens + (qsl[r + 1] - qsl[r]) - (len(drafts_of[r]) + 1) + len(sampled[r])
+                         for r in active], dtype=np.int32)
+        A = len(active)
+        bt = torch.zeros(A, runner.max_blocks_per_req, dtype=torch.int32, device=dev)
+        for i, r in enumerate(active):
+            b_ids = runner.requests[req_ids[r]].block_ids
+            bt[i, : len(b_ids)] = torch.tensor(b_ids, dtype=torch.int32)
+        tok = torch.tensor([sampled[r][-1] for r in active], dtype=torch.int32, device=dev)
+        drafts = []
+        for step in range(self.k):
+            pos = pos0 + step
+            ok = pos < runner.max_model_len - 1
+            slots = np.full(A, -1, dtype=np.int32)
+            for i, r in enumerate(active):
+                b_ids = runner.requests[req_ids[r]].block_ids
+                if ok[i] and pos[i] // bs < len(b_ids):
+                    slots[i] = b_ids[pos[i] // bs] * bs + pos[i] % bs
+            md1 = AttentionMetadata(A, A, torch.arange(A + 1, dtype=torch.int32, device=dev), torch.tensor(pos + 1, dtype=torch.int32, device=dev), bt,
+                                    torch.tensor(slots, dtype=torch.int32, device=dev), torch.tensor(pos, dtype=torch.int32, device=dev), 1,
+                                    int(pos.max()) + 1, query_lens_cpu=[1] * A, seq_lens_cpu=(pos + 1).tolist())
+            h = draft.model(tok, md1, runner.draft_caches)
+            tok = draft.compute_logits(h).argmax(-1).to(torch.int32)
+            drafts.append(tok)
+        d = torch.stack(drafts, dim=1).tolist()
+        for i, r in enumerate(active):
+            out[r] = d[i]
+        return out
+
+
 class MedusaHeads(torch.nn.Module):
     """Medusa: head ``i`` maps the target's last hidden state to the token ``i + 2`` positions ahead through residual SiLU blocks
     and its own vocabulary projection; no attention and no KV cache (reference: models/medusa.py ``ResidualBlock`` / ``Medusa``;
@@ -231,6 +279,8 @@ def make_proposer(runner):
         return NgramProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
     if sc.method in ("mtp", "eagle", "eagle3"):
         return MTPProposer(runner)
+    if sc.method == "draft_model":
+        return DraftModelProposer(runner)
     if sc.method == "suffix":
         return SuffixProposer(sc.num_speculative_tokens, sc.prompt_lookup_min, sc.prompt_lookup_max)
     if sc.method == "medusa":

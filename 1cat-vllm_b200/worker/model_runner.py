@@ -85,6 +85,8 @@ class ModelRunner:
         self.requests: dict[str, CachedRequestState] = {}
         self.model = None
         self.mtp = None
+        self.draft = None          # speculative method draft_model: a second CausalLM and its K/V pages
+        self.draft_caches = None
         self.kv_caches: list = []
         self._pending_saves: list = []
         self.lora_manager = None
@@ -132,6 +134,19 @@ class ModelRunner:
                 load_eagle_weights(self.mtp, self.spec.model)
             process_weights_after_loading(self.mtp)
             self.mtp.eval()
+        if self.spec.method == "draft_model":
+            import dataclasses
+            from onecat_vllm.config import ModelConfig
+            from onecat_vllm.loader.weights import load_model
+            if not (self.spec.model and os.path.isdir(self.spec.model)):
+                raise ValueError("speculative method draft_model needs speculative_config.model = the draft model's checkpoint directory")
+            dcfg = ModelConfig.from_pretrained(self.spec.model, dtype=self.mc.dtype, seed=self.mc.seed)
+            dcfg.max_model_len = self.mc.max_model_len
+            if dcfg.vocab_size != self.mc.vocab_size:
+                raise ValueError(f"the draft model's vocabulary ({dcfg.vocab_size}) differs from the target's ({self.mc.vocab_size})")
+            if dcfg.is_hybrid or dcfg.use_mla:
+                raise ValueError("the draft model must be a plain attention decoder (its K/V pages live under the target's block ids)")
+            self.draft = load_model(dcfg, self.device)
         if self.spec.method == "eagle3":
             from onecat_vllm.loader.weights import dummy_init, load_eagle3_weights, process_weights_after_loading
             from onecat_vllm.models.decoder import Eagle3Head
@@ -181,6 +196,8 @@ class ModelRunner:
                 specs[f"layers.{i}"] = KVCacheSpec("mla", self.block_size, 1, mc.kv_lora_rank + mc.qk_rope_head_dim, esz)
             else:
                 specs[f"layers.{i}"] = KVCacheSpec("full", self.block_size, layer.self_attn.Hkv, mc.head_dim, asz)
+        for i, layer in (self.draft.model.local_layers() if self.draft is not None else ()):
+            specs[f"draft.{i}"] = KVCacheSpec("full", self.block_size, layer.self_attn.Hkv, self.draft.cfg.head_dim, asz)
         if self.mtp is not None:
             a = self.mtp.layer.self_attn
             if self.mc.use_mla:
@@ -233,6 +250,8 @@ class ModelRunner:
                 self.kv_caches.append(alloc(spec))
         if self.mtp is not None:
             self.mtp_cache = alloc(kvc.layer_specs["mtp.0"])
+        if self.draft is not None:
+            self.draft_caches = [alloc(kvc.layer_specs[f"draft.{i}"]) for i, _ in self.draft.model.local_layers()]
         # host mirror for the CPU tier of the prefix cache: same page layout, pinned when copies come from a GPU
         self.cpu_kv = []
         if kvc.num_cpu_blocks > 0:

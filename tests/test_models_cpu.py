@@ -376,6 +376,38 @@ def test_eagle3_head_is_lossless_loads_its_checkpoint_and_matches_plain_torch(tm
     llm.shutdown()
 
 
+def test_draft_model_proposer_is_lossless_and_a_twin_draft_is_always_accepted(tmp_path):
+    """A separate draft model under the target's block ids. With the target's own weights as the draft every proposed token is
+    accepted (which pins the position and slot bookkeeping of the drafting passes); with another model the output is still the
+    target's greedy decode."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    big = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256)
+    small = dict(big, hidden_size=32, intermediate_size=64, num_hidden_layers=1, num_attention_heads=2, num_key_value_heads=1)
+    for name, cfg, seed in (("big", big, 0), ("small", small, 7)):
+        m = build_model(ModelConfig.from_hf_dict(cfg, dtype=torch.float32), "cpu")
+        dummy_init(m, seed, std=0.1)
+        save_pretrained(m, cfg, str(tmp_path / name))
+    p = _prompts(500)
+    sp = SamplingParams(temperature=0, max_tokens=20, ignore_eos=True)
+
+    def run(**kw):
+        llm = LLM(model=str(tmp_path / "big"), max_model_len=256, dtype="float32", device="cpu", max_num_batched_tokens=64, disable_log_stats=False, **kw)
+        out = [o.outputs[0].token_ids for o in llm.generate(p, sp)]
+        mt = llm.llm_engine.get_metrics()
+        acc = (mt.get("vllm:spec_decode_num_accepted_tokens_total"), mt.get("vllm:spec_decode_num_draft_tokens_total"))
+        llm.shutdown()
+        return out, acc
+    want, _ = run()
+    twin, acc = run(speculative_config=dict(method="draft_model", num_speculative_tokens=3, model=str(tmp_path / "big")))
+    assert twin == want
+    assert acc[1] and acc[0] == acc[1], acc     # every draft of the twin was accepted
+    other, _ = run(speculative_config=dict(method="draft_model", num_speculative_tokens=3, model=str(tmp_path / "small")))
+    assert other == want
+
+
 def test_medusa_heads_are_lossless_and_load(tmp_path):
     from safetensors.torch import save_file
     from onecat_vllm.spec_decode.proposers import MedusaHeads

@@ -14,7 +14,7 @@ def build(force: bool = False) -> str:
     srcs = [os.path.join(HERE, f) for f in sorted(os.listdir(HERE)) if f.endswith(".cpp")]
     if not force and os.path.exists(OUT) and all(os.path.getmtime(s) < os.path.getmtime(OUT) for s in srcs):
         return OUT
-    cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
+    cmd = ["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-fvisibility=hidden", f"-I{pybind11.get_include()}",
            f"-I{sysconfig.get_paths()['include']}"] + srcs + ["-o", OUT, "-lrt", "-lpthread"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

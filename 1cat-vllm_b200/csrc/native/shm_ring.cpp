@@ -170,9 +170,11 @@ bool spin_wait_changed(py::buffer b, size_t offset, uint64_t old, double timeout
 }  // namespace
 
 void register_drafting(py::module_& m);  // ngram.cpp
+void register_cpu_attention(py::module_& m);  // cpu_attention.cpp
 
 PYBIND11_MODULE(_native, m) {
   register_drafting(m);
+  register_cpu_attention(m);
   py::class_<ShmRing>(m, "ShmRing")
       .def(py::init<const std::string&, int, int, int, bool>(), py::arg("name"), py::arg("n_readers"), py::arg("max_chunks"), py::arg("chunk_bytes"),
            py::arg("create"))

@@ -33,6 +33,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_RPC_RING_CHUNK_BYTES": _i("ONECAT_RPC_RING_CHUNK_BYTES", 1 << 22),
     "ONECAT_RPC_RING_CHUNKS": _i("ONECAT_RPC_RING_CHUNKS", 8),
     # kernels
+    "ONECAT_CPU_ATTENTION": _s("ONECAT_CPU_ATTENTION", "torch"),  # paged attention of the CPU backend: "torch" (the oracle) | "native" (C++ threads)
     "ONECAT_GEMM_BACKEND": _s("ONECAT_GEMM_BACKEND", "tcgen05"),  # "tcgen05" | "library" (debug only)
     "ONECAT_ATTN_PREFILL": _s("ONECAT_ATTN_PREFILL", "tcgen05"),  # head size 128 prefill attention: "tcgen05" | "mma"
     "ONECAT_TP_COMM": _s("ONECAT_TP_COMM", "fused"),  # "fused" (peer-memory kernels) | "nccl" (baseline)

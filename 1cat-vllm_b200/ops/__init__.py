@@ -51,8 +51,33 @@ def paged_attention(q, kv_cache, md, scale, out=None, window=0, softcap=0.0, sin
     of the scaled scores (0 = off); ``sinks``: fp32 ``[Hq]`` sink logits that join the softmax denominator."""
     if q.is_cuda:
         return ext().paged_attention(q, kv_cache, md, scale, out, window=window, softcap=softcap, sinks=sinks)
+    from onecat_vllm import envs
+    if envs.ONECAT_CPU_ATTENTION == "native" and kv_cache.dtype in (torch.float32, torch.bfloat16) and q.dtype in (torch.float32, torch.bfloat16):
+        return cpu_paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out, window=window, softcap=softcap, sinks=sinks)
     return ref.paged_attention(q, kv_cache, md.block_table, md.query_start_loc, md.seq_lens, scale, out, window=window, softcap=softcap,
                                sinks=sinks)
+
+
+def cpu_paged_attention(q, kv_cache, block_table, query_start_loc, seq_lens, scale, out=None, return_lse=False, window=0, softcap=0.0, sinks=None,
+                        threads: int = 0):
+    """The C++ paged attention of the CPU backend (``csrc/native/cpu_attention.cpp``): same contract as ``ref.paged_attention`` for fp32 /
+    bf16 queries and caches."""
+    from onecat_vllm.utils import _native
+    T, Hq, D = q.shape
+    if q.stride(2) != 1:
+        q = q.contiguous()
+    o = torch.empty(T, Hq, D, dtype=q.dtype) if out is None else out
+    assert o.stride(2) == 1 and kv_cache.is_contiguous() and o.dtype == q.dtype
+    lse = torch.full((T, Hq), -float("inf"), dtype=torch.float32) if return_lse else None
+    bt = block_table if block_table.dtype == torch.int32 else block_table.to(torch.int32)
+    qsl = query_start_loc.to(torch.int32).contiguous()
+    sl = seq_lens.to(torch.int32).contiguous()
+    sk = sinks.float().contiguous() if sinks is not None else None
+    _native.cpu_paged_attention(q.data_ptr(), kv_cache.data_ptr(), o.data_ptr(), lse.data_ptr() if lse is not None else 0, bt.data_ptr(), qsl.data_ptr(),
+                                sl.data_ptr(), sk.data_ptr() if sk is not None else 0, q.stride(0), q.stride(1), o.stride(0), o.stride(1), bt.stride(0),
+                                sl.shape[0], Hq, kv_cache.shape[2], D, kv_cache.shape[3], float(scale), int(window), float(softcap),
+                                int(q.dtype == torch.bfloat16), int(kv_cache.dtype == torch.bfloat16), int(threads))
+    return (o, lse) if return_lse else o
 
 
 def rms_norm_gated(x, z, w, eps, heads):

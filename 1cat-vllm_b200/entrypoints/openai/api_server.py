@@ -584,6 +584,46 @@ def build_app(state: ServingState) -> FastAPI:
             return JSONResponse(error_body(str(e)), status_code=400)
         return {"id": rid, "object": "text_completion", "created": now(), "model": model, "choices": choices, "usage": _usage(n_prompt, n_out)}
 
+    # ---- rendering only: what the engine would be asked to generate from, without generating
+    # (reference: entrypoints/serve/render/api_router.py ``/v1/chat/completions/render``, ``/v1/completions/render``)
+    def _rendered(prompt, sp) -> dict:
+        tok = state.engine.tokenizer
+        ids = list(prompt) if isinstance(prompt, (list, tuple)) else (tok.encode(prompt) if tok is not None else None)
+        if ids is None:
+            raise ValueError("text prompts need a tokenizer")
+        return {"token_ids": ids, "prompt": prompt if isinstance(prompt, str) else None,
+                "sampling_params": {"max_tokens": sp.max_tokens, "temperature": sp.temperature, "top_p": sp.top_p, "top_k": sp.top_k,
+                                    "stop": sp.stop, "seed": sp.seed, "n": sp.n}}
+
+    @app.post("/v1/chat/completions/render")
+    async def render_chat_completion(req: ChatCompletionRequest):
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("chat completions need a tokenizer with a chat template"), status_code=400)
+        kw = dict(req.chat_template_kwargs or {})
+        if req.tools and req.tool_choice != "none":
+            kw["tools"] = req.tools
+        try:
+            from onecat_vllm.engine.renderers import render_chat
+            tools = kw.pop("tools", None)
+            prompt = render_chat(tok, [m.model_dump(exclude_none=True) for m in req.messages], architecture=state.engine.cfg.model_config.architecture,
+                                 tools=tools, add_generation_prompt=req.add_generation_prompt, **kw)
+            if req.max_completion_tokens is not None and req.max_tokens is None:
+                req.max_tokens = req.max_completion_tokens
+            return _rendered(prompt, req.to_sampling_params(state.max_model_len))
+        except Exception as e:
+            return JSONResponse(error_body(f"rendering failed: {e}"), status_code=400)
+
+    @app.post("/v1/completions/render")
+    async def render_completion(req: CompletionRequest):
+        try:
+            sp = req.to_sampling_params(state.max_model_len)
+            p = req.prompt
+            many = isinstance(p, list) and p and isinstance(p[0], (str, list))
+            return [_rendered(x, sp) for x in (p if many else [p])]
+        except Exception as e:
+            return JSONResponse(error_body(f"rendering failed: {e}"), status_code=400)
+
     # ---- chat completions
     @app.post("/v1/chat/completions")
     async def chat(req: ChatCompletionRequest, raw: Request):

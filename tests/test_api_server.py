@@ -378,3 +378,22 @@ def test_remaining_tool_call_formats():
         assert c == content, (name, c)
         assert get_tool_parser(name).extract("plain answer") == ("plain answer", [])
     assert len(TOOL_PARSERS) >= 46
+
+
+@pytest.mark.timeout(300)
+def test_render_routes_return_the_prompt_the_engine_would_see(client):
+    r = client.post("/v1/chat/completions/render", json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 5, "temperature": 0.3})
+    assert r.status_code == 200, r.text
+    body = r.json()
+    assert body["prompt"].endswith("<|assistant|>") and "hi" in body["prompt"]
+    assert body["token_ids"][0] == 256 and bytes(t for t in body["token_ids"] if t < 256).decode() == body["prompt"]
+    assert body["sampling_params"]["max_tokens"] == 5 and abs(body["sampling_params"]["temperature"] - 0.3) < 1e-6
+    r = client.post("/v1/completions/render", json={"model": "tiny", "prompt": ["ab", "c"], "max_tokens": 4})
+    assert r.status_code == 200, r.text
+    a, b = r.json()
+    assert a["prompt"] == "ab" and a["token_ids"][-2:] == [97, 98] and b["token_ids"][-1] == 99
+    r = client.post("/v1/completions/render", json={"model": "tiny", "prompt": [1, 2, 3], "max_tokens": 4})
+    assert r.status_code == 200 and r.json()[0]["token_ids"] == [1, 2, 3] and r.json()[0]["prompt"] is None
+    # the same messages through the generating route consume exactly the rendered prompt
+    g = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0})
+    assert g.status_code == 200 and g.json()["usage"]["prompt_tokens"] == len(body["token_ids"])

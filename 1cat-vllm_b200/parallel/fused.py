@@ -61,8 +61,10 @@ class FusedTP:
         self.nvls_min_t = int(envs.ONECAT_TP_NVLS_MIN_T)
         self.full_residual = False
         self.parity = 0
-        self.nv = self._nvls_setup(tp, rank, device, buf, group) if envs.ONECAT_TP_NVLS != "0" else None
         self.nvls_mode = {"1": "always", "0": "never"}.get(envs.ONECAT_TP_NVLS, "auto")
+        # the switch only pays from four ranks up (see mode_for): below that the automatic policy never takes it, so nothing is set up
+        want_nv = self.nvls_mode == "always" or (self.nvls_mode == "auto" and tp >= 4)
+        self.nv = self._nvls_setup(tp, rank, device, buf, group) if want_nv else None
         self.wait_ns = int(envs.ONECAT_DEVICE_WAIT_LIMIT_MS) * 1_000_000
         self.num_sms = torch.cuda.get_device_properties(device).multi_processor_count
         self.launches = 0

@@ -36,6 +36,10 @@ class Worker:
         pc = self.cfg.parallel_config
         if self.cfg.device == "cuda":
             torch.cuda.set_device(self.local_rank)
+            from onecat_vllm import envs as _envs
+            if _envs.ONECAT_NUMA_BIND:
+                from onecat_vllm.utils.numa import bind_to_gpu
+                bind_to_gpu(self.local_rank)
             self.device = torch.device("cuda", self.local_rank)
             gc.collect()
             torch.cuda.empty_cache()

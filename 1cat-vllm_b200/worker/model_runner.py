@@ -978,23 +978,33 @@ class ModelRunner:
         B = sum(1 for r in rows if r > 0)
         V = logits.shape[-1]
         dev = logits.device
-        tl = torch.zeros(B, k + 1, V, dtype=logits.dtype, device=dev)
-        draft = torch.zeros(B, k, dtype=torch.long, device=dev)
-        nd = torch.zeros(B, dtype=torch.long, device=dev)
-        last_rows, j, b = [], 0, 0
-        nd_host = []
-        for i, r in enumerate(rows):
-            if r == 0:
-                continue
-            d = drafts_of[i]
-            tl[b, :r] = logits[j:j + r]
-            if d:
-                draft[b, : len(d)] = torch.tensor(d, device=dev)
-            nd_host.append(len(d))
-            last_rows.append(j + r - 1)
-            j += r
-            b += 1
-        nd.copy_(torch.tensor(nd_host))
+        live = [(r, drafts_of[i]) for i, r in enumerate(rows) if r > 0]
+        if live and all(r == k + 1 and len(d) == k for r, d in live) and logits.is_contiguous() and logits.shape[0] == B * (k + 1):
+            # every request verified a full set of drafts (the steady state of decoding): the logits already are [B, k + 1, V]
+            tl = logits.view(B, k + 1, V)
+            if not self._verify_is_unconstrained(smd):
+                tl = tl.clone()      # constrained rows are rewritten below; the caller's logits stay as they are
+            draft = torch.tensor([d for _, d in live], dtype=torch.long).to(dev)
+            nd = torch.full((B,), k, dtype=torch.long, device=dev)
+            last_rows = [b * (k + 1) + k for b in range(B)]
+        else:
+            tl = torch.zeros(B, k + 1, V, dtype=logits.dtype, device=dev)
+            draft = torch.zeros(B, k, dtype=torch.long, device=dev)
+            nd = torch.zeros(B, dtype=torch.long, device=dev)
+            last_rows, j, b = [], 0, 0
+            nd_host = []
+            for i, r in enumerate(rows):
+                if r == 0:
+                    continue
+                d = drafts_of[i]
+                tl[b, :r] = logits[j:j + r]
+                if d:
+                    draft[b, : len(d)] = torch.tensor(d, device=dev)
+                nd_host.append(len(d))
+                last_rows.append(j + r - 1)
+                j += r
+                b += 1
+            nd.copy_(torch.tensor(nd_host))
         bonus_md = smd
         if not self._verify_is_unconstrained(smd):
             # The drafts are judged against the distribution the sampler would have drawn from: every verified row goes through the

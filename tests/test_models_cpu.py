@@ -89,6 +89,12 @@ def test_verifier_applies_filters_and_processors_to_draft_rows():
         out = runner._verify(logits.clone(), md(top_k=torch.tensor([1, 1])), rows, drafts)
         assert out == [[A], [A]]                   # first draft rejected, the recovered token is the only one left in the filter
     assert accepted_raw > 0                        # the crafted draft is plausible without the filter
+    # a batch in which every request verified a full set of drafts takes the copy-free path: same rules, caller's logits untouched
+    full = row.repeat(8, 1)
+    keep = full.clone()
+    assert runner._verify(full, md(top_k=torch.tensor([1, 1])), [4, 4], [[D, D, D], [D, D, D]]) == [[A], [A]]
+    assert torch.equal(full, keep)
+    assert runner._verify(full, md(temperature=None, all_greedy=True, all_random=False), [4, 4], [[A, A, A], [A, D, A]]) == [[A, A, A, A], [A, A]]
     greedy = dict(temperature=None, all_greedy=True, all_random=False)
     assert runner._verify(logits.clone(), md(**greedy), rows, [[A, A, A], [A]]) == [[A, A, A, A], [A, A]]
     out = runner._verify(logits.clone(), md(bad_words_token_ids={0: [[A]]}, **greedy), rows, [[A, A, A], [A]])

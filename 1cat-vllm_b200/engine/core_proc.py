@@ -40,7 +40,8 @@ def _ipc_path(tag: str) -> str:
 
 
 # ----------------------------------------------------------------------------- engine side
-def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_index: int, log_stats: bool, death_conn) -> None:
+def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_index: int, log_stats: bool, death_conn,
+                    coord_addrs: Optional[dict] = None) -> None:
     decorate_logs(f"EngineCore_{engine_index}")
     signal.signal(signal.SIGINT, signal.SIG_IGN)
     if death_conn is not None:
@@ -73,7 +74,11 @@ def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_i
         core = EngineCore(cfg, log_stats=log_stats)
         inp.send_multipart(serial.encode({"status": "READY", "num_gpu_blocks": cfg.cache_config.num_gpu_blocks,
                                           "max_model_len": cfg.model_config.max_model_len, "dtype": str(cfg.model_config.dtype)}))
-        _busy_loop(core, inp, out, engine_index)
+        reporter = None
+        if coord_addrs is not None:
+            from onecat_vllm.engine.coordinator import EngineReporter
+            reporter = EngineReporter(engine_index, coord_addrs)
+        _busy_loop(core, inp, out, engine_index, reporter)
     except Exception:
         log.error("engine core failed:\n" + traceback.format_exc())
         try:
@@ -88,9 +93,16 @@ def run_engine_core(cfg: VllmConfig, input_addr: str, output_addr: str, engine_i
         ctx.term()
 
 
-def _busy_loop(core, inp, out, engine_index: int) -> None:
-    """Drain inputs, step while there is work, block on the socket when idle (reference: core.py:1376-1440)."""
+def _busy_loop(core, inp, out, engine_index: int, reporter=None) -> None:
+    """Drain inputs, step while there is work, block on the socket when idle (reference: core.py:1376-1440). With a data-parallel
+    coordinator the engine reports its queue lengths after every step and the edges between having work and having none."""
     while True:
+        if reporter is not None:
+            reporter.poll_start_wave()
+            if core.scheduler.has_requests():
+                reporter.became_busy()
+            else:
+                reporter.became_idle()
         timeout = 0 if core.scheduler.has_requests() else 200
         while inp.poll(timeout):
             frames = inp.recv_multipart()
@@ -120,9 +132,13 @@ def _busy_loop(core, inp, out, engine_index: int) -> None:
                 out.send_multipart(serial.encode({"utility_output": reply, "engine_index": engine_index}))
             timeout = 0
         if core.scheduler.has_requests():
+            if reporter is not None:
+                reporter.became_busy()
             outs, _ = core.step()
             for client, o in outs.items():
                 out.send_multipart(serial.encode(_outs_wire(o, engine_index)))
+            if reporter is not None:
+                reporter.report(len(core.scheduler.waiting), len(core.scheduler.running))
 
 
 def _outs_wire(o: EngineCoreOutputs, engine_index: int) -> dict:
@@ -146,9 +162,17 @@ class _MPClientBase:
         # the ROUTER addresses a replica by its identity (reference: v1/engine/core_client.py:1169 DPAsyncMPClient, :1349 DPLBAsyncMPClient)
         self.num_engines = max(1, cfg.parallel_config.data_parallel_size)
         self.procs, self._death_ws = [], []
+        # opt-in coordinator process: the replicas' queue lengths reach every front end that subscribes, and idle / running waves
+        # are kept for the group (reference: v1/engine/coordinator.py)
+        self.coordinator = self._coord_sub = None
+        coord_addrs = None
+        if self.num_engines > 1 and envs.ONECAT_DP_COORDINATOR:
+            from onecat_vllm.engine.coordinator import DPCoordinator
+            self.coordinator = DPCoordinator(self.num_engines)
+            coord_addrs = self.coordinator.addresses
         for i in range(self.num_engines):
             d_r, d_w = mctx.Pipe(duplex=False)
-            pr = mctx.Process(target=run_engine_core, args=(cfg, self.input_addr, self.output_addr, i, log_stats, d_r), daemon=True,
+            pr = mctx.Process(target=run_engine_core, args=(cfg, self.input_addr, self.output_addr, i, log_stats, d_r, coord_addrs), daemon=True,
                               name=f"onecat-engine-core-{i}")
             pr.start()
             d_r.close()
@@ -160,6 +184,13 @@ class _MPClientBase:
         self._owner: dict = {}                      # request id -> replica
         self._inflight = [0] * self.num_engines     # requests sent and not yet finished
         self._lb = [(0, 0)] * self.num_engines      # last reported (waiting, running) per replica
+        if coord_addrs is not None:
+            from onecat_vllm.engine.coordinator import FrontendSubscriber
+
+            def _table(m: dict) -> None:
+                for i, c in enumerate(m.get("counts", [])[: self.num_engines]):
+                    self._lb[i] = (int(c[0]), int(c[1]))
+            self._coord_sub = FrontendSubscriber(coord_addrs, on_update=_table)
         self.dead = False
         try:
             self._handshake(hs)
@@ -215,6 +246,8 @@ class _MPClientBase:
             e = min(range(n), key=lambda i: (4 * self._lb[i][0] + self._lb[i][1] + self._inflight[i], i))
         self._owner[req.request_id] = e
         self._inflight[e] += 1
+        if self._coord_sub is not None:
+            self._coord_sub.request_routed(e)
         return self.engine_ids[e]
 
     def _abort_targets(self, ids: list) -> dict:
@@ -240,8 +273,17 @@ class _MPClientBase:
         if self.dead:
             raise EngineDeadError("the engine core process died")
 
+    def _close_coordinator(self) -> None:
+        if getattr(self, "_coord_sub", None) is not None:
+            self._coord_sub.close()
+            self._coord_sub = None
+        if getattr(self, "coordinator", None) is not None:
+            self.coordinator.close()
+            self.coordinator = None
+
     def _kill(self) -> None:
         self._closing = True
+        self._close_coordinator()
         for pr in self.procs:
             if pr.is_alive():
                 pr.terminate()  # exact children we started

@@ -32,6 +32,7 @@ environment_variables: dict[str, Callable[[], Any]] = {
     "ONECAT_HANDSHAKE_TIMEOUT_SECONDS": _i("ONECAT_HANDSHAKE_TIMEOUT_SECONDS", 120),
     "ONECAT_RPC_RING_CHUNK_BYTES": _i("ONECAT_RPC_RING_CHUNK_BYTES", 1 << 22),
     "ONECAT_RPC_RING_CHUNKS": _i("ONECAT_RPC_RING_CHUNKS", 8),
+    "ONECAT_DP_COORDINATOR": _i("ONECAT_DP_COORDINATOR", 0),  # 1: data-parallel replicas report to a coordinator process (shared load table, waves)
     "ONECAT_NUMA_BIND": _i("ONECAT_NUMA_BIND", 0),  # 1: each GPU worker pins itself to the cores of its GPU's NUMA node
     # kernels
     "ONECAT_CPU_ATTENTION": _s("ONECAT_CPU_ATTENTION", "torch"),  # paged attention of the CPU backend: "torch" (the oracle) | "native" (C++ threads)

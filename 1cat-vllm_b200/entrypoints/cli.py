@@ -95,6 +95,8 @@ def _cmd_collect_env(argv):
             "cuda_available": torch.cuda.is_available()}
     if torch.cuda.is_available():
         info["gpus"] = [torch.cuda.get_device_name(i) for i in range(torch.cuda.device_count())]
+    from onecat_vllm.platforms import current_platform
+    info["platform_summary"] = current_platform().describe()
     try:
         from onecat_vllm.ops import _C  # noqa: F401
         info["extension"] = "built"

@@ -3,6 +3,7 @@ sleep / wake_up / collective_rpc / get_metrics; run loop entrypoints/offline_uti
 from __future__ import annotations
 
 import itertools
+import os
 from typing import Optional, Sequence, Union
 
 from onecat_vllm.config import EngineArgs
@@ -21,6 +22,11 @@ class LLM:
         self.engine_args = EngineArgs(model=model, **kwargs)
         self.llm_engine = LLMEngine.from_engine_args(self.engine_args)
         self._counter = itertools.count()
+        if os.environ.get("ONECAT_USAGE_STATS_FILE"):
+            from onecat_vllm.platforms import usage_record
+            cfg = self.llm_engine.cfg
+            usage_record("LLM_CLASS", cfg.model_config.architecture, {"tensor_parallel_size": cfg.parallel_config.tensor_parallel_size,
+                                                                      "quantization": cfg.model_config.quant.method})
 
     def get_tokenizer(self):
         return self.llm_engine.tokenizer

@@ -58,6 +58,33 @@ class TaggedReasoningParser(ReasoningParser):
         self.start, self.end = start, end
 
 
+class Gemma4ReasoningParser(TaggedReasoningParser):
+    """Gemma-4: reasoning sits in a channel, ``<|channel>thought\n ... <channel|>``; the ``thought`` role label at the start of the
+    channel is structure, not reasoning text (reference: reasoning/gemma4_reasoning_parser.py:17-40)."""
+
+    def __init__(self):
+        super().__init__("<|channel>", "<channel|>", False)
+
+    @staticmethod
+    def _strip_label(r):
+        if r is None:
+            return None
+        for label in ("thought\n", "thought"):
+            if r.startswith(label):
+                return r[len(label):] or None
+        return r
+
+    def extract(self, text):
+        r, c = super().extract(text)
+        return self._strip_label(r), c
+
+    def _split_partial(self, text):
+        r, c = super()._split_partial(text)
+        if r and "thought\n".startswith(r):   # the label itself is still arriving
+            return "", c
+        return self._strip_label(r) or "", c
+
+
 class PhraseReasoningParser(ReasoningParser):
     """Granite-style: reasoning and answer are introduced by fixed phrases instead of tags."""
 
@@ -129,6 +156,7 @@ REASONING_PARSERS = {"identity": IdentityReasoningParser, "gptoss": ChannelReaso
                      "minimax_m2": lambda: ReasoningParser(True), "olmo3": lambda: ReasoningParser(False), "kimi_k2": lambda: ReasoningParser(False),
                      "mistral": lambda: TaggedReasoningParser("[THINK]", "[/THINK]"),
                      "seed_oss": lambda: TaggedReasoningParser("<seed:think>", "</seed:think>"),
+                     "seedoss": lambda: TaggedReasoningParser("<seed:think>", "</seed:think>"), "gemma4": Gemma4ReasoningParser,
                      "hunyuan_a13b": lambda: TaggedReasoningParser("<think>", "</think>"),
                      "granite": lambda: PhraseReasoningParser()}
 

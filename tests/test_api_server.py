@@ -58,6 +58,14 @@ def test_parser_manager_and_channel_reasoning():
     assert g.extract("<|channel|>analysis<|message|>thinking<|end|><|start|>assistant<|channel|>final<|message|>Answer.") == ("thinking", "Answer.")
     assert g.stream("<|channel|>analysis<|message|>thin", "<|channel|>analysis<|message|>thinking<|en") == ("king", "")
     assert get_reasoning_parser("identity").extract("abc") == (None, "abc")
+    g4 = get_reasoning_parser("gemma4")
+    assert g4.extract("<|channel>thought\nlet me see<channel|>4.") == ("let me see", "4.") and g4.extract("plain") == (None, "plain")
+    prev, deltas = "", []
+    for cur in ("<|chan", "<|channel>tho", "<|channel>thought\nlet", "<|channel>thought\nlet me<channel|>An", "<|channel>thought\nlet me<channel|>Answer"):
+        deltas.append(g4.stream(prev, cur))
+        prev = cur
+    assert "".join(d[0] for d in deltas) == "let me" and "".join(d[1] for d in deltas) == "Answer"
+    assert get_reasoning_parser("seedoss").extract("<seed:think>a</seed:think>b") == ("a", "b")
     assert get_reasoning_parser("cohere_command").extract("<|START_THINKING|>a<|END_THINKING|>b") == ("a", "b")
 
 

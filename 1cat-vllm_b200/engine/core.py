@@ -46,6 +46,7 @@ class EngineCore:
             not (vllm_config.speculative_config and vllm_config.speculative_config.method) and \
             not vllm_config.model_config.logits_processors   # user processors may read the tokens produced so far
         self.scheduler.async_scheduling = self.async_scheduling
+        self._stalled = 0      # consecutive idle schedules that placed nothing (see _unschedulable)
         self._inflight = None  # SchedulerOutput of the launched, uncollected step
         self._overlap = True   # set_overlap(False): finish what is in flight without launching behind it (drains the pipeline)
         self._structured = None  # built on the first request that asks for a grammar
@@ -88,10 +89,38 @@ class EngineCore:
         if not self.scheduler.has_requests() or self.paused:
             return {}, False
         so = self.scheduler.schedule()
+        stuck = self._unschedulable(so)
+        if stuck is not None:
+            return stuck, False
         if self._structured is not None and self._structured.grammars:
             so.grammar_bitmask, so.structured_rows = self._structured.grammar_bitmask(list(so.num_scheduled_tokens))
         mro = self._guarded(so, lambda: self.executor.execute_model(so))
         return self._finish_step(so, mro)
+
+    def _unschedulable(self, so) -> Optional[dict]:
+        """An idle engine (nothing running, nothing in flight, no block copies pending) that schedules no token of its first waiting
+        request, sixteen times in a row, will never schedule it: the request asks for more than the engine can ever give (an encoder
+        input larger than the encoder cache, more blocks than the pool holds). It is finished with an error instead of spinning."""
+        sch = self.scheduler
+        idle = (so.total_num_scheduled_tokens == 0 and not sch.running and sch.waiting and self._inflight is None and not so.kv_swap_in
+                and not so.kv_swap_out)
+        if not idle:
+            self._stalled = 0
+            return None
+        self._stalled += 1
+        if self._stalled < 16:
+            return None
+        self._stalled = 0
+        r = sch.waiting.peek()
+        log.error(f"request {r.request_id} can never be scheduled on this engine ({r.num_tokens} tokens, {len(r.mm_features or ())} multimodal items): "
+                  "finished with an error")
+        from onecat_vllm.request import EngineCoreOutput, FinishReason
+        out = EngineCoreOutput(r.request_id, [], FinishReason.ERROR if hasattr(FinishReason, "ERROR") else FinishReason.ABORT,
+                               "the request does not fit this engine (KV blocks or encoder cache)")
+        sch.finish_requests(r.request_id, RequestStatus.FINISHED_ERROR)
+        if self._structured is not None:
+            self._structured.free(r.request_id)
+        return {r.client_index: EngineCoreOutputs([out])}
 
     def _guarded(self, so, call):
         try:
@@ -118,6 +147,9 @@ class EngineCore:
             if not sch.has_requests() or self.paused:
                 return {}, False
             so = sch.schedule()
+            stuck = self._unschedulable(so)
+            if stuck is not None:
+                return stuck, False
             if not overlap_ok or so.total_num_scheduled_tokens == 0:
                 if self._structured is not None and self._structured.grammars:
                     so.grammar_bitmask, so.structured_rows = self._structured.grammar_bitmask(list(so.num_scheduled_tokens))

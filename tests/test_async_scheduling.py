@@ -81,3 +81,24 @@ def test_a_stop_found_one_step_late_drops_the_extra_token():
     more = [o.outputs[0].token_ids for o in a.generate(_prompts(3, (15, 28, 9)), base)]
     a.shutdown()
     assert got == ref and more == [o.outputs[0].token_ids for o in free]
+
+
+@pytest.mark.parametrize("async_on", [False, True])
+def test_a_request_that_can_never_be_scheduled_ends_with_an_error(async_on):
+    """An idle engine whose scheduler keeps placing nothing for its first waiting request gives that request an error finish
+    instead of spinning (host-side fault: the block pool is made to look too small for the prompt)."""
+    import torch
+    from onecat_vllm import LLM, SamplingParams
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=1, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, vocab_size=300, max_position_embeddings=256)
+    llm = LLM(hf_config=cfg, device="cpu", dtype="float32", max_model_len=128, async_scheduling=async_on)
+    core = llm.llm_engine.engine_core.core
+    km = core.scheduler.kv_cache_manager
+    orig = km.allocate_slots
+    km.allocate_slots = lambda *a, **k: None            # "no room", for every request, for ever
+    outs = llm.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0, max_tokens=4))
+    assert outs[0].finished and outs[0].outputs[0].finish_reason == "error" and outs[0].outputs[0].token_ids == []
+    km.allocate_slots = orig
+    ok = llm.generate([[1, 2, 3, 4, 5]], SamplingParams(temperature=0, max_tokens=4, ignore_eos=True))
+    assert len(ok[0].outputs[0].token_ids) == 4         # the engine is still good for other requests
+    llm.shutdown()

@@ -34,12 +34,13 @@ class PPMissingLayer(nn.Module):
 class DecoderLayer(nn.Module):
     def __init__(self, cfg: ModelConfig, idx: int, prefix: str, device):
         super().__init__()
+        from onecat_vllm.utils.plugins import layer_class
         self.kind = cfg.layer_type(idx)
         if cfg.use_mla:
             self.kind = "mla"
-            self.self_attn = MLAAttention(cfg, idx, prefix + ".self_attn", device)
+            self.self_attn = layer_class("MLAAttention", MLAAttention)(cfg, idx, prefix + ".self_attn", device)
         elif self.kind == "linear_attention":
-            self.linear_attn = GatedDeltaNet(cfg, idx, prefix + ".linear_attn")
+            self.linear_attn = layer_class("GatedDeltaNet", GatedDeltaNet)(cfg, idx, prefix + ".linear_attn")
         elif self.kind in ("mamba2", "mamba1", "short_conv"):
             if self.kind == "mamba2":
                 from onecat_vllm.layers.mamba2 import Mamba2Mixer as Mixer
@@ -51,15 +52,15 @@ class DecoderLayer(nn.Module):
             self.kind = "linear_attention"   # a state-slot layer like Gated-DeltaNet for the runner and the scheduler
             self.graph_safe = False          # its convolution and scan read batch geometry on the host
         else:
-            self.self_attn = Attention(cfg, idx, prefix + ".self_attn", device)
+            self.self_attn = layer_class("Attention", Attention)(cfg, idx, prefix + ".self_attn", device)
         if cfg.mixer_only_layers:
             self.mlp = None
             self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
             return
         if cfg.is_moe_layer(idx):
-            self.mlp = SparseMoeBlock(cfg, prefix + ".mlp")
+            self.mlp = layer_class("SparseMoeBlock", SparseMoeBlock)(cfg, prefix + ".mlp")
         else:
-            self.mlp = MLP(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
+            self.mlp = layer_class("MLP", MLP)(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
                            act=cfg.hidden_act, bias=cfg.mlp_bias)
         self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
         self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)

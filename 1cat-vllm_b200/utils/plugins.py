@@ -45,3 +45,22 @@ def load_general_plugins() -> list[str]:
         except Exception as e:
             log.error(f"plugin {name} raised: {e!r}")
     return ran
+
+
+# ---- out-of-tree layer classes (reference: model_executor/custom_op.py:32,103 ``CustomOp.register`` / ``PluggableLayer``)
+_LAYER_OVERRIDES: dict[str, type] = {}
+
+
+def register_layer(name: str, cls: type) -> None:
+    """Replace one of the decoder's building blocks (``Attention``, ``MLAAttention``, ``GatedDeltaNet``, ``MLP``, ``SparseMoeBlock``,
+    ``RMSNorm``) by ``cls``, which must take the same constructor arguments and keep the parameter names (checkpoints load by name).
+    A plugin calls this before the engine is built."""
+    _LAYER_OVERRIDES[name] = cls
+
+
+def unregister_layer(name: str) -> None:
+    _LAYER_OVERRIDES.pop(name, None)
+
+
+def layer_class(name: str, default: type) -> type:
+    return _LAYER_OVERRIDES.get(name, default)

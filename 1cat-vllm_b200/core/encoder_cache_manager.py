@@ -71,6 +71,19 @@ class EncoderCacheManager:
         for i in range(len(getattr(request, "mm_features", None) or [])):
             self.free_encoder_input(request, i)
 
+    def reset(self) -> int:
+        """Evict every entry that no request references (the workers drop the outputs with the next step's freed list). Entries
+        still in use stay. Returns how many were evicted (reference: encoder_cache_manager.py ``reset``; the ``/reset_mm_cache`` route)."""
+        n = 0
+        for h, size in list(self.freeable.items()):
+            del self.freeable[h]
+            self.cached.pop(h, None)
+            self.sizes.pop(h, None)
+            self.num_free_slots += size
+            self.freed.append(h)
+            n += 1
+        return n
+
     def get_freed_mm_hashes(self) -> list[str]:
         out, self.freed = self.freed, []
         return out

@@ -143,6 +143,9 @@ class AsyncLLM:
     async def reset_prefix_cache(self) -> bool:
         return await self._utility("reset_prefix_cache")
 
+    async def reset_mm_cache(self) -> int:
+        return await self._utility("reset_encoder_cache")
+
     async def sleep(self, level: int = 1) -> None:
         await self._utility("sleep", level)
 

@@ -192,6 +192,9 @@ class EngineCore:
     def reset_prefix_cache(self) -> bool:
         return self.scheduler.reset_prefix_cache()
 
+    def reset_encoder_cache(self) -> int:
+        return self.scheduler.encoder_cache_manager.reset()
+
     def sleep(self, level: int = 1) -> None:
         self.paused = True
         self.executor.collective_rpc("sleep", (level,))

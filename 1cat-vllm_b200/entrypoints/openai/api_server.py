@@ -41,6 +41,13 @@ class ServingState:
         self.inflight = 0
         self.loras: dict = {}  # served adapter name -> LoRARequest
         self._next_lora_id = 1
+        self.responses: dict = {}   # id -> finished Responses object (kept while ``store`` is true; the 1024 most recent)
+
+    def keep_response(self, obj: dict) -> dict:
+        self.responses[obj["id"]] = obj
+        while len(self.responses) > 1024:
+            self.responses.pop(next(iter(self.responses)))
+        return obj
 
     def register_lora(self, name: str, path: str):
         from onecat_vllm.lora import LoRARequest
@@ -94,7 +101,7 @@ def build_app(state: ServingState) -> FastAPI:
     # switch (reference: the dev-mode routers of entrypoints/serve/ are registered only under VLLM_SERVER_DEV_MODE, the LoRA
     # routes only under VLLM_ALLOW_RUNTIME_LORA_UPDATING). Without the switch they answer 404 as if they were not registered.
     dev_paths = {"/reset_prefix_cache", "/sleep", "/wake_up", "/is_sleeping", "/pause", "/resume", "/is_paused", "/collective_rpc",
-                 "/start_profile", "/stop_profile", "/server_info"}
+                 "/start_profile", "/stop_profile", "/server_info", "/abort_requests", "/reset_mm_cache", "/reset_encoder_cache", "/get_world_size"}
     lora_paths = {"/v1/load_lora_adapter", "/v1/unload_lora_adapter"}
     open_paths = {"/health", "/ping", "/version", "/metrics", "/load"}  # probes and scrapers carry no key
 
@@ -190,7 +197,33 @@ def build_app(state: ServingState) -> FastAPI:
             return JSONResponse(error_body("the server has no tokenizer"), status_code=400)
         return {"prompt": tok.decode(req.tokens)}
 
+    @app.get("/tokenizer_info")
+    async def tokenizer_info():
+        tok = state.engine.tokenizer
+        if tok is None:
+            return JSONResponse(error_body("this server runs without a tokenizer"), status_code=400)
+        return {"tokenizer_class": type(tok).__name__, "vocab_size": getattr(tok, "vocab_size", None), "bos_token_id": getattr(tok, "bos_token_id", None),
+                "eos_token_id": getattr(tok, "eos_token_id", None), "chat_template": getattr(tok, "chat_template", None)}
+
+    @app.get("/get_world_size")
+    async def get_world_size(include_dp: bool = True):
+        pc = state.engine.cfg.parallel_config
+        return {"world_size": pc.world_size * (pc.data_parallel_size if include_dp else 1)}
+
     # ---- control routes
+    @app.post("/abort_requests")
+    async def abort_requests(body: dict):
+        ids = [str(x) for x in body.get("request_ids", [])]
+        for rid in ids:
+            await state.engine.abort(rid)
+        return {"aborted": ids}
+
+    @app.post("/reset_mm_cache")
+    @app.post("/reset_encoder_cache")
+    async def reset_mm_cache():
+        """Drops cached encoder outputs on every worker (reference: ``/reset_mm_cache``, ``/reset_encoder_cache``)."""
+        return {"evicted": await state.engine.reset_mm_cache()}
+
     @app.post("/reset_prefix_cache")
     async def reset_prefix_cache():
         ok = await state.engine.reset_prefix_cache()
@@ -431,10 +464,28 @@ def build_app(state: ServingState) -> FastAPI:
             out.append({"type": "message", "id": new_id("msg"), "role": "assistant", "status": "completed",
                         "content": [{"type": "output_text", "text": ch["message"]["content"], "annotations": []}]})
         u = res["usage"]
-        return {"id": new_id("resp"), "object": "response", "created_at": now(), "model": res["model"], "status": "completed",
-                "incomplete_details": {"reason": "max_output_tokens"} if ch["finish_reason"] == "length" else None, "output": out,
-                "output_text": ch["message"].get("content") or "",
-                "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"]}}
+        obj = {"id": new_id("resp"), "object": "response", "created_at": now(), "model": res["model"], "status": "completed",
+               "incomplete_details": {"reason": "max_output_tokens"} if ch["finish_reason"] == "length" else None, "output": out,
+               "output_text": ch["message"].get("content") or "",
+               "usage": {"input_tokens": u["prompt_tokens"], "output_tokens": u["completion_tokens"], "total_tokens": u["total_tokens"]}}
+        return state.keep_response(obj) if body.get("store", True) else obj
+
+    @app.get("/v1/responses/{response_id}")
+    async def get_response(response_id: str):
+        """A finished response kept by ``store`` (reference: entrypoints/openai/responses ``retrieve_responses``)."""
+        obj = state.responses.get(response_id)
+        if obj is None:
+            return JSONResponse(error_body(f"response {response_id} not found", "NotFoundError", 404), status_code=404)
+        return obj
+
+    @app.post("/v1/responses/{response_id}/cancel")
+    async def cancel_response(response_id: str):
+        """Responses run to completion inside their request here, so only a stored, finished one can be named: it is returned as it is
+        (cancelling a finished response is a no-op in the reference too)."""
+        obj = state.responses.get(response_id)
+        if obj is None:
+            return JSONResponse(error_body(f"response {response_id} not found", "NotFoundError", 404), status_code=404)
+        return obj
 
     @app.post("/v1/messages")
     async def anthropic_messages(body: dict, raw: Request):

@@ -405,3 +405,37 @@ def test_render_routes_return_the_prompt_the_engine_would_see(client):
     # the same messages through the generating route consume exactly the rendered prompt
     g = client.post("/v1/chat/completions", json={"model": "tiny", "messages": [{"role": "user", "content": "hi"}], "max_tokens": 2, "temperature": 0})
     assert g.status_code == 200 and g.json()["usage"]["prompt_tokens"] == len(body["token_ids"])
+
+
+@pytest.mark.timeout(300)
+def test_stored_responses_and_small_info_routes(client):
+    r = client.post("/v1/responses", json={"model": "tiny", "input": "hi", "max_output_tokens": 3, "temperature": 0})
+    assert r.status_code == 200, r.text
+    rid = r.json()["id"]
+    got = client.get(f"/v1/responses/{rid}")
+    assert got.status_code == 200 and got.json() == r.json()
+    assert client.post(f"/v1/responses/{rid}/cancel").json()["id"] == rid
+    assert client.get("/v1/responses/resp_nope").status_code == 404
+    r2 = client.post("/v1/responses", json={"model": "tiny", "input": "hi", "max_output_tokens": 3, "temperature": 0, "store": False})
+    assert client.get(f"/v1/responses/{r2.json()['id']}").status_code == 404
+    info = client.get("/tokenizer_info").json()
+    assert info["tokenizer_class"] == "ByteTokenizer" and info["vocab_size"] == 258
+    assert client.get("/get_world_size").json() == {"world_size": 1}
+    assert client.post("/abort_requests", json={"request_ids": ["nothing-by-this-name"]}).status_code == 200
+    assert client.post("/reset_mm_cache").json() == {"evicted": 0} and client.post("/reset_encoder_cache").status_code == 200
+
+
+def test_encoder_cache_reset_evicts_only_unreferenced_entries():
+    from types import SimpleNamespace
+    from onecat_vllm.core.encoder_cache_manager import EncoderCacheManager
+    from onecat_vllm.multimodal import MultiModalFeature
+    m = EncoderCacheManager(10)
+    f = lambda h, n: MultiModalFeature("image", h, 0, n, "embeds")
+    a = SimpleNamespace(request_id="a", mm_features=[f("x", 4)])
+    b = SimpleNamespace(request_id="b", mm_features=[f("y", 3)])
+    for r in (a, b):
+        assert m.can_allocate(r, 0, 100)
+        m.allocate(r, 0)
+    m.free(a)                                            # x is cached but nobody uses it; y is in use
+    assert m.reset() == 1 and m.get_freed_mm_hashes() == ["x"]
+    assert m.num_free_slots == 7 and m.num_freeable_slots == 7 and "y" in m.cached and "x" not in m.cached

@@ -101,7 +101,8 @@ def build_app(state: ServingState) -> FastAPI:
     # switch (reference: the dev-mode routers of entrypoints/serve/ are registered only under VLLM_SERVER_DEV_MODE, the LoRA
     # routes only under VLLM_ALLOW_RUNTIME_LORA_UPDATING). Without the switch they answer 404 as if they were not registered.
     dev_paths = {"/reset_prefix_cache", "/sleep", "/wake_up", "/is_sleeping", "/pause", "/resume", "/is_paused", "/collective_rpc",
-                 "/start_profile", "/stop_profile", "/server_info", "/abort_requests", "/reset_mm_cache", "/reset_encoder_cache", "/get_world_size"}
+                 "/start_profile", "/stop_profile", "/server_info", "/abort_requests", "/reset_mm_cache", "/reset_encoder_cache", "/get_world_size",
+                 "/init_weight_transfer_engine", "/start_weight_update", "/update_weights", "/finish_weight_update"}
     lora_paths = {"/v1/load_lora_adapter", "/v1/unload_lora_adapter"}
     open_paths = {"/health", "/ping", "/version", "/metrics", "/load"}  # probes and scrapers carry no key
 
@@ -223,6 +224,45 @@ def build_app(state: ServingState) -> FastAPI:
     async def reset_mm_cache():
         """Drops cached encoder outputs on every worker (reference: ``/reset_mm_cache``, ``/reset_encoder_cache``)."""
         return {"evicted": await state.engine.reset_mm_cache()}
+
+    # ---- weight updates between rollouts (reference: entrypoints/serve/rlhf/api_router.py:113-170)
+    @app.post("/init_weight_transfer_engine")
+    async def init_weight_transfer_engine(body: dict):
+        info = body.get("init_info")
+        if not info or "init_method" not in info or "world_size" not in info:
+            return JSONResponse(error_body("init_info needs init_method and world_size (and rank_offset, backend)"), status_code=400)
+        await state.engine.collective_rpc("init_weight_transfer_offset", (info["init_method"], int(info.get("rank_offset", 1)), int(info["world_size"]),
+                                                                         info.get("backend")))
+        return {"message": "Weight transfer initialized"}
+
+    @app.post("/start_weight_update")
+    async def start_weight_update(body: Optional[dict] = None):
+        await state.engine.pause_generation()
+        state.updating_weights = True
+        return {"message": "Weight update started"}
+
+    @app.post("/update_weights")
+    async def update_weights(body: dict):
+        info = body.get("update_info")
+        if not info:
+            return JSONResponse(error_body("Missing 'update_info' in request body"), status_code=400)
+        try:
+            if "path" in info:       # a checkpoint directory every worker can read
+                n = await state.engine.collective_rpc("update_weights_from_path", (info["path"],))
+            elif "tensors" in info:  # names / dtypes / shapes of what the trainer (rank 0 of the transfer group) is broadcasting now
+                n = await state.engine.collective_rpc("update_weights_broadcast", (info,))
+            else:
+                return JSONResponse(error_body("update_info needs 'path' or the broadcast description ('bucket_bytes', 'tensors')"), status_code=400)
+        except Exception as e:
+            return JSONResponse(error_body(f"weight update failed: {e}"), status_code=400)
+        return {"message": "Weights updated", "tensors": n}
+
+    @app.post("/finish_weight_update")
+    async def finish_weight_update():
+        await state.engine.reset_prefix_cache()      # cached KV belongs to the old weights
+        await state.engine.resume_generation()
+        state.updating_weights = False
+        return {"message": "Weight update finished"}
 
     @app.post("/reset_prefix_cache")
     async def reset_prefix_cache():

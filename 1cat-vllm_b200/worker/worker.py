@@ -183,6 +183,15 @@ class Worker:
         self._wt = BroadcastWeightTransfer.init(init_method, rank, world_size, self.device, backend)
         return True
 
+    def init_weight_transfer_offset(self, init_method: str, rank_offset: int, world_size: int, backend=None) -> bool:
+        """The same call for every worker of the engine: worker r joins as rank ``rank_offset + r`` (the trainer is rank 0)."""
+        return self.init_weight_transfer(init_method, int(rank_offset) + self.rank, world_size, backend)
+
+    def update_weights_from_path(self, path: str) -> int:
+        """Load the tensors of a safetensors checkpoint directory in place (HF names; any subset of the model)."""
+        from onecat_vllm.loader.weights import iter_safetensors
+        return self.update_weights(iter_safetensors(path))
+
     def update_weights_broadcast(self, meta: dict) -> int:
         """Receive the tensors the trainer (rank 0 of the transfer group) broadcasts and load them in place."""
         if getattr(self, "_wt", None) is None:

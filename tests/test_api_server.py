@@ -439,3 +439,22 @@ def test_encoder_cache_reset_evicts_only_unreferenced_entries():
     m.free(a)                                            # x is cached but nobody uses it; y is in use
     assert m.reset() == 1 and m.get_freed_mm_hashes() == ["x"]
     assert m.num_free_slots == 7 and m.num_freeable_slots == 7 and "y" in m.cached and "x" not in m.cached
+
+
+@pytest.mark.timeout(300)
+def test_weight_update_routes_load_a_checkpoint_in_place(client, tmp_path):
+    import torch
+    from safetensors.torch import save_file
+    body = {"model": "tiny", "prompt": [5, 6, 7], "max_tokens": 6, "temperature": 0}
+    before = client.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    save_file({"model.norm.weight": torch.linspace(-1.0, 2.0, 64)}, str(tmp_path / "model.safetensors"))
+    assert client.post("/start_weight_update", json={}).status_code == 200
+    assert client.get("/is_paused").json()["is_paused"] is True
+    assert client.post("/update_weights", json={}).status_code == 400
+    r = client.post("/update_weights", json={"update_info": {"path": str(tmp_path)}})
+    assert r.status_code == 200 and r.json()["tensors"] == [1], r.text
+    assert client.post("/finish_weight_update").status_code == 200
+    assert client.get("/is_paused").json()["is_paused"] is False
+    after = client.post("/v1/completions", json=body).json()["choices"][0]["text"]
+    assert after != before
+    assert client.post("/init_weight_transfer_engine", json={"init_info": {}}).status_code == 400

@@ -123,6 +123,7 @@ class ModelConfig:
     attn_sinks: bool = False  # one learned sink logit per query head joins the softmax denominator (GPT-OSS)
     attn_o_bias: bool = False  # bias on the attention output projection
     mlp_bias: bool = False  # biases on the dense feed-forward projections (Llama / Granite ``mlp_bias``)
+    mlp_gated: bool = True  # False: down(act(up(x))) without a gate projection (Arcee: squared ReLU)
     router_linear_bias: bool = False  # the router is a linear layer with bias
     expert_bias: bool = False  # every expert projection has a bias
     moe_act: str = "silu"  # silu | swiglu_oai: (up + 1) * gate * sigmoid(1.702 gate) with gate <= 7 and |up| <= 7 (GPT-OSS)
@@ -461,6 +462,8 @@ class ModelConfig:
                       scoring_func="sigmoid", n_group=hf.get("n_group", 1), topk_group=hf.get("topk_group", 1), norm_topk_prob=bool(hf.get("norm_topk_prob", True)),
                       routed_scaling_factor=hf.get("routed_scaling_factor", 1.0), first_k_dense_replace=0,
                       dense_layers=tuple(i for i, t in enumerate(kinds) if t != "sparse") if kinds else tuple(range(int(hf.get("first_k_dense_replace", 0)))))
+        if a.startswith("arcee"):
+            kw.update(mlp_gated=False, hidden_act="relu2")
         if a.startswith("exaonemoe"):
             # pre-norm blocks with per-head q/k norm; global layers of the hybrid form apply no rotary embedding; DeepSeek-V3-style router
             kinds = hf.get("mlp_layer_types") or []

@@ -4,7 +4,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from onecat_vllm.layers.linear import MergedColumnParallelLinear, RowParallelLinear
+from onecat_vllm.layers.linear import ColumnParallelLinear, MergedColumnParallelLinear, RowParallelLinear
 
 
 class MLP(nn.Module):
@@ -24,4 +24,30 @@ class MLP(nn.Module):
         if not self.fuse_act:
             from onecat_vllm import ops
             h = ops.silu_and_mul(h) if self.act == "silu" else ops.gelu_tanh_and_mul(h)
+        return self.down_proj(h)
+
+
+class PlainMLP(nn.Module):
+    """Feed-forward without a gate: ``down(act(up(x)))`` with ``act`` = squared ReLU (Arcee) or GELU
+    (reference: models/arcee.py ``ArceeMLP``; layers/activation.py ``ReLUSquaredActivation``). The activation is an elementwise
+    PyTorch operation between the two GEMMs."""
+
+    def __init__(self, hidden: int, inter: int, quant, prefix: str, dtype, act: str = "relu2", bias: bool = False):
+        super().__init__()
+        self.act = act
+        self.up_proj = ColumnParallelLinear(hidden, inter, bias=bias, quant=quant, prefix=prefix + ".up_proj", dtype=dtype)
+        self.down_proj = RowParallelLinear(inter, hidden, bias=bias, quant=quant, prefix=prefix + ".down_proj", dtype=dtype)
+
+    def forward(self, x):
+        import torch
+        import torch.nn.functional as F
+        h = self.up_proj(x)
+        if self.act == "relu2":
+            h = torch.square(F.relu(h))
+        elif self.act == "gelu_tanh":
+            h = F.gelu(h, approximate="tanh")
+        elif self.act == "gelu":
+            h = F.gelu(h)
+        else:
+            h = F.silu(h)
         return self.down_proj(h)

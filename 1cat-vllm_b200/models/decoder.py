@@ -59,6 +59,10 @@ class DecoderLayer(nn.Module):
             return
         if cfg.is_moe_layer(idx):
             self.mlp = layer_class("SparseMoeBlock", SparseMoeBlock)(cfg, prefix + ".mlp")
+        elif not cfg.mlp_gated:
+            from onecat_vllm.layers.mlp import PlainMLP
+            self.mlp = layer_class("PlainMLP", PlainMLP)(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, act=cfg.hidden_act,
+                                                         bias=cfg.mlp_bias)
         else:
             self.mlp = layer_class("MLP", MLP)(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
                            act=cfg.hidden_act, bias=cfg.mlp_bias)

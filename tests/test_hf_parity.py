@@ -119,6 +119,7 @@ CASES = {
     "Glm4MoeLiteForCausalLM": dict(BASE, model_type="glm4_moe_lite", num_key_value_heads=4, q_lora_rank=32, kv_lora_rank=32, qk_nope_head_dim=16,
                                    qk_rope_head_dim=16, v_head_dim=16, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48,
                                    routed_scaling_factor=1.5, mlp_layer_types=["dense", "sparse"], pad_token_id=0),
+    "ArceeForCausalLM": dict(BASE, model_type="arcee", head_dim=16, rope_theta=10000.0, pad_token_id=0),
     "MiniMaxM2ForCausalLM": dict(BASE, model_type="minimax_m2", head_dim=16, intermediate_size=48, num_local_experts=8, num_experts_per_tok=2,
                                  pad_token_id=0),
 }

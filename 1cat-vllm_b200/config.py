@@ -123,6 +123,11 @@ class ModelConfig:
     attn_sinks: bool = False  # one learned sink logit per query head joins the softmax denominator (GPT-OSS)
     attn_o_bias: bool = False  # bias on the attention output projection
     mlp_bias: bool = False  # biases on the dense feed-forward projections (Llama / Granite ``mlp_bias``)
+    norm_type: str = "rms"  # rms | layernorm (mean-and-variance normalisation; ``gemma_norm`` then means the weight is stored minus one)
+    norm_affine: bool = True  # False: the layer norm has no learned parameters (OLMo)
+    norm_bias: bool = False  # the layer norm has a bias
+    parallel_block: bool = False  # h += attn(norm(h)) + mlp(norm(h)) with one norm per block (Cohere)
+    qkv_clip: Optional[float] = None  # clamp of the q / k / v projections (OLMo ``clip_qkv``)
     mlp_gated: bool = True  # False: down(act(up(x))) without a gate projection (Arcee: squared ReLU)
     router_linear_bias: bool = False  # the router is a linear layer with bias
     expert_bias: bool = False  # every expert projection has a bias
@@ -464,6 +469,34 @@ class ModelConfig:
                       dense_layers=tuple(i for i, t in enumerate(kinds) if t != "sparse") if kinds else tuple(range(int(hf.get("first_k_dense_replace", 0)))))
         if a.startswith("arcee"):
             kw.update(mlp_gated=False, hidden_act="relu2")
+        # families on mean-and-variance layer norms
+        if a.startswith("olmofor"):           # OLMo-1: layer norms without learned parameters, optional clamp of q / k / v
+            kw.update(norm_type="layernorm", norm_affine=False, rms_norm_eps=1e-5, qkv_clip=hf.get("clip_qkv"))
+        if a.startswith("stablelm"):
+            if hf.get("qk_layernorm") or hf.get("use_parallel_residual"):
+                raise ValueError("StableLM with per-head layer norms or the parallel residual form is not served")
+            kw.update(norm_type="layernorm", norm_bias=True, rms_norm_eps=hf.get("layer_norm_eps", 1e-5),
+                      attention_bias=bool(hf.get("use_qkv_bias", False)), attn_o_bias=False)
+        if a.startswith("starcoder2"):
+            b = bool(hf.get("use_bias", True))
+            kw.update(norm_type="layernorm", norm_bias=True, rms_norm_eps=hf.get("norm_epsilon", 1e-5), attention_bias=b, attn_o_bias=b,
+                      mlp_bias=b, mlp_gated=False, hidden_act="gelu_tanh", tie_word_embeddings=hf.get("tie_word_embeddings", True))
+            if hf.get("sliding_window"):
+                kw.update(sliding_window=int(hf["sliding_window"]), sliding_layers=tuple(range(kw["num_hidden_layers"])))
+        if a.startswith("nemotronfor"):       # layer norms whose weight is stored minus one; squared-ReLU feed-forward without a gate
+            kw.update(norm_type="layernorm", norm_bias=True, gemma_norm=True, rms_norm_eps=hf.get("norm_eps", 1e-5), mlp_gated=False,
+                      hidden_act="relu2", attn_o_bias=bool(hf.get("attention_bias", False)))
+        if a.startswith("cohere"):            # Command-R: parallel blocks on weight-only layer norms, adjacent-pair rotary, scaled logits
+            if hf.get("use_qk_norm"):
+                raise ValueError("Cohere checkpoints with per-head q / k layer norms are not served")
+            kw.update(norm_type="layernorm", norm_bias=False, rms_norm_eps=hf.get("layer_norm_eps", 1e-5), parallel_block=True,
+                      rope_interleaved=True, logit_scale=float(hf.get("logit_scale", 0.0625)),
+                      tie_word_embeddings=hf.get("tie_word_embeddings", True), attn_o_bias=bool(hf.get("attention_bias", False)))
+            if kw.get("sliding_layers"):          # Command-R7B / Command-A: only the sliding-window layers rotate
+                kw["nope_layers"] = tuple(i for i in range(kw["num_hidden_layers"]) if i not in kw["sliding_layers"])
+        if a.startswith("jais2"):
+            kw.update(norm_type="layernorm", norm_bias=True, rms_norm_eps=hf.get("layer_norm_eps", 1e-5), mlp_gated=False,
+                      hidden_act="relu2", attn_o_bias=bool(hf.get("attention_bias", False)))
         if a.startswith("exaonemoe"):
             # pre-norm blocks with per-head q/k norm; global layers of the hybrid form apply no rotary embedding; DeepSeek-V3-style router
             kinds = hf.get("mlp_layer_types") or []

@@ -51,6 +51,7 @@ class Attention(nn.Module):
                              None if local else cfg.rope_scaling)
         self.scale = cfg.attn_scale if cfg.attn_scale is not None else cfg.head_dim ** -0.5
         self.layer_idx = layer_idx
+        self.qkv_clip = cfg.qkv_clip
 
     def load_weight(self, pname: str, w: torch.Tensor, shard_id=None) -> None:
         """Parameters that belong to the block itself: the per-head sink logits are sharded with the query heads."""
@@ -63,6 +64,8 @@ class Attention(nn.Module):
         T = x.shape[0]
         D, Hq, Hkv = self.D, self.Hq, self.Hkv
         qkv = self.qkv_proj(x)
+        if self.qkv_clip is not None:      # OLMo: projections clamped to ±clip before the rotary embedding
+            qkv = qkv.clamp(-self.qkv_clip, self.qkv_clip)
         qw = Hq * D * (2 if self.gated else 1)
         if self.gated:
             qg = qkv[:, :qw].view(T, Hq, 2 * D)

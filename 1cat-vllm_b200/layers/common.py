@@ -27,6 +27,42 @@ class RMSNorm(nn.Module):
         self.weight.data.copy_(w)
 
 
+class LayerNorm(nn.Module):
+    """Mean-and-variance normalisation with the interface of ``RMSNorm`` (returns ``(normed, residual_out)``), for the families that
+    predate RMSNorm or keep it: OLMo (no learned parameters), StableLM / Starcoder2 / Jais-2 (weight and bias), Nemotron (weight
+    stored minus one, reference: models/nemotron.py ``NemotronLayerNorm1P``). It runs as PyTorch operations on every device and is
+    not folded into the tensor-parallel reduction kernel (``plain`` tells ``reduce_add_norm`` to reduce first and call it after)."""
+
+    plain = True
+
+    def __init__(self, hidden: int, eps: float, affine: bool = True, bias: bool = True, plus_one: bool = False, dtype=torch.float32):
+        super().__init__()
+        self.hidden, self.eps, self.gemma = hidden, eps, plus_one
+        self.weight = nn.Parameter(torch.zeros(hidden, dtype=dtype) if plus_one else torch.ones(hidden, dtype=dtype), requires_grad=False) \
+            if affine else None
+        self.bias = nn.Parameter(torch.zeros(hidden, dtype=dtype), requires_grad=False) if affine and bias else None
+
+    def forward(self, x, residual: Optional[torch.Tensor] = None):
+        if residual is not None:
+            x = x + residual
+        w = self.weight
+        if w is not None:
+            w = w.float() + 1.0 if self.gemma else w.float()
+        y = torch.nn.functional.layer_norm(x.float(), (self.hidden,), w, None if self.bias is None else self.bias.float(), self.eps)
+        return y.to(x.dtype), x
+
+    def load_weight(self, pname, w, shard_id=None):
+        getattr(self, pname).data.copy_(w)
+
+
+def make_norm(cfg, hidden: Optional[int] = None) -> nn.Module:
+    """The normalisation a model's blocks use: RMSNorm unless its configuration names the mean-and-variance form."""
+    hidden = hidden or cfg.hidden_size
+    if cfg.norm_type == "layernorm":
+        return LayerNorm(hidden, cfg.rms_norm_eps, cfg.norm_affine, cfg.norm_bias, cfg.gemma_norm, cfg.dtype)
+    return RMSNorm(hidden, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+
+
 class RotaryEmbedding:
     """NeoX-style rotary with a precomputed fp32 cos|sin table."""
 

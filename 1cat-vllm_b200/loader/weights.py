@@ -35,7 +35,7 @@ _RENAMES = ((".conv.conv.weight", ".linear_attn.conv_weight"), (".conv.conv.bias
             (".conv.out_proj.", ".linear_attn.out_proj."), (".feed_forward.w1.", ".mlp.gate_proj."), (".feed_forward.w3.", ".mlp.up_proj."),
             (".feed_forward.w2.", ".mlp.down_proj."), (".operator_norm.", ".input_layernorm."), (".ffn_norm.", ".post_attention_layernorm."),
             ("model.embedding_norm.", "model.norm."), (".self_attn.out_proj.", ".self_attn.o_proj."), (".q_layernorm.weight", ".q_norm"),
-            (".k_layernorm.weight", ".k_norm"),
+            (".k_layernorm.weight", ".k_norm"), (".mlp.c_fc.", ".mlp.up_proj."), (".mlp.c_proj.", ".mlp.down_proj."),
             (".mamba.", ".linear_attn."), (".mixer.", ".linear_attn."), (".feed_forward.", ".mlp."), (".pre_ff_layernorm.", ".post_attention_layernorm."),
             ("model.final_layernorm.", "model.norm."), ("backbone.embeddings.", "model.embed_tokens."), ("backbone.norm_f.", "model.norm."),
             ("backbone.layers.", "model.layers."), (".linear_attn.conv1d.bias", ".linear_attn.conv_bias"),

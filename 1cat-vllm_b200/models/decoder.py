@@ -15,7 +15,7 @@ import torch.nn as nn
 
 from onecat_vllm.config import ModelConfig
 from onecat_vllm.layers.attention import Attention
-from onecat_vllm.layers.common import ParallelLMHead, RMSNorm, VocabParallelEmbedding
+from onecat_vllm.layers.common import ParallelLMHead, RMSNorm, VocabParallelEmbedding, make_norm
 from onecat_vllm.layers.gdn import GatedDeltaNet
 from onecat_vllm.layers.mla import MLAAttention
 from onecat_vllm.layers.mlp import MLP
@@ -55,7 +55,7 @@ class DecoderLayer(nn.Module):
             self.self_attn = layer_class("Attention", Attention)(cfg, idx, prefix + ".self_attn", device)
         if cfg.mixer_only_layers:
             self.mlp = None
-            self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+            self.input_layernorm = make_norm(cfg)
             return
         if cfg.is_moe_layer(idx):
             self.mlp = layer_class("SparseMoeBlock", SparseMoeBlock)(cfg, prefix + ".mlp")
@@ -66,13 +66,14 @@ class DecoderLayer(nn.Module):
         else:
             self.mlp = layer_class("MLP", MLP)(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix + ".mlp", cfg.dtype, fuse_act=not cfg.enable_lora,
                            act=cfg.hidden_act, bias=cfg.mlp_bias)
-        self.input_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
-        self.post_attention_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+        self.input_layernorm = make_norm(cfg)
+        if not cfg.parallel_block:
+            self.post_attention_layernorm = make_norm(cfg)
         if cfg.sandwich_norm:
             # Gemma2/3 and GLM-4: post_attention_layernorm normalises the mixer's output, pre_feedforward_layernorm is the pre-norm of
             # the feed-forward, post_feedforward_layernorm normalises its output (GLM-4's names are mapped to these at load)
-            self.pre_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
-            self.post_feedforward_layernorm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype)
+            self.pre_feedforward_layernorm = make_norm(cfg)
+            self.post_feedforward_layernorm = make_norm(cfg)
 
     def mixer(self, x, md, cache):
         if self.kind == "linear_attention":
@@ -93,7 +94,7 @@ class DecoderModel(nn.Module):
         self.embed_tokens = VocabParallelEmbedding(cfg.vocab_size, cfg.hidden_size, cfg.dtype) if need_embed else PPMissingLayer()
         self.layers = nn.ModuleList([DecoderLayer(cfg, i, f"model.layers.{i}", device) if self.start <= i < self.end else PPMissingLayer()
                                      for i in range(cfg.num_hidden_layers)])
-        self.norm = RMSNorm(cfg.hidden_size, cfg.rms_norm_eps, cfg.gemma_norm, cfg.dtype) if self.last_stage else PPMissingLayer()
+        self.norm = make_norm(cfg) if self.last_stage else PPMissingLayer()
         # EAGLE-3 drafting reads the residual stream at a few depths: layer indices to record, and what the last forward recorded
         self.aux_hidden_layers: tuple = ()
         self.last_aux: list = []
@@ -122,6 +123,8 @@ class DecoderModel(nn.Module):
             x, residual = layers[self.start].input_layernorm(intermediate[0], intermediate[1])
         if not cfg.pre_norm:
             return self._forward_post_norm(x if intermediate is None else None, residual, md, caches)
+        if cfg.parallel_block:
+            return self._forward_parallel(residual, md, caches)
         plain = not cfg.sandwich_norm and cfg.residual_multiplier == 1.0
         aux_at = self.aux_hidden_layers
         if aux_at:
@@ -167,6 +170,18 @@ class DecoderModel(nn.Module):
             layer = self.layers[i]
             h = h + layer.post_attention_layernorm(reduce_only(layer.mixer(h, md, caches[li])), None)[0]
             h = h + layer.post_feedforward_layernorm(reduce_only(layer.mlp(h)), None)[0]
+        return self.norm(h, None)[0]
+
+    def _forward_parallel(self, h, md, caches):
+        """Cohere block order: attention and feed-forward both read ``norm(h)`` and their outputs are added to ``h`` together
+        (reference: models/commandr.py). The two partial outputs are summed before the tensor-parallel reduction, so a layer costs
+        one reduction. Pipeline stages are not split for this order."""
+        if self.start != 0 or not self.last_stage:
+            raise ValueError("the parallel block order is served without pipeline parallelism")
+        for li, i in enumerate(range(self.start, self.end)):
+            layer = self.layers[i]
+            x = layer.input_layernorm(h, None)[0]
+            h = h + reduce_only(layer.mixer(x, md, caches[li]) + layer.mlp(x))
         return self.norm(h, None)[0]
 
     def _join(self, part, residual, post_norm, next_norm):

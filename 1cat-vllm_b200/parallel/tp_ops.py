@@ -20,6 +20,8 @@ def reduce_add_norm(partial: torch.Tensor, residual: Optional[torch.Tensor], nor
     st = ps.get_state()
     if st.tp_size == 1:
         return norm(partial, residual)
+    if getattr(norm, "plain", False):      # a normalisation the fused kernel does not compute: reduce, then normalise
+        return norm(reduce_only(partial), residual)
     if st.fused is not None and partial.is_cuda and st.tp_comm == "fused":
         return st.fused.reduce_add_norm(partial, residual, norm.weight, norm.eps, norm.gemma, pushed=getattr(partial, "_tp_pushed", False))
     ps.all_reduce(partial)

@@ -120,6 +120,16 @@ CASES = {
                                    qk_rope_head_dim=16, v_head_dim=16, n_routed_experts=8, num_experts_per_tok=2, moe_intermediate_size=48,
                                    routed_scaling_factor=1.5, mlp_layer_types=["dense", "sparse"], pad_token_id=0),
     "ArceeForCausalLM": dict(BASE, model_type="arcee", head_dim=16, rope_theta=10000.0, pad_token_id=0),
+    # mean-and-variance layer norms: without parameters (OLMo, with the q/k/v clamp), with weight and bias, with the weight stored minus one
+    "OlmoForCausalLM": dict(BASE, model_type="olmo", clip_qkv=0.8, pad_token_id=0),
+    "StableLmForCausalLM": dict(BASE, model_type="stablelm", use_qkv_bias=True, partial_rotary_factor=0.25, pad_token_id=0),
+    "Starcoder2ForCausalLM": dict(BASE, model_type="starcoder2", sliding_window=16, use_bias=True, pad_token_id=0),
+    "NemotronForCausalLM": dict(BASE, model_type="nemotron", partial_rotary_factor=0.5, pad_token_id=0),
+    # attention and feed-forward in parallel off one layer norm; in the second form only the sliding-window layers rotate
+    "CohereForCausalLM": dict(BASE, model_type="cohere", logit_scale=0.25, pad_token_id=0, tie_word_embeddings=True),
+    "Cohere2ForCausalLM": dict(BASE, model_type="cohere2", num_hidden_layers=4, logit_scale=0.25, sliding_window=16, pad_token_id=0, tie_word_embeddings=True,
+                               layer_types=["sliding_attention", "sliding_attention", "sliding_attention", "full_attention"]),
+    "Jais2ForCausalLM": dict(BASE, model_type="jais2", attention_bias=True, mlp_bias=True, pad_token_id=0),
     "MiniMaxM2ForCausalLM": dict(BASE, model_type="minimax_m2", head_dim=16, intermediate_size=48, num_local_experts=8, num_experts_per_tok=2,
                                  pad_token_id=0),
 }

@@ -111,6 +111,35 @@ def test_row_parallel_biases_join_the_sum_once(tmp_path):
     assert got == ref
 
 
+@pytest.mark.timeout(300)
+@pytest.mark.parametrize("arch,extra", [("Starcoder2ForCausalLM", dict(use_bias=True, tie_word_embeddings=False)),
+                                        ("CohereForCausalLM", dict(logit_scale=0.25, tie_word_embeddings=False))])
+def test_layer_norm_families_on_two_ranks(tmp_path, arch, extra):
+    """Mean-and-variance layer norms are not part of the fused reduce + add + norm: the reduction runs first and the norm after it.
+    Starcoder2 adds biases on every projection of an ungated feed-forward; Cohere sums attention and feed-forward before one reduction."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    cfg = dict(CFG, architectures=[arch], **extra)
+    m = build_model(ModelConfig.from_hf_dict(cfg, dtype=torch.float32), "cpu")
+    dummy_init(m, 0, std=0.05)
+    gb = torch.Generator().manual_seed(3)
+    for n, p in m.named_parameters():
+        if n.endswith("bias"):
+            p.data.normal_(0.0, 0.3, generator=gb)
+    save_pretrained(m, cfg, str(tmp_path))
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (9, 33)]
+    sp = SamplingParams(temperature=0.0, max_tokens=8, ignore_eos=True)
+    outs = []
+    for tp in (1, 2):
+        kw = dict(tensor_parallel_size=2, distributed_executor_backend="mp") if tp == 2 else {}
+        llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=128, **kw)
+        outs.append([o.outputs[0].token_ids for o in llm.generate(prompts, sp)])
+        llm.shutdown()
+    assert outs[0] == outs[1]
+
+
 CFG_MOE = dict(architectures=["Qwen3MoeForCausalLM"], hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
                num_key_value_heads=2, head_dim=16, vocab_size=500, max_position_embeddings=256, num_experts=8, num_experts_per_tok=2,
                moe_intermediate_size=32, norm_topk_prob=True)

@@ -366,9 +366,21 @@ class ModelConfig:
                 kw["intermediate_size"] = shared
             if hf.get("position_embedding_type") == "nope":
                 kw["nope_layers"] = tuple(range(kw["num_hidden_layers"]))
-        if arch in ("BambaForCausalLM", "Mamba2ForCausalLM", "GraniteMoeHybridForCausalLM"):
+        if arch == "NemotronHForCausalLM":
+            # every block is norm -> one mixer -> residual; the mixers are Mamba-2, attention without positions, or an ungated feed-forward
+            kinds = list(hf.get("layers_block_type") or hf.get("layer_types") or [])
+            if not kinds and hf.get("hybrid_override_pattern"):
+                kinds = [{"M": "mamba", "*": "attention", "-": "mlp", "E": "moe"}[c] for c in hf["hybrid_override_pattern"]]
+            if not kinds or any(k not in ("mamba", "attention", "mlp") for k in kinds):
+                raise ValueError("NemotronH is served with mamba / attention / mlp blocks (its expert blocks are not)")
+            kw["num_hidden_layers"] = len(kinds)
+            hf = dict(hf, attn_layer_indices=[i for i, t in enumerate(kinds) if t == "attention"], mamba_n_heads=hf.get("mamba_num_heads", 128),
+                      mamba_d_head=hf.get("mamba_head_dim", 64), mamba_d_state=hf.get("ssm_state_size", 128), mamba_proj_bias=hf.get("use_bias", False))
+            kw.update(nope_layers=tuple(range(len(kinds))), mlp_gated=False, hidden_act={"relu2": "relu2", "silu": "silu"}.get(hf.get("mlp_hidden_act", "relu2"), "gelu"),
+                      mlp_bias=bool(hf.get("mlp_bias", False)))
+        if arch in ("BambaForCausalLM", "Mamba2ForCausalLM", "GraniteMoeHybridForCausalLM", "NemotronHForCausalLM"):
             L = kw["num_hidden_layers"]
-            pure = arch == "Mamba2ForCausalLM"
+            pure = arch in ("Mamba2ForCausalLM", "NemotronHForCausalLM")
             expand = hf.get("mamba_expand", hf.get("expand", 2))
             heads = hf.get("mamba_n_heads", hf.get("num_heads", 128))
             d_head = hf.get("mamba_d_head", hf.get("head_dim", "auto"))
@@ -390,7 +402,9 @@ class ModelConfig:
                       mamba_proj_bias=bool(hf.get("mamba_proj_bias", hf.get("use_bias", False))),
                       mamba_time_step_limit=(float(lim[0]), float(lim[1])), mamba_norm_groups=int(hf.get("mamba_norm_groups", groups)),
                       mixer_only_layers=pure, rms_norm_eps=hf.get("rms_norm_eps", hf.get("layer_norm_epsilon", 1e-5)))
-            if pure:
+            if arch == "NemotronHForCausalLM":
+                kw["layer_types"] = [{"mamba": "mamba2", "attention": "full_attention", "mlp": "ffn"}[k] for k in kinds]
+            elif pure:
                 kw.update(tie_word_embeddings=hf.get("tie_word_embeddings", True), intermediate_size=0)
         rp = hf.get("rope_parameters") or hf.get("rope_scaling") or {}
         if rp.get("mrope_section"):

@@ -51,3 +51,18 @@ class PlainMLP(nn.Module):
         else:
             h = F.silu(h)
         return self.down_proj(h)
+
+
+class FeedForwardBlock(PlainMLP):
+    """An ungated feed-forward that is a block of its own (NemotronH: every block is ``h + mixer(norm(h))`` and the mixer is a
+    Mamba-2 layer, an attention layer or this; reference: models/nemotron_h.py ``NemotronHMLPDecoderLayer``). It takes the place of a
+    state-slot mixer in the decoder and declares a one-element state, so the runner and the scheduler need no third kind of layer."""
+
+    def __init__(self, cfg, layer_idx: int, prefix: str):
+        super().__init__(cfg.hidden_size, cfg.intermediate_size, cfg.quant, prefix, cfg.dtype, act=cfg.hidden_act, bias=cfg.mlp_bias)
+
+    def state_shapes(self):
+        return (1, 1), (1, 1, 1)
+
+    def forward(self, x, md=None, state=None):
+        return super().forward(x)

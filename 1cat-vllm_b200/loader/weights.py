@@ -37,7 +37,7 @@ _RENAMES = ((".conv.conv.weight", ".linear_attn.conv_weight"), (".conv.conv.bias
             ("model.embedding_norm.", "model.norm."), (".self_attn.out_proj.", ".self_attn.o_proj."), (".q_layernorm.weight", ".q_norm"),
             (".k_layernorm.weight", ".k_norm"), (".mlp.c_fc.", ".mlp.up_proj."), (".mlp.c_proj.", ".mlp.down_proj."),
             (".mamba.", ".linear_attn."), (".mixer.", ".linear_attn."), (".feed_forward.", ".mlp."), (".pre_ff_layernorm.", ".post_attention_layernorm."),
-            ("model.final_layernorm.", "model.norm."), ("backbone.embeddings.", "model.embed_tokens."), ("backbone.norm_f.", "model.norm."),
+            ("model.final_layernorm.", "model.norm."), ("backbone.embeddings.", "model.embed_tokens."), ("backbone.embedding.", "model.embed_tokens."), ("backbone.norm_f.", "model.norm."),
             ("backbone.layers.", "model.layers."), (".linear_attn.conv1d.bias", ".linear_attn.conv_bias"),
             (".q_norm.weight", ".q_norm"), (".k_norm.weight", ".k_norm"), (".query_layernorm.weight", ".q_norm"), (".key_layernorm.weight", ".k_norm"), (".linear_attn.conv1d.weight", ".linear_attn.conv_weight"),
             (".linear_attn.norm.weight", ".linear_attn.norm_weight"), (".mlp.gate.moe_statics.e_score_correction_bias", ".mlp.e_score_correction_bias"),
@@ -71,6 +71,7 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
     interleaved = cfg is not None and cfg.rope_interleaved
     mixer_only = cfg is not None and getattr(cfg, "mixer_only_layers", False)
     vault = cfg is not None and cfg.architecture.startswith("VaultGemma")
+    nemotron_h = cfg is not None and cfg.architecture.startswith("NemotronH")
     loaded = set()
     for name, w in weights:
         if name.startswith("language_model."):
@@ -84,6 +85,10 @@ def load_weights(model: nn.Module, weights: Iterable[tuple[str, torch.Tensor]]) 
             continue
         if "rotary_emb.inv_freq" in name:
             continue
+        if nemotron_h and ".mixer." in name:   # one name for every kind of block: attention blocks keep their projections under self_attn
+            base = name.split(".mixer.")[0].replace("backbone.layers.", "model.layers.")
+            if base + ".self_attn" in mods:
+                name = name.replace(".mixer.", ".self_attn.")
         for theirs, ours in _RENAMES:
             if theirs in name:
                 name = name.replace(theirs, ours)

@@ -11,7 +11,7 @@ _REGISTRY = {
     "SmolLM3ForCausalLM": "dense", "Olmo2ForCausalLM": "dense", "Olmo3ForCausalLM": "dense", "OlmoeForCausalLM": "moe",
     "GptOssForCausalLM": "moe", "GraniteMoeForCausalLM": "moe", "GraniteMoeSharedForCausalLM": "moe", "Ernie4_5_MoeForCausalLM": "moe", "HunYuanDenseV1ForCausalLM": "dense", "HeliumForCausalLM": "dense", "CwmForCausalLM": "dense",
     "Ernie4_5ForCausalLM": "dense", "Exaone4ForCausalLM": "dense", "MinistralForCausalLM": "dense", "Dots1ForCausalLM": "moe",
-    "Qwen3MoeForCausalLM": "moe", "MiniMaxM2ForCausalLM": "moe", "SolarOpenForCausalLM": "moe", "Glm4MoeLiteForCausalLM": "mla_moe", "ExaoneMoeForCausalLM": "moe", "FlexOlmoForCausalLM": "moe", "Ministral3ForCausalLM": "dense", "ArceeForCausalLM": "dense", "CohereForCausalLM": "dense", "Cohere2ForCausalLM": "dense", "OlmoForCausalLM": "dense", "StableLmForCausalLM": "dense", "Starcoder2ForCausalLM": "dense", "NemotronForCausalLM": "dense", "Jais2ForCausalLM": "dense", "VaultGemmaForCausalLM": "dense", "HunYuanMoEV1ForCausalLM": "moe", "Qwen2MoeForCausalLM": "moe", "MixtralForCausalLM": "moe",
+    "Qwen3MoeForCausalLM": "moe", "MiniMaxM2ForCausalLM": "moe", "SolarOpenForCausalLM": "moe", "Glm4MoeLiteForCausalLM": "mla_moe", "ExaoneMoeForCausalLM": "moe", "FlexOlmoForCausalLM": "moe", "Ministral3ForCausalLM": "dense", "ArceeForCausalLM": "dense", "NemotronHForCausalLM": "hybrid", "CohereForCausalLM": "dense", "Cohere2ForCausalLM": "dense", "OlmoForCausalLM": "dense", "StableLmForCausalLM": "dense", "Starcoder2ForCausalLM": "dense", "NemotronForCausalLM": "dense", "Jais2ForCausalLM": "dense", "VaultGemmaForCausalLM": "dense", "HunYuanMoEV1ForCausalLM": "moe", "Qwen2MoeForCausalLM": "moe", "MixtralForCausalLM": "moe",
     "Qwen3NextForCausalLM": "hybrid", "Qwen3_5ForCausalLM": "hybrid", "Qwen3_5ForConditionalGeneration": "hybrid",
     "Qwen3_5MoeForCausalLM": "hybrid", "Qwen3_5MoeForConditionalGeneration": "hybrid",
     "BambaForCausalLM": "hybrid", "Lfm2ForCausalLM": "hybrid", "Lfm2MoeForCausalLM": "hybrid", "JambaForCausalLM": "hybrid", "GraniteMoeHybridForCausalLM": "hybrid", "Mamba2ForCausalLM": "hybrid", "MambaForCausalLM": "hybrid", "FalconMambaForCausalLM": "hybrid",

@@ -41,8 +41,10 @@ class DecoderLayer(nn.Module):
             self.self_attn = layer_class("MLAAttention", MLAAttention)(cfg, idx, prefix + ".self_attn", device)
         elif self.kind == "linear_attention":
             self.linear_attn = layer_class("GatedDeltaNet", GatedDeltaNet)(cfg, idx, prefix + ".linear_attn")
-        elif self.kind in ("mamba2", "mamba1", "short_conv"):
-            if self.kind == "mamba2":
+        elif self.kind in ("mamba2", "mamba1", "short_conv", "ffn"):
+            if self.kind == "ffn":
+                from onecat_vllm.layers.mlp import FeedForwardBlock as Mixer
+            elif self.kind == "mamba2":
                 from onecat_vllm.layers.mamba2 import Mamba2Mixer as Mixer
             elif self.kind == "mamba1":
                 from onecat_vllm.layers.mamba1 import Mamba1Mixer as Mixer

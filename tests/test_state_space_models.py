@@ -107,6 +107,92 @@ def test_mamba2_matches_hugging_face(tmp_path):
     assert got == want
 
 
+def test_nemotron_h_matches_hugging_face(tmp_path):
+    """NemotronH: each block is one mixer. The installed transformers builds Mamba-2, attention (without positions) and expert blocks;
+    the feed-forward blocks of the dense checkpoints are covered by the test below."""
+    tr = pytest.importorskip("transformers")
+    try:
+        from transformers import NemotronHConfig, NemotronHForCausalLM
+    except Exception as e:  # pragma: no cover
+        pytest.skip(f"transformers has no NemotronH: {e}")
+    cfg = NemotronHConfig(vocab_size=300, hidden_size=64, layers_block_type=["mamba", "attention", "mamba", "mamba", "attention"], num_attention_heads=4,
+                          num_key_value_heads=2, head_dim=16, intermediate_size=128, ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=16,
+                          n_groups=2, conv_kernel=4, chunk_size=16, max_position_embeddings=256, tie_word_embeddings=False, pad_token_id=0,
+                          bos_token_id=1, eos_token_id=2, use_mamba_kernels=False)
+    torch.manual_seed(0)
+    hf = NemotronHForCausalLM(cfg).float().eval()
+    for n, p in hf.named_parameters():
+        if "norm" not in n and "A_log" not in n and "dt_bias" not in n and n.rsplit(".", 1)[-1] != "D":
+            torch.nn.init.normal_(p, std=0.15)
+    _save(hf, tmp_path, "NemotronHForCausalLM")
+    prompts = _prompts(300)
+    llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=48)
+    got = [o.outputs[0].token_ids for o in llm.generate(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))]
+    llm.shutdown()
+    # this random model's logits are flat (top-two gaps of 2e-4 occur, which fp32 rounding decides either way), so the check follows
+    # the engine's own path: at every step its token must be Hugging Face's arg-max, or within 1e-3 of it in log-probability
+    exact = 0
+    for p, toks in zip(prompts, got):
+        with torch.no_grad():
+            lp = torch.log_softmax(hf(torch.tensor([p + toks])).logits[0, len(p) - 1: -1].float(), -1)
+        for t, tok in enumerate(toks):
+            assert lp[t, tok].item() >= lp[t].max().item() - 1e-3, (len(p), t, tok, int(lp[t].argmax()))
+            exact += int(lp[t].argmax()) == tok
+    assert exact >= 33     # of 36 steps
+
+
+def test_nemotron_h_feed_forward_blocks(tmp_path):
+    """The dense NemotronH pattern (M = Mamba-2, - = feed-forward, * = attention): a checkpoint under the family's own names loads
+    completely, and the engine's tokens equal a plain forward over the same modules, whole prompt at once, with chunked prefill."""
+    from onecat_vllm.config import ModelConfig
+    from onecat_vllm.loader.weights import dummy_init, save_pretrained
+    from onecat_vllm.models import build_model
+    cfg = dict(architectures=["NemotronHForCausalLM"], vocab_size=300, hidden_size=64, hybrid_override_pattern="M-*-M-", num_attention_heads=4,
+               num_key_value_heads=2, head_dim=16, intermediate_size=128, ssm_state_size=16, mamba_num_heads=8, mamba_head_dim=16, n_groups=2,
+               conv_kernel=4, chunk_size=16, max_position_embeddings=256, tie_word_embeddings=False, mlp_hidden_act="relu2")
+    mc = ModelConfig.from_hf_dict(cfg, dtype=torch.float32)
+    assert [mc.layer_type(i) for i in range(6)] == ["mamba2", "ffn", "full_attention", "ffn", "mamba2", "ffn"]
+    m = build_model(mc, "cpu")
+    dummy_init(m, 0, std=0.15)
+    save_pretrained(m, cfg, str(tmp_path))
+    prompts = _prompts(300, (9, 70))
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    outs = []
+    for budget in (8192, 32):
+        llm = LLM(model=str(tmp_path), device="cpu", dtype="float32", max_model_len=256, max_num_batched_tokens=budget)
+        outs.append([o.outputs[0].token_ids for o in llm.generate(prompts, sp)])
+        llm.shutdown()
+    assert outs[0] == outs[1]
+    # the first generated token against a cache-free forward written out here: h += mixer(norm(h)) per block
+    import torch.nn.functional as F
+    layers = m.model.layers
+    for p, got in zip(prompts, outs[0]):
+        T = len(p)
+        h = m.model.embed_tokens(torch.tensor(p))
+        for i, layer in enumerate(layers):
+            x = layer.input_layernorm(h, None)[0]
+            kind = mc.layer_type(i)
+            if kind == "ffn":
+                y = layer.linear_attn.down_proj(F.relu(layer.linear_attn.up_proj(x)) ** 2)
+            elif kind == "full_attention":
+                a = layer.self_attn
+                qkv = a.qkv_proj(x)
+                q, k, v = qkv.split([a.Hq * a.D, a.Hkv * a.D, a.Hkv * a.D], -1)
+                q, k, v = (t.view(T, -1, a.D).transpose(0, 1) for t in (q, k, v))
+                o = F.scaled_dot_product_attention(q[None], k[None], v[None], is_causal=True, enable_gqa=True)[0]
+                y = a.o_proj(o.transpose(0, 1).reshape(T, -1))
+            else:
+                mx = layer.linear_attn
+                from types import SimpleNamespace
+                md = SimpleNamespace(query_start_loc=torch.tensor([0, T]), state_slots=torch.tensor([0]), has_initial_state=torch.tensor([False]),
+                                     gdn_record=None)
+                (cd, kw), (hh, pp, nn_) = mx.state_shapes()
+                y = mx(x, md, (torch.zeros(1, cd, kw), torch.zeros(1, hh, pp, nn_)))
+            h = h + y
+        logits = m.compute_logits(m.model.norm(h, None)[0][-1:])
+        assert int(logits[0, :300].argmax()) == got[0]
+
+
 @pytest.mark.parametrize("falcon", [False, True])
 def test_mamba1_matches_hugging_face(tmp_path, falcon):
     tr = pytest.importorskip("transformers")
